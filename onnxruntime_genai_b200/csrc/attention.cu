@@ -1,0 +1,356 @@
+// Paged variable-length GQA attention (prefill chunks, decode and speculative-verify rows in one
+// launch) over a block-table KV cache, with causal masking, sliding window, attention sinks,
+// soft-capping and split-KV.
+//
+// Semantics follow the PagedAttention / GroupQueryAttention contrib ops named by the reference's
+// builder (src/python/py/models/builders/base.py:3315-3386, 3484-3536): the packed query holds this
+// step's tokens of every request back to back (cumulative_sequence_lengths), the cache already
+// holds past_sequence_lengths[b] tokens plus this step's tokens (appended by the RoPE kernel),
+// key/value caches are [num_blocks * block_size, kv_heads, head_dim], block_table[b, c] names the
+// block that holds positions [c*block_size, (c+1)*block_size); local_window_size > 0 restricts a
+// query at position p to keys in (p - window, p]; `sinks` adds one learned logit per query head
+// to the softmax denominator; softcap applies cap * tanh(x / cap) to the scaled scores.
+//
+// Work decomposition: one CTA = (request, kv head, tile of 64 query rows, kv split) where a
+// "row" is one (query token, query head of the group) pair, so a decode step of a 4:1 GQA model
+// keeps its 4 heads in one MMA tile and reads each K/V row once.  K/V tiles of 64 keys are
+// gathered through the block table with 16-byte cp.async copies into XOR-swizzled shared memory,
+// double buffered; QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
+// tile's M is at most a few rows in decode, far below the 64-row minimum of tcgen05.mma, and
+// the kernel is bound by the KV stream, not by tensor throughput.)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ogb {
+
+constexpr int ATT_BM = 64;   // query rows per CTA (4 warps x 16)
+constexpr int ATT_BN = 64;   // keys per tile
+constexpr int ATT_THREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+  const __nv_bfloat16* q; int q_stride;
+  const __nv_bfloat16* k_cache; const __nv_bfloat16* v_cache;
+  const int32_t* cu_seqlens; const int32_t* past_lens;
+  const int32_t* block_table; int table_cols; int block_size;
+  __nv_bfloat16* out; int out_stride;
+  float* part_o; float* part_ml;
+  const float* sinks;
+  float scale, softcap;
+  int window, B, Hq, Hkv, splits, total_rows;
+};
+
+template <int SROW>
+__device__ __forceinline__ int swz(int row, int chunk) {  // element offset of a 16-byte chunk in a swizzled tile
+  return row * SROW + ((((chunk & ~7) | ((chunk ^ row) & 7))) << 3);
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnParams p) {
+  constexpr int SROW = ((D + 63) / 64) * 64;
+  constexpr int CHUNKS = D / 8;     // 16-byte chunks per row
+  constexpr int KSTEPS = D / 16;    // k-steps of QK^T
+  constexpr int DTILES = D / 8;     // n-tiles of PV
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* sK = sQ + ATT_BM * SROW;            // [2][BN][SROW]
+  __nv_bfloat16* sV = sK + 2 * ATT_BN * SROW;        // [2][BN][SROW]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int kvh = blockIdx.y;
+  const int b = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const int G = p.Hq / p.Hkv;
+  const int tok0 = p.cu_seqlens[b];
+  const int q_len = p.cu_seqlens[b + 1] - tok0;
+  const int rows = q_len * G;
+  const int row0 = blockIdx.x * ATT_BM;
+  if (row0 >= rows) return;
+  const int past = p.past_lens[b];
+  const int kv_total = past + q_len;
+  const int32_t* table = p.block_table + size_t(b) * p.table_cols;
+
+  // Key range needed by this tile of rows, then the part of it owned by this split.
+  const int last_tq = min(q_len - 1, (row0 + ATT_BM - 1) / G);
+  int kv_hi = past + last_tq + 1;
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, past + row0 / G - p.window + 1);
+  if (p.splits > 1) {
+    const int tiles = (kv_total + ATT_BN - 1) / ATT_BN;
+    const int per = (tiles + p.splits - 1) / p.splits * ATT_BN;
+    kv_lo = max(kv_lo, split * per);
+    kv_hi = min(kv_hi, (split + 1) * per);
+  }
+  const int tile_begin = kv_lo / ATT_BN;
+  const int tile_end = kv_hi > kv_lo ? (kv_hi + ATT_BN - 1) / ATT_BN : tile_begin;
+  const int n_tiles = tile_end - tile_begin;
+
+  auto load_kv = [&](int tile, int buf) {
+    const int base = tile * ATT_BN;
+    __nv_bfloat16* dk = sK + buf * ATT_BN * SROW;
+    __nv_bfloat16* dv = sV + buf * ATT_BN * SROW;
+    for (int c = tid; c < ATT_BN * CHUNKS; c += ATT_THREADS) {
+      const int key = c / CHUNKS, ch = c % CHUNKS;
+      const int j = base + key;
+      const bool ok = j < kv_hi && j >= 0;
+      size_t off = 0;
+      if (ok) {
+        const int blk = table[j / p.block_size];
+        off = ((size_t(blk) * p.block_size + j % p.block_size) * p.Hkv + kvh) * D + ch * 8;
+      }
+      cp_async16(dk + swz<SROW>(key, ch), p.k_cache + off, ok);
+      cp_async16(dv + swz<SROW>(key, ch), p.v_cache + off, ok);
+    }
+  };
+
+  // Q tile (zero rows beyond the request's rows).
+  for (int c = tid; c < ATT_BM * CHUNKS; c += ATT_THREADS) {
+    const int r = c / CHUNKS, ch = c % CHUNKS;
+    const int gr = row0 + r;
+    const bool ok = gr < rows;
+    const __nv_bfloat16* src = p.q;
+    if (ok) src = p.q + size_t(tok0 + gr / G) * p.q_stride + size_t(kvh * G + gr % G) * D + ch * 8;
+    cp_async16(sQ + swz<SROW>(r, ch), src, ok);
+  }
+  if (n_tiles > 0) load_kv(tile_begin, 0);
+  cp_async_commit();
+
+  const bool warp_active = row0 + warp * 16 < rows;
+  // Per-thread rows: r_lo = warp*16 + g, r_hi = r_lo + 8.
+  const int gr_lo = row0 + warp * 16 + g, gr_hi = gr_lo + 8;
+  const int qpos_lo = past + gr_lo / G, qpos_hi = past + gr_hi / G;
+  const bool valid_lo = gr_lo < rows, valid_hi = gr_hi < rows;
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  uint32_t qf[KSTEPS][4];
+  const float sc2 = p.scale * LOG2E;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    if (it + 1 < n_tiles) load_kv(tile_begin + it + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (it == 0 && warp_active) {
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(qf[ks], sQ + swz<SROW>(r, ks * 2 + (lane >> 4)));
+      }
+    }
+    if (warp_active) {
+      const __nv_bfloat16* tk = sK + buf * ATT_BN * SROW;
+      const __nv_bfloat16* tv = sV + buf * ATT_BN * SROW;
+      float s[ATT_BN / 8][4];
+#pragma unroll
+      for (int i = 0; i < ATT_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < ATT_BN / 16; ++np) {
+          uint32_t kb[4];
+          const int key = (np * 2 + (lane >> 4)) * 8 + (lane & 7);
+          ldmatrix_x4(kb, tk + swz<SROW>(key, ks * 2 + ((lane >> 3) & 1)));
+          mma_bf16_16816(s[np * 2], qf[ks], kb[0], kb[1]);
+          mma_bf16_16816(s[np * 2 + 1], qf[ks], kb[2], kb[3]);
+        }
+      }
+      // scale, softcap, mask, running max
+      const int jbase = (tile_begin + it) * ATT_BN;
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = jbase + nt * 8 + t4 * 2 + (e & 1);
+          const bool hi = e >= 2;
+          const int qpos = hi ? qpos_hi : qpos_lo;
+          bool ok = (hi ? valid_hi : valid_lo) && j >= kv_lo && j < kv_hi && j <= qpos;
+          if (p.window > 0) ok = ok && j > qpos - p.window;
+          float x = s[nt][e];
+          if (p.softcap > 0.f) x = p.softcap * tanhf(x * p.scale / p.softcap) * LOG2E;
+          else x *= sc2;
+          x = ok ? x : -INFINITY;
+          s[nt][e] = x;
+          if (hi) mx_hi = fmaxf(mx_hi, x); else mx_lo = fmaxf(mx_lo, x);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float a_lo = exp2f(m_lo - ms_lo), a_hi = exp2f(m_hi - ms_hi);  // m_* = -inf -> 0
+      m_lo = mn_lo; m_hi = mn_hi;
+      l_lo *= a_lo; l_hi *= a_hi;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
+#pragma unroll
+      for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+        s[nt][0] = exp2f(s[nt][0] - ms_lo); s[nt][1] = exp2f(s[nt][1] - ms_lo);
+        s[nt][2] = exp2f(s[nt][2] - ms_hi); s[nt][3] = exp2f(s[nt][3] - ms_hi);
+        l_lo += s[nt][0] + s[nt][1];
+        l_hi += s[nt][2] + s[nt][3];
+      }
+      // O += P V
+#pragma unroll
+      for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+        uint32_t pa[4];
+        pa[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+          uint32_t vb[4];
+          const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4_trans(vb, tv + swz<SROW>(key, dp * 2 + (lane >> 4)));
+          mma_bf16_16816(o[dp * 2], pa, vb[0], vb[1]);
+          mma_bf16_16816(o[dp * 2 + 1], pa, vb[2], vb[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  if (!warp_active) return;
+
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int gr = half ? gr_hi : gr_lo;
+    if (gr >= rows) continue;
+    const int tq = gr / G, hq = kvh * G + gr % G;
+    float m = half ? m_hi : m_lo, l = half ? l_hi : l_lo;
+    if (p.splits > 1) {
+      const size_t grow = size_t(tok0 + tq) * p.Hq + hq;
+      float* po = p.part_o + (size_t(split) * p.total_rows + grow) * D;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i)
+        *reinterpret_cast<float2*>(po + i * 8 + t4 * 2) = make_float2(o[i][half * 2], o[i][half * 2 + 1]);
+      if (t4 == 0) {
+        float* pm = p.part_ml + (size_t(split) * p.total_rows + grow) * 2;
+        pm[0] = m; pm[1] = l;
+      }
+    } else {
+      float scale_o = 1.f;
+      if (p.sinks) {
+        const float sk = p.sinks[hq] * LOG2E;
+        const float mm = fmaxf(m, sk);
+        scale_o = exp2f(m - mm);
+        l = l * scale_o + exp2f(sk - mm);
+      }
+      const float inv = l > 0.f ? scale_o / l : 0.f;
+      __nv_bfloat16* po = p.out + size_t(tok0 + tq) * p.out_stride + size_t(hq) * D;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i)
+        *reinterpret_cast<uint32_t*>(po + i * 8 + t4 * 2) = pack_bf16x2(o[i][half * 2] * inv, o[i][half * 2 + 1] * inv);
+    }
+  }
+}
+
+// One warp per (token, head) row: merges the split partials (and the sink) into the bf16 output.
+template <int D>
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int out_stride,
+                                         int total_rows, int Hq, int splits) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= total_rows) return;
+  const int tok = row / Hq, hq = row % Hq;
+  float M = sinks ? sinks[hq] * LOG2E : -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(size_t(s) * total_rows + row) * 2]);
+  float L = sinks ? exp2f(sinks[hq] * LOG2E - M) : 0.f;
+  constexpr int PER = (D + 31) / 32;
+  float acc[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* ml = part_ml + (size_t(s) * total_rows + row) * 2;
+    const float m = ml[0];
+    if (m == -INFINITY) continue;
+    const float w = exp2f(m - M);
+    L += w * ml[1];
+    const float* po = part_o + (size_t(s) * total_rows + row) * D;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) acc[i] += w * po[d];
+    }
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  __nv_bfloat16* o = out + size_t(tok) * out_stride + size_t(hq) * D;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) o[d] = f2bf(acc[i] * inv);
+  }
+}
+
+template <int D>
+static int LaunchAttention(const AttnParams& p, int max_q_len, cudaStream_t stream) {
+  constexpr int SROW = ((D + 63) / 64) * 64;
+  constexpr int SMEM = (ATT_BM + 4 * ATT_BN) * SROW * 2;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(paged_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  const int G = p.Hq / p.Hkv;
+  const int q_tiles = (max_q_len * G + ATT_BM - 1) / ATT_BM;
+  dim3 grid(q_tiles, p.Hkv, p.B * p.splits);
+  paged_attention_kernel<D><<<grid, ATT_THREADS, SMEM, stream>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  if (p.splits > 1) {
+    const int warps = 4;
+    attention_combine_kernel<D><<<(p.total_rows + warps - 1) / warps, warps * 32, 0, stream>>>(
+        p.part_o, p.part_ml, p.sinks, p.out, p.out_stride, p.total_rows, p.Hq, p.splits);
+    if (cudaGetLastError() != cudaSuccess) return -4;
+  }
+  return 0;
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+// Bytes of fp32 scratch needed for `splits` > 1.
+OGB_API long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, int splits) {
+  if (splits <= 1) return 0;
+  return (long long)splits * total_tokens * Hq * (D + 2) * 4;
+}
+
+OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                                const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                                int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                                int max_q_len, int Hq, int Hkv, int D, int splits, void* scratch, long long scratch_bytes,
+                                void* stream_) {
+  if (B <= 0 || total_tokens <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv || (q_stride % 8) || (out_stride % 2)) return -1;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && ogb_attention_scratch_bytes(total_tokens, Hq, D, splits) > scratch_bytes) return -2;
+  AttnParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.block_table = block_table; p.table_cols = table_cols;
+  p.block_size = block_size; p.out = static_cast<__nv_bfloat16*>(out); p.out_stride = out_stride;
+  p.total_rows = total_tokens * Hq;
+  p.part_o = static_cast<float*>(scratch);
+  p.part_ml = p.part_o ? p.part_o + size_t(splits) * p.total_rows * D : nullptr;
+  p.sinks = sinks; p.scale = scale; p.softcap = softcap; p.window = window;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.splits = splits;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  switch (D) {
+    case 64: return LaunchAttention<64>(p, max_q_len, stream);
+    case 96: return LaunchAttention<96>(p, max_q_len, stream);
+    case 128: return LaunchAttention<128>(p, max_q_len, stream);
+  }
+  return -5;
+}

@@ -1,0 +1,304 @@
+// Bandwidth-bound per-token kernels: embedding gather, RMSNorm / LayerNorm with fused residual add,
+// RoPE + (optional per-head q/k RMSNorm) + paged KV-cache append, SiLU*mul, logits edits.
+//
+// Reference semantics: SkipSimplifiedLayerNormalization returns both the normalised tensor and the
+// residual sum (src/python/py/models/builders/base.py:2342-2403); RotaryEmbedding uses
+// cos/sin caches of shape [ctx, rot/2] with an interleaved flag (base.py:2565-2637); PagedAttention
+// appends the new K/V rows at slots derived from the block table (base.py:3484-3536).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ogb {
+
+// ------------------------------------------------------------------------------------ embedding
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const uint4* __restrict__ table, uint4* __restrict__ out,
+                                 int vec_per_row, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const uint4* src = table + size_t(id) * vec_per_row;
+  uint4* dst = out + size_t(t) * vec_per_row;
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
+    uint4 v = __ldg(src + i);
+    if (scale != 1.f) {
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 f = unpack_bf16x2(w[k]);
+        w[k] = pack_bf16x2(f.x * scale, f.y * scale);
+      }
+    }
+    dst[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------------ norm
+// One CTA per row. h = x (+ residual_in); residual_out = h (optional); out = norm(h) * w (+ b).
+// The row is kept in registers (up to 2 vectors of 8 bf16 per thread, hidden size <= 16384).
+template <bool LAYERNORM>
+__global__ void __launch_bounds__(1024) norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in,
+                                                    uint4* __restrict__ res_out, const uint4* __restrict__ weight,
+                                                    const uint4* __restrict__ bias, uint4* __restrict__ out, int H, float eps) {
+  constexpr int MAXV = 2;
+  const int row = blockIdx.x, nvec = H / 8;
+  const uint4* xr = x + size_t(row) * nvec;
+  float v[MAXV][8];
+  float sum = 0.f, sumsq = 0.f;
+  int cnt = 0;
+  for (int i = threadIdx.x; i < nvec && cnt < MAXV; i += blockDim.x, ++cnt) {
+    uint4 a = xr[i];
+    const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (res_in) r = res_in[size_t(row) * nvec + i];
+    const uint32_t* rw = reinterpret_cast<const uint32_t*>(&r);
+    uint4 hs;
+    uint32_t* hw = reinterpret_cast<uint32_t*>(&hs);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 fa = unpack_bf16x2(aw[k]), fr = unpack_bf16x2(rw[k]);
+      float h0 = fa.x + fr.x, h1 = fa.y + fr.y;
+      hw[k] = pack_bf16x2(h0, h1);
+      if (res_in) {  // the residual stream is stored in bf16: normalise what is stored
+        float2 q = unpack_bf16x2(hw[k]);
+        h0 = q.x; h1 = q.y;
+      }
+      v[cnt][2 * k] = h0; v[cnt][2 * k + 1] = h1;
+      sum += h0 + h1;
+      sumsq += h0 * h0 + h1 * h1;
+    }
+    if (res_out) res_out[size_t(row) * nvec + i] = hs;
+  }
+  __shared__ float red[2][32];
+  sum = warp_sum(sum);
+  sumsq = warp_sum(sumsq);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) { red[0][warp] = sum; red[1][warp] = sumsq; }
+  __syncthreads();
+  if (warp == 0) {
+    float a = lane < nw ? red[0][lane] : 0.f, b = lane < nw ? red[1][lane] : 0.f;
+    a = warp_sum(a); b = warp_sum(b);
+    if (lane == 0) { red[0][0] = a; red[1][0] = b; }
+  }
+  __syncthreads();
+  const float mean = LAYERNORM ? red[0][0] / H : 0.f;
+  const float var = LAYERNORM ? fmaxf(red[1][0] / H - mean * mean, 0.f) : red[1][0] / H;
+  const float inv = rsqrtf(var + eps);
+  cnt = 0;
+  for (int i = threadIdx.x; i < nvec && cnt < MAXV; i += blockDim.x, ++cnt) {
+    uint4 w = weight[i];
+    const uint32_t* ww = reinterpret_cast<const uint32_t*>(&w);
+    uint4 b = make_uint4(0, 0, 0, 0);
+    if (bias) b = bias[i];
+    const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 fw = unpack_bf16x2(ww[k]), fb = unpack_bf16x2(bw[k]);
+      ow[k] = pack_bf16x2((v[cnt][2 * k] - mean) * inv * fw.x + fb.x, (v[cnt][2 * k + 1] - mean) * inv * fw.y + fb.y);
+    }
+    out[size_t(row) * nvec + i] = o;
+  }
+}
+
+// ------------------------------------------------------------------------------------ RoPE + KV append
+// One warp per (token, head) of the packed [T, (Hq + 2*Hkv) * D] activation.  Q heads are rotated in
+// place; K heads are rotated and written to the cache slot; V heads are copied to the cache slot.
+struct RopeParams {
+  __nv_bfloat16* qkv;
+  int qkv_stride;            // elements between tokens
+  const int32_t* positions;  // [T]
+  const int32_t* slots;      // [T] cache slot (block * block_size + offset); < 0 skips the append
+  const float* cos_cache;    // [ctx, rot/2]
+  const float* sin_cache;
+  __nv_bfloat16* k_cache;    // [slots, Hkv, D]
+  __nv_bfloat16* v_cache;
+  const __nv_bfloat16* q_norm_w;  // optional [D]
+  const __nv_bfloat16* k_norm_w;  // optional [D]
+  float norm_eps;
+  int T, Hq, Hkv, D, rot, interleaved, max_pos;
+};
+
+__global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
+  __shared__ float buf[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.Hq + 2 * p.Hkv;
+  const long item = long(blockIdx.x) * 8 + warp;
+  if (item >= long(p.T) * heads) return;
+  const int t = int(item / heads), h = int(item % heads);
+  __nv_bfloat16* src = p.qkv + size_t(t) * p.qkv_stride + size_t(h) * p.D;
+  float* v = buf[warp];
+  const bool is_q = h < p.Hq, is_k = !is_q && h < p.Hq + p.Hkv;
+  float ss = 0.f;
+  for (int e = lane; e < p.D; e += 32) { float x = bf2f(src[e]); v[e] = x; ss += x * x; }
+  const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+  if (nw) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / p.D + p.norm_eps);
+    __syncwarp();
+    for (int e = lane; e < p.D; e += 32) v[e] = bf2f(f2bf(v[e] * inv * bf2f(nw[e])));
+  }
+  __syncwarp();
+  const int slot = p.slots ? p.slots[t] : -1;
+  __nv_bfloat16* dst;
+  if (is_q) dst = src;
+  else {
+    if (slot < 0) return;
+    const int kvh = is_k ? h - p.Hq : h - p.Hq - p.Hkv;
+    dst = (is_k ? p.k_cache : p.v_cache) + (size_t(slot) * p.Hkv + kvh) * p.D;
+  }
+  if ((is_q || is_k) && p.rot > 0) {
+    int pos = p.positions[t];
+    pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+    const int half = p.rot / 2;
+    const float* cs = p.cos_cache + size_t(pos) * half;
+    const float* sn = p.sin_cache + size_t(pos) * half;
+    for (int i = lane; i < half; i += 32) {
+      const int a = p.interleaved ? 2 * i : i, b = p.interleaved ? 2 * i + 1 : i + half;
+      const float x1 = v[a], x2 = v[b], c = cs[i], s = sn[i];
+      dst[a] = f2bf(x1 * c - x2 * s);
+      dst[b] = f2bf(x2 * c + x1 * s);
+    }
+    for (int e = p.rot + lane; e < p.D; e += 32) dst[e] = f2bf(v[e]);
+  } else if (!is_q || nw) {
+    for (int e = lane; e < p.D; e += 32) dst[e] = f2bf(v[e]);
+  }
+}
+
+// ------------------------------------------------------------------------------------ SiLU * mul
+// out[t, i] = act(x[t, i]) * x[t, I + i];  act 0 = SiLU, 1 = GELU(tanh)
+__global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int T, int I, int act) {
+  const long n = long(T) * I;
+  for (long idx = long(blockIdx.x) * blockDim.x + threadIdx.x; idx < n; idx += long(gridDim.x) * blockDim.x) {
+    const long t = idx / I, i = idx % I;
+    const float g = bf2f(x[t * 2 * I + i]), u = bf2f(x[t * 2 * I + I + i]);
+    float a;
+    if (act == 0) a = g / (1.f + __expf(-g));
+    else a = 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
+    out[idx] = f2bf(a * u);
+  }
+}
+
+// ------------------------------------------------------------------------------------ logits edits
+// A sparse list of (row, token) edits: op 0 sets the logit to -FLT_MAX (min_length / no-repeat-ngram /
+// banned tokens), op 1 applies the repetition penalty (x < 0 ? x * v : x / v).  O(list) instead of
+// the O(vocab * length) scan the reference does on the GPU (src/cuda/search_cuda.cu:160-189).
+__global__ void logits_edit_kernel(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,
+                                   const float* values, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int tok = tokens[i];
+  if (tok < 0 || tok >= vocab) return;
+  float* p = logits + size_t(rows[i]) * vocab + tok;
+  if (ops[i] == 0) *p = -3.402823466e+38f;
+  else { const float x = *p, v = values[i]; *p = x < 0.f ? x * v : x / v; }
+}
+
+// logits[row, v] = -FLT_MAX where bit v of the row's mask is clear (grammar constraints).
+// mask_rows maps a logits row to a mask row (-1 = unconstrained).
+__global__ void logits_bitmask_kernel(float* logits, int vocab, const uint32_t* mask, const int32_t* mask_rows, int words) {
+  const int row = blockIdx.y;
+  const int mr = mask_rows ? mask_rows[row] : row;
+  if (mr < 0) return;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= vocab) return;
+  if (!((mask[size_t(mr) * words + (v >> 5)] >> (v & 31)) & 1u)) logits[size_t(row) * vocab + v] = -3.402823466e+38f;
+}
+
+// Cast rows of bf16 to fp32 (logits hand-off when a model computes bf16 logits).
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, long n) {
+  for (long i = long(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += long(gridDim.x) * blockDim.x) out[i] = bf2f(in[i]);
+}
+
+// Gather rows: out[i, :] = in[rows[i], :] (16-byte vectors).
+__global__ void gather_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ rows, uint4* __restrict__ out, int vec_per_row) {
+  const int r = rows[blockIdx.x];
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[size_t(blockIdx.x) * vec_per_row + i] = in[size_t(r) * vec_per_row + i];
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+OGB_API int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8) return -1;
+  embedding_kernel<<<T, min(256, H / 8), 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), H / 8, vocab, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias,
+                     void* out, int rows, int H, float eps, int layernorm, void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 || H / 8 > 8 * 1024) return -1;
+  const int nvec = H / 8;
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (nvec > threads * 2) return -1;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (layernorm)
+    norm_kernel<true><<<rows, threads, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
+                                               static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight),
+                                               static_cast<const uint4*>(bias), static_cast<uint4*>(out), H, eps);
+  else
+    norm_kernel<false><<<rows, threads, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
+                                                static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight),
+                                                static_cast<const uint4*>(bias), static_cast<uint4*>(out), H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
+                               const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
+                               float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream) {
+  if (T <= 0) return 0;
+  if (D > 256 || rot > D || (rot & 1)) return -1;
+  RopeParams p;
+  p.qkv = static_cast<__nv_bfloat16*>(qkv); p.qkv_stride = qkv_stride; p.positions = positions; p.slots = slots;
+  p.cos_cache = cos_cache; p.sin_cache = sin_cache;
+  p.k_cache = static_cast<__nv_bfloat16*>(k_cache); p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+  p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w); p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
+  p.norm_eps = norm_eps; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rot = rot; p.interleaved = interleaved; p.max_pos = max_pos;
+  const long items = long(T) * (Hq + 2 * Hkv);
+  rope_kv_kernel<<<unsigned((items + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream) {
+  if (T <= 0) return 0;
+  const long n = long(T) * I;
+  long nb = (n + 255) / 256; int blocks = int(nb < 148 * 16 ? nb : 148 * 16);
+  act_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                         static_cast<__nv_bfloat16*>(out), T, I, act);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,
+                            const float* values, int n, void* stream) {
+  if (n <= 0) return 0;
+  logits_edit_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, vocab, rows, tokens, ops, values, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_logits_bitmask(float* logits, int rows, int vocab, const uint32_t* mask, const int32_t* mask_rows, void* stream) {
+  if (rows <= 0) return 0;
+  const int words = (vocab - 1) / 32 + 1;
+  dim3 grid((vocab + 255) / 256, rows);
+  logits_bitmask_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, vocab, mask, mask_rows, words);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_bf16_to_f32(const void* in, float* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  long long nb = (n + 255) / 256; int blocks = int(nb < 148 * 16 ? nb : 148 * 16);
+  bf16_to_f32_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(in), out, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream) {
+  if (n_rows <= 0) return 0;
+  if (row_bytes % 16) return -1;
+  gather_rows_kernel<<<n_rows, min(256, row_bytes / 16), 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(in), rows, static_cast<uint4*>(out), row_bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

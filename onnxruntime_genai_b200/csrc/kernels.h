@@ -1,0 +1,58 @@
+// C entry points of libogb200_kernels.so (sm_100a).  Every launcher takes raw device pointers and
+// a CUDA stream (void* = cudaStream_t), launches asynchronously and returns 0 on success or a
+// negative code: -1 bad argument / alignment, -2 scratch or tensor-map failure, -3 attribute
+// failure, -4 launch failure, -5 unsupported shape.  None of them allocates device memory.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- runtime.cu
+int ogb_runtime_init(int device);                 // allocates the per-device status word (call outside graph capture)
+int* ogb_status_device_ptr(int device);           // device address of the status word
+int ogb_status_read_and_clear(int device);        // synchronises the device; returns the OgbStatus code seen since last call
+int ogb_sm_count(int device);
+
+// ---- gemm_tcgen05.cu
+int ogb_gemm_token_tile(int M, int dual);
+int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
+int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
+                  const void* residual, int ldr, int out_fp32, int dual, int dual_row_offset, int splits, void* workspace,
+                  long long workspace_bytes, int* counters, int num_counters, int* status, int sm_count, void* stream);
+
+// ---- elementwise.cu
+int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);
+int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias, void* out,
+             int rows, int H, float eps, int layernorm, void* stream);
+int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
+                       const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
+                       float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream);
+int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream);
+int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,
+                    const float* values, int n, void* stream);
+int ogb_logits_bitmask(float* logits, int rows, int vocab, const uint32_t* mask, const int32_t* mask_rows, void* stream);
+int ogb_bf16_to_f32(const void* in, float* out, long long n, void* stream);
+int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream);
+
+// ---- attention.cu
+long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, int splits);
+int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                        const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                        int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                        int max_q_len, int Hq, int Hkv, int D, int splits, void* scratch, long long scratch_bytes, void* stream);
+
+// ---- sampling.cu
+int ogb_sample(const float* logits, long long row_stride, int rows, int vocab, const int32_t* top_k, const float* top_p,
+               const float* temperature, const unsigned long long* seeds, const int32_t* positions, int32_t* out, void* stream);
+int ogb_argmax(const float* logits, long long row_stride, int rows, int vocab, int32_t* out, void* stream);
+int ogb_topk(const float* x, long long row_stride, int rows, int n, int k, int mode, const float* add, float* out_vals,
+             int32_t* out_idx, void* stream);
+int ogb_beam_merge(const float* in_vals, const int32_t* in_idx, int batch, int beams, int cand, float* out_scores,
+                   int32_t* out_tokens, int32_t* out_beams, void* stream);
+int ogb_verify_greedy(const int32_t* draft, const int32_t* target_argmax, int k, int32_t* accepted, int32_t* commit, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

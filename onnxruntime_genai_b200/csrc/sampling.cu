@@ -1,0 +1,504 @@
+// Token selection on the device: one kernel per step for a whole batch with PER-ROW parameters
+// (top_k, top_p, temperature, seed, position), plus top-k scoring for beam search and the
+// speculative-verification kernel.
+//
+// Semantics follow the reference pipeline (src/sampling_distribution.h:233-297 on the host,
+// src/cuda/cuda_sampling.cu:90-239 on the device): restrict to the k largest logits, softmax with
+// temperature, keep the shortest prefix (by descending probability) whose mass reaches top_p,
+// renormalise, draw.  Differences by design:
+//   * no sort: the kept set is described by a key threshold found with an 8-bit radix select (by
+//     count for top-k, by probability mass for top-p); the draw is a prefix scan over the kept
+//     set in index order;
+//   * probability masses are accumulated in 40-bit fixed point with integer atomics, so the
+//     result is bit-reproducible from run to run and independent of how rows are batched;
+//   * randomness is Philox4x32-10 keyed by (seed, sequence position): stateless, so rolling a
+//     step back needs no RNG bookkeeping, and a request samples the same tokens alone or batched;
+//   * rows are not bucketed by (k, p, T) (reference: src/cuda/interface.cpp:156-359): every row
+//     reads its own parameters.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ogb {
+
+constexpr int SAMP_THREADS = 1024;
+constexpr float SAMP_LOG2E = 1.4426950408889634f;
+constexpr float MASS_SCALE = 1099511627776.0f;  // 2^40
+
+__device__ __forceinline__ uint32_t to_key(float f) {  // order-preserving float -> uint
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct RowCtx {
+  const float* x;
+  int n;
+  float mx;      // row maximum
+  float inv_t2;  // log2(e) / temperature
+  // top-k membership: key > tk, or key == tk and index <= tk_idx
+  uint32_t tk;
+  int tk_idx;
+  bool use_k;
+  __device__ __forceinline__ bool in_k(int i, uint32_t key) const {
+    return !use_k || key > tk || (key == tk && i <= tk_idx);
+  }
+  __device__ __forceinline__ unsigned long long mass(float v) const {
+    return (unsigned long long)(exp2f((v - mx) * inv_t2) * MASS_SCALE);
+  }
+};
+
+struct SelectShared {
+  unsigned long long hist[256];
+  unsigned long long want, above;
+  uint32_t prefix, mask;
+  int found;
+  unsigned long long warp_tot[32];
+  unsigned long long carry;
+  int result;
+};
+
+// Radix select over the row.  MASS = false: weights are 1 (count); MASS = true: fixed-point
+// probability mass.  On return sh.prefix is the threshold key T, sh.above the total weight of
+// members with key > T, and sh.want the weight still needed from members with key == T.
+template <bool MASS>
+__device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long long want) {
+  const int tid = threadIdx.x;
+  if (tid == 0) { sh.want = want; sh.above = 0; sh.prefix = 0; sh.mask = 0; }
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0;
+    __syncthreads();
+    const uint32_t prefix = sh.prefix, mask = sh.mask;
+    for (int i = tid; i < c.n; i += blockDim.x) {
+      const float v = c.x[i];
+      const uint32_t key = to_key(v);
+      if ((key & mask) == prefix && c.in_k(i, key)) {
+        const unsigned long long w = MASS ? c.mass(v) : 1ull;
+        if (w) atomicAdd(&sh.hist[(key >> shift) & 255], w);
+      }
+    }
+    __syncthreads();
+    if (tid < 32) {
+      // lane l owns bins [8l, 8l+8); suffix sums from the top bin downwards
+      unsigned long long local = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local += sh.hist[tid * 8 + j];
+      unsigned long long suffix = local;  // inclusive suffix over lanes >= tid
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        unsigned long long up = __shfl_down_sync(0xffffffffu, suffix, o);
+        if (tid + o < 32) suffix += up;
+      }
+      const unsigned long long w = sh.want;
+      const unsigned long long higher = suffix - local;  // weight in lanes above this one
+      const bool here = higher < w && suffix >= w;
+      const unsigned found_mask = __ballot_sync(0xffffffffu, here);
+      if (found_mask == 0) {
+        // fewer members than requested: take everything (threshold = lowest non-empty bin)
+        const unsigned nonempty = __ballot_sync(0xffffffffu, local > 0);
+        if (tid == 0) sh.found = 0;
+        if (nonempty && tid == __ffs(nonempty) - 1) {
+          int bin = 0;
+          for (int j = 0; j < 8; ++j) if (sh.hist[tid * 8 + j]) { bin = tid * 8 + j; break; }
+          unsigned long long cum = higher;
+          for (int j = 7; j >= 0; --j) if (tid * 8 + j > bin) cum += sh.hist[tid * 8 + j];
+          sh.above += cum;
+          sh.want = sh.hist[bin];
+          sh.prefix |= uint32_t(bin) << shift;
+          sh.mask |= 255u << shift;
+          sh.found = 1;
+        }
+      } else if (here) {
+        unsigned long long cum = higher;
+        int bin = tid * 8;
+        for (int j = 7; j >= 0; --j) {
+          const unsigned long long h = sh.hist[tid * 8 + j];
+          if (cum + h >= w) { bin = tid * 8 + j; break; }
+          cum += h;
+        }
+        sh.above += cum;
+        sh.want = w - cum;
+        sh.prefix |= uint32_t(bin) << shift;
+        sh.mask |= 255u << shift;
+        sh.found = 1;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Block-wide inclusive scan of one value per thread (index order = thread order).
+__device__ __forceinline__ unsigned long long block_scan_incl(unsigned long long v, SelectShared& sh, unsigned long long& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    unsigned long long up = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += up;
+  }
+  if (lane == 31) sh.warp_tot[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    unsigned long long t = lane < (blockDim.x >> 5) ? sh.warp_tot[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned long long up = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) t += up;
+    }
+    sh.warp_tot[lane] = t;  // inclusive totals of warps
+  }
+  __syncthreads();
+  const unsigned long long before = warp ? sh.warp_tot[warp - 1] : 0;
+  total = sh.warp_tot[(blockDim.x >> 5) - 1];
+  return v + before;
+}
+
+// Smallest index I such that members with key == T and index <= I carry at least `want` weight
+// (weight 1 per member when !MASS).  Used only when ties straddle a threshold.
+template <bool MASS>
+__device__ int tie_index_cut(const RowCtx& c, SelectShared& sh, uint32_t T, unsigned long long want, bool k_member_only) {
+  if (threadIdx.x == 0) { sh.carry = 0; sh.result = c.n - 1; }
+  __syncthreads();
+  for (int base = 0; base < c.n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    unsigned long long w = 0;
+    if (i < c.n) {
+      const float v = c.x[i];
+      const uint32_t key = to_key(v);
+      if (key == T && (!k_member_only || c.in_k(i, key))) w = MASS ? c.mass(v) : 1ull;
+    }
+    unsigned long long total;
+    const unsigned long long incl = block_scan_incl(w, sh, total);
+    const unsigned long long carry = sh.carry;
+    const bool hit = w && carry + incl >= want && carry + incl - w < want;
+    if (hit) sh.result = i;
+    __syncthreads();
+    const bool done = carry + total >= want;
+    if (threadIdx.x == 0) sh.carry = carry + total;
+    __syncthreads();
+    if (done) break;
+  }
+  return sh.result;
+}
+
+struct SampleParams {
+  const float* logits;
+  long long row_stride;
+  int vocab, rows;
+  const int32_t* top_k; const float* top_p; const float* temperature;
+  const unsigned long long* seeds; const int32_t* positions;
+  int32_t* out;
+};
+
+__global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
+  __shared__ SelectShared sh;
+  __shared__ float red_v[32];
+  __shared__ int red_i[32];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* x = p.logits + size_t(row) * p.row_stride;
+  const int n = p.vocab;
+
+  // ---- pass 1: maximum and its lowest index
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = x[i];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < (blockDim.x >> 5) ? red_v[lane] : -INFINITY;
+    bi = lane < (blockDim.x >> 5) ? red_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { red_v[0] = bv; red_i[0] = bi; }
+  }
+  __syncthreads();
+  const float mx = red_v[0];
+  const int arg = red_i[0] == 0x7fffffff ? 0 : red_i[0];
+
+  const int k = p.top_k ? p.top_k[row] : 1;
+  const float top_p = p.top_p ? p.top_p[row] : 0.f;
+  const float temp = p.temperature ? p.temperature[row] : 1.f;
+  if (k == 1 || temp <= 0.f || !(mx > -INFINITY)) {
+    if (tid == 0) p.out[row] = arg;
+    return;
+  }
+
+  RowCtx c;
+  c.x = x; c.n = n; c.mx = mx; c.inv_t2 = SAMP_LOG2E / temp;
+  c.use_k = false; c.tk = 0; c.tk_idx = n;
+
+  // ---- top-k by count
+  if (k > 1 && k < n) {
+    radix_select<false>(c, sh, (unsigned long long)k);
+    const uint32_t T = sh.prefix;
+    const unsigned long long need = sh.want;
+    __syncthreads();
+    // ties at the threshold: keep the lowest `need` indices
+    int cut = tie_index_cut<false>(c, sh, T, need, false);
+    c.use_k = true; c.tk = T; c.tk_idx = cut;
+    __syncthreads();
+  }
+
+  // ---- final membership threshold (tp, tp_idx): starts as the top-k set, narrowed by top-p
+  uint32_t tp = c.use_k ? c.tk : 0u;
+  int tp_idx = c.use_k ? c.tk_idx : n;
+  if (top_p > 0.f && top_p < 1.f) {
+    // total mass of the top-k set
+    unsigned long long z = 0;
+    for (int i = tid; i < n; i += blockDim.x) {
+      const float v = x[i];
+      if (c.in_k(i, to_key(v))) z += c.mass(v);
+    }
+    unsigned long long total;
+    block_scan_incl(z, sh, total);
+    __syncthreads();
+    unsigned long long want = (unsigned long long)(double(total) * double(top_p));
+    if (want < 1) want = 1;
+    radix_select<true>(c, sh, want);
+    const uint32_t T = sh.prefix;
+    const unsigned long long need = sh.want;
+    __syncthreads();
+    const int cut = tie_index_cut<true>(c, sh, T, need, true);
+    __syncthreads();
+    tp = T; tp_idx = cut;
+  }
+
+  // ---- draw: prefix scan over kept masses in index order
+  auto kept_mass = [&](int i) -> unsigned long long {
+    const float v = x[i];
+    const uint32_t key = to_key(v);
+    if (!c.in_k(i, key)) return 0ull;
+    if (key > tp || (key == tp && i <= tp_idx)) { const unsigned long long m = c.mass(v); return m ? m : 1ull; }
+    return 0ull;
+  };
+  unsigned long long z = 0;
+  for (int i = tid; i < n; i += blockDim.x) z += kept_mass(i);
+  unsigned long long zt;
+  block_scan_incl(z, sh, zt);
+  __syncthreads();
+  uint32_t rnd[4];
+  Philox::gen(p.seeds ? p.seeds[row] : 0ull, (unsigned long long)(p.positions ? p.positions[row] : 0), 0x5a17u, rnd);
+  // 53-bit uniform in [0,1) -> target in [0, zt)
+  const double u = double((((unsigned long long)rnd[0] << 32) | rnd[1]) >> 11) * (1.0 / 9007199254740992.0);
+  unsigned long long target = (unsigned long long)(u * double(zt));
+  if (target >= zt) target = zt - 1;
+
+  if (tid == 0) { sh.carry = 0; sh.result = arg; }
+  __syncthreads();
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + tid;
+    const unsigned long long w = i < n ? kept_mass(i) : 0ull;
+    unsigned long long total;
+    const unsigned long long incl = block_scan_incl(w, sh, total);
+    const unsigned long long carry = sh.carry;
+    if (w && carry + incl > target && carry + incl - w <= target) sh.result = i;
+    __syncthreads();
+    const bool done = carry + total > target;
+    if (tid == 0) sh.carry = carry + total;
+    __syncthreads();
+    if (done) break;
+  }
+  if (tid == 0) p.out[row] = sh.result;
+}
+
+// ------------------------------------------------------------------------------------ top-k scores
+// Per row: the k largest entries (k <= 128), sorted descending (ties by lower index), written as
+// values and indices.  mode 0: raw values; mode 1: log-softmax values plus add[row] (beam search:
+// log-probabilities plus the running beam score, reference src/search.cpp:101-140).
+constexpr int TOPK_MAX = 128;
+
+struct TopKParams {
+  const float* x; long long row_stride; int n, rows, k, mode;
+  const float* add;
+  float* out_vals; int32_t* out_idx;
+};
+
+__global__ void __launch_bounds__(SAMP_THREADS) topk_kernel(TopKParams p) {
+  __shared__ SelectShared sh;
+  __shared__ float cand_v[TOPK_MAX];
+  __shared__ int cand_i[TOPK_MAX];
+  __shared__ int cand_n;
+  __shared__ float red[32];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* x = p.x + size_t(row) * p.row_stride;
+  const int n = p.n, k = min(p.k, n);
+
+  float mx = -INFINITY;
+  for (int i = tid; i < n; i += blockDim.x) mx = fmaxf(mx, x[i]);
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  if (warp == 0) { mx = lane < (blockDim.x >> 5) ? red[lane] : -INFINITY; mx = warp_max(mx); if (lane == 0) red[0] = mx; }
+  __syncthreads();
+  mx = red[0];
+  __syncthreads();
+  float lse = 0.f;
+  if (p.mode == 1) {
+    float s = 0.f;
+    for (int i = tid; i < n; i += blockDim.x) s += __expf(x[i] - mx);
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (warp == 0) { s = lane < (blockDim.x >> 5) ? red[lane] : 0.f; s = warp_sum(s); if (lane == 0) red[0] = s; }
+    __syncthreads();
+    lse = mx + __logf(red[0]);
+    __syncthreads();
+  }
+
+  RowCtx c;
+  c.x = x; c.n = n; c.mx = mx; c.inv_t2 = SAMP_LOG2E; c.use_k = false; c.tk = 0; c.tk_idx = n;
+  uint32_t T = 0;
+  int cut = n;
+  if (k < n) {
+    radix_select<false>(c, sh, (unsigned long long)k);
+    T = sh.prefix;
+    const unsigned long long need = sh.want;
+    __syncthreads();
+    cut = tie_index_cut<false>(c, sh, T, need, false);
+    __syncthreads();
+  }
+  if (tid == 0) cand_n = 0;
+  __syncthreads();
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = x[i];
+    const uint32_t key = to_key(v);
+    if (k >= n || key > T || (key == T && i <= cut)) {
+      const int slot = atomicAdd(&cand_n, 1);
+      if (slot < TOPK_MAX) { cand_v[slot] = v; cand_i[slot] = i; }
+    }
+  }
+  __syncthreads();
+  const int m = min(cand_n, TOPK_MAX);
+  // rank sort (m <= 128): position = number of candidates that come before this one
+  if (tid < m) {
+    const float v = cand_v[tid];
+    const int idx = cand_i[tid];
+    int rank = 0;
+    for (int j = 0; j < m; ++j) {
+      const float vj = cand_v[j];
+      const int ij = cand_i[j];
+      if (vj > v || (vj == v && ij < idx)) ++rank;
+    }
+    if (rank < k) {
+      float outv = v;
+      if (p.mode == 1) outv = v - lse + (p.add ? p.add[row] : 0.f);
+      p.out_vals[size_t(row) * p.k + rank] = outv;
+      p.out_idx[size_t(row) * p.k + rank] = idx;
+    }
+  }
+}
+
+// Beam merge: for each batch entry, the best 2*beams of its beams*(2*beams) candidates.
+// in_vals / in_idx: [batch*beams, cand]; out: [batch, cand] scores, tokens, source beams.
+__global__ void beam_merge_kernel(const float* in_vals, const int32_t* in_idx, int beams, int cand, float* out_scores,
+                                  int32_t* out_tokens, int32_t* out_beams) {
+  const int b = blockIdx.x;
+  const int total = beams * cand;
+  for (int e = threadIdx.x; e < total; e += blockDim.x) {
+    const float v = in_vals[size_t(b) * total + e];
+    int rank = 0;
+    for (int j = 0; j < total; ++j) {
+      const float vj = in_vals[size_t(b) * total + j];
+      if (vj > v || (vj == v && j < e)) ++rank;
+    }
+    if (rank < cand) {
+      out_scores[size_t(b) * cand + rank] = v;
+      out_tokens[size_t(b) * cand + rank] = in_idx[size_t(b) * total + e];
+      out_beams[size_t(b) * cand + rank] = e / cand;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ argmax rows
+__global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* logits, long long row_stride, int n, int32_t* out) {
+  __shared__ float red_v[32];
+  __shared__ int red_i[32];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* x = logits + size_t(row) * row_stride;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = tid; i < n; i += blockDim.x) {
+    const float v = x[i];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < (blockDim.x >> 5) ? red_v[lane] : -INFINITY;
+    bi = lane < (blockDim.x >> 5) ? red_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+// ------------------------------------------------------------------------------------ speculative verify (greedy)
+// target_argmax[K+1] vs draft[K]: accepted = length of the matching prefix; commit = accepted draft
+// tokens followed by the target's token at the first mismatch (or the bonus token).  One thread.
+__global__ void verify_greedy_kernel(const int32_t* draft, const int32_t* target_argmax, int k, int32_t* accepted, int32_t* commit) {
+  if (threadIdx.x || blockIdx.x) return;
+  int a = 0;
+  while (a < k && draft[a] == target_argmax[a]) { commit[a] = draft[a]; ++a; }
+  commit[a] = target_argmax[a];
+  *accepted = a;
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+OGB_API int ogb_sample(const float* logits, long long row_stride, int rows, int vocab, const int32_t* top_k, const float* top_p,
+                       const float* temperature, const unsigned long long* seeds, const int32_t* positions, int32_t* out,
+                       void* stream) {
+  if (rows <= 0) return 0;
+  SampleParams p{logits, row_stride, vocab, rows, top_k, top_p, temperature, seeds, positions, out};
+  sample_kernel<<<rows, SAMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_argmax(const float* logits, long long row_stride, int rows, int vocab, int32_t* out, void* stream) {
+  if (rows <= 0) return 0;
+  argmax_kernel<<<rows, SAMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(logits, row_stride, vocab, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_topk(const float* x, long long row_stride, int rows, int n, int k, int mode, const float* add, float* out_vals,
+                     int32_t* out_idx, void* stream) {
+  if (rows <= 0) return 0;
+  if (k < 1 || k > TOPK_MAX) return -1;
+  TopKParams p{x, row_stride, n, rows, k, mode, add, out_vals, out_idx};
+  topk_kernel<<<rows, SAMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_beam_merge(const float* in_vals, const int32_t* in_idx, int batch, int beams, int cand, float* out_scores,
+                           int32_t* out_tokens, int32_t* out_beams, void* stream) {
+  if (batch <= 0) return 0;
+  beam_merge_kernel<<<batch, 256, 0, static_cast<cudaStream_t>(stream)>>>(in_vals, in_idx, beams, cand, out_scores, out_tokens, out_beams);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_verify_greedy(const int32_t* draft, const int32_t* target_argmax, int k, int32_t* accepted, int32_t* commit, void* stream) {
+  verify_greedy_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(draft, target_argmax, k, accepted, commit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,429 @@
+#include "engine_core.h"
+
+#include <algorithm>
+#include <random>
+#include <stdexcept>
+
+namespace ogb::engine {
+
+// ----------------------------------------------------------------------------------- BlockPool
+BlockPool::BlockPool(int n) : state_(size_t(n), State::kFree) {
+  free_.reserve(size_t(n));
+  for (int i = n - 1; i >= 0; --i) free_.push_back(i);
+}
+
+bool BlockPool::Reserve(int n, std::vector<int>& out) {
+  if (n < 0) throw std::invalid_argument("BlockPool::Reserve: negative count");
+  if (n > int(free_.size())) return false;
+  for (int i = 0; i < n; ++i) {
+    int id = free_.back();
+    free_.pop_back();
+    state_[size_t(id)] = State::kReserved;
+    out.push_back(id);
+  }
+  return true;
+}
+
+void BlockPool::Commit(int id) {
+  if (id < 0 || id >= Total() || state_[size_t(id)] != State::kReserved)
+    throw std::logic_error("BlockPool::Commit: block " + std::to_string(id) + " is not reserved");
+  state_[size_t(id)] = State::kCommitted;
+}
+
+static void InsertFree(std::vector<int>& free_list, int id) {
+  // keep descending order so that back() is the lowest id
+  auto it = std::lower_bound(free_list.begin(), free_list.end(), id, std::greater<int>());
+  free_list.insert(it, id);
+}
+
+void BlockPool::Release(int id) {
+  if (id < 0 || id >= Total() || state_[size_t(id)] != State::kReserved)
+    throw std::logic_error("BlockPool::Release: block " + std::to_string(id) + " is not reserved");
+  state_[size_t(id)] = State::kFree;
+  InsertFree(free_, id);
+}
+
+void BlockPool::Free(int id) {
+  if (id < 0 || id >= Total() || state_[size_t(id)] != State::kCommitted)
+    throw std::logic_error("BlockPool::Free: block " + std::to_string(id) + " is not committed");
+  state_[size_t(id)] = State::kFree;
+  InsertFree(free_, id);
+}
+
+// ----------------------------------------------------------------------------------- strings
+const char* ToString(RequestStatus s) {
+  switch (s) {
+    case RequestStatus::kUnassigned: return "Unassigned";
+    case RequestStatus::kAssigned: return "Assigned";
+    case RequestStatus::kActive: return "Active";
+    case RequestStatus::kTurnComplete: return "TurnComplete";
+    case RequestStatus::kClosed: return "Closed";
+  }
+  return "?";
+}
+const char* ToString(StepOutcome o) {
+  switch (o) {
+    case StepOutcome::kNoWork: return "NoWork";
+    case StepOutcome::kCapacityDeferred: return "CapacityDeferred";
+    case StepOutcome::kUnserviceableRequest: return "UnserviceableRequest";
+    case StepOutcome::kCommitted: return "Committed";
+    case StepOutcome::kRetryableBatchAbort: return "RetryableBatchAbort";
+    case StepOutcome::kExecutionCapacityExceeded: return "ExecutionCapacityExceeded";
+    case StepOutcome::kExecutionContractFailure: return "ExecutionContractFailure";
+    case StepOutcome::kFatalExecutionFailure: return "FatalExecutionFailure";
+    case StepOutcome::kPlanned: return "Planned";
+  }
+  return "?";
+}
+
+// ----------------------------------------------------------------------------------- Request
+SamplingArgs RequestOptions::Resolve() const {
+  SamplingArgs a;
+  if (!do_sample || top_k == 1 || temperature == 0.f) return a;  // greedy
+  a.temperature = temperature;
+  const bool use_p = top_p > 0.f && top_p < 1.f;
+  if (top_k > 1 && use_p) { a.top_k = top_k; a.top_p = top_p; }
+  else if (top_k > 1) { a.top_k = top_k; a.top_p = 1.f; }
+  else { a.top_k = -1; a.top_p = use_p ? top_p : 1.f; }
+  return a;
+}
+
+Request::Request(uint64_t id, RequestOptions opt, std::vector<int32_t> eos)
+    : id_(id), opt_(opt), eos_ids_(std::move(eos)) {
+  if (opt_.batch_size != 1) throw std::runtime_error("Engine requests must use batch_size 1");
+  if (opt_.num_beams != 1) throw std::runtime_error("Engine requests do not support beam search");
+  if (opt_.random_seed >= 0) seed_ = uint64_t(opt_.random_seed);
+  else { std::random_device rd; seed_ = (uint64_t(rd()) << 32) | rd(); }
+}
+
+void Request::AddTokens(const int32_t* ids, size_t n) {
+  if (status_ != RequestStatus::kUnassigned)
+    throw std::runtime_error("add_tokens: tokens can only be added before the request is given to an engine");
+  if (n == 0) throw std::runtime_error("add_tokens: empty token list");
+  tokens_.insert(tokens_.end(), ids, ids + n);
+}
+
+void Request::ContinueWith(const int32_t* ids, size_t n) {
+  if (status_ != RequestStatus::kTurnComplete)
+    throw std::runtime_error("continue_with: the current turn is not complete");
+  if (n == 0) throw std::runtime_error("continue_with: empty token list");
+  if (int(tokens_.size() + n) >= opt_.max_length)
+    throw std::runtime_error("continue_with: max_length (cumulative across turns) would be exceeded");
+  tokens_.insert(tokens_.end(), ids, ids + n);
+  prefill_ = true;
+  status_ = RequestStatus::kAssigned;
+}
+
+int32_t Request::PopUnseen() {
+  if (unseen_.empty()) throw std::runtime_error("get_unseen_token: no unseen tokens");
+  int32_t t = unseen_.front();
+  unseen_.pop_front();
+  return t;
+}
+
+// ----------------------------------------------------------------------------------- EngineCore
+EngineCore::EngineCore(EngineOptions opt) : opt_(std::move(opt)), pool_(opt_.num_blocks) {
+  if (opt_.block_size <= 0 || opt_.num_blocks <= 0 || opt_.max_batch_size <= 0 || opt_.max_scheduled_tokens <= 0)
+    throw std::invalid_argument("engine: block_size, num_blocks, max_batch_size and max_scheduled_tokens must be > 0");
+  if (opt_.window_size > 0) {
+    // Ring of R blocks per request: holds one step's chunk plus the window behind it.
+    int chunk = opt_.max_scheduled_tokens;
+    ring_blocks_ = (chunk + opt_.window_size - 1 + opt_.block_size - 1) / opt_.block_size;
+    if (opt_.num_window_blocks <= 0) opt_.num_window_blocks = ring_blocks_ * opt_.max_batch_size;
+    wpool_ = std::make_unique<BlockPool>(opt_.num_window_blocks);
+  }
+}
+
+std::shared_ptr<Request> EngineCore::CreateRequest(RequestOptions o) {
+  return std::make_shared<Request>(next_id_++, o, opt_.eos_ids);
+}
+
+void EngineCore::AddRequest(const std::shared_ptr<Request>& r) {
+  if (!healthy_) throw std::runtime_error("engine is unhealthy after a fatal execution failure");
+  if (r->status_ != RequestStatus::kUnassigned) throw std::runtime_error("add_request: request was already added to an engine");
+  if (r->tokens_.empty()) throw std::runtime_error("add_request: request has no tokens");
+  if (r->opt_.max_length <= 0) throw std::runtime_error("add_request: max_length must be > 0");
+  if (int(r->tokens_.size()) >= r->opt_.max_length)
+    throw std::runtime_error("add_request: prompt length " + std::to_string(r->tokens_.size()) +
+                             " leaves no room under max_length " + std::to_string(r->opt_.max_length));
+  r->status_ = RequestStatus::kAssigned;
+  requests_.push_back(r);
+  ++metrics_.requests_admitted;
+}
+
+void EngineCore::ReleaseRequestBlocks(Request& r) {
+  for (int b : r.blocks_) pool_.Free(b);
+  r.blocks_.clear();
+  if (wpool_) for (int b : r.window_blocks_) wpool_->Free(b);
+  r.window_blocks_.clear();
+  r.resident_ = false;
+}
+
+void EngineCore::RemoveRequest(const std::shared_ptr<Request>& r) {
+  if (open_)
+    for (auto& e : plan_.entries)
+      if (e.request == r) throw std::runtime_error("remove_request: request is part of the step in flight");
+  auto it = std::find(requests_.begin(), requests_.end(), r);
+  if (it == requests_.end()) return;
+  ReleaseRequestBlocks(*r);
+  r->status_ = RequestStatus::kClosed;
+  requests_.erase(it);
+  ready_.erase(std::remove(ready_.begin(), ready_.end(), r), ready_.end());
+}
+
+bool EngineCore::HasPendingRequests() const {
+  if (!ready_.empty()) return true;
+  for (auto& r : requests_)
+    if (r->status_ == RequestStatus::kAssigned || r->status_ == RequestStatus::kActive || r->HasUnseen()) return true;
+  return false;
+}
+
+const StepPlan& EngineCore::Plan() {
+  if (!healthy_) throw std::runtime_error("engine is unhealthy after a fatal execution failure");
+  if (open_) throw std::logic_error("Plan: previous step transaction is still open");
+  plan_ = StepPlan{};
+  reserved_.clear();
+
+  // Candidates: residents first (admission order), then waiting requests; decodes before prefills.
+  std::vector<std::shared_ptr<Request>> cands;
+  auto executable = [](const Request& r) {
+    return (r.status_ == RequestStatus::kAssigned || r.status_ == RequestStatus::kActive) && r.Pending() > 0;
+  };
+  for (auto& r : requests_) if (r->resident_ && executable(*r)) cands.push_back(r);
+  for (auto& r : requests_) if (!r->resident_ && executable(*r)) cands.push_back(r);
+  std::stable_partition(cands.begin(), cands.end(), [](const std::shared_ptr<Request>& r) { return !r->prefill_; });
+
+  const int limit = std::min(opt_.max_scheduled_tokens, opt_.max_batch_size);
+  for (auto& r : cands) {
+    if (int(plan_.entries.size()) >= limit) break;
+    const int need_total = BlocksFor(int(r->tokens_.size()));
+    if (need_total > pool_.Total() || (wpool_ && ring_blocks_ > wpool_->Total())) {
+      plan_.unserviceable.push_back(r);
+      continue;
+    }
+    Reserved res;
+    const int need = need_total - int(r->blocks_.size());
+    if (need > 0 && !pool_.Reserve(need, res.blocks)) { ++plan_.deferred; continue; }
+    if (wpool_) {
+      const int wneed = ring_blocks_ - int(r->window_blocks_.size());
+      if (wneed > 0 && !wpool_->Reserve(wneed, res.wblocks)) {
+        for (int b : res.blocks) pool_.Release(b);
+        ++plan_.deferred;
+        continue;
+      }
+    }
+    PlanEntry e;
+    e.request = r;
+    e.num_tokens = 1;
+    e.processed_before = r->processed_;
+    e.is_prefill = r->prefill_;
+    e.newly_admitted = !r->resident_;
+    plan_.entries.push_back(std::move(e));
+    reserved_.push_back(std::move(res));
+  }
+
+  for (auto& r : plan_.unserviceable) {
+    ReleaseRequestBlocks(*r);
+    r->status_ = RequestStatus::kClosed;
+    requests_.erase(std::remove(requests_.begin(), requests_.end(), r), requests_.end());
+    ++metrics_.unserviceable;
+  }
+
+  if (plan_.entries.empty()) {
+    if (!plan_.unserviceable.empty()) plan_.outcome = StepOutcome::kUnserviceableRequest;
+    else if (plan_.deferred > 0) { plan_.outcome = StepOutcome::kCapacityDeferred; ++metrics_.steps_deferred; }
+    else plan_.outcome = StepOutcome::kNoWork;
+    return plan_;
+  }
+
+  // Token budget: one token each, then prefills share what is left in plan order.
+  int budget = opt_.max_scheduled_tokens - int(plan_.entries.size());
+  for (auto& e : plan_.entries) {
+    if (!e.is_prefill) continue;
+    int cap = e.request->Pending();
+    if (e.request->opt_.chunk_size > 0) cap = std::min(cap, e.request->opt_.chunk_size);
+    int extra = std::min(cap - 1, budget);
+    e.num_tokens += extra;
+    budget -= extra;
+  }
+
+  int off = 0;
+  plan_.graph_eligible = true;
+  for (auto& e : plan_.entries) {
+    e.packed_offset = off;
+    e.logits_row = off + e.num_tokens - 1;
+    e.samples = (e.num_tokens == e.request->Pending());
+    off += e.num_tokens;
+    plan_.max_query_len = std::max(plan_.max_query_len, e.num_tokens);
+    plan_.max_kv_len = std::max(plan_.max_kv_len, e.processed_before + e.num_tokens);
+    plan_.graph_eligible &= (!e.is_prefill && e.num_tokens == 1);
+    // checkpoint
+    Request& r = *e.request;
+    r.saved_ = Request::Saved{r.tokens_.size(), r.processed_, r.unseen_.size(), r.status_, r.prefill_,
+                              r.blocks_.size(), r.window_blocks_.size()};
+  }
+  plan_.token_count = off;
+  plan_.block_table_columns = BlocksFor(plan_.max_kv_len);
+  plan_.outcome = StepOutcome::kPlanned;
+  open_ = true;
+  return plan_;
+}
+
+void EngineCore::Pack(const PackBuffers& buf) const {
+  if (!open_) throw std::logic_error("Pack: no open step");
+  const int B = int(plan_.entries.size());
+  if (B > buf.max_batch || plan_.token_count > buf.max_tokens || plan_.block_table_columns > buf.table_columns)
+    throw std::runtime_error("Pack: step exceeds the staging buffer capacity");
+  const int bs = opt_.block_size, cols = buf.table_columns;
+  buf.cu_seqlens[0] = 0;
+  for (int i = 0; i < B; ++i) {
+    const PlanEntry& e = plan_.entries[size_t(i)];
+    const Request& r = *e.request;
+    const Reserved& res = reserved_[size_t(i)];
+    auto block_at = [&](int col) -> int {
+      size_t held = r.blocks_.size();
+      if (size_t(col) < held) return r.blocks_[size_t(col)];
+      size_t k = size_t(col) - held;
+      return k < res.blocks.size() ? res.blocks[k] : -1;
+    };
+    auto wblock_at = [&](int ring_idx) -> int {
+      size_t held = r.window_blocks_.size();
+      if (size_t(ring_idx) < held) return r.window_blocks_[size_t(ring_idx)];
+      size_t k = size_t(ring_idx) - held;
+      return k < res.wblocks.size() ? res.wblocks[k] : -1;
+    };
+    for (int t = 0; t < e.num_tokens; ++t) {
+      const int pos = e.processed_before + t, idx = e.packed_offset + t;
+      buf.input_ids[idx] = r.tokens_[size_t(pos)];
+      buf.positions[idx] = pos;
+      buf.token_row[idx] = i;
+      buf.slot_mapping[idx] = block_at(pos / bs) * bs + pos % bs;
+      if (buf.slot_mapping_w && wpool_) buf.slot_mapping_w[idx] = wblock_at((pos / bs) % ring_blocks_) * bs + pos % bs;
+    }
+    buf.cu_seqlens[i + 1] = e.packed_offset + e.num_tokens;
+    buf.past_lens[i] = e.processed_before;
+    buf.logits_rows[i] = e.logits_row;
+    const int used_cols = BlocksFor(e.processed_before + e.num_tokens);
+    for (int c = 0; c < cols; ++c) buf.block_table[size_t(i) * cols + c] = c < used_cols ? block_at(c) : -1;
+    if (buf.block_table_w && wpool_)
+      for (int c = 0; c < cols; ++c) buf.block_table_w[size_t(i) * cols + c] = c < used_cols ? wblock_at(c % ring_blocks_) : -1;
+    SamplingArgs a = r.opt_.Resolve();
+    buf.top_k[i] = a.top_k;
+    buf.top_p[i] = a.top_p;
+    buf.temperature[i] = a.temperature;
+    buf.seeds[i] = r.seed_;
+    buf.sample_pos[i] = int(r.tokens_.size());
+  }
+}
+
+StepOutcome EngineCore::Commit(const int32_t* tokens, size_t n) {
+  if (!open_) throw std::logic_error("Commit: no open step");
+  if (n != plan_.entries.size()) throw std::invalid_argument("Commit: one token per planned entry is required");
+  for (size_t i = 0; i < plan_.entries.size(); ++i) {
+    PlanEntry& e = plan_.entries[i];
+    Request& r = *e.request;
+    Reserved& res = reserved_[i];
+    for (int b : res.blocks) { pool_.Commit(b); r.blocks_.push_back(b); }
+    if (wpool_) for (int b : res.wblocks) { wpool_->Commit(b); r.window_blocks_.push_back(b); }
+    r.resident_ = true;
+    r.processed_ += e.num_tokens;
+    r.status_ = RequestStatus::kActive;
+    r.saved_.reset();
+    metrics_.tokens_scheduled += uint64_t(e.num_tokens);
+    if (!e.samples) continue;
+    r.prefill_ = false;
+    const int32_t tok = tokens[i];
+    const bool eos = std::find(r.eos_ids_.begin(), r.eos_ids_.end(), tok) != r.eos_ids_.end();
+    bool complete = eos;
+    if (!eos) {
+      r.tokens_.push_back(tok);
+      r.unseen_.push_back(tok);
+      ++metrics_.tokens_generated;
+      if (int(r.tokens_.size()) >= r.opt_.max_length) complete = true;
+    }
+    if (complete) { r.status_ = RequestStatus::kTurnComplete; ++metrics_.requests_completed; }
+    if (std::find(ready_.begin(), ready_.end(), e.request) == ready_.end()) ready_.push_back(e.request);
+  }
+  open_ = false;
+  ++metrics_.steps_committed;
+  plan_.outcome = StepOutcome::kCommitted;
+  return plan_.outcome;
+}
+
+StepOutcome EngineCore::Abort(FailureKind kind, const std::string&) {
+  if (!open_) throw std::logic_error("Abort: no open step");
+  for (size_t i = 0; i < plan_.entries.size(); ++i) {
+    Request& r = *plan_.entries[i].request;
+    for (int b : reserved_[i].blocks) pool_.Release(b);
+    if (wpool_) for (int b : reserved_[i].wblocks) wpool_->Release(b);
+    if (r.saved_) {
+      r.tokens_.resize(r.saved_->token_count);
+      r.processed_ = r.saved_->processed;
+      while (r.unseen_.size() > r.saved_->unseen) r.unseen_.pop_back();
+      r.status_ = r.saved_->status;
+      r.prefill_ = r.saved_->prefill;
+      r.saved_.reset();
+    }
+  }
+  reserved_.clear();
+  open_ = false;
+  ++metrics_.steps_aborted;
+  switch (kind) {
+    case FailureKind::kRetryableBeforeExecution:
+    case FailureKind::kRetryableDuringExecution: plan_.outcome = StepOutcome::kRetryableBatchAbort; break;
+    case FailureKind::kCapacityExceeded: plan_.outcome = StepOutcome::kExecutionCapacityExceeded; break;
+    case FailureKind::kPostProcessing: plan_.outcome = StepOutcome::kExecutionContractFailure; break;
+    case FailureKind::kFatal: plan_.outcome = StepOutcome::kFatalExecutionFailure; healthy_ = false; break;
+  }
+  return plan_.outcome;
+}
+
+std::shared_ptr<Request> EngineCore::NextReady() {
+  while (!ready_.empty()) {
+    auto r = ready_.front();
+    ready_.pop_front();
+    if (r->status_ == RequestStatus::kClosed) continue;
+    return r;
+  }
+  return nullptr;
+}
+
+void EngineCore::CheckInvariants() const {
+  auto check_pool = [&](const BlockPool& pool, bool windowed) {
+    std::vector<int> owners(size_t(pool.Total()), 0);
+    for (auto& r : requests_)
+      for (int b : (windowed ? r->window_blocks_ : r->blocks_)) {
+        if (b < 0 || b >= pool.Total()) throw std::logic_error("invariant: request holds an out-of-range block id");
+        if (pool.StateOf(b) != BlockPool::State::kCommitted) throw std::logic_error("invariant: request block is not committed in the pool");
+        if (++owners[size_t(b)] > 1) throw std::logic_error("invariant: block owned by two requests");
+      }
+    int reserved_listed = 0;
+    if (open_)
+      for (auto& res : reserved_)
+        for (int b : (windowed ? res.wblocks : res.blocks)) {
+          if (pool.StateOf(b) != BlockPool::State::kReserved) throw std::logic_error("invariant: reservation lists a block that is not reserved");
+          if (owners[size_t(b)]) throw std::logic_error("invariant: block both reserved and committed");
+          ++reserved_listed;
+        }
+    int free_n = 0, res_n = 0, com_n = 0;
+    for (int b = 0; b < pool.Total(); ++b) {
+      switch (pool.StateOf(b)) {
+        case BlockPool::State::kFree: ++free_n; break;
+        case BlockPool::State::kReserved: ++res_n; break;
+        case BlockPool::State::kCommitted: ++com_n; if (!owners[size_t(b)]) throw std::logic_error("invariant: committed block has no owner (leak)"); break;
+      }
+    }
+    if (free_n != pool.FreeCount()) throw std::logic_error("invariant: free list size disagrees with block states");
+    if (res_n != reserved_listed) throw std::logic_error("invariant: reserved blocks outside an open transaction");
+  };
+  check_pool(pool_, false);
+  if (wpool_) check_pool(*wpool_, true);
+  for (auto& r : requests_) {
+    if (r->processed_ < 0 || r->processed_ > int(r->tokens_.size())) throw std::logic_error("invariant: processed length out of range");
+    if (r->resident_ && BlocksFor(r->processed_) > int(r->blocks_.size())) throw std::logic_error("invariant: committed KV slots exceed owned blocks");
+    if ((r->status_ == RequestStatus::kAssigned || r->status_ == RequestStatus::kActive) && r->Pending() <= 0)
+      throw std::logic_error("invariant: executable request has no pending token");
+  }
+}
+
+}  // namespace ogb::engine
