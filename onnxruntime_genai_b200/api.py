@@ -1,0 +1,576 @@
+"""Public Python API: Config, Model, GeneratorParams, Generator, Tensor, NamedTensors.
+
+Surface and behaviour follow the reference binding (src/python/python.cpp:444-835) and the
+Generator it wraps (src/generators.cpp:564-1008): `append_tokens` runs the prompt (prefill, chunked
+by `search.chunk_size`), `generate_next_token` runs one decode step when the logits are stale, then
+applies guidance mask -> min_length -> repetition penalty -> no-repeat-ngram -> greedy / top-k /
+top-p / beam selection (src/standard_decoding_strategy.cpp:12-62); `rewind_to` drops tokens and their
+KV entries; `get_logits` / `set_logits` expose the fp32 scores of the next position.
+
+Differences by design: the model math runs in this process as PyTorch modules over sm_100a kernels
+(no ONNX Runtime session); the static-batch Generator uses the same paged KV cache and packed
+variable-length forward as the continuous-batching Engine, with one contiguous run of blocks per
+batch row, so padded prompts are handled by simply not feeding the pad tokens.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from . import ops
+from .models.decoder import PagedKVCache, StepInputs
+from .native_loader import native
+
+_cuda_device_id = 0
+
+
+def is_cuda_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def set_current_gpu_device_id(i: int) -> None:
+    global _cuda_device_id
+    _cuda_device_id = int(i)
+    if torch.cuda.is_available():
+        torch.cuda.set_device(_cuda_device_id)
+
+
+def get_current_gpu_device_id() -> int:
+    return _cuda_device_id
+
+
+def set_log_options(**kw) -> None:
+    for k, v in kw.items():
+        if isinstance(v, bool):
+            native.log_set_bool(k, v)
+        else:
+            native.log_set_string(k, str(v))
+
+
+def set_log_callback(fn) -> None:
+    native.log_set_callback(fn)
+
+
+class _Trace:
+    """RAII-style scope that writes a Chrome trace event when tracing is enabled."""
+
+    def __init__(self, cat: str, name: str):
+        self.cat, self.name = cat, name
+
+    def __enter__(self):
+        self.t0 = native.trace_now_us() if native.trace_enabled() else -1
+        return self
+
+    def __exit__(self, *exc):
+        if self.t0 >= 0:
+            native.trace_complete(self.cat, self.name, self.t0, native.trace_now_us() - self.t0)
+        return False
+
+
+# ------------------------------------------------------------------------------------------------ Config
+class Config:
+    def __init__(self, path: str, overlay: str = ""):
+        self._c = native.Config(str(path), overlay)
+        self._model_data: Dict[str, bytes] = {}
+
+    def __getattr__(self, name):
+        return getattr(self._c, name)
+
+    def append_provider(self, name: str):
+        self._c.append_provider(name)
+
+    def set_provider_option(self, provider: str, key: str, value: str):
+        self._c.set_provider_option(provider, key, value)
+
+    def clear_providers(self):
+        self._c.clear_providers()
+
+    def overlay(self, json_text: str):
+        self._c.overlay(json_text)
+
+    def add_model_data(self, filename: str, data: bytes):
+        self._model_data[filename] = bytes(data)
+
+    def remove_model_data(self, filename: str):
+        self._model_data.pop(filename, None)
+
+
+# ------------------------------------------------------------------------------------------------ Tensor
+class Tensor:
+    """A named-less n-d array handed to / returned from the runtime (wraps numpy or torch)."""
+
+    def __init__(self, array):
+        self._t = array if isinstance(array, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(array))
+
+    def shape(self):
+        return list(self._t.shape)
+
+    def type(self):
+        return str(self._t.dtype)
+
+    def as_numpy(self):
+        return self._t.detach().float().cpu().numpy() if self._t.dtype == torch.bfloat16 else self._t.detach().cpu().numpy()
+
+    def torch(self):
+        return self._t
+
+
+class NamedTensors(dict):
+    pass
+
+
+# ------------------------------------------------------------------------------------------------ Model
+class Model:
+    def __init__(self, config_or_path, tp=None):
+        self.config = config_or_path if isinstance(config_or_path, Config) else Config(str(config_or_path))
+        c = self.config
+        provs = [p for p, _ in c.decoder["provider_options"]]
+        want_cuda = "cuda" in provs
+        if want_cuda and not torch.cuda.is_available():
+            raise RuntimeError("the model config selects the cuda provider but no CUDA device is available "
+                               "(use Config.clear_providers() to run the CPU path)")
+        self.device_type = "cuda" if want_cuda else "cpu"
+        self.device = torch.device("cuda", torch.cuda.current_device()) if want_cuda else torch.device("cpu")
+        self.type = c.model_type
+        from .models.arch import LLM_TYPES
+        if self.type not in LLM_TYPES:
+            raise RuntimeError(f"Unsupported model type: {self.type}")
+        self.dtype = torch.bfloat16 if want_cuda else torch.float32
+        from .models.loader import load_decoder
+        with _Trace("model", "load"):
+            self.decoder = load_decoder(c.config_path, c, self.device, self.dtype, tp)
+            self.draft = load_decoder(c.config_path, c, self.device, self.dtype, tp, decoder=c.draft) if c.draft else None
+        self.arch = self.decoder.arch
+        self.graph_capture = bool(c.decoder.get("graph_capture", False))
+        if self.draft is not None and self.draft.arch.vocab_size != self.arch.vocab_size:
+            raise RuntimeError("speculative decoding: draft and target vocabularies differ")
+
+    def create_multimodal_processor(self):
+        raise RuntimeError("this model has no vision or speech component")
+
+    def create_streaming_processor(self):
+        raise RuntimeError("this model has no streaming audio component")
+
+
+# ------------------------------------------------------------------------------------------------ params
+_SEARCH_BOOLS = {"do_sample", "past_present_share_buffer", "early_stopping"}
+
+
+class GeneratorParams:
+    def __init__(self, model: Model):
+        self.model = model
+        self.search: Dict[str, Any] = dict(model.config.search)
+        self.speculative: Dict[str, Any] = dict(model.config.speculative)
+        self.guidance_type: Optional[str] = None
+        self.guidance_data: Optional[str] = None
+        self.guidance_ff_tokens = False
+
+    def set_search_options(self, **kw):
+        for k, v in kw.items():
+            if k in _SEARCH_BOOLS:
+                v = bool(v)
+            native.validate_search_option(k, v)  # throws on unknown names / non-integers
+            self.search[k] = v
+
+    def get_search_options(self) -> Dict[str, Any]:
+        return dict(self.search)
+
+    def set_speculative_options(self, **kw):
+        for k, v in kw.items():
+            native.validate_speculative_option(k, v)
+            self.speculative[k] = v
+
+    def get_speculative_options(self) -> Dict[str, Any]:
+        return dict(self.speculative)
+
+    def set_guidance(self, type: str, data: str, enable_ff_tokens: bool = False):
+        if type not in ("json_schema", "regex", "lark_grammar"):
+            raise RuntimeError(f"Unsupported guidance type: {type} (json_schema, regex, lark_grammar)")
+        self.guidance_type, self.guidance_data, self.guidance_ff_tokens = type, data, bool(enable_ff_tokens)
+
+
+def _sampling_method(search: Dict[str, Any], vocab: int):
+    """(method, k, p, t) following src/generators.cpp:661-682."""
+    do_sample, k, p, t = search["do_sample"], int(search["top_k"]), float(search["top_p"]), float(search["temperature"])
+    if not do_sample or k == 1 or t == 0:
+        return "greedy", 1, 0.0, 1.0
+    if search["num_beams"] > 1:
+        raise RuntimeError("sampling (do_sample=True) is not supported with beam search")
+    if not (0.0 <= p <= 1.0):
+        raise RuntimeError("top_p must be between 0.0 and 1.0")
+    if k < 0 or k > vocab:
+        raise RuntimeError("top_k must be between 0 and vocab_size")
+    if 0.0 < p < 1.0 and k > 1:
+        return "top_k_top_p", k, p, t
+    if k > 1:
+        return "top_k", k, 1.0, t
+    return "top_p", 0, p if p > 0 else 1.0, t
+
+
+# ------------------------------------------------------------------------------------------------ Generator
+class SequenceState:
+    """Device state of a static batch: paged KV with one contiguous run of blocks per row."""
+
+    def __init__(self, decoder, rows: int, max_length: int, block_size: int = 16):
+        self.decoder = decoder
+        self.rows = rows
+        self.block_size = block_size
+        self.blocks_per_row = (max_length + block_size - 1) // block_size
+        dev = decoder.device
+        self.kv = PagedKVCache(decoder.arch, rows * self.blocks_per_row, block_size, dev, decoder.dtype,
+                               kv_heads=decoder.kv_heads_local)
+        self.block_table = (torch.arange(rows * self.blocks_per_row, dtype=torch.int32).view(rows, self.blocks_per_row)).to(dev)
+        self.kv_len = [0] * rows
+
+    def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None) -> torch.Tensor:
+        """Feeds row_tokens[r] (possibly empty) after the cached prefix of row r; returns fp32 logits of the last
+        fed token of every non-empty row (or of every token)."""
+        dev = self.decoder.device
+        ids, pos, slots, cu, past, rows_used, last = [], [], [], [0], [], [], []
+        for r, toks in enumerate(row_tokens):
+            if not toks:
+                continue
+            base = self.kv_len[r]
+            if base + len(toks) > self.blocks_per_row * self.block_size:
+                raise RuntimeError("sequence exceeds the allocated KV cache (max_length)")
+            for j, t in enumerate(toks):
+                p = base + j
+                ids.append(t)
+                pos.append(p)
+                slots.append(r * self.blocks_per_row * self.block_size + p)
+            cu.append(len(ids))
+            past.append(base)
+            rows_used.append(r)
+            last.append(len(ids) - 1)
+            self.kv_len[r] = base + len(toks)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        s = StepInputs(input_ids=i32(ids), positions=i32(pos), slot_mapping=i32(slots), cu_seqlens=i32(cu), past_lens=i32(past),
+                       block_table=self.block_table[rows_used].contiguous() if len(rows_used) != self.rows else self.block_table,
+                       logits_rows=None if want_all_logits else i32(last),
+                       max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds)
+        return self.decoder.forward(s, self.kv), rows_used
+
+    def rewind(self, row: int, length: int):
+        self.kv_len[row] = min(self.kv_len[row], length)
+
+    def reorder_rows(self, src_rows: List[int]):
+        """Beam search: row r continues from the cache of row src_rows[r]."""
+        if all(r == s for r, s in enumerate(src_rows)):
+            return
+        span = self.blocks_per_row * self.block_size
+        n = max(self.kv_len)
+        idx_dst, idx_src = [], []
+        for r, s in enumerate(src_rows):
+            if r != s:
+                idx_dst.append(torch.arange(r * span, r * span + n))
+                idx_src.append(torch.arange(s * span, s * span + n))
+        if idx_dst:
+            d = torch.cat(idx_dst).to(self.kv.full.device)
+            sidx = torch.cat(idx_src).to(self.kv.full.device)
+            self.kv.full[:, :, d] = self.kv.full[:, :, sidx]
+        self.kv_len = [self.kv_len[s] for s in src_rows]
+
+
+class Generator:
+    def __init__(self, model: Model, params: GeneratorParams):
+        self.model = model
+        self.params = params
+        s = dict(params.search)
+        cfg = model.config
+        if s["max_length"] > cfg.context_length:
+            raise RuntimeError(f"max_length ({s['max_length']}) cannot be greater than model context_length ({cfg.context_length})")
+        if not (1 <= s["batch_size"] <= 32 * 64):
+            raise RuntimeError("batch_size must be >= 1")
+        if not (1 <= s["num_beams"] <= 32):
+            raise RuntimeError("num_beams must be between 1 and 32")
+        if s["num_return_sequences"] > s["num_beams"] and s["num_beams"] > 1:
+            raise RuntimeError("num_return_sequences cannot exceed num_beams")
+        self.search_opts = s
+        self.method, self.k, self.p, self.t = _sampling_method(s, cfg.vocab_size)
+        sp = native.SearchParams()
+        sp.batch_size, sp.num_beams, sp.num_return_sequences = s["batch_size"], s["num_beams"], s["num_return_sequences"]
+        sp.max_length, sp.min_length, sp.vocab_size = s["max_length"], s["min_length"], cfg.vocab_size
+        sp.pad_token_id, sp.eos_token_ids = cfg.pad_token_id, list(cfg.eos_token_ids)
+        sp.repetition_penalty, sp.no_repeat_ngram_size = s["repetition_penalty"], s["no_repeat_ngram_size"]
+        sp.length_penalty, sp.early_stopping, sp.random_seed = s["length_penalty"], s["early_stopping"], s["random_seed"]
+        self._sp = sp
+        self.search = native.Search(sp)
+        self.rows = s["batch_size"] * s["num_beams"]
+        self.state = SequenceState(model.decoder, self.rows, s["max_length"])
+        self._logits: Optional[torch.Tensor] = None
+        self._fresh = False
+        self._started = False
+        self._seed = s["random_seed"] if s["random_seed"] >= 0 else int.from_bytes(os.urandom(4), "little")
+        self._guidance = None
+        if params.guidance_type:
+            from .guidance import GuidanceProcessor
+            self._guidance = GuidanceProcessor(model, params.guidance_type, params.guidance_data, s["batch_size"],
+                                               params.guidance_ff_tokens)
+        self._strategy = None
+        spec = params.speculative
+        if model.draft is not None or spec.get("ngram_size", 0) > 0:
+            from .speculative import make_strategy
+            self._strategy = make_strategy(self, spec)
+        self._runtime_options: Dict[str, str] = {}
+        self._terminated = False
+
+    # ------------------------------------------------------------------ tokens in
+    def append_tokens(self, tokens):
+        with _Trace("generator", "append_tokens"):
+            if isinstance(tokens, Tensor):
+                tokens = tokens.as_numpy()
+            arr = np.asarray(tokens, dtype=np.int32)
+            if arr.ndim == 1:
+                arr = arr.reshape(1, -1)
+            B = self.search_opts["batch_size"]
+            if arr.shape[0] != B:
+                raise RuntimeError(f"append_tokens: expected {B} rows, got {arr.shape[0]}")
+            if arr.shape[1] == 0:
+                raise RuntimeError("append_tokens: empty token list")
+            if self._started and B > 1:
+                raise RuntimeError("continuous decoding (append after generate) requires batch_size 1")
+            if native.log_flag("append_next_tokens"):
+                native.log_write("append_next_tokens", str(arr.tolist()))
+            self.search.append_tokens(arr)
+            pad = self.model.config.pad_token_id
+            nb = self.search_opts["num_beams"]
+            row_tokens: List[List[int]] = []
+            for b in range(B):
+                toks = arr[b].tolist()
+                if not self._started and B > 1:  # padded batch: pad tokens are not fed to the model
+                    while len(toks) > 1 and toks[-1] == pad:
+                        toks.pop()
+                    while len(toks) > 1 and toks[0] == pad:
+                        toks.pop(0)
+                for _ in range(nb):
+                    row_tokens.append(list(toks))
+            if self._started and self._unfed_last:
+                # the last generated token has not been through the model yet
+                last = self.search.next_tokens().tolist()
+                row_tokens = [[last[r]] + row_tokens[r] for r in range(self.rows)]
+                self._unfed_last = False
+            if self._guidance is not None:
+                self._guidance.commit_prompt(arr)
+            if self._strategy is not None:
+                self._strategy.on_append(arr)
+            self._compute_logits(row_tokens)
+            self._started = True
+
+    _unfed_last = False  # True while the newest token has not been run through the model
+
+    def _compute_logits(self, row_tokens: List[List[int]]):
+        chunk = int(self.search_opts.get("chunk_size") or 0)
+        with _Trace("model", "run"), torch.no_grad():
+            if chunk > 0:
+                longest = max(len(t) for t in row_tokens)
+                logits = None
+                for c0 in range(0, longest, chunk):
+                    part = [t[c0:c0 + chunk] for t in row_tokens]
+                    out, used = self.state.run(part)
+                    if logits is None:
+                        logits = torch.empty(self.rows, out.shape[1], dtype=torch.float32, device=out.device)
+                    logits[used] = out
+            else:
+                logits, used = self.state.run(row_tokens)
+                if len(used) != self.rows:
+                    full = torch.empty(self.rows, logits.shape[1], dtype=torch.float32, device=logits.device)
+                    full[used] = logits
+                    logits = full
+        self._logits = logits
+        self._fresh = True
+
+    # ------------------------------------------------------------------ one step
+    def generate_next_token(self):
+        with _Trace("generator", "generate_next_token"):
+            if self._terminated:
+                raise RuntimeError("session terminated")
+            if self.search.is_done:
+                return
+            if not self._started:
+                raise RuntimeError("generate_next_token called before append_tokens")
+            if self._strategy is not None:
+                self._strategy.step()
+                return
+            self._standard_step()
+
+    def _ensure_logits(self):
+        if not self._fresh:
+            last = self.search.next_tokens().tolist()
+            self._compute_logits([[t] for t in last])
+            self._unfed_last = False
+
+    def _standard_step(self):
+        self._ensure_logits()
+        logits = self._logits
+        so = self.search_opts
+        if self._guidance is not None:
+            logits = self._guidance.apply(logits)
+        on_cpu = not logits.is_cuda
+        if on_cpu:
+            arr = np.ascontiguousarray(logits.float().numpy())
+            self.search.score(arr, "beam" if so["num_beams"] > 1 else self.method, self.k, self.p, self.t)
+            if so["num_beams"] > 1:
+                self.state.reorder_rows(self.search.beam_rows().tolist())
+        else:
+            self._device_step(logits)
+        self._fresh = False
+        self._unfed_last = True
+        toks = self.search.next_tokens()
+        if self._guidance is not None:
+            self._guidance.commit_tokens(toks)
+        if native.log_flag("generate_next_token"):
+            native.log_write("generate_next_token", str(toks.tolist()))
+        if self.search.is_done and native.log_flag("hit_eos"):
+            native.log_write("hit_eos", "generation finished")
+
+    def _device_step(self, logits: torch.Tensor):
+        so = self.search_opts
+        dev = logits.device
+        need_edit = so["min_length"] > 0 or so["repetition_penalty"] != 1.0 or so["no_repeat_ngram_size"] > 0
+        if need_edit:
+            logits = logits.clone() if logits is self._logits else logits
+            self._apply_penalties_device(logits)
+        if so["num_beams"] > 1:
+            scores = torch.from_numpy(self.search.beam_scores()).to(dev)
+            cs, ct, cb = ops.beam_candidates(logits, scores, so["batch_size"], so["num_beams"])
+            self.search.commit_beam_step(cs.cpu().numpy(), ct.cpu().numpy(), cb.cpu().numpy())
+            self.state.reorder_rows(self.search.beam_rows().tolist())
+            return
+        R = self.rows
+        if self.method == "greedy":
+            toks = ops.argmax(logits)
+        else:
+            k = torch.full((R,), self.k if self.k > 0 else -1, dtype=torch.int32, device=dev)
+            p = torch.full((R,), self.p, dtype=torch.float32, device=dev)
+            t = torch.full((R,), self.t, dtype=torch.float32, device=dev)
+            seeds = (torch.arange(R, dtype=torch.int64, device=dev) * 0x9E3779B97F4A7C15 % (1 << 62)) + self._seed
+            pos = torch.full((R,), self.search.length, dtype=torch.int32, device=dev)
+            toks = ops.sample(logits, k, p, t, seeds, pos)
+        self.search.commit_tokens(toks.cpu().numpy())
+
+    def _apply_penalties_device(self, logits: torch.Tensor):
+        """Builds the sparse edit list on the host from the sequences and applies it in one kernel."""
+        so = self.search_opts
+        rows, toks, opsl, vals = [], [], [], []
+        cur = self.search.length
+        eos = list(self.model.config.eos_token_ids)
+        for r in range(self.rows):
+            seq = self.search.sequence(r)
+            if cur < so["min_length"]:
+                for e in eos:
+                    rows.append(r); toks.append(e); opsl.append(0); vals.append(0.0)
+            if so["repetition_penalty"] != 1.0:
+                for tkn in np.unique(seq).tolist():
+                    rows.append(r); toks.append(tkn); opsl.append(1); vals.append(float(so["repetition_penalty"]))
+            if so["no_repeat_ngram_size"] > 0:
+                for tkn in native.no_repeat_ngram_banned(seq, so["no_repeat_ngram_size"], logits.shape[1]):
+                    rows.append(r); toks.append(tkn); opsl.append(0); vals.append(0.0)
+        if not rows:
+            return
+        dev = logits.device
+        # repetition penalty first, then bans: order inside one launch is irrelevant because a ban wins anyway
+        order = np.argsort(np.asarray(opsl), kind="stable")[::-1]
+        i32 = lambda x: torch.tensor(np.asarray(x)[order], dtype=torch.int32, device=dev)
+        pen = [i for i in range(len(opsl)) if opsl[i] == 1]
+        ban = [i for i in range(len(opsl)) if opsl[i] == 0]
+        for sel in (pen, ban):
+            if sel:
+                ops.logits_edit(logits, torch.tensor([rows[i] for i in sel], dtype=torch.int32, device=dev),
+                                torch.tensor([toks[i] for i in sel], dtype=torch.int32, device=dev),
+                                torch.tensor([opsl[i] for i in sel], dtype=torch.int32, device=dev),
+                                torch.tensor([vals[i] for i in sel], dtype=torch.float32, device=dev))
+
+    # ------------------------------------------------------------------ accessors
+    def is_done(self) -> bool:
+        return bool(self.search.is_done)
+
+    def get_next_tokens(self) -> np.ndarray:
+        return self.search.next_tokens()
+
+    def get_sequence(self, index: int) -> np.ndarray:
+        so = self.search_opts
+        if so["num_beams"] > 1 and self.search.is_done:
+            self.search.finalize()
+            b, rank = divmod(index, so["num_return_sequences"])
+            return self.search.hypothesis(b, rank)[0]
+        return self.search.sequence(index)
+
+    def token_count(self) -> int:
+        return int(self.search.length)
+
+    def get_logits(self) -> np.ndarray:
+        self._ensure_logits()
+        return self._logits.detach().float().cpu().numpy().reshape(self.rows, 1, -1)
+
+    def set_logits(self, new_logits):
+        arr = np.asarray(new_logits, dtype=np.float32).reshape(self.rows, -1)
+        if arr.shape[1] != self.model.config.vocab_size:
+            raise RuntimeError("set_logits: last dimension must equal vocab_size")
+        self._logits = torch.from_numpy(arr.copy()).to(self.model.device)
+        self._fresh = True
+
+    def rewind_to(self, length: int):
+        if self.search_opts["batch_size"] > 1 and length != 0:
+            raise RuntimeError("rewind_to a non-zero length requires batch_size 1")
+        if length > self.search.length:
+            raise RuntimeError("rewind_to: length exceeds the current sequence length")
+        self.search.rewind_to(int(length))
+        for r in range(self.rows):
+            self.state.rewind(r, int(length))
+        self._fresh = False
+        self._unfed_last = False
+        if length == 0:
+            self._started = False
+        else:
+            # the token at position length-1 must be fed again to produce logits
+            self.state.rewind(0, int(length) - 1)
+            last = int(self.search.sequence(0)[-1])
+            self._compute_logits([[last]])
+        if self._guidance is not None:
+            self._guidance.reset()
+        if self._strategy is not None:
+            self._strategy.on_rewind(int(length))
+
+    def get_input(self, name: str):
+        if name == "input_ids":
+            return self.search.next_tokens()
+        raise RuntimeError(f"unknown model input: {name}")
+
+    def get_output(self, name: str):
+        if name == "logits":
+            return self.get_logits()
+        if name == "hidden_states":
+            return self.model.decoder.last_hidden.detach().float().cpu().numpy()
+        raise RuntimeError(f"unknown model output: {name}")
+
+    def set_inputs(self, named: NamedTensors):
+        self._extra_inputs = dict(named)
+
+    def set_model_input(self, name: str, tensor):
+        self._extra_inputs = getattr(self, "_extra_inputs", {})
+        self._extra_inputs[name] = tensor
+
+    def set_active_adapter(self, adapters, name: str):
+        adapters._activate(self.model, name)
+
+    def set_runtime_option(self, key: str, value: str):
+        if key == "terminate_session":
+            self._terminated = value in ("1", "true", True)
+        elif key == "enable_profiling":
+            if value not in ("0", "", False):
+                native.trace_enable("" if value in ("1", True) else str(value))
+            else:
+                native.trace_disable()
+        else:
+            raise RuntimeError(f"Unknown runtime option: {key}")
+        self._runtime_options[key] = str(value)
+
+    def get_speculative_stats(self) -> Dict[str, Any]:
+        if self._strategy is None:
+            return {}
+        return self._strategy.stats()

@@ -1,0 +1,245 @@
+"""Architecture description of a decoder-only transformer.
+
+One dataclass covers the model families the reference's registry lists as LLM types
+(src/models/model_type.h:20): llama, mistral, qwen2, qwen3, phi3, phi, gemma/gemma2/gemma3, granite,
+olmo, smollm3, internlm2, ernie4_5, nemotron, chatglm, gptoss (mixture of experts) ...  A family
+is a set of flag values, not a class.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import asdict, dataclass, field
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+
+LLM_TYPES = [
+    "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
+    "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
+    "smollm3", "lfm2", "gpt2", "helium", "exaone",
+]
+
+
+@dataclass
+class ArchConfig:
+    model_type: str = "llama"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 32
+    head_dim: int = 128
+    intermediate_size: int = 11008
+    context_length: int = 4096
+    # normalisation
+    norm_eps: float = 1e-5
+    layernorm: bool = False          # LayerNorm (mean/var, bias) instead of RMSNorm
+    norm_offset: float = 0.0         # gemma stores weight - 1; the exporter bakes the offset in
+    post_sublayer_norms: bool = False  # gemma2/3: extra norms after attention and MLP outputs
+    qk_norm: bool = False            # qwen3 / gemma3: per-head RMSNorm on q and k before RoPE
+    # rotary embedding
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[Dict[str, Any]] = None
+    partial_rotary_factor: float = 1.0
+    rotary_interleaved: bool = False
+    # attention
+    attn_bias: bool = False          # bias on q/k/v projections
+    o_bias: bool = False
+    attn_scale: Optional[float] = None  # default 1/sqrt(head_dim)
+    softcap: float = 0.0
+    sliding_window: int = 0
+    sliding_layers: Optional[List[int]] = None  # None + sliding_window > 0 = every layer
+    attn_sinks: bool = False
+    # MLP
+    mlp_bias: bool = False
+    activation: str = "silu"         # silu | gelu
+    # mixture of experts (gpt-oss style)
+    num_experts: int = 0
+    experts_per_token: int = 0
+    moe_swiglu_alpha: float = 1.702
+    moe_swiglu_limit: float = 7.0
+    # embedding / head
+    embed_scale: float = 1.0
+    tie_embeddings: bool = False
+    lm_head_bias: bool = False
+    final_logit_softcap: float = 0.0
+    # multipliers (granite)
+    residual_multiplier: float = 1.0
+    logits_scale: float = 1.0
+    # token ids
+    bos_token_id: int = 1
+    eos_token_id: Any = 2
+    pad_token_id: int = 0
+
+    @property
+    def rotary_dim(self) -> int:
+        r = int(self.head_dim * self.partial_rotary_factor)
+        return r - (r % 2)
+
+    @property
+    def q_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def scale(self) -> float:
+        return self.attn_scale if self.attn_scale is not None else 1.0 / math.sqrt(self.head_dim)
+
+    def layer_window(self, layer: int) -> int:
+        if self.sliding_window <= 0:
+            return 0
+        if self.sliding_layers is None:
+            return self.sliding_window
+        return self.sliding_window if layer in self.sliding_layers else 0
+
+    def eos_list(self) -> List[int]:
+        return list(self.eos_token_id) if isinstance(self.eos_token_id, (list, tuple)) else [int(self.eos_token_id)]
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+
+def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
+    """Maps a Hugging Face `config.json` dictionary to an ArchConfig."""
+    archs = cfg.get("architectures") or [cfg.get("model_type", "llama")]
+    name = archs[0]
+    mtype = name.split("For")[0].lower() if "For" in name else cfg.get("model_type", name).lower()
+    hs = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    a = ArchConfig(
+        model_type=mtype,
+        vocab_size=cfg["vocab_size"],
+        hidden_size=hs,
+        num_layers=cfg["num_hidden_layers"],
+        num_heads=nh,
+        num_kv_heads=cfg.get("num_key_value_heads", nh),
+        head_dim=cfg.get("head_dim") or hs // nh,
+        intermediate_size=cfg.get("intermediate_size", 4 * hs),
+        context_length=cfg.get("max_position_embeddings", 4096),
+        norm_eps=cfg.get("rms_norm_eps", cfg.get("layer_norm_eps", cfg.get("layer_norm_epsilon", 1e-5))),
+        rope_theta=cfg.get("rope_theta", 10000.0),
+        rope_scaling=cfg.get("rope_scaling"),
+        partial_rotary_factor=cfg.get("partial_rotary_factor", 1.0),
+        attn_bias=bool(cfg.get("attention_bias", False)),
+        mlp_bias=bool(cfg.get("mlp_bias", False)),
+        tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        bos_token_id=cfg.get("bos_token_id") or 0,
+        eos_token_id=cfg.get("eos_token_id") if cfg.get("eos_token_id") is not None else 0,
+        pad_token_id=cfg.get("pad_token_id") if cfg.get("pad_token_id") is not None else 0,
+    )
+    mt = cfg.get("model_type", mtype)
+    if mt == "qwen2":
+        a.attn_bias = True
+    if mt in ("qwen3", "gemma3_text", "olmo2"):
+        a.qk_norm = mt != "olmo2" or True
+    if mt in ("mistral", "qwen2", "phi3") and cfg.get("sliding_window") and cfg.get("use_sliding_window", mt != "qwen2"):
+        a.sliding_window = int(cfg["sliding_window"])
+    if mt.startswith("gemma"):
+        a.embed_scale = math.sqrt(hs)
+        a.activation = "gelu"
+        a.norm_offset = 1.0
+        a.tie_embeddings = True
+        if mt in ("gemma2", "gemma3_text"):
+            a.post_sublayer_norms = True
+            a.softcap = cfg.get("attn_logit_softcapping") or 0.0
+            a.final_logit_softcap = cfg.get("final_logit_softcapping") or 0.0
+            if cfg.get("query_pre_attn_scalar"):
+                a.attn_scale = 1.0 / math.sqrt(cfg["query_pre_attn_scalar"])
+            sw = cfg.get("sliding_window") or 0
+            if sw:
+                a.sliding_window = sw
+                pattern = cfg.get("sliding_window_pattern", 2 if mt == "gemma2" else 6)
+                a.sliding_layers = [i for i in range(a.num_layers) if (i + 1) % pattern != 0]
+    if mt in ("gpt_oss", "gptoss"):
+        a.model_type = "gptoss"
+        a.num_experts = cfg.get("num_local_experts", 32)
+        a.experts_per_token = cfg.get("num_experts_per_tok", cfg.get("experts_per_token", 4))
+        a.attn_sinks = True
+        a.attn_bias = a.o_bias = a.mlp_bias = True
+        a.sliding_window = cfg.get("sliding_window", 128)
+        lt = cfg.get("layer_types")
+        a.sliding_layers = ([i for i, t in enumerate(lt) if t == "sliding_attention"] if lt
+                            else [i for i in range(a.num_layers) if i % 2 == 0])
+        a.moe_swiglu_limit = cfg.get("swiglu_limit", 7.0)
+    if mt == "granite":
+        a.residual_multiplier = cfg.get("residual_multiplier", 1.0)
+        a.logits_scale = 1.0 / cfg.get("logits_scaling", 1.0)
+        a.embed_scale = cfg.get("embedding_multiplier", 1.0)
+        a.attn_scale = cfg.get("attention_multiplier")
+    if mt == "phi":
+        a.layernorm = True
+        a.activation = "gelu"
+        a.attn_bias = a.o_bias = a.mlp_bias = a.lm_head_bias = True
+    return a
+
+
+# --------------------------------------------------------------------------------------------- RoPE caches
+def rope_caches(arch: ArchConfig, max_positions: Optional[int] = None):
+    """cos/sin caches of shape [positions, rotary_dim/2] (fp32), with the frequency rescaling the
+    reference's exporter applies (default, linear, llama3, yarn; src/python/py/models/builders/
+    base.py:2478-2617, builders/llama.py:15-31)."""
+    n = max_positions or arch.context_length
+    rot = arch.rotary_dim
+    inv_freq = 1.0 / (arch.rope_theta ** (np.arange(0, rot, 2, dtype=np.float64) / rot))
+    attn_factor = 1.0
+    sc = arch.rope_scaling or {}
+    kind = sc.get("rope_type", sc.get("type", "default"))
+    if kind == "linear":
+        inv_freq = inv_freq / float(sc["factor"])
+    elif kind == "llama3":
+        factor = float(sc["factor"])
+        low, high = float(sc.get("low_freq_factor", 1.0)), float(sc.get("high_freq_factor", 4.0))
+        old = float(sc.get("original_max_position_embeddings", 8192))
+        wavelen = 2 * math.pi / inv_freq
+        smooth = (old / wavelen - low) / (high - low)
+        scaled = np.where(wavelen > old / low, inv_freq / factor, inv_freq)
+        mid = (wavelen <= old / low) & (wavelen >= old / high)
+        inv_freq = np.where(mid, (1 - smooth) * inv_freq / factor + smooth * inv_freq, scaled)
+    elif kind == "yarn":
+        factor = float(sc["factor"])
+        old = float(sc.get("original_max_position_embeddings", arch.context_length / factor))
+        beta_fast, beta_slow = float(sc.get("beta_fast", 32)), float(sc.get("beta_slow", 1))
+
+        def corr(num_rot):
+            return (rot * math.log(old / (num_rot * 2 * math.pi))) / (2 * math.log(arch.rope_theta))
+
+        lo, hi = max(math.floor(corr(beta_fast)), 0), min(math.ceil(corr(beta_slow)), rot // 2 - 1)
+        ramp = np.clip((np.arange(rot // 2, dtype=np.float64) - lo) / max(hi - lo, 1e-3), 0, 1)
+        mask = 1.0 - ramp
+        inv_freq = inv_freq / factor * (1 - mask) + inv_freq * mask
+        attn_factor = float(sc.get("attention_factor") or (0.1 * math.log(factor) + 1.0))
+    t = np.arange(n, dtype=np.float64)
+    freqs = np.outer(t, inv_freq)
+    return (np.cos(freqs) * attn_factor).astype(np.float32), (np.sin(freqs) * attn_factor).astype(np.float32)
+
+
+# --------------------------------------------------------------------------------------------- presets
+PRESETS: Dict[str, ArchConfig] = {
+    # BASELINE config 1: tiny Llama-style decoder.
+    "tiny-llama": ArchConfig(model_type="llama", vocab_size=32000, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                             head_dim=64, intermediate_size=512, context_length=2048, norm_eps=1e-5, rope_theta=10000.0,
+                             bos_token_id=1, eos_token_id=2, pad_token_id=0),
+    "phi3-mini": ArchConfig(model_type="phi3", vocab_size=32064, hidden_size=3072, num_layers=32, num_heads=32, num_kv_heads=32,
+                            head_dim=96, intermediate_size=8192, context_length=4096, norm_eps=1e-5, rope_theta=10000.0,
+                            bos_token_id=1, eos_token_id=32000, pad_token_id=32000),
+    "llama-3.1-8b": ArchConfig(model_type="llama", vocab_size=128256, hidden_size=4096, num_layers=32, num_heads=32,
+                               num_kv_heads=8, head_dim=128, intermediate_size=14336, context_length=8192, norm_eps=1e-5,
+                               rope_theta=500000.0, bos_token_id=128000, eos_token_id=[128001, 128008, 128009],
+                               pad_token_id=128001),
+    "llama-3.2-1b": ArchConfig(model_type="llama", vocab_size=128256, hidden_size=2048, num_layers=16, num_heads=32,
+                               num_kv_heads=8, head_dim=64, intermediate_size=8192, context_length=8192, norm_eps=1e-5,
+                               rope_theta=500000.0, bos_token_id=128000, eos_token_id=[128001, 128008, 128009],
+                               pad_token_id=128001, tie_embeddings=True),
+    "llama-3.1-70b": ArchConfig(model_type="llama", vocab_size=128256, hidden_size=8192, num_layers=80, num_heads=64,
+                                num_kv_heads=8, head_dim=128, intermediate_size=28672, context_length=8192, norm_eps=1e-5,
+                                rope_theta=500000.0, bos_token_id=128000, eos_token_id=[128001, 128008, 128009],
+                                pad_token_id=128001),
+    "gpt-oss-20b": ArchConfig(model_type="gptoss", vocab_size=201088, hidden_size=2880, num_layers=24, num_heads=64,
+                              num_kv_heads=8, head_dim=64, intermediate_size=2880, context_length=8192, norm_eps=1e-5,
+                              rope_theta=150000.0, attn_bias=True, o_bias=True, mlp_bias=True, attn_sinks=True,
+                              sliding_window=128, sliding_layers=[i for i in range(24) if i % 2 == 0], num_experts=32,
+                              experts_per_token=4, bos_token_id=199998, eos_token_id=[200002, 199999], pad_token_id=199999),
+}

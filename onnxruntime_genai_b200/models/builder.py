@@ -1,0 +1,606 @@
+"""Checkpoint exporter: architecture + weights -> `genai_config.json` + `model.onnx` + `model.onnx.data`.
+
+The output directory follows the reference builder's contract (src/python/py/models/builder.py:289-589,
+builders/base.py): transposed `[in, out]` MatMul initializers named
+`model.layers.{i}.attn.qkv_proj.MatMul.weight` etc., `SimplifiedLayerNormalization` /
+`SkipSimplifiedLayerNormalization` nodes carrying `epsilon`, a `GroupQueryAttention` (or `PagedAttention`)
+node per layer carrying `num_heads / kv_num_heads / scale / local_window_size / softcap / do_rotary /
+rotary_interleaved`, `cos_cache` / `sin_cache` initializers of shape `[ctx, rot/2]`, MatMulNBits
+int4 block-32 weights as `qweight [N, K/32, 16]` + `scales` + packed uint4 `zero_points`
+(base.py:1963-2022, quantized_model.py:1060-1107), and the `genai_config.json` layout of
+base.py:1033-1128.
+
+CLI:  python -m onnxruntime_genai_b200.models.builder -m <hf_dir | preset> -o <out_dir> -p bf16|fp16|fp32|int4
+          -e cuda|cpu [--extra_options k=v ...]
+
+Extension (not in the reference): `--extra_options synthetic_weights=1` writes initializers whose
+external-data entry carries `synthetic = normal:<std>:<seed>` instead of bytes on disk, so that a
+70B-shaped random-init checkpoint for benchmarking is a few kilobytes; the loader generates those
+tensors on the device.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import sys
+import zlib
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from ..utils import onnx_proto as op
+from .arch import PRESETS, ArchConfig, from_hf_config, rope_caches
+
+_ONNX_DT = {"fp32": op.FLOAT, "fp16": op.FLOAT16, "bf16": op.BFLOAT16}
+_TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+# ---------------------------------------------------------------------------------------------- weights
+def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
+    """Canonical (Hugging Face style, [out, in]) parameter names and shapes."""
+    H, I, V = arch.hidden_size, arch.intermediate_size, arch.vocab_size
+    s: Dict[str, tuple] = {"model.embed_tokens.weight": (V, H)}
+    for i in range(arch.num_layers):
+        p = f"model.layers.{i}."
+        s[p + "input_layernorm.weight"] = (H,)
+        s[p + "post_attention_layernorm.weight"] = (H,)
+        if arch.layernorm:
+            s[p + "input_layernorm.bias"] = (H,)
+            s[p + "post_attention_layernorm.bias"] = (H,)
+        if arch.post_sublayer_norms:
+            s[p + "pre_feedforward_layernorm.weight"] = (H,)
+            s[p + "post_feedforward_layernorm.weight"] = (H,)
+        s[p + "self_attn.q_proj.weight"] = (arch.q_size, H)
+        s[p + "self_attn.k_proj.weight"] = (arch.kv_size, H)
+        s[p + "self_attn.v_proj.weight"] = (arch.kv_size, H)
+        s[p + "self_attn.o_proj.weight"] = (H, arch.q_size)
+        if arch.attn_bias:
+            s[p + "self_attn.q_proj.bias"] = (arch.q_size,)
+            s[p + "self_attn.k_proj.bias"] = (arch.kv_size,)
+            s[p + "self_attn.v_proj.bias"] = (arch.kv_size,)
+        if arch.o_bias:
+            s[p + "self_attn.o_proj.bias"] = (H,)
+        if arch.qk_norm:
+            s[p + "self_attn.q_norm.weight"] = (arch.head_dim,)
+            s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
+        if arch.attn_sinks:
+            s[p + "self_attn.sinks"] = (arch.num_heads,)
+        if arch.num_experts > 0:
+            E = arch.num_experts
+            s[p + "mlp.router.weight"] = (E, H)
+            s[p + "mlp.router.bias"] = (E,)
+            s[p + "mlp.experts.gate_up_proj"] = (E, 2 * I, H)   # rows interleaved gate0, up0, gate1, up1 ...
+            s[p + "mlp.experts.gate_up_proj_bias"] = (E, 2 * I)
+            s[p + "mlp.experts.down_proj"] = (E, H, I)
+            s[p + "mlp.experts.down_proj_bias"] = (E, H)
+        else:
+            s[p + "mlp.gate_proj.weight"] = (I, H)
+            s[p + "mlp.up_proj.weight"] = (I, H)
+            s[p + "mlp.down_proj.weight"] = (H, I)
+            if arch.mlp_bias:
+                s[p + "mlp.gate_proj.bias"] = (I,)
+                s[p + "mlp.up_proj.bias"] = (I,)
+                s[p + "mlp.down_proj.bias"] = (H,)
+    s["model.norm.weight"] = (H,)
+    if arch.layernorm:
+        s["model.norm.bias"] = (H,)
+    if not arch.tie_embeddings:
+        s["lm_head.weight"] = (V, H)
+        if arch.lm_head_bias:
+            s["lm_head.bias"] = (V,)
+    return s
+
+
+def _is_norm_weight(name: str) -> bool:
+    return name.endswith("norm.weight") or name.endswith("layernorm.weight")
+
+
+def tensor_seed(name: str, seed: int) -> int:
+    return (zlib.crc32(name.encode()) ^ (seed * 0x9E3779B1)) & 0x7FFFFFFF
+
+
+def random_tensor(name: str, shape, seed: int, std: float, device="cpu", dtype=torch.float32) -> torch.Tensor:
+    """Deterministic N(0, std) tensor for a parameter name (norm weights are ones, sinks N(0, 1))."""
+    if _is_norm_weight(name):
+        return torch.ones(shape, dtype=dtype, device=device)
+    g = torch.Generator(device=device)
+    g.manual_seed(tensor_seed(name, seed))
+    s = 1.0 if name.endswith(".sinks") or "router" in name else std
+    return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * s).to(dtype)
+
+
+def random_state_dict(arch: ArchConfig, seed: int = 0, std: float = 0.02) -> Dict[str, torch.Tensor]:
+    return {n: random_tensor(n, shp, seed, std) for n, shp in weight_shapes(arch).items()}
+
+
+# ---------------------------------------------------------------------------------------------- int4
+def quantize_int4_block32(w: torch.Tensor, symmetric: bool = False, block: int = 32):
+    """RTN block quantisation in the MatMulNBits layout.  w: [N, K] float.
+    Returns qweight uint8 [N, K/block, block/2] (low nibble = even k), scales fp32 [N, K/block],
+    zero_points uint8 [N, ceil(K/block/2)] packed two per byte (low nibble first) or None."""
+    N, K = w.shape
+    assert K % block == 0
+    wb = w.float().view(N, K // block, block)
+    if symmetric:
+        amax_idx = wb.abs().argmax(-1, keepdim=True)
+        amax = torch.gather(wb, -1, amax_idx)
+        scale = (amax / -8.0).squeeze(-1)
+        scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+        q = torch.clamp(torch.round(wb / scale[..., None]) + 8, 0, 15)
+        zp = None
+    else:
+        mn = torch.minimum(wb.amin(-1), torch.zeros(()))
+        mx = torch.maximum(wb.amax(-1), torch.zeros(()))
+        scale = (mx - mn) / 15.0
+        scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+        zpf = torch.clamp(torch.round(-mn / scale), 0, 15)
+        q = torch.clamp(torch.round(wb / scale[..., None]) + zpf[..., None], 0, 15)
+        zp = zpf.to(torch.uint8)
+    q = q.to(torch.uint8)
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).contiguous()
+    zp_packed = None
+    if zp is not None:
+        nb = K // block
+        if nb % 2:
+            zp = torch.cat([zp, torch.full((N, 1), 8, dtype=torch.uint8)], dim=1)
+        zp_packed = (zp[:, 0::2] | (zp[:, 1::2] << 4)).contiguous()
+    return packed, scale, zp_packed
+
+
+def dequantize_int4_block32(qweight, scales, zero_points, N: int, K: int, block: int = 32) -> torch.Tensor:
+    """Inverse of quantize_int4_block32: returns fp32 [N, K] with w = (q - zp) * scale."""
+    q = torch.as_tensor(qweight).view(N, K // block, block // 2)
+    lo, hi = (q & 0xF).float(), (q >> 4).float()
+    w = torch.stack([lo, hi], dim=-1).view(N, K // block, block)
+    nb = K // block
+    if zero_points is not None:
+        z = torch.as_tensor(zero_points).view(N, -1)
+        zz = torch.stack([(z & 0xF), (z >> 4)], dim=-1).view(N, -1)[:, :nb].float()
+    else:
+        zz = torch.full((N, nb), 8.0)
+    s = torch.as_tensor(scales).float().view(N, nb)
+    return ((w - zz[..., None]) * s[..., None]).view(N, K)
+
+
+# ---------------------------------------------------------------------------------------------- export
+class _Writer:
+    def __init__(self, out_dir: str, precision: str, synthetic: bool, seed: int, std: float):
+        self.model = op.Model()
+        self.precision = precision
+        self.io = "fp32" if precision == "fp32" else ("bf16" if precision in ("bf16", "int4") else "fp16")
+        self.ext = None if synthetic else op.ExternalDataWriter(os.path.join(out_dir, "model.onnx.data"))
+        self.synthetic = synthetic
+        self.seed, self.std = seed, std
+
+    def add_array(self, name: str, arr: np.ndarray, onnx_dtype: int, dims=None):
+        if self.ext is None:
+            t = op.Tensor(name=name, dtype=onnx_dtype, dims=tuple(dims if dims is not None else arr.shape),
+                          raw=np.ascontiguousarray(arr).tobytes())
+        else:
+            t = self.ext.add(name, onnx_dtype, arr, dims)
+        self.model.initializers[name] = t
+
+    def add_float(self, name: str, t: torch.Tensor, force_fp32: bool = False):
+        prec = "fp32" if force_fp32 else self.io
+        tt = t.detach().to(_TORCH_DT[prec]).contiguous()
+        arr = tt.view(torch.int16).numpy() if prec == "bf16" else tt.numpy()
+        self.add_array(name, arr, _ONNX_DT[prec], dims=tuple(tt.shape))
+
+    def add_synthetic(self, name: str, shape, kind: str):
+        t = op.Tensor(name=name, dtype=_ONNX_DT[self.io], dims=tuple(shape))
+        t.ext_location = "synthetic"
+        t.ext_offset = 0
+        t.ext_length = 0
+        t.raw = None
+        self.model.initializers[name] = t
+
+    def node(self, op_type, name, inputs, outputs, domain="", **attrs):
+        self.model.nodes.append(op.Node(op_type=op_type, name=name, inputs=list(inputs), outputs=list(outputs), domain=domain, attrs=attrs))
+
+
+def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execution_provider: str = "cuda",
+                 state_dict: Optional[Dict[str, torch.Tensor]] = None, seed: int = 0, std: float = 0.02,
+                 paged: bool = False, block_size: int = 16, max_batch_size: int = 64, int4_symmetric: bool = False,
+                 synthetic_weights: bool = False, search: Optional[dict] = None, engine: Optional[dict] = None,
+                 filename: str = "model.onnx", write_config: bool = True, speculative: Optional[dict] = None,
+                 draft_dir_entry: Optional[dict] = None, num_blocks: Optional[int] = None,
+                 max_scheduled_tokens: Optional[int] = None, context_length: Optional[int] = None) -> str:
+    """Writes a checkpoint directory.  With state_dict=None the weights are random N(0, std) from `seed`."""
+    os.makedirs(out_dir, exist_ok=True)
+    if precision not in ("fp32", "fp16", "bf16", "int4"):
+        raise ValueError(f"unsupported precision {precision}")
+    if context_length:
+        arch.context_length = context_length
+    if synthetic_weights and precision == "int4":
+        raise ValueError("synthetic_weights cannot be combined with int4")
+    W = _Writer(out_dir, precision, synthetic_weights, seed, std)
+    shapes = weight_shapes(arch)
+
+    def get(name: str) -> torch.Tensor:
+        if state_dict is not None:
+            if name == "lm_head.weight" and name not in state_dict:
+                return state_dict["model.embed_tokens.weight"]
+            return state_dict[name]
+        return random_tensor(name, shapes[name], seed, std)
+
+    synth_meta: Dict[str, dict] = {}
+
+    def put_plain(onnx_name: str, src_names, transform=None, force_fp32=False):
+        """Adds an initializer built from canonical tensors (or a synthetic descriptor)."""
+        if synthetic_weights:
+            W.add_synthetic(onnx_name, transform["shape"], "")
+            synth_meta[onnx_name] = {"sources": src_names, "op": transform["op"], "seed": seed, "std": std}
+            return
+        ts = [get(n) for n in src_names]
+        W.add_float(onnx_name, transform["fn"](ts), force_fp32)
+
+    def put_linear(base: str, node_name: str, src_names, inp: str, out: str, N: int, K: int):
+        """A linear layer y = x @ W^T from one or more stacked [n_i, K] canonical weights."""
+        if precision == "int4" and not synthetic_weights:
+            w = torch.cat([get(n).float() for n in src_names], dim=0)
+            q, s, zp = quantize_int4_block32(w, symmetric=int4_symmetric)
+            W.add_array(base + ".MatMul.weight_Q4", q.numpy(), op.UINT8)
+            W.add_array(base + ".MatMul.weight_scales", s.reshape(-1).to(torch.float16).numpy(), op.FLOAT16)
+            ins = [inp, base + ".MatMul.weight_Q4", base + ".MatMul.weight_scales"]
+            if zp is not None:
+                W.add_array(base + ".MatMul.weight_zp", zp.reshape(-1).numpy(), op.UINT8)
+                ins.append(base + ".MatMul.weight_zp")
+            W.node("MatMulNBits", node_name + "_Q4", ins, [out], domain="com.microsoft", K=K, N=N, bits=4, block_size=32,
+                   accuracy_level=4)
+        else:
+            put_plain(base + ".MatMul.weight", src_names,
+                      {"shape": (K, N), "op": "cat_t", "fn": lambda ts: torch.cat([t.float() for t in ts], 0).t().contiguous()})
+            W.node("MatMul", node_name, [inp, base + ".MatMul.weight"], [out])
+
+    def put_vec(onnx_name: str, src_names, offset: float = 0.0):
+        if synthetic_weights:
+            shp = (sum(shapes[n][0] for n in src_names),)
+            W.add_synthetic(onnx_name, shp, "")
+            synth_meta[onnx_name] = {"sources": src_names, "op": "cat", "seed": seed, "std": std, "offset": offset}
+            return
+        W.add_float(onnx_name, torch.cat([get(n).float() for n in src_names], 0) + offset)
+
+    H, I, V, L = arch.hidden_size, arch.intermediate_size, arch.vocab_size, arch.num_layers
+    io_dt = _ONNX_DT[W.io]
+
+    # ---- embedding
+    put_plain("model.embed_tokens.weight", ["model.embed_tokens.weight"],
+              {"shape": (V, H), "op": "id", "fn": lambda ts: ts[0].float()})
+    W.node("Gather", "/model/embed_tokens/Gather", ["model.embed_tokens.weight", "input_ids"], ["/model/embed_tokens/Gather/output_0"])
+    hidden = "/model/embed_tokens/Gather/output_0"
+    if arch.embed_scale != 1.0:
+        W.model.initializers["/model/constants/embed_scale"] = op.Tensor("/model/constants/embed_scale", op.FLOAT, (),
+                                                                         raw=np.float32(arch.embed_scale).tobytes())
+        W.node("Mul", "/model/embed_tokens/Mul", [hidden, "/model/constants/embed_scale"], ["/model/embed_tokens/Mul/output_0"])
+        hidden = "/model/embed_tokens/Mul/output_0"
+
+    # ---- rotary caches
+    cos, sin = rope_caches(arch)
+    W.add_float("cos_cache", torch.from_numpy(cos), force_fp32=(precision == "fp32"))
+    W.add_float("sin_cache", torch.from_numpy(sin), force_fp32=(precision == "fp32"))
+
+    norm_op = "LayerNormalization" if arch.layernorm else "SimplifiedLayerNormalization"
+    skip_op = "SkipLayerNormalization" if arch.layernorm else "SkipSimplifiedLayerNormalization"
+    attn_op = "PagedAttention" if paged else "GroupQueryAttention"
+    residual = None
+    for i in range(L):
+        p, n = f"model.layers.{i}.", f"/model/layers.{i}"
+        # input norm
+        put_vec(p + "input_layernorm.weight", [p + "input_layernorm.weight"], arch.norm_offset)
+        ins = [hidden, p + "input_layernorm.weight"] if residual is None else [hidden, residual, p + "input_layernorm.weight"]
+        if arch.layernorm:
+            put_vec(p + "input_layernorm.bias", [p + "input_layernorm.bias"])
+            ins.append(p + "input_layernorm.bias")
+        outs = [f"{n}/input_layernorm/output_0"] + ([] if residual is None else ["", "", f"{n}/input_layernorm/output_3"])
+        W.node(norm_op if residual is None else skip_op, f"{n}/input_layernorm/{'LayerNorm' if residual is None else 'SkipLayerNorm'}",
+               ins, outs, domain="" if residual is None else "com.microsoft", epsilon=float(arch.norm_eps),
+               **({"axis": -1, "stash_type": 1} if residual is None else {}))
+        residual = hidden if residual is None else f"{n}/input_layernorm/output_3"
+        x = f"{n}/input_layernorm/output_0"
+        # attention
+        qkv_out = f"{n}/attn/qkv_proj/MatMul/output_0"
+        put_linear(p + "attn.qkv_proj", f"{n}/attn/qkv_proj/MatMul",
+                   [p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"], x, qkv_out,
+                   arch.q_size + 2 * arch.kv_size, H)
+        if arch.attn_bias:
+            put_vec(p + "attn.qkv_proj.Add.bias", [p + "self_attn.q_proj.bias", p + "self_attn.k_proj.bias", p + "self_attn.v_proj.bias"])
+            W.node("Add", f"{n}/attn/qkv_proj/Add", [qkv_out, p + "attn.qkv_proj.Add.bias"], [f"{n}/attn/qkv_proj/Add/output_0"])
+            qkv_out = f"{n}/attn/qkv_proj/Add/output_0"
+        attn_inputs = [qkv_out, "", ""]
+        if paged:
+            attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "cumulative_sequence_lengths",
+                            "past_sequence_lengths", "block_table_windowed" if arch.layer_window(i) else "block_table",
+                            "cos_cache", "sin_cache", ""]
+        else:
+            attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "/model/attn_mask_reformat/seqlens_k",
+                            "/model/attn_mask_reformat/total_seq_len", "cos_cache", "sin_cache", "", ""]
+        if arch.attn_sinks:
+            put_plain(p + "attn.sinks", [p + "self_attn.sinks"], {"shape": (arch.num_heads,), "op": "id", "fn": lambda ts: ts[0].float()})
+            attn_inputs.append(p + "attn.sinks")
+        else:
+            attn_inputs.append("")
+        if arch.qk_norm:
+            put_vec(p + "attn.q_norm.layernorm.weight", [p + "self_attn.q_norm.weight"], arch.norm_offset)
+            put_vec(p + "attn.k_norm.layernorm.weight", [p + "self_attn.k_norm.weight"], arch.norm_offset)
+            attn_inputs += ["", ""] if not paged else []
+            attn_inputs += [p + "attn.q_norm.layernorm.weight", p + "attn.k_norm.layernorm.weight"]
+        attrs = dict(num_heads=arch.num_heads, kv_num_heads=arch.num_kv_heads, scale=float(arch.scale),
+                     local_window_size=int(arch.layer_window(i)) if arch.layer_window(i) else -1, softcap=float(arch.softcap),
+                     do_rotary=1, rotary_interleaved=int(arch.rotary_interleaved))
+        if arch.qk_norm:
+            attrs["qk_norm_epsilon"] = float(arch.norm_eps)
+        if arch.rotary_dim != arch.head_dim:
+            attrs["rotary_embedding_dim"] = int(arch.rotary_dim)
+        W.node(attn_op, f"{n}/attn/{attn_op}", attn_inputs, [f"{n}/attn/{attn_op}/output_0", f"present.{i}.key", f"present.{i}.value"],
+               domain="com.microsoft", **attrs)
+        o_out = f"{n}/attn/o_proj/MatMul/output_0"
+        put_linear(p + "attn.o_proj", f"{n}/attn/o_proj/MatMul", [p + "self_attn.o_proj.weight"], f"{n}/attn/{attn_op}/output_0", o_out,
+                   H, arch.q_size)
+        if arch.o_bias:
+            put_vec(p + "attn.o_proj.Add.bias", [p + "self_attn.o_proj.bias"])
+            W.node("Add", f"{n}/attn/o_proj/Add", [o_out, p + "attn.o_proj.Add.bias"], [f"{n}/attn/o_proj/Add/output_0"])
+            o_out = f"{n}/attn/o_proj/Add/output_0"
+        if arch.post_sublayer_norms:
+            put_vec(p + "post_attention_layernorm.weight", [p + "post_attention_layernorm.weight"], arch.norm_offset)
+            W.node(norm_op, f"{n}/post_attention_layernorm/LayerNorm", [o_out, p + "post_attention_layernorm.weight"],
+                   [f"{n}/post_attention_layernorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1)
+            o_out = f"{n}/post_attention_layernorm/output_0"
+            mid_name = "pre_feedforward_layernorm"
+        else:
+            mid_name = "post_attention_layernorm"
+        # norm before the MLP (adds the attention output to the residual stream)
+        put_vec(p + mid_name + ".weight", [p + mid_name + ".weight"], arch.norm_offset)
+        ins = [o_out, residual, p + mid_name + ".weight"]
+        if arch.layernorm:
+            put_vec(p + mid_name + ".bias", [p + mid_name + ".bias"])
+            ins.append(p + mid_name + ".bias")
+        W.node(skip_op, f"{n}/{mid_name}/SkipLayerNorm", ins, [f"{n}/{mid_name}/output_0", "", "", f"{n}/{mid_name}/output_3"],
+               domain="com.microsoft", epsilon=float(arch.norm_eps))
+        residual = f"{n}/{mid_name}/output_3"
+        x = f"{n}/{mid_name}/output_0"
+        # MLP / MoE
+        if arch.num_experts > 0:
+            E = arch.num_experts
+            put_linear(p + "moe.router", f"{n}/moe/router/MatMul", [p + "mlp.router.weight"], x, f"{n}/moe/router/MatMul/output_0", E, H)
+            put_vec(p + "moe.router.Add.bias", [p + "mlp.router.bias"])
+            W.node("Add", f"{n}/moe/router/Add", [f"{n}/moe/router/MatMul/output_0", p + "moe.router.Add.bias"], [f"{n}/moe/router/Add/output_0"])
+            for nm, shape in (("gate_up_proj", (E, 2 * I, H)), ("down_proj", (E, H, I))):
+                put_plain(p + f"moe.experts.{nm}.weight", [p + f"mlp.experts.{nm}"], {"shape": shape, "op": "id", "fn": lambda ts: ts[0].float()})
+                put_plain(p + f"moe.experts.{nm}.bias", [p + f"mlp.experts.{nm}_bias"],
+                          {"shape": shape[:2], "op": "id", "fn": lambda ts: ts[0].float()})
+            W.node("MoE", f"{n}/moe/MoE", [x, f"{n}/moe/router/Add/output_0", p + "moe.experts.gate_up_proj.weight",
+                                           p + "moe.experts.gate_up_proj.bias", p + "moe.experts.down_proj.weight",
+                                           p + "moe.experts.down_proj.bias"], [f"{n}/moe/MoE/output_0"], domain="com.microsoft",
+                   k=arch.experts_per_token, activation_type="swiglu", activation_alpha=float(arch.moe_swiglu_alpha),
+                   activation_beta=1.0, swiglu_fusion=1, swiglu_limit=float(arch.moe_swiglu_limit), normalize_routing_weights=1)
+            mlp_out = f"{n}/moe/MoE/output_0"
+        else:
+            gu = f"{n}/mlp/gate_up_proj/MatMul/output_0"
+            put_linear(p + "mlp.gate_up_proj", f"{n}/mlp/gate_up_proj/MatMul", [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], x, gu, 2 * I, H)
+            if arch.mlp_bias:
+                put_vec(p + "mlp.gate_up_proj.Add.bias", [p + "mlp.gate_proj.bias", p + "mlp.up_proj.bias"])
+                W.node("Add", f"{n}/mlp/gate_up_proj/Add", [gu, p + "mlp.gate_up_proj.Add.bias"], [f"{n}/mlp/gate_up_proj/Add/output_0"])
+                gu = f"{n}/mlp/gate_up_proj/Add/output_0"
+            W.node("Split", f"{n}/mlp/gate_up_proj/Split", [gu], [f"{n}/mlp/gate", f"{n}/mlp/up"], axis=-1, num_outputs=2)
+            if arch.activation == "silu":
+                W.node("Sigmoid", f"{n}/mlp/act_fn/Sigmoid", [f"{n}/mlp/gate"], [f"{n}/mlp/act_fn/Sigmoid/output_0"])
+                W.node("Mul", f"{n}/mlp/act_fn/Mul", [f"{n}/mlp/gate", f"{n}/mlp/act_fn/Sigmoid/output_0"], [f"{n}/mlp/act_fn/Mul/output_0"])
+            else:
+                W.node("FastGelu", f"{n}/mlp/act_fn/FastGelu", [f"{n}/mlp/gate"], [f"{n}/mlp/act_fn/Mul/output_0"], domain="com.microsoft")
+            W.node("Mul", f"{n}/mlp/Mul", [f"{n}/mlp/act_fn/Mul/output_0", f"{n}/mlp/up"], [f"{n}/mlp/Mul/output_0"])
+            mlp_out = f"{n}/mlp/down_proj/MatMul/output_0"
+            put_linear(p + "mlp.down_proj", f"{n}/mlp/down_proj/MatMul", [p + "mlp.down_proj.weight"], f"{n}/mlp/Mul/output_0", mlp_out, H, I)
+            if arch.mlp_bias:
+                put_vec(p + "mlp.down_proj.Add.bias", [p + "mlp.down_proj.bias"])
+                W.node("Add", f"{n}/mlp/down_proj/Add", [mlp_out, p + "mlp.down_proj.Add.bias"], [f"{n}/mlp/down_proj/Add/output_0"])
+                mlp_out = f"{n}/mlp/down_proj/Add/output_0"
+        if arch.post_sublayer_norms:
+            put_vec(p + "post_feedforward_layernorm.weight", [p + "post_feedforward_layernorm.weight"], arch.norm_offset)
+            W.node(norm_op, f"{n}/post_feedforward_layernorm/LayerNorm", [mlp_out, p + "post_feedforward_layernorm.weight"],
+                   [f"{n}/post_feedforward_layernorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1)
+            mlp_out = f"{n}/post_feedforward_layernorm/output_0"
+        hidden = mlp_out
+
+    # ---- final norm + head
+    fname = f"model.layers.{L}.final_norm_layernorm.weight"
+    put_vec(fname, ["model.norm.weight"], arch.norm_offset)
+    ins = [hidden, residual, fname]
+    if arch.layernorm:
+        put_vec(f"model.layers.{L}.final_norm_layernorm.bias", ["model.norm.bias"])
+        ins.append(f"model.layers.{L}.final_norm_layernorm.bias")
+    W.node(skip_op, f"/model/layers.{L}/final_norm_layernorm/SkipLayerNorm", ins,
+           [f"/model/layers.{L}/final_norm_layernorm/output_0", "", "", ""], domain="com.microsoft", epsilon=float(arch.norm_eps))
+    head_src = ["model.embed_tokens.weight"] if arch.tie_embeddings else ["lm_head.weight"]
+    put_linear("lm_head", "/lm_head/MatMul", head_src, f"/model/layers.{L}/final_norm_layernorm/output_0", "/lm_head/MatMul/output_0", V, H)
+    logits_name = "/lm_head/MatMul/output_0"
+    if arch.lm_head_bias:
+        put_vec("lm_head.Add.bias", ["lm_head.bias"])
+        W.node("Add", "/lm_head/Add", [logits_name, "lm_head.Add.bias"], ["/lm_head/Add/output_0"])
+        logits_name = "/lm_head/Add/output_0"
+    if arch.logits_scale != 1.0:
+        W.model.initializers["/model/constants/logits_scale"] = op.Tensor("/model/constants/logits_scale", op.FLOAT, (),
+                                                                          raw=np.float32(arch.logits_scale).tobytes())
+        W.node("Mul", "/lm_head/Mul", [logits_name, "/model/constants/logits_scale"], ["/lm_head/Mul/output_0"])
+        logits_name = "/lm_head/Mul/output_0"
+    if arch.final_logit_softcap > 0:
+        W.node("Softcap", "/lm_head/softcap", [logits_name], ["/lm_head/softcap/output_0"], domain="com.microsoft",
+               softcap=float(arch.final_logit_softcap))
+        logits_name = "/lm_head/softcap/output_0"
+    W.node("Cast" if W.io != "fp32" else "Identity", "/lm_head/Cast", [logits_name], ["logits"], **({"to": op.FLOAT} if W.io != "fp32" else {}))
+
+    # ---- graph inputs / outputs
+    m = W.model
+    if paged:
+        m.inputs = [op.ValueInfo("input_ids", op.INT64, ("num_tokens",)),
+                    op.ValueInfo("block_table", op.INT32, ("batch_size", "max_num_blocks")),
+                    op.ValueInfo("cumulative_sequence_lengths", op.INT32, ("batch_size_plus_1",)),
+                    op.ValueInfo("past_sequence_lengths", op.INT32, ("batch_size",)),
+                    op.ValueInfo("attention_metadata", op.INT32, (3,))]
+        if arch.sliding_window > 0 and arch.sliding_layers is not None:
+            m.inputs.insert(2, op.ValueInfo("block_table_windowed", op.INT32, ("batch_size", "max_num_blocks")))
+        kv_shape = ("num_blocks", block_size, arch.num_kv_heads, arch.head_dim)
+        m.outputs = [op.ValueInfo("logits", op.FLOAT, ("batch_size", V))]
+    else:
+        m.inputs = [op.ValueInfo("input_ids", op.INT64, ("batch_size", "sequence_length")),
+                    op.ValueInfo("attention_mask", op.INT64, ("batch_size", "total_sequence_length"))]
+        kv_shape = ("batch_size", arch.num_kv_heads, "past_sequence_length", arch.head_dim)
+        m.outputs = [op.ValueInfo("logits", op.FLOAT, ("batch_size", "sequence_length", V))]
+    for i in range(L):
+        m.inputs += [op.ValueInfo(f"past_key_values.{i}.key", io_dt, kv_shape), op.ValueInfo(f"past_key_values.{i}.value", io_dt, kv_shape)]
+        m.outputs += [op.ValueInfo(f"present.{i}.key", io_dt, kv_shape), op.ValueInfo(f"present.{i}.value", io_dt, kv_shape)]
+
+    if W.ext is not None:
+        W.ext.close()
+    _save_with_synthetic(m, os.path.join(out_dir, filename), synth_meta)
+
+    if write_config:
+        cfg = make_genai_config(arch, precision, execution_provider, paged, block_size, max_batch_size, filename, search, engine,
+                                num_blocks=num_blocks, max_scheduled_tokens=max_scheduled_tokens)
+        if speculative:
+            cfg["speculative"] = speculative
+        if draft_dir_entry:
+            cfg["model"]["draft"] = draft_dir_entry
+        with open(os.path.join(out_dir, "genai_config.json"), "w") as f:
+            json.dump(cfg, f, indent=4)
+    return out_dir
+
+
+def _save_with_synthetic(model: op.Model, path: str, synth_meta: Dict[str, dict]) -> None:
+    """Synthetic initializers are stored as external-data entries {location: 'synthetic', spec: <json>}."""
+    if not synth_meta:
+        op.save_model(model, path)
+        return
+    # Encode the synthetic spec in the `location` string so that the stock wire format is kept.
+    for name, meta in synth_meta.items():
+        t = model.initializers[name]
+        t.ext_location = "synthetic:" + json.dumps(meta, separators=(",", ":"))
+        t.ext_offset = 0
+        t.ext_length = 0
+    op.save_model(model, path)
+
+
+def make_genai_config(arch: ArchConfig, precision: str, ep: str, paged: bool, block_size: int, max_batch_size: int,
+                      filename: str = "model.onnx", search: Optional[dict] = None, engine: Optional[dict] = None,
+                      num_blocks: Optional[int] = None, max_scheduled_tokens: Optional[int] = None) -> dict:
+    inputs = {"input_ids": "input_ids", "past_key_names": "past_key_values.%d.key", "past_value_names": "past_key_values.%d.value"}
+    if paged:
+        inputs.update({"block_table": "block_table", "cumulative_sequence_lengths": "cumulative_sequence_lengths",
+                       "past_sequence_lengths": "past_sequence_lengths", "attention_metadata": "attention_metadata"})
+        if arch.sliding_window > 0 and arch.sliding_layers is not None:
+            inputs["block_table_windowed"] = "block_table_windowed"
+    else:
+        inputs["attention_mask"] = "attention_mask"
+    provider_options = [] if ep == "cpu" else [{ep: {"enable_cuda_graph": "0"} if ep == "cuda" else {}}]
+    decoder = {
+        "session_options": {"log_id": "onnxruntime-genai", "provider_options": provider_options},
+        "filename": filename, "head_size": arch.head_dim, "hidden_size": arch.hidden_size, "inputs": inputs,
+        "outputs": {"logits": "logits", "present_key_names": "present.%d.key", "present_value_names": "present.%d.value"},
+        "num_attention_heads": arch.num_heads, "num_hidden_layers": arch.num_layers, "num_key_value_heads": arch.num_kv_heads,
+    }
+    if arch.sliding_window > 0:
+        sw = {"window_size": arch.sliding_window, "slide_key_value_cache": False, "slide_inputs": False}
+        if arch.sliding_layers is not None:
+            sw["layers"] = list(arch.sliding_layers)
+        decoder["sliding_window"] = sw
+    cfg = {
+        "model": {"bos_token_id": arch.bos_token_id, "context_length": arch.context_length, "decoder": decoder,
+                  "eos_token_id": arch.eos_token_id, "pad_token_id": arch.pad_token_id, "type": arch.model_type,
+                  "vocab_size": arch.vocab_size},
+        "search": {"diversity_penalty": 0.0, "do_sample": False, "early_stopping": True, "length_penalty": 1.0,
+                   "max_length": arch.context_length, "min_length": 0, "no_repeat_ngram_size": 0, "num_beams": 1,
+                   "num_return_sequences": 1, "past_present_share_buffer": ep == "cuda", "repetition_penalty": 1.0,
+                   "temperature": 1.0, "top_k": 50, "top_p": 1.0},
+    }
+    if search:
+        cfg["search"].update(search)
+    if paged or engine:
+        dyn = {"block_size": block_size, "gpu_utilization_factor": 0.6, "max_batch_size": max_batch_size}
+        if num_blocks:
+            dyn["num_blocks"] = num_blocks
+        if max_scheduled_tokens:
+            dyn["max_scheduled_tokens"] = max_scheduled_tokens
+        cfg["engine"] = engine or {"dynamic_batching": dyn}
+    return cfg
+
+
+# ---------------------------------------------------------------------------------------------- HF loading
+def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
+    """Reads *.safetensors (preferred) or pytorch_model*.bin from a Hugging Face model directory."""
+    sd: Dict[str, torch.Tensor] = {}
+    files = sorted(f for f in os.listdir(model_dir) if f.endswith(".safetensors"))
+    if files:
+        from safetensors.torch import load_file
+        for f in files:
+            sd.update(load_file(os.path.join(model_dir, f)))
+    else:
+        for f in sorted(f for f in os.listdir(model_dir) if f.startswith("pytorch_model") and f.endswith(".bin")):
+            sd.update(torch.load(os.path.join(model_dir, f), map_location="cpu", weights_only=True))
+    if not sd:
+        raise FileNotFoundError(f"no weights found in {model_dir}")
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("qkv_proj.weight"):  # phi3 packs q, k, v
+            base = k[: -len("qkv_proj.weight")]
+            out[base + "q_proj.weight"], out[base + "k_proj.weight"], out[base + "v_proj.weight"] = v, None, None
+            out[base + "__packed_qkv__"] = v
+        elif k.endswith("gate_up_proj.weight"):
+            base = k[: -len("gate_up_proj.weight")]
+            half = v.shape[0] // 2
+            out[base + "gate_proj.weight"], out[base + "up_proj.weight"] = v[:half], v[half:]
+        else:
+            out[k] = v
+    return out
+
+
+def _split_packed_qkv(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
+    for k in [k for k in sd if k.endswith("__packed_qkv__")]:
+        base = k[: -len("__packed_qkv__")]
+        v = sd.pop(k)
+        q, kk, vv = torch.split(v, [arch.q_size, arch.kv_size, arch.kv_size], dim=0)
+        sd[base + "q_proj.weight"], sd[base + "k_proj.weight"], sd[base + "v_proj.weight"] = q, kk, vv
+
+
+def create_model(model_name_or_dir: str, output_dir: str, precision: str, execution_provider: str, extra_options: Optional[dict] = None):
+    extra = dict(extra_options or {})
+    state_dict = None
+    if model_name_or_dir in PRESETS:
+        import copy
+        arch = copy.deepcopy(PRESETS[model_name_or_dir])
+    else:
+        with open(os.path.join(model_name_or_dir, "config.json")) as f:
+            arch = from_hf_config(json.load(f))
+        if not int(extra.get("random_weights", 0)) and not int(extra.get("synthetic_weights", 0)):
+            state_dict = load_hf_state_dict(model_name_or_dir)
+            _split_packed_qkv(state_dict, arch)
+        for fn in ("tokenizer.json", "tokenizer_config.json", "special_tokens_map.json", "tokenizer.model", "chat_template.jinja",
+                   "generation_config.json"):
+            src = os.path.join(model_name_or_dir, fn)
+            if os.path.exists(src):
+                os.makedirs(output_dir, exist_ok=True)
+                shutil.copy(src, os.path.join(output_dir, fn))
+    return export_model(
+        arch, output_dir, precision, execution_provider, state_dict=state_dict, seed=int(extra.get("seed", 0)),
+        paged=bool(int(extra.get("paged_attention", extra.get("use_paged_attention", 0)))),
+        block_size=int(extra.get("paged_block_size", 16)), max_batch_size=int(extra.get("max_batch_size", 64)),
+        int4_symmetric=bool(int(extra.get("int4_is_symmetric", 0))), synthetic_weights=bool(int(extra.get("synthetic_weights", 0))),
+        filename=extra.get("filename", "model.onnx"), context_length=int(extra["context_length"]) if "context_length" in extra else None)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="Export a model directory (genai_config.json + ONNX + external data)")
+    ap.add_argument("-m", "--model_name", required=True, help="Hugging Face model directory or a preset: " + ", ".join(PRESETS))
+    ap.add_argument("-o", "--output", required=True)
+    ap.add_argument("-p", "--precision", required=True, choices=["int4", "bf16", "fp16", "fp32"])
+    ap.add_argument("-e", "--execution_provider", default="cuda", choices=["cpu", "cuda"])
+    ap.add_argument("--extra_options", nargs="*", default=[], help="key=value pairs")
+    a = ap.parse_args(argv)
+    extra = dict(kv.split("=", 1) for kv in a.extra_options)
+    out = create_model(a.model_name, a.output, a.precision, a.execution_provider, extra)
+    print("saved", out)
+
+
+if __name__ == "__main__":
+    main()

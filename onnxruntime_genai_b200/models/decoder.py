@@ -1,0 +1,222 @@
+"""Decoder-only transformer runtime over packed variable-length steps and a paged KV cache.
+
+The same forward serves prefill chunks, decode steps and speculative verification: a step is a flat
+list of tokens from several requests (`cu_seqlens`), each request has `past_lens[b]` tokens already
+in the cache, new K/V rows are appended at `slot_mapping`, and attention reads the cache through
+`block_table` (the I/O contract of the reference's paged decoder graph,
+src/python/py/models/builders/base.py:484-542 and src/engine/decoders/varlen_decoder_io.h:14-76).
+
+Every op goes through `onnxruntime_genai_b200.ops`: sm_100a kernels on CUDA tensors, fp32 PyTorch
+restatements on CPU tensors.  Tensor parallelism shards attention heads and MLP columns; the
+row-parallel projections hand their partial sums to `self.tp.reduce` (NCCL baseline or the fused
+NVLink kernels in `parallel/`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from .arch import ArchConfig
+
+
+@dataclass
+class StepInputs:
+    input_ids: torch.Tensor        # [T] int32
+    positions: torch.Tensor        # [T] int32
+    slot_mapping: torch.Tensor     # [T] int32
+    cu_seqlens: torch.Tensor       # [B+1] int32
+    past_lens: torch.Tensor        # [B] int32
+    block_table: torch.Tensor      # [B, cols] int32
+    logits_rows: Optional[torch.Tensor] = None  # [R] int32 rows of the packed output that need logits
+    slot_mapping_w: Optional[torch.Tensor] = None
+    block_table_w: Optional[torch.Tensor] = None
+    max_q_len: int = 1
+    max_kv_len: int = 1
+    inputs_embeds: Optional[torch.Tensor] = None  # overrides the embedding lookup (multimodal / MTP)
+    return_hidden: bool = False
+
+
+class PagedKVCache:
+    """Per-layer key/value pools of shape [num_blocks * block_size, kv_heads, head_dim].  Layers with a
+    sliding window may use a second, smaller pool addressed through ring block tables."""
+
+    def __init__(self, arch: ArchConfig, num_blocks: int, block_size: int, device, dtype, kv_heads: Optional[int] = None,
+                 num_window_blocks: int = 0):
+        self.block_size = block_size
+        self.num_blocks = num_blocks
+        self.num_window_blocks = num_window_blocks
+        hk = kv_heads if kv_heads is not None else arch.num_kv_heads
+        self.windowed = [num_window_blocks > 0 and arch.layer_window(i) > 0 for i in range(arch.num_layers)]
+        n_full = sum(1 for w in self.windowed if not w)
+        n_win = arch.num_layers - n_full
+        self.full = torch.zeros(max(n_full, 1), 2, num_blocks * block_size, hk, arch.head_dim, dtype=dtype, device=device)
+        self.win = (torch.zeros(n_win, 2, num_window_blocks * block_size, hk, arch.head_dim, dtype=dtype, device=device)
+                    if n_win else None)
+        self._index = []
+        fi = wi = 0
+        for w in self.windowed:
+            if w:
+                self._index.append((True, wi)); wi += 1
+            else:
+                self._index.append((False, fi)); fi += 1
+
+    def layer(self, i: int):
+        win, j = self._index[i]
+        pool = self.win if win else self.full
+        return pool[j, 0], pool[j, 1], win
+
+    @staticmethod
+    def bytes_per_block(arch: ArchConfig, block_size: int, dtype, kv_heads: Optional[int] = None) -> int:
+        hk = kv_heads if kv_heads is not None else arch.num_kv_heads
+        return arch.num_layers * 2 * block_size * hk * arch.head_dim * torch.empty((), dtype=dtype).element_size()
+
+
+class NoTP:
+    rank, size = 0, 1
+
+    def reduce(self, x, residual=None):
+        return x
+
+    def gather_logits(self, x):
+        return x
+
+
+@dataclass
+class LayerWeights:
+    ln1_w: torch.Tensor
+    qkv_w: torch.Tensor
+    o_w: torch.Tensor
+    ln2_w: torch.Tensor
+    ln1_b: Optional[torch.Tensor] = None
+    ln2_b: Optional[torch.Tensor] = None
+    qkv_b: Optional[torch.Tensor] = None
+    o_b: Optional[torch.Tensor] = None
+    q_norm_w: Optional[torch.Tensor] = None
+    k_norm_w: Optional[torch.Tensor] = None
+    sinks: Optional[torch.Tensor] = None
+    post_attn_norm_w: Optional[torch.Tensor] = None
+    post_ffn_norm_w: Optional[torch.Tensor] = None
+    gate_up_w: Optional[torch.Tensor] = None
+    gate_up_b: Optional[torch.Tensor] = None
+    down_w: Optional[torch.Tensor] = None
+    down_b: Optional[torch.Tensor] = None
+    router_w: Optional[torch.Tensor] = None
+    router_b: Optional[torch.Tensor] = None
+    exp_gate_up_w: Optional[torch.Tensor] = None  # [E, 2I, H] rows interleaved (gate, up)
+    exp_gate_up_b: Optional[torch.Tensor] = None
+    exp_down_w: Optional[torch.Tensor] = None     # [E, H, I]
+    exp_down_b: Optional[torch.Tensor] = None
+    lora: Dict[str, dict] = field(default_factory=dict)
+    window: int = 0
+
+
+class DecoderModel:
+    def __init__(self, arch: ArchConfig, device, dtype, tp=None):
+        self.arch = arch
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.tp = tp or NoTP()
+        self.layers: List[LayerWeights] = []
+        self.embed: Optional[torch.Tensor] = None
+        self.final_norm_w: Optional[torch.Tensor] = None
+        self.final_norm_b: Optional[torch.Tensor] = None
+        self.lm_head_w: Optional[torch.Tensor] = None
+        self.lm_head_b: Optional[torch.Tensor] = None
+        self.cos: Optional[torch.Tensor] = None
+        self.sin: Optional[torch.Tensor] = None
+        self.heads_local = arch.num_heads // self.tp.size
+        self.kv_heads_local = max(1, arch.num_kv_heads // self.tp.size)
+        self.inter_local = arch.intermediate_size // self.tp.size
+        self.active_adapter = None  # name -> used by the LoRA hooks
+
+    # ------------------------------------------------------------------------------------ helpers
+    def _linear(self, x, w, b=None, residual=None, lora=None, out_fp32=False):
+        y = ops.linear(x, w, b, residual, out_fp32=out_fp32)
+        if lora is not None:
+            from .lora import apply_lora
+            y = apply_lora(y, x, lora)
+        return y
+
+    def _mlp(self, lw: LayerWeights, x):
+        a = self.arch
+        if a.num_experts > 0:
+            from .moe import moe_forward
+            return moe_forward(self, lw, x)
+        lora = self._lora(lw, "gate_up_proj")
+        if lora is None:
+            act = ops.gate_up_act(x, lw.gate_up_w, lw.gate_up_b, a.activation)
+        else:
+            act = ops.act_mul(self._linear(x, lw.gate_up_w, lw.gate_up_b, lora=lora), a.activation)
+        return self._linear(act, lw.down_w, lw.down_b if self.tp.rank == 0 else None, lora=self._lora(lw, "down_proj"))
+
+    def _lora(self, lw: LayerWeights, proj: str):
+        if self.active_adapter is None:
+            return None
+        return lw.lora.get(self.active_adapter, {}).get(proj)
+
+    # ------------------------------------------------------------------------------------ forward
+    def forward(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
+        """Returns fp32 logits for `s.logits_rows` (or for every token when it is None)."""
+        a = self.arch
+        h = s.inputs_embeds if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
+        residual = None
+        for li, lw in enumerate(self.layers):
+            if residual is None:
+                x, _ = ops.norm(h, lw.ln1_w, a.norm_eps, None, lw.ln1_b, a.layernorm)
+                residual = h
+            else:
+                x, residual = ops.norm(h, lw.ln1_w, a.norm_eps, residual, lw.ln1_b, a.layernorm)
+            # ---- attention
+            qkv = self._linear(x, lw.qkv_w, lw.qkv_b, lora=self._lora(lw, "qkv_proj"))
+            kc, vc, windowed = kv.layer(li)
+            slots = s.slot_mapping_w if windowed else s.slot_mapping
+            table = s.block_table_w if windowed else s.block_table
+            ops.rope_kv_append(qkv, s.positions, slots, self.cos, self.sin, kc, vc, self.heads_local, self.kv_heads_local,
+                               a.head_dim, a.rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+            att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
+                                      self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
+                                      max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
+            h = self._linear(att, lw.o_w, lw.o_b if self.tp.rank == 0 else None, lora=self._lora(lw, "o_proj"))
+            h = self.tp.reduce(h)
+            if lw.post_attn_norm_w is not None:
+                h, _ = ops.norm(h, lw.post_attn_norm_w, a.norm_eps)
+            if a.residual_multiplier != 1.0:
+                h = (h.float() * a.residual_multiplier).to(h.dtype)
+            x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
+            # ---- MLP
+            h = self._mlp(lw, x)
+            h = self.tp.reduce(h)
+            if lw.post_ffn_norm_w is not None:
+                h, _ = ops.norm(h, lw.post_ffn_norm_w, a.norm_eps)
+            if a.residual_multiplier != 1.0:
+                h = (h.float() * a.residual_multiplier).to(h.dtype)
+        x, residual = ops.norm(h, self.final_norm_w, a.norm_eps, residual, self.final_norm_b, a.layernorm)
+        self.last_hidden = x
+        if s.logits_rows is not None:
+            x = ops.gather_rows(x, s.logits_rows)
+        logits = ops.linear(x, self.lm_head_w, self.lm_head_b, out_fp32=True)
+        logits = self.tp.gather_logits(logits)
+        if a.logits_scale != 1.0:
+            logits = logits * a.logits_scale
+        if a.final_logit_softcap > 0:
+            logits = torch.tanh(logits / a.final_logit_softcap) * a.final_logit_softcap
+        return logits
+
+    # ------------------------------------------------------------------------------------ sizing
+    def weight_bytes(self) -> int:
+        n = 0
+        for t in self._all_tensors():
+            n += t.numel() * t.element_size()
+        return n
+
+    def _all_tensors(self):
+        for t in (self.embed, self.final_norm_w, self.final_norm_b, self.lm_head_w, self.lm_head_b, self.cos, self.sin):
+            if t is not None:
+                yield t
+        for lw in self.layers:
+            for v in vars(lw).values():
+                if isinstance(v, torch.Tensor):
+                    yield v

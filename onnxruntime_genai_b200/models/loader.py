@@ -1,0 +1,319 @@
+"""Checkpoint loader: `genai_config.json` + ONNX graph + external data -> DecoderModel.
+
+The ONNX file is read as a weight container plus architecture descriptor.  Structure is recovered
+from node names / op types / attributes (the naming contract of the reference builder, see
+builder.py in this package), weights from the initializers that those nodes name as inputs, so a
+checkpoint with separate q/k/v projections, packed qkv, float MatMul or MatMulNBits int4 weights
+loads through the same code.  MatMul initializers are stored `[in, out]` and are transposed to the
+K-major `[out, in]` layout that the tcgen05 GEMM consumes; tensor-parallel ranks keep only their
+shard (attention heads / MLP columns / vocabulary rows).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import re
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..utils import onnx_proto as op
+from .arch import ArchConfig
+from .builder import dequantize_int4_block32, random_tensor, weight_shapes
+from .decoder import DecoderModel, LayerWeights
+
+
+def _np_to_torch(arr: np.ndarray, onnx_dtype: int) -> torch.Tensor:
+    if onnx_dtype == op.BFLOAT16:
+        return torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16)
+    return torch.from_numpy(np.array(arr, copy=True))
+
+
+class GraphView:
+    """Name-indexed access to nodes and initializers of a loaded ONNX model."""
+
+    def __init__(self, path: str, seed_device="cpu"):
+        self.lm = op.LoadedModel(path)
+        self.nodes = self.lm.model.nodes
+        self.by_name = {n.name: n for n in self.nodes}
+        self.device = seed_device
+
+    def find(self, prefix: str, contains: str = "", ops: Optional[List[str]] = None):
+        for n in self.nodes:
+            if n.name.startswith(prefix) and contains in n.name and (ops is None or n.op_type in ops):
+                return n
+        return None
+
+    def find_all(self, prefix: str, ops: Optional[List[str]] = None):
+        return [n for n in self.nodes if n.name.startswith(prefix) and (ops is None or n.op_type in ops)]
+
+    def has_init(self, name: str) -> bool:
+        return bool(name) and self.lm.has(name)
+
+    def tensor(self, name: str, device="cpu") -> torch.Tensor:
+        t = self.lm.info(name)
+        if t.ext_location and t.ext_location.startswith("synthetic:"):
+            return self._synthetic(t, json.loads(t.ext_location[len("synthetic:"):]), device)
+        return _np_to_torch(self.lm.array(name), t.dtype)
+
+    def _synthetic(self, t: op.Tensor, meta: dict, device) -> torch.Tensor:
+        parts = []
+        shapes = self._shapes
+        for src in meta["sources"]:
+            parts.append(random_tensor(src, shapes[src], meta["seed"], meta["std"], device=device))
+        x = parts[0] if len(parts) == 1 else torch.cat(parts, 0)
+        if meta["op"] == "cat_t":
+            x = x.t()
+        if meta.get("offset"):
+            x = x + meta["offset"]
+        return x
+
+    def set_arch_shapes(self, arch: ArchConfig):
+        self._shapes = weight_shapes(arch)
+
+
+def _attr(node, name, default=None):
+    return node.attrs.get(name, default) if node is not None else default
+
+
+def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> ArchConfig:
+    """Rebuilds the architecture description from genai_config.json and the graph."""
+    d = decoder or cfg.decoder
+    L = d["num_hidden_layers"]
+    a = ArchConfig(model_type=cfg.model_type, vocab_size=cfg.vocab_size, hidden_size=d["hidden_size"], num_layers=L,
+                   num_heads=d["num_attention_heads"], num_kv_heads=d["num_key_value_heads"] or d["num_attention_heads"],
+                   head_dim=d["head_size"], context_length=cfg.context_length, bos_token_id=cfg.bos_token_id,
+                   eos_token_id=list(cfg.eos_token_ids), pad_token_id=cfg.pad_token_id)
+    first_norm = g.find("/model/layers.0/input_layernorm/")
+    if first_norm is not None:
+        a.norm_eps = float(_attr(first_norm, "epsilon", 1e-5))
+        a.layernorm = "Simplified" not in first_norm.op_type
+    attn = g.find("/model/layers.0/attn/", ops=["GroupQueryAttention", "PagedAttention", "MultiHeadAttention"])
+    if attn is not None:
+        a.attn_scale = float(_attr(attn, "scale", 0.0)) or None
+        a.softcap = float(_attr(attn, "softcap", 0.0) or 0.0)
+        a.rotary_interleaved = bool(_attr(attn, "rotary_interleaved", 0))
+        rd = _attr(attn, "rotary_embedding_dim", 0)
+        if rd:
+            a.partial_rotary_factor = rd / a.head_dim
+        a.qk_norm = "qk_norm_epsilon" in attn.attrs
+        a.attn_sinks = any(".sinks" in i for i in attn.inputs)
+    windows = []
+    for i in range(L):
+        n = g.find(f"/model/layers.{i}/attn/", ops=["GroupQueryAttention", "PagedAttention"])
+        w = int(_attr(n, "local_window_size", -1) or -1)
+        windows.append(w if w > 0 else 0)
+    if any(windows):
+        a.sliding_window = max(windows)
+        a.sliding_layers = None if all(windows) else [i for i, w in enumerate(windows) if w > 0]
+    a.attn_bias = g.find("/model/layers.0/attn/", "_proj/Add") is not None and \
+        any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all("/model/layers.0/attn/"))
+    a.o_bias = g.by_name.get("/model/layers.0/attn/o_proj/Add") is not None
+    a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
+    moe = g.find("/model/layers.0/moe/", ops=["MoE", "QMoE"])
+    if moe is not None:
+        a.experts_per_token = int(_attr(moe, "k", 1))
+        a.moe_swiglu_alpha = float(_attr(moe, "activation_alpha", 1.702))
+        a.moe_swiglu_limit = float(_attr(moe, "swiglu_limit", 7.0))
+        wname = moe.inputs[2]
+        shp = g.lm.info(wname).dims
+        a.num_experts = shp[0]
+        a.intermediate_size = shp[1] // 2
+        a.mlp_bias = True
+    else:
+        gu = g.find("/model/layers.0/mlp/gate_up_proj/", ops=["MatMul", "MatMulNBits"])
+        if gu is not None:
+            a.intermediate_size = _linear_shape(g, gu)[0] // 2
+        else:
+            gp = g.find("/model/layers.0/mlp/gate_proj/", ops=["MatMul", "MatMulNBits"])
+            if gp is not None:
+                a.intermediate_size = _linear_shape(g, gp)[0]
+        a.mlp_bias = g.find("/model/layers.0/mlp/down_proj/Add") is not None
+        a.activation = "gelu" if g.find("/model/layers.0/mlp/act_fn/", ops=["FastGelu", "Gelu", "BiasGelu"]) is not None else "silu"
+    if g.by_name.get("/model/embed_tokens/Mul") is not None:
+        a.embed_scale = float(g.tensor("/model/constants/embed_scale").float().item())
+    if g.by_name.get("/lm_head/Mul") is not None:
+        a.logits_scale = float(g.tensor("/model/constants/logits_scale").float().item())
+    sc = g.by_name.get("/lm_head/softcap")
+    if sc is not None:
+        a.final_logit_softcap = float(_attr(sc, "softcap", 0.0))
+    a.lm_head_bias = g.by_name.get("/lm_head/Add") is not None
+    return a
+
+
+def _linear_shape(g: GraphView, node):
+    """(N, K) of a MatMul / MatMulNBits node."""
+    if node.op_type == "MatMulNBits":
+        return int(node.attrs["N"]), int(node.attrs["K"])
+    k, n = g.lm.info(node.inputs[1]).dims
+    return n, k
+
+
+def _linear_weight(g: GraphView, node, dtype, device, rows: Optional[slice] = None, cols: Optional[slice] = None) -> torch.Tensor:
+    """Weight of a linear node as [N, K] (optionally a row/column shard), on `device`."""
+    if node.op_type == "MatMulNBits":
+        N, K = int(node.attrs["N"]), int(node.attrs["K"])
+        bs = int(node.attrs.get("block_size", 32))
+        if int(node.attrs.get("bits", 4)) != 4:
+            raise NotImplementedError("MatMulNBits: only 4-bit weights are supported")
+        q = g.tensor(node.inputs[1])
+        s = g.tensor(node.inputs[2])
+        zp = g.tensor(node.inputs[3]) if len(node.inputs) > 3 and node.inputs[3] else None
+        w = dequantize_int4_block32(q, s, zp, N, K, bs)
+    else:
+        w = g.tensor(node.inputs[1], device=device if g.lm.info(node.inputs[1]).ext_location and
+                     g.lm.info(node.inputs[1]).ext_location.startswith("synthetic:") else "cpu").t()
+    if rows is not None:
+        w = w[rows]
+    if cols is not None:
+        w = w[:, cols]
+    return w.to(device=device, dtype=dtype).contiguous()
+
+
+def _vec(g: GraphView, name: str, dtype, device, sl: Optional[slice] = None) -> Optional[torch.Tensor]:
+    if not g.has_init(name):
+        return None
+    t = g.tensor(name)
+    if sl is not None:
+        t = t[sl]
+    return t.to(device=device, dtype=dtype).contiguous()
+
+
+def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[dict] = None) -> DecoderModel:
+    d = decoder or cfg.decoder
+    g = GraphView(os.path.join(model_dir, d["filename"]))
+    arch = arch_from_checkpoint(cfg, g, d)
+    g.set_arch_shapes(arch)
+    model = DecoderModel(arch, device, dtype, tp)
+    tpn, tpr = model.tp.size, model.tp.rank
+    if arch.num_heads % tpn or (arch.num_kv_heads % tpn and tpn % arch.num_kv_heads):
+        raise ValueError(f"tensor parallel degree {tpn} does not divide the attention heads")
+    if arch.num_kv_heads < tpn:
+        raise NotImplementedError("tensor parallel degree larger than the number of KV heads")
+    Hq, Hkv, D, I = arch.num_heads, arch.num_kv_heads, arch.head_dim, arch.intermediate_size
+    hq_l, hkv_l, i_l = Hq // tpn, Hkv // tpn, I // tpn
+    q_rows = slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)
+    k_rows = slice(Hq * D + tpr * hkv_l * D, Hq * D + (tpr + 1) * hkv_l * D)
+    v_rows = slice(Hq * D + Hkv * D + tpr * hkv_l * D, Hq * D + Hkv * D + (tpr + 1) * hkv_l * D)
+
+    def linear_node(prefix: str, *names):
+        for nm in names:
+            n = g.find(prefix + nm + "/", ops=["MatMul", "MatMulNBits"])
+            if n is not None:
+                return n
+        return None
+
+    def shard_rows(w: torch.Tensor, slices) -> torch.Tensor:
+        return torch.cat([w[s] for s in slices], 0).contiguous() if tpn > 1 else w
+
+    emb = g.tensor("model.embed_tokens.weight", device=device)
+    model.embed = emb.to(device=device, dtype=dtype).contiguous()
+    cos, sin = g.tensor("cos_cache").float(), g.tensor("sin_cache").float()
+    model.cos, model.sin = cos.to(device).contiguous(), sin.to(device).contiguous()
+
+    for i in range(arch.num_layers):
+        p, n = f"model.layers.{i}.", f"/model/layers.{i}"
+        ln1 = g.find(f"{n}/input_layernorm/")
+        mid = "pre_feedforward_layernorm" if arch.post_sublayer_norms else "post_attention_layernorm"
+        ln2 = g.find(f"{n}/{mid}/")
+        w_idx1 = 1 if ln1.op_type in ("SimplifiedLayerNormalization", "LayerNormalization") else 2
+        lw = LayerWeights(
+            ln1_w=_vec(g, ln1.inputs[w_idx1], dtype, device),
+            ln1_b=_vec(g, ln1.inputs[w_idx1 + 1], dtype, device) if arch.layernorm and len(ln1.inputs) > w_idx1 + 1 else None,
+            ln2_w=_vec(g, ln2.inputs[2], dtype, device),
+            ln2_b=_vec(g, ln2.inputs[3], dtype, device) if arch.layernorm and len(ln2.inputs) > 3 else None,
+            qkv_w=None, o_w=None, window=arch.layer_window(i))
+        # attention projections: packed or separate
+        qkv = linear_node(f"{n}/attn/", "qkv_proj")
+        if qkv is not None:
+            w = _linear_weight(g, qkv, dtype, device)
+            lw.qkv_w = shard_rows(w, [q_rows, k_rows, v_rows])
+            badd = g.by_name.get(f"{n}/attn/qkv_proj/Add")
+            if badd is not None:
+                b = g.tensor(badd.inputs[1])
+                lw.qkv_b = shard_rows(b, [q_rows, k_rows, v_rows]).to(device=device, dtype=dtype)
+        else:
+            ws, bs = [], []
+            for nm, rows in (("q_proj", slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)),
+                             ("k_proj", slice(tpr * hkv_l * D, (tpr + 1) * hkv_l * D)),
+                             ("v_proj", slice(tpr * hkv_l * D, (tpr + 1) * hkv_l * D))):
+                node = linear_node(f"{n}/attn/", nm)
+                ws.append(_linear_weight(g, node, dtype, device, rows=rows if tpn > 1 else None))
+                badd = g.by_name.get(f"{n}/attn/{nm}/Add")
+                if badd is not None:
+                    b = g.tensor(badd.inputs[1])
+                    bs.append((b[rows] if tpn > 1 else b).to(device=device, dtype=dtype))
+            lw.qkv_w = torch.cat(ws, 0).contiguous()
+            lw.qkv_b = torch.cat(bs, 0).contiguous() if bs else None
+        o = linear_node(f"{n}/attn/", "o_proj")
+        lw.o_w = _linear_weight(g, o, dtype, device, cols=slice(tpr * hq_l * D, (tpr + 1) * hq_l * D) if tpn > 1 else None)
+        oadd = g.by_name.get(f"{n}/attn/o_proj/Add")
+        if oadd is not None:
+            lw.o_b = _vec(g, oadd.inputs[1], dtype, device)
+        attn = g.find(f"{n}/attn/", ops=["GroupQueryAttention", "PagedAttention"])
+        for inp in attn.inputs:
+            if inp.endswith(".sinks"):
+                s = g.tensor(inp).float()
+                lw.sinks = (s[tpr * hq_l:(tpr + 1) * hq_l] if tpn > 1 else s).to(device).contiguous()
+            elif "q_norm" in inp:
+                lw.q_norm_w = _vec(g, inp, dtype, device)
+            elif "k_norm" in inp:
+                lw.k_norm_w = _vec(g, inp, dtype, device)
+        if arch.post_sublayer_norms:
+            pa = g.find(f"{n}/post_attention_layernorm/")
+            pf = g.find(f"{n}/post_feedforward_layernorm/")
+            lw.post_attn_norm_w = _vec(g, pa.inputs[1], dtype, device)
+            lw.post_ffn_norm_w = _vec(g, pf.inputs[1], dtype, device)
+        # MLP / MoE
+        moe = g.find(f"{n}/moe/", ops=["MoE", "QMoE"])
+        if moe is not None:
+            if tpn > 1:
+                raise NotImplementedError("mixture-of-experts models use expert parallelism (parallel/ep.py), not TP sharding")
+            r = linear_node(f"{n}/moe/", "router")
+            lw.router_w = _linear_weight(g, r, dtype, device)
+            radd = g.by_name.get(f"{n}/moe/router/Add")
+            lw.router_b = _vec(g, radd.inputs[1], dtype, device) if radd is not None else None
+            lw.exp_gate_up_w = g.tensor(moe.inputs[2], device=device).to(device=device, dtype=dtype).contiguous()
+            lw.exp_gate_up_b = g.tensor(moe.inputs[3], device=device).to(device=device, dtype=dtype).contiguous() if moe.inputs[3] else None
+            lw.exp_down_w = g.tensor(moe.inputs[4], device=device).to(device=device, dtype=dtype).contiguous()
+            lw.exp_down_b = g.tensor(moe.inputs[5], device=device).to(device=device, dtype=dtype).contiguous() if moe.inputs[5] else None
+        else:
+            gu = linear_node(f"{n}/mlp/", "gate_up_proj")
+            g_rows, u_rows = slice(tpr * i_l, (tpr + 1) * i_l), slice(I + tpr * i_l, I + (tpr + 1) * i_l)
+            if gu is not None:
+                w = _linear_weight(g, gu, dtype, device)
+                lw.gate_up_w = shard_rows(w, [g_rows, u_rows])
+                badd = g.by_name.get(f"{n}/mlp/gate_up_proj/Add")
+                if badd is not None:
+                    lw.gate_up_b = shard_rows(g.tensor(badd.inputs[1]), [g_rows, u_rows]).to(device=device, dtype=dtype)
+            else:
+                gw = _linear_weight(g, linear_node(f"{n}/mlp/", "gate_proj"), dtype, device, rows=g_rows if tpn > 1 else None)
+                uw = _linear_weight(g, linear_node(f"{n}/mlp/", "up_proj"), dtype, device, rows=g_rows if tpn > 1 else None)
+                lw.gate_up_w = torch.cat([gw, uw], 0).contiguous()
+            dn = linear_node(f"{n}/mlp/", "down_proj")
+            lw.down_w = _linear_weight(g, dn, dtype, device, cols=g_rows if tpn > 1 else None)
+            dadd = g.by_name.get(f"{n}/mlp/down_proj/Add")
+            if dadd is not None:
+                lw.down_b = _vec(g, dadd.inputs[1], dtype, device)
+        model.layers.append(lw)
+
+    fin = g.find(f"/model/layers.{arch.num_layers}/final_norm_layernorm/")
+    model.final_norm_w = _vec(g, fin.inputs[2 if len(fin.inputs) >= 3 else 1], dtype, device)
+    if arch.layernorm and len(fin.inputs) > 3:
+        model.final_norm_b = _vec(g, fin.inputs[3], dtype, device)
+    head = g.find("/lm_head/", ops=["MatMul", "MatMulNBits"])
+    V = arch.vocab_size
+    if tpn > 1:
+        per = (V + tpn - 1) // tpn
+        rows = slice(tpr * per, min(V, (tpr + 1) * per))
+        model.vocab_shard = (rows.start, rows.stop, per)
+    else:
+        rows = None
+    model.lm_head_w = _linear_weight(g, head, dtype, device, rows=rows)
+    hadd = g.by_name.get("/lm_head/Add")
+    if hadd is not None:
+        model.lm_head_b = _vec(g, hadd.inputs[1], dtype, device, rows)
+    g.lm.close()
+    return model

@@ -1,0 +1,307 @@
+"""Device ops.  CUDA tensors run the hand-written sm_100a kernels (ctypes into
+libogb200_kernels.so); CPU tensors run the fp32 PyTorch restatements in `reference.py`.
+
+There is deliberately no third path: a CUDA tensor never falls back to PyTorch math, and a missing
+kernel library on a GPU machine is an error.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import reference as ref
+from . import _lib
+
+_ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+class _Workspace:
+    """Per-device scratch shared by the kernels: split-K partial tiles + tile counters for the GEMM,
+    split-KV partials for attention.  Allocated once (outside graph capture) and reused."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.index = idx
+        _lib.init_device(idx)
+        self.status = _lib.lib().ogb_status_device_ptr(idx)
+        self.sm_count = _lib.lib().ogb_sm_count(idx)
+        self.gemm_ws = torch.empty(48 << 20, dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
+
+    def attn_scratch(self, nbytes: int) -> torch.Tensor:
+        if nbytes > self.attn_ws.numel():
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("attention scratch too small during CUDA graph capture; warm up eagerly first")
+            self.attn_ws = torch.empty(int(nbytes * 1.25), dtype=torch.uint8, device=self.device)
+        return self.attn_ws
+
+
+_workspaces = {}
+
+
+def workspace(device: torch.device) -> _Workspace:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = _workspaces[key] = _Workspace(torch.device("cuda", key))
+    return ws
+
+
+def check_kernel_status(device=None) -> None:
+    """Synchronises and raises if any kernel reported that a bounded wait ran out."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    _lib.init_device(idx)
+    _lib.check_status(idx)
+
+
+# ------------------------------------------------------------------------------------------ embedding
+def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    if not table.is_cuda:
+        return ref.embedding(ids, table, scale)
+    assert table.dtype == torch.bfloat16 and ids.dtype == torch.int32
+    T, H = ids.numel(), table.shape[1]
+    out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    _lib.check(_lib.lib().ogb_embedding(_ptr(ids), _ptr(table), _ptr(out), T, H, table.shape[0], float(scale), _stream()), "embedding")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ norm
+def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Returns (normalised, new_residual).  With `residual`, normalises x + residual and returns the
+    sum as new_residual (written in place into `residual`)."""
+    if not x.is_cuda:
+        y, r = ref.norm(x, weight, eps, residual, bias, layernorm)
+        if residual is not None:
+            residual.copy_(r)
+            r = residual
+        return y, r
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    rows, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _lib.check(_lib.lib().ogb_norm(_ptr(x), _ptr(residual), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out), rows, H,
+                                   float(eps), int(layernorm), _stream()), "norm")
+    return out, residual
+
+
+# ------------------------------------------------------------------------------------------ GEMM
+def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0):
+    """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous)."""
+    if not x.is_cuda:
+        return ref.linear(x, w, bias, residual, out_fp32)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.stride(-1) == 1 and w.stride(-1) == 1
+    T, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+    ws = workspace(x.device)
+    rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, N, K, _ptr(bias),
+                                  _ptr(residual), residual.stride(0) if residual is not None else 0, int(out_fp32), 0, 0,
+                                  int(splits), _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.counters), ws.counters.numel(),
+                                  ws.status, ws.sm_count, _stream())
+    _lib.check(rc, "gemm_bf16")
+    return out
+
+
+def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0):
+    """act(x @ Wg.T) * (x @ Wu.T) with w = [Wg; Wu] stacked along rows ([2I, K])."""
+    if not x.is_cuda:
+        return ref.gate_up_act(x, w, bias, act)
+    T, K = x.shape
+    inter = w.shape[0] // 2
+    if act != "silu":
+        y = linear(x, w, bias)
+        return act_mul(y, act)
+    if out is None:
+        out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
+    ws = workspace(x.device)
+    rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, inter, K, _ptr(bias),
+                                  None, 0, 0, 1, inter, int(splits), _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.counters),
+                                  ws.counters.numel(), ws.status, ws.sm_count, _stream())
+    _lib.check(rc, "gemm_bf16(dual)")
+    return out
+
+
+def act_mul(x, act="silu"):
+    if not x.is_cuda:
+        return ref.act_mul(x, act)
+    T, two_i = x.shape
+    out = torch.empty(T, two_i // 2, dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().ogb_act_mul(_ptr(x), _ptr(out), T, two_i // 2, _ACT[act], _stream()), "act_mul")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ RoPE + KV append
+def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
+    if not qkv.is_cuda:
+        return ref.rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved,
+                                  q_norm_w, k_norm_w, norm_eps)
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    assert cos_cache is None or cos_cache.dtype == torch.float32
+    T = qkv.shape[0]
+    max_pos = cos_cache.shape[0] if cos_cache is not None else 1
+    rc = _lib.lib().ogb_rope_kv_append(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(slots), _ptr(cos_cache), _ptr(sin_cache),
+                                       _ptr(k_cache), _ptr(v_cache), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), T, Hq, Hkv,
+                                       D, int(rot if cos_cache is not None else 0), int(interleaved), max_pos, _stream())
+    _lib.check(rc, "rope_kv_append")
+    return qkv
+
+
+# ------------------------------------------------------------------------------------------ attention
+def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_count: int = 148) -> int:
+    """Split the KV range when the (request, kv head) grid alone cannot fill the GPU."""
+    if max_q_len > 16:
+        return 1
+    ctas = max(1, batch * Hkv)
+    want = (2 * sm_count + ctas - 1) // ctas
+    by_len = max(1, max_kv_len // 256)
+    return int(max(1, min(want, by_len, 16)))
+
+
+def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale, window=0,
+                    sinks=None, softcap=0.0, max_q_len=None, max_kv_len=None, splits=None, out=None, total_tokens=None):
+    """q: [T, stride] with the Hq*D query columns first.  Returns [T, Hq*D]."""
+    if not q.is_cuda:
+        return ref.paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
+                                   window, sinks, softcap)
+    T = q.shape[0] if total_tokens is None else total_tokens
+    B = past_lens.shape[0]
+    if out is None:
+        out = torch.empty(q.shape[0], Hq * D, dtype=q.dtype, device=q.device)
+    if max_q_len is None:
+        max_q_len = T
+    if splits is None:
+        splits = choose_kv_splits(B, Hkv, max_q_len, max_kv_len or 1024)
+    ws = workspace(q.device)
+    need = _lib.lib().ogb_attention_scratch_bytes(q.shape[0], Hq, D, splits)
+    scratch = ws.attn_scratch(need) if splits > 1 else None
+    rc = _lib.lib().ogb_paged_attention(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
+                                        _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0),
+                                        _ptr(sinks), float(scale), float(softcap), int(window), B, q.shape[0], int(max_q_len),
+                                        Hq, Hkv, D, int(splits), _ptr(scratch), scratch.numel() if scratch is not None else 0,
+                                        _stream())
+    _lib.check(rc, "paged_attention")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ logits processing
+def logits_bitmask(logits, mask_words, mask_rows=None):
+    if not logits.is_cuda:
+        return ref.logits_bitmask(logits, mask_words, mask_rows)
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and mask_words.dtype == torch.int32
+    _lib.check(_lib.lib().ogb_logits_bitmask(_ptr(logits), rows, V, _ptr(mask_words), _ptr(mask_rows), _stream()), "logits_bitmask")
+    return logits
+
+
+def logits_edit(logits, rows, tokens, ops, values):
+    if not logits.is_cuda:
+        return ref.logits_edit(logits, rows, tokens, ops, values)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _lib.check(_lib.lib().ogb_logits_edit(_ptr(logits), logits.shape[1], _ptr(rows), _ptr(tokens), _ptr(ops), _ptr(values),
+                                          rows.numel(), _stream()), "logits_edit")
+    return logits
+
+
+def to_float32(x):
+    if x.dtype == torch.float32:
+        return x
+    if not x.is_cuda:
+        return x.float()
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().ogb_bf16_to_f32(_ptr(x.contiguous()), _ptr(out), x.numel(), _stream()), "bf16_to_f32")
+    return out
+
+
+def gather_rows(x, rows):
+    if not x.is_cuda:
+        return x[rows.long()]
+    out = torch.empty(rows.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().ogb_gather_rows(_ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1] * x.element_size(), _stream()),
+               "gather_rows")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def _cpu_sample_row(row, k, p, t, seed, pos):
+    if k == 1 or t <= 0:
+        return int(torch.argmax(row))
+    ids, probs = ref.sampled_distribution(row, k if k > 1 else None, p if 0 < p < 1 else None, t)
+    rng = np.random.Generator(np.random.Philox(key=int(seed) & ((1 << 64) - 1), counter=[int(pos), 0x5A17, 0, 0]))
+    u = rng.random()
+    cum = torch.cumsum(probs, 0)
+    j = int(torch.searchsorted(cum, torch.tensor(u, dtype=cum.dtype)).clamp(max=len(ids) - 1))
+    return int(ids[j])
+
+
+def sample(logits, top_k, top_p, temperature, seeds, positions, out=None):
+    """Per-row sampling.  logits [B, V] fp32; top_k int32 [B] (1 = greedy, <= 0 = no top-k);
+    top_p / temperature fp32 [B]; seeds int64 [B]; positions int32 [B] (RNG counter)."""
+    B, V = logits.shape
+    if not logits.is_cuda:
+        res = [_cpu_sample_row(logits[i].float(), int(top_k[i]), float(top_p[i]), float(temperature[i]), int(seeds[i]),
+                               int(positions[i])) for i in range(B)]
+        return torch.tensor(res, dtype=torch.int32)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib().ogb_sample(_ptr(logits), logits.stride(0), B, V, _ptr(top_k), _ptr(top_p), _ptr(temperature),
+                                     _ptr(seeds), _ptr(positions), _ptr(out), _stream()), "sample")
+    return out
+
+
+def argmax(logits, out=None):
+    if not logits.is_cuda:
+        return torch.argmax(logits.float(), dim=-1).to(torch.int32)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib().ogb_argmax(_ptr(logits), logits.stride(0), B, V, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def topk(x, k, log_softmax=False, add=None):
+    """Sorted top-k per row (k <= 128).  With log_softmax the values are log-probabilities (+ add[row])."""
+    if not x.is_cuda:
+        return ref.topk(x, k, log_softmax, add)
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and k <= 128
+    R, n = x.shape
+    vals = torch.empty(R, k, dtype=torch.float32, device=x.device)
+    idx = torch.empty(R, k, dtype=torch.int32, device=x.device)
+    _lib.check(_lib.lib().ogb_topk(_ptr(x), x.stride(0), R, n, k, int(log_softmax), _ptr(add), _ptr(vals), _ptr(idx), _stream()), "topk")
+    return vals, idx
+
+
+def beam_candidates(logits, beam_scores, batch, beams):
+    """Beam-search scoring: log-softmax + running beam score, top 2*beams per beam, merged to the best
+    2*beams per batch entry.  Returns (scores, tokens, source_beams), each [batch, 2*beams]."""
+    cand = 2 * beams
+    vals, idx = topk(logits, cand, log_softmax=True, add=beam_scores)
+    if not logits.is_cuda:
+        v = vals.view(batch, beams * cand)
+        order = torch.sort(v, dim=-1, descending=True, stable=True).indices[:, :cand]
+        scores = torch.gather(v, 1, order)
+        tokens = torch.gather(idx.view(batch, beams * cand), 1, order)
+        return scores, tokens.to(torch.int32), (order // cand).to(torch.int32)
+    scores = torch.empty(batch, cand, dtype=torch.float32, device=logits.device)
+    tokens = torch.empty(batch, cand, dtype=torch.int32, device=logits.device)
+    src = torch.empty(batch, cand, dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib().ogb_beam_merge(_ptr(vals), _ptr(idx), batch, beams, cand, _ptr(scores), _ptr(tokens), _ptr(src), _stream()),
+               "beam_merge")
+    return scores, tokens, src

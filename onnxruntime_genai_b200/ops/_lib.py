@@ -1,0 +1,101 @@
+"""ctypes binding of libogb200_kernels.so (the sm_100a kernel library).
+
+The library is built in-tree by `onnxruntime_genai_b200.build_native`.  On a machine with a CUDA
+device the library MUST load: ops on CUDA tensors never fall back to PyTorch silently.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libogb200_kernels.so")
+
+_lib = None
+_initialised_devices = set()
+
+_P = c_void_p
+_SIGS = {
+    "ogb_runtime_init": (c_int, [c_int]),
+    "ogb_status_device_ptr": (_P, [c_int]),
+    "ogb_status_read_and_clear": (c_int, [c_int]),
+    "ogb_sm_count": (c_int, [c_int]),
+    "ogb_gemm_token_tile": (c_int, [c_int, c_int]),
+    "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                              _P, c_longlong, _P, c_int, _P, c_int, _P]),
+    "ogb_embedding": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, _P]),
+    "ogb_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
+    "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, _P]),
+    "ogb_act_mul": (c_int, [_P, _P, c_int, c_int, c_int, _P]),
+    "ogb_logits_edit": (c_int, [_P, c_int, _P, _P, _P, _P, c_int, _P]),
+    "ogb_logits_bitmask": (c_int, [_P, c_int, c_int, _P, _P, _P]),
+    "ogb_bf16_to_f32": (c_int, [_P, _P, c_longlong, _P]),
+    "ogb_gather_rows": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "ogb_attention_scratch_bytes": (c_longlong, [c_int, c_int, c_int, c_int]),
+    "ogb_paged_attention": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, _P]),
+    "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
+    "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),
+    "ogb_topk": (c_int, [_P, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P]),
+    "ogb_beam_merge": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P]),
+    "ogb_verify_greedy": (c_int, [_P, _P, c_int, _P, _P, _P]),
+}
+
+_OPTIONAL = set()
+
+
+def lib():
+    """Returns the loaded kernel library, building it first when the sources are newer."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        from ..build_native import build_kernels
+        build_kernels()
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in _SIGS.items():
+        try:
+            fn = getattr(handle, name)
+        except AttributeError:
+            if name in _OPTIONAL:
+                continue
+            raise RuntimeError(f"{LIB_PATH} is stale (missing {name}); rebuild with python -m onnxruntime_genai_b200.build_native")
+        fn.restype = res
+        fn.argtypes = args
+    _lib = handle
+    return _lib
+
+
+def bind(name: str, restype, argtypes):
+    """Registers the signature of an extra entry point (used by optional kernel files)."""
+    fn = getattr(lib(), name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+    return fn
+
+
+def init_device(index: int) -> None:
+    if index in _initialised_devices:
+        return
+    rc = lib().ogb_runtime_init(index)
+    if rc != 0:
+        raise RuntimeError(f"ogb_runtime_init({index}) failed with {rc}")
+    _initialised_devices.add(index)
+
+
+STATUS_NAMES = {0: "ok", 1: "TMA pipeline wait ran out", 2: "accumulator wait ran out", 3: "peer wait ran out", 4: "bad argument"}
+
+
+def check_status(index: int) -> None:
+    """Synchronises the device and raises if a kernel reported a bounded wait that ran out."""
+    code = lib().ogb_status_read_and_clear(index)
+    if code != 0:
+        raise RuntimeError(f"sm_100a kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")

@@ -1,0 +1,206 @@
+"""Plain PyTorch fp32 restatements of every device op.
+
+They serve two purposes: (1) the CPU execution path (tiny models, CI without a GPU) and (2) the
+numerical oracle that the GPU tests compare each sm_100a kernel against.  All math is done in fp32
+regardless of the storage dtype; results are cast back to the input dtype.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+
+def embedding(ids, table, scale=1.0):
+    out = table[ids.long().clamp(0, table.shape[0] - 1)]
+    if scale != 1.0:
+        out = (out.float() * scale).to(table.dtype)
+    return out
+
+
+def norm(x, weight, eps, residual=None, bias=None, layernorm=False):
+    h = x.float()
+    new_res = None
+    if residual is not None:
+        new_res = (h + residual.float()).to(x.dtype)
+        h = new_res.float()
+    if layernorm:
+        mean = h.mean(-1, keepdim=True)
+        var = ((h - mean) ** 2).mean(-1, keepdim=True)
+        y = (h - mean) * torch.rsqrt(var + eps)
+    else:
+        y = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps)
+    y = y * weight.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype), new_res
+
+
+def linear(x, w, bias=None, residual=None, out_fp32=False):
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y if out_fp32 else y.to(x.dtype)
+
+
+def gate_up_act(x, w, bias=None, act="silu"):
+    """w is the stacked [gate; up] weight of shape [2I, K]."""
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    inter = y.shape[-1] // 2
+    g, u = y[..., :inter], y[..., inter:]
+    a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    return (a * u).to(x.dtype)
+
+
+def act_mul(x, act="silu"):
+    inter = x.shape[-1] // 2
+    g, u = x[..., :inter].float(), x[..., inter:].float()
+    a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    return (a * u).to(x.dtype)
+
+
+def _rotate(v, cos, sin, rot, interleaved):
+    # v: [T, H, D] fp32, cos/sin: [T, rot/2]
+    out = v.clone()
+    c, s = cos[:, None, :], sin[:, None, :]
+    if interleaved:
+        x1, x2 = v[..., 0:rot:2], v[..., 1:rot:2]
+        out[..., 0:rot:2] = x1 * c - x2 * s
+        out[..., 1:rot:2] = x2 * c + x1 * s
+    else:
+        half = rot // 2
+        x1, x2 = v[..., :half], v[..., half:rot]
+        out[..., :half] = x1 * c - x2 * s
+        out[..., half:rot] = x2 * c + x1 * s
+    return out
+
+
+def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
+    """In place: rotates q inside `qkv`, writes rotated k and v into the caches at `slots`."""
+    T = qkv.shape[0]
+    dt = qkv.dtype
+    x = qkv.float().view(T, Hq + 2 * Hkv, D)
+    q, k, v = x[:, :Hq], x[:, Hq:Hq + Hkv], x[:, Hq + Hkv:]
+
+    def head_norm(t, w):
+        y = t * torch.rsqrt((t * t).mean(-1, keepdim=True) + norm_eps) * w.float()
+        return y.to(dt).float()
+
+    if q_norm_w is not None:
+        q = head_norm(q, q_norm_w)
+    if k_norm_w is not None:
+        k = head_norm(k, k_norm_w)
+    if rot > 0:
+        pos = positions.long().clamp(0, cos_cache.shape[0] - 1)
+        cos, sin = cos_cache[pos].float(), sin_cache[pos].float()
+        q = _rotate(q, cos, sin, rot, interleaved)
+        k = _rotate(k, cos, sin, rot, interleaved)
+    qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq] = q.to(dt)
+    if slots is not None:
+        ok = slots >= 0
+        idx = slots[ok].long()
+        k_cache.view(-1, Hkv, D)[idx] = k[ok].to(k_cache.dtype)
+        v_cache.view(-1, Hkv, D)[idx] = v[ok].to(v_cache.dtype)
+    return qkv
+
+
+def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
+                    window=0, sinks=None, softcap=0.0):
+    """q: [T, >=Hq*D] (only the first Hq*D columns are read).  Returns [T, Hq*D]."""
+    T = q.shape[0]
+    out = torch.zeros(T, Hq * D, dtype=q.dtype, device=q.device)
+    kc = k_cache.view(-1, Hkv, D)
+    vc = v_cache.view(-1, Hkv, D)
+    G = Hq // Hkv
+    B = past_lens.shape[0]
+    cu = cu_seqlens.tolist()
+    for b in range(B):
+        t0, t1 = cu[b], cu[b + 1]
+        n = t1 - t0
+        if n == 0:
+            continue
+        past = int(past_lens[b])
+        total = past + n
+        pos = torch.arange(total, device=q.device)
+        slots = block_table[b, (pos // block_size).long()].long() * block_size + pos % block_size
+        k = kc[slots].float()  # [total, Hkv, D]
+        v = vc[slots].float()
+        qq = q[t0:t1, :Hq * D].float().view(n, Hq, D)
+        k = k.repeat_interleave(G, dim=1)
+        v = v.repeat_interleave(G, dim=1)
+        s = torch.einsum("qhd,khd->hqk", qq, k) * scale
+        if softcap and softcap > 0:
+            s = softcap * torch.tanh(s / softcap)
+        qpos = past + torch.arange(n, device=q.device)
+        mask = pos[None, :] <= qpos[:, None]
+        if window and window > 0:
+            mask = mask & (pos[None, :] > qpos[:, None] - window)
+        s = s.masked_fill(~mask[None], float("-inf"))
+        if sinks is not None:
+            sk = sinks.float().view(Hq, 1, 1).expand(Hq, n, 1)
+            p = torch.softmax(torch.cat([s, sk], dim=-1), dim=-1)[..., :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
+        o = torch.einsum("hqk,khd->qhd", p, v)
+        out[t0:t1] = o.reshape(n, Hq * D).to(q.dtype)
+    return out
+
+
+def sampled_distribution(logits_row, top_k, top_p, temperature):
+    """Kept token ids and renormalised probabilities for one row (fp64 math, sorted descending)."""
+    x = logits_row.double() / max(temperature, 1e-30)
+    order = torch.sort(x, descending=True, stable=True).indices
+    if top_k is not None and 1 < top_k < x.numel():
+        order = order[:top_k]
+    p = torch.softmax(x[order], dim=-1)
+    if top_p is not None and 0.0 < top_p < 1.0:
+        cum = torch.cumsum(p, 0)
+        keep = int(torch.searchsorted(cum, torch.tensor(top_p, dtype=cum.dtype)).item()) + 1
+        keep = min(keep, p.numel())
+        order, p = order[:keep], p[:keep]
+        p = p / p.sum()
+    return order, p
+
+
+def logits_bitmask(logits, mask_words, mask_rows=None):
+    V = logits.shape[-1]
+    v = torch.arange(V, device=logits.device)
+    lowest = torch.finfo(torch.float32).min
+    for r in range(logits.shape[0]):
+        mr = r if mask_rows is None else int(mask_rows[r])
+        if mr < 0:
+            continue
+        words = mask_words[mr].to(torch.int64) & 0xFFFFFFFF
+        bits = (words[(v // 32).long()] >> (v % 32)) & 1
+        logits[r][bits == 0] = lowest
+    return logits
+
+
+def logits_edit(logits, rows, tokens, ops, values):
+    lowest = torch.finfo(torch.float32).min
+    for r, t, o, val in zip(rows.tolist(), tokens.tolist(), ops.tolist(), values.tolist()):
+        if t < 0 or t >= logits.shape[-1]:
+            continue
+        if o == 0:
+            logits[r, t] = lowest
+        else:
+            x = float(logits[r, t])
+            logits[r, t] = x * val if x < 0 else x / val
+    return logits
+
+
+def topk(x, k, log_softmax=False, add=None):
+    y = x.float()
+    if log_softmax:
+        y = torch.log_softmax(y, dim=-1)
+        if add is not None:
+            y = y + add.float()[:, None]
+    # ties resolved towards the lower index
+    vals, idx = torch.sort(y, dim=-1, descending=True, stable=True)
+    return vals[:, :k].contiguous(), idx[:, :k].to(torch.int32).contiguous()
