@@ -1,0 +1,273 @@
+"""Headline benchmark: decode tokens/s (+ p50 TTFT / TPOT) of Llama-3.1-8B-shaped serving through
+the paged-attention continuous-batching engine, bf16, tensor-parallel over N GPUs of one node.
+
+Workload (BASELINE config 3): 64 concurrent requests, prompt lengths uniform in [128, 2048] of
+random token ids (seed 2), 256 output tokens each, sampling with temperature 0.7, top_k 50,
+top_p 0.9, KV block size 16; random-init weights N(0, 0.02) generated on the device.
+
+A "step" is one decode step of the whole batch (64 new tokens).  Two measurements:
+  * value: device-timed (CUDA events) back-to-back replays of the engine's captured decode graph plus
+    the sampler — the kernels alone;
+  * e2e:   the same steps through the public API (`Engine.step()`), each step packing its inputs
+    on the host, copying them from pinned memory to the device and reading the sampled ids back.
+Timing rules: >= 3 warm-up steps, barrier + synchronize on both sides, max over ranks, the
+working set (16 GB of weights + KV) is far larger than L2 so no flush is needed, SM clocks and
+throttle reasons are sampled with nvidia-smi during the timed region.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s"
+MODEL = "llama-3.1-8b"
+N_REQ, PROMPT_LO, PROMPT_HI, NEW_TOKENS, BLOCK = 64, 128, 2048, 256, 16
+
+
+def reference_arm(args):
+    """The reference needs ONNX Runtime binaries fetched from a package feed at build time
+    (cmake/ortlib.cmake) and the `onnx` / `onnxruntime` Python packages, none of which exist offline."""
+    why = "reference cannot be installed offline: its build downloads ONNX Runtime binaries (cmake/ortlib.cmake) and needs onnx/onnxruntime"
+    log = os.path.join(ROOT, "baseline", "install.log")
+    if os.path.exists(log):
+        with open(log) as f:
+            tail = [l.strip() for l in f.read().strip().splitlines() if l.strip()]
+        if tail:
+            why += " (pip: " + tail[-1][:160] + ")"
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import onnxruntime_genai  # noqa: F401
+        why = "reference package imported but no ONNX Runtime CUDA provider / ONNX model exporter is available offline"
+    except Exception:
+        pass
+    finally:
+        sys.path.pop(0)
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import onnxruntime_genai_b200 as og
+    from onnxruntime_genai_b200 import ops
+    from onnxruntime_genai_b200.models.builder import create_model
+    from onnxruntime_genai_b200.ops import _lib
+    from onnxruntime_genai_b200.parallel.tp import TensorParallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} processes (WORLD_SIZE={world})")
+    torch.cuda.set_device(local)
+    tp = TensorParallel.from_env(os.environ.get("OGB_TP_BACKEND")) if world > 1 else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- checkpoint (synthetic weights: the ONNX file only describes the tensors) + model + engine
+    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{os.getuid()}")
+    if rank == 0 and not os.path.exists(os.path.join(ckpt, "genai_config.json")):
+        create_model(MODEL, ckpt, "bf16", "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
+                                                  "max_batch_size": N_REQ, "context_length": 4096})
+    barrier()
+    cfg = og.Config(ckpt)
+    blocks = N_REQ * ((PROMPT_HI + NEW_TOKENS + BLOCK - 1) // BLOCK + 1)
+    # eos_token_id -1 never matches a sampled id: every request produces exactly NEW_TOKENS tokens (fixed workload).
+    cfg.overlay(json.dumps({"model": {"eos_token_id": -1},
+                            "engine": {"dynamic_batching": {"block_size": BLOCK, "num_blocks": blocks, "max_batch_size": N_REQ,
+                                                             "max_scheduled_tokens": 4096}}}))
+    t0 = time.perf_counter()
+    model = og.Model(cfg, tp=tp)
+    load_s = time.perf_counter() - t0
+    engine = og.Engine(model)
+
+    rng = np.random.RandomState(2)
+    lens = rng.randint(PROMPT_LO, PROMPT_HI + 1, size=N_REQ)
+    reqs = []
+    for i, n in enumerate(lens):
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=int(n) + NEW_TOKENS + 1, do_sample=True, temperature=0.7, top_k=50, top_p=0.9, random_seed=2 + i)
+        r = og.Request(p)
+        r.add_tokens(rng.randint(0, model.arch.vocab_size, size=int(n)).astype(np.int32))
+        reqs.append(r)
+
+    def drain(r):
+        n = 0
+        while r is not None and r.has_unseen_tokens():
+            r.get_unseen_token()
+            n += 1
+        return n
+
+    # ---- prefill (TTFT): admit everything, step until every request has its first token
+    barrier()
+    t_start = time.perf_counter()
+    for r in reqs:
+        engine.add_request(r)
+    while any(r.t_first is None for r in reqs):
+        drain(engine.step())
+    torch.cuda.synchronize()
+    ttft = sorted((r.t_first - t_start) * 1e3 for r in reqs)
+    prefill_s = time.perf_counter() - t_start
+    prefill_tok_s = float(lens.sum()) / prefill_s
+
+    def model_steps(k):
+        """Runs k decode steps through the public API; returns tokens produced."""
+        done = 0
+        target = engine.step_count + k
+        while engine.step_count < target:
+            done += drain(engine.step())
+        # drain what the last model step made ready without running the model again
+        return done
+
+    W, K = max(3, args.warmup), args.steps
+    K = min(K, NEW_TOKENS - 40 - W)  # requests admitted first have decoded ~20-30 tokens by the end of the prefill phase
+    # ---- e2e: public API, pinned H2D of the step inputs + D2H of the sampled ids every step
+    model_steps(W)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_e0 = time.perf_counter()
+    ev0.record()
+    model_steps(K)
+    ev1.record()
+    barrier()
+    e2e_wall = time.perf_counter() - t_e0
+    e2e_ms = ev0.elapsed_time(ev1)
+    step_wall = e2e_wall / K
+
+    # ---- device-only: replay the decode graph + sampler K times (inputs stay on the device)
+    ex = engine.executor
+    key = sorted(ex.graphs.keys())[-1] if ex.graphs else None
+    st = engine.staging
+    B = N_REQ
+
+    def device_step():
+        graph, logits = ex.graphs[key]
+        graph.replay()
+        ops.sample(logits[:B], st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
+                   st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
+
+    if key is None:
+        raise SystemExit("decode graph was not captured")
+    for _ in range(W):
+        device_step()
+    barrier()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d0.record()
+    for _ in range(K):
+        device_step()
+    d1.record()
+    barrier()
+    dev_ms = d0.elapsed_time(d1)
+    clocks = sampler.stop()
+    ops.check_kernel_status()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dev_ms, e2e_ms, e2e_wall = max_over_ranks(dev_ms), max_over_ranks(e2e_ms), max_over_ranks(e2e_wall)
+    value = B * K / (dev_ms / 1e3)
+    e2e_value = B * K / e2e_wall
+    launches = getattr(ex, "graph_launches", {}).get(key, 0) + 1
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (random token ids, random-init N(0,0.02) weights generated on device)",
+            "config": {"model": "Llama-3.1-8B shape", "global_batch": B, "seq_len": "prompts U[128,2048] + 256 new tokens",
+                       "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": "T=0.7 top_k=50 top_p=0.9",
+                       "engine": "paged-attention continuous batching", "l2": "inputs larger than L2 (weights 16 GB + KV), no flush",
+                       "tp_backend": getattr(tp, "backend", None)},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes, "d2h_bytes_per_step": 4 * B,
+                    "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4)},
+            "gpu_launches": int(launches * K),
+            "clocks": clocks,
+            "ttft_ms_p50": round(ttft[len(ttft) // 2], 2), "tpot_ms_p50": round(step_wall * 1e3, 4),
+            "prefill_tokens_per_s": round(prefill_tok_s, 1), "model_load_s": round(load_s, 1),
+            "kv_tokens_in_cache": int(lens.sum() + N_REQ * (W + K)),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    return ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,435 @@
+"""Continuous-batching engine: `Engine.add_request / step / remove_request / has_pending_requests`
+and `Request` (reference API: src/python/python.cpp:731-768; canonical loop:
+examples/python/engine/continuous-batching.py:80-113).
+
+One `step()` is a transaction driven by the native core (native/engine_core.cpp):
+plan + reserve blocks + checkpoint -> pack the step inputs into ONE pinned staging buffer -> one
+H2D copy -> forward over the packed tokens (CUDA graph replay for pure-decode steps, bucketed by
+batch and block-table width) -> logits edits / grammar masks -> one sampler launch with per-row
+parameters -> one small D2H of the sampled ids -> commit.  A failure while executing aborts the
+transaction: every request and every reserved block returns to its state before the step; a fatal
+failure marks the engine unhealthy (reference: src/engine/engine.cpp:227-478).
+
+The executor is injectable (`Engine(model, executor=...)`), which is how the tests script
+retryable / capacity / fatal failures on the host without touching a GPU.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..api import GeneratorParams, Model, _Trace
+from ..models.decoder import PagedKVCache, StepInputs
+from ..native_loader import native
+
+FailureKind = native.FailureKind
+StepOutcome = native.StepOutcome
+
+
+class EngineStepError(RuntimeError):
+    def __init__(self, outcome, message):
+        super().__init__(f"{outcome.name}: {message}")
+        self.outcome = outcome
+
+
+class ExecutionFailure(Exception):
+    """Raised by an executor to classify a failure (kind: native.FailureKind)."""
+
+    def __init__(self, kind, message=""):
+        super().__init__(message or kind.name)
+        self.kind = kind
+
+
+class Request:
+    def __init__(self, params: GeneratorParams):
+        self.params = params
+        self._pending_tokens: List[int] = []
+        self._native = None
+        self._engine = None
+        self._opaque = None
+        self.t_added = self.t_first = self.t_last = None
+        self.n_generated = 0
+
+    # tokens ------------------------------------------------------------------------------------
+    def add_tokens(self, ids):
+        arr = np.asarray(ids, dtype=np.int32).reshape(-1)
+        if self._native is not None:
+            self._native.add_tokens(arr)  # raises: already assigned
+        if arr.size == 0:
+            raise RuntimeError("add_tokens: empty token list")
+        self._pending_tokens.extend(arr.tolist())
+
+    def continue_with(self, ids):
+        if self._native is None:
+            raise RuntimeError("continue_with: the request has not been added to an engine")
+        self._native.continue_with(np.asarray(ids, dtype=np.int32).reshape(-1))
+
+    def has_unseen_tokens(self) -> bool:
+        return self._native is not None and self._native.has_unseen_tokens()
+
+    def get_unseen_token(self) -> int:
+        if self._native is None:
+            raise RuntimeError("get_unseen_token: no unseen tokens")
+        return self._native.get_unseen_token()
+
+    def is_turn_complete(self) -> bool:
+        return self._native is not None and self._native.is_turn_complete()
+
+    def is_done(self) -> bool:
+        return self.is_turn_complete()
+
+    def set_opaque_data(self, obj):
+        self._opaque = obj
+
+    def get_opaque_data(self):
+        return self._opaque
+
+    @property
+    def status(self):
+        return self._native.status if self._native is not None else native.RequestStatus.Unassigned
+
+    def tokens(self) -> np.ndarray:
+        return self._native.tokens() if self._native is not None else np.asarray(self._pending_tokens, dtype=np.int32)
+
+    def _options(self):
+        s = self.params.search
+        o = native.RequestOptions()
+        o.max_length, o.min_length, o.do_sample = int(s["max_length"]), int(s["min_length"]), bool(s["do_sample"])
+        o.top_k, o.top_p, o.temperature = int(s["top_k"]), float(s["top_p"]), float(s["temperature"])
+        o.repetition_penalty, o.no_repeat_ngram_size = float(s["repetition_penalty"]), int(s["no_repeat_ngram_size"])
+        o.random_seed, o.chunk_size = int(s["random_seed"]), int(s.get("chunk_size") or 0)
+        o.num_beams, o.batch_size = int(s["num_beams"]), int(s["batch_size"])
+        if self.params.guidance_type and self.params.guidance_ff_tokens:
+            raise RuntimeError("Engine requests do not support guidance ff_tokens")
+        return o
+
+
+# ------------------------------------------------------------------------------------------------ staging
+class _Staging:
+    """All per-step inputs in one pinned host buffer with a device mirror (one H2D copy per step)."""
+
+    FIELDS_TOK = ["input_ids", "positions", "token_row", "slot_mapping", "slot_mapping_w"]
+    FIELDS_ROW = ["past_lens", "logits_rows", "top_k", "sample_pos"]
+
+    def __init__(self, max_tokens: int, max_batch: int, table_cols: int, device: torch.device, windowed: bool):
+        self.max_tokens, self.max_batch, self.table_cols = max_tokens, max_batch, table_cols
+        lay, off = {}, 0
+
+        def add(name, n_words):
+            nonlocal off
+            lay[name] = (off, n_words)
+            off += (n_words + 3) // 4 * 4  # 16-byte alignment
+        for f in self.FIELDS_TOK:
+            add(f, max_tokens)
+        add("cu_seqlens", max_batch + 1)
+        for f in self.FIELDS_ROW:
+            add(f, max_batch)
+        add("top_p", max_batch)
+        add("temperature", max_batch)
+        add("seeds", 2 * max_batch)
+        add("block_table", max_batch * table_cols)
+        if windowed:
+            add("block_table_w", max_batch * table_cols)
+        self.layout, self.words = lay, off
+        pin = device.type == "cuda"
+        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=pin)
+        self.dev = torch.zeros(off, dtype=torch.int32, device=device) if pin else self.host
+        self.tokens_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        base = self.host.data_ptr()
+        self.addr = {k: base + 4 * o for k, (o, _) in lay.items()}
+        if not windowed:
+            self.addr.pop("slot_mapping_w", None)
+
+    def view(self, name, n=None, dtype=torch.int32, host=False):
+        o, w = self.layout[name]
+        t = (self.host if host else self.dev)[o:o + w]
+        if dtype != torch.int32:
+            t = t.view(dtype)
+        return t if n is None else t[:n]
+
+    def upload(self):
+        if self.dev is not self.host:
+            self.dev.copy_(self.host, non_blocking=True)
+
+    @property
+    def h2d_bytes(self):
+        return self.words * 4
+
+
+# ------------------------------------------------------------------------------------------------ executor
+class ModelExecutor:
+    """Runs the model for a planned step and returns the sampled token per plan entry."""
+
+    def __init__(self, model: Model, core, staging: _Staging, kv: PagedKVCache, use_graphs: bool):
+        self.model, self.core, self.staging, self.kv = model, core, staging, kv
+        self.decoder = model.decoder
+        self.use_graphs = use_graphs and model.device.type == "cuda"
+        self.graphs: Dict[Any, Any] = {}
+        self.windowed = kv.win is not None
+        self.graph_launches: Dict[Any, int] = {}
+
+    def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int) -> StepInputs:
+        st = self.staging
+        table = st.view("block_table").view(st.max_batch, st.table_cols)[:B, :cols]
+        s = StepInputs(input_ids=st.view("input_ids", T), positions=st.view("positions", T), slot_mapping=st.view("slot_mapping", T),
+                       cu_seqlens=st.view("cu_seqlens", B + 1), past_lens=st.view("past_lens", B), block_table=table,
+                       logits_rows=st.view("logits_rows", B), max_q_len=max_q, max_kv_len=max_kv)
+        if self.windowed:
+            s.slot_mapping_w = st.view("slot_mapping_w", T)
+            s.block_table_w = st.view("block_table_w").view(st.max_batch, st.table_cols)[:B, :cols]
+        return s
+
+    @staticmethod
+    def _bucket(n: int, lo: int = 1) -> int:
+        b = lo
+        while b < n:
+            b *= 2
+        return b
+
+    def forward(self, plan) -> torch.Tensor:
+        B, T = len(plan.entries), plan.token_count
+        st = self.staging
+        if self.use_graphs and plan.graph_eligible:
+            bb = min(self._bucket(B), st.max_batch)
+            cb = min(self._bucket(plan.block_table_columns, 8), st.table_cols)
+            key = (bb, cb)
+            if bb > B:  # padded rows: zero-length requests that append nothing
+                h = st.host
+                o, _ = st.layout["cu_seqlens"]
+                h[o + B + 1:o + bb + 1] = int(h[o + B])
+                for f, val in (("past_lens", 0), ("logits_rows", 0)):
+                    o, _ = st.layout[f]
+                    h[o + B:o + bb] = val
+                for f, val in (("input_ids", 0), ("positions", 0), ("slot_mapping", -1)):
+                    o, _ = st.layout[f]
+                    h[o + T:o + bb] = val
+                if self.windowed:
+                    o, _ = st.layout["slot_mapping_w"]
+                    h[o + T:o + bb] = -1
+            st.upload()
+            g = self.graphs.get(key)
+            if g is None:
+                g = self._capture(bb, cb)
+                self.graphs[key] = g
+            graph, logits = g
+            graph.replay()
+            return logits[:B]
+        st.upload()
+        s = self._step_inputs(T, B, st.table_cols, plan.max_query_len, plan.max_kv_len)
+        return self.decoder.forward(s, self.kv)
+
+    def _capture(self, bb: int, cb: int):
+        st = self.staging
+        s = self._step_inputs(bb, bb, st.table_cols, 1, cb * self.kv.block_size)
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):  # warm-up: tensor maps, attribute set-up, allocator
+                self.decoder.forward(s, self.kv)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        from ..ops import _lib
+        before = _lib.LAUNCH_COUNT
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.decoder.forward(s, self.kv)
+        self.graph_launches[(bb, cb)] = _lib.LAUNCH_COUNT - before
+        return graph, logits
+
+    def execute(self, plan, edits=None, masks=None) -> np.ndarray:
+        st = self.staging
+        B = len(plan.entries)
+        with torch.no_grad():
+            logits = self.forward(plan)
+            for e in edits or ():  # penalties first, then bans (separate launches: no write race on a token)
+                ops.logits_edit(logits, *e)
+            if masks is not None:
+                ops.logits_bitmask(logits, *masks)
+            toks = ops.sample(logits, st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
+                              st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
+        if toks.is_cuda:
+            st.tokens_host[:B].copy_(toks, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return st.tokens_host[:B].numpy()
+        return toks.numpy()
+
+
+# ------------------------------------------------------------------------------------------------ engine
+class Engine:
+    def __init__(self, model: Model, executor=None, num_blocks: Optional[int] = None):
+        self.model = model
+        cfg = model.config
+        eng = cfg.engine.get("dynamic_batching")
+        if eng is None:
+            sb = cfg.engine.get("static_batching")
+            eng = {"block_size": 16, "num_blocks": None, "gpu_utilization_factor": None,
+                   "max_batch_size": sb["max_batch_size"] if sb else 16, "max_scheduled_tokens": 2048}
+        arch = model.arch
+        self.block_size = int(eng["block_size"])
+        dec = model.decoder
+        nb = num_blocks or eng.get("num_blocks")
+        if not nb:
+            nb = self._blocks_from_memory(eng.get("gpu_utilization_factor") or 0.9)
+        o = native.EngineOptions()
+        o.block_size, o.num_blocks = self.block_size, int(nb)
+        o.max_batch_size, o.max_scheduled_tokens = int(eng["max_batch_size"]), int(eng["max_scheduled_tokens"])
+        o.vocab_size, o.pad_token_id, o.eos_ids = cfg.vocab_size, cfg.pad_token_id, list(cfg.eos_token_ids)
+        windowed = arch.sliding_window > 0 and arch.sliding_layers is not None
+        if windowed:
+            o.window_size = arch.sliding_window
+        self.core = native.EngineCore(o)
+        self.options = o
+        n_win = self.core.ring_blocks_per_request * o.max_batch_size if windowed else 0
+        self.kv = PagedKVCache(arch, o.num_blocks, self.block_size, model.device, model.dtype, kv_heads=dec.kv_heads_local,
+                               num_window_blocks=n_win)
+        max_ctx = min(cfg.context_length, o.num_blocks * self.block_size)
+        cols = (max_ctx + self.block_size - 1) // self.block_size
+        self.staging = _Staging(o.max_scheduled_tokens + o.max_batch_size, o.max_batch_size, cols, model.device, windowed)
+        self.executor = executor or ModelExecutor(model, self.core, self.staging, self.kv, use_graphs=True)
+        self._by_native: Dict[int, Request] = {}
+        self._guidance: Dict[int, Any] = {}
+        self.last_outcome = StepOutcome.NoWork
+        self.step_count = 0
+
+    def _blocks_from_memory(self, utilization: float) -> int:
+        arch, dec = self.model.arch, self.model.decoder
+        per_block = PagedKVCache.bytes_per_block(arch, self.block_size, self.model.dtype, dec.kv_heads_local)
+        if self.model.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.model.device)
+            budget = int(free * 0.9 * utilization)
+        else:
+            budget = 256 << 20
+        return max(16, budget // per_block)
+
+    # ------------------------------------------------------------------ API
+    def add_request(self, request: Request):
+        if request._native is not None:
+            raise RuntimeError("add_request: request was already added to an engine")
+        nat = self.core.create_request(request._options())
+        nat.add_tokens(np.asarray(request._pending_tokens, dtype=np.int32))
+        self.core.add_request(nat)
+        request._native, request._engine = nat, self
+        request.t_added = time.perf_counter()
+        self._by_native[nat.id] = request
+        if request.params.guidance_type:
+            from ..guidance import GuidanceProcessor
+            self._guidance[nat.id] = GuidanceProcessor(self.model, request.params.guidance_type, request.params.guidance_data, 1, False)
+            self._guidance[nat.id].commit_prompt(np.asarray(request._pending_tokens, dtype=np.int32).reshape(1, -1))
+
+    def remove_request(self, request: Request):
+        if request._native is None:
+            return
+        self.core.remove_request(request._native)
+        self._by_native.pop(request._native.id, None)
+        self._guidance.pop(request._native.id, None)
+
+    def has_pending_requests(self) -> bool:
+        return self.core.has_pending_requests()
+
+    def step(self) -> Optional[Request]:
+        """Returns one request that has unseen tokens (or just finished its turn), running the model when
+        no such request is waiting; returns None when there is nothing to do."""
+        nat = self.core.next_ready()
+        if nat is None:
+            self._run_model_step()
+            nat = self.core.next_ready()
+        return self._by_native.get(nat.id) if nat is not None else None
+
+    # ------------------------------------------------------------------ internals
+    def _run_model_step(self):
+        with _Trace("engine", "step"):
+            plan = self.core.plan()
+            self.last_outcome = plan.outcome
+            if plan.unserviceable:
+                for nat in plan.unserviceable:
+                    self._by_native.pop(nat.id, None)
+                if plan.outcome != StepOutcome.Planned:
+                    raise EngineStepError(StepOutcome.UnserviceableRequest, "a request needs more KV-cache blocks than the engine owns")
+            if plan.outcome != StepOutcome.Planned:
+                return
+            st = self.staging
+            try:
+                self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
+                edits, masks = self._logits_processors(plan)
+                toks = self.executor.execute(plan, edits, masks)
+            except ExecutionFailure as e:
+                outcome = self.core.abort(e.kind, str(e))
+                self.last_outcome = outcome
+                if outcome in (StepOutcome.FatalExecutionFailure, StepOutcome.ExecutionContractFailure):
+                    raise EngineStepError(outcome, str(e)) from e
+                return
+            except torch.cuda.OutOfMemoryError as e:
+                self.last_outcome = self.core.abort(FailureKind.CapacityExceeded, str(e))
+                return
+            except Exception as e:
+                kind = FailureKind.CapacityExceeded if "out of memory" in str(e).lower() else FailureKind.Fatal
+                self.last_outcome = self.core.abort(kind, str(e))
+                if kind == FailureKind.Fatal:
+                    raise EngineStepError(self.last_outcome, str(e)) from e
+                return
+            now = time.perf_counter()
+            for i, e in enumerate(plan.entries):
+                if not e.samples:
+                    continue
+                rq = self._by_native.get(e.request.id)
+                if rq is not None:
+                    if rq.t_first is None:
+                        rq.t_first = now
+                    rq.t_last = now
+                    rq.n_generated += 1
+                gp = self._guidance.get(e.request.id)
+                if gp is not None:
+                    gp.commit_tokens(np.asarray([toks[i]], dtype=np.int32))
+            self.last_outcome = self.core.commit(np.ascontiguousarray(toks, dtype=np.int32))
+            self.step_count += 1
+
+    def _logits_processors(self, plan):
+        """Sparse logits edits (min_length, repetition penalty, no-repeat-ngram) and grammar masks."""
+        rows, toks, opsl, vals = [], [], [], []
+        mask_rows, mask_list = [], []
+        V = self.model.config.vocab_size
+        eos = list(self.model.config.eos_token_ids)
+        any_mask = False
+        for i, e in enumerate(plan.entries):
+            if not e.samples:
+                mask_rows.append(-1)
+                continue
+            o = e.request.options
+            seq = None
+            if o.min_length > 0 and e.request.num_tokens < o.min_length:
+                for t in eos:
+                    rows.append(i); toks.append(t); opsl.append(0); vals.append(0.0)
+            if o.repetition_penalty != 1.0:
+                seq = e.request.tokens()
+                for t in np.unique(seq).tolist():
+                    rows.append(i); toks.append(t); opsl.append(1); vals.append(float(o.repetition_penalty))
+            if o.no_repeat_ngram_size > 0:
+                seq = e.request.tokens() if seq is None else seq
+                for t in native.no_repeat_ngram_banned(seq, o.no_repeat_ngram_size, V):
+                    rows.append(i); toks.append(t); opsl.append(0); vals.append(0.0)
+            gp = self._guidance.get(e.request.id)
+            if gp is not None:
+                mask_rows.append(len(mask_list))
+                mask_list.append(gp.compute_mask()[0])
+                any_mask = True
+            else:
+                mask_rows.append(-1)
+        dev = self.model.device
+        edits = []
+        for want in (1, 0):  # penalties before bans
+            sel = [j for j, o_ in enumerate(opsl) if o_ == want]
+            if sel:
+                g = lambda x, dt: torch.tensor([x[j] for j in sel], dtype=dt, device=dev)
+                edits.append((g(rows, torch.int32), g(toks, torch.int32), g(opsl, torch.int32), g(vals, torch.float32)))
+        masks = None
+        if any_mask:
+            masks = (torch.from_numpy(np.stack(mask_list)).to(dev), torch.tensor(mask_rows, dtype=torch.int32, device=dev))
+        return edits, masks
+
+    @property
+    def metrics(self) -> Dict[str, int]:
+        return dict(self.core.metrics)

@@ -196,6 +196,8 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
                                         Hq, Hkv, D, int(splits), _ptr(scratch), scratch.numel() if scratch is not None else 0,
                                         _stream())
     _lib.check(rc, "paged_attention")
+    if splits > 1:
+        _lib.LAUNCH_COUNT += 1  # the combine kernel
     return out
 
 

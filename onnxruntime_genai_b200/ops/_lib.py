@@ -96,6 +96,11 @@ def check_status(index: int) -> None:
         raise RuntimeError(f"sm_100a kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
+LAUNCH_COUNT = 0  # launcher calls so far (one kernel each; split-KV attention adds its combine kernel)
+
+
 def check(rc: int, what: str) -> None:
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")

@@ -190,8 +190,8 @@ def logits_edit(logits, rows, tokens, ops, values):
         if o == 0:
             logits[r, t] = lowest
         else:
-            x = float(logits[r, t])
-            logits[r, t] = x * val if x < 0 else x / val
+            x = logits[r, t]
+            logits[r, t] = torch.where(x < 0, x * val, x / val)  # fp32 arithmetic (may saturate to -inf like the kernel)
     return logits
 
 

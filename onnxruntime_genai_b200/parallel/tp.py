@@ -1,0 +1,77 @@
+"""Tensor parallelism over one node: one process per GPU, `torch.distributed` (NCCL) for rendezvous.
+
+The reference has no distributed layer at all (no NCCL / MPI anywhere in its tree), so everything
+here is new: attention heads and MLP columns are sharded at load time (models/loader.py), the
+row-parallel projections (o_proj, down_proj) produce partial sums that must be added over ranks,
+and the vocabulary-parallel LM head is gathered.
+
+Two reduction back ends:
+  * "nccl": `dist.all_reduce` — the baseline;
+  * "fused": the one-shot all-reduce kernel over NVLink peer memory in csrc/comm.cu (every rank
+    writes its partial tile into a symmetric buffer, signals, then reads all peers' tiles and sums
+    them in a fixed rank order, so every rank produces bit-identical results); see parallel/symm.py.
+On CPU (gloo) the same class runs the multi-rank tests of the sharding math.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class TensorParallel:
+    def __init__(self, rank: int, size: int, device: torch.device, group=None, backend: str = "nccl"):
+        self.rank, self.size, self.device, self.group = rank, size, device, group
+        self.backend = backend
+        self.comm = None
+        if backend == "fused":
+            from .symm import SymmetricComm
+            self.comm = SymmetricComm(rank, size, device, group)
+
+    @classmethod
+    def from_env(cls, backend: Optional[str] = None) -> Optional["TensorParallel"]:
+        """Builds the TP context from torchrun's environment; returns None for a single process."""
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world <= 1:
+            return None
+        rank = int(os.environ["RANK"])
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+            device = torch.device("cuda", local)
+            if not dist.is_initialized():
+                dist.init_process_group("nccl", device_id=device)
+            be = backend or os.environ.get("OGB_TP_BACKEND", "fused")
+        else:
+            device = torch.device("cpu")
+            if not dist.is_initialized():
+                dist.init_process_group("gloo")
+            be = "nccl"
+        return cls(rank, world, device, None, be)
+
+    # row-parallel output: sum of partials over ranks (in place)
+    def reduce(self, x: torch.Tensor, residual=None) -> torch.Tensor:
+        if self.size == 1:
+            return x
+        if self.comm is not None and x.is_cuda:
+            return self.comm.all_reduce(x)
+        if x.dtype == torch.bfloat16 and not x.is_cuda:
+            y = x.float()
+            dist.all_reduce(y, group=self.group)
+            return y.to(x.dtype)
+        dist.all_reduce(x, group=self.group)
+        return x
+
+    # vocabulary-parallel logits [B, V/size] -> [B, V]
+    def gather_logits(self, x: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(self.size)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def barrier(self):
+        if self.size > 1:
+            dist.barrier(group=self.group)

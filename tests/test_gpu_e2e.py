@@ -1,0 +1,114 @@
+"""End-to-end checks on the GPU: the bf16 sm_100a path against the fp32 CPU path of the same checkpoint."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import onnxruntime_genai_b200 as og
+from onnxruntime_genai_b200 import ops
+from onnxruntime_genai_b200.models.arch import PRESETS, ArchConfig
+from onnxruntime_genai_b200.models.builder import export_model
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    arch = copy.deepcopy(PRESETS["tiny-llama"])
+    sd_dir = tmp_path_factory.mktemp("ckpt")
+    from onnxruntime_genai_b200.models.builder import random_state_dict
+    sd = random_state_dict(arch, seed=0, std=0.05)
+    gpu, cpu = str(sd_dir / "gpu"), str(sd_dir / "cpu")
+    export_model(copy.deepcopy(arch), gpu, "bf16", "cuda", state_dict=sd, paged=True, block_size=16, num_blocks=512, max_batch_size=16)
+    export_model(copy.deepcopy(arch), cpu, "fp32", "cpu", state_dict=sd, paged=True, block_size=16, num_blocks=512, max_batch_size=16)
+    return gpu, cpu
+
+
+def _logits(model, prompt):
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=256, batch_size=prompt.shape[0])
+    g = og.Generator(model, p)
+    g.append_tokens(prompt)
+    return g, g.get_logits()[:, 0, :]
+
+
+def test_gpu_logits_match_cpu_fp32(dirs):
+    gpu, cpu = og.Model(dirs[0]), og.Model(dirs[1])
+    assert gpu.device_type == "cuda" and cpu.device_type == "cpu"
+    prompt = np.random.RandomState(5).randint(0, 32000, size=(3, 45)).astype(np.int32)
+    _, lg = _logits(gpu, prompt)
+    _, lc = _logits(cpu, prompt)
+    ops.check_kernel_status()
+    err = np.abs(lg - lc).max()
+    spread = lc.std()
+    assert err < 0.08 * spread + 0.02, f"max |gpu - cpu| = {err:.4f}, logits std {spread:.4f}"
+    # top-1 agreement wherever the fp32 margin is not tiny
+    top2 = np.sort(lc, axis=-1)[:, -2:]
+    for b in range(3):
+        if top2[b, 1] - top2[b, 0] > 0.1 * spread:
+            assert lg[b].argmax() == lc[b].argmax()
+
+
+def test_gpu_decode_steps_track_cpu(dirs):
+    gpu, cpu = og.Model(dirs[0]), og.Model(dirs[1])
+    prompt = np.random.RandomState(6).randint(0, 32000, size=(2, 20)).astype(np.int32)
+    gg, _ = _logits(gpu, prompt)
+    gc, _ = _logits(cpu, prompt)
+    for _ in range(12):
+        gc.generate_next_token()
+        # teacher-force the GPU generator with the CPU tokens so both see the same history
+        forced = np.full((2, 32000), -1e9, dtype=np.float32)
+        toks = gc.get_next_tokens()
+        forced[np.arange(2), toks] = 0
+        lg = gg.get_logits()[:, 0, :]
+        gg.set_logits(forced)
+        gg.generate_next_token()
+        assert gg.get_next_tokens().tolist() == toks.tolist()
+    lc = gc.get_logits()[:, 0, :]
+    lg = gg.get_logits()[:, 0, :]
+    assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
+
+
+def test_engine_isolated_equals_batched_on_gpu(dirs):
+    model = og.Model(dirs[0])
+    rng = np.random.RandomState(7)
+    prompts = [rng.randint(0, 32000, size=(n,)).astype(np.int32) for n in (33, 5, 70, 18, 129)]
+
+    def run(engine, plist, seeds):
+        reqs, outs = [], {}
+        for p, sd in zip(plist, seeds):
+            gp = og.GeneratorParams(model)
+            gp.set_search_options(max_length=len(p) + 20, do_sample=True, top_k=40, top_p=0.9, temperature=0.8, random_seed=sd)
+            r = og.Request(gp)
+            r.add_tokens(p)
+            engine.add_request(r)
+            reqs.append(r)
+            outs[id(r)] = []
+        while engine.has_pending_requests():
+            r = engine.step()
+            if r is None:
+                continue
+            while r.has_unseen_tokens():
+                outs[id(r)].append(r.get_unseen_token())
+            if r.is_turn_complete():
+                engine.remove_request(r)
+        engine.core.check_invariants()
+        return [outs[id(r)] for r in reqs]
+
+    engine = og.Engine(model)
+    together = run(engine, prompts, range(5))
+    alone = [run(engine, [p], [i])[0] for i, p in enumerate(prompts)]
+    ops.check_kernel_status()
+    same = sum(a == b for a, b in zip(alone, together))
+    # bf16 attention over a different batch composition is not bitwise identical; sampling is keyed by (seed, position),
+    # so sequences agree unless a near-tie flips.  Require most of them to agree exactly and all to agree on a prefix.
+    assert same >= 3, f"only {same}/5 requests produced identical tokens alone and batched"
+    for a, b in zip(alone, together):
+        assert a[:3] == b[:3]
+    assert engine.core.free_blocks == engine.options.num_blocks
+
+
+def test_smoke_entry():
+    import __graft_entry__ as g
+    g.smoke()

@@ -1,0 +1,298 @@
+"""Each sm_100a kernel against the plain PyTorch fp32 restatement of the same op."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from onnxruntime_genai_b200 import ops
+from onnxruntime_genai_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, std=1.0, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(DEV)
+
+
+def _close(a, b, rtol, atol):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (tol {tol.flatten()[err.argmax()].item():.4g}), mean err {err.mean().item():.4g}"
+
+
+def test_library_loaded():
+    from onnxruntime_genai_b200.ops import _lib
+    assert _lib.lib() is not None
+    ws = ops.workspace(torch.device("cuda", 0))
+    assert ws.sm_count >= 100
+
+
+# ------------------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (7, 256, 256), (64, 4096, 4096), (64, 6144, 4096), (33, 1000, 2880),
+                                   (128, 512, 1024), (300, 384, 512), (1024, 2048, 1024), (16, 128256, 256)])
+def test_gemm_matches_fp32(M, N, K):
+    x = _rand(M, K, std=1.0, seed=1)
+    w = _rand(N, K, std=0.05, seed=2)
+    y = ops.linear(x, w)
+    ops.check_kernel_status()
+    want = ref.linear(x.cpu(), w.cpu())
+    _close(y, want, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.05)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+def test_gemm_split_k(splits):
+    M, N, K = 48, 512, 2048
+    x, w = _rand(M, K, seed=3), _rand(N, K, std=0.05, seed=4)
+    y = ops.linear(x, w, splits=splits)
+    ops.check_kernel_status()
+    _close(y, ref.linear(x.cpu(), w.cpu()), rtol=2e-2, atol=0.05)
+    y2 = ops.linear(x, w, splits=splits)
+    assert torch.equal(y, y2), "split-K reduction must be deterministic and the tile counters self-cleaning"
+
+
+def test_gemm_epilogues():
+    M, N, K = 40, 768, 512
+    x, w = _rand(M, K, seed=5), _rand(N, K, std=0.05, seed=6)
+    bias, res = _rand(N, seed=7), _rand(M, N, seed=8)
+    y = ops.linear(x, w, bias=bias, residual=res)
+    _close(y, ref.linear(x.cpu(), w.cpu(), bias.cpu(), res.cpu()), rtol=2e-2, atol=0.05)
+    y32 = ops.linear(x, w, out_fp32=True)
+    assert y32.dtype == torch.float32
+    _close(y32, ref.linear(x.cpu(), w.cpu(), out_fp32=True), rtol=1e-2, atol=0.02)
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("M,I,K,splits", [(5, 256, 256, 1), (64, 1024, 512, 1), (64, 1024, 2048, 4), (200, 384, 256, 1)])
+def test_gemm_gate_up_silu(M, I, K, splits):
+    x = _rand(M, K, seed=9)
+    w = _rand(2 * I, K, std=0.05, seed=10)
+    y = ops.gate_up_act(x, w, splits=splits)
+    ops.check_kernel_status()
+    _close(y, ref.gate_up_act(x.cpu(), w.cpu()), rtol=3e-2, atol=0.05)
+
+
+def test_gemm_strided_activation():
+    M, K, N = 20, 256, 256
+    big = _rand(M, 3 * K, seed=11)
+    x = big[:, K:2 * K]
+    w = _rand(N, K, std=0.05, seed=12)
+    _close(ops.linear(x, w), ref.linear(x.cpu(), w.cpu()), rtol=2e-2, atol=0.05)
+
+
+# ------------------------------------------------------------------------------------------- norm / rope / misc
+@pytest.mark.parametrize("H", [256, 3072, 4096, 8192])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(H, with_res):
+    x, w = _rand(9, H, seed=13), _rand(H, seed=14)
+    res = _rand(9, H, seed=15) if with_res else None
+    res_ref = res.cpu().clone() if with_res else None
+    y, r = ops.norm(x, w, 1e-5, res)
+    yr, rr = ref.norm(x.cpu(), w.cpu(), 1e-5, res_ref)
+    _close(y, yr, rtol=2e-2, atol=2e-2)
+    if with_res:
+        _close(r, rr, rtol=1e-2, atol=1e-2)
+
+
+def test_layernorm_bias():
+    H = 2560
+    x, w, b = _rand(5, H, seed=16), _rand(H, seed=17), _rand(H, seed=18)
+    y, _ = ops.norm(x, w, 1e-5, None, b, layernorm=True)
+    yr, _ = ref.norm(x.cpu(), w.cpu(), 1e-5, None, b.cpu(), layernorm=True)
+    _close(y, yr, rtol=2e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("D,rot,inter,qk_norm", [(128, 128, False, False), (64, 64, False, True), (96, 96, False, False),
+                                                   (128, 64, True, False), (64, 32, False, False)])
+def test_rope_kv_append(D, rot, inter, qk_norm):
+    T, Hq, Hkv, slots_n = 11, 8, 2, 64
+    qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=19)
+    pos = torch.arange(3, 3 + T, dtype=torch.int32, device=DEV)
+    slots = torch.randperm(slots_n)[:T].to(torch.int32).to(DEV)
+    slots[2] = -1
+    freqs = torch.outer(torch.arange(64).float(), 1.0 / (10000 ** (torch.arange(0, rot, 2).float() / rot)))
+    cos, sin = freqs.cos().to(DEV), freqs.sin().to(DEV)
+    kc, vc = torch.zeros(slots_n, Hkv, D, dtype=torch.bfloat16, device=DEV), torch.zeros(slots_n, Hkv, D, dtype=torch.bfloat16, device=DEV)
+    qn = _rand(D, seed=20) if qk_norm else None
+    kn = _rand(D, seed=21) if qk_norm else None
+    q2, kc2, vc2 = qkv.cpu().clone(), kc.cpu().clone(), vc.cpu().clone()
+    ops.rope_kv_append(qkv, pos, slots, cos, sin, kc, vc, Hq, Hkv, D, rot, inter, qn, kn, 1e-6)
+    ref.rope_kv_append(q2, pos.cpu(), slots.cpu(), cos.cpu(), sin.cpu(), kc2, vc2, Hq, Hkv, D, rot, inter,
+                       qn.cpu() if qk_norm else None, kn.cpu() if qk_norm else None, 1e-6)
+    _close(qkv[:, :Hq * D], q2[:, :Hq * D], rtol=2e-2, atol=3e-2)
+    _close(kc, kc2, rtol=2e-2, atol=3e-2)
+    _close(vc, vc2, rtol=0, atol=0)
+
+
+def test_embedding_gather_actmul_cast():
+    table = _rand(1000, 512, seed=22)
+    ids = torch.tensor([0, 5, 999, 17], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    _close(ops.embedding(ids, table, 3.0), ref.embedding(ids.cpu(), table.cpu(), 3.0), rtol=1e-2, atol=1e-2)
+    x = _rand(6, 512, seed=23)
+    assert torch.equal(ops.gather_rows(x, torch.tensor([5, 0, 3], dtype=torch.int32, device=DEV)), x[[5, 0, 3]])
+    _close(ops.act_mul(x), ref.act_mul(x.cpu()), rtol=2e-2, atol=2e-2)
+    _close(ops.act_mul(x, "gelu"), ref.act_mul(x.cpu(), "gelu"), rtol=2e-2, atol=2e-2)
+    assert torch.equal(ops.to_float32(x), x.float())
+
+
+# ------------------------------------------------------------------------------------------- attention
+def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, softcap=0.0, splits=None, seed=30):
+    rng = np.random.RandomState(seed)
+    T = sum(q_lens)
+    cols = max((p + q + bs - 1) // bs for p, q in zip(past, q_lens))
+    nblocks = B * cols + 3
+    perm = rng.permutation(nblocks)
+    table = torch.full((B, cols), -1, dtype=torch.int32)
+    k_cache = _rand(nblocks * bs, Hkv, D, std=1.0, seed=seed + 1)
+    v_cache = _rand(nblocks * bs, Hkv, D, std=1.0, seed=seed + 2)
+    used = 0
+    for b in range(B):
+        need = (past[b] + q_lens[b] + bs - 1) // bs
+        table[b, :need] = torch.from_numpy(perm[used:used + need].astype(np.int32))
+        used += need
+    q = _rand(T, (Hq + 2 * Hkv) * D, std=1.0, seed=seed + 3)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    pl = torch.tensor(past, dtype=torch.int32)
+    sk = (torch.randn(Hq, generator=torch.Generator().manual_seed(seed)) * 2).float() if sinks else None
+    scale = 1.0 / math.sqrt(D)
+    out = ops.paged_attention(q, k_cache, v_cache, cu.to(DEV), pl.to(DEV), table.to(DEV), bs, Hq, Hkv, D, scale, window,
+                              sk.to(DEV) if sinks else None, softcap, max_q_len=max(q_lens), max_kv_len=max(p + q for p, q in zip(past, q_lens)),
+                              splits=splits)
+    want = ref.paged_attention(q.cpu(), k_cache.cpu(), v_cache.cpu(), cu, pl, table, bs, Hq, Hkv, D, scale, window, sk, softcap)
+    _close(out, want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("D", [64, 96, 128])
+def test_attention_decode(D):
+    _attention_case(B=5, q_lens=[1] * 5, past=[0, 15, 16, 200, 1023], Hq=8, Hkv=2, D=D, bs=16)
+
+
+@pytest.mark.parametrize("splits", [2, 4, 7])
+def test_attention_decode_split_kv(splits):
+    _attention_case(B=3, q_lens=[1, 1, 1], past=[5, 700, 2047], Hq=32, Hkv=8, D=128, bs=16, splits=splits)
+
+
+def test_attention_prefill_and_mixed():
+    _attention_case(B=3, q_lens=[70, 1, 33], past=[0, 90, 17], Hq=8, Hkv=2, D=128, bs=16)
+    _attention_case(B=2, q_lens=[257, 5], past=[0, 300], Hq=4, Hkv=4, D=64, bs=256)
+
+
+def test_attention_mha_and_wide_group():
+    _attention_case(B=2, q_lens=[20, 1], past=[3, 50], Hq=4, Hkv=4, D=96, bs=16)
+    _attention_case(B=2, q_lens=[9, 1], past=[40, 333], Hq=16, Hkv=2, D=64, bs=16)
+
+
+def test_attention_window_sinks_softcap():
+    _attention_case(B=3, q_lens=[1, 1, 40], past=[500, 30, 100], Hq=8, Hkv=2, D=64, bs=16, window=128, sinks=True)
+    _attention_case(B=2, q_lens=[1, 1], past=[500, 130], Hq=8, Hkv=2, D=64, bs=16, window=128, sinks=True, splits=3)
+    _attention_case(B=2, q_lens=[1, 19], past=[77, 0], Hq=8, Hkv=4, D=128, bs=16, softcap=30.0)
+
+
+# ------------------------------------------------------------------------------------------- sampling
+def test_argmax_and_greedy_rows():
+    x = _rand(7, 32000, dtype=torch.float32, seed=40)
+    want = x.argmax(-1).to(torch.int32)
+    assert torch.equal(ops.argmax(x), want)
+    ones = torch.ones(7, dtype=torch.int32, device=DEV)
+    f = torch.ones(7, dtype=torch.float32, device=DEV)
+    z = torch.zeros(7, dtype=torch.int64, device=DEV)
+    assert torch.equal(ops.sample(x, ones, f, f, z, ones), want)
+
+
+def test_sampling_distribution_matches_reference():
+    """Empirical token frequencies of the device sampler vs the exact truncated distribution."""
+    V, n = 512, 20000
+    g = torch.Generator().manual_seed(41)
+    row = (torch.randn(V, generator=g) * 2.5).float()
+    for k, p, t in [(50, 0.9, 0.7), (8, 1.0, 1.0), (0, 0.8, 1.3), (0, 1.0, 1.0)]:
+        logits = row.to(DEV).repeat(n, 1).contiguous()
+        tk = torch.full((n,), k if k > 0 else -1, dtype=torch.int32, device=DEV)
+        tp = torch.full((n,), p, dtype=torch.float32, device=DEV)
+        tt = torch.full((n,), t, dtype=torch.float32, device=DEV)
+        seeds = torch.full((n,), 1234, dtype=torch.int64, device=DEV)
+        pos = torch.arange(n, dtype=torch.int32, device=DEV)
+        toks = ops.sample(logits, tk, tp, tt, seeds, pos).cpu().long()
+        ids, probs = ref.sampled_distribution(row, k if k > 1 else None, p if 0 < p < 1 else None, t)
+        allowed = set(ids.tolist())
+        assert set(toks.tolist()) <= allowed, "sampled a token outside the truncated support"
+        freq = torch.bincount(toks, minlength=V).double() / n
+        expect = torch.zeros(V, dtype=torch.double)
+        expect[ids] = probs
+        # total variation distance; for n=20000 and support <= 512 the noise floor is ~0.05
+        tv = 0.5 * (freq - expect).abs().sum().item()
+        assert tv < 0.06, f"(k={k}, p={p}, t={t}) total variation {tv:.3f}"
+
+
+def test_sampling_reproducible_and_batch_independent():
+    V = 32000
+    x = _rand(16, V, dtype=torch.float32, seed=42) * 3
+    tk = torch.full((16,), 40, dtype=torch.int32, device=DEV)
+    tp = torch.full((16,), 0.95, dtype=torch.float32, device=DEV)
+    tt = torch.full((16,), 0.8, dtype=torch.float32, device=DEV)
+    seeds = torch.arange(16, dtype=torch.int64, device=DEV) + 99
+    pos = torch.full((16,), 7, dtype=torch.int32, device=DEV)
+    a = ops.sample(x, tk, tp, tt, seeds, pos)
+    b = ops.sample(x, tk, tp, tt, seeds, pos)
+    assert torch.equal(a, b)
+    one = ops.sample(x[5:6].contiguous(), tk[5:6], tp[5:6], tt[5:6], seeds[5:6], pos[5:6])
+    assert int(one[0]) == int(a[5]), "a row must sample the same token alone or inside a batch"
+
+
+def test_sampling_ties_and_masked_rows():
+    V = 1000
+    x = torch.zeros(4, V, dtype=torch.float32, device=DEV)           # every logit ties
+    tk = torch.full((4,), 10, dtype=torch.int32, device=DEV)
+    f1 = torch.ones(4, dtype=torch.float32, device=DEV)
+    seeds = torch.arange(4, dtype=torch.int64, device=DEV)
+    toks = ops.sample(x, tk, f1, f1, seeds, torch.zeros(4, dtype=torch.int32, device=DEV))
+    assert bool((toks < 10).all()), "ties at the top-k threshold keep the lowest indices"
+    y = torch.full((2, V), torch.finfo(torch.float32).min, device=DEV)
+    y[0, 77] = 0.0
+    y[1, 5] = 1.0
+    y[1, 6] = 1.0
+    toks = ops.sample(y, torch.tensor([50, 50], dtype=torch.int32, device=DEV), f1[:2] * 0.9, f1[:2], seeds[:2],
+                      torch.zeros(2, dtype=torch.int32, device=DEV))
+    assert int(toks[0]) == 77 and int(toks[1]) in (5, 6)
+
+
+def test_topk_and_beam_candidates():
+    x = _rand(6, 5000, dtype=torch.float32, seed=43)
+    for k in (1, 8, 64):
+        v, i = ops.topk(x, k)
+        rv, ri = ref.topk(x.cpu(), k)
+        assert torch.equal(i.cpu(), ri)
+        _close(v, rv, 0, 0)
+    add = _rand(6, dtype=torch.float32, seed=44)
+    v, i = ops.topk(x, 8, log_softmax=True, add=add)
+    rv, ri = ref.topk(x.cpu(), 8, log_softmax=True, add=add.cpu())
+    assert torch.equal(i.cpu(), ri)
+    _close(v, rv, rtol=1e-4, atol=1e-4)
+    s, t, b = ops.beam_candidates(x, add, batch=2, beams=3)
+    rs, rt, rb = ops.beam_candidates(x.cpu(), add.cpu(), batch=2, beams=3)
+    assert torch.equal(t.cpu(), rt) and torch.equal(b.cpu(), rb)
+    _close(s, rs, rtol=1e-4, atol=1e-4)
+
+
+def test_logits_mask_and_edit():
+    V = 1003
+    x = _rand(3, V, dtype=torch.float32, seed=45)
+    xr = x.cpu().clone()
+    words = (V - 1) // 32 + 1
+    mask = torch.randint(-2**31, 2**31 - 1, (2, words), dtype=torch.int64).to(torch.int32)
+    rows = torch.tensor([1, -1, 0], dtype=torch.int32)
+    ops.logits_bitmask(x, mask.to(DEV), rows.to(DEV))
+    ref.logits_bitmask(xr, mask, rows)
+    assert torch.equal(x.cpu(), xr)
+    x = _rand(3, V, dtype=torch.float32, seed=46)
+    xr = x.cpu().clone()
+    r = torch.tensor([0, 0, 2], dtype=torch.int32)
+    t = torch.tensor([5, 9, 1000], dtype=torch.int32)
+    o = torch.tensor([1, 0, 1], dtype=torch.int32)
+    v = torch.tensor([1.3, 0.0, 2.0])
+    ops.logits_edit(x, r.to(DEV), t.to(DEV), o.to(DEV), v.to(DEV))
+    ref.logits_edit(xr, r, t, o, v)
+    _close(x, xr, rtol=1e-6, atol=1e-6)
