@@ -11,11 +11,11 @@
 // query at position p to keys in (p - window, p]; `sinks` adds one learned logit per query head
 // to the softmax denominator; softcap applies cap * tanh(x / cap) to the scaled scores.
 //
-// Work decomposition: one CTA = (request, kv head, tile of 64 query rows, kv split) where a
+// Work decomposition: one CTA = (request, kv head, tile of 64 (or, in decode, 16) query rows, kv split) where a
 // "row" is one (query token, query head of the group) pair, so a decode step of a 4:1 GQA model
 // keeps its 4 heads in one MMA tile and reads each K/V row once.  K/V tiles of 64 keys are
 // gathered through the block table with 16-byte cp.async copies into XOR-swizzled shared memory,
-// double buffered; QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
+// three tiles in flight per CTA; QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
 // tile's M is at most a few rows in decode, far below the 64-row minimum of tcgen05.mma, and
 // the kernel is bound by the KV stream, not by tensor throughput.)
 #include "common.cuh"
@@ -26,6 +26,7 @@ namespace ogb {
 constexpr int ATT_BM = 64;   // query rows per CTA (4 warps x 16)
 constexpr int ATT_BN = 64;   // keys per tile
 constexpr int ATT_THREADS = 128;
+constexpr int ATT_STAGES = 3;  // K/V tiles in flight per CTA
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
@@ -45,16 +46,22 @@ __device__ __forceinline__ int swz(int row, int chunk) {  // element offset of a
   return row * SROW + ((((chunk & ~7) | ((chunk ^ row) & 7))) << 3);
 }
 
-template <int D>
+// DECODE = true: the tile has at most 16 query rows (e.g. one token x a GQA group of up to 16 heads).
+// All four warps then share those rows and split the 64 keys of every K/V tile between them
+// (16 keys each), keeping private online-softmax state that is merged through shared memory at the
+// end.  DECODE = false: each warp owns 16 of the 64 query rows and walks the whole tile.
+template <int D, bool DECODE>
 __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnParams p) {
   constexpr int SROW = ((D + 63) / 64) * 64;
   constexpr int CHUNKS = D / 8;     // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;    // k-steps of QK^T
   constexpr int DTILES = D / 8;     // n-tiles of PV
+  constexpr int BM = DECODE ? 16 : ATT_BM;
+  constexpr int NT = DECODE ? 2 : ATT_BN / 8;  // score n-tiles (8 keys each) per warp and K/V tile
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* sK = sQ + ATT_BM * SROW;            // [2][BN][SROW]
-  __nv_bfloat16* sV = sK + 2 * ATT_BN * SROW;        // [2][BN][SROW]
+  __nv_bfloat16* sK = sQ + BM * SROW;                        // [STAGES][BN][SROW]
+  __nv_bfloat16* sV = sK + ATT_STAGES * ATT_BN * SROW;       // [STAGES][BN][SROW]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int kvh = blockIdx.y;
@@ -63,14 +70,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
   const int tok0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - tok0;
   const int rows = q_len * G;
-  const int row0 = blockIdx.x * ATT_BM;
+  const int row0 = blockIdx.x * BM;
   if (row0 >= rows) return;
   const int past = p.past_lens[b];
   const int kv_total = past + q_len;
   const int32_t* table = p.block_table + size_t(b) * p.table_cols;
 
   // Key range needed by this tile of rows, then the part of it owned by this split.
-  const int last_tq = min(q_len - 1, (row0 + ATT_BM - 1) / G);
+  const int last_tq = min(q_len - 1, (row0 + BM - 1) / G);
   int kv_hi = past + last_tq + 1;
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, past + row0 / G - p.window + 1);
@@ -84,26 +91,30 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
   const int tile_end = kv_hi > kv_lo ? (kv_hi + ATT_BN - 1) / ATT_BN : tile_begin;
   const int n_tiles = tile_end - tile_begin;
 
+  // Each warp copies 16 key rows of the tile.  Lanes 0..15 look up the cache slot of one row each; the
+  // copies then walk the warp's rows chunk by chunk with consecutive lanes on consecutive 16-byte
+  // chunks, so every warp instruction covers whole 32-byte sectors (full rows for head_dim 128).
   auto load_kv = [&](int tile, int buf) {
-    const int base = tile * ATT_BN;
+    const int jrow = tile * ATT_BN + warp * 16 + (lane & 15);
+    int slot = -1;
+    if (jrow < kv_hi) slot = table[jrow / p.block_size] * p.block_size + jrow % p.block_size;
     __nv_bfloat16* dk = sK + buf * ATT_BN * SROW;
     __nv_bfloat16* dv = sV + buf * ATT_BN * SROW;
-    for (int c = tid; c < ATT_BN * CHUNKS; c += ATT_THREADS) {
-      const int key = c / CHUNKS, ch = c % CHUNKS;
-      const int j = base + key;
-      const bool ok = j < kv_hi && j >= 0;
-      size_t off = 0;
-      if (ok) {
-        const int blk = table[j / p.block_size];
-        off = ((size_t(blk) * p.block_size + j % p.block_size) * p.Hkv + kvh) * D + ch * 8;
-      }
+#pragma unroll
+    for (int c = 0; c < CHUNKS / 2; ++c) {
+      const int item = c * 32 + lane;
+      const int kl = item / CHUNKS, ch = item % CHUNKS;
+      const int sl = __shfl_sync(0xffffffffu, slot, kl);
+      const bool ok = sl >= 0;
+      const size_t off = ok ? (size_t(sl) * p.Hkv + kvh) * D + ch * 8 : 0;
+      const int key = warp * 16 + kl;
       cp_async16(dk + swz<SROW>(key, ch), p.k_cache + off, ok);
       cp_async16(dv + swz<SROW>(key, ch), p.v_cache + off, ok);
     }
   };
 
   // Q tile (zero rows beyond the request's rows).
-  for (int c = tid; c < ATT_BM * CHUNKS; c += ATT_THREADS) {
+  for (int c = tid; c < BM * CHUNKS; c += ATT_THREADS) {
     const int r = c / CHUNKS, ch = c % CHUNKS;
     const int gr = row0 + r;
     const bool ok = gr < rows;
@@ -113,10 +124,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
   }
   if (n_tiles > 0) load_kv(tile_begin, 0);
   cp_async_commit();
+  if (n_tiles > 1) load_kv(tile_begin + 1, 1);
+  cp_async_commit();
 
-  const bool warp_active = row0 + warp * 16 < rows;
-  // Per-thread rows: r_lo = warp*16 + g, r_hi = r_lo + 8.
-  const int gr_lo = row0 + warp * 16 + g, gr_hi = gr_lo + 8;
+  const int row_base = DECODE ? 0 : warp * 16;       // first tile row of this warp
+  const int key_base = DECODE ? warp * 16 : 0;       // first key (within a K/V tile) of this warp
+  const bool warp_active = row0 + row_base < rows;
+  // Per-thread rows: r_lo = row_base + g, r_hi = r_lo + 8.
+  const int gr_lo = row0 + row_base + g, gr_hi = gr_lo + 8;
   const int qpos_lo = past + gr_lo / G, qpos_hi = past + gr_hi / G;
   const bool valid_lo = gr_lo < rows, valid_hi = gr_hi < rows;
 
@@ -128,40 +143,40 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
   const float sc2 = p.scale * LOG2E;
 
   for (int it = 0; it < n_tiles; ++it) {
-    const int buf = it & 1;
-    if (it + 1 < n_tiles) load_kv(tile_begin + it + 1, buf ^ 1);
+    const int buf = it % ATT_STAGES;
+    if (it + 2 < n_tiles) load_kv(tile_begin + it + 2, (it + 2) % ATT_STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<2>();
     __syncthreads();
     if (it == 0 && warp_active) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
-        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int r = row_base + (lane & 7) + ((lane >> 3) & 1) * 8;
         ldmatrix_x4(qf[ks], sQ + swz<SROW>(r, ks * 2 + (lane >> 4)));
       }
     }
     if (warp_active) {
       const __nv_bfloat16* tk = sK + buf * ATT_BN * SROW;
       const __nv_bfloat16* tv = sV + buf * ATT_BN * SROW;
-      float s[ATT_BN / 8][4];
+      float s[NT][4];
 #pragma unroll
-      for (int i = 0; i < ATT_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+      for (int i = 0; i < NT; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
 #pragma unroll
-        for (int np = 0; np < ATT_BN / 16; ++np) {
+        for (int np = 0; np < NT / 2; ++np) {
           uint32_t kb[4];
-          const int key = (np * 2 + (lane >> 4)) * 8 + (lane & 7);
+          const int key = key_base + (np * 2 + (lane >> 4)) * 8 + (lane & 7);
           ldmatrix_x4(kb, tk + swz<SROW>(key, ks * 2 + ((lane >> 3) & 1)));
           mma_bf16_16816(s[np * 2], qf[ks], kb[0], kb[1]);
           mma_bf16_16816(s[np * 2 + 1], qf[ks], kb[2], kb[3]);
         }
       }
       // scale, softcap, mask, running max
-      const int jbase = (tile_begin + it) * ATT_BN;
+      const int jbase = (tile_begin + it) * ATT_BN + key_base;
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = jbase + nt * 8 + t4 * 2 + (e & 1);
@@ -189,7 +204,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
 #pragma unroll
       for (int i = 0; i < DTILES; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
 #pragma unroll
-      for (int nt = 0; nt < ATT_BN / 8; ++nt) {
+      for (int nt = 0; nt < NT; ++nt) {
         s[nt][0] = exp2f(s[nt][0] - ms_lo); s[nt][1] = exp2f(s[nt][1] - ms_lo);
         s[nt][2] = exp2f(s[nt][2] - ms_hi); s[nt][3] = exp2f(s[nt][3] - ms_hi);
         l_lo += s[nt][0] + s[nt][1];
@@ -197,7 +212,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
       }
       // O += P V
 #pragma unroll
-      for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+      for (int kk = 0; kk < NT / 2; ++kk) {
         uint32_t pa[4];
         pa[0] = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]);
         pa[1] = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
@@ -206,7 +221,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
 #pragma unroll
         for (int dp = 0; dp < DTILES / 2; ++dp) {
           uint32_t vb[4];
-          const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int key = key_base + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
           ldmatrix_x4_trans(vb, tv + swz<SROW>(key, dp * 2 + (lane >> 4)));
           mma_bf16_16816(o[dp * 2], pa, vb[0], vb[1]);
           mma_bf16_16816(o[dp * 2 + 1], pa, vb[2], vb[3]);
@@ -216,13 +231,77 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
     __syncthreads();
   }
   cp_async_wait<0>();
-  if (!warp_active) return;
 
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 
+  if (DECODE) {
+    // Merge the four warps' partial states: warp w parks (m, l, O) in shared memory (the K/V stages
+    // are idle now), then all threads combine: thread t owns row t/8 and dims [(t%8)*D/8, +D/8).
+    __syncthreads();
+    float* mo = reinterpret_cast<float*>(sK);          // [4 warps][16 rows][D]
+    float* mml = mo + 4 * 16 * D;                      // [4 warps][16 rows][2]
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+      *reinterpret_cast<float2*>(mo + (warp * 16 + g) * D + i * 8 + t4 * 2) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(mo + (warp * 16 + g + 8) * D + i * 8 + t4 * 2) = make_float2(o[i][2], o[i][3]);
+    }
+    if (t4 == 0) {
+      mml[(warp * 16 + g) * 2] = m_lo; mml[(warp * 16 + g) * 2 + 1] = l_lo;
+      mml[(warp * 16 + g + 8) * 2] = m_hi; mml[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+    }
+    __syncthreads();
+    const int r = tid >> 3, seg = tid & 7;
+    const int gr = row0 + r;
+    if (gr >= rows) return;
+    constexpr int SEG = D / 8;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+    float wgt[4], L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mml[(w * 16 + r) * 2];
+      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += wgt[w] * mml[(w * 16 + r) * 2 + 1];
+    }
+    float acc[SEG];
+#pragma unroll
+    for (int d = 0; d < SEG; ++d) {
+      float a = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) a += wgt[w] * mo[(w * 16 + r) * D + seg * SEG + d];
+      acc[d] = a;
+    }
+    const int tq = gr / G, hq = kvh * G + gr % G;
+    if (p.splits > 1) {
+      const size_t grow = size_t(tok0 + tq) * p.Hq + hq;
+      float* po = p.part_o + (size_t(split) * p.total_rows + grow) * D + seg * SEG;
+#pragma unroll
+      for (int d = 0; d < SEG; ++d) po[d] = acc[d];
+      if (seg == 0) {
+        float* pm = p.part_ml + (size_t(split) * p.total_rows + grow) * 2;
+        pm[0] = M; pm[1] = L;
+      }
+    } else {
+      float scale_o = 1.f;
+      if (p.sinks) {
+        const float sk = p.sinks[hq] * LOG2E;
+        const float mm = fmaxf(M, sk);
+        scale_o = exp2f(M - mm);
+        L = L * scale_o + exp2f(sk - mm);
+      }
+      const float inv = L > 0.f ? scale_o / L : 0.f;
+      __nv_bfloat16* po = p.out + size_t(tok0 + tq) * p.out_stride + size_t(hq) * D + seg * SEG;
+#pragma unroll
+      for (int d = 0; d < SEG; d += 2) *reinterpret_cast<uint32_t*>(po + d) = pack_bf16x2(acc[d] * inv, acc[d + 1] * inv);
+    }
+    return;
+  }
+
+  if (!warp_active) return;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int gr = half ? gr_hi : gr_lo;
@@ -294,19 +373,21 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
-template <int D>
-static int LaunchAttention(const AttnParams& p, int max_q_len, cudaStream_t stream) {
+template <int D, bool DECODE>
+static int LaunchAttentionMode(const AttnParams& p, int max_q_len, cudaStream_t stream) {
   constexpr int SROW = ((D + 63) / 64) * 64;
-  constexpr int SMEM = (ATT_BM + 4 * ATT_BN) * SROW * 2;
+  constexpr int BM = DECODE ? 16 : ATT_BM;
+  constexpr int SMEM = (BM + 2 * ATT_STAGES * ATT_BN) * SROW * 2;
+  static_assert(!DECODE || (4 * 16 * D + 4 * 16 * 2) * 4 <= ATT_STAGES * ATT_BN * SROW * 2, "merge buffers must fit in the K stages");
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(paged_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(paged_attention_kernel<D, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
     configured = true;
   }
   const int G = p.Hq / p.Hkv;
-  const int q_tiles = (max_q_len * G + ATT_BM - 1) / ATT_BM;
+  const int q_tiles = (max_q_len * G + BM - 1) / BM;
   dim3 grid(q_tiles, p.Hkv, p.B * p.splits);
-  paged_attention_kernel<D><<<grid, ATT_THREADS, SMEM, stream>>>(p);
+  paged_attention_kernel<D, DECODE><<<grid, ATT_THREADS, SMEM, stream>>>(p);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (p.splits > 1) {
     const int warps = 4;
@@ -315,6 +396,13 @@ static int LaunchAttention(const AttnParams& p, int max_q_len, cudaStream_t stre
     if (cudaGetLastError() != cudaSuccess) return -4;
   }
   return 0;
+}
+
+template <int D>
+static int LaunchAttention(const AttnParams& p, int max_q_len, cudaStream_t stream) {
+  const int G = p.Hq / p.Hkv;
+  if (max_q_len * G <= 16) return LaunchAttentionMode<D, true>(p, max_q_len, stream);
+  return LaunchAttentionMode<D, false>(p, max_q_len, stream);
 }
 
 }  // namespace ogb

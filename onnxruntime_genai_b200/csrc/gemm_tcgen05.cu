@@ -1,23 +1,43 @@
-// bf16 linear layer on the 5th-generation tensor cores:  C[M,N] = A[M,K] * W[N,K]^T  (+ epilogue)
+// bf16 linear layer on the 5th-generation tensor cores:  C[M,N] = A[M,K] * W[N,K]^T  (+ epilogue),
+// optionally fused with the tensor-parallel all-reduce of the partial sums over NVLink.
 //
 // The weight is the UMMA "M" operand (128 output features per CTA) and the activations are the
 // UMMA "N" operand (16..256 tokens), so the same kernel serves decode (few tokens, bandwidth bound:
-// every SM streams weight tiles through a deep TMA pipeline, split-K fills the machine when N/128
-// is small) and prefill (256-token tiles, compute bound).  Both operands are K-major in shared
-// memory with the 128-byte swizzle written by TMA; accumulators live in tensor memory and are read
-// back with tcgen05.ld by four epilogue warps.
+// every SM streams weight tiles through a deep TMA pipeline, two CTAs per SM) and prefill
+// (256-token tiles, compute bound).  Both operands are K-major in shared memory with the 128-byte
+// swizzle written by TMA; accumulators live in tensor memory and are read back with tcgen05.ld.
 //
 // Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane),
 // warps 2..5 = epilogue (warp 2 also owns the TMEM allocation).
 //
-// Epilogues: optional bias[N], optional residual add, fp32 or bf16 output, and a dual-accumulator
-// mode that computes silu(A*Wg^T) * (A*Wu^T) for a stacked [gate; up] weight (reference graph:
-// gate_proj/up_proj MatMul + Sigmoid/Mul, src/python/py/models/builders/base.py:4065-4131).
-// Split-K partial tiles go to a caller-provided fp32 workspace; the CTA that arrives last at the
-// tile's counter reduces them in a fixed order (deterministic) and runs the epilogue.
+// Split-K (decode: N/128 tiles alone cannot fill 148 SMs) runs as a thread-block CLUSTER of up to
+// 8 CTAs along z: each CTA accumulates its K slice in its own tensor memory and parks the fp32 tile
+// in its (by then idle) pipeline shared memory; after a cluster barrier every CTA reduces a slice
+// of the token columns by reading its peers' tiles through distributed shared memory in rank order
+// (deterministic).  No global workspace, no atomics.  The same shared-memory tile transposes the
+// accumulator (one thread per output feature) into 16-byte row segments for the stores.
 //
-// Every mbarrier wait is bounded: when one runs out the kernel records a status code, waits
-// (bounded) for its own TMA copies in flight, frees its tensor memory and returns.
+// Programmatic dependent launch: the producer prefetches WEIGHT tiles (which no earlier kernel
+// writes) for every pipeline stage before griddepcontrol.wait; activations, residual reads and all
+// stores come after it, so weight streaming overlaps the tail of the previous kernel.
+//
+// Epilogues: bias[N], residual add, fp32 or bf16 output, and a paired activation for the MLP: with
+// the gate and up projection rows interleaved in blocks of 64 (tile t = 64 gate rows then the 64
+// up rows of the same features) the kernel writes silu(gate) * up, N/2 columns (reference graph:
+// gate_proj/up_proj MatMul + Sigmoid/Mul, src/python/py/models/builders/base.py:4065-4131).
+//
+// Tensor-parallel all-reduce (row-parallel o_proj / down_proj in decode), fused: instead of
+// storing its reduced slice, a CTA pushes it (bf16) into the receive buffer of EVERY rank with
+// plain peer stores over NVLink, adds one to that slice's arrival counter on every rank
+// (red.release.sys), waits (bounded) until its own counter shows all ranks' arrivals, then sums
+// the world's partials from its local buffer in rank order (bit-identical on every rank), adds
+// the residual and stores.  Counters only grow and buffers alternate by the parity of a per-slice
+// use count kept on the device, so the kernel replays unchanged inside CUDA graphs.  The
+// reference has no distributed code at all; the comparison bar is GEMM + ncclAllReduce.
+//
+// Every wait is bounded: when one runs out the kernel records a status code, waits (bounded) for
+// its own TMA copies in flight, still meets its barriers, frees its tensor memory and returns.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -31,39 +51,85 @@ constexpr int GEMM_BLOCK_K = 64;
 constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 constexpr int W_TILE_BYTES = GEMM_BLOCK_N * GEMM_BLOCK_K * 2;  // 16 KiB
+constexpr int COMM_MAX_WORLD = 8;
+
+struct CommParams {
+  int world, rank;                        // world <= 1 with buf[0] == nullptr disables the fused all-reduce
+  __nv_bfloat16* buf[COMM_MAX_WORLD];     // receive buffer of every rank: [2 parities][world sources][plane_elems]
+  uint32_t* flag[COMM_MAX_WORLD];         // arrival counters of every rank: [max_slots]
+  uint32_t* uses;                         // this rank's use count per slot
+  long long plane_elems;
+  int max_slots;
+};
 
 struct GemmParams {
-  int M, N, K;
-  int dual_row_offset;  // rows between the gate tile and the up tile (dual mode)
+  int M, N, K;          // N = weight rows
   int splits, kb_per_split, total_kb;
   void* C;
   int ldc;
   int out_fp32;
+  int act_pair;         // 1: tiles hold 64 gate rows + 64 up rows; output silu(gate)*up with N/2 columns
   const __nv_bfloat16* residual;
   int ldr;
   const __nv_bfloat16* bias;
-  float* workspace;
-  int* counters;
   int* status;
+  int pdl;
+  CommParams comm;
 };
 
-template <int BT, bool DUAL>
+template <int BT>
 struct GemmCfg {
   static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
-  static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * W_TILE_BYTES + A_TILE_BYTES;
-  static constexpr int MAX_STAGES = (196 * 1024) / STAGE_BYTES;
+  static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES;
+  // Decode-sized tiles keep two CTAs per SM: more bytes in flight per SM, dynamic balance between
+  // SMs, and room for the next kernel's CTAs to become resident and prefetch weights.
+  static constexpr bool TWO_PER_SM = BT <= 64;
+  static constexpr int BUDGET = TWO_PER_SM ? 100 * 1024 : 196 * 1024;
+  static constexpr int MAX_STAGES = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
-  static constexpr int TMEM_COLS_RAW = (DUAL ? 2 : 1) * BT;
-  static constexpr int TMEM_COLS = TMEM_COLS_RAW < 32 ? 32 : TMEM_COLS_RAW;
+  static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
+  static constexpr int PARTIAL_BYTES = BT * GEMM_BLOCK_N * 4;  // fp32 tile parked in stage memory
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static_assert(PARTIAL_BYTES <= STAGES * STAGE_BYTES, "the parked tile must fit in the pipeline memory");
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
-template <int BT, bool DUAL>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, GemmParams p) {
-  using Cfg = GemmCfg<BT, DUAL>;
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {  // bypass L1: the data was written by a peer GPU
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <int BT>
+__global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BT>::TWO_PER_SM ? 2 : 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
+  using Cfg = GemmCfg<BT>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -72,7 +138,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
+  volatile uint32_t* use_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
@@ -83,7 +149,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
@@ -96,25 +161,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl) pdl_launch_dependents();
 
-  auto stage_w0 = [&](int s) { return smem + s * Cfg::STAGE_BYTES; };
-  auto stage_w1 = [&](int s) { return smem + s * Cfg::STAGE_BYTES + W_TILE_BYTES; };
-  auto stage_a = [&](int s) { return smem + s * Cfg::STAGE_BYTES + (DUAL ? 2 : 1) * W_TILE_BYTES; };
+  auto stage_w = [&](int s) { return smem + s * Cfg::STAGE_BYTES; };
+  auto stage_a = [&](int s) { return smem + s * Cfg::STAGE_BYTES + W_TILE_BYTES; };
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
 
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------------------------ TMA producer
-      int issued = 0;
-      for (int i = 0; i < num_kb; ++i) {
+      auto load_w = [&](int i) {
+        const int s = i % STAGES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d(stage_w(s), &tmap_w, &full_bar[s], (kb0 + i) * GEMM_BLOCK_K, n_tile * GEMM_BLOCK_N);
+      };
+      auto load_a = [&](int i) {
+        tma_load_2d(stage_a(i % STAGES), &tmap_a, &full_bar[i % STAGES], (kb0 + i) * GEMM_BLOCK_K, m_tile * BT);
+      };
+      // Weights are never written by an earlier kernel of the stream: fill the pipeline with them
+      // before waiting for the producer of the activations.
+      const int pre = min(STAGES, num_kb);
+      for (int i = 0; i < pre; ++i) load_w(i);
+      if (p.pdl) pdl_wait();
+      for (int i = 0; i < pre; ++i) load_a(i);
+      int issued = pre;
+      for (int i = pre; i < num_kb; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); break; }
-        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        const int kx = (kb0 + i) * GEMM_BLOCK_K;
-        tma_load_2d(stage_w0(s), &tmap_w, &full_bar[s], kx, n_tile * GEMM_BLOCK_N);
-        if (DUAL) tma_load_2d(stage_w1(s), &tmap_w, &full_bar[s], kx, p.dual_row_offset + n_tile * GEMM_BLOCK_N);
-        tma_load_2d(stage_a(s), &tmap_a, &full_bar[s], kx, m_tile * BT);
+        load_w(i);
+        load_a(i);
         ++issued;
       }
       if (*abort_flag) {
@@ -134,91 +210,176 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t ph = (i / STAGES) & 1;
         if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag)) { fail(OGB_ERR_WAIT_TMA); ok = false; break; }
         tc_fence_after();
-        const uint32_t w0 = smem_u32(stage_w0(s)), w1 = smem_u32(stage_w1(s)), a = smem_u32(stage_a(s));
+        const uint32_t w = smem_u32(stage_w(s)), a = smem_u32(stage_a(s));
 #pragma unroll
-        for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k) {
-          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          const uint64_t db = umma_desc_sw128(a + k * GEMM_UMMA_K * 2);
-          umma_f16(tmem_base, umma_desc_sw128(w0 + k * GEMM_UMMA_K * 2), db, idesc, acc);
-          if (DUAL) umma_f16(tmem_base + BT, umma_desc_sw128(w1 + k * GEMM_UMMA_K * 2), db, idesc, acc);
-        }
+        for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
+          umma_f16(tmem_base, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc,
+                   (i > 0 || k > 0) ? 1u : 0u);
         umma_commit(&empty_bar[s]);
       }
       if (ok) umma_commit(accum_bar);
     }
-  } else {
-    // -------------------------------------------------------------------- epilogue (4 warps)
+  }
+
+  // -------------------------------------------------------------------- epilogue (warps 2..5)
+  const bool epi = warp >= 2;
+  const int et = threadIdx.x - 64;   // 0..127 for epilogue threads
+  float* part = reinterpret_cast<float*>(smem);  // [BT][128] fp32, reuses the pipeline stages
+  if (epi) {
     const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
     const int row = quarter * 32 + lane;
-    const int n = n_tile * GEMM_BLOCK_N + row;
-    const bool n_ok = n < p.N;
     const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
     if (!mbar_wait_bounded(accum_bar, 0, abort_flag, 4000000000ull)) fail(OGB_ERR_WAIT_MMA);
-    // Make the decision uniform over the 128 epilogue threads: they meet at named barriers below.
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // uniform decision over the 128 epilogue threads
     const bool have = (*abort_flag == 0);
     tc_fence_after();
-
-    const float bias0 = (p.bias && n_ok) ? bf2f(p.bias[n]) : 0.f;
-    const float bias1 = (DUAL && p.bias && n_ok) ? bf2f(p.bias[p.dual_row_offset + n]) : 0.f;
-    auto emit = [&](int m, float g, float u) {
-      float v = g + bias0;
-      if (DUAL) v = silu(v) * (u + bias1);
-      if (p.residual) v += bf2f(p.residual[size_t(m) * p.ldr + n]);
-      if (p.out_fp32) reinterpret_cast<float*>(p.C)[size_t(m) * p.ldc + n] = v;
-      else reinterpret_cast<__nv_bfloat16*>(p.C)[size_t(m) * p.ldc + n] = f2bf(v);
-    };
-
     if (have) {
-      const size_t plane = size_t(p.M) * p.N;  // one fp32 plane of the split-K workspace
-      float* ws = p.workspace + (size_t(split) * (DUAL ? 2 : 1)) * plane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BT; c0 += 16) {
-        uint32_t r0[16], r1[16];
+        uint32_t r0[16];
         tmem_ld16(taddr + c0, r0);
-        if (DUAL) tmem_ld16(taddr + BT + c0, r1);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m_tile * BT + c0 + j;
-          if (m < p.M && n_ok) {
-            const float g = __uint_as_float(r0[j]);
-            const float u = DUAL ? __uint_as_float(r1[j]) : 0.f;
-            if (p.splits == 1) emit(m, g, u);
-            else {
-              ws[size_t(m) * p.N + n] = g;
-              if (DUAL) ws[plane + size_t(m) * p.N + n] = u;
-            }
-          }
-        }
-      }
-      if (p.splits > 1) {
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int tile_id = m_tile * gridDim.x + n_tile;
-        if (threadIdx.x == 64) {
-          const int prev = atomicAdd(&p.counters[tile_id], 1);
-          *last_flag = (prev == p.splits - 1);
-          if (prev == p.splits - 1) p.counters[tile_id] = 0;  // self-cleaning for the next launch
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          __threadfence();
-          const int m_end = min(p.M, (m_tile + 1) * BT);
-          if (n_ok) {
-            for (int m = m_tile * BT; m < m_end; ++m) {
-              float g = 0.f, u = 0.f;
-              for (int s = 0; s < p.splits; ++s) {
-                const float* w = p.workspace + (size_t(s) * (DUAL ? 2 : 1)) * plane;
-                g += __ldcg(&w[size_t(m) * p.N + n]);
-                if (DUAL) u += __ldcg(&w[plane + size_t(m) * p.N + n]);
-              }
-              emit(m, g, u);
-            }
-          }
-        }
+        for (int j = 0; j < 16; ++j) part[(c0 + j) * GEMM_BLOCK_N + row] = __uint_as_float(r0[j]);
       }
     }
+    if (p.pdl) pdl_wait();  // residual reads and every store come after the previous kernel has finished
+  }
+  // The parked tiles are complete and visible (cluster-wide when split) after this barrier.  Every
+  // thread of every CTA of the cluster meets here, also after an abort.
+  __syncwarp();
+  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
+
+  if (epi && *abort_flag == 0) {
+    const int my_rank = p.splits > 1 ? int(cluster_ctarank()) : 0;
+    const int per = (BT + p.splits - 1) / p.splits;  // token columns finished by this CTA
+    const int c_begin = min(BT, my_rank * per), c_end = min(BT, c_begin + per);
+    const int OCT = p.act_pair ? 8 : 16;             // 8-wide output segments per token column
+    const int items = (c_end - c_begin) * OCT;
+    const int n_out = p.act_pair ? p.N / 2 : p.N;    // output columns of the whole problem
+    const int col0 = n_tile * (p.act_pair ? 64 : 128);
+    const uint32_t part_addr = smem_u32(part);
+    const bool comm_on = p.comm.buf[0] != nullptr;
+
+    auto reduce8 = [&](int mc, int n_local, float (&v)[8]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      for (int s = 0; s < p.splits; ++s) {
+        float4 a, b;
+        if (p.splits > 1) {
+          const uint32_t ra = dsmem_addr(part_addr + uint32_t(mc * GEMM_BLOCK_N + n_local) * 4, uint32_t(s));
+          a = ld_dsmem_f32x4(ra);
+          b = ld_dsmem_f32x4(ra + 16);
+        } else {
+          a = *reinterpret_cast<const float4*>(part + mc * GEMM_BLOCK_N + n_local);
+          b = *reinterpret_cast<const float4*>(part + mc * GEMM_BLOCK_N + n_local + 4);
+        }
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
+    };
+    auto add_bias8 = [&](int n_glob, float (&v)[8]) {
+      if (!p.bias) return;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (n_glob + j < p.N) v[j] += bf2f(p.bias[n_glob + j]);
+    };
+    auto store8 = [&](int m, int col, float (&v)[8]) {  // residual add + store of one 8-wide segment
+      if (p.residual) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (col + j < n_out) v[j] += bf2f(p.residual[size_t(m) * p.ldr + col + j]);
+      }
+      if (p.out_fp32) {
+        float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
+        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = v[j];
+        }
+      } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;
+        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = f2bf(v[j]);
+        }
+      }
+    };
+
+    uint32_t use = 0;
+    int slot = 0;
+    if (comm_on) {
+      slot = (m_tile * gridDim.x + n_tile) * gridDim.z + my_rank;
+      if (et == 0) *use_slot = p.comm.uses[slot];
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      use = *use_slot;
+    }
+    const size_t plane = size_t(p.comm.plane_elems);
+    const size_t par_off = size_t(use & 1) * p.comm.world * plane;
+
+    for (int item = et; item < items; item += 128) {
+      const int mc = c_begin + item / OCT, oc = item % OCT;
+      const int m = m_tile * BT + mc;
+      if (m >= p.M) continue;
+      float v[8];
+      if (p.act_pair) {
+        float u[8];
+        reduce8(mc, oc * 8, v);
+        reduce8(mc, 64 + oc * 8, u);
+        add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
+        add_bias8(n_tile * GEMM_BLOCK_N + 64 + oc * 8, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = silu(v[j]) * u[j];
+      } else {
+        reduce8(mc, oc * 8, v);
+        add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
+      }
+      const int col = col0 + oc * 8;
+      if (!comm_on) {
+        store8(m, col, v);
+      } else if (col < n_out) {
+        // push this rank's partial (bf16) into every rank's receive buffer: plain peer stores
+        const uint4 pk = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+        const size_t off = par_off + size_t(p.comm.rank) * plane + size_t(m) * n_out + col;
+        for (int r = 0; r < p.comm.world; ++r) *reinterpret_cast<uint4*>(p.comm.buf[r] + off) = pk;
+      }
+    }
+
+    if (comm_on) {
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        for (int r = 0; r < p.comm.world; ++r) red_add_release_sys(p.comm.flag[r] + slot, 1u);
+        const uint32_t target = uint32_t(p.comm.world) * (use + 1);
+        const uint32_t* mine = p.comm.flag[p.comm.rank] + slot;
+        const uint64_t t0 = global_timer_ns();
+        uint32_t spins = 0;
+        while (int32_t(ld_acquire_sys(mine) - target) < 0) {
+          if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 5000000000ull) { fail(OGB_ERR_WAIT_PEER); break; }
+        }
+        p.comm.uses[slot] = use + 1;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int item = et; item < items; item += 128) {
+        const int mc = c_begin + item / OCT, oc = item % OCT;
+        const int m = m_tile * BT + mc;
+        const int col = col0 + oc * 8;
+        if (m >= p.M || col >= n_out) continue;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const __nv_bfloat16* base = p.comm.buf[p.comm.rank] + par_off + size_t(m) * n_out + col;
+        for (int r = 0; r < p.comm.world; ++r) {
+          const uint4 q = ld_cg_u4(base + size_t(r) * plane);
+          const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+          v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+        }
+        store8(m, col, v);
+      }
+    }
+  }
+  if (p.splits > 1) {
+    __syncwarp();
+    cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
   }
 
   tc_fence_before();
@@ -277,86 +438,136 @@ static bool MakeMap(CUtensorMap* out, const void* ptr, int rows, int cols, int l
   return true;
 }
 
-template <int BT, bool DUAL>
+template <int BT>
 static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  using Cfg = GemmCfg<BT, DUAL>;
+  using Cfg = GemmCfg<BT>;
   static bool configured = false;
-  auto kern = gemm_tcgen05_kernel<BT, DUAL>;
+  auto kern = gemm_tcgen05_kernel<BT>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tw, ta, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (p.splits > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = unsigned(p.splits);
+    ++na;
+  }
+  if (p.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = unsigned(na);
+  return cudaLaunchKernelEx(&cfg, kern, tw, ta, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace ogb
 
 using namespace ogb;
 
+// Per-device registration of the symmetric buffers used by the fused all-reduce.
+static CommParams g_comm[16] = {};
+
 OGB_API int ogb_gemm_token_tile(int M, int dual) {
+  (void)dual;
   if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
-  if (M <= 128 || dual) return 128;
+  if (M <= 128) return 128;
   return 256;
 }
 
-// Number of split-K partitions the launcher picks for a problem (workspace sizing helper).
+// Number of split-K partitions (cluster size along z: 1, 2, 4 or 8; other sizes schedule poorly onto
+// the GPCs): the largest that still fits every CTA of the launch on the GPU at once (two resident
+// CTAs per SM for decode-sized tiles) while leaving each split at least 16 k-blocks to stream.
 OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
   const int bt = ogb_gemm_token_tile(M, dual);
   const int tiles = ((N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N) * ((M + bt - 1) / bt);
   const int total_kb = (K + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
-  if (tiles >= sm_count || total_kb < 8) return 1;
-  int splits = (sm_count + tiles / 2) / tiles;          // round to the nearest whole wave
-  splits = splits < 1 ? 1 : splits;
-  const int max_by_k = total_kb / 4 > 0 ? total_kb / 4 : 1;  // keep >= 4 k-blocks per split
-  if (splits > max_by_k) splits = max_by_k;
-  if (splits > 16) splits = 16;
-  return splits;
+  const int slots = (bt <= 64 ? 2 : 1) * sm_count;
+  int best = 1;
+  for (int s = 2; s <= 8; s *= 2) {
+    if (s > bt || total_kb / s < 16 || tiles * s > slots) break;
+    best = s;
+  }
+  return best;
 }
 
+// Registers this rank's view of the symmetric buffers (peer-mapped pointers) for a device.
+// buf[r] / flag[r]: rank r's receive buffer / arrival counters as mapped into this process;
+// uses: a local zero-initialised array of max_slots counters.  world = 0 unregisters.
+OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* uses, long long plane_elems,
+                              int max_slots) {
+  if (device < 0 || device >= 16 || world < 0 || world > COMM_MAX_WORLD) return -1;
+  CommParams c = {};
+  c.world = world; c.rank = rank; c.plane_elems = plane_elems; c.max_slots = max_slots;
+  for (int r = 0; r < world; ++r) {
+    c.buf[r] = static_cast<__nv_bfloat16*>(buf[r]);
+    c.flag[r] = static_cast<uint32_t*>(flag[r]);
+  }
+  c.uses = static_cast<uint32_t*>(uses);
+  g_comm[device] = c;
+  return 0;
+}
+
+// flags bit 0: fp32 output; bit 1: paired silu(gate)*up epilogue (N = 2 * output columns, rows
+// interleaved in blocks of 64); bit 2: fused all-reduce over the registered symmetric buffers.
 OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
-                          const void* bias, const void* residual, int ldr, int out_fp32, int dual, int dual_row_offset,
-                          int splits, void* workspace, long long workspace_bytes, int* counters, int num_counters,
-                          int* status, int sm_count, void* stream_) {
+                          const void* bias, const void* residual, int ldr, int flags, int splits, int device, int* status,
+                          int sm_count, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (lda % 8) || (ldw % 8)) return -1;  // 16-byte global strides for TMA
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -1;
-  const int bt = ogb_gemm_token_tile(M, dual);
+  const int out_fp32 = flags & 1, act_pair = (flags >> 1) & 1, fused_ar = (flags >> 2) & 1;
+  if (act_pair && (N % 128)) return -1;
+  static const int pdl_enabled = [] { const char* e = getenv("OGB_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
+  const int bt = ogb_gemm_token_tile(M, 0);
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, m_tiles = (M + bt - 1) / bt;
   const int total_kb = (K + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
-  if (splits <= 0) splits = ogb_gemm_auto_splits(M, N, K, dual, sm_count);
+  if (splits <= 0) splits = ogb_gemm_auto_splits(M, N, K, 0, sm_count);
+  if (splits > 8) splits = 8;          // portable cluster size
+  if (splits > bt) splits = bt;        // every cluster rank finishes at least one token column
   if (splits > total_kb) splits = total_kb;
-  // shrink until the workspace and the counters fit
-  while (splits > 1 && (size_t(splits) * (dual ? 2 : 1) * size_t(M) * N * 4 > size_t(workspace_bytes) || n_tiles * m_tiles > num_counters || !workspace || !counters))
-    --splits;
   int kb_per = (total_kb + splits - 1) / splits;
-  splits = (total_kb + kb_per - 1) / kb_per;  // no empty split
+  while (splits > 1 && kb_per * (splits - 1) >= total_kb) { --splits; kb_per = (total_kb + splits - 1) / splits; }  // no empty split
 
-  const int w_rows = dual ? dual_row_offset + N : N;
   CUtensorMap tw, ta;
-  if (!MakeMap(&tw, W, w_rows, K, ldw, GEMM_BLOCK_N)) return -2;
+  if (!MakeMap(&tw, W, N, K, ldw, GEMM_BLOCK_N)) return -2;
   if (!MakeMap(&ta, A, M, K, lda, bt)) return -2;
 
-  GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.dual_row_offset = dual_row_offset;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
   p.splits = splits; p.kb_per_split = kb_per; p.total_kb = total_kb;
-  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.act_pair = act_pair;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
-  p.workspace = static_cast<float*>(workspace); p.counters = counters; p.status = status;
-  dim3 grid(n_tiles, m_tiles, splits);
-#define OGB_GEMM_CASE(BT_)                                                         \
-  case BT_: return dual ? Launch<BT_, true>(tw, ta, p, grid, stream) : Launch<BT_, false>(tw, ta, p, grid, stream);
-  switch (bt) {
-    OGB_GEMM_CASE(16)
-    OGB_GEMM_CASE(32)
-    OGB_GEMM_CASE(64)
-    OGB_GEMM_CASE(128)
-    case 256: return Launch<256, false>(tw, ta, p, grid, stream);
+  p.status = status;
+  p.pdl = pdl_enabled;
+  if (fused_ar) {
+    if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
+    const CommParams& c = g_comm[device];
+    const long long n_out = act_pair ? N / 2 : N;
+    if (n_out % 8 || (long long)M * n_out > c.plane_elems || n_tiles * m_tiles * splits > c.max_slots) return -2;
+    p.comm = c;
   }
-#undef OGB_GEMM_CASE
+  dim3 grid(n_tiles, m_tiles, splits);
+  switch (bt) {
+    case 16: return Launch<16>(tw, ta, p, grid, stream);
+    case 32: return Launch<32>(tw, ta, p, grid, stream);
+    case 64: return Launch<64>(tw, ta, p, grid, stream);
+    case 128: return Launch<128>(tw, ta, p, grid, stream);
+    case 256: return Launch<256>(tw, ta, p, grid, stream);
+  }
   return -5;
 }

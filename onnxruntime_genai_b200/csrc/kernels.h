@@ -18,9 +18,10 @@ int ogb_sm_count(int device);
 // ---- gemm_tcgen05.cu
 int ogb_gemm_token_tile(int M, int dual);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
+int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* uses, long long plane_elems, int max_slots);
+// flags: bit 0 fp32 output, bit 1 paired silu(gate)*up epilogue, bit 2 fused tensor-parallel all-reduce
 int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
-                  const void* residual, int ldr, int out_fp32, int dual, int dual_row_offset, int splits, void* workspace,
-                  long long workspace_bytes, int* counters, int num_counters, int* status, int sm_count, void* stream);
+                  const void* residual, int ldr, int flags, int splits, int device, int* status, int sm_count, void* stream);
 
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);

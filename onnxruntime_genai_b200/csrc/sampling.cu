@@ -47,33 +47,61 @@ struct RowCtx {
 };
 
 struct SelectShared {
-  unsigned long long hist[256];
-  unsigned long long want, above;
+  unsigned long long hist[256];   // combined histogram of the current pass
+  unsigned long long want, above, ties;
   uint32_t prefix, mask;
-  int found;
   unsigned long long warp_tot[32];
   unsigned long long carry;
   int result;
 };
 
-// Radix select over the row.  MASS = false: weights are 1 (count); MASS = true: fixed-point
-// probability mass.  On return sh.prefix is the threshold key T, sh.above the total weight of
-// members with key > T, and sh.want the weight still needed from members with key == T.
+// Radix select over the row, 8 bits per pass.  MASS = false: weights are 1 (count); MASS = true:
+// fixed-point probability mass.  Each warp owns a private 256-bin histogram (`priv`, dynamic shared
+// memory, [warps][256]); lanes that fall into the same bin are combined with match.any first, so
+// the hot bins (most float keys share their top byte) cost one plain add per warp, no atomics.
+// On return sh.prefix is the threshold key T, sh.above the weight of members with key > T,
+// sh.want the weight still needed from members with key == T and sh.ties their total weight.
 template <bool MASS>
-__device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long long want) {
-  const int tid = threadIdx.x;
-  if (tid == 0) { sh.want = want; sh.above = 0; sh.prefix = 0; sh.mask = 0; }
+__device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long long* priv, unsigned long long want) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  unsigned long long* mine = priv + warp * 256;
+  if (tid == 0) { sh.want = want; sh.above = 0; sh.prefix = 0; sh.mask = 0; sh.ties = 0; }
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int b = tid; b < 256; b += blockDim.x) sh.hist[b] = 0;
+    for (int b = tid; b < nwarps * 256; b += blockDim.x) priv[b] = 0;
     __syncthreads();
     const uint32_t prefix = sh.prefix, mask = sh.mask;
-    for (int i = tid; i < c.n; i += blockDim.x) {
-      const float v = c.x[i];
-      const uint32_t key = to_key(v);
-      if ((key & mask) == prefix && c.in_k(i, key)) {
-        const unsigned long long w = MASS ? c.mass(v) : 1ull;
-        if (w) atomicAdd(&sh.hist[(key >> shift) & 255], w);
+    for (int base = 0; base < c.n; base += blockDim.x) {
+      const int i = base + tid;
+      uint32_t bin = 0xFFFFFFFFu;
+      unsigned long long w = 0;
+      if (i < c.n) {
+        const float v = c.x[i];
+        const uint32_t key = to_key(v);
+        if ((key & mask) == prefix && c.in_k(i, key)) {
+          w = MASS ? c.mass(v) : 1ull;
+          if (w) bin = (key >> shift) & 255;
+        }
       }
+      if (!__any_sync(0xffffffffu, bin != 0xFFFFFFFFu)) continue;  // later passes: most warps see no candidate
+      const unsigned grp = __match_any_sync(0xffffffffu, bin);
+      if (bin != 0xFFFFFFFFu) {
+        unsigned long long sum;
+        if (MASS) {
+          const unsigned lo = __reduce_add_sync(grp, unsigned(w & 0xFFFFFu));
+          const unsigned hi = __reduce_add_sync(grp, unsigned(w >> 20));
+          sum = ((unsigned long long)hi << 20) + lo;
+        } else {
+          sum = __popc(grp);
+        }
+        if (lane == __ffs(grp) - 1) mine[bin] += sum;
+      }
+      __syncwarp();
+    }
+    __syncthreads();
+    for (int b = tid; b < 256; b += blockDim.x) {
+      unsigned long long t = 0;
+      for (int w = 0; w < nwarps; ++w) t += priv[w * 256 + b];
+      sh.hist[b] = t;
     }
     __syncthreads();
     if (tid < 32) {
@@ -94,7 +122,6 @@ __device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long lo
       if (found_mask == 0) {
         // fewer members than requested: take everything (threshold = lowest non-empty bin)
         const unsigned nonempty = __ballot_sync(0xffffffffu, local > 0);
-        if (tid == 0) sh.found = 0;
         if (nonempty && tid == __ffs(nonempty) - 1) {
           int bin = 0;
           for (int j = 0; j < 8; ++j) if (sh.hist[tid * 8 + j]) { bin = tid * 8 + j; break; }
@@ -102,9 +129,9 @@ __device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long lo
           for (int j = 7; j >= 0; --j) if (tid * 8 + j > bin) cum += sh.hist[tid * 8 + j];
           sh.above += cum;
           sh.want = sh.hist[bin];
+          sh.ties = sh.hist[bin];
           sh.prefix |= uint32_t(bin) << shift;
           sh.mask |= 255u << shift;
-          sh.found = 1;
         }
       } else if (here) {
         unsigned long long cum = higher;
@@ -116,9 +143,9 @@ __device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long lo
         }
         sh.above += cum;
         sh.want = w - cum;
+        sh.ties = sh.hist[bin];
         sh.prefix |= uint32_t(bin) << shift;
         sh.mask |= 255u << shift;
-        sh.found = 1;
       }
     }
     __syncthreads();
@@ -187,73 +214,152 @@ struct SampleParams {
   int32_t* out;
 };
 
+constexpr int SMALL_K = 1024;  // top-k sets up to this size are finished on a sorted list in shared memory
+
+// 53-bit uniform in [0, 1) from the stateless generator keyed by (seed, position).
+__device__ __forceinline__ double draw_uniform(const SampleParams& p, int row) {
+  uint32_t rnd[4];
+  Philox::gen(p.seeds ? p.seeds[row] : 0ull, (unsigned long long)(p.positions ? p.positions[row] : 0), 0x5a17u, rnd);
+  return double((((unsigned long long)rnd[0] << 32) | rnd[1]) >> 11) * (1.0 / 9007199254740992.0);
+}
+
 __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
+  extern __shared__ unsigned long long priv[];  // [warps][256] private histograms; reused as the candidate list
   __shared__ SelectShared sh;
   __shared__ float red_v[32];
   __shared__ int red_i[32];
+  __shared__ int cand_n;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* x = p.logits + size_t(row) * p.row_stride;
   const int n = p.vocab;
+  const int k = p.top_k ? p.top_k[row] : 1;
+  const float top_p = p.top_p ? p.top_p[row] : 0.f;
+  const float temp = p.temperature ? p.temperature[row] : 1.f;
+  const bool greedy = (k == 1 || temp <= 0.f);
+  const bool small = !greedy && k > 1 && k < n && k <= SMALL_K;
 
-  // ---- pass 1: maximum and its lowest index
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = tid; i < n; i += blockDim.x) {
-    const float v = x[i];
-    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-  }
-  if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
-  __syncthreads();
-  if (warp == 0) {
-    bv = lane < (blockDim.x >> 5) ? red_v[lane] : -INFINITY;
-    bi = lane < (blockDim.x >> 5) ? red_i[lane] : 0x7fffffff;
+  float mx = 0.f;
+  int arg = 0;
+  if (!small) {
+    // ---- maximum and its lowest index (greedy rows stop here; the full-vocabulary path needs the max)
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < n; i += blockDim.x) {
+      const float v = x[i];
+      if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) { red_v[0] = bv; red_i[0] = bi; }
-  }
-  __syncthreads();
-  const float mx = red_v[0];
-  const int arg = red_i[0] == 0x7fffffff ? 0 : red_i[0];
-
-  const int k = p.top_k ? p.top_k[row] : 1;
-  const float top_p = p.top_p ? p.top_p[row] : 0.f;
-  const float temp = p.temperature ? p.temperature[row] : 1.f;
-  if (k == 1 || temp <= 0.f || !(mx > -INFINITY)) {
-    if (tid == 0) p.out[row] = arg;
-    return;
+    if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      bv = lane < (blockDim.x >> 5) ? red_v[lane] : -INFINITY;
+      bi = lane < (blockDim.x >> 5) ? red_i[lane] : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (lane == 0) { red_v[0] = bv; red_i[0] = bi; }
+    }
+    __syncthreads();
+    mx = red_v[0];
+    arg = red_i[0] == 0x7fffffff ? 0 : red_i[0];
+    if (greedy || !(mx > -INFINITY)) {
+      if (tid == 0) p.out[row] = arg;
+      return;
+    }
   }
 
   RowCtx c;
   c.x = x; c.n = n; c.mx = mx; c.inv_t2 = SAMP_LOG2E / temp;
   c.use_k = false; c.tk = 0; c.tk_idx = n;
 
-  // ---- top-k by count
-  if (k > 1 && k < n) {
-    radix_select<false>(c, sh, (unsigned long long)k);
+  if (small) {
+    // ---- top-k by count, then everything else on the k candidates
+    radix_select<false>(c, sh, priv, (unsigned long long)k);
     const uint32_t T = sh.prefix;
-    const unsigned long long need = sh.want;
+    const unsigned long long need = sh.want, ties = sh.ties;
     __syncthreads();
-    // ties at the threshold: keep the lowest `need` indices
-    int cut = tie_index_cut<false>(c, sh, T, need, false);
+    int cut = n;
+    if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);  // ties straddle the threshold: keep the lowest indices
+    __syncthreads();
+    float* cv = reinterpret_cast<float*>(priv);            // candidate values   [SMALL_K]
+    int* ci = reinterpret_cast<int*>(cv + SMALL_K);        // candidate indices  [SMALL_K]
+    float* sv = reinterpret_cast<float*>(ci + SMALL_K);    // sorted values
+    int* si = reinterpret_cast<int*>(sv + SMALL_K);        // sorted indices
+    if (tid == 0) cand_n = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += blockDim.x) {
+      const float v = x[i];
+      const uint32_t key = to_key(v);
+      if (key > T || (key == T && i <= cut)) {
+        const int slot = atomicAdd(&cand_n, 1);
+        if (slot < SMALL_K) { cv[slot] = v; ci[slot] = i; }
+      }
+    }
+    __syncthreads();
+    const int m = min(cand_n, SMALL_K);
+    // rank sort: descending value, ascending index (deterministic whatever order the slots were filled in)
+    if (tid < m) {
+      const float v = cv[tid];
+      const int idx = ci[tid];
+      int rank = 0;
+      for (int j = 0; j < m; ++j) {
+        const float vj = cv[j];
+        const int ij = ci[j];
+        rank += (vj > v || (vj == v && ij < idx)) ? 1 : 0;
+      }
+      sv[rank] = v;
+      si[rank] = idx;
+    }
+    __syncthreads();
+    const float top = sv[0];
+    unsigned long long w = 0;
+    if (tid < m) {
+      w = (unsigned long long)(exp2f((sv[tid] - top) * c.inv_t2) * MASS_SCALE);
+      if (w == 0) w = 1;
+    }
+    unsigned long long total;
+    const unsigned long long incl = block_scan_incl(w, sh, total);
+    __syncthreads();
+    // top-p: shortest prefix whose mass reaches p * total ("include while the mass before it is < p")
+    unsigned long long kept = total;
+    if (top_p > 0.f && top_p < 1.f) {
+      const unsigned long long want = (unsigned long long)(double(total) * double(top_p));
+      if (tid == 0) sh.carry = total;
+      __syncthreads();
+      if (tid < m && incl >= want && incl - w < want) sh.carry = incl;  // exactly one thread
+      __syncthreads();
+      kept = sh.carry;
+    }
+    unsigned long long target = (unsigned long long)(draw_uniform(p, row) * double(kept));
+    if (target >= kept) target = kept - 1;
+    if (tid < m && incl > target && incl - w <= target) p.out[row] = si[tid];
+    return;
+  }
+
+  // ---- full-vocabulary path (no top-k, or k > SMALL_K)
+  if (k > 1 && k < n) {
+    radix_select<false>(c, sh, priv, (unsigned long long)k);
+    const uint32_t T = sh.prefix;
+    const unsigned long long need = sh.want, ties = sh.ties;
+    __syncthreads();
+    int cut = n;
+    if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);
     c.use_k = true; c.tk = T; c.tk_idx = cut;
     __syncthreads();
   }
 
-  // ---- final membership threshold (tp, tp_idx): starts as the top-k set, narrowed by top-p
+  // final membership threshold (tp, tp_idx): starts as the top-k set, narrowed by top-p
   uint32_t tp = c.use_k ? c.tk : 0u;
   int tp_idx = c.use_k ? c.tk_idx : n;
   if (top_p > 0.f && top_p < 1.f) {
-    // total mass of the top-k set
     unsigned long long z = 0;
     for (int i = tid; i < n; i += blockDim.x) {
       const float v = x[i];
@@ -264,16 +370,17 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
     __syncthreads();
     unsigned long long want = (unsigned long long)(double(total) * double(top_p));
     if (want < 1) want = 1;
-    radix_select<true>(c, sh, want);
+    radix_select<true>(c, sh, priv, want);
     const uint32_t T = sh.prefix;
-    const unsigned long long need = sh.want;
+    const unsigned long long need = sh.want, ties = sh.ties;
     __syncthreads();
-    const int cut = tie_index_cut<true>(c, sh, T, need, true);
+    int cut = n;
+    if (need < ties) cut = tie_index_cut<true>(c, sh, T, need, true);
     __syncthreads();
     tp = T; tp_idx = cut;
   }
 
-  // ---- draw: prefix scan over kept masses in index order
+  // draw: prefix scan over kept masses in index order
   auto kept_mass = [&](int i) -> unsigned long long {
     const float v = x[i];
     const uint32_t key = to_key(v);
@@ -286,11 +393,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
   unsigned long long zt;
   block_scan_incl(z, sh, zt);
   __syncthreads();
-  uint32_t rnd[4];
-  Philox::gen(p.seeds ? p.seeds[row] : 0ull, (unsigned long long)(p.positions ? p.positions[row] : 0), 0x5a17u, rnd);
-  // 53-bit uniform in [0,1) -> target in [0, zt)
-  const double u = double((((unsigned long long)rnd[0] << 32) | rnd[1]) >> 11) * (1.0 / 9007199254740992.0);
-  unsigned long long target = (unsigned long long)(u * double(zt));
+  unsigned long long target = (unsigned long long)(draw_uniform(p, row) * double(zt));
   if (target >= zt) target = zt - 1;
 
   if (tid == 0) { sh.carry = 0; sh.result = arg; }
@@ -324,6 +427,7 @@ struct TopKParams {
 };
 
 __global__ void __launch_bounds__(SAMP_THREADS) topk_kernel(TopKParams p) {
+  extern __shared__ unsigned long long priv[];
   __shared__ SelectShared sh;
   __shared__ float cand_v[TOPK_MAX];
   __shared__ int cand_i[TOPK_MAX];
@@ -360,11 +464,11 @@ __global__ void __launch_bounds__(SAMP_THREADS) topk_kernel(TopKParams p) {
   uint32_t T = 0;
   int cut = n;
   if (k < n) {
-    radix_select<false>(c, sh, (unsigned long long)k);
+    radix_select<false>(c, sh, priv, (unsigned long long)k);
     T = sh.prefix;
-    const unsigned long long need = sh.want;
+    const unsigned long long need = sh.want, ties = sh.ties;
     __syncthreads();
-    cut = tie_index_cut<false>(c, sh, T, need, false);
+    if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);
     __syncthreads();
   }
   if (tid == 0) cand_n = 0;
@@ -472,7 +576,13 @@ OGB_API int ogb_sample(const float* logits, long long row_stride, int rows, int 
                        void* stream) {
   if (rows <= 0) return 0;
   SampleParams p{logits, row_stride, vocab, rows, top_k, top_p, temperature, seeds, positions, out};
-  sample_kernel<<<rows, SAMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  constexpr int kDyn = (SAMP_THREADS / 32) * 256 * 8;  // 64 KiB of per-warp histograms
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
+    configured = true;
+  }
+  sample_kernel<<<rows, SAMP_THREADS, kDyn, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -487,7 +597,13 @@ OGB_API int ogb_topk(const float* x, long long row_stride, int rows, int n, int 
   if (rows <= 0) return 0;
   if (k < 1 || k > TOPK_MAX) return -1;
   TopKParams p{x, row_stride, n, rows, k, mode, add, out_vals, out_idx};
-  topk_kernel<<<rows, SAMP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  constexpr int kDyn = (SAMP_THREADS / 32) * 256 * 8;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
+    configured = true;
+  }
+  topk_kernel<<<rows, SAMP_THREADS, kDyn, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -167,11 +167,11 @@ def dequantize_int4_block32(qweight, scales, zero_points, N: int, K: int, block:
 
 # ---------------------------------------------------------------------------------------------- export
 class _Writer:
-    def __init__(self, out_dir: str, precision: str, synthetic: bool, seed: int, std: float):
+    def __init__(self, out_dir: str, precision: str, synthetic: bool, seed: int, std: float, filename: str = "model.onnx"):
         self.model = op.Model()
         self.precision = precision
         self.io = "fp32" if precision == "fp32" else ("bf16" if precision in ("bf16", "int4") else "fp16")
-        self.ext = None if synthetic else op.ExternalDataWriter(os.path.join(out_dir, "model.onnx.data"))
+        self.ext = None if synthetic else op.ExternalDataWriter(os.path.join(out_dir, filename + ".data"))
         self.synthetic = synthetic
         self.seed, self.std = seed, std
 
@@ -216,7 +216,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
         arch.context_length = context_length
     if synthetic_weights and precision == "int4":
         raise ValueError("synthetic_weights cannot be combined with int4")
-    W = _Writer(out_dir, precision, synthetic_weights, seed, std)
+    W = _Writer(out_dir, precision, synthetic_weights, seed, std, filename)
     shapes = weight_shapes(arch)
 
     def get(name: str) -> torch.Tensor:

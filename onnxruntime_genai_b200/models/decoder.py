@@ -83,6 +83,9 @@ class NoTP:
     def gather_logits(self, x):
         return x
 
+    def fused_ok(self, x):
+        return False
+
 
 @dataclass
 class LayerWeights:
@@ -111,6 +114,7 @@ class LayerWeights:
     exp_down_b: Optional[torch.Tensor] = None
     lora: Dict[str, dict] = field(default_factory=dict)
     window: int = 0
+    gate_up_interleaved: bool = False  # gate/up rows stored in blocks of 64 (layout of the fused SiLU*mul GEMM)
 
 
 class DecoderModel:
@@ -147,10 +151,22 @@ class DecoderModel:
             return moe_forward(self, lw, x)
         lora = self._lora(lw, "gate_up_proj")
         if lora is None:
-            act = ops.gate_up_act(x, lw.gate_up_w, lw.gate_up_b, a.activation)
+            act = ops.gate_up_act(x, lw.gate_up_w, lw.gate_up_b, a.activation, interleaved=lw.gate_up_interleaved)
         else:
-            act = ops.act_mul(self._linear(x, lw.gate_up_w, lw.gate_up_b, lora=lora), a.activation)
-        return self._linear(act, lw.down_w, lw.down_b if self.tp.rank == 0 else None, lora=self._lora(lw, "down_proj"))
+            y = ops.linear(x, lw.gate_up_w, lw.gate_up_b)
+            if lw.gate_up_interleaved:
+                inter = y.shape[1] // 2
+                y = y.view(-1, inter // 64, 2, 64).transpose(1, 2).reshape(-1, 2 * inter).contiguous()
+            from .lora import apply_lora
+            act = ops.act_mul(apply_lora(y, x, lora), a.activation)
+        return self._row_parallel(act, lw.down_w, lw.down_b, self._lora(lw, "down_proj"))
+
+    def _row_parallel(self, x, w, b, lora):
+        """Row-parallel projection: partial products summed over the tensor-parallel ranks."""
+        bias = b if self.tp.rank == 0 else None
+        if self.tp.size > 1 and lora is None and self.tp.fused_ok(x):
+            return ops.linear(x, w, bias, all_reduce=True)   # GEMM + all-reduce in one kernel over NVLink
+        return self.tp.reduce(self._linear(x, w, bias, lora=lora))
 
     def _lora(self, lw: LayerWeights, proj: str):
         if self.active_adapter is None:
@@ -179,8 +195,7 @@ class DecoderModel:
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
                                       max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
-            h = self._linear(att, lw.o_w, lw.o_b if self.tp.rank == 0 else None, lora=self._lora(lw, "o_proj"))
-            h = self.tp.reduce(h)
+            h = self._row_parallel(att, lw.o_w, lw.o_b, self._lora(lw, "o_proj"))
             if lw.post_attn_norm_w is not None:
                 h, _ = ops.norm(h, lw.post_attn_norm_w, a.norm_eps)
             if a.residual_multiplier != 1.0:
@@ -188,7 +203,6 @@ class DecoderModel:
             x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
             # ---- MLP
             h = self._mlp(lw, x)
-            h = self.tp.reduce(h)
             if lw.post_ffn_norm_w is not None:
                 h, _ = ops.norm(h, lw.post_ffn_norm_w, a.norm_eps)
             if a.residual_multiplier != 1.0:

@@ -292,6 +292,12 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                 gw = _linear_weight(g, linear_node(f"{n}/mlp/", "gate_proj"), dtype, device, rows=g_rows if tpn > 1 else None)
                 uw = _linear_weight(g, linear_node(f"{n}/mlp/", "up_proj"), dtype, device, rows=g_rows if tpn > 1 else None)
                 lw.gate_up_w = torch.cat([gw, uw], 0).contiguous()
+            if torch.device(device).type == "cuda" and arch.activation == "silu" and (lw.gate_up_w.shape[0] // 2) % 64 == 0:
+                from ..ops import interleave_gate_up
+                lw.gate_up_w = interleave_gate_up(lw.gate_up_w)
+                if lw.gate_up_b is not None:
+                    lw.gate_up_b = interleave_gate_up(lw.gate_up_b)
+                lw.gate_up_interleaved = True
             dn = linear_node(f"{n}/mlp/", "down_proj")
             lw.down_w = _linear_weight(g, dn, dtype, device, cols=g_rows if tpn > 1 else None)
             dadd = g.by_name.get(f"{n}/mlp/down_proj/Add")

@@ -27,8 +27,8 @@ def _stream():
 
 
 class _Workspace:
-    """Per-device scratch shared by the kernels: split-K partial tiles + tile counters for the GEMM,
-    split-KV partials for attention.  Allocated once (outside graph capture) and reused."""
+    """Per-device state shared by the kernels: the status word and the split-KV scratch of attention
+    (the GEMM's split-K reduces on chip and needs none).  Allocated once (outside graph capture)."""
 
     def __init__(self, device: torch.device):
         self.device = device
@@ -37,8 +37,6 @@ class _Workspace:
         _lib.init_device(idx)
         self.status = _lib.lib().ogb_status_device_ptr(idx)
         self.sm_count = _lib.lib().ogb_sm_count(idx)
-        self.gemm_ws = torch.empty(48 << 20, dtype=torch.uint8, device=device)
-        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
         self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
 
     def attn_scratch(self, nbytes: int) -> torch.Tensor:
@@ -98,42 +96,55 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) ->
 
 
 # ------------------------------------------------------------------------------------------ GEMM
-def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0):
-    """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous)."""
-    if not x.is_cuda:
-        return ref.linear(x, w, bias, residual, out_fp32)
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    assert x.stride(-1) == 1 and w.stride(-1) == 1
-    T, K = x.shape
-    N = w.shape[0]
-    if out is None:
-        out = torch.empty(T, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE = 1, 2, 4
+
+
+def _gemm(x, w, out, bias, residual, flags, splits):
     ws = workspace(x.device)
-    rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, N, K, _ptr(bias),
-                                  _ptr(residual), residual.stride(0) if residual is not None else 0, int(out_fp32), 0, 0,
-                                  int(splits), _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.counters), ws.counters.numel(),
-                                  ws.status, ws.sm_count, _stream())
+    T, K = x.shape
+    rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, w.shape[0], K, _ptr(bias),
+                                  _ptr(residual), residual.stride(0) if residual is not None else 0, int(flags), int(splits),
+                                  ws.index, ws.status, ws.sm_count, _stream())
     _lib.check(rc, "gemm_bf16")
     return out
 
 
-def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0):
-    """act(x @ Wg.T) * (x @ Wu.T) with w = [Wg; Wu] stacked along rows ([2I, K])."""
+def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False):
+    """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous).  With all_reduce the
+    partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory."""
     if not x.is_cuda:
-        return ref.gate_up_act(x, w, bias, act)
-    T, K = x.shape
-    inter = w.shape[0] // 2
-    if act != "silu":
-        y = linear(x, w, bias)
-        return act_mul(y, act)
+        return ref.linear(x, w, bias, residual, out_fp32)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.stride(-1) == 1 and w.stride(-1) == 1
     if out is None:
-        out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
-    ws = workspace(x.device)
-    rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, inter, K, _ptr(bias),
-                                  None, 0, 0, 1, inter, int(splits), _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.counters),
-                                  ws.counters.numel(), ws.status, ws.sm_count, _stream())
-    _lib.check(rc, "gemm_bf16(dual)")
-    return out
+        out = torch.empty(x.shape[0], w.shape[0], dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+    flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0)
+    return _gemm(x, w, out, bias, residual, flags, splits)
+
+
+def interleave_gate_up(w: torch.Tensor, block: int = 64) -> torch.Tensor:
+    """[gate; up] stacked rows ([2I, ...]) -> blocks of 64 gate rows followed by the 64 up rows of the same
+    features, the row order the paired-activation GEMM epilogue expects.  Works for weights and biases."""
+    inter = w.shape[0] // 2
+    assert inter % block == 0
+    g, u = w[:inter].reshape(inter // block, 1, block, *w.shape[1:]), w[inter:].reshape(inter // block, 1, block, *w.shape[1:])
+    return torch.cat([g, u], dim=1).reshape(w.shape).contiguous()
+
+
+def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False):
+    """act(x @ Wg.T) * (x @ Wu.T).  w is [2I, K]: stacked [Wg; Wu], or (interleaved=True) blocks of 64 gate
+    rows + 64 up rows as produced by interleave_gate_up (the layout the fused kernel needs)."""
+    if not x.is_cuda:
+        return ref.gate_up_act(x, w, bias, act, interleaved)
+    inter = w.shape[0] // 2
+    if act != "silu" or not interleaved or inter % 64:
+        y = linear(x, w, bias)
+        if interleaved:
+            y = y.view(-1, inter // 64, 2, 64).transpose(1, 2).reshape(-1, 2 * inter)
+        return act_mul(y.contiguous(), act)
+    if out is None:
+        out = torch.empty(x.shape[0], inter, dtype=torch.bfloat16, device=x.device)
+    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR, splits)
 
 
 def act_mul(x, act="silu"):

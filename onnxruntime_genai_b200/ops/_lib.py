@@ -23,8 +23,8 @@ _SIGS = {
     "ogb_sm_count": (c_int, [c_int]),
     "ogb_gemm_token_tile": (c_int, [c_int, c_int]),
     "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
-    "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int,
-                              _P, c_longlong, _P, c_int, _P, c_int, _P]),
+    "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P]),
+    "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, _P, c_longlong, c_int]),
     "ogb_embedding": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
     "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -46,12 +46,14 @@ def linear(x, w, bias=None, residual=None, out_fp32=False):
     return y if out_fp32 else y.to(x.dtype)
 
 
-def gate_up_act(x, w, bias=None, act="silu"):
-    """w is the stacked [gate; up] weight of shape [2I, K]."""
+def gate_up_act(x, w, bias=None, act="silu", interleaved=False):
+    """w is the stacked [gate; up] weight of shape [2I, K] (or 64-row interleaved blocks)."""
     y = x.float() @ w.float().t()
     if bias is not None:
         y = y + bias.float()
     inter = y.shape[-1] // 2
+    if interleaved:
+        y = y.view(-1, inter // 64, 2, 64).transpose(1, 2).reshape(-1, 2 * inter)
     g, u = y[..., :inter], y[..., inter:]
     a = torch.nn.functional.silu(g) if act == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
     return (a * u).to(x.dtype)

@@ -27,8 +27,13 @@ class TensorParallel:
         self.backend = backend
         self.comm = None
         if backend == "fused":
-            from .symm import SymmetricComm
-            self.comm = SymmetricComm(rank, size, device, group)
+            try:
+                from .symm import SymmetricComm
+                self.comm = SymmetricComm(rank, size, device, group)
+            except Exception as e:  # symmetric memory unavailable: keep running on the NCCL baseline, loudly
+                import warnings
+                warnings.warn(f"fused tensor-parallel kernels disabled, falling back to NCCL: {e}")
+                self.backend = "nccl"
 
     @classmethod
     def from_env(cls, backend: Optional[str] = None) -> Optional["TensorParallel"]:
@@ -51,12 +56,14 @@ class TensorParallel:
             be = "nccl"
         return cls(rank, world, device, None, be)
 
+    def fused_ok(self, x: torch.Tensor) -> bool:
+        """True when the GEMM + all-reduce kernel can take this activation (decode-sized token counts)."""
+        return self.comm is not None and x.is_cuda and x.shape[0] <= self.comm.max_tokens
+
     # row-parallel output: sum of partials over ranks (in place)
     def reduce(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         if self.size == 1:
             return x
-        if self.comm is not None and x.is_cuda:
-            return self.comm.all_reduce(x)
         if x.dtype == torch.bfloat16 and not x.is_cuda:
             y = x.float()
             dist.all_reduce(y, group=self.group)

@@ -1,0 +1,357 @@
+"""Engine contracts with scripted doubles on the host (modelled on the reference's engine_unit_tests and
+test_onnxruntime_genai_engine.py: closed-form model, isolated == simultaneous, staggered admission, EOS /
+max_length, continuation, capacity, transaction rollback, fatal failure, invariants)."""
+import copy
+
+import numpy as np
+import pytest
+
+import onnxruntime_genai_b200 as og
+from onnxruntime_genai_b200.engine.engine import Engine, EngineStepError, ExecutionFailure, FailureKind, Request, StepOutcome
+from onnxruntime_genai_b200.native_loader import native
+
+VOCAB, EOS = 64, 1
+
+
+class ClosedFormExecutor:
+    """next = (first_prompt_token + current_token + current_length) % vocab — no model math at all."""
+
+    def __init__(self):
+        self.calls = []
+        self.script = []  # failures to raise, consumed front to back
+
+    def execute(self, plan, edits=None, masks=None):
+        self.calls.append([(e.request.id, e.num_tokens, e.processed_before, e.is_prefill) for e in plan.entries])
+        if self.script:
+            f = self.script.pop(0)
+            if f is not None:
+                raise f
+        out = []
+        for e in plan.entries:
+            toks = e.request.tokens()
+            cur = int(toks[e.processed_before + e.num_tokens - 1])
+            out.append((int(toks[0]) + cur + e.processed_before + e.num_tokens) % VOCAB)
+        return np.asarray(out, dtype=np.int32)
+
+
+def closed_form(prompt, max_length):
+    seq = list(prompt)
+    out = []
+    while len(seq) < max_length:
+        t = (seq[0] + seq[-1] + len(seq)) % VOCAB
+        if t == EOS:
+            break
+        seq.append(t)
+        out.append(t)
+    return out
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_model
+    arch = ArchConfig(model_type="llama", vocab_size=VOCAB, hidden_size=32, num_layers=1, num_heads=2, num_kv_heads=1, head_dim=16,
+                      intermediate_size=32, context_length=128, bos_token_id=0, eos_token_id=EOS, pad_token_id=0)
+    d = str(tmp_path_factory.mktemp("synthetic_paged"))
+    export_model(arch, d, "fp32", "cpu", paged=True, block_size=4, num_blocks=128, max_batch_size=8, max_scheduled_tokens=32)
+    return og.Model(d)
+
+
+def make_engine(model, **kw):
+    ex = ClosedFormExecutor()
+    return Engine(model, executor=ex, **kw), ex
+
+
+def request(model, prompt, max_length=40, **opts):
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=max_length, **opts)
+    r = Request(p)
+    r.add_tokens(np.asarray(prompt, dtype=np.int32))
+    return r
+
+
+def run_all(engine, reqs, check=True):
+    outs = {id(r): [] for r in reqs}
+    guard = 0
+    while engine.has_pending_requests():
+        guard += 1
+        assert guard < 5000
+        r = engine.step()
+        if check:
+            engine.core.check_invariants()
+        if r is None:
+            continue
+        while r.has_unseen_tokens():
+            outs[id(r)].append(r.get_unseen_token())
+        if r.is_turn_complete():
+            engine.remove_request(r)
+    return [outs[id(r)] for r in reqs]
+
+
+def test_single_request_matches_closed_form(model):
+    engine, _ = make_engine(model)
+    r = request(model, [5, 9, 3])
+    engine.add_request(r)
+    assert run_all(engine, [r]) == [closed_form([5, 9, 3], 40)]
+    assert engine.core.free_blocks == 128
+
+
+def test_isolated_equals_simultaneous_and_staggered(model):
+    prompts = [[5, 9, 3], [7], [2, 2, 2, 2, 2, 2, 2, 2, 2], [11, 60], [33] * 17]
+    want = [closed_form(p, 40) for p in prompts]
+    engine, _ = make_engine(model)
+    reqs = [request(model, p) for p in prompts]
+    for r in reqs:
+        engine.add_request(r)
+    assert run_all(engine, reqs) == want
+    # staggered admission: add a request every few steps
+    engine, _ = make_engine(model)
+    reqs = [request(model, p) for p in prompts]
+    outs = {id(r): [] for r in reqs}
+    pending = list(reqs)
+    steps = 0
+    while pending or engine.has_pending_requests():
+        if pending and steps % 3 == 0:
+            engine.add_request(pending.pop(0))
+        steps += 1
+        r = engine.step()
+        engine.core.check_invariants()
+        if r is None:
+            continue
+        while r.has_unseen_tokens():
+            outs[id(r)].append(r.get_unseen_token())
+        if r.is_turn_complete():
+            engine.remove_request(r)
+    assert [outs[id(r)] for r in reqs] == want
+
+
+def test_eos_is_not_returned_and_max_length_is_respected(model):
+    # first=1, current=62, length 2 -> (1 + 62 + 2) % 64 == 1 == EOS immediately
+    engine, _ = make_engine(model)
+    r = request(model, [1, 62])
+    engine.add_request(r)
+    assert run_all(engine, [r]) == [[]] and r.status == native.RequestStatus.Closed
+    engine, _ = make_engine(model)
+    r = request(model, [5, 9, 3], max_length=6)
+    engine.add_request(r)
+    out = run_all(engine, [r])[0]
+    assert len(out) == 3 and len(r.tokens()) == 6
+
+
+def test_decode_first_schedule_and_token_budget(model):
+    engine, ex = make_engine(model)
+    a, b = request(model, [3] * 40, max_length=60), request(model, [4] * 30, max_length=60)
+    engine.add_request(a)
+    engine.step()   # a prefill, budget 32
+    assert ex.calls[0] == [(a._native.id, 32, 0, True)]
+    engine.add_request(b)
+    engine.step()
+    # a still prefilling (8 left) comes first as a resident, then b gets the rest of the 32-token budget
+    assert ex.calls[1] == [(a._native.id, 8, 32, True), (b._native.id, 24, 0, True)]
+    engine.step()
+    # a is now decoding: decodes are planned before prefills
+    assert ex.calls[2][0] == (a._native.id, 1, 40, False) and ex.calls[2][1] == (b._native.id, 6, 24, True)
+
+
+def test_chunk_size_caps_prefill_per_request(model):
+    engine, ex = make_engine(model)
+    r = request(model, [3] * 20, chunk_size=8)
+    engine.add_request(r)
+    engine.step(); engine.step(); engine.step()
+    assert [c[0][1] for c in ex.calls[:3]] == [8, 8, 4]
+
+
+def test_capacity_deferral_and_handle_release(model):
+    engine, ex = make_engine(model, num_blocks=6)      # 24 slots
+    a, b = request(model, [3] * 14, max_length=20), request(model, [4] * 14, max_length=20)
+    engine.add_request(a)
+    engine.add_request(b)
+    engine.step()
+    assert [c[0] for c in ex.calls[0]] == [a._native.id], "b does not fit while a holds 4 of 6 blocks"
+    assert engine.last_outcome == StepOutcome.Committed
+    outs = run_all(engine, [a, b])
+    assert outs == [closed_form([3] * 14, 20), closed_form([4] * 14, 20)]
+    assert engine.core.free_blocks == 6
+
+
+def test_unserviceable_request_is_rejected(model):
+    engine, _ = make_engine(model, num_blocks=2)
+    r = request(model, [3] * 20, max_length=30)
+    engine.add_request(r)
+    with pytest.raises(EngineStepError, match="UnserviceableRequest"):
+        engine.step()
+    assert not engine.has_pending_requests()
+    engine.core.check_invariants()
+
+
+@pytest.mark.parametrize("kind,outcome", [(FailureKind.RetryableBeforeExecution, StepOutcome.RetryableBatchAbort),
+                                          (FailureKind.RetryableDuringExecution, StepOutcome.RetryableBatchAbort),
+                                          (FailureKind.CapacityExceeded, StepOutcome.ExecutionCapacityExceeded)])
+def test_retryable_failure_rolls_the_step_back(model, kind, outcome):
+    engine, ex = make_engine(model)
+    reqs = [request(model, [5, 9, 3]), request(model, [7] * 9)]
+    for r in reqs:
+        engine.add_request(r)
+    engine._run_model_step()
+    free_before = engine.core.free_blocks
+    tokens_before = [r.tokens().tolist() for r in reqs]
+    ex.script = [ExecutionFailure(kind, "scripted")]
+    engine._run_model_step()
+    assert engine.last_outcome == outcome
+    assert engine.core.free_blocks == free_before and [r.tokens().tolist() for r in reqs] == tokens_before
+    assert engine.metrics["steps_aborted"] == 1 and not engine.core.transaction_open
+    engine.core.check_invariants()
+    # the retried step and everything after it produce exactly what an undisturbed run produces
+    run_all(engine, reqs)
+    assert [r.tokens().tolist() for r in reqs] == [[5, 9, 3] + closed_form([5, 9, 3], 40), [7] * 9 + closed_form([7] * 9, 40)]
+
+
+def test_fatal_failure_marks_engine_unhealthy(model):
+    engine, ex = make_engine(model)
+    r = request(model, [5, 9, 3])
+    engine.add_request(r)
+    ex.script = [ExecutionFailure(FailureKind.Fatal, "device lost")]
+    with pytest.raises(EngineStepError, match="FatalExecutionFailure"):
+        engine.step()
+    assert not engine.core.healthy
+    with pytest.raises(RuntimeError, match="unhealthy"):
+        engine.step()
+    with pytest.raises(RuntimeError, match="unhealthy"):
+        engine.add_request(request(model, [1, 2]))
+    engine.core.check_invariants()
+
+
+def test_post_processing_failure_is_a_contract_failure(model):
+    engine, ex = make_engine(model)
+    r = request(model, [5, 9, 3])
+    engine.add_request(r)
+    ex.script = [ExecutionFailure(FailureKind.PostProcessing, "bad logits shape")]
+    with pytest.raises(EngineStepError, match="ExecutionContractFailure"):
+        engine.step()
+    assert engine.core.healthy and r.tokens().tolist() == [5, 9, 3]
+
+
+def test_multi_turn_continuation_reuses_the_cache(model):
+    engine, ex = make_engine(model)
+    r = request(model, [5, 9, 3], max_length=8)
+    engine.add_request(r)
+    first = run_all_keep(engine, r)
+    assert r.is_turn_complete() and len(r.tokens()) == 8
+    with pytest.raises(RuntimeError):
+        r.continue_with([4])                     # max_length is cumulative across turns
+    r2 = request(model, [5, 9, 3], max_length=30)
+    engine.add_request(r2)
+    while not r2.is_turn_complete() or r2.has_unseen_tokens():
+        x = engine.step()
+        while x is not None and x.has_unseen_tokens():
+            x.get_unseen_token()
+        if len(r2.tokens()) >= 7:
+            break
+    n_calls = len(ex.calls)
+    # finish the turn by hitting max_length, then continue
+    r3 = request(model, [6, 6], max_length=5)
+    engine.add_request(r3)
+    run_all_keep(engine, r3)
+    assert r3.is_turn_complete()
+    p = r3._native.processed
+    r3.params.search["max_length"] = 5
+    with pytest.raises(RuntimeError):
+        r3.continue_with([1, 2, 3])
+
+
+def run_all_keep(engine, r):
+    out = []
+    guard = 0
+    while not r.is_turn_complete() or r.has_unseen_tokens():
+        guard += 1
+        assert guard < 1000
+        x = engine.step()
+        engine.core.check_invariants()
+        while x is not None and x.has_unseen_tokens():
+            out.append(x.get_unseen_token())
+    return out
+
+
+def test_continue_with_only_processes_the_new_tokens(model):
+    engine, ex = make_engine(model)
+    r = request(model, [5, 9, 3], max_length=40)
+    # stop the turn early through EOS: craft so that the next token is EOS
+    engine.add_request(r)
+    for _ in range(3):
+        engine.step()
+    r.get_unseen_token() if r.has_unseen_tokens() else None
+    # cannot continue an active turn
+    with pytest.raises(RuntimeError):
+        r.continue_with([4, 4])
+    engine.remove_request(r)
+    q = request(model, [1, 62], max_length=40)      # EOS at once -> turn complete with processed == 2
+    engine.add_request(q)
+    run_all_keep(engine, q)
+    assert q.is_turn_complete() and q._native.processed == 2
+    ex.calls.clear()
+    q.continue_with([10, 11, 12])
+    assert q.status == native.RequestStatus.Assigned
+    engine.step()
+    assert ex.calls[0] == [(q._native.id, 3, 2, True)], "only the new tokens are fed; the cached prefix is reused"
+
+
+def test_remove_request_reclaims_blocks_and_teardown(model):
+    engine, _ = make_engine(model)
+    reqs = [request(model, [i + 2] * 10) for i in range(4)]
+    for r in reqs:
+        engine.add_request(r)
+    engine.step()
+    assert engine.core.free_blocks < 128
+    for r in reqs:
+        engine.remove_request(r)
+    assert engine.core.free_blocks == 128 and not engine.has_pending_requests()
+    engine.core.check_invariants()
+    del engine
+    engine, _ = make_engine(model)                  # recreate after teardown
+    r = request(model, [5, 9, 3])
+    engine.add_request(r)
+    assert run_all(engine, [r]) == [closed_form([5, 9, 3], 40)]
+
+
+def test_request_validation(model):
+    engine, _ = make_engine(model)
+    with pytest.raises(RuntimeError):
+        engine.add_request(request(model, [1] * 50, max_length=40))          # prompt leaves no room
+    p = og.GeneratorParams(model)
+    p.set_search_options(num_beams=2)
+    r = Request(p)
+    r.add_tokens(np.asarray([1, 2], dtype=np.int32))
+    with pytest.raises(RuntimeError, match="beam"):
+        engine.add_request(r)
+    r = request(model, [1, 2])
+    engine.add_request(r)
+    with pytest.raises(RuntimeError):
+        engine.add_request(r)
+    with pytest.raises(RuntimeError):
+        r.add_tokens([3])
+
+
+def test_block_pool_unit():
+    pool = native.BlockPool(4)
+    a = pool.reserve(3)
+    assert a == [0, 1, 2] and pool.free_count == 1
+    assert pool.reserve(2) is None and pool.free_count == 1, "reservation is all-or-nothing"
+    pool.commit(0); pool.release(1); pool.release(2)
+    assert pool.free_count == 3
+    with pytest.raises(Exception):
+        pool.free(1)                                 # not committed
+    pool.free(0)
+    assert pool.reserve(4) == [0, 1, 2, 3]
+
+
+def test_sampling_args_resolution():
+    o = native.RequestOptions()
+    o.do_sample = False
+    assert o.resolve() == (1, 0.0, 1.0)
+    o.do_sample, o.top_k, o.top_p, o.temperature = True, 40, 0.0, 0.7
+    assert o.resolve()[0] == 40 and o.resolve()[1] == 1.0
+    o.top_k, o.top_p = 0, 0.9
+    k, p, t = o.resolve()
+    assert k == -1 and abs(p - 0.9) < 1e-6 and abs(t - 0.7) < 1e-6
+    o.top_k = 1
+    assert o.resolve() == (1, 0.0, 1.0)

@@ -43,7 +43,7 @@ def test_gemm_matches_fp32(M, N, K):
     _close(y, want, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.05)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 5, 7, 8])
 def test_gemm_split_k(splits):
     M, N, K = 48, 512, 2048
     x, w = _rand(M, K, seed=3), _rand(N, K, std=0.05, seed=4)
@@ -66,13 +66,36 @@ def test_gemm_epilogues():
     ops.check_kernel_status()
 
 
-@pytest.mark.parametrize("M,I,K,splits", [(5, 256, 256, 1), (64, 1024, 512, 1), (64, 1024, 2048, 4), (200, 384, 256, 1)])
+@pytest.mark.parametrize("M,I,K,splits", [(5, 256, 256, 1), (64, 1024, 512, 1), (64, 1024, 2048, 4), (200, 384, 256, 1), (33, 128, 512, 3)])
 def test_gemm_gate_up_silu(M, I, K, splits):
     x = _rand(M, K, seed=9)
     w = _rand(2 * I, K, std=0.05, seed=10)
-    y = ops.gate_up_act(x, w, splits=splits)
+    b = _rand(2 * I, std=0.5, seed=11)
+    want = ref.gate_up_act(x.cpu(), w.cpu(), b.cpu())
+    wi, bi = ops.interleave_gate_up(w), ops.interleave_gate_up(b)
+    _close(ref.gate_up_act(x.cpu(), wi.cpu(), bi.cpu(), interleaved=True), want, rtol=1e-3, atol=1e-3)
+    y = ops.gate_up_act(x, wi, bi, splits=splits, interleaved=True)
     ops.check_kernel_status()
-    _close(y, ref.gate_up_act(x.cpu(), w.cpu()), rtol=3e-2, atol=0.05)
+    _close(y, want, rtol=3e-2, atol=0.05)
+    # stacked (not interleaved) weights take the unfused route and must agree too
+    _close(ops.gate_up_act(x, w, b), want, rtol=3e-2, atol=0.05)
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(64, 4096, 512, 0), (17, 256, 2048, 4), (130, 384, 256, 1)])
+def test_gemm_fused_allreduce_world_of_one(M, N, K, splits):
+    """The fused GEMM + all-reduce protocol (peer push, arrival counters, parity) with a single rank."""
+    from onnxruntime_genai_b200.parallel.symm import LocalComm
+    comm = LocalComm(torch.device("cuda", 0))
+    try:
+        x, w = _rand(M, K, seed=12), _rand(N, K, std=0.05, seed=13)
+        res = _rand(M, N, seed=14)
+        want = ref.linear(x.cpu(), w.cpu(), None, res.cpu())
+        for _ in range(3):   # consecutive uses alternate the buffer parity and advance the counters
+            y = ops.linear(x, w, residual=res, splits=splits, all_reduce=True)
+            ops.check_kernel_status()
+            _close(y, want, rtol=3e-2, atol=0.06)
+    finally:
+        comm.close()
 
 
 def test_gemm_strided_activation():
@@ -184,6 +207,14 @@ def test_attention_prefill_and_mixed():
 def test_attention_mha_and_wide_group():
     _attention_case(B=2, q_lens=[20, 1], past=[3, 50], Hq=4, Hkv=4, D=96, bs=16)
     _attention_case(B=2, q_lens=[9, 1], past=[40, 333], Hq=16, Hkv=2, D=64, bs=16)
+
+
+def test_attention_decode_mode_shapes():
+    # decode mode = at most 16 (token, head) rows per kv head: full 16-wide group, multi-token verify rows, MHA
+    _attention_case(B=3, q_lens=[1, 1, 1], past=[0, 63, 64], Hq=32, Hkv=2, D=128, bs=16)
+    _attention_case(B=3, q_lens=[3, 4, 1], past=[10, 200, 65], Hq=8, Hkv=2, D=64, bs=16)
+    _attention_case(B=2, q_lens=[1, 1], past=[129, 1], Hq=4, Hkv=4, D=96, bs=16, splits=2)
+    _attention_case(B=4, q_lens=[1] * 4, past=[1500, 31, 32, 700], Hq=32, Hkv=8, D=128, bs=16, splits=3)
 
 
 def test_attention_window_sinks_softcap():

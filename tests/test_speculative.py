@@ -1,0 +1,175 @@
+"""Speculative decoding (reference tests: test/python/models/test_speculative_decoding.py — a draft equal to
+the target must reproduce plain greedy decoding; n_gram_lookup_tests.cpp; speculative_sampling_tests.cpp)."""
+import copy
+import json
+import os
+
+import numpy as np
+import pytest
+
+import onnxruntime_genai_b200 as og
+from onnxruntime_genai_b200.models.arch import ArchConfig
+from onnxruntime_genai_b200.models.builder import export_model, make_genai_config, random_state_dict
+from onnxruntime_genai_b200.native_loader import native
+
+
+def small_arch(layers=2, hidden=64):
+    return ArchConfig(model_type="llama", vocab_size=97, hidden_size=hidden, num_layers=layers, num_heads=4, num_kv_heads=2,
+                      head_dim=16, intermediate_size=128, context_length=256, bos_token_id=0, eos_token_id=96, pad_token_id=0)
+
+
+@pytest.fixture(scope="module")
+def spec_dir(tmp_path_factory):
+    """Target + a draft that is the same network (acceptance must then be 100 % under greedy)."""
+    d = str(tmp_path_factory.mktemp("spec"))
+    arch = small_arch()
+    sd = random_state_dict(arch, seed=3, std=0.3)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd, filename="draft.onnx", write_config=False)
+    weak = small_arch(layers=1)
+    export_model(weak, d, "fp32", "cpu", state_dict=random_state_dict(weak, seed=9, std=0.3), filename="weak_draft.onnx", write_config=False)
+    return d
+
+
+def with_draft(spec_dir, filename, tmp_path, layers):
+    cfg = json.load(open(os.path.join(spec_dir, "genai_config.json")))
+    dec = copy.deepcopy(cfg["model"]["decoder"])
+    dec["filename"] = filename
+    dec["num_hidden_layers"] = layers
+    cfg["model"]["draft"] = dec
+    out = str(tmp_path)
+    for f in os.listdir(spec_dir):
+        if f != "genai_config.json":
+            os.symlink(os.path.join(spec_dir, f), os.path.join(out, f))
+    json.dump(cfg, open(os.path.join(out, "genai_config.json"), "w"))
+    return out
+
+
+def generate(model, prompt, n, **opts):
+    p = og.GeneratorParams(model)
+    spec = {k: opts.pop(k) for k in list(opts) if k in ("max_draft_tokens", "ngram_size", "ngram_chained_lookup", "min_adaptive_k", "cooldown")}
+    p.set_search_options(max_length=len(prompt) + n, **opts)
+    if spec:
+        p.set_speculative_options(**spec)
+    g = og.Generator(model, p)
+    g.append_tokens(np.asarray(prompt, dtype=np.int32))
+    calls = 0
+    while not g.is_done():
+        before = g.token_count()
+        g.generate_next_token()
+        assert g.token_count() == before + 1, "the API yields exactly one token per call"
+        calls += 1
+    return g.get_sequence(0).tolist(), g
+
+
+PROMPT = [5, 17, 40, 3, 22, 9, 61, 5, 17, 40, 3]
+
+
+def test_self_speculation_equals_greedy(spec_dir, tmp_path):
+    plain, _ = generate(og.Model(spec_dir), PROMPT, 40)
+    model = og.Model(with_draft(spec_dir, "draft.onnx", tmp_path, 2))
+    spec, g = generate(model, PROMPT, 40, max_draft_tokens=4)
+    assert spec == plain
+    st = g.get_speculative_stats()
+    assert st["rounds"] > 0 and st["acceptance_rate"] == 1.0 and st["tokens_per_round"] > 4.0
+
+
+def test_weak_draft_still_equals_greedy(spec_dir, tmp_path):
+    plain, _ = generate(og.Model(spec_dir), PROMPT, 30)
+    model = og.Model(with_draft(spec_dir, "weak_draft.onnx", tmp_path, 1))
+    spec, g = generate(model, PROMPT, 30, max_draft_tokens=3, cooldown=True)
+    assert spec == plain
+    st = g.get_speculative_stats()
+    assert st["proposed"] >= st["accepted"] and st["corrections"] > 0
+
+
+def test_ngram_speculation_equals_greedy(spec_dir):
+    model = og.Model(spec_dir)
+    plain, _ = generate(model, PROMPT, 60)
+    for chained in (False, True):
+        spec, g = generate(model, PROMPT, 60, ngram_size=3, max_draft_tokens=5, ngram_chained_lookup=chained)
+        assert spec == plain
+        st = g.get_speculative_stats()
+        assert st["ngram_hits"] + st["ngram_misses"] > 0
+
+
+def test_sampled_speculation_runs_and_respects_support(spec_dir, tmp_path):
+    model = og.Model(with_draft(spec_dir, "draft.onnx", tmp_path, 2))
+    seq, g = generate(model, PROMPT, 30, max_draft_tokens=4, do_sample=True, top_k=5, temperature=0.9, random_seed=11)
+    assert len(seq) <= len(PROMPT) + 30 and g.get_speculative_stats()["rounds"] > 0
+    seq2, _ = generate(model, PROMPT, 30, max_draft_tokens=4, do_sample=True, top_k=5, temperature=0.9, random_seed=11)
+    assert seq == seq2, "same seed, same tokens"
+
+
+def test_speculative_guards(spec_dir, tmp_path):
+    model = og.Model(spec_dir)
+    p = og.GeneratorParams(model)
+    p.set_search_options(batch_size=2, max_length=30)
+    p.set_speculative_options(ngram_size=3)
+    with pytest.raises(RuntimeError, match="batch_size 1"):
+        og.Generator(model, p)
+    with pytest.raises(RuntimeError):
+        p.set_speculative_options(max_draft_tokens=17)
+
+
+# ------------------------------------------------------------------------------------------ host math
+def test_ngram_index():
+    ix = native.NGramIndex(3)
+    ix.append(np.array([1, 2, 3, 4, 1, 2], dtype=np.int32))
+    assert ix.propose(3, False) == [3, 4, 1]
+    assert ix.propose(8, True)[:4] == [3, 4, 1, 2]
+    ix.append(np.array([9, 1, 2], dtype=np.int32))
+    assert ix.propose(2, False) == [9, 1], "the latest occurrence wins"
+    assert native.NGramIndex(2).propose(3, False) == []
+    with pytest.raises(RuntimeError):
+        native.NGramIndex(1)
+
+
+def test_verify_greedy_math():
+    logits = np.full((4, 10), -5.0, dtype=np.float32)
+    for i, t in enumerate([3, 7, 2, 9]):
+        logits[i, t] = 1.0
+    assert native.verify_greedy(np.array([3, 7, 2], dtype=np.int32), logits) == (3, [3, 7, 2, 9], True)
+    assert native.verify_greedy(np.array([3, 1, 2], dtype=np.int32), logits) == (1, [3, 7], False)
+
+
+def test_accept_probability_and_statistics():
+    assert native.accept_probability(0.2, 0.4) == pytest.approx(0.5)
+    assert native.accept_probability(0.5, 0.4) == 1.0
+    assert native.accept_probability(0.0, 0.0) == 0.0
+    # distribution equivalence: speculative sampling with a mismatched draft reproduces the target distribution
+    vocab, n = 6, 4000
+    rng = np.random.RandomState(0)
+    target = rng.randn(2, vocab).astype(np.float32)
+    q = np.exp(rng.randn(vocab)); q /= q.sum()
+    p = native.SearchParams(); p.vocab_size, p.max_length, p.random_seed, p.eos_token_ids = vocab, 4, 5, [99]
+    s = native.Search(p)
+    counts = np.zeros(vocab)
+    ids = np.arange(vocab, dtype=np.int32)
+    for _ in range(n):
+        d = int(np.searchsorted(np.cumsum(q), s.uniform(), side="right").clip(max=vocab - 1))
+        acc, commit, _ = native.verify_sampled(np.array([d], dtype=np.int32), [(ids, q.astype(np.float32))], target, 0, 0.0, 1.0, s)
+        counts[commit[0]] += 1
+    want = np.exp(target[0] - target[0].max()); want /= want.sum()
+    assert 0.5 * np.abs(counts / n - want).sum() < 0.04
+
+
+def test_adaptive_k_and_cooldown():
+    a = native.AdaptiveK(4, 2)
+    assert a.k == 2 and a.min_k == 2
+    for _ in range(12):
+        a.record(a.k, a.k, a.k, a.k + 1, True, 1.0)
+    assert a.k > 2 and a.increases > 0
+    k_hi = a.k
+    for _ in range(30):
+        a.record(a.k, a.k, 0, 1, True, 1.0)
+    assert a.k < k_hi and a.k >= 2
+    fixed = native.AdaptiveK(4, 0)
+    fixed.record(4, 4, 4, 5, True, 1.0)
+    assert fixed.k == 4
+    c = native.ZeroAcceptCooldown(True)
+    for _ in range(3):
+        assert not c.should_skip_round()
+        c.record(4, 0)
+    assert c.should_skip_round() and not c.should_skip_round() and c.skips == 1
+    assert not native.ZeroAcceptCooldown(False).should_skip_round()
