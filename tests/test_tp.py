@@ -1,0 +1,65 @@
+"""Tensor parallelism: multi-rank CPU (gloo) check of the sharding math, and 2-GPU checks of the NCCL and
+fused NVLink reductions against the single-GPU run of the same checkpoint."""
+import copy
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(model_dir, out, nproc, port, extra=(), env_extra=None):
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+    env.update(env_extra or {})
+    if nproc == 1:
+        cmd = [sys.executable, "-m", "onnxruntime_genai_b200.parallel.tp_check", "--model", model_dir, "--out", out, *extra]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+               "--master-port", str(port), "-m", "onnxruntime_genai_b200.parallel.tp_check", "--model", model_dir, "--out", out, *extra]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return np.load(out)
+
+
+@pytest.fixture(scope="module")
+def ckpt(tmp_path_factory):
+    from onnxruntime_genai_b200.models.arch import PRESETS
+    from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+    arch = copy.deepcopy(PRESETS["tiny-llama"])
+    arch.attn_bias = True
+    arch.mlp_bias = True
+    sd = random_state_dict(arch, seed=1, std=0.05)
+    base = tmp_path_factory.mktemp("tp")
+    cpu, gpu = str(base / "cpu"), str(base / "gpu")
+    export_model(copy.deepcopy(arch), cpu, "fp32", "cpu", state_dict=sd, paged=True, block_size=16, num_blocks=256, max_batch_size=8)
+    export_model(copy.deepcopy(arch), gpu, "bf16", "cuda", state_dict=sd, paged=True, block_size=16, num_blocks=256, max_batch_size=8)
+    return cpu, gpu, str(base)
+
+
+def test_tp2_on_cpu_matches_single_rank(ckpt):
+    cpu, _, base = ckpt
+    one = _run(cpu, os.path.join(base, "cpu1.npz"), 1, 0, ["--engine"])
+    two = _run(cpu, os.path.join(base, "cpu2.npz"), 2, 29611, ["--engine"])
+    np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
+    assert two["seqs"].tolist() == one["seqs"].tolist()
+    assert two["engine"].tolist() == one["engine"].tolist()
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("backend", ["nccl", "fused"])
+def test_tp2_on_gpu_matches_single_gpu(ckpt, backend):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _, gpu, base = ckpt
+    one = _run(gpu, os.path.join(base, "gpu1.npz"), 1, 0, ["--engine"])
+    two = _run(gpu, os.path.join(base, f"gpu2_{backend}.npz"), 2, 29621 if backend == "nccl" else 29631, ["--backend", backend, "--engine"],
+               {"NCCL_NVLS_ENABLE": "0"})
+    assert str(two["backend"]) == backend, "the fused path must not silently fall back"
+    spread = one["logits"].std()
+    assert np.abs(two["logits"] - one["logits"]).max() < 0.08 * spread + 0.02
+    assert two["seqs"].shape == one["seqs"].shape
