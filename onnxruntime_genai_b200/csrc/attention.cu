@@ -442,3 +442,38 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
   }
   return -5;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (see noalloc.h): the split-KV partials live in a fixed array of
+// the library's device image instead of caller-provided scratch.
+#include "noalloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[OGB_NOALLOC_SCRATCH_BYTES];
+// Device address of g_noalloc_scratch per device, resolved on the first call with that device current.
+static void* g_noalloc_scratch_addr[16] = {};
+
+OGB_API long long ogb_paged_attention_noalloc_required_bytes(int total_tokens, int Hq, int D, int splits) {
+  return ogb_attention_scratch_bytes(total_tokens, Hq, D, splits);
+}
+
+OGB_API int ogb_paged_attention_noalloc(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                        const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                                        int table_cols, int block_size, void* out, int out_stride, const float* sinks, float scale,
+                                        float softcap, int window, int B, int total_tokens, int max_q_len, int Hq, int Hkv, int D,
+                                        int splits, void* stream) {
+  if (splits < 1) splits = 1;
+  const long long need = ogb_attention_scratch_bytes(total_tokens, Hq, D, splits);
+  if (need > OGB_NOALLOC_SCRATCH_BYTES) return OGB_ERR_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return OGB_ERR_NOALLOC_SETUP;
+  if (!g_noalloc_scratch_addr[dev]) {
+    // In host code `g_noalloc_scratch` names a host-side shadow of the symbol; the kernel needs the
+    // address the array has on the current device.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return OGB_ERR_NOALLOC_SETUP;
+    g_noalloc_scratch_addr[dev] = p;
+  }
+  return ogb_paged_attention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out,
+                             out_stride, sinks, scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits,
+                             g_noalloc_scratch_addr[dev], OGB_NOALLOC_SCRATCH_BYTES, stream);
+}
