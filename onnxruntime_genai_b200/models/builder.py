@@ -282,6 +282,17 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
     W.add_float("cos_cache", torch.from_numpy(cos), force_fp32=(precision == "fp32"))
     W.add_float("sin_cache", torch.from_numpy(sin), force_fp32=(precision == "fp32"))
 
+    if arch.residual_multiplier != 1.0:
+        W.model.initializers["/model/constants/residual_multiplier"] = op.Tensor(
+            "/model/constants/residual_multiplier", op.FLOAT, (), raw=np.float32(arch.residual_multiplier).tobytes())
+
+    def residual_scale(name: str, value: str) -> str:
+        """Granite-style residual multiplier: the sub-layer output is scaled before it joins the residual stream."""
+        if arch.residual_multiplier == 1.0:
+            return value
+        W.node("Mul", name, [value, "/model/constants/residual_multiplier"], [name + "/output_0"])
+        return name + "/output_0"
+
     norm_op = "LayerNormalization" if arch.layernorm else "SimplifiedLayerNormalization"
     skip_op = "SkipLayerNormalization" if arch.layernorm else "SkipSimplifiedLayerNormalization"
     attn_op = "PagedAttention" if paged else "GroupQueryAttention"
@@ -351,6 +362,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             mid_name = "pre_feedforward_layernorm"
         else:
             mid_name = "post_attention_layernorm"
+        o_out = residual_scale(f"{n}/attn/residual_mul/Mul", o_out)
         # norm before the MLP (adds the attention output to the residual stream)
         put_vec(p + mid_name + ".weight", [p + mid_name + ".weight"], arch.norm_offset)
         ins = [o_out, residual, p + mid_name + ".weight"]
@@ -402,7 +414,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             W.node(norm_op, f"{n}/post_feedforward_layernorm/LayerNorm", [mlp_out, p + "post_feedforward_layernorm.weight"],
                    [f"{n}/post_feedforward_layernorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1)
             mlp_out = f"{n}/post_feedforward_layernorm/output_0"
-        hidden = mlp_out
+        hidden = residual_scale(f"{n}/mlp/residual_mul/Mul", mlp_out)
 
     # ---- final norm + head
     fname = f"model.layers.{L}.final_norm_layernorm.weight"

@@ -134,6 +134,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         a.activation = "gelu" if g.find("/model/layers.0/mlp/act_fn/", ops=["FastGelu", "Gelu", "BiasGelu"]) is not None else "silu"
     if g.by_name.get("/model/embed_tokens/Mul") is not None:
         a.embed_scale = float(g.tensor("/model/constants/embed_scale").float().item())
+    if g.has_init("/model/constants/residual_multiplier"):
+        a.residual_multiplier = float(g.tensor("/model/constants/residual_multiplier").float().item())
     if g.by_name.get("/lm_head/Mul") is not None:
         a.logits_scale = float(g.tensor("/model/constants/logits_scale").float().item())
     sc = g.by_name.get("/lm_head/softcap")

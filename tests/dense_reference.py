@@ -1,0 +1,104 @@
+"""Independent dense fp32 reference of the decoder families (full recompute, no cache, no paging, no ops
+from the package): canonical Hugging Face style state dict + ArchConfig -> next-token logits."""
+import math
+
+import torch
+
+from onnxruntime_genai_b200.models.arch import rope_caches
+
+
+def _norm(x, w, b, arch):
+    if arch.layernorm:
+        y = torch.nn.functional.layer_norm(x, (x.shape[-1],), None, None, arch.norm_eps)
+    else:
+        y = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + arch.norm_eps)
+    y = y * (w.float() + arch.norm_offset)
+    return y + b.float() if b is not None else y
+
+
+def _rope(x, cos, sin, rot, interleaved):
+    out = x.clone()
+    c, s = cos[:, None, :], sin[:, None, :]
+    if interleaved:
+        a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+        out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * s, b * c + a * s
+    else:
+        h = rot // 2
+        a, b = x[..., :h], x[..., h:rot]
+        out[..., :h], out[..., h:rot] = a * c - b * s, b * c + a * s
+    return out
+
+
+def logits(arch, sd, ids):
+    """ids: list of token ids; returns logits [len(ids), vocab] (fp32)."""
+    sd = {k: v.float() for k, v in sd.items()}
+    S = len(ids)
+    pos = torch.arange(S)
+    cos, sin = rope_caches(arch, max(S, 8))
+    cos, sin = torch.from_numpy(cos)[pos], torch.from_numpy(sin)[pos]
+    h = sd["model.embed_tokens.weight"][torch.tensor(ids)] * arch.embed_scale
+    G = arch.num_heads // arch.num_kv_heads
+    D = arch.head_dim
+    for i in range(arch.num_layers):
+        p = f"model.layers.{i}."
+        g = lambda n: sd.get(p + n)
+        x = _norm(h, g("input_layernorm.weight"), g("input_layernorm.bias"), arch)
+        lin = lambda t, n: t @ g(n + ".weight").t() + (g(n + ".bias") if g(n + ".bias") is not None else 0)
+        q = lin(x, "self_attn.q_proj").view(S, arch.num_heads, D)
+        k = lin(x, "self_attn.k_proj").view(S, arch.num_kv_heads, D)
+        v = lin(x, "self_attn.v_proj").view(S, arch.num_kv_heads, D)
+        if arch.qk_norm:
+            hn = lambda t, w: t * torch.rsqrt((t * t).mean(-1, keepdim=True) + arch.norm_eps) * (w + arch.norm_offset)
+            q, k = hn(q, g("self_attn.q_norm.weight")), hn(k, g("self_attn.k_norm.weight"))
+        q, k = _rope(q, cos, sin, arch.rotary_dim, arch.rotary_interleaved), _rope(k, cos, sin, arch.rotary_dim, arch.rotary_interleaved)
+        k, v = k.repeat_interleave(G, 1), v.repeat_interleave(G, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) * arch.scale
+        if arch.softcap > 0:
+            s = arch.softcap * torch.tanh(s / arch.softcap)
+        mask = pos[None, :] <= pos[:, None]
+        w = arch.layer_window(i)
+        if w > 0:
+            mask &= pos[None, :] > pos[:, None] - w
+        s = s.masked_fill(~mask[None], float("-inf"))
+        if arch.attn_sinks:
+            sk = g("self_attn.sinks").view(-1, 1, 1).expand(-1, S, 1)
+            pr = torch.softmax(torch.cat([s, sk], -1), -1)[..., :-1]
+        else:
+            pr = torch.softmax(s, -1)
+        att = torch.einsum("hqk,khd->qhd", pr, v).reshape(S, arch.num_heads * D)
+        o = lin(att, "self_attn.o_proj")
+        if arch.post_sublayer_norms:
+            o = _norm(o, g("post_attention_layernorm.weight"), None, arch)
+            mid = "pre_feedforward_layernorm"
+        else:
+            mid = "post_attention_layernorm"
+        h = h + o * arch.residual_multiplier
+        x = _norm(h, g(mid + ".weight"), g(mid + ".bias"), arch)
+        if arch.num_experts > 0:
+            router = x @ g("mlp.router.weight").t() + g("mlp.router.bias")
+            tv, ti = torch.topk(router, arch.experts_per_token, -1)
+            tw = torch.softmax(tv, -1)
+            y = torch.zeros_like(x)
+            for t in range(S):
+                for j in range(arch.experts_per_token):
+                    e = int(ti[t, j])
+                    gu = x[t] @ g("mlp.experts.gate_up_proj")[e].t() + g("mlp.experts.gate_up_proj_bias")[e]
+                    gt, up = gu[0::2].clamp(max=arch.moe_swiglu_limit), gu[1::2].clamp(-arch.moe_swiglu_limit, arch.moe_swiglu_limit)
+                    a = gt * torch.sigmoid(arch.moe_swiglu_alpha * gt) * (up + 1)
+                    y[t] += tw[t, j] * (a @ g("mlp.experts.down_proj")[e].t() + g("mlp.experts.down_proj_bias")[e])
+        else:
+            gt, up = lin(x, "mlp.gate_proj"), lin(x, "mlp.up_proj")
+            a = torch.nn.functional.silu(gt) if arch.activation == "silu" else torch.nn.functional.gelu(gt, approximate="tanh")
+            y = lin(a * up, "mlp.down_proj")
+        if arch.post_sublayer_norms:
+            y = _norm(y, g("post_feedforward_layernorm.weight"), None, arch)
+        h = h + y * arch.residual_multiplier
+    x = _norm(h, sd["model.norm.weight"], sd.get("model.norm.bias"), arch)
+    head = sd["model.embed_tokens.weight"] if arch.tie_embeddings else sd["lm_head.weight"]
+    out = x @ head.t()
+    if sd.get("lm_head.bias") is not None and not arch.tie_embeddings:
+        out = out + sd["lm_head.bias"]
+    out = out * arch.logits_scale
+    if arch.final_logit_softcap > 0:
+        out = torch.tanh(out / arch.final_logit_softcap) * arch.final_logit_softcap
+    return out

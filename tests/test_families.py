@@ -1,0 +1,107 @@
+"""Model families through export -> load -> generate, against the independent dense reference
+(tests/dense_reference.py).  Each family is a set of ArchConfig flags: biases, q/k norms, soft-capping,
+sliding windows on some layers, attention sinks, LayerNorm + partial rotary, embedding / logit scales,
+post-sublayer norms, mixture of experts."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import onnxruntime_genai_b200 as og
+from dense_reference import logits as dense_logits
+from onnxruntime_genai_b200.models.arch import ArchConfig, from_hf_config
+from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+
+BASE = dict(vocab_size=211, hidden_size=64, num_layers=3, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+            context_length=256, bos_token_id=0, eos_token_id=210, pad_token_id=0)
+
+FAMILIES = {
+    "llama": dict(model_type="llama"),
+    "llama3_rope": dict(model_type="llama", rope_theta=500000.0,
+                        rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                      "original_max_position_embeddings": 64}),
+    "mistral_window": dict(model_type="mistral", sliding_window=8),
+    "qwen2": dict(model_type="qwen2", attn_bias=True),
+    "qwen3": dict(model_type="qwen3", qk_norm=True, tie_embeddings=True),
+    "phi3": dict(model_type="phi3", num_kv_heads=4),
+    "phi": dict(model_type="phi", layernorm=True, partial_rotary_factor=0.5, attn_bias=True, o_bias=True, mlp_bias=True,
+                lm_head_bias=True, activation="gelu", num_kv_heads=4),
+    "gemma2": dict(model_type="gemma2", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, softcap=20.0,
+                   final_logit_softcap=15.0, sliding_window=8, sliding_layers=[0, 2], attn_scale=0.2, tie_embeddings=True),
+    "gemma3": dict(model_type="gemma3_text", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, qk_norm=True,
+                   sliding_window=8, sliding_layers=[0, 1], tie_embeddings=True),
+    "granite": dict(model_type="granite", residual_multiplier=0.5, logits_scale=0.25, embed_scale=3.0, attn_scale=0.3),
+    "interleaved_rope": dict(model_type="chatglm", rotary_interleaved=True, partial_rotary_factor=0.5, attn_bias=True),
+    "gptoss": dict(model_type="gptoss", attn_bias=True, o_bias=True, mlp_bias=True, attn_sinks=True, sliding_window=8,
+                   sliding_layers=[0, 2], num_experts=4, experts_per_token=2, intermediate_size=64),
+}
+
+
+@pytest.mark.parametrize("family", sorted(FAMILIES))
+def test_family_logits_and_decode_match_dense_reference(family, tmp_path):
+    arch = ArchConfig(**{**BASE, **FAMILIES[family]})
+    sd = random_state_dict(arch, seed=11, std=0.15)
+    d = str(tmp_path)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    model = og.Model(d)
+    assert model.type == arch.model_type
+    a2 = model.arch
+    for f in ("norm_eps", "layernorm", "qk_norm", "attn_bias", "o_bias", "mlp_bias", "softcap", "sliding_window", "attn_sinks",
+              "activation", "num_experts", "experts_per_token", "post_sublayer_norms", "rotary_interleaved", "lm_head_bias"):
+        assert getattr(a2, f) == pytest.approx(getattr(arch, f)), f
+    assert a2.intermediate_size == arch.intermediate_size and a2.rotary_dim == arch.rotary_dim
+    prompt = np.random.RandomState(4).randint(0, arch.vocab_size - 1, size=(1, 23)).astype(np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=40)
+    g = og.Generator(model, p)
+    g.append_tokens(prompt)
+    want = dense_logits(arch, sd, prompt[0].tolist())[-1].numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=2e-4)
+    # decode steps (KV cache, windows crossing the cache) against full recompute
+    ids = prompt[0].tolist()
+    for _ in range(6):
+        g.generate_next_token()
+        ids.append(int(g.get_next_tokens()[0]))
+        if g.is_done():
+            break
+        want = dense_logits(arch, sd, ids)[-1].numpy()
+        np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
+
+
+def test_hf_config_mapping():
+    a = from_hf_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 64, "num_attention_heads": 4,
+                        "num_key_value_heads": 2, "num_hidden_layers": 2, "intermediate_size": 128, "vocab_size": 100,
+                        "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "eos_token_id": [5, 6]})
+    assert a.model_type == "qwen2" and a.attn_bias and a.head_dim == 16 and a.eos_list() == [5, 6] and a.norm_eps == 1e-6
+    g = from_hf_config({"architectures": ["GptOssForCausalLM"], "model_type": "gpt_oss", "hidden_size": 64, "num_attention_heads": 8,
+                        "num_key_value_heads": 2, "head_dim": 16, "num_hidden_layers": 4, "intermediate_size": 64, "vocab_size": 100,
+                        "num_local_experts": 8, "num_experts_per_tok": 2, "sliding_window": 16,
+                        "layer_types": ["sliding_attention", "full_attention"] * 2})
+    assert g.model_type == "gptoss" and g.num_experts == 8 and g.attn_sinks and g.sliding_layers == [0, 2]
+
+
+def test_int4_checkpoint_roundtrip(tmp_path):
+    """MatMulNBits int4 block-32 (asymmetric, uint4 zero points) export -> load reproduces the dequantised weights."""
+    from onnxruntime_genai_b200.models.builder import dequantize_int4_block32, quantize_int4_block32
+    w = torch.randn(48, 96) * 0.1
+    for sym in (False, True):
+        q, s, zp = quantize_int4_block32(w, symmetric=sym)
+        assert q.shape == (48, 3, 16) and q.dtype == torch.uint8 and (zp is None) == sym
+        wd = dequantize_int4_block32(q, s, zp, 48, 96)
+        assert (wd - w).abs().max() < (s.max() * (0.51 if not sym else 1.01))
+    arch = ArchConfig(**{**BASE, "model_type": "phi3", "num_kv_heads": 4})
+    sd = random_state_dict(arch, seed=2, std=0.1)
+    export_model(copy.deepcopy(arch), str(tmp_path), "int4", "cpu", state_dict=sd)
+    model = og.Model(str(tmp_path))
+    q, s, zp = quantize_int4_block32(torch.cat([sd[f"model.layers.0.self_attn.{n}_proj.weight"] for n in "qkv"], 0))
+    want = dequantize_int4_block32(q, s.to(torch.float16).float(), zp, q.shape[0], 64)
+    torch.testing.assert_close(model.decoder.layers[0].qkv_w.float(), want, rtol=1e-3, atol=1e-4)
+    prompt = np.arange(1, 12, dtype=np.int32).reshape(1, -1)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=20)
+    g = og.Generator(model, p)
+    g.append_tokens(prompt)
+    fp = dense_logits(arch, sd, prompt[0].tolist())[-1].numpy()
+    got = g.get_logits().reshape(-1)
+    assert np.corrcoef(got, fp)[0, 1] > 0.9, "int4 logits must stay close to the fp32 model"
