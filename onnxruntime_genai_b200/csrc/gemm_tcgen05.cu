@@ -41,90 +41,10 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 #include "kernels.h"
 
 namespace ogb {
-
-constexpr int GEMM_BLOCK_N = 128;
-constexpr int GEMM_BLOCK_K = 64;
-constexpr int GEMM_UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
-constexpr int W_TILE_BYTES = GEMM_BLOCK_N * GEMM_BLOCK_K * 2;  // 16 KiB
-constexpr int COMM_MAX_WORLD = 8;
-
-struct CommParams {
-  int world, rank;                        // world <= 1 with buf[0] == nullptr disables the fused all-reduce
-  __nv_bfloat16* buf[COMM_MAX_WORLD];     // receive buffer of every rank: [2 parities][world sources][plane_elems]
-  uint32_t* flag[COMM_MAX_WORLD];         // arrival counters of every rank: [max_slots]
-  uint32_t* uses;                         // this rank's use count per slot
-  long long plane_elems;
-  int max_slots;
-};
-
-struct GemmParams {
-  int M, N, K;          // N = weight rows
-  int splits, kb_per_split, total_kb;
-  void* C;
-  int ldc;
-  int out_fp32;
-  int act_pair;         // 1: tiles hold 64 gate rows + 64 up rows; output silu(gate)*up with N/2 columns
-  const __nv_bfloat16* residual;
-  int ldr;
-  const __nv_bfloat16* bias;
-  int* status;
-  int pdl;
-  CommParams comm;
-};
-
-template <int BT>
-struct GemmCfg {
-  static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
-  static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES;
-  // Decode-sized tiles keep two CTAs per SM: more bytes in flight per SM, dynamic balance between
-  // SMs, and room for the next kernel's CTAs to become resident and prefetch weights.
-  static constexpr bool TWO_PER_SM = BT <= 64;
-  static constexpr int BUDGET = TWO_PER_SM ? 100 * 1024 : 196 * 1024;
-  static constexpr int MAX_STAGES = BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
-  static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
-  static constexpr int PARTIAL_BYTES = BT * GEMM_BLOCK_N * 4;  // fp32 tile parked in stage memory
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static_assert(PARTIAL_BYTES <= STAGES * STAGE_BYTES, "the parked tile must fit in the pipeline memory");
-};
-
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
-
-__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {  // bypass L1: the data was written by a peer GPU
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
 
 template <int BT>
 __global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BT>::TWO_PER_SM ? 2 : 1)
@@ -221,166 +141,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
   }
 
-  // -------------------------------------------------------------------- epilogue (warps 2..5)
-  const bool epi = warp >= 2;
-  const int et = threadIdx.x - 64;   // 0..127 for epilogue threads
-  float* part = reinterpret_cast<float*>(smem);  // [BT][128] fp32, reuses the pipeline stages
-  if (epi) {
-    const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
-    const int row = quarter * 32 + lane;
-    const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
-    if (!mbar_wait_bounded(accum_bar, 0, abort_flag, 4000000000ull)) fail(OGB_ERR_WAIT_MMA);
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // uniform decision over the 128 epilogue threads
-    const bool have = (*abort_flag == 0);
-    tc_fence_after();
-    if (have) {
-#pragma unroll 1
-      for (int c0 = 0; c0 < BT; c0 += 16) {
-        uint32_t r0[16];
-        tmem_ld16(taddr + c0, r0);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) part[(c0 + j) * GEMM_BLOCK_N + row] = __uint_as_float(r0[j]);
-      }
-    }
-    if (p.pdl) pdl_wait();  // residual reads and every store come after the previous kernel has finished
-  }
-  // The parked tiles are complete and visible (cluster-wide when split) after this barrier.  Every
-  // thread of every CTA of the cluster meets here, also after an abort.
-  __syncwarp();
-  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
-
-  if (epi && *abort_flag == 0) {
-    const int my_rank = p.splits > 1 ? int(cluster_ctarank()) : 0;
-    const int per = (BT + p.splits - 1) / p.splits;  // token columns finished by this CTA
-    const int c_begin = min(BT, my_rank * per), c_end = min(BT, c_begin + per);
-    const int OCT = p.act_pair ? 8 : 16;             // 8-wide output segments per token column
-    const int items = (c_end - c_begin) * OCT;
-    const int n_out = p.act_pair ? p.N / 2 : p.N;    // output columns of the whole problem
-    const int col0 = n_tile * (p.act_pair ? 64 : 128);
-    const uint32_t part_addr = smem_u32(part);
-    const bool comm_on = p.comm.buf[0] != nullptr;
-
-    auto reduce8 = [&](int mc, int n_local, float (&v)[8]) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = 0.f;
-      for (int s = 0; s < p.splits; ++s) {
-        float4 a, b;
-        if (p.splits > 1) {
-          const uint32_t ra = dsmem_addr(part_addr + uint32_t(mc * GEMM_BLOCK_N + n_local) * 4, uint32_t(s));
-          a = ld_dsmem_f32x4(ra);
-          b = ld_dsmem_f32x4(ra + 16);
-        } else {
-          a = *reinterpret_cast<const float4*>(part + mc * GEMM_BLOCK_N + n_local);
-          b = *reinterpret_cast<const float4*>(part + mc * GEMM_BLOCK_N + n_local + 4);
-        }
-        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-      }
-    };
-    auto add_bias8 = [&](int n_glob, float (&v)[8]) {
-      if (!p.bias) return;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) if (n_glob + j < p.N) v[j] += bf2f(p.bias[n_glob + j]);
-    };
-    auto store8 = [&](int m, int col, float (&v)[8]) {  // residual add + store of one 8-wide segment
-      if (p.residual) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) if (col + j < n_out) v[j] += bf2f(p.residual[size_t(m) * p.ldr + col + j]);
-      }
-      if (p.out_fp32) {
-        float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
-        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = v[j];
-        }
-      } else {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;
-        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = f2bf(v[j]);
-        }
-      }
-    };
-
-    uint32_t use = 0;
-    int slot = 0;
-    if (comm_on) {
-      slot = (m_tile * gridDim.x + n_tile) * gridDim.z + my_rank;
-      if (et == 0) *use_slot = p.comm.uses[slot];
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      use = *use_slot;
-    }
-    const size_t plane = size_t(p.comm.plane_elems);
-    const size_t par_off = size_t(use & 1) * p.comm.world * plane;
-
-    for (int item = et; item < items; item += 128) {
-      const int mc = c_begin + item / OCT, oc = item % OCT;
-      const int m = m_tile * BT + mc;
-      if (m >= p.M) continue;
-      float v[8];
-      if (p.act_pair) {
-        float u[8];
-        reduce8(mc, oc * 8, v);
-        reduce8(mc, 64 + oc * 8, u);
-        add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
-        add_bias8(n_tile * GEMM_BLOCK_N + 64 + oc * 8, u);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = silu(v[j]) * u[j];
-      } else {
-        reduce8(mc, oc * 8, v);
-        add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
-      }
-      const int col = col0 + oc * 8;
-      if (!comm_on) {
-        store8(m, col, v);
-      } else if (col < n_out) {
-        // push this rank's partial (bf16) into every rank's receive buffer: plain peer stores
-        const uint4 pk = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-        const size_t off = par_off + size_t(p.comm.rank) * plane + size_t(m) * n_out + col;
-        for (int r = 0; r < p.comm.world; ++r) *reinterpret_cast<uint4*>(p.comm.buf[r] + off) = pk;
-      }
-    }
-
-    if (comm_on) {
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        for (int r = 0; r < p.comm.world; ++r) red_add_release_sys(p.comm.flag[r] + slot, 1u);
-        const uint32_t target = uint32_t(p.comm.world) * (use + 1);
-        const uint32_t* mine = p.comm.flag[p.comm.rank] + slot;
-        const uint64_t t0 = global_timer_ns();
-        uint32_t spins = 0;
-        while (int32_t(ld_acquire_sys(mine) - target) < 0) {
-          if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 5000000000ull) { fail(OGB_ERR_WAIT_PEER); break; }
-        }
-        p.comm.uses[slot] = use + 1;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int item = et; item < items; item += 128) {
-        const int mc = c_begin + item / OCT, oc = item % OCT;
-        const int m = m_tile * BT + mc;
-        const int col = col0 + oc * 8;
-        if (m >= p.M || col >= n_out) continue;
-        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const __nv_bfloat16* base = p.comm.buf[p.comm.rank] + par_off + size_t(m) * n_out + col;
-        for (int r = 0; r < p.comm.world; ++r) {
-          const uint4 q = ld_cg_u4(base + size_t(r) * plane);
-          const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
-          v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
-        }
-        store8(m, col, v);
-      }
-    }
-  }
-  if (p.splits > 1) {
-    __syncwarp();
-    cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
-  }
+  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile);
 
   tc_fence_before();
   __syncthreads();
@@ -436,6 +197,11 @@ static bool MakeMap(CUtensorMap* out, const void* ptr, int rows, int cols, int l
   if (cache.size() > 65536) cache.clear();
   cache.emplace(key, *out);
   return true;
+}
+
+// Shared with gemm_w4.cu (activation tensor maps).
+bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  return MakeMap(out, ptr, rows, cols, ld, box_rows);
 }
 
 template <int BT>

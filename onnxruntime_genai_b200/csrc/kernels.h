@@ -23,6 +23,11 @@ int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, 
 int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
                   const void* residual, int ldr, int flags, int splits, int device, int* status, int sm_count, void* stream);
 
+// ---- gemm_w4.cu (int4 block-32 weights, repacked by ops.pack_w4)
+long long ogb_w4_packed_bytes(int N, int K);
+int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int M, int N, int K, const void* bias,
+                const void* residual, int ldr, int flags, int splits, int* status, int sm_count, void* stream);
+
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);
 int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias, void* out,

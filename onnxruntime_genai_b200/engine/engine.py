@@ -225,6 +225,9 @@ class ModelExecutor:
     def _capture(self, bb: int, cb: int):
         st = self.staging
         s = self._step_inputs(bb, bb, st.table_cols, 1, cb * self.kv.block_size)
+        tp = self.decoder.tp
+        if tp.size > 1:
+            tp.barrier()   # ranks enter warm-up and capture together (peer waits in the fused kernels are bounded)
         stream = torch.cuda.Stream()
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):

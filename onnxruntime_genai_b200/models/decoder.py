@@ -86,6 +86,9 @@ class NoTP:
     def fused_ok(self, x):
         return False
 
+    def barrier(self):
+        pass
+
 
 @dataclass
 class LayerWeights:

@@ -174,6 +174,28 @@ def _linear_weight(g: GraphView, node, dtype, device, rows: Optional[slice] = No
     return w.to(device=device, dtype=dtype).contiguous()
 
 
+def _is_q4(nodes) -> bool:
+    return all(n is not None and n.op_type == "MatMulNBits" and int(n.attrs.get("bits", 4)) == 4 and
+               int(n.attrs.get("block_size", 32)) == 32 and int(n.attrs["K"]) % 64 == 0 for n in nodes)
+
+
+def _q4_weight(g: GraphView, nodes, device, interleave: bool = False):
+    """One W4Weight from one or more MatMulNBits nodes stacked along N (kept in int4 for the dequant GEMM)."""
+    from ..ops.w4 import W4Weight, unpack_ort_q4
+    qs, ss, zs = [], [], []
+    for n in nodes:
+        N, K = int(n.attrs["N"]), int(n.attrs["K"])
+        q, zp = unpack_ort_q4(g.tensor(n.inputs[1]), g.tensor(n.inputs[3]) if len(n.inputs) > 3 and n.inputs[3] else None, N, K)
+        qs.append(q)
+        ss.append(g.tensor(n.inputs[2]).float().view(N, K // 32))
+        zs.append(zp if zp is not None else torch.full((N, K // 32), 8, dtype=torch.uint8))
+    q, s, z = torch.cat(qs, 0), torch.cat(ss, 0), torch.cat(zs, 0)
+    if interleave:
+        from ..ops import interleave_gate_up
+        q, s, z = interleave_gate_up(q), interleave_gate_up(s), interleave_gate_up(z)
+    return W4Weight.from_quantized(q, s, z, device, interleaved=interleave)
+
+
 def _vec(g: GraphView, name: str, dtype, device, sl: Optional[slice] = None) -> Optional[torch.Tensor]:
     if not g.has_init(name):
         return None
@@ -190,6 +212,8 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
     g.set_arch_shapes(arch)
     model = DecoderModel(arch, device, dtype, tp)
     tpn, tpr = model.tp.size, model.tp.rank
+    # int4 MatMulNBits weights stay int4 (dequant GEMM) on a single GPU; tensor-parallel shards are dequantised to bf16
+    keep_q4 = tpn == 1 and os.environ.get("OGB_DEQUANT_INT4_AT_LOAD", "0") != "1"
     if arch.num_heads % tpn or (arch.num_kv_heads % tpn and tpn % arch.num_kv_heads):
         raise ValueError(f"tensor parallel degree {tpn} does not divide the attention heads")
     if arch.num_kv_heads < tpn:
@@ -230,8 +254,11 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         # attention projections: packed or separate
         qkv = linear_node(f"{n}/attn/", "qkv_proj")
         if qkv is not None:
-            w = _linear_weight(g, qkv, dtype, device)
-            lw.qkv_w = shard_rows(w, [q_rows, k_rows, v_rows])
+            if keep_q4 and _is_q4([qkv]):
+                lw.qkv_w = _q4_weight(g, [qkv], device)
+            else:
+                w = _linear_weight(g, qkv, dtype, device)
+                lw.qkv_w = shard_rows(w, [q_rows, k_rows, v_rows])
             badd = g.by_name.get(f"{n}/attn/qkv_proj/Add")
             if badd is not None:
                 b = g.tensor(badd.inputs[1])
@@ -250,7 +277,10 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
             lw.qkv_w = torch.cat(ws, 0).contiguous()
             lw.qkv_b = torch.cat(bs, 0).contiguous() if bs else None
         o = linear_node(f"{n}/attn/", "o_proj")
-        lw.o_w = _linear_weight(g, o, dtype, device, cols=slice(tpr * hq_l * D, (tpr + 1) * hq_l * D) if tpn > 1 else None)
+        if keep_q4 and _is_q4([o]):
+            lw.o_w = _q4_weight(g, [o], device)
+        else:
+            lw.o_w = _linear_weight(g, o, dtype, device, cols=slice(tpr * hq_l * D, (tpr + 1) * hq_l * D) if tpn > 1 else None)
         oadd = g.by_name.get(f"{n}/attn/o_proj/Add")
         if oadd is not None:
             lw.o_b = _vec(g, oadd.inputs[1], dtype, device)
@@ -284,7 +314,16 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         else:
             gu = linear_node(f"{n}/mlp/", "gate_up_proj")
             g_rows, u_rows = slice(tpr * i_l, (tpr + 1) * i_l), slice(I + tpr * i_l, I + (tpr + 1) * i_l)
-            if gu is not None:
+            if gu is not None and keep_q4 and _is_q4([gu]):
+                il = arch.activation == "silu" and I % 64 == 0
+                lw.gate_up_w = _q4_weight(g, [gu], device, interleave=il)
+                lw.gate_up_interleaved = il
+                badd = g.by_name.get(f"{n}/mlp/gate_up_proj/Add")
+                if badd is not None:
+                    b = g.tensor(badd.inputs[1])
+                    from ..ops import interleave_gate_up as _il
+                    lw.gate_up_b = (_il(b) if il else b).to(device=device, dtype=dtype)
+            elif gu is not None:
                 w = _linear_weight(g, gu, dtype, device)
                 lw.gate_up_w = shard_rows(w, [g_rows, u_rows])
                 badd = g.by_name.get(f"{n}/mlp/gate_up_proj/Add")
@@ -294,14 +333,18 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                 gw = _linear_weight(g, linear_node(f"{n}/mlp/", "gate_proj"), dtype, device, rows=g_rows if tpn > 1 else None)
                 uw = _linear_weight(g, linear_node(f"{n}/mlp/", "up_proj"), dtype, device, rows=g_rows if tpn > 1 else None)
                 lw.gate_up_w = torch.cat([gw, uw], 0).contiguous()
-            if torch.device(device).type == "cuda" and arch.activation == "silu" and (lw.gate_up_w.shape[0] // 2) % 64 == 0:
+            if (isinstance(lw.gate_up_w, torch.Tensor) and torch.device(device).type == "cuda" and arch.activation == "silu"
+                    and (lw.gate_up_w.shape[0] // 2) % 64 == 0):
                 from ..ops import interleave_gate_up
                 lw.gate_up_w = interleave_gate_up(lw.gate_up_w)
                 if lw.gate_up_b is not None:
                     lw.gate_up_b = interleave_gate_up(lw.gate_up_b)
                 lw.gate_up_interleaved = True
             dn = linear_node(f"{n}/mlp/", "down_proj")
-            lw.down_w = _linear_weight(g, dn, dtype, device, cols=g_rows if tpn > 1 else None)
+            if keep_q4 and _is_q4([dn]):
+                lw.down_w = _q4_weight(g, [dn], device)
+            else:
+                lw.down_w = _linear_weight(g, dn, dtype, device, cols=g_rows if tpn > 1 else None)
             dadd = g.by_name.get(f"{n}/mlp/down_proj/Add")
             if dadd is not None:
                 lw.down_b = _vec(g, dadd.inputs[1], dtype, device)
@@ -319,7 +362,10 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         model.vocab_shard = (rows.start, rows.stop, per)
     else:
         rows = None
-    model.lm_head_w = _linear_weight(g, head, dtype, device, rows=rows)
+    if keep_q4 and _is_q4([head]):
+        model.lm_head_w = _q4_weight(g, [head], device)
+    else:
+        model.lm_head_w = _linear_weight(g, head, dtype, device, rows=rows)
     hadd = g.by_name.get("/lm_head/Add")
     if hadd is not None:
         model.lm_head_b = _vec(g, hadd.inputs[1], dtype, device, rows)

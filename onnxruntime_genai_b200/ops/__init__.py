@@ -14,6 +14,7 @@ import torch
 
 from . import reference as ref
 from . import _lib
+from .w4 import W4Weight, unpack_ort_q4
 
 _ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1}
 
@@ -109,9 +110,26 @@ def _gemm(x, w, out, bias, residual, flags, splits):
     return out
 
 
+def _gemm_w4(x, w, out, bias, residual, flags, splits):
+    ws = workspace(x.device)
+    rc = _lib.lib().ogb_gemm_w4(_ptr(x), x.stride(0), _ptr(w.packed), _ptr(out), out.stride(0), x.shape[0], w.N, w.K, _ptr(bias),
+                                _ptr(residual), residual.stride(0) if residual is not None else 0, int(flags), int(splits),
+                                ws.status, ws.sm_count, _stream())
+    _lib.check(rc, "gemm_w4")
+    return out
+
+
 def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False):
     """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous).  With all_reduce the
     partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory."""
+    if isinstance(w, W4Weight):
+        if not x.is_cuda:
+            return ref.linear(x, w.dequantize(), bias, residual, out_fp32)
+        if all_reduce:
+            raise RuntimeError("the fused all-reduce is not available for int4 weights")
+        if out is None:
+            out = torch.empty(x.shape[0], w.N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+        return _gemm_w4(x, w, out, bias, residual, GEMM_FP32_OUT if out_fp32 else 0, splits)
     if not x.is_cuda:
         return ref.linear(x, w, bias, residual, out_fp32)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -134,6 +152,18 @@ def interleave_gate_up(w: torch.Tensor, block: int = 64) -> torch.Tensor:
 def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False):
     """act(x @ Wg.T) * (x @ Wu.T).  w is [2I, K]: stacked [Wg; Wu], or (interleaved=True) blocks of 64 gate
     rows + 64 up rows as produced by interleave_gate_up (the layout the fused kernel needs)."""
+    if isinstance(w, W4Weight):
+        if not x.is_cuda:
+            return ref.gate_up_act(x, w.dequantize(), bias, act, w.interleaved)
+        inter = w.N // 2
+        if act == "silu" and w.interleaved:
+            if out is None:
+                out = torch.empty(x.shape[0], inter, dtype=torch.bfloat16, device=x.device)
+            return _gemm_w4(x, w, out, bias, None, GEMM_ACT_PAIR, splits)
+        y = linear(x, w, bias)
+        if w.interleaved:
+            y = y.view(-1, inter // 64, 2, 64).transpose(1, 2).reshape(-1, 2 * inter)
+        return act_mul(y.contiguous(), act)
     if not x.is_cuda:
         return ref.gate_up_act(x, w, bias, act, interleaved)
     inter = w.shape[0] // 2

@@ -25,6 +25,8 @@ _SIGS = {
     "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P]),
     "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, _P, c_longlong, c_int]),
+    "ogb_w4_packed_bytes": (c_longlong, [c_int, c_int]),
+    "ogb_gemm_w4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P]),
     "ogb_embedding": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
     "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,

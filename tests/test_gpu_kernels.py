@@ -327,3 +327,52 @@ def test_logits_mask_and_edit():
     ops.logits_edit(x, r.to(DEV), t.to(DEV), o.to(DEV), v.to(DEV))
     ref.logits_edit(xr, r, t, o, v)
     _close(x, xr, rtol=1e-6, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------- int4 dequant GEMM
+def _w4_case(N, K, seed, symmetric=False):
+    from onnxruntime_genai_b200.models.builder import quantize_int4_block32
+    from onnxruntime_genai_b200.ops.w4 import W4Weight, unpack_ort_q4
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g) * 0.05
+    qw, s, zp = quantize_int4_block32(w, symmetric=symmetric)
+    q, z = unpack_ort_q4(qw, zp, N, K)
+    return W4Weight.from_quantized(q, s.to(torch.float16).float(), z, DEV), w
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (5, 3072, 3072, 0), (64, 1000, 512, 1), (16, 256, 4096, 4), (130, 384, 256, 1),
+                                          (300, 512, 1024, 1), (33, 9216, 3072, 0)])
+def test_gemm_w4_matches_dequantised_fp32(M, N, K, splits):
+    w4, w = _w4_case(N, K, seed=50)
+    x = _rand(M, K, seed=51)
+    y = ops.linear(x, w4, splits=splits)
+    ops.check_kernel_status()
+    want = ref.linear(x.cpu(), w4.dequantize())
+    _close(y, want, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.05)
+    assert (w4.dequantize() - w).abs().max() < 0.02, "the kernel-side dequantisation formula stays close to the original weights"
+
+
+def test_gemm_w4_epilogues_and_symmetric():
+    w4, _ = _w4_case(512, 256, seed=52, symmetric=True)
+    x, bias, res = _rand(20, 256, seed=53), _rand(512, seed=54), _rand(20, 512, seed=55)
+    y = ops.linear(x, w4, bias=bias, residual=res)
+    _close(y, ref.linear(x.cpu(), w4.dequantize(), bias.cpu(), res.cpu()), rtol=2e-2, atol=0.05)
+    y32 = ops.linear(x, w4, out_fp32=True)
+    _close(y32, ref.linear(x.cpu(), w4.dequantize(), out_fp32=True), rtol=1e-2, atol=0.02)
+    ops.check_kernel_status()
+
+
+def test_gemm_w4_gate_up_pair():
+    from onnxruntime_genai_b200.models.builder import quantize_int4_block32
+    from onnxruntime_genai_b200.ops.w4 import W4Weight, unpack_ort_q4
+    I, K, M = 256, 512, 24
+    w = torch.randn(2 * I, K, generator=torch.Generator().manual_seed(56)) * 0.05
+    qw, s, zp = quantize_int4_block32(w)
+    q, z = unpack_ort_q4(qw, zp, 2 * I, K)
+    plain = W4Weight.from_quantized(q, s, z, DEV)
+    il = W4Weight.from_quantized(ops.interleave_gate_up(q), ops.interleave_gate_up(s), ops.interleave_gate_up(z), DEV, interleaved=True)
+    x = _rand(M, K, seed=57)
+    want = ref.gate_up_act(x.cpu(), plain.dequantize())
+    _close(ops.gate_up_act(x, il), want, rtol=3e-2, atol=0.05)
+    _close(ops.gate_up_act(x, plain), want, rtol=3e-2, atol=0.05)
+    ops.check_kernel_status()
