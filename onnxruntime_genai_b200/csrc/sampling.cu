@@ -70,32 +70,43 @@ __device__ void radix_select(const RowCtx& c, SelectShared& sh, unsigned long lo
     for (int b = tid; b < nwarps * 256; b += blockDim.x) priv[b] = 0;
     __syncthreads();
     const uint32_t prefix = sh.prefix, mask = sh.mask;
-    for (int base = 0; base < c.n; base += blockDim.x) {
-      const int i = base + tid;
-      uint32_t bin = 0xFFFFFFFFu;
-      unsigned long long w = 0;
-      if (i < c.n) {
-        const float v = c.x[i];
-        const uint32_t key = to_key(v);
-        if ((key & mask) == prefix && c.in_k(i, key)) {
-          w = MASS ? c.mass(v) : 1ull;
-          if (w) bin = (key >> shift) & 255;
-        }
+    // The row is read in batches of UNR independent loads per thread: one trip to L2 per batch, not per element.
+    constexpr int UNR = 8;
+    for (int base = 0; base < c.n; base += UNR * blockDim.x) {
+      float vals[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        vals[u] = i < c.n ? c.x[i] : 0.f;
       }
-      if (!__any_sync(0xffffffffu, bin != 0xFFFFFFFFu)) continue;  // later passes: most warps see no candidate
-      const unsigned grp = __match_any_sync(0xffffffffu, bin);
-      if (bin != 0xFFFFFFFFu) {
-        unsigned long long sum;
-        if (MASS) {
-          const unsigned lo = __reduce_add_sync(grp, unsigned(w & 0xFFFFFu));
-          const unsigned hi = __reduce_add_sync(grp, unsigned(w >> 20));
-          sum = ((unsigned long long)hi << 20) + lo;
-        } else {
-          sum = __popc(grp);
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        uint32_t bin = 0xFFFFFFFFu;
+        unsigned long long w = 0;
+        if (i < c.n) {
+          const float v = vals[u];
+          const uint32_t key = to_key(v);
+          if ((key & mask) == prefix && c.in_k(i, key)) {
+            w = MASS ? c.mass(v) : 1ull;
+            if (w) bin = (key >> shift) & 255;
+          }
         }
-        if (lane == __ffs(grp) - 1) mine[bin] += sum;
+        if (!__any_sync(0xffffffffu, bin != 0xFFFFFFFFu)) continue;  // later passes: most warps see no candidate
+        const unsigned grp = __match_any_sync(0xffffffffu, bin);
+        if (bin != 0xFFFFFFFFu) {
+          unsigned long long sum;
+          if (MASS) {
+            const unsigned lo = __reduce_add_sync(grp, unsigned(w & 0xFFFFFu));
+            const unsigned hi = __reduce_add_sync(grp, unsigned(w >> 20));
+            sum = ((unsigned long long)hi << 20) + lo;
+          } else {
+            sum = __popc(grp);
+          }
+          if (lane == __ffs(grp) - 1) mine[bin] += sum;
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
     __syncthreads();
     for (int b = tid; b < 256; b += blockDim.x) {
@@ -295,12 +306,21 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
     int* si = reinterpret_cast<int*>(sv + SMALL_K);        // sorted indices
     if (tid == 0) cand_n = 0;
     __syncthreads();
-    for (int i = tid; i < n; i += blockDim.x) {
-      const float v = x[i];
-      const uint32_t key = to_key(v);
-      if (key > T || (key == T && i <= cut)) {
-        const int slot = atomicAdd(&cand_n, 1);
-        if (slot < SMALL_K) { cv[slot] = v; ci[slot] = i; }
+    for (int base = 0; base < n; base += 8 * blockDim.x) {
+      float vals[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        vals[u] = i < n ? x[i] : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        const uint32_t key = to_key(vals[u]);
+        if (i < n && (key > T || (key == T && i <= cut))) {
+          const int slot = atomicAdd(&cand_n, 1);
+          if (slot < SMALL_K) { cv[slot] = vals[u]; ci[slot] = i; }
+        }
       }
     }
     __syncthreads();
@@ -531,9 +551,18 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* logit
   const float* x = logits + size_t(row) * row_stride;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < n; i += blockDim.x) {
-    const float v = x[i];
-    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  for (int base = 0; base < n; base += 8 * blockDim.x) {   // 8 independent loads per thread and trip
+    float vals[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      vals[u] = i < n ? x[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      if (i < n && (vals[u] > bv || (vals[u] == bv && i < bi))) { bv = vals[u]; bi = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
