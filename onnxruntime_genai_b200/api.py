@@ -255,6 +255,58 @@ class SequenceState:
                        max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds)
         return self.decoder.forward(s, self.kv), rows_used
 
+    # ---- single-token decode steps replayed from CUDA graphs (one graph per power-of-two bound on the KV length)
+    def graph_ok(self) -> bool:
+        dec = self.decoder
+        if dec.device.type != "cuda" or os.environ.get("OGB_GENERATOR_GRAPH", "1") == "0":
+            return False
+        if dec.arch.num_experts > 0 and not all(lw.exp_blocked for lw in dec.layers):
+            return False   # the unfused expert loop reads counts back to the host
+        return dec.tp.size == 1
+
+    def run_decode_graph(self, last_tokens: List[int]) -> torch.Tensor:
+        """One token per row through a captured forward.  Returns the (static) fp32 logits buffer [rows, vocab]."""
+        dev = self.decoder.device
+        R = self.rows
+        cap = self.blocks_per_row * self.block_size
+        if max(self.kv_len) + 1 > cap:
+            raise RuntimeError("sequence exceeds the allocated KV cache (max_length)")
+        if not hasattr(self, "_g_host"):
+            self._g_host = torch.empty(4 * R, dtype=torch.int32).pin_memory()
+            self._g_dev = torch.empty(4 * R, dtype=torch.int32, device=dev)
+            self._g_cu = torch.arange(R + 1, dtype=torch.int32, device=dev)
+            self._g_rows = torch.arange(R, dtype=torch.int32, device=dev)
+            self._g_np = self._g_host.numpy()
+            self._g_pool = torch.cuda.graph_pool_handle()
+            self._graphs: Dict[Any, Any] = {}
+        h = self._g_np
+        span = cap
+        for r in range(R):
+            p = self.kv_len[r]
+            h[r], h[R + r], h[2 * R + r], h[3 * R + r] = int(last_tokens[r]), p, r * span + p, p
+        self._g_dev.copy_(self._g_host, non_blocking=True)
+        bound = 256
+        while bound < max(self.kv_len) + 1:
+            bound *= 2
+        bound = min(bound, cap)
+        key = (bound, self.decoder.active_adapter)
+        d = self._g_dev
+        if key not in self._graphs:
+            s = StepInputs(input_ids=d[:R], positions=d[R:2 * R], slot_mapping=d[2 * R:3 * R], cu_seqlens=self._g_cu, past_lens=d[3 * R:],
+                           block_table=self.block_table, logits_rows=self._g_rows, max_q_len=1, max_kv_len=bound)
+            with torch.no_grad():
+                self.decoder.forward(s, self.kv)   # warm-up: allocator, tensor maps, scratch
+                torch.cuda.synchronize(dev)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=self._g_pool):   # graphs are replayed one at a time: they may share memory
+                    out = self.decoder.forward(s, self.kv)
+            self._graphs[key] = (g, out)
+        g, out = self._graphs[key]
+        g.replay()
+        for r in range(R):
+            self.kv_len[r] += 1
+        return out
+
     def rewind(self, row: int, length: int):
         self.kv_len[row] = min(self.kv_len[row], length)
 
@@ -375,6 +427,8 @@ class Generator:
                     if logits is None:
                         logits = torch.empty(self.rows, out.shape[1], dtype=torch.float32, device=out.device)
                     logits[used] = out
+            elif all(len(t) == 1 for t in row_tokens) and self._started and self.state.graph_ok():
+                logits = self.state.run_decode_graph([t[0] for t in row_tokens])
             else:
                 logits, used = self.state.run(row_tokens)
                 if len(used) != self.rows:

@@ -1,0 +1,126 @@
+// Stand-alone collectives over the symmetric NVLink buffers (the same buffers, arrival stamps and call
+// counter as the all-reduce fused into the GEMM epilogue, gemm_common.cuh): one-shot all-reduce,
+// all-gather and reduce-scatter for bf16 tensors that did not come out of a fused GEMM, e.g. the
+// expert-parallel combine or the logits gather.  The reference has no communication layer; the bar these
+// are measured against is the NCCL call of the same name.
+//
+// Every block owns one contiguous chunk of the payload and one arrival slot:
+//   all-reduce      push chunk to every rank (plane = source rank) | stamp | wait | out = sum over planes
+//   all-gather      push chunk to every rank (plane = source rank) | stamp | wait | out[s * n + i] = plane s
+//   reduce-scatter  push chunk of slice j to rank j only           | stamp | wait | out = sum over planes
+// Transfers are plain 16-byte peer stores; waits are bounded (status word, then the kernel finishes without
+// hanging); the last block closes the call's epoch.  No multimem / NVLS: ranks may leave between steps.
+#include "gemm_common.cuh"
+#include "kernels.h"
+
+namespace ogb {
+
+enum CollMode { COLL_ALLREDUCE = 0, COLL_ALLGATHER = 1, COLL_REDUCE_SCATTER = 2 };
+
+constexpr int COLL_THREADS = 256;
+
+// n: elements per rank plane (all-reduce: tensor size; all-gather: shard size; reduce-scatter: output slice size).
+template <int MODE>
+__global__ void __launch_bounds__(COLL_THREADS)
+collective_kernel(const CommParams c, const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                  const __nv_bfloat16* __restrict__ residual, long long n, int* status) {
+  __shared__ uint32_t epoch_sh;
+  const int tid = threadIdx.x;
+  if (tid == 0) epoch_sh = *reinterpret_cast<volatile uint32_t*>(c.epoch);
+  __syncthreads();
+  const uint32_t e = epoch_sh;
+  const size_t plane = size_t(c.plane_elems);
+  const size_t par_off = size_t(e & 1) * c.world * plane;
+  const long long vecs = n / 8;
+  const long long per = (vecs + gridDim.x - 1) / gridDim.x;
+  const long long v0 = blockIdx.x * per, v1 = min(vecs, v0 + per);
+
+  // ---- push
+  for (long long v = v0 + tid; v < v1; v += COLL_THREADS) {
+    const size_t off = par_off + size_t(c.rank) * plane + size_t(v) * 8;
+    if (MODE == COLL_REDUCE_SCATTER) {
+      for (int r = 0; r < c.world; ++r)
+        *reinterpret_cast<uint4*>(c.buf[r] + off) = *reinterpret_cast<const uint4*>(in + size_t(r) * n + size_t(v) * 8);
+    } else {
+      const uint4 q = *reinterpret_cast<const uint4*>(in + size_t(v) * 8);
+      for (int r = 0; r < c.world; ++r) *reinterpret_cast<uint4*>(c.buf[r] + off) = q;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  // ---- stamp and wait: lane r handles rank r
+  if (tid < c.world) {
+    st_release_sys(c.flag[tid] + size_t(blockIdx.x) * COMM_MAX_WORLD + c.rank, e + 1);
+    const uint32_t* mine = c.flag[c.rank] + size_t(blockIdx.x) * COMM_MAX_WORLD + tid;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    const bool poisoned = *reinterpret_cast<volatile int*>(status) != 0;
+    while (!poisoned && int32_t(ld_acquire_sys(mine) - (e + 1)) < 0) {
+      if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 2000000000ull) { atomicMax(status, OGB_ERR_WAIT_PEER); break; }
+    }
+  }
+  __syncthreads();
+  // ---- combine from the local receive buffer
+  const __nv_bfloat16* base = c.buf[c.rank] + par_off;
+  for (long long v = v0 + tid; v < v1; v += COLL_THREADS) {
+    if (MODE == COLL_ALLGATHER) {
+      for (int r = 0; r < c.world; ++r)
+        *reinterpret_cast<uint4*>(out + size_t(r) * n + size_t(v) * 8) = ld_cg_u4(base + size_t(r) * plane + size_t(v) * 8);
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (residual) {
+        const uint4 q = *reinterpret_cast<const uint4*>(residual + size_t(v) * 8);
+        const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), cc = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+        acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = cc.x; acc[5] = cc.y; acc[6] = d.x; acc[7] = d.y;
+      }
+      for (int r = 0; r < c.world; ++r) {   // rank order: bit-identical on every rank
+        const uint4 q = ld_cg_u4(base + size_t(r) * plane + size_t(v) * 8);
+        const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), cc = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
+      }
+      *reinterpret_cast<uint4*>(out + size_t(v) * 8) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+  // ---- close the epoch
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(c.epoch + 1, 1u) == gridDim.x - 1) {
+      c.epoch[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(c.epoch) = e + 1;
+    }
+  }
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+// mode 0 all-reduce (in/out n elements), 1 all-gather (in n, out world * n), 2 reduce-scatter (in world * n, out n).
+// n must be a multiple of 8 and at most the registered plane size; pointers 16-byte aligned.  residual (modes 0, 2) is
+// added to the sum.  Uses the symmetric buffers registered for `device` with ogb_comm_register.
+OGB_API int ogb_collective(int mode, const void* in, void* out, const void* residual, long long n, int device, int* status,
+                           int sm_count, void* stream_) {
+  const CommParams* cp = ogb_comm_params(device);
+  if (!cp || cp->world < 1 || !cp->buf[0]) return -2;
+  if (n <= 0) return 0;
+  if ((n % 8) || n > cp->plane_elems) return -1;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15) return -1;
+  long long blocks = (n / 8 + COLL_THREADS * 4 - 1) / (COLL_THREADS * 4);   // ~4 vectors per thread
+  const long long cap = sm_count * 2 < cp->max_slots ? sm_count * 2 : cp->max_slots;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const __nv_bfloat16* i = static_cast<const __nv_bfloat16*>(in);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  const __nv_bfloat16* r = static_cast<const __nv_bfloat16*>(residual);
+  switch (mode) {
+    case COLL_ALLREDUCE: collective_kernel<COLL_ALLREDUCE><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, o, r, n, status); break;
+    case COLL_ALLGATHER: collective_kernel<COLL_ALLGATHER><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, o, nullptr, n, status); break;
+    case COLL_REDUCE_SCATTER: collective_kernel<COLL_REDUCE_SCATTER><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, o, r, n, status); break;
+    default: return -1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -15,28 +15,48 @@ constexpr int GEMM_THREADS = 192;
 constexpr int W_TILE_BYTES = GEMM_BLOCK_N * GEMM_BLOCK_K * 2;  // 16 KiB
 constexpr int COMM_MAX_WORLD = 8;
 
+// Symmetric buffers of the fused all-reduce.  All fused calls of a device form one sequence numbered by a device-side
+// epoch (the same sequence on every rank): call e writes parity e & 1 of the receive buffers and stamps its arrival
+// flags with e + 1.  A rank cannot start call e + 2 (which reuses the parity of call e) before it has finished call e + 1,
+// i.e. before every peer has arrived at every slice of call e + 1 and therefore finished reading call e: the scheme
+// needs no second barrier and does not depend on how a call maps slices to CTAs.
 struct CommParams {
   int world, rank;                        // world <= 1 with buf[0] == nullptr disables the fused all-reduce
   __nv_bfloat16* buf[COMM_MAX_WORLD];     // receive buffer of every rank: [2 parities][world sources][plane_elems]
-  uint32_t* flag[COMM_MAX_WORLD];         // arrival counters of every rank: [max_slots]
-  uint32_t* uses;                         // this rank's use count per slot
+  uint32_t* flag[COMM_MAX_WORLD];         // arrival stamps of every rank: [max_slots][COMM_MAX_WORLD sources]
+  uint32_t* epoch;                        // this rank: [0] = calls finished so far, [1] = CTAs of the running call that are done
   long long plane_elems;
   int max_slots;
 };
 
+// Registered symmetric buffers of a device (gemm_tcgen05.cu); nullptr when the index is out of range.
+const CommParams* ogb_comm_params(int device);
+
+// Grouped (mixture-of-experts) mode: the token rows are sorted by expert and blockIdx.y walks a device-built
+// list of token tiles, each inside one expert's row range; the weight is [experts * N, K].
+struct GroupParams {
+  const int* tile_expert;   // nullptr: not grouped
+  const int* tile_row0;     // first (sorted) token row of the tile
+  const int* tile_rows;     // rows of the tile that belong to its expert (<= token tile)
+  const int* num_tiles;     // device scalar: tiles in use; CTAs beyond it return at once
+};
+
 struct GemmParams {
-  int M, N, K;          // N = weight rows
+  int M, N, K;          // N = weight rows (per expert when grouped)
   int splits, kb_per_split, total_kb;
   void* C;
   int ldc;
   int out_fp32;
-  int act_pair;         // 1: tiles hold 64 gate rows + 64 up rows; output silu(gate)*up with N/2 columns
+  int act_pair;         // tiles hold 64 gate rows + 64 up rows, output has N/2 columns: 1 = silu(gate)*up,
+                        // 2 = clamped SwiGLU: g = min(gate, limit), u = clamp(up, +-limit), g*sigmoid(alpha*g)*(u+1)
+  float act_alpha, act_limit;
   const __nv_bfloat16* residual;
   int ldr;
   const __nv_bfloat16* bias;
   int* status;
   int pdl;
   CommParams comm;
+  GroupParams grp;
 };
 
 template <int BT>
@@ -74,8 +94,8 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -92,7 +112,8 @@ __device__ __forceinline__ uint4 ld_cg_u4(const void* p) {  // bypass L1: the da
 // committed the last k-block to `accum_bar`; `smem` is the (idle) pipeline memory, reused for the fp32 tile.
 template <int BT>
 __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem, uint32_t tmem_base, uint64_t* accum_bar,
-                                              volatile int* abort_flag, volatile uint32_t* use_slot, int n_tile, int m_tile) {
+                                              volatile int* abort_flag, volatile uint32_t* use_slot, int n_tile, int m_tile,
+                                              int row0, int rows, int bias_off) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
   // -------------------------------------------------------------------- epilogue (warps 2..5)
@@ -154,7 +175,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     auto add_bias8 = [&](int n_glob, float (&v)[8]) {
       if (!p.bias) return;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) if (n_glob + j < p.N) v[j] += bf2f(p.bias[n_glob + j]);
+      for (int j = 0; j < 8; ++j) if (n_glob + j < p.N) v[j] += bf2f(p.bias[bias_off + n_glob + j]);
     };
     auto store8 = [&](int m, int col, float (&v)[8]) {  // residual add + store of one 8-wide segment
       if (p.residual) {
@@ -181,11 +202,12 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
       }
     };
 
-    uint32_t use = 0;
+    uint32_t use = 0;   // epoch of this call
     int slot = 0;
     if (comm_on) {
       slot = (m_tile * gridDim.x + n_tile) * gridDim.z + my_rank;
-      if (et == 0) *use_slot = p.comm.uses[slot];
+      // read after griddepcontrol.wait: the previous call has finished and published its increment
+      if (et == 0) *use_slot = *reinterpret_cast<volatile uint32_t*>(p.comm.epoch);
       asm volatile("bar.sync 1, 128;" ::: "memory");
       use = *use_slot;
     }
@@ -194,8 +216,8 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
 
     for (int item = et; item < items; item += 128) {
       const int mc = c_begin + item / OCT, oc = item % OCT;
-      const int m = m_tile * BT + mc;
-      if (m >= p.M) continue;
+      const int m = row0 + mc;
+      if (mc >= rows) continue;
       float v[8];
       if (p.act_pair) {
         float u[8];
@@ -203,8 +225,17 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         reduce8(mc, 64 + oc * 8, u);
         add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
         add_bias8(n_tile * GEMM_BLOCK_N + 64 + oc * 8, u);
+        if (p.act_pair == 1) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = silu(v[j]) * u[j];
+          for (int j = 0; j < 8; ++j) v[j] = silu(v[j]) * u[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float g = p.act_limit > 0.f ? fminf(v[j], p.act_limit) : v[j];
+            const float w = p.act_limit > 0.f ? fminf(fmaxf(u[j], -p.act_limit), p.act_limit) : u[j];
+            v[j] = g / (1.f + __expf(-p.act_alpha * g)) * (w + 1.f);
+          }
+        }
       } else {
         reduce8(mc, oc * 8, v);
         add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
@@ -223,26 +254,25 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     if (comm_on) {
       __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        for (int r = 0; r < p.comm.world; ++r) red_add_release_sys(p.comm.flag[r] + slot, 1u);
-        const uint32_t target = uint32_t(p.comm.world) * (use + 1);
-        const uint32_t* mine = p.comm.flag[p.comm.rank] + slot;
+      if (et < p.comm.world) {
+        // lane r: stamp this rank's arrival on rank r, then wait for rank r's stamp here
+        st_release_sys(p.comm.flag[et] + size_t(slot) * COMM_MAX_WORLD + p.comm.rank, use + 1);
+        const uint32_t* mine = p.comm.flag[p.comm.rank] + size_t(slot) * COMM_MAX_WORLD + et;
         const uint64_t t0 = global_timer_ns();
         uint32_t spins = 0;
         // Once any kernel of this device has reported a failed wait, later kernels do not wait again: a broken
         // peer (or a broken set-up) then costs one time limit in total, not one per launch.
         const bool poisoned = *reinterpret_cast<volatile int*>(p.status) != 0;
-        while (!poisoned && int32_t(ld_acquire_sys(mine) - target) < 0) {
-          if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 5000000000ull) { fail(OGB_ERR_WAIT_PEER); break; }
+        while (!poisoned && int32_t(ld_acquire_sys(mine) - (use + 1)) < 0) {
+          if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 2000000000ull) { fail(OGB_ERR_WAIT_PEER); break; }
         }
-        p.comm.uses[slot] = use + 1;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       for (int item = et; item < items; item += 128) {
         const int mc = c_begin + item / OCT, oc = item % OCT;
-        const int m = m_tile * BT + mc;
+        const int m = row0 + mc;
         const int col = col0 + oc * 8;
-        if (m >= p.M || col >= n_out) continue;
+        if (mc >= rows || col >= n_out) continue;
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         const __nv_bfloat16* base = p.comm.buf[p.comm.rank] + par_off + size_t(m) * n_out + col;
         for (int r = 0; r < p.comm.world; ++r) {
@@ -257,6 +287,19 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
   if (p.splits > 1) {
     __syncwarp();
     cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
+  }
+  if (p.comm.buf[0] != nullptr) {
+    // The last CTA of the call to get here closes the epoch (every CTA passes this point, also after an abort).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+      if (atomicAdd(p.comm.epoch + 1, 1u) == total - 1) {
+        p.comm.epoch[1] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(p.comm.epoch) = *reinterpret_cast<volatile uint32_t*>(p.comm.epoch) + 1;
+      }
+    }
   }
 
 }

@@ -28,11 +28,11 @@
 //
 // Tensor-parallel all-reduce (row-parallel o_proj / down_proj in decode), fused: instead of
 // storing its reduced slice, a CTA pushes it (bf16) into the receive buffer of EVERY rank with
-// plain peer stores over NVLink, adds one to that slice's arrival counter on every rank
-// (red.release.sys), waits (bounded) until its own counter shows all ranks' arrivals, then sums
+// plain peer stores over NVLink, stamps that slice's arrival flag on every rank
+// (st.release.sys), waits (bounded) until its own flags show all ranks' arrivals, then sums
 // the world's partials from its local buffer in rank order (bit-identical on every rank), adds
-// the residual and stores.  Counters only grow and buffers alternate by the parity of a per-slice
-// use count kept on the device, so the kernel replays unchanged inside CUDA graphs.  The
+// the residual and stores.  Arrival stamps only grow and buffers alternate by the parity of a call
+// counter kept on the device, so the kernel replays unchanged inside CUDA graphs.  The
 // reference has no distributed code at all; the comparison bar is GEMM + ncclAllReduce.
 //
 // Every wait is bounded: when one runs out the kernel records a status code, waits (bounded) for
@@ -64,6 +64,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
   const int kb0 = split * p.kb_per_split;
   const int num_kb = min(p.kb_per_split, p.total_kb - kb0);
+  // Grouped mode: the tile list is written by the kernel before this one, so nothing is read ahead of it.
+  const bool grouped = p.grp.tile_expert != nullptr;
+  int row0 = m_tile * BT, rows = min(BT, p.M - row0), w_row0 = 0;
+  if (grouped) {
+    if (p.pdl) pdl_wait();
+    if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA and over its split-K cluster
+    row0 = p.grp.tile_row0[m_tile];
+    rows = p.grp.tile_rows[m_tile];
+    w_row0 = p.grp.tile_expert[m_tile] * p.N;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -93,10 +103,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       auto load_w = [&](int i) {
         const int s = i % STAGES;
         mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        tma_load_2d(stage_w(s), &tmap_w, &full_bar[s], (kb0 + i) * GEMM_BLOCK_K, n_tile * GEMM_BLOCK_N);
+        tma_load_2d(stage_w(s), &tmap_w, &full_bar[s], (kb0 + i) * GEMM_BLOCK_K, w_row0 + n_tile * GEMM_BLOCK_N);
       };
       auto load_a = [&](int i) {
-        tma_load_2d(stage_a(i % STAGES), &tmap_a, &full_bar[i % STAGES], (kb0 + i) * GEMM_BLOCK_K, m_tile * BT);
+        tma_load_2d(stage_a(i % STAGES), &tmap_a, &full_bar[i % STAGES], (kb0 + i) * GEMM_BLOCK_K, row0);
       };
       // Weights are never written by an earlier kernel of the stream: fill the pipeline with them
       // before waiting for the producer of the activations.
@@ -141,7 +151,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     }
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile);
+  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0);
 
   tc_fence_before();
   __syncthreads();
@@ -244,6 +254,10 @@ using namespace ogb;
 // Per-device registration of the symmetric buffers used by the fused all-reduce.
 static CommParams g_comm[16] = {};
 
+namespace ogb {
+const CommParams* ogb_comm_params(int device) { return (device >= 0 && device < 16) ? &g_comm[device] : nullptr; }
+}  // namespace ogb
+
 OGB_API int ogb_gemm_token_tile(int M, int dual) {
   (void)dual;
   if (M <= 16) return 16;
@@ -271,8 +285,8 @@ OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
 
 // Registers this rank's view of the symmetric buffers (peer-mapped pointers) for a device.
 // buf[r] / flag[r]: rank r's receive buffer / arrival counters as mapped into this process;
-// uses: a local zero-initialised array of max_slots counters.  world = 0 unregisters.
-OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* uses, long long plane_elems,
+// ([max_slots][8] words, zero-initialised); epoch: two local zero-initialised words.  world = 0 unregisters.
+OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* epoch, long long plane_elems,
                               int max_slots) {
   if (device < 0 || device >= 16 || world < 0 || world > COMM_MAX_WORLD) return -1;
   CommParams c = {};
@@ -281,7 +295,7 @@ OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void*
     c.buf[r] = static_cast<__nv_bfloat16*>(buf[r]);
     c.flag[r] = static_cast<uint32_t*>(flag[r]);
   }
-  c.uses = static_cast<uint32_t*>(uses);
+  c.epoch = static_cast<uint32_t*>(epoch);
   g_comm[device] = c;
   return 0;
 }
@@ -328,6 +342,48 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     p.comm = c;
   }
   dim3 grid(n_tiles, m_tiles, splits);
+  switch (bt) {
+    case 16: return Launch<16>(tw, ta, p, grid, stream);
+    case 32: return Launch<32>(tw, ta, p, grid, stream);
+    case 64: return Launch<64>(tw, ta, p, grid, stream);
+    case 128: return Launch<128>(tw, ta, p, grid, stream);
+    case 256: return Launch<256>(tw, ta, p, grid, stream);
+  }
+  return -5;
+}
+
+// Grouped expert GEMM (mixture of experts): A holds `rows_total` token rows sorted by expert, W is
+// [experts * N, K], the device-built tile list (ogb_moe_sort) gives for every token tile its expert, first
+// row and row count.  C[row, :] = A[row, :] * W[expert(row)]^T (+ bias[expert]) (+ paired activation).
+// `token_tile` must be the tile size the list was built for; `max_tiles` bounds the list length (the grid).
+// flags bit 1: paired activation; act_kind selects it (1 = silu(gate)*up, 2 = clamped SwiGLU(alpha, limit)).
+OGB_API int ogb_moe_gemm(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int rows_total, int N, int K, int experts,
+                         const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
+                         const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
+                         int* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows_total <= 0 || N <= 0 || K <= 0 || experts <= 0 || max_tiles <= 0) return 0;
+  if ((K % 8) || (lda % 8) || (ldw % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -1;
+  const int act_pair = (flags >> 1) & 1;
+  if (act_pair && (N % 128)) return -1;
+  if (max_tiles > 65535) return -1;
+  static const int pdl_enabled = [] { const char* e = getenv("OGB_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
+  const int bt = token_tile;
+  CUtensorMap tw, ta;
+  if (!MakeMap(&tw, W, experts * N, K, ldw, GEMM_BLOCK_N)) return -2;
+  if (!MakeMap(&ta, A, rows_total, K, lda, bt)) return -2;
+  GemmParams p = {};
+  p.M = rows_total; p.N = N; p.K = K;
+  p.total_kb = (K + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
+  p.splits = 1; p.kb_per_split = p.total_kb;
+  p.C = C; p.ldc = ldc; p.out_fp32 = flags & 1; p.act_pair = act_pair ? act_kind : 0;
+  p.act_alpha = act_alpha; p.act_limit = act_limit;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = status;
+  p.pdl = pdl_enabled;
+  p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
+  dim3 grid((N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, max_tiles, 1);
   switch (bt) {
     case 16: return Launch<16>(tw, ta, p, grid, stream);
     case 32: return Launch<32>(tw, ta, p, grid, stream);

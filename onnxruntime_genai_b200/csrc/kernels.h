@@ -18,10 +18,30 @@ int ogb_sm_count(int device);
 // ---- gemm_tcgen05.cu
 int ogb_gemm_token_tile(int M, int dual);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
-int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* uses, long long plane_elems, int max_slots);
+int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* epoch, long long plane_elems, int max_slots);
 // flags: bit 0 fp32 output, bit 1 paired silu(gate)*up epilogue, bit 2 fused tensor-parallel all-reduce
 int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
                   const void* residual, int ldr, int flags, int splits, int device, int* status, int sm_count, void* stream);
+
+// Grouped expert GEMM over token rows sorted by expert (tile list from ogb_moe_sort); act_kind 1 = silu(gate)*up,
+// 2 = clamped SwiGLU(alpha, limit); flags as above (bit 2 unused).
+int ogb_moe_gemm(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int rows_total, int N, int K, int experts,
+                 const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
+                 const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile, int* status,
+                 void* stream);
+
+// ---- collectives.cu: mode 0 all-reduce, 1 all-gather, 2 reduce-scatter over the registered symmetric buffers (bf16)
+int ogb_collective(int mode, const void* in, void* out, const void* residual, long long n, int device, int* status, int sm_count,
+                   void* stream);
+
+// ---- moe.cu
+int ogb_moe_topk(const float* logits, int ld, int T, int E, int k, int mode, int32_t* topk_idx, float* topk_w, void* stream);
+int ogb_moe_max_tiles(int n, int experts, int bt);
+int ogb_moe_sort(const int32_t* topk_idx, int T, int k, int E, int e_lo, int e_hi, int bt, int32_t* expert_offsets,
+                 int32_t* sorted_token, int32_t* inv_pos, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows,
+                 int32_t* num_tiles, int max_tiles, void* stream);
+int ogb_moe_combine(const void* y, int ldy, const int32_t* inv_pos, const float* topk_w, int T, int k, int H, const void* residual,
+                    int ldr, void* out, int ldo, void* stream);
 
 // ---- gemm_w4.cu (int4 block-32 weights, repacked by ops.pack_w4)
 long long ogb_w4_packed_bytes(int N, int K);
@@ -57,6 +77,10 @@ int ogb_topk(const float* x, long long row_stride, int rows, int n, int k, int m
              int32_t* out_idx, void* stream);
 int ogb_beam_merge(const float* in_vals, const int32_t* in_idx, int batch, int beams, int cand, float* out_scores,
                    int32_t* out_tokens, int32_t* out_beams, void* stream);
+int ogb_verify_sampled(const float* logits, long long row_stride, int vocab, int K, const int32_t* top_k, const float* top_p,
+                       const float* temperature, const unsigned long long* seeds, const int32_t* positions, const int32_t* draft,
+                       const int32_t* q_idx, const float* q_prob, const int32_t* q_n, int q_stride, int32_t* scratch,
+                       float* accept_prob, int32_t* accepted, int32_t* commit, int32_t* status, void* stream);
 int ogb_verify_greedy(const int32_t* draft, const int32_t* target_argmax, int k, int32_t* accepted, int32_t* commit, void* stream);
 
 #ifdef __cplusplus

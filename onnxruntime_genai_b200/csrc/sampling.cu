@@ -23,6 +23,7 @@ namespace ogb {
 constexpr int SAMP_THREADS = 1024;
 constexpr float SAMP_LOG2E = 1.4426950408889634f;
 constexpr float MASS_SCALE = 1099511627776.0f;  // 2^40
+constexpr int SMALL_K = 1024;  // top-k sets up to this size are finished on a sorted list in shared memory
 
 __device__ __forceinline__ uint32_t to_key(float f) {  // order-preserving float -> uint
   uint32_t u = __float_as_uint(f);
@@ -225,13 +226,95 @@ struct SampleParams {
   int32_t* out;
 };
 
-constexpr int SMALL_K = 1024;  // top-k sets up to this size are finished on a sorted list in shared memory
+
+// The k <= SMALL_K candidates of a row as a sorted list in shared memory (descending value, ties by lower
+// index) with their fixed-point masses: thread j < m owns entry j (mass w, inclusive prefix incl); `kept` is
+// the mass of the prefix that survives top-p (entries with incl <= kept are the sampled distribution).
+struct SmallList {
+  float* sv; int* si;
+  int m;
+  unsigned long long w, incl, kept;
+};
+
+__device__ void small_list(const RowCtx& c, SelectShared& sh, unsigned long long* priv, int* cand_n, int k, float top_p, SmallList& L) {
+  const int tid = threadIdx.x, n = c.n;
+  const float* x = c.x;
+  radix_select<false>(c, sh, priv, (unsigned long long)k);
+  const uint32_t T = sh.prefix;
+  const unsigned long long need = sh.want, ties = sh.ties;
+  __syncthreads();
+  int cut = n;
+  if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);  // ties straddle the threshold: keep the lowest indices
+  __syncthreads();
+  float* cv = reinterpret_cast<float*>(priv);            // candidate values   [SMALL_K]
+  int* ci = reinterpret_cast<int*>(cv + SMALL_K);        // candidate indices  [SMALL_K]
+  float* sv = reinterpret_cast<float*>(ci + SMALL_K);    // sorted values
+  int* si = reinterpret_cast<int*>(sv + SMALL_K);        // sorted indices
+  if (tid == 0) *cand_n = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 8 * blockDim.x) {
+    float vals[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      vals[u] = i < n ? x[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      const uint32_t key = to_key(vals[u]);
+      if (i < n && (key > T || (key == T && i <= cut))) {
+        const int slot = atomicAdd(cand_n, 1);
+        if (slot < SMALL_K) { cv[slot] = vals[u]; ci[slot] = i; }
+      }
+    }
+  }
+  __syncthreads();
+  const int m = min(*cand_n, SMALL_K);
+  // rank sort: descending value, ascending index (deterministic whatever order the slots were filled in)
+  if (tid < m) {
+    const float v = cv[tid];
+    const int idx = ci[tid];
+    int rank = 0;
+    for (int j = 0; j < m; ++j) {
+      const float vj = cv[j];
+      const int ij = ci[j];
+      rank += (vj > v || (vj == v && ij < idx)) ? 1 : 0;
+    }
+    sv[rank] = v;
+    si[rank] = idx;
+  }
+  __syncthreads();
+  const float top = sv[0];
+  unsigned long long w = 0;
+  if (tid < m) {
+    w = (unsigned long long)(exp2f((sv[tid] - top) * c.inv_t2) * MASS_SCALE);
+    if (w == 0) w = 1;
+  }
+  unsigned long long total;
+  const unsigned long long incl = block_scan_incl(w, sh, total);
+  __syncthreads();
+  // top-p: shortest prefix whose mass reaches p * total ("include while the mass before it is < p")
+  unsigned long long kept = total;
+  if (top_p > 0.f && top_p < 1.f) {
+    const unsigned long long want = (unsigned long long)(double(total) * double(top_p));
+    if (tid == 0) sh.carry = total;
+    __syncthreads();
+    if (tid < m && incl >= want && incl - w < want) sh.carry = incl;  // exactly one thread
+    __syncthreads();
+    kept = sh.carry;
+  }
+  L.sv = sv; L.si = si; L.m = m; L.w = w; L.incl = incl; L.kept = kept;
+}
 
 // 53-bit uniform in [0, 1) from the stateless generator keyed by (seed, position).
-__device__ __forceinline__ double draw_uniform(const SampleParams& p, int row) {
+__device__ __forceinline__ double uniform53(unsigned long long seed, unsigned long long position, uint32_t stream) {
   uint32_t rnd[4];
-  Philox::gen(p.seeds ? p.seeds[row] : 0ull, (unsigned long long)(p.positions ? p.positions[row] : 0), 0x5a17u, rnd);
+  Philox::gen(seed, position, stream, rnd);
   return double((((unsigned long long)rnd[0] << 32) | rnd[1]) >> 11) * (1.0 / 9007199254740992.0);
+}
+__device__ __forceinline__ double draw_uniform(const SampleParams& p, int row) {
+  return uniform53(p.seeds ? p.seeds[row] : 0ull, (unsigned long long)(p.positions ? p.positions[row] : 0), 0x5a17u);
 }
 
 __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
@@ -293,74 +376,11 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
 
   if (small) {
     // ---- top-k by count, then everything else on the k candidates
-    radix_select<false>(c, sh, priv, (unsigned long long)k);
-    const uint32_t T = sh.prefix;
-    const unsigned long long need = sh.want, ties = sh.ties;
-    __syncthreads();
-    int cut = n;
-    if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);  // ties straddle the threshold: keep the lowest indices
-    __syncthreads();
-    float* cv = reinterpret_cast<float*>(priv);            // candidate values   [SMALL_K]
-    int* ci = reinterpret_cast<int*>(cv + SMALL_K);        // candidate indices  [SMALL_K]
-    float* sv = reinterpret_cast<float*>(ci + SMALL_K);    // sorted values
-    int* si = reinterpret_cast<int*>(sv + SMALL_K);        // sorted indices
-    if (tid == 0) cand_n = 0;
-    __syncthreads();
-    for (int base = 0; base < n; base += 8 * blockDim.x) {
-      float vals[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = base + u * blockDim.x + tid;
-        vals[u] = i < n ? x[i] : -INFINITY;
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = base + u * blockDim.x + tid;
-        const uint32_t key = to_key(vals[u]);
-        if (i < n && (key > T || (key == T && i <= cut))) {
-          const int slot = atomicAdd(&cand_n, 1);
-          if (slot < SMALL_K) { cv[slot] = vals[u]; ci[slot] = i; }
-        }
-      }
-    }
-    __syncthreads();
-    const int m = min(cand_n, SMALL_K);
-    // rank sort: descending value, ascending index (deterministic whatever order the slots were filled in)
-    if (tid < m) {
-      const float v = cv[tid];
-      const int idx = ci[tid];
-      int rank = 0;
-      for (int j = 0; j < m; ++j) {
-        const float vj = cv[j];
-        const int ij = ci[j];
-        rank += (vj > v || (vj == v && ij < idx)) ? 1 : 0;
-      }
-      sv[rank] = v;
-      si[rank] = idx;
-    }
-    __syncthreads();
-    const float top = sv[0];
-    unsigned long long w = 0;
-    if (tid < m) {
-      w = (unsigned long long)(exp2f((sv[tid] - top) * c.inv_t2) * MASS_SCALE);
-      if (w == 0) w = 1;
-    }
-    unsigned long long total;
-    const unsigned long long incl = block_scan_incl(w, sh, total);
-    __syncthreads();
-    // top-p: shortest prefix whose mass reaches p * total ("include while the mass before it is < p")
-    unsigned long long kept = total;
-    if (top_p > 0.f && top_p < 1.f) {
-      const unsigned long long want = (unsigned long long)(double(total) * double(top_p));
-      if (tid == 0) sh.carry = total;
-      __syncthreads();
-      if (tid < m && incl >= want && incl - w < want) sh.carry = incl;  // exactly one thread
-      __syncthreads();
-      kept = sh.carry;
-    }
-    unsigned long long target = (unsigned long long)(draw_uniform(p, row) * double(kept));
-    if (target >= kept) target = kept - 1;
-    if (tid < m && incl > target && incl - w <= target) p.out[row] = si[tid];
+    SmallList L;
+    small_list(c, sh, priv, &cand_n, k, top_p, L);
+    unsigned long long target = (unsigned long long)(draw_uniform(p, row) * double(L.kept));
+    if (target >= L.kept) target = L.kept - 1;
+    if (tid < L.m && L.incl > target && L.incl - L.w <= target) p.out[row] = L.si[tid];
     return;
   }
 
@@ -596,6 +616,112 @@ __global__ void verify_greedy_kernel(const int32_t* draft, const int32_t* target
   *accepted = a;
 }
 
+// ------------------------------------------------------------------------------------ speculative verify (sampled)
+// Rejection sampling over K draft tokens in one launch (reference on the host: src/speculative_sampling.h:39-177).
+// Block i < K: p = the target's sampled distribution of row i (temperature, top-k, top-p as in sample_kernel),
+// q = the draft's distribution for that position (sparse list, or one-hot on the draft token when its list is
+// empty: greedy draft, n-gram proposal).  It records accept_i = [u < min(1, p(x_i)/q(x_i))] and a token drawn
+// from the residual max(0, p - q) renormalised (from p when the residual is empty).  Block K draws the bonus
+// token from p_K with the same random stream the plain sampler would use at that position.  The last block
+// to finish scans the decisions: accepted = first rejected position (K if none), commit = accepted drafts +
+// the replacement / bonus token.  Rows need 1 < top_k <= 1024 (the sorted-list path).
+struct VerifyParams {
+  const float* logits; long long row_stride; int vocab, K;
+  const int32_t* top_k; const float* top_p; const float* temperature;
+  const unsigned long long* seeds; const int32_t* positions;   // per row
+  const int32_t* draft;                                         // [K]
+  const int32_t* q_idx; const float* q_prob; const int32_t* q_n; int q_stride;   // [K, q_stride]; q_n may be null (all one-hot)
+  int32_t* accept; int32_t* resample;                           // [K + 1] scratch
+  float* accept_prob;                                           // [K] (optional, statistics)
+  unsigned int* done_count;                                     // zero before the first launch; the kernel resets it
+  int32_t* accepted; int32_t* commit; int32_t* status;          // status: 1 = a row fell outside the supported range
+};
+
+__global__ void __launch_bounds__(SAMP_THREADS) verify_sampled_kernel(VerifyParams p) {
+  extern __shared__ unsigned long long priv[];
+  __shared__ SelectShared sh;
+  __shared__ int cand_n;
+  __shared__ double pt_sh;
+  __shared__ int last_block;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int n = p.vocab, K = p.K;
+  const int k = p.top_k ? p.top_k[row] : 0;
+  const float top_p = p.top_p ? p.top_p[row] : 0.f;
+  const float temp = p.temperature ? p.temperature[row] : 1.f;
+  const unsigned long long seed = p.seeds ? p.seeds[row] : 0ull;
+  const unsigned long long pos = (unsigned long long)(p.positions ? p.positions[row] : 0);
+  const bool supported = k > 1 && k < n && k <= SMALL_K && temp > 0.f;
+  if (!supported) {
+    if (tid == 0) { atomicExch(p.status, 1); p.accept[row] = 0; p.resample[row] = 0; }
+  } else {
+    RowCtx c;
+    c.x = p.logits + size_t(row) * p.row_stride; c.n = n; c.mx = 0.f; c.inv_t2 = SAMP_LOG2E / temp;
+    c.use_k = false; c.tk = 0; c.tk_idx = n;
+    SmallList L;
+    small_list(c, sh, priv, &cand_n, k, top_p, L);
+    const bool in_p = tid < L.m && L.incl <= L.kept;   // entry belongs to the sampled distribution
+    const bool bonus = row == K;
+    const int x = bonus ? -1 : p.draft[row];
+    const int qn = (bonus || !p.q_n) ? 0 : min(p.q_n[row], p.q_stride);
+    const int32_t* qi = p.q_idx + size_t(bonus ? 0 : row) * p.q_stride;
+    const float* qp = p.q_prob + size_t(bonus ? 0 : row) * p.q_stride;
+    auto q_of = [&](int token) -> float {
+      if (qn == 0) return token == x ? 1.f : 0.f;
+      for (int j = 0; j < qn; ++j) if (qi[j] == token) return qp[j];
+      return 0.f;
+    };
+    if (tid == 0) pt_sh = 0.0;
+    __syncthreads();
+    if (!bonus && in_p && L.si[tid] == x) pt_sh = double(L.w) / double(L.kept);
+    __syncthreads();
+    // residual mass of this thread's entry
+    unsigned long long r = 0;
+    if (in_p) {
+      if (bonus) r = L.w;
+      else {
+        const double qq = double(q_of(L.si[tid])) * double(L.kept);
+        r = double(L.w) > qq ? (unsigned long long)(double(L.w) - qq) : 0ull;
+      }
+    }
+    unsigned long long rt;
+    unsigned long long rincl = block_scan_incl(r, sh, rt);
+    __syncthreads();
+    if (rt == 0) {  // empty residual (p <= q everywhere): draw from p itself
+      r = in_p ? L.w : 0ull;
+      rincl = block_scan_incl(r, sh, rt);
+      __syncthreads();
+    }
+    unsigned long long target = (unsigned long long)(uniform53(seed, pos, 0x5a17u) * double(rt));
+    if (target >= rt) target = rt - 1;
+    if (r && rincl > target && rincl - r <= target) p.resample[row] = L.si[tid];
+    if (tid == 0) {
+      if (bonus) {
+        p.accept[row] = 0;
+      } else {
+        const float pt = float(pt_sh), qx = q_of(x);
+        const float a = qx > 0.f ? fminf(1.f, pt / qx) : (pt > 0.f ? 1.f : 0.f);
+        if (p.accept_prob) p.accept_prob[row] = a;
+        p.accept[row] = uniform53(seed, pos, 0x5a18u) < double(a) ? 1 : 0;
+      }
+    }
+  }
+  // ---- the last block to finish scans the decisions
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) last_block = (atomicAdd(p.done_count, 1u) == unsigned(K)) ? 1 : 0;
+  __syncthreads();
+  if (last_block && tid == 0) {
+    __threadfence();
+    int a = 0;
+    const volatile int32_t* acc = p.accept;
+    const volatile int32_t* res = p.resample;
+    while (a < K && acc[a]) { p.commit[a] = p.draft[a]; ++a; }
+    p.commit[a] = res[a];
+    *p.accepted = a;
+    *p.done_count = 0;   // ready for the next launch (graph replay included)
+  }
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -645,5 +771,24 @@ OGB_API int ogb_beam_merge(const float* in_vals, const int32_t* in_idx, int batc
 
 OGB_API int ogb_verify_greedy(const int32_t* draft, const int32_t* target_argmax, int k, int32_t* accepted, int32_t* commit, void* stream) {
   verify_greedy_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(draft, target_argmax, k, accepted, commit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Sampled speculative verification of K draft tokens against K + 1 rows of target logits; see verify_sampled_kernel.
+// scratch: (2 * (K + 1) + 1) int32 of device memory, zero before the first use (the kernel leaves it reusable).
+OGB_API int ogb_verify_sampled(const float* logits, long long row_stride, int vocab, int K, const int32_t* top_k, const float* top_p,
+                               const float* temperature, const unsigned long long* seeds, const int32_t* positions,
+                               const int32_t* draft, const int32_t* q_idx, const float* q_prob, const int32_t* q_n, int q_stride,
+                               int32_t* scratch, float* accept_prob, int32_t* accepted, int32_t* commit, int32_t* status, void* stream) {
+  if (K < 0 || K > 64 || vocab <= 0) return -1;
+  VerifyParams p{logits, row_stride, vocab, K, top_k, top_p, temperature, seeds, positions, draft, q_idx, q_prob, q_n, q_stride,
+                 scratch, scratch + (K + 1), accept_prob, reinterpret_cast<unsigned int*>(scratch + 2 * (K + 1)), accepted, commit, status};
+  constexpr int kDyn = (SAMP_THREADS / 32) * 256 * 8;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(verify_sampled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
+    configured = true;
+  }
+  verify_sampled_kernel<<<K + 1, SAMP_THREADS, kDyn, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -115,6 +115,9 @@ class LayerWeights:
     exp_gate_up_b: Optional[torch.Tensor] = None
     exp_down_w: Optional[torch.Tensor] = None     # [E, H, I]
     exp_down_b: Optional[torch.Tensor] = None
+    exp_lo: int = 0          # experts [exp_lo, exp_hi) live on this rank (expert parallelism)
+    exp_hi: int = 0
+    exp_blocked: bool = False  # gate/up rows in blocks of 64 gate + 64 up (grouped-GEMM layout) instead of even/odd
     lora: Dict[str, dict] = field(default_factory=dict)
     window: int = 0
     gate_up_interleaved: bool = False  # gate/up rows stored in blocks of 64 (layout of the fused SiLU*mul GEMM)

@@ -301,16 +301,32 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         # MLP / MoE
         moe = g.find(f"{n}/moe/", ops=["MoE", "QMoE"])
         if moe is not None:
-            if tpn > 1:
-                raise NotImplementedError("mixture-of-experts models use expert parallelism (parallel/ep.py), not TP sharding")
+            # Experts are not sharded along their matrices: with tensor parallelism every rank loads all experts' routing
+            # tables but computes only its own slice of the experts (expert parallelism over replicated tokens, models/moe.py).
             r = linear_node(f"{n}/moe/", "router")
             lw.router_w = _linear_weight(g, r, dtype, device)
             radd = g.by_name.get(f"{n}/moe/router/Add")
             lw.router_b = _vec(g, radd.inputs[1], dtype, device) if radd is not None else None
-            lw.exp_gate_up_w = g.tensor(moe.inputs[2], device=device).to(device=device, dtype=dtype).contiguous()
-            lw.exp_gate_up_b = g.tensor(moe.inputs[3], device=device).to(device=device, dtype=dtype).contiguous() if moe.inputs[3] else None
-            lw.exp_down_w = g.tensor(moe.inputs[4], device=device).to(device=device, dtype=dtype).contiguous()
-            lw.exp_down_b = g.tensor(moe.inputs[5], device=device).to(device=device, dtype=dtype).contiguous() if moe.inputs[5] else None
+            E = arch.num_experts
+            if E % tpn:
+                raise ValueError(f"expert parallel degree {tpn} does not divide the {E} experts")
+            lw.exp_lo, lw.exp_hi = tpr * (E // tpn), (tpr + 1) * (E // tpn)
+
+            def experts(name):
+                if not name:
+                    return None
+                t = g.tensor(name, device=device)
+                return t[lw.exp_lo:lw.exp_hi].to(device=device, dtype=dtype).contiguous()
+            lw.exp_gate_up_w, lw.exp_gate_up_b = experts(moe.inputs[2]), experts(moe.inputs[3])
+            lw.exp_down_w, lw.exp_down_b = experts(moe.inputs[4]), experts(moe.inputs[5])
+            lw.exp_blocked = False
+            if torch.device(device).type == "cuda" and (lw.exp_gate_up_w.shape[1] // 2) % 64 == 0:
+                # grouped GEMM layout: per expert, blocks of 64 gate rows + the 64 up rows of the same features
+                from ..ops import interleave_experts_gate_up
+                lw.exp_gate_up_w = interleave_experts_gate_up(lw.exp_gate_up_w)
+                if lw.exp_gate_up_b is not None:
+                    lw.exp_gate_up_b = interleave_experts_gate_up(lw.exp_gate_up_b)
+                lw.exp_blocked = True
         else:
             gu = linear_node(f"{n}/mlp/", "gate_up_proj")
             g_rows, u_rows = slice(tpr * i_l, (tpr + 1) * i_l), slice(I + tpr * i_l, I + (tpr + 1) * i_l)

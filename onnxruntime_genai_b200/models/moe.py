@@ -7,10 +7,14 @@ Semantics follow the MoE / QMoE contrib op the reference's builder emits
 (gate and up interleaved along the output dimension: even = gate, odd = up), activation
 gate * sigmoid(alpha * gate) * (up + 1) with gate clamped to <= limit and up to [-limit, limit].
 
-Expert matmuls run on the tcgen05 GEMM, one launch per (active expert, projection) over the tokens
-routed to that expert; routing and the activation are elementwise glue.  With expert parallelism
-(parallel/ep.py) each rank owns a contiguous slice of the experts and the token exchange is an
-all-to-all.
+CUDA path (everything on the device, no counts read back, so it replays inside a CUDA graph):
+router GEMM (fp32 out) -> `moe_topk` -> `moe_sort` (rows grouped by expert + tile list) -> row gather ->
+grouped tcgen05 GEMM gate/up with the clamped SwiGLU in its epilogue -> grouped GEMM down -> `moe_combine`.
+
+Expert parallelism: attention is tensor parallel, so after its all-reduce every rank already holds every
+token; a rank therefore needs no dispatch — it routes all tokens, runs only the experts it owns
+(`lw.exp_lo .. lw.exp_hi`), and the partial outputs are summed by the same all-reduce a dense row-parallel
+MLP uses.  The combine of the all-to-all formulation is that all-reduce.
 """
 from __future__ import annotations
 
@@ -34,30 +38,57 @@ def route(model, lw, x):
     return torch.softmax(top_v, dim=-1), top_i
 
 
+def _unblock(t: torch.Tensor) -> torch.Tensor:
+    """[.., 2I, ..] in blocks of 64 gate + 64 up rows -> even/odd interleaved rows."""
+    two_i = t.shape[0]
+    v = t.reshape(two_i // 128, 2, 64, *t.shape[1:])
+    return torch.stack([v[:, 0], v[:, 1]], dim=2).reshape(t.shape)
+
+
 def expert_mlp(model, lw, e: int, xs: torch.Tensor) -> torch.Tensor:
+    """One expert (index into this rank's slice) over its rows: the unfused path (CPU, odd shapes)."""
     a = model.arch
-    gu = ops.linear(xs, lw.exp_gate_up_w[e], lw.exp_gate_up_b[e] if lw.exp_gate_up_b is not None else None)
+    w, b = lw.exp_gate_up_w[e], lw.exp_gate_up_b[e] if lw.exp_gate_up_b is not None else None
+    if lw.exp_blocked:
+        w, b = _unblock(w).contiguous(), _unblock(b).contiguous() if b is not None else None
+    gu = ops.linear(xs, w, b)
     act = swiglu_interleaved(gu, a.moe_swiglu_alpha, a.moe_swiglu_limit)
     return ops.linear(act.contiguous(), lw.exp_down_w[e], lw.exp_down_b[e] if lw.exp_down_b is not None else None)
 
 
-def moe_forward(model, lw, x: torch.Tensor) -> torch.Tensor:
-    ep = getattr(model, "ep", None)
-    if ep is not None and ep.size > 1:
-        return ep.moe_forward(model, lw, x)
+def _forward_loop(model, lw, x):
+    a = model.arch
+    lo, hi = lw.exp_lo, lw.exp_hi or a.num_experts
     weights, experts = route(model, lw, x)
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
     flat_e = experts.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
-    counts = torch.bincount(flat_e, minlength=model.arch.num_experts).tolist()
-    tok = (order // model.arch.experts_per_token)
+    counts = torch.bincount(flat_e, minlength=a.num_experts).tolist()
+    tok = order // a.experts_per_token
     w_sorted = weights.reshape(-1)[order]
     start = 0
     for e, n in enumerate(counts):
-        if n == 0:
-            continue
-        idx = tok[start:start + n]
-        y = expert_mlp(model, lw, e, x[idx].contiguous()).float()
-        out.index_add_(0, idx, y * w_sorted[start:start + n, None])
+        if n and lo <= e < hi:
+            idx = tok[start:start + n]
+            y = expert_mlp(model, lw, e - lo, x[idx].contiguous()).float()
+            out.index_add_(0, idx, y * w_sorted[start:start + n, None])
         start += n
     return out.to(x.dtype)
+
+
+def _forward_device(model, lw, x):
+    a = model.arch
+    lo, hi = lw.exp_lo, lw.exp_hi or a.num_experts
+    logits = ops.linear(x, lw.router_w, lw.router_b, out_fp32=True)
+    plan = ops.moe_route(logits, a.experts_per_token, 0, (lo, hi))
+    xs = ops.gather_rows(x, plan.sorted_token)
+    h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, lw.exp_gate_up_b, act_kind=2, alpha=a.moe_swiglu_alpha, limit=a.moe_swiglu_limit)
+    y = ops.moe_gemm(h, lw.exp_down_w, plan, lw.exp_down_b)
+    return ops.moe_combine(y, plan)
+
+
+def moe_forward(model, lw, x: torch.Tensor) -> torch.Tensor:
+    a = model.arch
+    fast = x.is_cuda and lw.exp_blocked and a.hidden_size % 8 == 0 and a.num_experts <= 1024 and a.experts_per_token <= 32
+    out = _forward_device(model, lw, x) if fast else _forward_loop(model, lw, x)
+    return model.tp.reduce(out) if model.tp.size > 1 else out

@@ -186,6 +186,84 @@ def act_mul(x, act="silu"):
     return out
 
 
+# ------------------------------------------------------------------------------------------ mixture of experts
+def interleave_experts_gate_up(w: torch.Tensor, fused_interleaved: bool = True, block: int = 64) -> torch.Tensor:
+    """Per-expert gate/up rows ([E, 2I, ...]; fused_interleaved: even rows = gate, odd rows = up, else [gate; up])
+    -> per expert blocks of 64 gate rows followed by the 64 up rows of the same features."""
+    E, two_i = w.shape[0], w.shape[1]
+    inter = two_i // 2
+    assert inter % block == 0
+    if fused_interleaved:
+        g, u = w[:, 0::2], w[:, 1::2]
+    else:
+        g, u = w[:, :inter], w[:, inter:]
+    g = g.reshape(E, inter // block, 1, block, *w.shape[2:])
+    u = u.reshape(E, inter // block, 1, block, *w.shape[2:])
+    return torch.cat([g, u], dim=2).reshape(w.shape).contiguous()
+
+
+class MoePlan:
+    """Device-side routing of one MoE layer call (no host readback): which expert serves which sorted row."""
+    __slots__ = ("T", "k", "E", "bt", "max_tiles", "topk_idx", "topk_w", "expert_offsets", "sorted_token", "inv_pos", "tile_expert",
+                 "tile_row0", "tile_rows", "num_tiles")
+
+
+def moe_route(router_logits: torch.Tensor, k: int, mode: int = 0, expert_range=None, token_tile: int = 0) -> MoePlan:
+    """router_logits [T, E] fp32 -> MoePlan (top-k, routing weights, rows grouped by expert, GEMM tile list).
+    mode 0: softmax over the selected logits; 1: softmax over all experts; 2: the latter renormalised.
+    expert_range (lo, hi): only these experts are local (expert parallelism)."""
+    assert router_logits.is_cuda and router_logits.dtype == torch.float32 and router_logits.stride(-1) == 1
+    T, E = router_logits.shape
+    L = _lib.lib()
+    dev = router_logits.device
+    lo, hi = expert_range if expert_range is not None else (0, E)
+    pl = MoePlan()
+    n = T * k
+    bt = token_tile or L.ogb_gemm_token_tile(max(1, min(T, -(-2 * n // max(1, hi - lo)))), 0)
+    pl.T, pl.k, pl.E, pl.bt = T, k, E, bt
+    pl.max_tiles = L.ogb_moe_max_tiles(n, hi - lo, bt)
+    i32 = dict(dtype=torch.int32, device=dev)
+    pl.topk_idx = torch.empty(T, k, **i32)
+    pl.topk_w = torch.empty(T, k, dtype=torch.float32, device=dev)
+    pl.expert_offsets = torch.empty(E + 1, **i32)
+    pl.sorted_token = torch.empty(n, **i32)
+    pl.inv_pos = torch.empty(T, k, **i32)
+    tiles = torch.empty(3 * pl.max_tiles + 1, **i32)
+    pl.tile_expert, pl.tile_row0, pl.tile_rows = tiles[:pl.max_tiles], tiles[pl.max_tiles:2 * pl.max_tiles], tiles[2 * pl.max_tiles:3 * pl.max_tiles]
+    pl.num_tiles = tiles[3 * pl.max_tiles:]
+    _lib.check(L.ogb_moe_topk(_ptr(router_logits), router_logits.stride(0), T, E, k, mode, _ptr(pl.topk_idx), _ptr(pl.topk_w), _stream()),
+               "moe_topk")
+    _lib.check(L.ogb_moe_sort(_ptr(pl.topk_idx), T, k, E, lo, hi, bt, _ptr(pl.expert_offsets), _ptr(pl.sorted_token), _ptr(pl.inv_pos),
+                              _ptr(pl.tile_expert), _ptr(pl.tile_row0), _ptr(pl.tile_rows), _ptr(pl.num_tiles), pl.max_tiles, _stream()),
+               "moe_sort")
+    return pl
+
+
+def moe_gemm(xs: torch.Tensor, w: torch.Tensor, plan: MoePlan, bias=None, act_kind: int = 0, alpha: float = 1.0, limit: float = 0.0):
+    """Grouped expert GEMM over rows sorted by expert.  xs [T*k, K] bf16; w [E, N, K] bf16; bias [E, N].
+    act_kind 0: plain; 1: silu(gate)*up; 2: clamped SwiGLU(alpha, limit) — both need the 64-row gate/up blocks
+    of interleave_experts_gate_up and return N/2 columns."""
+    E, N, K = w.shape
+    assert xs.is_cuda and xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and xs.stride(-1) == 1
+    out = torch.empty(xs.shape[0], N // 2 if act_kind else N, dtype=torch.bfloat16, device=xs.device)
+    ws = workspace(xs.device)
+    rc = _lib.lib().ogb_moe_gemm(_ptr(xs), xs.stride(0), _ptr(w), K, _ptr(out), out.stride(0), xs.shape[0], N, K, E, _ptr(bias),
+                                 GEMM_ACT_PAIR if act_kind else 0, int(act_kind), float(alpha), float(limit), _ptr(plan.tile_expert),
+                                 _ptr(plan.tile_row0), _ptr(plan.tile_rows), _ptr(plan.num_tiles), plan.max_tiles, plan.bt, ws.status,
+                                 _stream())
+    _lib.check(rc, "moe_gemm")
+    return out
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, residual=None) -> torch.Tensor:
+    """out[t] = (residual[t]) + sum_j w[t, j] * y[row(t, j)]; rows of experts that are not local are skipped."""
+    out = torch.empty(plan.T, y.shape[1], dtype=torch.bfloat16, device=y.device)
+    rc = _lib.lib().ogb_moe_combine(_ptr(y), y.stride(0), _ptr(plan.inv_pos), _ptr(plan.topk_w), plan.T, plan.k, y.shape[1], _ptr(residual),
+                                    residual.stride(0) if residual is not None else 0, _ptr(out), out.stride(0), _stream())
+    _lib.check(rc, "moe_combine")
+    return out
+
+
 # ------------------------------------------------------------------------------------------ RoPE + KV append
 def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
                    q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
@@ -348,3 +426,47 @@ def beam_candidates(logits, beam_scores, batch, beams):
     _lib.check(_lib.lib().ogb_beam_merge(_ptr(vals), _ptr(idx), batch, beams, cand, _ptr(scores), _ptr(tokens), _ptr(src), _stream()),
                "beam_merge")
     return scores, tokens, src
+
+
+_verify_scratch = {}
+
+
+def verify_sampled(logits, draft, q_dists, top_k: int, top_p: float, temperature: float, seed: int, first_position: int):
+    """Sampled speculative verification on the device.  logits [K+1, V] fp32 (target rows for the K draft
+    positions and the bonus position); draft: K token ids; q_dists: per draft position None (deterministic
+    proposal) or (ids, probs) of the draft model's sampled distribution.  Row i draws with the random stream of
+    (seed, first_position + i).  Returns (accepted, commit list, accept probabilities [K])."""
+    K = len(draft)
+    dev = logits.device
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.shape[0] == K + 1 and 1 < top_k <= 1024
+    R = K + 1
+    ki = torch.full((R,), int(top_k), dtype=torch.int32, device=dev)
+    pp = torch.full((R,), float(top_p), dtype=torch.float32, device=dev)
+    tt = torch.full((R,), float(temperature), dtype=torch.float32, device=dev)
+    seeds = torch.full((R,), int(seed) & ((1 << 63) - 1), dtype=torch.int64, device=dev)
+    pos = torch.arange(first_position, first_position + R, dtype=torch.int32, device=dev)
+    d = torch.tensor(list(draft) or [0], dtype=torch.int32, device=dev)
+    qs = max([len(q[0]) for q in q_dists if q is not None] + [1])
+    qi = np.zeros((max(K, 1), qs), dtype=np.int32)
+    qp = np.zeros((max(K, 1), qs), dtype=np.float32)
+    qn = np.zeros((max(K, 1),), dtype=np.int32)
+    for i, q in enumerate(q_dists):
+        if q is not None:
+            m = len(q[0])
+            qi[i, :m], qp[i, :m], qn[i] = q[0], q[1], m
+    qi_d, qp_d, qn_d = torch.from_numpy(qi).to(dev), torch.from_numpy(qp).to(dev), torch.from_numpy(qn).to(dev)
+    key = (dev.index, K)
+    if key not in _verify_scratch:
+        _verify_scratch[key] = torch.zeros(2 * R + 1, dtype=torch.int32, device=dev)
+    scratch = _verify_scratch[key]
+    out = torch.zeros(R + 2, dtype=torch.int32, device=dev)     # [accepted, status, commit...]
+    aprob = torch.zeros(max(K, 1), dtype=torch.float32, device=dev)
+    rc = _lib.lib().ogb_verify_sampled(_ptr(logits), logits.stride(0), logits.shape[1], K, _ptr(ki), _ptr(pp), _ptr(tt), _ptr(seeds), _ptr(pos),
+                                       _ptr(d), _ptr(qi_d), _ptr(qp_d), _ptr(qn_d), qs, _ptr(scratch), _ptr(aprob), _ptr(out[0:1]),
+                                       _ptr(out[2:]), _ptr(out[1:2]), _stream())
+    _lib.check(rc, "verify_sampled")
+    res = out.tolist()
+    if res[1] != 0:
+        raise RuntimeError("verify_sampled: sampling parameters outside the device path (needs 1 < top_k <= 1024, temperature > 0)")
+    accepted = res[0]
+    return accepted, res[2:2 + accepted + 1], aprob[:K].tolist()

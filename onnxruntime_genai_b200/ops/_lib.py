@@ -27,6 +27,13 @@ _SIGS = {
     "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, _P, c_longlong, c_int]),
     "ogb_w4_packed_bytes": (c_longlong, [c_int, c_int]),
     "ogb_gemm_w4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P]),
+    "ogb_moe_gemm": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_float, _P, _P, _P,
+                             _P, c_int, c_int, _P, _P]),
+    "ogb_collective": (c_int, [c_int, _P, _P, _P, c_longlong, c_int, _P, c_int, _P]),
+    "ogb_moe_topk": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P]),
+    "ogb_moe_max_tiles": (c_int, [c_int, c_int, c_int]),
+    "ogb_moe_sort": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, _P]),
+    "ogb_moe_combine": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P, c_int, _P]),
     "ogb_embedding": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
     "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -43,6 +50,7 @@ _SIGS = {
     "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),
     "ogb_topk": (c_int, [_P, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P]),
     "ogb_beam_merge": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P]),
+    "ogb_verify_sampled": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, _P]),
     "ogb_verify_greedy": (c_int, [_P, _P, c_int, _P, _P, _P]),
 }
 

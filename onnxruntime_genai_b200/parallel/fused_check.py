@@ -1,5 +1,6 @@
-"""Checks the fused GEMM + all-reduce kernel against GEMM followed by `dist.all_reduce` on every rank
-of a torchrun job, and times both (device events, max over ranks).
+"""Checks the fused GEMM + all-reduce kernel against GEMM followed by `dist.all_reduce`, and the stand-alone
+all-reduce / all-gather / reduce-scatter kernels against their NCCL counterparts, on every rank of a
+torchrun job, and times both sides (device events, max over ranks).
 
     torchrun --nproc-per-node N --master-addr 127.0.0.1 -m onnxruntime_genai_b200.parallel.fused_check [--tokens 64]
 """
@@ -19,6 +20,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
     a = ap.parse_args()
+    import faulthandler
+    faulthandler.dump_traceback_later(240, exit=True)   # a stuck rank reports where and ends instead of hanging the job
     from onnxruntime_genai_b200 import ops
     from onnxruntime_genai_b200.parallel.tp import TensorParallel
     tp = TensorParallel.from_env("fused")
@@ -60,6 +63,28 @@ def main():
             dist.all_reduce(y)
             return y
 
+        # stand-alone collectives against NCCL
+        comm = tp.comm
+        y = ops.linear(x, w)
+        ar_want = y.float()
+        dist.all_reduce(ar_want)
+        ar = comm.all_reduce(y)
+        res["allreduce_err"] = float((ar.float() - ar_want).abs().max())
+        parts = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(parts, y)
+        ag = comm.all_gather(y)
+        res["allgather_exact"] = bool(torch.equal(ag, torch.stack(parts)))
+        stacked = torch.stack([y * (r + 1) for r in range(world)]).contiguous()
+        rs_want = torch.empty_like(y, dtype=torch.float32)
+        dist.reduce_scatter_tensor(rs_want, stacked.float())
+        rs = comm.reduce_scatter(stacked)
+        res["reducescatter_err"] = float((rs.float() - rs_want).abs().max())
+        ops.check_kernel_status()
+        res["allreduce_us"] = timed(lambda: comm.all_reduce(y))
+        res["nccl_allreduce_us"] = timed(lambda: dist.all_reduce(y.clone()))
+        res["allgather_us"] = timed(lambda: comm.all_gather(y))
+        res["nccl_allgather_us"] = timed(lambda: dist.all_gather(parts, y))
+
         res["fused_us"] = timed(lambda: ops.linear(x, w, residual=resid, all_reduce=True))
         res["gemm_plus_nccl_us"] = timed(baseline)
         res["gemm_only_us"] = timed(lambda: ops.linear(x, w))
@@ -69,8 +94,8 @@ def main():
         if a.out:
             with open(a.out, "w") as f:
                 json.dump(res, f)
-    dist.barrier()
-    dist.destroy_process_group()
+    from onnxruntime_genai_b200.parallel.tp import leave
+    leave(0)
 
 
 if __name__ == "__main__":

@@ -1,13 +1,13 @@
 """Symmetric peer memory for the fused GEMM + all-reduce kernel (csrc/gemm_tcgen05.cu).
 
 Every rank owns one receive buffer `[2 parities][world sources][plane_elems]` bf16 and one array of
-arrival counters; both are mapped into every peer (NVLink peer access through
+arrival stamps `[slots][8 sources]`; both are mapped into every peer (NVLink peer access through
 `torch.distributed._symmetric_memory`, which exchanges the memory handles over the process group).
 The pointers are registered once with the kernel library (`ogb_comm_register`); after that the GEMM
 launcher only needs a flag to run the fused path, so the call captures into CUDA graphs unchanged.
 
 `LocalComm` registers a world of one on a single GPU: the kernel then pushes to and waits on its
-own buffers, which exercises the whole protocol (parity, counters, use counts) without peers.
+own buffers, which exercises the whole protocol (parity, stamps, call counter) without peers.
 """
 from __future__ import annotations
 
@@ -22,33 +22,69 @@ MAX_SLOTS = 4096
 DEFAULT_PLANE_ELEMS = 256 * 8192  # up to 256 tokens x 8192 output features per fused call
 
 
-def _register(device_index: int, world: int, rank: int, buf_ptrs: List[int], flag_ptrs: List[int], uses: torch.Tensor,
+def _register(device_index: int, world: int, rank: int, buf_ptrs: List[int], flag_ptrs: List[int], epoch: torch.Tensor,
               plane_elems: int) -> None:
     arr_t = ctypes.c_void_p * world
-    rc = _lib.lib().ogb_comm_register(device_index, world, rank, arr_t(*buf_ptrs), arr_t(*flag_ptrs), uses.data_ptr(),
+    rc = _lib.lib().ogb_comm_register(device_index, world, rank, arr_t(*buf_ptrs), arr_t(*flag_ptrs), epoch.data_ptr(),
                                       plane_elems, MAX_SLOTS)
     if rc != 0:
         raise RuntimeError(f"ogb_comm_register failed with {rc}")
 
 
-class LocalComm:
+class _Collectives:
+    """Stand-alone collectives over the registered buffers (csrc/collectives.cu).  Tensors are taken as raw 16-byte
+    vectors for the gather; reductions are bf16.  `fits` tells whether a tensor can go through the kernels; callers
+    fall back to NCCL otherwise."""
+
+    def fits(self, x: torch.Tensor, planes: int = 1) -> bool:
+        nbytes = x.numel() * x.element_size() // planes
+        return x.is_cuda and x.is_contiguous() and nbytes % 16 == 0 and nbytes // 2 <= self.plane_elems and x.data_ptr() % 16 == 0
+
+    def _run(self, mode: int, x: torch.Tensor, out: torch.Tensor, residual, n_units: int):
+        from .. import ops
+        ws = ops.workspace(x.device)
+        rc = _lib.lib().ogb_collective(mode, x.data_ptr(), out.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                       n_units, x.device.index, ws.status, ws.sm_count, torch.cuda.current_stream(x.device).cuda_stream)
+        _lib.check(rc, "collective")
+        return out
+
+    def all_reduce(self, x: torch.Tensor, residual=None, out=None) -> torch.Tensor:
+        """Sum over ranks (+ residual) of a bf16 tensor; every rank gets bit-identical results."""
+        assert x.dtype == torch.bfloat16 and self.fits(x)
+        return self._run(0, x, torch.empty_like(x) if out is None else out, residual, x.numel())
+
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """[world, *x.shape]: every rank's tensor, any dtype."""
+        assert self.fits(x)
+        out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        return self._run(1, x, out, None, x.numel() * x.element_size() // 2)
+
+    def reduce_scatter(self, x: torch.Tensor, residual=None) -> torch.Tensor:
+        """x [world, ...] bf16 partials -> sum over ranks of slice [rank] (+ residual)."""
+        assert x.dtype == torch.bfloat16 and x.shape[0] == self.size and self.fits(x, self.size)
+        out = torch.empty(x.shape[1:], dtype=x.dtype, device=x.device)
+        return self._run(2, x, out, residual, out.numel())
+
+
+class LocalComm(_Collectives):
     """World of one: the fused path talking to itself (single-GPU tests of the protocol)."""
 
     def __init__(self, device: torch.device, plane_elems: int = DEFAULT_PLANE_ELEMS):
         self.device = device
         self.plane_elems = plane_elems
+        self.rank, self.size = 0, 1
         self.max_tokens = 256
         self.buf = torch.zeros(2 * plane_elems, dtype=torch.bfloat16, device=device)
-        self.flags = torch.zeros(MAX_SLOTS, dtype=torch.int32, device=device)
-        self.uses = torch.zeros(MAX_SLOTS, dtype=torch.int32, device=device)
+        self.flags = torch.zeros(MAX_SLOTS * 8, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
         _lib.init_device(device.index)
-        _register(device.index, 1, 0, [self.buf.data_ptr()], [self.flags.data_ptr()], self.uses, plane_elems)
+        _register(device.index, 1, 0, [self.buf.data_ptr()], [self.flags.data_ptr()], self.epoch, plane_elems)
 
     def close(self):
         _lib.lib().ogb_comm_register(self.device.index, 0, 0, None, None, None, 0, 0)
 
 
-class SymmetricComm:
+class SymmetricComm(_Collectives):
     def __init__(self, rank: int, size: int, device: torch.device, group=None, plane_elems: int = DEFAULT_PLANE_ELEMS):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
@@ -56,20 +92,14 @@ class SymmetricComm:
         self.max_tokens = 256
         group = group or dist.group.WORLD
         self.buf = symm_mem.empty(2 * size * plane_elems, dtype=torch.bfloat16, device=device)
-        self.flags = symm_mem.empty(MAX_SLOTS, dtype=torch.int32, device=device)
+        self.flags = symm_mem.empty(MAX_SLOTS * 8, dtype=torch.int32, device=device)
         self.buf_h = symm_mem.rendezvous(self.buf, group)
         self.flag_h = symm_mem.rendezvous(self.flags, group)
         self.flags.zero_()
-        self.uses = torch.zeros(MAX_SLOTS, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
         _lib.init_device(device.index)
         _register(device.index, size, rank, [int(p) for p in self.buf_h.buffer_ptrs], [int(p) for p in self.flag_h.buffer_ptrs],
-                  self.uses, plane_elems)
+                  self.epoch, plane_elems)
         dist.barrier(group=group)
-
-    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
-        """Stand-alone all-reduce for tensors that did not come out of a fused GEMM (NCCL)."""
-        import torch.distributed as dist
-        dist.all_reduce(x)
-        return x

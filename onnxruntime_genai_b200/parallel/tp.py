@@ -7,9 +7,11 @@ and the vocabulary-parallel LM head is gathered.
 
 Two reduction back ends:
   * "nccl": `dist.all_reduce` — the baseline;
-  * "fused": the one-shot all-reduce kernel over NVLink peer memory in csrc/comm.cu (every rank
-    writes its partial tile into a symmetric buffer, signals, then reads all peers' tiles and sums
-    them in a fixed rank order, so every rank produces bit-identical results); see parallel/symm.py.
+  * "fused": the one-shot all-reduce over NVLink peer memory, inside the GEMM epilogue for the row-parallel
+    projections (csrc/gemm_common.cuh) and stand-alone for everything else (csrc/collectives.cu): every rank
+    writes its partial tile into every rank's symmetric buffer, stamps an arrival flag, then sums all ranks'
+    tiles from its own buffer in a fixed rank order, so every rank produces bit-identical results; see
+    parallel/symm.py.
 On CPU (gloo) the same class runs the multi-rank tests of the sharding math.
 """
 from __future__ import annotations
@@ -64,17 +66,22 @@ class TensorParallel:
     def reduce(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         if self.size == 1:
             return x
+        if self.comm is not None and x.dtype == torch.bfloat16 and self.comm.fits(x):
+            return self.comm.all_reduce(x, residual)    # one-shot kernel over NVLink peer memory
         if x.dtype == torch.bfloat16 and not x.is_cuda:
             y = x.float()
             dist.all_reduce(y, group=self.group)
-            return y.to(x.dtype)
+            return (y if residual is None else y + residual.float()).to(x.dtype)
         dist.all_reduce(x, group=self.group)
-        return x
+        return x if residual is None else x + residual
 
     # vocabulary-parallel logits [B, V/size] -> [B, V]
     def gather_logits(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:
             return x
+        if self.comm is not None and self.comm.fits(x.contiguous()):
+            g = self.comm.all_gather(x.contiguous())
+            return g.permute(1, 0, 2).reshape(x.shape[0], -1)
         parts = [torch.empty_like(x) for _ in range(self.size)]
         dist.all_gather(parts, x.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)
@@ -82,3 +89,17 @@ class TensorParallel:
     def barrier(self):
         if self.size > 1:
             dist.barrier(group=self.group)
+
+
+def leave(code: int = 0) -> None:
+    """Ends a multi-rank process once its work is done: synchronise, meet the other ranks, flush, and exit
+    without tearing the communicator down (captured graphs may still hold collective kernels, and destroying
+    the process group under them can block)."""
+    import sys
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if dist.is_initialized():
+        dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(code)

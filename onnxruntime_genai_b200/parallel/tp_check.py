@@ -21,6 +21,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--engine", action="store_true", help="also run the continuous-batching engine (CUDA graphs on GPU)")
     a = ap.parse_args()
+    import faulthandler
+    faulthandler.dump_traceback_later(240, exit=True)   # a stuck rank reports where and ends instead of hanging the job
     import torch
     import onnxruntime_genai_b200 as og
     from onnxruntime_genai_b200.parallel.tp import TensorParallel
@@ -64,9 +66,8 @@ def main():
     if rank == 0:
         np.savez(a.out, logits=logits, seqs=seqs, engine=eng_out, backend=str(getattr(tp, "backend", "single")))
     if tp is not None:
-        tp.barrier()
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        from onnxruntime_genai_b200.parallel.tp import leave
+        leave(0)
 
 
 if __name__ == "__main__":

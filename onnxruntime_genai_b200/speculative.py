@@ -148,6 +148,10 @@ class _SpecBase:
                 commit = com[:accepted + 1].tolist()
             else:
                 accepted, commit, _ = native.verify_greedy(np.asarray(draft, dtype=np.int32), logits.float().numpy())
+        elif logits.is_cuda and g.method != "greedy" and not penalties and 1 < g.k <= 1024 and g.t > 0:
+            # rejection sampling on the device: one launch over the K + 1 rows, stateless randomness keyed by position
+            accepted, commit, _ = ops.verify_sampled(logits.float(), draft, list(dists), g.k, g.p if 0 < g.p < 1 else 0.0, g.t,
+                                                     g._seed, n)
         else:
             rows = np.ascontiguousarray(logits.float().cpu().numpy())
             if penalties:

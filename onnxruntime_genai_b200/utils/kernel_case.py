@@ -1,0 +1,185 @@
+"""Single-kernel workloads for timing and profiling.
+
+    python -m onnxruntime_genai_b200.utils.kernel_case <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--json out.json]
+
+cases: gemm_qkv gemm_o gemm_gate_up gemm_down gemm_lm_head gemm_prefill w4_qkv w4_down attention_decode
+       attention_prefill norm rope sample argmax all
+
+Each case runs the kernel at the Llama-3.1-8B (or, for w4_*, Phi-3-mini) shapes with `--layers` distinct
+weight sets rotated between launches (so weights come from HBM, not L2), captures `--iters` launches
+in a CUDA graph and times graph replays with CUDA events.  It prints microseconds per launch and
+the achieved fraction of the algorithmic bytes or FLOPs over the measured peaks in
+MEASURED_PEAKS.json (when that file is next to the repository root).  With few `--layers` and
+`--iters` the same command is the small case used under `ncu`.
+"""
+import argparse
+import json
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+from .. import ops
+
+H, I, V, HQ, HKV, D = 4096, 14336, 128256, 32, 8, 128
+
+
+def _bf(*shape, std=0.02):
+    return (torch.randn(*shape, device="cuda") * std).to(torch.bfloat16)
+
+
+def _time_graph(fn, iters, reps=3):
+    fn(0); fn(1)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(iters):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); g.replay(); e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / iters * 1e3)
+    return best
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def build_case(name, T, L, tp=1):
+    """Returns (fn(i), algorithmic_bytes, flops).  tp > 1: the per-rank shapes of tensor parallelism; the row-parallel
+    projections then run the fused all-reduce against a world of one (protocol cost without a peer)."""
+    HQ, HKV = globals()["HQ"] // tp, max(1, globals()["HKV"] // tp)
+    if name.startswith("gemm_") or name.startswith("w4_"):
+        shapes = {"gemm_qkv": ((HQ + 2 * HKV) * D, H), "gemm_o": (H, HQ * D), "gemm_gate_up": (2 * I // tp, H), "gemm_down": (H, I // tp),
+                  "gemm_lm_head": (V // tp, H), "gemm_prefill": (2 * I // tp, H), "w4_qkv": (9216 // tp, 3072), "w4_down": (3072, 8192 // tp)}
+        N, K = shapes[name]
+        fused = tp > 1 and name in ("gemm_o", "gemm_down")
+        if name == "gemm_lm_head":
+            L = min(L, 2)
+        x = _bf(T, K, std=1.0)
+        if name.startswith("w4_"):
+            from ..models.builder import quantize_int4_block32
+            from ..ops.w4 import W4Weight, unpack_ort_q4
+            ws = []
+            for _ in range(L):
+                qw, s, zp = quantize_int4_block32(torch.randn(N, K) * 0.02)
+                q, z = unpack_ort_q4(qw, zp, N, K)
+                ws.append(W4Weight.from_quantized(q, s, z, "cuda", keep_host=False))
+            nbytes = ws[0].packed.numel()
+            return (lambda i: ops.linear(x, ws[i % L])), nbytes + T * (K + N) * 2, 2.0 * T * N * K
+        ws = [_bf(N, K) for _ in range(L)]
+        if name in ("gemm_gate_up", "gemm_prefill"):
+            ws = [ops.interleave_gate_up(w) for w in ws]
+            return (lambda i: ops.gate_up_act(x, ws[i % L], interleaved=True)), N * K * 2 + T * (K + N // 2) * 2, 2.0 * T * N * K
+        fp32 = name == "gemm_lm_head"
+        return (lambda i: ops.linear(x, ws[i % L], out_fp32=fp32, all_reduce=fused)), N * K * 2 + T * K * 2 + T * N * (4 if fp32 else 2), 2.0 * T * N * K
+    if name in ("attention_decode", "attention_prefill"):
+        bs = 16
+        rng = np.random.RandomState(2)
+        decode = name == "attention_decode"
+        B = T if decode else max(1, T // 1024)
+        q_lens = [1] * B if decode else [T // B] * B
+        past = (rng.randint(128, 2049, size=B) + 64).tolist() if decode else [0] * B
+        cols = max((p + q + bs - 1) // bs for p, q in zip(past, q_lens))
+        nblk = sum((p + q + bs - 1) // bs for p, q in zip(past, q_lens)) + 4
+        Lk = min(L, 4)
+        kc = [_bf(nblk * bs, HKV, D, std=1.0) for _ in range(Lk)]
+        vc = [_bf(nblk * bs, HKV, D, std=1.0) for _ in range(Lk)]
+        table = torch.zeros(B, cols, dtype=torch.int32)
+        used = 0
+        for b in range(B):
+            n = (past[b] + q_lens[b] + bs - 1) // bs
+            table[b, :n] = torch.arange(used, used + n, dtype=torch.int32)
+            used += n
+        table = table.cuda()
+        Tq = sum(q_lens)
+        qkv = _bf(Tq, (HQ + 2 * HKV) * D, std=1.0)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32).cuda()
+        pl = torch.tensor(past, dtype=torch.int32).cuda()
+        kv_tokens = sum(p + q for p, q in zip(past, q_lens))
+        nbytes = kv_tokens * HKV * D * 2 * 2 + Tq * HQ * D * 2 * 2
+        flops = sum(4.0 * HQ * D * (q * p + q * (q + 1) / 2) for p, q in zip(past, q_lens))
+        return (lambda i: ops.paged_attention(qkv, kc[i % Lk], vc[i % Lk], cu, pl, table, bs, HQ, HKV, D, 1 / math.sqrt(D),
+                                              max_q_len=max(q_lens), max_kv_len=max(p + q for p, q in zip(past, q_lens)))), nbytes, flops
+    if name == "norm":
+        x, r, w = _bf(T, H, std=1.0), _bf(T, H, std=1.0), _bf(H, std=1.0)
+        return (lambda i: ops.norm(x, w, 1e-5, r)), T * H * 2 * 4, 0.0
+    if name == "rope":
+        qkv = _bf(T, (HQ + 2 * HKV) * D, std=1.0)
+        pos = torch.arange(T, dtype=torch.int32, device="cuda")
+        slots = torch.arange(T, dtype=torch.int32, device="cuda")
+        cos, sin = torch.randn(4096, D // 2, device="cuda"), torch.randn(4096, D // 2, device="cuda")
+        kc, vc = _bf(T + 16, HKV, D), _bf(T + 16, HKV, D)
+        return (lambda i: ops.rope_kv_append(qkv, pos, slots, cos, sin, kc, vc, HQ, HKV, D, D)), T * (HQ + 2 * HKV) * D * 2 * 2, 0.0
+    if name in ("sample", "argmax"):
+        logits = torch.randn(T, V, device="cuda") * 3
+        k = torch.full((T,), 50, dtype=torch.int32, device="cuda")
+        p = torch.full((T,), 0.9, device="cuda")
+        t = torch.full((T,), 0.7, device="cuda")
+        seeds = torch.arange(T, dtype=torch.int64, device="cuda")
+        pos = torch.zeros(T, dtype=torch.int32, device="cuda")
+        if name == "argmax":
+            return (lambda i: ops.argmax(logits)), T * V * 4, 0.0
+        return (lambda i: ops.sample(logits, k, p, t, seeds, pos)), T * V * 4, 0.0
+    raise SystemExit(f"unknown case {name}")
+
+
+ALL = ["gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down", "gemm_lm_head", "w4_qkv", "w4_down", "attention_decode", "norm", "rope",
+       "sample", "argmax"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--json", default="")
+    ap.add_argument("--tp", type=int, default=1, help="use the per-rank shapes of this tensor-parallel degree")
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    comm = None
+    if a.tp > 1:
+        from ..parallel.symm import LocalComm
+        comm = LocalComm(torch.device("cuda", 0))
+    hbm, tflops, src = _peaks()
+    out = {}
+    for name in (ALL if a.case == "all" else [a.case]):
+        T = a.tokens if name != "gemm_prefill" and name != "attention_prefill" else max(a.tokens, 2048)
+        fn, nbytes, flops = build_case(name, T, a.layers, a.tp)
+        us = _time_graph(fn, a.iters if name not in ("gemm_lm_head", "sample", "argmax") else min(a.iters, 4))
+        gbs, tf = nbytes / us / 1e3, flops / us / 1e6
+        out[name] = {"tokens": T, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tf, 1),
+                     "frac_hbm": round(gbs / hbm, 3), "frac_bf16": round(tf / tflops, 3), "peaks": src}
+        print(f"{name:18s} T={T:5d} {us:9.2f} us  {gbs:8.1f} GB/s ({gbs / hbm:5.2f} of {src} HBM)  {tf:8.1f} TFLOP/s ({tf / tflops:5.2f} of {src} bf16)",
+              flush=True)
+        del fn
+        torch.cuda.empty_cache()
+    ops.check_kernel_status()
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump(out, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

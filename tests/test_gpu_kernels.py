@@ -98,6 +98,30 @@ def test_gemm_fused_allreduce_world_of_one(M, N, K, splits):
         comm.close()
 
 
+def test_standalone_collectives_world_of_one():
+    """all-reduce / all-gather / reduce-scatter kernels over the symmetric buffers with a single rank (push, stamp,
+    wait, combine, epoch) interleaved with the fused GEMM on the same buffers."""
+    from onnxruntime_genai_b200.parallel.symm import LocalComm
+    comm = LocalComm(torch.device("cuda", 0))
+    try:
+        x = _rand(64, 4096, seed=21)
+        r = _rand(64, 4096, seed=22)
+        w = _rand(256, 4096, std=0.05, seed=23)
+        for i in range(3):
+            assert torch.equal(comm.all_reduce(x), x)
+            _close(comm.all_reduce(x, residual=r), x.float() + r.float(), rtol=1e-2, atol=1e-2)
+            y = ops.linear(x, w, all_reduce=True)     # same buffers, different slice-to-slot mapping
+            assert torch.equal(comm.all_gather(x.float()), x.float()[None])
+            assert torch.equal(comm.reduce_scatter(x[None].contiguous()), x)
+            _close(y, ref.linear(x.cpu(), w.cpu()), rtol=3e-2, atol=0.06)
+            small = _rand(8, seed=24 + i)
+            assert torch.equal(comm.all_reduce(small), small)
+        ops.check_kernel_status()
+        assert not comm.fits(_rand(4096, 4096, seed=25))
+    finally:
+        comm.close()
+
+
 def test_gemm_strided_activation():
     M, K, N = 20, 256, 256
     big = _rand(M, 3 * K, seed=11)
@@ -376,3 +400,145 @@ def test_gemm_w4_gate_up_pair():
     _close(ops.gate_up_act(x, il), want, rtol=3e-2, atol=0.05)
     _close(ops.gate_up_act(x, plain), want, rtol=3e-2, atol=0.05)
     ops.check_kernel_status()
+
+
+# ------------------------------------------------------------------------------------------- mixture of experts
+@pytest.mark.parametrize("T,E,k,mode", [(1, 8, 2, 0), (37, 32, 4, 0), (64, 128, 8, 2), (300, 60, 4, 1)])
+def test_moe_topk_matches_torch(T, E, k, mode):
+    logits = _rand(T, E, std=2.0, dtype=torch.float32, seed=31)
+    plan = ops.moe_route(logits, k, mode)
+    v, i = torch.topk(logits, k, dim=-1)
+    if mode == 0:
+        w = torch.softmax(v, dim=-1)
+    else:
+        w = torch.softmax(logits, dim=-1).gather(1, i)
+        if mode == 2:
+            w = w / w.sum(-1, keepdim=True)
+    assert plan.topk_idx.cpu().tolist() == i.cpu().tolist()
+    _close(plan.topk_w, w, 1e-4, 1e-6)
+    # grouping: every assignment appears once, rows of an expert are contiguous, tiles cover exactly those rows
+    off = plan.expert_offsets.cpu().tolist()
+    inv = plan.inv_pos.cpu().reshape(-1).tolist()
+    src = plan.sorted_token.cpu().tolist()
+    flat = i.cpu().reshape(-1).tolist()
+    assert sorted(inv) == list(range(T * k)) and off[-1] == T * k
+    for a, pos in enumerate(inv):
+        assert off[flat[a]] <= pos < off[flat[a] + 1] and src[pos] == a // k
+    nt = int(plan.num_tiles.cpu()[0])
+    covered = []
+    for t in range(nt):
+        e, r0, n = int(plan.tile_expert[t]), int(plan.tile_row0[t]), int(plan.tile_rows[t])
+        assert off[e] <= r0 and r0 + n <= off[e + 1] and 0 < n <= plan.bt
+        covered += list(range(r0, r0 + n))
+    assert sorted(covered) == list(range(T * k)) and nt <= plan.max_tiles
+
+
+def _moe_reference(x, router_w, router_b, gu_w, gu_b, dn_w, dn_b, k, alpha, limit, lo=0, hi=None):
+    """fp32 loop over experts; gu_w [E, 2I, H] rows even = gate, odd = up."""
+    x = x.float()
+    logits = x @ router_w.float().t() + router_b.float()
+    v, i = torch.topk(logits, k, dim=-1)
+    w = torch.softmax(v, dim=-1)
+    out = torch.zeros_like(x)
+    hi = gu_w.shape[0] if hi is None else hi
+    for e in range(lo, hi):
+        tok, slot = (i == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        gu = x[tok].to(torch.bfloat16).float() @ gu_w[e].float().t() + gu_b[e].float()
+        g, u = gu[:, 0::2].clamp(max=limit), gu[:, 1::2].clamp(-limit, limit)
+        act = (g * torch.sigmoid(alpha * g) * (u + 1)).to(torch.bfloat16).float()
+        y = (act @ dn_w[e].float().t() + dn_b[e].float()).to(torch.bfloat16).float()
+        out.index_add_(0, tok, y * w[tok, slot][:, None])
+    return out, logits
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(3, 4, 2, 128, 64), (64, 32, 4, 256, 192), (700, 8, 2, 320, 128), (130, 16, 4, 2880, 64)])
+def test_moe_grouped_gemm_matches_expert_loop(T, E, k, H, I):
+    x = _rand(T, H, std=1.0, seed=41)
+    router_w, router_b = _rand(E, H, std=0.1, seed=42), _rand(E, std=0.1, seed=43)
+    gu_w, gu_b = _rand(E, 2 * I, H, std=0.05, seed=44), _rand(E, 2 * I, std=0.1, seed=45)
+    dn_w, dn_b = _rand(E, H, I, std=0.05, seed=46), _rand(E, H, std=0.1, seed=47)
+    alpha, limit = 1.702, 7.0
+    want, logits_ref = _moe_reference(x, router_w, router_b, gu_w, gu_b, dn_w, dn_b, k, alpha, limit)
+    logits = ops.linear(x, router_w, router_b, out_fp32=True)
+    # near-ties in the router would legitimately pick different experts: require a clear margin in this test's data
+    v = torch.topk(logits_ref, k + 1, dim=-1).values
+    assert float((v[:, k - 1] - v[:, k]).min()) > 1e-3 or T > 100
+    gw, gb = ops.interleave_experts_gate_up(gu_w), ops.interleave_experts_gate_up(gu_b)
+    for lo, hi in ((0, E), (E // 2, E)):
+        plan = ops.moe_route(logits, k, 0, (lo, hi))
+        xs = ops.gather_rows(x, plan.sorted_token)
+        h = ops.moe_gemm(xs, gw[lo:hi].contiguous(), plan, gb[lo:hi].contiguous(), act_kind=2, alpha=alpha, limit=limit)
+        y = ops.moe_gemm(h, dn_w[lo:hi].contiguous(), plan, dn_b[lo:hi].contiguous())
+        got = ops.moe_combine(y, plan)
+        ops.check_kernel_status()
+        ref_out = want if (lo, hi) == (0, E) else _moe_reference(x, router_w, router_b, gu_w, gu_b, dn_w, dn_b, k, alpha, limit, lo, hi)[0]
+        bad = ((got.float() - ref_out.to(got.device)).abs() > 0.03 + 0.03 * ref_out.abs().to(got.device)).float().mean().item()
+        assert bad < (0.002 if T <= 100 else 0.02), f"{bad:.4f} of the outputs differ (experts {lo}..{hi})"
+
+
+# ------------------------------------------------------------------------------------------- sampled speculative verify
+def test_verify_sampled_preserves_the_target_distribution():
+    """Rejection sampling theorem: whatever the proposal, the first committed token follows the target's sampled
+    distribution; and the accept probability is min(1, p(x)/q(x))."""
+    V, n, k, p, t = 300, 3000, 20, 0.9, 0.8
+    g = torch.Generator().manual_seed(7)
+    rows = (torch.randn(2, V, generator=g) * 2.0).float()
+    ids, probs = ref.sampled_distribution(rows[0], k, p, t)
+    expect = torch.zeros(V, dtype=torch.double)
+    expect[ids] = probs
+    logits = rows.to(DEV).contiguous()
+    top = int(ids[0])
+    second = int(ids[1])
+    # (a) deterministic proposal of the most likely token, (b) a sparse proposal distribution that over-weights the second token
+    q_sparse = (np.asarray([top, second, int(ids[2])], dtype=np.int32), np.asarray([0.2, 0.7, 0.1], dtype=np.float32))
+    for draft_tok, q in ((top, None), (second, q_sparse)):
+        counts = torch.zeros(V, dtype=torch.double)
+        acc = 0
+        for s in range(n):
+            a, commit, ap = ops.verify_sampled(logits, [draft_tok], [q], k, p, t, seed=1000 + s, first_position=5)
+            assert len(commit) == a + 1 and (a == 0 or commit[0] == draft_tok)
+            counts[commit[0]] += 1
+            acc += a
+        px = float(expect[draft_tok])
+        qx = 1.0 if q is None else float(q[1][list(q[0]).index(draft_tok)])
+        assert abs(ap[0] - min(1.0, px / qx)) < 1e-4
+        assert abs(acc / n - min(1.0, px / qx)) < 0.04
+        if q is None:
+            # one-hot proposal: committed token ~ p exactly (accept w.p. p(x), else residual p without x)
+            tv = 0.5 * (counts / n - expect).abs().sum().item()
+            assert tv < 0.06, f"total variation {tv:.3f}"
+        else:
+            # the draft token itself was drawn by us, not from q, so only the conditional law is checked:
+            # given rejection the replacement follows max(0, p - q) renormalised
+            resid = (expect - torch.zeros(V, dtype=torch.double).index_put((torch.tensor(q[0]).long(),), torch.tensor(q[1]).double())).clamp(min=0)
+            resid = resid / resid.sum()
+            rej = counts.clone()
+            rej[draft_tok] -= acc
+            tv = 0.5 * (rej / rej.sum() - resid).abs().sum().item()
+            assert tv < 0.08, f"residual total variation {tv:.3f}"
+
+
+def test_verify_sampled_multi_token_and_bonus():
+    V, k = 1000, 50
+    x = _rand(5, V, dtype=torch.float32, seed=77) * 3
+    # proposals equal to each row's arg max with sharp logits are accepted; the bonus token equals the plain sampler's draw
+    sharp = x.clone()
+    am = sharp.argmax(-1)
+    sharp[torch.arange(5), am] += 60.0
+    draft = am[:4].cpu().tolist()
+    a, commit, ap = ops.verify_sampled(sharp, draft, [None] * 4, k, 0.95, 0.7, seed=11, first_position=30)
+    assert a == 4 and commit[:4] == draft and all(v > 0.999 for v in ap)
+    tk = torch.full((1,), k, dtype=torch.int32, device=DEV)
+    one = ops.sample(sharp[4:5].contiguous(), tk, torch.full((1,), 0.95, device=DEV), torch.full((1,), 0.7, device=DEV),
+                     torch.full((1,), 11, dtype=torch.int64, device=DEV), torch.full((1,), 34, dtype=torch.int32, device=DEV))
+    assert commit[4] == int(one[0])
+    # a proposal outside the target's top-k is rejected at once and replaced by a token of the target's support
+    worst = int(x[0].argmin())
+    a, commit, ap = ops.verify_sampled(x, [worst, draft[1], draft[2], draft[3]], [None] * 4, k, 0.95, 0.7, seed=12, first_position=30)
+    assert a == 0 and len(commit) == 1 and ap[0] == 0.0
+    assert commit[0] in torch.topk(x[0], k).indices.cpu().tolist()
+    # twice in a row: the kernel's completion counter resets itself
+    b = ops.verify_sampled(x, [worst, draft[1], draft[2], draft[3]], [None] * 4, k, 0.95, 0.7, seed=12, first_position=30)
+    assert b[0] == a and b[1] == commit
