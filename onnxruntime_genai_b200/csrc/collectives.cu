@@ -1,15 +1,16 @@
-// Stand-alone collectives over the symmetric NVLink buffers (the same buffers, arrival stamps and call
+// Stand-alone collectives over the symmetric NVLink buffers (the same buffers, flagged lines and call
 // counter as the all-reduce fused into the GEMM epilogue, gemm_common.cuh): one-shot all-reduce,
-// all-gather and reduce-scatter for bf16 tensors that did not come out of a fused GEMM, e.g. the
+// all-gather and reduce-scatter for tensors that did not come out of a fused GEMM, e.g. the
 // expert-parallel combine or the logits gather.  The reference has no communication layer; the bar these
 // are measured against is the NCCL call of the same name.
 //
-// Every block owns one contiguous chunk of the payload and one arrival slot:
-//   all-reduce      push chunk to every rank (plane = source rank) | stamp | wait | out = sum over planes
-//   all-gather      push chunk to every rank (plane = source rank) | stamp | wait | out[s * n + i] = plane s
-//   reduce-scatter  push chunk of slice j to rank j only           | stamp | wait | out = sum over planes
-// Transfers are plain 16-byte peer stores; waits are bounded (status word, then the kernel finishes without
-// hanging); the last block closes the call's epoch.  No multimem / NVLS: ranks may leave between steps.
+// Every thread owns 16-byte vectors of the payload; a vector travels as two flagged lines:
+//   all-reduce      push to every rank (plane = source rank) | collect all planes | out = sum (rank order)
+//   all-gather      push to every rank (plane = source rank) | collect all planes | out[s * n + i] = plane s
+//   reduce-scatter  push vector of slice j to rank j only    | collect all planes | out = sum (rank order)
+// Transfers are 16-byte peer stores carrying their own arrival flag; waits are bounded (status word, then the
+// kernel finishes without hanging); the last block closes the call's epoch.  No multimem / NVLS: ranks may
+// leave between steps.
 #include "gemm_common.cuh"
 #include "kernels.h"
 
@@ -19,53 +20,46 @@ enum CollMode { COLL_ALLREDUCE = 0, COLL_ALLGATHER = 1, COLL_REDUCE_SCATTER = 2 
 
 constexpr int COLL_THREADS = 256;
 
-// n: elements per rank plane (all-reduce: tensor size; all-gather: shard size; reduce-scatter: output slice size).
+// n: bf16 elements per rank plane (all-reduce: tensor size; all-gather: shard size; reduce-scatter: output slice size).
 template <int MODE>
 __global__ void __launch_bounds__(COLL_THREADS)
 collective_kernel(const CommParams c, const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
                   const __nv_bfloat16* __restrict__ residual, long long n, int* status) {
-  __shared__ uint32_t epoch_sh;
-  const int tid = threadIdx.x;
-  if (tid == 0) epoch_sh = *reinterpret_cast<volatile uint32_t*>(c.epoch);
-  __syncthreads();
-  const uint32_t e = epoch_sh;
-  const size_t plane = size_t(c.plane_elems);
-  const size_t par_off = size_t(e & 1) * c.world * plane;
+  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(c.epoch);   // stable: only this call's last block changes it
+  const uint32_t flag = comm_flag(e);
+  const size_t plane_lines = size_t(c.plane_elems) / 4;
+  const size_t par_off = size_t(e & 1) * c.world * plane_lines;
   const long long vecs = n / 8;
-  const long long per = (vecs + gridDim.x - 1) / gridDim.x;
-  const long long v0 = blockIdx.x * per, v1 = min(vecs, v0 + per);
+  const long long stride = (long long)gridDim.x * COLL_THREADS;
+  const long long first = (long long)blockIdx.x * COLL_THREADS + threadIdx.x;
 
   // ---- push
-  for (long long v = v0 + tid; v < v1; v += COLL_THREADS) {
-    const size_t off = par_off + size_t(c.rank) * plane + size_t(v) * 8;
+  for (long long v = first; v < vecs; v += stride) {
+    const size_t line = par_off + size_t(c.rank) * plane_lines + size_t(v) * 2;
     if (MODE == COLL_REDUCE_SCATTER) {
-      for (int r = 0; r < c.world; ++r)
-        *reinterpret_cast<uint4*>(c.buf[r] + off) = *reinterpret_cast<const uint4*>(in + size_t(r) * n + size_t(v) * 8);
+      for (int r = 0; r < c.world; ++r) {
+        const uint4 q = *reinterpret_cast<const uint4*>(in + size_t(r) * n + size_t(v) * 8);
+        st_line(c.buf[r] + line, q.x, q.y, flag);
+        st_line(c.buf[r] + line + 1, q.z, q.w, flag);
+      }
     } else {
       const uint4 q = *reinterpret_cast<const uint4*>(in + size_t(v) * 8);
-      for (int r = 0; r < c.world; ++r) *reinterpret_cast<uint4*>(c.buf[r] + off) = q;
+      for (int r = 0; r < c.world; ++r) {
+        st_line(c.buf[r] + line, q.x, q.y, flag);
+        st_line(c.buf[r] + line + 1, q.z, q.w, flag);
+      }
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  // ---- stamp and wait: lane r handles rank r
-  if (tid < c.world) {
-    st_release_sys(c.flag[tid] + size_t(blockIdx.x) * COMM_MAX_WORLD + c.rank, e + 1);
-    const uint32_t* mine = c.flag[c.rank] + size_t(blockIdx.x) * COMM_MAX_WORLD + tid;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t spins = 0;
-    const bool poisoned = *reinterpret_cast<volatile int*>(status) != 0;
-    while (!poisoned && int32_t(ld_acquire_sys(mine) - (e + 1)) < 0) {
-      if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 2000000000ull) { atomicMax(status, OGB_ERR_WAIT_PEER); break; }
-    }
-  }
-  __syncthreads();
-  // ---- combine from the local receive buffer
-  const __nv_bfloat16* base = c.buf[c.rank] + par_off;
-  for (long long v = v0 + tid; v < v1; v += COLL_THREADS) {
+  // ---- collect the same vectors of every rank from the local receive buffer
+  bool dead = *reinterpret_cast<volatile int*>(status) != 0;
+  const uint4* base = c.buf[c.rank] + par_off;
+  for (long long v = first; v < vecs; v += stride) {
     if (MODE == COLL_ALLGATHER) {
-      for (int r = 0; r < c.world; ++r)
-        *reinterpret_cast<uint4*>(out + size_t(r) * n + size_t(v) * 8) = ld_cg_u4(base + size_t(r) * plane + size_t(v) * 8);
+      for (int r = 0; r < c.world; ++r) {
+        const uint4 q0 = wait_line(base + size_t(r) * plane_lines + size_t(v) * 2, flag, dead, status);
+        const uint4 q1 = wait_line(base + size_t(r) * plane_lines + size_t(v) * 2 + 1, flag, dead, status);
+        *reinterpret_cast<uint4*>(out + size_t(r) * n + size_t(v) * 8) = make_uint4(q0.x, q0.z, q1.x, q1.z);
+      }
     } else {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (residual) {
@@ -74,8 +68,9 @@ collective_kernel(const CommParams c, const __nv_bfloat16* __restrict__ in, __nv
         acc[0] = a.x; acc[1] = a.y; acc[2] = b.x; acc[3] = b.y; acc[4] = cc.x; acc[5] = cc.y; acc[6] = d.x; acc[7] = d.y;
       }
       for (int r = 0; r < c.world; ++r) {   // rank order: bit-identical on every rank
-        const uint4 q = ld_cg_u4(base + size_t(r) * plane + size_t(v) * 8);
-        const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), cc = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+        const uint4 q0 = wait_line(base + size_t(r) * plane_lines + size_t(v) * 2, flag, dead, status);
+        const uint4 q1 = wait_line(base + size_t(r) * plane_lines + size_t(v) * 2 + 1, flag, dead, status);
+        const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), cc = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
         acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += cc.x; acc[5] += cc.y; acc[6] += d.x; acc[7] += d.y;
       }
       *reinterpret_cast<uint4*>(out + size_t(v) * 8) =
@@ -84,7 +79,7 @@ collective_kernel(const CommParams c, const __nv_bfloat16* __restrict__ in, __nv
   }
   // ---- close the epoch
   __syncthreads();
-  if (tid == 0) {
+  if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(c.epoch + 1, 1u) == gridDim.x - 1) {
       c.epoch[1] = 0;
@@ -108,8 +103,8 @@ OGB_API int ogb_collective(int mode, const void* in, void* out, const void* resi
   if (n <= 0) return 0;
   if ((n % 8) || n > cp->plane_elems) return -1;
   if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15) return -1;
-  long long blocks = (n / 8 + COLL_THREADS * 4 - 1) / (COLL_THREADS * 4);   // ~4 vectors per thread
-  const long long cap = sm_count * 2 < cp->max_slots ? sm_count * 2 : cp->max_slots;
+  long long blocks = (n / 8 + COLL_THREADS * 2 - 1) / (COLL_THREADS * 2);   // ~2 vectors per thread
+  const long long cap = sm_count * 2;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);

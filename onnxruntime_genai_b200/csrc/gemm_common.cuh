@@ -15,18 +15,18 @@ constexpr int GEMM_THREADS = 192;
 constexpr int W_TILE_BYTES = GEMM_BLOCK_N * GEMM_BLOCK_K * 2;  // 16 KiB
 constexpr int COMM_MAX_WORLD = 8;
 
-// Symmetric buffers of the fused all-reduce.  All fused calls of a device form one sequence numbered by a device-side
-// epoch (the same sequence on every rank): call e writes parity e & 1 of the receive buffers and stamps its arrival
-// flags with e + 1.  A rank cannot start call e + 2 (which reuses the parity of call e) before it has finished call e + 1,
-// i.e. before every peer has arrived at every slice of call e + 1 and therefore finished reading call e: the scheme
-// needs no second barrier and does not depend on how a call maps slices to CTAs.
+// Symmetric buffers of the fused all-reduce.  Payload travels in 16-byte lines {data, flag, data, flag}: eight bytes
+// of data and the call's flag twice, written with one 16-byte peer store whose two halves are each atomic, so a
+// reader that sees the expected flag in both halves has the data: no fence, no separate arrival flag, no barrier.
+// All fused calls of a device form one sequence numbered by a device-side epoch (the same sequence on every rank): call
+// e writes parity e & 1 of the receive buffers with flag e + 1.  A rank cannot start call e + 2 (which reuses the
+// parity of call e) before it has finished call e + 1, i.e. before it has read every peer's lines of call e + 1, which
+// those peers wrote after finishing call e: no second barrier, whatever the mapping of slices to CTAs.
 struct CommParams {
   int world, rank;                        // world <= 1 with buf[0] == nullptr disables the fused all-reduce
-  __nv_bfloat16* buf[COMM_MAX_WORLD];     // receive buffer of every rank: [2 parities][world sources][plane_elems]
-  uint32_t* flag[COMM_MAX_WORLD];         // arrival stamps of every rank: [max_slots][COMM_MAX_WORLD sources]
+  uint4* buf[COMM_MAX_WORLD];             // receive buffer of every rank: [2 parities][world sources][plane_elems / 4 lines]
   uint32_t* epoch;                        // this rank: [0] = calls finished so far, [1] = CTAs of the running call that are done
-  long long plane_elems;
-  int max_slots;
+  long long plane_elems;                  // bf16 elements per source plane (4 per line)
 };
 
 // Registered symmetric buffers of a device (gemm_tcgen05.cu); nullptr when the index is out of range.
@@ -94,18 +94,35 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint32_t comm_flag(uint32_t epoch) { const uint32_t f = epoch + 1u; return f ? f : 1u; }
+// One line: 8 bytes of data + the flag in both halves (each 8-byte half of the store is atomic).
+__device__ __forceinline__ void st_line(uint4* p, uint32_t d0, uint32_t d1, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(d0), "r"(flag), "r"(d1), "r"(flag) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {  // bypass L1: the data was written by a peer GPU
+__device__ __forceinline__ uint4 ld_line(const uint4* p) {
   uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
+}
+// Waits (bounded) for a line of this call.  `dead` is the thread's give-up state: set when the device already carries a
+// failed wait or when this wait runs out (the status word is updated), after which lines are taken as they are.
+__device__ __forceinline__ uint4 wait_line(const uint4* p, uint32_t flag, bool& dead, int* status) {
+  uint4 v = ld_line(p);
+  if (v.y == flag && v.w == flag) return v;
+  if (dead) return v;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    v = ld_line(p);
+    if (v.y == flag && v.w == flag) return v;
+    if ((++spins & 0x3f) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0 || global_timer_ns() - t0 > 2000000000ull) {
+        atomicMax(status, OGB_ERR_WAIT_PEER);
+        dead = true;
+        return v;
+      }
+    }
+  }
 }
 
 // Epilogue shared by the linear-layer kernels.  Called by all 192 threads of the CTA once the MMA issuer has
@@ -203,16 +220,15 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     };
 
     uint32_t use = 0;   // epoch of this call
-    int slot = 0;
     if (comm_on) {
-      slot = (m_tile * gridDim.x + n_tile) * gridDim.z + my_rank;
       // read after griddepcontrol.wait: the previous call has finished and published its increment
       if (et == 0) *use_slot = *reinterpret_cast<volatile uint32_t*>(p.comm.epoch);
       asm volatile("bar.sync 1, 128;" ::: "memory");
       use = *use_slot;
     }
-    const size_t plane = size_t(p.comm.plane_elems);
-    const size_t par_off = size_t(use & 1) * p.comm.world * plane;
+    const uint32_t flag = comm_flag(use);
+    const size_t plane_lines = size_t(p.comm.plane_elems) / 4;
+    const size_t par_off = size_t(use & 1) * p.comm.world * plane_lines;
 
     for (int item = et; item < items; item += 128) {
       const int mc = c_begin + item / OCT, oc = item % OCT;
@@ -244,44 +260,36 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
       if (!comm_on) {
         store8(m, col, v);
       } else if (col < n_out) {
-        // push this rank's partial (bf16) into every rank's receive buffer: plain peer stores
-        const uint4 pk = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-        const size_t off = par_off + size_t(p.comm.rank) * plane + size_t(m) * n_out + col;
-        for (int r = 0; r < p.comm.world; ++r) *reinterpret_cast<uint4*>(p.comm.buf[r] + off) = pk;
+        // push this rank's partial (bf16) into every rank's receive buffer: two flagged lines per 8 values
+        const size_t line = par_off + size_t(p.comm.rank) * plane_lines + (size_t(m) * n_out + col) / 4;
+        const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
+        for (int r = 0; r < p.comm.world; ++r) {
+          st_line(p.comm.buf[r] + line, d0, d1, flag);
+          st_line(p.comm.buf[r] + line + 1, d2, d3, flag);
+        }
       }
     }
 
     if (comm_on) {
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et < p.comm.world) {
-        // lane r: stamp this rank's arrival on rank r, then wait for rank r's stamp here
-        st_release_sys(p.comm.flag[et] + size_t(slot) * COMM_MAX_WORLD + p.comm.rank, use + 1);
-        const uint32_t* mine = p.comm.flag[p.comm.rank] + size_t(slot) * COMM_MAX_WORLD + et;
-        const uint64_t t0 = global_timer_ns();
-        uint32_t spins = 0;
-        // Once any kernel of this device has reported a failed wait, later kernels do not wait again: a broken
-        // peer (or a broken set-up) then costs one time limit in total, not one per launch.
-        const bool poisoned = *reinterpret_cast<volatile int*>(p.status) != 0;
-        while (!poisoned && int32_t(ld_acquire_sys(mine) - (use + 1)) < 0) {
-          if ((++spins & 0xff) == 0 && global_timer_ns() - t0 > 2000000000ull) { fail(OGB_ERR_WAIT_PEER); break; }
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // Every thread collects the lines of the items it pushed itself: its own pushes are long under way, and the peers'
+      // lines of the same items arrive at about the same time.  The data carries its own arrival flag.
+      bool dead = *reinterpret_cast<volatile int*>(p.status) != 0;
       for (int item = et; item < items; item += 128) {
         const int mc = c_begin + item / OCT, oc = item % OCT;
         const int m = row0 + mc;
         const int col = col0 + oc * 8;
         if (mc >= rows || col >= n_out) continue;
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const __nv_bfloat16* base = p.comm.buf[p.comm.rank] + par_off + size_t(m) * n_out + col;
-        for (int r = 0; r < p.comm.world; ++r) {
-          const uint4 q = ld_cg_u4(base + size_t(r) * plane);
-          const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+        const uint4* base = p.comm.buf[p.comm.rank] + par_off + (size_t(m) * n_out + col) / 4;
+        for (int r = 0; r < p.comm.world; ++r) {   // rank order: bit-identical sums on every rank
+          const uint4 q0 = wait_line(base + size_t(r) * plane_lines, flag, dead, p.status);
+          const uint4 q1 = wait_line(base + size_t(r) * plane_lines + 1, flag, dead, p.status);
+          const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
           v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
         }
         store8(m, col, v);
       }
+      if (dead) *abort_flag = 1;
     }
   }
   if (p.splits > 1) {

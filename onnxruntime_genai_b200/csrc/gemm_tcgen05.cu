@@ -28,12 +28,13 @@
 //
 // Tensor-parallel all-reduce (row-parallel o_proj / down_proj in decode), fused: instead of
 // storing its reduced slice, a CTA pushes it (bf16) into the receive buffer of EVERY rank with
-// plain peer stores over NVLink, stamps that slice's arrival flag on every rank
-// (st.release.sys), waits (bounded) until its own flags show all ranks' arrivals, then sums
-// the world's partials from its local buffer in rank order (bit-identical on every rank), adds
-// the residual and stores.  Arrival stamps only grow and buffers alternate by the parity of a call
-// counter kept on the device, so the kernel replays unchanged inside CUDA graphs.  The
-// reference has no distributed code at all; the comparison bar is GEMM + ncclAllReduce.
+// 16-byte peer stores over NVLink that carry the call's flag next to the data, then collects
+// (bounded waits on the flags) the same slice of every rank from its local buffer, sums in rank
+// order (bit-identical on every rank), adds the residual and stores.  No fence, no separate
+// arrival flag, no barrier between ranks: one NVLink write latency per all-reduce.  Buffers
+// alternate by the parity of a call counter kept on the device, so the kernel replays unchanged
+// inside CUDA graphs.  The reference has no distributed code at all; the comparison bar is
+// GEMM + ncclAllReduce.
 //
 // Every wait is bounded: when one runs out the kernel records a status code, waits (bounded) for
 // its own TMA copies in flight, still meets its barriers, frees its tensor memory and returns.
@@ -284,17 +285,14 @@ OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
 }
 
 // Registers this rank's view of the symmetric buffers (peer-mapped pointers) for a device.
-// buf[r] / flag[r]: rank r's receive buffer / arrival counters as mapped into this process;
-// ([max_slots][8] words, zero-initialised); epoch: two local zero-initialised words.  world = 0 unregisters.
-OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* epoch, long long plane_elems,
-                              int max_slots) {
-  if (device < 0 || device >= 16 || world < 0 || world > COMM_MAX_WORLD) return -1;
+// buf[r]: rank r's receive buffer as mapped into this process, 2 * world * plane_elems * 4 bytes, zero-initialised
+// (flagged lines: every 8 payload bytes travel in a 16-byte line); epoch: two local zero-initialised words.
+// world = 0 unregisters.
+OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void* epoch, long long plane_elems) {
+  if (device < 0 || device >= 16 || world < 0 || world > COMM_MAX_WORLD || (plane_elems % 8)) return -1;
   CommParams c = {};
-  c.world = world; c.rank = rank; c.plane_elems = plane_elems; c.max_slots = max_slots;
-  for (int r = 0; r < world; ++r) {
-    c.buf[r] = static_cast<__nv_bfloat16*>(buf[r]);
-    c.flag[r] = static_cast<uint32_t*>(flag[r]);
-  }
+  c.world = world; c.rank = rank; c.plane_elems = plane_elems;
+  for (int r = 0; r < world; ++r) c.buf[r] = static_cast<uint4*>(buf[r]);
   c.epoch = static_cast<uint32_t*>(epoch);
   g_comm[device] = c;
   return 0;
@@ -338,7 +336,7 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
     const CommParams& c = g_comm[device];
     const long long n_out = act_pair ? N / 2 : N;
-    if (n_out % 8 || (long long)M * n_out > c.plane_elems || n_tiles * m_tiles * splits > c.max_slots) return -2;
+    if (n_out % 8 || (long long)M * n_out > c.plane_elems) return -2;
     p.comm = c;
   }
   dim3 grid(n_tiles, m_tiles, splits);

@@ -18,7 +18,7 @@ int ogb_sm_count(int device);
 // ---- gemm_tcgen05.cu
 int ogb_gemm_token_tile(int M, int dual);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
-int ogb_comm_register(int device, int world, int rank, void** buf, void** flag, void* epoch, long long plane_elems, int max_slots);
+int ogb_comm_register(int device, int world, int rank, void** buf, void* epoch, long long plane_elems);
 // flags: bit 0 fp32 output, bit 1 paired silu(gate)*up epilogue, bit 2 fused tensor-parallel all-reduce
 int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
                   const void* residual, int ldr, int flags, int splits, int device, int* status, int sm_count, void* stream);

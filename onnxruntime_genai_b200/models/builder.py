@@ -132,8 +132,8 @@ def quantize_int4_block32(w: torch.Tensor, symmetric: bool = False, block: int =
         q = torch.clamp(torch.round(wb / scale[..., None]) + 8, 0, 15)
         zp = None
     else:
-        mn = torch.minimum(wb.amin(-1), torch.zeros(()))
-        mx = torch.maximum(wb.amax(-1), torch.zeros(()))
+        mn = wb.amin(-1).clamp(max=0.0)
+        mx = wb.amax(-1).clamp(min=0.0)
         scale = (mx - mn) / 15.0
         scale = torch.where(scale == 0, torch.ones_like(scale), scale)
         zpf = torch.clamp(torch.round(-mn / scale), 0, 15)
@@ -145,7 +145,7 @@ def quantize_int4_block32(w: torch.Tensor, symmetric: bool = False, block: int =
     if zp is not None:
         nb = K // block
         if nb % 2:
-            zp = torch.cat([zp, torch.full((N, 1), 8, dtype=torch.uint8)], dim=1)
+            zp = torch.cat([zp, torch.full((N, 1), 8, dtype=torch.uint8, device=zp.device)], dim=1)
         zp_packed = (zp[:, 0::2] | (zp[:, 1::2] << 4)).contiguous()
     return packed, scale, zp_packed
 
@@ -160,7 +160,7 @@ def dequantize_int4_block32(qweight, scales, zero_points, N: int, K: int, block:
         z = torch.as_tensor(zero_points).view(N, -1)
         zz = torch.stack([(z & 0xF), (z >> 4)], dim=-1).view(N, -1)[:, :nb].float()
     else:
-        zz = torch.full((N, nb), 8.0)
+        zz = torch.full((N, nb), 8.0, device=q.device)
     s = torch.as_tensor(scales).float().view(N, nb)
     return ((w - zz[..., None]) * s[..., None]).view(N, K)
 
@@ -189,8 +189,8 @@ class _Writer:
         arr = tt.view(torch.int16).numpy() if prec == "bf16" else tt.numpy()
         self.add_array(name, arr, _ONNX_DT[prec], dims=tuple(tt.shape))
 
-    def add_synthetic(self, name: str, shape, kind: str):
-        t = op.Tensor(name=name, dtype=_ONNX_DT[self.io], dims=tuple(shape))
+    def add_synthetic(self, name: str, shape, kind: str, onnx_dtype: Optional[int] = None):
+        t = op.Tensor(name=name, dtype=_ONNX_DT[self.io] if onnx_dtype is None else onnx_dtype, dims=tuple(shape))
         t.ext_location = "synthetic"
         t.ext_offset = 0
         t.ext_length = 0
@@ -214,8 +214,6 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
         raise ValueError(f"unsupported precision {precision}")
     if context_length:
         arch.context_length = context_length
-    if synthetic_weights and precision == "int4":
-        raise ValueError("synthetic_weights cannot be combined with int4")
     W = _Writer(out_dir, precision, synthetic_weights, seed, std, filename)
     shapes = weight_shapes(arch)
 
@@ -239,7 +237,18 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
 
     def put_linear(base: str, node_name: str, src_names, inp: str, out: str, N: int, K: int):
         """A linear layer y = x @ W^T from one or more stacked [n_i, K] canonical weights."""
-        if precision == "int4" and not synthetic_weights:
+        if precision == "int4" and synthetic_weights:
+            # descriptors only: the loader draws the float weight on the device and quantises it there (RTN block-32)
+            nb = K // 32
+            for suffix, shp, dt, kind in (("weight_Q4", (N, nb, 16), op.UINT8, "q4_weight"), ("weight_scales", (N * nb,), op.FLOAT16, "q4_scales"),
+                                          ("weight_zp", (N * ((nb + 1) // 2),), op.UINT8, "q4_zp")):
+                if kind == "q4_zp" and int4_symmetric:
+                    continue
+                W.add_synthetic(f"{base}.MatMul.{suffix}", shp, "", dt)
+                synth_meta[f"{base}.MatMul.{suffix}"] = {"sources": src_names, "op": kind, "seed": seed, "std": std, "symmetric": int(int4_symmetric)}
+            ins = [inp, base + ".MatMul.weight_Q4", base + ".MatMul.weight_scales"] + ([] if int4_symmetric else [base + ".MatMul.weight_zp"])
+            W.node("MatMulNBits", node_name + "_Q4", ins, [out], domain="com.microsoft", K=K, N=N, bits=4, block_size=32, accuracy_level=4)
+        elif precision == "int4":
             w = torch.cat([get(n).float() for n in src_names], dim=0)
             q, s, zp = quantize_int4_block32(w, symmetric=int4_symmetric)
             W.add_array(base + ".MatMul.weight_Q4", q.numpy(), op.UINT8)

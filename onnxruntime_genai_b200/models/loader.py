@@ -21,7 +21,7 @@ import torch
 
 from ..utils import onnx_proto as op
 from .arch import ArchConfig
-from .builder import dequantize_int4_block32, random_tensor, weight_shapes
+from .builder import dequantize_int4_block32, quantize_int4_block32, random_tensor, weight_shapes
 from .decoder import DecoderModel, LayerWeights
 
 
@@ -64,6 +64,14 @@ class GraphView:
         for src in meta["sources"]:
             parts.append(random_tensor(src, shapes[src], meta["seed"], meta["std"], device=device))
         x = parts[0] if len(parts) == 1 else torch.cat(parts, 0)
+        if meta["op"].startswith("q4_"):
+            # the three tensors of one MatMulNBits node come from one quantisation of the same float weight
+            key = tuple(meta["sources"])
+            cache = getattr(self, "_q4_cache", None)
+            if cache is None or cache[0] != key:
+                q, sc, zp = quantize_int4_block32(x.float(), symmetric=bool(meta.get("symmetric", 0)))
+                cache = self._q4_cache = (key, {"q4_weight": q, "q4_scales": sc.reshape(-1).to(torch.float16), "q4_zp": zp})
+            return cache[1][meta["op"]]
         if meta["op"] == "cat_t":
             x = x.t()
         if meta.get("offset"):
@@ -160,9 +168,11 @@ def _linear_weight(g: GraphView, node, dtype, device, rows: Optional[slice] = No
         bs = int(node.attrs.get("block_size", 32))
         if int(node.attrs.get("bits", 4)) != 4:
             raise NotImplementedError("MatMulNBits: only 4-bit weights are supported")
-        q = g.tensor(node.inputs[1])
-        s = g.tensor(node.inputs[2])
-        zp = g.tensor(node.inputs[3]) if len(node.inputs) > 3 and node.inputs[3] else None
+        loc = g.lm.info(node.inputs[1]).ext_location or ""
+        src_dev = device if loc.startswith("synthetic:") else "cpu"
+        q = g.tensor(node.inputs[1], device=src_dev)
+        s = g.tensor(node.inputs[2], device=src_dev)
+        zp = g.tensor(node.inputs[3], device=src_dev) if len(node.inputs) > 3 and node.inputs[3] else None
         w = dequantize_int4_block32(q, s, zp, N, K, bs)
     else:
         w = g.tensor(node.inputs[1], device=device if g.lm.info(node.inputs[1]).ext_location and
@@ -183,16 +193,23 @@ def _q4_weight(g: GraphView, nodes, device, interleave: bool = False):
     """One W4Weight from one or more MatMulNBits nodes stacked along N (kept in int4 for the dequant GEMM)."""
     from ..ops.w4 import W4Weight, unpack_ort_q4
     qs, ss, zs = [], [], []
+    synthetic = False
     for n in nodes:
         N, K = int(n.attrs["N"]), int(n.attrs["K"])
-        q, zp = unpack_ort_q4(g.tensor(n.inputs[1]), g.tensor(n.inputs[3]) if len(n.inputs) > 3 and n.inputs[3] else None, N, K)
+        loc = g.lm.info(n.inputs[1]).ext_location or ""
+        synthetic = synthetic or loc.startswith("synthetic:")
+        src_dev = device if loc.startswith("synthetic:") else "cpu"     # synthetic weights are drawn and quantised on the device
+        has_zp = len(n.inputs) > 3 and n.inputs[3]
+        q, zp = unpack_ort_q4(g.tensor(n.inputs[1], device=src_dev), g.tensor(n.inputs[3], device=src_dev) if has_zp else None, N, K)
         qs.append(q)
-        ss.append(g.tensor(n.inputs[2]).float().view(N, K // 32))
-        zs.append(zp if zp is not None else torch.full((N, K // 32), 8, dtype=torch.uint8))
+        ss.append(g.tensor(n.inputs[2], device=src_dev).float().view(N, K // 32))
+        zs.append(zp if zp is not None else torch.full((N, K // 32), 8, dtype=torch.uint8, device=q.device))
     q, s, z = torch.cat(qs, 0), torch.cat(ss, 0), torch.cat(zs, 0)
     if interleave:
         from ..ops import interleave_gate_up
         q, s, z = interleave_gate_up(q), interleave_gate_up(s), interleave_gate_up(z)
+    if synthetic and torch.device(device).type == "cuda":   # no second copy of a weight that was generated on the device
+        return W4Weight.from_quantized(q, s, z, device, keep_host=False, interleaved=interleave)
     return W4Weight.from_quantized(q, s, z, device, interleaved=interleave)
 
 

@@ -32,17 +32,18 @@ class W4Weight:
         N, K = q.shape
         assert K % 64 == 0, "K must be a multiple of 64"
         nb = K // 32
+        dev = q.device   # the repack runs where the quantised tensors live (host for checkpoints, device for synthetic weights)
         if zp is None:
-            zp = torch.full((N, nb), 8, dtype=torch.uint8)
+            zp = torch.full((N, nb), 8, dtype=torch.uint8, device=dev)
         Np = (N + 127) // 128 * 128
-        qp = torch.zeros(Np, K, dtype=torch.int64)
+        qp = torch.zeros(Np, K, dtype=torch.int64, device=dev)
         qp[:N] = q.to(torch.int64)
-        sp = torch.zeros(Np, nb, dtype=torch.float32)
+        sp = torch.zeros(Np, nb, dtype=torch.float32, device=dev)
         sp[:N] = scales.float()
-        zpp = torch.zeros(Np, nb, dtype=torch.float32)
+        zpp = torch.zeros(Np, nb, dtype=torch.float32, device=dev)
         zpp[:N] = zp.float()
         # nibble m of a word: pair p = m // 2 at bit 4p, second element of the pair 16 bits higher
-        shifts = torch.tensor([0, 16, 4, 20, 8, 24, 12, 28], dtype=torch.int64)
+        shifts = torch.tensor([0, 16, 4, 20, 8, 24, 12, 28], dtype=torch.int64, device=dev)
         words = (qp.view(Np, K // 8, 8) << shifts).sum(-1)                       # [Np, K/8] values < 2^32
         b = torch.stack([(words >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.uint8)  # little endian bytes
         nib = b.view(Np // 128, 128, K // 64, 32).permute(2, 0, 1, 3)             # [K/64, tiles, 128, 32]

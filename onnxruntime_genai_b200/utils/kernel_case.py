@@ -1,6 +1,6 @@
 """Single-kernel workloads for timing and profiling.
 
-    python -m onnxruntime_genai_b200.utils.kernel_case <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--json out.json]
+    python -m onnxruntime_genai_b200.utils.kernel_case <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--eager] [--json out.json]
 
 cases: gemm_qkv gemm_o gemm_gate_up gemm_down gemm_lm_head gemm_prefill w4_qkv w4_down attention_decode
        attention_prefill norm rope sample argmax all
@@ -28,6 +28,19 @@ H, I, V, HQ, HKV, D = 4096, 14336, 128256, 32, 8, 128
 
 def _bf(*shape, std=0.02):
     return (torch.randn(*shape, device="cuda") * std).to(torch.bfloat16)
+
+
+def _time_eager(fn, iters):
+    """Plain launches (no graph): the form to run under a profiler."""
+    fn(0); fn(1)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
 
 
 def _time_graph(fn, iters, reps=3):
@@ -155,6 +168,7 @@ def main():
     ap.add_argument("--iters", type=int, default=16)
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--json", default="")
+    ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA graph (for profilers; includes launch gaps)")
     ap.add_argument("--tp", type=int, default=1, help="use the per-rank shapes of this tensor-parallel degree")
     a = ap.parse_args()
     torch.manual_seed(0)
@@ -167,7 +181,8 @@ def main():
     for name in (ALL if a.case == "all" else [a.case]):
         T = a.tokens if name != "gemm_prefill" and name != "attention_prefill" else max(a.tokens, 2048)
         fn, nbytes, flops = build_case(name, T, a.layers, a.tp)
-        us = _time_graph(fn, a.iters if name not in ("gemm_lm_head", "sample", "argmax") else min(a.iters, 4))
+        iters = a.iters if name not in ("gemm_lm_head", "sample", "argmax") else min(a.iters, 4)
+        us = _time_eager(fn, iters) if a.eager else _time_graph(fn, iters)
         gbs, tf = nbytes / us / 1e3, flops / us / 1e6
         out[name] = {"tokens": T, "us": round(us, 2), "GBps": round(gbs, 1), "TFLOPs": round(tf, 1),
                      "frac_hbm": round(gbs / hbm, 3), "frac_bf16": round(tf / tflops, 3), "peaks": src}
