@@ -226,6 +226,13 @@ class SequenceState:
                                kv_heads=decoder.kv_heads_local)
         self.block_table = (torch.arange(rows * self.blocks_per_row, dtype=torch.int32).view(rows, self.blocks_per_row)).to(dev)
         self.kv_len = [0] * rows
+        # Beam search shares cache blocks between rows (copy-on-write at block granularity).  Until the first reorder every
+        # row owns one contiguous run of blocks and none of this is active (`_tbl` is None).
+        self._tbl: Optional[np.ndarray] = None     # host mirror of the block table once rows share blocks
+        self._ref: Optional[np.ndarray] = None     # references per physical block
+        self._free: List[int] = []
+        self._moves: List[tuple] = []              # (src block, dst block) copies to do before the next forward
+        self._tbl_dirty = False
 
     def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None) -> torch.Tensor:
         """Feeds row_tokens[r] (possibly empty) after the cached prefix of row r; returns fp32 logits of the last
@@ -238,16 +245,19 @@ class SequenceState:
             base = self.kv_len[r]
             if base + len(toks) > self.blocks_per_row * self.block_size:
                 raise RuntimeError("sequence exceeds the allocated KV cache (max_length)")
+            if self._tbl is not None:
+                self._own_blocks(r, base, len(toks))
             for j, t in enumerate(toks):
                 p = base + j
                 ids.append(t)
                 pos.append(p)
-                slots.append(r * self.blocks_per_row * self.block_size + p)
+                slots.append(self._slot(r, p))
             cu.append(len(ids))
             past.append(base)
             rows_used.append(r)
             last.append(len(ids) - 1)
             self.kv_len[r] = base + len(toks)
+        self._flush_block_moves()
         i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
         s = StepInputs(input_ids=i32(ids), positions=i32(pos), slot_mapping=i32(slots), cu_seqlens=i32(cu), past_lens=i32(past),
                        block_table=self.block_table[rows_used].contiguous() if len(rows_used) != self.rows else self.block_table,
@@ -283,7 +293,10 @@ class SequenceState:
         span = cap
         for r in range(R):
             p = self.kv_len[r]
-            h[r], h[R + r], h[2 * R + r], h[3 * R + r] = int(last_tokens[r]), p, r * span + p, p
+            if self._tbl is not None:
+                self._own_blocks(r, p, 1)
+            h[r], h[R + r], h[2 * R + r], h[3 * R + r] = int(last_tokens[r]), p, self._slot(r, p), p
+        self._flush_block_moves()
         self._g_dev.copy_(self._g_host, non_blocking=True)
         bound = 256
         while bound < max(self.kv_len) + 1:
@@ -309,23 +322,68 @@ class SequenceState:
 
     def rewind(self, row: int, length: int):
         self.kv_len[row] = min(self.kv_len[row], length)
+        if self._tbl is not None:
+            self._recount()
+
+    def _slot(self, row: int, pos: int) -> int:
+        if self._tbl is None:
+            return row * self.blocks_per_row * self.block_size + pos
+        return int(self._tbl[row, pos // self.block_size]) * self.block_size + pos % self.block_size
+
+    def _used_blocks(self, row: int) -> int:
+        return (self.kv_len[row] + self.block_size - 1) // self.block_size
+
+    def _recount(self):
+        ref = np.zeros(self.rows * self.blocks_per_row, dtype=np.int32)
+        for r in range(self.rows):
+            np.add.at(ref, self._tbl[r, :self._used_blocks(r)], 1)
+        self._ref = ref
+        self._free = np.nonzero(ref == 0)[0][::-1].tolist()
+
+    def _own_blocks(self, row: int, start: int, count: int):
+        """Makes the blocks that positions [start, start + count) of `row` fall into writable by this row alone: a
+        shared block that already holds tokens is copied to a fresh one, a block past the cached tokens is taken from
+        the free list."""
+        bs = self.block_size
+        for j in range(start // bs, (start + count - 1) // bs + 1):
+            holds_tokens = j * bs < start
+            blk = int(self._tbl[row, j])
+            if holds_tokens and self._ref[blk] == 1:
+                continue
+            new = self._free.pop()
+            if holds_tokens:
+                self._ref[blk] -= 1
+                self._moves.append((blk, new))
+            self._tbl[row, j] = new
+            self._ref[new] = 1
+            self._tbl_dirty = True
+
+    def _flush_block_moves(self):
+        if self._moves:
+            bs = self.block_size
+            dev = self.kv.full.device
+            src = torch.tensor([m[0] for m in self._moves], dtype=torch.int64, device=dev)
+            dst = torch.tensor([m[1] for m in self._moves], dtype=torch.int64, device=dev)
+            ar = torch.arange(bs, device=dev)
+            s_idx, d_idx = (src[:, None] * bs + ar).reshape(-1), (dst[:, None] * bs + ar).reshape(-1)
+            self.kv.full[:, :, d_idx] = self.kv.full[:, :, s_idx]
+            self._moves = []
+        if self._tbl_dirty:
+            self.block_table.copy_(torch.from_numpy(self._tbl))
+            self._tbl_dirty = False
 
     def reorder_rows(self, src_rows: List[int]):
-        """Beam search: row r continues from the cache of row src_rows[r]."""
-        if all(r == s for r, s in enumerate(src_rows)):
-            return
-        span = self.blocks_per_row * self.block_size
-        n = max(self.kv_len)
-        idx_dst, idx_src = [], []
-        for r, s in enumerate(src_rows):
-            if r != s:
-                idx_dst.append(torch.arange(r * span, r * span + n))
-                idx_src.append(torch.arange(s * span, s * span + n))
-        if idx_dst:
-            d = torch.cat(idx_dst).to(self.kv.full.device)
-            sidx = torch.cat(idx_src).to(self.kv.full.device)
-            self.kv.full[:, :, d] = self.kv.full[:, :, sidx]
+        """Beam search: row r continues from the cache of row src_rows[r].  Only the block table is permuted; blocks are
+        shared between the rows that descend from the same hypothesis and copied when one of them writes into a shared
+        block (`_own_blocks`), so a step moves at most one block per row instead of whole caches."""
+        if self._tbl is None:
+            if all(r == s for r, s in enumerate(src_rows)):
+                return
+            self._tbl = self.block_table.cpu().numpy().copy()
+        self._tbl = self._tbl[np.asarray(src_rows, dtype=np.int64)].copy()
         self.kv_len = [self.kv_len[s] for s in src_rows]
+        self._recount()
+        self._tbl_dirty = True
 
 
 class Generator:

@@ -39,6 +39,7 @@ struct AttnParams {
   const float* sinks;
   float scale, softcap;
   int window, B, Hq, Hkv, splits, total_rows;
+  int chunk;   // > 0: every split owns a fixed range of `chunk` keys (multiple of 64); 0: a request's keys are divided evenly
 };
 
 template <int SROW>
@@ -82,14 +83,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, past + row0 / G - p.window + 1);
   if (p.splits > 1) {
+    // Fixed chunks give every CTA the same amount of work whatever the mix of sequence lengths in the batch (short
+    // requests simply use fewer of the launch's splits); the even division suits a batch of similar lengths.
     const int tiles = (kv_total + ATT_BN - 1) / ATT_BN;
-    const int per = (tiles + p.splits - 1) / p.splits * ATT_BN;
+    const int per = p.chunk > 0 ? p.chunk : (tiles + p.splits - 1) / p.splits * ATT_BN;
     kv_lo = max(kv_lo, split * per);
-    kv_hi = min(kv_hi, (split + 1) * per);
+    if (split + 1 < p.splits) kv_hi = min(kv_hi, (split + 1) * per);   // the last split takes whatever lies beyond the chunks
   }
   const int tile_begin = kv_lo / ATT_BN;
   const int tile_end = kv_hi > kv_lo ? (kv_hi + ATT_BN - 1) / ATT_BN : tile_begin;
   const int n_tiles = tile_end - tile_begin;
+  if (p.splits > 1 && n_tiles == 0) {
+    // Nothing in this split's range: mark its partials empty for the combine and leave before any copy is issued.
+    for (int r = tid; r < BM; r += ATT_THREADS) {
+      const int gr = row0 + r;
+      if (gr < rows) {
+        float* pm = p.part_ml + (size_t(split) * p.total_rows + size_t(tok0 + gr / G) * p.Hq + kvh * G + gr % G) * 2;
+        pm[0] = -INFINITY; pm[1] = 0.f;
+      }
+    }
+    return;
+  }
 
   // Each warp copies 16 key rows of the tile.  Lanes 0..15 look up the cache slot of one row each; the
   // copies then walk the warp's rows chunk by chunk with consecutive lanes on consecutive 16-byte
@@ -418,13 +432,15 @@ OGB_API long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, i
 OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
                                 const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                                 int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
-                                int max_q_len, int Hq, int Hkv, int D, int splits, void* scratch, long long scratch_bytes,
-                                void* stream_) {
+                                int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
+                                long long scratch_bytes, void* stream_) {
   if (B <= 0 || total_tokens <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv || (q_stride % 8) || (out_stride % 2)) return -1;
   if (splits < 1) splits = 1;
+  if (kv_chunk < 0 || (kv_chunk % ATT_BN)) return -1;
   if (splits > 1 && ogb_attention_scratch_bytes(total_tokens, Hq, D, splits) > scratch_bytes) return -2;
   AttnParams p;
+  p.chunk = splits > 1 ? kv_chunk : 0;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.block_table = block_table; p.table_cols = table_cols;
@@ -474,6 +490,6 @@ OGB_API int ogb_paged_attention_noalloc(const void* q, int q_stride, const void*
     g_noalloc_scratch_addr[dev] = p;
   }
   return ogb_paged_attention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out,
-                             out_stride, sinks, scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits,
+                             out_stride, sinks, scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, 0,
                              g_noalloc_scratch_addr[dev], OGB_NOALLOC_SCRATCH_BYTES, stream);
 }

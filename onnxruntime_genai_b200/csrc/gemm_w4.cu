@@ -229,6 +229,167 @@ static int LaunchW4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles_total,
   return cudaLaunchKernelEx(&cfg, kern, ta, wp, n_tiles_total, p) == cudaSuccess ? 0 : -4;
 }
 
+// ---------------------------------------------------------------------------------------------- GEMV (1..4 tokens)
+// Decode of a single sequence (or a few): with at most four activation rows the tensor cores have nothing to do and
+// the job is to stream the packed weights at HBM speed.  One thread per weight row reads its 32 bytes of nibbles and
+// its scale / zero-point pair of every 64-wide k-block straight from global memory (a warp covers 1 KiB contiguous),
+// several k-blocks in flight; the activations (and their sums per block of 32, so that the zero point costs one
+// multiply per block instead of a subtract per weight) sit in shared memory and are read as broadcasts:
+//     sum_k (q - z) s x  =  s * (sum_k (128 + q) x  -  (128 + z) * sum_k x)
+// The k range is split over a thread-block cluster (up to 8 CTAs) whose partial sums meet in the first CTA's
+// shared memory; that CTA adds bias / residual, applies the paired SiLU*mul and stores.
+constexpr int GEMV_THREADS = 128;
+constexpr int GEMV_MAX_KB = 32;   // k-blocks per CTA held as activations in shared memory (x: MT * 64 * 4 bytes each)
+
+template <int MT>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_total, const GemmParams p) {
+  __shared__ __align__(16) float xs[MT][GEMV_MAX_KB * 64];
+  __shared__ float xsum[MT][GEMV_MAX_KB * 2];
+  __shared__ float part[MT][GEMV_THREADS];      // this CTA's partial sums, read by the first CTA of the cluster
+  const int tid = threadIdx.x;
+  const int n_tile = blockIdx.x, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  const int num_kb = max(0, min(p.kb_per_split, p.total_kb - kb0));
+  const uint8_t* rec0 = wpacked + (size_t(kb0) * n_tiles_total + n_tile) * W4_RECORD_BYTES;
+  const size_t rec_stride = size_t(n_tiles_total) * W4_RECORD_BYTES;
+
+  // first weights before the wait on the previous kernel: nothing earlier in the stream writes them
+  uint4 nib0 = make_uint4(0, 0, 0, 0), nib1 = nib0;
+  uint2 sz = make_uint2(0, 0);
+  if (num_kb > 0) {
+    nib0 = *reinterpret_cast<const uint4*>(rec0 + tid * 32);
+    nib1 = *reinterpret_cast<const uint4*>(rec0 + tid * 32 + 16);
+    sz = *reinterpret_cast<const uint2*>(rec0 + GEMM_BLOCK_N * 32 + tid * 8);
+  }
+  if (p.pdl) { pdl_launch_dependents(); pdl_wait(); }
+
+  // stage the activations of this k range as fp32 and their sums per block of 32
+  for (int i = tid; i < num_kb * 64; i += GEMV_THREADS) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) xs[m][i] = m < p.M ? bf2f(A[size_t(m) * lda + size_t(kb0) * 64 + i]) : 0.f;
+  }
+  __syncthreads();
+  for (int i = tid; i < num_kb * 2 * MT; i += GEMV_THREADS) {
+    const int m = i / (num_kb * 2), b = i % (num_kb * 2);
+    float t = 0.f;
+    for (int j = 0; j < 32; ++j) t += xs[m][b * 32 + j];
+    xsum[m][b] = t;
+  }
+  __syncthreads();
+
+  float acc[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+
+  for (int kb = 0; kb < num_kb; ++kb) {
+    // software pipeline: issue the next record's loads before working on this one
+    uint4 nx0 = nib0, nx1 = nib1;
+    uint2 nsz = sz;
+    if (kb + 1 < num_kb) {
+      const uint8_t* r = rec0 + size_t(kb + 1) * rec_stride;
+      nx0 = *reinterpret_cast<const uint4*>(r + tid * 32);
+      nx1 = *reinterpret_cast<const uint4*>(r + tid * 32 + 16);
+      nsz = *reinterpret_cast<const uint2*>(r + GEMM_BLOCK_N * 32 + tid * 8);
+    }
+    const uint32_t words[8] = {nib0.x, nib0.y, nib0.z, nib0.w, nib1.x, nib1.y, nib1.z, nib1.w};
+    const float2 sz0 = unpack_bf16x2(sz.x), sz1 = unpack_bf16x2(sz.y);   // (scale, 128 + zero point) of the two blocks of 32
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float dot[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) dot[m] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = words[half * 4 + j];
+        float q[8];
+#pragma unroll
+        for (int pr = 0; pr < 4; ++pr) {
+          const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
+          q[2 * pr] = __uint_as_float(t << 16);
+          q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
+          dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
+        }
+      }
+      const float2 s = half ? sz1 : sz0;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] += s.x * (dot[m] - s.y * xsum[m][kb * 2 + half]);
+    }
+    nib0 = nx0; nib1 = nx1; sz = nsz;
+  }
+
+#pragma unroll
+  for (int m = 0; m < MT; ++m) part[m][tid] = acc[m];
+  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
+
+  if (split == 0) {
+    const bool pair = p.act_pair != 0;
+    const int n_out = pair ? p.N / 2 : p.N;
+    const uint32_t part_addr = smem_u32(&part[0][0]);
+    auto total = [&](int m, int row) {
+      float t = 0.f;
+      for (int s = 0; s < p.splits; ++s) {
+        if (p.splits > 1) {
+          float v;
+          const uint32_t ra = dsmem_addr(part_addr + uint32_t(m * GEMV_THREADS + row) * 4, uint32_t(s));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+          t += v;
+        } else {
+          t += part[m][row];
+        }
+      }
+      const int n = n_tile * GEMM_BLOCK_N + row;
+      if (p.bias && n < p.N) t += bf2f(p.bias[n]);
+      return t;
+    };
+    const int rows_out = pair ? 64 : GEMV_THREADS;
+    if (tid < rows_out) {
+      const int col = pair ? n_tile * 64 + tid : n_tile * GEMM_BLOCK_N + tid;
+      if (col < n_out) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          if (m >= p.M) break;
+          float v = total(m, tid);
+          if (pair) v = silu(v) * total(m, tid + 64);
+          if (p.residual) v += bf2f(p.residual[size_t(m) * p.ldr + col]);
+          if (p.out_fp32) reinterpret_cast<float*>(p.C)[size_t(m) * p.ldc + col] = v;
+          else reinterpret_cast<__nv_bfloat16*>(p.C)[size_t(m) * p.ldc + col] = f2bf(v);
+        }
+      }
+    }
+  }
+  if (p.splits > 1) cluster_sync_all();   // peers keep their shared memory alive until the first CTA has read it
+}
+
+template <int MT>
+static int LaunchGemvW4(const __nv_bfloat16* A, int lda, const uint8_t* wp, int n_tiles_total, const GemmParams& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles_total, 1, p.splits);
+  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (p.splits > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = unsigned(p.splits);
+    ++na;
+  }
+  if (p.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = unsigned(na);
+  return cudaLaunchKernelEx(&cfg, gemv_w4_kernel<MT>, A, lda, wp, n_tiles_total, p) == cudaSuccess ? 0 : -4;
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -250,7 +411,40 @@ OGB_API int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, in
   const int bt = ogb_gemm_token_tile(M, 0);
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, m_tiles = (M + bt - 1) / bt;
   const int total_kb = K / GEMM_BLOCK_K;
-  if (splits <= 0) splits = ogb_gemm_auto_splits(M, N, K, 0, sm_count);
+  static const int gemv_enabled = [] { const char* e = getenv("OGB_W4_GEMV"); return (e && e[0] == '0') ? 0 : 1; }();
+  if (M <= 4 && gemv_enabled && total_kb <= 8 * GEMV_MAX_KB) {
+    // a few tokens: stream the weights with one thread per row, k split over a cluster sized to fill the GPU
+    int gs = splits > 0 ? splits : 1;
+    if (splits <= 0) while (gs < 8 && n_tiles * gs < 4 * sm_count && total_kb / (gs * 2) >= 2) gs *= 2;
+    if (gs > 8) gs = 8;
+    while ((total_kb + gs - 1) / gs > GEMV_MAX_KB) gs *= 2;
+    if (gs > total_kb) gs = total_kb;
+    int per = (total_kb + gs - 1) / gs;
+    while (gs > 1 && per * (gs - 1) >= total_kb) { --gs; per = (total_kb + gs - 1) / gs; }
+    if (gs <= 8 && per <= GEMV_MAX_KB) {
+      GemmParams g = {};
+      g.M = M; g.N = N; g.K = K; g.splits = gs; g.kb_per_split = per; g.total_kb = total_kb;
+      g.C = C; g.ldc = ldc; g.out_fp32 = out_fp32; g.act_pair = act_pair;
+      g.residual = static_cast<const __nv_bfloat16*>(residual); g.ldr = ldr;
+      g.bias = static_cast<const __nv_bfloat16*>(bias);
+      g.status = status; g.pdl = pdl_enabled;
+      const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(A);
+      const uint8_t* w = static_cast<const uint8_t*>(Wpacked);
+      if (M == 1) return LaunchGemvW4<1>(a, lda, w, n_tiles, g, stream);
+      if (M == 2) return LaunchGemvW4<2>(a, lda, w, n_tiles, g, stream);
+      return LaunchGemvW4<4>(a, lda, w, n_tiles, g, stream);
+    }
+  }
+  if (splits <= 0) {
+    // Every k-block costs a dequantisation pass on top of the copy, so the k range is cut finer than for bf16 weights:
+    // the largest power of two that keeps 8 k-blocks per CTA and all CTAs resident at once.
+    const int slots = (bt <= 64 ? 2 : 1) * sm_count;
+    splits = 1;
+    for (int s2 = 2; s2 <= 8; s2 *= 2) {
+      if (s2 > bt || total_kb / s2 < 8 || n_tiles * m_tiles * s2 > slots) break;
+      splits = s2;
+    }
+  }
   if (splits > 8) splits = 8;
   if (splits > bt) splits = bt;
   if (splits > total_kb) splits = total_kb;

@@ -239,18 +239,39 @@ struct SmallList {
 __device__ void small_list(const RowCtx& c, SelectShared& sh, unsigned long long* priv, int* cand_n, int k, float top_p, SmallList& L) {
   const int tid = threadIdx.x, n = c.n;
   const float* x = c.x;
-  radix_select<false>(c, sh, priv, (unsigned long long)k);
-  const uint32_t T = sh.prefix;
-  const unsigned long long need = sh.want, ties = sh.ties;
-  __syncthreads();
-  int cut = n;
-  if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);  // ties straddle the threshold: keep the lowest indices
-  __syncthreads();
   float* cv = reinterpret_cast<float*>(priv);            // candidate values   [SMALL_K]
   int* ci = reinterpret_cast<int*>(cv + SMALL_K);        // candidate indices  [SMALL_K]
   float* sv = reinterpret_cast<float*>(ci + SMALL_K);    // sorted values
   int* si = reinterpret_cast<int*>(sv + SMALL_K);        // sorted indices
-  if (tid == 0) *cand_n = 0;
+
+  // ---- fast path: two light passes.  The k-th largest of the per-thread maxima (distinct elements of the row) is a
+  // lower bound of the k-th largest element, so everything >= it is a superset of the top-k set; for k << n and
+  // interleaved indexing that superset is a small multiple of k.  If it does not fit the list the exact radix
+  // select below takes over, so the result never depends on which path ran.
+  float tmax = -INFINITY;
+  for (int base = 0; base < n; base += 8 * blockDim.x) {
+    float vals[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x + tid;
+      vals[u] = i < n ? x[i] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) tmax = fmaxf(tmax, vals[u]);
+  }
+  sv[tid] = tmax;   // blockDim.x == SMALL_K
+  if (tid == 0) { *cand_n = 0; sh.result = 0; }
+  __syncthreads();
+  {
+    int rank = 0;
+    for (int j = 0; j < SAMP_THREADS; ++j) {
+      const float vj = sv[j];
+      rank += (vj > tmax || (vj == tmax && j < tid)) ? 1 : 0;
+    }
+    if (rank == k - 1) sh.carry = (unsigned long long)__float_as_uint(tmax);
+  }
+  __syncthreads();
+  const float t0 = __uint_as_float((uint32_t)sh.carry);
   __syncthreads();
   for (int base = 0; base < n; base += 8 * blockDim.x) {
     float vals[8];
@@ -262,16 +283,48 @@ __device__ void small_list(const RowCtx& c, SelectShared& sh, unsigned long long
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int i = base + u * blockDim.x + tid;
-      const uint32_t key = to_key(vals[u]);
-      if (i < n && (key > T || (key == T && i <= cut))) {
+      if (i < n && vals[u] >= t0) {
         const int slot = atomicAdd(cand_n, 1);
         if (slot < SMALL_K) { cv[slot] = vals[u]; ci[slot] = i; }
       }
     }
   }
   __syncthreads();
-  const int m = min(*cand_n, SMALL_K);
-  // rank sort: descending value, ascending index (deterministic whatever order the slots were filled in)
+  int m = *cand_n;
+  __syncthreads();
+  if (m > SMALL_K || m < k) {
+    // ---- exact path: radix select of the k-th key, then collect exactly the k members
+    radix_select<false>(c, sh, priv, (unsigned long long)k);
+    const uint32_t T = sh.prefix;
+    const unsigned long long need = sh.want, ties = sh.ties;
+    __syncthreads();
+    int cut = n;
+    if (need < ties) cut = tie_index_cut<false>(c, sh, T, need, false);  // ties straddle the threshold: keep the lowest indices
+    __syncthreads();
+    if (tid == 0) *cand_n = 0;
+    __syncthreads();
+    for (int base = 0; base < n; base += 8 * blockDim.x) {
+      float vals[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        vals[u] = i < n ? x[i] : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * blockDim.x + tid;
+        const uint32_t key = to_key(vals[u]);
+        if (i < n && (key > T || (key == T && i <= cut))) {
+          const int slot = atomicAdd(cand_n, 1);
+          if (slot < SMALL_K) { cv[slot] = vals[u]; ci[slot] = i; }
+        }
+      }
+    }
+    __syncthreads();
+    m = min(*cand_n, SMALL_K);
+  }
+  // rank sort: descending value, ascending index (deterministic whatever order the slots were filled in); the first k
+  // ranks are the top-k set (ties at the boundary go to the lowest indices)
   if (tid < m) {
     const float v = cv[tid];
     const int idx = ci[tid];
@@ -281,9 +334,9 @@ __device__ void small_list(const RowCtx& c, SelectShared& sh, unsigned long long
       const int ij = ci[j];
       rank += (vj > v || (vj == v && ij < idx)) ? 1 : 0;
     }
-    sv[rank] = v;
-    si[rank] = idx;
+    if (rank < k) { sv[rank] = v; si[rank] = idx; }
   }
+  m = min(m, k);
   __syncthreads();
   const float top = sv[0];
   unsigned long long w = 0;

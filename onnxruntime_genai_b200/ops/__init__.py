@@ -282,14 +282,21 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
 
 
 # ------------------------------------------------------------------------------------------ attention
-def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_count: int = 148) -> int:
-    """Split the KV range when the (request, kv head) grid alone cannot fill the GPU."""
-    if max_q_len > 16:
-        return 1
+def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_count: int = 148, group: int = 1):
+    """(splits, kv_chunk) of a paged-attention launch.  Decode-sized launches (the rows of a request fit one 16-row
+    tile) split every request's keys into fixed chunks so that all CTAs carry the same work whatever the mix of
+    sequence lengths; the chunk is sized for about four CTAs per SM and at most 512 keys.  Other launches: (1, 0)."""
+    if max_q_len * group > 16 or max_kv_len <= 128:
+        return 1, 0
     ctas = max(1, batch * Hkv)
-    want = (2 * sm_count + ctas - 1) // ctas
-    by_len = max(1, max_kv_len // 256)
-    return int(max(1, min(want, by_len, 16)))
+    chunks_wanted = max(1, (4 * sm_count + ctas - 1) // ctas)
+    chunk = (max_kv_len + chunks_wanted - 1) // chunks_wanted
+    chunk = min(512, max(64, (chunk + 63) // 64 * 64))
+    splits = min(64, (max_kv_len + chunk - 1) // chunk)
+    if splits <= 1:
+        return 1, 0
+    chunk = ((max_kv_len + splits - 1) // splits + 63) // 64 * 64   # the splits must cover the bound
+    return int(splits), int(chunk)
 
 
 def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale, window=0,
@@ -304,16 +311,19 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
         out = torch.empty(q.shape[0], Hq * D, dtype=q.dtype, device=q.device)
     if max_q_len is None:
         max_q_len = T
+    kv_chunk = 0
     if splits is None:
-        splits = choose_kv_splits(B, Hkv, max_q_len, max_kv_len or 1024)
+        splits, kv_chunk = choose_kv_splits(B, Hkv, max_q_len, max_kv_len or 1024, group=Hq // Hkv)
+    elif isinstance(splits, tuple):
+        splits, kv_chunk = splits
     ws = workspace(q.device)
     need = _lib.lib().ogb_attention_scratch_bytes(q.shape[0], Hq, D, splits)
     scratch = ws.attn_scratch(need) if splits > 1 else None
     rc = _lib.lib().ogb_paged_attention(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
                                         _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0),
                                         _ptr(sinks), float(scale), float(softcap), int(window), B, q.shape[0], int(max_q_len),
-                                        Hq, Hkv, D, int(splits), _ptr(scratch), scratch.numel() if scratch is not None else 0,
-                                        _stream())
+                                        Hq, Hkv, D, int(splits), int(kv_chunk), _ptr(scratch),
+                                        scratch.numel() if scratch is not None else 0, _stream())
     _lib.check(rc, "paged_attention")
     if splits > 1:
         _lib.LAUNCH_COUNT += 1  # the combine kernel

@@ -78,6 +78,10 @@ def _peaks():
         return 6650.0, 1590.0, "fallback"
 
 
+NO_FUSED = False     # --tp shapes without the fused all-reduce (the GEMM alone)
+ATTN_SPLITS = None   # None: the library's choice; (splits, kv_chunk) to force one
+
+
 def build_case(name, T, L, tp=1):
     """Returns (fn(i), algorithmic_bytes, flops).  tp > 1: the per-rank shapes of tensor parallelism; the row-parallel
     projections then run the fused all-reduce against a world of one (protocol cost without a peer)."""
@@ -86,7 +90,7 @@ def build_case(name, T, L, tp=1):
         shapes = {"gemm_qkv": ((HQ + 2 * HKV) * D, H), "gemm_o": (H, HQ * D), "gemm_gate_up": (2 * I // tp, H), "gemm_down": (H, I // tp),
                   "gemm_lm_head": (V // tp, H), "gemm_prefill": (2 * I // tp, H), "w4_qkv": (9216 // tp, 3072), "w4_down": (3072, 8192 // tp)}
         N, K = shapes[name]
-        fused = tp > 1 and name in ("gemm_o", "gemm_down")
+        fused = tp > 1 and name in ("gemm_o", "gemm_down") and not NO_FUSED
         if name == "gemm_lm_head":
             L = min(L, 2)
         x = _bf(T, K, std=1.0)
@@ -133,7 +137,8 @@ def build_case(name, T, L, tp=1):
         nbytes = kv_tokens * HKV * D * 2 * 2 + Tq * HQ * D * 2 * 2
         flops = sum(4.0 * HQ * D * (q * p + q * (q + 1) / 2) for p, q in zip(past, q_lens))
         return (lambda i: ops.paged_attention(qkv, kc[i % Lk], vc[i % Lk], cu, pl, table, bs, HQ, HKV, D, 1 / math.sqrt(D),
-                                              max_q_len=max(q_lens), max_kv_len=max(p + q for p, q in zip(past, q_lens)))), nbytes, flops
+                                              max_q_len=max(q_lens), max_kv_len=max(p + q for p, q in zip(past, q_lens)),
+                                              splits=ATTN_SPLITS)), nbytes, flops
     if name == "norm":
         x, r, w = _bf(T, H, std=1.0), _bf(T, H, std=1.0), _bf(H, std=1.0)
         return (lambda i: ops.norm(x, w, 1e-5, r)), T * H * 2 * 4, 0.0
@@ -169,9 +174,15 @@ def main():
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--json", default="")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA graph (for profilers; includes launch gaps)")
+    ap.add_argument("--no_fused", action="store_true", help="with --tp: run the row-parallel GEMMs without the fused all-reduce")
+    ap.add_argument("--attn_splits", default="", help="force the attention split: 'S' (even division) or 'S,chunk' (fixed key ranges)")
     ap.add_argument("--tp", type=int, default=1, help="use the per-rank shapes of this tensor-parallel degree")
     a = ap.parse_args()
     torch.manual_seed(0)
+    globals()["NO_FUSED"] = a.no_fused
+    if a.attn_splits:
+        v = [int(x) for x in a.attn_splits.split(",")]
+        globals()["ATTN_SPLITS"] = v[0] if len(v) == 1 else (v[0], v[1])
     comm = None
     if a.tp > 1:
         from ..parallel.symm import LocalComm

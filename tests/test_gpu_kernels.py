@@ -223,6 +223,14 @@ def test_attention_decode_split_kv(splits):
     _attention_case(B=3, q_lens=[1, 1, 1], past=[5, 700, 2047], Hq=32, Hkv=8, D=128, bs=16, splits=splits)
 
 
+@pytest.mark.parametrize("splits", [(8, 256), (5, 512), (33, 64), (3, 128)])
+def test_attention_decode_fixed_chunks(splits):
+    """Fixed key ranges per split: short requests leave most splits empty, long ones may end inside a chunk, and a
+    chunk count that does not cover the longest request must still be refused by nobody (the last chunk is clipped)."""
+    _attention_case(B=4, q_lens=[1, 1, 1, 1], past=[5, 700, 2047, 255], Hq=32, Hkv=8, D=128, bs=16, splits=splits)
+    _attention_case(B=3, q_lens=[1, 2, 1], past=[300, 64, 1], Hq=8, Hkv=2, D=64, bs=16, window=128, sinks=True, splits=splits)
+
+
 def test_attention_prefill_and_mixed():
     _attention_case(B=3, q_lens=[70, 1, 33], past=[0, 90, 17], Hq=8, Hkv=2, D=128, bs=16)
     _attention_case(B=2, q_lens=[257, 5], past=[0, 300], Hq=4, Hkv=4, D=64, bs=256)
@@ -399,6 +407,33 @@ def test_gemm_w4_gate_up_pair():
     want = ref.gate_up_act(x.cpu(), plain.dequantize())
     _close(ops.gate_up_act(x, il), want, rtol=3e-2, atol=0.05)
     _close(ops.gate_up_act(x, plain), want, rtol=3e-2, atol=0.05)
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_gemv_w4_few_tokens(M):
+    """One to four tokens take the weight-streaming GEMV: all epilogues, uneven k splits, rows past N, against the
+    dequantised fp32 product and against the tensor-core kernel on the same inputs."""
+    for N, K, splits in ((9216, 3072, 0), (1000, 512, 3), (128, 64, 1), (3072, 8192, 0)):
+        w4, _ = _w4_case(N, K, seed=60)
+        x, bias, res = _rand(M, K, seed=61), _rand(N, seed=62), _rand(M, N, seed=63)
+        want = ref.linear(x.cpu(), w4.dequantize(), bias.cpu(), res.cpu())
+        y = ops.linear(x, w4, bias=bias, residual=res, splits=splits)
+        _close(y, want, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.05)
+        y32 = ops.linear(x, w4, out_fp32=True, splits=splits)
+        _close(y32, ref.linear(x.cpu(), w4.dequantize(), out_fp32=True), rtol=1e-2, atol=1e-2 * math.sqrt(K) * 0.05)
+    ops.check_kernel_status()
+    # paired SiLU*mul epilogue
+    from onnxruntime_genai_b200.models.builder import quantize_int4_block32
+    from onnxruntime_genai_b200.ops.w4 import W4Weight, unpack_ort_q4
+    I, K = 256, 512
+    w = torch.randn(2 * I, K, generator=torch.Generator().manual_seed(64)) * 0.05
+    qw, s, zp = quantize_int4_block32(w)
+    q, z = unpack_ort_q4(qw, zp, 2 * I, K)
+    plain = W4Weight.from_quantized(q, s, z, DEV)
+    il = W4Weight.from_quantized(ops.interleave_gate_up(q), ops.interleave_gate_up(s), ops.interleave_gate_up(z), DEV, interleaved=True)
+    x = _rand(M, K, seed=65)
+    _close(ops.gate_up_act(x, il), ref.gate_up_act(x.cpu(), plain.dequantize()), rtol=3e-2, atol=0.05)
     ops.check_kernel_status()
 
 
