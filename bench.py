@@ -116,6 +116,9 @@ def ours(args):
         if args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} processes (WORLD_SIZE={world})")
     torch.cuda.set_device(local)
+    if world > 1:
+        import faulthandler
+        faulthandler.dump_traceback_later(1500, exit=True)   # a stuck rank reports where and ends instead of hanging the job
     tp = TensorParallel.from_env(os.environ.get("OGB_TP_BACKEND")) if world > 1 else None
 
     def barrier():

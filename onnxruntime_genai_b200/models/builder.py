@@ -165,6 +165,42 @@ def dequantize_int4_block32(qweight, scales, zero_points, N: int, K: int, block:
     return ((w - zz[..., None]) * s[..., None]).view(N, K)
 
 
+_FP4_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)   # e2m1 magnitudes; bit 3 of a code is the sign
+
+
+def quantize_mxfp4(w: torch.Tensor, block: int = 32):
+    """MXFP4 (OCP microscaling): FP4 e2m1 codes with one power-of-two (e8m0) scale per block of 32 along K.
+    w: [N, K] float.  Returns packed uint8 [K, N/2] in the QMoE layout (a byte holds two adjacent output features of
+    the same k: even n in the low nibble) and the scale codes uint8 [N, K/block] (value 2^(code - 127))."""
+    N, K = w.shape
+    assert K % block == 0 and N % 2 == 0
+    wb = w.float().view(N, K // block, block)
+    amax = wb.abs().amax(-1)
+    code = torch.full_like(amax, 127.0)
+    nz = amax > 0
+    code[nz] = torch.clamp(torch.round(torch.log2(amax[nz] / 6.0)) + 127.0, 1, 254)
+    scale = torch.pow(2.0, code - 127.0)
+    v = (wb / scale[..., None]).clamp(-6.0, 6.0)
+    grid = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=w.device)
+    idx = (v.abs()[..., None] - grid).abs().argmin(-1)        # nearest magnitude
+    codes = (idx + 8 * ((v < 0) & (idx > 0)).long()).to(torch.uint8).view(N, K)
+    kn = codes.t().contiguous()
+    packed = (kn[:, 0::2] | (kn[:, 1::2] << 4)).contiguous()
+    return packed, code.to(torch.uint8)
+
+
+def dequantize_mxfp4(packed: torch.Tensor, scale_codes: torch.Tensor, N: int, K: int, block: int = 32) -> torch.Tensor:
+    """Inverse of quantize_mxfp4: fp32 [N, K]."""
+    pk = torch.as_tensor(packed).view(K, N // 2)
+    kn = torch.stack([pk & 0xF, pk >> 4], dim=-1).view(K, N)
+    codes = kn.t().long()
+    grid = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=pk.device)
+    mag = grid[codes & 7]
+    val = torch.where(codes >= 8, -mag, mag)
+    scale = torch.pow(2.0, torch.as_tensor(scale_codes).view(N, K // block).float() - 127.0)
+    return (val.view(N, K // block, block) * scale[..., None]).view(N, K)
+
+
 # ---------------------------------------------------------------------------------------------- export
 class _Writer:
     def __init__(self, out_dir: str, precision: str, synthetic: bool, seed: int, std: float, filename: str = "model.onnx"):
@@ -388,15 +424,34 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             put_linear(p + "moe.router", f"{n}/moe/router/MatMul", [p + "mlp.router.weight"], x, f"{n}/moe/router/MatMul/output_0", E, H)
             put_vec(p + "moe.router.Add.bias", [p + "mlp.router.bias"])
             W.node("Add", f"{n}/moe/router/Add", [f"{n}/moe/router/MatMul/output_0", p + "moe.router.Add.bias"], [f"{n}/moe/router/Add/output_0"])
-            for nm, shape in (("gate_up_proj", (E, 2 * I, H)), ("down_proj", (E, H, I))):
-                put_plain(p + f"moe.experts.{nm}.weight", [p + f"mlp.experts.{nm}"], {"shape": shape, "op": "id", "fn": lambda ts: ts[0].float()})
-                put_plain(p + f"moe.experts.{nm}.bias", [p + f"mlp.experts.{nm}_bias"],
-                          {"shape": shape[:2], "op": "id", "fn": lambda ts: ts[0].float()})
-            W.node("MoE", f"{n}/moe/MoE", [x, f"{n}/moe/router/Add/output_0", p + "moe.experts.gate_up_proj.weight",
-                                           p + "moe.experts.gate_up_proj.bias", p + "moe.experts.down_proj.weight",
-                                           p + "moe.experts.down_proj.bias"], [f"{n}/moe/MoE/output_0"], domain="com.microsoft",
-                   k=arch.experts_per_token, activation_type="swiglu", activation_alpha=float(arch.moe_swiglu_alpha),
-                   activation_beta=1.0, swiglu_fusion=1, swiglu_limit=float(arch.moe_swiglu_limit), normalize_routing_weights=1)
+            if precision == "int4" and not synthetic_weights:
+                # quantised experts: QMoE with MXFP4 weights (FP4 e2m1 codes [E, K, N/2], e8m0 scales [E, N, K/32], unit global scales)
+                ins = [x, f"{n}/moe/router/Add/output_0"]
+                for nm in ("gate_up_proj", "down_proj"):
+                    wt = get(p + f"mlp.experts.{nm}").float()
+                    packs = [quantize_mxfp4(wt[e]) for e in range(E)]
+                    W.add_array(p + f"moe.experts.{nm}.weight_fp4", torch.stack([q for q, _ in packs]).numpy(), op.UINT8)
+                    W.add_array(p + f"moe.experts.{nm}.scales_e8m0", torch.stack([c for _, c in packs]).numpy(), op.UINT8)
+                    W.add_float(p + f"moe.experts.{nm}.bias", get(p + f"mlp.experts.{nm}_bias").float())
+                    ins += [p + f"moe.experts.{nm}.weight_fp4", p + f"moe.experts.{nm}.scales_e8m0", p + f"moe.experts.{nm}.bias"]
+                ins += [""] * (15 - len(ins))      # fc3, zero points, router weights: unused
+                for nm in ("gate_up_proj", "down_proj"):
+                    W.add_array(p + f"moe.experts.{nm}.global_scale", np.ones((E,), dtype=np.float32), op.FLOAT)
+                    ins.append(p + f"moe.experts.{nm}.global_scale")
+                W.node("QMoE", f"{n}/moe/QMoE", ins, [f"{n}/moe/MoE/output_0"], domain="com.microsoft", k=arch.experts_per_token,
+                       activation_type="swiglu", activation_alpha=float(arch.moe_swiglu_alpha), activation_beta=1.0, swiglu_fusion=1,
+                       swiglu_limit=float(arch.moe_swiglu_limit), normalize_routing_weights=1, expert_weight_bits=4, block_size=32,
+                       quant_type="fp4", use_sparse_mixer=0)
+            else:
+                for nm, shape in (("gate_up_proj", (E, 2 * I, H)), ("down_proj", (E, H, I))):
+                    put_plain(p + f"moe.experts.{nm}.weight", [p + f"mlp.experts.{nm}"], {"shape": shape, "op": "id", "fn": lambda ts: ts[0].float()})
+                    put_plain(p + f"moe.experts.{nm}.bias", [p + f"mlp.experts.{nm}_bias"],
+                              {"shape": shape[:2], "op": "id", "fn": lambda ts: ts[0].float()})
+                W.node("MoE", f"{n}/moe/MoE", [x, f"{n}/moe/router/Add/output_0", p + "moe.experts.gate_up_proj.weight",
+                                               p + "moe.experts.gate_up_proj.bias", p + "moe.experts.down_proj.weight",
+                                               p + "moe.experts.down_proj.bias"], [f"{n}/moe/MoE/output_0"], domain="com.microsoft",
+                       k=arch.experts_per_token, activation_type="swiglu", activation_alpha=float(arch.moe_swiglu_alpha),
+                       activation_beta=1.0, swiglu_fusion=1, swiglu_limit=float(arch.moe_swiglu_limit), normalize_routing_weights=1)
             mlp_out = f"{n}/moe/MoE/output_0"
         else:
             gu = f"{n}/mlp/gate_up_proj/MatMul/output_0"

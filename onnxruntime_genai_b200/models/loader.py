@@ -21,7 +21,7 @@ import torch
 
 from ..utils import onnx_proto as op
 from .arch import ArchConfig
-from .builder import dequantize_int4_block32, quantize_int4_block32, random_tensor, weight_shapes
+from .builder import dequantize_int4_block32, dequantize_mxfp4, quantize_int4_block32, random_tensor, weight_shapes
 from .decoder import DecoderModel, LayerWeights
 
 
@@ -128,7 +128,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         wname = moe.inputs[2]
         shp = g.lm.info(wname).dims
         a.num_experts = shp[0]
-        a.intermediate_size = shp[1] // 2
+        # MoE weight [E, 2I, H]; QMoE MXFP4 codes [E, H, (2I)/2]
+        a.intermediate_size = shp[2] if moe.op_type == "QMoE" else shp[1] // 2
         a.mlp_bias = True
     else:
         gu = g.find("/model/layers.0/mlp/gate_up_proj/", ops=["MatMul", "MatMulNBits"])
@@ -334,8 +335,27 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                     return None
                 t = g.tensor(name, device=device)
                 return t[lw.exp_lo:lw.exp_hi].to(device=device, dtype=dtype).contiguous()
-            lw.exp_gate_up_w, lw.exp_gate_up_b = experts(moe.inputs[2]), experts(moe.inputs[3])
-            lw.exp_down_w, lw.exp_down_b = experts(moe.inputs[4]), experts(moe.inputs[5])
+
+            def experts_fp4(wname, sname, gname):
+                """MXFP4 experts ([E, K, N/2] codes, [E, N, K/32] e8m0 scales, per-expert global scale) expanded to `dtype`."""
+                q, sc = g.tensor(wname)[lw.exp_lo:lw.exp_hi].to(device), g.tensor(sname)[lw.exp_lo:lw.exp_hi].to(device)
+                gs = g.tensor(gname)[lw.exp_lo:lw.exp_hi].float().to(device) if gname else None
+                Kk, Nn = q.shape[1], q.shape[2] * 2
+                out = torch.empty(q.shape[0], Nn, Kk, dtype=dtype, device=device)
+                for e in range(q.shape[0]):
+                    w = dequantize_mxfp4(q[e], sc[e], Nn, Kk)
+                    out[e] = (w * gs[e] if gs is not None else w).to(dtype)
+                return out
+
+            if moe.op_type == "QMoE":
+                if str(_attr(moe, "quant_type", "")) not in ("fp4", "mxfp4") or int(_attr(moe, "expert_weight_bits", 4)) != 4:
+                    raise NotImplementedError("QMoE: only MXFP4 (quant_type fp4, block 32) experts are supported")
+                ins = list(moe.inputs) + [""] * 17
+                lw.exp_gate_up_w, lw.exp_gate_up_b = experts_fp4(ins[2], ins[3], ins[15]), experts(ins[4])
+                lw.exp_down_w, lw.exp_down_b = experts_fp4(ins[5], ins[6], ins[16]), experts(ins[7])
+            else:
+                lw.exp_gate_up_w, lw.exp_gate_up_b = experts(moe.inputs[2]), experts(moe.inputs[3])
+                lw.exp_down_w, lw.exp_down_b = experts(moe.inputs[4]), experts(moe.inputs[5])
             lw.exp_blocked = False
             if torch.device(device).type == "cuda" and (lw.exp_gate_up_w.shape[1] // 2) % 64 == 0:
                 # grouped GEMM layout: per expert, blocks of 64 gate rows + the 64 up rows of the same features

@@ -99,7 +99,7 @@ def build_case(name, T, L, tp=1):
             from ..ops.w4 import W4Weight, unpack_ort_q4
             ws = []
             for _ in range(L):
-                qw, s, zp = quantize_int4_block32(torch.randn(N, K) * 0.02)
+                qw, s, zp = quantize_int4_block32(torch.randn(N, K, device="cuda") * 0.02)   # quantised and repacked on the device
                 q, z = unpack_ort_q4(qw, zp, N, K)
                 ws.append(W4Weight.from_quantized(q, s, z, "cuda", keep_host=False))
             nbytes = ws[0].packed.numel()

@@ -137,3 +137,32 @@ def test_beam_search_cache_sharing_matches_full_recompute(tmp_path):
     # the pool never leaks: every block is either referenced or free
     st = g.state
     assert int((st._ref > 0).sum()) + len(st._free) == st.rows * st.blocks_per_row
+
+
+def test_mxfp4_expert_round_trip_and_model(tmp_path):
+    """MXFP4 (FP4 e2m1 + e8m0 block scales) experts: quantiser / dequantiser agree, the QMoE export loads, and its
+    logits follow the bf16-free fp32 model built from the dequantised experts."""
+    from onnxruntime_genai_b200.models.builder import dequantize_mxfp4, quantize_mxfp4
+    w = torch.randn(64, 96, generator=torch.Generator().manual_seed(3)) * 0.3
+    packed, codes = quantize_mxfp4(w)
+    assert packed.shape == (96, 32) and codes.shape == (64, 3) and packed.dtype == torch.uint8
+    back = dequantize_mxfp4(packed, codes, 64, 96)
+    # the scale exponent is rounded to nearest, so a block maximum may clip at 6 * scale: error <= (6 * sqrt(2) - 6) * scale;
+    # inside the grid the largest half step is 1 * scale
+    scale = torch.pow(2.0, codes.float() - 127.0).repeat_interleave(32, dim=1)
+    assert bool(((back - w).abs() <= scale * 2.5 + 1e-6).all())
+    assert float(((back - w).abs() / scale).mean()) < 0.3
+    arch = ArchConfig(**{**BASE, **FAMILIES["gptoss"]})
+    sd = random_state_dict(arch, seed=5, std=0.15)
+    d = str(tmp_path / "q")
+    export_model(copy.deepcopy(arch), d, "int4", "cpu", state_dict=sd)
+    model = og.Model(d)
+    assert model.arch.num_experts == 4 and model.arch.intermediate_size == arch.intermediate_size
+    # reference: the same network with every quantised tensor replaced by its dequantised value
+    from onnxruntime_genai_b200.models.builder import dequantize_int4_block32, quantize_int4_block32
+    sd_q = dict(sd)
+    for k, v in sd.items():
+        if k.endswith(("mlp.experts.gate_up_proj", "mlp.experts.down_proj")):
+            sd_q[k] = torch.stack([dequantize_mxfp4(*quantize_mxfp4(v[e].float()), v.shape[1], v.shape[2]) for e in range(v.shape[0])])
+    lw = model.decoder.layers[0]
+    np.testing.assert_allclose(lw.exp_down_w.float().numpy(), sd_q["model.layers.0.mlp.experts.down_proj"].numpy(), rtol=0, atol=1e-6)

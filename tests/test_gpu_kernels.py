@@ -410,18 +410,24 @@ def test_gemm_w4_gate_up_pair():
     ops.check_kernel_status()
 
 
+_GEMV_CASES = {}
+
+
 @pytest.mark.parametrize("M", [1, 2, 3, 4])
 def test_gemv_w4_few_tokens(M):
-    """One to four tokens take the weight-streaming GEMV: all epilogues, uneven k splits, rows past N, against the
-    dequantised fp32 product and against the tensor-core kernel on the same inputs."""
-    for N, K, splits in ((9216, 3072, 0), (1000, 512, 3), (128, 64, 1), (3072, 8192, 0)):
-        w4, _ = _w4_case(N, K, seed=60)
+    """One to four tokens take the weight-streaming GEMV: all epilogues, uneven k splits, rows past N, many k-blocks per
+    CTA, against the dequantised fp32 product."""
+    for N, K, splits in ((1152, 768, 0), (1000, 512, 3), (128, 64, 1), (256, 4096, 2)):
+        if (N, K) not in _GEMV_CASES:      # quantising on the host is the slow part: once per shape
+            w4, _ = _w4_case(N, K, seed=60)
+            _GEMV_CASES[(N, K)] = (w4, w4.dequantize())
+        w4, wd = _GEMV_CASES[(N, K)]
         x, bias, res = _rand(M, K, seed=61), _rand(N, seed=62), _rand(M, N, seed=63)
-        want = ref.linear(x.cpu(), w4.dequantize(), bias.cpu(), res.cpu())
+        want = ref.linear(x.cpu(), wd, bias.cpu(), res.cpu())
         y = ops.linear(x, w4, bias=bias, residual=res, splits=splits)
         _close(y, want, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.05)
         y32 = ops.linear(x, w4, out_fp32=True, splits=splits)
-        _close(y32, ref.linear(x.cpu(), w4.dequantize(), out_fp32=True), rtol=1e-2, atol=1e-2 * math.sqrt(K) * 0.05)
+        _close(y32, ref.linear(x.cpu(), wd, out_fp32=True), rtol=1e-2, atol=1e-2 * math.sqrt(K) * 0.05)
     ops.check_kernel_status()
     # paired SiLU*mul epilogue
     from onnxruntime_genai_b200.models.builder import quantize_int4_block32
