@@ -14,10 +14,16 @@
 // Work decomposition: one CTA = (request, kv head, tile of 64 (or, in decode, 16) query rows, kv split) where a
 // "row" is one (query token, query head of the group) pair, so a decode step of a 4:1 GQA model
 // keeps its 4 heads in one MMA tile and reads each K/V row once.  K/V tiles of 64 keys are
-// gathered through the block table with 16-byte cp.async copies into XOR-swizzled shared memory,
-// three tiles in flight per CTA; QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
+// gathered through the block table into swizzled shared memory, three tiles in flight per CTA:
+// with cache blocks of a multiple of 16 tokens and head_dim 64 or 128, by TMA — one elected thread issues a
+// [16 keys x 64 dims] box per cache block and half row (tensor map over the cache as [slots, kv_heads * head_dim],
+// 128-byte swizzle, completion on an mbarrier), so the warps spend no instructions on the copies; otherwise with
+// 16-byte cp.async copies.  QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
 // tile's M is at most a few rows in decode, far below the 64-row minimum of tcgen05.mma, and
 // the kernel is bound by the KV stream, not by tensor throughput.)
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -39,6 +45,7 @@ struct AttnParams {
   const float* sinks;
   float scale, softcap;
   int window, B, Hq, Hkv, splits, total_rows;
+  int* status;       // device status word (bounded waits)
   int chunk;   // > 0: every split owns a fixed range of `chunk` keys (multiple of 64); 0: a request's keys are divided evenly
 };
 
@@ -51,15 +58,20 @@ __device__ __forceinline__ int swz(int row, int chunk) {  // element offset of a
 // All four warps then share those rows and split the 64 keys of every K/V tile between them
 // (16 keys each), keeping private online-softmax state that is merged through shared memory at the
 // end.  DECODE = false: each warp owns 16 of the 64 query rows and walks the whole tile.
-template <int D, bool DECODE>
-__global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnParams p) {
+// TMA = true: K/V tiles arrive as [half row of 64 dims][64 keys][128 bytes] boxes with the 128-byte swizzle.
+template <int D, bool DECODE, bool TMA>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, AttnParams p) {
   constexpr int SROW = ((D + 63) / 64) * 64;
   constexpr int CHUNKS = D / 8;     // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;    // k-steps of QK^T
   constexpr int DTILES = D / 8;     // n-tiles of PV
   constexpr int BM = DECODE ? 16 : ATT_BM;
   constexpr int NT = DECODE ? 2 : ATT_BN / 8;  // score n-tiles (8 keys each) per warp and K/V tile
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(128) uint8_t smem_dyn[];
+  // TMA boxes with the 128-byte swizzle need 1 KiB-aligned destinations (the launcher adds the slack)
+  uint8_t* smem_raw = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023)) : smem_dyn;
+  __shared__ uint64_t kv_full[ATT_STAGES];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sK = sQ + BM * SROW;                        // [STAGES][BN][SROW]
   __nv_bfloat16* sV = sK + ATT_STAGES * ATT_BN * SROW;       // [STAGES][BN][SROW]
@@ -105,6 +117,37 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
     return;
   }
 
+  // element offset of 16-byte chunk `ch` of key row `key` inside a K/V stage
+  auto kvoff = [&](int key, int ch) -> int {
+    if (TMA) return (ch >> 3) * (ATT_BN * 64) + key * 64 + (((ch ^ key) & 7) << 3);
+    return swz<SROW>(key, ch);
+  };
+  if (TMA) {
+    if (tid == 0) {
+      for (int sgi = 0; sgi < ATT_STAGES; ++sgi) mbar_init(&kv_full[sgi], 1);
+      mbar_fence_init();
+    }
+    __syncthreads();
+  }
+  // TMA: one thread, per 16 keys and half row one box for K and one for V.  Key groups past the end of the range re-read
+  // the last valid group (finite data; their scores are masked), so every stage always receives the same byte count.
+  auto load_kv_tma = [&](int tile, int buf) {
+    constexpr int HALVES = D / 64;
+    mbar_expect_tx(&kv_full[buf], 2 * ATT_BN * D * 2);
+    __nv_bfloat16* dk = sK + buf * ATT_BN * SROW;
+    __nv_bfloat16* dv = sV + buf * ATT_BN * SROW;
+    const int last_group = max(0, (kv_hi - 1) / 16 * 16);
+#pragma unroll
+    for (int gq = 0; gq < ATT_BN / 16; ++gq) {
+      const int j0 = min(tile * ATT_BN + gq * 16, last_group);
+      const int slot0 = table[j0 / p.block_size] * p.block_size + j0 % p.block_size;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_2d(dk + h * (ATT_BN * 64) + gq * 16 * 64, &tmap_k, &kv_full[buf], kvh * D + h * 64, slot0);
+        tma_load_2d(dv + h * (ATT_BN * 64) + gq * 16 * 64, &tmap_v, &kv_full[buf], kvh * D + h * 64, slot0);
+      }
+    }
+  };
   // Each warp copies 16 key rows of the tile.  Lanes 0..15 look up the cache slot of one row each; the
   // copies then walk the warp's rows chunk by chunk with consecutive lanes on consecutive 16-byte
   // chunks, so every warp instruction covers whole 32-byte sectors (full rows for head_dim 128).
@@ -136,10 +179,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
     if (ok) src = p.q + size_t(tok0 + gr / G) * p.q_stride + size_t(kvh * G + gr % G) * D + ch * 8;
     cp_async16(sQ + swz<SROW>(r, ch), src, ok);
   }
-  if (n_tiles > 0) load_kv(tile_begin, 0);
-  cp_async_commit();
-  if (n_tiles > 1) load_kv(tile_begin + 1, 1);
-  cp_async_commit();
+  if (TMA) {
+    if (tid == 0) {
+      if (n_tiles > 0) load_kv_tma(tile_begin, 0);
+      if (n_tiles > 1) load_kv_tma(tile_begin + 1, 1);
+    }
+    cp_async_commit();   // the Q tile
+  } else {
+    if (n_tiles > 0) load_kv(tile_begin, 0);
+    cp_async_commit();
+    if (n_tiles > 1) load_kv(tile_begin + 1, 1);
+    cp_async_commit();
+  }
+  bool kv_dead = false;
+  volatile int kv_dead_flag = 0;   // never set: the wait gives up on its time limit only
 
   const int row_base = DECODE ? 0 : warp * 16;       // first tile row of this warp
   const int key_base = DECODE ? warp * 16 : 0;       // first key (within a K/V tile) of this warp
@@ -148,6 +201,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
   const int gr_lo = row0 + row_base + g, gr_hi = gr_lo + 8;
   const int qpos_lo = past + gr_lo / G, qpos_hi = past + gr_hi / G;
   const bool valid_lo = gr_lo < rows, valid_hi = gr_hi < rows;
+  const bool use_hi = !DECODE || rows > 8;   // uniform over the CTA: decode tiles of a group of <= 8 heads use rows 0..7 only
 
   float o[DTILES][4];
 #pragma unroll
@@ -158,10 +212,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
 
   for (int it = 0; it < n_tiles; ++it) {
     const int buf = it % ATT_STAGES;
-    if (it + 2 < n_tiles) load_kv(tile_begin + it + 2, (it + 2) % ATT_STAGES);
-    cp_async_commit();
-    cp_async_wait<2>();
-    __syncthreads();
+    if (TMA) {
+      if (tid == 0 && it + 2 < n_tiles) load_kv_tma(tile_begin + it + 2, (it + 2) % ATT_STAGES);
+      if (it == 0) { cp_async_wait<0>(); __syncthreads(); }   // the Q tile
+      if (!kv_dead && !mbar_wait_bounded(&kv_full[buf], (it / ATT_STAGES) & 1, &kv_dead_flag)) {
+        atomicMax(p.status, OGB_ERR_WAIT_TMA);
+        kv_dead = true;
+      }
+    } else {
+      if (it + 2 < n_tiles) load_kv(tile_begin + it + 2, (it + 2) % ATT_STAGES);
+      cp_async_commit();
+      cp_async_wait<2>();
+      __syncthreads();
+    }
     if (it == 0 && warp_active) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -181,7 +244,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
         for (int np = 0; np < NT / 2; ++np) {
           uint32_t kb[4];
           const int key = key_base + (np * 2 + (lane >> 4)) * 8 + (lane & 7);
-          ldmatrix_x4(kb, tk + swz<SROW>(key, ks * 2 + ((lane >> 3) & 1)));
+          ldmatrix_x4(kb, tk + kvoff(key, ks * 2 + ((lane >> 3) & 1)));
           mma_bf16_16816(s[np * 2], qf[ks], kb[0], kb[1]);
           mma_bf16_16816(s[np * 2 + 1], qf[ks], kb[2], kb[3]);
         }
@@ -195,6 +258,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
         for (int e = 0; e < 4; ++e) {
           const int j = jbase + nt * 8 + t4 * 2 + (e & 1);
           const bool hi = e >= 2;
+          if (hi && !use_hi) { s[nt][e] = -INFINITY; continue; }   // rows 8..15 of the tile are empty: no math for them
           const int qpos = hi ? qpos_hi : qpos_lo;
           bool ok = (hi ? valid_hi : valid_lo) && j >= kv_lo && j < kv_hi && j <= qpos;
           if (p.window > 0) ok = ok && j > qpos - p.window;
@@ -212,17 +276,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
       const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-      const float a_lo = exp2f(m_lo - ms_lo), a_hi = exp2f(m_hi - ms_hi);  // m_* = -inf -> 0
+      const float a_lo = exp2f(m_lo - ms_lo), a_hi = use_hi ? exp2f(m_hi - ms_hi) : 1.f;  // m_* = -inf -> 0
       m_lo = mn_lo; m_hi = mn_hi;
       l_lo *= a_lo; l_hi *= a_hi;
+      // the running maximum settles after the first tiles: skip the rescale of the accumulator when no row of the warp moved
+      if (__any_sync(0xffffffffu, a_lo != 1.f || a_hi != 1.f)) {
 #pragma unroll
-      for (int i = 0; i < DTILES; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
+        for (int i = 0; i < DTILES; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
+      }
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         s[nt][0] = exp2f(s[nt][0] - ms_lo); s[nt][1] = exp2f(s[nt][1] - ms_lo);
-        s[nt][2] = exp2f(s[nt][2] - ms_hi); s[nt][3] = exp2f(s[nt][3] - ms_hi);
         l_lo += s[nt][0] + s[nt][1];
-        l_hi += s[nt][2] + s[nt][3];
+        if (use_hi) {
+          s[nt][2] = exp2f(s[nt][2] - ms_hi); s[nt][3] = exp2f(s[nt][3] - ms_hi);
+          l_hi += s[nt][2] + s[nt][3];
+        } else {
+          s[nt][2] = 0.f; s[nt][3] = 0.f;
+        }
       }
       // O += P V
 #pragma unroll
@@ -236,7 +307,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) paged_attention_kernel(AttnPar
         for (int dp = 0; dp < DTILES / 2; ++dp) {
           uint32_t vb[4];
           const int key = key_base + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-          ldmatrix_x4_trans(vb, tv + swz<SROW>(key, dp * 2 + (lane >> 4)));
+          ldmatrix_x4_trans(vb, tv + kvoff(key, dp * 2 + (lane >> 4)));
           mma_bf16_16816(o[dp * 2], pa, vb[0], vb[1]);
           mma_bf16_16816(o[dp * 2 + 1], pa, vb[2], vb[3]);
         }
@@ -387,21 +458,32 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
-template <int D, bool DECODE>
-static int LaunchAttentionMode(const AttnParams& p, int max_q_len, cudaStream_t stream) {
+bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
+
+template <int D, bool DECODE, bool TMA>
+static int LaunchAttentionMode(const AttnParams& p, int max_q_len, int cache_slots, cudaStream_t stream) {
   constexpr int SROW = ((D + 63) / 64) * 64;
   constexpr int BM = DECODE ? 16 : ATT_BM;
-  constexpr int SMEM = (BM + 2 * ATT_STAGES * ATT_BN) * SROW * 2;
+  constexpr int SMEM = (BM + 2 * ATT_STAGES * ATT_BN) * SROW * 2 + (TMA ? 1024 : 0);
   static_assert(!DECODE || (4 * 16 * D + 4 * 16 * 2) * 4 <= ATT_STAGES * ATT_BN * SROW * 2, "merge buffers must fit in the K stages");
   static bool configured = false;
+  auto kern = paged_attention_kernel<D, DECODE, TMA>;
   if (!configured) {
-    if (cudaFuncSetAttribute(paged_attention_kernel<D, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
     configured = true;
+  }
+  CUtensorMap mk, mv;
+  memset(&mk, 0, sizeof(mk));
+  memset(&mv, 0, sizeof(mv));
+  if (TMA) {
+    // the cache as a 2-D tensor [slots, kv_heads * head_dim]; a box is 16 consecutive slots x 64 dims of one head
+    if (!MakeMapBf16(&mk, p.k_cache, cache_slots, p.Hkv * D, p.Hkv * D, 16)) return -2;
+    if (!MakeMapBf16(&mv, p.v_cache, cache_slots, p.Hkv * D, p.Hkv * D, 16)) return -2;
   }
   const int G = p.Hq / p.Hkv;
   const int q_tiles = (max_q_len * G + BM - 1) / BM;
   dim3 grid(q_tiles, p.Hkv, p.B * p.splits);
-  paged_attention_kernel<D, DECODE><<<grid, ATT_THREADS, SMEM, stream>>>(p);
+  kern<<<grid, ATT_THREADS, SMEM, stream>>>(mk, mv, p);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (p.splits > 1) {
     const int warps = 4;
@@ -413,10 +495,20 @@ static int LaunchAttentionMode(const AttnParams& p, int max_q_len, cudaStream_t 
 }
 
 template <int D>
-static int LaunchAttention(const AttnParams& p, int max_q_len, cudaStream_t stream) {
+static int LaunchAttention(const AttnParams& p, int max_q_len, int cache_slots, cudaStream_t stream) {
   const int G = p.Hq / p.Hkv;
-  if (max_q_len * G <= 16) return LaunchAttentionMode<D, true>(p, max_q_len, stream);
-  return LaunchAttentionMode<D, false>(p, max_q_len, stream);
+  static const int tma_enabled = [] { const char* e = getenv("OGB_ATTN_TMA"); return (e && e[0] == '0') ? 0 : 1; }();
+  // TMA path: whole 16-key groups inside one cache block, 128-byte half rows, aligned cache, a status word for the waits
+  const bool tma = tma_enabled && (D == 64 || D == 128) && p.block_size % 16 == 0 && cache_slots >= 16 && p.status != nullptr &&
+                   ((reinterpret_cast<uintptr_t>(p.k_cache) | reinterpret_cast<uintptr_t>(p.v_cache)) & 15) == 0;
+  if constexpr (D == 64 || D == 128) {
+    if (tma) {
+      if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, true>(p, max_q_len, cache_slots, stream);
+      return LaunchAttentionMode<D, false, true>(p, max_q_len, cache_slots, stream);
+    }
+  }
+  if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, false>(p, max_q_len, cache_slots, stream);
+  return LaunchAttentionMode<D, false, false>(p, max_q_len, cache_slots, stream);
 }
 
 }  // namespace ogb
@@ -433,7 +525,7 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
                                 const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                                 int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
                                 int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
-                                long long scratch_bytes, void* stream_) {
+                                long long scratch_bytes, int cache_slots, int* status, void* stream_) {
   if (B <= 0 || total_tokens <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv || (q_stride % 8) || (out_stride % 2)) return -1;
   if (splits < 1) splits = 1;
@@ -441,6 +533,7 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
   if (splits > 1 && ogb_attention_scratch_bytes(total_tokens, Hq, D, splits) > scratch_bytes) return -2;
   AttnParams p;
   p.chunk = splits > 1 ? kv_chunk : 0;
+  p.status = status;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.block_table = block_table; p.table_cols = table_cols;
@@ -452,9 +545,9 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.splits = splits;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   switch (D) {
-    case 64: return LaunchAttention<64>(p, max_q_len, stream);
-    case 96: return LaunchAttention<96>(p, max_q_len, stream);
-    case 128: return LaunchAttention<128>(p, max_q_len, stream);
+    case 64: return LaunchAttention<64>(p, max_q_len, cache_slots, stream);
+    case 96: return LaunchAttention<96>(p, max_q_len, cache_slots, stream);
+    case 128: return LaunchAttention<128>(p, max_q_len, cache_slots, stream);
   }
   return -5;
 }
@@ -491,5 +584,5 @@ OGB_API int ogb_paged_attention_noalloc(const void* q, int q_stride, const void*
   }
   return ogb_paged_attention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out,
                              out_stride, sinks, scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, 0,
-                             g_noalloc_scratch_addr[dev], OGB_NOALLOC_SCRATCH_BYTES, stream);
+                             g_noalloc_scratch_addr[dev], OGB_NOALLOC_SCRATCH_BYTES, 0, nullptr, stream);
 }

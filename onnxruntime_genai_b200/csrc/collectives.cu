@@ -8,6 +8,9 @@
 //   all-reduce      push to every rank (plane = source rank) | collect all planes | out = sum (rank order)
 //   all-gather      push to every rank (plane = source rank) | collect all planes | out[s * n + i] = plane s
 //   reduce-scatter  push vector of slice j to rank j only    | collect all planes | out = sum (rank order)
+//   push            push to every rank (plane = source rank) and return: the consumer is the next kernel, a GEMM that
+//                   assembles its activation tiles from these lines (all-gather -> GEMM, gemm_tcgen05.cu).  Two pushes
+//                   must be separated by a call that waits on every peer (any of the three above, or a fused GEMM).
 // Transfers are 16-byte peer stores carrying their own arrival flag; waits are bounded (status word, then the
 // kernel finishes without hanging); the last block closes the call's epoch.  No multimem / NVLS: ranks may
 // leave between steps.
@@ -16,7 +19,7 @@
 
 namespace ogb {
 
-enum CollMode { COLL_ALLREDUCE = 0, COLL_ALLGATHER = 1, COLL_REDUCE_SCATTER = 2 };
+enum CollMode { COLL_ALLREDUCE = 0, COLL_ALLGATHER = 1, COLL_REDUCE_SCATTER = 2, COLL_PUSH = 3 };
 
 constexpr int COLL_THREADS = 256;
 
@@ -53,7 +56,7 @@ collective_kernel(const CommParams c, const __nv_bfloat16* __restrict__ in, __nv
   // ---- collect the same vectors of every rank from the local receive buffer
   bool dead = *reinterpret_cast<volatile int*>(status) != 0;
   const uint4* base = c.buf[c.rank] + par_off;
-  for (long long v = first; v < vecs; v += stride) {
+  for (long long v = first; v < vecs && MODE != COLL_PUSH; v += stride) {
     if (MODE == COLL_ALLGATHER) {
       for (int r = 0; r < c.world; ++r) {
         const uint4 q0 = wait_line(base + size_t(r) * plane_lines + size_t(v) * 2, flag, dead, status);
@@ -93,7 +96,8 @@ collective_kernel(const CommParams c, const __nv_bfloat16* __restrict__ in, __nv
 
 using namespace ogb;
 
-// mode 0 all-reduce (in/out n elements), 1 all-gather (in n, out world * n), 2 reduce-scatter (in world * n, out n).
+// mode 0 all-reduce (in/out n elements), 1 all-gather (in n, out world * n), 2 reduce-scatter (in world * n, out n),
+// 3 push (in n; no output: the next kernel reads the lines).
 // n must be a multiple of 8 and at most the registered plane size; pointers 16-byte aligned.  residual (modes 0, 2) is
 // added to the sum.  Uses the symmetric buffers registered for `device` with ogb_comm_register.
 OGB_API int ogb_collective(int mode, const void* in, void* out, const void* residual, long long n, int device, int* status,
@@ -103,6 +107,7 @@ OGB_API int ogb_collective(int mode, const void* in, void* out, const void* resi
   if (n <= 0) return 0;
   if ((n % 8) || n > cp->plane_elems) return -1;
   if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15) return -1;
+  if (mode != COLL_PUSH && !out) return -1;
   long long blocks = (n / 8 + COLL_THREADS * 2 - 1) / (COLL_THREADS * 2);   // ~2 vectors per thread
   const long long cap = sm_count * 2;
   if (blocks > cap) blocks = cap;
@@ -115,6 +120,7 @@ OGB_API int ogb_collective(int mode, const void* in, void* out, const void* resi
     case COLL_ALLREDUCE: collective_kernel<COLL_ALLREDUCE><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, o, r, n, status); break;
     case COLL_ALLGATHER: collective_kernel<COLL_ALLGATHER><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, o, nullptr, n, status); break;
     case COLL_REDUCE_SCATTER: collective_kernel<COLL_REDUCE_SCATTER><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, o, r, n, status); break;
+    case COLL_PUSH: collective_kernel<COLL_PUSH><<<unsigned(blocks), COLL_THREADS, 0, stream>>>(*cp, i, nullptr, nullptr, n, status); break;
     default: return -1;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

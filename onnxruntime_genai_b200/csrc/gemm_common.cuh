@@ -56,6 +56,11 @@ struct GemmParams {
   int* status;
   int pdl;
   CommParams comm;
+  int comm_epilogue;    // 1: the epilogue runs the fused all-reduce / reduce-scatter (and the call closes an epoch)
+  int ag_rows;          // > 0: all-gather -> GEMM: the activations are not read through the tensor map but assembled from the
+                        // flagged lines that the ranks pushed into this rank's receive buffer in the previous fused call
+                        // (rank r pushed token rows [r * ag_rows, (r + 1) * ag_rows) as [row][K] into its plane)
+  int rs_rows;          // > 0: reduce-scatter by token rows: rank r receives (and stores, as its rows 0..) rows [r * rs_rows, (r + 1) * rs_rows)
   GroupParams grp;
 };
 
@@ -171,7 +176,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     const int n_out = p.act_pair ? p.N / 2 : p.N;    // output columns of the whole problem
     const int col0 = n_tile * (p.act_pair ? 64 : 128);
     const uint32_t part_addr = smem_u32(part);
-    const bool comm_on = p.comm.buf[0] != nullptr;
+    const bool comm_on = p.comm_epilogue != 0;
 
     auto reduce8 = [&](int mc, int n_local, float (&v)[8]) {
 #pragma unroll
@@ -260,10 +265,12 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
       if (!comm_on) {
         store8(m, col, v);
       } else if (col < n_out) {
-        // push this rank's partial (bf16) into every rank's receive buffer: two flagged lines per 8 values
+        // push this rank's partial (bf16) into every rank's receive buffer (all-reduce) or into the buffer of the rank
+        // that owns the token row (reduce-scatter): two flagged lines per 8 values
         const size_t line = par_off + size_t(p.comm.rank) * plane_lines + (size_t(m) * n_out + col) / 4;
         const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
-        for (int r = 0; r < p.comm.world; ++r) {
+        const int r_lo = p.rs_rows > 0 ? m / p.rs_rows : 0, r_hi = p.rs_rows > 0 ? r_lo + 1 : p.comm.world;
+        for (int r = r_lo; r < r_hi; ++r) {
           st_line(p.comm.buf[r] + line, d0, d1, flag);
           st_line(p.comm.buf[r] + line + 1, d2, d3, flag);
         }
@@ -279,6 +286,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         const int m = row0 + mc;
         const int col = col0 + oc * 8;
         if (mc >= rows || col >= n_out) continue;
+        if (p.rs_rows > 0 && m / p.rs_rows != p.comm.rank) continue;   // another rank's row
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         const uint4* base = p.comm.buf[p.comm.rank] + par_off + (size_t(m) * n_out + col) / 4;
         for (int r = 0; r < p.comm.world; ++r) {   // rank order: bit-identical sums on every rank
@@ -287,7 +295,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
           const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
           v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
         }
-        store8(m, col, v);
+        store8(p.rs_rows > 0 ? m - p.comm.rank * p.rs_rows : m, col, v);
       }
       if (dead) *abort_flag = 1;
     }
@@ -296,7 +304,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     __syncwarp();
     cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
   }
-  if (p.comm.buf[0] != nullptr) {
+  if (p.comm_epilogue) {
     // The last CTA of the call to get here closes the epoch (every CTA passes this point, also after an abort).
     __syncthreads();
     if (threadIdx.x == 0) {

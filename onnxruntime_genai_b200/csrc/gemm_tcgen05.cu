@@ -76,8 +76,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     w_row0 = p.grp.tile_expert[m_tile] * p.N;
   }
 
+  const bool gather = p.ag_rows > 0;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    // gathered activations: a stage is full when the weight tile has landed AND the 128 assembling threads have arrived
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], gather ? 1 + 128 : 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -103,10 +105,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       // ------------------------------------------------------------------ TMA producer
       auto load_w = [&](int i) {
         const int s = i % STAGES;
-        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], gather ? W_TILE_BYTES : Cfg::STAGE_BYTES);
         tma_load_2d(stage_w(s), &tmap_w, &full_bar[s], (kb0 + i) * GEMM_BLOCK_K, w_row0 + n_tile * GEMM_BLOCK_N);
       };
       auto load_a = [&](int i) {
+        if (gather) return;   // assembled by warps 2..5 below
         tma_load_2d(stage_a(i % STAGES), &tmap_a, &full_bar[i % STAGES], (kb0 + i) * GEMM_BLOCK_K, row0);
       };
       // Weights are never written by an earlier kernel of the stream: fill the pipeline with them
@@ -150,6 +153,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       }
       if (ok) umma_commit(accum_bar);
     }
+  }
+
+  if (gather && warp >= 2) {
+    // ------------------------------------------------------------------ all-gather -> GEMM: assemble the activation tiles
+    // Each k-block's [BT rows][64] tile is built from 16-byte lines {4 bf16, flag} of the local receive buffer (written by
+    // every rank's push in the previous fused call), waiting for each line's flag, and stored in the 128-byte-swizzled
+    // K-major layout the tensor core reads; then the 128 threads arrive on the stage's barrier.
+    const int gt = threadIdx.x - 64;
+    if (p.pdl) pdl_wait();
+    const uint32_t ep = *reinterpret_cast<volatile uint32_t*>(p.comm.epoch) - 1u;   // the push was the previous call
+    const uint32_t flag = comm_flag(ep);
+    const size_t plane_lines = size_t(p.comm.plane_elems) / 4;
+    const uint4* base = p.comm.buf[p.comm.rank] + size_t(ep & 1) * p.comm.world * plane_lines;
+    bool dead = *reinterpret_cast<volatile int*>(p.status) != 0;
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES && !mbar_wait_bounded(&empty_bar[s], ((i / STAGES) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); }
+      uint8_t* tile = stage_a(s);
+      const int k0 = (kb0 + i) * GEMM_BLOCK_K;
+      for (int idx = gt; idx < BT * 16; idx += 128) {
+        const int r = idx >> 4, ln = idx & 15;          // row of the tile, line of the row (4 bf16 each)
+        const int m = row0 + r, k = k0 + ln * 4;
+        uint2 d = make_uint2(0u, 0u);
+        if (r < rows && k < p.K) {
+          const int owner = m / p.ag_rows, rl = m - owner * p.ag_rows;
+          const uint4 q = wait_line(base + size_t(owner) * plane_lines + (size_t(rl) * p.K + k) / 4, flag, dead, p.status);
+          d = make_uint2(q.x, q.z);
+        }
+        const int chunk = ln >> 1;
+        *reinterpret_cast<uint2*>(tile + r * 128 + (((chunk ^ (r & 7)) << 4) | ((ln & 1) << 3))) = d;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to tcgen05.mma
+      mbar_arrive(&full_bar[s]);
+    }
+    if (dead) *abort_flag = 1;
   }
 
   gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0);
@@ -299,7 +337,9 @@ OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void*
 }
 
 // flags bit 0: fp32 output; bit 1: paired silu(gate)*up epilogue (N = 2 * output columns, rows
-// interleaved in blocks of 64); bit 2: fused all-reduce over the registered symmetric buffers.
+// interleaved in blocks of 64); bit 2: fused all-reduce over the registered symmetric buffers; bit 3: fused
+// reduce-scatter by token rows instead (rank r ends up with rows [r * ceil(M / world), ...) of the sum, written as
+// rows 0.. of C; residual, if given, is that slice too).
 OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
                           const void* bias, const void* residual, int ldr, int flags, int splits, int device, int* status,
                           int sm_count, void* stream_) {
@@ -307,7 +347,7 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (lda % 8) || (ldw % 8)) return -1;  // 16-byte global strides for TMA
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -1;
-  const int out_fp32 = flags & 1, act_pair = (flags >> 1) & 1, fused_ar = (flags >> 2) & 1;
+  const int out_fp32 = flags & 1, act_pair = (flags >> 1) & 1, fused_rs = (flags >> 3) & 1, fused_ar = ((flags >> 2) & 1) | fused_rs;
   if (act_pair && (N % 128)) return -1;
   static const int pdl_enabled = [] { const char* e = getenv("OGB_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
   const int bt = ogb_gemm_token_tile(M, 0);
@@ -338,6 +378,18 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     const long long n_out = act_pair ? N / 2 : N;
     if (n_out % 8 || (long long)M * n_out > c.plane_elems) return -2;
     p.comm = c;
+    p.comm_epilogue = 1;
+    if (fused_rs) p.rs_rows = (M + c.world - 1) / c.world;
+  }
+  if (flags & 16) {
+    // all-gather -> GEMM: A is ignored; the activations come from the receive buffer filled by the previous fused call
+    // (ogb_collective mode 3: every rank pushed its ceil(M / world) token rows of K values)
+    if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
+    const CommParams& c = g_comm[device];
+    const int per = (M + c.world - 1) / c.world;
+    if ((K % 8) || (long long)per * K > c.plane_elems) return -2;
+    p.comm = c;          // the mainloop needs the buffer and epoch pointers; the epilogue stays local unless bits 2/3 are set
+    p.ag_rows = per;
   }
   dim3 grid(n_tiles, m_tiles, splits);
   switch (bt) {

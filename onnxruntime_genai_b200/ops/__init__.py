@@ -97,7 +97,7 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) ->
 
 
 # ------------------------------------------------------------------------------------------ GEMM
-GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE = 1, 2, 4
+GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A = 1, 2, 4, 8, 16
 
 
 def _gemm(x, w, out, bias, residual, flags, splits):
@@ -119,9 +119,11 @@ def _gemm_w4(x, w, out, bias, residual, flags, splits):
     return out
 
 
-def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False):
+def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None):
     """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous).  With all_reduce the
-    partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory."""
+    partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory.
+    reduce_scatter=(rank, world): the sum is scattered by token rows instead (sequence-parallel form): the result has
+    this rank's rows [rank * ceil(T / world), ...) only, and `residual` is that slice."""
     if isinstance(w, W4Weight):
         if not x.is_cuda:
             return ref.linear(x, w.dequantize(), bias, residual, out_fp32)
@@ -134,10 +136,31 @@ def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, a
         return ref.linear(x, w, bias, residual, out_fp32)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert x.stride(-1) == 1 and w.stride(-1) == 1
+    rows_out = x.shape[0]
+    if reduce_scatter is not None:
+        rank, world = reduce_scatter
+        per = -(-x.shape[0] // world)
+        rows_out = max(0, min(per, x.shape[0] - rank * per))
     if out is None:
-        out = torch.empty(x.shape[0], w.shape[0], dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
-    flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0)
+        out = torch.empty(rows_out, w.shape[0], dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
+    flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0) | (GEMM_REDUCE_SCATTER if reduce_scatter else 0)
     return _gemm(x, w, out, bias, residual, flags, splits)
+
+
+def linear_gathered(M: int, w, bias=None, out_fp32=False, act_pair=False, splits=0):
+    """all-gather -> GEMM in one kernel: y[M, N] = X @ w.T where X's token rows were pushed by the ranks with
+    `comm.all_gather_push` (rank r: rows [r * ceil(M / world), ...)) just before; the kernel builds its activation
+    tiles from the flagged lines in the local receive buffer as they arrive.  act_pair: silu(gate) * up epilogue for
+    weights in the 64-row gate/up block layout."""
+    N, K = w.shape
+    dev = w.device
+    out = torch.empty(M, N // 2 if act_pair else N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=dev)
+    ws = workspace(dev)
+    flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ACT_PAIR if act_pair else 0) | GEMM_GATHERED_A
+    rc = _lib.lib().ogb_gemm_bf16(_ptr(w), K, _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _ptr(bias), None, 0, int(flags),
+                                  int(splits), ws.index, ws.status, ws.sm_count, _stream())
+    _lib.check(rc, "gemm_bf16 (gathered activations)")
+    return out
 
 
 def interleave_gate_up(w: torch.Tensor, block: int = 64) -> torch.Tensor:
@@ -283,12 +306,13 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
 
 # ------------------------------------------------------------------------------------------ attention
 def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_count: int = 148, group: int = 1):
-    """(splits, kv_chunk) of a paged-attention launch.  Decode-sized launches (the rows of a request fit one 16-row
-    tile) split every request's keys into fixed chunks so that all CTAs carry the same work whatever the mix of
-    sequence lengths; the chunk is sized for about four CTAs per SM and at most 512 keys.  Other launches: (1, 0)."""
-    if max_q_len * group > 16 or max_kv_len <= 128:
-        return 1, 0
+    """(splits, kv_chunk) of a paged-attention launch.  A launch whose (request, kv head) grid already fills the GPU
+    twice over is not split (measured on B200: at 64 requests x 8 heads any split costs more in partial traffic and
+    the merge than it gains in balance).  Smaller decode-sized launches split every request's keys into fixed chunks
+    of 64..512 keys sized for about four CTAs per SM; other launches: (1, 0)."""
     ctas = max(1, batch * Hkv)
+    if max_q_len * group > 16 or max_kv_len <= 128 or ctas >= 2 * sm_count:
+        return 1, 0
     chunks_wanted = max(1, (4 * sm_count + ctas - 1) // ctas)
     chunk = (max_kv_len + chunks_wanted - 1) // chunks_wanted
     chunk = min(512, max(64, (chunk + 63) // 64 * 64))
@@ -323,7 +347,7 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
                                         _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0),
                                         _ptr(sinks), float(scale), float(softcap), int(window), B, q.shape[0], int(max_q_len),
                                         Hq, Hkv, D, int(splits), int(kv_chunk), _ptr(scratch),
-                                        scratch.numel() if scratch is not None else 0, _stream())
+                                        scratch.numel() if scratch is not None else 0, int(k_cache.shape[0]), ws.status, _stream())
     _lib.check(rc, "paged_attention")
     if splits > 1:
         _lib.LAUNCH_COUNT += 1  # the combine kernel

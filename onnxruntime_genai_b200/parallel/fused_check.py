@@ -41,6 +41,19 @@ def main():
         for _ in range(3):
             got = ops.linear(x, w, residual=resid, all_reduce=True)
             errs.append(float((got.float() - want).abs().max()))
+        per = -(-a.tokens // world)
+        rs = ops.linear(x, w, reduce_scatter=(rank, world))          # GEMM -> reduce-scatter by token rows, one kernel
+        errs_rs = float((rs.float() - want[rank * per:rank * per + rs.shape[0]]).abs().max()) if rs.shape[0] else 0.0
+        res["gemm_reduce_scatter_err"] = errs_rs
+        # all-gather -> GEMM: every rank pushes its token rows of a common activation matrix, then multiplies all rows
+        gx = torch.Generator(device=dev).manual_seed(99)
+        X = (torch.randn(a.tokens, a.hidden, generator=gx, device=dev) * 0.5).to(torch.bfloat16)
+        wg = (torch.randn(1024, a.hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        comm0 = tp.comm
+        comm0.all_gather_push(X[rank * per:(rank + 1) * per].contiguous())
+        yg = ops.linear_gathered(a.tokens, wg)
+        res["all_gather_gemm_exact"] = bool(torch.equal(yg, ops.linear(X, wg)))
+        comm0.all_reduce(X[:8].contiguous())     # a waiting call before any further push
         ops.check_kernel_status()
         res["max_err"] = max(errs)
         res["ref_scale"] = float(want.abs().mean())
@@ -86,6 +99,7 @@ def main():
         res["nccl_allgather_us"] = timed(lambda: dist.all_gather(parts, y))
 
         res["fused_us"] = timed(lambda: ops.linear(x, w, residual=resid, all_reduce=True))
+        res["fused_reduce_scatter_us"] = timed(lambda: ops.linear(x, w, reduce_scatter=(rank, world)))
         res["gemm_plus_nccl_us"] = timed(baseline)
         res["gemm_only_us"] = timed(lambda: ops.linear(x, w))
         ops.check_kernel_status()

@@ -56,6 +56,13 @@ class _Collectives:
         out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
         return self._run(1, x, out, None, x.numel() * x.element_size() // 2)
 
+    def all_gather_push(self, x: torch.Tensor) -> None:
+        """First half of all-gather -> GEMM: pushes this rank's token rows [rows, K] (bf16) into every rank's receive
+        buffer and returns; the GEMM launched next (`ops.linear_gathered`) assembles its activation tiles from the lines
+        as they arrive.  The call after that GEMM must be one that waits on every peer (any fused reduction)."""
+        assert x.dtype == torch.bfloat16 and self.fits(x)
+        self._run(3, x, x, None, x.numel())
+
     def reduce_scatter(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         """x [world, ...] bf16 partials -> sum over ranks of slice [rank] (+ residual)."""
         assert x.dtype == torch.bfloat16 and x.shape[0] == self.size and self.fits(x, self.size)

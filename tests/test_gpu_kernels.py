@@ -94,6 +94,8 @@ def test_gemm_fused_allreduce_world_of_one(M, N, K, splits):
             y = ops.linear(x, w, residual=res, splits=splits, all_reduce=True)
             ops.check_kernel_status()
             _close(y, want, rtol=3e-2, atol=0.06)
+            z = ops.linear(x, w, residual=res, splits=splits, reduce_scatter=(0, 1))   # scatter over one rank: every row stays
+            _close(z, want, rtol=3e-2, atol=0.06)
     finally:
         comm.close()
 
@@ -118,6 +120,27 @@ def test_standalone_collectives_world_of_one():
             assert torch.equal(comm.all_reduce(small), small)
         ops.check_kernel_status()
         assert not comm.fits(_rand(4096, 4096, seed=25))
+    finally:
+        comm.close()
+
+
+@pytest.mark.parametrize("M,N,K,pair", [(64, 512, 1024, False), (5, 256, 4096, False), (200, 384, 512, False), (48, 512, 256, True)])
+def test_gemm_all_gather_fused_world_of_one(M, N, K, pair):
+    """all-gather -> GEMM: activations pushed as flagged lines, tiles assembled inside the GEMM (swizzled layout,
+    row / k tails, split-K clusters), against the plain GEMM on the same data."""
+    from onnxruntime_genai_b200.parallel.symm import LocalComm
+    comm = LocalComm(torch.device("cuda", 0))
+    try:
+        x, w = _rand(M, K, seed=71), _rand(N, K, std=0.05, seed=72)
+        if pair:
+            w = ops.interleave_gate_up(w)
+        for _ in range(3):
+            comm.all_gather_push(x)
+            y = ops.linear_gathered(M, w, act_pair=pair)
+            want = ops.gate_up_act(x, w, interleaved=True) if pair else ops.linear(x, w)
+            ops.check_kernel_status()
+            assert torch.equal(y, want), f"max diff {(y.float() - want.float()).abs().max().item()}"
+            assert torch.equal(comm.all_reduce(x), x)     # a waiting call between two pushes
     finally:
         comm.close()
 
