@@ -15,6 +15,7 @@ retryable / capacity / fatal failures on the host without touching a GPU.
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Any, Dict, List, Optional
 
@@ -260,6 +261,29 @@ class ModelExecutor:
             return st.tokens_host[:B].numpy()
         return toks.numpy()
 
+    def execute_async(self, plan, edits=None, masks=None):
+        """Enqueues the step (input copy, model, sampler, copy of the ids to pinned memory) and returns a handle for
+        `collect`; the host does not wait."""
+        st = self.staging
+        B = len(plan.entries)
+        with torch.no_grad():
+            logits = self.forward(plan)
+            for e in edits or ():
+                ops.logits_edit(logits, *e)
+            if masks is not None:
+                ops.logits_bitmask(logits, *masks)
+            toks = ops.sample(logits, st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
+                              st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
+            st.tokens_host[:B].copy_(toks, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        return ev, B
+
+    def collect(self, handle) -> np.ndarray:
+        ev, B = handle
+        ev.synchronize()
+        return self.staging.tokens_host[:B].numpy().copy()   # the pinned buffer is reused by the step already in flight
+
 
 # ------------------------------------------------------------------------------------------------ engine
 class Engine:
@@ -297,6 +321,9 @@ class Engine:
         self._guidance: Dict[int, Any] = {}
         self.last_outcome = StepOutcome.NoWork
         self.step_count = 0
+        self._inflight = None
+        # one step ahead of the caller: only with the built-in executor on a GPU (OGB_ENGINE_RUN_AHEAD=0 turns it off)
+        self.run_ahead = (executor is None and model.device.type == "cuda" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
 
     def _blocks_from_memory(self, utilization: float) -> int:
         arch, dec = self.model.arch, self.model.decoder
@@ -326,6 +353,8 @@ class Engine:
     def remove_request(self, request: Request):
         if request._native is None:
             return
+        if self._inflight is not None and any(e.request.id == request._native.id for e in self._inflight[0].entries):
+            self._drain()     # the request is part of the step in flight: let that step commit first
         self.core.remove_request(request._native)
         self._by_native.pop(request._native.id, None)
         self._guidance.pop(request._native.id, None)
@@ -335,16 +364,57 @@ class Engine:
 
     def step(self) -> Optional[Request]:
         """Returns one request that has unseen tokens (or just finished its turn), running the model when
-        no such request is waiting; returns None when there is nothing to do."""
+        no such request is waiting; returns None when there is nothing to do.
+
+        On CUDA the engine runs one step ahead: as soon as the ids of a step are committed the next step is planned,
+        packed and enqueued, and only then are the ready requests handed out, so the GPU computes step n + 1 while the
+        caller consumes the tokens of step n."""
         nat = self.core.next_ready()
         if nat is None:
-            self._run_model_step()
+            self._advance()
             nat = self.core.next_ready()
         return self._by_native.get(nat.id) if nat is not None else None
 
     # ------------------------------------------------------------------ internals
+    def _advance(self):
+        if self._inflight is None:
+            self._launch()
+        if self._inflight is not None:
+            self._finish()
+            if self.run_ahead and self.last_outcome == StepOutcome.Committed:
+                self._launch()
+
+    def _drain(self):
+        """Completes the step in flight, if any (before the set of requests changes under it)."""
+        if self._inflight is not None:
+            self._finish()
+
     def _run_model_step(self):
-        with _Trace("engine", "step"):
+        """One synchronous step: plan, execute, commit."""
+        self._drain()
+        self._launch()
+        if self._inflight is not None:
+            self._finish()
+
+    def _fail(self, e: Exception):
+        if isinstance(e, ExecutionFailure):
+            outcome = self.core.abort(e.kind, str(e))
+            self.last_outcome = outcome
+            if outcome in (StepOutcome.FatalExecutionFailure, StepOutcome.ExecutionContractFailure):
+                raise EngineStepError(outcome, str(e)) from e
+            return
+        if isinstance(e, torch.cuda.OutOfMemoryError):
+            self.last_outcome = self.core.abort(FailureKind.CapacityExceeded, str(e))
+            return
+        kind = FailureKind.CapacityExceeded if "out of memory" in str(e).lower() else FailureKind.Fatal
+        self.last_outcome = self.core.abort(kind, str(e))
+        if kind == FailureKind.Fatal:
+            raise EngineStepError(self.last_outcome, str(e)) from e
+
+    def _launch(self):
+        """Plans and packs a step and hands it to the executor; leaves it in `_inflight` (with its ids already there
+        when the executor is synchronous)."""
+        with _Trace("engine", "launch"):
             plan = self.core.plan()
             self.last_outcome = plan.outcome
             if plan.unserviceable:
@@ -358,22 +428,23 @@ class Engine:
             try:
                 self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
                 edits, masks = self._logits_processors(plan)
-                toks = self.executor.execute(plan, edits, masks)
-            except ExecutionFailure as e:
-                outcome = self.core.abort(e.kind, str(e))
-                self.last_outcome = outcome
-                if outcome in (StepOutcome.FatalExecutionFailure, StepOutcome.ExecutionContractFailure):
-                    raise EngineStepError(outcome, str(e)) from e
-                return
-            except torch.cuda.OutOfMemoryError as e:
-                self.last_outcome = self.core.abort(FailureKind.CapacityExceeded, str(e))
-                return
+                if self.run_ahead:
+                    self._inflight = (plan, self.executor.execute_async(plan, edits, masks), None)
+                else:
+                    self._inflight = (plan, None, self.executor.execute(plan, edits, masks))
             except Exception as e:
-                kind = FailureKind.CapacityExceeded if "out of memory" in str(e).lower() else FailureKind.Fatal
-                self.last_outcome = self.core.abort(kind, str(e))
-                if kind == FailureKind.Fatal:
-                    raise EngineStepError(self.last_outcome, str(e)) from e
-                return
+                self._fail(e)
+
+    def _finish(self):
+        with _Trace("engine", "finish"):
+            plan, handle, toks = self._inflight
+            self._inflight = None
+            if handle is not None:
+                try:
+                    toks = self.executor.collect(handle)
+                except Exception as e:
+                    self._fail(e)
+                    return
             now = time.perf_counter()
             for i, e in enumerate(plan.entries):
                 if not e.samples:

@@ -160,3 +160,57 @@ def test_beam_search_on_gpu_matches_cpu(dirs):
                 break
             same += 1
         assert same >= 17 + 6, f"prompt {b}: GPU and CPU beams diverge after {same - 17} generated tokens"
+
+
+def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, monkeypatch):
+    """The engine computes step n + 1 while the caller consumes step n: same tokens as the synchronous engine, requests
+    added and cancelled while a step is in flight, every block back in the pool at the end."""
+    model = og.Model(dirs[0])
+    rng = np.random.RandomState(17)
+    prompts = [rng.randint(0, 32000, size=(n,)).astype(np.int32) for n in (21, 64, 9, 40)]
+
+    def make(p, sd, extra=24):
+        gp = og.GeneratorParams(model)
+        gp.set_search_options(max_length=len(p) + extra, do_sample=True, top_k=40, top_p=0.9, temperature=0.8, random_seed=sd)
+        r = og.Request(gp)
+        r.add_tokens(p)
+        return r
+
+    def run(engine, cancel_at=None, late_add=None):
+        reqs = [make(p, i) for i, p in enumerate(prompts)]
+        outs = {id(r): [] for r in reqs}
+        for r in reqs[:3]:
+            engine.add_request(r)
+        n_calls = 0
+        cancelled = False
+        while engine.has_pending_requests():
+            r = engine.step()
+            n_calls += 1
+            if late_add is not None and n_calls == late_add:
+                engine.add_request(reqs[3])
+            if r is None:
+                continue
+            while r.has_unseen_tokens():
+                outs[id(r)].append(r.get_unseen_token())
+            if cancel_at is not None and not cancelled and r is reqs[1] and len(outs[id(r)]) >= cancel_at:
+                engine.remove_request(r)      # active request, possibly part of the step in flight
+                cancelled = True
+                continue
+            if r.is_turn_complete():
+                engine.remove_request(r)
+        engine.core.check_invariants()
+        assert engine.core.free_blocks == engine.options.num_blocks
+        return [outs[id(r)] for r in reqs]
+
+    ahead = og.Engine(model)
+    assert ahead.run_ahead
+    a = run(ahead, late_add=7)
+    monkeypatch.setenv("OGB_ENGINE_RUN_AHEAD", "0")
+    sync = og.Engine(model)
+    assert not sync.run_ahead
+    b = run(sync, late_add=7)
+    ops.check_kernel_status()
+    assert all(0 < len(x) <= 24 for x in a) and max(len(x) for x in a) == 24
+    assert sum(x == y for x, y in zip(a, b)) >= 3      # batch composition may differ by a step around the late admission
+    c = run(ahead, cancel_at=5, late_add=3)
+    assert len(c[1]) <= max(5, len(a[1])) and all(len(c[i]) > 0 for i in (0, 2, 3))
