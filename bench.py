@@ -14,7 +14,7 @@ Timing rules: >= 3 warm-up steps, barrier + synchronize on both sides, max over 
 working set (16 GB of weights + KV) is far larger than L2 so no flush is needed, SM clocks and
 throttle reasons are sampled with nvidia-smi during the timed region.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config llama8b|gptoss20b|llama70b]
 """
 import argparse
 import json
@@ -32,6 +32,16 @@ sys.path.insert(0, ROOT)
 METRIC = "decode_tokens_per_s"
 MODEL = "llama-3.1-8b"
 N_REQ, PROMPT_LO, PROMPT_HI, NEW_TOKENS, BLOCK = 64, 128, 2048, 256, 16
+SAMPLING = dict(do_sample=True, temperature=0.7, top_k=50, top_p=0.9)
+# Other named workloads (--config): same engine, same timing rules.
+CONFIGS = {
+    "llama8b": dict(model="llama-3.1-8b", label="Llama-3.1-8B shape", n_req=64, lo=128, hi=2048, new=256, sampling=SAMPLING,
+                    sampling_label="T=0.7 top_k=50 top_p=0.9"),
+    "gptoss20b": dict(model="gpt-oss-20b", label="gpt-oss-20B shape (bf16 experts, expert parallel over the ranks)", n_req=32, lo=1024,
+                      hi=1024, new=256, sampling={}, sampling_label="greedy"),
+    "llama70b": dict(model="llama-3.1-70b", label="Llama-3.1-70B shape", n_req=16, lo=2048, hi=2048, new=512, sampling={},
+                     sampling_label="greedy"),
+}
 
 
 def reference_arm(args):
@@ -99,6 +109,9 @@ class ClockSampler:
 
 
 def ours(args):
+    global MODEL, N_REQ, PROMPT_LO, PROMPT_HI, NEW_TOKENS, SAMPLING
+    cfg_w = CONFIGS[args.config]
+    MODEL, N_REQ, PROMPT_LO, PROMPT_HI, NEW_TOKENS, SAMPLING = cfg_w["model"], cfg_w["n_req"], cfg_w["lo"], cfg_w["hi"], cfg_w["new"], cfg_w["sampling"]
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -148,7 +161,7 @@ def ours(args):
     reqs = []
     for i, n in enumerate(lens):
         p = og.GeneratorParams(model)
-        p.set_search_options(max_length=int(n) + NEW_TOKENS + 1, do_sample=True, temperature=0.7, top_k=50, top_p=0.9, random_seed=2 + i)
+        p.set_search_options(max_length=int(n) + NEW_TOKENS + 1, random_seed=2 + i, **SAMPLING)
         r = og.Request(p)
         r.add_tokens(rng.randint(0, model.arch.vocab_size, size=int(n)).astype(np.int32))
         reqs.append(r)
@@ -241,9 +254,10 @@ def ours(args):
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (random token ids, random-init N(0,0.02) weights generated on device)",
-            "config": {"model": "Llama-3.1-8B shape", "global_batch": B, "seq_len": "prompts U[128,2048] + 256 new tokens",
-                       "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": "T=0.7 top_k=50 top_p=0.9",
-                       "engine": "paged-attention continuous batching", "l2": "inputs larger than L2 (weights 16 GB + KV), no flush",
+            "config": {"model": cfg_w["label"], "global_batch": B,
+                       "seq_len": f"prompts U[{PROMPT_LO},{PROMPT_HI}] + {NEW_TOKENS} new tokens",
+                       "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": cfg_w["sampling_label"],
+                       "engine": "paged-attention continuous batching", "l2": "inputs larger than L2 (weights + KV of tens of GB), no flush",
                        "tp_backend": getattr(tp, "backend", None)},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4)},
@@ -271,6 +285,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS), help="workload; the default is the headline configuration")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -52,8 +52,7 @@ class Request:
         self._native = None
         self._engine = None
         self._opaque = None
-        self.t_added = self.t_first = self.t_last = None
-        self.n_generated = 0
+        self.t_added = self.t_first = None
 
     # tokens ------------------------------------------------------------------------------------
     def add_tokens(self, ids):
@@ -321,6 +320,8 @@ class Engine:
         self._guidance: Dict[int, Any] = {}
         self.last_outcome = StepOutcome.NoWork
         self.step_count = 0
+        self._with_processors = set()   # ids of requests with min_length / repetition penalty / no-repeat-ngram
+        self._need_first = set()        # ids of requests that have not produced a token yet (time to first token)
         self._inflight = None
         # one step ahead of the caller: only with the built-in executor on a GPU (OGB_ENGINE_RUN_AHEAD=0 turns it off)
         self.run_ahead = (executor is None and model.device.type == "cuda" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
@@ -345,6 +346,10 @@ class Engine:
         request._native, request._engine = nat, self
         request.t_added = time.perf_counter()
         self._by_native[nat.id] = request
+        self._need_first.add(nat.id)
+        so = request.params.search
+        if so.get("min_length", 0) > 0 or so.get("repetition_penalty", 1.0) != 1.0 or so.get("no_repeat_ngram_size", 0) > 0:
+            self._with_processors.add(nat.id)
         if request.params.guidance_type:
             from ..guidance import GuidanceProcessor
             self._guidance[nat.id] = GuidanceProcessor(self.model, request.params.guidance_type, request.params.guidance_data, 1, False)
@@ -358,6 +363,8 @@ class Engine:
         self.core.remove_request(request._native)
         self._by_native.pop(request._native.id, None)
         self._guidance.pop(request._native.id, None)
+        self._with_processors.discard(request._native.id)
+        self._need_first.discard(request._native.id)
 
     def has_pending_requests(self) -> bool:
         return self.core.has_pending_requests()
@@ -446,23 +453,27 @@ class Engine:
                     self._fail(e)
                     return
             now = time.perf_counter()
-            for i, e in enumerate(plan.entries):
-                if not e.samples:
-                    continue
-                rq = self._by_native.get(e.request.id)
-                if rq is not None:
-                    if rq.t_first is None:
-                        rq.t_first = now
-                    rq.t_last = now
-                    rq.n_generated += 1
-                gp = self._guidance.get(e.request.id)
-                if gp is not None:
-                    gp.commit_tokens(np.asarray([toks[i]], dtype=np.int32))
+            if self._need_first or self._guidance:      # steady-state decode has neither: no per-entry work on the host
+                for i, e in enumerate(plan.entries):
+                    if not e.samples:
+                        continue
+                    rid = e.request.id
+                    if rid in self._need_first:
+                        self._need_first.discard(rid)
+                        rq = self._by_native.get(rid)
+                        if rq is not None:
+                            rq.t_first = now
+                    gp = self._guidance.get(rid)
+                    if gp is not None:
+                        gp.commit_tokens(np.asarray([toks[i]], dtype=np.int32))
+            self.t_last_step = now
             self.last_outcome = self.core.commit(np.ascontiguousarray(toks, dtype=np.int32))
             self.step_count += 1
 
     def _logits_processors(self, plan):
         """Sparse logits edits (min_length, repetition penalty, no-repeat-ngram) and grammar masks."""
+        if not self._with_processors and not self._guidance:
+            return [], None        # no admitted request edits its logits: nothing to look at per entry
         rows, toks, opsl, vals = [], [], [], []
         mask_rows, mask_list = [], []
         V = self.model.config.vocab_size
