@@ -302,6 +302,8 @@ class SequenceState:
         while bound < max(self.kv_len) + 1:
             bound *= 2
         bound = min(bound, cap)
+        if self.decoder.cos_small is not None and max(self.kv_len) + 1 <= self.decoder.rope_original_context:
+            bound = min(bound, self.decoder.rope_original_context)   # the bound also selects the RoPE cache pair
         key = (bound, self.decoder.active_adapter)
         d = self._g_dev
         if key not in self._graphs:
@@ -474,6 +476,16 @@ class Generator:
     _unfed_last = False  # True while the newest token has not been run through the model
 
     def _compute_logits(self, row_tokens: List[List[int]]):
+        dec = self.model.decoder
+        if dec.cos_small is not None:
+            # Long-context RoPE: the cache of a sequence that grows past the original context length was filled with the
+            # short-factor rotation; rebuild it from the whole sequence with the long-factor caches
+            # (reference: src/standard_decoding_strategy.cpp:64-76).
+            cur = max(self.state.kv_len)
+            if 0 < cur <= dec.rope_original_context < cur + max(len(t) for t in row_tokens):
+                for r in range(self.rows):
+                    self.state.rewind(r, 0)
+                row_tokens = [self.search.sequence(r).tolist() for r in range(self.rows)]
         chunk = int(self.search_opts.get("chunk_size") or 0)
         with _Trace("model", "run"), torch.no_grad():
             if chunk > 0:

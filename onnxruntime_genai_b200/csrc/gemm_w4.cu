@@ -254,27 +254,32 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
   const uint8_t* rec0 = wpacked + (size_t(kb0) * n_tiles_total + n_tile) * W4_RECORD_BYTES;
   const size_t rec_stride = size_t(n_tiles_total) * W4_RECORD_BYTES;
 
-  // first weights before the wait on the previous kernel: nothing earlier in the stream writes them
-  uint4 nib0 = make_uint4(0, 0, 0, 0), nib1 = nib0;
-  uint2 sz = make_uint2(0, 0);
-  if (num_kb > 0) {
-    nib0 = *reinterpret_cast<const uint4*>(rec0 + tid * 32);
-    nib1 = *reinterpret_cast<const uint4*>(rec0 + tid * 32 + 16);
-    sz = *reinterpret_cast<const uint2*>(rec0 + GEMM_BLOCK_N * 32 + tid * 8);
-  }
+  // Weights first, before the wait on the previous kernel (nothing earlier in the stream writes them): up to GEMV_AHEAD
+  // records per thread are in flight at any time, which is what covers the HBM latency of this short kernel.
+  constexpr int GEMV_AHEAD = 4;
+  uint4 nb0[GEMV_AHEAD], nb1[GEMV_AHEAD];
+  uint2 szq[GEMV_AHEAD];
+  auto fetch = [&](int kb, int slot) {
+    const uint8_t* r = rec0 + size_t(kb) * rec_stride;
+    nb0[slot] = *reinterpret_cast<const uint4*>(r + tid * 32);
+    nb1[slot] = *reinterpret_cast<const uint4*>(r + tid * 32 + 16);
+    szq[slot] = *reinterpret_cast<const uint2*>(r + GEMM_BLOCK_N * 32 + tid * 8);
+  };
+#pragma unroll
+  for (int a = 0; a < GEMV_AHEAD; ++a)
+    if (a < num_kb) fetch(a, a);
   if (p.pdl) { pdl_launch_dependents(); pdl_wait(); }
 
-  // stage the activations of this k range as fp32 and their sums per block of 32
+  // stage the activations of this k range as fp32 and their sums per block of 32 (one warp per block, shuffle reduction)
   for (int i = tid; i < num_kb * 64; i += GEMV_THREADS) {
 #pragma unroll
     for (int m = 0; m < MT; ++m) xs[m][i] = m < p.M ? bf2f(A[size_t(m) * lda + size_t(kb0) * 64 + i]) : 0.f;
   }
   __syncthreads();
-  for (int i = tid; i < num_kb * 2 * MT; i += GEMV_THREADS) {
-    const int m = i / (num_kb * 2), b = i % (num_kb * 2);
-    float t = 0.f;
-    for (int j = 0; j < 32; ++j) t += xs[m][b * 32 + j];
-    xsum[m][b] = t;
+  for (int b = tid >> 5; b < num_kb * 2 * MT; b += GEMV_THREADS / 32) {
+    const int m = b / (num_kb * 2), blk = b % (num_kb * 2);
+    const float t = warp_sum(xs[m][blk * 32 + (tid & 31)]);
+    if ((tid & 31) == 0) xsum[m][blk] = t;
   }
   __syncthreads();
 
@@ -282,45 +287,43 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
 #pragma unroll
   for (int m = 0; m < MT; ++m) acc[m] = 0.f;
 
-  for (int kb = 0; kb < num_kb; ++kb) {
-    // software pipeline: issue the next record's loads before working on this one
-    uint4 nx0 = nib0, nx1 = nib1;
-    uint2 nsz = sz;
-    if (kb + 1 < num_kb) {
-      const uint8_t* r = rec0 + size_t(kb + 1) * rec_stride;
-      nx0 = *reinterpret_cast<const uint4*>(r + tid * 32);
-      nx1 = *reinterpret_cast<const uint4*>(r + tid * 32 + 16);
-      nsz = *reinterpret_cast<const uint2*>(r + GEMM_BLOCK_N * 32 + tid * 8);
-    }
-    const uint32_t words[8] = {nib0.x, nib0.y, nib0.z, nib0.w, nib1.x, nib1.y, nib1.z, nib1.w};
-    const float2 sz0 = unpack_bf16x2(sz.x), sz1 = unpack_bf16x2(sz.y);   // (scale, 128 + zero point) of the two blocks of 32
+  for (int kb0i = 0; kb0i < num_kb; kb0i += GEMV_AHEAD) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      float dot[MT];
+    for (int a = 0; a < GEMV_AHEAD; ++a) {
+      const int kb = kb0i + a;
+      if (kb >= num_kb) break;
+      const uint4 nib0 = nb0[a], nib1 = nb1[a];
+      const uint2 sz = szq[a];
+      if (kb + GEMV_AHEAD < num_kb) fetch(kb + GEMV_AHEAD, a);     // refill the slot just consumed
+      const uint32_t words[8] = {nib0.x, nib0.y, nib0.z, nib0.w, nib1.x, nib1.y, nib1.z, nib1.w};
+      const float2 sz0 = unpack_bf16x2(sz.x), sz1 = unpack_bf16x2(sz.y);   // (scale, 128 + zero point) of the two blocks of 32
 #pragma unroll
-      for (int m = 0; m < MT; ++m) dot[m] = 0.f;
+      for (int half = 0; half < 2; ++half) {
+        float dot[MT];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t w = words[half * 4 + j];
-        float q[8];
+        for (int m = 0; m < MT; ++m) dot[m] = 0.f;
 #pragma unroll
-        for (int pr = 0; pr < 4; ++pr) {
-          const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
-          q[2 * pr] = __uint_as_float(t << 16);
-          q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t w = words[half * 4 + j];
+          float q[8];
+#pragma unroll
+          for (int pr = 0; pr < 4; ++pr) {
+            const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
+            q[2 * pr] = __uint_as_float(t << 16);
+            q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
+          }
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
+            dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
+          }
         }
+        const float2 s = half ? sz1 : sz0;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
-          const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
-          dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
-        }
+        for (int m = 0; m < MT; ++m) acc[m] += s.x * (dot[m] - s.y * xsum[m][kb * 2 + half]);
       }
-      const float2 s = half ? sz1 : sz0;
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[m] += s.x * (dot[m] - s.y * xsum[m][kb * 2 + half]);
     }
-    nib0 = nx0; nib1 = nx1; sz = nsz;
   }
 
 #pragma unroll

@@ -261,17 +261,20 @@ __device__ void small_list(const RowCtx& c, SelectShared& sh, unsigned long long
   }
   sv[tid] = tmax;   // blockDim.x == SMALL_K
   if (tid == 0) { *cand_n = 0; sh.result = 0; }
-  __syncthreads();
-  {
-    int rank = 0;
-    for (int j = 0; j < SAMP_THREADS; ++j) {
-      const float vj = sv[j];
-      rank += (vj > tmax || (vj == tmax && j < tid)) ? 1 : 0;
+  // bitonic sort of the 1024 maxima, descending: 55 compare-exchange steps, one element per thread
+  for (int size = 2; size <= SAMP_THREADS; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      __syncthreads();
+      const int partner = tid ^ stride;
+      if (partner > tid) {
+        const bool desc = (tid & size) == 0;
+        const float a = sv[tid], b = sv[partner];
+        if ((a < b) == desc && a != b) { sv[tid] = b; sv[partner] = a; }
+      }
     }
-    if (rank == k - 1) sh.carry = (unsigned long long)__float_as_uint(tmax);
   }
   __syncthreads();
-  const float t0 = __uint_as_float((uint32_t)sh.carry);
+  const float t0 = sv[k - 1];
   __syncthreads();
   for (int base = 0; base < n; base += 8 * blockDim.x) {
     float vals[8];

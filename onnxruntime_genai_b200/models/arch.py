@@ -121,7 +121,9 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         context_length=cfg.get("max_position_embeddings", 4096),
         norm_eps=cfg.get("rms_norm_eps", cfg.get("layer_norm_eps", cfg.get("layer_norm_epsilon", 1e-5))),
         rope_theta=cfg.get("rope_theta", 10000.0),
-        rope_scaling=cfg.get("rope_scaling"),
+        rope_scaling=({**cfg["rope_scaling"], "original_max_position_embeddings": cfg["original_max_position_embeddings"]}
+                      if cfg.get("rope_scaling") and "original_max_position_embeddings" in cfg and
+                      "original_max_position_embeddings" not in cfg["rope_scaling"] else cfg.get("rope_scaling")),
         partial_rotary_factor=cfg.get("partial_rotary_factor", 1.0),
         attn_bias=bool(cfg.get("attention_bias", False)),
         mlp_bias=bool(cfg.get("mlp_bias", False)),
@@ -187,6 +189,9 @@ def rope_caches(arch: ArchConfig, max_positions: Optional[int] = None):
     attn_factor = 1.0
     sc = arch.rope_scaling or {}
     kind = sc.get("rope_type", sc.get("type", "default"))
+    if kind in ("longrope", "su"):
+        multi = longrope_caches(arch)
+        return multi[2][:n], multi[3][:n]
     if kind == "linear":
         inv_freq = inv_freq / float(sc["factor"])
     elif kind == "llama3":
@@ -214,6 +219,33 @@ def rope_caches(arch: ArchConfig, max_positions: Optional[int] = None):
     t = np.arange(n, dtype=np.float64)
     freqs = np.outer(t, inv_freq)
     return (np.cos(freqs) * attn_factor).astype(np.float32), (np.sin(freqs) * attn_factor).astype(np.float32)
+
+
+def longrope_caches(arch: ArchConfig):
+    """Phi-3 long-context RoPE ("longrope" / "su", src/python/py/models/builders/phi.py:75-95, base.py:2637-2660): two
+    cache pairs — per-frequency `short_factor` for sequences up to the original context length, `long_factor` beyond —
+    both scaled by sqrt(1 + ln(context / original) / ln(original)) unless the config gives short_mscale / long_mscale.
+    Returns None for other scaling types, else (cos_small, sin_small, cos_large, sin_large, original_context)."""
+    sc = arch.rope_scaling or {}
+    kind = sc.get("rope_type", sc.get("type", "default"))
+    if kind not in ("longrope", "su"):
+        return None
+    rot = arch.rotary_dim
+    orig = int(sc.get("original_max_position_embeddings", arch.context_length))
+    ratio = arch.context_length / orig
+    default_m = 1.0 if ratio <= 1.0 else math.sqrt(1.0 + math.log(ratio) / math.log(orig))
+    base = arch.rope_theta ** (np.arange(0, rot, 2, dtype=np.float64) / rot)
+
+    def cache(factors, n, mscale):
+        inv_freq = 1.0 / (np.asarray(factors, dtype=np.float64) * base)
+        freqs = np.outer(np.arange(n, dtype=np.float64), inv_freq)
+        return (np.cos(freqs) * mscale).astype(np.float32), (np.sin(freqs) * mscale).astype(np.float32)
+
+    sm = float(sc.get("short_mscale") or 0) or default_m
+    lm = float(sc.get("long_mscale") or 0) or default_m
+    cs, ss = cache(sc["short_factor"], orig, sm)
+    cl, sl = cache(sc["long_factor"], arch.context_length, lm)
+    return cs, ss, cl, sl, orig
 
 
 # --------------------------------------------------------------------------------------------- presets

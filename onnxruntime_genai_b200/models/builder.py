@@ -32,7 +32,7 @@ import numpy as np
 import torch
 
 from ..utils import onnx_proto as op
-from .arch import PRESETS, ArchConfig, from_hf_config, rope_caches
+from .arch import PRESETS, ArchConfig, from_hf_config, longrope_caches, rope_caches
 
 _ONNX_DT = {"fp32": op.FLOAT, "fp16": op.FLOAT16, "bf16": op.BFLOAT16}
 _TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
@@ -323,6 +323,13 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
         hidden = "/model/embed_tokens/Mul/output_0"
 
     # ---- rotary caches
+    multi = longrope_caches(arch)
+    if multi is not None:
+        # two cache pairs and the length at which the model switches from the short to the long one
+        for nm, arr in zip(("cos_cache_small", "sin_cache_small", "cos_cache_large", "sin_cache_large"), multi[:4]):
+            W.add_float(nm, torch.from_numpy(arr), force_fp32=(precision == "fp32"))
+        W.model.initializers["/model/rope_caches_subgraph/original_context_length"] = op.Tensor(
+            "/model/rope_caches_subgraph/original_context_length", op.INT64, (), raw=np.int64(multi[4]).tobytes())
     cos, sin = rope_caches(arch)
     W.add_float("cos_cache", torch.from_numpy(cos), force_fp32=(precision == "fp32"))
     W.add_float("sin_cache", torch.from_numpy(sin), force_fp32=(precision == "fp32"))

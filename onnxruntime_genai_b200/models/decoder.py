@@ -137,6 +137,11 @@ class DecoderModel:
         self.lm_head_b: Optional[torch.Tensor] = None
         self.cos: Optional[torch.Tensor] = None
         self.sin: Optional[torch.Tensor] = None
+        # long-context RoPE (Phi-3 longrope): `cos` / `sin` are the long-factor caches; these serve steps whose KV bound
+        # stays within the original context length
+        self.cos_small: Optional[torch.Tensor] = None
+        self.sin_small: Optional[torch.Tensor] = None
+        self.rope_original_context = 0
         self.heads_local = arch.num_heads // self.tp.size
         self.kv_heads_local = max(1, arch.num_kv_heads // self.tp.size)
         self.inter_local = arch.intermediate_size // self.tp.size
@@ -185,6 +190,9 @@ class DecoderModel:
         a = self.arch
         h = s.inputs_embeds if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
         residual = None
+        cos, sin = self.cos, self.sin
+        if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
+            cos, sin = self.cos_small, self.sin_small      # the whole step lies within the original context length
         for li, lw in enumerate(self.layers):
             if residual is None:
                 x, _ = ops.norm(h, lw.ln1_w, a.norm_eps, None, lw.ln1_b, a.layernorm)
@@ -196,7 +204,7 @@ class DecoderModel:
             kc, vc, windowed = kv.layer(li)
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
-            ops.rope_kv_append(qkv, s.positions, slots, self.cos, self.sin, kc, vc, self.heads_local, self.kv_heads_local,
+            ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
                                a.head_dim, a.rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,

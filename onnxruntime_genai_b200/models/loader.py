@@ -256,6 +256,12 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
     model.embed = emb.to(device=device, dtype=dtype).contiguous()
     cos, sin = g.tensor("cos_cache").float(), g.tensor("sin_cache").float()
     model.cos, model.sin = cos.to(device).contiguous(), sin.to(device).contiguous()
+    if g.has_init("cos_cache_small") and g.has_init("cos_cache_large"):
+        # long-context RoPE: short-factor caches up to the original context length, long-factor caches beyond
+        model.rope_original_context = int(g.tensor("/model/rope_caches_subgraph/original_context_length").item())
+        model.cos_small = g.tensor("cos_cache_small").float().to(device).contiguous()
+        model.sin_small = g.tensor("sin_cache_small").float().to(device).contiguous()
+        model.cos, model.sin = g.tensor("cos_cache_large").float().to(device).contiguous(), g.tensor("sin_cache_large").float().to(device).contiguous()
 
     for i in range(arch.num_layers):
         p, n = f"model.layers.{i}.", f"/model/layers.{i}"

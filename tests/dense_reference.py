@@ -4,7 +4,7 @@ import math
 
 import torch
 
-from onnxruntime_genai_b200.models.arch import rope_caches
+from onnxruntime_genai_b200.models.arch import longrope_caches, rope_caches
 
 
 def _norm(x, w, b, arch):
@@ -35,6 +35,9 @@ def logits(arch, sd, ids):
     S = len(ids)
     pos = torch.arange(S)
     cos, sin = rope_caches(arch, max(S, 8))
+    multi = longrope_caches(arch)
+    if multi is not None and S <= multi[4]:
+        cos, sin = multi[0], multi[1]      # sequences within the original context use the short-factor caches
     cos, sin = torch.from_numpy(cos)[pos], torch.from_numpy(sin)[pos]
     h = sd["model.embed_tokens.weight"][torch.tensor(ids)] * arch.embed_scale
     G = arch.num_heads // arch.num_kv_heads

@@ -166,3 +166,33 @@ def test_mxfp4_expert_round_trip_and_model(tmp_path):
             sd_q[k] = torch.stack([dequantize_mxfp4(*quantize_mxfp4(v[e].float()), v.shape[1], v.shape[2]) for e in range(v.shape[0])])
     lw = model.decoder.layers[0]
     np.testing.assert_allclose(lw.exp_down_w.float().numpy(), sd_q["model.layers.0.mlp.experts.down_proj"].numpy(), rtol=0, atol=1e-6)
+
+
+def test_longrope_switches_caches_and_rebuilds_the_kv_cache(tmp_path):
+    """Phi-3 long-context RoPE: short-factor caches within the original context length, long-factor caches (and a
+    rebuilt KV cache) once the sequence grows past it."""
+    half = 8
+    arch = ArchConfig(**{**BASE, "model_type": "phi3", "num_kv_heads": 4, "context_length": 128,
+                         "rope_scaling": {"rope_type": "longrope", "original_max_position_embeddings": 32,
+                                          "short_factor": [1.0 + 0.02 * i for i in range(half)],
+                                          "long_factor": [1.5 + 0.3 * i for i in range(half)]}})
+    sd = random_state_dict(arch, seed=13, std=0.15)
+    d = str(tmp_path)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    model = og.Model(d)
+    assert model.decoder.cos_small is not None and model.decoder.rope_original_context == 32
+    prompt = np.random.RandomState(6).randint(0, arch.vocab_size - 1, size=(1, 27)).astype(np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=60)
+    g = og.Generator(model, p)
+    g.append_tokens(prompt)
+    ids = prompt[0].tolist()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), dense_logits(arch, sd, ids)[-1].numpy(), rtol=2e-3, atol=3e-4)
+    for _ in range(12):          # crosses 32 tokens on the way
+        g.generate_next_token()
+        ids.append(int(g.get_next_tokens()[0]))
+        if g.is_done():
+            break
+        want = dense_logits(arch, sd, ids)[-1].numpy()
+        np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4, err_msg=f"length {len(ids)}")
+    assert len(ids) > 33, "the sequence must cross the original context length"
