@@ -229,25 +229,28 @@ static int LaunchW4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles_total,
   return cudaLaunchKernelEx(&cfg, kern, ta, wp, n_tiles_total, p) == cudaSuccess ? 0 : -4;
 }
 
-// ---------------------------------------------------------------------------------------------- GEMV (1..4 tokens)
-// Decode of a single sequence (or a few): with at most four activation rows the tensor cores have nothing to do and
-// the job is to stream the packed weights at HBM speed.  One thread per weight row reads its 32 bytes of nibbles and
-// its scale / zero-point pair of every 64-wide k-block straight from global memory (a warp covers 1 KiB contiguous),
-// several k-blocks in flight; the activations (and their sums per block of 32, so that the zero point costs one
-// multiply per block instead of a subtract per weight) sit in shared memory and are read as broadcasts:
+// ---------------------------------------------------------------------------------------------- GEMV (1 or 2 tokens)
+// Decode of a single sequence (or two): with one or two activation rows the tensor cores have nothing to do and
+// the job is to stream the packed weights at HBM speed.  Two threads per weight row each read the 16 bytes of nibbles
+// and the scale / zero-point pair of one block of 32 of every 64-wide k-block straight from global memory (a warp covers
+// 512 contiguous bytes), eight k-blocks in flight per thread; the activations (and their sums per block of 32, so that
+// the zero point costs one multiply per block instead of a subtract per weight) sit in shared memory and are read as
+// broadcasts:
 //     sum_k (q - z) s x  =  s * (sum_k (128 + q) x  -  (128 + z) * sum_k x)
 // The k range is split over a thread-block cluster (up to 8 CTAs) whose partial sums meet in the first CTA's
 // shared memory; that CTA adds bias / residual, applies the paired SiLU*mul and stores.
-constexpr int GEMV_THREADS = 128;
-constexpr int GEMV_MAX_KB = 32;   // k-blocks per CTA held as activations in shared memory (x: MT * 64 * 4 bytes each)
+constexpr int GEMV_ROWS = 128;     // weight rows per CTA (one packed record per k-block)
+constexpr int GEMV_THREADS = 256;  // two threads per row: each takes one block of 32 of every 64-wide k-block
+constexpr int GEMV_MAX_KB = 32;    // k-blocks per CTA held as activations in shared memory (x: MT * 64 * 4 bytes each)
 
 template <int MT>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_total, const GemmParams p) {
   __shared__ __align__(16) float xs[MT][GEMV_MAX_KB * 64];
   __shared__ float xsum[MT][GEMV_MAX_KB * 2];
-  __shared__ float part[MT][GEMV_THREADS];      // this CTA's partial sums, read by the first CTA of the cluster
+  __shared__ float part[MT][GEMV_ROWS];         // this CTA's partial sums, read by the first CTA of the cluster
   const int tid = threadIdx.x;
+  const int row = tid >> 1, half = tid & 1;     // weight row of the tile, which block of 32 of each k-block
   const int n_tile = blockIdx.x, split = blockIdx.z;
   const int kb0 = split * p.kb_per_split;
   const int num_kb = max(0, min(p.kb_per_split, p.total_kb - kb0));
@@ -255,15 +258,14 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
   const size_t rec_stride = size_t(n_tiles_total) * W4_RECORD_BYTES;
 
   // Weights first, before the wait on the previous kernel (nothing earlier in the stream writes them): up to GEMV_AHEAD
-  // records per thread are in flight at any time, which is what covers the HBM latency of this short kernel.
-  constexpr int GEMV_AHEAD = 4;
-  uint4 nb0[GEMV_AHEAD], nb1[GEMV_AHEAD];
-  uint2 szq[GEMV_AHEAD];
+  // half records per thread are in flight at any time, which is what covers the HBM latency of this short kernel.
+  constexpr int GEMV_AHEAD = 8;
+  uint4 nb[GEMV_AHEAD];
+  uint32_t szq[GEMV_AHEAD];
   auto fetch = [&](int kb, int slot) {
     const uint8_t* r = rec0 + size_t(kb) * rec_stride;
-    nb0[slot] = *reinterpret_cast<const uint4*>(r + tid * 32);
-    nb1[slot] = *reinterpret_cast<const uint4*>(r + tid * 32 + 16);
-    szq[slot] = *reinterpret_cast<const uint2*>(r + GEMM_BLOCK_N * 32 + tid * 8);
+    nb[slot] = *reinterpret_cast<const uint4*>(r + row * 32 + half * 16);
+    szq[slot] = *reinterpret_cast<const uint32_t*>(r + GEMM_BLOCK_N * 32 + row * 8 + half * 4);
   };
 #pragma unroll
   for (int a = 0; a < GEMV_AHEAD; ++a)
@@ -292,42 +294,42 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
     for (int a = 0; a < GEMV_AHEAD; ++a) {
       const int kb = kb0i + a;
       if (kb >= num_kb) break;
-      const uint4 nib0 = nb0[a], nib1 = nb1[a];
-      const uint2 sz = szq[a];
+      const uint4 nib = nb[a];
+      const float2 s = unpack_bf16x2(szq[a]);                       // (scale, 128 + zero point) of this block of 32
       if (kb + GEMV_AHEAD < num_kb) fetch(kb + GEMV_AHEAD, a);     // refill the slot just consumed
-      const uint32_t words[8] = {nib0.x, nib0.y, nib0.z, nib0.w, nib1.x, nib1.y, nib1.z, nib1.w};
-      const float2 sz0 = unpack_bf16x2(sz.x), sz1 = unpack_bf16x2(sz.y);   // (scale, 128 + zero point) of the two blocks of 32
+      const uint32_t words[4] = {nib.x, nib.y, nib.z, nib.w};
+      float dot[MT];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float dot[MT];
+      for (int m = 0; m < MT; ++m) dot[m] = 0.f;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) dot[m] = 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = words[j];
+        float q[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t w = words[half * 4 + j];
-          float q[8];
-#pragma unroll
-          for (int pr = 0; pr < 4; ++pr) {
-            const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
-            q[2 * pr] = __uint_as_float(t << 16);
-            q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
-          }
-#pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
-            const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
-            dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
-          }
+        for (int pr = 0; pr < 4; ++pr) {
+          const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
+          q[2 * pr] = __uint_as_float(t << 16);
+          q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
         }
-        const float2 s = half ? sz1 : sz0;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] += s.x * (dot[m] - s.y * xsum[m][kb * 2 + half]);
+        for (int m = 0; m < MT; ++m) {
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
+          dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
+        }
       }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] += s.x * (dot[m] - s.y * xsum[m][kb * 2 + half]);
     }
   }
-
+  // the two threads of a row
 #pragma unroll
-  for (int m = 0; m < MT; ++m) part[m][tid] = acc[m];
+  for (int m = 0; m < MT; ++m) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
+
+  if (half == 0) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) part[m][row] = acc[m];
+  }
   if (p.splits > 1) cluster_sync_all(); else __syncthreads();
 
   if (split == 0) {
@@ -339,7 +341,7 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
       for (int s = 0; s < p.splits; ++s) {
         if (p.splits > 1) {
           float v;
-          const uint32_t ra = dsmem_addr(part_addr + uint32_t(m * GEMV_THREADS + row) * 4, uint32_t(s));
+          const uint32_t ra = dsmem_addr(part_addr + uint32_t(m * GEMV_ROWS + row) * 4, uint32_t(s));
           asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
           t += v;
         } else {
@@ -350,7 +352,7 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
       if (p.bias && n < p.N) t += bf2f(p.bias[n]);
       return t;
     };
-    const int rows_out = pair ? 64 : GEMV_THREADS;
+    const int rows_out = pair ? 64 : GEMV_ROWS;
     if (tid < rows_out) {
       const int col = pair ? n_tile * 64 + tid : n_tile * GEMM_BLOCK_N + tid;
       if (col < n_out) {
@@ -415,7 +417,7 @@ OGB_API int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, in
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, m_tiles = (M + bt - 1) / bt;
   const int total_kb = K / GEMM_BLOCK_K;
   static const int gemv_enabled = [] { const char* e = getenv("OGB_W4_GEMV"); return (e && e[0] == '0') ? 0 : 1; }();
-  if (M <= 4 && gemv_enabled && total_kb <= 8 * GEMV_MAX_KB) {
+  if (M <= 2 && gemv_enabled && total_kb <= 8 * GEMV_MAX_KB) {
     // a few tokens: stream the weights with one thread per row, k split over a cluster sized to fill the GPU
     int gs = splits > 0 ? splits : 1;
     if (splits <= 0) while (gs < 8 && n_tiles * gs < 4 * sm_count && total_kb / (gs * 2) >= 2) gs *= 2;
@@ -434,8 +436,7 @@ OGB_API int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, in
       const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(A);
       const uint8_t* w = static_cast<const uint8_t*>(Wpacked);
       if (M == 1) return LaunchGemvW4<1>(a, lda, w, n_tiles, g, stream);
-      if (M == 2) return LaunchGemvW4<2>(a, lda, w, n_tiles, g, stream);
-      return LaunchGemvW4<4>(a, lda, w, n_tiles, g, stream);
+      return LaunchGemvW4<2>(a, lda, w, n_tiles, g, stream);
     }
   }
   if (splits <= 0) {

@@ -179,7 +179,7 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
     def run(engine, cancel_at=None, late_add=None):
         reqs = [make(p, i) for i, p in enumerate(prompts)]
         outs = {id(r): [] for r in reqs}
-        for r in reqs[:3]:
+        for r in (reqs[:3] if late_add is not None else reqs):
             engine.add_request(r)
         n_calls = 0
         cancelled = False
@@ -204,11 +204,11 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
 
     ahead = og.Engine(model)
     assert ahead.run_ahead
-    a = run(ahead, late_add=1)          # every request admitted before the first model step: identical batches in both engines
+    a = run(ahead)                      # every request admitted before the first model step: identical batches in both engines
     monkeypatch.setenv("OGB_ENGINE_RUN_AHEAD", "0")
     sync = og.Engine(model)
     assert not sync.run_ahead
-    b = run(sync, late_add=1)
+    b = run(sync)
     ops.check_kernel_status()
     assert all(0 < len(x) <= 24 for x in a) and max(len(x) for x in a) == 24
     assert a == b, "running one step ahead must not change any token"
