@@ -231,41 +231,48 @@ static int LaunchW4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles_total,
 
 // ---------------------------------------------------------------------------------------------- GEMV (1 or 2 tokens)
 // Decode of a single sequence (or two): with one or two activation rows the tensor cores have nothing to do and
-// the job is to stream the packed weights at HBM speed.  Two threads per weight row each read the 16 bytes of nibbles
-// and the scale / zero-point pair of one block of 32 of every 64-wide k-block straight from global memory (a warp covers
-// 512 contiguous bytes), eight k-blocks in flight per thread; the activations (and their sums per block of 32, so that
+// the job is to stream the packed weights at HBM speed.  One or two threads per weight row read the nibbles and the
+// scale / zero-point pairs of every 64-wide k-block straight from global memory (a warp covers 512 or 1024 contiguous
+// bytes), four or eight k-blocks in flight per thread; the activations (and their sums per block of 32, so that
 // the zero point costs one multiply per block instead of a subtract per weight) sit in shared memory and are read as
 // broadcasts:
 //     sum_k (q - z) s x  =  s * (sum_k (128 + q) x  -  (128 + z) * sum_k x)
 // The k range is split over a thread-block cluster (up to 8 CTAs) whose partial sums meet in the first CTA's
 // shared memory; that CTA adds bias / residual, applies the paired SiLU*mul and stores.
 constexpr int GEMV_ROWS = 128;     // weight rows per CTA (one packed record per k-block)
-constexpr int GEMV_THREADS = 256;  // two threads per row: each takes one block of 32 of every 64-wide k-block
 constexpr int GEMV_MAX_KB = 32;    // k-blocks per CTA held as activations in shared memory (x: MT * 64 * 4 bytes each)
 
-template <int MT>
-__global__ void __launch_bounds__(GEMV_THREADS)
+// TPR = threads per weight row: 1 (each thread takes both blocks of 32 of a k-block; launches with many CTAs) or 2 (one
+// block of 32 each: twice the threads and loads in flight, for launches whose CTAs alone cannot fill the GPU).
+template <int MT, int TPR>
+__global__ void __launch_bounds__(GEMV_ROWS * TPR)
 gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_total, const GemmParams p) {
+  constexpr int THREADS = GEMV_ROWS * TPR;
+  constexpr int HB = 2 / TPR;                   // blocks of 32 per thread and k-block
+  constexpr int GEMV_AHEAD = 4 * TPR;           // k-blocks in flight per thread (32 or 16 bytes each)
   __shared__ __align__(16) float xs[MT][GEMV_MAX_KB * 64];
   __shared__ float xsum[MT][GEMV_MAX_KB * 2];
   __shared__ float part[MT][GEMV_ROWS];         // this CTA's partial sums, read by the first CTA of the cluster
   const int tid = threadIdx.x;
-  const int row = tid >> 1, half = tid & 1;     // weight row of the tile, which block of 32 of each k-block
+  const int row = tid / TPR, half = tid % TPR;  // weight row of the tile; first block of 32 of each k-block for this thread
   const int n_tile = blockIdx.x, split = blockIdx.z;
   const int kb0 = split * p.kb_per_split;
   const int num_kb = max(0, min(p.kb_per_split, p.total_kb - kb0));
   const uint8_t* rec0 = wpacked + (size_t(kb0) * n_tiles_total + n_tile) * W4_RECORD_BYTES;
   const size_t rec_stride = size_t(n_tiles_total) * W4_RECORD_BYTES;
 
-  // Weights first, before the wait on the previous kernel (nothing earlier in the stream writes them): up to GEMV_AHEAD
-  // half records per thread are in flight at any time, which is what covers the HBM latency of this short kernel.
-  constexpr int GEMV_AHEAD = 8;
-  uint4 nb[GEMV_AHEAD];
-  uint32_t szq[GEMV_AHEAD];
+  // Weights first, before the wait on the previous kernel (nothing earlier in the stream writes them): several k-blocks
+  // per thread are in flight at any time, which is what covers the HBM latency of this short kernel.
+  uint4 nb[GEMV_AHEAD][HB];
+  uint32_t szq[GEMV_AHEAD][HB];
   auto fetch = [&](int kb, int slot) {
     const uint8_t* r = rec0 + size_t(kb) * rec_stride;
-    nb[slot] = *reinterpret_cast<const uint4*>(r + row * 32 + half * 16);
-    szq[slot] = *reinterpret_cast<const uint32_t*>(r + GEMM_BLOCK_N * 32 + row * 8 + half * 4);
+#pragma unroll
+    for (int h = 0; h < HB; ++h) {
+      const int hh = half * HB + h;
+      nb[slot][h] = *reinterpret_cast<const uint4*>(r + row * 32 + hh * 16);
+      szq[slot][h] = *reinterpret_cast<const uint32_t*>(r + GEMM_BLOCK_N * 32 + row * 8 + hh * 4);
+    }
   };
 #pragma unroll
   for (int a = 0; a < GEMV_AHEAD; ++a)
@@ -273,12 +280,12 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
   if (p.pdl) { pdl_launch_dependents(); pdl_wait(); }
 
   // stage the activations of this k range as fp32 and their sums per block of 32 (one warp per block, shuffle reduction)
-  for (int i = tid; i < num_kb * 64; i += GEMV_THREADS) {
+  for (int i = tid; i < num_kb * 64; i += THREADS) {
 #pragma unroll
     for (int m = 0; m < MT; ++m) xs[m][i] = m < p.M ? bf2f(A[size_t(m) * lda + size_t(kb0) * 64 + i]) : 0.f;
   }
   __syncthreads();
-  for (int b = tid >> 5; b < num_kb * 2 * MT; b += GEMV_THREADS / 32) {
+  for (int b = tid >> 5; b < num_kb * 2 * MT; b += THREADS / 32) {
     const int m = b / (num_kb * 2), blk = b % (num_kb * 2);
     const float t = warp_sum(xs[m][blk * 32 + (tid & 31)]);
     if ((tid & 31) == 0) xsum[m][blk] = t;
@@ -294,37 +301,44 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
     for (int a = 0; a < GEMV_AHEAD; ++a) {
       const int kb = kb0i + a;
       if (kb >= num_kb) break;
-      const uint4 nib = nb[a];
-      const float2 s = unpack_bf16x2(szq[a]);                       // (scale, 128 + zero point) of this block of 32
+      uint4 nib[HB];
+      float2 sc[HB];
+#pragma unroll
+      for (int h = 0; h < HB; ++h) { nib[h] = nb[a][h]; sc[h] = unpack_bf16x2(szq[a][h]); }   // (scale, 128 + zero point)
       if (kb + GEMV_AHEAD < num_kb) fetch(kb + GEMV_AHEAD, a);     // refill the slot just consumed
-      const uint32_t words[4] = {nib.x, nib.y, nib.z, nib.w};
-      float dot[MT];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) dot[m] = 0.f;
+      for (int h = 0; h < HB; ++h) {
+        const int hh = half * HB + h;
+        const uint32_t words[4] = {nib[h].x, nib[h].y, nib[h].z, nib[h].w};
+        float dot[MT];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t w = words[j];
-        float q[8];
+        for (int m = 0; m < MT; ++m) dot[m] = 0.f;
 #pragma unroll
-        for (int pr = 0; pr < 4; ++pr) {
-          const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
-          q[2 * pr] = __uint_as_float(t << 16);
-          q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t w = words[j];
+          float q[8];
+#pragma unroll
+          for (int pr = 0; pr < 4; ++pr) {
+            const uint32_t t = ((w >> (4 * pr)) & 0x000F000Fu) | 0x43004300u;   // two bf16 numbers 128 + q
+            q[2 * pr] = __uint_as_float(t << 16);
+            q[2 * pr + 1] = __uint_as_float(t & 0xFFFF0000u);
+          }
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + hh * 32 + j * 8]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + hh * 32 + j * 8 + 4]);
+            dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
+          }
         }
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
-          const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
-          dot[m] += q[0] * xa.x + q[1] * xa.y + q[2] * xa.z + q[3] * xa.w + q[4] * xb.x + q[5] * xb.y + q[6] * xb.z + q[7] * xb.w;
-        }
+        for (int m = 0; m < MT; ++m) acc[m] += sc[h].x * (dot[m] - sc[h].y * xsum[m][kb * 2 + hh]);
       }
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[m] += s.x * (dot[m] - s.y * xsum[m][kb * 2 + half]);
     }
   }
-  // the two threads of a row
+  if (TPR == 2) {   // the two threads of a row
 #pragma unroll
-  for (int m = 0; m < MT; ++m) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
+    for (int m = 0; m < MT; ++m) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
+  }
 
   if (half == 0) {
 #pragma unroll
@@ -371,11 +385,11 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
   if (p.splits > 1) cluster_sync_all();   // peers keep their shared memory alive until the first CTA has read it
 }
 
-template <int MT>
+template <int MT, int TPR>
 static int LaunchGemvW4(const __nv_bfloat16* A, int lda, const uint8_t* wp, int n_tiles_total, const GemmParams& p, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_tiles_total, 1, p.splits);
-  cfg.blockDim = dim3(GEMV_THREADS);
+  cfg.blockDim = dim3(GEMV_ROWS * TPR);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -392,7 +406,7 @@ static int LaunchGemvW4(const __nv_bfloat16* A, int lda, const uint8_t* wp, int 
   }
   cfg.attrs = attrs;
   cfg.numAttrs = unsigned(na);
-  return cudaLaunchKernelEx(&cfg, gemv_w4_kernel<MT>, A, lda, wp, n_tiles_total, p) == cudaSuccess ? 0 : -4;
+  return cudaLaunchKernelEx(&cfg, gemv_w4_kernel<MT, TPR>, A, lda, wp, n_tiles_total, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace ogb
@@ -435,8 +449,9 @@ OGB_API int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, in
       g.status = status; g.pdl = pdl_enabled;
       const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(A);
       const uint8_t* w = static_cast<const uint8_t*>(Wpacked);
-      if (M == 1) return LaunchGemvW4<1>(a, lda, w, n_tiles, g, stream);
-      return LaunchGemvW4<2>(a, lda, w, n_tiles, g, stream);
+      const bool wide = n_tiles * gs < 2 * sm_count;   // few CTAs: two threads per row double the loads in flight
+      if (M == 1) return wide ? LaunchGemvW4<1, 2>(a, lda, w, n_tiles, g, stream) : LaunchGemvW4<1, 1>(a, lda, w, n_tiles, g, stream);
+      return wide ? LaunchGemvW4<2, 2>(a, lda, w, n_tiles, g, stream) : LaunchGemvW4<2, 1>(a, lda, w, n_tiles, g, stream);
     }
   }
   if (splits <= 0) {
