@@ -74,9 +74,25 @@ class _Trace:
 
 # ------------------------------------------------------------------------------------------------ Config
 class Config:
-    def __init__(self, path: str, overlay: str = ""):
-        self._c = native.Config(str(path), overlay)
+    def __init__(self, path: str, overlay: str = "", provider: Optional[str] = None):
+        """path: a model directory (genai_config.json + graph) or a model package (manifest.json + one directory per
+        build variant); for a package the variant matching `provider` ("cuda" / "cpu"; default: what this machine has) is
+        loaded."""
+        from . import model_package
+        self._package_root, self._manifest = None, None
+        path = str(path)
+        if model_package.is_package(path):
+            self._package_root = path
+            path, self._manifest = model_package.resolve_package(path, provider)
+        self._c = native.Config(path, overlay)
         self._model_data: Dict[str, bytes] = {}
+
+    @property
+    def tokenizer_path(self) -> str:
+        """Directory of the tokenizer files: the model directory, a relative `model.tokenizer_dir` under it, or a shared
+        asset of the package (`sha256:<hex>[/tail]`)."""
+        from . import model_package
+        return model_package.resolve_asset(self._c.config_path, self._c.tokenizer_dir, self._package_root, self._manifest)
 
     def __getattr__(self, name):
         return getattr(self._c, name)

@@ -24,7 +24,7 @@ _TOKENIZER_CACHE = {}
 def _ll_tokenizer(model):
     import llguidance
     cfg = model.config
-    d = os.path.join(cfg.config_path, cfg.tokenizer_dir) if cfg.tokenizer_dir else cfg.config_path
+    d = cfg.tokenizer_path if hasattr(cfg, "tokenizer_path") else (os.path.join(cfg.config_path, cfg.tokenizer_dir) if cfg.tokenizer_dir else cfg.config_path)
     path = os.path.join(d, "tokenizer.json")
     key = (path, cfg.vocab_size)
     tok = _TOKENIZER_CACHE.get(key)

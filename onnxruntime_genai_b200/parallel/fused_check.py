@@ -98,6 +98,26 @@ def main():
         res["allgather_us"] = timed(lambda: comm.all_gather(y))
         res["nccl_allgather_us"] = timed(lambda: dist.all_gather(parts, y))
 
+        # all-gather -> GEMM (column-parallel projection over gathered token rows) against ncclAllGather + GEMM; every
+        # iteration ends with a waiting call (a tiny all-reduce) as the protocol requires between two pushes
+        xs_local = X[rank * per:(rank + 1) * per].contiguous()
+        tiny = X[:8].contiguous()
+        gathered = [torch.empty_like(xs_local) for _ in range(world)]
+
+        def ag_fused():
+            comm.all_gather_push(xs_local)
+            y_ = ops.linear_gathered(a.tokens, wg)
+            comm.all_reduce(tiny)
+            return y_
+
+        def ag_nccl():
+            dist.all_gather(gathered, xs_local)
+            y_ = ops.linear(torch.cat(gathered), wg)
+            comm.all_reduce(tiny)
+            return y_
+
+        res["all_gather_gemm_fused_us"] = timed(ag_fused)
+        res["all_gather_gemm_nccl_us"] = timed(ag_nccl)
         res["fused_us"] = timed(lambda: ops.linear(x, w, residual=resid, all_reduce=True))
         res["fused_reduce_scatter_us"] = timed(lambda: ops.linear(x, w, reduce_scatter=(rank, world)))
         res["gemm_plus_nccl_us"] = timed(baseline)

@@ -20,7 +20,7 @@ class Tokenizer:
     def __init__(self, model):
         from tokenizers import Tokenizer as HFTokenizer
         cfg = model.config
-        self._dir = os.path.join(cfg.config_path, cfg.tokenizer_dir) if cfg.tokenizer_dir else cfg.config_path
+        self._dir = cfg.tokenizer_path if hasattr(cfg, "tokenizer_path") else (os.path.join(cfg.config_path, cfg.tokenizer_dir) if cfg.tokenizer_dir else cfg.config_path)
         path = os.path.join(self._dir, "tokenizer.json")
         if not os.path.exists(path):
             raise RuntimeError(f"tokenizer.json not found in {self._dir}")
