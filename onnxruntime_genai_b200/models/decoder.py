@@ -185,9 +185,77 @@ class DecoderModel:
         return lw.lora.get(self.active_adapter, {}).get(proj)
 
     # ------------------------------------------------------------------------------------ forward
+    # ------------------------------------------------------------------------------------ sequence-parallel form
+    def _sp_ok(self, s: StepInputs) -> bool:
+        """Prefill-sized steps of a plain dense model under tensor parallelism run in the sequence-parallel form: the
+        residual stream is split by token rows between the ranks, the row-parallel projections end in a fused
+        reduce-scatter and the column-parallel ones start from a fused all-gather."""
+        tp, a = self.tp, self.arch
+        comm = getattr(tp, "comm", None)
+        if tp.size <= 1 or comm is None or s.inputs_embeds is not None or self.active_adapter is not None:
+            return False
+        T = s.input_ids.shape[0]
+        lw = self.layers[0]
+        plain = (a.num_experts == 0 and not a.layernorm and a.residual_multiplier == 1.0 and a.activation == "silu" and lw.post_attn_norm_w is None and
+                 lw.gate_up_interleaved and isinstance(lw.gate_up_w, torch.Tensor) and isinstance(lw.qkv_w, torch.Tensor) and
+                 self.embed.dtype == torch.bfloat16)
+        return (plain and T >= tp.sp_min_tokens and T % tp.size == 0 and T * a.hidden_size <= comm.plane_elems and
+                T * self.lm_head_w.shape[1] <= comm.plane_elems)
+
+    sp_steps = 0   # forwards that took the sequence-parallel form (diagnostics / tests)
+
+    def _forward_sp(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
+        a, tp = self.arch, self.tp
+        self.sp_steps += 1
+        comm, rank, W = tp.comm, tp.rank, tp.size
+        T = s.input_ids.shape[0]
+        per = T // W
+        rows = slice(rank * per, (rank + 1) * per)
+        cos, sin = self.cos, self.sin
+        if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
+            cos, sin = self.cos_small, self.sin_small
+        # this rank's token rows of the residual stream
+        h = ops.embedding(s.input_ids[rows].contiguous(), self.embed, a.embed_scale)
+        residual = None
+        for li, lw in enumerate(self.layers):
+            if residual is None:
+                x, _ = ops.norm(h, lw.ln1_w, a.norm_eps)
+                residual = h
+            else:
+                x, residual = ops.norm(h, lw.ln1_w, a.norm_eps, residual)
+            comm.all_gather_push(x)                                        # all-gather -> QKV GEMM (one consumer kernel)
+            qkv = ops.linear_gathered(T, lw.qkv_w, lw.qkv_b)
+            kc, vc, windowed = kv.layer(li)
+            slots = s.slot_mapping_w if windowed else s.slot_mapping
+            table = s.block_table_w if windowed else s.block_table
+            ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
+                               a.head_dim, a.rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+            att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
+                                      self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
+                                      max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
+            # o_proj GEMM -> reduce-scatter by token rows (one kernel); the bias joins once, on rank 0's partial
+            h = ops.linear(att, lw.o_w, lw.o_b if rank == 0 else None, reduce_scatter=(rank, W))
+            x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual)
+            comm.all_gather_push(x)                                        # all-gather -> gate/up GEMM + SiLU*mul
+            act = ops.linear_gathered(T, lw.gate_up_w, lw.gate_up_b, act_pair=True)
+            h = ops.linear(act, lw.down_w, lw.down_b if rank == 0 else None, reduce_scatter=(rank, W))
+        x, residual = ops.norm(h, self.final_norm_w, a.norm_eps, residual)
+        x = comm.all_gather(x).reshape(T, -1)                              # every rank needs the rows its logits come from
+        self.last_hidden = x
+        if s.logits_rows is not None:
+            x = ops.gather_rows(x, s.logits_rows)
+        logits = tp.gather_logits(ops.linear(x, self.lm_head_w, self.lm_head_b, out_fp32=True))
+        if a.logits_scale != 1.0:
+            logits = logits * a.logits_scale
+        if a.final_logit_softcap > 0:
+            logits = torch.tanh(logits / a.final_logit_softcap) * a.final_logit_softcap
+        return logits
+
     def forward(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
         """Returns fp32 logits for `s.logits_rows` (or for every token when it is None)."""
         a = self.arch
+        if self._sp_ok(s):
+            return self._forward_sp(s, kv)
         h = s.inputs_embeds if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
         residual = None
         cos, sin = self.cos, self.sin

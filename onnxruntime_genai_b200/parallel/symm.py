@@ -18,7 +18,7 @@ import torch
 
 from ..ops import _lib
 
-DEFAULT_PLANE_ELEMS = 256 * 8192  # up to 256 tokens x 8192 output features per fused call
+DEFAULT_PLANE_ELEMS = int(__import__("os").environ.get("OGB_COMM_PLANE_ELEMS", 2048 * 4096))  # bf16 elements per source plane of the receive buffer
 
 
 def _register(device_index: int, world: int, rank: int, buf_ptrs: List[int], epoch: torch.Tensor, plane_elems: int) -> None:

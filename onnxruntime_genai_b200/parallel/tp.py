@@ -28,6 +28,8 @@ class TensorParallel:
         self.rank, self.size, self.device, self.group = rank, size, device, group
         self.backend = backend
         self.comm = None
+        # steps with at least this many tokens (and a multiple of the world size) take the sequence-parallel form
+        self.sp_min_tokens = int(os.environ.get("OGB_TP_SP_MIN_TOKENS", "257"))
         if backend == "fused":
             try:
                 from .symm import SymmetricComm
@@ -66,8 +68,10 @@ class TensorParallel:
     def reduce(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         if self.size == 1:
             return x
-        if self.comm is not None and x.dtype == torch.bfloat16 and self.comm.fits(x):
-            return self.comm.all_reduce(x, residual)    # one-shot kernel over NVLink peer memory
+        if self.comm is not None and x.dtype == torch.bfloat16 and x.numel() <= (1 << 20) and self.comm.fits(x):
+            # one-shot kernel over NVLink peer memory: every rank pushes its whole tensor to every peer, which wins while
+            # the tensor is small (latency bound); larger ones go to NCCL's bandwidth-optimal algorithms
+            return self.comm.all_reduce(x, residual)
         if x.dtype == torch.bfloat16 and not x.is_cuda:
             y = x.float()
             dist.all_reduce(y, group=self.group)

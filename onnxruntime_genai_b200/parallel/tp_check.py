@@ -64,7 +64,8 @@ def main():
         ops.check_kernel_status()
     rank = tp.rank if tp is not None else 0
     if rank == 0:
-        np.savez(a.out, logits=logits, seqs=seqs, engine=eng_out, backend=str(getattr(tp, "backend", "single")))
+        np.savez(a.out, logits=logits, seqs=seqs, engine=eng_out, backend=str(getattr(tp, "backend", "single")),
+                 sp_steps=int(model.decoder.sp_steps))
     if tp is not None:
         from onnxruntime_genai_b200.parallel.tp import leave
         leave(0)

@@ -51,15 +51,21 @@ def test_tp2_on_cpu_matches_single_rank(ckpt):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("backend", ["nccl", "fused"])
+@pytest.mark.parametrize("backend", ["nccl", "fused", "fused-sp"])
 def test_tp2_on_gpu_matches_single_gpu(ckpt, backend):
+    """fused-sp: prompts also take the sequence-parallel form (all-gather -> GEMM, GEMM -> reduce-scatter kernels)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _, gpu, base = ckpt
     one = _run(gpu, os.path.join(base, "gpu1.npz"), 1, 0, ["--engine"])
-    two = _run(gpu, os.path.join(base, f"gpu2_{backend}.npz"), 2, 29621 if backend == "nccl" else 29631, ["--backend", backend, "--engine"],
-               {"NCCL_NVLS_ENABLE": "0"})
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    if backend == "fused-sp":
+        env["OGB_TP_SP_MIN_TOKENS"] = "8"
+    port = {"nccl": 29621, "fused": 29631, "fused-sp": 29651}[backend]
+    backend = backend.split("-")[0]
+    two = _run(gpu, os.path.join(base, f"gpu2_{port}.npz"), 2, port, ["--backend", backend, "--engine"], env)
     assert str(two["backend"]) == backend, "the fused path must not silently fall back"
+    assert (int(two["sp_steps"]) > 0) == ("OGB_TP_SP_MIN_TOKENS" in env), "sequence-parallel steps ran exactly when asked for"
     spread = one["logits"].std()
     assert np.abs(two["logits"] - one["logits"]).max() < 0.08 * spread + 0.02
     assert two["seqs"].shape == one["seqs"].shape
