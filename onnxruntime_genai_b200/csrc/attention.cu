@@ -76,6 +76,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   __nv_bfloat16* sK = sQ + BM * SROW;                        // [STAGES][BN][SROW]
   __nv_bfloat16* sV = sK + ATT_STAGES * ATT_BN * SROW;       // [STAGES][BN][SROW]
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int kvh = blockIdx.y;
   const int b = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
@@ -416,6 +418,8 @@ template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out, int out_stride,
                                          int total_rows, int Hq, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= total_rows) return;
@@ -474,12 +478,12 @@ static int LaunchAttentionMode(const AttnParams& p, int max_q_len, int cache_slo
   const int G = p.Hq / p.Hkv;
   const int q_tiles = (max_q_len * G + BM - 1) / BM;
   dim3 grid(q_tiles, p.Hkv, p.B * p.splits);
-  kern<<<grid, ATT_THREADS, SMEM, stream>>>(mk, mv, p);
+  launch_pdl(kern, grid, dim3(ATT_THREADS), SMEM, stream, mk, mv, p);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (p.splits > 1) {
     const int warps = 4;
-    attention_combine_kernel<D><<<(p.total_rows + warps - 1) / warps, warps * 32, 0, stream>>>(
-        p.part_o, p.part_ml, p.sinks, p.out, p.out_stride, p.total_rows, p.Hq, p.splits);
+    launch_pdl(attention_combine_kernel<D>, dim3((p.total_rows + warps - 1) / warps), dim3(warps * 32), 0, stream,
+               static_cast<const float*>(p.part_o), static_cast<const float*>(p.part_ml), p.sinks, p.out, p.out_stride, p.total_rows, p.Hq, p.splits);
     if (cudaGetLastError() != cudaSuccess) return -4;
   }
   return 0;

@@ -2,6 +2,7 @@
 // tcgen05 PTX wrappers with *bounded* waits, and the per-device status word that kernels use to
 // report a wait that ran out instead of hanging.
 #pragma once
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -96,6 +97,31 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
       if (global_timer_ns() - t0 > timeout_ns) return false;
     }
   }
+}
+
+// ------------------------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with launch_pdl may start while its predecessor in the stream is still running; it must execute
+// pdl_wait() before touching anything the predecessor writes (the wait returns once that grid has completed and its
+// memory is visible).  pdl_launch_dependents() lets the NEXT kernel of the stream start its own prologue early.  Every
+// kernel of the decode step does both first thing, so launch latency and prologues hide under the predecessor's tail
+// while the data dependences stay those of ordinary stream order.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename Kern, typename... Args>
+inline bool launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  static const int enabled = [] { const char* e = getenv("OGB_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess;
 }
 
 // ------------------------------------------------------------------------------- TMA

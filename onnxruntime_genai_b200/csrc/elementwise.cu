@@ -13,6 +13,8 @@ namespace ogb {
 // ------------------------------------------------------------------------------------ embedding
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const uint4* __restrict__ table, uint4* __restrict__ out,
                                  int vec_per_row, int vocab, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -46,6 +48,8 @@ __global__ void __launch_bounds__(1024) norm_kernel(const uint4* __restrict__ x,
   float sum = 0.f, sumsq = 0.f;
   int cnt = 0;
   for (int i = threadIdx.x; i < nvec && cnt < MAXV; i += blockDim.x, ++cnt) {
+  pdl_launch_dependents();
+  pdl_wait();
     uint4 a = xr[i];
     const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
     uint4 r = make_uint4(0, 0, 0, 0);
@@ -130,7 +134,9 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
   float* v = buf[warp];
   const bool is_q = h < p.Hq, is_k = !is_q && h < p.Hq + p.Hkv;
   float ss = 0.f;
-  for (int e = lane; e < p.D; e += 32) { float x = bf2f(src[e]); v[e] = x; ss += x * x; }
+  for (int e = lane; e < p.D; e += 32) {
+  pdl_launch_dependents();
+  pdl_wait(); float x = bf2f(src[e]); v[e] = x; ss += x * x; }
   const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
   if (nw) {
     ss = warp_sum(ss);
@@ -212,6 +218,8 @@ __global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ in, float* 
 
 // Gather rows: out[i, :] = in[rows[i], :] (16-byte vectors).
 __global__ void gather_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ rows, uint4* __restrict__ out, int vec_per_row) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = rows[blockIdx.x];
   for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[size_t(blockIdx.x) * vec_per_row + i] = in[size_t(r) * vec_per_row + i];
 }
@@ -223,7 +231,7 @@ using namespace ogb;
 OGB_API int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream) {
   if (T <= 0) return 0;
   if (H % 8) return -1;
-  embedding_kernel<<<T, min(256, H / 8), 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(embedding_kernel, dim3(T), dim3(min(256, H / 8)), 0, static_cast<cudaStream_t>(stream),
       ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), H / 8, vocab, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -238,11 +246,11 @@ OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out,
   if (nvec > threads * 2) return -1;
   auto s = static_cast<cudaStream_t>(stream);
   if (layernorm)
-    norm_kernel<true><<<rows, threads, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
+    launch_pdl(norm_kernel<true>, dim3(rows), dim3(threads), 0, s, static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
                                                static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight),
                                                static_cast<const uint4*>(bias), static_cast<uint4*>(out), H, eps);
   else
-    norm_kernel<false><<<rows, threads, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
+    launch_pdl(norm_kernel<false>, dim3(rows), dim3(threads), 0, s, static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
                                                 static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight),
                                                 static_cast<const uint4*>(bias), static_cast<uint4*>(out), H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -260,7 +268,7 @@ OGB_API int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positio
   p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w); p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
   p.norm_eps = norm_eps; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rot = rot; p.interleaved = interleaved; p.max_pos = max_pos;
   const long items = long(T) * (Hq + 2 * Hkv);
-  rope_kv_kernel<<<unsigned((items + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  launch_pdl(rope_kv_kernel, dim3(unsigned((items + 7) / 8)), dim3(256), 0, static_cast<cudaStream_t>(stream), p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -298,7 +306,7 @@ OGB_API int ogb_bf16_to_f32(const void* in, float* out, long long n, void* strea
 OGB_API int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream) {
   if (n_rows <= 0) return 0;
   if (row_bytes % 16) return -1;
-  gather_rows_kernel<<<n_rows, min(256, row_bytes / 16), 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(gather_rows_kernel, dim3(n_rows), dim3(min(256, row_bytes / 16)), 0, static_cast<cudaStream_t>(stream),
       static_cast<const uint4*>(in), rows, static_cast<uint4*>(out), row_bytes / 16);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -70,7 +70,7 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES;
   // Decode-sized tiles keep two CTAs per SM: more bytes in flight per SM, dynamic balance between
   // SMs, and room for the next kernel's CTAs to become resident and prefetch weights.
-  static constexpr bool TWO_PER_SM = BT <= 64;
+  static constexpr bool TWO_PER_SM = BT <= 128;   // 128-token tiles: two CTAs per SM, one's epilogue under the other's main loop
   static constexpr int BUDGET = TWO_PER_SM ? 100 * 1024 : 196 * 1024;
   static constexpr int MAX_STAGES = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
@@ -97,8 +97,6 @@ __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
   asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
   return v;
 }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ uint32_t comm_flag(uint32_t epoch) { const uint32_t f = epoch + 1u; return f ? f : 1u; }
 // One line: 8 bytes of data + the flag in both halves (each 8-byte half of the store is atomic).
 __device__ __forceinline__ void st_line(uint4* p, uint32_t d0, uint32_t d1, uint32_t flag) {

@@ -299,11 +299,13 @@ const CommParams* ogb_comm_params(int device) { return (device >= 0 && device < 
 
 OGB_API int ogb_gemm_token_tile(int M, int dual) {
   (void)dual;
+  // prefill-sized problems: 256-token tiles with one CTA per SM, or (OGB_GEMM_PREFILL_TILE=128) 128-token tiles with two
+  static const int big = [] { const char* e = getenv("OGB_GEMM_PREFILL_TILE"); return (e && atoi(e) == 128) ? 128 : 256; }();
   if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
   if (M <= 128) return 128;
-  return 256;
+  return big;
 }
 
 // Number of split-K partitions (cluster size along z: 1, 2, 4 or 8; other sizes schedule poorly onto
@@ -313,7 +315,7 @@ OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
   const int bt = ogb_gemm_token_tile(M, dual);
   const int tiles = ((N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N) * ((M + bt - 1) / bt);
   const int total_kb = (K + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
-  const int slots = (bt <= 64 ? 2 : 1) * sm_count;
+  const int slots = (bt <= 128 ? 2 : 1) * sm_count;
   int best = 1;
   for (int s = 2; s <= 8; s *= 2) {
     if (s > bt || total_kb / s < 16 || tiles * s > slots) break;

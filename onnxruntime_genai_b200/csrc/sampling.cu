@@ -379,6 +379,8 @@ __global__ void __launch_bounds__(SAMP_THREADS) sample_kernel(SampleParams p) {
   __shared__ float red_v[32];
   __shared__ int red_i[32];
   __shared__ int cand_n;
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* x = p.logits + size_t(row) * p.row_stride;
   const int n = p.vocab;
@@ -793,7 +795,7 @@ OGB_API int ogb_sample(const float* logits, long long row_stride, int rows, int 
     if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
     configured = true;
   }
-  sample_kernel<<<rows, SAMP_THREADS, kDyn, static_cast<cudaStream_t>(stream)>>>(p);
+  launch_pdl(sample_kernel, dim3(rows), dim3(SAMP_THREADS), kDyn, static_cast<cudaStream_t>(stream), p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

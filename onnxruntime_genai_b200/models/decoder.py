@@ -199,7 +199,7 @@ class DecoderModel:
         plain = (a.num_experts == 0 and not a.layernorm and a.residual_multiplier == 1.0 and a.activation == "silu" and lw.post_attn_norm_w is None and
                  lw.gate_up_interleaved and isinstance(lw.gate_up_w, torch.Tensor) and isinstance(lw.qkv_w, torch.Tensor) and
                  self.embed.dtype == torch.bfloat16)
-        return (plain and T >= tp.sp_min_tokens and T % tp.size == 0 and T * a.hidden_size <= comm.plane_elems and
+        return (plain and 0 < tp.sp_min_tokens <= T and T % tp.size == 0 and T * a.hidden_size <= comm.plane_elems and
                 T * self.lm_head_w.shape[1] <= comm.plane_elems)
 
     sp_steps = 0   # forwards that took the sequence-parallel form (diagnostics / tests)

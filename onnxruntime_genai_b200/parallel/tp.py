@@ -28,8 +28,9 @@ class TensorParallel:
         self.rank, self.size, self.device, self.group = rank, size, device, group
         self.backend = backend
         self.comm = None
-        # steps with at least this many tokens (and a multiple of the world size) take the sequence-parallel form
-        self.sp_min_tokens = int(os.environ.get("OGB_TP_SP_MIN_TOKENS", "257"))
+        # steps with at least this many tokens (and a multiple of the world size) take the sequence-parallel form;
+        # 0 (the default) keeps every step in the all-reduce form
+        self.sp_min_tokens = int(os.environ.get("OGB_TP_SP_MIN_TOKENS", "0"))
         if backend == "fused":
             try:
                 from .symm import SymmetricComm
