@@ -60,6 +60,8 @@ struct GemmParams {
   int ag_rows;          // > 0: all-gather -> GEMM: the activations are not read through the tensor map but assembled from the
                         // flagged lines that the ranks pushed into this rank's receive buffer in the previous fused call
                         // (rank r pushed token rows [r * ag_rows, (r + 1) * ag_rows) as [row][K] into its plane)
+  int ar2_rows;         // > 0: the all-reduce runs in two hops (reduce-scatter by token rows to an owner rank, which sums and
+                        // broadcasts): each partial crosses NVLink once instead of world times; owner of row m = m / ar2_rows
   int rs_rows;          // > 0: reduce-scatter by token rows: rank r receives (and stores, as its rows 0..) rows [r * rs_rows, (r + 1) * rs_rows)
   GroupParams grp;
 };
@@ -267,7 +269,8 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         // that owns the token row (reduce-scatter): two flagged lines per 8 values
         const size_t line = par_off + size_t(p.comm.rank) * plane_lines + (size_t(m) * n_out + col) / 4;
         const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
-        const int r_lo = p.rs_rows > 0 ? m / p.rs_rows : 0, r_hi = p.rs_rows > 0 ? r_lo + 1 : p.comm.world;
+        const int own_rows = p.rs_rows > 0 ? p.rs_rows : p.ar2_rows;      // > 0: the partial goes to the row's owner only
+        const int r_lo = own_rows > 0 ? m / own_rows : 0, r_hi = own_rows > 0 ? r_lo + 1 : p.comm.world;
         for (int r = r_lo; r < r_hi; ++r) {
           st_line(p.comm.buf[r] + line, d0, d1, flag);
           st_line(p.comm.buf[r] + line + 1, d2, d3, flag);
@@ -279,7 +282,50 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
       // Every thread collects the lines of the items it pushed itself: its own pushes are long under way, and the peers'
       // lines of the same items arrive at about the same time.  The data carries its own arrival flag.
       bool dead = *reinterpret_cast<volatile int*>(p.status) != 0;
-      for (int item = et; item < items; item += 128) {
+      if (p.ar2_rows > 0) {
+        // Two-hop all-reduce.  Hop 1 (above) sent every partial to the owner of its token row.  Here the owner sums the
+        // world's partials of its rows in rank order, rounds to bf16 (so that every rank ends up with the same bits),
+        // stores, and broadcasts the sums as flagged lines into plane `owner` of every other rank — a plane position no
+        // hop-1 line of this call uses there; the other ranks then collect the rows they do not own.
+        for (int item = et; item < items; item += 128) {
+          const int mc = c_begin + item / OCT, oc = item % OCT;
+          const int m = row0 + mc;
+          const int col = col0 + oc * 8;
+          if (mc >= rows || col >= n_out || m / p.ar2_rows != p.comm.rank) continue;
+          float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          const size_t line = par_off + (size_t(m) * n_out + col) / 4;
+          for (int r = 0; r < p.comm.world; ++r) {
+            const uint4 q0 = wait_line(p.comm.buf[p.comm.rank] + line + size_t(r) * plane_lines, flag, dead, p.status);
+            const uint4 q1 = wait_line(p.comm.buf[p.comm.rank] + line + size_t(r) * plane_lines + 1, flag, dead, p.status);
+            const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
+            v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+          }
+          const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
+          for (int r = 0; r < p.comm.world; ++r) {
+            if (r == p.comm.rank) continue;
+            st_line(p.comm.buf[r] + line + size_t(p.comm.rank) * plane_lines, d0, d1, flag);
+            st_line(p.comm.buf[r] + line + size_t(p.comm.rank) * plane_lines + 1, d2, d3, flag);
+          }
+          const float2 a = unpack_bf16x2(d0), b = unpack_bf16x2(d1), c = unpack_bf16x2(d2), d = unpack_bf16x2(d3);
+          float w[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+          store8(m, col, w);
+        }
+        for (int item = et; item < items; item += 128) {
+          const int mc = c_begin + item / OCT, oc = item % OCT;
+          const int m = row0 + mc;
+          const int col = col0 + oc * 8;
+          if (mc >= rows || col >= n_out) continue;
+          const int owner = m / p.ar2_rows;
+          if (owner == p.comm.rank) continue;
+          const uint4* src = p.comm.buf[p.comm.rank] + par_off + size_t(owner) * plane_lines + (size_t(m) * n_out + col) / 4;
+          const uint4 q0 = wait_line(src, flag, dead, p.status);
+          const uint4 q1 = wait_line(src + 1, flag, dead, p.status);
+          const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
+          float w[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+          store8(m, col, w);
+        }
+      }
+      for (int item = et; item < items && p.ar2_rows == 0; item += 128) {
         const int mc = c_begin + item / OCT, oc = item % OCT;
         const int m = row0 + mc;
         const int col = col0 + oc * 8;

@@ -382,6 +382,11 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     p.comm = c;
     p.comm_epilogue = 1;
     if (fused_rs) p.rs_rows = (M + c.world - 1) / c.world;
+    else {
+      // one hop (every partial to every rank) costs world x the payload on the wire: fine for 2 ranks, not for 8
+      static const int two_shot = [] { const char* e = getenv("OGB_AR_TWO_SHOT"); return e ? atoi(e) : -1; }();
+      if (two_shot == 1 || (two_shot == -1 && c.world >= 4)) p.ar2_rows = (M + c.world - 1) / c.world;
+    }
   }
   if (flags & 16) {
     // all-gather -> GEMM: A is ignored; the activations come from the receive buffer filled by the previous fused call

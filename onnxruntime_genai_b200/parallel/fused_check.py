@@ -26,7 +26,7 @@ def main():
     from onnxruntime_genai_b200.parallel.tp import TensorParallel
     tp = TensorParallel.from_env("fused")
     rank, world, dev = tp.rank, tp.size, tp.device
-    res = {"world": world, "backend": tp.backend}
+    res = {"world": world, "backend": tp.backend, "two_shot_env": os.environ.get("OGB_AR_TWO_SHOT", "auto")}
     if tp.comm is None:
         res["error"] = "symmetric memory unavailable"
     else:

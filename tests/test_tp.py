@@ -51,9 +51,10 @@ def test_tp2_on_cpu_matches_single_rank(ckpt):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("backend", ["nccl", "fused", "fused-sp"])
+@pytest.mark.parametrize("backend", ["nccl", "fused", "fused-sp", "fused-2hop"])
 def test_tp2_on_gpu_matches_single_gpu(ckpt, backend):
-    """fused-sp: prompts also take the sequence-parallel form (all-gather -> GEMM, GEMM -> reduce-scatter kernels)."""
+    """fused-sp: prompts also take the sequence-parallel form (all-gather -> GEMM, GEMM -> reduce-scatter kernels);
+    fused-2hop: the all-reduce inside the GEMM runs as reduce-scatter to the row owner + broadcast (the form used from 4 ranks up)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _, gpu, base = ckpt
@@ -61,7 +62,9 @@ def test_tp2_on_gpu_matches_single_gpu(ckpt, backend):
     env = {"NCCL_NVLS_ENABLE": "0"}
     if backend == "fused-sp":
         env["OGB_TP_SP_MIN_TOKENS"] = "8"
-    port = {"nccl": 29621, "fused": 29631, "fused-sp": 29651}[backend]
+    if backend == "fused-2hop":
+        env["OGB_AR_TWO_SHOT"] = "1"
+    port = {"nccl": 29621, "fused": 29631, "fused-sp": 29651, "fused-2hop": 29661}[backend]
     backend = backend.split("-")[0]
     two = _run(gpu, os.path.join(base, f"gpu2_{port}.npz"), 2, port, ["--backend", backend, "--engine"], env)
     assert str(two["backend"]) == backend, "the fused path must not silently fall back"
