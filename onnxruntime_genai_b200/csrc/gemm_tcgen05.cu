@@ -286,6 +286,227 @@ static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams
   return cudaLaunchKernelEx(&cfg, kern, tw, ta, p) == cudaSuccess ? 0 : -4;
 }
 
+// ------------------------------------------------------------------------------------------ persistent prefill kernel
+// Compute-bound shapes (hundreds of tokens and more): one CTA per SM walks a list of 128 x 256 output tiles, weight-tile
+// index slowest so that the CTAs of the moment share a few weight tiles and the whole activation matrix in L2.  The TMA
+// producer streams k-blocks across tile boundaries without draining the ring; the accumulator is double buffered in
+// tensor memory (2 x 256 columns), so the MMA warp starts the next tile while the four epilogue warps drain the previous
+// one (tcgen05.ld, 16 token columns at a time through a small staging tile that pairs gate / up rows and makes the
+// stores 16-byte row segments).  Same epilogues as the other kernel except split-K and the collectives, which prefill
+// does not use.
+constexpr int PERS_BT = 256;
+constexpr int PERS_STAGES = 4;
+constexpr int PERS_STAGE_BYTES = W_TILE_BYTES + PERS_BT * GEMM_BLOCK_K * 2;       // 16 KiB + 32 KiB
+constexpr int PERS_STAGING_BYTES = 2 * 16 * GEMM_BLOCK_N * 4;                     // two [16][128] fp32 chunks
+constexpr int PERS_SMEM_BYTES = PERS_STAGES * PERS_STAGE_BYTES + PERS_STAGING_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p,
+                               int n_tiles, int m_tiles) {
+  constexpr int BT = PERS_BT, STAGES = PERS_STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* staging = reinterpret_cast<float*>(smem + STAGES * PERS_STAGE_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * PERS_STAGE_BYTES + PERS_STAGING_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;     // [2] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;          // [2] epilogue (128 arrivals) -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_abort = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = n_tiles * m_tiles;
+  const int num_kb = p.total_kb;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    *abort_flag = 0;
+    *epi_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl) pdl_launch_dependents();
+  auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
+  auto stage_w = [&](int s) { return smem + s * PERS_STAGE_BYTES; };
+  auto stage_a = [&](int s) { return smem + s * PERS_STAGE_BYTES + W_TILE_BYTES; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer: k-blocks of all my tiles, back to back
+      bool waited = false;
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        const int n_tile = t / m_tiles, m_tile = t % m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait_bounded(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); break; }
+          mbar_expect_tx(&full_bar[s], PERS_STAGE_BYTES);
+          tma_load_2d(stage_w(s), &tmap_w, &full_bar[s], kb * GEMM_BLOCK_K, n_tile * GEMM_BLOCK_N);
+          if (!waited) {               // the first weight tile may go out before the previous kernel has finished; activations may not
+            if (p.pdl) pdl_wait();
+            waited = true;
+          }
+          tma_load_2d(stage_a(s), &tmap_a, &full_bar[s], kb * GEMM_BLOCK_K, m_tile * BT);
+        }
+      }
+      if (*abort_flag) {   // copies already issued still write this CTA's shared memory: give them time to land
+        volatile int never = 0;
+        for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait_bounded(&full_bar[i % STAGES], (i / STAGES) & 1, &never, 200000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer: alternate the two accumulators
+      constexpr uint32_t idesc = umma_idesc_f16(GEMM_BLOCK_N, BT, 1);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++j) {
+        const int buf = j & 1;
+        if (j >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_MMA); ok = false; break; }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + uint32_t(buf * BT);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); ok = false; break; }
+          tc_fence_after();
+          const uint32_t w = smem_u32(stage_w(s)), a = smem_u32(stage_a(s));
+#pragma unroll
+          for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
+            umma_f16(acc, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue warps 2..5
+    const int et = threadIdx.x - 64;
+    const int quarter = warp & 3;            // TMEM lanes this warp may read
+    const int row = quarter * 32 + lane;     // weight row of the tile held by this thread
+    const bool pair = p.act_pair != 0;
+    const int OCT = pair ? 8 : 16;
+    const int n_out = pair ? p.N / 2 : p.N;
+    if (p.pdl) pdl_wait();                   // residual reads and all stores come after the previous kernel
+    int j = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
+      const int buf = j & 1;
+      const int n_tile = t / m_tiles, m_tile = t % m_tiles;
+      // a failed wait is published in a word only the epilogue threads write, before the barrier: all 128 take the same branch
+      if (!mbar_wait_bounded(&acc_full[buf], (j >> 1) & 1, abort_flag, 4000000000ull)) { fail(OGB_ERR_WAIT_MMA); *epi_abort = 1; }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*epi_abort) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BT);
+      const int col0 = n_tile * (pair ? 64 : 128);
+      for (int c0 = 0, ch = 0; c0 < BT; c0 += 16, ++ch) {
+        float* part = staging + (ch & 1) * 16 * GEMM_BLOCK_N;      // [16 token columns][128 weight rows]
+        uint32_t r0[16];
+        tmem_ld16(taddr + c0, r0);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q = 0; q < 16; ++q) part[q * GEMM_BLOCK_N + row] = __uint_as_float(r0[q]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");             // chunk visible; the other buffer is free again after the NEXT sync
+        for (int item = et; item < 16 * OCT; item += 128) {
+          const int mc = item / OCT, oc = item % OCT;
+          const int m = m_tile * BT + c0 + mc;
+          if (m >= p.M) continue;
+          float v[8];
+          const float* src = part + mc * GEMM_BLOCK_N + oc * 8;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) v[q] = src[q];
+          if (p.bias) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) if (n_tile * GEMM_BLOCK_N + oc * 8 + q < p.N) v[q] += bf2f(p.bias[n_tile * GEMM_BLOCK_N + oc * 8 + q]);
+          }
+          if (pair) {
+            float u[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) u[q] = src[64 + q];
+            if (p.bias) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) u[q] += bf2f(p.bias[n_tile * GEMM_BLOCK_N + 64 + oc * 8 + q]);
+            }
+            if (p.act_pair == 1) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) v[q] = silu(v[q]) * u[q];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float g = p.act_limit > 0.f ? fminf(v[q], p.act_limit) : v[q];
+                const float w = p.act_limit > 0.f ? fminf(fmaxf(u[q], -p.act_limit), p.act_limit) : u[q];
+                v[q] = g / (1.f + __expf(-p.act_alpha * g)) * (w + 1.f);
+              }
+            }
+          }
+          const int col = col0 + oc * 8;
+          if (col >= n_out) continue;
+          if (p.residual) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) if (col + q < n_out) v[q] += bf2f(p.residual[size_t(m) * p.ldr + col + q]);
+          }
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
+            if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) if (col + q < n_out) dst[q] = v[q];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;
+            if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) if (col + q < n_out) dst[q] = f2bf(v[q]);
+            }
+          }
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, 512);
+}
+
+static int LaunchPersistent(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, int n_tiles, int m_tiles, int sm_count,
+                            cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PERS_SMEM_BYTES) != cudaSuccess) return -3;
+    configured = true;
+  }
+  const int tiles = n_tiles * m_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(tiles < sm_count ? tiles : sm_count));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = PERS_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel, tw, ta, p, n_tiles, m_tiles) == cudaSuccess ? 0 : -4;
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -398,6 +619,9 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     p.comm = c;          // the mainloop needs the buffer and epoch pointers; the epilogue stays local unless bits 2/3 are set
     p.ag_rows = per;
   }
+  static const int persistent = [] { const char* e = getenv("OGB_GEMM_PERSISTENT"); return (e && e[0] == '0') ? 0 : 1; }();
+  if (persistent && bt == 256 && splits == 1 && !p.comm_epilogue && p.ag_rows == 0 && n_tiles * m_tiles >= sm_count)
+    return LaunchPersistent(tw, ta, p, n_tiles, m_tiles, sm_count, stream);
   dim3 grid(n_tiles, m_tiles, splits);
   switch (bt) {
     case 16: return Launch<16>(tw, ta, p, grid, stream);

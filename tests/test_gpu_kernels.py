@@ -145,6 +145,25 @@ def test_gemm_all_gather_fused_world_of_one(M, N, K, pair):
         comm.close()
 
 
+def test_gemm_persistent_prefill_kernel():
+    """Prefill-sized problems (at least one 128 x 256 tile per SM) take the persistent kernel with the double-buffered
+    accumulator: several tiles per CTA, token and feature tails, every epilogue, against fp32."""
+    x = _rand(1000, 512, seed=81)
+    w, b, r = _rand(6144, 512, std=0.05, seed=82), _rand(6144, seed=83), _rand(1000, 6144, seed=84)
+    _close(ops.linear(x, w, b, r), ref.linear(x.cpu(), w.cpu(), b.cpu(), r.cpu()), rtol=2e-2, atol=0.06)
+    w2 = _rand(20000, 256, std=0.05, seed=85)          # 157 feature tiles with a tail, fp32 output (LM-head form)
+    x2 = _rand(300, 256, seed=86)
+    _close(ops.linear(x2, w2, out_fp32=True), ref.linear(x2.cpu(), w2.cpu(), out_fp32=True), rtol=1e-2, atol=0.03)
+    w3, b3 = _rand(8192, 384, std=0.05, seed=87), _rand(8192, seed=88)     # gate/up pairs, 600 tokens: 64 x 3 tiles
+    x3 = _rand(600, 384, seed=89)
+    want = ref.gate_up_act(x3.cpu(), w3.cpu(), b3.cpu())
+    _close(ops.gate_up_act(x3, ops.interleave_gate_up(w3), ops.interleave_gate_up(b3), interleaved=True), want, rtol=3e-2, atol=0.05)
+    # many k-blocks per tile and many tiles per CTA
+    x4, w4 = _rand(2048, 4096, seed=90), _rand(4096, 4096, std=0.02, seed=91)
+    _close(ops.linear(x4, w4), ref.linear(x4.cpu(), w4.cpu()), rtol=2e-2, atol=0.08)
+    ops.check_kernel_status()
+
+
 def test_gemm_strided_activation():
     M, K, N = 20, 256, 256
     big = _rand(M, 3 * K, seed=11)
