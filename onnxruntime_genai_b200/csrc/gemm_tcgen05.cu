@@ -507,6 +507,304 @@ static int LaunchPersistent(const CUtensorMap& tw, const CUtensorMap& ta, const 
   return cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel, tw, ta, p, n_tiles, m_tiles) == cudaSuccess ? 0 : -4;
 }
 
+// ------------------------------------------------------------------------------------------ stream-K decode kernel
+// Decode-sized problems (one token tile of 16..64) are bound by the weight stream, and a grid of (feature tiles x k splits)
+// CTAs rarely divides the GPU evenly: 224 gate/up tiles leave half the SMs with twice the work of the others, and every CTA
+// pays its own prologue, pipeline fill and epilogue.  Here one persistent CTA per SM takes an EQUAL share of all
+// (tile, k-block) units, laid out tile after tile, and its TMA producer streams that share without a bubble at tile
+// boundaries.  A share therefore covers the tail of one tile, whole tiles, and the head of another.  The accumulator is
+// double buffered in tensor memory; for every segment the epilogue warps either
+//   * own the tile (the segment contains its last k-block): add the partial sums of the CTAs before them that hold the
+//     tile's earlier k-blocks, in CTA order (deterministic), then bias / activation / residual / store; or
+//   * contribute: write the fp32 partial tile to this CTA's slot of a scratch buffer as flagged 16-byte lines
+//     {value, flag, value, flag} stamped with the launch's epoch, which the owner polls (bounded) — no barrier, no
+//     clearing of the scratch between launches.  Contributors always have lower CTA indices than the owner and never
+//     wait on anyone, so the owner's wait cannot deadlock.
+struct StreamKParams {
+  uint4* scratch;        // [grid][BT/2 * 128] lines
+  uint32_t* epoch;       // [0] launches finished, [1] CTAs of the running launch that are done
+};
+
+template <int BT>
+struct SKCfg {
+  static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES;
+  static constexpr int PART_BYTES = BT * GEMM_BLOCK_N * 4;
+  static constexpr int MAX_STAGES = (200 * 1024 - PART_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int TMEM_COLS = 2 * BT < 32 ? 32 : 2 * BT;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PART_BYTES + 1024 + 256;
+  static constexpr int SLOT_LINES = BT / 2 * GEMM_BLOCK_N;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p,
+                    const StreamKParams sk, int n_tiles) {
+  using Cfg = SKCfg<BT>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* part = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);   // [BT][128] fp32
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::PART_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_abort = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile uint32_t* epoch_sh = reinterpret_cast<volatile uint32_t*>(tmem_slot + 3);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = p.total_kb;
+  const long long U = (long long)n_tiles * KB;
+  const int G = gridDim.x, c = blockIdx.x;
+  auto share_begin = [&](int cta) { return (U * cta) / G; };
+  const long long u0 = share_begin(c), u1 = share_begin(c + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+    *abort_flag = 0;
+    *epi_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl) pdl_launch_dependents();
+  auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
+  auto stage_w = [&](int s) { return smem + s * Cfg::STAGE_BYTES; };
+  auto stage_a = [&](int s) { return smem + s * Cfg::STAGE_BYTES + W_TILE_BYTES; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer: the whole share, back to back
+      const int n_units = int(u1 - u0);
+      auto load_w = [&](int i) {
+        const long long u = u0 + i;
+        mbar_expect_tx(&full_bar[i % STAGES], Cfg::STAGE_BYTES);
+        tma_load_2d(stage_w(i % STAGES), &tmap_w, &full_bar[i % STAGES], int(u % KB) * GEMM_BLOCK_K, int(u / KB) * GEMM_BLOCK_N);
+      };
+      auto load_a = [&](int i) {
+        tma_load_2d(stage_a(i % STAGES), &tmap_a, &full_bar[i % STAGES], int((u0 + i) % KB) * GEMM_BLOCK_K, 0);
+      };
+      const int pre = min(STAGES, n_units);
+      for (int i = 0; i < pre; ++i) load_w(i);      // weights are never written by an earlier kernel of the stream
+      if (p.pdl) pdl_wait();
+      for (int i = 0; i < pre; ++i) load_a(i);
+      int issued = pre;
+      for (int i = pre; i < n_units; ++i) {
+        if (!mbar_wait_bounded(&empty_bar[i % STAGES], ((i / STAGES) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); break; }
+        load_w(i);
+        load_a(i);
+        ++issued;
+      }
+      if (*abort_flag) {
+        volatile int never = 0;
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait_bounded(&full_bar[i % STAGES], (i / STAGES) & 1, &never, 200000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer: one accumulator per segment, alternating
+      constexpr uint32_t idesc = umma_idesc_f16(GEMM_BLOCK_N, BT, 1);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (long long u = u0; u < u1 && ok; ++j) {
+        const long long seg_end = min(u1, (u / KB + 1) * KB);
+        const int buf = j & 1;
+        if (j >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_MMA); ok = false; break; }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + uint32_t(buf * BT);
+        for (int kk = 0; u < seg_end; ++u, ++kk, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); ok = false; break; }
+          tc_fence_after();
+          const uint32_t w = smem_u32(stage_w(s)), a = smem_u32(stage_a(s));
+#pragma unroll
+          for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
+            umma_f16(acc, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc, (kk > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue warps 2..5
+    const int et = threadIdx.x - 64;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool pair = p.act_pair != 0;
+    const int OCT = pair ? 8 : 16;
+    const int n_out = pair ? p.N / 2 : p.N;
+    if (p.pdl) pdl_wait();     // scratch, epoch, residual reads and all stores come after the previous kernel has finished
+    if (et == 0) *epoch_sh = *reinterpret_cast<volatile uint32_t*>(sk.epoch);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const uint32_t flag = comm_flag(*epoch_sh);
+    bool dead = *reinterpret_cast<volatile int*>(p.status) != 0;
+    int j = 0;
+    for (long long u = u0; u < u1; ++j) {
+      const int tile = int(u / KB);
+      const long long tile_begin = (long long)tile * KB, seg_end = min(u1, tile_begin + KB);
+      const bool owner = seg_end == tile_begin + KB;
+      const bool has_contrib = u > tile_begin;            // earlier k-blocks of this tile live in lower CTAs
+      const int buf = j & 1;
+      if (!mbar_wait_bounded(&acc_full[buf], (j >> 1) & 1, abort_flag, 4000000000ull)) { fail(OGB_ERR_WAIT_MMA); *epi_abort = 1; }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*epi_abort) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BT);
+      if (!owner) {
+        // contributor: the fp32 partial tile goes to this CTA's scratch slot as flagged lines (token-column pairs x rows)
+        uint4* slot = sk.scratch + size_t(c) * Cfg::SLOT_LINES;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          uint32_t r0[16];
+          tmem_ld16(taddr + c0, r0);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) st_line(slot + size_t(c0 / 2 + q) * GEMM_BLOCK_N + row, r0[2 * q], r0[2 * q + 1], flag);
+        }
+      } else {
+        // owner: own sums, plus the contributors' in CTA order, parked for the transposing store loop
+        int c_first = c;
+        if (has_contrib) while (c_first > 0 && share_begin(c_first) > tile_begin) --c_first;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          uint32_t r0[16];
+          tmem_ld16(taddr + c0, r0);
+          tmem_ld_wait();
+          float v[16];
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[q] = 0.f;
+          for (int cc = c_first; cc < c; ++cc) {
+            const uint4* slot = sk.scratch + size_t(cc) * Cfg::SLOT_LINES;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const uint4 ln = wait_line(slot + size_t(c0 / 2 + q) * GEMM_BLOCK_N + row, flag, dead, p.status);
+              v[2 * q] += __uint_as_float(ln.x);
+              v[2 * q + 1] += __uint_as_float(ln.z);
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 16; ++q) part[(c0 + q) * GEMM_BLOCK_N + row] = v[q] + __uint_as_float(r0[q]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int col0 = tile * (pair ? 64 : 128);
+        for (int item = et; item < BT * OCT; item += 128) {
+          const int m = item / OCT, oc = item % OCT;
+          if (m >= p.M) continue;
+          float v[8];
+          const float* src = part + m * GEMM_BLOCK_N + oc * 8;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) v[q] = src[q];
+          if (p.bias) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) if (tile * GEMM_BLOCK_N + oc * 8 + q < p.N) v[q] += bf2f(p.bias[tile * GEMM_BLOCK_N + oc * 8 + q]);
+          }
+          if (pair) {
+            float w2[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) w2[q] = src[64 + q];
+            if (p.bias) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) w2[q] += bf2f(p.bias[tile * GEMM_BLOCK_N + 64 + oc * 8 + q]);
+            }
+            if (p.act_pair == 1) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) v[q] = silu(v[q]) * w2[q];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float g = p.act_limit > 0.f ? fminf(v[q], p.act_limit) : v[q];
+                const float w = p.act_limit > 0.f ? fminf(fmaxf(w2[q], -p.act_limit), p.act_limit) : w2[q];
+                v[q] = g / (1.f + __expf(-p.act_alpha * g)) * (w + 1.f);
+              }
+            }
+          }
+          const int col = col0 + oc * 8;
+          if (col >= n_out) continue;
+          if (p.residual) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) if (col + q < n_out) v[q] += bf2f(p.residual[size_t(m) * p.ldr + col + q]);
+          }
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
+            if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) if (col + q < n_out) dst[q] = v[q];
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;
+            if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) if (col + q < n_out) dst[q] = f2bf(v[q]);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // `part` is rewritten by the next owned segment
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+      u = seg_end;
+    }
+    if (dead) *abort_flag = 1;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  // the last CTA of the launch closes the epoch (every CTA gets here, also after an abort)
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(sk.epoch + 1, 1u) == gridDim.x - 1) {
+      sk.epoch[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(sk.epoch) = *reinterpret_cast<volatile uint32_t*>(sk.epoch) + 1;
+    }
+  }
+}
+
+// Per-device stream-K scratch (registered once by the host: ogb_streamk_register).
+static StreamKParams g_sk[16] = {};
+static int g_sk_grid[16] = {};
+
+template <int BT>
+static int LaunchStreamK(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const StreamKParams& sk, int n_tiles, int grid,
+                         cudaStream_t stream) {
+  using Cfg = SKCfg<BT>;
+  static bool configured = false;
+  auto kern = gemm_streamk_kernel<BT>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tw, ta, p, sk, n_tiles) == cudaSuccess ? 0 : -4;
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -559,6 +857,17 @@ OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void*
   return 0;
 }
 
+// Scratch of the stream-K decode kernel for a device: `scratch` holds max_ctas slots of 64 KiB (flagged lines of a 64 x 128 fp32
+// tile), zero-initialised once; `epoch` two zero-initialised words.  Without a registration decode GEMMs use the
+// (tiles x k-splits) kernel.
+OGB_API int ogb_streamk_register(int device, void* scratch, void* epoch, int max_ctas) {
+  if (device < 0 || device >= 16) return -1;
+  g_sk[device].scratch = static_cast<uint4*>(scratch);
+  g_sk[device].epoch = static_cast<uint32_t*>(epoch);
+  g_sk_grid[device] = max_ctas;
+  return 0;
+}
+
 // flags bit 0: fp32 output; bit 1: paired silu(gate)*up epilogue (N = 2 * output columns, rows
 // interleaved in blocks of 64); bit 2: fused all-reduce over the registered symmetric buffers; bit 3: fused
 // reduce-scatter by token rows instead (rank r ends up with rows [r * ceil(M / world), ...) of the sum, written as
@@ -576,6 +885,7 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
   const int bt = ogb_gemm_token_tile(M, 0);
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, m_tiles = (M + bt - 1) / bt;
   const int total_kb = (K + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
+  const bool auto_split = splits <= 0;      // an explicit split count asks for the (tiles x k-splits) kernel
   if (splits <= 0) splits = ogb_gemm_auto_splits(M, N, K, 0, sm_count);
   if (splits > 8) splits = 8;          // portable cluster size
   if (splits > bt) splits = bt;        // every cluster rank finishes at least one token column
@@ -619,8 +929,23 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     p.comm = c;          // the mainloop needs the buffer and epoch pointers; the epilogue stays local unless bits 2/3 are set
     p.ag_rows = per;
   }
+  static const int streamk = [] { const char* e = getenv("OGB_GEMM_STREAMK"); return (e && e[0] == '0') ? 0 : 1; }();
+  if (streamk && auto_split && bt <= 64 && m_tiles == 1 && !p.comm_epilogue && p.ag_rows == 0 && device >= 0 && device < 16 && g_sk[device].scratch &&
+      (flags & 32) == 0) {
+    // equal shares of all (tile, k-block) units over one persistent CTA per SM; worth it when every CTA gets a few k-blocks
+    const long long units = (long long)n_tiles * total_kb;
+    int grid = sm_count < g_sk_grid[device] ? sm_count : g_sk_grid[device];
+    if (units >= 8ll * grid) {
+      p.splits = 1; p.kb_per_split = total_kb;
+      switch (bt) {
+        case 16: return LaunchStreamK<16>(tw, ta, p, g_sk[device], n_tiles, grid, stream);
+        case 32: return LaunchStreamK<32>(tw, ta, p, g_sk[device], n_tiles, grid, stream);
+        case 64: return LaunchStreamK<64>(tw, ta, p, g_sk[device], n_tiles, grid, stream);
+      }
+    }
+  }
   static const int persistent = [] { const char* e = getenv("OGB_GEMM_PERSISTENT"); return (e && e[0] == '0') ? 0 : 1; }();
-  if (persistent && bt == 256 && splits == 1 && !p.comm_epilogue && p.ag_rows == 0 && n_tiles * m_tiles >= sm_count)
+  if (persistent && auto_split && bt == 256 && splits == 1 && !p.comm_epilogue && p.ag_rows == 0 && n_tiles * m_tiles >= sm_count)
     return LaunchPersistent(tw, ta, p, n_tiles, m_tiles, sm_count, stream);
   dim3 grid(n_tiles, m_tiles, splits);
   switch (bt) {

@@ -39,6 +39,12 @@ class _Workspace:
         self.status = _lib.lib().ogb_status_device_ptr(idx)
         self.sm_count = _lib.lib().ogb_sm_count(idx)
         self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
+        # stream-K decode GEMM: one 64 KiB slot of flagged lines per persistent CTA (one CTA per SM) + its launch counter
+        self.sk_scratch = torch.zeros(self.sm_count * (64 << 10), dtype=torch.uint8, device=device)
+        self.sk_epoch = torch.zeros(2, dtype=torch.int32, device=device)
+        rc = _lib.lib().ogb_streamk_register(idx, self.sk_scratch.data_ptr(), self.sk_epoch.data_ptr(), self.sm_count)
+        if rc != 0:
+            raise RuntimeError(f"ogb_streamk_register failed with {rc}")
 
     def attn_scratch(self, nbytes: int) -> torch.Tensor:
         if nbytes > self.attn_ws.numel():
