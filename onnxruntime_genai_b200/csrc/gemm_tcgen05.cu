@@ -514,12 +514,13 @@ static int LaunchPersistent(const CUtensorMap& tw, const CUtensorMap& ta, const 
 // (tile, k-block) units, laid out tile after tile, and its TMA producer streams that share without a bubble at tile
 // boundaries.  A share therefore covers the tail of one tile, whole tiles, and the head of another.  The accumulator is
 // double buffered in tensor memory; for every segment the epilogue warps either
-//   * own the tile (the segment contains its last k-block): add the partial sums of the CTAs before them that hold the
-//     tile's earlier k-blocks, in CTA order (deterministic), then bias / activation / residual / store; or
+//   * own the tile (the segment contains its FIRST k-block): add the partial sums of the following CTAs that hold the
+//     tile's later k-blocks, in CTA order (deterministic), then bias / activation / residual / store; or
 //   * contribute: write the fp32 partial tile to this CTA's slot of a scratch buffer as flagged 16-byte lines
 //     {value, flag, value, flag} stamped with the launch's epoch, which the owner polls (bounded) — no barrier, no
-//     clearing of the scratch between launches.  Contributors always have lower CTA indices than the owner and never
-//     wait on anyone, so the owner's wait cannot deadlock.
+//     clearing of the scratch between launches.  Contributors never wait on anyone and all CTAs are resident at once
+//     (one per SM), so the owner's wait cannot deadlock; it comes last in the owner's share and concerns data produced
+//     first in the contributors' shares, so it does not stall the streams either.
 struct StreamKParams {
   uint4* scratch;        // [grid][BT/2 * 128] lines
   uint32_t* epoch;       // [0] launches finished, [1] CTAs of the running launch that are done
@@ -654,8 +655,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     for (long long u = u0; u < u1; ++j) {
       const int tile = int(u / KB);
       const long long tile_begin = (long long)tile * KB, seg_end = min(u1, tile_begin + KB);
-      const bool owner = seg_end == tile_begin + KB;
-      const bool has_contrib = u > tile_begin;            // earlier k-blocks of this tile live in lower CTAs
+      // The CTA that holds a tile's FIRST k-blocks owns it.  That segment is the last one of the owner's share, while the
+      // rest of the tile is the first (or only) segment of the following CTAs: the owner waits at the end of its work for
+      // partials that were produced at the start of the others', so the wait never holds up anybody's weight stream.
+      const bool owner = u == tile_begin;
+      const bool has_contrib = seg_end < tile_begin + KB;   // later k-blocks of this tile live in the following CTAs
       const int buf = j & 1;
       if (!mbar_wait_bounded(&acc_full[buf], (j >> 1) & 1, abort_flag, 4000000000ull)) { fail(OGB_ERR_WAIT_MMA); *epi_abort = 1; }
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -675,8 +679,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         }
       } else {
         // owner: own sums, plus the contributors' in CTA order, parked for the transposing store loop
-        int c_first = c;
-        if (has_contrib) while (c_first > 0 && share_begin(c_first) > tile_begin) --c_first;
+        int c_last = c;
+        if (has_contrib) while (c_last + 1 < G && share_begin(c_last + 1) < tile_begin + KB) ++c_last;
 #pragma unroll 1
         for (int c0 = 0; c0 < BT; c0 += 16) {
           uint32_t r0[16];
@@ -685,7 +689,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           float v[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) v[q] = 0.f;
-          for (int cc = c_first; cc < c; ++cc) {
+          for (int cc = c + 1; cc <= c_last; ++cc) {
             const uint4* slot = sk.scratch + size_t(cc) * Cfg::SLOT_LINES;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
