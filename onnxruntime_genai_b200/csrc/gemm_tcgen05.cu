@@ -516,13 +516,14 @@ static int LaunchPersistent(const CUtensorMap& tw, const CUtensorMap& ta, const 
 // double buffered in tensor memory; for every segment the epilogue warps either
 //   * own the tile (the segment contains its FIRST k-block): add the partial sums of the following CTAs that hold the
 //     tile's later k-blocks, in CTA order (deterministic), then bias / activation / residual / store; or
-//   * contribute: write the fp32 partial tile to this CTA's slot of a scratch buffer as flagged 16-byte lines
-//     {value, flag, value, flag} stamped with the launch's epoch, which the owner polls (bounded) — no barrier, no
+//   * contribute: write the fp32 partial tile to this CTA's slot of a scratch buffer and stamp the slot (release store)
+//     with the launch's epoch, which the owner polls (bounded, acquire) before reading the slot — no barrier, no
 //     clearing of the scratch between launches.  Contributors never wait on anyone and all CTAs are resident at once
 //     (one per SM), so the owner's wait cannot deadlock; it comes last in the owner's share and concerns data produced
 //     first in the contributors' shares, so it does not stall the streams either.
 struct StreamKParams {
-  uint4* scratch;        // [grid][BT/2 * 128] lines
+  float* scratch;        // [grid][BT * 128] fp32 partial tiles
+  uint32_t* flags;       // [grid] epoch stamp of the partial tile in each slot
   uint32_t* epoch;       // [0] launches finished, [1] CTAs of the running launch that are done
 };
 
@@ -535,7 +536,7 @@ struct SKCfg {
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int TMEM_COLS = 2 * BT < 32 ? 32 : 2 * BT;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PART_BYTES + 1024 + 256;
-  static constexpr int SLOT_LINES = BT / 2 * GEMM_BLOCK_N;
+  static constexpr int SLOT_FLOATS = BT * GEMM_BLOCK_N;
 };
 
 template <int BT>
@@ -667,18 +668,22 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BT);
       if (!owner) {
-        // contributor: the fp32 partial tile goes to this CTA's scratch slot as flagged lines (token-column pairs x rows)
-        uint4* slot = sk.scratch + size_t(c) * Cfg::SLOT_LINES;
+        // contributor: the fp32 partial tile goes to this CTA's scratch slot ([token column][row]: a warp writes 128
+        // contiguous bytes), then one release store stamps the slot with the launch's epoch
+        float* slot = sk.scratch + size_t(c) * Cfg::SLOT_FLOATS;
 #pragma unroll 1
         for (int c0 = 0; c0 < BT; c0 += 16) {
           uint32_t r0[16];
           tmem_ld16(taddr + c0, r0);
           tmem_ld_wait();
 #pragma unroll
-          for (int q = 0; q < 8; ++q) st_line(slot + size_t(c0 / 2 + q) * GEMM_BLOCK_N + row, r0[2 * q], r0[2 * q + 1], flag);
+          for (int q = 0; q < 16; ++q) slot[(c0 + q) * GEMM_BLOCK_N + row] = __uint_as_float(r0[q]);
         }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk.flags + c), "r"(flag) : "memory");
       } else {
-        // owner: own sums, plus the contributors' in CTA order, parked for the transposing store loop
+        // owner: own sums parked for the transposing store loop, then the contributors' added in CTA order
         int c_last = c;
         if (has_contrib) while (c_last + 1 < G && share_begin(c_last + 1) < tile_begin + KB) ++c_last;
 #pragma unroll 1
@@ -686,20 +691,31 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
           uint32_t r0[16];
           tmem_ld16(taddr + c0, r0);
           tmem_ld_wait();
-          float v[16];
 #pragma unroll
-          for (int q = 0; q < 16; ++q) v[q] = 0.f;
-          for (int cc = c + 1; cc <= c_last; ++cc) {
-            const uint4* slot = sk.scratch + size_t(cc) * Cfg::SLOT_LINES;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const uint4 ln = wait_line(slot + size_t(c0 / 2 + q) * GEMM_BLOCK_N + row, flag, dead, p.status);
-              v[2 * q] += __uint_as_float(ln.x);
-              v[2 * q + 1] += __uint_as_float(ln.z);
+          for (int q = 0; q < 16; ++q) part[(c0 + q) * GEMM_BLOCK_N + row] = __uint_as_float(r0[q]);
+        }
+        for (int cc = c + 1; cc <= c_last; ++cc) {
+          // wait (bounded) for the contributor's stamp, then read its tile with plain L2 loads: every thread the positions it owns
+          if (!dead) {
+            const uint64_t t0 = global_timer_ns();
+            uint32_t seen, spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sk.flags + cc) : "memory");
+              if (seen == flag) break;
+              if ((++spins & 0x3f) == 0 && (*reinterpret_cast<volatile int*>(p.status) != 0 || global_timer_ns() - t0 > 2000000000ull)) {
+                atomicMax(p.status, OGB_ERR_WAIT_PEER);
+                dead = true;
+                break;
+              }
             }
           }
-#pragma unroll
-          for (int q = 0; q < 16; ++q) part[(c0 + q) * GEMM_BLOCK_N + row] = v[q] + __uint_as_float(r0[q]);
+          const float* slot = sk.scratch + size_t(cc) * Cfg::SLOT_FLOATS;
+#pragma unroll 8
+          for (int q = 0; q < BT; ++q) {
+            float v;
+            asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(slot + q * GEMM_BLOCK_N + row) : "memory");
+            part[q * GEMM_BLOCK_N + row] += v;
+          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int col0 = tile * (pair ? 64 : 128);
@@ -861,12 +877,13 @@ OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void*
   return 0;
 }
 
-// Scratch of the stream-K decode kernel for a device: `scratch` holds max_ctas slots of 64 KiB (flagged lines of a 64 x 128 fp32
-// tile), zero-initialised once; `epoch` two zero-initialised words.  Without a registration decode GEMMs use the
+// Scratch of the stream-K decode kernel for a device: `scratch` holds max_ctas slots of 32 KiB (a 64 x 128 fp32 tile), `flags`
+// max_ctas zero-initialised words, `epoch` two zero-initialised words.  Without a registration decode GEMMs use the
 // (tiles x k-splits) kernel.
-OGB_API int ogb_streamk_register(int device, void* scratch, void* epoch, int max_ctas) {
+OGB_API int ogb_streamk_register(int device, void* scratch, void* flags, void* epoch, int max_ctas) {
   if (device < 0 || device >= 16) return -1;
-  g_sk[device].scratch = static_cast<uint4*>(scratch);
+  g_sk[device].scratch = static_cast<float*>(scratch);
+  g_sk[device].flags = static_cast<uint32_t*>(flags);
   g_sk[device].epoch = static_cast<uint32_t*>(epoch);
   g_sk_grid[device] = max_ctas;
   return 0;

@@ -18,7 +18,7 @@ int ogb_sm_count(int device);
 // ---- gemm_tcgen05.cu
 int ogb_gemm_token_tile(int M, int dual);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
-int ogb_streamk_register(int device, void* scratch, void* epoch, int max_ctas);
+int ogb_streamk_register(int device, void* scratch, void* flags, void* epoch, int max_ctas);
 int ogb_comm_register(int device, int world, int rank, void** buf, void* epoch, long long plane_elems);
 // flags: bit 0 fp32 output, bit 1 paired silu(gate)*up epilogue, bit 2 fused tensor-parallel all-reduce,
 // bit 3 fused reduce-scatter by token rows (sequence-parallel form)

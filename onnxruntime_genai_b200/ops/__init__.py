@@ -39,10 +39,12 @@ class _Workspace:
         self.status = _lib.lib().ogb_status_device_ptr(idx)
         self.sm_count = _lib.lib().ogb_sm_count(idx)
         self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
-        # stream-K decode GEMM: one 64 KiB slot of flagged lines per persistent CTA (one CTA per SM) + its launch counter
-        self.sk_scratch = torch.zeros(self.sm_count * (64 << 10), dtype=torch.uint8, device=device)
+        # stream-K decode GEMM: one 32 KiB slot (a 64 x 128 fp32 partial tile) and one stamp per persistent CTA + the launch counter
+        self.sk_scratch = torch.zeros(self.sm_count * (32 << 10), dtype=torch.uint8, device=device)
+        self.sk_flags = torch.zeros(self.sm_count, dtype=torch.int32, device=device)
         self.sk_epoch = torch.zeros(2, dtype=torch.int32, device=device)
-        rc = _lib.lib().ogb_streamk_register(idx, self.sk_scratch.data_ptr(), self.sk_epoch.data_ptr(), self.sm_count)
+        rc = _lib.lib().ogb_streamk_register(idx, self.sk_scratch.data_ptr(), self.sk_flags.data_ptr(), self.sk_epoch.data_ptr(),
+                                             self.sm_count)
         if rc != 0:
             raise RuntimeError(f"ogb_streamk_register failed with {rc}")
 
