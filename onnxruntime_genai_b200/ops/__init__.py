@@ -105,7 +105,7 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) ->
 
 
 # ------------------------------------------------------------------------------------------ GEMM
-GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A = 1, 2, 4, 8, 16
+GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A, GEMM_STREAM_K = 1, 2, 4, 8, 16, 32
 
 
 def _gemm(x, w, out, bias, residual, flags, splits):
@@ -127,7 +127,7 @@ def _gemm_w4(x, w, out, bias, residual, flags, splits):
     return out
 
 
-def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None):
+def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None, stream_k=False):
     """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous).  With all_reduce the
     partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory.
     reduce_scatter=(rank, world): the sum is scattered by token rows instead (sequence-parallel form): the result has
@@ -151,7 +151,8 @@ def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, a
         rows_out = max(0, min(per, x.shape[0] - rank * per))
     if out is None:
         out = torch.empty(rows_out, w.shape[0], dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
-    flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0) | (GEMM_REDUCE_SCATTER if reduce_scatter else 0)
+    flags = ((GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0) | (GEMM_REDUCE_SCATTER if reduce_scatter else 0) |
+             (GEMM_STREAM_K if stream_k else 0))
     return _gemm(x, w, out, bias, residual, flags, splits)
 
 
@@ -180,7 +181,7 @@ def interleave_gate_up(w: torch.Tensor, block: int = 64) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(w.shape).contiguous()
 
 
-def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False):
+def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False, stream_k=False):
     """act(x @ Wg.T) * (x @ Wu.T).  w is [2I, K]: stacked [Wg; Wu], or (interleaved=True) blocks of 64 gate
     rows + 64 up rows as produced by interleave_gate_up (the layout the fused kernel needs)."""
     if isinstance(w, W4Weight):
@@ -205,7 +206,7 @@ def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=Fal
         return act_mul(y.contiguous(), act)
     if out is None:
         out = torch.empty(x.shape[0], inter, dtype=torch.bfloat16, device=x.device)
-    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR, splits)
+    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR | (GEMM_STREAM_K if stream_k else 0), splits)
 
 
 def act_mul(x, act="silu"):
