@@ -42,14 +42,14 @@ __global__ void __launch_bounds__(1024) norm_kernel(const uint4* __restrict__ x,
                                                     uint4* __restrict__ res_out, const uint4* __restrict__ weight,
                                                     const uint4* __restrict__ bias, uint4* __restrict__ out, int H, float eps) {
   constexpr int MAXV = 2;
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, nvec = H / 8;
   const uint4* xr = x + size_t(row) * nvec;
   float v[MAXV][8];
   float sum = 0.f, sumsq = 0.f;
   int cnt = 0;
   for (int i = threadIdx.x; i < nvec && cnt < MAXV; i += blockDim.x, ++cnt) {
-  pdl_launch_dependents();
-  pdl_wait();
     uint4 a = xr[i];
     const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
     uint4 r = make_uint4(0, 0, 0, 0);
@@ -124,6 +124,8 @@ struct RopeParams {
 };
 
 __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float buf[8][256];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.Hq + 2 * p.Hkv;
@@ -134,9 +136,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
   float* v = buf[warp];
   const bool is_q = h < p.Hq, is_k = !is_q && h < p.Hq + p.Hkv;
   float ss = 0.f;
-  for (int e = lane; e < p.D; e += 32) {
-  pdl_launch_dependents();
-  pdl_wait(); float x = bf2f(src[e]); v[e] = x; ss += x * x; }
+  for (int e = lane; e < p.D; e += 32) { float x = bf2f(src[e]); v[e] = x; ss += x * x; }
   const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
   if (nw) {
     ss = warp_sum(ss);
@@ -182,6 +182,28 @@ __global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
     if (act == 0) a = g / (1.f + __expf(-g));
     else a = 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
     out[idx] = f2bf(a * u);
+  }
+}
+
+// ------------------------------------------------------------------------------------ plain activation
+// out[i] = act(x[i]) for the fc1 -> act -> fc2 MLPs (phi, gpt2): 0 SiLU, 1 GELU(tanh), 2 ReLU, 3 GELU(erf).
+// Eight bf16 per thread (16-byte loads and stores); n is a multiple of 8.
+__global__ void act_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, long n_vec, int act) {
+  pdl_launch_dependents(); pdl_wait();
+  for (long idx = long(blockIdx.x) * blockDim.x + threadIdx.x; idx < n_vec; idx += long(gridDim.x) * blockDim.x) {
+    uint4 v = x[idx];
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = bf2f(e[j]);
+      float a;
+      if (act == 0) a = g / (1.f + __expf(-g));
+      else if (act == 1) a = 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
+      else if (act == 2) a = fmaxf(g, 0.f);
+      else a = 0.5f * g * (1.f + erff(g * 0.70710678f));
+      e[j] = f2bf(a);
+    }
+    out[idx] = v;
   }
 }
 
@@ -279,6 +301,15 @@ OGB_API int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* s
   act_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
                                                                          static_cast<__nv_bfloat16*>(out), T, I, act);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_act(const void* x, void* out, long long n, int act, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 8) return -2;
+  const long nv = n / 8;
+  long nb = (nv + 255) / 256; int blocks = int(nb < 148 * 8 ? nb : 148 * 8);
+  return launch_pdl(act_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const uint4*>(x), static_cast<uint4*>(out), nv, act) ? 0 : -4;
 }
 
 OGB_API int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,

@@ -58,6 +58,7 @@ int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, cons
                        const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
                        float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream);
 int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream);
+int ogb_act(const void* x, void* out, long long n, int act, void* stream);
 int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,
                     const float* values, int n, void* stream);
 int ogb_logits_bitmask(float* logits, int rows, int vocab, const uint32_t* mask, const int32_t* mask_rows, void* stream);

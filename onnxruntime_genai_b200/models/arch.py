@@ -53,6 +53,9 @@ class ArchConfig:
     # MLP
     mlp_bias: bool = False
     activation: str = "silu"         # silu | gelu
+    mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
+    parallel_block: bool = False     # phi: attention and MLP both read the input norm; their outputs are summed
+    learned_positions: bool = False  # gpt2: a learned position table added to the token embedding, no rotary embedding
     # mixture of experts (gpt-oss style)
     num_experts: int = 0
     experts_per_token: int = 0
@@ -107,13 +110,13 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
     archs = cfg.get("architectures") or [cfg.get("model_type", "llama")]
     name = archs[0]
     mtype = name.split("For")[0].lower() if "For" in name else cfg.get("model_type", name).lower()
-    hs = cfg["hidden_size"]
-    nh = cfg["num_attention_heads"]
+    hs = cfg.get("hidden_size", cfg.get("n_embd"))
+    nh = cfg.get("num_attention_heads", cfg.get("n_head"))
     a = ArchConfig(
         model_type=mtype,
         vocab_size=cfg["vocab_size"],
         hidden_size=hs,
-        num_layers=cfg["num_hidden_layers"],
+        num_layers=cfg.get("num_hidden_layers", cfg.get("n_layer")),
         num_heads=nh,
         num_kv_heads=cfg.get("num_key_value_heads", nh),
         head_dim=cfg.get("head_dim") or hs // nh,
@@ -133,6 +136,13 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         pad_token_id=cfg.get("pad_token_id") if cfg.get("pad_token_id") is not None else 0,
     )
     mt = cfg.get("model_type", mtype)
+    if mt == "gpt2":
+        a.hidden_size = cfg.get("n_embd", a.hidden_size)
+        a.num_heads = a.num_kv_heads = cfg.get("n_head", a.num_heads)
+        a.num_layers = cfg.get("n_layer", a.num_layers)
+        a.head_dim = a.hidden_size // a.num_heads
+        a.intermediate_size = cfg.get("n_inner") or 4 * a.hidden_size
+        a.context_length = cfg.get("n_positions", a.context_length)
     if mt == "qwen2":
         a.attn_bias = True
     if mt in ("qwen3", "gemma3_text", "olmo2"):
@@ -175,6 +185,16 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.layernorm = True
         a.activation = "gelu"
         a.attn_bias = a.o_bias = a.mlp_bias = a.lm_head_bias = True
+        a.mlp_gated = False
+        a.parallel_block = True
+    if mt == "gpt2":
+        a.layernorm = True
+        a.activation = "gelu"
+        a.attn_bias = a.o_bias = a.mlp_bias = True
+        a.mlp_gated = False
+        a.learned_positions = True
+        a.tie_embeddings = True
+        a.norm_eps = cfg.get("layer_norm_epsilon", 1e-5)
     return a
 
 

@@ -43,13 +43,17 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
     """Canonical (Hugging Face style, [out, in]) parameter names and shapes."""
     H, I, V = arch.hidden_size, arch.intermediate_size, arch.vocab_size
     s: Dict[str, tuple] = {"model.embed_tokens.weight": (V, H)}
+    if arch.learned_positions:
+        s["model.position_embeddings.weight"] = (arch.context_length, H)
     for i in range(arch.num_layers):
         p = f"model.layers.{i}."
         s[p + "input_layernorm.weight"] = (H,)
-        s[p + "post_attention_layernorm.weight"] = (H,)
         if arch.layernorm:
             s[p + "input_layernorm.bias"] = (H,)
-            s[p + "post_attention_layernorm.bias"] = (H,)
+        if not arch.parallel_block:
+            s[p + "post_attention_layernorm.weight"] = (H,)
+            if arch.layernorm:
+                s[p + "post_attention_layernorm.bias"] = (H,)
         if arch.post_sublayer_norms:
             s[p + "pre_feedforward_layernorm.weight"] = (H,)
             s[p + "post_feedforward_layernorm.weight"] = (H,)
@@ -76,6 +80,12 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             s[p + "mlp.experts.gate_up_proj_bias"] = (E, 2 * I)
             s[p + "mlp.experts.down_proj"] = (E, H, I)
             s[p + "mlp.experts.down_proj_bias"] = (E, H)
+        elif not arch.mlp_gated:
+            s[p + "mlp.fc1.weight"] = (I, H)
+            s[p + "mlp.fc2.weight"] = (H, I)
+            if arch.mlp_bias:
+                s[p + "mlp.fc1.bias"] = (I,)
+                s[p + "mlp.fc2.bias"] = (H,)
         else:
             s[p + "mlp.gate_proj.weight"] = (I, H)
             s[p + "mlp.up_proj.weight"] = (I, H)
@@ -322,6 +332,14 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
         W.node("Mul", "/model/embed_tokens/Mul", [hidden, "/model/constants/embed_scale"], ["/model/embed_tokens/Mul/output_0"])
         hidden = "/model/embed_tokens/Mul/output_0"
 
+    if arch.learned_positions:
+        # gpt2: a learned table indexed by position joins the token embedding; attention then runs without rotary embedding
+        put_plain("model.position_embeddings.weight", ["model.position_embeddings.weight"],
+                  {"shape": (arch.context_length, H), "op": "id", "fn": lambda ts: ts[0].float()})
+        W.node("Gather", "/model/pos_embed/Gather", ["model.position_embeddings.weight", "position_ids"], ["/model/pos_embed/Gather/output_0"])
+        W.node("Add", "/model/pos_embed/Add", [hidden, "/model/pos_embed/Gather/output_0"], ["/model/pos_embed/Add/output_0"])
+        hidden = "/model/pos_embed/Add/output_0"
+
     # ---- rotary caches
     multi = longrope_caches(arch)
     if multi is not None:
@@ -392,7 +410,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             attn_inputs += [p + "attn.q_norm.layernorm.weight", p + "attn.k_norm.layernorm.weight"]
         attrs = dict(num_heads=arch.num_heads, kv_num_heads=arch.num_kv_heads, scale=float(arch.scale),
                      local_window_size=int(arch.layer_window(i)) if arch.layer_window(i) else -1, softcap=float(arch.softcap),
-                     do_rotary=1, rotary_interleaved=int(arch.rotary_interleaved))
+                     do_rotary=0 if arch.learned_positions else 1, rotary_interleaved=int(arch.rotary_interleaved))
         if arch.qk_norm:
             attrs["qk_norm_epsilon"] = float(arch.norm_eps)
         if arch.rotary_dim != arch.head_dim:
@@ -415,16 +433,18 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
         else:
             mid_name = "post_attention_layernorm"
         o_out = residual_scale(f"{n}/attn/residual_mul/Mul", o_out)
-        # norm before the MLP (adds the attention output to the residual stream)
-        put_vec(p + mid_name + ".weight", [p + mid_name + ".weight"], arch.norm_offset)
-        ins = [o_out, residual, p + mid_name + ".weight"]
-        if arch.layernorm:
-            put_vec(p + mid_name + ".bias", [p + mid_name + ".bias"])
-            ins.append(p + mid_name + ".bias")
-        W.node(skip_op, f"{n}/{mid_name}/SkipLayerNorm", ins, [f"{n}/{mid_name}/output_0", "", "", f"{n}/{mid_name}/output_3"],
-               domain="com.microsoft", epsilon=float(arch.norm_eps))
-        residual = f"{n}/{mid_name}/output_3"
-        x = f"{n}/{mid_name}/output_0"
+        if not arch.parallel_block:
+            # norm before the MLP (adds the attention output to the residual stream)
+            put_vec(p + mid_name + ".weight", [p + mid_name + ".weight"], arch.norm_offset)
+            ins = [o_out, residual, p + mid_name + ".weight"]
+            if arch.layernorm:
+                put_vec(p + mid_name + ".bias", [p + mid_name + ".bias"])
+                ins.append(p + mid_name + ".bias")
+            W.node(skip_op, f"{n}/{mid_name}/SkipLayerNorm", ins, [f"{n}/{mid_name}/output_0", "", "", f"{n}/{mid_name}/output_3"],
+                   domain="com.microsoft", epsilon=float(arch.norm_eps))
+            residual = f"{n}/{mid_name}/output_3"
+            x = f"{n}/{mid_name}/output_0"
+        # (parallel block: the MLP reads the same normalised input as the attention)
         # MLP / MoE
         if arch.num_experts > 0:
             E = arch.num_experts
@@ -460,6 +480,24 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                        k=arch.experts_per_token, activation_type="swiglu", activation_alpha=float(arch.moe_swiglu_alpha),
                        activation_beta=1.0, swiglu_fusion=1, swiglu_limit=float(arch.moe_swiglu_limit), normalize_routing_weights=1)
             mlp_out = f"{n}/moe/MoE/output_0"
+        elif not arch.mlp_gated:
+            f1 = f"{n}/mlp/fc1/MatMul/output_0"
+            put_linear(p + "mlp.fc1", f"{n}/mlp/fc1/MatMul", [p + "mlp.fc1.weight"], x, f1, I, H)
+            if arch.mlp_bias:
+                put_vec(p + "mlp.fc1.Add.bias", [p + "mlp.fc1.bias"])
+                W.node("Add", f"{n}/mlp/fc1/Add", [f1, p + "mlp.fc1.Add.bias"], [f"{n}/mlp/fc1/Add/output_0"])
+                f1 = f"{n}/mlp/fc1/Add/output_0"
+            if arch.activation == "silu":
+                W.node("Sigmoid", f"{n}/mlp/act_fn/Sigmoid", [f1], [f"{n}/mlp/act_fn/Sigmoid/output_0"])
+                W.node("Mul", f"{n}/mlp/act_fn/Mul", [f1, f"{n}/mlp/act_fn/Sigmoid/output_0"], [f"{n}/mlp/act_fn/output_0"])
+            else:
+                W.node("FastGelu", f"{n}/mlp/act_fn/FastGelu", [f1], [f"{n}/mlp/act_fn/output_0"], domain="com.microsoft")
+            mlp_out = f"{n}/mlp/fc2/MatMul/output_0"
+            put_linear(p + "mlp.fc2", f"{n}/mlp/fc2/MatMul", [p + "mlp.fc2.weight"], f"{n}/mlp/act_fn/output_0", mlp_out, H, I)
+            if arch.mlp_bias:
+                put_vec(p + "mlp.fc2.Add.bias", [p + "mlp.fc2.bias"])
+                W.node("Add", f"{n}/mlp/fc2/Add", [mlp_out, p + "mlp.fc2.Add.bias"], [f"{n}/mlp/fc2/Add/output_0"])
+                mlp_out = f"{n}/mlp/fc2/Add/output_0"
         else:
             gu = f"{n}/mlp/gate_up_proj/MatMul/output_0"
             put_linear(p + "mlp.gate_up_proj", f"{n}/mlp/gate_up_proj/MatMul", [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"], x, gu, 2 * I, H)
@@ -486,6 +524,9 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                    [f"{n}/post_feedforward_layernorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1)
             mlp_out = f"{n}/post_feedforward_layernorm/output_0"
         hidden = residual_scale(f"{n}/mlp/residual_mul/Mul", mlp_out)
+        if arch.parallel_block:
+            W.node("Add", f"{n}/parallel_block/Add", [o_out, hidden], [f"{n}/parallel_block/Add/output_0"])
+            hidden = f"{n}/parallel_block/Add/output_0"
 
     # ---- final norm + head
     fname = f"model.layers.{L}.final_norm_layernorm.weight"
@@ -531,6 +572,8 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                     op.ValueInfo("attention_mask", op.INT64, ("batch_size", "total_sequence_length"))]
         kv_shape = ("batch_size", arch.num_kv_heads, "past_sequence_length", arch.head_dim)
         m.outputs = [op.ValueInfo("logits", op.FLOAT, ("batch_size", "sequence_length", V))]
+    if arch.learned_positions:
+        m.inputs.append(op.ValueInfo("position_ids", op.INT64, ("num_tokens",) if paged else ("batch_size", "sequence_length")))
     for i in range(L):
         m.inputs += [op.ValueInfo(f"past_key_values.{i}.key", io_dt, kv_shape), op.ValueInfo(f"past_key_values.{i}.value", io_dt, kv_shape)]
         m.outputs += [op.ValueInfo(f"present.{i}.key", io_dt, kv_shape), op.ValueInfo(f"present.{i}.value", io_dt, kv_shape)]
@@ -576,6 +619,8 @@ def make_genai_config(arch: ArchConfig, precision: str, ep: str, paged: bool, bl
             inputs["block_table_windowed"] = "block_table_windowed"
     else:
         inputs["attention_mask"] = "attention_mask"
+    if arch.learned_positions:
+        inputs["position_ids"] = "position_ids"
     provider_options = [] if ep == "cpu" else [{ep: {"enable_cuda_graph": "0"} if ep == "cuda" else {}}]
     decoder = {
         "session_options": {"log_id": "onnxruntime-genai", "provider_options": provider_options},

@@ -109,6 +109,10 @@ class LayerWeights:
     gate_up_b: Optional[torch.Tensor] = None
     down_w: Optional[torch.Tensor] = None
     down_b: Optional[torch.Tensor] = None
+    fc1_w: Optional[torch.Tensor] = None       # non-gated MLP (phi, gpt2): fc1 -> activation -> fc2
+    fc1_b: Optional[torch.Tensor] = None
+    fc2_w: Optional[torch.Tensor] = None
+    fc2_b: Optional[torch.Tensor] = None
     router_w: Optional[torch.Tensor] = None
     router_b: Optional[torch.Tensor] = None
     exp_gate_up_w: Optional[torch.Tensor] = None  # [E, 2I, H] rows interleaved (gate, up)
@@ -142,6 +146,7 @@ class DecoderModel:
         self.cos_small: Optional[torch.Tensor] = None
         self.sin_small: Optional[torch.Tensor] = None
         self.rope_original_context = 0
+        self.pos_embed: Optional[torch.Tensor] = None   # learned position table (gpt2)
         self.heads_local = arch.num_heads // self.tp.size
         self.kv_heads_local = max(1, arch.num_kv_heads // self.tp.size)
         self.inter_local = arch.intermediate_size // self.tp.size
@@ -160,6 +165,9 @@ class DecoderModel:
         if a.num_experts > 0:
             from .moe import moe_forward
             return moe_forward(self, lw, x)
+        if not a.mlp_gated:
+            y = ops.activation(self._linear(x, lw.fc1_w, lw.fc1_b, lora=self._lora(lw, "fc1")), a.activation)
+            return self._row_parallel(y, lw.fc2_w, lw.fc2_b, self._lora(lw, "fc2"))
         lora = self._lora(lw, "gate_up_proj")
         if lora is None:
             act = ops.gate_up_act(x, lw.gate_up_w, lw.gate_up_b, a.activation, interleaved=lw.gate_up_interleaved)
@@ -257,6 +265,9 @@ class DecoderModel:
         if self._sp_ok(s):
             return self._forward_sp(s, kv)
         h = s.inputs_embeds if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
+        if a.learned_positions:
+            h = h + ops.embedding(s.positions, self.pos_embed, 1.0)
+        rot = 0 if a.learned_positions else a.rotary_dim
         residual = None
         cos, sin = self.cos, self.sin
         if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
@@ -273,11 +284,14 @@ class DecoderModel:
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
             ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
-                               a.head_dim, a.rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+                               a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
                                       max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
             h = self._row_parallel(att, lw.o_w, lw.o_b, self._lora(lw, "o_proj"))
+            if a.parallel_block:
+                h = h + self._mlp(lw, x)      # attention and MLP read the same normalised input; one residual join
+                continue
             if lw.post_attn_norm_w is not None:
                 h, _ = ops.norm(h, lw.post_attn_norm_w, a.norm_eps)
             if a.residual_multiplier != 1.0:

@@ -120,6 +120,13 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all("/model/layers.0/attn/"))
     a.o_bias = g.by_name.get("/model/layers.0/attn/o_proj/Add") is not None
     a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
+    a.parallel_block = g.find("/model/layers.0/parallel_block/") is not None
+    a.learned_positions = g.by_name.get("/model/pos_embed/Gather") is not None
+    fc1 = g.find("/model/layers.0/mlp/fc1/", ops=["MatMul", "MatMulNBits"])
+    if fc1 is not None:
+        a.mlp_gated = False
+        a.intermediate_size = _linear_shape(g, fc1)[0]
+        a.mlp_bias = g.by_name.get("/model/layers.0/mlp/fc1/Add") is not None
     moe = g.find("/model/layers.0/moe/", ops=["MoE", "QMoE"])
     if moe is not None:
         a.experts_per_token = int(_attr(moe, "k", 1))
@@ -139,7 +146,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
             gp = g.find("/model/layers.0/mlp/gate_proj/", ops=["MatMul", "MatMulNBits"])
             if gp is not None:
                 a.intermediate_size = _linear_shape(g, gp)[0]
-        a.mlp_bias = g.find("/model/layers.0/mlp/down_proj/Add") is not None
+        if fc1 is None:
+            a.mlp_bias = g.find("/model/layers.0/mlp/down_proj/Add") is not None
         a.activation = "gelu" if g.find("/model/layers.0/mlp/act_fn/", ops=["FastGelu", "Gelu", "BiasGelu"]) is not None else "silu"
     if g.by_name.get("/model/embed_tokens/Mul") is not None:
         a.embed_scale = float(g.tensor("/model/constants/embed_scale").float().item())
@@ -256,6 +264,8 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
     model.embed = emb.to(device=device, dtype=dtype).contiguous()
     cos, sin = g.tensor("cos_cache").float(), g.tensor("sin_cache").float()
     model.cos, model.sin = cos.to(device).contiguous(), sin.to(device).contiguous()
+    if arch.learned_positions:
+        model.pos_embed = g.tensor("model.position_embeddings.weight", device=device).to(device=device, dtype=dtype).contiguous()
     if g.has_init("cos_cache_small") and g.has_init("cos_cache_large"):
         # long-context RoPE: short-factor caches up to the original context length, long-factor caches beyond
         model.rope_original_context = int(g.tensor("/model/rope_caches_subgraph/original_context_length").item())
@@ -272,8 +282,8 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         lw = LayerWeights(
             ln1_w=_vec(g, ln1.inputs[w_idx1], dtype, device),
             ln1_b=_vec(g, ln1.inputs[w_idx1 + 1], dtype, device) if arch.layernorm and len(ln1.inputs) > w_idx1 + 1 else None,
-            ln2_w=_vec(g, ln2.inputs[2], dtype, device),
-            ln2_b=_vec(g, ln2.inputs[3], dtype, device) if arch.layernorm and len(ln2.inputs) > 3 else None,
+            ln2_w=_vec(g, ln2.inputs[2], dtype, device) if ln2 is not None else None,      # parallel blocks have one norm
+            ln2_b=_vec(g, ln2.inputs[3], dtype, device) if ln2 is not None and arch.layernorm and len(ln2.inputs) > 3 else None,
             qkv_w=None, o_w=None, window=arch.layer_window(i))
         # attention projections: packed or separate
         qkv = linear_node(f"{n}/attn/", "qkv_proj")
@@ -370,6 +380,15 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                 if lw.exp_gate_up_b is not None:
                     lw.exp_gate_up_b = interleave_experts_gate_up(lw.exp_gate_up_b)
                 lw.exp_blocked = True
+        elif not arch.mlp_gated:
+            i_rows = slice(tpr * i_l, (tpr + 1) * i_l)
+            lw.fc1_w = _linear_weight(g, linear_node(f"{n}/mlp/", "fc1"), dtype, device, rows=i_rows if tpn > 1 else None)
+            lw.fc2_w = _linear_weight(g, linear_node(f"{n}/mlp/", "fc2"), dtype, device, cols=i_rows if tpn > 1 else None)
+            b1, b2 = g.by_name.get(f"{n}/mlp/fc1/Add"), g.by_name.get(f"{n}/mlp/fc2/Add")
+            if b1 is not None:
+                lw.fc1_b = _vec(g, b1.inputs[1], dtype, device, i_rows if tpn > 1 else None)
+            if b2 is not None:
+                lw.fc2_b = _vec(g, b2.inputs[1], dtype, device)
         else:
             gu = linear_node(f"{n}/mlp/", "gate_up_proj")
             g_rows, u_rows = slice(tpr * i_l, (tpr + 1) * i_l), slice(I + tpr * i_l, I + (tpr + 1) * i_l)

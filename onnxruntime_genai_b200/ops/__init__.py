@@ -16,7 +16,7 @@ from . import reference as ref
 from . import _lib
 from .w4 import W4Weight, unpack_ort_q4
 
-_ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1}
+_ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "gelu_erf": 3}
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -215,6 +215,16 @@ def act_mul(x, act="silu"):
     T, two_i = x.shape
     out = torch.empty(T, two_i // 2, dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().ogb_act_mul(_ptr(x), _ptr(out), T, two_i // 2, _ACT[act], _stream()), "act_mul")
+    return out
+
+
+def activation(x, act="gelu"):
+    """Elementwise activation of a bf16 tensor (the fc1 -> act -> fc2 MLPs of phi and gpt2)."""
+    if not x.is_cuda:
+        return ref.activation(x, act)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    _lib.check(_lib.lib().ogb_act(_ptr(x), _ptr(out), x.numel(), _ACT[act], _stream()), "activation")
     return out
 
 

@@ -66,6 +66,19 @@ def act_mul(x, act="silu"):
     return (a * u).to(x.dtype)
 
 
+def activation(x, act="gelu"):
+    f = x.float()
+    if act == "silu":
+        y = torch.nn.functional.silu(f)
+    elif act == "relu":
+        y = torch.relu(f)
+    elif act == "gelu_erf":
+        y = torch.nn.functional.gelu(f)
+    else:
+        y = torch.nn.functional.gelu(f, approximate="tanh")
+    return y.to(x.dtype)
+
+
 def _rotate(v, cos, sin, rot, interleaved):
     # v: [T, H, D] fp32, cos/sin: [T, rot/2]
     out = v.clone()

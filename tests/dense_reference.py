@@ -40,6 +40,8 @@ def logits(arch, sd, ids):
         cos, sin = multi[0], multi[1]      # sequences within the original context use the short-factor caches
     cos, sin = torch.from_numpy(cos)[pos], torch.from_numpy(sin)[pos]
     h = sd["model.embed_tokens.weight"][torch.tensor(ids)] * arch.embed_scale
+    if arch.learned_positions:
+        h = h + sd["model.position_embeddings.weight"][pos]
     G = arch.num_heads // arch.num_kv_heads
     D = arch.head_dim
     for i in range(arch.num_layers):
@@ -53,7 +55,8 @@ def logits(arch, sd, ids):
         if arch.qk_norm:
             hn = lambda t, w: t * torch.rsqrt((t * t).mean(-1, keepdim=True) + arch.norm_eps) * (w + arch.norm_offset)
             q, k = hn(q, g("self_attn.q_norm.weight")), hn(k, g("self_attn.k_norm.weight"))
-        q, k = _rope(q, cos, sin, arch.rotary_dim, arch.rotary_interleaved), _rope(k, cos, sin, arch.rotary_dim, arch.rotary_interleaved)
+        if not arch.learned_positions:
+            q, k = _rope(q, cos, sin, arch.rotary_dim, arch.rotary_interleaved), _rope(k, cos, sin, arch.rotary_dim, arch.rotary_interleaved)
         k, v = k.repeat_interleave(G, 1), v.repeat_interleave(G, 1)
         s = torch.einsum("qhd,khd->hqk", q, k) * arch.scale
         if arch.softcap > 0:
@@ -70,6 +73,9 @@ def logits(arch, sd, ids):
             pr = torch.softmax(s, -1)
         att = torch.einsum("hqk,khd->qhd", pr, v).reshape(S, arch.num_heads * D)
         o = lin(att, "self_attn.o_proj")
+        if arch.parallel_block:      # attention and MLP both read the one normalised input
+            h = h + o + lin(torch.nn.functional.gelu(lin(x, "mlp.fc1"), approximate="tanh"), "mlp.fc2")
+            continue
         if arch.post_sublayer_norms:
             o = _norm(o, g("post_attention_layernorm.weight"), None, arch)
             mid = "pre_feedforward_layernorm"
@@ -89,6 +95,8 @@ def logits(arch, sd, ids):
                     gt, up = gu[0::2].clamp(max=arch.moe_swiglu_limit), gu[1::2].clamp(-arch.moe_swiglu_limit, arch.moe_swiglu_limit)
                     a = gt * torch.sigmoid(arch.moe_swiglu_alpha * gt) * (up + 1)
                     y[t] += tw[t, j] * (a @ g("mlp.experts.down_proj")[e].t() + g("mlp.experts.down_proj_bias")[e])
+        elif not arch.mlp_gated:
+            y = lin(torch.nn.functional.gelu(lin(x, "mlp.fc1"), approximate="tanh"), "mlp.fc2")
         else:
             gt, up = lin(x, "mlp.gate_proj"), lin(x, "mlp.up_proj")
             a = torch.nn.functional.silu(gt) if arch.activation == "silu" else torch.nn.functional.gelu(gt, approximate="tanh")

@@ -27,6 +27,10 @@ FAMILIES = {
     "phi3": dict(model_type="phi3", num_kv_heads=4),
     "phi": dict(model_type="phi", layernorm=True, partial_rotary_factor=0.5, attn_bias=True, o_bias=True, mlp_bias=True,
                 lm_head_bias=True, activation="gelu", num_kv_heads=4),
+    "phi_parallel": dict(model_type="phi", layernorm=True, partial_rotary_factor=0.5, attn_bias=True, o_bias=True, mlp_bias=True,
+                         lm_head_bias=True, activation="gelu", num_kv_heads=4, mlp_gated=False, parallel_block=True),
+    "gpt2": dict(model_type="gpt2", layernorm=True, attn_bias=True, o_bias=True, mlp_bias=True, activation="gelu", num_kv_heads=4,
+                 mlp_gated=False, learned_positions=True, tie_embeddings=True),
     "gemma2": dict(model_type="gemma2", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, softcap=20.0,
                    final_logit_softcap=15.0, sliding_window=8, sliding_layers=[0, 2], attn_scale=0.2, tie_embeddings=True),
     "gemma3": dict(model_type="gemma3_text", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, qk_norm=True,
@@ -48,7 +52,8 @@ def test_family_logits_and_decode_match_dense_reference(family, tmp_path):
     assert model.type == arch.model_type
     a2 = model.arch
     for f in ("norm_eps", "layernorm", "qk_norm", "attn_bias", "o_bias", "mlp_bias", "softcap", "sliding_window", "attn_sinks",
-              "activation", "num_experts", "experts_per_token", "post_sublayer_norms", "rotary_interleaved", "lm_head_bias"):
+              "activation", "num_experts", "experts_per_token", "post_sublayer_norms", "rotary_interleaved", "lm_head_bias",
+              "mlp_gated", "parallel_block", "learned_positions"):
         assert getattr(a2, f) == pytest.approx(getattr(arch, f)), f
     assert a2.intermediate_size == arch.intermediate_size and a2.rotary_dim == arch.rotary_dim
     prompt = np.random.RandomState(4).randint(0, arch.vocab_size - 1, size=(1, 23)).astype(np.int32)

@@ -214,3 +214,33 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
     assert a == b, "running one step ahead must not change any token"
     c = run(ahead, cancel_at=5, late_add=9)     # admission and cancellation while a step is in flight
     assert len(c[1]) <= max(5, len(a[1])) and all(len(c[i]) > 0 for i in (0, 2, 3))
+
+
+@pytest.mark.parametrize("family", ["phi_parallel", "gpt2"])
+def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_path):
+    """fc1 -> GELU -> fc2 MLPs, the parallel attention/MLP block and learned position tables: bf16 GPU against fp32 CPU."""
+    from onnxruntime_genai_b200.models.builder import random_state_dict
+    flags = {"phi_parallel": dict(model_type="phi", layernorm=True, partial_rotary_factor=0.5, attn_bias=True, o_bias=True, mlp_bias=True,
+                                  lm_head_bias=True, activation="gelu", mlp_gated=False, parallel_block=True),
+             "gpt2": dict(model_type="gpt2", layernorm=True, attn_bias=True, o_bias=True, mlp_bias=True, activation="gelu",
+                          mlp_gated=False, learned_positions=True, tie_embeddings=True)}[family]
+    arch = ArchConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=64, intermediate_size=512,
+                      context_length=256, bos_token_id=0, eos_token_id=1023, pad_token_id=0, **flags)
+    sd = random_state_dict(arch, seed=3, std=0.05)
+    gpu, cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    export_model(copy.deepcopy(arch), gpu, "bf16", "cuda", state_dict=sd)
+    export_model(copy.deepcopy(arch), cpu, "fp32", "cpu", state_dict=sd)
+    prompt = np.random.RandomState(8).randint(0, 1023, size=(2, 37)).astype(np.int32)
+    gg, lg = _logits(og.Model(gpu), prompt)
+    gc, lc = _logits(og.Model(cpu), prompt)
+    assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
+    for _ in range(4):
+        gc.generate_next_token()
+        toks = gc.get_next_tokens()
+        forced = np.full((2, 1024), -1e9, dtype=np.float32)
+        forced[np.arange(2), toks] = 0
+        gg.set_logits(forced)
+        gg.generate_next_token()
+    lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
+    ops.check_kernel_status()
+    assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02

@@ -246,6 +246,8 @@ def test_embedding_gather_actmul_cast():
     assert torch.equal(ops.gather_rows(x, torch.tensor([5, 0, 3], dtype=torch.int32, device=DEV)), x[[5, 0, 3]])
     _close(ops.act_mul(x), ref.act_mul(x.cpu()), rtol=2e-2, atol=2e-2)
     _close(ops.act_mul(x, "gelu"), ref.act_mul(x.cpu(), "gelu"), rtol=2e-2, atol=2e-2)
+    for act in ("silu", "gelu", "relu", "gelu_erf"):
+        _close(ops.activation(x * 4, act), ref.activation((x * 4).cpu().float(), act), rtol=1e-2, atol=1e-2)
     assert torch.equal(ops.to_float32(x), x.float())
 
 

@@ -89,3 +89,21 @@ def test_expert_parallel_on_cpu_matches_single_rank(tmp_path):
     two = _run(d, str(tmp_path / "m2.npz"), 2, 29641)
     np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
     assert two["seqs"].tolist() == one["seqs"].tolist()
+
+
+def test_non_gated_parallel_block_under_tp_on_cpu(tmp_path):
+    """fc1 is split by output rows, fc2 by input columns (its bias is added once, after the reduction); the parallel
+    attention/MLP block joins two reduced partial sums."""
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+    arch = ArchConfig(model_type="phi", vocab_size=96, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=8,
+                      intermediate_size=64, context_length=128, layernorm=True, partial_rotary_factor=0.5, attn_bias=True, o_bias=True,
+                      mlp_bias=True, lm_head_bias=True, activation="gelu", mlp_gated=False, parallel_block=True,
+                      eos_token_id=95, pad_token_id=95, bos_token_id=0)
+    sd = random_state_dict(arch, seed=5, std=0.1)
+    d = str(tmp_path / "phi")
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    one = _run(d, str(tmp_path / "p1.npz"), 1, 0)
+    two = _run(d, str(tmp_path / "p2.npz"), 2, 29671)
+    np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
+    assert two["seqs"].tolist() == one["seqs"].tolist()
