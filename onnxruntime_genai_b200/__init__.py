@@ -27,6 +27,9 @@ def __getattr__(name):
     if name == "Adapters":
         from .models.lora import Adapters
         return Adapters
+    if name in ("Images", "Audios", "MultiModalProcessor"):
+        from . import multimodal as _m
+        return getattr(_m, name)
     if name == "MtpGenerator":
         from .mtp import MtpGenerator
         return MtpGenerator

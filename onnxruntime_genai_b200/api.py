@@ -153,21 +153,41 @@ class Model:
         self.device_type = "cuda" if want_cuda else "cpu"
         self.device = torch.device("cuda", torch.cuda.current_device()) if want_cuda else torch.device("cpu")
         self.type = c.model_type
-        from .models.arch import LLM_TYPES
-        if self.type not in LLM_TYPES:
+        from .models.arch import ALM_TYPES, LLM_TYPES, VLM_TYPES
+        if self.type not in LLM_TYPES + VLM_TYPES + ALM_TYPES:
             raise RuntimeError(f"Unsupported model type: {self.type}")
         self.dtype = torch.bfloat16 if want_cuda else torch.float32
         from .models.loader import load_decoder
         with _Trace("model", "load"):
             self.decoder = load_decoder(c.config_path, c, self.device, self.dtype, tp)
             self.draft = load_decoder(c.config_path, c, self.device, self.dtype, tp, decoder=c.draft) if c.draft else None
+        # Multimodal components (reference: src/models/multi_modal.cpp:104-160, src/models/whisper.cpp:19-60): the audio or
+        # vision encoder named by the config's `encoder` / `vision` section.
+        tree = json.loads(c.to_json()).get("model", {})
+        self.multimodal: Dict[str, Any] = {}
+        self.encoder = self.vision = None
+        if self.type in ALM_TYPES or self.type in VLM_TYPES:
+            from .models.encoder import TransformerEncoder
+            if self.type in ALM_TYPES:
+                sec = tree.get("encoder") or {}
+                self.encoder = TransformerEncoder.load(os.path.join(c.config_path, sec.get("filename", "encoder.onnx")), self.device, self.dtype)
+                self.multimodal["audio"] = sec
+                self.multimodal["speech"] = tree.get("speech") or {}
+            if tree.get("vision"):
+                sec = tree["vision"]
+                self.vision = TransformerEncoder.load(os.path.join(c.config_path, sec["filename"]), self.device, self.dtype)
+                self.multimodal["vision"] = sec
+                self.image_token_id = int(tree.get("image_token_id", -1))
         self.arch = self.decoder.arch
         self.graph_capture = bool(c.decoder.get("graph_capture", False))
         if self.draft is not None and self.draft.arch.vocab_size != self.arch.vocab_size:
             raise RuntimeError("speculative decoding: draft and target vocabularies differ")
 
     def create_multimodal_processor(self):
-        raise RuntimeError("this model has no vision or speech component")
+        if not self.multimodal:
+            raise RuntimeError("this model has no vision or speech component")
+        from .multimodal import MultiModalProcessor
+        return MultiModalProcessor(self)
 
     def create_streaming_processor(self):
         raise RuntimeError("this model has no streaming audio component")
@@ -249,6 +269,38 @@ class SequenceState:
         self._free: List[int] = []
         self._moves: List[tuple] = []              # (src block, dst block) copies to do before the next forward
         self._tbl_dirty = False
+        self.cross = None                            # encoder keys / values of an encoder-decoder model (set_cross)
+        self.cross_table = self.cross_lens = None
+        self.max_cross_len = 0
+
+    def set_cross(self, enc_out: torch.Tensor, enc_lens: List[int], rows_per_item: int):
+        """Projects the encoder output of each batch item into the decoder layers' cross-attention keys / values once;
+        the item's rows (beams) all point at the same blocks."""
+        from .models.decoder import CrossKVCache
+        dec, dev, bs = self.decoder, self.decoder.device, self.block_size
+        if len(enc_lens) * rows_per_item != self.rows:
+            raise RuntimeError(f"encoder inputs for {len(enc_lens)} items do not match the batch ({self.rows // rows_per_item})")
+        nblk = [(n + bs - 1) // bs for n in enc_lens]
+        self.cross = CrossKVCache(dec.arch, sum(nblk), bs, dev, dec.dtype, dec.heads_local)
+        table = torch.full((self.rows, max(nblk)), -1, dtype=torch.int32)
+        slots, b0 = [], 0
+        for i, n in enumerate(enc_lens):
+            table[i * rows_per_item:(i + 1) * rows_per_item, :nblk[i]] = torch.arange(b0, b0 + nblk[i], dtype=torch.int32)
+            slots.append(torch.arange(n, dtype=torch.int32) + b0 * bs)
+            b0 += nblk[i]
+        with torch.no_grad():
+            dec.fill_cross_cache(self.cross, enc_out, torch.cat(slots).to(dev))
+        self.cross_table = table.to(dev)
+        self.cross_lens = torch.tensor([n for n in enc_lens for _ in range(rows_per_item)], dtype=torch.int32, device=dev)
+        self.max_cross_len = max(enc_lens)
+        self._graphs = {}     # captured steps hold the previous cross cache
+
+    def _cross_fields(self, rows_used=None) -> dict:
+        if self.cross is None:
+            return {}
+        sel = rows_used is not None and len(rows_used) != self.rows
+        return dict(cross=self.cross, cross_table=self.cross_table[rows_used].contiguous() if sel else self.cross_table,
+                    cross_lens=self.cross_lens[rows_used].contiguous() if sel else self.cross_lens, max_cross_len=self.max_cross_len)
 
     def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None) -> torch.Tensor:
         """Feeds row_tokens[r] (possibly empty) after the cached prefix of row r; returns fp32 logits of the last
@@ -278,7 +330,8 @@ class SequenceState:
         s = StepInputs(input_ids=i32(ids), positions=i32(pos), slot_mapping=i32(slots), cu_seqlens=i32(cu), past_lens=i32(past),
                        block_table=self.block_table[rows_used].contiguous() if len(rows_used) != self.rows else self.block_table,
                        logits_rows=None if want_all_logits else i32(last),
-                       max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds)
+                       max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds,
+                       **self._cross_fields(rows_used))
         return self.decoder.forward(s, self.kv), rows_used
 
     # ---- single-token decode steps replayed from CUDA graphs (one graph per power-of-two bound on the KV length)
@@ -324,7 +377,8 @@ class SequenceState:
         d = self._g_dev
         if key not in self._graphs:
             s = StepInputs(input_ids=d[:R], positions=d[R:2 * R], slot_mapping=d[2 * R:3 * R], cu_seqlens=self._g_cu, past_lens=d[3 * R:],
-                           block_table=self.block_table, logits_rows=self._g_rows, max_q_len=1, max_kv_len=bound)
+                           block_table=self.block_table, logits_rows=self._g_rows, max_q_len=1, max_kv_len=bound,
+                           **self._cross_fields())
             with torch.no_grad():
                 self.decoder.forward(s, self.kv)   # warm-up: allocator, tensor maps, scratch
                 torch.cuda.synchronize(dev)
@@ -504,7 +558,7 @@ class Generator:
                 row_tokens = [self.search.sequence(r).tolist() for r in range(self.rows)]
         chunk = int(self.search_opts.get("chunk_size") or 0)
         with _Trace("model", "run"), torch.no_grad():
-            if chunk > 0:
+            if chunk > 0 and self._image_features is None:
                 longest = max(len(t) for t in row_tokens)
                 logits = None
                 for c0 in range(0, longest, chunk):
@@ -516,7 +570,7 @@ class Generator:
             elif all(len(t) == 1 for t in row_tokens) and self._started and self.state.graph_ok():
                 logits = self.state.run_decode_graph([t[0] for t in row_tokens])
             else:
-                logits, used = self.state.run(row_tokens)
+                logits, used = self.state.run(row_tokens, inputs_embeds=self._embeds_with_images(row_tokens))
                 if len(used) != self.rows:
                     full = torch.empty(self.rows, logits.shape[1], dtype=torch.float32, device=logits.device)
                     full[used] = logits
@@ -689,7 +743,56 @@ class Generator:
         raise RuntimeError(f"unknown model output: {name}")
 
     def set_inputs(self, named: NamedTensors):
-        self._extra_inputs = dict(named)
+        """Inputs produced by the multimodal processor: `audio_features` run the audio encoder and fill the decoder's
+        cross-attention cache, `pixel_values` run the vision encoder (its features replace the image-token embeddings of
+        the prompt), `input_ids` are appended as the prompt (reference: src/generators.cpp:700-711 SetInputs)."""
+        named = dict(named)
+        self._extra_inputs = named
+        m = self.model
+        arr = lambda v: v.as_numpy() if isinstance(v, Tensor) else v
+        if "audio_features" in named:
+            if m.encoder is None:
+                raise RuntimeError("this model has no audio encoder")
+            feats = torch.as_tensor(np.asarray(arr(named["audio_features"])))
+            if feats.shape[0] != self.search_opts["batch_size"]:
+                raise RuntimeError(f"audio_features: expected {self.search_opts['batch_size']} clips, got {feats.shape[0]}")
+            with _Trace("model", "encoder"):
+                enc_out, lens = m.encoder.encode_audio(feats)
+                self.state.set_cross(enc_out, lens, self.search_opts["num_beams"])
+        if "pixel_values" in named:
+            if m.vision is None:
+                raise RuntimeError("this model has no vision encoder")
+            with _Trace("model", "vision"):
+                feats, lens = m.vision.encode_images(torch.as_tensor(np.asarray(arr(named["pixel_values"]))))
+            self._image_features = feats
+        if "input_ids" in named:
+            self.append_tokens(arr(named["input_ids"]))
+
+    _image_features: Optional[torch.Tensor] = None
+
+    def _embeds_with_images(self, row_tokens: List[List[int]]) -> Optional[torch.Tensor]:
+        """Token embeddings of the packed step with the rows at image-token positions replaced, in order, by the pending
+        image features (each batch item's beams read the same features)."""
+        feats = self._image_features
+        if feats is None:
+            return None
+        dec, m = self.model.decoder, self.model
+        nb = self.search_opts["num_beams"]
+        ids = torch.tensor([t for toks in row_tokens for t in toks], dtype=torch.int32, device=dec.device)
+        emb = ops.embedding(ids, dec.embed, dec.arch.embed_scale)
+        src, used = [], 0
+        for r, toks in enumerate(row_tokens):
+            n = sum(1 for t in toks if t == m.image_token_id)
+            if r % nb == 0:
+                start, used = used, used + n
+            src.append(torch.arange(start, start + n))
+        src = torch.cat(src) if src else torch.zeros(0, dtype=torch.long)
+        if used > feats.shape[0]:
+            raise RuntimeError(f"the prompt has {used} image tokens but the images give {feats.shape[0]} features")
+        if src.numel():
+            emb[(ids == m.image_token_id).nonzero().flatten()] = feats[src.to(dec.device)].to(emb.dtype)
+        self._image_features = feats[used:] if used < feats.shape[0] else None
+        return emb
 
     def set_model_input(self, name: str, tensor):
         self._extra_inputs = getattr(self, "_extra_inputs", {})

@@ -8,7 +8,8 @@
 // holds past_sequence_lengths[b] tokens plus this step's tokens (appended by the RoPE kernel),
 // key/value caches are [num_blocks * block_size, kv_heads, head_dim], block_table[b, c] names the
 // block that holds positions [c*block_size, (c+1)*block_size); local_window_size > 0 restricts a
-// query at position p to keys in (p - window, p]; `sinks` adds one learned logit per query head
+// query at position p to keys in (p - window, p], local_window_size < 0 makes every query see all of the request's cached
+// keys (bidirectional encoders and cross-attention); `sinks` adds one learned logit per query head
 // to the softmax denominator; softcap applies cap * tanh(x / cap) to the scaled scores.
 //
 // Work decomposition: one CTA = (request, kv head, tile of 64 (or, in decode, 16) query rows, kv split) where a
@@ -88,12 +89,15 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   const int row0 = blockIdx.x * BM;
   if (row0 >= rows) return;
   const int past = p.past_lens[b];
-  const int kv_total = past + q_len;
+  // window < 0: bidirectional attention over exactly the `past` keys already in the cache (encoder self-attention after
+  // its keys were appended, and cross-attention over an encoder's keys); the step's own tokens add no keys.
+  const bool full = p.window < 0;
+  const int kv_total = full ? past : past + q_len;
   const int32_t* table = p.block_table + size_t(b) * p.table_cols;
 
   // Key range needed by this tile of rows, then the part of it owned by this split.
   const int last_tq = min(q_len - 1, (row0 + BM - 1) / G);
-  int kv_hi = past + last_tq + 1;
+  int kv_hi = full ? past : past + last_tq + 1;
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, past + row0 / G - p.window + 1);
   if (p.splits > 1) {
@@ -260,7 +264,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           const int j = jbase + nt * 8 + t4 * 2 + (e & 1);
           const bool hi = e >= 2;
           const int qpos = hi ? qpos_hi : qpos_lo;
-          bool ok = (hi ? valid_hi : valid_lo) && j >= kv_lo && j < kv_hi && j <= qpos;
+          bool ok = (hi ? valid_hi : valid_lo) && j >= kv_lo && j < kv_hi && (full || j <= qpos);
           if (p.window > 0) ok = ok && j > qpos - p.window;
           float x = s[nt][e];
           if (p.softcap > 0.f) x = p.softcap * tanhf(x * p.scale / p.softcap) * LOG2E;

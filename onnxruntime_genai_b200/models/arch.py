@@ -20,6 +20,12 @@ LLM_TYPES = [
 ]
 
 
+# Vision-language types share one pipeline: ViT-style encoder + projector, image features spliced into the prompt's embeddings
+# at the image-token positions (reference: src/models/model_type.h:20-26 lists the VLM / ALM families).
+VLM_TYPES = ["phi3v", "gemma3", "mistral3", "llava", "fara"]
+ALM_TYPES = ["whisper"]
+
+
 @dataclass
 class ArchConfig:
     model_type: str = "llama"
@@ -53,6 +59,8 @@ class ArchConfig:
     # MLP
     mlp_bias: bool = False
     activation: str = "silu"         # silu | gelu
+    cross_attention: bool = False    # encoder-decoder (whisper): every layer also attends to the encoder's output
+    encoder_hidden_size: int = 0     # width of the encoder output the cross-attention keys / values are projected from (0 = hidden_size)
     mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
     parallel_block: bool = False     # phi: attention and MLP both read the input norm; their outputs are summed
     learned_positions: bool = False  # gpt2: a learned position table added to the token embedding, no rotary embedding

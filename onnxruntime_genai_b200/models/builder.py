@@ -67,6 +67,14 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             s[p + "self_attn.v_proj.bias"] = (arch.kv_size,)
         if arch.o_bias:
             s[p + "self_attn.o_proj.bias"] = (H,)
+        if arch.cross_attention:
+            s[p + "cross_attn_layernorm.weight"] = (H,)
+            if arch.layernorm:
+                s[p + "cross_attn_layernorm.bias"] = (H,)
+            for nm, shp in (("q", (arch.q_size, H)), ("k", (arch.q_size, arch.encoder_hidden_size or H)),
+                            ("v", (arch.q_size, arch.encoder_hidden_size or H)), ("o", (H, arch.q_size))):
+                s[p + f"cross_attn.{nm}_proj.weight"] = shp
+                s[p + f"cross_attn.{nm}_proj.bias"] = (shp[0],)
         if arch.qk_norm:
             s[p + "self_attn.q_norm.weight"] = (arch.head_dim,)
             s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
@@ -424,6 +432,35 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             put_vec(p + "attn.o_proj.Add.bias", [p + "self_attn.o_proj.bias"])
             W.node("Add", f"{n}/attn/o_proj/Add", [o_out, p + "attn.o_proj.Add.bias"], [f"{n}/attn/o_proj/Add/output_0"])
             o_out = f"{n}/attn/o_proj/Add/output_0"
+        if arch.cross_attention:
+            # encoder-decoder: queries from the decoder stream, keys / values projected once from the encoder output
+            put_vec(p + "cross_attn_layernorm.weight", [p + "cross_attn_layernorm.weight"], arch.norm_offset)
+            ins = [o_out, residual, p + "cross_attn_layernorm.weight"]
+            if arch.layernorm:
+                put_vec(p + "cross_attn_layernorm.bias", [p + "cross_attn_layernorm.bias"])
+                ins.append(p + "cross_attn_layernorm.bias")
+            W.node(skip_op, f"{n}/cross_attn_layernorm/SkipLayerNorm", ins,
+                   [f"{n}/cross_attn_layernorm/output_0", "", "", f"{n}/cross_attn_layernorm/output_3"], domain="com.microsoft",
+                   epsilon=float(arch.norm_eps))
+            residual = f"{n}/cross_attn_layernorm/output_3"
+            He = arch.encoder_hidden_size or H
+            cq, ckv = f"{n}/cross_attn/q_proj/Add/output_0", f"{n}/cross_attn/kv_proj/Add/output_0"
+            put_linear(p + "cross_attn.q_proj", f"{n}/cross_attn/q_proj/MatMul", [p + "cross_attn.q_proj.weight"],
+                       f"{n}/cross_attn_layernorm/output_0", f"{n}/cross_attn/q_proj/MatMul/output_0", arch.q_size, H)
+            put_vec(p + "cross_attn.q_proj.Add.bias", [p + "cross_attn.q_proj.bias"])
+            W.node("Add", f"{n}/cross_attn/q_proj/Add", [f"{n}/cross_attn/q_proj/MatMul/output_0", p + "cross_attn.q_proj.Add.bias"], [cq])
+            put_linear(p + "cross_attn.kv_proj", f"{n}/cross_attn/kv_proj/MatMul", [p + "cross_attn.k_proj.weight", p + "cross_attn.v_proj.weight"],
+                       "encoder_hidden_states", f"{n}/cross_attn/kv_proj/MatMul/output_0", 2 * arch.q_size, He)
+            put_vec(p + "cross_attn.kv_proj.Add.bias", [p + "cross_attn.k_proj.bias", p + "cross_attn.v_proj.bias"])
+            W.node("Add", f"{n}/cross_attn/kv_proj/Add", [f"{n}/cross_attn/kv_proj/MatMul/output_0", p + "cross_attn.kv_proj.Add.bias"], [ckv])
+            W.node("Split", f"{n}/cross_attn/kv_proj/Split", [ckv], [f"{n}/cross_attn/k", f"{n}/cross_attn/v"], axis=-1, num_outputs=2)
+            W.node("MultiHeadAttention", f"{n}/cross_attn/MultiHeadAttention", [cq, f"{n}/cross_attn/k", f"{n}/cross_attn/v"],
+                   [f"{n}/cross_attn/MultiHeadAttention/output_0"], domain="com.microsoft", num_heads=arch.num_heads, scale=float(arch.scale))
+            put_linear(p + "cross_attn.o_proj", f"{n}/cross_attn/o_proj/MatMul", [p + "cross_attn.o_proj.weight"],
+                       f"{n}/cross_attn/MultiHeadAttention/output_0", f"{n}/cross_attn/o_proj/MatMul/output_0", H, arch.q_size)
+            put_vec(p + "cross_attn.o_proj.Add.bias", [p + "cross_attn.o_proj.bias"])
+            o_out = f"{n}/cross_attn/o_proj/Add/output_0"
+            W.node("Add", f"{n}/cross_attn/o_proj/Add", [f"{n}/cross_attn/o_proj/MatMul/output_0", p + "cross_attn.o_proj.Add.bias"], [o_out])
         if arch.post_sublayer_norms:
             put_vec(p + "post_attention_layernorm.weight", [p + "post_attention_layernorm.weight"], arch.norm_offset)
             W.node(norm_op, f"{n}/post_attention_layernorm/LayerNorm", [o_out, p + "post_attention_layernorm.weight"],
@@ -490,6 +527,10 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             if arch.activation == "silu":
                 W.node("Sigmoid", f"{n}/mlp/act_fn/Sigmoid", [f1], [f"{n}/mlp/act_fn/Sigmoid/output_0"])
                 W.node("Mul", f"{n}/mlp/act_fn/Mul", [f1, f"{n}/mlp/act_fn/Sigmoid/output_0"], [f"{n}/mlp/act_fn/output_0"])
+            elif arch.activation == "gelu_erf":
+                W.node("Gelu", f"{n}/mlp/act_fn/Gelu", [f1], [f"{n}/mlp/act_fn/output_0"], domain="com.microsoft")
+            elif arch.activation == "relu":
+                W.node("Relu", f"{n}/mlp/act_fn/Relu", [f1], [f"{n}/mlp/act_fn/output_0"])
             else:
                 W.node("FastGelu", f"{n}/mlp/act_fn/FastGelu", [f1], [f"{n}/mlp/act_fn/output_0"], domain="com.microsoft")
             mlp_out = f"{n}/mlp/fc2/MatMul/output_0"
@@ -572,6 +613,8 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                     op.ValueInfo("attention_mask", op.INT64, ("batch_size", "total_sequence_length"))]
         kv_shape = ("batch_size", arch.num_kv_heads, "past_sequence_length", arch.head_dim)
         m.outputs = [op.ValueInfo("logits", op.FLOAT, ("batch_size", "sequence_length", V))]
+    if arch.cross_attention:
+        m.inputs.append(op.ValueInfo("encoder_hidden_states", io_dt, ("batch_size", "encoder_sequence_length", arch.encoder_hidden_size or H)))
     if arch.learned_positions:
         m.inputs.append(op.ValueInfo("position_ids", op.INT64, ("num_tokens",) if paged else ("batch_size", "sequence_length")))
     for i in range(L):
@@ -655,6 +698,79 @@ def make_genai_config(arch: ArchConfig, precision: str, ep: str, paged: bool, bl
 
 
 # ---------------------------------------------------------------------------------------------- HF loading
+# ------------------------------------------------------------------------------------------------ multimodal checkpoints
+def _patch_config(out_dir: str, edit) -> None:
+    path = os.path.join(out_dir, "genai_config.json")
+    with open(path) as f:
+        cfg = json.load(f)
+    edit(cfg)
+    with open(path, "w") as f:
+        json.dump(cfg, f, indent=4)
+
+
+def whisper_decoder_arch(vocab_size: int, hidden_size: int, num_layers: int, num_heads: int, intermediate_size: int,
+                         encoder_hidden_size: int = 0, context_length: int = 448, **kw) -> ArchConfig:
+    """The decoder half of a Whisper model as family flags: LayerNorm, learned positions, biased projections, fc1 -> GELU(erf)
+    -> fc2, cross-attention to the encoder output in every layer, tied output embedding."""
+    return ArchConfig(model_type="whisper", vocab_size=vocab_size, hidden_size=hidden_size, num_layers=num_layers, num_heads=num_heads,
+                      num_kv_heads=num_heads, head_dim=hidden_size // num_heads, intermediate_size=intermediate_size,
+                      context_length=context_length, layernorm=True, norm_eps=1e-5, learned_positions=True, cross_attention=True,
+                      encoder_hidden_size=encoder_hidden_size, attn_bias=True, o_bias=True, mlp_bias=True, mlp_gated=False,
+                      activation="gelu_erf", tie_embeddings=True, **kw)
+
+
+def export_whisper(arch: ArchConfig, enc, out_dir: str, precision: str = "bf16", execution_provider: str = "cuda",
+                   decoder_state_dict=None, encoder_state_dict=None, seed: int = 0, std: float = 0.02, num_frames: int = 3000,
+                   search: Optional[dict] = None) -> str:
+    """Encoder-decoder speech checkpoint: decoder.onnx (cross-attention decoder), encoder.onnx, genai_config.json with
+    model.type "whisper" and an `encoder` section, audio_processor_config.json for the log-mel front end."""
+    from .encoder import export_encoder, random_encoder_state_dict
+    export_model(arch, out_dir, precision, execution_provider, state_dict=decoder_state_dict, seed=seed, std=std, filename="decoder.onnx",
+                 search=search)
+    export_encoder(enc, out_dir, "encoder.onnx", encoder_state_dict or random_encoder_state_dict(enc, seed, std), precision)
+
+    def edit(cfg):
+        cfg["model"]["type"] = "whisper"
+        cfg["model"]["encoder"] = {"filename": "encoder.onnx", "hidden_size": enc.hidden_size, "num_attention_heads": enc.num_heads,
+                                   "num_hidden_layers": enc.num_layers, "head_size": enc.head_dim,
+                                   "inputs": {"audio_features": "audio_features"}, "outputs": {"encoder_hidden_states": "encoder_hidden_states"}}
+        cfg["model"]["decoder"]["inputs"]["encoder_hidden_states"] = "encoder_hidden_states"
+    _patch_config(out_dir, edit)
+    with open(os.path.join(out_dir, "audio_processor_config.json"), "w") as f:
+        json.dump({"processor": {"name": "whisper_log_mel", "num_mel_bins": enc.num_mel_bins, "n_fft": 400, "hop_length": 160,
+                                 "sample_rate": 16000, "num_frames": num_frames}}, f, indent=2)
+    return out_dir
+
+
+def export_vision_language(arch: ArchConfig, vis, out_dir: str, image_token_id: int, precision: str = "bf16",
+                           execution_provider: str = "cuda", decoder_state_dict=None, vision_state_dict=None, seed: int = 0,
+                           std: float = 0.02, model_type: str = "phi3v", image_token: str = "<|image|>", **export_kw) -> str:
+    """Vision-language checkpoint: model.onnx (the text decoder), vision.onnx (ViT + projector into the decoder's width),
+    genai_config.json with a `vision` section and `image_token_id`, processor_config.json for the image front end."""
+    from .encoder import export_encoder, random_encoder_state_dict
+    if vis.projection_size != arch.hidden_size:
+        raise ValueError("the projector must map to the decoder's hidden size")
+    export_model(arch, out_dir, precision, execution_provider, state_dict=decoder_state_dict, seed=seed, std=std, **export_kw)
+    export_encoder(vis, out_dir, "vision.onnx", vision_state_dict or random_encoder_state_dict(vis, seed, std), precision)
+
+    def edit(cfg):
+        cfg["model"]["type"] = model_type
+        cfg["model"]["image_token_id"] = int(image_token_id)
+        cfg["model"]["vision"] = {"filename": "vision.onnx", "config_filename": "processor_config.json", "patch_size": vis.patch_size,
+                                  "num_visual_tokens": vis.num_patches,
+                                  "inputs": {"pixel_values": "pixel_values", "image_sizes": "image_sizes"},
+                                  "outputs": {"image_features": "image_features"}}
+        cfg["model"]["embedding"] = {"filename": cfg["model"]["decoder"]["filename"],
+                                     "inputs": {"input_ids": "input_ids", "image_features": "image_features"},
+                                     "outputs": {"inputs_embeds": "inputs_embeds"}}
+    _patch_config(out_dir, edit)
+    with open(os.path.join(out_dir, "processor_config.json"), "w") as f:
+        json.dump({"processor": {"name": "image_processing", "image_size": vis.image_size, "patch_size": vis.patch_size,
+                                 "image_mean": [0.48145466, 0.4578275, 0.40821073], "image_std": [0.26862954, 0.26130258, 0.27577711],
+                                 "image_token": image_token, "image_token_id": int(image_token_id), "num_image_tokens": vis.num_patches}}, f, indent=2)
+    return out_dir
+
+
 def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
     """Reads *.safetensors (preferred) or pytorch_model*.bin from a Hugging Face model directory."""
     sd: Dict[str, torch.Tensor] = {}

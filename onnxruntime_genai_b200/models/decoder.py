@@ -36,6 +36,10 @@ class StepInputs:
     max_q_len: int = 1
     max_kv_len: int = 1
     inputs_embeds: Optional[torch.Tensor] = None  # overrides the embedding lookup (multimodal / MTP)
+    cross: Optional["CrossKVCache"] = None        # encoder keys / values of an encoder-decoder model
+    cross_table: Optional[torch.Tensor] = None    # [B, cols] blocks of each request's encoder keys in `cross`
+    cross_lens: Optional[torch.Tensor] = None     # [B] encoder positions per request
+    max_cross_len: int = 0
     return_hidden: bool = False
 
 
@@ -74,6 +78,19 @@ class PagedKVCache:
         return arch.num_layers * 2 * block_size * hk * arch.head_dim * torch.empty((), dtype=dtype).element_size()
 
 
+class CrossKVCache:
+    """Keys and values of an encoder's output, projected once per request and per decoder layer: pools of shape
+    [layers, 2, num_blocks * block_size, heads, head_dim] addressed through block tables like the self-attention cache, so
+    beams of one request (and requests sharing an input) point at the same blocks."""
+
+    def __init__(self, arch: ArchConfig, num_blocks: int, block_size: int, device, dtype, heads: int):
+        self.block_size, self.num_blocks = block_size, num_blocks
+        self.pool = torch.zeros(arch.num_layers, 2, num_blocks * block_size, heads, arch.head_dim, dtype=dtype, device=device)
+
+    def layer(self, i: int):
+        return self.pool[i, 0], self.pool[i, 1]
+
+
 class NoTP:
     rank, size = 0, 1
 
@@ -109,6 +126,14 @@ class LayerWeights:
     gate_up_b: Optional[torch.Tensor] = None
     down_w: Optional[torch.Tensor] = None
     down_b: Optional[torch.Tensor] = None
+    cross_ln_w: Optional[torch.Tensor] = None  # encoder-decoder cross-attention (whisper)
+    cross_ln_b: Optional[torch.Tensor] = None
+    cross_q_w: Optional[torch.Tensor] = None
+    cross_q_b: Optional[torch.Tensor] = None
+    cross_kv_w: Optional[torch.Tensor] = None  # stacked [k; v] projection of the encoder output
+    cross_kv_b: Optional[torch.Tensor] = None
+    cross_o_w: Optional[torch.Tensor] = None
+    cross_o_b: Optional[torch.Tensor] = None
     fc1_w: Optional[torch.Tensor] = None       # non-gated MLP (phi, gpt2): fc1 -> activation -> fc2
     fc1_b: Optional[torch.Tensor] = None
     fc2_w: Optional[torch.Tensor] = None
@@ -289,6 +314,16 @@ class DecoderModel:
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
                                       max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
             h = self._row_parallel(att, lw.o_w, lw.o_b, self._lora(lw, "o_proj"))
+            if lw.cross_q_w is not None:
+                if s.cross is None:
+                    raise RuntimeError("this model needs encoder inputs (set_inputs with audio_features) before tokens")
+                x, residual = ops.norm(h, lw.cross_ln_w, a.norm_eps, residual, lw.cross_ln_b, a.layernorm)
+                q = self._linear(x, lw.cross_q_w, lw.cross_q_b)
+                ck, cv = s.cross.layer(li)
+                att = ops.paged_attention(q, ck, cv, s.cu_seqlens, s.cross_lens, s.cross_table, s.cross.block_size, self.heads_local,
+                                          self.heads_local, a.head_dim, a.scale, -1, None, 0.0, max_q_len=s.max_q_len,
+                                          max_kv_len=s.max_cross_len)
+                h = self._row_parallel(att, lw.cross_o_w, lw.cross_o_b, None)
             if a.parallel_block:
                 h = h + self._mlp(lw, x)      # attention and MLP read the same normalised input; one residual join
                 continue
@@ -314,6 +349,15 @@ class DecoderModel:
         if a.final_logit_softcap > 0:
             logits = torch.tanh(logits / a.final_logit_softcap) * a.final_logit_softcap
         return logits
+
+    def fill_cross_cache(self, cross: CrossKVCache, enc_out: torch.Tensor, slots: torch.Tensor) -> None:
+        """Projects encoder output rows [S, encoder_hidden] to every layer's cross-attention keys and values and writes
+        them at `slots` of the cross cache (once per request; the decoder steps only read them)."""
+        a = self.arch
+        for li, lw in enumerate(self.layers):
+            kv = self._linear(enc_out, lw.cross_kv_w, lw.cross_kv_b)
+            ck, cv = cross.layer(li)
+            ops.rope_kv_append(kv, slots, slots, None, None, ck, cv, 0, self.heads_local, a.head_dim, 0)
 
     # ------------------------------------------------------------------------------------ sizing
     def weight_bytes(self) -> int:

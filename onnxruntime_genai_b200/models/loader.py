@@ -120,6 +120,9 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all("/model/layers.0/attn/"))
     a.o_bias = g.by_name.get("/model/layers.0/attn/o_proj/Add") is not None
     a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
+    a.cross_attention = g.find("/model/layers.0/cross_attn/") is not None
+    if a.cross_attention:
+        a.encoder_hidden_size = _linear_shape(g, g.find("/model/layers.0/cross_attn/kv_proj/", ops=["MatMul", "MatMulNBits"]))[1]
     a.parallel_block = g.find("/model/layers.0/parallel_block/") is not None
     a.learned_positions = g.by_name.get("/model/pos_embed/Gather") is not None
     fc1 = g.find("/model/layers.0/mlp/fc1/", ops=["MatMul", "MatMulNBits"])
@@ -148,7 +151,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
                 a.intermediate_size = _linear_shape(g, gp)[0]
         if fc1 is None:
             a.mlp_bias = g.find("/model/layers.0/mlp/down_proj/Add") is not None
-        a.activation = "gelu" if g.find("/model/layers.0/mlp/act_fn/", ops=["FastGelu", "Gelu", "BiasGelu"]) is not None else "silu"
+        act = g.find("/model/layers.0/mlp/act_fn/", ops=["FastGelu", "Gelu", "BiasGelu", "Relu"])
+        a.activation = "silu" if act is None else {"Gelu": "gelu_erf", "Relu": "relu"}.get(act.op_type, "gelu") if fc1 is not None else "gelu"
     if g.by_name.get("/model/embed_tokens/Mul") is not None:
         a.embed_scale = float(g.tensor("/model/constants/embed_scale").float().item())
     if g.has_init("/model/constants/residual_multiplier"):
@@ -318,6 +322,25 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         oadd = g.by_name.get(f"{n}/attn/o_proj/Add")
         if oadd is not None:
             lw.o_b = _vec(g, oadd.inputs[1], dtype, device)
+        if arch.cross_attention:
+            cn = g.by_name[f"{n}/cross_attn_layernorm/SkipLayerNorm"]
+            lw.cross_ln_w = _vec(g, cn.inputs[2], dtype, device)
+            lw.cross_ln_b = _vec(g, cn.inputs[3], dtype, device) if arch.layernorm and len(cn.inputs) > 3 else None
+            hd = slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)
+            Hq = arch.num_heads * D
+            kv_rows = [hd, slice(Hq + hd.start, Hq + hd.stop)]
+            lw.cross_q_w = _linear_weight(g, linear_node(f"{n}/cross_attn/", "q_proj"), dtype, device, rows=hd if tpn > 1 else None)
+            lw.cross_q_b = _vec(g, g.by_name[f"{n}/cross_attn/q_proj/Add"].inputs[1], dtype, device, hd if tpn > 1 else None)
+            kvn = linear_node(f"{n}/cross_attn/", "kv_proj")
+            kvb = g.tensor(g.by_name[f"{n}/cross_attn/kv_proj/Add"].inputs[1])
+            if tpn > 1:
+                lw.cross_kv_w = torch.cat([_linear_weight(g, kvn, dtype, device, rows=r) for r in kv_rows], 0).contiguous()
+                lw.cross_kv_b = shard_rows(kvb, kv_rows).to(device=device, dtype=dtype)
+            else:
+                lw.cross_kv_w = _linear_weight(g, kvn, dtype, device)
+                lw.cross_kv_b = kvb.to(device=device, dtype=dtype).contiguous()
+            lw.cross_o_w = _linear_weight(g, linear_node(f"{n}/cross_attn/", "o_proj"), dtype, device, cols=hd if tpn > 1 else None)
+            lw.cross_o_b = _vec(g, g.by_name[f"{n}/cross_attn/o_proj/Add"].inputs[1], dtype, device)
         attn = g.find(f"{n}/attn/", ops=["GroupQueryAttention", "PagedAttention"])
         for inp in attn.inputs:
             if inp.endswith(".sinks"):

@@ -141,7 +141,8 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
         if n == 0:
             continue
         past = int(past_lens[b])
-        total = past + n
+        full = window is not None and window < 0     # bidirectional over the `past` cached keys (encoders, cross-attention)
+        total = past if full else past + n
         pos = torch.arange(total, device=q.device)
         slots = block_table[b, (pos // block_size).long()].long() * block_size + pos % block_size
         k = kc[slots].float()  # [total, Hkv, D]
@@ -153,7 +154,7 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
         if softcap and softcap > 0:
             s = softcap * torch.tanh(s / softcap)
         qpos = past + torch.arange(n, device=q.device)
-        mask = pos[None, :] <= qpos[:, None]
+        mask = (pos[None, :] <= qpos[:, None]) | full
         if window and window > 0:
             mask = mask & (pos[None, :] > qpos[:, None] - window)
         s = s.masked_fill(~mask[None], float("-inf"))

@@ -29,8 +29,9 @@ def _rope(x, cos, sin, rot, interleaved):
     return out
 
 
-def logits(arch, sd, ids):
-    """ids: list of token ids; returns logits [len(ids), vocab] (fp32)."""
+def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None):
+    """ids: list of token ids; returns logits [len(ids), vocab] (fp32).  encoder_hidden [S_enc, H_enc]: output of the
+    encoder for cross-attention decoders; inputs_embeds [len(ids), H] overrides the token embeddings."""
     sd = {k: v.float() for k, v in sd.items()}
     S = len(ids)
     pos = torch.arange(S)
@@ -40,6 +41,8 @@ def logits(arch, sd, ids):
         cos, sin = multi[0], multi[1]      # sequences within the original context use the short-factor caches
     cos, sin = torch.from_numpy(cos)[pos], torch.from_numpy(sin)[pos]
     h = sd["model.embed_tokens.weight"][torch.tensor(ids)] * arch.embed_scale
+    if inputs_embeds is not None:
+        h = inputs_embeds.float()
     if arch.learned_positions:
         h = h + sd["model.position_embeddings.weight"][pos]
     G = arch.num_heads // arch.num_kv_heads
@@ -73,6 +76,15 @@ def logits(arch, sd, ids):
             pr = torch.softmax(s, -1)
         att = torch.einsum("hqk,khd->qhd", pr, v).reshape(S, arch.num_heads * D)
         o = lin(att, "self_attn.o_proj")
+        if arch.cross_attention:
+            h = h + o
+            xc = _norm(h, g("cross_attn_layernorm.weight"), g("cross_attn_layernorm.bias"), arch)
+            e = encoder_hidden.float()
+            cq = lin(xc, "cross_attn.q_proj").view(S, arch.num_heads, D)
+            ckk = lin(e, "cross_attn.k_proj").view(-1, arch.num_heads, D)
+            cvv = lin(e, "cross_attn.v_proj").view(-1, arch.num_heads, D)
+            cp = torch.softmax(torch.einsum("qhd,khd->hqk", cq, ckk) * arch.scale, -1)
+            o = lin(torch.einsum("hqk,khd->qhd", cp, cvv).reshape(S, -1), "cross_attn.o_proj")
         if arch.parallel_block:      # attention and MLP both read the one normalised input
             h = h + o + lin(torch.nn.functional.gelu(lin(x, "mlp.fc1"), approximate="tanh"), "mlp.fc2")
             continue
@@ -96,7 +108,8 @@ def logits(arch, sd, ids):
                     a = gt * torch.sigmoid(arch.moe_swiglu_alpha * gt) * (up + 1)
                     y[t] += tw[t, j] * (a @ g("mlp.experts.down_proj")[e].t() + g("mlp.experts.down_proj_bias")[e])
         elif not arch.mlp_gated:
-            y = lin(torch.nn.functional.gelu(lin(x, "mlp.fc1"), approximate="tanh"), "mlp.fc2")
+            approx = "none" if arch.activation == "gelu_erf" else "tanh"
+            y = lin(torch.nn.functional.gelu(lin(x, "mlp.fc1"), approximate=approx), "mlp.fc2")
         else:
             gt, up = lin(x, "mlp.gate_proj"), lin(x, "mlp.up_proj")
             a = torch.nn.functional.silu(gt) if arch.activation == "silu" else torch.nn.functional.gelu(gt, approximate="tanh")
@@ -113,3 +126,46 @@ def logits(arch, sd, ids):
     if arch.final_logit_softcap > 0:
         out = torch.tanh(out / arch.final_logit_softcap) * arch.final_logit_softcap
     return out
+
+
+def encoder(cfg, sd, x):
+    """The audio / vision encoder on one sequence of embedded frames or patches x [S, H] (positions already added):
+    pre-LayerNorm blocks with bidirectional attention, final LayerNorm."""
+    F = torch.nn.functional
+    sd = {k: v.float() for k, v in sd.items()}
+    H, nh = cfg.hidden_size, cfg.num_heads
+    D = H // nh
+    ln = lambda t, n: F.layer_norm(t, (H,), sd[n + ".weight"], sd[n + ".bias"], cfg.norm_eps)
+    h = x.float()
+    S = h.shape[0]
+    for i in range(cfg.num_layers):
+        p = f"encoder.layers.{i}."
+        lin = lambda t, n: t @ sd[p + n + ".weight"].t() + sd[p + n + ".bias"]
+        y = ln(h, p + "self_attn_layer_norm")
+        q, k, v = (lin(y, "self_attn." + n).view(S, nh, D) for n in ("q_proj", "k_proj", "v_proj"))
+        pr = torch.softmax(torch.einsum("qhd,khd->hqk", q, k) / D ** 0.5, -1)
+        h = h + lin(torch.einsum("hqk,khd->qhd", pr, v).reshape(S, H), "self_attn.out_proj")
+        y = ln(h, p + "final_layer_norm")
+        h = h + lin(F.gelu(lin(y, "fc1")), "fc2")
+    return ln(h, "encoder.layer_norm")
+
+
+def whisper_encoder(cfg, sd, features):
+    """features [n_mels, frames] -> encoder output [frames / 2, H]."""
+    F = torch.nn.functional
+    f = features.float()[None]
+    x = F.gelu(F.conv1d(f, sd["encoder.conv1.weight"].float(), sd["encoder.conv1.bias"].float(), padding=1))
+    x = F.gelu(F.conv1d(x, sd["encoder.conv2.weight"].float(), sd["encoder.conv2.bias"].float(), padding=1, stride=2))[0].t()
+    return encoder(cfg, sd, x + sd["encoder.embed_positions.weight"].float()[:x.shape[0]])
+
+
+def vision_encoder(cfg, sd, pixels):
+    """pixels [C, size, size] -> projected image features [patches, projection_size]."""
+    F = torch.nn.functional
+    x = F.conv2d(pixels.float()[None], sd["encoder.patch_embedding.weight"].float(), sd["encoder.patch_embedding.bias"].float(),
+                 stride=cfg.patch_size)[0].flatten(1).t()
+    h = encoder(cfg, sd, x + sd["encoder.embed_positions.weight"].float())
+    if cfg.projection_size:
+        h = F.gelu(h @ sd["projector.fc1.weight"].float().t() + sd["projector.fc1.bias"].float())
+        h = h @ sd["projector.fc2.weight"].float().t() + sd["projector.fc2.bias"].float()
+    return h

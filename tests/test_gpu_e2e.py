@@ -244,3 +244,80 @@ def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_pat
     lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
     ops.check_kernel_status()
     assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
+
+
+def _export_pair(tmp_path, export, **kw):
+    gpu, cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    export(gpu, "cuda", "bf16", **kw)
+    export(cpu, "cpu", "fp32", **kw)
+    return og.Model(gpu), og.Model(cpu)
+
+
+def test_whisper_encoder_decoder_on_gpu_tracks_cpu(tmp_path):
+    """Audio encoder (unfold + GEMM convolutions, bidirectional paged attention) and the cross-attention decoder, with the
+    decode steps replayed from CUDA graphs, against the fp32 CPU path of the same checkpoint."""
+    from onnxruntime_genai_b200.models.builder import export_whisper, random_state_dict, whisper_decoder_arch
+    from onnxruntime_genai_b200.models.encoder import EncoderConfig, random_encoder_state_dict
+    enc = EncoderConfig(kind="audio", hidden_size=256, num_layers=2, num_heads=4, intermediate_size=512, num_mel_bins=80,
+                        max_source_positions=150)
+    arch = whisper_decoder_arch(1024, 256, 2, 4, 512, encoder_hidden_size=256, context_length=128, bos_token_id=0, eos_token_id=1023,
+                                pad_token_id=1023)
+    dsd, esd = random_state_dict(arch, seed=2, std=0.05), random_encoder_state_dict(enc, seed=3, std=0.05)
+
+    def export(d, ep, prec):
+        export_whisper(copy.deepcopy(arch), enc, d, prec, ep, decoder_state_dict=dsd, encoder_state_dict=esd, num_frames=300)
+    gpu, cpu = _export_pair(tmp_path, export)
+    feats = np.random.RandomState(0).randn(2, 80, 300).astype(np.float32)
+    enc_g, _ = gpu.encoder.encode_audio(torch.from_numpy(feats))
+    enc_c, _ = cpu.encoder.encode_audio(torch.from_numpy(feats))
+    assert (enc_g.float().cpu() - enc_c).abs().max() < 0.08 * enc_c.std() + 0.02
+    prompt = np.array([[0, 7, 9, 11], [0, 8, 10, 12]], dtype=np.int32)
+    gens = []
+    for m in (gpu, cpu):
+        p = og.GeneratorParams(m)
+        p.set_search_options(max_length=32, batch_size=2)
+        g = og.Generator(m, p)
+        g.set_inputs(og.NamedTensors(audio_features=feats, input_ids=prompt))
+        gens.append(g)
+    gg, gc = gens
+    lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
+    assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
+    for _ in range(6):
+        gc.generate_next_token()
+        toks = gc.get_next_tokens()
+        forced = np.full((2, 1024), -1e9, dtype=np.float32)
+        forced[np.arange(2), toks] = 0
+        gg.set_logits(forced)
+        gg.generate_next_token()
+    lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
+    ops.check_kernel_status()
+    assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
+
+
+def test_vision_language_on_gpu_tracks_cpu(tmp_path):
+    """ViT encoder with a head size the attention kernel does not have (72, run zero-padded to 96) + projector; image features
+    spliced into the prompt embeddings."""
+    from onnxruntime_genai_b200.models.builder import export_vision_language, random_state_dict
+    from onnxruntime_genai_b200.models.encoder import EncoderConfig, random_encoder_state_dict
+    arch = ArchConfig(model_type="phi3", vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      intermediate_size=512, context_length=512, bos_token_id=0, eos_token_id=1023, pad_token_id=1023)
+    vis = EncoderConfig(kind="vision", hidden_size=288, num_layers=2, num_heads=4, intermediate_size=576, image_size=56, patch_size=14,
+                        projection_size=256)
+    dsd, vsd = random_state_dict(arch, seed=4, std=0.05), random_encoder_state_dict(vis, seed=5, std=0.05)
+
+    def export(d, ep, prec):
+        export_vision_language(copy.deepcopy(arch), vis, d, image_token_id=1000, precision=prec, execution_provider=ep,
+                               decoder_state_dict=dsd, vision_state_dict=vsd)
+    gpu, cpu = _export_pair(tmp_path, export)
+    assert gpu.vision.head_pad == 96 and cpu.vision.head_pad == 72
+    px = np.random.RandomState(1).randn(2, 3, 56, 56).astype(np.float32)
+    ids = np.array([[0, 5] + [1000] * 16 + [6, 7] + [1000] * 16 + [8]], dtype=np.int32)
+    out = []
+    for m in (gpu, cpu):
+        p = og.GeneratorParams(m)
+        p.set_search_options(max_length=64)
+        g = og.Generator(m, p)
+        g.set_inputs(og.NamedTensors(pixel_values=px, input_ids=ids))
+        out.append(g.get_logits()[:, 0, :])
+    ops.check_kernel_status()
+    assert np.abs(out[0] - out[1]).max() < 0.08 * out[1].std() + 0.02

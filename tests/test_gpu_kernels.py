@@ -278,6 +278,15 @@ def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, soft
     _close(out, want, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("splits", [None, 3])
+def test_attention_bidirectional_over_cached_keys(splits):
+    """window < 0: every query sees exactly the `past` cached keys (encoder self-attention after its keys were appended,
+    cross-attention over encoder keys) - prefill-sized and single-query rows."""
+    _attention_case(B=3, q_lens=[70, 9, 33], past=[70, 150, 1500], Hq=8, Hkv=8, D=64, bs=16, window=-1, splits=splits)
+    _attention_case(B=4, q_lens=[1] * 4, past=[1, 64, 333, 1500], Hq=12, Hkv=12, D=64, bs=16, window=-1, splits=splits)
+    _attention_case(B=2, q_lens=[40, 17], past=[40, 17], Hq=8, Hkv=2, D=128, bs=16, window=-1, splits=splits)
+
+
 @pytest.mark.parametrize("D", [64, 96, 128])
 def test_attention_decode(D):
     _attention_case(B=5, q_lens=[1] * 5, past=[0, 15, 16, 200, 1023], Hq=8, Hkv=2, D=D, bs=16)
