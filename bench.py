@@ -199,6 +199,7 @@ def ours(args):
     # ---- e2e: public API, pinned H2D of the step inputs + D2H of the sampled ids every step
     model_steps(W)
     barrier()
+    hs0 = dict(engine.host_stats)
     sampler = ClockSampler(local)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -209,6 +210,10 @@ def ours(args):
     barrier()
     e2e_wall = time.perf_counter() - t_e0
     e2e_ms = ev0.elapsed_time(ev1)
+    hs1 = engine.host_stats
+    n_l = max(1, hs1["launches"] - hs0["launches"])
+    host = {"launch_ms_per_step": round((hs1["launch_s"] - hs0["launch_s"]) / n_l * 1e3, 4),
+            "wait_ms_per_step": round((hs1["wait_s"] - hs0["wait_s"]) / n_l * 1e3, 4)}
     step_wall = e2e_wall / K
 
     # ---- device-only: replay the decode graph + sampler K times (inputs stay on the device)
@@ -260,7 +265,8 @@ def ours(args):
                        "engine": "paged-attention continuous batching", "l2": "inputs larger than L2 (weights + KV of tens of GB), no flush",
                        "tp_backend": getattr(tp, "backend", None)},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes, "d2h_bytes_per_step": 4 * B,
-                    "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4)},
+                    "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4),
+                    "host_launch_ms_per_step": host["launch_ms_per_step"], "host_wait_ms_per_step": host["wait_ms_per_step"]},
             "gpu_launches": int(launches * K),
             "clocks": clocks,
             "ttft_ms_p50": round(ttft[len(ttft) // 2], 2), "tpot_ms_p50": round(step_wall * 1e3, 4),

@@ -324,6 +324,8 @@ class Engine:
         self._need_first = set()        # ids of requests that have not produced a token yet (time to first token)
         self._inflight = None
         # one step ahead of the caller: only with the built-in executor on a GPU (OGB_ENGINE_RUN_AHEAD=0 turns it off)
+        # host time spent planning / packing / enqueueing steps, and time spent waiting for the device to finish one
+        self.host_stats = {"launch_s": 0.0, "wait_s": 0.0, "launches": 0}
         self.run_ahead = (executor is None and model.device.type == "cuda" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
 
     def _blocks_from_memory(self, utilization: float) -> int:
@@ -421,6 +423,14 @@ class Engine:
     def _launch(self):
         """Plans and packs a step and hands it to the executor; leaves it in `_inflight` (with its ids already there
         when the executor is synchronous)."""
+        t0 = time.perf_counter()
+        try:
+            self._launch_inner()
+        finally:
+            self.host_stats["launch_s"] += time.perf_counter() - t0
+            self.host_stats["launches"] += 1
+
+    def _launch_inner(self):
         with _Trace("engine", "launch"):
             plan = self.core.plan()
             self.last_outcome = plan.outcome
@@ -447,11 +457,14 @@ class Engine:
             plan, handle, toks = self._inflight
             self._inflight = None
             if handle is not None:
+                t0 = time.perf_counter()
                 try:
                     toks = self.executor.collect(handle)
                 except Exception as e:
                     self._fail(e)
                     return
+                finally:
+                    self.host_stats["wait_s"] += time.perf_counter() - t0
             now = time.perf_counter()
             if self._need_first or self._guidance:      # steady-state decode has neither: no per-entry work on the host
                 for i, e in enumerate(plan.entries):

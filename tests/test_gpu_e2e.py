@@ -239,6 +239,7 @@ def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_pat
         toks = gc.get_next_tokens()
         forced = np.full((2, 1024), -1e9, dtype=np.float32)
         forced[np.arange(2), toks] = 0
+        gg.get_logits()              # runs the newest token through the model before its logits are replaced
         gg.set_logits(forced)
         gg.generate_next_token()
     lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
@@ -287,6 +288,7 @@ def test_whisper_encoder_decoder_on_gpu_tracks_cpu(tmp_path):
         toks = gc.get_next_tokens()
         forced = np.full((2, 1024), -1e9, dtype=np.float32)
         forced[np.arange(2), toks] = 0
+        gg.get_logits()              # runs the newest token through the model before its logits are replaced
         gg.set_logits(forced)
         gg.generate_next_token()
     lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
