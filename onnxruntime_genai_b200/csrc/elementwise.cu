@@ -207,6 +207,28 @@ __global__ void act_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
   }
 }
 
+// ------------------------------------------------------------------------------------ decode look-ahead
+// Turns the packed inputs of a decode step (one token per request) into those of the next one on the device: the token
+// just sampled becomes the input, position, past length and sampling counter move on by one, and the cache slot of the
+// new position is looked up in the request's block table (which already lists the block of that position).  The engine
+// uses it to enqueue step n + 1 before the ids of step n have reached the host.
+__global__ void decode_advance_kernel(const int32_t* __restrict__ sampled, int32_t* input_ids, int32_t* positions, int32_t* past_lens,
+                                      int32_t* slot_mapping, int32_t* sample_pos, const int32_t* __restrict__ block_table,
+                                      int table_cols, int block_size, int B) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B) return;
+  const int pos = positions[i] + 1;
+  input_ids[i] = sampled[i];
+  positions[i] = pos;
+  past_lens[i] += 1;
+  sample_pos[i] += 1;
+  const int col = pos / block_size;
+  const int blk = col < table_cols ? block_table[size_t(i) * table_cols + col] : -1;
+  slot_mapping[i] = blk < 0 ? -1 : blk * block_size + pos % block_size;
+}
+
 // ------------------------------------------------------------------------------------ logits edits
 // A sparse list of (row, token) edits: op 0 sets the logit to -FLT_MAX (min_length / no-repeat-ngram /
 // banned tokens), op 1 applies the repetition penalty (x < 0 ? x * v : x / v).  O(list) instead of
@@ -310,6 +332,14 @@ OGB_API int ogb_act(const void* x, void* out, long long n, int act, void* stream
   long nb = (nv + 255) / 256; int blocks = int(nb < 148 * 8 ? nb : 148 * 8);
   return launch_pdl(act_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint4*>(x), static_cast<uint4*>(out), nv, act) ? 0 : -4;
+}
+
+OGB_API int ogb_decode_advance(const int32_t* sampled, int32_t* input_ids, int32_t* positions, int32_t* past_lens, int32_t* slot_mapping,
+                               int32_t* sample_pos, const int32_t* block_table, int table_cols, int block_size, int B, void* stream) {
+  if (B <= 0) return 0;
+  if (block_size <= 0 || table_cols <= 0) return -1;
+  return launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), sampled, input_ids,
+                    positions, past_lens, slot_mapping, sample_pos, block_table, table_cols, block_size, B) ? 0 : -4;
 }
 
 OGB_API int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,

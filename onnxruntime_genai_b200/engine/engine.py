@@ -139,6 +139,9 @@ class _Staging:
         self.host = torch.zeros(off, dtype=torch.int32, pin_memory=pin)
         self.dev = torch.zeros(off, dtype=torch.int32, device=device) if pin else self.host
         self.tokens_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        # asynchronous steps land their ids in a ring of pinned buffers (a step's ids are read while the next step runs)
+        self.tokens_ring = [torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
+        self.ring_next = 0
         base = self.host.data_ptr()
         self.addr = {k: base + 4 * o for k, (o, _) in lay.items()}
         if not windowed:
@@ -171,6 +174,7 @@ class ModelExecutor:
         self.graphs: Dict[Any, Any] = {}
         self.windowed = kv.win is not None
         self.graph_launches: Dict[Any, int] = {}
+        self.last_key = None       # graph key of the step enqueued last (None: it did not run from a graph)
 
     def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int) -> StepInputs:
         st = self.staging
@@ -217,6 +221,7 @@ class ModelExecutor:
                 self.graphs[key] = g
             graph, logits = g
             graph.replay()
+            self.last_key = key
             return logits[:B]
         st.upload()
         s = self._step_inputs(T, B, st.table_cols, plan.max_query_len, plan.max_kv_len)
@@ -260,33 +265,56 @@ class ModelExecutor:
             return st.tokens_host[:B].numpy()
         return toks.numpy()
 
+    def _sample_async(self, logits, B: int):
+        st = self.staging
+        toks = ops.sample(logits, st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
+                          st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
+        buf = st.tokens_ring[st.ring_next % len(st.tokens_ring)]
+        st.ring_next += 1
+        buf[:B].copy_(toks, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return ev, B, buf, toks
+
     def execute_async(self, plan, edits=None, masks=None):
         """Enqueues the step (input copy, model, sampler, copy of the ids to pinned memory) and returns a handle for
         `collect`; the host does not wait."""
-        st = self.staging
         B = len(plan.entries)
+        self.last_key = None
         with torch.no_grad():
             logits = self.forward(plan)
             for e in edits or ():
                 ops.logits_edit(logits, *e)
             if masks is not None:
                 ops.logits_bitmask(logits, *masks)
-            toks = ops.sample(logits, st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
-                              st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
-            st.tokens_host[:B].copy_(toks, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-        return ev, B
+            return self._sample_async(logits, B)
+
+    def enqueue_next(self, plan, handle):
+        """Decode look-ahead: enqueues the step that follows `plan` (a graph step whose ids, `handle`, are still on their
+        way) with inputs derived on the device - sampled ids become input ids, positions and cache slots move on by one -
+        and returns its handle, or None when that step cannot reuse the captured graph of this one."""
+        key = self.last_key
+        if key is None or not plan.lookahead_ok or plan.max_kv_len + 1 > key[1] * self.kv.block_size:
+            return None
+        st = self.staging
+        B = len(plan.entries)
+        with torch.no_grad():
+            table = st.view("block_table").view(st.max_batch, st.table_cols)
+            ops.decode_advance(handle[3], st.view("input_ids", B), st.view("positions", B), st.view("past_lens", B),
+                               st.view("slot_mapping", B), st.view("sample_pos", B), table[:B], self.kv.block_size)
+            graph, logits = self.graphs[key]
+            graph.replay()
+            return self._sample_async(logits[:B], B)
 
     def collect(self, handle) -> np.ndarray:
-        ev, B = handle
+        ev, B, buf, _ = handle
         ev.synchronize()
-        return self.staging.tokens_host[:B].numpy().copy()   # the pinned buffer is reused by the step already in flight
+        return buf[:B].numpy().copy()   # the pinned buffer is reused by a later step
 
 
 # ------------------------------------------------------------------------------------------------ engine
 class Engine:
-    def __init__(self, model: Model, executor=None, num_blocks: Optional[int] = None):
+    def __init__(self, model: Model, executor=None, num_blocks: Optional[int] = None, lookahead: Optional[bool] = None):
         self.model = model
         cfg = model.config
         eng = cfg.engine.get("dynamic_batching")
@@ -307,6 +335,15 @@ class Engine:
         windowed = arch.sliding_window > 0 and arch.sliding_layers is not None
         if windowed:
             o.window_size = arch.sliding_window
+        # Decode look-ahead: with the built-in executor on a GPU, pure decode steps are enqueued one step before their
+        # input ids reach the host (OGB_ENGINE_LOOKAHEAD=0 turns it off); the core then also reserves the block of every
+        # request's next position so that the device can compute the next cache slots by itself.
+        # (`lookahead=True` forces it for an executor that has execute_async / enqueue_next / collect.)
+        self.lookahead = (executor is None and model.device.type == "cuda" and not windowed and
+                          os.environ.get("OGB_ENGINE_LOOKAHEAD", "1") != "0" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
+        if lookahead is not None:
+            self.lookahead = bool(lookahead) and not windowed
+        o.lookahead = 1 if self.lookahead else 0
         self.core = native.EngineCore(o)
         self.options = o
         n_win = self.core.ring_blocks_per_request * o.max_batch_size if windowed else 0
@@ -323,10 +360,12 @@ class Engine:
         self._with_processors = set()   # ids of requests with min_length / repetition penalty / no-repeat-ngram
         self._need_first = set()        # ids of requests that have not produced a token yet (time to first token)
         self._inflight = None
+        self._ahead = None              # (signature of the plan it belongs to, handle) of a step enqueued ahead of time
+        self.lookahead_hits = 0
         # one step ahead of the caller: only with the built-in executor on a GPU (OGB_ENGINE_RUN_AHEAD=0 turns it off)
         # host time spent planning / packing / enqueueing steps, and time spent waiting for the device to finish one
         self.host_stats = {"launch_s": 0.0, "wait_s": 0.0, "launches": 0}
-        self.run_ahead = (executor is None and model.device.type == "cuda" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
+        self.run_ahead = (executor is None and model.device.type == "cuda" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0") or self.lookahead
 
     def _blocks_from_memory(self, utilization: float) -> int:
         arch, dec = self.model.arch, self.model.decoder
@@ -406,6 +445,7 @@ class Engine:
             self._finish()
 
     def _fail(self, e: Exception):
+        self._ahead = None      # a step enqueued ahead of the failed one is never used
         if isinstance(e, ExecutionFailure):
             outcome = self.core.abort(e.kind, str(e))
             self.last_outcome = outcome
@@ -442,14 +482,28 @@ class Engine:
             if plan.outcome != StepOutcome.Planned:
                 return
             st = self.staging
+            ahead, self._ahead = self._ahead, None
+            plain = not self._with_processors and not self._guidance
             try:
-                self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
-                edits, masks = self._logits_processors(plan)
-                if self.run_ahead:
-                    self._inflight = (plan, self.executor.execute_async(plan, edits, masks), None)
+                if ahead is not None and plain and ahead[0] == plan.signature:
+                    # this very step is already running: it was enqueued while the previous one was in flight
+                    handle = ahead[1]
+                    self.lookahead_hits += 1
+                    self._inflight = (plan, handle, None)
                 else:
-                    self._inflight = (plan, None, self.executor.execute(plan, edits, masks))
+                    self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
+                    edits, masks = self._logits_processors(plan)
+                    if self.run_ahead:
+                        handle = self.executor.execute_async(plan, edits, masks)
+                        self._inflight = (plan, handle, None)
+                    else:
+                        self._inflight = (plan, None, self.executor.execute(plan, edits, masks))
+                if self.lookahead and plain and plan.lookahead_ok:
+                    nxt = self.executor.enqueue_next(plan, handle)
+                    if nxt is not None:
+                        self._ahead = (plan.next_signature, nxt)
             except Exception as e:
+                self._ahead = None
                 self._fail(e)
 
     def _finish(self):

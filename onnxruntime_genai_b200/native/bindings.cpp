@@ -352,7 +352,8 @@ PYBIND11_MODULE(_og_native, m) {
       .def_readonly("token_count", &StepPlan::token_count).def_readonly("max_query_len", &StepPlan::max_query_len)
       .def_readonly("max_kv_len", &StepPlan::max_kv_len).def_readonly("block_table_columns", &StepPlan::block_table_columns)
       .def_readonly("graph_eligible", &StepPlan::graph_eligible).def_readonly("unserviceable", &StepPlan::unserviceable)
-      .def_readonly("deferred", &StepPlan::deferred)
+      .def_readonly("deferred", &StepPlan::deferred).def_readonly("lookahead_ok", &StepPlan::lookahead_ok)
+      .def_readonly("signature", &StepPlan::signature).def_readonly("next_signature", &StepPlan::next_signature)
       .def_property_readonly("batch", [](const StepPlan& p) { return p.entries.size(); });
 
   py::class_<EngineOptions>(m, "EngineOptions")
@@ -360,7 +361,7 @@ PYBIND11_MODULE(_og_native, m) {
       .def_readwrite("block_size", &EngineOptions::block_size).def_readwrite("num_blocks", &EngineOptions::num_blocks)
       .def_readwrite("max_batch_size", &EngineOptions::max_batch_size)
       .def_readwrite("max_scheduled_tokens", &EngineOptions::max_scheduled_tokens)
-      .def_readwrite("window_size", &EngineOptions::window_size)
+      .def_readwrite("window_size", &EngineOptions::window_size).def_readwrite("lookahead", &EngineOptions::lookahead)
       .def_readwrite("num_window_blocks", &EngineOptions::num_window_blocks)
       .def_readwrite("vocab_size", &EngineOptions::vocab_size).def_readwrite("pad_token_id", &EngineOptions::pad_token_id)
       .def_readwrite("eos_ids", &EngineOptions::eos_ids);

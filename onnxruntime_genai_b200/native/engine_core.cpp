@@ -202,8 +202,15 @@ const StepPlan& EngineCore::Plan() {
       continue;
     }
     Reserved res;
-    const int need = need_total - int(r->blocks_.size());
-    if (need > 0 && !pool_.Reserve(need, res.blocks)) { ++plan_.deferred; continue; }
+    int need = need_total - int(r->blocks_.size());
+    bool reserved = false;
+    if (opt_.lookahead > 0 && !r->prefill_) {
+      // the block of the next positions too (never past max_length or the pool): kept by the request once committed
+      const int ahead = std::min(int(r->tokens_.size()) + opt_.lookahead, std::max(r->opt_.max_length, int(r->tokens_.size())));
+      const int want = std::min(BlocksFor(ahead), pool_.Total()) - int(r->blocks_.size());
+      if (want > need) reserved = pool_.Reserve(want, res.blocks);
+    }
+    if (!reserved && need > 0 && !pool_.Reserve(need, res.blocks)) { ++plan_.deferred; continue; }
     if (wpool_) {
       const int wneed = ring_blocks_ - int(r->window_blocks_.size());
       if (wneed > 0 && !wpool_->Reserve(wneed, res.wblocks)) {
@@ -249,6 +256,20 @@ const StepPlan& EngineCore::Plan() {
 
   int off = 0;
   plan_.graph_eligible = true;
+  plan_.lookahead_ok = opt_.lookahead > 0 && !wpool_;
+  uint64_t sig = 1469598103934665603ull, nsig = 1469598103934665603ull;
+  auto mix = [](uint64_t h, uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); return h * 1099511628211ull; };
+  for (size_t i = 0; i < plan_.entries.size(); ++i) {
+    const PlanEntry& e = plan_.entries[i];
+    const Request& r = *e.request;
+    sig = mix(mix(sig, r.id_), uint64_t(e.processed_before));
+    nsig = mix(mix(nsig, r.id_), uint64_t(e.processed_before + 1));
+    const int owned = int(r.blocks_.size() + reserved_[i].blocks.size());
+    plan_.lookahead_ok = plan_.lookahead_ok && !e.is_prefill && e.num_tokens == 1 && int(r.tokens_.size()) + 1 < r.opt_.max_length &&
+                         owned >= BlocksFor(int(r.tokens_.size()) + 1);
+  }
+  plan_.signature = sig;
+  plan_.next_signature = nsig;
   for (auto& e : plan_.entries) {
     e.packed_offset = off;
     e.logits_row = off + e.num_tokens - 1;
@@ -303,7 +324,8 @@ void EngineCore::Pack(const PackBuffers& buf) const {
     buf.cu_seqlens[i + 1] = e.packed_offset + e.num_tokens;
     buf.past_lens[i] = e.processed_before;
     buf.logits_rows[i] = e.logits_row;
-    const int used_cols = BlocksFor(e.processed_before + e.num_tokens);
+    // with look-ahead the table also shows the block of the next positions (block_at gives -1 where none is owned)
+    const int used_cols = std::min(cols, BlocksFor(e.processed_before + e.num_tokens + (e.is_prefill ? 0 : opt_.lookahead)));
     for (int c = 0; c < cols; ++c) buf.block_table[size_t(i) * cols + c] = c < used_cols ? block_at(c) : -1;
     if (buf.block_table_w && wpool_)
       for (int c = 0; c < cols; ++c) buf.block_table_w[size_t(i) * cols + c] = c < used_cols ? wblock_at(c % ring_blocks_) : -1;

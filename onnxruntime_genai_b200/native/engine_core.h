@@ -149,6 +149,12 @@ struct StepPlan {
   int max_kv_len{0};
   int block_table_columns{0};  // exact number of columns needed
   bool graph_eligible{false};  // every entry is a 1-token decode
+  // Decode look-ahead (EngineOptions::lookahead): the executor may enqueue the step after this one before this step's
+  // tokens reach the host.  lookahead_ok: every entry is a 1-token decode that stays below its max_length and owns the
+  // block its next position falls in.  signature identifies (request, position) of every entry in order;
+  // next_signature is the signature the following plan has if the same requests simply advance by one token.
+  bool lookahead_ok{false};
+  uint64_t signature{0}, next_signature{0};
   std::vector<std::shared_ptr<Request>> unserviceable;
   int deferred{0};
 };
@@ -158,6 +164,7 @@ struct EngineOptions {
   int num_blocks{0};
   int max_batch_size{16};
   int max_scheduled_tokens{2048};
+  int lookahead{0};           // decode entries also reserve the block of their next `lookahead` positions
   int window_size{0};         // > 0 enables the sliding-window ring pool
   int num_window_blocks{0};   // blocks in the windowed pool
   int vocab_size{0};

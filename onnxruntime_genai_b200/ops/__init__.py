@@ -218,6 +218,26 @@ def act_mul(x, act="silu"):
     return out
 
 
+def decode_advance(sampled, input_ids, positions, past_lens, slot_mapping, sample_pos, block_table, block_size: int):
+    """In place: the packed inputs of a one-token-per-request step become those of the next step (see
+    csrc/elementwise.cu::decode_advance_kernel).  block_table [B, cols] int32, everything else [B] int32."""
+    B = sampled.shape[0]
+    if not sampled.is_cuda:
+        pos = positions[:B] + 1
+        input_ids[:B] = sampled
+        positions[:B] = pos
+        past_lens[:B] += 1
+        sample_pos[:B] += 1
+        col = (pos // block_size).long()
+        blk = torch.where(col < block_table.shape[1], block_table[torch.arange(B), col.clamp(max=block_table.shape[1] - 1)], torch.full_like(pos, -1))
+        slot_mapping[:B] = torch.where(blk < 0, torch.full_like(pos, -1), blk * block_size + pos % block_size)
+        return
+    assert block_table.stride(1) == 1
+    _lib.check(_lib.lib().ogb_decode_advance(_ptr(sampled), _ptr(input_ids), _ptr(positions), _ptr(past_lens), _ptr(slot_mapping),
+                                            _ptr(sample_pos), _ptr(block_table), block_table.stride(0), int(block_size), B, _stream()),
+               "decode_advance")
+
+
 def activation(x, act="gelu"):
     """Elementwise activation of a bf16 tensor (the fc1 -> act -> fc2 MLPs of phi and gpt2)."""
     if not x.is_cuda:

@@ -355,3 +355,113 @@ def test_sampling_args_resolution():
     assert k == -1 and abs(p - 0.9) < 1e-6 and abs(t - 0.7) < 1e-6
     o.top_k = 1
     assert o.resolve() == (1, 0.0, 1.0)
+
+
+# ------------------------------------------------------------------------------------------------ decode look-ahead
+class AheadExecutor(ClosedFormExecutor):
+    """The asynchronous executor seam with a stand-in for the device: `enqueue_next` computes the following step from the
+    PREVIOUS handle's ids and its own copy of positions (never from the requests, whose new ids have not been committed
+    yet), as the device-side advance does."""
+
+    def __init__(self):
+        super().__init__()
+        self.ahead_calls = 0
+
+    def execute_async(self, plan, edits=None, masks=None):
+        toks = self.execute(plan, edits, masks)
+        state = None
+        if plan.graph_eligible:
+            state = [(int(e.request.tokens()[0]), e.processed_before + 1) for e in plan.entries]   # (first token, length after)
+        return {"toks": toks, "state": state}
+
+    def enqueue_next(self, plan, handle):
+        if handle["state"] is None or not plan.lookahead_ok:
+            return None
+        self.ahead_calls += 1
+        toks, state = [], []
+        for (first, length), cur in zip(handle["state"], handle["toks"].tolist()):
+            toks.append((first + cur + length + 1) % VOCAB)
+            state.append((first, length + 1))
+        return {"toks": np.asarray(toks, dtype=np.int32), "state": state}
+
+    def collect(self, handle):
+        return handle["toks"]
+
+
+def test_lookahead_steps_match_the_synchronous_engine(model):
+    prompts = [[5, 9, 2], [7], [11, 3, 4, 8, 15, 16, 23], [2, 2]]
+    sync, _ = make_engine(model)
+    sreqs = [request(model, p, max_length=30 + i) for i, p in enumerate(prompts)]
+    for r in sreqs:
+        sync.add_request(r)
+    want = run_all(sync, sreqs)
+    ex = AheadExecutor()
+    engine = Engine(model, executor=ex, lookahead=True)
+    assert engine.options.lookahead == 1
+    reqs = [request(model, p, max_length=30 + i) for i, p in enumerate(prompts)]
+    for r in reqs[:3]:
+        engine.add_request(r)
+    outs = {id(r): [] for r in reqs}
+    steps = 0
+    while engine.has_pending_requests():
+        steps += 1
+        assert steps < 2000
+        if steps == 9:
+            engine.add_request(reqs[3])          # a new request arrives while a step enqueued ahead is pending: it is dropped
+        r = engine.step()
+        if r is None:
+            continue
+        while r.has_unseen_tokens():
+            outs[id(r)].append(r.get_unseen_token())
+        if r.is_turn_complete():
+            engine.remove_request(r)
+    assert [outs[id(r)] for r in reqs] == want
+    assert engine.lookahead_hits > 10 and ex.ahead_calls >= engine.lookahead_hits
+    engine.core.check_invariants()
+    assert engine.core.free_blocks == engine.options.num_blocks
+
+
+def test_lookahead_plan_reserves_the_next_block_and_predicts_the_next_signature():
+    o = native.EngineOptions()
+    o.block_size, o.num_blocks, o.max_batch_size, o.max_scheduled_tokens, o.vocab_size, o.eos_ids, o.lookahead = 4, 16, 4, 16, VOCAB, [EOS], 1
+    core = native.EngineCore(o)
+    ro = native.RequestOptions()
+    ro.max_length = 12
+    r = core.create_request(ro)
+    r.add_tokens(np.asarray([3, 4, 5], dtype=np.int32))
+    core.add_request(r)
+    plan = core.plan()                               # prefill of 3 tokens: no look-ahead for prefill entries
+    assert not plan.lookahead_ok and plan.entries[0].is_prefill
+    core.commit(np.asarray([7], dtype=np.int32))
+    held = lambda: o.num_blocks - core.free_blocks
+    assert held() == 1
+    plan = core.plan()                               # decode of token 4 (position 3): position 4 opens block 1 -> reserved now
+    assert plan.lookahead_ok and plan.graph_eligible
+    nxt = plan.next_signature
+    core.commit(np.asarray([8], dtype=np.int32))
+    assert held() == 2
+    plan = core.plan()
+    assert plan.signature == nxt and plan.lookahead_ok
+    core.commit(np.asarray([9], dtype=np.int32))
+    # a different request set gives a different signature
+    r2 = core.create_request(ro)
+    r2.add_tokens(np.asarray([1, 2], dtype=np.int32))
+    core.add_request(r2)
+    nxt = plan.next_signature
+    plan = core.plan()
+    assert plan.signature != nxt and not plan.lookahead_ok
+    core.abort(native.FailureKind.RetryableBeforeExecution, "test")
+    core.check_invariants()
+
+
+def test_decode_advance_reference():
+    import torch
+    from onnxruntime_genai_b200 import ops
+    table = torch.tensor([[5, 9, -1], [2, 7, 3]], dtype=torch.int32)
+    ids, pos = torch.tensor([1, 2], dtype=torch.int32), torch.tensor([3, 7], dtype=torch.int32)
+    past, slots, spos = pos.clone(), torch.tensor([5 * 4 + 3, 7 * 4 + 3], dtype=torch.int32), torch.tensor([4, 8], dtype=torch.int32)
+    ops.decode_advance(torch.tensor([40, 41], dtype=torch.int32), ids, pos, past, slots, spos, table, 4)
+    assert ids.tolist() == [40, 41] and pos.tolist() == [4, 8] and past.tolist() == [4, 8] and spos.tolist() == [5, 9]
+    assert slots.tolist() == [9 * 4 + 0, 3 * 4 + 0]
+    ops.decode_advance(torch.tensor([1, 1], dtype=torch.int32), ids, pos, past, slots, spos, table[:, :2], 4)
+    assert slots.tolist() == [9 * 4 + 1, -1]       # position 9 lies in column 2, which this table does not have

@@ -203,11 +203,16 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
         return [outs[id(r)] for r in reqs]
 
     ahead = og.Engine(model)
-    assert ahead.run_ahead
+    assert ahead.run_ahead and ahead.lookahead
     a = run(ahead)                      # every request admitted before the first model step: identical batches in both engines
+    assert ahead.lookahead_hits >= 10, "pure decode steps must be enqueued before the previous step's ids reach the host"
+    monkeypatch.setenv("OGB_ENGINE_LOOKAHEAD", "0")
+    one = og.Engine(model)
+    assert one.run_ahead and not one.lookahead
+    assert run(one) == a and one.lookahead_hits == 0
     monkeypatch.setenv("OGB_ENGINE_RUN_AHEAD", "0")
     sync = og.Engine(model)
-    assert not sync.run_ahead
+    assert not sync.run_ahead and not sync.lookahead
     b = run(sync)
     ops.check_kernel_status()
     assert all(0 < len(x) <= 24 for x in a) and max(len(x) for x in a) == 24

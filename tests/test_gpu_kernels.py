@@ -251,6 +251,24 @@ def test_embedding_gather_actmul_cast():
     assert torch.equal(ops.to_float32(x), x.float())
 
 
+def test_decode_advance_matches_reference():
+    rng = np.random.RandomState(3)
+    B, cols, bs = 37, 9, 16
+    table = torch.from_numpy(rng.randint(0, 500, size=(B, cols)).astype(np.int32))
+    table[::5, 6:] = -1
+    pos = torch.from_numpy(rng.randint(0, cols * bs - 1, size=(B,)).astype(np.int32))
+    fields = [torch.from_numpy(rng.randint(0, 1000, size=(B,)).astype(np.int32)) for _ in range(4)]   # ids, past, slots, sample_pos
+    sampled = torch.from_numpy(rng.randint(0, 32000, size=(B,)).astype(np.int32))
+    cpu = [f.clone() for f in (fields[0], pos, fields[1], fields[2], fields[3])]
+    gpu = [f.clone().to(DEV) for f in (fields[0], pos, fields[1], fields[2], fields[3])]
+    ops.decode_advance(sampled, *cpu, table, bs)
+    big = torch.full((64, cols + 3), -7, dtype=torch.int32, device=DEV)      # a strided view, as in the engine's staging buffer
+    big[:B, :cols] = table.to(DEV)
+    ops.decode_advance(sampled.to(DEV), *gpu, big[:B, :cols], bs)
+    for a, b in zip(cpu, gpu):
+        assert torch.equal(a, b.cpu())
+
+
 # ------------------------------------------------------------------------------------------- attention
 def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, softcap=0.0, splits=None, seed=30):
     rng = np.random.RandomState(seed)
