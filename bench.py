@@ -266,7 +266,8 @@ def ours(args):
                        "tp_backend": getattr(tp, "backend", None)},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4),
-                    "host_launch_ms_per_step": host["launch_ms_per_step"], "host_wait_ms_per_step": host["wait_ms_per_step"]},
+                    "host_launch_ms_per_step": host["launch_ms_per_step"], "host_wait_ms_per_step": host["wait_ms_per_step"],
+                    "steps_enqueued_ahead": int(engine.lookahead_hits)},
             "gpu_launches": int(launches * K),
             "clocks": clocks,
             "ttft_ms_p50": round(ttft[len(ttft) // 2], 2), "tpot_ms_p50": round(step_wall * 1e3, 4),

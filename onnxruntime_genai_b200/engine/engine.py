@@ -136,16 +136,28 @@ class _Staging:
             add("block_table_w", max_batch * table_cols)
         self.layout, self.words = lay, off
         pin = device.type == "cuda"
-        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=pin)
+        # Two pinned host images used in turn: with decode look-ahead the copy of one step's inputs may still be queued
+        # behind the running step when the host packs the next one.
+        self._hosts = [torch.zeros(off, dtype=torch.int32, pin_memory=pin) for _ in range(2 if pin else 1)]
+        self._addrs = []
+        self.host = self._hosts[0]
         self.dev = torch.zeros(off, dtype=torch.int32, device=device) if pin else self.host
         self.tokens_host = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
         # asynchronous steps land their ids in a ring of pinned buffers (a step's ids are read while the next step runs)
         self.tokens_ring = [torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
         self.ring_next = 0
-        base = self.host.data_ptr()
-        self.addr = {k: base + 4 * o for k, (o, _) in lay.items()}
-        if not windowed:
-            self.addr.pop("slot_mapping_w", None)
+        for h in self._hosts:
+            a = {k: h.data_ptr() + 4 * o for k, (o, _) in lay.items()}
+            if not windowed:
+                a.pop("slot_mapping_w", None)
+            self._addrs.append(a)
+        self.addr = self._addrs[0]
+        self._cur = 0
+
+    def flip(self):
+        """Switches to the other pinned host image (call before packing a step)."""
+        self._cur = (self._cur + 1) % len(self._hosts)
+        self.host, self.addr = self._hosts[self._cur], self._addrs[self._cur]
 
     def view(self, name, n=None, dtype=torch.int32, host=False):
         o, w = self.layout[name]
@@ -198,26 +210,10 @@ class ModelExecutor:
         B, T = len(plan.entries), plan.token_count
         st = self.staging
         if self.use_graphs and plan.graph_eligible:
-            bb = min(self._bucket(B), st.max_batch)
-            cb = min(self._bucket(plan.block_table_columns, 8), st.table_cols)
-            key = (bb, cb)
-            if bb > B:  # padded rows: zero-length requests that append nothing
-                h = st.host
-                o, _ = st.layout["cu_seqlens"]
-                h[o + B + 1:o + bb + 1] = int(h[o + B])
-                for f, val in (("past_lens", 0), ("logits_rows", 0)):
-                    o, _ = st.layout[f]
-                    h[o + B:o + bb] = val
-                for f, val in (("input_ids", 0), ("positions", 0), ("slot_mapping", -1)):
-                    o, _ = st.layout[f]
-                    h[o + T:o + bb] = val
-                if self.windowed:
-                    o, _ = st.layout["slot_mapping_w"]
-                    h[o + T:o + bb] = -1
-            st.upload()
+            key = self.upload_graph_inputs(plan)
             g = self.graphs.get(key)
             if g is None:
-                g = self._capture(bb, cb)
+                g = self._capture(*key)
                 self.graphs[key] = g
             graph, logits = g
             graph.replay()
@@ -226,6 +222,30 @@ class ModelExecutor:
         st.upload()
         s = self._step_inputs(T, B, st.table_cols, plan.max_query_len, plan.max_kv_len)
         return self.decoder.forward(s, self.kv)
+
+    def upload_graph_inputs(self, plan):
+        """Pads the packed inputs of a one-token-per-request step to the graph's batch bucket, copies them to the device
+        and returns the graph key (batch bucket, block-table column bucket)."""
+        B, T = len(plan.entries), plan.token_count
+        st = self.staging
+        bb = min(self._bucket(B), st.max_batch)
+        cb = min(self._bucket(plan.block_table_columns, 8), st.table_cols)
+        key = (bb, cb)
+        if bb > B:  # padded rows: zero-length requests that append nothing
+            h = st.host
+            o, _ = st.layout["cu_seqlens"]
+            h[o + B + 1:o + bb + 1] = int(h[o + B])
+            for f, val in (("past_lens", 0), ("logits_rows", 0)):
+                o, _ = st.layout[f]
+                h[o + B:o + bb] = val
+            for f, val in (("input_ids", 0), ("positions", 0), ("slot_mapping", -1)):
+                o, _ = st.layout[f]
+                h[o + T:o + bb] = val
+            if self.windowed:
+                o, _ = st.layout["slot_mapping_w"]
+                h[o + T:o + bb] = -1
+        st.upload()
+        return key
 
     def _capture(self, bb: int, cb: int):
         st = self.staging
@@ -294,7 +314,7 @@ class ModelExecutor:
         way) with inputs derived on the device - sampled ids become input ids, positions and cache slots move on by one -
         and returns its handle, or None when that step cannot reuse the captured graph of this one."""
         key = self.last_key
-        if key is None or not plan.lookahead_ok or plan.max_kv_len + 1 > key[1] * self.kv.block_size:
+        if key is None or key not in self.graphs or not plan.lookahead_ok or plan.max_kv_len + 1 > key[1] * self.kv.block_size:
             return None
         st = self.staging
         B = len(plan.entries)
@@ -305,6 +325,10 @@ class ModelExecutor:
             graph, logits = self.graphs[key]
             graph.replay()
             return self._sample_async(logits[:B], B)
+
+    def refresh_inputs(self, plan):
+        """Copies the packed inputs of a step that was enqueued ahead of time (see Engine._launch_inner)."""
+        self.last_key = self.upload_graph_inputs(plan)
 
     def collect(self, handle) -> np.ndarray:
         ev, B, buf, _ = handle
@@ -485,11 +509,16 @@ class Engine:
             ahead, self._ahead = self._ahead, None
             plain = not self._with_processors and not self._guidance
             try:
+                st.flip()
                 if ahead is not None and plain and ahead[0] == plan.signature:
-                    # this very step is already running: it was enqueued while the previous one was in flight
+                    # This very step is already running: it was enqueued while the previous one was in flight.  Its packed
+                    # inputs are copied to the device all the same (behind the running kernels, which read identical values):
+                    # they carry the block-table columns that the step after this one needs.
                     handle = ahead[1]
                     self.lookahead_hits += 1
                     self._inflight = (plan, handle, None)
+                    self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
+                    self.executor.refresh_inputs(plan)
                 else:
                     self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
                     edits, masks = self._logits_processors(plan)

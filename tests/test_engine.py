@@ -384,6 +384,9 @@ class AheadExecutor(ClosedFormExecutor):
             state.append((first, length + 1))
         return {"toks": np.asarray(toks, dtype=np.int32), "state": state}
 
+    def refresh_inputs(self, plan):
+        self.refreshed = getattr(self, "refreshed", 0) + 1      # the device copy of the inputs of a step that is already running
+
     def collect(self, handle):
         return handle["toks"]
 
@@ -416,7 +419,7 @@ def test_lookahead_steps_match_the_synchronous_engine(model):
         if r.is_turn_complete():
             engine.remove_request(r)
     assert [outs[id(r)] for r in reqs] == want
-    assert engine.lookahead_hits > 10 and ex.ahead_calls >= engine.lookahead_hits
+    assert engine.lookahead_hits > 10 and ex.ahead_calls >= engine.lookahead_hits and ex.refreshed == engine.lookahead_hits
     engine.core.check_invariants()
     assert engine.core.free_blocks == engine.options.num_blocks
 
