@@ -187,6 +187,7 @@ class ModelExecutor:
         self.windowed = kv.win is not None
         self.graph_launches: Dict[Any, int] = {}
         self.last_key = None       # graph key of the step enqueued last (None: it did not run from a graph)
+        self._unsplit: Dict[int, bool] = {}
 
     def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int) -> StepInputs:
         st = self.staging
@@ -230,6 +231,14 @@ class ModelExecutor:
         st = self.staging
         bb = min(self._bucket(B), st.max_batch)
         cb = min(self._bucket(plan.block_table_columns, 8), st.table_cols)
+        if bb not in self._unsplit:
+            # The column bucket only bounds the key range that the attention launch splits; a batch large enough to fill the
+            # GPU without splitting has one graph for every length (no capture in the middle of a long decode).  Not for
+            # long-context RoPE models, whose step bound also selects the cache pair.
+            dec = self.decoder
+            self._unsplit[bb] = dec.cos_small is None and ops.choose_kv_splits(bb, dec.kv_heads_local, 1, 1 << 24, group=dec.heads_local // dec.kv_heads_local)[0] == 1
+        if self._unsplit[bb]:
+            cb = st.table_cols
         key = (bb, cb)
         if bb > B:  # padded rows: zero-length requests that append nothing
             h = st.host
