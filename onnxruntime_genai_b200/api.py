@@ -259,7 +259,7 @@ class SequenceState:
         self.blocks_per_row = (max_length + block_size - 1) // block_size
         dev = decoder.device
         self.kv = PagedKVCache(decoder.arch, rows * self.blocks_per_row, block_size, dev, decoder.dtype,
-                               kv_heads=decoder.kv_heads_local)
+                               kv_heads=decoder.kv_heads_local, conv_channels=decoder.conv_channels_local)
         self.block_table = (torch.arange(rows * self.blocks_per_row, dtype=torch.int32).view(rows, self.blocks_per_row)).to(dev)
         self.kv_len = [0] * rows
         # Beam search shares cache blocks between rows (copy-on-write at block granularity).  Until the first reorder every
@@ -439,6 +439,8 @@ class SequenceState:
             ar = torch.arange(bs, device=dev)
             s_idx, d_idx = (src[:, None] * bs + ar).reshape(-1), (dst[:, None] * bs + ar).reshape(-1)
             self.kv.full[:, :, d_idx] = self.kv.full[:, :, s_idx]
+            if self.kv.conv is not None:
+                self.kv.conv[:, d_idx] = self.kv.conv[:, s_idx]
             self._moves = []
         if self._tbl_dirty:
             self.block_table.copy_(torch.from_numpy(self._tbl))

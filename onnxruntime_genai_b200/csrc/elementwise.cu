@@ -207,6 +207,75 @@ __global__ void act_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
   }
 }
 
+// ------------------------------------------------------------------------------------ gated short convolution
+// Hybrid (LFM2) layers: y[t] = c[t] * sum_{k < L} w[:, L-1-k] * (b*x)[pos(t) - k] (+ bias), channels independent.
+// The product b*x of every position lives in a paged cache addressed like the key/value cache ([slots, C]); a token
+// writes its own entry and reads the entries of the L-1 positions before it: from the packed input when that position
+// belongs to this step (another CTA may not have written it yet), otherwise from the cache through the block table.
+// One CTA per token, eight channels per thread.
+struct ShortConvParams {
+  const uint4* bcx; int bcx_stride;       // [T, 3C] bf16, stride in elements
+  const __nv_bfloat16* weight;            // [C, L]
+  const __nv_bfloat16* bias;              // [C] or null
+  uint4* cache;                           // [slots, C]
+  const int32_t* slots; const int32_t* positions; const int32_t* cu_seqlens; const int32_t* past_lens;
+  const int32_t* block_table; int table_cols, block_size;
+  uint4* out;                             // [T, C]
+  int T, B, C, L;
+};
+
+__global__ void __launch_bounds__(256) short_conv_kernel(ShortConvParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  // the request this token belongs to: last r with cu_seqlens[r] <= t
+  int lo = 0, hi = p.B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (p.cu_seqlens[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int r = lo, pos = p.positions[t], past = p.past_lens[r], t0 = p.cu_seqlens[r];
+  const int slot = p.slots[t];
+  const int nvec = p.C / 8;
+  const int32_t* table = p.block_table + size_t(r) * p.table_cols;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = p.bias ? bf2f(p.bias[v * 8 + j]) : 0.f;
+    uint4 mine = make_uint4(0, 0, 0, 0);
+    for (int k = 0; k < p.L; ++k) {
+      const int q = pos - k;
+      if (q < 0) break;
+      uint4 e;
+      if (q >= past) {
+        // produced in this step by token t0 + (q - past): recompute b * x from the packed input
+        const uint4* row = p.bcx + size_t(t0 + (q - past)) * (p.bcx_stride / 8);
+        const uint4 bb = row[v], xx = row[2 * nvec + v];
+        const __nv_bfloat16* be = reinterpret_cast<const __nv_bfloat16*>(&bb);
+        const __nv_bfloat16* xe = reinterpret_cast<const __nv_bfloat16*>(&xx);
+        __nv_bfloat16* ee = reinterpret_cast<__nv_bfloat16*>(&e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ee[j] = f2bf(bf2f(be[j]) * bf2f(xe[j]));
+        if (k == 0) mine = e;
+      } else {
+        const int blk = table[q / p.block_size];
+        e = p.cache[(size_t(blk) * p.block_size + q % p.block_size) * nvec + v];
+      }
+      const __nv_bfloat16* ee = reinterpret_cast<const __nv_bfloat16*>(&e);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += bf2f(p.weight[size_t(v * 8 + j) * p.L + (p.L - 1 - k)]) * bf2f(ee[j]);
+    }
+    if (slot >= 0) p.cache[size_t(slot) * nvec + v] = mine;
+    const uint4 cc = (p.bcx + size_t(t) * (p.bcx_stride / 8))[nvec + v];
+    const __nv_bfloat16* ce = reinterpret_cast<const __nv_bfloat16*>(&cc);
+    uint4 o;
+    __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = f2bf(bf2f(ce[j]) * acc[j]);
+    p.out[size_t(t) * nvec + v] = o;
+  }
+}
+
 // ------------------------------------------------------------------------------------ decode look-ahead
 // Turns the packed inputs of a decode step (one token per request) into those of the next one on the device: the token
 // just sampled becomes the input, position, past length and sampling counter move on by one, and the cache slot of the
@@ -332,6 +401,21 @@ OGB_API int ogb_act(const void* x, void* out, long long n, int act, void* stream
   long nb = (nv + 255) / 256; int blocks = int(nb < 148 * 8 ? nb : 148 * 8);
   return launch_pdl(act_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const uint4*>(x), static_cast<uint4*>(out), nv, act) ? 0 : -4;
+}
+
+OGB_API int ogb_short_conv(const void* bcx, int bcx_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
+                           const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                           int table_cols, int block_size, void* out, int T, int B, int C, int L, void* stream) {
+  if (T <= 0) return 0;
+  if (B <= 0 || (C % 8) || (bcx_stride % 8) || L < 1 || L > 16 || block_size <= 0) return -1;
+  ShortConvParams p;
+  p.bcx = static_cast<const uint4*>(bcx); p.bcx_stride = bcx_stride;
+  p.weight = static_cast<const __nv_bfloat16*>(weight); p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.cache = static_cast<uint4*>(cache); p.slots = slots; p.positions = positions; p.cu_seqlens = cu_seqlens; p.past_lens = past_lens;
+  p.block_table = block_table; p.table_cols = table_cols; p.block_size = block_size; p.out = static_cast<uint4*>(out);
+  p.T = T; p.B = B; p.C = C; p.L = L;
+  const int threads = min(256, max(32, (C / 8 + 31) / 32 * 32));
+  return launch_pdl(short_conv_kernel, dim3(T), dim3(threads), 0, static_cast<cudaStream_t>(stream), p) ? 0 : -4;
 }
 
 OGB_API int ogb_decode_advance(const int32_t* sampled, int32_t* input_ids, int32_t* positions, int32_t* past_lens, int32_t* slot_mapping,

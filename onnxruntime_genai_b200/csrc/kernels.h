@@ -59,6 +59,9 @@ int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, cons
                        float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream);
 int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream);
 int ogb_act(const void* x, void* out, long long n, int act, void* stream);
+int ogb_short_conv(const void* bcx, int bcx_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
+                   const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                   int table_cols, int block_size, void* out, int T, int B, int C, int L, void* stream);
 int ogb_decode_advance(const int32_t* sampled, int32_t* input_ids, int32_t* positions, int32_t* past_lens, int32_t* slot_mapping,
                        int32_t* sample_pos, const int32_t* block_table, int table_cols, int block_size, int B, void* stream);
 int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t* tokens, const int32_t* ops,

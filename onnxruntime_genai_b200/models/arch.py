@@ -59,6 +59,11 @@ class ArchConfig:
     # MLP
     mlp_bias: bool = False
     activation: str = "silu"         # silu | gelu
+    # Hybrid models (LFM2): layers of type "conv" replace attention by a gated short depthwise convolution over the last
+    # conv_L_cache positions; "full_attention" layers are ordinary attention layers.  None: every layer attends.
+    layer_types: Optional[List[str]] = None
+    conv_L_cache: int = 3
+    conv_bias: bool = False
     cross_attention: bool = False    # encoder-decoder (whisper): every layer also attends to the encoder's output
     encoder_hidden_size: int = 0     # width of the encoder output the cross-attention keys / values are projected from (0 = hidden_size)
     mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
@@ -98,6 +103,9 @@ class ArchConfig:
     @property
     def scale(self) -> float:
         return self.attn_scale if self.attn_scale is not None else 1.0 / math.sqrt(self.head_dim)
+
+    def is_conv_layer(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] == "conv"
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window <= 0:
@@ -195,6 +203,14 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.attn_bias = a.o_bias = a.mlp_bias = a.lm_head_bias = True
         a.mlp_gated = False
         a.parallel_block = True
+    if mt == "lfm2":
+        a.layer_types = list(cfg.get("layer_types") or ["full_attention"] * a.num_layers)
+        a.conv_L_cache = int(cfg.get("conv_L_cache", 3))
+        a.conv_bias = bool(cfg.get("conv_bias", False))
+        a.qk_norm = True
+        a.norm_eps = cfg.get("norm_eps", a.norm_eps)
+        a.intermediate_size = cfg.get("block_ff_dim", a.intermediate_size) if not cfg.get("intermediate_size") else a.intermediate_size
+        a.tie_embeddings = bool(cfg.get("tie_embedding", cfg.get("tie_word_embeddings", True)))
     if mt == "gpt2":
         a.layernorm = True
         a.activation = "gelu"

@@ -57,16 +57,23 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
         if arch.post_sublayer_norms:
             s[p + "pre_feedforward_layernorm.weight"] = (H,)
             s[p + "post_feedforward_layernorm.weight"] = (H,)
-        s[p + "self_attn.q_proj.weight"] = (arch.q_size, H)
-        s[p + "self_attn.k_proj.weight"] = (arch.kv_size, H)
-        s[p + "self_attn.v_proj.weight"] = (arch.kv_size, H)
-        s[p + "self_attn.o_proj.weight"] = (H, arch.q_size)
-        if arch.attn_bias:
-            s[p + "self_attn.q_proj.bias"] = (arch.q_size,)
-            s[p + "self_attn.k_proj.bias"] = (arch.kv_size,)
-            s[p + "self_attn.v_proj.bias"] = (arch.kv_size,)
-        if arch.o_bias:
-            s[p + "self_attn.o_proj.bias"] = (H,)
+        if arch.is_conv_layer(i):
+            s[p + "conv.in_proj.weight"] = (3 * H, H)
+            s[p + "conv.conv.weight"] = (H, arch.conv_L_cache)
+            if arch.conv_bias:
+                s[p + "conv.conv.bias"] = (H,)
+            s[p + "conv.out_proj.weight"] = (H, H)
+        else:
+            s[p + "self_attn.q_proj.weight"] = (arch.q_size, H)
+            s[p + "self_attn.k_proj.weight"] = (arch.kv_size, H)
+            s[p + "self_attn.v_proj.weight"] = (arch.kv_size, H)
+            s[p + "self_attn.o_proj.weight"] = (H, arch.q_size)
+            if arch.attn_bias:
+                s[p + "self_attn.q_proj.bias"] = (arch.q_size,)
+                s[p + "self_attn.k_proj.bias"] = (arch.kv_size,)
+                s[p + "self_attn.v_proj.bias"] = (arch.kv_size,)
+            if arch.o_bias:
+                s[p + "self_attn.o_proj.bias"] = (H,)
         if arch.cross_attention:
             s[p + "cross_attn_layernorm.weight"] = (H,)
             if arch.layernorm:
@@ -75,7 +82,7 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
                             ("v", (arch.q_size, arch.encoder_hidden_size or H)), ("o", (H, arch.q_size))):
                 s[p + f"cross_attn.{nm}_proj.weight"] = shp
                 s[p + f"cross_attn.{nm}_proj.bias"] = (shp[0],)
-        if arch.qk_norm:
+        if arch.qk_norm and not arch.is_conv_layer(i):
             s[p + "self_attn.q_norm.weight"] = (arch.head_dim,)
             s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
         if arch.attn_sinks:
@@ -389,49 +396,68 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                **({"axis": -1, "stash_type": 1} if residual is None else {}))
         residual = hidden if residual is None else f"{n}/input_layernorm/output_3"
         x = f"{n}/input_layernorm/output_0"
-        # attention
-        qkv_out = f"{n}/attn/qkv_proj/MatMul/output_0"
-        put_linear(p + "attn.qkv_proj", f"{n}/attn/qkv_proj/MatMul",
-                   [p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"], x, qkv_out,
-                   arch.q_size + 2 * arch.kv_size, H)
-        if arch.attn_bias:
-            put_vec(p + "attn.qkv_proj.Add.bias", [p + "self_attn.q_proj.bias", p + "self_attn.k_proj.bias", p + "self_attn.v_proj.bias"])
-            W.node("Add", f"{n}/attn/qkv_proj/Add", [qkv_out, p + "attn.qkv_proj.Add.bias"], [f"{n}/attn/qkv_proj/Add/output_0"])
-            qkv_out = f"{n}/attn/qkv_proj/Add/output_0"
-        attn_inputs = [qkv_out, "", ""]
-        if paged:
-            attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "cumulative_sequence_lengths",
-                            "past_sequence_lengths", "block_table_windowed" if arch.layer_window(i) else "block_table",
-                            "cos_cache", "sin_cache", ""]
+        if arch.is_conv_layer(i):
+            # hybrid (LFM2) layer: in_proj -> (b, c, x); depthwise convolution of b * x over the last conv_L_cache positions
+            # (state input past_conv.N / output present_conv.N); c * conv -> out_proj
+            Lc = arch.conv_L_cache
+            put_linear(p + "conv.in_proj", f"{n}/conv/in_proj/MatMul", [p + "conv.in_proj.weight"], x, f"{n}/conv/in_proj/MatMul/output_0", 3 * H, H)
+            W.node("Split", f"{n}/conv/Split", [f"{n}/conv/in_proj/MatMul/output_0"], [f"{n}/conv/b", f"{n}/conv/c", f"{n}/conv/x"], axis=-1, num_outputs=3)
+            W.node("Mul", f"{n}/conv/Mul_1", [f"{n}/conv/b", f"{n}/conv/x"], [f"{n}/conv/Mul_1/output_0"])
+            W.node("Concat", f"{n}/conv/Conv_1", [f"past_conv.{i}", f"{n}/conv/Mul_1/output_0"], [f"{n}/conv/Conv_1/output_0"], axis=1)
+            put_plain(p + "conv.conv.weight", [p + "conv.conv.weight"], {"shape": (H, 1, Lc), "op": "id", "fn": lambda ts: ts[0].float().reshape(H, 1, Lc)})
+            cins = [f"{n}/conv/Conv_1/output_0", p + "conv.conv.weight"]
+            if arch.conv_bias:
+                put_vec(p + "conv.conv.bias", [p + "conv.conv.bias"])
+                cins.append(p + "conv.conv.bias")
+            W.node("Conv", f"{n}/conv/Conv_2", cins, [f"{n}/conv/Conv_2/output_0"], kernel_shape=[Lc], group=H, pads=[0, 0])
+            W.node("Mul", f"{n}/conv/Mul_2", [f"{n}/conv/c", f"{n}/conv/Conv_2/output_0"], [f"{n}/conv/Mul_2/output_0"])
+            W.node("Identity", f"{n}/conv/present", [f"{n}/conv/Conv_1/output_0"], [f"present_conv.{i}"])
+            o_out = f"{n}/conv/out_proj/MatMul/output_0"
+            put_linear(p + "conv.out_proj", f"{n}/conv/out_proj/MatMul", [p + "conv.out_proj.weight"], f"{n}/conv/Mul_2/output_0", o_out, H, H)
         else:
-            attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "/model/attn_mask_reformat/seqlens_k",
-                            "/model/attn_mask_reformat/total_seq_len", "cos_cache", "sin_cache", "", ""]
-        if arch.attn_sinks:
-            put_plain(p + "attn.sinks", [p + "self_attn.sinks"], {"shape": (arch.num_heads,), "op": "id", "fn": lambda ts: ts[0].float()})
-            attn_inputs.append(p + "attn.sinks")
-        else:
-            attn_inputs.append("")
-        if arch.qk_norm:
-            put_vec(p + "attn.q_norm.layernorm.weight", [p + "self_attn.q_norm.weight"], arch.norm_offset)
-            put_vec(p + "attn.k_norm.layernorm.weight", [p + "self_attn.k_norm.weight"], arch.norm_offset)
-            attn_inputs += ["", ""] if not paged else []
-            attn_inputs += [p + "attn.q_norm.layernorm.weight", p + "attn.k_norm.layernorm.weight"]
-        attrs = dict(num_heads=arch.num_heads, kv_num_heads=arch.num_kv_heads, scale=float(arch.scale),
-                     local_window_size=int(arch.layer_window(i)) if arch.layer_window(i) else -1, softcap=float(arch.softcap),
-                     do_rotary=0 if arch.learned_positions else 1, rotary_interleaved=int(arch.rotary_interleaved))
-        if arch.qk_norm:
-            attrs["qk_norm_epsilon"] = float(arch.norm_eps)
-        if arch.rotary_dim != arch.head_dim:
-            attrs["rotary_embedding_dim"] = int(arch.rotary_dim)
-        W.node(attn_op, f"{n}/attn/{attn_op}", attn_inputs, [f"{n}/attn/{attn_op}/output_0", f"present.{i}.key", f"present.{i}.value"],
-               domain="com.microsoft", **attrs)
-        o_out = f"{n}/attn/o_proj/MatMul/output_0"
-        put_linear(p + "attn.o_proj", f"{n}/attn/o_proj/MatMul", [p + "self_attn.o_proj.weight"], f"{n}/attn/{attn_op}/output_0", o_out,
-                   H, arch.q_size)
-        if arch.o_bias:
-            put_vec(p + "attn.o_proj.Add.bias", [p + "self_attn.o_proj.bias"])
-            W.node("Add", f"{n}/attn/o_proj/Add", [o_out, p + "attn.o_proj.Add.bias"], [f"{n}/attn/o_proj/Add/output_0"])
-            o_out = f"{n}/attn/o_proj/Add/output_0"
+            # attention
+            qkv_out = f"{n}/attn/qkv_proj/MatMul/output_0"
+            put_linear(p + "attn.qkv_proj", f"{n}/attn/qkv_proj/MatMul",
+                       [p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"], x, qkv_out,
+                       arch.q_size + 2 * arch.kv_size, H)
+            if arch.attn_bias:
+                put_vec(p + "attn.qkv_proj.Add.bias", [p + "self_attn.q_proj.bias", p + "self_attn.k_proj.bias", p + "self_attn.v_proj.bias"])
+                W.node("Add", f"{n}/attn/qkv_proj/Add", [qkv_out, p + "attn.qkv_proj.Add.bias"], [f"{n}/attn/qkv_proj/Add/output_0"])
+                qkv_out = f"{n}/attn/qkv_proj/Add/output_0"
+            attn_inputs = [qkv_out, "", ""]
+            if paged:
+                attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "cumulative_sequence_lengths",
+                                "past_sequence_lengths", "block_table_windowed" if arch.layer_window(i) else "block_table",
+                                "cos_cache", "sin_cache", ""]
+            else:
+                attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "/model/attn_mask_reformat/seqlens_k",
+                                "/model/attn_mask_reformat/total_seq_len", "cos_cache", "sin_cache", "", ""]
+            if arch.attn_sinks:
+                put_plain(p + "attn.sinks", [p + "self_attn.sinks"], {"shape": (arch.num_heads,), "op": "id", "fn": lambda ts: ts[0].float()})
+                attn_inputs.append(p + "attn.sinks")
+            else:
+                attn_inputs.append("")
+            if arch.qk_norm:
+                put_vec(p + "attn.q_norm.layernorm.weight", [p + "self_attn.q_norm.weight"], arch.norm_offset)
+                put_vec(p + "attn.k_norm.layernorm.weight", [p + "self_attn.k_norm.weight"], arch.norm_offset)
+                attn_inputs += ["", ""] if not paged else []
+                attn_inputs += [p + "attn.q_norm.layernorm.weight", p + "attn.k_norm.layernorm.weight"]
+            attrs = dict(num_heads=arch.num_heads, kv_num_heads=arch.num_kv_heads, scale=float(arch.scale),
+                         local_window_size=int(arch.layer_window(i)) if arch.layer_window(i) else -1, softcap=float(arch.softcap),
+                         do_rotary=0 if arch.learned_positions else 1, rotary_interleaved=int(arch.rotary_interleaved))
+            if arch.qk_norm:
+                attrs["qk_norm_epsilon"] = float(arch.norm_eps)
+            if arch.rotary_dim != arch.head_dim:
+                attrs["rotary_embedding_dim"] = int(arch.rotary_dim)
+            W.node(attn_op, f"{n}/attn/{attn_op}", attn_inputs, [f"{n}/attn/{attn_op}/output_0", f"present.{i}.key", f"present.{i}.value"],
+                   domain="com.microsoft", **attrs)
+            o_out = f"{n}/attn/o_proj/MatMul/output_0"
+            put_linear(p + "attn.o_proj", f"{n}/attn/o_proj/MatMul", [p + "self_attn.o_proj.weight"], f"{n}/attn/{attn_op}/output_0", o_out,
+                       H, arch.q_size)
+            if arch.o_bias:
+                put_vec(p + "attn.o_proj.Add.bias", [p + "self_attn.o_proj.bias"])
+                W.node("Add", f"{n}/attn/o_proj/Add", [o_out, p + "attn.o_proj.Add.bias"], [f"{n}/attn/o_proj/Add/output_0"])
+                o_out = f"{n}/attn/o_proj/Add/output_0"
         if arch.cross_attention:
             # encoder-decoder: queries from the decoder stream, keys / values projected once from the encoder output
             put_vec(p + "cross_attn_layernorm.weight", [p + "cross_attn_layernorm.weight"], arch.norm_offset)
@@ -618,6 +644,10 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
     if arch.learned_positions:
         m.inputs.append(op.ValueInfo("position_ids", op.INT64, ("num_tokens",) if paged else ("batch_size", "sequence_length")))
     for i in range(L):
+        if arch.is_conv_layer(i):
+            m.inputs.append(op.ValueInfo(f"past_conv.{i}", io_dt, ("batch_size", H, arch.conv_L_cache)))
+            m.outputs.append(op.ValueInfo(f"present_conv.{i}", io_dt, ("batch_size", H, arch.conv_L_cache)))
+            continue
         m.inputs += [op.ValueInfo(f"past_key_values.{i}.key", io_dt, kv_shape), op.ValueInfo(f"past_key_values.{i}.value", io_dt, kv_shape)]
         m.outputs += [op.ValueInfo(f"present.{i}.key", io_dt, kv_shape), op.ValueInfo(f"present.{i}.value", io_dt, kv_shape)]
 
@@ -676,6 +706,11 @@ def make_genai_config(arch: ArchConfig, precision: str, ep: str, paged: bool, bl
         if arch.sliding_layers is not None:
             sw["layers"] = list(arch.sliding_layers)
         decoder["sliding_window"] = sw
+    if arch.layer_types is not None and "conv" in arch.layer_types:
+        decoder["layer_types"] = list(arch.layer_types)
+        decoder["conv_cache_size"] = int(arch.conv_L_cache)
+        inputs["past_conv_names"] = "past_conv.%d"
+        decoder["outputs"]["present_conv_names"] = "present_conv.%d"
     cfg = {
         "model": {"bos_token_id": arch.bos_token_id, "context_length": arch.context_length, "decoder": decoder,
                   "eos_token_id": arch.eos_token_id, "pad_token_id": arch.pad_token_id, "type": arch.model_type,

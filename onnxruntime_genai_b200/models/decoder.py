@@ -48,21 +48,30 @@ class PagedKVCache:
     sliding window may use a second, smaller pool addressed through ring block tables."""
 
     def __init__(self, arch: ArchConfig, num_blocks: int, block_size: int, device, dtype, kv_heads: Optional[int] = None,
-                 num_window_blocks: int = 0):
+                 num_window_blocks: int = 0, conv_channels: Optional[int] = None):
         self.block_size = block_size
         self.num_blocks = num_blocks
         self.num_window_blocks = num_window_blocks
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
-        self.windowed = [num_window_blocks > 0 and arch.layer_window(i) > 0 for i in range(arch.num_layers)]
-        n_full = sum(1 for w in self.windowed if not w)
-        n_win = arch.num_layers - n_full
+        conv = [arch.is_conv_layer(i) for i in range(arch.num_layers)]
+        self.windowed = [num_window_blocks > 0 and arch.layer_window(i) > 0 and not conv[i] for i in range(arch.num_layers)]
+        n_full = sum(1 for w, c in zip(self.windowed, conv) if not w and not c)
+        n_win = sum(1 for w in self.windowed if w)
+        # Hybrid models: the gated input (b * x) of every position of every convolution layer, in the same paged slots as
+        # the keys and values - rewinding, beam reordering and block sharing need nothing layer-specific.
+        self.conv_index = {i: j for j, i in enumerate(i for i, c in enumerate(conv) if c)}
+        cc = conv_channels if conv_channels is not None else arch.hidden_size
+        self.conv = (torch.zeros(len(self.conv_index), num_blocks * block_size, cc, dtype=dtype, device=device)
+                     if self.conv_index else None)
         self.full = torch.zeros(max(n_full, 1), 2, num_blocks * block_size, hk, arch.head_dim, dtype=dtype, device=device)
         self.win = (torch.zeros(n_win, 2, num_window_blocks * block_size, hk, arch.head_dim, dtype=dtype, device=device)
                     if n_win else None)
         self._index = []
         fi = wi = 0
-        for w in self.windowed:
-            if w:
+        for w, c in zip(self.windowed, conv):
+            if c:
+                self._index.append((False, -1))
+            elif w:
                 self._index.append((True, wi)); wi += 1
             else:
                 self._index.append((False, fi)); fi += 1
@@ -72,10 +81,16 @@ class PagedKVCache:
         pool = self.win if win else self.full
         return pool[j, 0], pool[j, 1], win
 
+    def conv_layer(self, i: int) -> torch.Tensor:
+        return self.conv[self.conv_index[i]]
+
     @staticmethod
-    def bytes_per_block(arch: ArchConfig, block_size: int, dtype, kv_heads: Optional[int] = None) -> int:
+    def bytes_per_block(arch: ArchConfig, block_size: int, dtype, kv_heads: Optional[int] = None, conv_channels: Optional[int] = None) -> int:
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
-        return arch.num_layers * 2 * block_size * hk * arch.head_dim * torch.empty((), dtype=dtype).element_size()
+        n_conv = sum(1 for i in range(arch.num_layers) if arch.is_conv_layer(i))
+        cc = conv_channels if conv_channels is not None else arch.hidden_size
+        per_token = (arch.num_layers - n_conv) * 2 * hk * arch.head_dim + n_conv * cc
+        return per_token * block_size * torch.empty((), dtype=dtype).element_size()
 
 
 class CrossKVCache:
@@ -126,6 +141,10 @@ class LayerWeights:
     gate_up_b: Optional[torch.Tensor] = None
     down_w: Optional[torch.Tensor] = None
     down_b: Optional[torch.Tensor] = None
+    conv_in_w: Optional[torch.Tensor] = None   # hybrid (LFM2) convolution layer: in_proj [3C, H] (b, c, x), depthwise taps [C, L], out_proj
+    conv_w: Optional[torch.Tensor] = None
+    conv_b: Optional[torch.Tensor] = None
+    conv_out_w: Optional[torch.Tensor] = None
     cross_ln_w: Optional[torch.Tensor] = None  # encoder-decoder cross-attention (whisper)
     cross_ln_b: Optional[torch.Tensor] = None
     cross_q_w: Optional[torch.Tensor] = None
@@ -174,6 +193,7 @@ class DecoderModel:
         self.pos_embed: Optional[torch.Tensor] = None   # learned position table (gpt2)
         self.heads_local = arch.num_heads // self.tp.size
         self.kv_heads_local = max(1, arch.num_kv_heads // self.tp.size)
+        self.conv_channels_local = arch.hidden_size // self.tp.size      # channels of a hybrid model's convolution layers
         self.inter_local = arch.intermediate_size // self.tp.size
         self.active_adapter = None  # name -> used by the LoRA hooks
 
@@ -303,6 +323,15 @@ class DecoderModel:
                 residual = h
             else:
                 x, residual = ops.norm(h, lw.ln1_w, a.norm_eps, residual, lw.ln1_b, a.layernorm)
+            if lw.conv_in_w is not None:
+                # ---- gated short convolution instead of attention (hybrid models)
+                bcx = self._linear(x, lw.conv_in_w, None, lora=self._lora(lw, "in_proj"))
+                y = ops.short_conv(bcx, lw.conv_w, lw.conv_b, kv.conv_layer(li), s.slot_mapping, s.positions, s.cu_seqlens, s.past_lens,
+                                   s.block_table, kv.block_size)
+                h = self._row_parallel(y, lw.conv_out_w, None, self._lora(lw, "out_proj"))
+                x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
+                h = self._mlp(lw, x)
+                continue
             # ---- attention
             qkv = self._linear(x, lw.qkv_w, lw.qkv_b, lora=self._lora(lw, "qkv_proj"))
             kc, vc, windowed = kv.layer(li)

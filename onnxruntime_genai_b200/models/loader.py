@@ -98,7 +98,10 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
     if first_norm is not None:
         a.norm_eps = float(_attr(first_norm, "epsilon", 1e-5))
         a.layernorm = "Simplified" not in first_norm.op_type
-    attn = g.find("/model/layers.0/attn/", ops=["GroupQueryAttention", "PagedAttention", "MultiHeadAttention"])
+    # the first layer that attends (hybrid models may start with convolution layers)
+    fa = next((i for i in range(L) if g.find(f"/model/layers.{i}/attn/", ops=["GroupQueryAttention", "PagedAttention"]) is not None), 0)
+    fa = f"/model/layers.{fa}"
+    attn = g.find(f"{fa}/attn/", ops=["GroupQueryAttention", "PagedAttention", "MultiHeadAttention"])
     if attn is not None:
         a.attn_scale = float(_attr(attn, "scale", 0.0)) or None
         a.softcap = float(_attr(attn, "softcap", 0.0) or 0.0)
@@ -116,10 +119,18 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
     if any(windows):
         a.sliding_window = max(windows)
         a.sliding_layers = None if all(windows) else [i for i, w in enumerate(windows) if w > 0]
-    a.attn_bias = g.find("/model/layers.0/attn/", "_proj/Add") is not None and \
-        any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all("/model/layers.0/attn/"))
-    a.o_bias = g.by_name.get("/model/layers.0/attn/o_proj/Add") is not None
+    a.attn_bias = g.find(f"{fa}/attn/", "_proj/Add") is not None and \
+        any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all(f"{fa}/attn/"))
+    a.o_bias = g.by_name.get(f"{fa}/attn/o_proj/Add") is not None
     a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
+    types = ["conv" if g.find(f"/model/layers.{i}/conv/in_proj/", ops=["MatMul", "MatMulNBits"]) is not None else "full_attention"
+             for i in range(a.num_layers)]
+    if "conv" in types:
+        a.layer_types = types
+        first = types.index("conv")
+        taps = g.lm.info(f"model.layers.{first}.conv.conv.weight").dims
+        a.conv_L_cache = int(taps[-1])
+        a.conv_bias = g.has_init(f"model.layers.{first}.conv.conv.bias")
     a.cross_attention = g.find("/model/layers.0/cross_attn/") is not None
     if a.cross_attention:
         a.encoder_hidden_size = _linear_shape(g, g.find("/model/layers.0/cross_attn/kv_proj/", ops=["MatMul", "MatMulNBits"]))[1]
@@ -289,67 +300,85 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
             ln2_w=_vec(g, ln2.inputs[2], dtype, device) if ln2 is not None else None,      # parallel blocks have one norm
             ln2_b=_vec(g, ln2.inputs[3], dtype, device) if ln2 is not None and arch.layernorm and len(ln2.inputs) > 3 else None,
             qkv_w=None, o_w=None, window=arch.layer_window(i))
-        # attention projections: packed or separate
-        qkv = linear_node(f"{n}/attn/", "qkv_proj")
-        if qkv is not None:
-            if keep_q4 and _is_q4([qkv]):
-                lw.qkv_w = _q4_weight(g, [qkv], device)
+        conv_in = linear_node(f"{n}/conv/", "in_proj")
+        if conv_in is not None:
+            # hybrid (LFM2) convolution layer: channels are independent, so tensor parallelism splits them - in_proj rows of
+            # this rank's channels of b, c and x, the matching taps, out_proj columns
+            C = arch.hidden_size
+            c_l = C // tpn
+            ch = slice(tpr * c_l, (tpr + 1) * c_l)
+            if tpn > 1:
+                lw.conv_in_w = torch.cat([_linear_weight(g, conv_in, dtype, device, rows=slice(j * C + ch.start, j * C + ch.stop))
+                                          for j in range(3)], 0).contiguous()
             else:
-                w = _linear_weight(g, qkv, dtype, device)
-                lw.qkv_w = shard_rows(w, [q_rows, k_rows, v_rows])
-            badd = g.by_name.get(f"{n}/attn/qkv_proj/Add")
-            if badd is not None:
-                b = g.tensor(badd.inputs[1])
-                lw.qkv_b = shard_rows(b, [q_rows, k_rows, v_rows]).to(device=device, dtype=dtype)
+                lw.conv_in_w = _linear_weight(g, conv_in, dtype, device)
+            taps = g.tensor(f"model.layers.{i}.conv.conv.weight").reshape(C, -1)
+            lw.conv_w = (taps[ch] if tpn > 1 else taps).to(device=device, dtype=dtype).contiguous()
+            if g.has_init(f"model.layers.{i}.conv.conv.bias"):
+                lw.conv_b = _vec(g, f"model.layers.{i}.conv.conv.bias", dtype, device, ch if tpn > 1 else None)
+            lw.conv_out_w = _linear_weight(g, linear_node(f"{n}/conv/", "out_proj"), dtype, device, cols=ch if tpn > 1 else None)
         else:
-            ws, bs = [], []
-            for nm, rows in (("q_proj", slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)),
-                             ("k_proj", slice(tpr * hkv_l * D, (tpr + 1) * hkv_l * D)),
-                             ("v_proj", slice(tpr * hkv_l * D, (tpr + 1) * hkv_l * D))):
-                node = linear_node(f"{n}/attn/", nm)
-                ws.append(_linear_weight(g, node, dtype, device, rows=rows if tpn > 1 else None))
-                badd = g.by_name.get(f"{n}/attn/{nm}/Add")
+            # attention projections: packed or separate
+            qkv = linear_node(f"{n}/attn/", "qkv_proj")
+            if qkv is not None:
+                if keep_q4 and _is_q4([qkv]):
+                    lw.qkv_w = _q4_weight(g, [qkv], device)
+                else:
+                    w = _linear_weight(g, qkv, dtype, device)
+                    lw.qkv_w = shard_rows(w, [q_rows, k_rows, v_rows])
+                badd = g.by_name.get(f"{n}/attn/qkv_proj/Add")
                 if badd is not None:
                     b = g.tensor(badd.inputs[1])
-                    bs.append((b[rows] if tpn > 1 else b).to(device=device, dtype=dtype))
-            lw.qkv_w = torch.cat(ws, 0).contiguous()
-            lw.qkv_b = torch.cat(bs, 0).contiguous() if bs else None
-        o = linear_node(f"{n}/attn/", "o_proj")
-        if keep_q4 and _is_q4([o]):
-            lw.o_w = _q4_weight(g, [o], device)
-        else:
-            lw.o_w = _linear_weight(g, o, dtype, device, cols=slice(tpr * hq_l * D, (tpr + 1) * hq_l * D) if tpn > 1 else None)
-        oadd = g.by_name.get(f"{n}/attn/o_proj/Add")
-        if oadd is not None:
-            lw.o_b = _vec(g, oadd.inputs[1], dtype, device)
-        if arch.cross_attention:
-            cn = g.by_name[f"{n}/cross_attn_layernorm/SkipLayerNorm"]
-            lw.cross_ln_w = _vec(g, cn.inputs[2], dtype, device)
-            lw.cross_ln_b = _vec(g, cn.inputs[3], dtype, device) if arch.layernorm and len(cn.inputs) > 3 else None
-            hd = slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)
-            Hq = arch.num_heads * D
-            kv_rows = [hd, slice(Hq + hd.start, Hq + hd.stop)]
-            lw.cross_q_w = _linear_weight(g, linear_node(f"{n}/cross_attn/", "q_proj"), dtype, device, rows=hd if tpn > 1 else None)
-            lw.cross_q_b = _vec(g, g.by_name[f"{n}/cross_attn/q_proj/Add"].inputs[1], dtype, device, hd if tpn > 1 else None)
-            kvn = linear_node(f"{n}/cross_attn/", "kv_proj")
-            kvb = g.tensor(g.by_name[f"{n}/cross_attn/kv_proj/Add"].inputs[1])
-            if tpn > 1:
-                lw.cross_kv_w = torch.cat([_linear_weight(g, kvn, dtype, device, rows=r) for r in kv_rows], 0).contiguous()
-                lw.cross_kv_b = shard_rows(kvb, kv_rows).to(device=device, dtype=dtype)
+                    lw.qkv_b = shard_rows(b, [q_rows, k_rows, v_rows]).to(device=device, dtype=dtype)
             else:
-                lw.cross_kv_w = _linear_weight(g, kvn, dtype, device)
-                lw.cross_kv_b = kvb.to(device=device, dtype=dtype).contiguous()
-            lw.cross_o_w = _linear_weight(g, linear_node(f"{n}/cross_attn/", "o_proj"), dtype, device, cols=hd if tpn > 1 else None)
-            lw.cross_o_b = _vec(g, g.by_name[f"{n}/cross_attn/o_proj/Add"].inputs[1], dtype, device)
-        attn = g.find(f"{n}/attn/", ops=["GroupQueryAttention", "PagedAttention"])
-        for inp in attn.inputs:
-            if inp.endswith(".sinks"):
-                s = g.tensor(inp).float()
-                lw.sinks = (s[tpr * hq_l:(tpr + 1) * hq_l] if tpn > 1 else s).to(device).contiguous()
-            elif "q_norm" in inp:
-                lw.q_norm_w = _vec(g, inp, dtype, device)
-            elif "k_norm" in inp:
-                lw.k_norm_w = _vec(g, inp, dtype, device)
+                ws, bs = [], []
+                for nm, rows in (("q_proj", slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)),
+                                 ("k_proj", slice(tpr * hkv_l * D, (tpr + 1) * hkv_l * D)),
+                                 ("v_proj", slice(tpr * hkv_l * D, (tpr + 1) * hkv_l * D))):
+                    node = linear_node(f"{n}/attn/", nm)
+                    ws.append(_linear_weight(g, node, dtype, device, rows=rows if tpn > 1 else None))
+                    badd = g.by_name.get(f"{n}/attn/{nm}/Add")
+                    if badd is not None:
+                        b = g.tensor(badd.inputs[1])
+                        bs.append((b[rows] if tpn > 1 else b).to(device=device, dtype=dtype))
+                lw.qkv_w = torch.cat(ws, 0).contiguous()
+                lw.qkv_b = torch.cat(bs, 0).contiguous() if bs else None
+            o = linear_node(f"{n}/attn/", "o_proj")
+            if keep_q4 and _is_q4([o]):
+                lw.o_w = _q4_weight(g, [o], device)
+            else:
+                lw.o_w = _linear_weight(g, o, dtype, device, cols=slice(tpr * hq_l * D, (tpr + 1) * hq_l * D) if tpn > 1 else None)
+            oadd = g.by_name.get(f"{n}/attn/o_proj/Add")
+            if oadd is not None:
+                lw.o_b = _vec(g, oadd.inputs[1], dtype, device)
+            if arch.cross_attention:
+                cn = g.by_name[f"{n}/cross_attn_layernorm/SkipLayerNorm"]
+                lw.cross_ln_w = _vec(g, cn.inputs[2], dtype, device)
+                lw.cross_ln_b = _vec(g, cn.inputs[3], dtype, device) if arch.layernorm and len(cn.inputs) > 3 else None
+                hd = slice(tpr * hq_l * D, (tpr + 1) * hq_l * D)
+                Hq = arch.num_heads * D
+                kv_rows = [hd, slice(Hq + hd.start, Hq + hd.stop)]
+                lw.cross_q_w = _linear_weight(g, linear_node(f"{n}/cross_attn/", "q_proj"), dtype, device, rows=hd if tpn > 1 else None)
+                lw.cross_q_b = _vec(g, g.by_name[f"{n}/cross_attn/q_proj/Add"].inputs[1], dtype, device, hd if tpn > 1 else None)
+                kvn = linear_node(f"{n}/cross_attn/", "kv_proj")
+                kvb = g.tensor(g.by_name[f"{n}/cross_attn/kv_proj/Add"].inputs[1])
+                if tpn > 1:
+                    lw.cross_kv_w = torch.cat([_linear_weight(g, kvn, dtype, device, rows=r) for r in kv_rows], 0).contiguous()
+                    lw.cross_kv_b = shard_rows(kvb, kv_rows).to(device=device, dtype=dtype)
+                else:
+                    lw.cross_kv_w = _linear_weight(g, kvn, dtype, device)
+                    lw.cross_kv_b = kvb.to(device=device, dtype=dtype).contiguous()
+                lw.cross_o_w = _linear_weight(g, linear_node(f"{n}/cross_attn/", "o_proj"), dtype, device, cols=hd if tpn > 1 else None)
+                lw.cross_o_b = _vec(g, g.by_name[f"{n}/cross_attn/o_proj/Add"].inputs[1], dtype, device)
+            attn = g.find(f"{n}/attn/", ops=["GroupQueryAttention", "PagedAttention"])
+            for inp in attn.inputs:
+                if inp.endswith(".sinks"):
+                    s = g.tensor(inp).float()
+                    lw.sinks = (s[tpr * hq_l:(tpr + 1) * hq_l] if tpn > 1 else s).to(device).contiguous()
+                elif "q_norm" in inp:
+                    lw.q_norm_w = _vec(g, inp, dtype, device)
+                elif "k_norm" in inp:
+                    lw.k_norm_w = _vec(g, inp, dtype, device)
         if arch.post_sublayer_norms:
             pa = g.find(f"{n}/post_attention_layernorm/")
             pf = g.find(f"{n}/post_feedforward_layernorm/")

@@ -218,6 +218,21 @@ def act_mul(x, act="silu"):
     return out
 
 
+def short_conv(bcx, weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, block_size: int):
+    """Gated short depthwise convolution of a hybrid (LFM2) layer over packed sequences; appends b * x of this step's tokens
+    to the paged `cache` [slots, C] (see ops/reference.py::short_conv for the definition).  Returns [T, C]."""
+    if not bcx.is_cuda:
+        return ref.short_conv(bcx, weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, block_size)
+    T, C = bcx.shape[0], weight.shape[0]
+    assert bcx.dtype == torch.bfloat16 and bcx.stride(1) == 1 and weight.is_contiguous() and cache.is_contiguous()
+    assert block_table.stride(1) == 1
+    out = torch.empty(T, C, dtype=bcx.dtype, device=bcx.device)
+    _lib.check(_lib.lib().ogb_short_conv(_ptr(bcx), bcx.stride(0), _ptr(weight), _ptr(bias), _ptr(cache), _ptr(slots), _ptr(positions),
+                                        _ptr(cu_seqlens), _ptr(past_lens), _ptr(block_table), block_table.stride(0), int(block_size),
+                                        _ptr(out), T, past_lens.shape[0], C, weight.shape[1], _stream()), "short_conv")
+    return out
+
+
 def decode_advance(sampled, input_ids, positions, past_lens, slot_mapping, sample_pos, block_table, block_size: int):
     """In place: the packed inputs of a one-token-per-request step become those of the next step (see
     csrc/elementwise.cu::decode_advance_kernel).  block_table [B, cols] int32, everything else [B] int32."""

@@ -41,6 +41,7 @@ _SIGS = {
                                    c_int, _P]),
     "ogb_act_mul": (c_int, [_P, _P, c_int, c_int, c_int, _P]),
     "ogb_act": (c_int, [_P, _P, c_longlong, c_int, _P]),
+    "ogb_short_conv": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P]),
     "ogb_decode_advance": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
     "ogb_logits_edit": (c_int, [_P, c_int, _P, _P, _P, _P, c_int, _P]),
     "ogb_logits_bitmask": (c_int, [_P, c_int, c_int, _P, _P, _P]),

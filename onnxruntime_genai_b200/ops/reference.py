@@ -220,3 +220,34 @@ def topk(x, k, log_softmax=False, add=None):
     # ties resolved towards the lower index
     vals, idx = torch.sort(y, dim=-1, descending=True, stable=True)
     return vals[:, :k].contiguous(), idx[:, :k].to(torch.int32).contiguous()
+
+
+def short_conv(bcx, weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, block_size):
+    """Gated short depthwise convolution of a hybrid (LFM2) layer over packed sequences.
+    bcx [T, 3C]: per token the gates b, c and the value x; weight [C, L]; cache [slots, C] holds b * x of every cached
+    position (this step's are written at `slots`).  y[t] = c[t] * sum_k weight[:, L-1-k] * (b*x)[position(t) - k] (+ bias),
+    positions before the start of the sequence contribute nothing."""
+    T, C3 = bcx.shape
+    C, L = weight.shape
+    f = bcx.float()
+    b, c, x = f[:, :C], f[:, C:2 * C], f[:, 2 * C:]
+    bx = (b * x).to(bcx.dtype)
+    ok = slots >= 0
+    cache[slots[ok].long()] = bx[ok].to(cache.dtype)
+    out = torch.zeros(T, C, dtype=torch.float32, device=bcx.device)
+    cu = cu_seqlens.tolist()
+    w = weight.float()
+    for r in range(len(cu) - 1):
+        for t in range(cu[r], cu[r + 1]):
+            p = int(positions[t])
+            acc = torch.zeros(C, dtype=torch.float32, device=bcx.device)
+            for k in range(L):
+                q = p - k
+                if q < 0:
+                    break
+                slot = int(block_table[r, q // block_size]) * block_size + q % block_size
+                acc += w[:, L - 1 - k] * cache[slot].float()
+            if bias is not None:
+                acc = acc + bias.float()
+            out[t] = c[t] * acc
+    return out.to(bcx.dtype)

@@ -52,6 +52,17 @@ def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None):
         g = lambda n: sd.get(p + n)
         x = _norm(h, g("input_layernorm.weight"), g("input_layernorm.bias"), arch)
         lin = lambda t, n: t @ g(n + ".weight").t() + (g(n + ".bias") if g(n + ".bias") is not None else 0)
+        if arch.is_conv_layer(i):
+            # gated short convolution: causal depthwise conv1d of b * x, gated by c
+            H, Lc = arch.hidden_size, arch.conv_L_cache
+            b_, c_, x_ = lin(x, "conv.in_proj").split(H, dim=-1)
+            bx = (b_ * x_).t()[None]                                              # [1, H, S]
+            conv = torch.nn.functional.conv1d(torch.nn.functional.pad(bx, (Lc - 1, 0)), g("conv.conv.weight").view(H, 1, Lc),
+                                              g("conv.conv.bias"), groups=H)[0].t()
+            h = h + lin(c_ * conv, "conv.out_proj")
+            x = _norm(h, g("post_attention_layernorm.weight"), g("post_attention_layernorm.bias"), arch)
+            h = h + lin(torch.nn.functional.silu(lin(x, "mlp.gate_proj")) * lin(x, "mlp.up_proj"), "mlp.down_proj")
+            continue
         q = lin(x, "self_attn.q_proj").view(S, arch.num_heads, D)
         k = lin(x, "self_attn.k_proj").view(S, arch.num_kv_heads, D)
         v = lin(x, "self_attn.v_proj").view(S, arch.num_kv_heads, D)

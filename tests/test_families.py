@@ -31,6 +31,10 @@ FAMILIES = {
                          lm_head_bias=True, activation="gelu", num_kv_heads=4, mlp_gated=False, parallel_block=True),
     "gpt2": dict(model_type="gpt2", layernorm=True, attn_bias=True, o_bias=True, mlp_bias=True, activation="gelu", num_kv_heads=4,
                  mlp_gated=False, learned_positions=True, tie_embeddings=True),
+    "lfm2_hybrid": dict(model_type="lfm2", qk_norm=True, tie_embeddings=True, conv_L_cache=3,
+                        layer_types=["conv", "full_attention", "conv"]),
+    "lfm2_conv_bias": dict(model_type="lfm2", qk_norm=True, conv_L_cache=4, conv_bias=True, num_layers=4,
+                           layer_types=["conv", "conv", "full_attention", "conv"]),
     "gemma2": dict(model_type="gemma2", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, softcap=20.0,
                    final_logit_softcap=15.0, sliding_window=8, sliding_layers=[0, 2], attn_scale=0.2, tie_embeddings=True),
     "gemma3": dict(model_type="gemma3_text", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, qk_norm=True,
@@ -53,9 +57,9 @@ def test_family_logits_and_decode_match_dense_reference(family, tmp_path):
     a2 = model.arch
     for f in ("norm_eps", "layernorm", "qk_norm", "attn_bias", "o_bias", "mlp_bias", "softcap", "sliding_window", "attn_sinks",
               "activation", "num_experts", "experts_per_token", "post_sublayer_norms", "rotary_interleaved", "lm_head_bias",
-              "mlp_gated", "parallel_block", "learned_positions"):
+              "mlp_gated", "parallel_block", "learned_positions", "conv_L_cache", "conv_bias"):
         assert getattr(a2, f) == pytest.approx(getattr(arch, f)), f
-    assert a2.intermediate_size == arch.intermediate_size and a2.rotary_dim == arch.rotary_dim
+    assert a2.intermediate_size == arch.intermediate_size and a2.rotary_dim == arch.rotary_dim and a2.layer_types == arch.layer_types
     prompt = np.random.RandomState(4).randint(0, arch.vocab_size - 1, size=(1, 23)).astype(np.int32)
     p = og.GeneratorParams(model)
     p.set_search_options(max_length=40)
@@ -114,10 +118,12 @@ def test_int4_checkpoint_roundtrip(tmp_path):
     assert np.corrcoef(got, fp)[0, 1] > 0.9, "int4 logits must stay close to the fp32 model"
 
 
-def test_beam_search_cache_sharing_matches_full_recompute(tmp_path):
+@pytest.mark.parametrize("family", ["llama", "lfm2_hybrid"])
+def test_beam_search_cache_sharing_matches_full_recompute(family, tmp_path):
     """Beam reordering permutes block tables and copies blocks on write; every row's logits must still equal a
-    full recompute of that row's token sequence (prompt ending inside a block, rows crossing block boundaries)."""
-    arch = ArchConfig(**{**BASE, **FAMILIES["llama"]})
+    full recompute of that row's token sequence (prompt ending inside a block, rows crossing block boundaries).
+    The hybrid family keeps its convolution inputs in the same paged slots, so its state follows the beams too."""
+    arch = ArchConfig(**{**BASE, **FAMILIES[family]})
     sd = random_state_dict(arch, seed=21, std=0.3)
     d = str(tmp_path)
     export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
@@ -201,3 +207,23 @@ def test_longrope_switches_caches_and_rebuilds_the_kv_cache(tmp_path):
         want = dense_logits(arch, sd, ids)[-1].numpy()
         np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4, err_msg=f"length {len(ids)}")
     assert len(ids) > 33, "the sequence must cross the original context length"
+
+
+def test_hybrid_model_rewind_and_continue(tmp_path):
+    """Rewinding a hybrid model needs no state snapshot: the convolution reads earlier positions from the paged cache."""
+    arch = ArchConfig(**{**BASE, **FAMILIES["lfm2_conv_bias"]})
+    sd = random_state_dict(arch, seed=12, std=0.15)
+    d = str(tmp_path)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    model = og.Model(d)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=64)
+    g = og.Generator(model, p)
+    ids = [3, 9, 27, 81, 32, 96, 77, 20, 60]
+    g.append_tokens(np.asarray([ids], dtype=np.int32))
+    for _ in range(5):
+        g.generate_next_token()
+    g.rewind_to(6)
+    g.append_tokens(np.asarray([[5, 6]], dtype=np.int32))
+    want = dense_logits(arch, sd, ids[:6] + [5, 6])[-1].numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)

@@ -221,14 +221,16 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
     assert len(c[1]) <= max(5, len(a[1])) and all(len(c[i]) > 0 for i in (0, 2, 3))
 
 
-@pytest.mark.parametrize("family", ["phi_parallel", "gpt2"])
+@pytest.mark.parametrize("family", ["phi_parallel", "gpt2", "lfm2"])
 def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_path):
-    """fc1 -> GELU -> fc2 MLPs, the parallel attention/MLP block and learned position tables: bf16 GPU against fp32 CPU."""
+    """fc1 -> GELU -> fc2 MLPs, the parallel attention/MLP block, learned position tables, hybrid convolution layers: bf16 GPU
+    against fp32 CPU."""
     from onnxruntime_genai_b200.models.builder import random_state_dict
     flags = {"phi_parallel": dict(model_type="phi", layernorm=True, partial_rotary_factor=0.5, attn_bias=True, o_bias=True, mlp_bias=True,
                                   lm_head_bias=True, activation="gelu", mlp_gated=False, parallel_block=True),
              "gpt2": dict(model_type="gpt2", layernorm=True, attn_bias=True, o_bias=True, mlp_bias=True, activation="gelu",
-                          mlp_gated=False, learned_positions=True, tie_embeddings=True)}[family]
+                          mlp_gated=False, learned_positions=True, tie_embeddings=True),
+             "lfm2": dict(model_type="lfm2", qk_norm=True, tie_embeddings=True, conv_L_cache=3, layer_types=["conv", "full_attention"])}[family]
     arch = ArchConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=64, intermediate_size=512,
                       context_length=256, bos_token_id=0, eos_token_id=1023, pad_token_id=0, **flags)
     sd = random_state_dict(arch, seed=3, std=0.05)

@@ -251,6 +251,42 @@ def test_embedding_gather_actmul_cast():
     assert torch.equal(ops.to_float32(x), x.float())
 
 
+@pytest.mark.parametrize("L,bias", [(3, False), (4, True)])
+def test_short_conv_matches_reference(L, bias):
+    """Prefill chunks, single-token rows and a chunk continuing a cached prefix in one packed launch; the paged cache after
+    the launch must hold b * x of the new positions."""
+    rng = np.random.RandomState(5)
+    C, bs = 256, 16
+    q_lens, past = [19, 1, 5, 1], [0, 37, 14, 2]
+    B, T = len(q_lens), sum(q_lens)
+    cols = max((p_ + q_ + bs - 1) // bs for p_, q_ in zip(past, q_lens))
+    perm = rng.permutation(B * cols + 2)
+    table = torch.full((B, cols), -1, dtype=torch.int32)
+    used = 0
+    for b in range(B):
+        need = (past[b] + q_lens[b] + bs - 1) // bs
+        table[b, :need] = torch.from_numpy(perm[used:used + need].astype(np.int32))
+        used += need
+    cache = _rand((B * cols + 2) * bs, C, std=1.0, seed=40)
+    bcx = _rand(T, 3 * C, std=1.0, seed=41)
+    w = _rand(C, L, std=0.5, seed=42)
+    bvec = _rand(C, std=0.5, seed=43) if bias else None
+    pos, slots = [], []
+    for b in range(B):
+        for j in range(q_lens[b]):
+            p_ = past[b] + j
+            pos.append(p_)
+            slots.append(int(table[b, p_ // bs]) * bs + p_ % bs)
+    pos, slots = torch.tensor(pos, dtype=torch.int32), torch.tensor(slots, dtype=torch.int32)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    pl = torch.tensor(past, dtype=torch.int32)
+    c_cpu = cache.cpu().clone()
+    want = ref.short_conv(bcx.cpu(), w.cpu(), bvec.cpu() if bias else None, c_cpu, slots, pos, cu, pl, table, bs)
+    got = ops.short_conv(bcx, w, bvec, cache, slots.to(DEV), pos.to(DEV), cu.to(DEV), pl.to(DEV), table.to(DEV), bs)
+    _close(got, want, rtol=3e-2, atol=3e-2)
+    assert torch.equal(cache.cpu(), c_cpu)
+
+
 def test_decode_advance_matches_reference():
     rng = np.random.RandomState(3)
     B, cols, bs = 37, 9, 16

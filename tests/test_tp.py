@@ -107,3 +107,21 @@ def test_non_gated_parallel_block_under_tp_on_cpu(tmp_path):
     two = _run(d, str(tmp_path / "p2.npz"), 2, 29671)
     np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
     assert two["seqs"].tolist() == one["seqs"].tolist()
+
+
+def test_hybrid_convolution_layers_under_tp_on_cpu(tmp_path):
+    """Convolution layers of a hybrid model split their (independent) channels between the ranks: in_proj rows of this
+    rank's b / c / x channels, its taps, out_proj columns; the paged convolution cache holds the local channels."""
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+    arch = ArchConfig(model_type="lfm2", vocab_size=96, hidden_size=32, num_layers=3, num_heads=4, num_kv_heads=2, head_dim=8,
+                      intermediate_size=64, context_length=128, qk_norm=True, tie_embeddings=True, conv_L_cache=3, conv_bias=True,
+                      layer_types=["conv", "full_attention", "conv"], eos_token_id=95, pad_token_id=95, bos_token_id=0)
+    sd = random_state_dict(arch, seed=6, std=0.1)
+    d = str(tmp_path / "lfm2")
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    one = _run(d, str(tmp_path / "h1.npz"), 1, 0, ["--engine"])
+    two = _run(d, str(tmp_path / "h2.npz"), 2, 29681, ["--engine"])
+    np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
+    assert two["seqs"].tolist() == one["seqs"].tolist()
+    assert two["engine"].tolist() == one["engine"].tolist()
