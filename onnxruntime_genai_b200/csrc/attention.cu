@@ -48,6 +48,10 @@ struct AttnParams {
   int window, B, Hq, Hkv, splits, total_rows;
   int* status;       // device status word (bounded waits)
   int chunk;   // > 0: every split owns a fixed range of `chunk` keys (multiple of 64); 0: a request's keys are divided evenly
+  // Optional [B] permutation of the requests: blockIdx.z walks `order`, so a caller that lists the requests longest first
+  // gets longest-processing-time-first scheduling (CTAs are dispatched in block-index order) - with a mix of 128..2300
+  // cached keys per request and fewer than two waves of CTAs the tail of a late long request otherwise sets the time.
+  const int32_t* order;
 };
 
 template <int SROW>
@@ -81,7 +85,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int kvh = blockIdx.y;
-  const int b = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const int bz = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const int b = p.order ? p.order[bz] : bz;
   const int G = p.Hq / p.Hkv;
   const int tok0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - tok0;
@@ -526,7 +531,7 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
                                 const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                                 int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
                                 int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
-                                long long scratch_bytes, int cache_slots, int* status, void* stream_) {
+                                long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_) {
   if (B <= 0 || total_tokens <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv || (q_stride % 8) || (out_stride % 2)) return -1;
   if (splits < 1) splits = 1;
@@ -535,6 +540,7 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
   AttnParams p;
   p.chunk = splits > 1 ? kv_chunk : 0;
   p.status = status;
+  p.order = order;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.block_table = block_table; p.table_cols = table_cols;
@@ -585,5 +591,5 @@ OGB_API int ogb_paged_attention_noalloc(const void* q, int q_stride, const void*
   }
   return ogb_paged_attention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out,
                              out_stride, sinks, scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, 0,
-                             g_noalloc_scratch_addr[dev], OGB_NOALLOC_SCRATCH_BYTES, 0, nullptr, stream);
+                             g_noalloc_scratch_addr[dev], OGB_NOALLOC_SCRATCH_BYTES, 0, nullptr, nullptr, stream);
 }

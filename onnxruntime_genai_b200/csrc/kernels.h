@@ -73,12 +73,13 @@ int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, 
 // ---- attention.cu
 long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, int splits);
 // cache_slots (rows of the key / value cache) and status (device status word) enable the TMA-fed K/V path; 0 / null keep
-// the cp.async path.  splits > 1 divides a request's keys between CTAs: evenly (kv_chunk 0) or in fixed ranges of kv_chunk keys (multiple of 64).
+// the cp.async path.  order: optional [B] permutation of the requests in which the CTAs are issued (longest first balances
+// a batch of mixed lengths).  splits > 1 divides a request's keys between CTAs: evenly (kv_chunk 0) or in fixed ranges of kv_chunk keys (multiple of 64).
 int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
                         const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                         int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
                         int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch, long long scratch_bytes,
-                        int cache_slots, int* status, void* stream);
+                        int cache_slots, const int32_t* order, int* status, void* stream);
 
 // ---- sampling.cu
 int ogb_sample(const float* logits, long long row_stride, int rows, int vocab, const int32_t* top_k, const float* top_p,

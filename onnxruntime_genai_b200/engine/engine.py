@@ -113,7 +113,7 @@ class _Staging:
     """All per-step inputs in one pinned host buffer with a device mirror (one H2D copy per step)."""
 
     FIELDS_TOK = ["input_ids", "positions", "token_row", "slot_mapping", "slot_mapping_w"]
-    FIELDS_ROW = ["past_lens", "logits_rows", "top_k", "sample_pos"]
+    FIELDS_ROW = ["past_lens", "logits_rows", "top_k", "sample_pos", "attn_order"]
 
     def __init__(self, max_tokens: int, max_batch: int, table_cols: int, device: torch.device, windowed: bool):
         self.max_tokens, self.max_batch, self.table_cols = max_tokens, max_batch, table_cols
@@ -154,6 +154,12 @@ class _Staging:
         self.addr = self._addrs[0]
         self._cur = 0
 
+    def host_np(self) -> np.ndarray:
+        """The current pinned host image as a numpy array (shares memory)."""
+        if not hasattr(self, "_np"):
+            self._np = [h.numpy() for h in self._hosts]
+        return self._np[self._cur]
+
     def flip(self):
         """Switches to the other pinned host image (call before packing a step)."""
         self._cur = (self._cur + 1) % len(self._hosts)
@@ -188,8 +194,10 @@ class ModelExecutor:
         self.graph_launches: Dict[Any, int] = {}
         self.last_key = None       # graph key of the step enqueued last (None: it did not run from a graph)
         self._unsplit: Dict[int, bool] = {}
+        # decode steps issue the attention CTAs of long requests first (OGB_ATTN_ORDER=0: in batch order)
+        self.order_attention = self.use_graphs and os.environ.get("OGB_ATTN_ORDER", "1") != "0"
 
-    def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int) -> StepInputs:
+    def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int, ordered: bool = False) -> StepInputs:
         st = self.staging
         table = st.view("block_table").view(st.max_batch, st.table_cols)[:B, :cols]
         s = StepInputs(input_ids=st.view("input_ids", T), positions=st.view("positions", T), slot_mapping=st.view("slot_mapping", T),
@@ -198,6 +206,8 @@ class ModelExecutor:
         if self.windowed:
             s.slot_mapping_w = st.view("slot_mapping_w", T)
             s.block_table_w = st.view("block_table_w").view(st.max_batch, st.table_cols)[:B, :cols]
+        if ordered:
+            s.attn_order = st.view("attn_order", B)
         return s
 
     @staticmethod
@@ -253,12 +263,18 @@ class ModelExecutor:
             if self.windowed:
                 o, _ = st.layout["slot_mapping_w"]
                 h[o + T:o + bb] = -1
+        if self.order_attention:
+            # requests by cached length, longest first: the order in which the attention kernel issues its CTAs
+            hn = st.host_np()
+            o, _ = st.layout["past_lens"]
+            oo, _ = st.layout["attn_order"]
+            hn[oo:oo + bb] = np.argsort(-hn[o:o + bb], kind="stable")
         st.upload()
         return key
 
     def _capture(self, bb: int, cb: int):
         st = self.staging
-        s = self._step_inputs(bb, bb, st.table_cols, 1, cb * self.kv.block_size)
+        s = self._step_inputs(bb, bb, st.table_cols, 1, cb * self.kv.block_size, ordered=self.order_attention)
         tp = self.decoder.tp
         if tp.size > 1:
             tp.barrier()   # ranks enter warm-up and capture together (peer waits in the fused kernels are bounded)

@@ -36,6 +36,7 @@ class StepInputs:
     max_q_len: int = 1
     max_kv_len: int = 1
     inputs_embeds: Optional[torch.Tensor] = None  # overrides the embedding lookup (multimodal / MTP)
+    attn_order: Optional[torch.Tensor] = None     # [B] int32 permutation of the requests, longest first (attention CTA issue order)
     cross: Optional["CrossKVCache"] = None        # encoder keys / values of an encoder-decoder model
     cross_table: Optional[torch.Tensor] = None    # [B, cols] blocks of each request's encoder keys in `cross`
     cross_lens: Optional[torch.Tensor] = None     # [B] encoder positions per request
@@ -341,7 +342,7 @@ class DecoderModel:
                                a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
-                                      max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
+                                      max_q_len=s.max_q_len, max_kv_len=s.max_kv_len, order=s.attn_order)
             h = self._row_parallel(att, lw.o_w, lw.o_b, self._lora(lw, "o_proj"))
             if lw.cross_q_w is not None:
                 if s.cross is None:

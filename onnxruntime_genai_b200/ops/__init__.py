@@ -378,7 +378,7 @@ def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_c
 
 
 def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale, window=0,
-                    sinks=None, softcap=0.0, max_q_len=None, max_kv_len=None, splits=None, out=None, total_tokens=None):
+                    sinks=None, softcap=0.0, max_q_len=None, max_kv_len=None, splits=None, out=None, total_tokens=None, order=None):
     """q: [T, stride] with the Hq*D query columns first.  Returns [T, Hq*D]."""
     if not q.is_cuda:
         return ref.paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
@@ -401,7 +401,7 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
                                         _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0),
                                         _ptr(sinks), float(scale), float(softcap), int(window), B, q.shape[0], int(max_q_len),
                                         Hq, Hkv, D, int(splits), int(kv_chunk), _ptr(scratch),
-                                        scratch.numel() if scratch is not None else 0, int(k_cache.shape[0]), ws.status, _stream())
+                                        scratch.numel() if scratch is not None else 0, int(k_cache.shape[0]), _ptr(order), ws.status, _stream())
     _lib.check(rc, "paged_attention")
     if splits > 1:
         _lib.LAUNCH_COUNT += 1  # the combine kernel

@@ -49,7 +49,7 @@ _SIGS = {
     "ogb_gather_rows": (c_int, [_P, _P, _P, c_int, c_int, _P]),
     "ogb_attention_scratch_bytes": (c_longlong, [c_int, c_int, c_int, c_int]),
     "ogb_paged_attention": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
-                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P]),
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
     "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),
     "ogb_topk": (c_int, [_P, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P]),

@@ -80,6 +80,7 @@ def _peaks():
 
 NO_FUSED = False     # --tp shapes without the fused all-reduce (the GEMM alone)
 ATTN_SPLITS = None   # None: the library's choice; (splits, kv_chunk) to force one
+ATTN_ORDER = False   # --attn_order: longest request first
 
 
 def build_case(name, T, L, tp=1):
@@ -136,9 +137,10 @@ def build_case(name, T, L, tp=1):
         kv_tokens = sum(p + q for p, q in zip(past, q_lens))
         nbytes = kv_tokens * HKV * D * 2 * 2 + Tq * HQ * D * 2 * 2
         flops = sum(4.0 * HQ * D * (q * p + q * (q + 1) / 2) for p, q in zip(past, q_lens))
+        order = torch.argsort(-pl.long(), stable=True).to(torch.int32) if ATTN_ORDER else None   # longest request first
         return (lambda i: ops.paged_attention(qkv, kc[i % Lk], vc[i % Lk], cu, pl, table, bs, HQ, HKV, D, 1 / math.sqrt(D),
                                               max_q_len=max(q_lens), max_kv_len=max(p + q for p, q in zip(past, q_lens)),
-                                              splits=ATTN_SPLITS)), nbytes, flops
+                                              splits=ATTN_SPLITS, order=order)), nbytes, flops
     if name == "norm":
         x, r, w = _bf(T, H, std=1.0), _bf(T, H, std=1.0), _bf(H, std=1.0)
         return (lambda i: ops.norm(x, w, 1e-5, r)), T * H * 2 * 4, 0.0
@@ -176,10 +178,12 @@ def main():
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA graph (for profilers; includes launch gaps)")
     ap.add_argument("--no_fused", action="store_true", help="with --tp: run the row-parallel GEMMs without the fused all-reduce")
     ap.add_argument("--attn_splits", default="", help="force the attention split: 'S' (even division) or 'S,chunk' (fixed key ranges)")
+    ap.add_argument("--attn_order", action="store_true", help="issue the attention CTAs of the longest requests first")
     ap.add_argument("--tp", type=int, default=1, help="use the per-rank shapes of this tensor-parallel degree")
     a = ap.parse_args()
     torch.manual_seed(0)
     globals()["NO_FUSED"] = a.no_fused
+    globals()["ATTN_ORDER"] = a.attn_order
     if a.attn_splits:
         v = [int(x) for x in a.attn_splits.split(",")]
         globals()["ATTN_SPLITS"] = v[0] if len(v) == 1 else (v[0], v[1])

@@ -306,7 +306,7 @@ def test_decode_advance_matches_reference():
 
 
 # ------------------------------------------------------------------------------------------- attention
-def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, softcap=0.0, splits=None, seed=30):
+def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, softcap=0.0, splits=None, seed=30, order=False):
     rng = np.random.RandomState(seed)
     T = sum(q_lens)
     cols = max((p + q + bs - 1) // bs for p, q in zip(past, q_lens))
@@ -327,7 +327,7 @@ def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, soft
     scale = 1.0 / math.sqrt(D)
     out = ops.paged_attention(q, k_cache, v_cache, cu.to(DEV), pl.to(DEV), table.to(DEV), bs, Hq, Hkv, D, scale, window,
                               sk.to(DEV) if sinks else None, softcap, max_q_len=max(q_lens), max_kv_len=max(p + q for p, q in zip(past, q_lens)),
-                              splits=splits)
+                              splits=splits, order=torch.argsort(-pl.long(), stable=True).to(torch.int32).to(DEV) if order else None)
     want = ref.paged_attention(q.cpu(), k_cache.cpu(), v_cache.cpu(), cu, pl, table, bs, Hq, Hkv, D, scale, window, sk, softcap)
     _close(out, want, rtol=3e-2, atol=3e-2)
 
@@ -339,6 +339,13 @@ def test_attention_bidirectional_over_cached_keys(splits):
     _attention_case(B=3, q_lens=[70, 9, 33], past=[70, 150, 1500], Hq=8, Hkv=8, D=64, bs=16, window=-1, splits=splits)
     _attention_case(B=4, q_lens=[1] * 4, past=[1, 64, 333, 1500], Hq=12, Hkv=12, D=64, bs=16, window=-1, splits=splits)
     _attention_case(B=2, q_lens=[40, 17], past=[40, 17], Hq=8, Hkv=2, D=128, bs=16, window=-1, splits=splits)
+
+
+@pytest.mark.parametrize("splits", [None, 3])
+def test_attention_longest_first_issue_order(splits):
+    """A permutation of the requests only changes which CTA serves which request."""
+    _attention_case(B=7, q_lens=[1] * 7, past=[5, 900, 64, 2047, 130, 0, 333], Hq=32, Hkv=8, D=128, bs=16, splits=splits, order=True)
+    _attention_case(B=3, q_lens=[33, 1, 8], past=[0, 700, 40], Hq=8, Hkv=2, D=64, bs=16, splits=splits, order=True)
 
 
 @pytest.mark.parametrize("D", [64, 96, 128])
