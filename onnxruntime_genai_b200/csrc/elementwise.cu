@@ -5,6 +5,7 @@
 // residual sum (src/python/py/models/builders/base.py:2342-2403); RotaryEmbedding uses
 // cos/sin caches of shape [ctx, rot/2] with an interleaved flag (base.py:2565-2637); PagedAttention
 // appends the new K/V rows at slots derived from the block table (base.py:3484-3536).
+#include <cuda_fp16.h>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -31,6 +32,37 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const uint4* _
       }
     }
     dst[i] = v;
+  }
+}
+
+// Embedding rows gathered straight from an int4 block-32 weight (GatherBlockQuantized over the tied LM-head weight):
+// q [vocab, K / 2] bytes (low nibble = even k), scales fp16 [vocab, K / 32], zero points packed two per byte
+// [vocab, ceil(K / 64)] or null (8).  out[t, k] = (q - zp) * scale * mult, restated in bf16 exactly like the int4 GEMM's
+// dequantisation.  One CTA per token, eight values (four bytes) per thread.
+__global__ void embedding_q4_kernel(const int32_t* __restrict__ ids, const uint32_t* __restrict__ q, const __half* __restrict__ scales,
+                                    const uint8_t* __restrict__ zps, uint4* __restrict__ out, int K, int vocab, float mult) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const int nb = K / 32, zp_pitch = (nb + 1) / 2;
+  const uint32_t* row = q + size_t(id) * (K / 8);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    const uint32_t w = __ldg(row + i);
+    const int blk = i / 4;
+    const float sc = bf2f(f2bf(__half2float(scales[size_t(id) * nb + blk])));
+    int zp = 8;
+    if (zps) { const uint8_t z = zps[size_t(id) * zp_pitch + blk / 2]; zp = (blk & 1) ? (z >> 4) : (z & 0xF); }
+    uint4 o;
+    __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int nib = (w >> (4 * j)) & 0xF;
+      const float v = bf2f(f2bf(float(nib - zp) * sc));
+      oe[j] = f2bf(mult == 1.f ? v : v * mult);
+    }
+    out[size_t(t) * (K / 8) + i] = o;
   }
 }
 
@@ -347,6 +379,15 @@ OGB_API int ogb_embedding(const int32_t* ids, const void* table, void* out, int 
   launch_pdl(embedding_kernel, dim3(T), dim3(min(256, H / 8)), 0, static_cast<cudaStream_t>(stream),
       ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), H / 8, vocab, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_embedding_q4(const int32_t* ids, const void* q, const void* scales, const void* zps, void* out, int T, int K, int vocab,
+                             float mult, void* stream) {
+  if (T <= 0) return 0;
+  if (K % 32) return -1;
+  return launch_pdl(embedding_q4_kernel, dim3(T), dim3(min(256, K / 8)), 0, static_cast<cudaStream_t>(stream), ids,
+                    static_cast<const uint32_t*>(q), static_cast<const __half*>(scales), static_cast<const uint8_t*>(zps),
+                    static_cast<uint4*>(out), K, vocab, mult) ? 0 : -4;
 }
 
 OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias,

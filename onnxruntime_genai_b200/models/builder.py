@@ -268,7 +268,8 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                  synthetic_weights: bool = False, search: Optional[dict] = None, engine: Optional[dict] = None,
                  filename: str = "model.onnx", write_config: bool = True, speculative: Optional[dict] = None,
                  draft_dir_entry: Optional[dict] = None, num_blocks: Optional[int] = None,
-                 max_scheduled_tokens: Optional[int] = None, context_length: Optional[int] = None) -> str:
+                 max_scheduled_tokens: Optional[int] = None, context_length: Optional[int] = None,
+                 int4_tied_embeddings: bool = False) -> str:
     """Writes a checkpoint directory.  With state_dict=None the weights are random N(0, std) from `seed`."""
     os.makedirs(out_dir, exist_ok=True)
     if precision not in ("fp32", "fp16", "bf16", "int4"):
@@ -337,10 +338,22 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
     io_dt = _ONNX_DT[W.io]
 
     # ---- embedding
-    put_plain("model.embed_tokens.weight", ["model.embed_tokens.weight"],
-              {"shape": (V, H), "op": "id", "fn": lambda ts: ts[0].float()})
-    W.node("Gather", "/model/embed_tokens/Gather", ["model.embed_tokens.weight", "input_ids"], ["/model/embed_tokens/Gather/output_0"])
-    hidden = "/model/embed_tokens/Gather/output_0"
+    tied_q4 = int4_tied_embeddings and precision == "int4" and arch.tie_embeddings
+    if tied_q4:
+        # one int4 tensor serves the LM head (MatMulNBits) and the embedding (rows gathered and dequantised by block)
+        W.model.initializers["/model/constants/INT64/embed_shape"] = op.Tensor("/model/constants/INT64/embed_shape", op.INT64, (2,),
+                                                                               raw=np.asarray([V, H // 2], dtype=np.int64).tobytes())
+        W.node("Reshape", "/model/embed_tokens/Reshape", ["lm_head.MatMul.weight_Q4", "/model/constants/INT64/embed_shape"],
+               ["/model/embed_tokens/Reshape/output_0"])
+        gins = ["/model/embed_tokens/Reshape/output_0", "input_ids", "lm_head.MatMul.weight_scales"] + ([] if int4_symmetric else ["lm_head.MatMul.weight_zp"])
+        W.node("GatherBlockQuantized", "/model/embed_tokens/GatherBlockQuantized", gins, ["/model/embed_tokens/GatherBlockQuantized/output_0"],
+               domain="com.microsoft", bits=4, block_size=32, gather_axis=0, quantize_axis=1)
+        hidden = "/model/embed_tokens/GatherBlockQuantized/output_0"
+    else:
+        put_plain("model.embed_tokens.weight", ["model.embed_tokens.weight"],
+                  {"shape": (V, H), "op": "id", "fn": lambda ts: ts[0].float()})
+        W.node("Gather", "/model/embed_tokens/Gather", ["model.embed_tokens.weight", "input_ids"], ["/model/embed_tokens/Gather/output_0"])
+        hidden = "/model/embed_tokens/Gather/output_0"
     if arch.embed_scale != 1.0:
         W.model.initializers["/model/constants/embed_scale"] = op.Tensor("/model/constants/embed_scale", op.FLOAT, (),
                                                                          raw=np.float32(arch.embed_scale).tobytes())
@@ -865,7 +878,8 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         paged=bool(int(extra.get("paged_attention", extra.get("use_paged_attention", 0)))),
         block_size=int(extra.get("paged_block_size", 16)), max_batch_size=int(extra.get("max_batch_size", 64)),
         int4_symmetric=bool(int(extra.get("int4_is_symmetric", 0))), synthetic_weights=bool(int(extra.get("synthetic_weights", 0))),
-        filename=extra.get("filename", "model.onnx"), context_length=int(extra["context_length"]) if "context_length" in extra else None)
+        filename=extra.get("filename", "model.onnx"), context_length=int(extra["context_length"]) if "context_length" in extra else None,
+        int4_tied_embeddings=bool(int(extra.get("int4_tied_embeddings", 0))))
 
 
 def main(argv=None):

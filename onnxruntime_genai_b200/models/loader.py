@@ -275,8 +275,21 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
     def shard_rows(w: torch.Tensor, slices) -> torch.Tensor:
         return torch.cat([w[s] for s in slices], 0).contiguous() if tpn > 1 else w
 
-    emb = g.tensor("model.embed_tokens.weight", device=device)
-    model.embed = emb.to(device=device, dtype=dtype).contiguous()
+    gq = g.by_name.get("/model/embed_tokens/GatherBlockQuantized")
+    if gq is not None:
+        # Tied quantised embedding: the rows of the int4 LM-head weight (through a Reshape to [vocab, hidden / 2] bytes).  On a
+        # CUDA device the table stays int4 and rows are dequantised as they are gathered; elsewhere it is expanded once.
+        from ..ops.w4 import QuantizedEmbedding
+        rs = g.by_name[gq.inputs[0].rsplit("/", 1)[0]] if gq.inputs[0].endswith("/output_0") else None
+        wname = rs.inputs[0] if rs is not None else gq.inputs[0]
+        V, Kh = arch.vocab_size, arch.hidden_size
+        has_zp = len(gq.inputs) > 3 and gq.inputs[3]
+        qe = QuantizedEmbedding(g.tensor(wname, device=device).reshape(V, Kh // 2).to(device), g.tensor(gq.inputs[2], device=device).to(device).view(V, -1),
+                                g.tensor(gq.inputs[3], device=device).to(device).view(V, -1) if has_zp else None, V, Kh)
+        model.embed = qe if torch.device(device).type == "cuda" else qe.dequantize(dtype).contiguous()
+    else:
+        emb = g.tensor("model.embed_tokens.weight", device=device)
+        model.embed = emb.to(device=device, dtype=dtype).contiguous()
     cos, sin = g.tensor("cos_cache").float(), g.tensor("sin_cache").float()
     model.cos, model.sin = cos.to(device).contiguous(), sin.to(device).contiguous()
     if arch.learned_positions:

@@ -14,7 +14,7 @@ import torch
 
 from . import reference as ref
 from . import _lib
-from .w4 import W4Weight, unpack_ort_q4
+from .w4 import QuantizedEmbedding, W4Weight, unpack_ort_q4
 
 _ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "gelu_erf": 3}
 
@@ -75,7 +75,15 @@ def check_kernel_status(device=None) -> None:
 
 
 # ------------------------------------------------------------------------------------------ embedding
-def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+def embedding(ids: torch.Tensor, table, scale: float = 1.0) -> torch.Tensor:
+    if isinstance(table, QuantizedEmbedding):
+        if table.device.type != "cuda":
+            return ref.embedding(ids, table.dequantize(), scale)
+        T = ids.numel()
+        out = torch.empty(T, table.K, dtype=torch.bfloat16, device=table.device)
+        _lib.check(_lib.lib().ogb_embedding_q4(_ptr(ids), _ptr(table.q), _ptr(table.scales), _ptr(table.zp), _ptr(out), T, table.K,
+                                              table.V, float(scale), _stream()), "embedding_q4")
+        return out
     if not table.is_cuda:
         return ref.embedding(ids, table, scale)
     assert table.dtype == torch.bfloat16 and ids.dtype == torch.int32

@@ -74,3 +74,32 @@ def unpack_ort_q4(qweight: torch.Tensor, zero_points: Optional[torch.Tensor], N:
         z = torch.as_tensor(zero_points).view(N, -1)
         zp = torch.stack([z & 0xF, z >> 4], dim=-1).view(N, -1)[:, :K // 32].contiguous()
     return q.contiguous(), zp
+
+
+class QuantizedEmbedding:
+    """An embedding table kept as the int4 block-32 tensors of a tied LM head (GatherBlockQuantized): q uint8 [V, K/2]
+    (low nibble = even k), scales fp16 [V, K/32], zero points uint8 packed two per byte [V, ceil(K/64)] or None (8).
+    `ops.embedding` gathers and dequantises rows on the fly; 5 bits per weight of HBM instead of 16."""
+    dtype = torch.bfloat16
+
+    def __init__(self, q: torch.Tensor, scales: torch.Tensor, zp: Optional[torch.Tensor], V: int, K: int):
+        self.q, self.scales, self.zp, self.V, self.K = q.contiguous(), scales.contiguous(), zp.contiguous() if zp is not None else None, V, K
+        self.shape = (V, K)
+
+    @property
+    def device(self):
+        return self.q.device
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        """[V, K] exactly as the gather kernel reconstructs the rows (bf16 roundings included)."""
+        V, K = self.V, self.K
+        nb = K // 32
+        qb = self.q.view(V, K // 2)
+        qv = torch.stack([qb & 0xF, qb >> 4], dim=-1).view(V, nb, 32).float()
+        if self.zp is not None:
+            z = self.zp.view(V, -1)
+            zp = torch.stack([z & 0xF, z >> 4], dim=-1).view(V, -1)[:, :nb].float()
+        else:
+            zp = torch.full((V, nb), 8.0, device=self.q.device)
+        sc = self.scales.view(V, nb).float().to(torch.bfloat16).float()
+        return ((qv - zp[:, :, None]) * sc[:, :, None]).to(torch.bfloat16).to(dtype).view(V, K)

@@ -118,6 +118,35 @@ def test_int4_checkpoint_roundtrip(tmp_path):
     assert np.corrcoef(got, fp)[0, 1] > 0.9, "int4 logits must stay close to the fp32 model"
 
 
+def test_int4_tied_quantized_embedding(tmp_path):
+    """int4 + tied embeddings: one int4 tensor is both the LM head (MatMulNBits) and the embedding table
+    (GatherBlockQuantized over its rows); no dense embedding is stored."""
+    from onnxruntime_genai_b200.models.builder import dequantize_int4_block32, quantize_int4_block32
+    from onnxruntime_genai_b200.ops.w4 import QuantizedEmbedding
+    from onnxruntime_genai_b200.utils import onnx_proto as op
+    arch = ArchConfig(**{**BASE, "model_type": "qwen3", "qk_norm": True, "tie_embeddings": True})
+    sd = random_state_dict(arch, seed=9, std=0.1)
+    for sym in (False, True):
+        d = str(tmp_path / f"sym{int(sym)}")
+        export_model(copy.deepcopy(arch), d, "int4", "cpu", state_dict=sd, int4_tied_embeddings=True, int4_symmetric=sym)
+        names = op.LoadedModel(d + "/model.onnx").names()
+        assert "model.embed_tokens.weight" not in names and "lm_head.MatMul.weight_Q4" in names
+        model = og.Model(d)
+        q, s, zp = quantize_int4_block32(sd["model.embed_tokens.weight"], symmetric=sym)
+        want = dequantize_int4_block32(q, s.to(torch.float16).float(), zp, arch.vocab_size, arch.hidden_size)
+        torch.testing.assert_close(model.decoder.embed.float(), want, rtol=2e-2, atol=1e-3)
+        # the table object used on a GPU restates the same rows
+        qe = QuantizedEmbedding(q.reshape(arch.vocab_size, -1), s.to(torch.float16).view(arch.vocab_size, -1),
+                                zp.reshape(arch.vocab_size, -1) if zp is not None else None, arch.vocab_size, arch.hidden_size)
+        torch.testing.assert_close(qe.dequantize(), want, rtol=2e-2, atol=1e-3)
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=20)
+        g = og.Generator(model, p)
+        g.append_tokens(np.arange(1, 12, dtype=np.int32).reshape(1, -1))
+        fp = dense_logits(arch, sd, list(range(1, 12)))[-1].numpy()
+        assert np.corrcoef(g.get_logits().reshape(-1), fp)[0, 1] > 0.9
+
+
 @pytest.mark.parametrize("family", ["llama", "lfm2_hybrid"])
 def test_beam_search_cache_sharing_matches_full_recompute(family, tmp_path):
     """Beam reordering permutes block tables and copies blocks on write; every row's logits must still equal a

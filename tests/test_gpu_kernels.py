@@ -251,6 +251,21 @@ def test_embedding_gather_actmul_cast():
     assert torch.equal(ops.to_float32(x), x.float())
 
 
+@pytest.mark.parametrize("sym", [False, True])
+def test_embedding_q4_gather_matches_dequantised_rows(sym):
+    from onnxruntime_genai_b200.models.builder import quantize_int4_block32
+    from onnxruntime_genai_b200.ops.w4 import QuantizedEmbedding
+    V, K = 777, 320
+    w = torch.randn(V, K, generator=torch.Generator().manual_seed(3)) * 0.1
+    q, s, zp = quantize_int4_block32(w, symmetric=sym)
+    qe = QuantizedEmbedding(q.reshape(V, -1).to(DEV), s.to(torch.float16).view(V, -1).to(DEV), zp.reshape(V, -1).to(DEV) if zp is not None else None, V, K)
+    ids = torch.tensor([0, 5, 776, 17, 5, 900], dtype=torch.int32, device=DEV)     # the last id is clamped
+    table = qe.dequantize()
+    want = table[ids.long().clamp(max=V - 1)]
+    assert torch.equal(ops.embedding(ids, qe).float(), want)
+    _close(ops.embedding(ids, qe, 3.0), want * 3.0, rtol=1e-2, atol=1e-2)
+
+
 @pytest.mark.parametrize("L,bias", [(3, False), (4, True)])
 def test_short_conv_matches_reference(L, bias):
     """Prefill chunks, single-token rows and a chunk continuing a cached prefix in one packed launch; the paged cache after
