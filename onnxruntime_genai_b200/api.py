@@ -179,6 +179,14 @@ class Model:
                 self.multimodal["vision"] = sec
                 self.image_token_id = int(tree.get("image_token_id", -1))
         self.arch = self.decoder.arch
+        # KV-cache quantisation is a provider option of the decoder session (reference: src/config_utils.cpp:13-45)
+        self.kv_bits = 16
+        for _, opts in c.decoder["provider_options"]:
+            bits = str(dict(opts).get("kvCacheQuantizationBits", "0"))
+            if bits not in ("0", "8"):
+                raise RuntimeError(f"kvCacheQuantizationBits={bits} is not supported (0 or 8)")
+            if bits == "8":
+                self.kv_bits = 8
         self.graph_capture = bool(c.decoder.get("graph_capture", False))
         if self.draft is not None and self.draft.arch.vocab_size != self.arch.vocab_size:
             raise RuntimeError("speculative decoding: draft and target vocabularies differ")
@@ -252,14 +260,14 @@ def _sampling_method(search: Dict[str, Any], vocab: int):
 class SequenceState:
     """Device state of a static batch: paged KV with one contiguous run of blocks per row."""
 
-    def __init__(self, decoder, rows: int, max_length: int, block_size: int = 16):
+    def __init__(self, decoder, rows: int, max_length: int, block_size: int = 16, kv_bits: int = 16):
         self.decoder = decoder
         self.rows = rows
         self.block_size = block_size
         self.blocks_per_row = (max_length + block_size - 1) // block_size
         dev = decoder.device
         self.kv = PagedKVCache(decoder.arch, rows * self.blocks_per_row, block_size, dev, decoder.dtype,
-                               kv_heads=decoder.kv_heads_local, conv_channels=decoder.conv_channels_local)
+                               kv_heads=decoder.kv_heads_local, conv_channels=decoder.conv_channels_local, kv_bits=kv_bits)
         self.block_table = (torch.arange(rows * self.blocks_per_row, dtype=torch.int32).view(rows, self.blocks_per_row)).to(dev)
         self.kv_len = [0] * rows
         # Beam search shares cache blocks between rows (copy-on-write at block granularity).  Until the first reorder every
@@ -485,7 +493,7 @@ class Generator:
         self._sp = sp
         self.search = native.Search(sp)
         self.rows = s["batch_size"] * s["num_beams"]
-        self.state = SequenceState(model.decoder, self.rows, s["max_length"])
+        self.state = SequenceState(model.decoder, self.rows, s["max_length"], kv_bits=model.kv_bits)
         self._logits: Optional[torch.Tensor] = None
         self._fresh = False
         self._started = False

@@ -52,6 +52,9 @@ struct AttnParams {
   // gets longest-processing-time-first scheduling (CTAs are dispatched in block-index order) - with a mix of 128..2300
   // cached keys per request and fewer than two waves of CTAs the tail of a late long request otherwise sets the time.
   const int32_t* order;
+  // 8-bit cache: a (slot, head) row is head_dim int8 values followed by their fp32 scale and 12 bytes of padding
+  // (row pitch head_dim + 16); k_cache / v_cache then point at bytes.
+  int kv8;
 };
 
 template <int SROW>
@@ -64,7 +67,9 @@ __device__ __forceinline__ int swz(int row, int chunk) {  // element offset of a
 // (16 keys each), keeping private online-softmax state that is merged through shared memory at the
 // end.  DECODE = false: each warp owns 16 of the 64 query rows and walks the whole tile.
 // TMA = true: K/V tiles arrive as [half row of 64 dims][64 keys][128 bytes] boxes with the 128-byte swizzle.
-template <int D, bool DECODE, bool TMA>
+// KV8 = true: the cache holds int8 rows with an inline scale; raw tiles are staged by cp.async (three in flight) and
+// expanded to one bf16 K tile and one bf16 V tile per iteration, so the tensor-core part is the same code.
+template <int D, bool DECODE, bool TMA, bool KV8 = false>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, AttnParams p) {
   constexpr int SROW = ((D + 63) / 64) * 64;
@@ -78,8 +83,11 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   uint8_t* smem_raw = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023)) : smem_dyn;
   __shared__ uint64_t kv_full[ATT_STAGES];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* sK = sQ + BM * SROW;                        // [STAGES][BN][SROW]
-  __nv_bfloat16* sV = sK + ATT_STAGES * ATT_BN * SROW;       // [STAGES][BN][SROW]
+  constexpr int BF_STAGES = KV8 ? 1 : ATT_STAGES;
+  constexpr int RP = D + 16;                                 // bytes of an int8 cache row (KV8)
+  __nv_bfloat16* sK = sQ + BM * SROW;                        // [BF_STAGES][BN][SROW]
+  __nv_bfloat16* sV = sK + BF_STAGES * ATT_BN * SROW;        // [BF_STAGES][BN][SROW]
+  uint8_t* sRaw = reinterpret_cast<uint8_t*>(sV + BF_STAGES * ATT_BN * SROW);   // KV8: [STAGES][K, V][BN][RP]
 
   pdl_launch_dependents();
   pdl_wait();
@@ -181,6 +189,58 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     }
   };
 
+  // KV8: each warp copies the raw bytes of 16 key rows (values + inline scale); rows past the range are zero-filled, which
+  // makes their scale 0 and their expanded values 0.
+  auto load_kv8 = [&](int tile, int buf) {
+    constexpr int RCH = RP / 16;
+    const int jrow = tile * ATT_BN + warp * 16 + (lane & 15);
+    int slot = -1;
+    if (jrow < kv_hi) slot = table[jrow / p.block_size] * p.block_size + jrow % p.block_size;
+    const uint8_t* kc = reinterpret_cast<const uint8_t*>(p.k_cache);
+    const uint8_t* vc = reinterpret_cast<const uint8_t*>(p.v_cache);
+    uint8_t* dk = sRaw + size_t(buf * 2) * ATT_BN * RP;
+    uint8_t* dv = dk + ATT_BN * RP;
+#pragma unroll
+    for (int c = 0; c < (16 * RCH + 31) / 32; ++c) {
+      const int item = c * 32 + lane;
+      const int kl = min(item / RCH, 15), ch = item % RCH;
+      const int sl = __shfl_sync(0xffffffffu, slot, kl);
+      if (item < 16 * RCH) {
+        const bool ok = sl >= 0;
+        const size_t off = ok ? (size_t(sl) * p.Hkv + kvh) * RP + ch * 16 : 0;
+        const int key = warp * 16 + kl;
+        cp_async16(dk + key * RP + ch * 16, kc + off, ok);
+        cp_async16(dv + key * RP + ch * 16, vc + off, ok);
+      }
+    }
+  };
+  // KV8: expands raw stage `buf` into the bf16 K and V tiles (value * scale, rounded to bf16).
+  auto expand_kv8 = [&](int buf) {
+    constexpr int VCH = D / 16;          // 16-byte chunks of int8 values per row
+    const uint8_t* rk = sRaw + size_t(buf * 2) * ATT_BN * RP;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint8_t* src = rk + which * ATT_BN * RP;
+      __nv_bfloat16* dst = which ? sV : sK;
+      for (int item = tid; item < ATT_BN * VCH; item += ATT_THREADS) {
+        const int key = item / VCH, c = item % VCH;
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + key * RP + c * 16);
+        const float sc = *reinterpret_cast<const float*>(src + key * RP + D);
+        const int8_t* qv = reinterpret_cast<const int8_t*>(&raw);
+        uint4 lo, hi;
+        uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+        uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          lw[j] = pack_bf16x2(float(qv[2 * j]) * sc, float(qv[2 * j + 1]) * sc);
+          hw[j] = pack_bf16x2(float(qv[8 + 2 * j]) * sc, float(qv[8 + 2 * j + 1]) * sc);
+        }
+        *reinterpret_cast<uint4*>(dst + swz<SROW>(key, 2 * c)) = lo;
+        *reinterpret_cast<uint4*>(dst + swz<SROW>(key, 2 * c + 1)) = hi;
+      }
+    }
+  };
+
   // Q tile (zero rows beyond the request's rows).
   for (int c = tid; c < BM * CHUNKS; c += ATT_THREADS) {
     const int r = c / CHUNKS, ch = c % CHUNKS;
@@ -196,6 +256,11 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       if (n_tiles > 1) load_kv_tma(tile_begin + 1, 1);
     }
     cp_async_commit();   // the Q tile
+  } else if (KV8) {
+    if (n_tiles > 0) load_kv8(tile_begin, 0);
+    cp_async_commit();
+    if (n_tiles > 1) load_kv8(tile_begin + 1, 1);
+    cp_async_commit();
   } else {
     if (n_tiles > 0) load_kv(tile_begin, 0);
     cp_async_commit();
@@ -229,6 +294,13 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         atomicMax(p.status, OGB_ERR_WAIT_TMA);
         kv_dead = true;
       }
+    } else if (KV8) {
+      if (it + 2 < n_tiles) load_kv8(tile_begin + it + 2, (it + 2) % ATT_STAGES);
+      cp_async_commit();
+      cp_async_wait<2>();
+      __syncthreads();          // raw stage `buf` has landed; every warp is done with the bf16 tiles of the last iteration
+      expand_kv8(buf);
+      __syncthreads();
     } else {
       if (it + 2 < n_tiles) load_kv(tile_begin + it + 2, (it + 2) % ATT_STAGES);
       cp_async_commit();
@@ -243,8 +315,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       }
     }
     if (warp_active) {
-      const __nv_bfloat16* tk = sK + buf * ATT_BN * SROW;
-      const __nv_bfloat16* tv = sV + buf * ATT_BN * SROW;
+      const __nv_bfloat16* tk = sK + (KV8 ? 0 : buf) * ATT_BN * SROW;
+      const __nv_bfloat16* tv = sV + (KV8 ? 0 : buf) * ATT_BN * SROW;
       float s[NT][4];
 #pragma unroll
       for (int i = 0; i < NT; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
@@ -464,14 +536,16 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
 
-template <int D, bool DECODE, bool TMA>
+template <int D, bool DECODE, bool TMA, bool KV8 = false>
 static int LaunchAttentionMode(const AttnParams& p, int max_q_len, int cache_slots, cudaStream_t stream) {
   constexpr int SROW = ((D + 63) / 64) * 64;
   constexpr int BM = DECODE ? 16 : ATT_BM;
-  constexpr int SMEM = (BM + 2 * ATT_STAGES * ATT_BN) * SROW * 2 + (TMA ? 1024 : 0);
-  static_assert(!DECODE || (4 * 16 * D + 4 * 16 * 2) * 4 <= ATT_STAGES * ATT_BN * SROW * 2, "merge buffers must fit in the K stages");
+  constexpr int KV_BYTES = KV8 ? 2 * ATT_BN * SROW * 2 + ATT_STAGES * 2 * ATT_BN * (D + 16) : 2 * ATT_STAGES * ATT_BN * SROW * 2;
+  constexpr int SMEM = BM * SROW * 2 + KV_BYTES + (TMA ? 1024 : 0);
+  // decode mode parks the four warps' partial states in the (idle) K/V area, which starts at the K tile and is contiguous
+  static_assert(!DECODE || (4 * 16 * D + 4 * 16 * 2) * 4 <= (KV8 ? KV_BYTES : ATT_STAGES * ATT_BN * SROW * 2), "merge buffers must fit in the K/V area");
   static bool configured = false;
-  auto kern = paged_attention_kernel<D, DECODE, TMA>;
+  auto kern = paged_attention_kernel<D, DECODE, TMA, KV8>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
     configured = true;
@@ -505,13 +579,17 @@ static int LaunchAttention(const AttnParams& p, int max_q_len, int cache_slots, 
   // issuing thread, two tiles ahead) run at 0.52 of the copy bandwidth against 0.68 for the cp.async gather below.
   static const int tma_enabled = [] { const char* e = getenv("OGB_ATTN_TMA"); return (e && e[0] == '1') ? 1 : 0; }();
   // TMA path: whole 16-key groups inside one cache block, 128-byte half rows, aligned cache, a status word for the waits
-  const bool tma = tma_enabled && (D == 64 || D == 128) && p.block_size % 16 == 0 && cache_slots >= 16 && p.status != nullptr &&
+  const bool tma = tma_enabled && !p.kv8 && (D == 64 || D == 128) && p.block_size % 16 == 0 && cache_slots >= 16 && p.status != nullptr &&
                    ((reinterpret_cast<uintptr_t>(p.k_cache) | reinterpret_cast<uintptr_t>(p.v_cache)) & 15) == 0;
   if constexpr (D == 64 || D == 128) {
     if (tma) {
       if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, true>(p, max_q_len, cache_slots, stream);
       return LaunchAttentionMode<D, false, true>(p, max_q_len, cache_slots, stream);
     }
+  }
+  if (p.kv8) {
+    if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, false, true>(p, max_q_len, cache_slots, stream);
+    return LaunchAttentionMode<D, false, false, true>(p, max_q_len, cache_slots, stream);
   }
   if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, false>(p, max_q_len, cache_slots, stream);
   return LaunchAttentionMode<D, false, false>(p, max_q_len, cache_slots, stream);
@@ -527,12 +605,13 @@ OGB_API long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, i
   return (long long)splits * total_tokens * Hq * (D + 2) * 4;
 }
 
-OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
-                                const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
-                                int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
-                                int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
-                                long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_) {
+static int PagedAttention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                          const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                          int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                          int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
+                          long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_, int kv_bits) {
   if (B <= 0 || total_tokens <= 0) return 0;
+  if (kv_bits != 16 && kv_bits != 8) return -1;
   if (Hkv <= 0 || Hq % Hkv || (q_stride % 8) || (out_stride % 2)) return -1;
   if (splits < 1) splits = 1;
   if (kv_chunk < 0 || (kv_chunk % ATT_BN)) return -1;
@@ -541,6 +620,7 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
   p.chunk = splits > 1 ? kv_chunk : 0;
   p.status = status;
   p.order = order;
+  p.kv8 = kv_bits == 8;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.block_table = block_table; p.table_cols = table_cols;
@@ -557,6 +637,27 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
     case 128: return LaunchAttention<128>(p, max_q_len, cache_slots, stream);
   }
   return -5;
+}
+
+OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                                const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                                int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                                int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
+                                long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_) {
+  return PagedAttention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out, out_stride, sinks,
+                        scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, kv_chunk, scratch, scratch_bytes,
+                        cache_slots, order, status, stream_, 16);
+}
+
+// Same over an 8-bit cache: rows of head_dim int8 values + fp32 scale + 12 bytes of padding (see AttnParams::kv8).
+OGB_API int ogb_paged_attention_kv8(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                                    const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                                    int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                                    int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
+                                    long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_) {
+  return PagedAttention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out, out_stride, sinks,
+                        scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, kv_chunk, scratch, scratch_bytes,
+                        cache_slots, order, status, stream_, 8);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -153,6 +153,7 @@ struct RopeParams {
   const __nv_bfloat16* k_norm_w;  // optional [D]
   float norm_eps;
   int T, Hq, Hkv, D, rot, interleaved, max_pos;
+  int kv8;   // 8-bit cache: rows of D int8 values + fp32 scale (absmax / 127 of the row) + 12 bytes of padding
 };
 
 __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
@@ -183,6 +184,33 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
   else {
     if (slot < 0) return;
     const int kvh = is_k ? h - p.Hq : h - p.Hq - p.Hkv;
+    if (p.kv8) {
+      // rotate in the row buffer, then quantise the whole row against its largest magnitude
+      if (is_k && p.rot > 0) {
+        int pos = p.positions[t];
+        pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+        const int half = p.rot / 2;
+        const float* cs = p.cos_cache + size_t(pos) * half;
+        const float* sn = p.sin_cache + size_t(pos) * half;
+        for (int i = lane; i < half; i += 32) {
+          const int a = p.interleaved ? 2 * i : i, b = p.interleaved ? 2 * i + 1 : i + half;
+          const float x1 = v[a], x2 = v[b], c = cs[i], s = sn[i];
+          v[a] = x1 * c - x2 * s;
+          v[b] = x2 * c + x1 * s;
+        }
+        __syncwarp();
+      }
+      float amax = 0.f;
+      for (int e = lane; e < p.D; e += 32) amax = fmaxf(amax, fabsf(v[e]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float scale = amax > 0.f ? amax / 127.f : 1.f;
+      const float inv = 1.f / scale;
+      int8_t* row = reinterpret_cast<int8_t*>(is_k ? p.k_cache : p.v_cache) + (size_t(slot) * p.Hkv + kvh) * (p.D + 16);
+      for (int e = lane; e < p.D; e += 32) row[e] = int8_t(max(-127, min(127, __float2int_rn(v[e] * inv))));
+      if (lane == 0) *reinterpret_cast<float*>(row + p.D) = scale;
+      return;
+    }
     dst = (is_k ? p.k_cache : p.v_cache) + (size_t(slot) * p.Hkv + kvh) * p.D;
   }
   if ((is_q || is_k) && p.rot > 0) {
@@ -413,9 +441,20 @@ OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out,
 OGB_API int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
                                const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
                                float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream) {
+  return ogb_rope_kv_append_bits(qkv, qkv_stride, positions, slots, cos_cache, sin_cache, k_cache, v_cache, q_norm_w, k_norm_w, norm_eps, T,
+                                 Hq, Hkv, D, rot, interleaved, max_pos, 16, stream);
+}
+
+// kv_bits 16: bf16 cache rows; 8: int8 rows with an inline scale (row pitch D + 16 bytes, D a multiple of 16).
+OGB_API int ogb_rope_kv_append_bits(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
+                                    const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
+                                    float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, int kv_bits,
+                                    void* stream) {
   if (T <= 0) return 0;
   if (D > 256 || rot > D || (rot & 1)) return -1;
+  if (kv_bits != 16 && (kv_bits != 8 || (D % 16))) return -1;
   RopeParams p;
+  p.kv8 = kv_bits == 8;
   p.qkv = static_cast<__nv_bfloat16*>(qkv); p.qkv_stride = qkv_stride; p.positions = positions; p.slots = slots;
   p.cos_cache = cos_cache; p.sin_cache = sin_cache;
   p.k_cache = static_cast<__nv_bfloat16*>(k_cache); p.v_cache = static_cast<__nv_bfloat16*>(v_cache);

@@ -57,6 +57,9 @@ int ogb_norm(const void* x, const void* residual_in, void* residual_out, const v
 int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
                        const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
                        float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream);
+int ogb_rope_kv_append_bits(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
+                       const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
+                       float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, int kv_bits, void* stream);
 int ogb_embedding_q4(const int32_t* ids, const void* q, const void* scales, const void* zps, void* out, int T, int K, int vocab,
                      float mult, void* stream);
 int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream);
@@ -78,6 +81,11 @@ long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, int split
 // the cp.async path.  order: optional [B] permutation of the requests in which the CTAs are issued (longest first balances
 // a batch of mixed lengths).  splits > 1 divides a request's keys between CTAs: evenly (kv_chunk 0) or in fixed ranges of kv_chunk keys (multiple of 64).
 int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                        const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                        int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                        int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch, long long scratch_bytes,
+                        int cache_slots, const int32_t* order, int* status, void* stream);
+int ogb_paged_attention_kv8(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
                         const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                         int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
                         int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch, long long scratch_bytes,

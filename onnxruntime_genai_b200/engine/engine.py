@@ -397,7 +397,7 @@ class Engine:
         self.options = o
         n_win = self.core.ring_blocks_per_request * o.max_batch_size if windowed else 0
         self.kv = PagedKVCache(arch, o.num_blocks, self.block_size, model.device, model.dtype, kv_heads=dec.kv_heads_local,
-                               num_window_blocks=n_win, conv_channels=dec.conv_channels_local)
+                               num_window_blocks=n_win, conv_channels=dec.conv_channels_local, kv_bits=getattr(model, "kv_bits", 16))
         max_ctx = min(cfg.context_length, o.num_blocks * self.block_size)
         cols = (max_ctx + self.block_size - 1) // self.block_size
         self.staging = _Staging(o.max_scheduled_tokens + o.max_batch_size, o.max_batch_size, cols, model.device, windowed)
@@ -418,7 +418,8 @@ class Engine:
 
     def _blocks_from_memory(self, utilization: float) -> int:
         arch, dec = self.model.arch, self.model.decoder
-        per_block = PagedKVCache.bytes_per_block(arch, self.block_size, self.model.dtype, dec.kv_heads_local, dec.conv_channels_local)
+        per_block = PagedKVCache.bytes_per_block(arch, self.block_size, self.model.dtype, dec.kv_heads_local, dec.conv_channels_local,
+                                                 getattr(self.model, "kv_bits", 16))
         if self.model.device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(self.model.device)
             budget = int(free * 0.9 * utilization)

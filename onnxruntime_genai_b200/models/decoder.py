@@ -49,8 +49,14 @@ class PagedKVCache:
     sliding window may use a second, smaller pool addressed through ring block tables."""
 
     def __init__(self, arch: ArchConfig, num_blocks: int, block_size: int, device, dtype, kv_heads: Optional[int] = None,
-                 num_window_blocks: int = 0, conv_channels: Optional[int] = None):
+                 num_window_blocks: int = 0, conv_channels: Optional[int] = None, kv_bits: int = 16):
         self.block_size = block_size
+        # kv_bits 8: keys and values are stored as int8 rows with an inline fp32 scale (head_dim + 16 bytes per row and head)
+        if kv_bits not in (16, 8):
+            raise RuntimeError(f"KV cache quantization: {kv_bits}-bit caches are not supported (8 or none)")
+        if kv_bits == 8 and arch.head_dim % 16:
+            raise RuntimeError("KV cache quantization requires head_size to be a multiple of 16")
+        self.kv_bits = kv_bits
         self.num_blocks = num_blocks
         self.num_window_blocks = num_window_blocks
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
@@ -64,8 +70,9 @@ class PagedKVCache:
         cc = conv_channels if conv_channels is not None else arch.hidden_size
         self.conv = (torch.zeros(len(self.conv_index), num_blocks * block_size, cc, dtype=dtype, device=device)
                      if self.conv_index else None)
-        self.full = torch.zeros(max(n_full, 1), 2, num_blocks * block_size, hk, arch.head_dim, dtype=dtype, device=device)
-        self.win = (torch.zeros(n_win, 2, num_window_blocks * block_size, hk, arch.head_dim, dtype=dtype, device=device)
+        row, kdt = (arch.head_dim + 16, torch.int8) if kv_bits == 8 else (arch.head_dim, dtype)
+        self.full = torch.zeros(max(n_full, 1), 2, num_blocks * block_size, hk, row, dtype=kdt, device=device)
+        self.win = (torch.zeros(n_win, 2, num_window_blocks * block_size, hk, row, dtype=kdt, device=device)
                     if n_win else None)
         self._index = []
         fi = wi = 0
@@ -86,12 +93,14 @@ class PagedKVCache:
         return self.conv[self.conv_index[i]]
 
     @staticmethod
-    def bytes_per_block(arch: ArchConfig, block_size: int, dtype, kv_heads: Optional[int] = None, conv_channels: Optional[int] = None) -> int:
+    def bytes_per_block(arch: ArchConfig, block_size: int, dtype, kv_heads: Optional[int] = None, conv_channels: Optional[int] = None,
+                        kv_bits: int = 16) -> int:
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
         n_conv = sum(1 for i in range(arch.num_layers) if arch.is_conv_layer(i))
         cc = conv_channels if conv_channels is not None else arch.hidden_size
-        per_token = (arch.num_layers - n_conv) * 2 * hk * arch.head_dim + n_conv * cc
-        return per_token * block_size * torch.empty((), dtype=dtype).element_size()
+        es = torch.empty((), dtype=dtype).element_size()
+        kv_row = arch.head_dim + 16 if kv_bits == 8 else arch.head_dim * es
+        return ((arch.num_layers - n_conv) * 2 * hk * kv_row + n_conv * cc * es) * block_size
 
 
 class CrossKVCache:

@@ -359,9 +359,10 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
     assert cos_cache is None or cos_cache.dtype == torch.float32
     T = qkv.shape[0]
     max_pos = cos_cache.shape[0] if cos_cache is not None else 1
-    rc = _lib.lib().ogb_rope_kv_append(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(slots), _ptr(cos_cache), _ptr(sin_cache),
-                                       _ptr(k_cache), _ptr(v_cache), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), T, Hq, Hkv,
-                                       D, int(rot if cos_cache is not None else 0), int(interleaved), max_pos, _stream())
+    kv_bits = 8 if k_cache.dtype == torch.int8 else 16      # an int8 cache has rows of D values + inline scale (D + 16 bytes)
+    rc = _lib.lib().ogb_rope_kv_append_bits(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(slots), _ptr(cos_cache), _ptr(sin_cache),
+                                            _ptr(k_cache), _ptr(v_cache), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), T, Hq, Hkv,
+                                            D, int(rot if cos_cache is not None else 0), int(interleaved), max_pos, kv_bits, _stream())
     _lib.check(rc, "rope_kv_append")
     return qkv
 
@@ -405,7 +406,8 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
     ws = workspace(q.device)
     need = _lib.lib().ogb_attention_scratch_bytes(q.shape[0], Hq, D, splits)
     scratch = ws.attn_scratch(need) if splits > 1 else None
-    rc = _lib.lib().ogb_paged_attention(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
+    fn = _lib.lib().ogb_paged_attention_kv8 if k_cache.dtype == torch.int8 else _lib.lib().ogb_paged_attention
+    rc = fn(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
                                         _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0),
                                         _ptr(sinks), float(scale), float(softcap), int(window), B, q.shape[0], int(max_q_len),
                                         Hq, Hkv, D, int(splits), int(kv_chunk), _ptr(scratch),

@@ -39,6 +39,8 @@ _SIGS = {
     "ogb_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
     "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, _P]),
+    "ogb_rope_kv_append_bits": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, _P]),
     "ogb_embedding_q4": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_act_mul": (c_int, [_P, _P, c_int, c_int, c_int, _P]),
     "ogb_act": (c_int, [_P, _P, c_longlong, c_int, _P]),
@@ -50,6 +52,8 @@ _SIGS = {
     "ogb_gather_rows": (c_int, [_P, _P, _P, c_int, c_int, _P]),
     "ogb_attention_scratch_bytes": (c_longlong, [c_int, c_int, c_int, c_int]),
     "ogb_paged_attention": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
+    "ogb_paged_attention_kv8": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
     "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),

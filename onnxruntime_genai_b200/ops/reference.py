@@ -120,9 +120,30 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
     if slots is not None:
         ok = slots >= 0
         idx = slots[ok].long()
-        k_cache.view(-1, Hkv, D)[idx] = k[ok].to(k_cache.dtype)
-        v_cache.view(-1, Hkv, D)[idx] = v[ok].to(v_cache.dtype)
+        if k_cache.dtype == torch.int8:
+            kv8_store(k_cache, idx, k[ok], Hkv, D)
+            kv8_store(v_cache, idx, v[ok], Hkv, D)
+        else:
+            k_cache.view(-1, Hkv, D)[idx] = k[ok].to(k_cache.dtype)
+            v_cache.view(-1, Hkv, D)[idx] = v[ok].to(v_cache.dtype)
     return qkv
+
+
+def kv8_store(cache, idx, rows, Hkv, D):
+    """8-bit cache rows: D int8 values, the row's fp32 scale (absmax / 127), 12 bytes of padding."""
+    c = cache.view(-1, Hkv, D + 16)
+    amax = rows.abs().amax(-1, keepdim=True)
+    scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax)).float()
+    q = torch.round(rows.float() * (1.0 / scale)).clamp(-127, 127).to(torch.int8)
+    c[idx, :, :D] = q
+    c[idx, :, D:D + 4] = scale.contiguous().view(torch.int8).view(-1, Hkv, 4)
+
+
+def kv8_load(cache, Hkv, D):
+    """fp32 [slots, Hkv, D] values of an 8-bit cache, as the attention kernel expands them (value * scale rounded to bf16)."""
+    c = cache.view(-1, Hkv, D + 16)
+    scale = c[:, :, D:D + 4].contiguous().view(torch.float32)
+    return (c[:, :, :D].float() * scale).to(torch.bfloat16).float()
 
 
 def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
@@ -130,8 +151,11 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
     """q: [T, >=Hq*D] (only the first Hq*D columns are read).  Returns [T, Hq*D]."""
     T = q.shape[0]
     out = torch.zeros(T, Hq * D, dtype=q.dtype, device=q.device)
-    kc = k_cache.view(-1, Hkv, D)
-    vc = v_cache.view(-1, Hkv, D)
+    if k_cache.dtype == torch.int8:
+        kc, vc = kv8_load(k_cache, Hkv, D), kv8_load(v_cache, Hkv, D)
+    else:
+        kc = k_cache.view(-1, Hkv, D)
+        vc = v_cache.view(-1, Hkv, D)
     G = Hq // Hkv
     B = past_lens.shape[0]
     cu = cu_seqlens.tolist()

@@ -80,6 +80,7 @@ def _peaks():
 
 NO_FUSED = False     # --tp shapes without the fused all-reduce (the GEMM alone)
 ATTN_SPLITS = None   # None: the library's choice; (splits, kv_chunk) to force one
+GEMM_SPLITS = 0      # --gemm_splits: force the split-K cluster size of the GEMM cases (0: the library's choice)
 ATTN_ORDER = False   # --attn_order: longest request first
 
 
@@ -108,9 +109,9 @@ def build_case(name, T, L, tp=1):
         ws = [_bf(N, K) for _ in range(L)]
         if name in ("gemm_gate_up", "gemm_prefill"):
             ws = [ops.interleave_gate_up(w) for w in ws]
-            return (lambda i: ops.gate_up_act(x, ws[i % L], interleaved=True)), N * K * 2 + T * (K + N // 2) * 2, 2.0 * T * N * K
+            return (lambda i: ops.gate_up_act(x, ws[i % L], interleaved=True, splits=GEMM_SPLITS)), N * K * 2 + T * (K + N // 2) * 2, 2.0 * T * N * K
         fp32 = name == "gemm_lm_head"
-        return (lambda i: ops.linear(x, ws[i % L], out_fp32=fp32, all_reduce=fused)), N * K * 2 + T * K * 2 + T * N * (4 if fp32 else 2), 2.0 * T * N * K
+        return (lambda i: ops.linear(x, ws[i % L], out_fp32=fp32, all_reduce=fused, splits=GEMM_SPLITS)), N * K * 2 + T * K * 2 + T * N * (4 if fp32 else 2), 2.0 * T * N * K
     if name in ("attention_decode", "attention_prefill"):
         bs = 16
         rng = np.random.RandomState(2)
@@ -178,12 +179,14 @@ def main():
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA graph (for profilers; includes launch gaps)")
     ap.add_argument("--no_fused", action="store_true", help="with --tp: run the row-parallel GEMMs without the fused all-reduce")
     ap.add_argument("--attn_splits", default="", help="force the attention split: 'S' (even division) or 'S,chunk' (fixed key ranges)")
+    ap.add_argument("--gemm_splits", type=int, default=0, help="force the split-K cluster size of the GEMM cases (1, 2, 4, 8)")
     ap.add_argument("--attn_order", action="store_true", help="issue the attention CTAs of the longest requests first")
     ap.add_argument("--tp", type=int, default=1, help="use the per-rank shapes of this tensor-parallel degree")
     a = ap.parse_args()
     torch.manual_seed(0)
     globals()["NO_FUSED"] = a.no_fused
     globals()["ATTN_ORDER"] = a.attn_order
+    globals()["GEMM_SPLITS"] = a.gemm_splits
     if a.attn_splits:
         v = [int(x) for x in a.attn_splits.split(",")]
         globals()["ATTN_SPLITS"] = v[0] if len(v) == 1 else (v[0], v[1])

@@ -256,3 +256,43 @@ def test_hybrid_model_rewind_and_continue(tmp_path):
     g.append_tokens(np.asarray([[5, 6]], dtype=np.int32))
     want = dense_logits(arch, sd, ids[:6] + [5, 6])[-1].numpy()
     np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
+
+
+def test_int8_kv_cache_tracks_the_full_precision_cache(tmp_path):
+    """kvCacheQuantizationBits=8 (a provider option of the decoder session): keys and values are stored as int8 rows with one
+    scale per token and head; logits stay close to the unquantised cache through prefill, decode and a rewind."""
+    from helpers import tiny_model_dir
+    d, arch = tiny_model_dir(str(tmp_path), std=0.3)
+    prompt = np.random.RandomState(3).randint(2, arch.vocab_size, size=(2, 21)).astype(np.int32)
+
+    def run(bits):
+        cfg = og.Config(d)
+        if bits:
+            cfg.append_provider("cpu")
+            cfg.set_provider_option("cpu", "kvCacheQuantizationBits", str(bits))
+        model = og.Model(cfg)
+        assert model.kv_bits == (bits or 16)
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=48, batch_size=2)
+        g = og.Generator(model, p)
+        g.append_tokens(prompt)
+        outs = [g.get_logits().copy()]
+        for _ in range(4):
+            forced = np.full((2, arch.vocab_size), -1e9, dtype=np.float32)
+            forced[:, 7] = 0
+            g.set_logits(forced)
+            g.generate_next_token()
+            outs.append(g.get_logits().copy())
+        return g, outs
+
+    g8, q = run(8)
+    assert g8.state.kv.full.dtype == torch.int8 and g8.state.kv.full.shape[-1] == arch.head_dim + 16
+    _, f = run(0)
+    for a, b in zip(q, f):
+        assert np.abs(a - b).max() < 0.12 * b.std() + 0.02 and np.corrcoef(a.reshape(-1), b.reshape(-1))[0, 1] > 0.999
+        assert np.abs(a - b).max() > 0          # the cache really is quantised
+    with pytest.raises(RuntimeError, match="not supported"):
+        cfg = og.Config(d)
+        cfg.append_provider("cpu")
+        cfg.set_provider_option("cpu", "kvCacheQuantizationBits", "4")
+        og.Model(cfg)

@@ -330,3 +330,48 @@ def test_vision_language_on_gpu_tracks_cpu(tmp_path):
         out.append(g.get_logits()[:, 0, :])
     ops.check_kernel_status()
     assert np.abs(out[0] - out[1]).max() < 0.08 * out[1].std() + 0.02
+
+
+def test_int8_kv_cache_on_gpu(dirs):
+    """kvCacheQuantizationBits=8: the append kernel quantises rows, the attention kernel expands them tile by tile; Generator
+    (graph decode) and engine paths against the fp32 CPU model with a full-precision cache."""
+    cfg = og.Config(dirs[0])
+    cfg.set_provider_option("cuda", "kvCacheQuantizationBits", "8")
+    gpu, cpu = og.Model(cfg), og.Model(dirs[1])
+    assert gpu.kv_bits == 8
+    prompt = np.random.RandomState(9).randint(0, 32000, size=(2, 150)).astype(np.int32)
+    gg, lg = _logits(gpu, prompt)
+    gc, lc = _logits(cpu, prompt)
+    assert gg.state.kv.full.dtype == torch.int8
+    assert np.abs(lg - lc).max() < 0.12 * lc.std() + 0.03
+    for _ in range(6):
+        gc.generate_next_token()
+        toks = gc.get_next_tokens()
+        forced = np.full((2, 32000), -1e9, dtype=np.float32)
+        forced[np.arange(2), toks] = 0
+        gg.get_logits()
+        gg.set_logits(forced)
+        gg.generate_next_token()
+    lg, lc = gg.get_logits()[:, 0, :], gc.get_logits()[:, 0, :]
+    assert np.abs(lg - lc).max() < 0.12 * lc.std() + 0.03
+    # engine: paged cache sized in int8 rows, decode graphs, look-ahead
+    engine = og.Engine(gpu)
+    assert engine.kv.full.dtype == torch.int8
+    reqs = []
+    for i in range(3):
+        p = og.GeneratorParams(gpu)
+        p.set_search_options(max_length=60 + i)
+        r = og.Request(p)
+        r.add_tokens(prompt[0, :40 + 5 * i])
+        engine.add_request(r)
+        reqs.append(r)
+    n = 0
+    while engine.has_pending_requests():
+        r = engine.step()
+        while r is not None and r.has_unseen_tokens():
+            r.get_unseen_token()
+            n += 1
+        if r is not None and r.is_turn_complete():
+            engine.remove_request(r)
+    ops.check_kernel_status()
+    assert n >= 3 * 10

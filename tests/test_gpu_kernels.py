@@ -356,6 +356,52 @@ def test_attention_bidirectional_over_cached_keys(splits):
     _attention_case(B=2, q_lens=[40, 17], past=[40, 17], Hq=8, Hkv=2, D=128, bs=16, window=-1, splits=splits)
 
 
+def _attention_case_kv8(B, q_lens, past, Hq, Hkv, D, bs, splits=None, seed=50, window=0):
+    """The same problem over an 8-bit cache filled by the append kernel: compared with the reference attention over the
+    reference's own quantised cache (bit-identical rows are not required, close outputs are)."""
+    rng = np.random.RandomState(seed)
+    cols = max((p + q + bs - 1) // bs for p, q in zip(past, q_lens))
+    nblocks = B * cols + 3
+    perm = rng.permutation(nblocks)
+    table = torch.full((B, cols), -1, dtype=torch.int32)
+    used = 0
+    for b in range(B):
+        need = (past[b] + q_lens[b] + bs - 1) // bs
+        table[b, :need] = torch.from_numpy(perm[used:used + need].astype(np.int32))
+        used += need
+    kc_g = torch.zeros(nblocks * bs, Hkv, D + 16, dtype=torch.int8, device=DEV)
+    vc_g = torch.zeros_like(kc_g)
+    kc_c, vc_c = kc_g.cpu().clone(), vc_g.cpu().clone()
+    # fill every request's cached prefix and this step's tokens through the append path (rot = 0: plain append)
+    for b in range(B):
+        n = past[b] + q_lens[b]
+        rows = _rand(n, 2 * Hkv * D, std=1.0, seed=seed + 10 + b)
+        pos = torch.arange(n, dtype=torch.int32)
+        slots = (table[b, (pos // bs).long()] * bs + pos % bs).to(torch.int32)
+        ops.rope_kv_append(rows.clone(), pos.to(DEV), slots.to(DEV), None, None, kc_g, vc_g, 0, Hkv, D, 0)
+        ref.rope_kv_append(rows.cpu().clone(), pos, slots, None, None, kc_c, vc_c, 0, Hkv, D, 0)
+    # the two append paths agree on the stored rows (scales equal, values within one step)
+    d = (kc_g.cpu()[..., :D].int() - kc_c[..., :D].int()).abs().max()
+    assert d <= 1 and torch.equal(kc_g.cpu()[..., D:D + 4], kc_c[..., D:D + 4])
+    T = sum(q_lens)
+    q = _rand(T, Hq * D, std=1.0, seed=seed + 3)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    pl = torch.tensor(past, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    out = ops.paged_attention(q, kc_g, vc_g, cu.to(DEV), pl.to(DEV), table.to(DEV), bs, Hq, Hkv, D, scale, window,
+                              max_q_len=max(q_lens), max_kv_len=max(p + q_ for p, q_ in zip(past, q_lens)), splits=splits)
+    want = ref.paged_attention(q.cpu(), kc_g.cpu(), vc_g.cpu(), cu, pl, table, bs, Hq, Hkv, D, scale, window)
+    _close(out, want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("D", [64, 96, 128])
+def test_attention_int8_cache(D):
+    _attention_case_kv8(B=4, q_lens=[1] * 4, past=[0, 15, 200, 1023], Hq=8, Hkv=2, D=D, bs=16)           # decode mode
+    _attention_case_kv8(B=3, q_lens=[70, 1, 9], past=[0, 130, 64], Hq=8, Hkv=2, D=D, bs=16)               # prefill / mixed rows
+    _attention_case_kv8(B=2, q_lens=[1, 1], past=[700, 2047], Hq=32, Hkv=8, D=D, bs=16, splits=(8, 256))  # split keys
+    _attention_case_kv8(B=2, q_lens=[1, 30], past=[500, 100], Hq=8, Hkv=2, D=D, bs=16, window=128)
+
+
 @pytest.mark.parametrize("splits", [None, 3])
 def test_attention_longest_first_issue_order(splits):
     """A permutation of the requests only changes which CTA serves which request."""
