@@ -743,6 +743,9 @@ class Generator:
     def get_input(self, name: str):
         if name == "input_ids":
             return self.search.next_tokens()
+        if name in getattr(self, "_extra_inputs", {}):
+            v = self._extra_inputs[name]
+            return v.as_numpy() if isinstance(v, Tensor) else np.asarray(v)
         raise RuntimeError(f"unknown model input: {name}")
 
     def get_output(self, name: str):
@@ -807,6 +810,20 @@ class Generator:
     def set_model_input(self, name: str, tensor):
         self._extra_inputs = getattr(self, "_extra_inputs", {})
         self._extra_inputs[name] = tensor
+
+    def snapshot_state(self):
+        """Marks the current state as a point speculative decoding may roll back to (reference:
+        src/generators.h:135, recurrent models copy their state to a snapshot slot).  Every cache of this runtime - keys /
+        values and the convolution inputs of hybrid layers - is addressed by position through block tables, so `rewind_to`
+        restores any earlier length without a copy; the call only records the length."""
+        self._snapshot_length = self.token_count()
+        return self._snapshot_length
+
+    def set_hidden_states(self, hidden_states):
+        """Stages a `hidden_states` input for the next model run (the input of a multi-token-prediction head, reference:
+        src/generators.h:141); read back with get_input("hidden_states")."""
+        arr = hidden_states.as_numpy() if isinstance(hidden_states, Tensor) else np.asarray(hidden_states)
+        self.set_model_input("hidden_states", arr)
 
     def set_active_adapter(self, adapters, name: str):
         adapters._activate(self.model, name)

@@ -296,3 +296,25 @@ def test_int8_kv_cache_tracks_the_full_precision_cache(tmp_path):
         cfg.append_provider("cpu")
         cfg.set_provider_option("cpu", "kvCacheQuantizationBits", "4")
         og.Model(cfg)
+
+
+def test_snapshot_state_and_staged_hidden_states(tmp_path):
+    from helpers import tiny_model_dir
+    d, arch = tiny_model_dir(str(tmp_path))
+    model = og.Model(d)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=32)
+    g = og.Generator(model, p)
+    g.append_tokens(np.asarray([[2, 3, 4, 5]], dtype=np.int32))
+    before = g.get_logits().copy()
+    assert g.snapshot_state() == 4
+    for _ in range(3):
+        g.generate_next_token()
+    g.rewind_to(4)
+    g.append_tokens(np.asarray([[9]], dtype=np.int32))
+    g.rewind_to(3)
+    g.append_tokens(np.asarray([[5]], dtype=np.int32))
+    np.testing.assert_allclose(g.get_logits(), before, rtol=1e-5, atol=1e-6)
+    hs = np.random.RandomState(0).randn(1, 1, arch.hidden_size).astype(np.float32)
+    g.set_hidden_states(hs)
+    np.testing.assert_array_equal(g.get_input("hidden_states"), hs)
