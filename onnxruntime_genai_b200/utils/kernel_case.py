@@ -80,6 +80,7 @@ def _peaks():
 
 NO_FUSED = False     # --tp shapes without the fused all-reduce (the GEMM alone)
 ATTN_SPLITS = None   # None: the library's choice; (splits, kv_chunk) to force one
+KV_BITS = 16         # --kv_bits 8: the attention cases read an int8 cache
 GEMM_SPLITS = 0      # --gemm_splits: force the split-K cluster size of the GEMM cases (0: the library's choice)
 ATTN_ORDER = False   # --attn_order: longest request first
 
@@ -122,8 +123,15 @@ def build_case(name, T, L, tp=1):
         cols = max((p + q + bs - 1) // bs for p, q in zip(past, q_lens))
         nblk = sum((p + q + bs - 1) // bs for p, q in zip(past, q_lens)) + 4
         Lk = min(L, 4)
-        kc = [_bf(nblk * bs, HKV, D, std=1.0) for _ in range(Lk)]
-        vc = [_bf(nblk * bs, HKV, D, std=1.0) for _ in range(Lk)]
+        if KV_BITS == 8:
+            def q8():   # int8 rows with an inline fp32 scale (row pitch D + 16 bytes)
+                c = torch.randint(-127, 128, (nblk * bs, HKV, D + 16), dtype=torch.int8, device="cuda")
+                c[:, :, D:D + 4] = torch.full((nblk * bs, HKV, 1), 1.0 / 64, device="cuda").view(torch.int8).view(nblk * bs, HKV, 4)
+                return c
+            kc, vc = [q8() for _ in range(Lk)], [q8() for _ in range(Lk)]
+        else:
+            kc = [_bf(nblk * bs, HKV, D, std=1.0) for _ in range(Lk)]
+            vc = [_bf(nblk * bs, HKV, D, std=1.0) for _ in range(Lk)]
         table = torch.zeros(B, cols, dtype=torch.int32)
         used = 0
         for b in range(B):
@@ -136,7 +144,7 @@ def build_case(name, T, L, tp=1):
         cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32).cuda()
         pl = torch.tensor(past, dtype=torch.int32).cuda()
         kv_tokens = sum(p + q for p, q in zip(past, q_lens))
-        nbytes = kv_tokens * HKV * D * 2 * 2 + Tq * HQ * D * 2 * 2
+        nbytes = kv_tokens * HKV * ((D + 16) if KV_BITS == 8 else D * 2) * 2 + Tq * HQ * D * 2 * 2
         flops = sum(4.0 * HQ * D * (q * p + q * (q + 1) / 2) for p, q in zip(past, q_lens))
         order = torch.argsort(-pl.long(), stable=True).to(torch.int32) if ATTN_ORDER else None   # longest request first
         return (lambda i: ops.paged_attention(qkv, kc[i % Lk], vc[i % Lk], cu, pl, table, bs, HQ, HKV, D, 1 / math.sqrt(D),
@@ -179,6 +187,7 @@ def main():
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA graph (for profilers; includes launch gaps)")
     ap.add_argument("--no_fused", action="store_true", help="with --tp: run the row-parallel GEMMs without the fused all-reduce")
     ap.add_argument("--attn_splits", default="", help="force the attention split: 'S' (even division) or 'S,chunk' (fixed key ranges)")
+    ap.add_argument("--kv_bits", type=int, default=16, choices=[16, 8], help="attention cases: bf16 or int8 key/value cache")
     ap.add_argument("--gemm_splits", type=int, default=0, help="force the split-K cluster size of the GEMM cases (1, 2, 4, 8)")
     ap.add_argument("--attn_order", action="store_true", help="issue the attention CTAs of the longest requests first")
     ap.add_argument("--tp", type=int, default=1, help="use the per-rank shapes of this tensor-parallel degree")
@@ -187,6 +196,7 @@ def main():
     globals()["NO_FUSED"] = a.no_fused
     globals()["ATTN_ORDER"] = a.attn_order
     globals()["GEMM_SPLITS"] = a.gemm_splits
+    globals()["KV_BITS"] = a.kv_bits
     if a.attn_splits:
         v = [int(x) for x in a.attn_splits.split(",")]
         globals()["ATTN_SPLITS"] = v[0] if len(v) == 1 else (v[0], v[1])
