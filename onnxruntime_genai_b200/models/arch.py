@@ -16,7 +16,7 @@ import numpy as np
 LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
-    "smollm3", "lfm2", "gpt2", "helium", "exaone",
+    "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe",
 ]
 
 
@@ -74,6 +74,11 @@ class ArchConfig:
     experts_per_token: int = 0
     moe_swiglu_alpha: float = 1.702
     moe_swiglu_limit: float = 7.0
+    # "gptoss": router with bias, fused gate/up with biases, clamped SwiGLU(alpha, limit).  "standard" (Mixtral, Qwen-MoE,
+    # PhiMoE, GraniteMoE): bias-free router and experts, separate gate / up matrices, silu(gate) * up, softmax over all
+    # experts with the selected weights renormalised (moe_norm_topk) or left as they are.
+    moe_style: str = "gptoss"
+    moe_norm_topk: bool = True
     # embedding / head
     embed_scale: float = 1.0
     tie_embeddings: bool = False
@@ -192,6 +197,14 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.sliding_layers = ([i for i, t in enumerate(lt) if t == "sliding_attention"] if lt
                             else [i for i in range(a.num_layers) if i % 2 == 0])
         a.moe_swiglu_limit = cfg.get("swiglu_limit", 7.0)
+    if mt in ("mixtral", "phimoe", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe"):
+        a.moe_style = "standard"
+        a.num_experts = cfg.get("num_local_experts", cfg.get("num_experts", 8))
+        a.experts_per_token = cfg.get("num_experts_per_tok", 2)
+        a.moe_norm_topk = bool(cfg.get("norm_topk_prob", True))
+        a.intermediate_size = cfg.get("moe_intermediate_size", a.intermediate_size)
+        if mt == "qwen3_moe":
+            a.qk_norm = True
     if mt == "granite":
         a.residual_multiplier = cfg.get("residual_multiplier", 1.0)
         a.logits_scale = 1.0 / cfg.get("logits_scaling", 1.0)

@@ -87,7 +87,13 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
         if arch.attn_sinks:
             s[p + "self_attn.sinks"] = (arch.num_heads,)
-        if arch.num_experts > 0:
+        if arch.num_experts > 0 and arch.moe_style == "standard":
+            E = arch.num_experts
+            s[p + "mlp.router.weight"] = (E, H)
+            s[p + "mlp.experts.gate_proj"] = (E, I, H)
+            s[p + "mlp.experts.up_proj"] = (E, I, H)
+            s[p + "mlp.experts.down_proj"] = (E, H, I)
+        elif arch.num_experts > 0:
             E = arch.num_experts
             s[p + "mlp.router.weight"] = (E, H)
             s[p + "mlp.router.bias"] = (E,)
@@ -522,7 +528,19 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             x = f"{n}/{mid_name}/output_0"
         # (parallel block: the MLP reads the same normalised input as the attention)
         # MLP / MoE
-        if arch.num_experts > 0:
+        if arch.num_experts > 0 and arch.moe_style == "standard":
+            # MoE contrib op with three expert matrices: fc1 = gate [E, I, H], fc2 = down [E, H, I], fc3 = up [E, I, H];
+            # silu(fc1 x) * fc3 x, routing weights = softmax over all experts (renormalised over the selected if asked)
+            E = arch.num_experts
+            put_linear(p + "moe.router", f"{n}/moe/router/MatMul", [p + "mlp.router.weight"], x, f"{n}/moe/router/MatMul/output_0", E, H)
+            for nm in ("gate_proj", "down_proj", "up_proj"):
+                put_plain(p + f"moe.experts.{nm}.weight", [p + f"mlp.experts.{nm}"], {"shape": shapes[p + f"mlp.experts.{nm}"], "op": "id", "fn": lambda ts: ts[0].float()})
+            W.node("MoE", f"{n}/moe/MoE", [x, f"{n}/moe/router/MatMul/output_0", p + "moe.experts.gate_proj.weight", "",
+                                          p + "moe.experts.down_proj.weight", "", p + "moe.experts.up_proj.weight", ""],
+                   [f"{n}/moe/MoE/output_0"], domain="com.microsoft", k=arch.experts_per_token, activation_type="silu", activation_alpha=1.0,
+                   activation_beta=0.0, swiglu_fusion=0, normalize_routing_weights=int(arch.moe_norm_topk), use_sparse_mixer=0)
+            mlp_out = f"{n}/moe/MoE/output_0"
+        elif arch.num_experts > 0:
             E = arch.num_experts
             put_linear(p + "moe.router", f"{n}/moe/router/MatMul", [p + "mlp.router.weight"], x, f"{n}/moe/router/MatMul/output_0", E, H)
             put_vec(p + "moe.router.Add.bias", [p + "mlp.router.bias"])

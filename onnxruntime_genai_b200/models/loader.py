@@ -149,9 +149,16 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         wname = moe.inputs[2]
         shp = g.lm.info(wname).dims
         a.num_experts = shp[0]
-        # MoE weight [E, 2I, H]; QMoE MXFP4 codes [E, H, (2I)/2]
-        a.intermediate_size = shp[2] if moe.op_type == "QMoE" else shp[1] // 2
-        a.mlp_bias = True
+        if moe.op_type == "MoE" and int(_attr(moe, "swiglu_fusion", 0)) == 0 and len(moe.inputs) > 6 and moe.inputs[6]:
+            # three expert matrices (gate, down, up), silu(gate) * up, no biases
+            a.moe_style = "standard"
+            a.moe_norm_topk = bool(int(_attr(moe, "normalize_routing_weights", 0)))
+            a.intermediate_size = shp[1]
+            a.mlp_bias = False
+        else:
+            # MoE weight [E, 2I, H]; QMoE MXFP4 codes [E, H, (2I)/2]
+            a.intermediate_size = shp[2] if moe.op_type == "QMoE" else shp[1] // 2
+            a.mlp_bias = True
     else:
         gu = g.find("/model/layers.0/mlp/gate_up_proj/", ops=["MatMul", "MatMulNBits"])
         if gu is not None:
@@ -434,6 +441,12 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                 ins = list(moe.inputs) + [""] * 17
                 lw.exp_gate_up_w, lw.exp_gate_up_b = experts_fp4(ins[2], ins[3], ins[15]), experts(ins[4])
                 lw.exp_down_w, lw.exp_down_b = experts_fp4(ins[5], ins[6], ins[16]), experts(ins[7])
+            elif arch.moe_style == "standard":
+                # gate [E, I, H] and up [E, I, H] become one matrix with even rows = gate, odd rows = up (the fused layout)
+                gate, up = experts(moe.inputs[2]), experts(moe.inputs[6])
+                lw.exp_gate_up_w = torch.stack([gate, up], dim=2).reshape(gate.shape[0], 2 * gate.shape[1], gate.shape[2]).contiguous()
+                lw.exp_down_w = experts(moe.inputs[4])
+                del gate, up
             else:
                 lw.exp_gate_up_w, lw.exp_gate_up_b = experts(moe.inputs[2]), experts(moe.inputs[3])
                 lw.exp_down_w, lw.exp_down_b = experts(moe.inputs[4]), experts(moe.inputs[5])

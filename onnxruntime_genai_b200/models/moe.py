@@ -1,5 +1,6 @@
-"""Mixture-of-experts MLP (gpt-oss style): router -> top-k -> softmax over the selected logits ->
-per-expert SwiGLU(alpha, limit) MLP -> weighted sum.
+"""Mixture-of-experts MLP: router -> top-k -> routing weights -> per-expert gated MLP -> weighted sum.
+Two styles: gpt-oss (biases, softmax over the selected logits, clamped SwiGLU(alpha, limit)) and standard (Mixtral, Qwen-MoE,
+PhiMoE, GraniteMoE: no biases, silu(gate) * up, softmax over all experts with or without renormalisation).
 
 Semantics follow the MoE / QMoE contrib op the reference's builder emits
 (src/python/py/models/builders/base.py:4176-4408, builders/gptoss.py:653-847): `k` experts per token,
@@ -32,10 +33,19 @@ def swiglu_interleaved(gu: torch.Tensor, alpha: float, limit: float) -> torch.Te
 
 
 def route(model, lw, x):
+    """Routing weights and expert ids [T, k].  Softmax over the selected logits equals softmax over all experts renormalised
+    over the selected; the standard style without renormalisation keeps the probabilities of the full softmax."""
     a = model.arch
     logits = ops.linear(x, lw.router_w, lw.router_b).float()
     top_v, top_i = torch.topk(logits, a.experts_per_token, dim=-1)
+    if a.moe_style == "standard" and not a.moe_norm_topk:
+        return torch.softmax(logits, dim=-1).gather(-1, top_i), top_i
     return torch.softmax(top_v, dim=-1), top_i
+
+
+def silu_mul_interleaved(gu: torch.Tensor) -> torch.Tensor:
+    g, u = gu[..., 0::2].float(), gu[..., 1::2].float()
+    return (torch.nn.functional.silu(g) * u).to(gu.dtype)
 
 
 def _unblock(t: torch.Tensor) -> torch.Tensor:
@@ -52,7 +62,7 @@ def expert_mlp(model, lw, e: int, xs: torch.Tensor) -> torch.Tensor:
     if lw.exp_blocked:
         w, b = _unblock(w).contiguous(), _unblock(b).contiguous() if b is not None else None
     gu = ops.linear(xs, w, b)
-    act = swiglu_interleaved(gu, a.moe_swiglu_alpha, a.moe_swiglu_limit)
+    act = silu_mul_interleaved(gu) if a.moe_style == "standard" else swiglu_interleaved(gu, a.moe_swiglu_alpha, a.moe_swiglu_limit)
     return ops.linear(act.contiguous(), lw.exp_down_w[e], lw.exp_down_b[e] if lw.exp_down_b is not None else None)
 
 
@@ -80,9 +90,13 @@ def _forward_device(model, lw, x):
     a = model.arch
     lo, hi = lw.exp_lo, lw.exp_hi or a.num_experts
     logits = ops.linear(x, lw.router_w, lw.router_b, out_fp32=True)
-    plan = ops.moe_route(logits, a.experts_per_token, 0, (lo, hi))
+    standard = a.moe_style == "standard"
+    plan = ops.moe_route(logits, a.experts_per_token, 1 if standard and not a.moe_norm_topk else 0, (lo, hi))
     xs = ops.gather_rows(x, plan.sorted_token)
-    h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, lw.exp_gate_up_b, act_kind=2, alpha=a.moe_swiglu_alpha, limit=a.moe_swiglu_limit)
+    if standard:
+        h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, None, act_kind=1)
+    else:
+        h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, lw.exp_gate_up_b, act_kind=2, alpha=a.moe_swiglu_alpha, limit=a.moe_swiglu_limit)
     y = ops.moe_gemm(h, lw.exp_down_w, plan, lw.exp_down_b)
     return ops.moe_combine(y, plan)
 

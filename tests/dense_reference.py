@@ -106,7 +106,18 @@ def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None):
             mid = "post_attention_layernorm"
         h = h + o * arch.residual_multiplier
         x = _norm(h, g(mid + ".weight"), g(mid + ".bias"), arch)
-        if arch.num_experts > 0:
+        if arch.num_experts > 0 and arch.moe_style == "standard":
+            probs = torch.softmax(x @ g("mlp.router.weight").t(), -1)
+            tw, ti = torch.topk(probs, arch.experts_per_token, -1)
+            if arch.moe_norm_topk:
+                tw = tw / tw.sum(-1, keepdim=True)
+            y = torch.zeros_like(x)
+            for t in range(S):
+                for j in range(arch.experts_per_token):
+                    e = int(ti[t, j])
+                    a_ = torch.nn.functional.silu(x[t] @ g("mlp.experts.gate_proj")[e].t()) * (x[t] @ g("mlp.experts.up_proj")[e].t())
+                    y[t] += tw[t, j] * (a_ @ g("mlp.experts.down_proj")[e].t())
+        elif arch.num_experts > 0:
             router = x @ g("mlp.router.weight").t() + g("mlp.router.bias")
             tv, ti = torch.topk(router, arch.experts_per_token, -1)
             tw = torch.softmax(tv, -1)

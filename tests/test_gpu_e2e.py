@@ -221,7 +221,7 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
     assert len(c[1]) <= max(5, len(a[1])) and all(len(c[i]) > 0 for i in (0, 2, 3))
 
 
-@pytest.mark.parametrize("family", ["phi_parallel", "gpt2", "lfm2"])
+@pytest.mark.parametrize("family", ["phi_parallel", "gpt2", "lfm2", "mixtral", "qwen_moe"])
 def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_path):
     """fc1 -> GELU -> fc2 MLPs, the parallel attention/MLP block, learned position tables, hybrid convolution layers: bf16 GPU
     against fp32 CPU."""
@@ -230,9 +230,12 @@ def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_pat
                                   lm_head_bias=True, activation="gelu", mlp_gated=False, parallel_block=True),
              "gpt2": dict(model_type="gpt2", layernorm=True, attn_bias=True, o_bias=True, mlp_bias=True, activation="gelu",
                           mlp_gated=False, learned_positions=True, tie_embeddings=True),
-             "lfm2": dict(model_type="lfm2", qk_norm=True, tie_embeddings=True, conv_L_cache=3, layer_types=["conv", "full_attention"])}[family]
-    arch = ArchConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=64, intermediate_size=512,
-                      context_length=256, bos_token_id=0, eos_token_id=1023, pad_token_id=0, **flags)
+             "lfm2": dict(model_type="lfm2", qk_norm=True, tie_embeddings=True, conv_L_cache=3, layer_types=["conv", "full_attention"]),
+             "mixtral": dict(model_type="mixtral", moe_style="standard", num_experts=4, experts_per_token=2, intermediate_size=128),
+             "qwen_moe": dict(model_type="qwen3_moe", moe_style="standard", moe_norm_topk=False, qk_norm=True, num_experts=8,
+                              experts_per_token=3, intermediate_size=128)}[family]
+    arch = ArchConfig(**{**dict(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=64, intermediate_size=512,
+                                context_length=256, bos_token_id=0, eos_token_id=1023, pad_token_id=0), **flags})
     sd = random_state_dict(arch, seed=3, std=0.05)
     gpu, cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
     export_model(copy.deepcopy(arch), gpu, "bf16", "cuda", state_dict=sd)
