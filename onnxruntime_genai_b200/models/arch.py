@@ -79,6 +79,8 @@ class ArchConfig:
     # experts with the selected weights renormalised (moe_norm_topk) or left as they are.
     moe_style: str = "gptoss"
     moe_norm_topk: bool = True
+    moe_sparse_mixer: bool = False   # PhiMoE: two experts picked one after the other, each weighted by a softmax over the logits
+    moe_jitter_eps: float = 0.01     # within a relative margin 2 * eps of the current maximum
     # embedding / head
     embed_scale: float = 1.0
     tie_embeddings: bool = False
@@ -205,6 +207,12 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.intermediate_size = cfg.get("moe_intermediate_size", a.intermediate_size)
         if mt == "qwen3_moe":
             a.qk_norm = True
+        if mt == "phimoe":
+            a.moe_sparse_mixer = True
+            a.moe_jitter_eps = float(cfg.get("router_jitter_noise", 0.01))
+            a.layernorm = True
+            a.attn_bias = a.o_bias = True
+            a.lm_head_bias = bool(cfg.get("lm_head_bias", True))
     if mt == "granite":
         a.residual_multiplier = cfg.get("residual_multiplier", 1.0)
         a.logits_scale = 1.0 / cfg.get("logits_scaling", 1.0)

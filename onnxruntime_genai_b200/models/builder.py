@@ -538,7 +538,8 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             W.node("MoE", f"{n}/moe/MoE", [x, f"{n}/moe/router/MatMul/output_0", p + "moe.experts.gate_proj.weight", "",
                                           p + "moe.experts.down_proj.weight", "", p + "moe.experts.up_proj.weight", ""],
                    [f"{n}/moe/MoE/output_0"], domain="com.microsoft", k=arch.experts_per_token, activation_type="silu", activation_alpha=1.0,
-                   activation_beta=0.0, swiglu_fusion=0, normalize_routing_weights=int(arch.moe_norm_topk), use_sparse_mixer=0)
+                   activation_beta=0.0, swiglu_fusion=0, normalize_routing_weights=int(arch.moe_norm_topk),
+                   use_sparse_mixer=int(arch.moe_sparse_mixer), **({"sparse_mixer_jitter_eps": float(arch.moe_jitter_eps)} if arch.moe_sparse_mixer else {}))
             mlp_out = f"{n}/moe/MoE/output_0"
         elif arch.num_experts > 0:
             E = arch.num_experts

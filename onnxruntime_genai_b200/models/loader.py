@@ -153,6 +153,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
             # three expert matrices (gate, down, up), silu(gate) * up, no biases
             a.moe_style = "standard"
             a.moe_norm_topk = bool(int(_attr(moe, "normalize_routing_weights", 0)))
+            a.moe_sparse_mixer = bool(int(_attr(moe, "use_sparse_mixer", 0)))
+            a.moe_jitter_eps = float(_attr(moe, "sparse_mixer_jitter_eps", 0.01))
             a.intermediate_size = shp[1]
             a.mlp_bias = False
         else:

@@ -37,10 +37,32 @@ def route(model, lw, x):
     over the selected; the standard style without renormalisation keeps the probabilities of the full softmax."""
     a = model.arch
     logits = ops.linear(x, lw.router_w, lw.router_b).float()
+    if a.moe_sparse_mixer:
+        return sparse_mixer(logits, a.moe_jitter_eps)
     top_v, top_i = torch.topk(logits, a.experts_per_token, dim=-1)
     if a.moe_style == "standard" and not a.moe_norm_topk:
         return torch.softmax(logits, dim=-1).gather(-1, top_i), top_i
     return torch.softmax(top_v, dim=-1), top_i
+
+
+def sparse_mixer(logits: torch.Tensor, eps: float):
+    """PhiMoE's inference-time routing (reference: the MoE contrib op's use_sparse_mixer attribute,
+    src/python/py/models/builders/phi.py:542-547): the best expert, then the best of the rest; each weight is that
+    expert's probability in a softmax over the logits that lie within a relative margin of 2 * eps below the current
+    maximum.  Pure tensor ops (no host synchronisation), so the step still captures into a CUDA graph."""
+    s = logits.float()
+    neg = torch.finfo(torch.float32).min
+
+    def pick(scores):
+        top, idx = scores.max(dim=-1, keepdim=True)
+        factor = s.abs().clamp(min=top)
+        keep = ((top - s) / factor) <= 2.0 * eps
+        gates = torch.softmax(torch.where(keep, scores, torch.full_like(scores, neg)), dim=-1)
+        return gates.gather(-1, idx), idx
+
+    w1, i1 = pick(s)
+    w2, i2 = pick(s.scatter(-1, i1, neg))
+    return torch.cat([w1, w2], dim=-1), torch.cat([i1, i2], dim=-1)
 
 
 def silu_mul_interleaved(gu: torch.Tensor) -> torch.Tensor:
@@ -91,7 +113,11 @@ def _forward_device(model, lw, x):
     lo, hi = lw.exp_lo, lw.exp_hi or a.num_experts
     logits = ops.linear(x, lw.router_w, lw.router_b, out_fp32=True)
     standard = a.moe_style == "standard"
-    plan = ops.moe_route(logits, a.experts_per_token, 1 if standard and not a.moe_norm_topk else 0, (lo, hi))
+    if a.moe_sparse_mixer:
+        tw, ti = sparse_mixer(logits, a.moe_jitter_eps)
+        plan = ops.moe_route(logits, 2, 0, (lo, hi), topk=(ti.to(torch.int32).contiguous(), tw.contiguous()))
+    else:
+        plan = ops.moe_route(logits, a.experts_per_token, 1 if standard and not a.moe_norm_topk else 0, (lo, hi))
     xs = ops.gather_rows(x, plan.sorted_token)
     if standard:
         h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, None, act_kind=1)

@@ -293,10 +293,11 @@ class MoePlan:
                  "tile_row0", "tile_rows", "num_tiles")
 
 
-def moe_route(router_logits: torch.Tensor, k: int, mode: int = 0, expert_range=None, token_tile: int = 0) -> MoePlan:
+def moe_route(router_logits: torch.Tensor, k: int, mode: int = 0, expert_range=None, token_tile: int = 0, topk=None) -> MoePlan:
     """router_logits [T, E] fp32 -> MoePlan (top-k, routing weights, rows grouped by expert, GEMM tile list).
     mode 0: softmax over the selected logits; 1: softmax over all experts; 2: the latter renormalised.
-    expert_range (lo, hi): only these experts are local (expert parallelism)."""
+    expert_range (lo, hi): only these experts are local (expert parallelism).  topk = (idx int32 [T, k], weights fp32 [T, k]):
+    a selection made elsewhere (PhiMoE's sparse mixer); only the grouping by expert is computed."""
     assert router_logits.is_cuda and router_logits.dtype == torch.float32 and router_logits.stride(-1) == 1
     T, E = router_logits.shape
     L = _lib.lib()
@@ -308,16 +309,21 @@ def moe_route(router_logits: torch.Tensor, k: int, mode: int = 0, expert_range=N
     pl.T, pl.k, pl.E, pl.bt = T, k, E, bt
     pl.max_tiles = L.ogb_moe_max_tiles(n, hi - lo, bt)
     i32 = dict(dtype=torch.int32, device=dev)
-    pl.topk_idx = torch.empty(T, k, **i32)
-    pl.topk_w = torch.empty(T, k, dtype=torch.float32, device=dev)
+    if topk is not None:
+        pl.topk_idx, pl.topk_w = topk
+        assert pl.topk_idx.dtype == torch.int32 and pl.topk_w.dtype == torch.float32 and pl.topk_idx.shape == (T, k)
+    else:
+        pl.topk_idx = torch.empty(T, k, **i32)
+        pl.topk_w = torch.empty(T, k, dtype=torch.float32, device=dev)
     pl.expert_offsets = torch.empty(E + 1, **i32)
     pl.sorted_token = torch.empty(n, **i32)
     pl.inv_pos = torch.empty(T, k, **i32)
     tiles = torch.empty(3 * pl.max_tiles + 1, **i32)
     pl.tile_expert, pl.tile_row0, pl.tile_rows = tiles[:pl.max_tiles], tiles[pl.max_tiles:2 * pl.max_tiles], tiles[2 * pl.max_tiles:3 * pl.max_tiles]
     pl.num_tiles = tiles[3 * pl.max_tiles:]
-    _lib.check(L.ogb_moe_topk(_ptr(router_logits), router_logits.stride(0), T, E, k, mode, _ptr(pl.topk_idx), _ptr(pl.topk_w), _stream()),
-               "moe_topk")
+    if topk is None:
+        _lib.check(L.ogb_moe_topk(_ptr(router_logits), router_logits.stride(0), T, E, k, mode, _ptr(pl.topk_idx), _ptr(pl.topk_w), _stream()),
+                   "moe_topk")
     _lib.check(L.ogb_moe_sort(_ptr(pl.topk_idx), T, k, E, lo, hi, bt, _ptr(pl.expert_offsets), _ptr(pl.sorted_token), _ptr(pl.inv_pos),
                               _ptr(pl.tile_expert), _ptr(pl.tile_row0), _ptr(pl.tile_rows), _ptr(pl.num_tiles), pl.max_tiles, _stream()),
                "moe_sort")

@@ -107,10 +107,13 @@ def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None):
         h = h + o * arch.residual_multiplier
         x = _norm(h, g(mid + ".weight"), g(mid + ".bias"), arch)
         if arch.num_experts > 0 and arch.moe_style == "standard":
-            probs = torch.softmax(x @ g("mlp.router.weight").t(), -1)
+            rl = x @ g("mlp.router.weight").t()
+            probs = torch.softmax(rl, -1)
             tw, ti = torch.topk(probs, arch.experts_per_token, -1)
             if arch.moe_norm_topk:
                 tw = tw / tw.sum(-1, keepdim=True)
+            if arch.moe_sparse_mixer:
+                tw, ti = _sparse_mixer_loop(rl, arch.moe_jitter_eps)
             y = torch.zeros_like(x)
             for t in range(S):
                 for j in range(arch.experts_per_token):
@@ -191,3 +194,22 @@ def vision_encoder(cfg, sd, pixels):
         h = F.gelu(h @ sd["projector.fc1.weight"].float().t() + sd["projector.fc1.bias"].float())
         h = h @ sd["projector.fc2.weight"].float().t() + sd["projector.fc2.bias"].float()
     return h
+
+
+def _sparse_mixer_loop(logits, eps):
+    """PhiMoE routing, token by token in plain Python: pick the best expert, weight it by a softmax over the logits within
+    the relative margin of the maximum; remove it and repeat once."""
+    T, E = logits.shape
+    w, idx = torch.zeros(T, 2), torch.zeros(T, 2, dtype=torch.long)
+    for t in range(T):
+        s = logits[t].tolist()
+        cur = list(s)
+        for j in range(2):
+            top = max(cur)
+            i = cur.index(top)
+            kept = [cur[e] for e in range(E) if cur[e] != float("-inf") and (top - s[e]) / max(abs(s[e]), top) <= 2 * eps]
+            m = max(kept)
+            z = sum(math.exp(v - m) for v in kept)
+            w[t, j], idx[t, j] = math.exp(top - m) / z, i
+            cur[i] = float("-inf")
+    return w, idx

@@ -38,6 +38,8 @@ FAMILIES = {
     "mixtral": dict(model_type="mixtral", moe_style="standard", num_experts=4, experts_per_token=2, intermediate_size=64),
     "qwen3_moe": dict(model_type="qwen3_moe", moe_style="standard", moe_norm_topk=False, qk_norm=True, num_experts=8, experts_per_token=3,
                       intermediate_size=64),
+    "phimoe": dict(model_type="phimoe", moe_style="standard", moe_sparse_mixer=True, moe_jitter_eps=0.05, layernorm=True, attn_bias=True,
+                   o_bias=True, lm_head_bias=True, num_experts=4, experts_per_token=2, intermediate_size=64),
     "gemma2": dict(model_type="gemma2", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, softcap=20.0,
                    final_logit_softcap=15.0, sliding_window=8, sliding_layers=[0, 2], attn_scale=0.2, tie_embeddings=True),
     "gemma3": dict(model_type="gemma3_text", activation="gelu", norm_offset=1.0, embed_scale=8.0, post_sublayer_norms=True, qk_norm=True,
@@ -60,7 +62,7 @@ def test_family_logits_and_decode_match_dense_reference(family, tmp_path):
     a2 = model.arch
     for f in ("norm_eps", "layernorm", "qk_norm", "attn_bias", "o_bias", "mlp_bias", "softcap", "sliding_window", "attn_sinks",
               "activation", "num_experts", "experts_per_token", "post_sublayer_norms", "rotary_interleaved", "lm_head_bias",
-              "mlp_gated", "parallel_block", "learned_positions", "conv_L_cache", "conv_bias", "moe_style", "moe_norm_topk"):
+              "mlp_gated", "parallel_block", "learned_positions", "conv_L_cache", "conv_bias", "moe_style", "moe_norm_topk", "moe_sparse_mixer", "moe_jitter_eps"):
         assert getattr(a2, f) == pytest.approx(getattr(arch, f)), f
     assert a2.intermediate_size == arch.intermediate_size and a2.rotary_dim == arch.rotary_dim and a2.layer_types == arch.layer_types
     prompt = np.random.RandomState(4).randint(0, arch.vocab_size - 1, size=(1, 23)).astype(np.int32)

@@ -221,7 +221,7 @@ def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, mon
     assert len(c[1]) <= max(5, len(a[1])) and all(len(c[i]) > 0 for i in (0, 2, 3))
 
 
-@pytest.mark.parametrize("family", ["phi_parallel", "gpt2", "lfm2", "mixtral", "qwen_moe"])
+@pytest.mark.parametrize("family", ["phi_parallel", "gpt2", "lfm2", "mixtral", "qwen_moe", "phimoe"])
 def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_path):
     """fc1 -> GELU -> fc2 MLPs, the parallel attention/MLP block, learned position tables, hybrid convolution layers: bf16 GPU
     against fp32 CPU."""
@@ -232,6 +232,8 @@ def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_pat
                           mlp_gated=False, learned_positions=True, tie_embeddings=True),
              "lfm2": dict(model_type="lfm2", qk_norm=True, tie_embeddings=True, conv_L_cache=3, layer_types=["conv", "full_attention"]),
              "mixtral": dict(model_type="mixtral", moe_style="standard", num_experts=4, experts_per_token=2, intermediate_size=128),
+             "phimoe": dict(model_type="phimoe", moe_style="standard", moe_sparse_mixer=True, moe_jitter_eps=0.05, layernorm=True,
+                            attn_bias=True, o_bias=True, lm_head_bias=True, num_experts=4, experts_per_token=2, intermediate_size=128),
              "qwen_moe": dict(model_type="qwen3_moe", moe_style="standard", moe_norm_topk=False, qk_norm=True, num_experts=8,
                               experts_per_token=3, intermediate_size=128)}[family]
     arch = ArchConfig(**{**dict(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=64, intermediate_size=512,
