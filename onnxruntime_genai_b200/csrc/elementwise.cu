@@ -204,8 +204,9 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
       for (int e = lane; e < p.D; e += 32) amax = fmaxf(amax, fabsf(v[e]));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      const float scale = amax > 0.f ? amax / 127.f : 1.f;
-      const float inv = 1.f / scale;
+      // correctly rounded divisions (the library is built with fast-math): the stored scale is the same on every path
+      const float scale = amax > 0.f ? __fdiv_rn(amax, 127.f) : 1.f;
+      const float inv = __fdiv_rn(1.f, scale);
       int8_t* row = reinterpret_cast<int8_t*>(is_k ? p.k_cache : p.v_cache) + (size_t(slot) * p.Hkv + kvh) * (p.D + 16);
       for (int e = lane; e < p.D; e += 32) row[e] = int8_t(max(-127, min(127, __float2int_rn(v[e] * inv))));
       if (lane == 0) *reinterpret_cast<float*>(row + p.D) = scale;
