@@ -55,6 +55,7 @@ struct GemmParams {
   const __nv_bfloat16* bias;
   int* status;
   int pdl;
+  int l2_prefetch;      // 1: the producer prefetches its whole weight stream into L2 before waiting for the previous kernel
   CommParams comm;
   int comm_epilogue;    // 1: the epilogue runs the fused all-reduce / reduce-scatter (and the call closes an epoch)
   int ag_rows;          // > 0: all-gather -> GEMM: the activations are not read through the tensor map but assembled from the

@@ -116,6 +116,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       // before waiting for the producer of the activations.
       const int pre = min(STAGES, num_kb);
       for (int i = 0; i < pre; ++i) load_w(i);
+      // The rest of this CTA's weight stream goes to L2 while the previous kernel is still finishing (opt-in)
+      if (p.l2_prefetch)
+        for (int i = pre; i < num_kb; ++i) tma_prefetch_l2_2d(&tmap_w, (kb0 + i) * GEMM_BLOCK_K, w_row0 + n_tile * GEMM_BLOCK_N);
       if (p.pdl) pdl_wait();
       for (int i = 0; i < pre; ++i) load_a(i);
       int issued = pre;
@@ -929,6 +932,11 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.status = status;
   p.pdl = pdl_enabled;
+  // OGB_GEMM_L2_PREFETCH=1: decode-sized launches prefetch each CTA's whole weight stream into L2 before the dependency wait.
+  // Opt-in: measured on B200 at 64 tokens it only adds traffic ahead of the demand loads - gate/up 42.9 -> 55.0 us, down
+  // 28.0 -> 31.0 us, qkv 15.8 -> 16.4 us, o 13.0 -> 13.2 us; the decode step 5.54 -> 6.16 ms.
+  static const int l2_prefetch = [] { const char* e = getenv("OGB_GEMM_L2_PREFETCH"); return (e && e[0] == '1') ? 1 : 0; }();
+  p.l2_prefetch = l2_prefetch && pdl_enabled && bt <= 64;
   if (fused_ar) {
     if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
     const CommParams& c = g_comm[device];
