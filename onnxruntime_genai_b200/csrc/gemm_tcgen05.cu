@@ -289,6 +289,27 @@ static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams
   return cudaLaunchKernelEx(&cfg, kern, tw, ta, p) == cudaSuccess ? 0 : -4;
 }
 
+// How many split-K clusters of `splits` CTAs of the decode kernel the device can hold at once (0: the query failed).  The
+// CTAs of a cluster must sit in one GPC, so this is less than (resident CTAs) / splits in general.
+template <int BT>
+static int MaxActiveClusters(int splits) {
+  using Cfg = GemmCfg<BT>;
+  auto kern = gemm_tcgen05_kernel<BT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, unsigned(splits));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = unsigned(splits);
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
 // ------------------------------------------------------------------------------------------ persistent prefill kernel
 // Compute-bound shapes (hundreds of tokens and more): one CTA per SM walks a list of 128 x 256 output tiles, weight-tile
 // index slowest so that the CTAs of the moment share a few weight tiles and the whole activation matrix in L2.  The TMA
@@ -852,9 +873,14 @@ OGB_API int ogb_gemm_token_tile(int M, int dual) {
   return big;
 }
 
-// Number of split-K partitions (cluster size along z: 1, 2, 4 or 8; other sizes schedule poorly onto
-// the GPCs): the largest that still fits every CTA of the launch on the GPU at once (two resident
-// CTAs per SM for decode-sized tiles) while leaving each split at least 16 k-blocks to stream.
+// Number of split-K partitions (cluster size along z: 1, 2, 4 or 8): the largest that still fits every CTA of the launch
+// on the GPU at once (two resident CTAs per SM for decode-sized tiles) while leaving each split at least 16 k-blocks to
+// stream.  Measured on B200 at 64 tokens (Llama-3.1-8B shapes, us per launch; utils/kernel_case.py --gemm_splits):
+//   qkv  (N 6144, K 4096):  s=2 16.8  s=3 16.1  s=4 15.5  s=5 15.5  s=6 24.7  s=8 25.8      (a second wave from 288 CTAs on)
+//   o    (N 4096, K 4096):  s=2 15.8  s=4 12.9  s=5 14.0  s=8 14.7
+//   down (N 4096, K 14336): s=2 41.3  s=4 28.4  s=5 28.0  s=7 27.9  s=8 27.6
+// Reducing through global memory instead of the cluster's shared memory (partials in an fp32 scratch, the last CTA of a
+// tile sums them) was measured too and is not kept: o 22.5..29.7, qkv 24.3..27.6, down 38.6..45.5 us.
 OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
   const int bt = ogb_gemm_token_tile(M, dual);
   const int tiles = ((N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N) * ((M + bt - 1) / bt);
@@ -866,6 +892,17 @@ OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
     best = s;
   }
   return best;
+}
+
+OGB_API int ogb_gemm_max_active_clusters(int bt, int splits) {
+  if (splits < 1 || splits > 8) return 0;
+  switch (bt) {
+    case 16: return MaxActiveClusters<16>(splits);
+    case 32: return MaxActiveClusters<32>(splits);
+    case 64: return MaxActiveClusters<64>(splits);
+    case 128: return MaxActiveClusters<128>(splits);
+  }
+  return 0;
 }
 
 // Registers this rank's view of the symmetric buffers (peer-mapped pointers) for a device.

@@ -17,6 +17,7 @@ int ogb_sm_count(int device);
 
 // ---- gemm_tcgen05.cu
 int ogb_gemm_token_tile(int M, int dual);
+int ogb_gemm_max_active_clusters(int bt, int splits);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
 int ogb_streamk_register(int device, void* scratch, void* flags, void* epoch, int max_ctas);
 int ogb_comm_register(int device, int world, int rank, void** buf, void* epoch, long long plane_elems);

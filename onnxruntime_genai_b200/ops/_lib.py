@@ -23,6 +23,7 @@ _SIGS = {
     "ogb_sm_count": (c_int, [c_int]),
     "ogb_gemm_token_tile": (c_int, [c_int, c_int]),
     "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "ogb_gemm_max_active_clusters": (c_int, [c_int, c_int]),
     "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P]),
     "ogb_streamk_register": (c_int, [c_int, _P, _P, _P, c_int]),
     "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, c_longlong]),
