@@ -215,15 +215,15 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     }
   };
   // KV8: expands raw stage `buf` into the bf16 K and V tiles (value * scale, rounded to bf16).
-  auto expand_kv8 = [&](int buf) {
+  auto expand_kv8_rows = [&](int buf, int key0, int nkeys, int worker, int workers) {
     constexpr int VCH = D / 16;          // 16-byte chunks of int8 values per row
     const uint8_t* rk = sRaw + size_t(buf * 2) * ATT_BN * RP;
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
       const uint8_t* src = rk + which * ATT_BN * RP;
       __nv_bfloat16* dst = which ? sV : sK;
-      for (int item = tid; item < ATT_BN * VCH; item += ATT_THREADS) {
-        const int key = item / VCH, c = item % VCH;
+      for (int item = worker; item < nkeys * VCH; item += workers) {
+        const int key = key0 + item / VCH, c = item % VCH;
         const uint4 raw = *reinterpret_cast<const uint4*>(src + key * RP + c * 16);
         const float sc = *reinterpret_cast<const float*>(src + key * RP + D);
         const int8_t* qv = reinterpret_cast<const int8_t*>(&raw);
@@ -298,14 +298,22 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
       if (it + 2 < n_tiles) load_kv8(tile_begin + it + 2, (it + 2) % ATT_STAGES);
       cp_async_commit();
       cp_async_wait<2>();
-      __syncthreads();          // raw stage `buf` has landed; every warp is done with the bf16 tiles of the last iteration
-      expand_kv8(buf);
-      __syncthreads();
+      if (DECODE) {
+        // decode mode: a warp loads, expands and consumes the same 16 keys of every tile, so after the Q tile (first
+        // iteration) the warps need not meet again until the merge
+        if (it == 0) __syncthreads(); else __syncwarp();
+        expand_kv8_rows(buf, warp * 16, 16, lane, 32);
+        __syncwarp();
+      } else {
+        __syncthreads();        // raw stage `buf` has landed; every warp is done with the bf16 tiles of the last iteration
+        expand_kv8_rows(buf, 0, ATT_BN, tid, ATT_THREADS);
+        __syncthreads();
+      }
     } else {
       if (it + 2 < n_tiles) load_kv(tile_begin + it + 2, (it + 2) % ATT_STAGES);
       cp_async_commit();
       cp_async_wait<2>();
-      __syncthreads();
+      if (DECODE && it > 0) __syncwarp(); else __syncthreads();   // decode mode: the K/V rows of a warp are its own (see above)
     }
     if (it == 0 && warp_active) {
 #pragma unroll
@@ -387,7 +395,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
       }
     }
-    __syncthreads();
+    if (DECODE && !TMA) __syncwarp(); else __syncthreads();
   }
   cp_async_wait<0>();
 
