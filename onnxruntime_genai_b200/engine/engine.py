@@ -242,11 +242,14 @@ class ModelExecutor:
         bb = min(self._bucket(B), st.max_batch)
         cb = min(self._bucket(plan.block_table_columns, 8), st.table_cols)
         if bb not in self._unsplit:
-            # The column bucket only bounds the key range that the attention launch splits; a batch large enough to fill the
-            # GPU without splitting has one graph for every length (no capture in the middle of a long decode).  Not for
-            # long-context RoPE models, whose step bound also selects the cache pair.
+            # The column bucket only bounds the key range that the attention launch splits; a batch whose split choice does not
+            # depend on the length (no split, or an even division) has one graph for every length (no capture in the middle of
+            # a long decode).  Not for long-context RoPE models, whose step bound also selects the cache pair.
             dec = self.decoder
-            self._unsplit[bb] = dec.cos_small is None and ops.choose_kv_splits(bb, dec.kv_heads_local, 1, 1 << 24, group=dec.heads_local // dec.kv_heads_local)[0] == 1
+            g_ = dec.heads_local // dec.kv_heads_local
+            far = ops.choose_kv_splits(bb, dec.kv_heads_local, 1, 1 << 24, group=g_, ordered=self.order_attention)
+            near = ops.choose_kv_splits(bb, dec.kv_heads_local, 1, 4096, group=g_, ordered=self.order_attention)
+            self._unsplit[bb] = dec.cos_small is None and far == near and far[1] == 0
         if self._unsplit[bb]:
             cb = st.table_cols
         key = (bb, cb)

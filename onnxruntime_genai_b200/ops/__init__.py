@@ -374,12 +374,21 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
 
 
 # ------------------------------------------------------------------------------------------ attention
-def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_count: int = 148, group: int = 1):
+def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_count: int = 148, group: int = 1, ordered: bool = False):
     """(splits, kv_chunk) of a paged-attention launch.  A launch whose (request, kv head) grid already fills the GPU
     twice over is not split (measured on B200: at 64 requests x 8 heads any split costs more in partial traffic and
     the merge than it gains in balance).  Smaller decode-sized launches split every request's keys into fixed chunks
-    of 64..512 keys sized for about four CTAs per SM; other launches: (1, 0)."""
+    of 64..512 keys sized for about four CTAs per SM; other launches: (1, 0).
+
+    ordered: the caller issues the requests longest first.  Then every request is divided evenly into as many parts as
+    bring the launch to about 1.75 waves of CTAs - measured on B200 with 64 requests of 192..2112 keys and 4 / 2 / 1 kv
+    heads per GPU (the tensor-parallel shapes): 2 parts 35.3 us against 43.1 us for fixed chunks, 4 parts 25.1 against
+    29.4, 4 parts 18.7 against 22.0."""
     ctas = max(1, batch * Hkv)
+    if ordered and ctas >= 32 and max_q_len * group <= 16 and max_kv_len > 128:
+        s = int(round(1.75 * 2 * sm_count / ctas))
+        s = max(1, min(4, s, max_kv_len // 256))     # more than 4 parts: the pieces get too short (1 kv head: 8 parts 20.5 us, 16 parts 27.7)
+        return s, 0
     if max_q_len * group > 16 or max_kv_len <= 128 or ctas >= 2 * sm_count:
         return 1, 0
     chunks_wanted = max(1, (4 * sm_count + ctas - 1) // ctas)
@@ -406,7 +415,7 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
         max_q_len = T
     kv_chunk = 0
     if splits is None:
-        splits, kv_chunk = choose_kv_splits(B, Hkv, max_q_len, max_kv_len or 1024, group=Hq // Hkv)
+        splits, kv_chunk = choose_kv_splits(B, Hkv, max_q_len, max_kv_len or 1024, group=Hq // Hkv, ordered=order is not None)
     elif isinstance(splits, tuple):
         splits, kv_chunk = splits
     ws = workspace(q.device)
