@@ -468,3 +468,17 @@ def test_decode_advance_reference():
     assert slots.tolist() == [9 * 4 + 0, 3 * 4 + 0]
     ops.decode_advance(torch.tensor([1, 1], dtype=torch.int32), ids, pos, past, slots, spos, table[:, :2], 4)
     assert slots.tolist() == [9 * 4 + 1, -1]       # position 9 lies in column 2, which this table does not have
+
+
+def test_attention_split_choice():
+    from onnxruntime_genai_b200 import ops
+    # 64 requests x 8 / 4 / 2 / 1 kv heads per GPU, requests issued longest first: 1 / 2 / 4 / 4 even parts (no fixed chunk)
+    for hkv, want in ((8, 1), (4, 2), (2, 4), (1, 4)):
+        assert ops.choose_kv_splits(64, hkv, 1, 4096, group=4, ordered=True) == (want, 0)
+        assert ops.choose_kv_splits(64, hkv, 1, 1 << 24, group=4, ordered=True) == (want, 0)     # independent of the bound
+    assert ops.choose_kv_splits(64, 2, 1, 300, group=4, ordered=True) == (1, 0)                   # pieces would be too short
+    # unordered small batches keep fixed chunks sized for the GPU; big batches and prefill-sized steps do not split
+    s, chunk = ops.choose_kv_splits(1, 8, 1, 8192, group=4)
+    assert s > 1 and chunk % 64 == 0 and s * chunk >= 8192
+    assert ops.choose_kv_splits(64, 8, 1, 4096, group=4) == (1, 0)
+    assert ops.choose_kv_splits(4, 8, 512, 4096, group=4) == (1, 0)
