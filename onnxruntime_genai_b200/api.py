@@ -277,6 +277,7 @@ class SequenceState:
         self._free: List[int] = []
         self._moves: List[tuple] = []              # (src block, dst block) copies to do before the next forward
         self._tbl_dirty = False
+        self.rope_delta = [0] * rows                 # multimodal RoPE: offset of a row's rotary position from its cache position
         self.cross = None                            # encoder keys / values of an encoder-decoder model (set_cross)
         self.cross_table = self.cross_lens = None
         self.max_cross_len = 0
@@ -310,10 +311,13 @@ class SequenceState:
         return dict(cross=self.cross, cross_table=self.cross_table[rows_used].contiguous() if sel else self.cross_table,
                     cross_lens=self.cross_lens[rows_used].contiguous() if sel else self.cross_lens, max_cross_len=self.max_cross_len)
 
-    def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None) -> torch.Tensor:
+    def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None, positions3=None) -> torch.Tensor:
         """Feeds row_tokens[r] (possibly empty) after the cached prefix of row r; returns fp32 logits of the last
-        fed token of every non-empty row (or of every token)."""
+        fed token of every non-empty row (or of every token).  positions3[r]: [3, len(row_tokens[r])] rotary position
+        components of the fed tokens (multimodal RoPE); later tokens continue one past the largest component."""
         dev = self.decoder.device
+        mrope = self.decoder.arch.mrope_section is not None and (positions3 is not None or any(self.rope_delta))
+        p3: List[np.ndarray] = []
         ids, pos, slots, cu, past, rows_used, last = [], [], [], [0], [], [], []
         for r, toks in enumerate(row_tokens):
             if not toks:
@@ -328,6 +332,13 @@ class SequenceState:
                 ids.append(t)
                 pos.append(p)
                 slots.append(self._slot(r, p))
+            if mrope:
+                if positions3 is not None and positions3[r] is not None:
+                    comp = np.asarray(positions3[r], dtype=np.int32).reshape(3, len(toks))
+                    self.rope_delta[r] = int(comp.max()) + 1 - (base + len(toks))
+                else:
+                    comp = np.tile(np.arange(base, base + len(toks), dtype=np.int32) + self.rope_delta[r], (3, 1))
+                p3.append(comp)
             cu.append(len(ids))
             past.append(base)
             rows_used.append(r)
@@ -340,6 +351,8 @@ class SequenceState:
                        logits_rows=None if want_all_logits else i32(last),
                        max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds,
                        **self._cross_fields(rows_used))
+        if mrope:
+            s.positions3 = torch.from_numpy(np.ascontiguousarray(np.concatenate(p3, axis=1))).to(dev)
         return self.decoder.forward(s, self.kv), rows_used
 
     # ---- single-token decode steps replayed from CUDA graphs (one graph per power-of-two bound on the KV length)
@@ -349,6 +362,8 @@ class SequenceState:
             return False
         if dec.arch.num_experts > 0 and not all(lw.exp_blocked for lw in dec.layers):
             return False   # the unfused expert loop reads counts back to the host
+        if any(self.rope_delta):
+            return False   # rotary positions differ from the cache positions (multimodal RoPE after an image)
         return dec.tp.size == 1
 
     def run_decode_graph(self, last_tokens: List[int]) -> torch.Tensor:
@@ -402,6 +417,8 @@ class SequenceState:
 
     def rewind(self, row: int, length: int):
         self.kv_len[row] = min(self.kv_len[row], length)
+        if length == 0:
+            self.rope_delta[row] = 0
         if self._tbl is not None:
             self._recount()
 
@@ -580,7 +597,8 @@ class Generator:
             elif all(len(t) == 1 for t in row_tokens) and self._started and self.state.graph_ok():
                 logits = self.state.run_decode_graph([t[0] for t in row_tokens])
             else:
-                logits, used = self.state.run(row_tokens, inputs_embeds=self._embeds_with_images(row_tokens))
+                logits, used = self.state.run(row_tokens, inputs_embeds=self._embeds_with_images(row_tokens),
+                                              positions3=self._take_position_ids(row_tokens))
                 if len(used) != self.rows:
                     full = torch.empty(self.rows, logits.shape[1], dtype=torch.float32, device=logits.device)
                     full[used] = logits
@@ -782,6 +800,26 @@ class Generator:
             self.append_tokens(arr(named["input_ids"]))
 
     _image_features: Optional[torch.Tensor] = None
+
+    def _take_position_ids(self, row_tokens: List[List[int]]):
+        """A staged `position_ids` input of shape [3, batch, sequence] (multimodal RoPE, reference:
+        src/models/position_inputs.cpp, the Qwen2-VL branch) applies to the next tokens fed: per row the three components of
+        its tokens."""
+        extra = getattr(self, "_extra_inputs", {})
+        if self.model.arch.mrope_section is None or "position_ids" not in extra:
+            return None
+        v = extra.pop("position_ids")
+        arr = np.asarray(v.as_numpy() if isinstance(v, Tensor) else v)
+        if arr.ndim != 3 or arr.shape[0] != 3:
+            raise RuntimeError("position_ids for multimodal RoPE must have shape [3, batch, sequence]")
+        nb = self.search_opts["num_beams"]
+        out = []
+        for r, toks in enumerate(row_tokens):
+            comp = arr[:, r // nb, :]
+            if comp.shape[1] < len(toks):
+                raise RuntimeError("position_ids are shorter than the tokens they describe")
+            out.append(comp[:, comp.shape[1] - len(toks):] if toks else None)
+        return out
 
     def _embeds_with_images(self, row_tokens: List[List[int]]) -> Optional[torch.Tensor]:
         """Token embeddings of the packed step with the rows at image-token positions replaced, in order, by the pending

@@ -154,7 +154,16 @@ struct RopeParams {
   float norm_eps;
   int T, Hq, Hkv, D, rot, interleaved, max_pos;
   int kv8;   // 8-bit cache: rows of D int8 values + fp32 scale (absmax / 127 of the row) + 12 bytes of padding
+  // Multimodal RoPE (Qwen2-VL): three position components per token ([3, T]: temporal, height, width); rotary pair i takes
+  // component 0 below sec0, component 1 below sec1, component 2 above.  Null: the single `positions` array.
+  const int32_t* positions3;
+  int sec0, sec1;
 };
+
+__device__ __forceinline__ int rope_pos(const RopeParams& p, int t, int i) {
+  int pos = p.positions3 ? p.positions3[size_t(i < p.sec0 ? 0 : (i < p.sec1 ? 1 : 2)) * p.T + t] : p.positions[t];
+  return pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+}
 
 __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
   pdl_launch_dependents();
@@ -187,14 +196,11 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
     if (p.kv8) {
       // rotate in the row buffer, then quantise the whole row against its largest magnitude
       if (is_k && p.rot > 0) {
-        int pos = p.positions[t];
-        pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
         const int half = p.rot / 2;
-        const float* cs = p.cos_cache + size_t(pos) * half;
-        const float* sn = p.sin_cache + size_t(pos) * half;
         for (int i = lane; i < half; i += 32) {
           const int a = p.interleaved ? 2 * i : i, b = p.interleaved ? 2 * i + 1 : i + half;
-          const float x1 = v[a], x2 = v[b], c = cs[i], s = sn[i];
+          const size_t ci = size_t(rope_pos(p, t, i)) * half + i;
+          const float x1 = v[a], x2 = v[b], c = p.cos_cache[ci], s = p.sin_cache[ci];
           v[a] = x1 * c - x2 * s;
           v[b] = x2 * c + x1 * s;
         }
@@ -215,14 +221,11 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeParams p) {
     dst = (is_k ? p.k_cache : p.v_cache) + (size_t(slot) * p.Hkv + kvh) * p.D;
   }
   if ((is_q || is_k) && p.rot > 0) {
-    int pos = p.positions[t];
-    pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
     const int half = p.rot / 2;
-    const float* cs = p.cos_cache + size_t(pos) * half;
-    const float* sn = p.sin_cache + size_t(pos) * half;
     for (int i = lane; i < half; i += 32) {
       const int a = p.interleaved ? 2 * i : i, b = p.interleaved ? 2 * i + 1 : i + half;
-      const float x1 = v[a], x2 = v[b], c = cs[i], s = sn[i];
+      const size_t ci = size_t(rope_pos(p, t, i)) * half + i;
+      const float x1 = v[a], x2 = v[b], c = p.cos_cache[ci], s = p.sin_cache[ci];
       dst[a] = f2bf(x1 * c - x2 * s);
       dst[b] = f2bf(x2 * c + x1 * s);
     }
@@ -443,19 +446,20 @@ OGB_API int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positio
                                const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
                                float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream) {
   return ogb_rope_kv_append_bits(qkv, qkv_stride, positions, slots, cos_cache, sin_cache, k_cache, v_cache, q_norm_w, k_norm_w, norm_eps, T,
-                                 Hq, Hkv, D, rot, interleaved, max_pos, 16, stream);
+                                 Hq, Hkv, D, rot, interleaved, max_pos, 16, nullptr, 0, 0, stream);
 }
 
 // kv_bits 16: bf16 cache rows; 8: int8 rows with an inline scale (row pitch D + 16 bytes, D a multiple of 16).
 OGB_API int ogb_rope_kv_append_bits(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
                                     const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
                                     float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, int kv_bits,
-                                    void* stream) {
+                                    const int32_t* positions3, int sec0, int sec1, void* stream) {
   if (T <= 0) return 0;
   if (D > 256 || rot > D || (rot & 1)) return -1;
   if (kv_bits != 16 && (kv_bits != 8 || (D % 16))) return -1;
   RopeParams p;
   p.kv8 = kv_bits == 8;
+  p.positions3 = positions3; p.sec0 = sec0; p.sec1 = sec1;
   p.qkv = static_cast<__nv_bfloat16*>(qkv); p.qkv_stride = qkv_stride; p.positions = positions; p.slots = slots;
   p.cos_cache = cos_cache; p.sin_cache = sin_cache;
   p.k_cache = static_cast<__nv_bfloat16*>(k_cache); p.v_cache = static_cast<__nv_bfloat16*>(v_cache);

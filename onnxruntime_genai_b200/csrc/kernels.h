@@ -60,7 +60,7 @@ int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, cons
                        float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream);
 int ogb_rope_kv_append_bits(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
                        const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
-                       float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, int kv_bits, void* stream);
+                       float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, int kv_bits, const int32_t* positions3, int sec0, int sec1, void* stream);
 int ogb_embedding_q4(const int32_t* ids, const void* q, const void* scales, const void* zps, void* out, int T, int K, int vocab,
                      float mult, void* stream);
 int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream);

@@ -16,7 +16,7 @@ import numpy as np
 LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
-    "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe",
+    "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl",
 ]
 
 
@@ -64,6 +64,8 @@ class ArchConfig:
     layer_types: Optional[List[str]] = None
     conv_L_cache: int = 3
     conv_bias: bool = False
+    # Multimodal RoPE (Qwen2-VL): rotary pairs per position component (temporal, height, width); None: ordinary RoPE
+    mrope_section: Optional[List[int]] = None
     cross_attention: bool = False    # encoder-decoder (whisper): every layer also attends to the encoder's output
     encoder_hidden_size: int = 0     # width of the encoder output the cross-attention keys / values are projected from (0 = hidden_size)
     mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
@@ -224,6 +226,10 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.attn_bias = a.o_bias = a.mlp_bias = a.lm_head_bias = True
         a.mlp_gated = False
         a.parallel_block = True
+    if mt in ("qwen2_vl", "qwen2_5_vl") or (cfg.get("rope_scaling") or {}).get("mrope_section"):
+        a.mrope_section = list((cfg.get("rope_scaling") or {}).get("mrope_section") or [16, 24, 24])
+        a.rope_scaling = None
+        a.attn_bias = True
     if mt == "lfm2":
         a.layer_types = list(cfg.get("layer_types") or ["full_attention"] * a.num_layers)
         a.conv_L_cache = int(cfg.get("conv_L_cache", 3))

@@ -36,6 +36,7 @@ class StepInputs:
     max_q_len: int = 1
     max_kv_len: int = 1
     inputs_embeds: Optional[torch.Tensor] = None  # overrides the embedding lookup (multimodal / MTP)
+    positions3: Optional[torch.Tensor] = None     # [3, T] int32 position components of multimodal RoPE (None: `positions`)
     attn_order: Optional[torch.Tensor] = None     # [B] int32 permutation of the requests, longest first (attention CTA issue order)
     cross: Optional["CrossKVCache"] = None        # encoder keys / values of an encoder-decoder model
     cross_table: Optional[torch.Tensor] = None    # [B, cols] blocks of each request's encoder keys in `cross`
@@ -348,7 +349,8 @@ class DecoderModel:
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
             ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
-                               a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+                               a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
+                               s.positions3 if a.mrope_section else None, a.mrope_section)
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
                                       max_q_len=s.max_q_len, max_kv_len=s.max_kv_len, order=s.attn_order)

@@ -110,6 +110,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         if rd:
             a.partial_rotary_factor = rd / a.head_dim
         a.qk_norm = "qk_norm_epsilon" in attn.attrs
+        ms = _attr(attn, "mrope_section")
+        a.mrope_section = [int(v) for v in ms] if ms else None
         a.attn_sinks = any(".sinks" in i for i in attn.inputs)
     windows = []
     for i in range(L):

@@ -357,10 +357,12 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, residual=None) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------ RoPE + KV append
 def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
-                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None):
+    """positions3 [3, T] int32 + mrope_section (rotary pairs per component: temporal, height, width): multimodal RoPE, the
+    pairs of each section rotate by their own position component."""
     if not qkv.is_cuda:
         return ref.rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved,
-                                  q_norm_w, k_norm_w, norm_eps)
+                                  q_norm_w, k_norm_w, norm_eps, positions3, mrope_section)
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
     assert cos_cache is None or cos_cache.dtype == torch.float32
     T = qkv.shape[0]
@@ -368,7 +370,10 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
     kv_bits = 8 if k_cache.dtype == torch.int8 else 16      # an int8 cache has rows of D values + inline scale (D + 16 bytes)
     rc = _lib.lib().ogb_rope_kv_append_bits(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(slots), _ptr(cos_cache), _ptr(sin_cache),
                                             _ptr(k_cache), _ptr(v_cache), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), T, Hq, Hkv,
-                                            D, int(rot if cos_cache is not None else 0), int(interleaved), max_pos, kv_bits, _stream())
+                                            D, int(rot if cos_cache is not None else 0), int(interleaved), max_pos, kv_bits,
+                                            _ptr(positions3.contiguous()) if positions3 is not None else None,
+                                            int(mrope_section[0]) if positions3 is not None else 0,
+                                            int(mrope_section[0] + mrope_section[1]) if positions3 is not None else 0, _stream())
     _lib.check(rc, "rope_kv_append")
     return qkv
 

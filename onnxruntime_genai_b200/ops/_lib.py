@@ -41,7 +41,7 @@ _SIGS = {
     "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, _P]),
     "ogb_rope_kv_append_bits": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_int, c_int, _P]),
+                                        c_int, c_int, _P, c_int, c_int, _P]),
     "ogb_embedding_q4": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_act_mul": (c_int, [_P, _P, c_int, c_int, c_int, _P]),
     "ogb_act": (c_int, [_P, _P, c_longlong, c_int, _P]),

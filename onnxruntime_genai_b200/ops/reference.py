@@ -96,7 +96,7 @@ def _rotate(v, cos, sin, rot, interleaved):
 
 
 def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
-                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6):
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None):
     """In place: rotates q inside `qkv`, writes rotated k and v into the caches at `slots`."""
     T = qkv.shape[0]
     dt = qkv.dtype
@@ -114,6 +114,13 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
     if rot > 0:
         pos = positions.long().clamp(0, cos_cache.shape[0] - 1)
         cos, sin = cos_cache[pos].float(), sin_cache[pos].float()
+        if positions3 is not None:
+            # multimodal RoPE: rotary pair i takes the angle of its section's position component
+            p3 = positions3.long().clamp(0, cos_cache.shape[0] - 1)
+            comp = torch.repeat_interleave(torch.arange(3), torch.tensor([mrope_section[0], mrope_section[1], rot // 2 - mrope_section[0] - mrope_section[1]]))
+            idx = torch.arange(rot // 2)
+            cos = cos_cache[p3[comp], idx[:, None]].t().float()      # [T, rot/2]
+            sin = sin_cache[p3[comp], idx[:, None]].t().float()
         q = _rotate(q, cos, sin, rot, interleaved)
         k = _rotate(k, cos, sin, rot, interleaved)
     qkv.view(T, Hq + 2 * Hkv, D)[:, :Hq] = q.to(dt)

@@ -29,7 +29,7 @@ def _rope(x, cos, sin, rot, interleaved):
     return out
 
 
-def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None):
+def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None, positions3=None):
     """ids: list of token ids; returns logits [len(ids), vocab] (fp32).  encoder_hidden [S_enc, H_enc]: output of the
     encoder for cross-attention decoders; inputs_embeds [len(ids), H] overrides the token embeddings."""
     sd = {k: v.float() for k, v in sd.items()}
@@ -39,7 +39,16 @@ def logits(arch, sd, ids, encoder_hidden=None, inputs_embeds=None):
     multi = longrope_caches(arch)
     if multi is not None and S <= multi[4]:
         cos, sin = multi[0], multi[1]      # sequences within the original context use the short-factor caches
-    cos, sin = torch.from_numpy(cos)[pos], torch.from_numpy(sin)[pos]
+    cos_t, sin_t = torch.from_numpy(cos), torch.from_numpy(sin)
+    cos, sin = cos_t[pos], sin_t[pos]
+    if positions3 is not None:
+        # multimodal RoPE: rotary pair i turns by the angle of its section's position component ([3, S] positions)
+        half = arch.rotary_dim // 2
+        sec = list(arch.mrope_section)
+        comp = [0] * sec[0] + [1] * sec[1] + [2] * (half - sec[0] - sec[1])
+        p3 = torch.as_tensor(positions3).long()
+        cos = torch.stack([cos_t[p3[comp[i]], i] for i in range(half)], dim=1)
+        sin = torch.stack([sin_t[p3[comp[i]], i] for i in range(half)], dim=1)
     h = sd["model.embed_tokens.weight"][torch.tensor(ids)] * arch.embed_scale
     if inputs_embeds is not None:
         h = inputs_embeds.float()

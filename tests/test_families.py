@@ -323,3 +323,40 @@ def test_snapshot_state_and_staged_hidden_states(tmp_path):
     hs = np.random.RandomState(0).randn(1, 1, arch.hidden_size).astype(np.float32)
     g.set_hidden_states(hs)
     np.testing.assert_array_equal(g.get_input("hidden_states"), hs)
+
+
+def test_multimodal_rope_positions(tmp_path):
+    """Qwen2-VL style decoder: with ordinary positions it equals plain RoPE; with three-component positions for the prompt
+    (an image block whose height / width components differ from the temporal one) the logits follow the dense reference, and
+    generated tokens continue one past the largest component."""
+    arch = ArchConfig(**{**BASE, "model_type": "qwen2_vl", "attn_bias": True, "mrope_section": [2, 3, 3]})
+    sd = random_state_dict(arch, seed=13, std=0.15)
+    d = str(tmp_path)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    model = og.Model(d)
+    assert model.arch.mrope_section == [2, 3, 3]
+    ids = np.random.RandomState(2).randint(0, arch.vocab_size - 1, size=(1, 12)).astype(np.int32)
+
+    def gen():
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=32)
+        return og.Generator(model, p)
+    g = gen()
+    g.append_tokens(ids)
+    np.testing.assert_allclose(g.get_logits().reshape(-1), dense_logits(arch, sd, ids[0].tolist())[-1].numpy(), rtol=2e-3, atol=3e-4)
+    # tokens 3..8 are a 2 x 3 image block: temporal stays at 3, height 3..4, width 3..5; text resumes at max + 1 = 6
+    t = [0, 1, 2, 3, 3, 3, 3, 3, 3, 6, 7, 8]
+    h = [0, 1, 2, 3, 3, 3, 4, 4, 4, 6, 7, 8]
+    w = [0, 1, 2, 3, 4, 5, 3, 4, 5, 6, 7, 8]
+    p3 = np.asarray([t, h, w], dtype=np.int32)
+    g = gen()
+    g.set_model_input("position_ids", p3[:, None, :])
+    g.append_tokens(ids)
+    want = dense_logits(arch, sd, ids[0].tolist(), positions3=p3)[-1].numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
+    assert g.state.rope_delta[0] == 9 - 12
+    g.generate_next_token()
+    seq = ids[0].tolist() + [int(g.get_next_tokens()[0])]
+    p3b = np.concatenate([p3, np.full((3, 1), 9, dtype=np.int32)], axis=1)
+    want = dense_logits(arch, sd, seq, positions3=p3b)[-1].numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=4e-4)

@@ -237,6 +237,34 @@ def test_rope_kv_append(D, rot, inter, qk_norm):
     _close(vc, vc2, rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("kv8", [False, True])
+def test_rope_multimodal_positions(kv8):
+    """Three position components per token, rotary pairs split into sections (Qwen2-VL); bf16 and int8 caches."""
+    T, Hq, Hkv, D, slots_n = 9, 4, 2, 128, 32
+    qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=29)
+    rng = np.random.RandomState(1)
+    p3 = torch.from_numpy(rng.randint(0, 60, size=(3, T)).astype(np.int32))
+    pos = torch.arange(T, dtype=torch.int32)
+    slots = torch.randperm(slots_n)[:T].to(torch.int32)
+    freqs = torch.outer(torch.arange(64).float(), 1.0 / (10000 ** (torch.arange(0, D, 2).float() / D)))
+    cos, sin = freqs.cos(), freqs.sin()
+    row = D + 16 if kv8 else D
+    dt = torch.int8 if kv8 else torch.bfloat16
+    kc, vc = torch.zeros(slots_n, Hkv, row, dtype=dt, device=DEV), torch.zeros(slots_n, Hkv, row, dtype=dt, device=DEV)
+    q2, kc2, vc2 = qkv.cpu().clone(), kc.cpu().clone(), vc.cpu().clone()
+    sec = [16, 24, 24]
+    ops.rope_kv_append(qkv, pos.to(DEV), slots.to(DEV), cos.to(DEV), sin.to(DEV), kc, vc, Hq, Hkv, D, D, False, None, None, 1e-6, p3.to(DEV), sec)
+    ref.rope_kv_append(q2, pos, slots, cos, sin, kc2, vc2, Hq, Hkv, D, D, False, None, None, 1e-6, p3, sec)
+    _close(qkv[:, :Hq * D], q2[:, :Hq * D], rtol=2e-2, atol=3e-2)
+    if kv8:
+        _close(ref.kv8_load(kc.cpu(), Hkv, D), ref.kv8_load(kc2, Hkv, D), rtol=3e-2, atol=3e-2)
+    else:
+        _close(kc, kc2, rtol=2e-2, atol=3e-2)
+    plain = q2.clone()
+    ref.rope_kv_append(plain.copy_(_rand(T, (Hq + 2 * Hkv) * D, seed=29).cpu()), pos, None, cos, sin, None, None, Hq, Hkv, D, D)
+    assert (plain[:, :Hq * D].float() - q2[:, :Hq * D].float()).abs().max() > 0.05      # the components really differ
+
+
 def test_embedding_gather_actmul_cast():
     table = _rand(1000, 512, seed=22)
     ids = torch.tensor([0, 5, 999, 17], dtype=torch.int32, device=DEV)
