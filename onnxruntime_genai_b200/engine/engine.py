@@ -232,6 +232,14 @@ class ModelExecutor:
             return logits[:B]
         st.upload()
         s = self._step_inputs(T, B, st.table_cols, plan.max_query_len, plan.max_kv_len)
+        if plan.max_query_len > 1:
+            # decode-first schedule: the requests that feed one token lead the batch
+            nd = 0
+            for e in plan.entries:
+                if e.num_tokens != 1:
+                    break
+                nd += 1
+            s.num_decode = nd
         return self.decoder.forward(s, self.kv)
 
     def upload_graph_inputs(self, plan):

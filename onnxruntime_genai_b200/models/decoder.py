@@ -36,6 +36,7 @@ class StepInputs:
     max_q_len: int = 1
     max_kv_len: int = 1
     inputs_embeds: Optional[torch.Tensor] = None  # overrides the embedding lookup (multimodal / MTP)
+    num_decode: int = 0                           # leading requests of the batch that feed exactly one token (mixed steps)
     positions3: Optional[torch.Tensor] = None     # [3, T] int32 position components of multimodal RoPE (None: `positions`)
     attn_order: Optional[torch.Tensor] = None     # [B] int32 permutation of the requests, longest first (attention CTA issue order)
     cross: Optional["CrossKVCache"] = None        # encoder keys / values of an encoder-decoder model
@@ -243,6 +244,23 @@ class DecoderModel:
             return ops.linear(x, w, bias, all_reduce=True)   # GEMM + all-reduce in one kernel over NVLink
         return self.tp.reduce(self._linear(x, w, bias, lora=lora))
 
+    def _attention(self, s: StepInputs, qkv, kc, vc, table, block_size: int, lw: LayerWeights):
+        """Paged attention of one layer.  A mixed step (single-token requests first, then prompt chunks) runs as two launches:
+        the single-token requests on the decode tiles (16 rows, the four warps share every K/V tile), the chunks on the
+        64-row tiles - in one launch every single-token request would occupy a 64-row tile that one warp walks alone."""
+        a = self.arch
+        args = (block_size, self.heads_local, self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap)
+        nd, B = s.num_decode, s.past_lens.shape[0]
+        if not (qkv.is_cuda and 0 < nd < B and s.max_q_len > 1):
+            return ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, *args, max_q_len=s.max_q_len,
+                                       max_kv_len=s.max_kv_len, order=s.attn_order)
+        out = torch.empty(qkv.shape[0], self.heads_local * a.head_dim, dtype=qkv.dtype, device=qkv.device)
+        ops.paged_attention(qkv, kc, vc, s.cu_seqlens[:nd + 1], s.past_lens[:nd], table[:nd], *args, max_q_len=1,
+                            max_kv_len=s.max_kv_len, out=out, total_tokens=nd)
+        ops.paged_attention(qkv, kc, vc, s.cu_seqlens[nd:], s.past_lens[nd:], table[nd:], *args, max_q_len=s.max_q_len,
+                            max_kv_len=s.max_kv_len, out=out)
+        return out
+
     def _lora(self, lw: LayerWeights, proj: str):
         if self.active_adapter is None:
             return None
@@ -351,9 +369,7 @@ class DecoderModel:
             ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
                                a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
                                s.positions3 if a.mrope_section else None, a.mrope_section)
-            att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
-                                      self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
-                                      max_q_len=s.max_q_len, max_kv_len=s.max_kv_len, order=s.attn_order)
+            att = self._attention(s, qkv, kc, vc, table, kv.block_size, lw)
             h = self._row_parallel(att, lw.o_w, lw.o_b, self._lora(lw, "o_proj"))
             if lw.cross_q_w is not None:
                 if s.cross is None:

@@ -408,7 +408,8 @@ def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_c
 
 def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale, window=0,
                     sinks=None, softcap=0.0, max_q_len=None, max_kv_len=None, splits=None, out=None, total_tokens=None, order=None):
-    """q: [T, stride] with the Hq*D query columns first.  Returns [T, Hq*D]."""
+    """q: [T, stride] with the Hq*D query columns first.  Returns [T, Hq*D].  total_tokens: the requests of this call only cover
+    the first `total_tokens` rows of q (sizes the split-KV scratch)."""
     if not q.is_cuda:
         return ref.paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
                                    window, sinks, softcap)
@@ -424,12 +425,12 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
     elif isinstance(splits, tuple):
         splits, kv_chunk = splits
     ws = workspace(q.device)
-    need = _lib.lib().ogb_attention_scratch_bytes(q.shape[0], Hq, D, splits)
+    need = _lib.lib().ogb_attention_scratch_bytes(T, Hq, D, splits)
     scratch = ws.attn_scratch(need) if splits > 1 else None
     fn = _lib.lib().ogb_paged_attention_kv8 if k_cache.dtype == torch.int8 else _lib.lib().ogb_paged_attention
     rc = fn(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
                                         _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0),
-                                        _ptr(sinks), float(scale), float(softcap), int(window), B, q.shape[0], int(max_q_len),
+                                        _ptr(sinks), float(scale), float(softcap), int(window), B, T, int(max_q_len),
                                         Hq, Hkv, D, int(splits), int(kv_chunk), _ptr(scratch),
                                         scratch.numel() if scratch is not None else 0, int(k_cache.shape[0]), _ptr(order), ws.status, _stream())
     _lib.check(rc, "paged_attention")

@@ -430,6 +430,37 @@ def test_attention_int8_cache(D):
     _attention_case_kv8(B=2, q_lens=[1, 30], past=[500, 100], Hq=8, Hkv=2, D=D, bs=16, window=128)
 
 
+def test_attention_mixed_step_as_two_launches():
+    """Single-token requests first, prompt chunks after: the decoder runs them as a decode-tile launch (with its own split
+    choice and a scratch sized for the leading rows only) and a 64-row-tile launch writing into one output."""
+    rng = np.random.RandomState(7)
+    q_lens, past = [1, 1, 1, 40, 17], [900, 5, 2047, 0, 64]
+    B, nd, Hq, Hkv, D, bs = 5, 3, 8, 2, 128, 16
+    cols = max((p_ + q_ + bs - 1) // bs for p_, q_ in zip(past, q_lens))
+    nblocks = B * cols + 3
+    perm = rng.permutation(nblocks)
+    table = torch.full((B, cols), -1, dtype=torch.int32)
+    used = 0
+    for b in range(B):
+        need = (past[b] + q_lens[b] + bs - 1) // bs
+        table[b, :need] = torch.from_numpy(perm[used:used + need].astype(np.int32))
+        used += need
+    kc, vc = _rand(nblocks * bs, Hkv, D, std=1.0, seed=61), _rand(nblocks * bs, Hkv, D, std=1.0, seed=62)
+    T = sum(q_lens)
+    q = _rand(T, (Hq + 2 * Hkv) * D, std=1.0, seed=63)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    pl = torch.tensor(past, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    cu_d, pl_d, tb_d = cu.to(DEV), pl.to(DEV), table.to(DEV)
+    out = torch.zeros(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q, kc, vc, cu_d[:nd + 1], pl_d[:nd], tb_d[:nd], bs, Hq, Hkv, D, scale, max_q_len=1, max_kv_len=2048, out=out,
+                        total_tokens=nd)
+    ops.paged_attention(q, kc, vc, cu_d[nd:], pl_d[nd:], tb_d[nd:], bs, Hq, Hkv, D, scale, max_q_len=40, max_kv_len=2048, out=out)
+    want = ref.paged_attention(q.cpu(), kc.cpu(), vc.cpu(), cu, pl, table, bs, Hq, Hkv, D, scale)
+    _close(out, want, rtol=3e-2, atol=3e-2)
+    assert ops.choose_kv_splits(nd, Hkv, 1, 2048, group=Hq // Hkv)[0] > 1      # the leading launch really used the split path
+
+
 @pytest.mark.parametrize("splits", [None, 3])
 def test_attention_longest_first_issue_order(splits):
     """A permutation of the requests only changes which CTA serves which request."""
