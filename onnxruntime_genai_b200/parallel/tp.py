@@ -39,6 +39,41 @@ class TensorParallel:
                 import warnings
                 warnings.warn(f"fused tensor-parallel kernels disabled, falling back to NCCL: {e}")
                 self.backend = "nccl"
+            if self.comm is not None and os.environ.get("OGB_TP_SELF_TEST", "1") != "0" and not self._self_test():
+                import warnings
+                warnings.warn("fused tensor-parallel kernels failed their start-up check against NCCL; using the NCCL back end")
+                self.comm = None
+                self.backend = "nccl"
+
+    def _self_test(self) -> bool:
+        """One decode-sized GEMM + all-reduce in a single kernel and one stand-alone all-reduce, both against NCCL on the same
+        data; every rank takes the same decision (the flags are min-reduced).  Bounded waits that run out surface as a kernel
+        status, which is cleared here - a world whose peer protocol does not work runs on NCCL instead of failing later."""
+        from .. import ops
+        from ..ops import _lib
+        dev = self.device
+        ok = True
+        try:
+            g = torch.Generator(device="cpu").manual_seed(1234 + self.rank)
+            x = (torch.randn(64, 512, generator=g) * 0.5).to(dev, torch.bfloat16)
+            w = (torch.randn(1024, 512, generator=torch.Generator().manual_seed(99)) * 0.05).to(dev, torch.bfloat16)
+            for _ in range(3):      # both buffer parities and a reuse
+                want = ops.linear(x, w).float()
+                dist.all_reduce(want, group=self.group)
+                got = ops.linear(x, w, all_reduce=True).float()
+                ok = ok and bool(torch.allclose(got, want, rtol=3e-2, atol=3e-2))
+                y = x.clone()
+                want2 = x.float().clone()
+                dist.all_reduce(want2, group=self.group)
+                got2 = self.comm.all_reduce(y).float()
+                ok = ok and bool(torch.allclose(got2, want2, rtol=3e-2, atol=3e-2))
+            torch.cuda.synchronize(dev)
+            ok = ok and _lib.lib().ogb_status_read_and_clear(dev.index if dev.index is not None else torch.cuda.current_device()) == 0
+        except Exception:
+            ok = False
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(flag.item())
 
     @classmethod
     def from_env(cls, backend: Optional[str] = None) -> Optional["TensorParallel"]:
