@@ -58,7 +58,9 @@ def spec_dir(tmp_path_factory):
     cfg = json.load(open(os.path.join(d, "genai_config.json")))
     plain = str(tmp_path_factory.mktemp("gpu_plain"))
     for f in os.listdir(d):
-        os.symlink(os.path.join(d, f), os.path.join(plain, f))
+        if f != "genai_config.json":
+            os.symlink(os.path.join(d, f), os.path.join(plain, f))
+    json.dump(cfg, open(os.path.join(plain, "genai_config.json"), "w"))      # the same weights without the draft section
     dec = copy.deepcopy(cfg["model"]["decoder"])
     dec["filename"] = "draft.onnx"
     cfg["model"]["draft"] = dec
