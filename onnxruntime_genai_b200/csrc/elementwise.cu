@@ -401,6 +401,24 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ in, const int32_t* 
   for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[size_t(blockIdx.x) * vec_per_row + i] = in[size_t(r) * vec_per_row + i];
 }
 
+// Gather rows with a bf16 -> fp16 conversion (activations of the fp16 form of the packed FP4 expert GEMM).
+__global__ void gather_rows_f16_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ rows, uint4* __restrict__ out, int vec_per_row) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = rows[blockIdx.x];
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
+    uint4 v = in[size_t(r) * vec_per_row + i];
+    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      const __half2 h = __floats2half2_rn(f.x, f.y);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    out[size_t(blockIdx.x) * vec_per_row + i] = v;
+  }
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -530,6 +548,14 @@ OGB_API int ogb_bf16_to_f32(const void* in, float* out, long long n, void* strea
   if (n <= 0) return 0;
   long long nb = (n + 255) / 256; int blocks = int(nb < 148 * 16 ? nb : 148 * 16);
   bf16_to_f32_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(in), out, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_gather_rows_f16(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream) {
+  if (n_rows <= 0) return 0;
+  if (row_bytes % 16) return -1;
+  launch_pdl(gather_rows_f16_kernel, dim3(n_rows), dim3(min(256, row_bytes / 16)), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const uint4*>(in), rows, static_cast<uint4*>(out), row_bytes / 16);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -4,6 +4,8 @@
 // reduce the split-K cluster through distributed shared memory, apply bias / paired SiLU*mul / residual,
 // store 16-byte row segments, or run the fused tensor-parallel all-reduce over NVLink peer memory.
 #pragma once
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace ogb {
@@ -46,7 +48,7 @@ struct GemmParams {
   int splits, kb_per_split, total_kb;
   void* C;
   int ldc;
-  int out_fp32;
+  int out_fp32;         // 0 bf16, 1 fp32, 2 fp16 output
   int act_pair;         // tiles hold 64 gate rows + 64 up rows, output has N/2 columns: 1 = silu(gate)*up,
                         // 2 = clamped SwiGLU: g = min(gate, limit), u = clamp(up, +-limit), g*sigmoid(alpha*g)*(u+1)
   float act_alpha, act_limit;
@@ -82,6 +84,11 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static_assert(PARTIAL_BYTES <= STAGES * STAGE_BYTES, "the parked tile must fit in the pipeline memory");
 };
+
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
@@ -205,7 +212,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
 #pragma unroll
         for (int j = 0; j < 8; ++j) if (col + j < n_out) v[j] += bf2f(p.residual[size_t(m) * p.ldr + col + j]);
       }
-      if (p.out_fp32) {
+      if (p.out_fp32 == 1) {
         float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
         if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
           *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -213,6 +220,14 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = v[j];
+        }
+      } else if (p.out_fp32 == 2) {   // fp16 output (feeds the fp16 form of the packed FP4 expert GEMM)
+        __half* dst = reinterpret_cast<__half*>(p.C) + size_t(m) * p.ldc + col;
+        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]), pack_f16x2(v[6], v[7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = __float2half_rn(v[j]);
         }
       } else {
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;

@@ -1,0 +1,317 @@
+// Grouped expert GEMM over MXFP4 weights kept packed in HBM (QMoE semantics) on the 5th-generation tensor cores:
+//     C[row, :] = A[row, :] * dequant(W[expert(row)])^T  (+ bias[expert]) (+ paired activation)
+//
+// Checkpoint semantics (reference: src/python/py/models/builders/base.py:4276-4408, builders/gptoss.py:653-847):
+// FP4 e2m1 codes (sign, two exponent bits, one mantissa bit: 0, 0.5, 1, 1.5, 2, 3, 4, 6) with one power-of-two e8m0
+// scale 2^(code - 127) per block of 32 along K.  The QMoE layout ([E, K, N/2] bytes + [E, N, K/32] scale codes) is
+// repacked once at load time (ops/fp4.py) into tiles that one bulk copy streams: for every (expert, k-block of 64,
+// tile of 128 output rows) a contiguous 4352-byte record
+//     [128 rows][32 bytes of nibbles]  +  [128 rows][2 multiplier bytes]
+// with the nibbles of each 32-bit word ordered so that `(word >> 4j)` puts two consecutive k values in the low
+// nibbles of the two halves of a register.  HBM traffic is 4.25 bits per weight instead of 16.
+//
+// Expansion to bf16 without a table: the three magnitude bits of a code, placed at bits 8..6 of a bf16, are the
+// number e2m1 * 2^-126 (the codes 0 and 1 land on zero and on the subnormal 2^-127, exactly as e2m1's own
+// subnormal), so one bf16x2 multiply by 2^126 * 2^(scale - 127) = 2^(scale - 1) yields the weight exactly
+// (PTX `mul.bf16x2` keeps subnormal inputs).  The multiplier byte stored in the record is that power's bf16
+// exponent field, scale + 126; scale codes above 128 cannot be represented and are refused by the packer.
+//
+// fp16 form (the default when every block scale lies in 2^-14 .. 2^13): the tensor cores run fp16 x fp16 with the
+// activations converted to fp16 by the row gather (and by the gate/up epilogue for the down projection), the
+// nibbles stay in their natural order and `cvt.rn.f16x2.e2m1x2` expands two codes per instruction; the multiplier
+// byte is then the fp16 exponent field of 2^(scale - 127), scale - 112.  One conversion and one multiply per pair
+// of weights instead of six integer / bf16 operations: the expansion stops being the limit of the weight stream.
+//
+// Pipeline and epilogue are those of the int4 kernel (gemm_w4.cu): warp 0 streams records through a deep ring and
+// the activation tiles through a 2-deep ring, warps 2..5 (one thread per weight row) expand a record into the
+// swizzled K-major bf16 tile, warp 1 issues tcgen05.mma into tensor memory.  The tile list of ogb_moe_sort selects
+// the expert, first row and row count of each token tile.  Every wait is bounded.
+#include <cstdlib>
+
+#include <cuda_fp16.h>
+
+#include "gemm_common.cuh"
+#include "kernels.h"
+
+namespace ogb {
+
+constexpr int FP4_RECORD_BYTES = GEMM_BLOCK_N * 32 + GEMM_BLOCK_N * 2;  // 4352
+constexpr int FP4_WBUF = 2;
+
+template <int BT>
+struct Fp4Cfg {
+  static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
+  static constexpr bool TWO_PER_SM = BT <= 64;
+  static constexpr int BUDGET = TWO_PER_SM ? 100 * 1024 : 196 * 1024;
+  static constexpr int FIXED = FP4_WBUF * (W_TILE_BYTES + A_TILE_BYTES);
+  static constexpr int MAX_RAW = (BUDGET - FIXED) / FP4_RECORD_BYTES;
+  // a multiple of 4 records keeps the tiles behind the ring 1 KiB aligned (4 * 4352 = 17 KiB)
+  static constexpr int RAW = (MAX_RAW > 16 ? 16 : MAX_RAW) / 4 * 4;
+  static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
+  static constexpr int DATA_BYTES = RAW * FP4_RECORD_BYTES + FIXED;
+  static constexpr int SMEM_BYTES = DATA_BYTES + 1024 + 512;
+  static_assert(RAW >= 4, "raw ring too shallow");
+  static_assert((RAW * FP4_RECORD_BYTES) % 1024 == 0, "swizzled tiles need 1 KiB alignment");
+  static_assert(BT * GEMM_BLOCK_N * 4 <= DATA_BYTES, "the parked fp32 tile must fit in the pipeline memory");
+};
+
+__device__ __forceinline__ void fp4_bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// two e2m1 codes (low nibbles of the two halves of `u`) times the block's power-of-two multiplier
+__device__ __forceinline__ uint32_t deq_fp4_pair(uint32_t u, __nv_bfloat162 s2) {
+  uint32_t t = ((u & 0x00070007u) << 6) | ((u & 0x00080008u) << 12);
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&t);
+  v = __hmul2(v, s2);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// four bytes of e2m1 pairs (low nibble = first element) -> four fp16x2 registers times the block's multiplier
+__device__ __forceinline__ uint4 deq_fp4_word_f16(uint32_t word, __half2 s2) {
+  uint32_t h0, h1, h2, h3;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(word));
+  auto mul = [&](uint32_t h) {
+    __half2 v = __hmul2(*reinterpret_cast<__half2*>(&h), s2);
+    return *reinterpret_cast<uint32_t*>(&v);
+  };
+  return make_uint4(mul(h0), mul(h1), mul(h2), mul(h3));
+}
+
+template <int BT, bool HALF>
+__global__ void __launch_bounds__(GEMM_THREADS, Fp4Cfg<BT>::TWO_PER_SM ? 2 : 1)
+gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert,
+                        const GemmParams p) {
+  using Cfg = Fp4Cfg<BT>;
+  constexpr int RAW = Cfg::RAW;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw_ring = smem;
+  uint8_t* w_ring = smem + RAW * FP4_RECORD_BYTES;
+  uint8_t* a_ring = w_ring + FP4_WBUF * W_TILE_BYTES;
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem + Cfg::DATA_BYTES);
+  uint64_t* raw_empty = raw_full + RAW;
+  uint64_t* deq_full = raw_empty + RAW;
+  uint64_t* a_full = deq_full + FP4_WBUF;
+  uint64_t* w_empty = a_full + FP4_WBUF;
+  uint64_t* accum_bar = w_empty + FP4_WBUF;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile uint32_t* use_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  const int num_kb = p.total_kb;
+  // The tile list is written by the kernel before this one, so nothing is read ahead of it.
+  if (p.pdl) pdl_wait();
+  if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA
+  const int row0 = p.grp.tile_row0[m_tile];
+  const int rows = p.grp.tile_rows[m_tile];
+  const int expert = p.grp.tile_expert[m_tile];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RAW; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 128); }
+    for (int s = 0; s < FP4_WBUF; ++s) { mbar_init(&deq_full[s], 128); mbar_init(&a_full[s], 1); mbar_init(&w_empty[s], 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl) pdl_launch_dependents();
+  auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer: packed records + activation tiles
+      const uint8_t* rec0 = wpacked + (size_t(expert) * num_kb * n_tiles_per_expert + n_tile) * FP4_RECORD_BYTES;
+      const size_t rec_stride = size_t(n_tiles_per_expert) * FP4_RECORD_BYTES;
+      auto load_raw = [&](int i) {
+        const int s = i % RAW;
+        mbar_expect_tx(&raw_full[s], FP4_RECORD_BYTES);
+        fp4_bulk_copy_g2s(raw_ring + s * FP4_RECORD_BYTES, rec0 + size_t(i) * rec_stride, FP4_RECORD_BYTES, &raw_full[s]);
+      };
+      auto load_a = [&](int i) {
+        const int s = i % FP4_WBUF;
+        mbar_expect_tx(&a_full[s], Cfg::A_TILE_BYTES);
+        tma_load_2d(a_ring + s * Cfg::A_TILE_BYTES, &tmap_a, &a_full[s], i * GEMM_BLOCK_K, row0);
+      };
+      int ri = 0, ai = 0;
+      const int pre = min(RAW, num_kb);
+      for (; ri < pre; ++ri) load_raw(ri);
+      const uint64_t t0 = global_timer_ns();
+      uint32_t idle = 0;
+      while ((ri < num_kb || ai < num_kb) && !*abort_flag) {
+        bool progressed = false;
+        if (ri < num_kb && mbar_try_wait(&raw_empty[ri % RAW], ((ri / RAW) & 1) ^ 1)) { load_raw(ri); ++ri; progressed = true; }
+        if (ai < num_kb && (ai < FP4_WBUF || mbar_try_wait(&w_empty[ai % FP4_WBUF], ((ai / FP4_WBUF) & 1) ^ 1))) { load_a(ai); ++ai; progressed = true; }
+        if (progressed) { idle = 0; continue; }
+        if ((++idle & 0x3ff) == 0 && global_timer_ns() - t0 > 4000000000ull) { fail(OGB_ERR_WAIT_TMA); break; }
+      }
+      if (*abort_flag) {
+        volatile int never = 0;
+        for (int i = max(0, ri - RAW); i < ri; ++i) mbar_wait_bounded(&raw_full[i % RAW], (i / RAW) & 1, &never, 200000000ull);
+        for (int i = max(0, ai - FP4_WBUF); i < ai; ++i) mbar_wait_bounded(&a_full[i % FP4_WBUF], (i / FP4_WBUF) & 1, &never, 200000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = umma_idesc_f16(GEMM_BLOCK_N, BT, HALF ? 0 : 1);   // operand format: fp16 or bf16
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % FP4_WBUF;
+        const uint32_t ph = (i / FP4_WBUF) & 1;
+        if (!mbar_wait_bounded(&deq_full[s], ph, abort_flag) || !mbar_wait_bounded(&a_full[s], ph, abort_flag)) {
+          fail(OGB_ERR_WAIT_TMA); ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t w = smem_u32(w_ring + s * W_TILE_BYTES), a = smem_u32(a_ring + s * Cfg::A_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
+          umma_f16(tmem_base, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc,
+                   (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&w_empty[s]);
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  } else {
+    // -------------------------------------------------------------- expanders: thread = weight row of the tile
+    const int row = threadIdx.x - 64;
+    for (int i = 0; i < num_kb; ++i) {
+      const int rs = i % RAW, ws = i % FP4_WBUF;
+      bool ok = mbar_wait_bounded(&raw_full[rs], (i / RAW) & 1, abort_flag);
+      if (ok && i >= FP4_WBUF) ok = mbar_wait_bounded(&w_empty[ws], ((i / FP4_WBUF) & 1) ^ 1, abort_flag);
+      if (!ok) { fail(OGB_ERR_WAIT_TMA); break; }
+      const uint8_t* rec = raw_ring + rs * FP4_RECORD_BYTES;
+      const uint4 q0 = *reinterpret_cast<const uint4*>(rec + row * 32);
+      const uint4 q1 = *reinterpret_cast<const uint4*>(rec + row * 32 + 16);
+      const uint32_t mul = *reinterpret_cast<const uint16_t*>(rec + GEMM_BLOCK_N * 32 + row * 2);
+      const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      uint8_t* dst = w_ring + ws * W_TILE_BYTES + row * 128;
+      if constexpr (HALF) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);     // fp16 exponent field of the block's scale
+          const uint32_t sb = (m8 << 10) | (m8 << 26);
+          *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = deq_fp4_word_f16(words[j], *reinterpret_cast<const __half2*>(&sb));
+        }
+      } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);       // bf16 exponent field of the block's multiplier
+        const uint32_t sb = (m8 << 7) | (m8 << 23);
+        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sb);
+        uint4 o;
+        o.x = deq_fp4_pair(words[j], s2);
+        o.y = deq_fp4_pair(words[j] >> 4, s2);
+        o.z = deq_fp4_pair(words[j] >> 8, s2);
+        o.w = deq_fp4_pair(words[j] >> 12, s2);
+        *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = o;
+      }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
+      mbar_arrive(&deq_full[ws]);
+      mbar_arrive(&raw_empty[rs]);
+    }
+  }
+
+  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, expert * p.N);
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
+
+template <int BT, bool HALF>
+static int LaunchFp4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  using Cfg = Fp4Cfg<BT>;
+  static bool configured = false;
+  auto kern = gemm_fp4_grouped_kernel<BT, HALF>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int na = 0;
+  if (p.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = unsigned(na);
+  return cudaLaunchKernelEx(&cfg, kern, ta, wp, n_tiles, p) == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace ogb
+
+using namespace ogb;
+
+// Bytes of the repacked experts: `experts` matrices of [N, K] e2m1 codes (K a multiple of 64; N is padded to 128).
+OGB_API long long ogb_fp4_packed_bytes(int experts, int N, int K) {
+  return (long long)experts * (K / 64) * ((N + 127) / 128) * FP4_RECORD_BYTES;
+}
+
+// Grouped expert GEMM over packed MXFP4 experts; arguments as ogb_moe_gemm with `Wpacked` in the record layout above.
+// flags: bit 0 fp32 output, bit 1 paired activation, bit 4 fp16 form (A holds fp16 rows, records in the fp16 layout),
+// bit 5 fp16 output.
+OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
+                             const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
+                             const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
+                             int* status, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (rows_total <= 0 || N <= 0 || K <= 0 || experts <= 0 || max_tiles <= 0) return 0;
+  if ((K % 64) || (lda % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Wpacked)) & 15) return -1;
+  const int act_pair = (flags >> 1) & 1;
+  if (act_pair && (N % 128)) return -1;
+  if (max_tiles > 65535) return -1;
+  static const int pdl_enabled = [] { const char* e = getenv("OGB_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
+  const int bt = token_tile;
+  CUtensorMap ta;
+  if (!MakeMapBf16(&ta, A, rows_total, K, lda, bt)) return -2;
+  GemmParams p = {};
+  p.M = rows_total; p.N = N; p.K = K;
+  p.total_kb = K / GEMM_BLOCK_K;
+  p.splits = 1; p.kb_per_split = p.total_kb;
+  p.C = C; p.ldc = ldc; p.out_fp32 = (flags & 1) ? 1 : ((flags & 32) ? 2 : 0); p.act_pair = act_pair ? act_kind : 0;
+  const bool half = (flags & 16) != 0;
+  p.act_alpha = act_alpha; p.act_limit = act_limit;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = status;
+  p.pdl = pdl_enabled;
+  p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
+  const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N;
+  dim3 grid(n_tiles, max_tiles, 1);
+  const uint8_t* wp = static_cast<const uint8_t*>(Wpacked);
+  switch (bt) {
+    case 16: return half ? LaunchFp4<16, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<16, false>(ta, wp, n_tiles, p, grid, stream);
+    case 32: return half ? LaunchFp4<32, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<32, false>(ta, wp, n_tiles, p, grid, stream);
+    case 64: return half ? LaunchFp4<64, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<64, false>(ta, wp, n_tiles, p, grid, stream);
+    case 128: return half ? LaunchFp4<128, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<128, false>(ta, wp, n_tiles, p, grid, stream);
+    case 256: return half ? LaunchFp4<256, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<256, false>(ta, wp, n_tiles, p, grid, stream);
+  }
+  return -5;
+}

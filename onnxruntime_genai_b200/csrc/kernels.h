@@ -51,6 +51,13 @@ long long ogb_w4_packed_bytes(int N, int K);
 int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int M, int N, int K, const void* bias,
                 const void* residual, int ldr, int flags, int splits, int* status, int sm_count, void* stream);
 
+// ---- gemm_fp4.cu (MXFP4 experts kept packed: e2m1 codes + e8m0 block scales, repacked by ops/fp4.py)
+long long ogb_fp4_packed_bytes(int experts, int N, int K);
+int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
+                     const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
+                     const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile, int* status,
+                     void* stream);
+
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);
 int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias, void* out,
@@ -75,6 +82,7 @@ int ogb_logits_edit(float* logits, int vocab, const int32_t* rows, const int32_t
 int ogb_logits_bitmask(float* logits, int rows, int vocab, const uint32_t* mask, const int32_t* mask_rows, void* stream);
 int ogb_bf16_to_f32(const void* in, float* out, long long n, void* stream);
 int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream);
+int ogb_gather_rows_f16(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream);  // bf16 -> fp16
 
 // ---- attention.cu
 long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, int splits);

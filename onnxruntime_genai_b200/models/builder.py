@@ -548,7 +548,22 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             put_linear(p + "moe.router", f"{n}/moe/router/MatMul", [p + "mlp.router.weight"], x, f"{n}/moe/router/MatMul/output_0", E, H)
             put_vec(p + "moe.router.Add.bias", [p + "mlp.router.bias"])
             W.node("Add", f"{n}/moe/router/Add", [f"{n}/moe/router/MatMul/output_0", p + "moe.router.Add.bias"], [f"{n}/moe/router/Add/output_0"])
-            if precision == "int4" and not synthetic_weights:
+            if precision == "int4" and synthetic_weights:
+                # descriptors only: the loader draws random e2m1 codes and scale codes on the device (no float weight is made)
+                ins = [x, f"{n}/moe/router/Add/output_0"]
+                for nm, (Nn, Kk) in (("gate_up_proj", (2 * I, H)), ("down_proj", (H, I))):
+                    for suffix, shp, kind in (("weight_fp4", (E, Kk, Nn // 2), "fp4_codes"), ("scales_e8m0", (E, Nn, Kk // 32), "fp4_scales")):
+                        W.add_synthetic(p + f"moe.experts.{nm}.{suffix}", shp, "", op.UINT8)
+                        synth_meta[p + f"moe.experts.{nm}.{suffix}"] = {"sources": [p + f"mlp.experts.{nm}"], "op": kind, "seed": seed, "std": std,
+                                                                        "shape": list(shp)}
+                    put_plain(p + f"moe.experts.{nm}.bias", [p + f"mlp.experts.{nm}_bias"],
+                              {"shape": (E, Nn), "op": "id", "fn": lambda ts: ts[0].float()})
+                    ins += [p + f"moe.experts.{nm}.weight_fp4", p + f"moe.experts.{nm}.scales_e8m0", p + f"moe.experts.{nm}.bias"]
+                W.node("QMoE", f"{n}/moe/QMoE", ins, [f"{n}/moe/MoE/output_0"], domain="com.microsoft", k=arch.experts_per_token,
+                       activation_type="swiglu", activation_alpha=float(arch.moe_swiglu_alpha), activation_beta=1.0, swiglu_fusion=1,
+                       swiglu_limit=float(arch.moe_swiglu_limit), normalize_routing_weights=1, expert_weight_bits=4, block_size=32,
+                       quant_type="fp4", use_sparse_mixer=0)
+            elif precision == "int4":
                 # quantised experts: QMoE with MXFP4 weights (FP4 e2m1 codes [E, K, N/2], e8m0 scales [E, N, K/32], unit global scales)
                 ins = [x, f"{n}/moe/router/Add/output_0"]
                 for nm in ("gate_up_proj", "down_proj"):

@@ -21,7 +21,7 @@ import torch
 
 from ..utils import onnx_proto as op
 from .arch import ArchConfig
-from .builder import dequantize_int4_block32, dequantize_mxfp4, quantize_int4_block32, random_tensor, weight_shapes
+from .builder import dequantize_int4_block32, dequantize_mxfp4, quantize_int4_block32, random_tensor, tensor_seed, weight_shapes
 from .decoder import DecoderModel, LayerWeights
 
 
@@ -59,6 +59,12 @@ class GraphView:
         return _np_to_torch(self.lm.array(name), t.dtype)
 
     def _synthetic(self, t: op.Tensor, meta: dict, device) -> torch.Tensor:
+        if meta["op"] in ("fp4_codes", "fp4_scales"):
+            # MXFP4 experts: uniform random e2m1 codes; block scales 2^-8 .. 2^-5 (weights of the usual magnitude)
+            gen = torch.Generator(device=device)
+            gen.manual_seed(tensor_seed(meta["sources"][0] + "." + meta["op"], meta["seed"]))
+            lo, hi = (0, 256) if meta["op"] == "fp4_codes" else (119, 123)
+            return torch.randint(lo, hi, tuple(meta["shape"]), generator=gen, device=device, dtype=torch.uint8)
         parts = []
         shapes = self._shapes
         for src in meta["sources"]:
@@ -439,12 +445,48 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                     out[e] = (w * gs[e] if gs is not None else w).to(dtype)
                 return out
 
+            def experts_fp4_packed(wname, sname, gname, gate_up):
+                """MXFP4 experts kept packed for the grouped FP4 GEMM (ops/fp4.py), or None when this checkpoint or device
+                needs the expanded form: CPU, OGB_FP4_EXPERTS=0, non-unit global scales, K not a multiple of 64, block
+                scales above 2^1, or gate/up widths the 64-row blocking cannot cover."""
+                from ..ops.fp4 import Fp4Experts, unpack_qmoe_fp4
+                if torch.device(device).type != "cuda" or os.environ.get("OGB_FP4_EXPERTS", "1") == "0":
+                    return None
+                if gname and not bool((g.tensor(gname).float() == 1.0).all()):
+                    return None
+                sc = g.tensor(sname, device=device)[lw.exp_lo:lw.exp_hi]
+                q = g.tensor(wname, device=device)[lw.exp_lo:lw.exp_hi]
+                Kk, Nn = q.shape[1], q.shape[2] * 2
+                if not Fp4Experts.supported(sc, Kk) or (gate_up and (Nn // 2) % 64):
+                    return None
+                codes, sc = unpack_qmoe_fp4(q.to(device)), sc.to(device)
+                if gate_up:
+                    from ..ops import interleave_experts_gate_up
+                    codes, sc = interleave_experts_gate_up(codes), interleave_experts_gate_up(sc)
+                return codes, sc
+
+            packed_experts = False
             if moe.op_type == "QMoE":
                 if str(_attr(moe, "quant_type", "")) not in ("fp4", "mxfp4") or int(_attr(moe, "expert_weight_bits", 4)) != 4:
                     raise NotImplementedError("QMoE: only MXFP4 (quant_type fp4, block 32) experts are supported")
                 ins = list(moe.inputs) + [""] * 17
-                lw.exp_gate_up_w, lw.exp_gate_up_b = experts_fp4(ins[2], ins[3], ins[15]), experts(ins[4])
-                lw.exp_down_w, lw.exp_down_b = experts_fp4(ins[5], ins[6], ins[16]), experts(ins[7])
+                gu_p = experts_fp4_packed(ins[2], ins[3], ins[15], True)
+                dn_p = experts_fp4_packed(ins[5], ins[6], ins[16], False) if gu_p is not None else None
+                if gu_p is not None and dn_p is not None:
+                    from ..ops.fp4 import Fp4Experts
+                    # the fp16 form (two codes per conversion instruction) needs both matrices' block scales in its range
+                    half = Fp4Experts.fits_fp16(*gu_p) and Fp4Experts.fits_fp16(*dn_p) and os.environ.get("OGB_FP4_FORM", "") != "bf16"
+                    gu_p, dn_p = (Fp4Experts.from_codes(c, sc, device, keep_host=c.numel() <= (1 << 24), half=half) for c, sc in (gu_p, dn_p))
+                    packed_experts = True
+                    lw.exp_gate_up_w, lw.exp_gate_up_b = gu_p, experts(ins[4])
+                    lw.exp_down_w, lw.exp_down_b = dn_p, experts(ins[7])
+                    if lw.exp_gate_up_b is not None:
+                        from ..ops import interleave_experts_gate_up
+                        lw.exp_gate_up_b = interleave_experts_gate_up(lw.exp_gate_up_b)
+                    lw.exp_blocked = True
+                else:
+                    lw.exp_gate_up_w, lw.exp_gate_up_b = experts_fp4(ins[2], ins[3], ins[15]), experts(ins[4])
+                    lw.exp_down_w, lw.exp_down_b = experts_fp4(ins[5], ins[6], ins[16]), experts(ins[7])
             elif arch.moe_style == "standard":
                 # gate [E, I, H] and up [E, I, H] become one matrix with even rows = gate, odd rows = up (the fused layout)
                 gate, up = experts(moe.inputs[2]), experts(moe.inputs[6])
@@ -454,8 +496,9 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
             else:
                 lw.exp_gate_up_w, lw.exp_gate_up_b = experts(moe.inputs[2]), experts(moe.inputs[3])
                 lw.exp_down_w, lw.exp_down_b = experts(moe.inputs[4]), experts(moe.inputs[5])
-            lw.exp_blocked = False
-            if torch.device(device).type == "cuda" and (lw.exp_gate_up_w.shape[1] // 2) % 64 == 0:
+            if not packed_experts:
+                lw.exp_blocked = False
+            if not packed_experts and torch.device(device).type == "cuda" and (lw.exp_gate_up_w.shape[1] // 2) % 64 == 0:
                 # grouped GEMM layout: per expert, blocks of 64 gate rows + the 64 up rows of the same features
                 from ..ops import interleave_experts_gate_up
                 lw.exp_gate_up_w = interleave_experts_gate_up(lw.exp_gate_up_w)

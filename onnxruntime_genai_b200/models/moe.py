@@ -80,12 +80,15 @@ def _unblock(t: torch.Tensor) -> torch.Tensor:
 def expert_mlp(model, lw, e: int, xs: torch.Tensor) -> torch.Tensor:
     """One expert (index into this rank's slice) over its rows: the unfused path (CPU, odd shapes)."""
     a = model.arch
-    w, b = lw.exp_gate_up_w[e], lw.exp_gate_up_b[e] if lw.exp_gate_up_b is not None else None
+    packed = isinstance(lw.exp_gate_up_w, ops.Fp4Experts)   # MXFP4 experts: expand this one expert
+    w = lw.exp_gate_up_w.dequantize(e).to(xs) if packed else lw.exp_gate_up_w[e]
+    b = lw.exp_gate_up_b[e] if lw.exp_gate_up_b is not None else None
     if lw.exp_blocked:
         w, b = _unblock(w).contiguous(), _unblock(b).contiguous() if b is not None else None
     gu = ops.linear(xs, w, b)
     act = silu_mul_interleaved(gu) if a.moe_style == "standard" else swiglu_interleaved(gu, a.moe_swiglu_alpha, a.moe_swiglu_limit)
-    return ops.linear(act.contiguous(), lw.exp_down_w[e], lw.exp_down_b[e] if lw.exp_down_b is not None else None)
+    wd = lw.exp_down_w.dequantize(e).to(xs) if packed else lw.exp_down_w[e]
+    return ops.linear(act.contiguous(), wd, lw.exp_down_b[e] if lw.exp_down_b is not None else None)
 
 
 def _forward_loop(model, lw, x):
@@ -118,6 +121,14 @@ def _forward_device(model, lw, x):
         plan = ops.moe_route(logits, 2, 0, (lo, hi), topk=(ti.to(torch.int32).contiguous(), tw.contiguous()))
     else:
         plan = ops.moe_route(logits, a.experts_per_token, 1 if standard and not a.moe_norm_topk else 0, (lo, hi))
+    half = isinstance(lw.exp_gate_up_w, ops.Fp4Experts) and lw.exp_gate_up_w.half and lw.exp_down_w.half
+    if half:
+        # packed MXFP4 experts in their fp16 form: fp16 rows in, fp16 between the two grouped GEMMs, bf16 out
+        xs = ops.gather_rows(x, plan.sorted_token, f16=True)
+        h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, lw.exp_gate_up_b, act_kind=2, alpha=a.moe_swiglu_alpha, limit=a.moe_swiglu_limit,
+                         out_dtype=torch.float16)
+        y = ops.moe_gemm(h, lw.exp_down_w, plan, lw.exp_down_b)
+        return ops.moe_combine(y, plan)
     xs = ops.gather_rows(x, plan.sorted_token)
     if standard:
         h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, None, act_kind=1)

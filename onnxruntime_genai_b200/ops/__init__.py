@@ -14,6 +14,7 @@ import torch
 
 from . import reference as ref
 from . import _lib
+from .fp4 import Fp4Experts
 from .w4 import QuantizedEmbedding, W4Weight, unpack_ort_q4
 
 _ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "gelu_erf": 3}
@@ -330,14 +331,28 @@ def moe_route(router_logits: torch.Tensor, k: int, mode: int = 0, expert_range=N
     return pl
 
 
-def moe_gemm(xs: torch.Tensor, w: torch.Tensor, plan: MoePlan, bias=None, act_kind: int = 0, alpha: float = 1.0, limit: float = 0.0):
+def moe_gemm(xs: torch.Tensor, w: torch.Tensor, plan: MoePlan, bias=None, act_kind: int = 0, alpha: float = 1.0, limit: float = 0.0,
+             out_dtype=torch.bfloat16):
     """Grouped expert GEMM over rows sorted by expert.  xs [T*k, K] bf16; w [E, N, K] bf16; bias [E, N].
     act_kind 0: plain; 1: silu(gate)*up; 2: clamped SwiGLU(alpha, limit) — both need the 64-row gate/up blocks
     of interleave_experts_gate_up and return N/2 columns."""
     E, N, K = w.shape
-    assert xs.is_cuda and xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and xs.stride(-1) == 1
-    out = torch.empty(xs.shape[0], N // 2 if act_kind else N, dtype=torch.bfloat16, device=xs.device)
+    assert xs.is_cuda and xs.stride(-1) == 1
     ws = workspace(xs.device)
+    if isinstance(w, Fp4Experts):
+        # MXFP4 experts stay packed in HBM; the kernel expands each tile in shared memory (csrc/gemm_fp4.cu).  The fp16 form
+        # takes fp16 rows (ops.gather_rows(..., f16=True) or the previous grouped GEMM with out_dtype=torch.float16).
+        assert xs.dtype == (torch.float16 if w.half else torch.bfloat16) and out_dtype in (torch.bfloat16, torch.float16)
+        out = torch.empty(xs.shape[0], N // 2 if act_kind else N, dtype=out_dtype, device=xs.device)
+        flags = (GEMM_ACT_PAIR if act_kind else 0) | (16 if w.half else 0) | (32 if out_dtype == torch.float16 else 0)
+        rc = _lib.lib().ogb_moe_gemm_fp4(_ptr(xs), xs.stride(0), _ptr(w.packed), _ptr(out), out.stride(0), xs.shape[0], N, K, E, _ptr(bias),
+                                         flags, int(act_kind), float(alpha), float(limit),
+                                         _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.tile_rows), _ptr(plan.num_tiles),
+                                         plan.max_tiles, plan.bt, ws.status, _stream())
+        _lib.check(rc, "moe_gemm_fp4")
+        return out
+    assert xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()
+    out = torch.empty(xs.shape[0], N // 2 if act_kind else N, dtype=torch.bfloat16, device=xs.device)
     rc = _lib.lib().ogb_moe_gemm(_ptr(xs), xs.stride(0), _ptr(w), K, _ptr(out), out.stride(0), xs.shape[0], N, K, E, _ptr(bias),
                                  GEMM_ACT_PAIR if act_kind else 0, int(act_kind), float(alpha), float(limit), _ptr(plan.tile_expert),
                                  _ptr(plan.tile_row0), _ptr(plan.tile_rows), _ptr(plan.num_tiles), plan.max_tiles, plan.bt, ws.status,
@@ -468,10 +483,15 @@ def to_float32(x):
     return out
 
 
-def gather_rows(x, rows):
+def gather_rows(x, rows, f16: bool = False):
+    """out[i] = x[rows[i]]; f16: bf16 rows come out as fp16 (input of the fp16 form of the packed FP4 expert GEMM)."""
     if not x.is_cuda:
-        return x[rows.long()]
-    out = torch.empty(rows.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+        return x[rows.long()].to(torch.float16) if f16 else x[rows.long()]
+    out = torch.empty(rows.numel(), x.shape[1], dtype=torch.float16 if f16 else x.dtype, device=x.device)
+    if f16:
+        assert x.dtype == torch.bfloat16
+        _lib.check(_lib.lib().ogb_gather_rows_f16(_ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1] * 2, _stream()), "gather_rows_f16")
+        return out
     _lib.check(_lib.lib().ogb_gather_rows(_ptr(x), _ptr(rows), _ptr(out), rows.numel(), x.shape[1] * x.element_size(), _stream()),
                "gather_rows")
     return out

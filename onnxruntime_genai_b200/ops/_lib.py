@@ -31,6 +31,9 @@ _SIGS = {
     "ogb_gemm_w4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P]),
     "ogb_moe_gemm": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_float, _P, _P, _P,
                              _P, c_int, c_int, _P, _P]),
+    "ogb_fp4_packed_bytes": (c_longlong, [c_int, c_int, c_int]),
+    "ogb_moe_gemm_fp4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_float, _P, _P, _P,
+                                 _P, c_int, c_int, _P, _P]),
     "ogb_collective": (c_int, [c_int, _P, _P, _P, c_longlong, c_int, _P, c_int, _P]),
     "ogb_moe_topk": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P]),
     "ogb_moe_max_tiles": (c_int, [c_int, c_int, c_int]),
@@ -51,6 +54,7 @@ _SIGS = {
     "ogb_logits_bitmask": (c_int, [_P, c_int, c_int, _P, _P, _P]),
     "ogb_bf16_to_f32": (c_int, [_P, _P, c_longlong, _P]),
     "ogb_gather_rows": (c_int, [_P, _P, _P, c_int, c_int, _P]),
+    "ogb_gather_rows_f16": (c_int, [_P, _P, _P, c_int, c_int, _P]),
     "ogb_attention_scratch_bytes": (c_longlong, [c_int, c_int, c_int, c_int]),
     "ogb_paged_attention": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),

@@ -3,7 +3,8 @@
     python -m onnxruntime_genai_b200.utils.kernel_case <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--eager] [--json out.json]
 
 cases: gemm_qkv gemm_o gemm_gate_up gemm_down gemm_lm_head gemm_prefill w4_qkv w4_down attention_decode
-       attention_prefill norm rope sample argmax all
+       attention_prefill norm rope sample argmax all; moe_fp4_gate_up moe_fp4_down moe_fp4b_gate_up moe_fp4b_down moe_bf16_gate_up moe_bf16_down
+       (gpt-oss-20b experts, packed MXFP4 in the fp16 form, in the bf16 form (fp4b) or bf16 weights; not part of `all`)
 
 Each case runs the kernel at the Llama-3.1-8B (or, for w4_*, Phi-3-mini) shapes with `--layers` distinct
 weight sets rotated between launches (so weights come from HBM, not L2), captures `--iters` launches
@@ -113,6 +114,33 @@ def build_case(name, T, L, tp=1):
             return (lambda i: ops.gate_up_act(x, ws[i % L], interleaved=True, splits=GEMM_SPLITS)), N * K * 2 + T * (K + N // 2) * 2, 2.0 * T * N * K
         fp32 = name == "gemm_lm_head"
         return (lambda i: ops.linear(x, ws[i % L], out_fp32=fp32, all_reduce=fused, splits=GEMM_SPLITS)), N * K * 2 + T * K * 2 + T * N * (4 if fp32 else 2), 2.0 * T * N * K
+    if name.startswith("moe_"):
+        # gpt-oss-20b experts: 32 experts, 4 per token, hidden 2880, intermediate 2880; tokens routed uniformly at random.
+        # moe_fp4_*: MXFP4 experts kept packed (csrc/gemm_fp4.cu); moe_bf16_*: the same shapes with bf16 experts.
+        E, k, Hm, Im = 32, 4, 2880, 2880
+        gate_up = name.endswith("gate_up")
+        N, K = (2 * Im, Hm) if gate_up else (Hm, Im)
+        L = min(L, 2 if "bf16" in name else 4)
+        logits = torch.randn(T, E, device="cuda")
+        plan = ops.moe_route(logits, k, 0, (0, E))
+        xs = _bf(T * k, K, std=1.0)
+        touched = int(torch.unique(plan.topk_idx).numel())
+        if "fp4" in name:
+            from ..ops.fp4 import Fp4Experts
+            half = "fp4b" not in name       # moe_fp4b_*: the bf16 form of the packed experts
+            xs = xs.to(torch.float16) if half else xs
+            ws = [Fp4Experts.from_codes(torch.randint(0, 16, (E, N, K), device="cuda", dtype=torch.uint8),
+                                        torch.randint(119, 123, (E, N, K // 32), device="cuda", dtype=torch.uint8), "cuda", keep_host=False,
+                                        half=half)
+                  for _ in range(L)]
+            wbytes = touched * N * K * 17 // 32
+        else:
+            ws = [_bf(E, N, K) for _ in range(L)]
+            wbytes = touched * N * K * 2
+        bias = _bf(E, N, std=0.1)
+        if gate_up:
+            return (lambda i: ops.moe_gemm(xs, ws[i % L], plan, bias, act_kind=2, alpha=1.702, limit=7.0)), wbytes + T * k * (K + N // 2) * 2, 2.0 * T * k * N * K
+        return (lambda i: ops.moe_gemm(xs, ws[i % L], plan, bias)), wbytes + T * k * (K + N) * 2, 2.0 * T * k * N * K
     if name in ("attention_decode", "attention_prefill"):
         bs = 16
         rng = np.random.RandomState(2)

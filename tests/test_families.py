@@ -213,6 +213,61 @@ def test_mxfp4_expert_round_trip_and_model(tmp_path):
     np.testing.assert_allclose(lw.exp_down_w.float().numpy(), sd_q["model.layers.0.mlp.experts.down_proj"].numpy(), rtol=0, atol=1e-6)
 
 
+def _read_fp4_records(packed: torch.Tensor, N: int, K: int, half: bool) -> torch.Tensor:
+    """Restates on the host what csrc/gemm_fp4.cu does with a packed expert: thread = weight row reads 8 words and
+    2 multiplier bytes of a 4352-byte record.  bf16 form: pair p of word j is `(word >> 4p)` (low nibbles of the two
+    16-bit halves) and the e2m1 value * 2^-126 is multiplied by the bf16 whose exponent field is the multiplier byte.
+    fp16 form: byte p of word j holds the pair (low nibble first), multiplied by the fp16 whose exponent field is the byte."""
+    KB, tiles = packed.shape[0], packed.shape[1]
+    rec = packed.view(KB, tiles, 128 * 34)
+    nib = rec[:, :, :128 * 32].reshape(KB, tiles, 128, 8, 4).to(torch.int64)
+    words = nib[..., 0] | (nib[..., 1] << 8) | (nib[..., 2] << 16) | (nib[..., 3] << 24)           # [KB, tiles, 128, 8]
+    mul = rec[:, :, 128 * 32:].reshape(KB, tiles, 128, 2).to(torch.int64)
+    grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=torch.float64)
+    out = torch.zeros(tiles * 128, KB * 64, dtype=torch.float64)
+    for j in range(8):
+        m = mul[..., 0 if j < 4 else 1]
+        s = torch.where(m > 0, torch.pow(2.0, m.double() - (15.0 if half else 127.0 + 126.0)), torch.zeros((), dtype=torch.float64))
+        for pr in range(4):
+            u = words[..., j] >> ((8 if half else 4) * pr)
+            for second, sh in ((0, 0), (1, 4 if half else 16)):
+                c = (u >> sh) & 0xF
+                val = grid[c & 7] * torch.where(c >= 8, -1.0, 1.0) * s                               # [KB, tiles, 128]
+                k = j * 8 + pr * 2 + second
+                out.view(tiles, 128, KB, 64)[:, :, :, k] = val.permute(1, 2, 0)
+    return out[:N, :K].float()
+
+
+def test_fp4_expert_packing_matches_the_qmoe_tensors():
+    """The record layout the grouped FP4 GEMM streams, read back the way the kernel reads it, equals the plain
+    dequantisation of the QMoE tensors (codes [E, K, N/2], e8m0 scales [E, N, K/32]); N is padded to 128 rows."""
+    from onnxruntime_genai_b200.models.builder import dequantize_mxfp4, quantize_mxfp4
+    from onnxruntime_genai_b200.ops.fp4 import Fp4Experts, unpack_qmoe_fp4
+    E, N, K = 3, 160, 192
+    g = torch.Generator().manual_seed(9)
+    w = torch.randn(E, N, K, generator=g) * 0.2
+    packs = [quantize_mxfp4(w[e]) for e in range(E)]
+    q, sc = torch.stack([a for a, _ in packs]), torch.stack([b for _, b in packs])
+    # every code at least once, the subnormal 0.5 and both zeros included
+    q[0, 0, :8] = torch.tensor([0x10, 0x32, 0x54, 0x76, 0x98, 0xBA, 0xDC, 0xFE], dtype=torch.uint8)
+    codes = unpack_qmoe_fp4(q)
+    assert Fp4Experts.fits_fp16(codes, sc) and Fp4Experts.from_codes(codes, sc, "cpu").half
+    for half in (False, True):
+        fe = Fp4Experts.from_codes(codes, sc, "cpu", half=half)
+        assert fe.packed.shape == (E, K // 64, 2, 4352) and fe.shape == (E, N, K) and fe.half == half
+        for e in range(E):
+            want = dequantize_mxfp4(q[e], sc[e], N, K)
+            np.testing.assert_array_equal(fe.dequantize(e).numpy(), want.numpy())
+            np.testing.assert_array_equal(_read_fp4_records(fe.packed[e], N, K, half).numpy(), want.numpy())
+    assert not Fp4Experts.supported(torch.tensor([200], dtype=torch.uint8), K) and not Fp4Experts.supported(sc, 96)
+    tiny = sc.clone()
+    tiny[0, 0, 0] = 90                                # 2^-37: outside the fp16 form, fine for the bf16 form
+    assert not Fp4Experts.fits_fp16(codes, tiny) and not Fp4Experts.from_codes(codes, tiny, "cpu").half
+    zeros = codes.clone()
+    zeros[0, 0, :32] &= 8                              # a block of signed zeros may carry any scale
+    assert Fp4Experts.fits_fp16(zeros, tiny)
+
+
 def test_longrope_switches_caches_and_rebuilds_the_kv_cache(tmp_path):
     """Phi-3 long-context RoPE: short-factor caches within the original context length, long-factor caches (and a
     rebuilt KV cache) once the sequence grows past it."""

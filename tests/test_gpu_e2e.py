@@ -259,6 +259,38 @@ def test_non_gated_parallel_and_learned_position_families_on_gpu(family, tmp_pat
     assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
 
 
+def test_mxfp4_experts_stay_packed_on_gpu(tmp_path, monkeypatch):
+    """A QMoE checkpoint (MXFP4 experts) on the GPU keeps its experts packed and runs the grouped FP4 GEMM; its logits
+    follow the same checkpoint with the experts expanded to bf16 at load (OGB_FP4_EXPERTS=0) and the fp32 CPU path."""
+    from onnxruntime_genai_b200.models.builder import random_state_dict
+    from onnxruntime_genai_b200.ops.fp4 import Fp4Experts
+    arch = ArchConfig(vocab_size=1024, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=64, intermediate_size=128,
+                      context_length=256, bos_token_id=0, eos_token_id=1023, pad_token_id=0, model_type="gptoss", num_experts=8,
+                      experts_per_token=2, attn_bias=True, o_bias=True, mlp_bias=True, attn_sinks=True, sliding_window=16, sliding_layers=[0])
+    sd = random_state_dict(arch, seed=4, std=0.05)
+    gpu, cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
+    export_model(copy.deepcopy(arch), gpu, "int4", "cuda", state_dict=sd)
+    export_model(copy.deepcopy(arch), cpu, "int4", "cpu", state_dict=sd)
+    prompt = np.random.RandomState(9).randint(0, 1023, size=(2, 37)).astype(np.int32)
+    packed = og.Model(gpu)
+    assert isinstance(packed.decoder.layers[0].exp_gate_up_w, Fp4Experts) and isinstance(packed.decoder.layers[1].exp_down_w, Fp4Experts)
+    assert packed.decoder.layers[0].exp_gate_up_w.half and packed.decoder.layers[0].exp_down_w.half   # block scales fit the fp16 form
+    _, lp = _logits(packed, prompt)
+    monkeypatch.setenv("OGB_FP4_FORM", "bf16")
+    packed_bf16 = og.Model(gpu)
+    assert isinstance(packed_bf16.decoder.layers[0].exp_down_w, Fp4Experts) and not packed_bf16.decoder.layers[0].exp_down_w.half
+    _, lb = _logits(packed_bf16, prompt)
+    monkeypatch.setenv("OGB_FP4_EXPERTS", "0")
+    expanded = og.Model(gpu)
+    assert torch.is_tensor(expanded.decoder.layers[0].exp_gate_up_w)
+    _, le = _logits(expanded, prompt)
+    _, lc = _logits(og.Model(cpu), prompt)
+    ops.check_kernel_status()
+    assert np.abs(lp - le).max() < 0.03 * le.std() + 0.01      # same weights; fp16 instead of bf16 between the two expert GEMMs
+    assert np.abs(lb - le).max() < 0.03 * le.std() + 0.01      # same weights, same bf16 arithmetic up to summation order
+    assert np.abs(lp - lc).max() < 0.08 * lc.std() + 0.02
+
+
 def _export_pair(tmp_path, export, **kw):
     gpu, cpu = str(tmp_path / "gpu"), str(tmp_path / "cpu")
     export(gpu, "cuda", "bf16", **kw)

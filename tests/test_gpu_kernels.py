@@ -788,6 +788,75 @@ def test_moe_grouped_gemm_matches_expert_loop(T, E, k, H, I):
         assert bad < (0.002 if T <= 100 else 0.02), f"{bad:.4f} of the outputs differ (experts {lo}..{hi})"
 
 
+def _random_fp4(E, N, K, seed):
+    """Random MXFP4 experts: codes [E, N, K] (every e2m1 value, both signs), scale codes [E, N, K/32]."""
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(0, 16, (E, N, K), generator=g, dtype=torch.uint8)
+    scales = torch.randint(117, 123, (E, N, K // 32), generator=g, dtype=torch.uint8)
+    return codes, scales
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_fp4_expansion_is_exact_for_every_code(half):
+    """One expert whose rows hold every e2m1 code against an identity activation: the grouped FP4 GEMM returns the
+    weights themselves, so every code (the subnormal 0.5 and both zeros included) times several block scales is
+    checked bit for bit."""
+    from onnxruntime_genai_b200.ops.fp4 import Fp4Experts
+    N, K = 128, 64
+    codes = (torch.arange(N * K, dtype=torch.int64).view(1, N, K) * 7 % 16).to(torch.uint8)
+    codes[0, :, :16] = torch.arange(16, dtype=torch.uint8)
+    # bf16 form 2^-112 .. 2^1, fp16 form 2^-14 .. 2^9 (times 6 still below the fp16 maximum divided by the fp32 round trip):
+    # every product is a normal bf16 (the kernels are built with flush-to-zero fp32 arithmetic)
+    if half:
+        scales = (torch.arange(N * 2, dtype=torch.int64).view(1, N, 2) % 24 + 113).to(torch.uint8)
+    else:
+        scales = (torch.arange(N * 2, dtype=torch.int64).view(1, N, 2) % 114 + 15).to(torch.uint8)
+    scales[0, :8] = 127
+    fe = Fp4Experts.from_codes(codes, scales, DEV, half=half)
+    x = torch.eye(K, dtype=torch.float16 if half else torch.bfloat16, device=DEV)
+    logits = torch.zeros(K, 1, dtype=torch.float32, device=DEV)
+    plan = ops.moe_route(logits, 1, 0, (0, 1))
+    xs = x[plan.sorted_token.long()].contiguous()
+    y = ops.moe_gemm(xs, fe, plan, None)
+    ops.check_kernel_status()
+    got = torch.empty_like(y)
+    got[plan.sorted_token.long()] = y
+    want = fe.dequantize(0).t().to(torch.bfloat16)          # [K, N]: row k of the output is column k of the weight
+    assert torch.equal(got.cpu(), want), f"{(got.cpu() != want).sum().item()} of {want.numel()} weights differ"
+
+
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("T,E,k,H,I", [(3, 4, 2, 128, 64), (64, 32, 4, 256, 192), (700, 8, 2, 320, 128), (40, 8, 4, 2880, 64)])
+def test_moe_fp4_grouped_gemm_matches_expert_loop(T, E, k, H, I, half):
+    """Packed MXFP4 experts through the grouped FP4 GEMM (clamped SwiGLU epilogue, then the down projection whose
+    row count is not a multiple of the 128-row tile) against the fp32 loop over the dequantised experts."""
+    from onnxruntime_genai_b200.ops.fp4 import Fp4Experts
+    x = _rand(T, H, std=1.0, seed=51)
+    router_w, router_b = _rand(E, H, std=0.1, seed=52), _rand(E, std=0.1, seed=53)
+    gu_c, gu_s = _random_fp4(E, 2 * I, H, 54)
+    dn_c, dn_s = _random_fp4(E, H, I, 55)
+    gu_b, dn_b = _rand(E, 2 * I, std=0.1, seed=56), _rand(E, H, std=0.1, seed=57)
+    gu_w = Fp4Experts.from_codes(gu_c, gu_s, "cpu").dequantize().to(DEV)
+    dn_w = Fp4Experts.from_codes(dn_c, dn_s, "cpu").dequantize().to(DEV)
+    alpha, limit = 1.702, 7.0
+    want, _ = _moe_reference(x, router_w, router_b, gu_w, gu_b, dn_w, dn_b, k, alpha, limit)
+    logits = ops.linear(x, router_w, router_b, out_fp32=True)
+    gb = ops.interleave_experts_gate_up(gu_b)
+    for lo, hi in ((0, E), (E // 2, E)):
+        gw = Fp4Experts.from_codes(ops.interleave_experts_gate_up(gu_c[lo:hi]), ops.interleave_experts_gate_up(gu_s[lo:hi]), DEV, half=half)
+        dw = Fp4Experts.from_codes(dn_c[lo:hi].contiguous(), dn_s[lo:hi].contiguous(), DEV, half=half)
+        plan = ops.moe_route(logits, k, 0, (lo, hi))
+        xs = ops.gather_rows(x, plan.sorted_token, f16=half)
+        h = ops.moe_gemm(xs, gw, plan, gb[lo:hi].contiguous(), act_kind=2, alpha=alpha, limit=limit,
+                         out_dtype=torch.float16 if half else torch.bfloat16)
+        y = ops.moe_gemm(h, dw, plan, dn_b[lo:hi].contiguous())
+        got = ops.moe_combine(y, plan)
+        ops.check_kernel_status()
+        ref_out = want if (lo, hi) == (0, E) else _moe_reference(x, router_w, router_b, gu_w, gu_b, dn_w, dn_b, k, alpha, limit, lo, hi)[0]
+        bad = ((got.float() - ref_out.to(got.device)).abs() > 0.03 + 0.03 * ref_out.abs().to(got.device)).float().mean().item()
+        assert bad < (0.002 if T <= 100 else 0.02), f"{bad:.4f} of the outputs differ (experts {lo}..{hi})"
+
+
 # ------------------------------------------------------------------------------------------- sampled speculative verify
 def test_verify_sampled_preserves_the_target_distribution():
     """Rejection sampling theorem: whatever the proposal, the first committed token follows the target's sampled
