@@ -317,8 +317,13 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             ins = [inp, base + ".MatMul.weight_Q4", base + ".MatMul.weight_scales"] + ([] if int4_symmetric else [base + ".MatMul.weight_zp"])
             W.node("MatMulNBits", node_name + "_Q4", ins, [out], domain="com.microsoft", K=K, N=N, bits=4, block_size=32, accuracy_level=4)
         elif precision == "int4":
-            w = torch.cat([get(n).float() for n in src_names], dim=0)
-            q, s, zp = quantize_int4_block32(w, symmetric=int4_symmetric)
+            srcs = [get(n) for n in src_names]
+            if all(hasattr(t, "matmulnbits") for t in srcs):
+                # AWQ / GPTQ checkpoint: the quantised tensors are carried over, not quantised a second time
+                from .quantized_checkpoint import QuantizedLinear
+                q, s, zp = QuantizedLinear.cat(srcs).matmulnbits()
+            else:
+                q, s, zp = quantize_int4_block32(torch.cat([t.float() for t in srcs], dim=0), symmetric=int4_symmetric)
             W.add_array(base + ".MatMul.weight_Q4", q.numpy(), op.UINT8)
             W.add_array(base + ".MatMul.weight_scales", s.reshape(-1).to(torch.float16).numpy(), op.FLOAT16)
             ins = [inp, base + ".MatMul.weight_Q4", base + ".MatMul.weight_scales"]
@@ -868,6 +873,14 @@ def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
             sd.update(torch.load(os.path.join(model_dir, f), map_location="cpu", weights_only=True))
     if not sd:
         raise FileNotFoundError(f"no weights found in {model_dir}")
+    cfg_path = os.path.join(model_dir, "config.json")
+    if os.path.exists(cfg_path):
+        with open(cfg_path) as f:
+            qc = json.load(f).get("quantization_config")
+        if qc and any(k.endswith(".qweight") for k in sd):
+            # AWQ / GPTQ linears become QuantizedLinear entries: an int4 export writes them as they are
+            from .quantized_checkpoint import convert_state_dict
+            sd = convert_state_dict(sd, qc)
     out = {}
     for k, v in sd.items():
         if k.endswith("qkv_proj.weight"):  # phi3 packs q, k, v
@@ -877,7 +890,7 @@ def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
         elif k.endswith("gate_up_proj.weight"):
             base = k[: -len("gate_up_proj.weight")]
             half = v.shape[0] // 2
-            out[base + "gate_proj.weight"], out[base + "up_proj.weight"] = v[:half], v[half:]
+            out[base + "gate_proj.weight"], out[base + "up_proj.weight"] = (v.rows(0, half), v.rows(half, 2 * half)) if hasattr(v, "rows") else (v[:half], v[half:])
         else:
             out[k] = v
     return out
@@ -887,7 +900,11 @@ def _split_packed_qkv(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
     for k in [k for k in sd if k.endswith("__packed_qkv__")]:
         base = k[: -len("__packed_qkv__")]
         v = sd.pop(k)
-        q, kk, vv = torch.split(v, [arch.q_size, arch.kv_size, arch.kv_size], dim=0)
+        if hasattr(v, "rows"):   # a pre-quantised (AWQ / GPTQ) packed projection
+            a, b = arch.q_size, arch.q_size + arch.kv_size
+            q, kk, vv = v.rows(0, a), v.rows(a, b), v.rows(b, b + arch.kv_size)
+        else:
+            q, kk, vv = torch.split(v, [arch.q_size, arch.kv_size, arch.kv_size], dim=0)
         sd[base + "q_proj.weight"], sd[base + "k_proj.weight"], sd[base + "v_proj.weight"] = q, kk, vv
 
 
@@ -903,6 +920,8 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         if not int(extra.get("random_weights", 0)) and not int(extra.get("synthetic_weights", 0)):
             state_dict = load_hf_state_dict(model_name_or_dir)
             _split_packed_qkv(state_dict, arch)
+            if precision != "int4":   # a pre-quantised checkpoint exported at a float precision: dequantise
+                state_dict = {k: (v.float() if hasattr(v, "matmulnbits") else v) for k, v in state_dict.items()}
         for fn in ("tokenizer.json", "tokenizer_config.json", "special_tokens_map.json", "tokenizer.model", "chat_template.jinja",
                    "generation_config.json"):
             src = os.path.join(model_name_or_dir, fn)

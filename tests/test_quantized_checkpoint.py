@@ -1,0 +1,106 @@
+"""AWQ / GPTQ checkpoints are carried into the MatMulNBits layout without a second quantisation
+(reference: src/python/py/models/quantized_model.py:1017-1107)."""
+import copy
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import onnxruntime_genai_b200 as og
+from onnxruntime_genai_b200.models.arch import ArchConfig
+from onnxruntime_genai_b200.models.builder import create_model, random_state_dict
+from onnxruntime_genai_b200.models.quantized_checkpoint import (QuantizedLinear, convert_state_dict, pack_awq, pack_gptq, unpack_awq,
+                                                                unpack_gptq)
+from dense_reference import logits as dense_logits
+
+ARCH = dict(model_type="llama", vocab_size=96, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32,
+            intermediate_size=256, context_length=64, bos_token_id=1, eos_token_id=2, pad_token_id=0)
+
+
+def _random_ql(N, K, group, seed):
+    g = torch.Generator().manual_seed(seed)
+    r = group // 32
+    q = torch.randint(0, 16, (N, K), generator=g, dtype=torch.uint8)
+    s = (torch.rand(N, K // group, generator=g) * 0.02 + 0.002).to(torch.float16).float().repeat_interleave(r, dim=1)
+    z = torch.randint(0, 16, (N, K // group), generator=g, dtype=torch.uint8).repeat_interleave(r, dim=1)
+    return QuantizedLinear(q, s, z)
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+def test_awq_and_gptq_words_round_trip(group):
+    ql = _random_ql(48, 256, group, 1)
+    a = unpack_awq(*pack_awq(ql, group), group)
+    assert torch.equal(a.q, ql.q) and torch.equal(a.zp, ql.zp) and torch.equal(a.scales, ql.scales)
+    for off in (0, 1):
+        qw, qz, sc, g_idx = pack_gptq(ql, group, off)
+        b = unpack_gptq(qw, qz, sc, group, g_idx, off)
+        assert torch.equal(b.q, ql.q) and torch.equal(b.zp, ql.zp) and torch.equal(b.scales, ql.scales)
+    # the AWQ nibble order: nibble 1 of a word holds column 2
+    one = QuantizedLinear(torch.zeros(8, 32, dtype=torch.uint8), torch.ones(8, 1), torch.zeros(8, 1, dtype=torch.uint8))
+    one.q[2, 0] = 5
+    assert int(pack_awq(one, 32)[0][0, 0]) == 5 << 4
+    with pytest.raises(NotImplementedError):
+        unpack_gptq(qw, qz, sc, group, torch.flip(g_idx, [0]), 1)
+    with pytest.raises(NotImplementedError):
+        convert_state_dict({}, {"quant_method": "awq", "bits": 8})
+
+
+@pytest.mark.parametrize("method", ["awq", "gptq"])
+def test_quantised_hf_checkpoint_exports_without_requantisation(method, tmp_path):
+    """A Hugging Face directory with AWQ / GPTQ linears (group 64) -> int4 export -> the loaded model computes with exactly
+    the checkpoint's quantised weights: logits equal the dense fp32 model built from the dequantised tensors."""
+    from safetensors.torch import save_file
+    arch = ArchConfig(**ARCH)
+    sd = random_state_dict(arch, seed=11, std=0.1)
+    group = 64
+    hf, dense, qls = {}, {}, {}
+    for i, (k, v) in enumerate(sd.items()):
+        if k.endswith("_proj.weight"):
+            ql = _random_ql(v.shape[0], v.shape[1], group, 100 + i)
+            base = k[: -len(".weight")]
+            if method == "awq":
+                hf[base + ".qweight"], hf[base + ".qzeros"], hf[base + ".scales"] = pack_awq(ql, group)
+            else:
+                hf[base + ".qweight"], hf[base + ".qzeros"], hf[base + ".scales"], hf[base + ".g_idx"] = pack_gptq(ql, group)
+            dense[k] = ql.float()
+            qls[k] = ql
+        elif k == "lm_head.weight":
+            # not quantised in the checkpoint: the int4 export quantises it (round to nearest, block 32, fp16 scales)
+            from onnxruntime_genai_b200.models.builder import dequantize_int4_block32, quantize_int4_block32
+            q, sc, zp = quantize_int4_block32(v.float())
+            hf[k] = v
+            dense[k] = dequantize_int4_block32(q, sc.to(torch.float16).float(), zp, v.shape[0], v.shape[1])
+        else:
+            hf[k] = v
+            dense[k] = v
+    src = tmp_path / "hf"
+    os.makedirs(src)
+    save_file({k: v.contiguous() for k, v in hf.items()}, str(src / "model.safetensors"))
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=96, hidden_size=128, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, intermediate_size=256, max_position_embeddings=64,
+               rms_norm_eps=1e-5, rope_theta=10000.0, bos_token_id=1, eos_token_id=2, pad_token_id=0, tie_word_embeddings=False,
+               quantization_config={"quant_method": method, "bits": 4, "group_size": group})
+    (src / "config.json").write_text(json.dumps(cfg))
+    out = str(tmp_path / "out")
+    create_model(str(src), out, "int4", "cpu")
+    model = og.Model(out)
+    # the quantised tensors arrive unchanged: codes, scales and zero points of the packed q / k / v projection and of o
+    lw = model.decoder.layers[0]
+    pre = "model.layers.0.self_attn."
+    for got, names in ((lw.qkv_w, ("q_proj", "k_proj", "v_proj")), (lw.o_w, ("o_proj",))):
+        want_q = torch.cat([qls[pre + n + ".weight"].q for n in names], 0)
+        want_s = torch.cat([qls[pre + n + ".weight"].scales for n in names], 0)
+        want_z = torch.cat([qls[pre + n + ".weight"].zp for n in names], 0)
+        assert torch.equal(got._q.cpu().to(torch.uint8), want_q) and torch.equal(got._zp.cpu().to(torch.uint8), want_z)
+        np.testing.assert_allclose(got._s.cpu().float().numpy(), want_s.numpy(), rtol=0, atol=0)
+    ids = np.random.RandomState(3).randint(3, 96, size=(1, 9)).astype(np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=16)
+    g = og.Generator(model, p)
+    g.append_tokens(ids)
+    want = dense_logits(model.arch, dense, ids[0].tolist())[-1].numpy()
+    # the int4 path rounds the dequantised weights and the activations to bf16: logits agree to that precision
+    got = g.get_logits().reshape(-1)
+    assert np.abs(got - want).max() < 0.05 * want.std() + 0.02
