@@ -147,7 +147,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
   // -------------------------------------------------------------------- epilogue (warps 2..5)
-  const bool epi = warp >= 2;
+  const bool epi = warp >= 2 && warp < 6;   // kernels with more than six warps: the others only meet the CTA-wide barriers
   const int et = threadIdx.x - 64;   // 0..127 for epilogue threads
   float* part = reinterpret_cast<float*>(smem);  // [BT][128] fp32, reuses the pipeline stages
   if (epi) {

@@ -23,8 +23,11 @@
 // of weights instead of six integer / bf16 operations: the expansion stops being the limit of the weight stream.
 //
 // Pipeline and epilogue are those of the int4 kernel (gemm_w4.cu): warp 0 streams records through a deep ring and
-// the activation tiles through a 2-deep ring, warps 2..5 (one thread per weight row) expand a record into the
-// swizzled K-major bf16 tile, warp 1 issues tcgen05.mma into tensor memory.  The tile list of ogb_moe_sort selects
+// the activation tiles through a ring of their own (4 or 8 deep), warps 2..9 (two threads per weight row, a block of 32 weights each)
+// expand a record into the swizzled K-major tile, warp 1 issues tcgen05.mma into tensor memory, warps 2..5 run the
+// epilogue.  Eight expander warps per CTA, two CTAs per SM: the expansion is a chain of dependent integer / half
+// operations per thread, and it takes that many warps to keep a k-block's expansion under the time its 4352 bytes
+// take to arrive (with four warps the kernel ran at 0.33 of the HBM rate, bound by that chain, not by its bytes).  The tile list of ogb_moe_sort selects
 // the expert, first row and row count of each token tile.  Every wait is bounded.
 #include <cstdlib>
 
@@ -36,14 +39,19 @@
 namespace ogb {
 
 constexpr int FP4_RECORD_BYTES = GEMM_BLOCK_N * 32 + GEMM_BLOCK_N * 2;  // 4352
-constexpr int FP4_WBUF = 2;
+constexpr int FP4_THREADS = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2..9 expanders (2..5 also run the epilogue)
+constexpr int FP4_DEQ_WARPS = 8;
 
-template <int BT>
+template <int BT, int FP4_WBUF>
 struct Fp4Cfg {
   static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
   static constexpr bool TWO_PER_SM = BT <= 64;
   static constexpr int BUDGET = TWO_PER_SM ? 100 * 1024 : 196 * 1024;
-  static constexpr int FIXED = FP4_WBUF * (W_TILE_BYTES + A_TILE_BYTES);
+  // Activation tiles have their own, deeper ring: a tile is requested when the MMA that read the slot has finished, and
+  // the copy takes most of a microsecond to arrive, so with two slots every k-block waited half that latency (the
+  // kernel then ran at 0.3 of the HBM rate whatever the expansion cost).
+  static constexpr int A_STAGES = BT <= 32 ? 8 : 4;
+  static constexpr int FIXED = FP4_WBUF * W_TILE_BYTES + A_STAGES * A_TILE_BYTES;
   static constexpr int MAX_RAW = (BUDGET - FIXED) / FP4_RECORD_BYTES;
   // a multiple of 4 records keeps the tiles behind the ring 1 KiB aligned (4 * 4352 = 17 KiB)
   static constexpr int RAW = (MAX_RAW > 16 ? 16 : MAX_RAW) / 4 * 4;
@@ -85,12 +93,15 @@ __device__ __forceinline__ uint4 deq_fp4_word_f16(uint32_t word, __half2 s2) {
   return make_uint4(mul(h0), mul(h1), mul(h2), mul(h3));
 }
 
-template <int BT, bool HALF>
-__global__ void __launch_bounds__(GEMM_THREADS, Fp4Cfg<BT>::TWO_PER_SM ? 2 : 1)
+// FP4_WBUF: expanded weight tiles in flight; GROUPS: 1 = all eight expander warps share every k-block (two threads per
+// row), 2 = warps 2..5 take the even k-blocks and warps 6..9 the odd ones (one thread per row).
+template <int BT, bool HALF, int FP4_WBUF, int GROUPS>
+__global__ void __launch_bounds__(FP4_THREADS, Fp4Cfg<BT, FP4_WBUF>::TWO_PER_SM ? 2 : 1)
 gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert,
                         const GemmParams p) {
-  using Cfg = Fp4Cfg<BT>;
+  using Cfg = Fp4Cfg<BT, FP4_WBUF>;
   constexpr int RAW = Cfg::RAW;
+  constexpr int ARRIVALS = FP4_DEQ_WARPS / GROUPS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_ring = smem;
@@ -99,9 +110,11 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem + Cfg::DATA_BYTES);
   uint64_t* raw_empty = raw_full + RAW;
   uint64_t* deq_full = raw_empty + RAW;
-  uint64_t* a_full = deq_full + FP4_WBUF;
-  uint64_t* w_empty = a_full + FP4_WBUF;
-  uint64_t* accum_bar = w_empty + FP4_WBUF;
+  constexpr int A_ST = Cfg::A_STAGES;
+  uint64_t* w_empty = deq_full + FP4_WBUF;
+  uint64_t* a_full = w_empty + FP4_WBUF;
+  uint64_t* a_empty = a_full + A_ST;
+  uint64_t* accum_bar = a_empty + A_ST;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile uint32_t* use_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
@@ -117,8 +130,9 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
   const int expert = p.grp.tile_expert[m_tile];
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < RAW; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 128); }
-    for (int s = 0; s < FP4_WBUF; ++s) { mbar_init(&deq_full[s], 128); mbar_init(&a_full[s], 1); mbar_init(&w_empty[s], 1); }
+    for (int s = 0; s < RAW; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], ARRIVALS); }
+    for (int s = 0; s < FP4_WBUF; ++s) { mbar_init(&deq_full[s], ARRIVALS); mbar_init(&w_empty[s], 1); }
+    for (int s = 0; s < A_ST; ++s) { mbar_init(&a_full[s], 1); mbar_init(&a_empty[s], 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -146,7 +160,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
         fp4_bulk_copy_g2s(raw_ring + s * FP4_RECORD_BYTES, rec0 + size_t(i) * rec_stride, FP4_RECORD_BYTES, &raw_full[s]);
       };
       auto load_a = [&](int i) {
-        const int s = i % FP4_WBUF;
+        const int s = i % A_ST;
         mbar_expect_tx(&a_full[s], Cfg::A_TILE_BYTES);
         tma_load_2d(a_ring + s * Cfg::A_TILE_BYTES, &tmap_a, &a_full[s], i * GEMM_BLOCK_K, row0);
       };
@@ -158,14 +172,14 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
       while ((ri < num_kb || ai < num_kb) && !*abort_flag) {
         bool progressed = false;
         if (ri < num_kb && mbar_try_wait(&raw_empty[ri % RAW], ((ri / RAW) & 1) ^ 1)) { load_raw(ri); ++ri; progressed = true; }
-        if (ai < num_kb && (ai < FP4_WBUF || mbar_try_wait(&w_empty[ai % FP4_WBUF], ((ai / FP4_WBUF) & 1) ^ 1))) { load_a(ai); ++ai; progressed = true; }
+        if (ai < num_kb && (ai < A_ST || mbar_try_wait(&a_empty[ai % A_ST], ((ai / A_ST) & 1) ^ 1))) { load_a(ai); ++ai; progressed = true; }
         if (progressed) { idle = 0; continue; }
         if ((++idle & 0x3ff) == 0 && global_timer_ns() - t0 > 4000000000ull) { fail(OGB_ERR_WAIT_TMA); break; }
       }
       if (*abort_flag) {
         volatile int never = 0;
         for (int i = max(0, ri - RAW); i < ri; ++i) mbar_wait_bounded(&raw_full[i % RAW], (i / RAW) & 1, &never, 200000000ull);
-        for (int i = max(0, ai - FP4_WBUF); i < ai; ++i) mbar_wait_bounded(&a_full[i % FP4_WBUF], (i / FP4_WBUF) & 1, &never, 200000000ull);
+        for (int i = max(0, ai - A_ST); i < ai; ++i) mbar_wait_bounded(&a_full[i % A_ST], (i / A_ST) & 1, &never, 200000000ull);
       }
     }
   } else if (warp == 1) {
@@ -174,59 +188,72 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
       constexpr uint32_t idesc = umma_idesc_f16(GEMM_BLOCK_N, BT, HALF ? 0 : 1);   // operand format: fp16 or bf16
       bool ok = true;
       for (int i = 0; i < num_kb && ok; ++i) {
-        const int s = i % FP4_WBUF;
-        const uint32_t ph = (i / FP4_WBUF) & 1;
-        if (!mbar_wait_bounded(&deq_full[s], ph, abort_flag) || !mbar_wait_bounded(&a_full[s], ph, abort_flag)) {
+        const int s = i % FP4_WBUF, as = i % A_ST;
+        if (!mbar_wait_bounded(&deq_full[s], (i / FP4_WBUF) & 1, abort_flag) || !mbar_wait_bounded(&a_full[as], (i / A_ST) & 1, abort_flag)) {
           fail(OGB_ERR_WAIT_TMA); ok = false; break;
         }
         tc_fence_after();
-        const uint32_t w = smem_u32(w_ring + s * W_TILE_BYTES), a = smem_u32(a_ring + s * Cfg::A_TILE_BYTES);
+        const uint32_t w = smem_u32(w_ring + s * W_TILE_BYTES), a = smem_u32(a_ring + as * Cfg::A_TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
           umma_f16(tmem_base, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc,
                    (i > 0 || k > 0) ? 1u : 0u);
         umma_commit(&w_empty[s]);
+        umma_commit(&a_empty[as]);
       }
       if (ok) umma_commit(accum_bar);
     }
   } else {
-    // -------------------------------------------------------------- expanders: thread = weight row of the tile
-    const int row = threadIdx.x - 64;
-    for (int i = 0; i < num_kb; ++i) {
+    // -------------------------------------------------------------- expanders: two threads per weight row of the tile,
+    // one block of 32 weights (16 bytes of nibbles, one multiplier byte) each; one arrival per warp on the barriers
+    const int dt = threadIdx.x - 64;
+    const int row = dt & 127;
+    constexpr int WORDS = 4 * GROUPS;                       // 32-bit words of nibbles per thread and k-block
+    const int group = GROUPS == 2 ? dt >> 7 : 0;            // which k-blocks this thread expands
+    const int part = GROUPS == 2 ? 0 : dt >> 7;             // which block of 32 of the row's 64 weights (GROUPS == 1)
+    for (int i = group; i < num_kb; i += GROUPS) {
       const int rs = i % RAW, ws = i % FP4_WBUF;
       bool ok = mbar_wait_bounded(&raw_full[rs], (i / RAW) & 1, abort_flag);
       if (ok && i >= FP4_WBUF) ok = mbar_wait_bounded(&w_empty[ws], ((i / FP4_WBUF) & 1) ^ 1, abort_flag);
-      if (!ok) { fail(OGB_ERR_WAIT_TMA); break; }
+      if (!__all_sync(0xffffffffu, ok)) { fail(OGB_ERR_WAIT_TMA); break; }   // the warp gives up as one (it meets at __syncwarp below)
       const uint8_t* rec = raw_ring + rs * FP4_RECORD_BYTES;
-      const uint4 q0 = *reinterpret_cast<const uint4*>(rec + row * 32);
-      const uint4 q1 = *reinterpret_cast<const uint4*>(rec + row * 32 + 16);
-      const uint32_t mul = *reinterpret_cast<const uint16_t*>(rec + GEMM_BLOCK_N * 32 + row * 2);
-      const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      uint32_t words[WORDS];
+#pragma unroll
+      for (int h = 0; h < WORDS / 4; ++h) {
+        const uint4 q = *reinterpret_cast<const uint4*>(rec + row * 32 + (part + h) * 16);
+        words[4 * h] = q.x; words[4 * h + 1] = q.y; words[4 * h + 2] = q.z; words[4 * h + 3] = q.w;
+      }
+      const uint32_t mul = *reinterpret_cast<const uint16_t*>(rec + GEMM_BLOCK_N * 32 + row * 2);   // exponent fields of the two multipliers
       uint8_t* dst = w_ring + ws * W_TILE_BYTES + row * 128;
       if constexpr (HALF) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);     // fp16 exponent field of the block's scale
+        for (int jj = 0; jj < WORDS; ++jj) {
+          const int j = part * 4 + jj;
+          const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);
           const uint32_t sb = (m8 << 10) | (m8 << 26);
-          *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = deq_fp4_word_f16(words[j], *reinterpret_cast<const __half2*>(&sb));
+          *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = deq_fp4_word_f16(words[jj], *reinterpret_cast<const __half2*>(&sb));
         }
       } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);       // bf16 exponent field of the block's multiplier
-        const uint32_t sb = (m8 << 7) | (m8 << 23);
-        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sb);
-        uint4 o;
-        o.x = deq_fp4_pair(words[j], s2);
-        o.y = deq_fp4_pair(words[j] >> 4, s2);
-        o.z = deq_fp4_pair(words[j] >> 8, s2);
-        o.w = deq_fp4_pair(words[j] >> 12, s2);
-        *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = o;
-      }
+        for (int jj = 0; jj < WORDS; ++jj) {
+          const int j = part * 4 + jj;
+          const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);
+          const uint32_t sb = (m8 << 7) | (m8 << 23);
+          const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&sb);
+          uint4 o;
+          o.x = deq_fp4_pair(words[jj], s2);
+          o.y = deq_fp4_pair(words[jj] >> 4, s2);
+          o.z = deq_fp4_pair(words[jj] >> 8, s2);
+          o.w = deq_fp4_pair(words[jj] >> 12, s2);
+          *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = o;
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
-      mbar_arrive(&deq_full[ws]);
-      mbar_arrive(&raw_empty[rs]);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&deq_full[ws]);
+        mbar_arrive(&raw_empty[rs]);
+      }
     }
   }
 
@@ -239,18 +266,18 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
 
 bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
 
-template <int BT, bool HALF>
-static int LaunchFp4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  using Cfg = Fp4Cfg<BT>;
+template <int BT, bool HALF, int WBUF, int GROUPS>
+static int LaunchFp4V(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  using Cfg = Fp4Cfg<BT, WBUF>;
   static bool configured = false;
-  auto kern = gemm_fp4_grouped_kernel<BT, HALF>;
+  auto kern = gemm_fp4_grouped_kernel<BT, HALF, WBUF, GROUPS>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.blockDim = dim3(FP4_THREADS);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[1];
@@ -263,6 +290,18 @@ static int LaunchFp4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, cons
   cfg.attrs = attrs;
   cfg.numAttrs = unsigned(na);
   return cudaLaunchKernelEx(&cfg, kern, ta, wp, n_tiles, p) == cudaSuccess ? 0 : -4;
+}
+
+template <int BT, bool HALF>
+static int LaunchFp4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  // OGB_FP4_VARIANT (16-token tiles only): 0 = two expanded tiles in flight, 1 = four, 2 = four with the expander
+  // warps in two groups that alternate k-blocks
+  static const int variant = [] { const char* e = getenv("OGB_FP4_VARIANT"); return e ? atoi(e) : 0; }();
+  if constexpr (BT <= 16) {
+    if (variant == 1) return LaunchFp4V<BT, HALF, 4, 1>(ta, wp, n_tiles, p, grid, stream);
+    if (variant == 2) return LaunchFp4V<BT, HALF, 4, 2>(ta, wp, n_tiles, p, grid, stream);
+  }
+  return LaunchFp4V<BT, HALF, 2, 1>(ta, wp, n_tiles, p, grid, stream);
 }
 
 }  // namespace ogb

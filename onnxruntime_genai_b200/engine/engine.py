@@ -378,8 +378,10 @@ class Engine:
         self.model = model
         cfg = model.config
         eng = cfg.engine.get("dynamic_batching")
+        static = False
         if eng is None:
             sb = cfg.engine.get("static_batching")
+            static = sb is not None     # fixed batches of up to 4 requests that run to completion, on the paged cache
             eng = {"block_size": 16, "num_blocks": None, "gpu_utilization_factor": None,
                    "max_batch_size": sb["max_batch_size"] if sb else 16, "max_scheduled_tokens": 2048}
         arch = model.arch
@@ -391,6 +393,7 @@ class Engine:
         o = native.EngineOptions()
         o.block_size, o.num_blocks = self.block_size, int(nb)
         o.max_batch_size, o.max_scheduled_tokens = int(eng["max_batch_size"]), int(eng["max_scheduled_tokens"])
+        o.static_batching = static
         o.vocab_size, o.pad_token_id, o.eos_ids = cfg.vocab_size, cfg.pad_token_id, list(cfg.eos_token_ids)
         windowed = arch.sliding_window > 0 and arch.sliding_layers is not None
         if windowed:

@@ -914,6 +914,11 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
     if model_name_or_dir in PRESETS:
         import copy
         arch = copy.deepcopy(PRESETS[model_name_or_dir])
+    elif model_name_or_dir.endswith(".gguf") and os.path.isfile(model_name_or_dir):
+        # a GGUF file: metadata -> architecture, tensors dequantised to fp32 under their Hugging Face names
+        from .gguf_reader import hf_config_and_state_dict
+        cfg, state_dict = hf_config_and_state_dict(model_name_or_dir)
+        arch = from_hf_config(cfg)
     else:
         with open(os.path.join(model_name_or_dir, "config.json")) as f:
             arch = from_hf_config(json.load(f))

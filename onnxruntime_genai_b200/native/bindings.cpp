@@ -360,6 +360,7 @@ PYBIND11_MODULE(_og_native, m) {
       .def(py::init<>())
       .def_readwrite("block_size", &EngineOptions::block_size).def_readwrite("num_blocks", &EngineOptions::num_blocks)
       .def_readwrite("max_batch_size", &EngineOptions::max_batch_size)
+      .def_readwrite("static_batching", &EngineOptions::static_batching)
       .def_readwrite("max_scheduled_tokens", &EngineOptions::max_scheduled_tokens)
       .def_readwrite("window_size", &EngineOptions::window_size).def_readwrite("lookahead", &EngineOptions::lookahead)
       .def_readwrite("num_window_blocks", &EngineOptions::num_window_blocks)

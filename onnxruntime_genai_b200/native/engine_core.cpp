@@ -146,6 +146,8 @@ void EngineCore::AddRequest(const std::shared_ptr<Request>& r) {
   if (int(r->tokens_.size()) >= r->opt_.max_length)
     throw std::runtime_error("add_request: prompt length " + std::to_string(r->tokens_.size()) +
                              " leaves no room under max_length " + std::to_string(r->opt_.max_length));
+  if (opt_.static_batching && r->opt_.chunk_size > 0)
+    throw std::runtime_error("search.chunk_size requires dynamic batching; the static batch scheduler cannot chunk a prefill.");
   r->status_ = RequestStatus::kAssigned;
   requests_.push_back(r);
   ++metrics_.requests_admitted;
@@ -190,13 +192,39 @@ const StepPlan& EngineCore::Plan() {
     return (r.status_ == RequestStatus::kAssigned || r.status_ == RequestStatus::kActive) && r.Pending() > 0;
   };
   for (auto& r : requests_) if (r->resident_ && executable(*r)) cands.push_back(r);
-  for (auto& r : requests_) if (!r->resident_ && executable(*r)) cands.push_back(r);
+  if (opt_.static_batching) {
+    // Static batching (reference: src/engine/scheduler.cpp:57-113): a batch runs to completion before the next one is
+    // admitted; the next batch is the first 4 waiting requests, or 2, or 1, whichever the cache can hold at full length.
+    if (cands.empty()) {
+      std::vector<std::shared_ptr<Request>> waiting;
+      for (auto& r : requests_) if (!r->resident_ && executable(*r)) waiting.push_back(r);
+      constexpr size_t kStaticBatch = 4;
+      for (size_t n = std::min({kStaticBatch, waiting.size(), size_t(opt_.max_batch_size)}); n != 0; n /= 2) {
+        int blocks = 0;
+        for (size_t i = 0; i < n; ++i)
+          blocks += BlocksFor(std::max(waiting[i]->opt_.max_length, int(waiting[i]->tokens_.size())));
+        if (blocks <= pool_.FreeCount() && (!wpool_ || int(n) * ring_blocks_ <= wpool_->FreeCount())) {
+          cands.assign(waiting.begin(), waiting.begin() + long(n));
+          break;
+        }
+      }
+      if (cands.empty() && !waiting.empty()) {
+        // not even one request fits at full length: a request larger than the whole pool can never run
+        auto& r = waiting.front();
+        if (BlocksFor(std::max(r->opt_.max_length, int(r->tokens_.size()))) > pool_.Total()) plan_.unserviceable.push_back(r);
+        else ++plan_.deferred;
+      }
+    }
+  } else {
+    for (auto& r : requests_) if (!r->resident_ && executable(*r)) cands.push_back(r);
+  }
   std::stable_partition(cands.begin(), cands.end(), [](const std::shared_ptr<Request>& r) { return !r->prefill_; });
 
   const int limit = std::min(opt_.max_scheduled_tokens, opt_.max_batch_size);
   for (auto& r : cands) {
     if (int(plan_.entries.size()) >= limit) break;
-    const int need_total = BlocksFor(int(r->tokens_.size()));
+    // static batching owns the blocks of the whole max_length from the first step (the contiguous cache of the reference)
+    const int need_total = BlocksFor(opt_.static_batching ? std::max(r->opt_.max_length, int(r->tokens_.size())) : int(r->tokens_.size()));
     if (need_total > pool_.Total() || (wpool_ && ring_blocks_ > wpool_->Total())) {
       plan_.unserviceable.push_back(r);
       continue;

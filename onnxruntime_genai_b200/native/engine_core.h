@@ -164,6 +164,8 @@ struct EngineOptions {
   int num_blocks{0};
   int max_batch_size{16};
   int max_scheduled_tokens{2048};
+  bool static_batching{false};  // fixed batches: up to 4 waiting requests (then 2, then 1) are admitted together with all the
+                                // blocks their max_length needs, and only once the batch before them has finished
   int lookahead{0};           // decode entries also reserve the block of their next `lookahead` positions
   int window_size{0};         // > 0 enables the sliding-window ring pool
   int num_window_blocks{0};   // blocks in the windowed pool

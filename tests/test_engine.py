@@ -457,6 +457,71 @@ def test_lookahead_plan_reserves_the_next_block_and_predicts_the_next_signature(
     core.check_invariants()
 
 
+def test_static_batching_runs_fixed_batches_to_completion():
+    """engine.static_batching (reference: src/engine/scheduler.cpp:57-113): up to four waiting requests are admitted together
+    with the blocks of their whole max_length, nothing joins while the batch runs, the batch size halves (4, 2, 1) until the
+    cache holds it, and search.chunk_size is refused."""
+    o = native.EngineOptions()
+    o.block_size, o.num_blocks, o.max_batch_size, o.max_scheduled_tokens, o.vocab_size, o.eos_ids = 4, 12, 8, 64, VOCAB, [EOS]
+    o.static_batching = True
+    core = native.EngineCore(o)
+
+    def request(n_prompt, max_length, chunk=0):
+        ro = native.RequestOptions()
+        ro.max_length, ro.chunk_size = max_length, chunk
+        r = core.create_request(ro)
+        r.add_tokens(np.arange(3, 3 + n_prompt, dtype=np.int32))
+        return r
+
+    with pytest.raises(RuntimeError, match="chunk_size requires dynamic batching"):
+        core.add_request(request(3, 8, chunk=2))
+    reqs = [request(3, 8) for _ in range(6)]          # 2 blocks each at full length: 12 blocks hold 6, a batch is 4
+    for r in reqs:
+        core.add_request(r)
+    plan = core.plan()
+    assert [e.request.id for e in plan.entries] == [r.id for r in reqs[:4]] and all(e.is_prefill for e in plan.entries)
+    assert core.free_blocks == 12 - 4 * 2              # the whole max_length is owned from the first step
+    core.commit(np.full(4, 9, dtype=np.int32))
+    late = request(2, 6)
+    core.add_request(late)                             # arrives while the batch runs: waits for the next batch
+    for _ in range(4):                                 # 3 prompt tokens + 5 generated = max_length 8; one came with the prefill
+        plan = core.plan()
+        assert [e.request.id for e in plan.entries] == [r.id for r in reqs[:4]] and not any(e.newly_admitted for e in plan.entries)
+        core.commit(np.full(4, 9, dtype=np.int32))
+    # the finished batch keeps its blocks until its requests are removed: only one full-length request fits beside it
+    plan = core.plan()
+    assert [e.request.id for e in plan.entries] == [reqs[4].id] and plan.entries[0].newly_admitted
+    core.commit(np.asarray([EOS], dtype=np.int32))
+    for r in reqs[:5]:
+        core.remove_request(r)
+    plan = core.plan()                                 # two are waiting: the last of the first wave and the late arrival
+    assert [e.request.id for e in plan.entries] == [reqs[5].id, late.id]
+    core.commit(np.full(2, EOS, dtype=np.int32))
+    core.check_invariants()
+
+    # halving: a pool that cannot hold four full-length requests takes two
+    o.num_blocks = 5
+    small = native.EngineCore(o)
+    core = small
+    rs = [request(3, 8) for _ in range(4)]
+    for r in rs:
+        small.add_request(r)
+    plan = small.plan()
+    assert [e.request.id for e in plan.entries] == [rs[0].id, rs[1].id] and small.free_blocks == 1
+    small.commit(np.full(2, EOS, dtype=np.int32))      # both finish at once
+    plan = small.plan()                                # their blocks are still held: nothing fits, the step is deferred
+    assert not plan.entries and plan.deferred == 1
+    small.remove_request(rs[0])
+    small.remove_request(rs[1])
+    plan = small.plan()
+    assert [e.request.id for e in plan.entries] == [rs[2].id, rs[3].id]
+    small.commit(np.full(2, EOS, dtype=np.int32))
+    small.remove_request(rs[2])
+    small.remove_request(rs[3])
+    small.check_invariants()
+    assert small.free_blocks == 5
+
+
 def test_decode_advance_reference():
     import torch
     from onnxruntime_genai_b200 import ops
