@@ -232,6 +232,40 @@ def dequantize_mxfp4(packed: torch.Tensor, scale_codes: torch.Tensor, N: int, K:
     return (val.view(N, K // block, block) * scale[..., None]).view(N, K)
 
 
+def quantize_fp8_rows(w: torch.Tensor):
+    """FP8 e4m3 weights with one scale per output row: (uint8 view of float8_e4m3fn [N, K], fp32 scale [N, 1])."""
+    scale = (w.float().abs().amax(1, keepdim=True) / 448.0).clamp(min=1e-12)
+    return (w.float() / scale).to(torch.float8_e4m3fn).view(torch.uint8), scale
+
+
+def quantize_nvfp4(w: torch.Tensor):
+    """NVFP4: e2m1 codes with an e4m3 scale per block of 16 along K and one fp32 global scale.
+    Returns (codes uint8 [N, K/2], low nibble = even k; uint8 view of the e4m3 scales [N, K/16]; global scale fp32 [1])."""
+    N, K = w.shape
+    assert K % 16 == 0
+    wf = w.float()
+    glob = (wf.abs().amax() / (6.0 * 448.0)).clamp(min=1e-12)
+    wb = wf.view(N, K // 16, 16)
+    sc = (wb.abs().amax(-1) / 6.0 / glob).to(torch.float8_e4m3fn)
+    eff = (sc.float() * glob).clamp(min=1e-20)
+    v = (wb / eff[..., None]).clamp(-6.0, 6.0)
+    grid = torch.tensor(_FP4_VALUES, dtype=torch.float32)
+    idx = (v.abs()[..., None] - grid).abs().argmin(-1)
+    codes = (idx + 8 * ((v < 0) & (idx > 0)).long()).to(torch.uint8).view(N, K)
+    return (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous(), sc.view(torch.uint8), glob.reshape(1)
+
+
+def dequantize_nvfp4(packed: torch.Tensor, scales_e4m3: torch.Tensor, global_scale: torch.Tensor) -> torch.Tensor:
+    """Inverse of quantize_nvfp4: fp32 [N, K]."""
+    pk = torch.as_tensor(packed)
+    N, K = pk.shape[0], pk.shape[1] * 2
+    codes = torch.stack([pk & 0xF, pk >> 4], dim=-1).view(N, K).long()
+    grid = torch.tensor(_FP4_VALUES, dtype=torch.float32)
+    val = torch.where(codes >= 8, -grid[codes & 7], grid[codes & 7])
+    sc = torch.as_tensor(scales_e4m3).view(torch.float8_e4m3fn).float().view(N, K // 16) * torch.as_tensor(global_scale).float().reshape(())
+    return (val.view(N, K // 16, 16) * sc[..., None]).view(N, K)
+
+
 # ---------------------------------------------------------------------------------------------- export
 class _Writer:
     def __init__(self, out_dir: str, precision: str, synthetic: bool, seed: int, std: float, filename: str = "model.onnx"):
@@ -275,7 +309,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                  filename: str = "model.onnx", write_config: bool = True, speculative: Optional[dict] = None,
                  draft_dir_entry: Optional[dict] = None, num_blocks: Optional[int] = None,
                  max_scheduled_tokens: Optional[int] = None, context_length: Optional[int] = None,
-                 int4_tied_embeddings: bool = False) -> str:
+                 int4_tied_embeddings: bool = False, linear_format: str = "") -> str:
     """Writes a checkpoint directory.  With state_dict=None the weights are random N(0, std) from `seed`."""
     os.makedirs(out_dir, exist_ok=True)
     if precision not in ("fp32", "fp16", "bf16", "int4"):
@@ -305,7 +339,23 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
 
     def put_linear(base: str, node_name: str, src_names, inp: str, out: str, N: int, K: int):
         """A linear layer y = x @ W^T from one or more stacked [n_i, K] canonical weights."""
-        if precision == "int4" and synthetic_weights:
+        if linear_format in ("fp8", "nvfp4") and not synthetic_weights:
+            # block-quantised float formats (linear_format option): FP8 e4m3 rows or NVFP4 blocks of 16
+            w = torch.cat([get(n).float() for n in src_names], dim=0)
+            if linear_format == "fp8":
+                q8, sc = quantize_fp8_rows(w)
+                W.add_array(base + ".fp8_weight", q8.numpy(), op.FLOAT8E4M3FN)
+                W.add_array(base + ".fp8_weight_scale", sc.numpy(), op.FLOAT)
+                W.node("MatMulBlockQuantizedFp8Weight", node_name, [inp, base + ".fp8_weight", base + ".fp8_weight_scale"], [out],
+                       domain="com.microsoft", block_size=K)
+            else:
+                codes, sc, glob = quantize_nvfp4(w)
+                W.add_array(base + ".nvfp4_weight", codes.numpy(), op.UINT8)
+                W.add_array(base + ".nvfp4_weight_scale", sc.numpy(), op.FLOAT8E4M3FN)
+                W.add_array(base + ".nvfp4_weight_scale_2", glob.numpy(), op.FLOAT)
+                W.node("MatMulBlockQuantizedFp4Weight", node_name, [inp, base + ".nvfp4_weight", base + ".nvfp4_weight_scale",
+                                                                    base + ".nvfp4_weight_scale_2"], [out], domain="com.microsoft", block_size=16)
+        elif precision == "int4" and synthetic_weights:
             # descriptors only: the loader draws the float weight on the device and quantises it there (RTN block-32)
             nb = K // 32
             for suffix, shp, dt, kind in (("weight_Q4", (N, nb, 16), op.UINT8, "q4_weight"), ("weight_scales", (N * nb,), op.FLOAT16, "q4_scales"),
@@ -939,7 +989,7 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         block_size=int(extra.get("paged_block_size", 16)), max_batch_size=int(extra.get("max_batch_size", 64)),
         int4_symmetric=bool(int(extra.get("int4_is_symmetric", 0))), synthetic_weights=bool(int(extra.get("synthetic_weights", 0))),
         filename=extra.get("filename", "model.onnx"), context_length=int(extra["context_length"]) if "context_length" in extra else None,
-        int4_tied_embeddings=bool(int(extra.get("int4_tied_embeddings", 0))))
+        int4_tied_embeddings=bool(int(extra.get("int4_tied_embeddings", 0))), linear_format=str(extra.get("linear_format", "")))
 
 
 def main(argv=None):

@@ -131,7 +131,7 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all(f"{fa}/attn/"))
     a.o_bias = g.by_name.get(f"{fa}/attn/o_proj/Add") is not None
     a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
-    types = ["conv" if g.find(f"/model/layers.{i}/conv/in_proj/", ops=["MatMul", "MatMulNBits"]) is not None else "full_attention"
+    types = ["conv" if g.find(f"/model/layers.{i}/conv/in_proj/", ops=LINEAR_OPS) is not None else "full_attention"
              for i in range(a.num_layers)]
     if "conv" in types:
         a.layer_types = types
@@ -141,10 +141,10 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         a.conv_bias = g.has_init(f"model.layers.{first}.conv.conv.bias")
     a.cross_attention = g.find("/model/layers.0/cross_attn/") is not None
     if a.cross_attention:
-        a.encoder_hidden_size = _linear_shape(g, g.find("/model/layers.0/cross_attn/kv_proj/", ops=["MatMul", "MatMulNBits"]))[1]
+        a.encoder_hidden_size = _linear_shape(g, g.find("/model/layers.0/cross_attn/kv_proj/", ops=LINEAR_OPS))[1]
     a.parallel_block = g.find("/model/layers.0/parallel_block/") is not None
     a.learned_positions = g.by_name.get("/model/pos_embed/Gather") is not None
-    fc1 = g.find("/model/layers.0/mlp/fc1/", ops=["MatMul", "MatMulNBits"])
+    fc1 = g.find("/model/layers.0/mlp/fc1/", ops=LINEAR_OPS)
     if fc1 is not None:
         a.mlp_gated = False
         a.intermediate_size = _linear_shape(g, fc1)[0]
@@ -170,11 +170,11 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
             a.intermediate_size = shp[2] if moe.op_type == "QMoE" else shp[1] // 2
             a.mlp_bias = True
     else:
-        gu = g.find("/model/layers.0/mlp/gate_up_proj/", ops=["MatMul", "MatMulNBits"])
+        gu = g.find("/model/layers.0/mlp/gate_up_proj/", ops=LINEAR_OPS)
         if gu is not None:
             a.intermediate_size = _linear_shape(g, gu)[0] // 2
         else:
-            gp = g.find("/model/layers.0/mlp/gate_proj/", ops=["MatMul", "MatMulNBits"])
+            gp = g.find("/model/layers.0/mlp/gate_proj/", ops=LINEAR_OPS)
             if gp is not None:
                 a.intermediate_size = _linear_shape(g, gp)[0]
         if fc1 is None:
@@ -194,10 +194,19 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
     return a
 
 
+LINEAR_OPS = ["MatMul", "MatMulNBits", "MatMulBlockQuantizedFp8Weight", "MatMulBlockQuantizedFp4Weight"]
+
+
 def _linear_shape(g: GraphView, node):
-    """(N, K) of a MatMul / MatMulNBits node."""
+    """(N, K) of a linear node."""
     if node.op_type == "MatMulNBits":
         return int(node.attrs["N"]), int(node.attrs["K"])
+    if node.op_type == "MatMulBlockQuantizedFp8Weight":
+        n, k = g.lm.info(node.inputs[1]).dims
+        return n, k
+    if node.op_type == "MatMulBlockQuantizedFp4Weight":
+        n, k2 = g.lm.info(node.inputs[1]).dims
+        return n, 2 * k2
     k, n = g.lm.info(node.inputs[1]).dims
     return n, k
 
@@ -215,6 +224,17 @@ def _linear_weight(g: GraphView, node, dtype, device, rows: Optional[slice] = No
         s = g.tensor(node.inputs[2], device=src_dev)
         zp = g.tensor(node.inputs[3], device=src_dev) if len(node.inputs) > 3 and node.inputs[3] else None
         w = dequantize_int4_block32(q, s, zp, N, K, bs)
+    elif node.op_type == "MatMulBlockQuantizedFp8Weight":
+        # FP8 e4m3 weight [N, K] with one fp32 scale per output row (or one for the matrix), expanded at load: the GEMMs run
+        # in bf16 on the dequantised weight; the optional activation scale (input 3) is not used
+        # (reference: src/python/py/models/builders/base.py:1878-1917)
+        w8 = g.tensor(node.inputs[1]).view(torch.float8_e4m3fn).float()
+        w = w8 * g.tensor(node.inputs[2]).float().reshape(-1, 1)
+    elif node.op_type == "MatMulBlockQuantizedFp4Weight":
+        # NVFP4: e2m1 codes [N, K/2] (low nibble = even k), e4m3 scale per block of 16 [N, K/16], one fp32 global scale
+        # (reference: src/python/py/models/builders/base.py:1919-1949); expanded at load
+        from .builder import dequantize_nvfp4
+        w = dequantize_nvfp4(g.tensor(node.inputs[1]), g.tensor(node.inputs[2]), g.tensor(node.inputs[3]))
     else:
         w = g.tensor(node.inputs[1], device=device if g.lm.info(node.inputs[1]).ext_location and
                      g.lm.info(node.inputs[1]).ext_location.startswith("synthetic:") else "cpu").t()
@@ -284,7 +304,7 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
 
     def linear_node(prefix: str, *names):
         for nm in names:
-            n = g.find(prefix + nm + "/", ops=["MatMul", "MatMulNBits"])
+            n = g.find(prefix + nm + "/", ops=LINEAR_OPS)
             if n is not None:
                 return n
         return None
@@ -557,7 +577,7 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
     model.final_norm_w = _vec(g, fin.inputs[2 if len(fin.inputs) >= 3 else 1], dtype, device)
     if arch.layernorm and len(fin.inputs) > 3:
         model.final_norm_b = _vec(g, fin.inputs[3], dtype, device)
-    head = g.find("/lm_head/", ops=["MatMul", "MatMulNBits"])
+    head = g.find("/lm_head/", ops=LINEAR_OPS)
     V = arch.vocab_size
     if tpn > 1:
         per = (V + tpn - 1) // tpn

@@ -522,6 +522,40 @@ def test_static_batching_runs_fixed_batches_to_completion():
     assert small.free_blocks == 5
 
 
+def test_engine_with_a_static_batching_config(model, tmp_path):
+    """`engine.static_batching` in genai_config.json selects the fixed-batch policy; outputs equal the closed form and no
+    request joins a running batch."""
+    import json
+    import os
+    import shutil
+    d = str(tmp_path / "static")
+    shutil.copytree(model.config.config_path, d)
+    cfg_path = os.path.join(d, "genai_config.json")
+    with open(cfg_path) as f:
+        cfg = json.load(f)
+    cfg["engine"] = {"static_batching": {"max_batch_size": 4}}
+    with open(cfg_path, "w") as f:
+        json.dump(cfg, f)
+    m = og.Model(d)
+    engine, ex = make_engine(m, num_blocks=64)
+    assert engine.options.static_batching
+    prompts = [[3 + i, 9, 4 + i] for i in range(6)]
+    reqs = [request(m, p, max_length=12) for p in prompts]
+    for r in reqs:
+        engine.add_request(r)
+    outs = run_all(engine, reqs)
+    assert outs == [closed_form(p, 12) for p in prompts]
+    first = {c[0] for c in ex.calls[0]}
+    assert len(first) == 4                              # four requests start together ...
+    started = set()
+    for call in ex.calls:
+        ids = {c[0] for c in call}
+        if ids & first:
+            assert ids <= first                         # ... and nobody joins while any of them still runs
+        started |= ids
+    assert len(started) == 6
+
+
 def test_decode_advance_reference():
     import torch
     from onnxruntime_genai_b200 import ops

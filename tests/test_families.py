@@ -415,3 +415,41 @@ def test_multimodal_rope_positions(tmp_path):
     p3b = np.concatenate([p3, np.full((3, 1), 9, dtype=np.int32)], axis=1)
     want = dense_logits(arch, sd, seq, positions3=p3b)[-1].numpy()
     np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=4e-4)
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "nvfp4"])
+def test_block_quantised_float_linears_load_expanded(fmt, tmp_path):
+    """MatMulBlockQuantizedFp8Weight (e4m3 rows with a scale per output row) and MatMulBlockQuantizedFp4Weight (NVFP4: e2m1
+    codes, e4m3 scale per block of 16, one global scale) are read and expanded at load: logits equal the dense model on
+    the dequantised weights."""
+    from onnxruntime_genai_b200.models.builder import dequantize_nvfp4, quantize_fp8_rows, quantize_nvfp4
+    arch = ArchConfig(**BASE)
+    sd = random_state_dict(arch, seed=17, std=0.1)
+    d = str(tmp_path)
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd, linear_format=fmt)
+    model = og.Model(d)
+    sd_q = dict(sd)
+    for k, v in sd.items():
+        if k.endswith("_proj.weight") or k == "lm_head.weight":
+            if fmt == "fp8":
+                q8, sc = quantize_fp8_rows(v)
+                sd_q[k] = q8.view(torch.float8_e4m3fn).float() * sc
+                assert float((sd_q[k] - v).abs().max()) < float(v.abs().max()) * 0.07
+            else:
+                sd_q[k] = dequantize_nvfp4(*quantize_nvfp4(v))
+                assert float((sd_q[k] - v).abs().mean()) < float(v.abs().mean()) * 0.15
+    if fmt == "nvfp4":
+        # packed projections (qkv, gate/up) are quantised as one stacked matrix: one global scale for the stack
+        for i in range(arch.num_layers):
+            for names in (("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), ("mlp.gate_proj", "mlp.up_proj")):
+                keys = [f"model.layers.{i}.{n}.weight" for n in names]
+                deq = dequantize_nvfp4(*quantize_nvfp4(torch.cat([sd[k] for k in keys], 0)))
+                for k, part in zip(keys, torch.split(deq, [sd[k].shape[0] for k in keys], 0)):
+                    sd_q[k] = part
+    prompt = np.random.RandomState(4).randint(0, arch.vocab_size - 1, size=(1, 9)).astype(np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=16)
+    g = og.Generator(model, p)
+    g.append_tokens(prompt)
+    want = dense_logits(arch, sd_q, prompt[0].tolist())[-1].numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
