@@ -22,7 +22,7 @@ from typing import Any, Dict, List, Optional
 import numpy as np
 import torch
 
-from . import ops
+from . import ops, telemetry
 from .models.decoder import PagedKVCache, StepInputs
 from .native_loader import native
 
@@ -158,9 +158,16 @@ class Model:
             raise RuntimeError(f"Unsupported model type: {self.type}")
         self.dtype = torch.bfloat16 if want_cuda else torch.float32
         from .models.loader import load_decoder
+        t_load = time.perf_counter()
         with _Trace("model", "load"):
             self.decoder = load_decoder(c.config_path, c, self.device, self.dtype, tp)
             self.draft = load_decoder(c.config_path, c, self.device, self.dtype, tp, decoder=c.draft) if c.draft else None
+        if telemetry.enabled():
+            a = self.decoder.arch
+            telemetry.log_event("ModelLoad", {"model_type": self.type, "device": self.device_type, "layers": a.num_layers,
+                                              "hidden_size": a.hidden_size, "vocab_size": a.vocab_size, "dtype": str(self.dtype).replace("torch.", ""),
+                                              "load_ms": round((time.perf_counter() - t_load) * 1e3, 1),
+                                              "model_dir_hash": telemetry.redact_path(c.config_path)})
         # Multimodal components (reference: src/models/multi_modal.cpp:104-160, src/models/whisper.cpp:19-60): the audio or
         # vision encoder named by the config's `encoder` / `vision` section.
         tree = json.loads(c.to_json()).get("model", {})
@@ -514,6 +521,7 @@ class Generator:
         self._logits: Optional[torch.Tensor] = None
         self._fresh = False
         self._started = False
+        self._telemetry = telemetry.GenerationTimer()
         self._seed = s["random_seed"] if s["random_seed"] >= 0 else int.from_bytes(os.urandom(4), "little")
         self._guidance = None
         if params.guidance_type:
@@ -533,6 +541,8 @@ class Generator:
         with _Trace("generator", "append_tokens"):
             if isinstance(tokens, Tensor):
                 tokens = tokens.as_numpy()
+            if telemetry.enabled():
+                self._telemetry.on_prompt(np.asarray(tokens).size)
             arr = np.asarray(tokens, dtype=np.int32)
             if arr.ndim == 1:
                 arr = arr.reshape(1, -1)
@@ -617,8 +627,12 @@ class Generator:
                 raise RuntimeError("generate_next_token called before append_tokens")
             if self._strategy is not None:
                 self._strategy.step()
-                return
-            self._standard_step()
+            else:
+                self._standard_step()
+        if telemetry.enabled():
+            self._telemetry.on_token()
+            if self.search.is_done:
+                self._telemetry.finish(self.model.type, self.model.device_type, self.search_opts.get("batch_size", 1) if isinstance(self.search_opts, dict) else 1)
 
     def _ensure_logits(self):
         if not self._fresh:
