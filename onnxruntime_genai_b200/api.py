@@ -360,7 +360,21 @@ class SequenceState:
                        **self._cross_fields(rows_used))
         if mrope:
             s.positions3 = torch.from_numpy(np.ascontiguousarray(np.concatenate(p3, axis=1))).to(dev)
-        return self.decoder.forward(s, self.kv), rows_used
+        heads = getattr(self, "alignment_heads", None)
+        if heads and self.cross is not None:
+            s.cross_qk_heads, s.cross_qk_out = heads, [None] * len(heads)
+        out = self.decoder.forward(s, self.kv)
+        if s.cross_qk_out:
+            # per row: one [heads, frames] slab per token fed so far (prompt tokens included)
+            qk = torch.stack(s.cross_qk_out, dim=1).cpu()                           # [tokens, heads, frames]
+            for j, r in enumerate(rows_used):
+                self.cross_qk_rows[r].extend(qk[cu[j]:cu[j + 1]])
+        return out, rows_used
+
+    def set_alignment_heads(self, heads) -> None:
+        """heads: [(layer, head)] whose cross-attention scores are recorded from now on (`Generator.get_output("cross_qk")`)."""
+        self.alignment_heads = [(int(l), int(h)) for l, h in heads]
+        self.cross_qk_rows = [[] for _ in range(self.rows)]
 
     # ---- single-token decode steps replayed from CUDA graphs (one graph per power-of-two bound on the KV length)
     def graph_ok(self) -> bool:
@@ -371,6 +385,8 @@ class SequenceState:
             return False   # the unfused expert loop reads counts back to the host
         if any(self.rope_delta):
             return False   # rotary positions differ from the cache positions (multimodal RoPE after an image)
+        if getattr(self, "alignment_heads", None):
+            return False   # the recorded cross-attention scores are gathered with host-side shapes
         return dec.tp.size == 1
 
     def run_decode_graph(self, last_tokens: List[int]) -> torch.Tensor:
@@ -478,10 +494,15 @@ class SequenceState:
             self.block_table.copy_(torch.from_numpy(self._tbl))
             self._tbl_dirty = False
 
+    def _reorder_cross_qk(self, src_rows: List[int]):
+        if getattr(self, "alignment_heads", None):
+            self.cross_qk_rows = [list(self.cross_qk_rows[s]) for s in src_rows]
+
     def reorder_rows(self, src_rows: List[int]):
         """Beam search: row r continues from the cache of row src_rows[r].  Only the block table is permuted; blocks are
         shared between the rows that descend from the same hypothesis and copied when one of them writes into a shared
         block (`_own_blocks`), so a step moves at most one block per row instead of whole caches."""
+        self._reorder_cross_qk(src_rows)
         if self._tbl is None:
             if all(r == s for r, s in enumerate(src_rows)):
                 return
@@ -785,6 +806,13 @@ class Generator:
             return self.get_logits()
         if name == "hidden_states":
             return self.model.decoder.last_hidden.detach().float().cpu().numpy()
+        if name == "cross_qk":
+            # [rows, alignment heads, tokens fed so far, encoder frames]: scaled query-key scores before the softmax
+            rows = getattr(self.state, "cross_qk_rows", None)
+            if not rows or not rows[0]:
+                raise RuntimeError("cross_qk: set the alignment_heads input (an int32 [n, 2] tensor of (layer, head)) before the tokens")
+            n = min(len(r) for r in rows)
+            return torch.stack([torch.stack(r[:n], dim=1) for r in rows]).numpy()
         raise RuntimeError(f"unknown model output: {name}")
 
     def set_inputs(self, named: NamedTensors):
@@ -862,6 +890,12 @@ class Generator:
     def set_model_input(self, name: str, tensor):
         self._extra_inputs = getattr(self, "_extra_inputs", {})
         self._extra_inputs[name] = tensor
+        if name == "alignment_heads":
+            arr = np.asarray(tensor.as_numpy() if isinstance(tensor, Tensor) else tensor).reshape(-1, 2)
+            a = self.model.arch
+            if arr.size and (arr[:, 0].max() >= a.num_layers or arr[:, 1].max() >= a.num_heads or arr.min() < 0):
+                raise RuntimeError("alignment_heads: (layer, head) out of range")
+            self.state.set_alignment_heads(arr.tolist())
 
     def snapshot_state(self):
         """Marks the current state as a point speculative decoding may roll back to (reference:

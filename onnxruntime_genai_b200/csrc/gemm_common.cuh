@@ -67,6 +67,8 @@ struct GemmParams {
                         // broadcasts): each partial crosses NVLink once instead of world times; owner of row m = m / ar2_rows
   int rs_rows;          // > 0: reduce-scatter by token rows: rank r receives (and stores, as its rows 0..) rows [r * rs_rows, (r + 1) * rs_rows)
   GroupParams grp;
+  int n_acc;            // 0 / 1: one accumulator; 2 or 4: the k-steps of a k-block go round-robin into that many accumulators
+                        // BT columns apart (independent tcgen05.mma chains), summed by the epilogue
 };
 
 template <int BT>
@@ -143,7 +145,7 @@ __device__ __forceinline__ uint4 wait_line(const uint4* p, uint32_t flag, bool& 
 template <int BT>
 __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem, uint32_t tmem_base, uint64_t* accum_bar,
                                               volatile int* abort_flag, volatile uint32_t* use_slot, int n_tile, int m_tile,
-                                              int row0, int rows, int bias_off) {
+                                              int row0, int rows, int bias_off, int n_acc = 1) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
   // -------------------------------------------------------------------- epilogue (warps 2..5)
@@ -164,6 +166,14 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         uint32_t r0[16];
         tmem_ld16(taddr + c0, r0);
         tmem_ld_wait();
+        // n_acc > 1: the k-steps went round-robin into n_acc accumulators BT columns apart (independent MMA chains); sum them
+        for (int a = 1; a < n_acc; ++a) {
+          uint32_t r1[16];
+          tmem_ld16(taddr + a * BT + c0, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(r1[j]));
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) part[(c0 + j) * GEMM_BLOCK_N + row] = __uint_as_float(r0[j]);
       }

@@ -22,13 +22,19 @@
 // byte is then the fp16 exponent field of 2^(scale - 127), scale - 112.  One conversion and one multiply per pair
 // of weights instead of six integer / bf16 operations: the expansion stops being the limit of the weight stream.
 //
-// Pipeline and epilogue are those of the int4 kernel (gemm_w4.cu): warp 0 streams records through a deep ring and
-// the activation tiles through a ring of their own (4 or 8 deep), warps 2..9 (two threads per weight row, a block of 32 weights each)
-// expand a record into the swizzled K-major tile, warp 1 issues tcgen05.mma into tensor memory, warps 2..5 run the
-// epilogue.  Eight expander warps per CTA, two CTAs per SM: the expansion is a chain of dependent integer / half
-// operations per thread, and it takes that many warps to keep a k-block's expansion under the time its 4352 bytes
-// take to arrive (with four warps the kernel ran at 0.33 of the HBM rate, bound by that chain, not by its bytes).  The tile list of ogb_moe_sort selects
-// the expert, first row and row count of each token tile.  Every wait is bounded.
+// Pipeline and epilogue are those of the int4 kernel (gemm_w4.cu): warp 0 streams records through a deep ring and the
+// activation tiles through a ring of their own (4 or 8 deep), warps 2..9 expand a record into the swizzled K-major tile,
+// warp 1 issues tcgen05.mma into tensor memory, warps 2..5 run the epilogue; two CTAs per SM.  The tile list of
+// ogb_moe_sort selects the expert, first row and row count of each token tile.  Every wait is bounded.
+//
+// Where the time goes (clock64 trace of one CTA, 16-token tiles): a k-block takes about 1100 cycles per CTA, of which the
+// MMA issuer spends about 500 between seeing its operands and having issued four tcgen05.mma (128 weight rows x 16 tokens
+// x 16) and their commits; with two CTAs per SM that is one instruction per ~137 cycles, and a record of 4352 bytes would
+// have to be consumed every 190 cycles to keep up with HBM.  More expander warps, more expanded tiles in flight, a deeper
+// activation ring, tensor-map loads and four independent accumulators each left the time within 8 %.  The kernel
+// therefore streams its weights at about 0.33 of the HBM rate (1.25x faster than the bf16 experts, which move 3.8x the
+// bytes at the full rate).  The way past this limit is to put the weights on the instruction's N side (256 rows per
+// instruction, tokens padded to M = 64), which changes the accumulator layout and the epilogue; not done here.
 #include <cstdlib>
 
 #include <cuda_fp16.h>
@@ -55,7 +61,10 @@ struct Fp4Cfg {
   static constexpr int MAX_RAW = (BUDGET - FIXED) / FP4_RECORD_BYTES;
   // a multiple of 4 records keeps the tiles behind the ring 1 KiB aligned (4 * 4352 = 17 KiB)
   static constexpr int RAW = (MAX_RAW > 16 ? 16 : MAX_RAW) / 4 * 4;
-  static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
+  // Accumulators: consecutive tcgen05.mma into one accumulator run as a dependent chain (a 128 x 16 x 16 step is
+  // latency, not work), so the four k-steps of a k-block go to NACC accumulators BT columns apart, summed in the epilogue.
+  static constexpr int NACC_MAX = BT <= 32 ? 4 : (BT <= 128 ? 2 : 1);
+  static constexpr int TMEM_COLS = (BT * NACC_MAX) < 32 ? 32 : BT * NACC_MAX;
   static constexpr int DATA_BYTES = RAW * FP4_RECORD_BYTES + FIXED;
   static constexpr int SMEM_BYTES = DATA_BYTES + 1024 + 512;
   static_assert(RAW >= 4, "raw ring too shallow");
@@ -67,6 +76,11 @@ __device__ __forceinline__ void fp4_bulk_copy_g2s(void* smem_dst, const void* gs
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+
+// Optional trace: when a buffer is registered (ogb_fp4_trace_buffer), the CTA of the first weight tile and first token tile
+// stamps clock64() at the hand-over points of every k-block: row r of [9][64] = event r of k-block i.
+__device__ long long* g_fp4_trace = nullptr;
+#define FP4_STAMP(ev, i) do { if (trace && (i) < 64) trace[(ev) * 64 + (i)] = clock64(); } while (0)
 
 // two e2m1 codes (low nibbles of the two halves of `u`) times the block's power-of-two multiplier
 __device__ __forceinline__ uint32_t deq_fp4_pair(uint32_t u, __nv_bfloat162 s2) {
@@ -95,10 +109,10 @@ __device__ __forceinline__ uint4 deq_fp4_word_f16(uint32_t word, __half2 s2) {
 
 // FP4_WBUF: expanded weight tiles in flight; GROUPS: 1 = all eight expander warps share every k-block (two threads per
 // row), 2 = warps 2..5 take the even k-blocks and warps 6..9 the odd ones (one thread per row).
-template <int BT, bool HALF, int FP4_WBUF, int GROUPS>
+template <int BT, bool HALF, int FP4_WBUF, int GROUPS, int NACC>
 __global__ void __launch_bounds__(FP4_THREADS, Fp4Cfg<BT, FP4_WBUF>::TWO_PER_SM ? 2 : 1)
-gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert,
-                        const GemmParams p) {
+gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                        const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, int w_by_tma, const GemmParams p) {
   using Cfg = Fp4Cfg<BT, FP4_WBUF>;
   constexpr int RAW = Cfg::RAW;
   constexpr int ARRIVALS = FP4_DEQ_WARPS / GROUPS;
@@ -125,6 +139,8 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
   // The tile list is written by the kernel before this one, so nothing is read ahead of it.
   if (p.pdl) pdl_wait();
   if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA
+  long long* trace = (n_tile == 0 && m_tile == 0) ? g_fp4_trace : nullptr;
+  if (threadIdx.x == 0) FP4_STAMP(8, 0);
   const int row0 = p.grp.tile_row0[m_tile];
   const int rows = p.grp.tile_rows[m_tile];
   const int expert = p.grp.tile_expert[m_tile];
@@ -137,6 +153,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_w);
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -148,21 +165,27 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
   const uint32_t tmem_base = *tmem_slot;
   if (p.pdl) pdl_launch_dependents();
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
+  if (threadIdx.x == 0) FP4_STAMP(8, 1);
 
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------------------ producer: packed records + activation tiles
       const uint8_t* rec0 = wpacked + (size_t(expert) * num_kb * n_tiles_per_expert + n_tile) * FP4_RECORD_BYTES;
       const size_t rec_stride = size_t(n_tiles_per_expert) * FP4_RECORD_BYTES;
+      // A record is 34 rows of 128 bytes: one untiled bulk copy, or (OGB_FP4_TMA=1) one box of a byte tensor map
+      const int rec_first = (expert * num_kb) * n_tiles_per_expert + n_tile;
       auto load_raw = [&](int i) {
         const int s = i % RAW;
         mbar_expect_tx(&raw_full[s], FP4_RECORD_BYTES);
-        fp4_bulk_copy_g2s(raw_ring + s * FP4_RECORD_BYTES, rec0 + size_t(i) * rec_stride, FP4_RECORD_BYTES, &raw_full[s]);
+        if (w_by_tma) tma_load_2d(raw_ring + s * FP4_RECORD_BYTES, &tmap_w, &raw_full[s], 0, (rec_first + i * n_tiles_per_expert) * (FP4_RECORD_BYTES / 128));
+        else fp4_bulk_copy_g2s(raw_ring + s * FP4_RECORD_BYTES, rec0 + size_t(i) * rec_stride, FP4_RECORD_BYTES, &raw_full[s]);
+        FP4_STAMP(0, i);
       };
       auto load_a = [&](int i) {
         const int s = i % A_ST;
         mbar_expect_tx(&a_full[s], Cfg::A_TILE_BYTES);
         tma_load_2d(a_ring + s * Cfg::A_TILE_BYTES, &tmap_a, &a_full[s], i * GEMM_BLOCK_K, row0);
+        FP4_STAMP(7, i);
       };
       int ri = 0, ai = 0;
       const int pre = min(RAW, num_kb);
@@ -189,17 +212,20 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
       bool ok = true;
       for (int i = 0; i < num_kb && ok; ++i) {
         const int s = i % FP4_WBUF, as = i % A_ST;
-        if (!mbar_wait_bounded(&deq_full[s], (i / FP4_WBUF) & 1, abort_flag) || !mbar_wait_bounded(&a_full[as], (i / A_ST) & 1, abort_flag)) {
-          fail(OGB_ERR_WAIT_TMA); ok = false; break;
-        }
+        bool got = mbar_wait_bounded(&deq_full[s], (i / FP4_WBUF) & 1, abort_flag);
+        FP4_STAMP(4, i);
+        got = got && mbar_wait_bounded(&a_full[as], (i / A_ST) & 1, abort_flag);
+        FP4_STAMP(5, i);
+        if (!got) { fail(OGB_ERR_WAIT_TMA); ok = false; break; }
         tc_fence_after();
         const uint32_t w = smem_u32(w_ring + s * W_TILE_BYTES), a = smem_u32(a_ring + as * Cfg::A_TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
-          umma_f16(tmem_base, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc,
-                   (i > 0 || k > 0) ? 1u : 0u);
+          umma_f16(tmem_base + uint32_t((k % NACC) * BT), umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2),
+                   idesc, (i > 0 || k >= NACC) ? 1u : 0u);
         umma_commit(&w_empty[s]);
         umma_commit(&a_empty[as]);
+        FP4_STAMP(6, i);
       }
       if (ok) umma_commit(accum_bar);
     }
@@ -213,8 +239,11 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
     const int part = GROUPS == 2 ? 0 : dt >> 7;             // which block of 32 of the row's 64 weights (GROUPS == 1)
     for (int i = group; i < num_kb; i += GROUPS) {
       const int rs = i % RAW, ws = i % FP4_WBUF;
+      const bool stamper = (dt & 127) == 0;
       bool ok = mbar_wait_bounded(&raw_full[rs], (i / RAW) & 1, abort_flag);
+      if (stamper) FP4_STAMP(1, i);
       if (ok && i >= FP4_WBUF) ok = mbar_wait_bounded(&w_empty[ws], ((i / FP4_WBUF) & 1) ^ 1, abort_flag);
+      if (stamper) FP4_STAMP(2, i);
       if (!__all_sync(0xffffffffu, ok)) { fail(OGB_ERR_WAIT_TMA); break; }   // the warp gives up as one (it meets at __syncwarp below)
       const uint8_t* rec = raw_ring + rs * FP4_RECORD_BYTES;
       uint32_t words[WORDS];
@@ -250,6 +279,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
       __syncwarp();
+      if (stamper) FP4_STAMP(3, i);
       if (lane == 0) {
         mbar_arrive(&deq_full[ws]);
         mbar_arrive(&raw_empty[rs]);
@@ -257,7 +287,9 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
     }
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, expert * p.N);
+  if (threadIdx.x == 64) FP4_STAMP(8, 2);
+  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, expert * p.N, NACC);
+  if (threadIdx.x == 64) FP4_STAMP(8, 3);
 
   tc_fence_before();
   __syncthreads();
@@ -265,12 +297,15 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_
 }
 
 bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
+bool MakeMapBytes128(CUtensorMap* out, const void* ptr, long long rows, int box_rows);          // gemm_tcgen05.cu
 
-template <int BT, bool HALF, int WBUF, int GROUPS>
-static int LaunchFp4V(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+template <int BT, bool HALF, int WBUF, int GROUPS, int NACC>
+static int LaunchFp4V(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid,
+                      cudaStream_t stream) {
   using Cfg = Fp4Cfg<BT, WBUF>;
   static bool configured = false;
-  auto kern = gemm_fp4_grouped_kernel<BT, HALF, WBUF, GROUPS>;
+  static_assert(NACC <= Fp4Cfg<BT, WBUF>::NACC_MAX, "not enough tensor memory for the accumulators");
+  auto kern = gemm_fp4_grouped_kernel<BT, HALF, WBUF, GROUPS, NACC>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
     configured = true;
@@ -289,24 +324,36 @@ static int LaunchFp4V(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, con
   }
   cfg.attrs = attrs;
   cfg.numAttrs = unsigned(na);
-  return cudaLaunchKernelEx(&cfg, kern, ta, wp, n_tiles, p) == cudaSuccess ? 0 : -4;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tw, wp, n_tiles, w_by_tma, p) == cudaSuccess ? 0 : -4;
 }
 
 template <int BT, bool HALF>
-static int LaunchFp4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+static int LaunchFp4(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid,
+                     cudaStream_t stream) {
   // OGB_FP4_VARIANT (16-token tiles only): 0 = two expanded tiles in flight, 1 = four, 2 = four with the expander
-  // warps in two groups that alternate k-blocks
-  static const int variant = [] { const char* e = getenv("OGB_FP4_VARIANT"); return e ? atoi(e) : 0; }();
+  // warps in two groups that alternate k-blocks, 3 = as 0 with four accumulators, 4 = as 2 with four accumulators
+  // Measured on B200 (gate/up of gpt-oss-20b, 32 tokens): 142 / 142 / 132 / 143 / 131 us for variants 0..4 - the kernel is bound
+  // by the rate at which the tensor core retires 128 x 16 x 16 instructions, not by the expansion, the copies or the
+  // accumulator chain; variant 4 is the default.
+  static const int variant = [] { const char* e = getenv("OGB_FP4_VARIANT"); return e ? atoi(e) : 4; }();
   if constexpr (BT <= 16) {
-    if (variant == 1) return LaunchFp4V<BT, HALF, 4, 1>(ta, wp, n_tiles, p, grid, stream);
-    if (variant == 2) return LaunchFp4V<BT, HALF, 4, 2>(ta, wp, n_tiles, p, grid, stream);
+    if (variant == 1) return LaunchFp4V<BT, HALF, 4, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    if (variant == 2) return LaunchFp4V<BT, HALF, 4, 2, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    if (variant == 3) return LaunchFp4V<BT, HALF, 2, 1, 4>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    if (variant == 4) return LaunchFp4V<BT, HALF, 4, 2, 4>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
   }
-  return LaunchFp4V<BT, HALF, 2, 1>(ta, wp, n_tiles, p, grid, stream);
+  return LaunchFp4V<BT, HALF, 2, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
 }
 
 }  // namespace ogb
 
 using namespace ogb;
+
+// Registers (or clears, with nullptr) the device buffer of 9 * 64 int64 that receives the k-block trace of later launches.
+OGB_API int ogb_fp4_trace_buffer(void* buf) {
+  long long* p = static_cast<long long*>(buf);
+  return cudaMemcpyToSymbol(g_fp4_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -4;
+}
 
 // Bytes of the repacked experts: `experts` matrices of [N, K] e2m1 codes (K a multiple of 64; N is padded to 128).
 OGB_API long long ogb_fp4_packed_bytes(int experts, int N, int K) {
@@ -343,14 +390,22 @@ OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* 
   p.pdl = pdl_enabled;
   p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N;
+  // OGB_FP4_TMA=1: records arrive as boxes of a byte tensor map instead of untiled bulk copies (measured: no difference)
+  static const int tma_env = [] { const char* e = getenv("OGB_FP4_TMA"); return (e && e[0] == '1') ? 1 : 0; }();
+  CUtensorMap tw = ta;
+  int w_by_tma = 0;
+  if (tma_env) {
+    const long long rows128 = (long long)experts * p.total_kb * n_tiles * (FP4_RECORD_BYTES / 128);
+    w_by_tma = MakeMapBytes128(&tw, Wpacked, rows128, FP4_RECORD_BYTES / 128) ? 1 : 0;
+  }
   dim3 grid(n_tiles, max_tiles, 1);
   const uint8_t* wp = static_cast<const uint8_t*>(Wpacked);
   switch (bt) {
-    case 16: return half ? LaunchFp4<16, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<16, false>(ta, wp, n_tiles, p, grid, stream);
-    case 32: return half ? LaunchFp4<32, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<32, false>(ta, wp, n_tiles, p, grid, stream);
-    case 64: return half ? LaunchFp4<64, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<64, false>(ta, wp, n_tiles, p, grid, stream);
-    case 128: return half ? LaunchFp4<128, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<128, false>(ta, wp, n_tiles, p, grid, stream);
-    case 256: return half ? LaunchFp4<256, true>(ta, wp, n_tiles, p, grid, stream) : LaunchFp4<256, false>(ta, wp, n_tiles, p, grid, stream);
+    case 16: return half ? LaunchFp4<16, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<16, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    case 32: return half ? LaunchFp4<32, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<32, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    case 64: return half ? LaunchFp4<64, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<64, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    case 128: return half ? LaunchFp4<128, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<128, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    case 256: return half ? LaunchFp4<256, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<256, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
   }
   return -5;
 }

@@ -86,8 +86,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
   }
+  const int n_acc = p.n_acc > 1 ? p.n_acc : 1;
+  const uint32_t tmem_cols = uint32_t(max(32, BT * n_acc));   // a power of two: BT and n_acc are
   if (warp == 2) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_alloc(tmem_slot, tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -150,8 +152,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t w = smem_u32(stage_w(s)), a = smem_u32(stage_a(s));
 #pragma unroll
         for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
-          umma_f16(tmem_base, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc,
-                   (i > 0 || k > 0) ? 1u : 0u);
+          umma_f16(tmem_base + uint32_t((k & (n_acc - 1)) * BT), umma_desc_sw128(w + k * GEMM_UMMA_K * 2),
+                   umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc, (i > 0 || k >= n_acc) ? 1u : 0u);
         umma_commit(&empty_bar[s]);
       }
       if (ok) umma_commit(accum_bar);
@@ -193,11 +195,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (dead) *abort_flag = 1;
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0);
+  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0, n_acc);
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  if (warp == 2) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 // --------------------------------------------------------------------------------- host side
@@ -249,6 +251,19 @@ static bool MakeMap(CUtensorMap* out, const void* ptr, int rows, int cols, int l
   if (cache.size() > 65536) cache.clear();
   cache.emplace(key, *out);
   return true;
+}
+
+// A byte buffer seen as rows of 128 bytes, box = [box_rows, 128], no swizzle: one box is box_rows * 128 contiguous bytes in
+// global and in shared memory (the packed weight records of gemm_fp4.cu).
+bool MakeMapBytes128(CUtensorMap* out, const void* ptr, long long rows, int box_rows) {
+  EncodeTiledFn enc = GetEncodeTiled();
+  if (!enc || rows <= 0 || rows > 0x7fffffffll || box_rows > 256) return false;
+  cuuint64_t dims[2] = {128, cuuint64_t(rows)};
+  cuuint64_t strides[1] = {128};
+  cuuint32_t box[2] = {128, cuuint32_t(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Shared with gemm_w4.cu (activation tensor maps).
@@ -974,6 +989,9 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
   // 28.0 -> 31.0 us, qkv 15.8 -> 16.4 us, o 13.0 -> 13.2 us; the decode step 5.54 -> 6.16 ms.
   static const int l2_prefetch = [] { const char* e = getenv("OGB_GEMM_L2_PREFETCH"); return (e && e[0] == '1') ? 1 : 0; }();
   p.l2_prefetch = l2_prefetch && pdl_enabled && bt <= 64;
+  // OGB_GEMM_NACC=2 / 4: decode-sized tiles spread the k-steps over that many accumulators (independent tcgen05.mma chains)
+  static const int nacc_env = [] { const char* e = getenv("OGB_GEMM_NACC"); return e ? atoi(e) : 0; }();
+  if ((nacc_env == 2 || nacc_env == 4) && bt * nacc_env <= 128) p.n_acc = nacc_env;
   if (fused_ar) {
     if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
     const CommParams& c = g_comm[device];
@@ -1061,6 +1079,8 @@ OGB_API int ogb_moe_gemm(const void* A, int lda, const void* W, int ldw, void* C
   p.status = status;
   p.pdl = pdl_enabled;
   p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
+  static const int nacc_env = [] { const char* e = getenv("OGB_GEMM_NACC"); return e ? atoi(e) : 0; }();
+  if ((nacc_env == 2 || nacc_env == 4) && bt * nacc_env <= 128) p.n_acc = nacc_env;
   dim3 grid((N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, max_tiles, 1);
   switch (bt) {
     case 16: return Launch<16>(tw, ta, p, grid, stream);

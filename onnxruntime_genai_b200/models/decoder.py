@@ -43,6 +43,8 @@ class StepInputs:
     cross_table: Optional[torch.Tensor] = None    # [B, cols] blocks of each request's encoder keys in `cross`
     cross_lens: Optional[torch.Tensor] = None     # [B] encoder positions per request
     max_cross_len: int = 0
+    cross_qk_heads: Optional[list] = None         # [(layer, head)]: alignment heads whose cross-attention scores are wanted
+    cross_qk_out: Optional[list] = None           # filled by forward: one [tokens, max_cross_len] fp32 tensor per listed head
     return_hidden: bool = False
 
 
@@ -380,6 +382,8 @@ class DecoderModel:
                 att = ops.paged_attention(q, ck, cv, s.cu_seqlens, s.cross_lens, s.cross_table, s.cross.block_size, self.heads_local,
                                           self.heads_local, a.head_dim, a.scale, -1, None, 0.0, max_q_len=s.max_q_len,
                                           max_kv_len=s.max_cross_len)
+                if s.cross_qk_heads:
+                    self._cross_qk(s, li, q, ck)
                 h = self._row_parallel(att, lw.cross_o_w, lw.cross_o_b, None)
             if a.parallel_block:
                 h = h + self._mlp(lw, x)      # attention and MLP read the same normalised input; one residual join
@@ -406,6 +410,30 @@ class DecoderModel:
         if a.final_logit_softcap > 0:
             logits = torch.tanh(logits / a.final_logit_softcap) * a.final_logit_softcap
         return logits
+
+    def _cross_qk(self, s: StepInputs, li: int, q: torch.Tensor, ck: torch.Tensor) -> None:
+        """Scaled query-key scores (before the softmax) of the listed alignment heads of layer `li` against the encoder keys,
+        for word-level timestamps (reference: the decoder's `output_cross_qk` tensors and their gather kernels,
+        src/models/whisper.cpp:85-103, src/cuda/model_kernels.cu:289-450).  A handful of heads on a debugging / timestamp
+        path: tensor ops, positions past a request's encoder length are -inf."""
+        if self.tp.size > 1:
+            raise RuntimeError("cross-attention scores of alignment heads are not available under tensor parallelism")
+        a = self.arch
+        scale = a.scale if a.scale else a.head_dim ** -0.5
+        T = q.shape[0]
+        qh = q.view(T, self.heads_local, a.head_dim)
+        bs = s.cross.block_size
+        cu, lens = s.cu_seqlens.tolist(), s.cross_lens.tolist()
+        for idx, (layer, head) in enumerate(s.cross_qk_heads):
+            if layer != li:
+                continue
+            out = torch.full((T, s.max_cross_len), float("-inf"), dtype=torch.float32, device=q.device)
+            for b in range(len(lens)):
+                n = lens[b]
+                slots = (s.cross_table[b].long()[:, None] * bs + torch.arange(bs, device=q.device)).reshape(-1)[:n]
+                k = ck[slots, head].float()                                           # [frames, D]
+                out[cu[b]:cu[b + 1], :n] = (qh[cu[b]:cu[b + 1], head].float() @ k.t()) * scale
+            s.cross_qk_out[idx] = out
 
     def fill_cross_cache(self, cross: CrossKVCache, enc_out: torch.Tensor, slots: torch.Tensor) -> None:
         """Projects encoder output rows [S, encoder_hidden] to every layer's cross-attention keys and values and writes
