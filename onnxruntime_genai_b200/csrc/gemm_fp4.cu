@@ -79,8 +79,13 @@ __device__ __forceinline__ void fp4_bulk_copy_g2s(void* smem_dst, const void* gs
 
 // Optional trace: when a buffer is registered (ogb_fp4_trace_buffer), the CTA of the first weight tile and first token tile
 // stamps clock64() at the hand-over points of every k-block: row r of [9][64] = event r of k-block i.
+// Compiled in only with -DOGB_FP4_TRACE (the stamps cost about 10 % of the kernel's time even when no buffer is registered).
 __device__ long long* g_fp4_trace = nullptr;
+#ifdef OGB_FP4_TRACE
 #define FP4_STAMP(ev, i) do { if (trace && (i) < 64) trace[(ev) * 64 + (i)] = clock64(); } while (0)
+#else
+#define FP4_STAMP(ev, i) do { } while (0)
+#endif
 
 // two e2m1 codes (low nibbles of the two halves of `u`) times the block's power-of-two multiplier
 __device__ __forceinline__ uint32_t deq_fp4_pair(uint32_t u, __nv_bfloat162 s2) {
@@ -139,7 +144,9 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   // The tile list is written by the kernel before this one, so nothing is read ahead of it.
   if (p.pdl) pdl_wait();
   if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA
+#ifdef OGB_FP4_TRACE
   long long* trace = (n_tile == 0 && m_tile == 0) ? g_fp4_trace : nullptr;
+#endif
   if (threadIdx.x == 0) FP4_STAMP(8, 0);
   const int row0 = p.grp.tile_row0[m_tile];
   const int rows = p.grp.tile_rows[m_tile];
@@ -239,7 +246,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const int part = GROUPS == 2 ? 0 : dt >> 7;             // which block of 32 of the row's 64 weights (GROUPS == 1)
     for (int i = group; i < num_kb; i += GROUPS) {
       const int rs = i % RAW, ws = i % FP4_WBUF;
-      const bool stamper = (dt & 127) == 0;
+      [[maybe_unused]] const bool stamper = (dt & 127) == 0;
       bool ok = mbar_wait_bounded(&raw_full[rs], (i / RAW) & 1, abort_flag);
       if (stamper) FP4_STAMP(1, i);
       if (ok && i >= FP4_WBUF) ok = mbar_wait_bounded(&w_empty[ws], ((i / FP4_WBUF) & 1) ^ 1, abort_flag);
@@ -351,6 +358,9 @@ using namespace ogb;
 
 // Registers (or clears, with nullptr) the device buffer of 9 * 64 int64 that receives the k-block trace of later launches.
 OGB_API int ogb_fp4_trace_buffer(void* buf) {
+#ifndef OGB_FP4_TRACE
+  if (buf) return -5;   // built without the trace
+#endif
   long long* p = static_cast<long long*>(buf);
   return cudaMemcpyToSymbol(g_fp4_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -4;
 }

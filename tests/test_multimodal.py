@@ -191,3 +191,38 @@ def test_encoder_head_padding_is_exact():
     torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-5)
     want = torch.cat([dense.vision_encoder(cfg, sd, px[i]) for i in range(2)])
     torch.testing.assert_close(a, want, rtol=2e-4, atol=2e-4)
+
+
+def test_whisper_alignment_heads_record_cross_attention_scores(tmp_path):
+    """`alignment_heads` (an int32 [n, 2] input of (layer, head) pairs) makes the generator record the scaled query-key
+    scores of those cross-attention heads for every token fed: [rows, n, tokens, frames], readable as the `cross_qk` output
+    (word-level timestamps are computed from them).  Token-by-token decoding and one prefill of the same tokens agree."""
+    d = str(tmp_path)
+    arch, enc, dsd, esd = _whisper_dir(d)
+    model = og.Model(d)
+    feats = np.random.RandomState(0).randn(2, 16, 100).astype(np.float32)
+    heads = np.array([[0, 1], [1, 0], [1, 3]], dtype=np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=12, batch_size=2)
+    g = og.Generator(model, p)
+    g.set_model_input("alignment_heads", heads)
+    g.set_inputs(og.NamedTensors(audio_features=feats, input_ids=np.array([[0, 5, 9], [0, 7, 3]], dtype=np.int32)))
+    for _ in range(4):
+        g.generate_next_token()
+    g.get_logits()                                            # runs the newest token
+    qk = g.get_output("cross_qk")
+    frames = g.state.max_cross_len
+    n_tok = g.token_count()
+    assert qk.shape == (2, 3, n_tok, frames) and np.isfinite(qk).all() and np.abs(qk).max() > 0
+    # the same tokens as one prompt: identical scores (the recorded rows do not depend on how the tokens were fed)
+    g2 = og.Generator(model, p)
+    g2.set_model_input("alignment_heads", heads)
+    g2.set_inputs(og.NamedTensors(audio_features=feats, input_ids=np.stack([g.get_sequence(0), g.get_sequence(1)]).astype(np.int32)))
+    qk2 = g2.get_output("cross_qk")
+    np.testing.assert_allclose(qk2, qk, rtol=1e-4, atol=1e-5)
+    assert np.abs(qk[0] - qk[1]).max() > 1e-3                 # the two clips differ
+    with pytest.raises(RuntimeError, match="out of range"):
+        g2.set_model_input("alignment_heads", np.array([[9, 0]], dtype=np.int32))
+    g3 = og.Generator(model, p)
+    with pytest.raises(RuntimeError, match="alignment_heads"):
+        g3.get_output("cross_qk")
