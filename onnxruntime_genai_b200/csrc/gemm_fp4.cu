@@ -352,6 +352,169 @@ static int LaunchFp4(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma,
   return LaunchFp4V<BT, HALF, 2, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
 }
 
+// ---------------------------------------------------------------------------------------------- GEMV (up to 4 rows per tile)
+// Decode of one to four sequences: every expert tile holds at most four token rows, the tensor cores have nothing to do
+// and a 45-k-block chain per CTA is pure latency.  Two threads per weight row stream the records of the fp16 form straight
+// from global memory (a warp covers 512 contiguous bytes, eight k-blocks in flight per thread), the activations sit in
+// shared memory as fp32, a block of 32 costs 16 conversions (`cvt.rn.f16x2.e2m1x2`), 32 x rows FMAs and one multiply by
+// the block scale.  The k range is split over a thread-block cluster whose partial sums meet in the first CTA's shared
+// memory; that CTA adds the bias, applies the paired activation and stores.
+constexpr int FP4_GEMV_MAX_KB = 24;   // k-blocks per CTA (activations: rows * 24 * 64 fp32 of shared memory)
+constexpr int FP4_GEMV_AHEAD = 8;
+
+template <int MT>
+__global__ void __launch_bounds__(256)
+gemv_fp4_grouped_kernel(const void* __restrict__ A_, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, const GemmParams p) {
+  __shared__ __align__(16) float xs[MT][FP4_GEMV_MAX_KB * 64];
+  __shared__ float part[MT][GEMM_BLOCK_N];
+  const int tid = threadIdx.x, row = tid >> 1, half = tid & 1;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
+  if (p.pdl) { pdl_launch_dependents(); pdl_wait(); }
+  if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA and over its cluster (the cluster spans z only)
+  const int row0 = p.grp.tile_row0[m_tile];
+  const int rows = min(p.grp.tile_rows[m_tile], MT);
+  const int expert = p.grp.tile_expert[m_tile];
+  const int kb0 = split * p.kb_per_split;
+  const int num_kb = max(0, min(p.kb_per_split, p.total_kb - kb0));
+  const uint8_t* rec0 = wpacked + ((size_t(expert) * p.total_kb + kb0) * n_tiles_per_expert + n_tile) * FP4_RECORD_BYTES;
+  const size_t rec_stride = size_t(n_tiles_per_expert) * FP4_RECORD_BYTES;
+
+  uint4 nb[FP4_GEMV_AHEAD];
+  uint32_t mq[FP4_GEMV_AHEAD];
+  auto fetch = [&](int kb, int slot) {
+    const uint8_t* r = rec0 + size_t(kb) * rec_stride;
+    nb[slot] = *reinterpret_cast<const uint4*>(r + row * 32 + half * 16);
+    mq[slot] = r[GEMM_BLOCK_N * 32 + row * 2 + half];
+  };
+#pragma unroll
+  for (int a = 0; a < FP4_GEMV_AHEAD; ++a)
+    if (a < num_kb) fetch(a, a);
+
+  // activations of this k range as fp32 (fp16 rows of the sorted activation matrix)
+  const __half* A = static_cast<const __half*>(A_);
+  for (int i = tid; i < num_kb * 64; i += 256) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) xs[m][i] = m < rows ? __half2float(A[size_t(row0 + m) * lda + size_t(kb0) * 64 + i]) : 0.f;
+  }
+  __syncthreads();
+
+  float acc[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+  for (int kbase = 0; kbase < num_kb; kbase += FP4_GEMV_AHEAD) {
+#pragma unroll
+    for (int a = 0; a < FP4_GEMV_AHEAD; ++a) {
+      const int kb = kbase + a;
+      if (kb >= num_kb) break;
+      const uint4 nib = nb[a];
+      const uint32_t m8 = mq[a];
+      if (kb + FP4_GEMV_AHEAD < num_kb) fetch(kb + FP4_GEMV_AHEAD, a);
+      const uint32_t words[4] = {nib.x, nib.y, nib.z, nib.w};
+      float dot[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) dot[m] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t h0, h1, h2, h3;
+        asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+            "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+            "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+            "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+            "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+            "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+            : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(words[j]));
+        const float2 w0 = __half22float2(*reinterpret_cast<__half2*>(&h0)), w1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
+        const float2 w2 = __half22float2(*reinterpret_cast<__half2*>(&h2)), w3 = __half22float2(*reinterpret_cast<__half2*>(&h3));
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
+          const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
+          dot[m] += w0.x * xa.x + w0.y * xa.y + w1.x * xa.z + w1.y * xa.w + w2.x * xb.x + w2.y * xb.y + w3.x * xb.z + w3.y * xb.w;
+        }
+      }
+      const uint16_t sbits = uint16_t(m8 << 10);                      // fp16 exponent field of the block scale
+      const float scale = __half2float(__ushort_as_half(sbits));
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[m] += scale * dot[m];
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
+  if (half == 0) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) part[m][row] = acc[m];
+  }
+  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
+
+  if (split == 0) {
+    const int kind = p.act_pair;
+    const int n_out = kind ? p.N / 2 : p.N;
+    const uint32_t part_addr = smem_u32(&part[0][0]);
+    auto total = [&](int m, int r) {
+      float t = 0.f;
+      for (int s2 = 0; s2 < p.splits; ++s2) {
+        if (p.splits > 1) {
+          float v;
+          const uint32_t ra = dsmem_addr(part_addr + uint32_t(m * GEMM_BLOCK_N + r) * 4, uint32_t(s2));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+          t += v;
+        } else {
+          t += part[m][r];
+        }
+      }
+      const int n = n_tile * GEMM_BLOCK_N + r;
+      if (p.bias && n < p.N) t += bf2f(p.bias[size_t(expert) * p.N + n]);
+      return t;
+    };
+    const int rows_out = kind ? 64 : GEMM_BLOCK_N;
+    for (int item = tid; item < rows_out * MT; item += 256) {
+      const int m = item / rows_out, r = item % rows_out;
+      const int col = kind ? n_tile * 64 + r : n_tile * GEMM_BLOCK_N + r;
+      if (m >= rows || col >= n_out) continue;
+      float v = total(m, r);
+      if (kind) {
+        float u = total(m, r + 64);
+        if (kind == 2) {
+          const float g = p.act_limit > 0.f ? fminf(v, p.act_limit) : v;
+          if (p.act_limit > 0.f) u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+          v = g / (1.f + __expf(-p.act_alpha * g)) * (u + 1.f);
+        } else {
+          v = silu(v) * u;
+        }
+      }
+      const size_t o = size_t(row0 + m) * p.ldc + col;
+      if (p.out_fp32 == 1) reinterpret_cast<float*>(p.C)[o] = v;
+      else if (p.out_fp32 == 2) reinterpret_cast<__half*>(p.C)[o] = __float2half_rn(v);
+      else reinterpret_cast<__nv_bfloat16*>(p.C)[o] = f2bf(v);
+    }
+  }
+  if (p.splits > 1) cluster_sync_all();   // peers keep their shared memory alive until the first CTA has read it
+}
+
+template <int MT>
+static int LaunchGemvFp4(const void* A, int lda, const uint8_t* wp, int n_tiles, const GemmParams& p, int max_tiles, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles, max_tiles, p.splits);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (p.splits > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = unsigned(p.splits);
+    ++na;
+  }
+  if (p.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = unsigned(na);
+  return cudaLaunchKernelEx(&cfg, gemv_fp4_grouped_kernel<MT>, A, lda, wp, n_tiles, p) == cudaSuccess ? 0 : -4;
+}
+
 }  // namespace ogb
 
 using namespace ogb;
@@ -372,11 +535,12 @@ OGB_API long long ogb_fp4_packed_bytes(int experts, int N, int K) {
 
 // Grouped expert GEMM over packed MXFP4 experts; arguments as ogb_moe_gemm with `Wpacked` in the record layout above.
 // flags: bit 0 fp32 output, bit 1 paired activation, bit 4 fp16 form (A holds fp16 rows, records in the fp16 layout),
-// bit 5 fp16 output.
+// bit 5 fp16 output.  max_rows_per_tile: an upper bound on the rows of any tile known on the host (the number of tokens
+// of the step: an expert receives a token at most once), 0 if unknown; up to 4 selects the GEMV.
 OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
                              const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
                              const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
-                             int* status, void* stream_) {
+                             int max_rows_per_tile, int* status, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (rows_total <= 0 || N <= 0 || K <= 0 || experts <= 0 || max_tiles <= 0) return 0;
   if ((K % 64) || (lda % 8)) return -1;
@@ -401,6 +565,25 @@ OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* 
   p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N;
   // OGB_FP4_TMA=1: records arrive as boxes of a byte tensor map instead of untiled bulk copies (measured: no difference)
+  // Steps of one to four tokens can take the weight-streaming GEMV (OGB_FP4_GEMV=1).  Opt-in: measured on B200 at the
+  // gpt-oss-20b shapes it is slower than the tensor-core kernel - gate/up 54 vs 27 us at 1 token, 123 vs ~30 us at 4; down
+  // 31 vs 23 us at 1 token (three conversions per pair of weights on the CUDA cores against one in the tile expansion).
+  static const int gemv_env = [] { const char* e = getenv("OGB_FP4_GEMV"); return (e && e[0] == '1') ? 1 : 0; }();
+  if (gemv_env && half && max_rows_per_tile > 0 && max_rows_per_tile <= 4 && !(flags & 1)) {
+    int sm_count = 148;
+    { int dev = 0; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+    const int est_tiles = rows_total < max_tiles ? rows_total : max_tiles;
+    int gs = (p.total_kb + FP4_GEMV_MAX_KB - 1) / FP4_GEMV_MAX_KB;
+    while (gs < 8 && n_tiles * est_tiles * gs < 4 * sm_count && p.total_kb / (gs * 2) >= 2) gs *= 2;
+    if (gs > 8) gs = 8;
+    int per = (p.total_kb + gs - 1) / gs;
+    while (gs > 1 && per * (gs - 1) >= p.total_kb) { --gs; per = (p.total_kb + gs - 1) / gs; }
+    if (per <= FP4_GEMV_MAX_KB) {
+      GemmParams g = p;
+      g.splits = gs; g.kb_per_split = per;
+      return LaunchGemvFp4<4>(A, lda, static_cast<const uint8_t*>(Wpacked), n_tiles, g, max_tiles, stream);
+    }
+  }
   static const int tma_env = [] { const char* e = getenv("OGB_FP4_TMA"); return (e && e[0] == '1') ? 1 : 0; }();
   CUtensorMap tw = ta;
   int w_by_tma = 0;

@@ -55,8 +55,8 @@ int ogb_gemm_w4(const void* A, int lda, const void* Wpacked, void* C, int ldc, i
 long long ogb_fp4_packed_bytes(int experts, int N, int K);
 int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
                      const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
-                     const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile, int* status,
-                     void* stream);
+                     const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
+                     int max_rows_per_tile, int* status, void* stream);
 
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);

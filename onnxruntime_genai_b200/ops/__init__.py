@@ -348,7 +348,7 @@ def moe_gemm(xs: torch.Tensor, w: torch.Tensor, plan: MoePlan, bias=None, act_ki
         rc = _lib.lib().ogb_moe_gemm_fp4(_ptr(xs), xs.stride(0), _ptr(w.packed), _ptr(out), out.stride(0), xs.shape[0], N, K, E, _ptr(bias),
                                          flags, int(act_kind), float(alpha), float(limit),
                                          _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.tile_rows), _ptr(plan.num_tiles),
-                                         plan.max_tiles, plan.bt, ws.status, _stream())
+                                         plan.max_tiles, plan.bt, plan.T, ws.status, _stream())   # an expert sees a token at most once
         _lib.check(rc, "moe_gemm_fp4")
         return out
     assert xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()

@@ -33,7 +33,7 @@ _SIGS = {
                              _P, c_int, c_int, _P, _P]),
     "ogb_fp4_packed_bytes": (c_longlong, [c_int, c_int, c_int]),
     "ogb_moe_gemm_fp4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_float, _P, _P, _P,
-                                 _P, c_int, c_int, _P, _P]),
+                                 _P, c_int, c_int, c_int, _P, _P]),
     "ogb_collective": (c_int, [c_int, _P, _P, _P, c_longlong, c_int, _P, c_int, _P]),
     "ogb_moe_topk": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P]),
     "ogb_moe_max_tiles": (c_int, [c_int, c_int, c_int]),

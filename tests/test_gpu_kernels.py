@@ -796,8 +796,9 @@ def _random_fp4(E, N, K, seed):
     return codes, scales
 
 
+@pytest.mark.parametrize("rows", [64, 4])          # 4 rows: also the shape of the opt-in GEMV of the fp16 form (OGB_FP4_GEMV=1)
 @pytest.mark.parametrize("half", [False, True])
-def test_fp4_expansion_is_exact_for_every_code(half):
+def test_fp4_expansion_is_exact_for_every_code(half, rows):
     """One expert whose rows hold every e2m1 code against an identity activation: the grouped FP4 GEMM returns the
     weights themselves, so every code (the subnormal 0.5 and both zeros included) times several block scales is
     checked bit for bit."""
@@ -813,20 +814,21 @@ def test_fp4_expansion_is_exact_for_every_code(half):
         scales = (torch.arange(N * 2, dtype=torch.int64).view(1, N, 2) % 114 + 15).to(torch.uint8)
     scales[0, :8] = 127
     fe = Fp4Experts.from_codes(codes, scales, DEV, half=half)
-    x = torch.eye(K, dtype=torch.float16 if half else torch.bfloat16, device=DEV)
-    logits = torch.zeros(K, 1, dtype=torch.float32, device=DEV)
+    x = torch.eye(K, dtype=torch.float16 if half else torch.bfloat16, device=DEV)[:rows].contiguous()
+    logits = torch.zeros(rows, 1, dtype=torch.float32, device=DEV)
     plan = ops.moe_route(logits, 1, 0, (0, 1))
     xs = x[plan.sorted_token.long()].contiguous()
     y = ops.moe_gemm(xs, fe, plan, None)
     ops.check_kernel_status()
     got = torch.empty_like(y)
     got[plan.sorted_token.long()] = y
-    want = fe.dequantize(0).t().to(torch.bfloat16)          # [K, N]: row k of the output is column k of the weight
+    want = fe.dequantize(0).t().to(torch.bfloat16)[:rows]   # [rows, N]: row k of the output is column k of the weight
     assert torch.equal(got.cpu(), want), f"{(got.cpu() != want).sum().item()} of {want.numel()} weights differ"
 
 
 @pytest.mark.parametrize("half", [False, True])
-@pytest.mark.parametrize("T,E,k,H,I", [(3, 4, 2, 128, 64), (64, 32, 4, 256, 192), (700, 8, 2, 320, 128), (40, 8, 4, 2880, 64)])
+@pytest.mark.parametrize("T,E,k,H,I", [(3, 4, 2, 128, 64), (64, 32, 4, 256, 192), (700, 8, 2, 320, 128), (40, 8, 4, 2880, 64),
+                                       (2, 8, 2, 2880, 192), (4, 8, 4, 320, 2880)])
 def test_moe_fp4_grouped_gemm_matches_expert_loop(T, E, k, H, I, half):
     """Packed MXFP4 experts through the grouped FP4 GEMM (clamped SwiGLU epilogue, then the down projection whose
     row count is not a multiple of the 128-row tile) against the fp32 loop over the dequantised experts."""
