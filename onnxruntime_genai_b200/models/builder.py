@@ -339,17 +339,22 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
 
     def put_linear(base: str, node_name: str, src_names, inp: str, out: str, N: int, K: int):
         """A linear layer y = x @ W^T from one or more stacked [n_i, K] canonical weights."""
-        if linear_format in ("fp8", "nvfp4") and not synthetic_weights:
-            # block-quantised float formats (linear_format option): FP8 e4m3 rows or NVFP4 blocks of 16
-            w = torch.cat([get(n).float() for n in src_names], dim=0)
-            if linear_format == "fp8":
-                q8, sc = quantize_fp8_rows(w)
+        pre = [get(n) for n in src_names] if (state_dict is not None and not synthetic_weights) else []
+        pre_kind = getattr(pre[0], "kind", "") if pre and all(getattr(t, "kind", "") == getattr(pre[0], "kind", "") for t in pre) else ""
+        carried = type(pre[0]).cat(pre) if pre_kind in ("fp8", "nvfp4") else None
+        if carried is not None or (linear_format in ("fp8", "nvfp4") and not synthetic_weights):
+            # block-quantised float formats: FP8 e4m3 rows or NVFP4 blocks of 16, quantised here (linear_format option) or
+            # carried over from a ModelOpt checkpoint
+            fmt = pre_kind if carried is not None else linear_format
+            w = None if carried is not None else torch.cat([get(n).float() for n in src_names], dim=0)
+            if fmt == "fp8":
+                q8, sc = (carried.q8, carried.scale) if carried is not None else quantize_fp8_rows(w)
                 W.add_array(base + ".fp8_weight", q8.numpy(), op.FLOAT8E4M3FN)
                 W.add_array(base + ".fp8_weight_scale", sc.numpy(), op.FLOAT)
                 W.node("MatMulBlockQuantizedFp8Weight", node_name, [inp, base + ".fp8_weight", base + ".fp8_weight_scale"], [out],
                        domain="com.microsoft", block_size=K)
             else:
-                codes, sc, glob = quantize_nvfp4(w)
+                codes, sc, glob = (carried.codes, carried.scales, carried.global_scale) if carried is not None else quantize_nvfp4(w)
                 W.add_array(base + ".nvfp4_weight", codes.numpy(), op.UINT8)
                 W.add_array(base + ".nvfp4_weight_scale", sc.numpy(), op.FLOAT8E4M3FN)
                 W.add_array(base + ".nvfp4_weight_scale_2", glob.numpy(), op.FLOAT)
@@ -927,7 +932,7 @@ def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
     if os.path.exists(cfg_path):
         with open(cfg_path) as f:
             qc = json.load(f).get("quantization_config")
-        if qc and any(k.endswith(".qweight") for k in sd):
+        if qc and (any(k.endswith(".qweight") for k in sd) or str(qc.get("quant_method", "")).lower() == "modelopt"):
             # AWQ / GPTQ linears become QuantizedLinear entries: an int4 export writes them as they are
             from .quantized_checkpoint import convert_state_dict
             sd = convert_state_dict(sd, qc)
@@ -975,7 +980,7 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         if not int(extra.get("random_weights", 0)) and not int(extra.get("synthetic_weights", 0)):
             state_dict = load_hf_state_dict(model_name_or_dir)
             _split_packed_qkv(state_dict, arch)
-            if precision != "int4":   # a pre-quantised checkpoint exported at a float precision: dequantise
+            if precision != "int4":   # an int4 checkpoint exported at a float precision: dequantise
                 state_dict = {k: (v.float() if hasattr(v, "matmulnbits") else v) for k, v in state_dict.items()}
         for fn in ("tokenizer.json", "tokenizer_config.json", "special_tokens_map.json", "tokenizer.model", "chat_template.jinja",
                    "generation_config.json"):

@@ -1,5 +1,6 @@
-"""Readers for pre-quantised Hugging Face checkpoints (AWQ, GPTQ): their int4 tensors are carried over into the
-MatMulNBits layout without a second quantisation.
+"""Readers for pre-quantised Hugging Face checkpoints: AWQ and GPTQ int4 tensors are carried over into the MatMulNBits
+layout, ModelOpt FP8 / NVFP4 tensors into MatMulBlockQuantizedFp8Weight / MatMulBlockQuantizedFp4Weight, without a
+second quantisation.
 
 Reference: src/python/py/models/quantized_model.py (`AWQModel`, `GPTQModel`, unpack / repack at :1017-1107).  Those
 checkpoints group the scales over 128 (or 64, 32) input features; the kernels here use blocks of 32, and a group of
@@ -57,6 +58,83 @@ class QuantizedLinear:
         return packed, self.scales, (zp[:, 0::2] | (zp[:, 1::2] << 4)).contiguous()
 
 
+@dataclass
+class Fp8Linear:
+    """ModelOpt FP8 linear: w[n, k] = e4m3(q8[n, k]) * scale[n]  (a scalar scale of the checkpoint is repeated per row)."""
+    q8: torch.Tensor       # uint8 view of float8_e4m3fn [N, K]
+    scale: torch.Tensor    # fp32 [N, 1]
+    kind = "fp8"
+
+    @property
+    def shape(self):
+        return tuple(self.q8.shape)
+
+    def float(self) -> torch.Tensor:
+        return self.q8.view(torch.float8_e4m3fn).float() * self.scale
+
+    def rows(self, lo: int, hi: int) -> "Fp8Linear":
+        return Fp8Linear(self.q8[lo:hi], self.scale[lo:hi])
+
+    @staticmethod
+    def cat(parts) -> "Fp8Linear":
+        return Fp8Linear(torch.cat([p.q8 for p in parts], 0), torch.cat([p.scale for p in parts], 0))
+
+
+@dataclass
+class Nvfp4Linear:
+    """ModelOpt NVFP4 linear: e2m1 codes [N, K/2] (low nibble = even k), e4m3 scales per block of 16 [N, K/16] (uint8 view), one
+    fp32 global scale."""
+    codes: torch.Tensor
+    scales: torch.Tensor
+    global_scale: torch.Tensor
+    kind = "nvfp4"
+
+    @property
+    def shape(self):
+        return (self.codes.shape[0], self.codes.shape[1] * 2)
+
+    def float(self) -> torch.Tensor:
+        from .builder import dequantize_nvfp4
+        return dequantize_nvfp4(self.codes, self.scales, self.global_scale)
+
+    def rows(self, lo: int, hi: int) -> "Nvfp4Linear":
+        return Nvfp4Linear(self.codes[lo:hi], self.scales[lo:hi], self.global_scale)
+
+    @staticmethod
+    def cat(parts):
+        """Stacked projections share one global scale only if the checkpoint gave them the same one; otherwise None (the
+        caller falls back to the dequantised weights)."""
+        g0 = float(parts[0].global_scale.reshape(-1)[0])
+        if any(float(p.global_scale.reshape(-1)[0]) != g0 for p in parts):
+            return None
+        return Nvfp4Linear(torch.cat([p.codes for p in parts], 0), torch.cat([p.scales for p in parts], 0), parts[0].global_scale)
+
+
+def convert_modelopt(sd: Dict[str, torch.Tensor]) -> Dict[str, object]:
+    """ModelOpt checkpoints: `<name>.weight` in float8_e4m3fn with `<name>.weight_scale` (FP8), or packed uint8 codes with
+    `<name>.weight_scale` (e4m3 per block of 16) and `<name>.weight_scale_2` (NVFP4).  Activation scales (`input_scale`) and
+    KV scales are dropped: activations stay 16-bit here."""
+    out: Dict[str, object] = {}
+    for k, v in sd.items():
+        if k.endswith((".input_scale", ".k_scale", ".v_scale")):
+            continue
+        if k.endswith((".weight_scale", ".weight_scale_2")) and k.rsplit(".", 1)[0] + ".weight" in sd:
+            continue
+        if k.endswith(".weight") and k[:-len(".weight")] + ".weight_scale" in sd:
+            base = k[:-len(".weight")]
+            if base + ".weight_scale_2" in sd:
+                sc = sd[base + ".weight_scale"]
+                out[k] = Nvfp4Linear(v.view(torch.uint8), sc.view(torch.uint8) if sc.dtype != torch.uint8 else sc,
+                                     sd[base + ".weight_scale_2"].float().reshape(1))
+            else:
+                q8 = v.view(torch.uint8) if v.dtype != torch.uint8 else v
+                scale = sd[base + ".weight_scale"].float().reshape(-1, 1)
+                out[k] = Fp8Linear(q8, scale.expand(q8.shape[0], 1).contiguous() if scale.numel() == 1 else scale)
+        else:
+            out[k] = v
+    return out
+
+
 def _nibbles(words: torch.Tensor) -> torch.Tensor:
     """int32 [...] -> uint8 [..., 8]: nibble i = bits 4i .. 4i+3."""
     w = words.to(torch.int64) & 0xFFFFFFFF
@@ -97,6 +175,8 @@ def unpack_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
 def convert_state_dict(sd: Dict[str, torch.Tensor], quant_config: dict) -> Dict[str, object]:
     """Replaces every `<name>.qweight / .qzeros / .scales (/ .g_idx)` group by `<name>.weight = QuantizedLinear`."""
     method = str(quant_config.get("quant_method", "")).lower()
+    if method == "modelopt":
+        return convert_modelopt(sd)
     bits = int(quant_config.get("bits", quant_config.get("w_bit", 4)))
     group = int(quant_config.get("group_size", quant_config.get("q_group_size", 128)))
     if method not in ("awq", "gptq") or bits != 4:

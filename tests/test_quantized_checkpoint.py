@@ -104,3 +104,61 @@ def test_quantised_hf_checkpoint_exports_without_requantisation(method, tmp_path
     # the int4 path rounds the dequantised weights and the activations to bf16: logits agree to that precision
     got = g.get_logits().reshape(-1)
     assert np.abs(got - want).max() < 0.05 * want.std() + 0.02
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "nvfp4"])
+def test_modelopt_checkpoint_is_carried_into_the_block_quantised_ops(fmt, tmp_path):
+    """A ModelOpt-style Hugging Face directory (FP8: e4m3 `weight` + `weight_scale`; NVFP4: packed `weight`, e4m3 `weight_scale`
+    per block of 16, `weight_scale_2`) exports to MatMulBlockQuantizedFp8Weight / Fp4Weight nodes holding the checkpoint's
+    own codes; logits equal the dense model on the dequantised weights."""
+    from safetensors.torch import save_file
+    from onnxruntime_genai_b200.models.builder import dequantize_nvfp4, quantize_fp8_rows, quantize_nvfp4
+    from onnxruntime_genai_b200.utils import onnx_proto as op
+    arch = ArchConfig(**ARCH)
+    sd = random_state_dict(arch, seed=31, std=0.1)
+    hf, dense = {}, {}
+    for k, v in sd.items():
+        if k.endswith("_proj.weight"):
+            base = k[: -len(".weight")]
+            if fmt == "fp8":
+                q8, sc = quantize_fp8_rows(v)
+                hf[k], hf[base + ".weight_scale"] = q8.view(torch.float8_e4m3fn), sc.reshape(-1)
+                hf[base + ".input_scale"] = torch.tensor(1.0)
+                dense[k] = q8.view(torch.float8_e4m3fn).float() * sc
+            else:
+                # one global scale for every projection (stacked q / k / v must share it to be carried over)
+                wf = v.float()
+                glob = torch.tensor(0.1 * 4 / (6.0 * 448.0))
+                sc8 = (wf.view(v.shape[0], -1, 16).abs().amax(-1) / 6.0 / glob).to(torch.float8_e4m3fn)
+                codes, _, _ = quantize_nvfp4(v)          # reference packing helper, re-done below with the shared global
+                eff = (sc8.float() * glob).clamp(min=1e-20)
+                grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+                vv = (wf.view(v.shape[0], -1, 16) / eff[..., None]).clamp(-6, 6)
+                idx = (vv.abs()[..., None] - grid).abs().argmin(-1)
+                c = (idx + 8 * ((vv < 0) & (idx > 0)).long()).to(torch.uint8).view(v.shape)
+                packed = (c[:, 0::2] | (c[:, 1::2] << 4)).contiguous()
+                hf[k], hf[base + ".weight_scale"], hf[base + ".weight_scale_2"] = packed, sc8, glob.reshape(())
+                dense[k] = dequantize_nvfp4(packed, sc8.view(torch.uint8), glob.reshape(1))
+        else:
+            hf[k] = v
+            dense[k] = v
+    src = tmp_path / "hf"
+    os.makedirs(src)
+    save_file({k: v.contiguous() for k, v in hf.items()}, str(src / "model.safetensors"))
+    cfg = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=96, hidden_size=128, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=32, intermediate_size=256, max_position_embeddings=64,
+               rms_norm_eps=1e-5, rope_theta=10000.0, bos_token_id=1, eos_token_id=2, pad_token_id=0, tie_word_embeddings=False,
+               quantization_config={"quant_method": "modelopt", "quant_algo": fmt.upper()})
+    (src / "config.json").write_text(json.dumps(cfg))
+    out = str(tmp_path / "out")
+    create_model(str(src), out, "fp32", "cpu")
+    ops_seen = {n.op_type for n in op.LoadedModel(os.path.join(out, "model.onnx")).model.nodes}
+    assert ("MatMulBlockQuantizedFp8Weight" if fmt == "fp8" else "MatMulBlockQuantizedFp4Weight") in ops_seen
+    model = og.Model(out)
+    ids = np.random.RandomState(3).randint(3, 96, size=(1, 9)).astype(np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=16)
+    g = og.Generator(model, p)
+    g.append_tokens(ids)
+    want = dense_logits(model.arch, dense, ids[0].tolist())[-1].numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
