@@ -58,6 +58,10 @@ int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int l
                      const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
                      int max_rows_per_tile, int* status, void* stream);
 
+// Debug builds (-DOGB_FP4_TRACE) only: registers a device buffer of 9 * 64 int64 that receives clock64() stamps of one CTA's
+// k-block hand-overs (nullptr clears it); returns -5 in a build without the trace.
+int ogb_fp4_trace_buffer(void* buf);
+
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);
 int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias, void* out,
