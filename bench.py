@@ -48,12 +48,6 @@ def reference_arm(args):
     """The reference needs ONNX Runtime binaries fetched from a package feed at build time
     (cmake/ortlib.cmake) and the `onnx` / `onnxruntime` Python packages, none of which exist offline."""
     why = "reference cannot be installed offline: its build downloads ONNX Runtime binaries (cmake/ortlib.cmake) and needs onnx/onnxruntime"
-    log = os.path.join(ROOT, "baseline", "install.log")
-    if os.path.exists(log):
-        with open(log) as f:
-            tail = [l.strip() for l in f.read().strip().splitlines() if l.strip()]
-        if tail:
-            why += " (pip: " + tail[-1][:160] + ")"
     try:
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
         import onnxruntime_genai  # noqa: F401

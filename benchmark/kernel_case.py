@@ -1,6 +1,6 @@
 """Single-kernel workloads for timing and profiling.
 
-    python -m onnxruntime_genai_b200.utils.kernel_case <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--eager] [--json out.json]
+    python benchmark/kernel_case.py <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--eager] [--json out.json]
 
 cases: gemm_qkv gemm_o gemm_gate_up gemm_down gemm_lm_head gemm_prefill w4_qkv w4_down attention_decode
        attention_prefill norm rope sample argmax all; moe_fp4_gate_up moe_fp4_down moe_fp4b_gate_up moe_fp4b_down moe_bf16_gate_up moe_bf16_down
@@ -22,7 +22,9 @@ import sys
 import numpy as np
 import torch
 
-from .. import ops
+import os as _os, sys as _sys
+_sys.path.insert(0, _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))))
+from onnxruntime_genai_b200 import ops
 
 H, I, V, HQ, HKV, D = 4096, 14336, 128256, 32, 8, 128
 
@@ -70,7 +72,7 @@ def _time_graph(fn, iters, reps=3):
 
 
 def _peaks():
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     try:
         with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
             p = json.load(f)
@@ -99,8 +101,8 @@ def build_case(name, T, L, tp=1):
             L = min(L, 2)
         x = _bf(T, K, std=1.0)
         if name.startswith("w4_"):
-            from ..models.builder import quantize_int4_block32
-            from ..ops.w4 import W4Weight, unpack_ort_q4
+            from onnxruntime_genai_b200.models.builder import quantize_int4_block32
+            from onnxruntime_genai_b200.ops.w4 import W4Weight, unpack_ort_q4
             ws = []
             for _ in range(L):
                 qw, s, zp = quantize_int4_block32(torch.randn(N, K, device="cuda") * 0.02)   # quantised and repacked on the device
@@ -126,7 +128,7 @@ def build_case(name, T, L, tp=1):
         xs = _bf(T * k, K, std=1.0)
         touched = int(torch.unique(plan.topk_idx).numel())
         if "fp4" in name:
-            from ..ops.fp4 import Fp4Experts
+            from onnxruntime_genai_b200.ops.fp4 import Fp4Experts
             half = "fp4b" not in name       # moe_fp4b_*: the bf16 form of the packed experts
             xs = xs.to(torch.float16) if half else xs
             ws = [Fp4Experts.from_codes(torch.randint(0, 16, (E, N, K), device="cuda", dtype=torch.uint8),
@@ -230,7 +232,7 @@ def main():
         globals()["ATTN_SPLITS"] = v[0] if len(v) == 1 else (v[0], v[1])
     comm = None
     if a.tp > 1:
-        from ..parallel.symm import LocalComm
+        from onnxruntime_genai_b200.parallel.symm import LocalComm
         comm = LocalComm(torch.device("cuda", 0))
     hbm, tflops, src = _peaks()
     out = {}

@@ -2,11 +2,14 @@
 all-reduce / all-gather / reduce-scatter kernels against their NCCL counterparts, on every rank of a
 torchrun job, and times both sides (device events, max over ranks).
 
-    torchrun --nproc-per-node N --master-addr 127.0.0.1 -m onnxruntime_genai_b200.parallel.fused_check [--tokens 64]
+    torchrun --nproc-per-node N --master-addr 127.0.0.1 benchmark/tp_fused_check.py [--tokens 64]
 """
 import argparse
 import json
 import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 import torch.distributed as dist

@@ -552,12 +552,9 @@ static int LaunchAttentionMode(const AttnParams& p, int max_q_len, int cache_slo
   constexpr int SMEM = BM * SROW * 2 + KV_BYTES + (TMA ? 1024 : 0);
   // decode mode parks the four warps' partial states in the (idle) K/V area, which starts at the K tile and is contiguous
   static_assert(!DECODE || (4 * 16 * D + 4 * 16 * 2) * 4 <= (KV8 ? KV_BYTES : ATT_STAGES * ATT_BN * SROW * 2), "merge buffers must fit in the K/V area");
-  static bool configured = false;
   auto kern = paged_attention_kernel<D, DECODE, TMA, KV8>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(kern, SMEM, configured)) return -3;
   CUtensorMap mk, mv;
   memset(&mk, 0, sizeof(mk));
   memset(&mv, 0, sizeof(mv));

@@ -124,16 +124,26 @@ inline bool launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream
   return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess;
 }
 
+// The opt-in to more than 48 KiB of dynamic shared memory is a per-device attribute of a kernel.  `done` (one static
+// array per call site, i.e. per kernel instantiation) records the devices on which this process has set it already, so a
+// process that drives several GPUs configures each of them.
+constexpr int OGB_MAX_DEVICES = 64;
+template <typename Kern>
+inline bool set_max_dyn_smem(Kern kern, int bytes, bool (&done)[OGB_MAX_DEVICES]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const bool tracked = dev >= 0 && dev < OGB_MAX_DEVICES;
+  if (tracked && done[dev]) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  if (tracked) done[dev] = true;
+  return true;
+}
+
 // ------------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 // 2-D tiled load global -> shared, completion on an mbarrier (transaction bytes).
-// Prefetch of one box of a tiled tensor map into L2 (no shared-memory destination, no completion to wait for).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
-               : "memory");
-}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

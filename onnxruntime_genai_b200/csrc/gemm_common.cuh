@@ -57,7 +57,6 @@ struct GemmParams {
   const __nv_bfloat16* bias;
   int* status;
   int pdl;
-  int l2_prefetch;      // 1: the producer prefetches its whole weight stream into L2 before waiting for the previous kernel
   CommParams comm;
   int comm_epilogue;    // 1: the epilogue runs the fused all-reduce / reduce-scatter (and the call closes an epoch)
   int ag_rows;          // > 0: all-gather -> GEMM: the activations are not read through the tensor map but assembled from the
@@ -67,8 +66,6 @@ struct GemmParams {
                         // broadcasts): each partial crosses NVLink once instead of world times; owner of row m = m / ar2_rows
   int rs_rows;          // > 0: reduce-scatter by token rows: rank r receives (and stores, as its rows 0..) rows [r * rs_rows, (r + 1) * rs_rows)
   GroupParams grp;
-  int n_acc;            // 0 / 1: one accumulator; 2 or 4: the k-steps of a k-block go round-robin into that many accumulators
-                        // BT columns apart (independent tcgen05.mma chains), summed by the epilogue
 };
 
 template <int BT>
@@ -166,7 +163,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         uint32_t r0[16];
         tmem_ld16(taddr + c0, r0);
         tmem_ld_wait();
-        // n_acc > 1: the k-steps went round-robin into n_acc accumulators BT columns apart (independent MMA chains); sum them
+        // n_acc > 1 (packed FP4 experts): the k-steps went round-robin into n_acc accumulators BT columns apart; sum them
         for (int a = 1; a < n_acc; ++a) {
           uint32_t r1[16];
           tmem_ld16(taddr + a * BT + c0, r1);

@@ -77,16 +77,6 @@ __device__ __forceinline__ void fp4_bulk_copy_g2s(void* smem_dst, const void* gs
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// Optional trace: when a buffer is registered (ogb_fp4_trace_buffer), the CTA of the first weight tile and first token tile
-// stamps clock64() at the hand-over points of every k-block: row r of [9][64] = event r of k-block i.
-// Compiled in only with -DOGB_FP4_TRACE (the stamps cost about 10 % of the kernel's time even when no buffer is registered).
-__device__ long long* g_fp4_trace = nullptr;
-#ifdef OGB_FP4_TRACE
-#define FP4_STAMP(ev, i) do { if (trace && (i) < 64) trace[(ev) * 64 + (i)] = clock64(); } while (0)
-#else
-#define FP4_STAMP(ev, i) do { } while (0)
-#endif
-
 // two e2m1 codes (low nibbles of the two halves of `u`) times the block's power-of-two multiplier
 __device__ __forceinline__ uint32_t deq_fp4_pair(uint32_t u, __nv_bfloat162 s2) {
   uint32_t t = ((u & 0x00070007u) << 6) | ((u & 0x00080008u) << 12);
@@ -145,9 +135,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   if (p.pdl) pdl_wait();
   if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA
 #ifdef OGB_FP4_TRACE
-  long long* trace = (n_tile == 0 && m_tile == 0) ? g_fp4_trace : nullptr;
 #endif
-  if (threadIdx.x == 0) FP4_STAMP(8, 0);
   const int row0 = p.grp.tile_row0[m_tile];
   const int rows = p.grp.tile_rows[m_tile];
   const int expert = p.grp.tile_expert[m_tile];
@@ -172,7 +160,6 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const uint32_t tmem_base = *tmem_slot;
   if (p.pdl) pdl_launch_dependents();
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
-  if (threadIdx.x == 0) FP4_STAMP(8, 1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -186,13 +173,11 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         mbar_expect_tx(&raw_full[s], FP4_RECORD_BYTES);
         if (w_by_tma) tma_load_2d(raw_ring + s * FP4_RECORD_BYTES, &tmap_w, &raw_full[s], 0, (rec_first + i * n_tiles_per_expert) * (FP4_RECORD_BYTES / 128));
         else fp4_bulk_copy_g2s(raw_ring + s * FP4_RECORD_BYTES, rec0 + size_t(i) * rec_stride, FP4_RECORD_BYTES, &raw_full[s]);
-        FP4_STAMP(0, i);
       };
       auto load_a = [&](int i) {
         const int s = i % A_ST;
         mbar_expect_tx(&a_full[s], Cfg::A_TILE_BYTES);
         tma_load_2d(a_ring + s * Cfg::A_TILE_BYTES, &tmap_a, &a_full[s], i * GEMM_BLOCK_K, row0);
-        FP4_STAMP(7, i);
       };
       int ri = 0, ai = 0;
       const int pre = min(RAW, num_kb);
@@ -220,9 +205,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       for (int i = 0; i < num_kb && ok; ++i) {
         const int s = i % FP4_WBUF, as = i % A_ST;
         bool got = mbar_wait_bounded(&deq_full[s], (i / FP4_WBUF) & 1, abort_flag);
-        FP4_STAMP(4, i);
         got = got && mbar_wait_bounded(&a_full[as], (i / A_ST) & 1, abort_flag);
-        FP4_STAMP(5, i);
         if (!got) { fail(OGB_ERR_WAIT_TMA); ok = false; break; }
         tc_fence_after();
         const uint32_t w = smem_u32(w_ring + s * W_TILE_BYTES), a = smem_u32(a_ring + as * Cfg::A_TILE_BYTES);
@@ -232,7 +215,6 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                    idesc, (i > 0 || k >= NACC) ? 1u : 0u);
         umma_commit(&w_empty[s]);
         umma_commit(&a_empty[as]);
-        FP4_STAMP(6, i);
       }
       if (ok) umma_commit(accum_bar);
     }
@@ -246,11 +228,8 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const int part = GROUPS == 2 ? 0 : dt >> 7;             // which block of 32 of the row's 64 weights (GROUPS == 1)
     for (int i = group; i < num_kb; i += GROUPS) {
       const int rs = i % RAW, ws = i % FP4_WBUF;
-      [[maybe_unused]] const bool stamper = (dt & 127) == 0;
       bool ok = mbar_wait_bounded(&raw_full[rs], (i / RAW) & 1, abort_flag);
-      if (stamper) FP4_STAMP(1, i);
       if (ok && i >= FP4_WBUF) ok = mbar_wait_bounded(&w_empty[ws], ((i / FP4_WBUF) & 1) ^ 1, abort_flag);
-      if (stamper) FP4_STAMP(2, i);
       if (!__all_sync(0xffffffffu, ok)) { fail(OGB_ERR_WAIT_TMA); break; }   // the warp gives up as one (it meets at __syncwarp below)
       const uint8_t* rec = raw_ring + rs * FP4_RECORD_BYTES;
       uint32_t words[WORDS];
@@ -286,7 +265,6 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
       __syncwarp();
-      if (stamper) FP4_STAMP(3, i);
       if (lane == 0) {
         mbar_arrive(&deq_full[ws]);
         mbar_arrive(&raw_empty[rs]);
@@ -294,9 +272,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
   }
 
-  if (threadIdx.x == 64) FP4_STAMP(8, 2);
   gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, expert * p.N, NACC);
-  if (threadIdx.x == 64) FP4_STAMP(8, 3);
 
   tc_fence_before();
   __syncthreads();
@@ -310,13 +286,10 @@ template <int BT, bool HALF, int WBUF, int GROUPS, int NACC>
 static int LaunchFp4V(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid,
                       cudaStream_t stream) {
   using Cfg = Fp4Cfg<BT, WBUF>;
-  static bool configured = false;
   static_assert(NACC <= Fp4Cfg<BT, WBUF>::NACC_MAX, "not enough tensor memory for the accumulators");
   auto kern = gemm_fp4_grouped_kernel<BT, HALF, WBUF, GROUPS, NACC>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(kern, Cfg::SMEM_BYTES, configured)) return -3;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(FP4_THREADS);
@@ -337,196 +310,17 @@ static int LaunchFp4V(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma
 template <int BT, bool HALF>
 static int LaunchFp4(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid,
                      cudaStream_t stream) {
-  // OGB_FP4_VARIANT (16-token tiles only): 0 = two expanded tiles in flight, 1 = four, 2 = four with the expander
-  // warps in two groups that alternate k-blocks, 3 = as 0 with four accumulators, 4 = as 2 with four accumulators
-  // Measured on B200 (gate/up of gpt-oss-20b, 32 tokens): 142 / 142 / 132 / 143 / 131 us for variants 0..4 - the kernel is bound
-  // by the rate at which the tensor core retires 128 x 16 x 16 instructions, not by the expansion, the copies or the
-  // accumulator chain; variant 4 is the default.
-  static const int variant = [] { const char* e = getenv("OGB_FP4_VARIANT"); return e ? atoi(e) : 4; }();
-  if constexpr (BT <= 16) {
-    if (variant == 1) return LaunchFp4V<BT, HALF, 4, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    if (variant == 2) return LaunchFp4V<BT, HALF, 4, 2, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    if (variant == 3) return LaunchFp4V<BT, HALF, 2, 1, 4>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    if (variant == 4) return LaunchFp4V<BT, HALF, 4, 2, 4>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-  }
+  // 16-token tiles: four expanded tiles in flight, the expander warps in two groups that alternate k-blocks, four
+  // accumulators; larger tiles: two expanded tiles, one group, one accumulator.  Measured on B200 (gate/up of gpt-oss-20b,
+  // 32 tokens): 131 us against 142 us for the single-group forms - the kernel is bound by the rate at which the tensor
+  // core retires 128 x 16 x 16 instructions, not by the expansion, the copies or the accumulator chain.
+  if constexpr (BT <= 16) return LaunchFp4V<BT, HALF, 4, 2, 4>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
   return LaunchFp4V<BT, HALF, 2, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-}
-
-// ---------------------------------------------------------------------------------------------- GEMV (up to 4 rows per tile)
-// Decode of one to four sequences: every expert tile holds at most four token rows, the tensor cores have nothing to do
-// and a 45-k-block chain per CTA is pure latency.  Two threads per weight row stream the records of the fp16 form straight
-// from global memory (a warp covers 512 contiguous bytes, eight k-blocks in flight per thread), the activations sit in
-// shared memory as fp32, a block of 32 costs 16 conversions (`cvt.rn.f16x2.e2m1x2`), 32 x rows FMAs and one multiply by
-// the block scale.  The k range is split over a thread-block cluster whose partial sums meet in the first CTA's shared
-// memory; that CTA adds the bias, applies the paired activation and stores.
-constexpr int FP4_GEMV_MAX_KB = 24;   // k-blocks per CTA (activations: rows * 24 * 64 fp32 of shared memory)
-constexpr int FP4_GEMV_AHEAD = 8;
-
-template <int MT>
-__global__ void __launch_bounds__(256)
-gemv_fp4_grouped_kernel(const void* __restrict__ A_, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, const GemmParams p) {
-  __shared__ __align__(16) float xs[MT][FP4_GEMV_MAX_KB * 64];
-  __shared__ float part[MT][GEMM_BLOCK_N];
-  const int tid = threadIdx.x, row = tid >> 1, half = tid & 1;
-  const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
-  if (p.pdl) { pdl_launch_dependents(); pdl_wait(); }
-  if (m_tile >= *p.grp.num_tiles) return;   // uniform over the CTA and over its cluster (the cluster spans z only)
-  const int row0 = p.grp.tile_row0[m_tile];
-  const int rows = min(p.grp.tile_rows[m_tile], MT);
-  const int expert = p.grp.tile_expert[m_tile];
-  const int kb0 = split * p.kb_per_split;
-  const int num_kb = max(0, min(p.kb_per_split, p.total_kb - kb0));
-  const uint8_t* rec0 = wpacked + ((size_t(expert) * p.total_kb + kb0) * n_tiles_per_expert + n_tile) * FP4_RECORD_BYTES;
-  const size_t rec_stride = size_t(n_tiles_per_expert) * FP4_RECORD_BYTES;
-
-  uint4 nb[FP4_GEMV_AHEAD];
-  uint32_t mq[FP4_GEMV_AHEAD];
-  auto fetch = [&](int kb, int slot) {
-    const uint8_t* r = rec0 + size_t(kb) * rec_stride;
-    nb[slot] = *reinterpret_cast<const uint4*>(r + row * 32 + half * 16);
-    mq[slot] = r[GEMM_BLOCK_N * 32 + row * 2 + half];
-  };
-#pragma unroll
-  for (int a = 0; a < FP4_GEMV_AHEAD; ++a)
-    if (a < num_kb) fetch(a, a);
-
-  // activations of this k range as fp32 (fp16 rows of the sorted activation matrix)
-  const __half* A = static_cast<const __half*>(A_);
-  for (int i = tid; i < num_kb * 64; i += 256) {
-#pragma unroll
-    for (int m = 0; m < MT; ++m) xs[m][i] = m < rows ? __half2float(A[size_t(row0 + m) * lda + size_t(kb0) * 64 + i]) : 0.f;
-  }
-  __syncthreads();
-
-  float acc[MT];
-#pragma unroll
-  for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-  for (int kbase = 0; kbase < num_kb; kbase += FP4_GEMV_AHEAD) {
-#pragma unroll
-    for (int a = 0; a < FP4_GEMV_AHEAD; ++a) {
-      const int kb = kbase + a;
-      if (kb >= num_kb) break;
-      const uint4 nib = nb[a];
-      const uint32_t m8 = mq[a];
-      if (kb + FP4_GEMV_AHEAD < num_kb) fetch(kb + FP4_GEMV_AHEAD, a);
-      const uint32_t words[4] = {nib.x, nib.y, nib.z, nib.w};
-      float dot[MT];
-#pragma unroll
-      for (int m = 0; m < MT; ++m) dot[m] = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t h0, h1, h2, h3;
-        asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-            "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-            "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-            "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-            "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-            "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
-            : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(words[j]));
-        const float2 w0 = __half22float2(*reinterpret_cast<__half2*>(&h0)), w1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
-        const float2 w2 = __half22float2(*reinterpret_cast<__half2*>(&h2)), w3 = __half22float2(*reinterpret_cast<__half2*>(&h3));
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          const float4 xa = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8]);
-          const float4 xb = *reinterpret_cast<const float4*>(&xs[m][kb * 64 + half * 32 + j * 8 + 4]);
-          dot[m] += w0.x * xa.x + w0.y * xa.y + w1.x * xa.z + w1.y * xa.w + w2.x * xb.x + w2.y * xb.y + w3.x * xb.z + w3.y * xb.w;
-        }
-      }
-      const uint16_t sbits = uint16_t(m8 << 10);                      // fp16 exponent field of the block scale
-      const float scale = __half2float(__ushort_as_half(sbits));
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[m] += scale * dot[m];
-    }
-  }
-#pragma unroll
-  for (int m = 0; m < MT; ++m) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], 1);
-  if (half == 0) {
-#pragma unroll
-    for (int m = 0; m < MT; ++m) part[m][row] = acc[m];
-  }
-  if (p.splits > 1) cluster_sync_all(); else __syncthreads();
-
-  if (split == 0) {
-    const int kind = p.act_pair;
-    const int n_out = kind ? p.N / 2 : p.N;
-    const uint32_t part_addr = smem_u32(&part[0][0]);
-    auto total = [&](int m, int r) {
-      float t = 0.f;
-      for (int s2 = 0; s2 < p.splits; ++s2) {
-        if (p.splits > 1) {
-          float v;
-          const uint32_t ra = dsmem_addr(part_addr + uint32_t(m * GEMM_BLOCK_N + r) * 4, uint32_t(s2));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-          t += v;
-        } else {
-          t += part[m][r];
-        }
-      }
-      const int n = n_tile * GEMM_BLOCK_N + r;
-      if (p.bias && n < p.N) t += bf2f(p.bias[size_t(expert) * p.N + n]);
-      return t;
-    };
-    const int rows_out = kind ? 64 : GEMM_BLOCK_N;
-    for (int item = tid; item < rows_out * MT; item += 256) {
-      const int m = item / rows_out, r = item % rows_out;
-      const int col = kind ? n_tile * 64 + r : n_tile * GEMM_BLOCK_N + r;
-      if (m >= rows || col >= n_out) continue;
-      float v = total(m, r);
-      if (kind) {
-        float u = total(m, r + 64);
-        if (kind == 2) {
-          const float g = p.act_limit > 0.f ? fminf(v, p.act_limit) : v;
-          if (p.act_limit > 0.f) u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
-          v = g / (1.f + __expf(-p.act_alpha * g)) * (u + 1.f);
-        } else {
-          v = silu(v) * u;
-        }
-      }
-      const size_t o = size_t(row0 + m) * p.ldc + col;
-      if (p.out_fp32 == 1) reinterpret_cast<float*>(p.C)[o] = v;
-      else if (p.out_fp32 == 2) reinterpret_cast<__half*>(p.C)[o] = __float2half_rn(v);
-      else reinterpret_cast<__nv_bfloat16*>(p.C)[o] = f2bf(v);
-    }
-  }
-  if (p.splits > 1) cluster_sync_all();   // peers keep their shared memory alive until the first CTA has read it
-}
-
-template <int MT>
-static int LaunchGemvFp4(const void* A, int lda, const uint8_t* wp, int n_tiles, const GemmParams& p, int max_tiles, cudaStream_t stream) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(n_tiles, max_tiles, p.splits);
-  cfg.blockDim = dim3(256);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attrs[2];
-  int na = 0;
-  if (p.splits > 1) {
-    attrs[na].id = cudaLaunchAttributeClusterDimension;
-    attrs[na].val.clusterDim.x = 1; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = unsigned(p.splits);
-    ++na;
-  }
-  if (p.pdl) {
-    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = unsigned(na);
-  return cudaLaunchKernelEx(&cfg, gemv_fp4_grouped_kernel<MT>, A, lda, wp, n_tiles, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace ogb
 
 using namespace ogb;
-
-// Registers (or clears, with nullptr) the device buffer of 9 * 64 int64 that receives the k-block trace of later launches.
-OGB_API int ogb_fp4_trace_buffer(void* buf) {
-#ifndef OGB_FP4_TRACE
-  if (buf) return -5;   // built without the trace
-#endif
-  long long* p = static_cast<long long*>(buf);
-  return cudaMemcpyToSymbol(g_fp4_trace, &p, sizeof(p)) == cudaSuccess ? 0 : -4;
-}
 
 // Bytes of the repacked experts: `experts` matrices of [N, K] e2m1 codes (K a multiple of 64; N is padded to 128).
 OGB_API long long ogb_fp4_packed_bytes(int experts, int N, int K) {
@@ -536,7 +330,7 @@ OGB_API long long ogb_fp4_packed_bytes(int experts, int N, int K) {
 // Grouped expert GEMM over packed MXFP4 experts; arguments as ogb_moe_gemm with `Wpacked` in the record layout above.
 // flags: bit 0 fp32 output, bit 1 paired activation, bit 4 fp16 form (A holds fp16 rows, records in the fp16 layout),
 // bit 5 fp16 output.  max_rows_per_tile: an upper bound on the rows of any tile known on the host (the number of tokens
-// of the step: an expert receives a token at most once), 0 if unknown; up to 4 selects the GEMV.
+// of the step: an expert receives a token at most once), 0 if unknown (not used by the kernel selection).
 OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
                              const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
                              const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
@@ -564,33 +358,8 @@ OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* 
   p.pdl = pdl_enabled;
   p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
   const int n_tiles = (N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N;
-  // OGB_FP4_TMA=1: records arrive as boxes of a byte tensor map instead of untiled bulk copies (measured: no difference)
-  // Steps of one to four tokens can take the weight-streaming GEMV (OGB_FP4_GEMV=1).  Opt-in: measured on B200 at the
-  // gpt-oss-20b shapes it is slower than the tensor-core kernel - gate/up 54 vs 27 us at 1 token, 123 vs ~30 us at 4; down
-  // 31 vs 23 us at 1 token (three conversions per pair of weights on the CUDA cores against one in the tile expansion).
-  static const int gemv_env = [] { const char* e = getenv("OGB_FP4_GEMV"); return (e && e[0] == '1') ? 1 : 0; }();
-  if (gemv_env && half && max_rows_per_tile > 0 && max_rows_per_tile <= 4 && !(flags & 1)) {
-    int sm_count = 148;
-    { int dev = 0; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
-    const int est_tiles = rows_total < max_tiles ? rows_total : max_tiles;
-    int gs = (p.total_kb + FP4_GEMV_MAX_KB - 1) / FP4_GEMV_MAX_KB;
-    while (gs < 8 && n_tiles * est_tiles * gs < 4 * sm_count && p.total_kb / (gs * 2) >= 2) gs *= 2;
-    if (gs > 8) gs = 8;
-    int per = (p.total_kb + gs - 1) / gs;
-    while (gs > 1 && per * (gs - 1) >= p.total_kb) { --gs; per = (p.total_kb + gs - 1) / gs; }
-    if (per <= FP4_GEMV_MAX_KB) {
-      GemmParams g = p;
-      g.splits = gs; g.kb_per_split = per;
-      return LaunchGemvFp4<4>(A, lda, static_cast<const uint8_t*>(Wpacked), n_tiles, g, max_tiles, stream);
-    }
-  }
-  static const int tma_env = [] { const char* e = getenv("OGB_FP4_TMA"); return (e && e[0] == '1') ? 1 : 0; }();
-  CUtensorMap tw = ta;
-  int w_by_tma = 0;
-  if (tma_env) {
-    const long long rows128 = (long long)experts * p.total_kb * n_tiles * (FP4_RECORD_BYTES / 128);
-    w_by_tma = MakeMapBytes128(&tw, Wpacked, rows128, FP4_RECORD_BYTES / 128) ? 1 : 0;
-  }
+  CUtensorMap tw = ta;   // unused: records arrive by untiled bulk copies
+  const int w_by_tma = 0;
   dim3 grid(n_tiles, max_tiles, 1);
   const uint8_t* wp = static_cast<const uint8_t*>(Wpacked);
   switch (bt) {

@@ -86,8 +86,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
   }
-  const int n_acc = p.n_acc > 1 ? p.n_acc : 1;
-  const uint32_t tmem_cols = uint32_t(max(32, BT * n_acc));   // a power of two: BT and n_acc are
+  constexpr uint32_t tmem_cols = Cfg::TMEM_COLS;
   if (warp == 2) {
     tmem_alloc(tmem_slot, tmem_cols);
     tmem_relinquish();
@@ -118,9 +117,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       // before waiting for the producer of the activations.
       const int pre = min(STAGES, num_kb);
       for (int i = 0; i < pre; ++i) load_w(i);
-      // The rest of this CTA's weight stream goes to L2 while the previous kernel is still finishing (opt-in)
-      if (p.l2_prefetch)
-        for (int i = pre; i < num_kb; ++i) tma_prefetch_l2_2d(&tmap_w, (kb0 + i) * GEMM_BLOCK_K, w_row0 + n_tile * GEMM_BLOCK_N);
       if (p.pdl) pdl_wait();
       for (int i = 0; i < pre; ++i) load_a(i);
       int issued = pre;
@@ -152,8 +148,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t w = smem_u32(stage_w(s)), a = smem_u32(stage_a(s));
 #pragma unroll
         for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
-          umma_f16(tmem_base + uint32_t((k & (n_acc - 1)) * BT), umma_desc_sw128(w + k * GEMM_UMMA_K * 2),
-                   umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc, (i > 0 || k >= n_acc) ? 1u : 0u);
+          umma_f16(tmem_base, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc,
+                   (i > 0 || k > 0) ? 1u : 0u);
         umma_commit(&empty_bar[s]);
       }
       if (ok) umma_commit(accum_bar);
@@ -195,7 +191,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (dead) *abort_flag = 1;
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0, n_acc);
+  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0);
 
   tc_fence_before();
   __syncthreads();
@@ -274,12 +270,9 @@ bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, 
 template <int BT>
 static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BT>;
-  static bool configured = false;
   auto kern = gemm_tcgen05_kernel<BT>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(kern, Cfg::SMEM_BYTES, configured)) return -3;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(GEMM_THREADS);
@@ -527,11 +520,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const
 
 static int LaunchPersistent(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, int n_tiles, int m_tiles, int sm_count,
                             cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PERS_SMEM_BYTES) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(gemm_tcgen05_persistent_kernel, PERS_SMEM_BYTES, configured)) return -3;
   const int tiles = n_tiles * m_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(unsigned(tiles < sm_count ? tiles : sm_count));
@@ -544,326 +534,6 @@ static int LaunchPersistent(const CUtensorMap& tw, const CUtensorMap& ta, const 
   cfg.attrs = &attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, gemm_tcgen05_persistent_kernel, tw, ta, p, n_tiles, m_tiles) == cudaSuccess ? 0 : -4;
-}
-
-// ------------------------------------------------------------------------------------------ stream-K decode kernel
-// Decode-sized problems (one token tile of 16..64) are bound by the weight stream, and a grid of (feature tiles x k splits)
-// CTAs rarely divides the GPU evenly: 224 gate/up tiles leave half the SMs with twice the work of the others, and every CTA
-// pays its own prologue, pipeline fill and epilogue.  Here one persistent CTA per SM takes an EQUAL share of all
-// (tile, k-block) units, laid out tile after tile, and its TMA producer streams that share without a bubble at tile
-// boundaries.  A share therefore covers the tail of one tile, whole tiles, and the head of another.  The accumulator is
-// double buffered in tensor memory; for every segment the epilogue warps either
-//   * own the tile (the segment contains its FIRST k-block): add the partial sums of the following CTAs that hold the
-//     tile's later k-blocks, in CTA order (deterministic), then bias / activation / residual / store; or
-//   * contribute: write the fp32 partial tile to this CTA's slot of a scratch buffer and stamp the slot (release store)
-//     with the launch's epoch, which the owner polls (bounded, acquire) before reading the slot — no barrier, no
-//     clearing of the scratch between launches.  Contributors never wait on anyone and all CTAs are resident at once
-//     (one per SM), so the owner's wait cannot deadlock; it comes last in the owner's share and concerns data produced
-//     first in the contributors' shares, so it does not stall the streams either.
-struct StreamKParams {
-  float* scratch;        // [grid][BT * 128] fp32 partial tiles
-  uint32_t* flags;       // [grid] epoch stamp of the partial tile in each slot
-  uint32_t* epoch;       // [0] launches finished, [1] CTAs of the running launch that are done
-};
-
-template <int BT>
-struct SKCfg {
-  static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
-  static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES;
-  static constexpr int PART_BYTES = BT * GEMM_BLOCK_N * 4;
-  static constexpr int MAX_STAGES = (200 * 1024 - PART_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
-  static constexpr int TMEM_COLS = 2 * BT < 32 ? 32 : 2 * BT;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PART_BYTES + 1024 + 256;
-  static constexpr int SLOT_FLOATS = BT * GEMM_BLOCK_N;
-};
-
-template <int BT>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p,
-                    const StreamKParams sk, int n_tiles) {
-  using Cfg = SKCfg<BT>;
-  constexpr int STAGES = Cfg::STAGES;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* part = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);   // [BT][128] fp32
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::PART_BYTES);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* acc_full = empty_bar + STAGES;
-  uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* epi_abort = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  volatile uint32_t* epoch_sh = reinterpret_cast<volatile uint32_t*>(tmem_slot + 3);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KB = p.total_kb;
-  const long long U = (long long)n_tiles * KB;
-  const int G = gridDim.x, c = blockIdx.x;
-  auto share_begin = [&](int cta) { return (U * cta) / G; };
-  const long long u0 = share_begin(c), u1 = share_begin(c + 1);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
-    *abort_flag = 0;
-    *epi_abort = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_a);
-  }
-  if (warp == 2) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  if (p.pdl) pdl_launch_dependents();
-  auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
-  auto stage_w = [&](int s) { return smem + s * Cfg::STAGE_BYTES; };
-  auto stage_a = [&](int s) { return smem + s * Cfg::STAGE_BYTES + W_TILE_BYTES; };
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ TMA producer: the whole share, back to back
-      const int n_units = int(u1 - u0);
-      auto load_w = [&](int i) {
-        const long long u = u0 + i;
-        mbar_expect_tx(&full_bar[i % STAGES], Cfg::STAGE_BYTES);
-        tma_load_2d(stage_w(i % STAGES), &tmap_w, &full_bar[i % STAGES], int(u % KB) * GEMM_BLOCK_K, int(u / KB) * GEMM_BLOCK_N);
-      };
-      auto load_a = [&](int i) {
-        tma_load_2d(stage_a(i % STAGES), &tmap_a, &full_bar[i % STAGES], int((u0 + i) % KB) * GEMM_BLOCK_K, 0);
-      };
-      const int pre = min(STAGES, n_units);
-      for (int i = 0; i < pre; ++i) load_w(i);      // weights are never written by an earlier kernel of the stream
-      if (p.pdl) pdl_wait();
-      for (int i = 0; i < pre; ++i) load_a(i);
-      int issued = pre;
-      for (int i = pre; i < n_units; ++i) {
-        if (!mbar_wait_bounded(&empty_bar[i % STAGES], ((i / STAGES) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); break; }
-        load_w(i);
-        load_a(i);
-        ++issued;
-      }
-      if (*abort_flag) {
-        volatile int never = 0;
-        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait_bounded(&full_bar[i % STAGES], (i / STAGES) & 1, &never, 200000000ull);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer: one accumulator per segment, alternating
-      constexpr uint32_t idesc = umma_idesc_f16(GEMM_BLOCK_N, BT, 1);
-      int it = 0, j = 0;
-      bool ok = true;
-      for (long long u = u0; u < u1 && ok; ++j) {
-        const long long seg_end = min(u1, (u / KB + 1) * KB);
-        const int buf = j & 1;
-        if (j >= 2 && !mbar_wait_bounded(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort_flag)) { fail(OGB_ERR_WAIT_MMA); ok = false; break; }
-        tc_fence_after();
-        const uint32_t acc = tmem_base + uint32_t(buf * BT);
-        for (int kk = 0; u < seg_end; ++u, ++kk, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); ok = false; break; }
-          tc_fence_after();
-          const uint32_t w = smem_u32(stage_w(s)), a = smem_u32(stage_a(s));
-#pragma unroll
-          for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k)
-            umma_f16(acc, umma_desc_sw128(w + k * GEMM_UMMA_K * 2), umma_desc_sw128(a + k * GEMM_UMMA_K * 2), idesc, (kk > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&empty_bar[s]);
-        }
-        if (ok) umma_commit(&acc_full[buf]);
-      }
-    }
-  } else {
-    // -------------------------------------------------------------------- epilogue warps 2..5
-    const int et = threadIdx.x - 64;
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const bool pair = p.act_pair != 0;
-    const int OCT = pair ? 8 : 16;
-    const int n_out = pair ? p.N / 2 : p.N;
-    if (p.pdl) pdl_wait();     // scratch, epoch, residual reads and all stores come after the previous kernel has finished
-    if (et == 0) *epoch_sh = *reinterpret_cast<volatile uint32_t*>(sk.epoch);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    const uint32_t flag = comm_flag(*epoch_sh);
-    bool dead = *reinterpret_cast<volatile int*>(p.status) != 0;
-    int j = 0;
-    for (long long u = u0; u < u1; ++j) {
-      const int tile = int(u / KB);
-      const long long tile_begin = (long long)tile * KB, seg_end = min(u1, tile_begin + KB);
-      // The CTA that holds a tile's FIRST k-blocks owns it.  That segment is the last one of the owner's share, while the
-      // rest of the tile is the first (or only) segment of the following CTAs: the owner waits at the end of its work for
-      // partials that were produced at the start of the others', so the wait never holds up anybody's weight stream.
-      const bool owner = u == tile_begin;
-      const bool has_contrib = seg_end < tile_begin + KB;   // later k-blocks of this tile live in the following CTAs
-      const int buf = j & 1;
-      if (!mbar_wait_bounded(&acc_full[buf], (j >> 1) & 1, abort_flag, 4000000000ull)) { fail(OGB_ERR_WAIT_MMA); *epi_abort = 1; }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*epi_abort) break;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buf * BT);
-      if (!owner) {
-        // contributor: the fp32 partial tile goes to this CTA's scratch slot ([token column][row]: a warp writes 128
-        // contiguous bytes), then one release store stamps the slot with the launch's epoch
-        float* slot = sk.scratch + size_t(c) * Cfg::SLOT_FLOATS;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BT; c0 += 16) {
-          uint32_t r0[16];
-          tmem_ld16(taddr + c0, r0);
-          tmem_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 16; ++q) slot[(c0 + q) * GEMM_BLOCK_N + row] = __uint_as_float(r0[q]);
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk.flags + c), "r"(flag) : "memory");
-      } else {
-        // owner: own sums parked for the transposing store loop, then the contributors' added in CTA order
-        int c_last = c;
-        if (has_contrib) while (c_last + 1 < G && share_begin(c_last + 1) < tile_begin + KB) ++c_last;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BT; c0 += 16) {
-          uint32_t r0[16];
-          tmem_ld16(taddr + c0, r0);
-          tmem_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 16; ++q) part[(c0 + q) * GEMM_BLOCK_N + row] = __uint_as_float(r0[q]);
-        }
-        for (int cc = c + 1; cc <= c_last; ++cc) {
-          // wait (bounded) for the contributor's stamp, then read its tile with plain L2 loads: every thread the positions it owns
-          if (!dead) {
-            const uint64_t t0 = global_timer_ns();
-            uint32_t seen, spins = 0;
-            while (true) {
-              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(sk.flags + cc) : "memory");
-              if (seen == flag) break;
-              if ((++spins & 0x3f) == 0 && (*reinterpret_cast<volatile int*>(p.status) != 0 || global_timer_ns() - t0 > 2000000000ull)) {
-                atomicMax(p.status, OGB_ERR_WAIT_PEER);
-                dead = true;
-                break;
-              }
-            }
-          }
-          const float* slot = sk.scratch + size_t(cc) * Cfg::SLOT_FLOATS;
-#pragma unroll 1
-          for (int q0 = 0; q0 < BT; q0 += 16) {     // 16 independent L2 loads in flight per thread
-            float v[16];
-#pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] = __ldcg(slot + (q0 + q) * GEMM_BLOCK_N + row);
-#pragma unroll
-            for (int q = 0; q < 16; ++q) part[(q0 + q) * GEMM_BLOCK_N + row] += v[q];
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int col0 = tile * (pair ? 64 : 128);
-        for (int item = et; item < BT * OCT; item += 128) {
-          const int m = item / OCT, oc = item % OCT;
-          if (m >= p.M) continue;
-          float v[8];
-          const float* src = part + m * GEMM_BLOCK_N + oc * 8;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) v[q] = src[q];
-          if (p.bias) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) if (tile * GEMM_BLOCK_N + oc * 8 + q < p.N) v[q] += bf2f(p.bias[tile * GEMM_BLOCK_N + oc * 8 + q]);
-          }
-          if (pair) {
-            float w2[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) w2[q] = src[64 + q];
-            if (p.bias) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) w2[q] += bf2f(p.bias[tile * GEMM_BLOCK_N + 64 + oc * 8 + q]);
-            }
-            if (p.act_pair == 1) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) v[q] = silu(v[q]) * w2[q];
-            } else {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float g = p.act_limit > 0.f ? fminf(v[q], p.act_limit) : v[q];
-                const float w = p.act_limit > 0.f ? fminf(fmaxf(w2[q], -p.act_limit), p.act_limit) : w2[q];
-                v[q] = g / (1.f + __expf(-p.act_alpha * g)) * (w + 1.f);
-              }
-            }
-          }
-          const int col = col0 + oc * 8;
-          if (col >= n_out) continue;
-          if (p.residual) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) if (col + q < n_out) v[q] += bf2f(p.residual[size_t(m) * p.ldr + col + q]);
-          }
-          if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
-            if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-            } else {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) if (col + q < n_out) dst[q] = v[q];
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;
-            if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-            } else {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) if (col + q < n_out) dst[q] = f2bf(v[q]);
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // `part` is rewritten by the next owned segment
-      }
-      tc_fence_before();
-      mbar_arrive(&acc_empty[buf]);
-      u = seg_end;
-    }
-    if (dead) *abort_flag = 1;
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-  // the last CTA of the launch closes the epoch (every CTA gets here, also after an abort)
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(sk.epoch + 1, 1u) == gridDim.x - 1) {
-      sk.epoch[1] = 0;
-      __threadfence();
-      *reinterpret_cast<volatile uint32_t*>(sk.epoch) = *reinterpret_cast<volatile uint32_t*>(sk.epoch) + 1;
-    }
-  }
-}
-
-// Per-device stream-K scratch (registered once by the host: ogb_streamk_register).
-static StreamKParams g_sk[16] = {};
-static int g_sk_grid[16] = {};
-
-template <int BT>
-static int LaunchStreamK(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const StreamKParams& sk, int n_tiles, int grid,
-                         cudaStream_t stream) {
-  using Cfg = SKCfg<BT>;
-  static bool configured = false;
-  auto kern = gemm_streamk_kernel<BT>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
-    configured = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(unsigned(grid));
-  cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = p.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, tw, ta, p, sk, n_tiles) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace ogb
@@ -879,13 +549,12 @@ const CommParams* ogb_comm_params(int device) { return (device >= 0 && device < 
 
 OGB_API int ogb_gemm_token_tile(int M, int dual) {
   (void)dual;
-  // prefill-sized problems: 256-token tiles with one CTA per SM, or (OGB_GEMM_PREFILL_TILE=128) 128-token tiles with two
-  static const int big = [] { const char* e = getenv("OGB_GEMM_PREFILL_TILE"); return (e && atoi(e) == 128) ? 128 : 256; }();
+  // prefill-sized problems: 256-token tiles, one CTA per SM
   if (M <= 16) return 16;
   if (M <= 32) return 32;
   if (M <= 64) return 64;
   if (M <= 128) return 128;
-  return big;
+  return 256;
 }
 
 // Number of split-K partitions (cluster size along z: 1, 2, 4 or 8): the largest that still fits every CTA of the launch
@@ -934,23 +603,10 @@ OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void*
   return 0;
 }
 
-// Scratch of the stream-K decode kernel for a device: `scratch` holds max_ctas slots of 32 KiB (a 64 x 128 fp32 tile), `flags`
-// max_ctas zero-initialised words, `epoch` two zero-initialised words.  Without a registration decode GEMMs use the
-// (tiles x k-splits) kernel.
-OGB_API int ogb_streamk_register(int device, void* scratch, void* flags, void* epoch, int max_ctas) {
-  if (device < 0 || device >= 16) return -1;
-  g_sk[device].scratch = static_cast<float*>(scratch);
-  g_sk[device].flags = static_cast<uint32_t*>(flags);
-  g_sk[device].epoch = static_cast<uint32_t*>(epoch);
-  g_sk_grid[device] = max_ctas;
-  return 0;
-}
-
 // flags bit 0: fp32 output; bit 1: paired silu(gate)*up epilogue (N = 2 * output columns, rows
 // interleaved in blocks of 64); bit 2: fused all-reduce over the registered symmetric buffers; bit 3: fused
 // reduce-scatter by token rows instead (rank r ends up with rows [r * ceil(M / world), ...) of the sum, written as
-// rows 0.. of C; residual, if given, is that slice too); bit 4: activations gathered from the ranks' pushes; bit 5: take the
-// stream-K kernel when the shape allows.
+// rows 0.. of C; residual, if given, is that slice too); bit 4: activations gathered from the ranks' pushes.
 OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
                           const void* bias, const void* residual, int ldr, int flags, int splits, int device, int* status,
                           int sm_count, void* stream_) {
@@ -984,14 +640,6 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.status = status;
   p.pdl = pdl_enabled;
-  // OGB_GEMM_L2_PREFETCH=1: decode-sized launches prefetch each CTA's whole weight stream into L2 before the dependency wait.
-  // Opt-in: measured on B200 at 64 tokens it only adds traffic ahead of the demand loads - gate/up 42.9 -> 55.0 us, down
-  // 28.0 -> 31.0 us, qkv 15.8 -> 16.4 us, o 13.0 -> 13.2 us; the decode step 5.54 -> 6.16 ms.
-  static const int l2_prefetch = [] { const char* e = getenv("OGB_GEMM_L2_PREFETCH"); return (e && e[0] == '1') ? 1 : 0; }();
-  p.l2_prefetch = l2_prefetch && pdl_enabled && bt <= 64;
-  // OGB_GEMM_NACC=2 / 4: decode-sized tiles spread the k-steps over that many accumulators (independent tcgen05.mma chains)
-  static const int nacc_env = [] { const char* e = getenv("OGB_GEMM_NACC"); return e ? atoi(e) : 0; }();
-  if ((nacc_env == 2 || nacc_env == 4) && bt * nacc_env <= 128) p.n_acc = nacc_env;
   if (fused_ar) {
     if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
     const CommParams& c = g_comm[device];
@@ -1015,24 +663,6 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     if ((K % 8) || (long long)per * K > c.plane_elems) return -2;
     p.comm = c;          // the mainloop needs the buffer and epoch pointers; the epilogue stays local unless bits 2/3 are set
     p.ag_rows = per;
-  }
-  // Opt-in (flags bit 5 or OGB_GEMM_STREAMK=1).  Measured on B200 at 64 tokens, Llama-3.1-8B shapes, one persistent CTA per SM
-  // against the (tiles x k-splits) grid with two CTAs per SM: qkv 20.9 vs 15.7 us, o 23.0 vs 12.9, gate/up 45.5 vs 42.8,
-  // down 36.3 vs 27.6 — the balanced shares do not make up for the halved number of streams per SM and the fix-up pass.
-  static const int streamk = [] { const char* e = getenv("OGB_GEMM_STREAMK"); return (e && e[0] == '1') ? 1 : 0; }();
-  if ((streamk || (flags & 32)) && auto_split && bt <= 64 && m_tiles == 1 && !p.comm_epilogue && p.ag_rows == 0 && device >= 0 && device < 16 &&
-      g_sk[device].scratch) {
-    // equal shares of all (tile, k-block) units over one persistent CTA per SM; worth it when every CTA gets a few k-blocks
-    const long long units = (long long)n_tiles * total_kb;
-    int grid = sm_count < g_sk_grid[device] ? sm_count : g_sk_grid[device];
-    if (units >= 8ll * grid) {
-      p.splits = 1; p.kb_per_split = total_kb;
-      switch (bt) {
-        case 16: return LaunchStreamK<16>(tw, ta, p, g_sk[device], n_tiles, grid, stream);
-        case 32: return LaunchStreamK<32>(tw, ta, p, g_sk[device], n_tiles, grid, stream);
-        case 64: return LaunchStreamK<64>(tw, ta, p, g_sk[device], n_tiles, grid, stream);
-      }
-    }
   }
   static const int persistent = [] { const char* e = getenv("OGB_GEMM_PERSISTENT"); return (e && e[0] == '0') ? 0 : 1; }();
   if (persistent && auto_split && bt == 256 && splits == 1 && !p.comm_epilogue && p.ag_rows == 0 && n_tiles * m_tiles >= sm_count)
@@ -1079,8 +709,6 @@ OGB_API int ogb_moe_gemm(const void* A, int lda, const void* W, int ldw, void* C
   p.status = status;
   p.pdl = pdl_enabled;
   p.grp.tile_expert = tile_expert; p.grp.tile_row0 = tile_row0; p.grp.tile_rows = tile_rows; p.grp.num_tiles = num_tiles;
-  static const int nacc_env = [] { const char* e = getenv("OGB_GEMM_NACC"); return e ? atoi(e) : 0; }();
-  if ((nacc_env == 2 || nacc_env == 4) && bt * nacc_env <= 128) p.n_acc = nacc_env;
   dim3 grid((N + GEMM_BLOCK_N - 1) / GEMM_BLOCK_N, max_tiles, 1);
   switch (bt) {
     case 16: return Launch<16>(tw, ta, p, grid, stream);

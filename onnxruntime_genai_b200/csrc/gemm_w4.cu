@@ -201,12 +201,9 @@ bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, 
 template <int BT>
 static int LaunchW4(const CUtensorMap& ta, const uint8_t* wp, int n_tiles_total, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = W4Cfg<BT>;
-  static bool configured = false;
   auto kern = gemm_w4_kernel<BT>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(kern, Cfg::SMEM_BYTES, configured)) return -3;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(GEMM_THREADS);

@@ -19,7 +19,6 @@ int ogb_sm_count(int device);
 int ogb_gemm_token_tile(int M, int dual);
 int ogb_gemm_max_active_clusters(int bt, int splits);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
-int ogb_streamk_register(int device, void* scratch, void* flags, void* epoch, int max_ctas);
 int ogb_comm_register(int device, int world, int rank, void** buf, void* epoch, long long plane_elems);
 // flags: bit 0 fp32 output, bit 1 paired silu(gate)*up epilogue, bit 2 fused tensor-parallel all-reduce,
 // bit 3 fused reduce-scatter by token rows (sequence-parallel form)
@@ -57,10 +56,6 @@ int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int l
                      const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
                      const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
                      int max_rows_per_tile, int* status, void* stream);
-
-// Debug builds (-DOGB_FP4_TRACE) only: registers a device buffer of 9 * 64 int64 that receives clock64() stamps of one CTA's
-// k-block hand-overs (nullptr clears it); returns -5 in a build without the trace.
-int ogb_fp4_trace_buffer(void* buf);
 
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);

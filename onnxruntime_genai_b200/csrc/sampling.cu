@@ -790,11 +790,8 @@ OGB_API int ogb_sample(const float* logits, long long row_stride, int rows, int 
   if (rows <= 0) return 0;
   SampleParams p{logits, row_stride, vocab, rows, top_k, top_p, temperature, seeds, positions, out};
   constexpr int kDyn = (SAMP_THREADS / 32) * 256 * 8;  // 64 KiB of per-warp histograms
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(sample_kernel, kDyn, configured)) return -3;
   launch_pdl(sample_kernel, dim3(rows), dim3(SAMP_THREADS), kDyn, static_cast<cudaStream_t>(stream), p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -811,11 +808,8 @@ OGB_API int ogb_topk(const float* x, long long row_stride, int rows, int n, int 
   if (k < 1 || k > TOPK_MAX) return -1;
   TopKParams p{x, row_stride, n, rows, k, mode, add, out_vals, out_idx};
   constexpr int kDyn = (SAMP_THREADS / 32) * 256 * 8;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(topk_kernel, kDyn, configured)) return -3;
   topk_kernel<<<rows, SAMP_THREADS, kDyn, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -842,11 +836,8 @@ OGB_API int ogb_verify_sampled(const float* logits, long long row_stride, int vo
   VerifyParams p{logits, row_stride, vocab, K, top_k, top_p, temperature, seeds, positions, draft, q_idx, q_prob, q_n, q_stride,
                  scratch, scratch + (K + 1), accept_prob, reinterpret_cast<unsigned int*>(scratch + 2 * (K + 1)), accepted, commit, status};
   constexpr int kDyn = (SAMP_THREADS / 32) * 256 * 8;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(verify_sampled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn) != cudaSuccess) return -3;
-    configured = true;
-  }
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(verify_sampled_kernel, kDyn, configured)) return -3;
   verify_sampled_kernel<<<K + 1, SAMP_THREADS, kDyn, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -383,14 +383,18 @@ StepOutcome EngineCore::Commit(const int32_t* tokens, size_t n) {
     if (!e.samples) continue;
     r.prefill_ = false;
     const int32_t tok = tokens[i];
+    // A sampled end-of-sequence token is part of the sequence and of the stream the caller reads, as in the reference
+    // engine (src/engine/request.cpp CommitStep pushes whatever the search appended, and GreedySearch_Cpu appends the
+    // EOS it selected, src/search.cpp:266-296): it ends the turn, is never fed to the sampler again, and is the first
+    // token of the prefill of a continued turn.
     const bool eos = std::find(r.eos_ids_.begin(), r.eos_ids_.end(), tok) != r.eos_ids_.end();
     bool complete = eos;
-    if (!eos) {
+    if (int(r.tokens_.size()) < r.opt_.max_length) {
       r.tokens_.push_back(tok);
       r.unseen_.push_back(tok);
       ++metrics_.tokens_generated;
-      if (int(r.tokens_.size()) >= r.opt_.max_length) complete = true;
     }
+    if (int(r.tokens_.size()) >= r.opt_.max_length) complete = true;
     if (complete) { r.status_ = RequestStatus::kTurnComplete; ++metrics_.requests_completed; }
     if (std::find(ready_.begin(), ready_.end(), e.request) == ready_.end()) ready_.push_back(e.request);
   }

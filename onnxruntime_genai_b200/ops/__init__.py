@@ -40,19 +40,15 @@ class _Workspace:
         self.status = _lib.lib().ogb_status_device_ptr(idx)
         self.sm_count = _lib.lib().ogb_sm_count(idx)
         self.attn_ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)
-        # stream-K decode GEMM: one 32 KiB slot (a 64 x 128 fp32 partial tile) and one stamp per persistent CTA + the launch counter
-        self.sk_scratch = torch.zeros(self.sm_count * (32 << 10), dtype=torch.uint8, device=device)
-        self.sk_flags = torch.zeros(self.sm_count, dtype=torch.int32, device=device)
-        self.sk_epoch = torch.zeros(2, dtype=torch.int32, device=device)
-        rc = _lib.lib().ogb_streamk_register(idx, self.sk_scratch.data_ptr(), self.sk_flags.data_ptr(), self.sk_epoch.data_ptr(),
-                                             self.sm_count)
-        if rc != 0:
-            raise RuntimeError(f"ogb_streamk_register failed with {rc}")
+        self._retired = []
 
     def attn_scratch(self, nbytes: int) -> torch.Tensor:
         if nbytes > self.attn_ws.numel():
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("attention scratch too small during CUDA graph capture; warm up eagerly first")
+            # captured graphs hold the raw address of the buffer they were recorded with: a replaced buffer is kept alive
+            # for the life of the process instead of going back to the allocator, where a replay would write into it
+            self._retired.append(self.attn_ws)
             self.attn_ws = torch.empty(int(nbytes * 1.25), dtype=torch.uint8, device=self.device)
         return self.attn_ws
 
@@ -114,7 +110,7 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) ->
 
 
 # ------------------------------------------------------------------------------------------ GEMM
-GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A, GEMM_STREAM_K = 1, 2, 4, 8, 16, 32
+GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A = 1, 2, 4, 8, 16
 
 
 def _gemm(x, w, out, bias, residual, flags, splits):
@@ -136,7 +132,7 @@ def _gemm_w4(x, w, out, bias, residual, flags, splits):
     return out
 
 
-def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None, stream_k=False):
+def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None):
     """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous).  With all_reduce the
     partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory.
     reduce_scatter=(rank, world): the sum is scattered by token rows instead (sequence-parallel form): the result has
@@ -160,8 +156,7 @@ def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, a
         rows_out = max(0, min(per, x.shape[0] - rank * per))
     if out is None:
         out = torch.empty(rows_out, w.shape[0], dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
-    flags = ((GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0) | (GEMM_REDUCE_SCATTER if reduce_scatter else 0) |
-             (GEMM_STREAM_K if stream_k else 0))
+    flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0) | (GEMM_REDUCE_SCATTER if reduce_scatter else 0)
     return _gemm(x, w, out, bias, residual, flags, splits)
 
 
@@ -190,7 +185,7 @@ def interleave_gate_up(w: torch.Tensor, block: int = 64) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(w.shape).contiguous()
 
 
-def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False, stream_k=False):
+def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False):
     """act(x @ Wg.T) * (x @ Wu.T).  w is [2I, K]: stacked [Wg; Wu], or (interleaved=True) blocks of 64 gate
     rows + 64 up rows as produced by interleave_gate_up (the layout the fused kernel needs)."""
     if isinstance(w, W4Weight):
@@ -215,7 +210,7 @@ def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=Fal
         return act_mul(y.contiguous(), act)
     if out is None:
         out = torch.empty(x.shape[0], inter, dtype=torch.bfloat16, device=x.device)
-    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR | (GEMM_STREAM_K if stream_k else 0), splits)
+    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR, splits)
 
 
 def act_mul(x, act="silu"):

@@ -25,7 +25,6 @@ _SIGS = {
     "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "ogb_gemm_max_active_clusters": (c_int, [c_int, c_int]),
     "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P]),
-    "ogb_streamk_register": (c_int, [c_int, _P, _P, _P, c_int]),
     "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, c_longlong]),
     "ogb_w4_packed_bytes": (c_longlong, [c_int, c_int]),
     "ogb_gemm_w4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P]),

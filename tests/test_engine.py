@@ -39,10 +39,10 @@ def closed_form(prompt, max_length):
     out = []
     while len(seq) < max_length:
         t = (seq[0] + seq[-1] + len(seq)) % VOCAB
-        if t == EOS:
-            break
         seq.append(t)
         out.append(t)
+        if t == EOS:      # the end-of-sequence token is streamed, then the turn ends
+            break
     return out
 
 
@@ -125,12 +125,14 @@ def test_isolated_equals_simultaneous_and_staggered(model):
     assert [outs[id(r)] for r in reqs] == want
 
 
-def test_eos_is_not_returned_and_max_length_is_respected(model):
-    # first=1, current=62, length 2 -> (1 + 62 + 2) % 64 == 1 == EOS immediately
+def test_eos_ends_the_turn_and_is_streamed_and_max_length_is_respected(model):
+    # first=1, current=62, length 2 -> (1 + 62 + 2) % 64 == 1 == EOS immediately.  The sampled EOS is appended to the
+    # sequence and reaches the caller (reference: src/engine/request.cpp CommitStep + src/search.cpp:266-296), then the turn ends.
     engine, _ = make_engine(model)
     r = request(model, [1, 62])
     engine.add_request(r)
-    assert run_all(engine, [r]) == [[]] and r.status == native.RequestStatus.Closed
+    assert run_all(engine, [r]) == [[EOS]] and r.status == native.RequestStatus.Closed
+    assert list(r.tokens()) == [1, 62, EOS]
     engine, _ = make_engine(model)
     r = request(model, [5, 9, 3], max_length=6)
     engine.add_request(r)
@@ -292,7 +294,8 @@ def test_continue_with_only_processes_the_new_tokens(model):
     q.continue_with([10, 11, 12])
     assert q.status == native.RequestStatus.Assigned
     engine.step()
-    assert ex.calls[0] == [(q._native.id, 3, 2, True)], "only the new tokens are fed; the cached prefix is reused"
+    # the end-of-turn token of the first turn was sampled but never fed: it leads the next turn's prefill (4 tokens)
+    assert ex.calls[0] == [(q._native.id, 4, 2, True)], "only the unprocessed tokens are fed; the cached prefix is reused"
 
 
 def test_remove_request_reclaims_blocks_and_teardown(model):
