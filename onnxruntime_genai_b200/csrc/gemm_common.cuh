@@ -29,10 +29,26 @@ struct CommParams {
   uint4* buf[COMM_MAX_WORLD];             // receive buffer of every rank: [2 parities][world sources][plane_elems / 4 lines]
   uint32_t* epoch;                        // this rank: [0] = calls finished so far, [1] = CTAs of the running call that are done
   long long plane_elems;                  // bf16 elements per source plane (4 per line)
+  // NVLS (NVSwitch multicast) form of the same reductions; nv_data_mc == nullptr: not available, the flagged lines serve.
+  // Every rank keeps its partial sums in its own `nv_data` plane (plain bf16, no flags); after a per-CTA arrival barrier
+  // (one multimem.red on a counter that exists on every rank) a rank reads the SUM of all ranks' planes with
+  // multimem.ld_reduce through the multicast mapping - the switch adds, fp32 accumulation.
+  __nv_bfloat16* nv_data;                 // this rank: [2 parities][nv_plane_elems] partial sums
+  __nv_bfloat16* nv_data_mc;              // the same range of every rank through the multicast mapping
+  __nv_bfloat16* nv_out;                  // this rank: [2 parities][nv_plane_elems] sums broadcast by their owners (two-shot form)
+  __nv_bfloat16* nv_out_mc;
+  uint32_t* nv_ctr;                       // this rank: [2 phases][NV_MAX_CTAS] arrival counters, only ever incremented
+  uint32_t* nv_ctr_mc;
+  uint32_t* nv_expected;                  // this rank only (not symmetric): [2 phases][NV_MAX_CTAS] counter value after the last completed use
+  long long nv_plane_elems;
 };
+
+constexpr int NV_MAX_CTAS = 4096;         // CTAs (or chunks) of one NVLS call; each has its own counter
 
 // Registered symmetric buffers of a device (gemm_tcgen05.cu); nullptr when the index is out of range.
 const CommParams* ogb_comm_params(int device);
+// {use NVLS when registered, two-shot threshold in bytes}; see ogb_comm_set_options.
+const long long* ogb_comm_options();
 
 // Grouped (mixture-of-experts) mode: the token rows are sorted by expert and blockIdx.y walks a device-built
 // list of token tiles, each inside one expert's row range; the weight is [experts * N, K].
@@ -41,6 +57,19 @@ struct GroupParams {
   const int* tile_row0;     // first (sorted) token row of the tile
   const int* tile_rows;     // rows of the tile that belong to its expert (<= token tile)
   const int* num_tiles;     // device scalar: tiles in use; CTAs beyond it return at once
+};
+
+// Rotary embedding + KV-cache append fused into the epilogue of a QKV projection (positions == nullptr: off).  Output
+// columns are [Hq query heads | Hkv key heads | Hkv value heads] of D each; the rotation pairs element i with i + rot / 2
+// (the non-interleaved form); keys and values go to row `slots[m]` of the caches [slots, Hkv, D] (slot < 0: nowhere).
+struct FusedRope {
+  const int* positions;
+  const int* slots;
+  const float* cos;     // [max_pos, rot / 2] fp32
+  const float* sin;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  int Hq, Hkv, D, rot, max_pos;
 };
 
 struct GemmParams {
@@ -65,7 +94,13 @@ struct GemmParams {
   int ar2_rows;         // > 0: the all-reduce runs in two hops (reduce-scatter by token rows to an owner rank, which sums and
                         // broadcasts): each partial crosses NVLink once instead of world times; owner of row m = m / ar2_rows
   int rs_rows;          // > 0: reduce-scatter by token rows: rank r receives (and stores, as its rows 0..) rows [r * rs_rows, (r + 1) * rs_rows)
+  int nvls;             // comm_epilogue through NVSwitch multicast: 1 = one-shot (every rank reads the sum of its whole slice with
+                        // multimem.ld_reduce), 2 = two-shot (a rank reduces 1/world of the slice and multicasts the sums)
   GroupParams grp;
+  float norm_eps;       // > 0: RMS norm folded into this GEMM - the activations are the un-normalised rows, the weight carries the
+                        // norm's weight, the kernel sums the squares of each row as its tiles pass through shared memory and the
+                        // epilogue multiplies row m by rsqrt(mean(x_m^2) + eps)
+  FusedRope rope;
 };
 
 template <int BT>
@@ -80,8 +115,9 @@ struct GemmCfg {
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
   static constexpr int PARTIAL_BYTES = BT * GEMM_BLOCK_N * 4;  // fp32 tile parked in stage memory
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static_assert(PARTIAL_BYTES <= STAGES * STAGE_BYTES, "the parked tile must fit in the pipeline memory");
+  static constexpr int SSQ_OFFSET = STAGES * STAGE_BYTES + 256;   // per-row sums of squares (folded norm), after the barriers
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + BT * 4;
+  static_assert(PARTIAL_BYTES + 16 * 128 * 16 <= STAGES * STAGE_BYTES, "the parked tile and the reduction's staging lines must fit in the pipeline memory");
 };
 
 __device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
@@ -137,12 +173,127 @@ __device__ __forceinline__ uint4 wait_line(const uint4* p, uint32_t flag, bool& 
   }
 }
 
-// Epilogue shared by the linear-layer kernels.  Called by all 192 threads of the CTA once the MMA issuer has
-// committed the last k-block to `accum_bar`; `smem` is the (idle) pipeline memory, reused for the fp32 tile.
-template <int BT>
+// ------------------------------------------------------------------------------- NVLS (multimem) helpers
+// Sum over all ranks of eight bf16 values at the same offset of every rank's buffer (fp32 accumulation in the switch).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+// One 16-byte store that lands at the same offset of every rank's buffer.
+__device__ __forceinline__ void multimem_st_b128(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+// Adds 1 to the counter at the same offset on every rank; the release makes this CTA's earlier stores (ordered before it by a
+// CTA barrier) visible to whoever acquires the counter.
+__device__ __forceinline__ void multimem_signal(uint32_t* mc_ctr) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ctr), "r"(1u) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Arrival barrier between the CTAs with index `slot` of every rank, run by ONE thread: announce this rank, then wait
+// (bounded) until all `world` ranks have.  Counters only grow; the local `expected` word remembers the value the last use
+// ended on, so nothing is ever reset and the sequence replays inside CUDA graphs.  Returns false when the wait ran out.
+__device__ __forceinline__ bool nvls_arrive_and_wait(const CommParams& c, int phase, unsigned slot, int* status) {
+  uint32_t* exp = c.nv_expected + phase * NV_MAX_CTAS + slot;
+  const uint32_t target = *exp + uint32_t(c.world);
+  *exp = target;
+  multimem_signal(c.nv_ctr_mc + phase * NV_MAX_CTAS + slot);
+  const uint32_t* mine = c.nv_ctr + phase * NV_MAX_CTAS + slot;
+  if (int32_t(ld_acquire_sys_u32(mine) - target) >= 0) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (int32_t(ld_acquire_sys_u32(mine) - target) >= 0) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0 || global_timer_ns() - t0 > 2000000000ull) {
+        atomicMax(status, OGB_ERR_WAIT_PEER);
+        return false;
+      }
+    }
+  }
+}
+
+// Opens a fused call for this CTA, run by ONE thread after the kernel's dependency wait (the previous call of the device has
+// completed): returns the call's epoch and counts the CTA; the last CTA of the grid to get here publishes epoch + 1 for the
+// next call.  Nothing of this call depends on that store (the next call reads the epoch only after this grid has completed),
+// so the bookkeeping sits at the start of the kernel, under the main loop, instead of on the tail every CTA must finish.
+__device__ __forceinline__ uint32_t comm_open_call(const CommParams& c, unsigned total_ctas) {
+  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(c.epoch);
+  __threadfence();                       // the read above is performed before this CTA is counted
+  if (atomicAdd(c.epoch + 1, 1u) == total_ctas - 1) {
+    c.epoch[1] = 0;
+    __threadfence();
+    *reinterpret_cast<volatile uint32_t*>(c.epoch) = e + 1;
+  }
+  return e;
+}
+
+// Output side of the epilogue, kept out of line: the epilogue runs once per CTA, so its instructions are fetched cold, and
+// every inlined copy of this routine (three output types, vector and tail forms) costs instruction-cache misses.
+struct StoreArgs {
+  void* C;
+  const __nv_bfloat16* residual;
+  int ldc, ldr, out_kind, n_out;    // out_kind: 0 bf16, 1 fp32, 2 fp16
+};
+static __device__ __noinline__ void epi_store8(const StoreArgs a, int m, int col, float4 lo, float4 hi) {
+  float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  const bool full = col + 8 <= a.n_out;
+  if (a.residual) {
+    const __nv_bfloat16* r = a.residual + size_t(m) * a.ldr + col;
+    if (full && (reinterpret_cast<uintptr_t>(r) & 15) == 0) {
+      const uint4 q = *reinterpret_cast<const uint4*>(r);
+      const float2 x0 = unpack_bf16x2(q.x), x1 = unpack_bf16x2(q.y), x2 = unpack_bf16x2(q.z), x3 = unpack_bf16x2(q.w);
+      v[0] += x0.x; v[1] += x0.y; v[2] += x1.x; v[3] += x1.y; v[4] += x2.x; v[5] += x2.y; v[6] += x3.x; v[7] += x3.y;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (col + j < a.n_out) v[j] += bf2f(r[j]);
+    }
+  }
+  if (a.out_kind == 1) {
+    float* dst = reinterpret_cast<float*>(a.C) + size_t(m) * a.ldc + col;
+    if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (col + j < a.n_out) dst[j] = v[j];
+    }
+  } else if (a.out_kind == 2) {   // fp16 output (feeds the fp16 form of the packed FP4 expert GEMM)
+    __half* dst = reinterpret_cast<__half*>(a.C) + size_t(m) * a.ldc + col;
+    if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]), pack_f16x2(v[6], v[7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (col + j < a.n_out) dst[j] = __float2half_rn(v[j]);
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.C) + size_t(m) * a.ldc + col;
+    if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (col + j < a.n_out) dst[j] = f2bf(v[j]);
+    }
+  }
+}
+
+// Epilogue shared by the linear-layer kernels.  Called by all threads of the CTA once the MMA issuer has committed the last
+// k-block to `accum_bar`; `smem` is the (idle) pipeline memory, reused for the fp32 tile.
+// COMM: 0 = results stay on this GPU; 1 = tensor-parallel reduction with flagged lines over peer memory; 2 = through the
+// NVSwitch multicast mapping (NVLS).  A template parameter because the epilogue's instructions are fetched cold once per
+// CTA: the local form must not carry the reductions' code.
+// ssq: shared-memory array of the per-token-row sums of squares of this CTA's share of the activations (norm folded into the
+// GEMM, p.norm_eps > 0), or nullptr.
+template <int BT, int COMM>
 __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem, uint32_t tmem_base, uint64_t* accum_bar,
                                               volatile int* abort_flag, volatile uint32_t* use_slot, int n_tile, int m_tile,
-                                              int row0, int rows, int bias_off, int n_acc = 1) {
+                                              int row0, int rows, int bias_off, const float* ssq = nullptr, int n_acc = 1) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
   // -------------------------------------------------------------------- epilogue (warps 2..5)
@@ -191,9 +342,10 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     const int n_out = p.act_pair ? p.N / 2 : p.N;    // output columns of the whole problem
     const int col0 = n_tile * (p.act_pair ? 64 : 128);
     const uint32_t part_addr = smem_u32(part);
-    const bool comm_on = p.comm_epilogue != 0;
+    const StoreArgs sa{p.C, p.residual, p.ldc, p.ldr, p.out_fp32, n_out};
 
-    auto reduce8 = [&](int mc, int n_local, float (&v)[8]) {
+    // sum over the split-K cluster of 8 accumulators of token column mc, weight rows n_local.., scaled by the folded norm
+    auto reduce8 = [&](int mc, int n_local, float scale, float (&v)[8]) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
       for (int s = 0; s < p.splits; ++s) {
@@ -208,67 +360,48 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
         }
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
       }
-    };
-    auto add_bias8 = [&](int n_glob, float (&v)[8]) {
-      if (!p.bias) return;
+      const int n_glob = n_tile * GEMM_BLOCK_N + n_local;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) if (n_glob + j < p.N) v[j] += bf2f(p.bias[bias_off + n_glob + j]);
-    };
-    auto store8 = [&](int m, int col, float (&v)[8]) {  // residual add + store of one 8-wide segment
-      if (p.residual) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) if (col + j < n_out) v[j] += bf2f(p.residual[size_t(m) * p.ldr + col + j]);
+      for (int j = 0; j < 8; ++j) {
+        v[j] *= scale;
+        if (p.bias && n_glob + j < p.N) v[j] += bf2f(p.bias[bias_off + n_glob + j]);
       }
-      if (p.out_fp32 == 1) {
-        float* dst = reinterpret_cast<float*>(p.C) + size_t(m) * p.ldc + col;
-        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = v[j];
-        }
-      } else if (p.out_fp32 == 2) {   // fp16 output (feeds the fp16 form of the packed FP4 expert GEMM)
-        __half* dst = reinterpret_cast<__half*>(p.C) + size_t(m) * p.ldc + col;
-        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]), pack_f16x2(v[6], v[7]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = __float2half_rn(v[j]);
+    };
+    // 1 / rms of token column mc's activation row (norm folded into this GEMM: the weight already carries the norm's weight)
+    auto row_scale = [&](int mc) {
+      if (ssq == nullptr) return 1.f;
+      float t = 0.f;
+      if (p.splits > 1) {
+        for (int s = 0; s < p.splits; ++s) {
+          float x;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x) : "r"(dsmem_addr(smem_u32(ssq + mc), uint32_t(s))) : "memory");
+          t += x;
         }
       } else {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(m) * p.ldc + col;
-        if (col + 8 <= n_out && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) if (col + j < n_out) dst[j] = f2bf(v[j]);
-        }
+        t = ssq[mc];
       }
+      return rsqrtf(t / float(p.K) + p.norm_eps);
     };
 
-    uint32_t use = 0;   // epoch of this call
-    if (comm_on) {
-      // read after griddepcontrol.wait: the previous call has finished and published its increment
-      if (et == 0) *use_slot = *reinterpret_cast<volatile uint32_t*>(p.comm.epoch);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      use = *use_slot;
-    }
+    // Epoch of this call: read (and the call counted) by the kernel's producer thread right after its dependency wait, long
+    // before the epilogue (comm_open_call); visible here through the CTA-wide barrier above.
+    const uint32_t use = COMM != 0 ? *use_slot : 0u;
     const uint32_t flag = comm_flag(use);
     const size_t plane_lines = size_t(p.comm.plane_elems) / 4;
     const size_t par_off = size_t(use & 1) * p.comm.world * plane_lines;
 
+#pragma unroll 1
     for (int item = et; item < items; item += 128) {
       const int mc = c_begin + item / OCT, oc = item % OCT;
       const int m = row0 + mc;
       if (mc >= rows) continue;
+      const float rs = row_scale(mc);
       float v[8];
+      const int col = col0 + oc * 8;
       if (p.act_pair) {
         float u[8];
-        reduce8(mc, oc * 8, v);
-        reduce8(mc, 64 + oc * 8, u);
-        add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
-        add_bias8(n_tile * GEMM_BLOCK_N + 64 + oc * 8, u);
+        reduce8(mc, oc * 8, rs, v);
+        reduce8(mc, 64 + oc * 8, rs, u);
         if (p.act_pair == 1) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = silu(v[j]) * u[j];
@@ -281,15 +414,45 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
           }
         }
       } else {
-        reduce8(mc, oc * 8, v);
-        add_bias8(n_tile * GEMM_BLOCK_N + oc * 8, v);
+        reduce8(mc, oc * 8, rs, v);
+        if (COMM == 0 && p.rope.positions != nullptr) {
+          // Fused rotary embedding + KV-cache append of a QKV projection (heads never straddle a tile: 128 % D == 0).
+          // Query heads go to C rotated; key heads go rotated, value heads as they are, to this token's cache slot.
+          const FusedRope& R = p.rope;
+          const int head = col / R.D, d = col - head * R.D;
+          if (head < R.Hq + R.Hkv && d < R.rot) {
+            const int half = R.rot >> 1;
+            const bool first = d < half;
+            float u[8];
+            reduce8(mc, first ? oc * 8 + half : oc * 8 - half, rs, u);
+            int pos = R.positions[m];
+            pos = pos < 0 ? 0 : (pos >= R.max_pos ? R.max_pos - 1 : pos);
+            const float* cs = R.cos + size_t(pos) * half + (first ? d : d - half);
+            const float* sn = R.sin + size_t(pos) * half + (first ? d : d - half);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = first ? v[j] * cs[j] - u[j] * sn[j] : v[j] * cs[j] + u[j] * sn[j];
+          }
+          if (head >= R.Hq) {
+            const int slot = R.slots[m];
+            if (slot >= 0 && col < p.N) {
+              const bool is_k = head < R.Hq + R.Hkv;
+              __nv_bfloat16* dst = (is_k ? R.k_cache : R.v_cache) + (size_t(slot) * R.Hkv + (head - R.Hq - (is_k ? 0 : R.Hkv))) * R.D + d;
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            }
+            continue;
+          }
+        }
       }
-      const int col = col0 + oc * 8;
-      if (!comm_on) {
-        store8(m, col, v);
+      if (COMM == 0) {
+        epi_store8(sa, m, col, make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]));
+      } else if (COMM == 2) {
+        // this rank's partial stays in its own plane; the switch adds the planes when a rank reads through the multicast mapping
+        if (col < n_out)
+          *reinterpret_cast<uint4*>(p.comm.nv_data + size_t(use & 1) * p.comm.nv_plane_elems + size_t(m) * n_out + col) =
+              make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
       } else if (col < n_out) {
         // push this rank's partial (bf16) into every rank's receive buffer (all-reduce) or into the buffer of the rank
-        // that owns the token row (reduce-scatter): two flagged lines per 8 values
+        // that owns the token row (reduce-scatter, two-hop all-reduce): two flagged lines per 8 values
         const size_t line = par_off + size_t(p.comm.rank) * plane_lines + (size_t(m) * n_out + col) / 4;
         const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
         const int own_rows = p.rs_rows > 0 ? p.rs_rows : p.ar2_rows;      // > 0: the partial goes to the row's owner only
@@ -301,68 +464,131 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
       }
     }
 
-    if (comm_on) {
-      // Every thread collects the lines of the items it pushed itself: its own pushes are long under way, and the peers'
-      // lines of the same items arrive at about the same time.  The data carries its own arrival flag.
-      bool dead = *reinterpret_cast<volatile int*>(p.status) != 0;
-      if (p.ar2_rows > 0) {
-        // Two-hop all-reduce.  Hop 1 (above) sent every partial to the owner of its token row.  Here the owner sums the
-        // world's partials of its rows in rank order, rounds to bf16 (so that every rank ends up with the same bits),
-        // stores, and broadcasts the sums as flagged lines into plane `owner` of every other rank — a plane position no
-        // hop-1 line of this call uses there; the other ranks then collect the rows they do not own.
-        for (int item = et; item < items; item += 128) {
+    auto unpack8 = [&](const uint4& q, float (&w)[8]) {
+      const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+      w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y; w[4] = c.x; w[5] = c.y; w[6] = d.x; w[7] = d.y;
+    };
+    if (COMM == 2) {
+      // ---- NVLS: barrier with the same CTA of every rank, then read sums through the switch.
+      const unsigned slot = (blockIdx.y * gridDim.x + blockIdx.x) * gridDim.z + blockIdx.z;   // the grid is the same on every rank
+      const size_t par = size_t(use & 1) * p.comm.nv_plane_elems;
+      auto rank_barrier = [&](int phase) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // every thread's stores of this phase are ordered before thread 0's release
+        if (et == 0 && *abort_flag == 0 && !nvls_arrive_and_wait(p.comm, phase, slot, p.status)) *abort_flag = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        return *abort_flag == 0;
+      };
+      if (rank_barrier(0)) {
+        const bool one_shot = p.nvls == 1 || p.rs_rows > 0;
+        // one-shot: the sum of every item of the slice (reduce-scatter: of the rows this rank keeps).
+        // two-shot: each rank reduces every world-th item and multicasts the sum into every rank's `nv_out` plane; after a
+        // second barrier all sums of the slice are local.  A partial crosses NVLink once, a sum once.
+        int j = 0;
+#pragma unroll 1
+        for (int item = et; item < items; item += 128, ++j) {
           const int mc = c_begin + item / OCT, oc = item % OCT;
-          const int m = row0 + mc;
-          const int col = col0 + oc * 8;
-          if (mc >= rows || col >= n_out || m / p.ar2_rows != p.comm.rank) continue;
-          float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          const size_t line = par_off + (size_t(m) * n_out + col) / 4;
-          for (int r = 0; r < p.comm.world; ++r) {
-            const uint4 q0 = wait_line(p.comm.buf[p.comm.rank] + line + size_t(r) * plane_lines, flag, dead, p.status);
-            const uint4 q1 = wait_line(p.comm.buf[p.comm.rank] + line + size_t(r) * plane_lines + 1, flag, dead, p.status);
-            const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
-            v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
-          }
-          const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
-          for (int r = 0; r < p.comm.world; ++r) {
-            if (r == p.comm.rank) continue;
-            st_line(p.comm.buf[r] + line + size_t(p.comm.rank) * plane_lines, d0, d1, flag);
-            st_line(p.comm.buf[r] + line + size_t(p.comm.rank) * plane_lines + 1, d2, d3, flag);
-          }
-          const float2 a = unpack_bf16x2(d0), b = unpack_bf16x2(d1), c = unpack_bf16x2(d2), d = unpack_bf16x2(d3);
-          float w[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
-          store8(m, col, w);
-        }
-        for (int item = et; item < items; item += 128) {
-          const int mc = c_begin + item / OCT, oc = item % OCT;
-          const int m = row0 + mc;
-          const int col = col0 + oc * 8;
+          const int m = row0 + mc, col = col0 + oc * 8;
           if (mc >= rows || col >= n_out) continue;
-          const int owner = m / p.ar2_rows;
-          if (owner == p.comm.rank) continue;
-          const uint4* src = p.comm.buf[p.comm.rank] + par_off + size_t(owner) * plane_lines + (size_t(m) * n_out + col) / 4;
-          const uint4 q0 = wait_line(src, flag, dead, p.status);
-          const uint4 q1 = wait_line(src + 1, flag, dead, p.status);
-          const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
-          float w[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
-          store8(m, col, w);
+          const size_t off = par + size_t(m) * n_out + col;
+          if (one_shot) {
+            if (p.rs_rows > 0 && m / p.rs_rows != p.comm.rank) continue;
+            float w[8];
+            unpack8(multimem_ld_reduce_bf16x8(p.comm.nv_data_mc + off), w);
+            epi_store8(sa, p.rs_rows > 0 ? m - p.comm.rank * p.rs_rows : m, col, make_float4(w[0], w[1], w[2], w[3]), make_float4(w[4], w[5], w[6], w[7]));
+          } else if ((j + et) % p.comm.world == p.comm.rank) {
+            multimem_st_b128(p.comm.nv_out_mc + off, multimem_ld_reduce_bf16x8(p.comm.nv_data_mc + off));
+          }
+        }
+        if (!one_shot && rank_barrier(1)) {
+#pragma unroll 1
+          for (int item = et; item < items; item += 128) {
+            const int mc = c_begin + item / OCT, oc = item % OCT;
+            const int m = row0 + mc, col = col0 + oc * 8;
+            if (mc >= rows || col >= n_out) continue;
+            float w[8];
+            unpack8(ld_line(reinterpret_cast<const uint4*>(p.comm.nv_out + par + size_t(m) * n_out + col)), w);
+            epi_store8(sa, m, col, make_float4(w[0], w[1], w[2], w[3]), make_float4(w[4], w[5], w[6], w[7]));
+          }
         }
       }
-      for (int item = et; item < items && p.ar2_rows == 0; item += 128) {
-        const int mc = c_begin + item / OCT, oc = item % OCT;
-        const int m = row0 + mc;
-        const int col = col0 + oc * 8;
-        if (mc >= rows || col >= n_out) continue;
-        if (p.rs_rows > 0 && m / p.rs_rows != p.comm.rank) continue;   // another rank's row
-        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const uint4* base = p.comm.buf[p.comm.rank] + par_off + (size_t(m) * n_out + col) / 4;
-        for (int r = 0; r < p.comm.world; ++r) {   // rank order: bit-identical sums on every rank
-          const uint4 q0 = wait_line(base + size_t(r) * plane_lines, flag, dead, p.status);
-          const uint4 q1 = wait_line(base + size_t(r) * plane_lines + 1, flag, dead, p.status);
-          const float2 a = unpack_bf16x2(q0.x), b = unpack_bf16x2(q0.z), c = unpack_bf16x2(q1.x), d = unpack_bf16x2(q1.z);
-          v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+    } else if (COMM == 1) {
+      // Every thread collects the lines of the items it pushed itself: its own pushes are long under way, and the peers'
+      // lines of the same items arrive at about the same time.  The data carries its own arrival flag.
+      // A thread's lines are fetched sixteen at a time by asynchronous copies (L2 -> shared memory, all in flight together: a
+      // chain of dependent loads would cost one L2 round trip per line) into staging slots behind the parked tile; only
+      // lines that had not arrived yet are then waited for one by one.  Short loops on purpose: this code is fetched cold.
+      bool dead = false;      // the waits themselves look at the status word from time to time
+      const int W = p.comm.world;
+      const uint4* my_buf = p.comm.buf[p.comm.rank] + par_off;
+      uint4* stage = reinterpret_cast<uint4*>(smem + GemmCfg<BT>::PARTIAL_BYTES);   // [16 slots][128 threads] lines
+      // The reductions never pair columns (OCT == 16): thread et owns segment et % 16 of token columns c_begin + et / 16 + 8 k.
+      const int seg_col = col0 + (et & 15) * 8;
+      const int mc_first = c_begin + (et >> 4), mc_end = min(c_end, rows);
+      const size_t row_lines = size_t(n_out) / 4;
+      // hop: 0 = one-hop all-reduce / reduce-scatter (sum the W planes of the rows kept here), 1 = two-hop, owner's part (sum
+      // the W planes of the owned rows, store, broadcast), 2 = two-hop, the other rows (one plane: the owner's sums)
+#pragma unroll 1
+      for (int hop = (p.ar2_rows > 0 ? 1 : 0); hop <= (p.ar2_rows > 0 ? 2 : 0); ++hop) {
+        const int per_item = hop == 2 ? 2 : 2 * W;
+        // walk (item, line of the item) pairs: `mc` is the item's token column, `rem` the line (plane * 2 + half)
+        int mc = mc_first, rem = 0;
+        auto item_ok = [&](int mc_) {      // is this token column collected in this hop?
+          const int m = row0 + mc_;
+          if (hop == 0) return p.rs_rows == 0 || m / p.rs_rows == p.comm.rank;
+          return (m / p.ar2_rows == p.comm.rank) == (hop == 1);
+        };
+        while (mc < mc_end && !item_ok(mc)) mc += 8;
+        float v[8];
+        auto line_ptr = [&](int mc_, int rem_) {
+          const int m = row0 + mc_;
+          const int plane = hop == 2 ? m / p.ar2_rows : (rem_ >> 1);
+          return my_buf + size_t(plane) * plane_lines + size_t(m) * row_lines + (seg_col >> 2) + (rem_ & 1);
+        };
+        auto advance = [&](int& mc_, int& rem_) {
+          if (++rem_ < per_item) return;
+          rem_ = 0;
+          mc_ += 8;
+          while (mc_ < mc_end && !item_ok(mc_)) mc_ += 8;
+        };
+#pragma unroll 1
+        while (mc < mc_end && seg_col < n_out) {
+          // pass 1: asynchronous copies of up to 16 lines into this thread's staging slots (all in flight together)
+          int mc_w = mc, rem_w = rem, n = 0;
+#pragma unroll 1
+          for (; n < 16 && mc_w < mc_end; ++n) {
+            cp_async16(stage + (n * 128 + et), line_ptr(mc_w, rem_w), true);
+            advance(mc_w, rem_w);
+          }
+          cp_async_commit();
+          cp_async_wait<0>();
+          // pass 2: the same walk; a line whose flag is not this call's had not arrived yet and is waited for in place
+#pragma unroll 1
+          for (int i = 0; i < n; ++i) {
+            uint4 q = stage[i * 128 + et];
+            if (q.y != flag || q.w != flag) q = wait_line(line_ptr(mc, rem), flag, dead, p.status);
+            const int h4 = (rem & 1) * 4;
+            const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.z);
+            if (rem < 2) { v[h4] = a.x; v[h4 + 1] = a.y; v[h4 + 2] = b.x; v[h4 + 3] = b.y; }
+            else { v[h4] += a.x; v[h4 + 1] += a.y; v[h4 + 2] += b.x; v[h4 + 3] += b.y; }
+            if (rem == per_item - 1) {
+              const int m = row0 + mc;
+              if (hop == 1) {
+                // the owner rounds to bf16 (every rank ends up with the same bits) and broadcasts the sums as flagged lines
+                // into plane `owner` of every other rank - a plane position no hop-1 line of this call uses there
+                const size_t line = par_off + size_t(p.comm.rank) * plane_lines + size_t(m) * row_lines + (seg_col >> 2);
+                const uint32_t d0 = pack_bf16x2(v[0], v[1]), d1 = pack_bf16x2(v[2], v[3]), d2 = pack_bf16x2(v[4], v[5]), d3 = pack_bf16x2(v[6], v[7]);
+                for (int r = 0; r < W; ++r) {
+                  if (r == p.comm.rank) continue;
+                  st_line(p.comm.buf[r] + line, d0, d1, flag);
+                  st_line(p.comm.buf[r] + line + 1, d2, d3, flag);
+                }
+                unpack8(make_uint4(d0, d1, d2, d3), v);
+              }
+              epi_store8(sa, p.rs_rows > 0 ? m - p.comm.rank * p.rs_rows : m, seg_col, make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]));
+            }
+            advance(mc, rem);
+          }
         }
-        store8(p.rs_rows > 0 ? m - p.comm.rank * p.rs_rows : m, col, v);
       }
       if (dead) *abort_flag = 1;
     }
@@ -371,20 +597,6 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
     __syncwarp();
     cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
   }
-  if (p.comm_epilogue) {
-    // The last CTA of the call to get here closes the epoch (every CTA passes this point, also after an abort).
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      const unsigned total = gridDim.x * gridDim.y * gridDim.z;
-      if (atomicAdd(p.comm.epoch + 1, 1u) == total - 1) {
-        p.comm.epoch[1] = 0;
-        __threadfence();
-        *reinterpret_cast<volatile uint32_t*>(p.comm.epoch) = *reinterpret_cast<volatile uint32_t*>(p.comm.epoch) + 1;
-      }
-    }
-  }
-
 }
 
 }  // namespace ogb

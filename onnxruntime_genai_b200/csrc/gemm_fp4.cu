@@ -272,7 +272,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, expert * p.N, NACC);
+  gemm_epilogue<BT, 0>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, expert * p.N, nullptr, NACC);
 
   tc_fence_before();
   __syncthreads();

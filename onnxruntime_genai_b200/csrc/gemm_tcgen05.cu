@@ -47,7 +47,7 @@
 
 namespace ogb {
 
-template <int BT>
+template <int BT, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BT>::TWO_PER_SM ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using Cfg = GemmCfg<BT>;
@@ -60,6 +60,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile uint32_t* use_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
+  float* ssq = reinterpret_cast<float*>(smem + Cfg::SSQ_OFFSET);   // [BT] sums of squares of the activation rows (folded norm)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
@@ -77,9 +78,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
   }
 
   const bool gather = p.ag_rows > 0;
+  const bool norm = p.norm_eps > 0.f;   // warps 2..5 read every activation tile too: a stage is empty once they have as well
   if (threadIdx.x == 0) {
     // gathered activations: a stage is full when the weight tile has landed AND the 128 assembling threads have arrived
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], gather ? 1 + 128 : 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], gather ? 1 + 128 : 1); mbar_init(&empty_bar[s], norm ? 1 + 4 : 1); }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -118,6 +120,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
       const int pre = min(STAGES, num_kb);
       for (int i = 0; i < pre; ++i) load_w(i);
       if (p.pdl) pdl_wait();
+      if (COMM != 0) *use_slot = comm_open_call(p.comm, gridDim.x * gridDim.y * gridDim.z);
       for (int i = 0; i < pre; ++i) load_a(i);
       int issued = pre;
       for (int i = pre; i < num_kb; ++i) {
@@ -191,7 +194,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     if (dead) *abort_flag = 1;
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0);
+  if (norm && warp >= 2) {
+    // ------------------------------------------------------------------ folded RMS norm: sum of squares of every activation row
+    // The four epilogue warps (idle during the main loop) read each activation tile from shared memory once it has landed.  A
+    // row's 128 bytes are contiguous whatever the swizzle, so 16-byte chunk c of the tile belongs to row c / 8; thread t takes
+    // chunks t, t + 128, ...  Eight neighbouring threads share a row and combine at the end.
+    constexpr int CHUNKS = BT * 8, PER = (CHUNKS + 127) / 128;
+    const int t = threadIdx.x - 64;
+    float acc[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) acc[k] = 0.f;
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait_bounded(&full_bar[s], (i / STAGES) & 1, abort_flag)) { fail(OGB_ERR_WAIT_TMA); break; }
+      const uint8_t* tile = stage_a(s);
+#pragma unroll
+      for (int k = 0; k < PER; ++k) {
+        const int c = t + 128 * k;
+        if (c < CHUNKS) {
+          const uint4 q = *reinterpret_cast<const uint4*>(tile + c * 16);
+          const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), cc = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+          acc[k] += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + cc.x * cc.x + cc.y * cc.y + d.x * d.x + d.y * d.y;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      float v = acc[k];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      const int c = t + 128 * k;
+      if ((t & 7) == 0 && c < CHUNKS) ssq[c >> 3] = v;
+    }
+  }
+
+  gemm_epilogue<BT, COMM>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, row0, rows, w_row0, norm ? ssq : nullptr);
 
   tc_fence_before();
   __syncthreads();
@@ -267,10 +307,10 @@ bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, 
   return MakeMap(out, ptr, rows, cols, ld, box_rows);
 }
 
-template <int BT>
-static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+template <int BT, int COMM>
+static int LaunchC(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BT>;
-  auto kern = gemm_tcgen05_kernel<BT>;
+  auto kern = gemm_tcgen05_kernel<BT, COMM>;
   static bool configured[OGB_MAX_DEVICES] = {};
   if (!set_max_dyn_smem(kern, Cfg::SMEM_BYTES, configured)) return -3;
   cudaLaunchConfig_t cfg = {};
@@ -297,12 +337,19 @@ static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams
   return cudaLaunchKernelEx(&cfg, kern, tw, ta, p) == cudaSuccess ? 0 : -4;
 }
 
+// One kernel instantiation per token tile and per reduction form: the local form does not carry the reductions' code.
+template <int BT>
+static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  if (!p.comm_epilogue) return LaunchC<BT, 0>(tw, ta, p, grid, stream);
+  return p.nvls ? LaunchC<BT, 2>(tw, ta, p, grid, stream) : LaunchC<BT, 1>(tw, ta, p, grid, stream);
+}
+
 // How many split-K clusters of `splits` CTAs of the decode kernel the device can hold at once (0: the query failed).  The
 // CTAs of a cluster must sit in one GPC, so this is less than (resident CTAs) / splits in general.
 template <int BT>
 static int MaxActiveClusters(int splits) {
   using Cfg = GemmCfg<BT>;
-  auto kern = gemm_tcgen05_kernel<BT>;
+  auto kern = gemm_tcgen05_kernel<BT, 0>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1, 1, unsigned(splits));
@@ -557,12 +604,18 @@ OGB_API int ogb_gemm_token_tile(int M, int dual) {
   return 256;
 }
 
-// Number of split-K partitions (cluster size along z: 1, 2, 4 or 8): the largest that still fits every CTA of the launch
-// on the GPU at once (two resident CTAs per SM for decode-sized tiles) while leaving each split at least 16 k-blocks to
-// stream.  Measured on B200 at 64 tokens (Llama-3.1-8B shapes, us per launch; utils/kernel_case.py --gemm_splits):
-//   qkv  (N 6144, K 4096):  s=2 16.8  s=3 16.1  s=4 15.5  s=5 15.5  s=6 24.7  s=8 25.8      (a second wave from 288 CTAs on)
-//   o    (N 4096, K 4096):  s=2 15.8  s=4 12.9  s=5 14.0  s=8 14.7
-//   down (N 4096, K 14336): s=2 41.3  s=4 28.4  s=5 28.0  s=7 27.9  s=8 27.6
+// Number of split-K partitions (cluster size along z: 1, 2, 4 or 8).  Every CTA of the launch must fit on the GPU at once
+// (two resident CTAs per SM for decode-sized tiles).  Up to 4 partitions pay off as soon as each keeps two k-blocks: the
+// epilogue of a tile (one thread per 8 outputs, fetched cold) is divided between the cluster's CTAs, which matters more than
+// the short main loops.  8 partitions need 16 k-blocks each, or a launch so small that it fits one CTA per SM.
+// Measured on B200 at 64 tokens, us per launch (benchmark/kernel_case.py --gemm_splits; rows marked tpN are the per-rank
+// shapes of N-way tensor parallelism with the fused all-reduce talking to itself):
+//   qkv  (N 6144, K 4096):  s=2 16.8  s=4 15.5  s=8 25.8 (a second wave from 288 CTAs on)
+//   o    (N 4096, K 4096):  s=2 15.8  s=4 12.9  s=8 14.7
+//   down (N 4096, K 14336): s=2 41.3  s=4 28.4  s=8 27.6
+//   tp8 o    (N 4096, K 512):  s=1 15.7  s=2 11.6  s=4 10.2  s=8 12.9      tp8 qkv     (N 768,  K 4096): s=1 24.1  s=4 9.8   s=8 8.6
+//   tp8 down (N 4096, K 1792): s=1 21.7  s=2 14.9  s=4 12.2  s=8 14.4      tp4 gate/up (N 7168, K 4096): s=2 17.9  s=4 16.7  s=8 25.3
+//   tp2 down (N 4096, K 7168): s=1 47.6  s=2 28.8  s=4 20.7  s=8 20.4      tp2 gate/up (N 14336, K 4096): s=1 29.2 s=2 23.8  s=4 32.8
 // Reducing through global memory instead of the cluster's shared memory (partials in an fp32 scratch, the last CTA of a
 // tile sums them) was measured too and is not kept: o 22.5..29.7, qkv 24.3..27.6, down 38.6..45.5 us.
 OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
@@ -572,8 +625,10 @@ OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
   const int slots = (bt <= 128 ? 2 : 1) * sm_count;
   int best = 1;
   for (int s = 2; s <= 8; s *= 2) {
-    if (s > bt || total_kb / s < 16 || tiles * s > slots) break;
-    best = s;
+    if (s > bt || tiles * s > slots) break;
+    const int kbs = total_kb / s;
+    const bool ok = s <= 4 ? kbs >= 2 : (kbs >= 16 || (tiles * s <= sm_count && kbs >= 8));
+    if (ok) best = s;
   }
   return best;
 }
@@ -601,6 +656,58 @@ OGB_API int ogb_comm_register(int device, int world, int rank, void** buf, void*
   c.epoch = static_cast<uint32_t*>(epoch);
   g_comm[device] = c;
   return 0;
+}
+
+// Adds the NVLS (NVSwitch multicast) buffers to a registered device: `data` / `out` are this rank's two planes of
+// 2 * plane_elems bf16 each inside a symmetric allocation, `ctr` 2 * NV_MAX_CTAS zero-initialised words in it; the *_mc
+// pointers are the same ranges through the allocation's multicast mapping; `expected` is 2 * NV_MAX_CTAS local
+// zero-initialised words.  data == nullptr removes them (the flagged-line kernels serve again).
+OGB_API int ogb_comm_register_nvls(int device, void* data, void* data_mc, void* out, void* out_mc, void* ctr, void* ctr_mc, void* expected,
+                                   long long plane_elems) {
+  if (device < 0 || device >= 16 || (plane_elems % 8)) return -1;
+  CommParams& c = g_comm[device];
+  if (data && (c.world < 1 || !data_mc || !out || !out_mc || !ctr || !ctr_mc || !expected)) return -1;
+  c.nv_data = static_cast<__nv_bfloat16*>(data); c.nv_data_mc = static_cast<__nv_bfloat16*>(data_mc);
+  c.nv_out = static_cast<__nv_bfloat16*>(out); c.nv_out_mc = static_cast<__nv_bfloat16*>(out_mc);
+  c.nv_ctr = static_cast<uint32_t*>(ctr); c.nv_ctr_mc = static_cast<uint32_t*>(ctr_mc);
+  c.nv_expected = static_cast<uint32_t*>(expected);
+  c.nv_plane_elems = data ? plane_elems : 0;
+  return 0;
+}
+
+// Process-wide choices of the fused reductions: [0] use NVLS when registered (default: OGB_TP_NVLS == 1; off otherwise - measured
+// on B200 the multimem round trips cost more than flagged lines at decode sizes, 36 against 24 us for GEMM + all-reduce at two
+// ranks), [1] byte count
+// (world * tensor bytes) above which the NVLS all-reduce takes the two-shot form (default: OGB_NVLS_TWO_SHOT_BYTES or 2 MiB),
+// [2] flagged-line all-reduce in two hops: 1 yes, 0 no, -1 from 4 ranks up (default: OGB_AR_TWO_SHOT or -1).
+static long long g_comm_opts[3] = {-1, -1, -2};
+namespace ogb {
+const long long* ogb_comm_options() {
+  if (g_comm_opts[0] < 0) { const char* e = getenv("OGB_TP_NVLS"); g_comm_opts[0] = (e && e[0] == '1') ? 1 : 0; }
+  if (g_comm_opts[1] < 0) { const char* e = getenv("OGB_NVLS_TWO_SHOT_BYTES"); g_comm_opts[1] = e ? atoll(e) : (2ll << 20); }
+  if (g_comm_opts[2] < -1) { const char* e = getenv("OGB_AR_TWO_SHOT"); g_comm_opts[2] = e ? atoi(e) : -1; }
+  return g_comm_opts;
+}
+}  // namespace ogb
+// A negative value leaves an option as it is (p2p_two_hop: -2 leaves it, -1 is its automatic setting).
+OGB_API int ogb_comm_set_options(int use_nvls, long long two_shot_bytes, int p2p_two_hop) {
+  ogb_comm_options();
+  if (use_nvls >= 0) g_comm_opts[0] = use_nvls ? 1 : 0;
+  if (two_shot_bytes >= 0) g_comm_opts[1] = two_shot_bytes;
+  if (p2p_two_hop >= -1) g_comm_opts[2] = p2p_two_hop;
+  return 0;
+}
+
+// 1 when the NVLS buffers of `device` are registered, 2 when the reductions also use them (option [0]).
+OGB_API int ogb_comm_has_nvls(int device) {
+  if (!(device >= 0 && device < 16 && g_comm[device].nv_data_mc != nullptr)) return 0;
+  return ogb_comm_options()[0] ? 2 : 1;
+}
+
+// Elements (bf16) that one fused reduction may cover on `device`: the NVLS plane when registered, else the flagged-line plane.
+OGB_API long long ogb_comm_capacity(int device) {
+  if (device < 0 || device >= 16 || g_comm[device].world < 1) return 0;
+  return g_comm[device].nv_data_mc ? g_comm[device].nv_plane_elems : g_comm[device].plane_elems;
 }
 
 // flags bit 0: fp32 output; bit 1: paired silu(gate)*up epilogue (N = 2 * output columns, rows
@@ -644,16 +751,25 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     if (device < 0 || device >= 16 || g_comm[device].world < 1 || !g_comm[device].buf[0]) return -2;
     const CommParams& c = g_comm[device];
     const long long n_out = act_pair ? N / 2 : N;
-    if (n_out % 8 || (long long)M * n_out > c.plane_elems) return -2;
+    // NVLS when the multicast buffers are registered and the launch fits their counters (ogb_comm_set_options: switch it
+    // off, move the threshold between the one-shot and the two-shot form; the one-shot form pulls world * M * N * 2 bytes
+    // out of every rank).
+    const int nvls_env = ogb_comm_options()[0];
+    const long long two_shot_bytes = ogb_comm_options()[1];
+    const bool nvls = nvls_env && c.nv_data_mc && (long long)M * n_out <= c.nv_plane_elems &&
+                      (long long)n_tiles * m_tiles * splits <= NV_MAX_CTAS && !(n_out % 8);
+    if (n_out % 8 || (!nvls && (long long)M * n_out > c.plane_elems)) return -2;
     p.comm = c;
     p.comm_epilogue = 1;
+    if (nvls) p.nvls = ((long long)c.world * M * n_out * 2 > two_shot_bytes && c.world > 2) ? 2 : 1;
     if (fused_rs) p.rs_rows = (M + c.world - 1) / c.world;
-    else {
+    else if (!nvls) {
       // one hop (every partial to every rank) costs world x the payload on the wire: fine for 2 ranks, not for 8
-      static const int two_shot = [] { const char* e = getenv("OGB_AR_TWO_SHOT"); return e ? atoi(e) : -1; }();
+      const int two_shot = int(ogb_comm_options()[2]);
       if (two_shot == 1 || (two_shot == -1 && c.world >= 4)) p.ar2_rows = (M + c.world - 1) / c.world;
     }
   }
+  if ((flags & 16) && fused_ar) return -1;   // the gathered form reads the previous call's epoch: it cannot open a call of its own
   if (flags & 16) {
     // all-gather -> GEMM: A is ignored; the activations come from the receive buffer filled by the previous fused call
     // (ogb_collective mode 3: every rank pushed its ceil(M / world) token rows of K values)

@@ -188,7 +188,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __rest
     }
   }
 
-  gemm_epilogue<BT>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, m_tile * BT, min(BT, p.M - m_tile * BT), 0);
+  gemm_epilogue<BT, 0>(p, smem, tmem_base, accum_bar, abort_flag, use_slot, n_tile, m_tile, m_tile * BT, min(BT, p.M - m_tile * BT), 0);
 
   tc_fence_before();
   __syncthreads();

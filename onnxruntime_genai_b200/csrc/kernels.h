@@ -20,6 +20,11 @@ int ogb_gemm_token_tile(int M, int dual);
 int ogb_gemm_max_active_clusters(int bt, int splits);
 int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count);
 int ogb_comm_register(int device, int world, int rank, void** buf, void* epoch, long long plane_elems);
+int ogb_comm_register_nvls(int device, void* data, void* data_mc, void* out, void* out_mc, void* ctr, void* ctr_mc, void* expected,
+                           long long plane_elems);
+int ogb_comm_has_nvls(int device);
+int ogb_comm_set_options(int use_nvls, long long two_shot_bytes, int p2p_two_hop);   // negative (-2 for the last): leave unchanged
+long long ogb_comm_capacity(int device);
 // flags: bit 0 fp32 output, bit 1 paired silu(gate)*up epilogue, bit 2 fused tensor-parallel all-reduce,
 // bit 3 fused reduce-scatter by token rows (sequence-parallel form)
 int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,

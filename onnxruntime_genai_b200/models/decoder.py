@@ -129,7 +129,7 @@ class NoTP:
     def gather_logits(self, x):
         return x
 
-    def fused_ok(self, x):
+    def fused_ok(self, x, n_out=None):
         return False
 
     def barrier(self):
@@ -242,7 +242,7 @@ class DecoderModel:
     def _row_parallel(self, x, w, b, lora):
         """Row-parallel projection: partial products summed over the tensor-parallel ranks."""
         bias = b if self.tp.rank == 0 else None
-        if self.tp.size > 1 and lora is None and self.tp.fused_ok(x):
+        if self.tp.size > 1 and lora is None and isinstance(w, torch.Tensor) and self.tp.fused_ok(x, w.shape[0]):
             return ops.linear(x, w, bias, all_reduce=True)   # GEMM + all-reduce in one kernel over NVLink
         return self.tp.reduce(self._linear(x, w, bias, lora=lora))
 

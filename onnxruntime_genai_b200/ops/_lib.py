@@ -26,6 +26,10 @@ _SIGS = {
     "ogb_gemm_max_active_clusters": (c_int, [c_int, c_int]),
     "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P]),
     "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, c_longlong]),
+    "ogb_comm_register_nvls": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, c_longlong]),
+    "ogb_comm_has_nvls": (c_int, [c_int]),
+    "ogb_comm_set_options": (c_int, [c_int, c_longlong, c_int]),
+    "ogb_comm_capacity": (c_longlong, [c_int]),
     "ogb_w4_packed_bytes": (c_longlong, [c_int, c_int]),
     "ogb_gemm_w4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P]),
     "ogb_moe_gemm": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_float, _P, _P, _P,

@@ -19,6 +19,8 @@ import torch
 from ..ops import _lib
 
 DEFAULT_PLANE_ELEMS = int(__import__("os").environ.get("OGB_COMM_PLANE_ELEMS", 2048 * 4096))  # bf16 elements per source plane of the receive buffer
+NVLS_PLANE_ELEMS = int(__import__("os").environ.get("OGB_NVLS_PLANE_ELEMS", 4096 * 8192))       # bf16 elements per NVLS plane (64 MiB)
+NV_MAX_CTAS = 4096     # csrc/gemm_common.cuh
 
 
 def _register(device_index: int, world: int, rank: int, buf_ptrs: List[int], epoch: torch.Tensor, plane_elems: int) -> None:
@@ -33,9 +35,24 @@ class _Collectives:
     vectors for the gather; reductions are bf16.  `fits` tells whether a tensor can go through the kernels; callers
     fall back to NCCL otherwise."""
 
+    nvls = False          # NVSwitch multicast buffers registered (SymmetricComm on a world with multicast support)
+    nvls_plane_elems = 0
+
+    @property
+    def nvls_active(self) -> bool:
+        """The reductions go through the multicast buffers (registered and switched on: OGB_TP_NVLS=1 or ogb_comm_set_options)."""
+        return self.nvls and _lib.lib().ogb_comm_has_nvls(self.device.index) == 2
+
     def fits(self, x: torch.Tensor, planes: int = 1) -> bool:
-        nbytes = x.numel() * x.element_size() // planes
-        return x.is_cuda and x.is_contiguous() and nbytes % 16 == 0 and nbytes // 2 <= self.plane_elems and x.data_ptr() % 16 == 0
+        """planes: leading slices of a reduce-scatter input (each is one plane of the flagged-line buffers)."""
+        nbytes = x.numel() * x.element_size()
+        if not (x.is_cuda and x.is_contiguous() and (nbytes // planes) % 16 == 0 and x.data_ptr() % 16 == 0):
+            return False
+        return nbytes // planes // 2 <= self.plane_elems or (self.nvls_active and nbytes // 2 <= self.nvls_plane_elems)
+
+    def fits_gather(self, x: torch.Tensor) -> bool:
+        return self.fits(x) and (x.numel() * x.element_size() // 2 <= self.plane_elems or
+                                 (self.nvls_active and self.size * x.numel() * x.element_size() // 2 <= self.nvls_plane_elems))
 
     def _run(self, mode: int, x: torch.Tensor, out: torch.Tensor, residual, n_units: int):
         from .. import ops
@@ -52,7 +69,7 @@ class _Collectives:
 
     def all_gather(self, x: torch.Tensor) -> torch.Tensor:
         """[world, *x.shape]: every rank's tensor, any dtype."""
-        assert self.fits(x)
+        assert self.fits_gather(x)
         out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
         return self._run(1, x, out, None, x.numel() * x.element_size() // 2)
 
@@ -102,4 +119,36 @@ class SymmetricComm(_Collectives):
         dist.barrier(group=group)
         _lib.init_device(device.index)
         _register(device.index, size, rank, [int(p) for p in self.buf_h.buffer_ptrs], self.epoch, plane_elems)
+        dist.barrier(group=group)
+        if __import__("os").environ.get("OGB_TP_NVLS", "") != "0":      # "0": do not even map the multicast buffers
+            self._register_nvls(symm_mem, group, NVLS_PLANE_ELEMS)
+
+    def _register_nvls(self, symm_mem, group, elems: int) -> None:
+        """Second symmetric allocation for the multicast (NVLS) kernels: [data: 2 planes][out: 2 planes][counters], reached both
+        through this rank's address and through the allocation's multicast address.  Skipped (the flagged-line kernels keep
+        serving) when the allocation has no multicast mapping: no NVSwitch, or multicast objects cannot be shared here."""
+        import torch.distributed as dist
+        dev = self.device
+        ctr_bytes = 2 * NV_MAX_CTAS * 4
+        total = 2 * (2 * elems * 2) + ctr_bytes
+        self.nv_buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.nv_h = symm_mem.rendezvous(self.nv_buf, group)
+        mc = int(getattr(self.nv_h, "multicast_ptr", 0) or 0)
+        ok = torch.tensor([1 if mc else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if not int(ok.item()):
+            self.nv_buf = self.nv_h = None
+            return
+        self.nv_buf.zero_()
+        self.nv_expected = torch.zeros(2 * NV_MAX_CTAS, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+        base = self.nv_buf.data_ptr()
+        o_out, o_ctr = 2 * elems * 2, 2 * (2 * elems * 2)
+        P = ctypes.c_void_p
+        rc = _lib.lib().ogb_comm_register_nvls(dev.index, P(base), P(mc), P(base + o_out), P(mc + o_out), P(base + o_ctr), P(mc + o_ctr),
+                                               P(self.nv_expected.data_ptr()), elems)
+        if rc != 0:
+            raise RuntimeError(f"ogb_comm_register_nvls failed with {rc}")
+        self.nvls, self.nvls_plane_elems = True, elems
         dist.barrier(group=group)

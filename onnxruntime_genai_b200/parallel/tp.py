@@ -96,18 +96,27 @@ class TensorParallel:
             be = "nccl"
         return cls(rank, world, device, None, be)
 
-    def fused_ok(self, x: torch.Tensor) -> bool:
-        """True when the GEMM + all-reduce kernel can take this activation (decode-sized token counts)."""
-        return self.comm is not None and x.is_cuda and x.shape[0] <= self.comm.max_tokens
+    def fused_ok(self, x: torch.Tensor, n_out: Optional[int] = None) -> bool:
+        """True when the GEMM + all-reduce kernel can take this activation: decode-sized token counts with the flagged-line
+        protocol; with NVLS switched on and OGB_TP_FUSED_PREFILL=1 also any step whose [tokens, n_out] output fits the
+        multicast plane (measured slower than the persistent GEMM followed by a stand-alone all-reduce at two ranks)."""
+        if self.comm is None or not x.is_cuda:
+            return False
+        if x.shape[0] <= self.comm.max_tokens:
+            return True
+        if self.comm.nvls_active and os.environ.get("OGB_TP_FUSED_PREFILL", "0") == "1":
+            return n_out is None or x.shape[0] * n_out <= self.comm.nvls_plane_elems
+        return False
 
     # row-parallel output: sum of partials over ranks (in place)
     def reduce(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         if self.size == 1:
             return x
-        if self.comm is not None and x.dtype == torch.bfloat16 and x.numel() <= (1 << 20) and self.comm.fits(x):
-            # one-shot kernel over NVLink peer memory: every rank pushes its whole tensor to every peer, which wins while
-            # the tensor is small (latency bound); larger ones go to NCCL's bandwidth-optimal algorithms
-            return self.comm.all_reduce(x, residual)
+        if self.comm is not None and x.dtype == torch.bfloat16 and (self.comm.nvls_active or x.numel() <= (1 << 20)) and self.comm.fits(x):
+            # NVLS: the switch adds the ranks' planes (one-shot for small tensors, owner-reduces-and-multicasts for large ones).
+            # Without multicast: one-shot pushes over peer memory, which win while the tensor is small (latency bound); larger
+            # ones go to NCCL's bandwidth-optimal algorithms
+            return self.comm.all_reduce(x.contiguous(), residual)
         if x.dtype == torch.bfloat16 and not x.is_cuda:
             y = x.float()
             dist.all_reduce(y, group=self.group)
@@ -119,7 +128,7 @@ class TensorParallel:
     def gather_logits(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:
             return x
-        if self.comm is not None and self.comm.fits(x.contiguous()):
+        if self.comm is not None and self.comm.fits_gather(x.contiguous()):
             g = self.comm.all_gather(x.contiguous())
             return g.permute(1, 0, 2).reshape(x.shape[0], -1)
         parts = [torch.empty_like(x) for _ in range(self.size)]
