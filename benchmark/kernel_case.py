@@ -2,7 +2,7 @@
 
     python benchmark/kernel_case.py <case> [--tokens 64] [--iters 16] [--layers 8] [--tp 1] [--eager] [--json out.json]
 
-cases: gemm_qkv gemm_o gemm_gate_up gemm_down gemm_lm_head gemm_prefill w4_qkv w4_down attention_decode
+cases: gemm_qkv gemm_o gemm_gate_up gemm_down gemm_lm_head gemm_prefill gemm_qkv_fused gemm_gate_up_fused w4_qkv w4_down attention_decode
        attention_prefill norm rope sample argmax all; moe_fp4_gate_up moe_fp4_down moe_fp4b_gate_up moe_fp4b_down moe_bf16_gate_up moe_bf16_down
        (gpt-oss-20b experts, packed MXFP4 in the fp16 form, in the bf16 form (fp4b) or bf16 weights; not part of `all`)
 
@@ -92,6 +92,21 @@ def build_case(name, T, L, tp=1):
     """Returns (fn(i), algorithmic_bytes, flops).  tp > 1: the per-rank shapes of tensor parallelism; the row-parallel
     projections then run the fused all-reduce against a world of one (protocol cost without a peer)."""
     HQ, HKV = globals()["HQ"] // tp, max(1, globals()["HKV"] // tp)
+    if name in ("gemm_qkv_fused", "gemm_gate_up_fused"):
+        # the decode-step fusions: RMS norm folded into the projection (+ rotary embedding and KV-cache append for QKV)
+        x = _bf(T, H, std=1.0)
+        if name == "gemm_gate_up_fused":
+            N = 2 * I // tp
+            ws = [ops.interleave_gate_up(_bf(N, H)) for _ in range(L)]
+            return (lambda i: ops.gate_up_act(x, ws[i % L], interleaved=True, norm_eps=1e-5)), N * H * 2 + T * (H + N // 2) * 2, 2.0 * T * N * H
+        N = (HQ + 2 * HKV) * D
+        ws = [_bf(N, H) for _ in range(L)]
+        pos = torch.arange(T, dtype=torch.int32, device="cuda")
+        slots = torch.arange(T, dtype=torch.int32, device="cuda")
+        cos, sin = torch.randn(4096, D // 2, device="cuda"), torch.randn(4096, D // 2, device="cuda")
+        kc, vc = _bf(T + 16, HKV, D), _bf(T + 16, HKV, D)
+        return (lambda i: ops.qkv_rope_append(x, ws[i % L], None, pos, slots, cos, sin, kc, vc, HQ, HKV, D, D, norm_eps=1e-5)), \
+            N * H * 2 + T * (H + N) * 2, 2.0 * T * N * H
     if name.startswith("gemm_") or name.startswith("w4_"):
         shapes = {"gemm_qkv": ((HQ + 2 * HKV) * D, H), "gemm_o": (H, HQ * D), "gemm_gate_up": (2 * I // tp, H), "gemm_down": (H, I // tp),
                   "gemm_lm_head": (V // tp, H), "gemm_prefill": (2 * I // tp, H), "w4_qkv": (9216 // tp, 3072), "w4_down": (3072, 8192 // tp)}

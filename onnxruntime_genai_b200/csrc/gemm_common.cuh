@@ -103,20 +103,22 @@ struct GemmParams {
   FusedRope rope;
 };
 
-template <int BT>
+// DEEP: one CTA per SM with a pipeline twice as deep, for launches of at most one CTA per SM (the same bytes in flight per SM
+// as two resident CTAs of the shallow form would have, which such a launch never gets).
+template <int BT, bool DEEP = false>
 struct GemmCfg {
   static constexpr int A_TILE_BYTES = BT * GEMM_BLOCK_K * 2;
   static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES;
   // Decode-sized tiles keep two CTAs per SM: more bytes in flight per SM, dynamic balance between
   // SMs, and room for the next kernel's CTAs to become resident and prefetch weights.
-  static constexpr bool TWO_PER_SM = BT <= 128;   // 128-token tiles: two CTAs per SM, one's epilogue under the other's main loop
+  static constexpr bool TWO_PER_SM = BT <= 128 && !DEEP;   // 128-token tiles: two CTAs per SM, one's epilogue under the other's main loop
   static constexpr int BUDGET = TWO_PER_SM ? 100 * 1024 : 196 * 1024;
   static constexpr int MAX_STAGES = BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int STAGES = MAX_STAGES > (DEEP ? 12 : 8) ? (DEEP ? 12 : 8) : MAX_STAGES;
   static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
   static constexpr int PARTIAL_BYTES = BT * GEMM_BLOCK_N * 4;  // fp32 tile parked in stage memory
-  static constexpr int SSQ_OFFSET = STAGES * STAGE_BYTES + 256;   // per-row sums of squares (folded norm), after the barriers
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + BT * 4;
+  static constexpr int SSQ_OFFSET = STAGES * STAGE_BYTES + 512;   // per-row sums of squares (folded norm), after the barriers
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/ + BT * 4;
   static_assert(PARTIAL_BYTES + 16 * 128 * 16 <= STAGES * STAGE_BYTES, "the parked tile and the reduction's staging lines must fit in the pipeline memory");
 };
 
@@ -414,8 +416,12 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
           }
         }
       } else {
+        const bool roped = COMM == 0 && p.rope.positions != nullptr;
+        // the token's position and cache slot are fetched first: their latency passes under the reduction below
+        const int pos_raw = roped ? p.rope.positions[m] : 0;
+        const int slot = roped ? p.rope.slots[m] : -1;
         reduce8(mc, oc * 8, rs, v);
-        if (COMM == 0 && p.rope.positions != nullptr) {
+        if (roped) {
           // Fused rotary embedding + KV-cache append of a QKV projection (heads never straddle a tile: 128 % D == 0).
           // Query heads go to C rotated; key heads go rotated, value heads as they are, to this token's cache slot.
           const FusedRope& R = p.rope;
@@ -423,17 +429,18 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint8_t* smem
           if (head < R.Hq + R.Hkv && d < R.rot) {
             const int half = R.rot >> 1;
             const bool first = d < half;
+            const int pos = pos_raw < 0 ? 0 : (pos_raw >= R.max_pos ? R.max_pos - 1 : pos_raw);
+            const size_t ci = size_t(pos) * half + (first ? d : d - half);      // a multiple of 8: 32-byte aligned rows of 8 floats
+            const float4 c0 = *reinterpret_cast<const float4*>(R.cos + ci), c1 = *reinterpret_cast<const float4*>(R.cos + ci + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(R.sin + ci), s1 = *reinterpret_cast<const float4*>(R.sin + ci + 4);
             float u[8];
             reduce8(mc, first ? oc * 8 + half : oc * 8 - half, rs, u);
-            int pos = R.positions[m];
-            pos = pos < 0 ? 0 : (pos >= R.max_pos ? R.max_pos - 1 : pos);
-            const float* cs = R.cos + size_t(pos) * half + (first ? d : d - half);
-            const float* sn = R.sin + size_t(pos) * half + (first ? d : d - half);
+            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = first ? v[j] * cs[j] - u[j] * sn[j] : v[j] * cs[j] + u[j] * sn[j];
           }
           if (head >= R.Hq) {
-            const int slot = R.slots[m];
             if (slot >= 0 && col < p.N) {
               const bool is_k = head < R.Hq + R.Hkv;
               __nv_bfloat16* dst = (is_k ? R.k_cache : R.v_cache) + (size_t(slot) * R.Hkv + (head - R.Hq - (is_k ? 0 : R.Hkv))) * R.D + d;

@@ -47,10 +47,10 @@
 
 namespace ogb {
 
-template <int BT, int COMM>
-__global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BT>::TWO_PER_SM ? 2 : 1)
+template <int BT, int COMM, bool DEEP>
+__global__ void __launch_bounds__(GEMM_THREADS, GemmCfg<BT, DEEP>::TWO_PER_SM ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
-  using Cfg = GemmCfg<BT>;
+  using Cfg = GemmCfg<BT, DEEP>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -307,10 +307,10 @@ bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, 
   return MakeMap(out, ptr, rows, cols, ld, box_rows);
 }
 
-template <int BT, int COMM>
+template <int BT, int COMM, bool DEEP>
 static int LaunchC(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  using Cfg = GemmCfg<BT>;
-  auto kern = gemm_tcgen05_kernel<BT, COMM>;
+  using Cfg = GemmCfg<BT, DEEP>;
+  auto kern = gemm_tcgen05_kernel<BT, COMM, DEEP>;
   static bool configured[OGB_MAX_DEVICES] = {};
   if (!set_max_dyn_smem(kern, Cfg::SMEM_BYTES, configured)) return -3;
   cudaLaunchConfig_t cfg = {};
@@ -337,11 +337,26 @@ static int LaunchC(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParam
   return cudaLaunchKernelEx(&cfg, kern, tw, ta, p) == cudaSuccess ? 0 : -4;
 }
 
+static int ogb_sm_count_current() {
+  static int n = 0;
+  if (n == 0) { int dev = 0; if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 148; }
+  return n;
+}
+
 // One kernel instantiation per token tile and per reduction form: the local form does not carry the reductions' code.
 template <int BT>
 static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  if (!p.comm_epilogue) return LaunchC<BT, 0>(tw, ta, p, grid, stream);
-  return p.nvls ? LaunchC<BT, 2>(tw, ta, p, grid, stream) : LaunchC<BT, 1>(tw, ta, p, grid, stream);
+  // deep pipeline, one CTA per SM: decode-sized launches that put at most one CTA on an SM anyway
+  if constexpr (BT <= 64) {
+    static const int deep_env = [] { const char* e = getenv("OGB_GEMM_DEEP"); return e ? atoi(e) : -1; }();
+    const bool deep = deep_env != 0;      // OGB_GEMM_DEEP=0: always the two-CTAs-per-SM form
+    if (deep && (long long)grid.x * grid.y * grid.z <= ogb_sm_count_current()) {
+      if (!p.comm_epilogue) return LaunchC<BT, 0, true>(tw, ta, p, grid, stream);
+      if (!p.nvls) return LaunchC<BT, 1, true>(tw, ta, p, grid, stream);
+    }
+  }
+  if (!p.comm_epilogue) return LaunchC<BT, 0, false>(tw, ta, p, grid, stream);
+  return p.nvls ? LaunchC<BT, 2, false>(tw, ta, p, grid, stream) : LaunchC<BT, 1, false>(tw, ta, p, grid, stream);
 }
 
 // How many split-K clusters of `splits` CTAs of the decode kernel the device can hold at once (0: the query failed).  The
@@ -349,7 +364,7 @@ static int Launch(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams
 template <int BT>
 static int MaxActiveClusters(int splits) {
   using Cfg = GemmCfg<BT>;
-  auto kern = gemm_tcgen05_kernel<BT, 0>;
+  auto kern = gemm_tcgen05_kernel<BT, 0, false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1, 1, unsigned(splits));
@@ -607,7 +622,7 @@ OGB_API int ogb_gemm_token_tile(int M, int dual) {
 // Number of split-K partitions (cluster size along z: 1, 2, 4 or 8).  Every CTA of the launch must fit on the GPU at once
 // (two resident CTAs per SM for decode-sized tiles).  Up to 4 partitions pay off as soon as each keeps two k-blocks: the
 // epilogue of a tile (one thread per 8 outputs, fetched cold) is divided between the cluster's CTAs, which matters more than
-// the short main loops.  8 partitions need 16 k-blocks each, or a launch so small that it fits one CTA per SM.
+// the short main loops.  Launches of at most one CTA per SM run a pipeline twice as deep (one CTA per SM: o 13.0 -> 12.2 us).
 // Measured on B200 at 64 tokens, us per launch (benchmark/kernel_case.py --gemm_splits; rows marked tpN are the per-rank
 // shapes of N-way tensor parallelism with the fused all-reduce talking to itself):
 //   qkv  (N 6144, K 4096):  s=2 16.8  s=4 15.5  s=8 25.8 (a second wave from 288 CTAs on)
@@ -627,7 +642,9 @@ OGB_API int ogb_gemm_auto_splits(int M, int N, int K, int dual, int sm_count) {
   for (int s = 2; s <= 8; s *= 2) {
     if (s > bt || tiles * s > slots) break;
     const int kbs = total_kb / s;
-    const bool ok = s <= 4 ? kbs >= 2 : (kbs >= 16 || (tiles * s <= sm_count && kbs >= 8));
+    // 8 partitions: long k ranges whose 4-way split would not fit one CTA per SM (that form runs the deep pipeline: down
+    // 25.1 us at s=4 against 27.7 at s=8), or launches so small that even 8 partitions leave one CTA per SM
+    const bool ok = s <= 4 ? kbs >= 2 : ((kbs >= 16 && tiles * 4 > sm_count) || (tiles * s <= sm_count && kbs >= 8));
     if (ok) best = s;
   }
   return best;
@@ -717,6 +734,18 @@ OGB_API long long ogb_comm_capacity(int device) {
 OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
                           const void* bias, const void* residual, int ldr, int flags, int splits, int device, int* status,
                           int sm_count, void* stream_) {
+  return ogb_gemm_bf16_fused(A, lda, W, ldw, C, ldc, M, N, K, bias, residual, ldr, flags, splits, device, status, sm_count, stream_, nullptr);
+}
+
+// ogb_gemm_bf16 with the decode-step fusions of `f` (see OgbGemmFused in kernels.h; nullptr: none):
+//  * norm_eps > 0: A holds un-normalised rows and W carries the RMS norm's weight; row m of the product is multiplied by
+//    rsqrt(mean(A[m]^2) + norm_eps) before bias and activation (SimplifiedLayerNormalization folded into its consumer);
+//  * positions != nullptr: QKV projection with rotary embedding and KV-cache append in the epilogue: C [M, Hq * D] receives
+//    the rotated queries only, keys (rotated) and values go to row slots[m] of the caches.  Needs 128 % D == 0, rot % 16 == 0,
+//    N == (Hq + 2 * Hkv) * D, bf16 caches, and excludes the reductions, fp32 output and the paired activation.
+OGB_API int ogb_gemm_bf16_fused(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                                const void* bias, const void* residual, int ldr, int flags, int splits, int device, int* status,
+                                int sm_count, void* stream_, const OgbGemmFused* f) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) || (lda % 8) || (ldw % 8)) return -1;  // 16-byte global strides for TMA
@@ -780,8 +809,23 @@ OGB_API int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* 
     p.comm = c;          // the mainloop needs the buffer and epoch pointers; the epilogue stays local unless bits 2/3 are set
     p.ag_rows = per;
   }
+  bool extras = false;
+  if (f && f->norm_eps > 0.f) {
+    if (p.ag_rows > 0) return -1;        // gathered activations are assembled by the warps that would sum the squares
+    p.norm_eps = f->norm_eps;
+    extras = true;
+  }
+  if (f && f->positions) {
+    if (fused_ar || out_fp32 || act_pair || f->D <= 0 || (128 % f->D) || (f->rot % 16) || f->rot > f->D || N != (f->Hq + 2 * f->Hkv) * f->D ||
+        !f->slots || !f->k_cache || !f->v_cache || (f->rot > 0 && (!f->cos || !f->sin)))
+      return -1;
+    p.rope.positions = f->positions; p.rope.slots = f->slots; p.rope.cos = f->cos; p.rope.sin = f->sin;
+    p.rope.k_cache = static_cast<__nv_bfloat16*>(f->k_cache); p.rope.v_cache = static_cast<__nv_bfloat16*>(f->v_cache);
+    p.rope.Hq = f->Hq; p.rope.Hkv = f->Hkv; p.rope.D = f->D; p.rope.rot = f->rot; p.rope.max_pos = f->max_pos;
+    extras = true;
+  }
   static const int persistent = [] { const char* e = getenv("OGB_GEMM_PERSISTENT"); return (e && e[0] == '0') ? 0 : 1; }();
-  if (persistent && auto_split && bt == 256 && splits == 1 && !p.comm_epilogue && p.ag_rows == 0 && n_tiles * m_tiles >= sm_count)
+  if (persistent && !extras && auto_split && bt == 256 && splits == 1 && !p.comm_epilogue && p.ag_rows == 0 && n_tiles * m_tiles >= sm_count)
     return LaunchPersistent(tw, ta, p, n_tiles, m_tiles, sm_count, stream);
   dim3 grid(n_tiles, m_tiles, splits);
   switch (bt) {

@@ -30,6 +30,21 @@ long long ogb_comm_capacity(int device);
 int ogb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
                   const void* residual, int ldr, int flags, int splits, int device, int* status, int sm_count, void* stream);
 
+// Decode-step fusions of ogb_gemm_bf16_fused (all pointers are device pointers).
+typedef struct OgbGemmFused {
+  float norm_eps;            // > 0: RMS norm folded into the GEMM (row scale rsqrt(mean(x^2) + eps); the weight carries the norm's weight)
+  const int32_t* positions;  // != NULL: QKV projection with rotary embedding + KV-cache append in the epilogue
+  const int32_t* slots;      // cache row of each token (< 0: not stored)
+  const float* cos;          // [max_pos, rot / 2]
+  const float* sin;
+  void* k_cache;             // bf16 [slots, Hkv, D]
+  void* v_cache;
+  int Hq, Hkv, D, rot, max_pos;
+} OgbGemmFused;
+int ogb_gemm_bf16_fused(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const void* bias,
+                        const void* residual, int ldr, int flags, int splits, int device, int* status, int sm_count, void* stream,
+                        const OgbGemmFused* fused);
+
 // Grouped expert GEMM over token rows sorted by expert (tile list from ogb_moe_sort); act_kind 1 = silu(gate)*up,
 // 2 = clamped SwiGLU(alpha, limit); flags as above (bit 2 unused).
 int ogb_moe_gemm(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int rows_total, int N, int K, int experts,

@@ -181,6 +181,8 @@ class LayerWeights:
     exp_hi: int = 0
     exp_blocked: bool = False  # gate/up rows in blocks of 64 gate + 64 up (grouped-GEMM layout) instead of even/odd
     lora: Dict[str, dict] = field(default_factory=dict)
+    fold_ln1: Optional[torch.Tensor] = None    # norm weights that were multiplied into qkv_w / gate_up_w (see DecoderModel.fold_norms)
+    fold_ln2: Optional[torch.Tensor] = None
     window: int = 0
     gate_up_interleaved: bool = False  # gate/up rows stored in blocks of 64 (layout of the fused SiLU*mul GEMM)
 
@@ -210,6 +212,8 @@ class DecoderModel:
         self.conv_channels_local = arch.hidden_size // self.tp.size      # channels of a hybrid model's convolution layers
         self.inter_local = arch.intermediate_size // self.tp.size
         self.active_adapter = None  # name -> used by the LoRA hooks
+        self.norms_folded = False
+        self.fuse_steps = True      # decode-sized steps of a folded model take the five-kernel layer (tests compare both forms)
 
     # ------------------------------------------------------------------------------------ helpers
     def _linear(self, x, w, b=None, residual=None, lora=None, out_fp32=False):
@@ -267,6 +271,98 @@ class DecoderModel:
         if self.active_adapter is None:
             return None
         return lw.lora.get(self.active_adapter, {}).get(proj)
+
+    # ------------------------------------------------------------------------------------ decode-step fusions
+    def fold_norms(self) -> bool:
+        """Multiplies the RMS-norm weights of the attention and MLP inputs into the QKV and gate/up projection weights
+        (W[n, k] * g[k]) and replaces the norm weights by ones.  Every forward path stays valid (a norm with unit weight
+        followed by the folded projection is the same function), and decode-sized steps can then skip the norm kernels:
+        the projection GEMM takes the un-normalised residual stream, sums the squares of each row as the tiles pass through
+        shared memory and applies rsqrt(mean + eps) in its epilogue (`ops.linear(..., norm_eps=)`).  Semantics: the
+        SkipSimplifiedLayerNormalization -> MatMul pairs of the reference graph
+        (src/python/py/models/builders/base.py:2342-2403, 2149-2222).  bf16 CUDA models with plain (unquantised) gated
+        MLPs only; returns whether the model was folded."""
+        import os
+        a = self.arch
+        if self.norms_folded:
+            return True
+        if (self.device.type != "cuda" or self.dtype != torch.bfloat16 or a.layernorm or a.parallel_block or a.num_experts > 0 or
+                not a.mlp_gated or os.environ.get("OGB_FOLD_NORMS", "1") == "0"):
+            return False
+        for lw in self.layers:
+            if not (isinstance(lw.qkv_w, torch.Tensor) and isinstance(lw.gate_up_w, torch.Tensor) and lw.conv_in_w is None and
+                    lw.cross_q_w is None and lw.ln1_b is None and lw.ln2_b is None and lw.qkv_w.dtype == torch.bfloat16):
+                return False
+        for lw in self.layers:
+            lw.fold_ln1, lw.fold_ln2 = lw.ln1_w, lw.ln2_w
+            lw.qkv_w = (lw.qkv_w.float() * lw.ln1_w.float()[None, :]).to(torch.bfloat16)
+            lw.gate_up_w = (lw.gate_up_w.float() * lw.ln2_w.float()[None, :]).to(torch.bfloat16)
+            lw.ln1_w = torch.ones_like(lw.ln1_w)
+            lw.ln2_w = torch.ones_like(lw.ln2_w)
+        self.norms_folded = True
+        return True
+
+    def _fused_step_ok(self, s: StepInputs) -> bool:
+        """Decode-sized steps of a folded model run five kernels per layer: QKV (+ norm, rotary, cache append), attention,
+        o_proj (+ residual, + all-reduce), gate/up (+ norm, SiLU * mul), down_proj (+ residual, + all-reduce)."""
+        a = self.arch
+        lw = self.layers[0]
+        return (self.norms_folded and self.fuse_steps and self.active_adapter is None and s.input_ids.shape[0] <= ops.FUSED_MAX_TOKENS and
+                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and
+                lw.post_attn_norm_w is None and lw.post_ffn_norm_w is None and not s.cross_qk_heads)
+
+    def _forward_fused(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
+        a = self.arch
+        # the residual stream is updated in place by the projections' epilogues: never the caller's tensor
+        h = s.inputs_embeds.clone() if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
+        if a.learned_positions:
+            h = h + ops.embedding(s.positions, self.pos_embed, 1.0)
+        rot = 0 if a.learned_positions else a.rotary_dim
+        cos, sin = self.cos, self.sin
+        if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
+            cos, sin = self.cos_small, self.sin_small
+        for li, lw in enumerate(self.layers):
+            kc, vc, windowed = kv.layer(li)
+            slots = s.slot_mapping_w if windowed else s.slot_mapping
+            table = s.block_table_w if windowed else s.block_table
+            if (lw.q_norm_w is None and lw.k_norm_w is None and not a.rotary_interleaved and not a.mrope_section and
+                    ops.qkv_fusable(a.head_dim, rot if cos is not None else 0, kc)):
+                q = ops.qkv_rope_append(h, lw.qkv_w, lw.qkv_b, s.positions, slots, cos, sin, kc, vc, self.heads_local,
+                                        self.kv_heads_local, a.head_dim, rot, norm_eps=a.norm_eps)
+            else:
+                q = ops.linear(h, lw.qkv_w, lw.qkv_b, norm_eps=a.norm_eps)
+                ops.rope_kv_append(q, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local, a.head_dim, rot,
+                                   a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
+                                   s.positions3 if a.mrope_section else None, a.mrope_section)
+            att = self._attention(s, q, kc, vc, table, kv.block_size, lw)
+            h = self._row_parallel_residual(att, lw.o_w, lw.o_b, h)
+            act = ops.gate_up_act(h, lw.gate_up_w, lw.gate_up_b, a.activation, interleaved=lw.gate_up_interleaved, norm_eps=a.norm_eps)
+            h = self._row_parallel_residual(act, lw.down_w, lw.down_b, h)
+        x, _ = ops.norm(h, self.final_norm_w, a.norm_eps, None, self.final_norm_b, a.layernorm)
+        return self._logits(s, x)
+
+    def _row_parallel_residual(self, x, w, b, residual):
+        """residual + (row-parallel projection summed over the tensor-parallel ranks), written over `residual`."""
+        tp = self.tp
+        bias = b if tp.rank == 0 else None
+        if tp.size == 1:
+            return ops.linear(x, w, bias, residual=residual, out=residual)
+        if isinstance(w, torch.Tensor) and tp.fused_ok(x, w.shape[0]):
+            return ops.linear(x, w, bias, residual=residual, out=residual, all_reduce=True)
+        return tp.reduce(ops.linear(x, w, bias), residual)
+
+    def _logits(self, s: StepInputs, x: torch.Tensor) -> torch.Tensor:
+        a = self.arch
+        self.last_hidden = x
+        if s.logits_rows is not None:
+            x = ops.gather_rows(x, s.logits_rows)
+        logits = ops.linear(x, self.lm_head_w, self.lm_head_b, out_fp32=True)
+        logits = self.tp.gather_logits(logits)
+        if a.logits_scale != 1.0:
+            logits = logits * a.logits_scale
+        if a.final_logit_softcap > 0:
+            logits = torch.tanh(logits / a.final_logit_softcap) * a.final_logit_softcap
+        return logits
 
     # ------------------------------------------------------------------------------------ forward
     # ------------------------------------------------------------------------------------ sequence-parallel form
@@ -340,6 +436,8 @@ class DecoderModel:
         a = self.arch
         if self._sp_ok(s):
             return self._forward_sp(s, kv)
+        if self._fused_step_ok(s):
+            return self._forward_fused(s, kv)
         h = s.inputs_embeds if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
         if a.learned_positions:
             h = h + ops.embedding(s.positions, self.pos_embed, 1.0)
@@ -400,16 +498,7 @@ class DecoderModel:
             if a.residual_multiplier != 1.0:
                 h = (h.float() * a.residual_multiplier).to(h.dtype)
         x, residual = ops.norm(h, self.final_norm_w, a.norm_eps, residual, self.final_norm_b, a.layernorm)
-        self.last_hidden = x
-        if s.logits_rows is not None:
-            x = ops.gather_rows(x, s.logits_rows)
-        logits = ops.linear(x, self.lm_head_w, self.lm_head_b, out_fp32=True)
-        logits = self.tp.gather_logits(logits)
-        if a.logits_scale != 1.0:
-            logits = logits * a.logits_scale
-        if a.final_logit_softcap > 0:
-            logits = torch.tanh(logits / a.final_logit_softcap) * a.final_logit_softcap
-        return logits
+        return self._logits(s, x)
 
     def _cross_qk(self, s: StepInputs, li: int, q: torch.Tensor, ck: torch.Tensor) -> None:
         """Scaled query-key scores (before the softmax) of the listed alignment heads of layer `li` against the encoder keys,

@@ -593,4 +593,5 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
     if hadd is not None:
         model.lm_head_b = _vec(g, hadd.inputs[1], dtype, device, rows)
     g.lm.close()
+    model.fold_norms()      # bf16 CUDA models: the input norms' weights move into the QKV and gate/up projections
     return model

@@ -94,6 +94,12 @@ class Adapters:
             b = b if b.shape[1] == r else b.t()        # -> [n, r]
             if a.shape[1] != K or b.shape[1] != r:
                 raise RuntimeError(f"adapter '{name}': layer {layer} {proj} has inconsistent shapes {tuple(ab['A'].shape)} / {tuple(ab['B'].shape)}")
+            lw_ = dec.layers[layer]
+            fold = lw_.fold_ln1 if target == "qkv_proj" else (lw_.fold_ln2 if target == "gate_up_proj" else None)
+            if fold is not None:
+                # the model's input norms were folded into these projections (their norm weights are ones now): the low-rank
+                # path sees rows scaled by 1 / rms only, so A takes the norm's weight as the base weight did
+                a = a * fold.float().cpu()[None, :]
             rp = (r + 7) // 8 * 8                       # TMA needs 16-byte rows
             ap = torch.zeros(rp, K)
             ap[:r] = a

@@ -113,14 +113,41 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) ->
 GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A = 1, 2, 4, 8, 16
 
 
-def _gemm(x, w, out, bias, residual, flags, splits):
+FUSED_MAX_TOKENS = 128     # the decode-step fusions (folded norm, rotary + cache append) run in the decode-sized GEMM kernel
+
+
+def _gemm(x, w, out, bias, residual, flags, splits, fused=None):
     ws = workspace(x.device)
     T, K = x.shape
-    rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, w.shape[0], K, _ptr(bias),
-                                  _ptr(residual), residual.stride(0) if residual is not None else 0, int(flags), int(splits),
-                                  ws.index, ws.status, ws.sm_count, _stream())
+    if fused is None:
+        rc = _lib.lib().ogb_gemm_bf16(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, w.shape[0], K, _ptr(bias),
+                                      _ptr(residual), residual.stride(0) if residual is not None else 0, int(flags), int(splits),
+                                      ws.index, ws.status, ws.sm_count, _stream())
+    else:
+        import ctypes
+        rc = _lib.lib().ogb_gemm_bf16_fused(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), T, w.shape[0], K,
+                                            _ptr(bias), _ptr(residual), residual.stride(0) if residual is not None else 0, int(flags),
+                                            int(splits), ws.index, ws.status, ws.sm_count, _stream(), ctypes.byref(fused))
     _lib.check(rc, "gemm_bf16")
     return out
+
+
+_ones = {}
+
+
+def _unit_weight(n: int, device) -> torch.Tensor:
+    key = (n, str(device))
+    t = _ones.get(key)
+    if t is None:
+        t = _ones[key] = torch.ones(n, dtype=torch.bfloat16, device=device)
+    return t
+
+
+def rms_scale(x, eps: float):
+    """x / rms(x) (no weight): the rows a GEMM with a folded norm would see, for the paths that cannot fold."""
+    if not x.is_cuda:
+        return ref.rms_scale(x, eps)
+    return norm(x, _unit_weight(x.shape[1], x.device), eps)[0]
 
 
 def _gemm_w4(x, w, out, bias, residual, flags, splits):
@@ -132,12 +159,16 @@ def _gemm_w4(x, w, out, bias, residual, flags, splits):
     return out
 
 
-def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None):
+def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, all_reduce=False, reduce_scatter=None, norm_eps=0.0):
     """y = x @ w.T (+bias) (+residual).  x [T, K] bf16, w [N, K] bf16 (K contiguous).  With all_reduce the
     partial products of the tensor-parallel ranks are summed inside the kernel over NVLink peer memory.
     reduce_scatter=(rank, world): the sum is scattered by token rows instead (sequence-parallel form): the result has
-    this rank's rows [rank * ceil(T / world), ...) only, and `residual` is that slice."""
+    this rank's rows [rank * ceil(T / world), ...) only, and `residual` is that slice.
+    norm_eps > 0: an RMS norm folded into the GEMM - x holds the un-normalised rows, w already carries the norm's weight
+    (w * norm_weight along K), and row m of the product is scaled by rsqrt(mean(x[m]^2) + norm_eps)."""
     if isinstance(w, W4Weight):
+        if norm_eps > 0:
+            x = rms_scale(x, norm_eps)
         if not x.is_cuda:
             return ref.linear(x, w.dequantize(), bias, residual, out_fp32)
         if all_reduce:
@@ -146,9 +177,15 @@ def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, a
             out = torch.empty(x.shape[0], w.N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
         return _gemm_w4(x, w, out, bias, residual, GEMM_FP32_OUT if out_fp32 else 0, splits)
     if not x.is_cuda:
-        return ref.linear(x, w, bias, residual, out_fp32)
+        return ref.linear(x, w, bias, residual, out_fp32, norm_eps)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert x.stride(-1) == 1 and w.stride(-1) == 1
+    fused = None
+    if norm_eps > 0:
+        if x.shape[0] > FUSED_MAX_TOKENS:
+            x = rms_scale(x, norm_eps)     # prefill-sized steps run the persistent kernel: normalise first
+        else:
+            fused = _lib.GemmFused(norm_eps=float(norm_eps))
     rows_out = x.shape[0]
     if reduce_scatter is not None:
         rank, world = reduce_scatter
@@ -157,7 +194,30 @@ def linear(x, w, bias=None, residual=None, out_fp32=False, out=None, splits=0, a
     if out is None:
         out = torch.empty(rows_out, w.shape[0], dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
     flags = (GEMM_FP32_OUT if out_fp32 else 0) | (GEMM_ALLREDUCE if all_reduce else 0) | (GEMM_REDUCE_SCATTER if reduce_scatter else 0)
-    return _gemm(x, w, out, bias, residual, flags, splits)
+    return _gemm(x, w, out, bias, residual, flags, splits, fused)
+
+
+def qkv_rope_append(x, w, bias, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, norm_eps=0.0):
+    """QKV projection + rotary embedding + KV-cache append (+ folded RMS norm) as one kernel for decode-sized steps.
+    Returns a tensor whose first Hq * D columns are the rotated queries (what paged_attention reads); rotated keys and the
+    values of token m are written to row slots[m] of the caches.  Non-interleaved rotation only; head_dim must divide 128,
+    the rotary dimension must be a multiple of 16 and the caches bf16 - `qkv_fusable` tells; other cases (and prefill-sized
+    steps) take the separate kernels."""
+    T = x.shape[0]
+    if x.is_cuda and T <= FUSED_MAX_TOKENS and not isinstance(w, W4Weight) and qkv_fusable(D, rot, k_cache):
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] == (Hq + 2 * Hkv) * D
+        q = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=x.device)
+        f = _lib.GemmFused(norm_eps=float(norm_eps), positions=_ptr(positions), slots=_ptr(slots), cos=_ptr(cos_cache), sin=_ptr(sin_cache),
+                           k_cache=_ptr(k_cache), v_cache=_ptr(v_cache), Hq=Hq, Hkv=Hkv, D=D, rot=int(rot if cos_cache is not None else 0),
+                           max_pos=cos_cache.shape[0] if cos_cache is not None else 1)
+        return _gemm(x, w, q, bias, None, 0, 0, f)
+    qkv = linear(x, w, bias, norm_eps=norm_eps)
+    rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot)
+    return qkv
+
+
+def qkv_fusable(D: int, rot: int, k_cache) -> bool:
+    return 128 % D == 0 and rot % 16 == 0 and k_cache.dtype == torch.bfloat16
 
 
 def linear_gathered(M: int, w, bias=None, out_fp32=False, act_pair=False, splits=0):
@@ -185,9 +245,18 @@ def interleave_gate_up(w: torch.Tensor, block: int = 64) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(w.shape).contiguous()
 
 
-def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False):
+def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=False, norm_eps=0.0):
     """act(x @ Wg.T) * (x @ Wu.T).  w is [2I, K]: stacked [Wg; Wu], or (interleaved=True) blocks of 64 gate
-    rows + 64 up rows as produced by interleave_gate_up (the layout the fused kernel needs)."""
+    rows + 64 up rows as produced by interleave_gate_up (the layout the fused kernel needs).  norm_eps: as in `linear`."""
+    fused = None
+    if norm_eps > 0:
+        if not x.is_cuda:
+            return ref.gate_up_act(x, w.dequantize() if isinstance(w, W4Weight) else w, bias, act,
+                                   w.interleaved if isinstance(w, W4Weight) else interleaved, norm_eps)
+        if isinstance(w, W4Weight) or x.shape[0] > FUSED_MAX_TOKENS or act != "silu" or not interleaved or (w.shape[0] // 2) % 64:
+            x = rms_scale(x, norm_eps)
+        else:
+            fused = _lib.GemmFused(norm_eps=float(norm_eps))
     if isinstance(w, W4Weight):
         if not x.is_cuda:
             return ref.gate_up_act(x, w.dequantize(), bias, act, w.interleaved)
@@ -210,7 +279,7 @@ def gate_up_act(x, w, bias=None, act="silu", out=None, splits=0, interleaved=Fal
         return act_mul(y.contiguous(), act)
     if out is None:
         out = torch.empty(x.shape[0], inter, dtype=torch.bfloat16, device=x.device)
-    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR, splits)
+    return _gemm(x, w, out, bias, None, GEMM_ACT_PAIR, splits, fused)
 
 
 def act_mul(x, act="silu"):

@@ -16,6 +16,14 @@ _lib = None
 _initialised_devices = set()
 
 _P = c_void_p
+
+
+class GemmFused(ctypes.Structure):
+    """OgbGemmFused of csrc/kernels.h: the decode-step fusions of ogb_gemm_bf16_fused."""
+    _fields_ = [("norm_eps", c_float), ("positions", _P), ("slots", _P), ("cos", _P), ("sin", _P), ("k_cache", _P), ("v_cache", _P),
+                ("Hq", c_int), ("Hkv", c_int), ("D", c_int), ("rot", c_int), ("max_pos", c_int)]
+
+
 _SIGS = {
     "ogb_runtime_init": (c_int, [c_int]),
     "ogb_status_device_ptr": (_P, [c_int]),
@@ -25,6 +33,7 @@ _SIGS = {
     "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "ogb_gemm_max_active_clusters": (c_int, [c_int, c_int]),
     "ogb_gemm_bf16": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P]),
+    "ogb_gemm_bf16_fused": (c_int, [_P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, c_int, c_int, _P, c_int, _P, _P]),
     "ogb_comm_register": (c_int, [c_int, c_int, c_int, _P, _P, c_longlong]),
     "ogb_comm_register_nvls": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, c_longlong]),
     "ogb_comm_has_nvls": (c_int, [c_int]),

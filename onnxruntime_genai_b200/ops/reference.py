@@ -37,7 +37,15 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False):
     return y.to(x.dtype), new_res
 
 
-def linear(x, w, bias=None, residual=None, out_fp32=False):
+def rms_scale(x, eps):
+    """x / rms(x) without a weight, in x's dtype: what a norm folded into the next GEMM applies to the rows."""
+    h = x.float()
+    return (h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def linear(x, w, bias=None, residual=None, out_fp32=False, norm_eps=0.0):
+    if norm_eps > 0:
+        x = rms_scale(x, norm_eps)
     y = x.float() @ w.float().t()
     if bias is not None:
         y = y + bias.float()
@@ -46,8 +54,10 @@ def linear(x, w, bias=None, residual=None, out_fp32=False):
     return y if out_fp32 else y.to(x.dtype)
 
 
-def gate_up_act(x, w, bias=None, act="silu", interleaved=False):
+def gate_up_act(x, w, bias=None, act="silu", interleaved=False, norm_eps=0.0):
     """w is the stacked [gate; up] weight of shape [2I, K] (or 64-row interleaved blocks)."""
+    if norm_eps > 0:
+        x = rms_scale(x, norm_eps)
     y = x.float() @ w.float().t()
     if bias is not None:
         y = y + bias.float()

@@ -70,8 +70,41 @@ def test_gpu_decode_steps_track_cpu(dirs):
     assert np.abs(lg - lc).max() < 0.08 * lc.std() + 0.02
 
 
+def test_fused_decode_layer_matches_separate_kernels(dirs):
+    """Decode-sized steps run five kernels per layer (norms folded into the QKV and gate/up GEMMs, rotary embedding and cache
+    append in the QKV epilogue, residual adds in the o_proj / down_proj epilogues); the logits must agree with the path of
+    separate norm / rotary kernels on the same weights, and both with the fp32 CPU model."""
+    model = og.Model(dirs[0])
+    assert model.decoder.norms_folded, "bf16 CUDA llama models fold their input norms at load"
+    cpu = og.Model(dirs[1])
+    rng = np.random.RandomState(11)
+    prompt = rng.randint(0, 32000, size=(2, 40)).astype(np.int32)
+    out = {}
+    for name, m, fuse in (("fused", model, True), ("separate", model, False), ("cpu", cpu, False)):
+        m.decoder.fuse_steps = fuse
+        p = og.GeneratorParams(m)
+        p.set_search_options(max_length=64, batch_size=2)
+        g = og.Generator(m, p)
+        g.append_tokens(prompt)
+        rows = [g.get_logits()[:, 0, :].copy()]
+        for _ in range(4):
+            g.generate_next_token()
+            rows.append(g.get_logits()[:, 0, :].copy())
+        out[name] = (np.stack(rows), np.stack([g.get_sequence(i) for i in range(2)]))
+    model.decoder.fuse_steps = True
+    ops.check_kernel_status()
+    spread = out["cpu"][0][0].std()
+    assert np.abs(out["fused"][0][0] - out["cpu"][0][0]).max() < 0.08 * spread + 0.02
+    assert np.abs(out["fused"][0][0] - out["separate"][0][0]).max() < 0.05 * spread + 0.01
+    if out["fused"][1].tolist() == out["separate"][1].tolist():      # same greedy tokens: the later steps are comparable too
+        assert np.abs(out["fused"][0] - out["separate"][0]).max() < 0.05 * spread + 0.01
+
+
 def test_engine_isolated_equals_batched_on_gpu(dirs):
     model = og.Model(dirs[0])
+    # one set of kernels for every step size: the five-kernel layer of decode-sized steps rounds differently from the
+    # separate norm / rotary kernels of larger steps, and this test is about packing and scheduling, not rounding
+    model.decoder.fuse_steps = False
     rng = np.random.RandomState(7)
     prompts = [rng.randint(0, 32000, size=(n,)).astype(np.int32) for n in (33, 5, 70, 18, 129)]
 

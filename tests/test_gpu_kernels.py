@@ -172,6 +172,65 @@ def test_gemm_strided_activation():
     _close(ops.linear(x, w), ref.linear(x.cpu(), w.cpu()), rtol=2e-2, atol=0.05)
 
 
+# ------------------------------------------------------------------------------------------- decode-step fusions
+@pytest.mark.parametrize("T,N,K,splits", [(1, 512, 256, 0), (5, 6144, 4096, 0), (64, 6144, 4096, 0), (64, 768, 4096, 0), (100, 1024, 512, 1),
+                                           (64, 4096, 1792, 4), (33, 1000, 4100 // 8 * 8, 0), (300, 1024, 1024, 0)])
+def test_gemm_with_folded_rms_norm(T, N, K, splits):
+    """ops.linear(x, W * g, norm_eps=eps) against the fp32 definition linear(rmsnorm(x, g), W): the kernel sums the squares of
+    every row from the activation tiles in shared memory (over the split-K cluster) and scales in the epilogue; steps beyond
+    the decode tile sizes normalise with a unit-weight norm kernel first."""
+    eps = 1e-5
+    x, w, g = _rand(T, K, std=1.5, seed=201), _rand(N, K, std=0.03, seed=202), (1.0 + _rand(K, std=0.2, seed=203).float()).to(torch.bfloat16)
+    b, r = _rand(N, seed=204), _rand(T, N, seed=205)
+    wf = (w.float() * g.float()[None, :]).to(torch.bfloat16)
+    xn = ref.norm(x.cpu(), g.cpu(), eps)[0]
+    tol = dict(rtol=3e-2, atol=3e-2 * math.sqrt(K) * 0.03 + 0.03)
+    _close(ops.linear(x, wf, norm_eps=eps, splits=splits), ref.linear(xn, w.cpu()), **tol)
+    _close(ops.linear(x, wf, b, r, norm_eps=eps, splits=splits), ref.linear(xn, w.cpu(), b.cpu(), r.cpu()), **tol)
+    y32 = ops.linear(x, wf, norm_eps=eps, out_fp32=True, splits=splits)
+    _close(y32, ref.linear(xn, w.cpu(), out_fp32=True), **tol)
+    # against the exact statement of what the kernel computes (folded weight, fp32 row scale): tight
+    exact = (x.float().cpu() @ wf.float().cpu().t()) * torch.rsqrt((x.float().cpu() ** 2).mean(-1, keepdim=True) + eps)
+    if T <= ops.FUSED_MAX_TOKENS:     # larger steps round the normalised rows to bf16 first
+        _close(y32, exact, rtol=2e-3, atol=2e-3 * math.sqrt(K) * 0.03 + 1e-3)
+    if N % 128 == 0:
+        wi, bi = ops.interleave_gate_up(wf), ops.interleave_gate_up(b)
+        _close(ops.gate_up_act(x, wi, bi, interleaved=True, norm_eps=eps, splits=splits), ref.gate_up_act(xn, w.cpu(), b.cpu()), rtol=4e-2, atol=0.08)
+    ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,rot,K,bias,eps", [(64, 32, 8, 128, 128, 4096, False, 1e-5), (7, 4, 1, 128, 128, 4096, True, 0.0),
+                                                        (33, 8, 2, 64, 64, 512, True, 1e-5), (1, 16, 2, 128, 64, 1024, False, 1e-6),
+                                                        (128, 6, 2, 32, 32, 256, False, 1e-5), (16, 4, 4, 128, 0, 256, True, 0.0)])
+def test_qkv_projection_with_fused_rope_and_cache_append(T, Hq, Hkv, D, rot, K, bias, eps):
+    """One kernel (GEMM + rotary embedding + KV-cache append, optionally + folded norm) against the fp32 restatement of the
+    three separate steps: rotated queries, and the cache rows at every token's slot (negative slots store nothing)."""
+    N = (Hq + 2 * Hkv) * D
+    x, w = _rand(T, K, std=1.0, seed=211), _rand(N, K, std=0.04, seed=212)
+    b = _rand(N, std=0.5, seed=213) if bias else None
+    max_pos = 300
+    pos = torch.randint(0, max_pos, (T,), generator=torch.Generator().manual_seed(1), dtype=torch.int32)
+    slots = torch.randperm(T + 9, generator=torch.Generator().manual_seed(2))[:T].to(torch.int32)
+    if T > 3:
+        slots[2] = -1
+    half = max(rot // 2, 1)
+    ang = torch.arange(max_pos)[:, None].float() * (1.0 / (10000 ** (torch.arange(half).float() / half)))[None, :]
+    cos, sin = (torch.cos(ang), torch.sin(ang)) if rot else (None, None)
+    kc_ref, vc_ref = torch.zeros(T + 9, Hkv, D), torch.zeros(T + 9, Hkv, D)
+    xn = ref.rms_scale(x.cpu(), eps) if eps > 0 else x.cpu()
+    qkv_ref = ref.linear(xn, w.cpu(), b.cpu() if bias else None, out_fp32=True)
+    ref.rope_kv_append(qkv_ref, pos, slots, cos, sin, kc_ref, vc_ref, Hq, Hkv, D, rot)
+    kc, vc = torch.zeros(T + 9, Hkv, D, dtype=torch.bfloat16, device=DEV), torch.zeros(T + 9, Hkv, D, dtype=torch.bfloat16, device=DEV)
+    q = ops.qkv_rope_append(x, w, b, pos.to(DEV), slots.to(DEV), cos.to(DEV) if rot else None, sin.to(DEV) if rot else None, kc, vc,
+                            Hq, Hkv, D, rot, norm_eps=eps)
+    assert q.shape == (T, Hq * D), "the fused kernel writes the query columns only"
+    tol = dict(rtol=3e-2, atol=3e-2 * math.sqrt(K) * 0.04 + 0.03)
+    _close(q, qkv_ref[:, :Hq * D], **tol)
+    _close(kc, kc_ref, **tol)
+    _close(vc, vc_ref, **tol)
+    ops.check_kernel_status()
+
+
 # ------------------------------------------------------------------------------------------- norm / rope / misc
 @pytest.mark.parametrize("H", [256, 3072, 4096, 8192])
 @pytest.mark.parametrize("with_res", [False, True])
