@@ -134,10 +134,27 @@ def ours(args):
         torch.cuda.synchronize()
 
     # ---- checkpoint (synthetic weights: the ONNX file only describes the tensors) + model + engine
-    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{os.getuid()}")
+    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{os.getuid()}" + ("_spec" if args.spec else ""))
     if rank == 0 and not os.path.exists(os.path.join(ckpt, "genai_config.json")):
         create_model(MODEL, ckpt, "bf16", "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
                                                   "max_batch_size": N_REQ, "context_length": 4096})
+        if args.spec:
+            # speculative decoding: a Llama-3.2-1B-shaped draft next to the target (its own ONNX file, `model.draft` in the config)
+            tmp = ckpt + "_draft"
+            create_model(args.draft_model, tmp, "bf16", "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
+                                                                  "max_batch_size": N_REQ, "context_length": 4096, "filename": "draft.onnx",
+                                                                  "seed": 1})
+            for fn in os.listdir(tmp):
+                if fn.startswith("draft.onnx"):
+                    os.replace(os.path.join(tmp, fn), os.path.join(ckpt, fn))
+            with open(os.path.join(tmp, "genai_config.json")) as f:
+                draft_dec = json.load(f)["model"]["decoder"]
+            with open(os.path.join(ckpt, "genai_config.json")) as f:
+                full = json.load(f)
+            full["model"]["draft"] = draft_dec
+            full["speculative"] = {"max_draft_tokens": args.draft_tokens}
+            with open(os.path.join(ckpt, "genai_config.json"), "w") as f:
+                json.dump(full, f, indent=1)
     barrier()
     cfg = og.Config(ckpt)
     blocks = N_REQ * ((PROMPT_HI + NEW_TOKENS + BLOCK - 1) // BLOCK + 1)
@@ -150,12 +167,23 @@ def ours(args):
     load_s = time.perf_counter() - t0
     engine = og.Engine(model)
 
+    schema = None
+    if args.json_schema:
+        # constrained decoding: every request generates under a JSON schema (llguidance masks on the host, applied on the device)
+        schema = json.dumps({"type": "object", "properties": {"name": {"type": "string"}, "tags": {"type": "array", "items": {"type": "string"}},
+                                                               "score": {"type": "number"}, "notes": {"type": "string"}},
+                             "required": ["name", "tags", "score", "notes"]})
+        if not os.path.exists(os.path.join(ckpt, "tokenizer.json")):
+            raise SystemExit("--json-schema needs a tokenizer.json in the checkpoint directory (the grammar walks token bytes)")
+
     rng = np.random.RandomState(2)
     lens = rng.randint(PROMPT_LO, PROMPT_HI + 1, size=N_REQ)
     reqs = []
     for i, n in enumerate(lens):
         p = og.GeneratorParams(model)
         p.set_search_options(max_length=int(n) + NEW_TOKENS + 1, random_seed=2 + i, **SAMPLING)
+        if schema:
+            p.set_guidance("json_schema", schema)
         r = og.Request(p)
         r.add_tokens(rng.randint(0, model.arch.vocab_size, size=int(n)).astype(np.int32))
         reqs.append(r)
@@ -212,9 +240,11 @@ def ours(args):
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_e0 = time.perf_counter()
+    launches0 = _lib.LAUNCH_COUNT
     ev0.record()
-    model_steps(K)
+    produced = model_steps(K)
     ev1.record()
+    e2e_launches = _lib.LAUNCH_COUNT - launches0
     barrier()
     e2e_wall = time.perf_counter() - t_e0
     e2e_ms = ev0.elapsed_time(ev1)
@@ -223,6 +253,40 @@ def ours(args):
     host = {"launch_ms_per_step": round((hs1["launch_s"] - hs0["launch_s"]) / n_l * 1e3, 4),
             "wait_ms_per_step": round((hs1["wait_s"] - hs0["wait_s"]) / n_l * 1e3, 4)}
     step_wall = e2e_wall / K
+
+    spec = getattr(engine, "spec", None)
+    if spec is not None:
+        # Speculative decoding: a step verifies several proposed tokens per request, there is no fixed decode graph to replay;
+        # the device-timed figure is the CUDA-event time of the same engine steps (draft proposals + one packed verify forward).
+        clocks = sampler.stop()
+        ops.check_kernel_status()
+
+        def mx(x):
+            if world == 1:
+                return x
+            t = torch.tensor([x], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        e2e_ms, e2e_wall = mx(e2e_ms), mx(e2e_wall)
+        if rank == 0:
+            st = spec.stats
+            print(json.dumps({
+                "metric": METRIC, "value": round(produced / (e2e_ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": round(e2e_ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic (random token ids, random-init N(0,0.02) weights generated on device)",
+                "config": {"model": cfg_w["label"] + f" + speculative decoding, draft {args.draft_model}, {args.draft_tokens} draft tokens per step",
+                           "global_batch": N_REQ, "seq_len": f"prompts U[{PROMPT_LO},{PROMPT_HI}] + {NEW_TOKENS} new tokens",
+                           "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": cfg_w["sampling_label"],
+                           "l2": "inputs larger than L2, no flush", "tp_backend": getattr(tp, "backend", None)},
+                "e2e": {"value": round(produced / e2e_wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": st_bytes(engine), "d2h_bytes_per_step": 4 * N_REQ * (args.draft_tokens + 1),
+                        "ms_per_step": round(e2e_wall / K * 1e3, 4)},
+                "speculative": {"acceptance_rate": round(spec.acceptance_rate, 4), "tokens_per_request_step": round(st["committed"] / max(1, st["rounds"]), 3),
+                                "rounds": st["rounds"], "note": "random-init target and draft share no distribution: the acceptance rate of random weights is a floor, not a forecast"},
+                "gpu_launches": int(e2e_launches), "clocks": clocks, "ttft_ms_p50": round(ttft[len(ttft) // 2], 2),
+                "tpot_ms_p50": round(e2e_wall / max(1, produced) * N_REQ * 1e3, 4), "prefill_tokens_per_s": round(prefill_tok_s, 1)}))
+        if world > 1:
+            torch.cuda.synchronize(); dist.barrier(); sys.stdout.flush(); sys.stderr.flush(); os._exit(0)
+        return 0
 
     # ---- device-only: the kernels of K consecutive decode steps, inputs advanced on the device (the sampled ids become the
     # next input ids, positions / cache slots / KV lengths move on by one: exactly what the engine enqueues ahead of the host),
@@ -318,6 +382,10 @@ def ours(args):
     return 0
 
 
+def st_bytes(engine):
+    return engine.staging.h2d_bytes
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -327,6 +395,10 @@ def main():
     ap.add_argument("--tp_backend", default="", choices=["", "fused", "nccl"],
                     help="tensor-parallel reductions: fused (GEMM + all-reduce in one kernel over peer memory; the default) or nccl "
                          "(GEMM, then ncclAllReduce: the baseline this framework is measured against, NCCL's own NVLS left on)")
+    ap.add_argument("--spec", action="store_true", help="speculative decoding inside the engine with a draft model (config llama70b: Llama-3.2-1B shape)")
+    ap.add_argument("--draft_model", default="llama-3.2-1b")
+    ap.add_argument("--draft_tokens", type=int, default=4)
+    ap.add_argument("--json-schema", dest="json_schema", action="store_true", help="every request decodes under a JSON schema (needs tokenizer.json)")
     ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS), help="workload; the default is the headline configuration")
     args = ap.parse_args()
     if args.impl == "reference":

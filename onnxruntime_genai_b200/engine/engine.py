@@ -321,6 +321,48 @@ class ModelExecutor:
             return st.tokens_host[:B].numpy()
         return toks.numpy()
 
+    def execute_speculative(self, plan, spec, edits=None, masks=None):
+        """A step whose decoding entries may carry proposed tokens: one packed forward with logits for every row that needs a
+        prediction (all 1 + K rows of an entry with K drafts, the last row of any other sampling entry), verification, and
+        the per-entry (accepted, next token) pair for EngineCore.commit_speculative.  Synchronous."""
+        st = self.staging
+        B, T = len(plan.entries), plan.token_count
+        rows, row_of = [], []
+        any_plain = False
+        for e in plan.entries:
+            row_of.append(len(rows))
+            if not e.samples:
+                any_plain = True
+                continue
+            k = e.request.draft_count if not e.is_prefill else 0
+            any_plain = any_plain or k == 0
+            rows.extend(range(e.packed_offset + e.num_tokens - 1 - k, e.packed_offset + e.num_tokens))
+        with torch.no_grad():
+            st.upload()
+            s = self._step_inputs(T, B, st.table_cols, plan.max_query_len, plan.max_kv_len)
+            dev = self.model.device
+            s.logits_rows = torch.tensor(rows or [0], dtype=torch.int32, device=dev)
+            nd = 0
+            for e in plan.entries:
+                if e.num_tokens != 1:
+                    break
+                nd += 1
+            s.num_decode = nd
+            logits = self.decoder.forward(s, self.kv)
+            if any_plain:
+                spec.mirror_prefill(s)         # the draft model's cache follows prompt chunks and plain decode tokens
+            if edits or masks is not None:
+                ro = torch.tensor(row_of, dtype=torch.int64, device=dev)
+                for (r_, t_, o_, v_) in edits or ():
+                    ops.logits_edit(logits, ro[r_.long()].to(torch.int32), t_, o_, v_)
+                if masks is not None:
+                    words, mrows = masks
+                    per_row = torch.full((logits.shape[0],), -1, dtype=torch.int32, device=dev)
+                    sel = torch.nonzero(mrows >= 0).flatten()
+                    per_row[ro[sel]] = mrows[sel]
+                    ops.logits_bitmask(logits, words, per_row)
+            return spec.verify(plan, logits, row_of)
+
     def _sample_async(self, logits, B: int):
         st = self.staging
         toks = ops.sample(logits, st.view("top_k", B), st.view("top_p", B, torch.float32), st.view("temperature", B, torch.float32),
@@ -335,10 +377,18 @@ class ModelExecutor:
     def execute_async(self, plan, edits=None, masks=None):
         """Enqueues the step (input copy, model, sampler, copy of the ids to pinned memory) and returns a handle for
         `collect`; the host does not wait."""
-        B = len(plan.entries)
+        return self.finish_async(plan, self.begin_async(plan), edits, masks)
+
+    def begin_async(self, plan) -> torch.Tensor:
+        """First half of execute_async: enqueues the input copy and the model.  The caller may compute logits edits and grammar
+        masks on the host while the device runs it, then call finish_async."""
         self.last_key = None
         with torch.no_grad():
-            logits = self.forward(plan)
+            return self.forward(plan)
+
+    def finish_async(self, plan, logits, edits=None, masks=None):
+        B = len(plan.entries)
+        with torch.no_grad():
             for e in edits or ():
                 ops.logits_edit(logits, *e)
             if masks is not None:
@@ -406,7 +456,19 @@ class Engine:
                           os.environ.get("OGB_ENGINE_LOOKAHEAD", "1") != "0" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
         if lookahead is not None:
             self.lookahead = bool(lookahead) and not windowed
-        o.lookahead = 1 if self.lookahead else 0
+        # Speculative decoding (a draft model in the checkpoint, or speculative.ngram_size > 0 in genai_config.json): decoding
+        # requests carry proposed tokens that one packed forward of the target verifies for the whole batch (engine/speculative.py).
+        # The block look-ahead then reserves room for the proposals instead of serving the enqueue-ahead of plain decode steps.
+        spec_cfg = dict(getattr(cfg, "speculative", None) or {})
+        want_spec = (executor is None and not windowed and not static and
+                     (getattr(model, "draft", None) is not None or int(spec_cfg.get("ngram_size", 0) or 0) > 0) and
+                     os.environ.get("OGB_ENGINE_SPECULATIVE", "1") != "0")
+        if want_spec:
+            self.lookahead = False
+            o.lookahead = max(1, min(16, int(spec_cfg.get("max_draft_tokens", 4)))) + 1
+            o.lookahead_execution = False
+        else:
+            o.lookahead = 1 if self.lookahead else 0
         self.core = native.EngineCore(o)
         self.options = o
         n_win = self.core.ring_blocks_per_request * o.max_batch_size if windowed else 0
@@ -416,6 +478,10 @@ class Engine:
         cols = (max_ctx + self.block_size - 1) // self.block_size
         self.staging = _Staging(o.max_scheduled_tokens + o.max_batch_size, o.max_batch_size, cols, model.device, windowed)
         self.executor = executor or ModelExecutor(model, self.core, self.staging, self.kv, use_graphs=True)
+        self.spec = None
+        if want_spec:
+            from .speculative import EngineSpeculator
+            self.spec = EngineSpeculator(self, spec_cfg)
         self._by_native: Dict[int, Request] = {}
         self._guidance: Dict[int, Any] = {}
         self.last_outcome = StepOutcome.NoWork
@@ -470,6 +536,8 @@ class Engine:
         self._guidance.pop(request._native.id, None)
         self._with_processors.discard(request._native.id)
         self._need_first.discard(request._native.id)
+        if self.spec is not None:
+            self.spec.forget(request._native.id)
 
     def has_pending_requests(self) -> bool:
         return self.core.has_pending_requests()
@@ -536,6 +604,11 @@ class Engine:
 
     def _launch_inner(self):
         with _Trace("engine", "launch"):
+            if self.spec is not None:
+                try:
+                    self.spec.propose()
+                except Exception as e:      # proposing touches no engine state: a failure here is a failed step without a plan
+                    raise EngineStepError(StepOutcome.FatalExecutionFailure, f"speculative proposal failed: {e}") from e
             plan = self.core.plan()
             self.last_outcome = plan.outcome
             if plan.unserviceable:
@@ -559,13 +632,26 @@ class Engine:
                     self._inflight = (plan, handle, None)
                     self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
                     self.executor.refresh_inputs(plan)
-                else:
+                elif self.spec is not None:
                     self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
                     edits, masks = self._logits_processors(plan)
-                    if self.run_ahead:
+                    self._inflight = (plan, None, self.executor.execute_speculative(plan, self.spec, edits, masks))
+                    return
+                else:
+                    self.core.pack(st.addr, st.max_tokens, st.max_batch, st.table_cols)
+                    if self.run_ahead and hasattr(self.executor, "begin_async"):
+                        # the model is enqueued first: penalties and grammar masks (host work: llguidance walks the grammar for
+                        # every constrained request) are computed while the device runs the forward pass
+                        logits = self.executor.begin_async(plan)
+                        edits, masks = self._logits_processors(plan)
+                        handle = self.executor.finish_async(plan, logits, edits, masks)
+                        self._inflight = (plan, handle, None)
+                    elif self.run_ahead:
+                        edits, masks = self._logits_processors(plan)
                         handle = self.executor.execute_async(plan, edits, masks)
                         self._inflight = (plan, handle, None)
                     else:
+                        edits, masks = self._logits_processors(plan)
                         self._inflight = (plan, None, self.executor.execute(plan, edits, masks))
                 if self.lookahead and plain and plan.lookahead_ok:
                     nxt = self.executor.enqueue_next(plan, handle)
@@ -579,6 +665,9 @@ class Engine:
         with _Trace("engine", "finish"):
             plan, handle, toks = self._inflight
             self._inflight = None
+            accepted = None
+            if isinstance(toks, tuple):       # a speculative step: (accepted drafts per entry, token after them)
+                accepted, toks = toks
             if handle is not None:
                 t0 = time.perf_counter()
                 try:
@@ -603,7 +692,11 @@ class Engine:
                     if gp is not None:
                         gp.commit_tokens(np.asarray([toks[i]], dtype=np.int32))
             self.t_last_step = now
-            self.last_outcome = self.core.commit(np.ascontiguousarray(toks, dtype=np.int32))
+            if accepted is not None:
+                self.last_outcome = self.core.commit_speculative(np.ascontiguousarray(accepted, dtype=np.int32),
+                                                                 np.ascontiguousarray(toks, dtype=np.int32))
+            else:
+                self.last_outcome = self.core.commit(np.ascontiguousarray(toks, dtype=np.int32))
             self.step_count += 1
 
     def _logits_processors(self, plan):

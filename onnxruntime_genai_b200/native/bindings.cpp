@@ -339,6 +339,8 @@ PYBIND11_MODULE(_og_native, m) {
       .def("has_unseen_tokens", &Request::HasUnseen)
       .def("get_unseen_token", &Request::PopUnseen)
       .def("is_turn_complete", &Request::TurnComplete)
+      .def("set_draft", [](Request& r, IntArray ids) { return r.SetDraft(ids.data(), size_t(ids.size())); })
+      .def_property_readonly("draft_count", &Request::DraftCount)
       .def("blocks", [](const Request& r) { return r.Blocks(); })
       .def("window_blocks", [](const Request& r) { return r.WindowBlocks(); });
 
@@ -363,6 +365,7 @@ PYBIND11_MODULE(_og_native, m) {
       .def_readwrite("static_batching", &EngineOptions::static_batching)
       .def_readwrite("max_scheduled_tokens", &EngineOptions::max_scheduled_tokens)
       .def_readwrite("window_size", &EngineOptions::window_size).def_readwrite("lookahead", &EngineOptions::lookahead)
+      .def_readwrite("lookahead_execution", &EngineOptions::lookahead_execution)
       .def_readwrite("num_window_blocks", &EngineOptions::num_window_blocks)
       .def_readwrite("vocab_size", &EngineOptions::vocab_size).def_readwrite("pad_token_id", &EngineOptions::pad_token_id)
       .def_readwrite("eos_ids", &EngineOptions::eos_ids);
@@ -395,6 +398,10 @@ PYBIND11_MODULE(_og_native, m) {
         e.Pack(b);
       })
       .def("commit", [](EngineCore& e, IntArray toks) { return e.Commit(toks.data(), size_t(toks.size())); })
+      .def("commit_speculative", [](EngineCore& e, IntArray accepted, IntArray toks) {
+        if (accepted.size() != toks.size()) throw std::invalid_argument("commit_speculative: arrays of different lengths");
+        return e.CommitSpeculative(accepted.data(), toks.data(), size_t(toks.size()));
+      })
       .def("abort", &EngineCore::Abort, py::arg("kind"), py::arg("what") = "")
       .def_property_readonly("transaction_open", &EngineCore::TransactionOpen)
       .def("next_ready", &EngineCore::NextReady)

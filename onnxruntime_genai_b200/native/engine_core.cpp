@@ -114,6 +114,15 @@ void Request::ContinueWith(const int32_t* ids, size_t n) {
   status_ = RequestStatus::kAssigned;
 }
 
+int Request::SetDraft(const int32_t* ids, size_t n) {
+  if ((status_ != RequestStatus::kActive && status_ != RequestStatus::kAssigned) || prefill_ || draft_ != 0 || Pending() != 1) return 0;
+  const int room = opt_.max_length - int(tokens_.size()) - 1;    // the token after the drafts needs a place too
+  const int take = std::max(0, std::min(int(n), room));
+  tokens_.insert(tokens_.end(), ids, ids + take);
+  draft_ = take;
+  return take;
+}
+
 int32_t Request::PopUnseen() {
   if (unseen_.empty()) throw std::runtime_error("get_unseen_token: no unseen tokens");
   int32_t t = unseen_.front();
@@ -271,8 +280,18 @@ const StepPlan& EngineCore::Plan() {
     return plan_;
   }
 
-  // Token budget: one token each, then prefills share what is left in plan order.
+  // Token budget: one token each, then staged drafts, then prefills share what is left in plan order.
   int budget = opt_.max_scheduled_tokens - int(plan_.entries.size());
+  for (auto& e : plan_.entries) {
+    if (e.is_prefill || e.request->draft_ == 0) continue;
+    if (e.request->draft_ > budget) {           // no room to verify the proposal this step: drop it
+      e.request->tokens_.resize(e.request->tokens_.size() - size_t(e.request->draft_));
+      e.request->draft_ = 0;
+      continue;
+    }
+    e.num_tokens += e.request->draft_;
+    budget -= e.request->draft_;
+  }
   for (auto& e : plan_.entries) {
     if (!e.is_prefill) continue;
     int cap = e.request->Pending();
@@ -284,7 +303,7 @@ const StepPlan& EngineCore::Plan() {
 
   int off = 0;
   plan_.graph_eligible = true;
-  plan_.lookahead_ok = opt_.lookahead > 0 && !wpool_;
+  plan_.lookahead_ok = opt_.lookahead > 0 && opt_.lookahead_execution && !wpool_;
   uint64_t sig = 1469598103934665603ull, nsig = 1469598103934665603ull;
   auto mix = [](uint64_t h, uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); return h * 1099511628211ull; };
   for (size_t i = 0; i < plan_.entries.size(); ++i) {
@@ -362,7 +381,7 @@ void EngineCore::Pack(const PackBuffers& buf) const {
     buf.top_p[i] = a.top_p;
     buf.temperature[i] = a.temperature;
     buf.seeds[i] = r.seed_;
-    buf.sample_pos[i] = int(r.tokens_.size());
+    buf.sample_pos[i] = int(r.tokens_.size()) - r.draft_;      // position of the first token this step decides
   }
 }
 
@@ -402,6 +421,56 @@ StepOutcome EngineCore::Commit(const int32_t* tokens, size_t n) {
   ++metrics_.steps_committed;
   plan_.outcome = StepOutcome::kCommitted;
   return plan_.outcome;
+}
+
+StepOutcome EngineCore::CommitSpeculative(const int32_t* accepted, const int32_t* tokens, size_t n) {
+  if (!open_) throw std::logic_error("CommitSpeculative: no open step");
+  if (n != plan_.entries.size()) throw std::invalid_argument("CommitSpeculative: one entry per planned entry is required");
+  for (size_t i = 0; i < n; ++i) {
+    Request& r = *plan_.entries[i].request;
+    const int staged = plan_.entries[i].num_tokens > 1 && !plan_.entries[i].is_prefill ? r.draft_ : 0;
+    if (accepted[i] < 0 || accepted[i] > staged) throw std::invalid_argument("CommitSpeculative: accepted count out of range");
+  }
+  // Rejected drafts leave the sequence and the number of fed tokens shrinks to what the cache keeps; then every entry is an
+  // ordinary entry that sampled tokens[i], except that the accepted drafts are generated output too.
+  std::vector<char> ended_on_draft(n, 0);
+  for (size_t i = 0; i < n; ++i) {
+    PlanEntry& e = plan_.entries[i];
+    Request& r = *e.request;
+    if (e.is_prefill || r.draft_ == 0 || e.num_tokens == 1) continue;
+    const int staged = r.draft_, keep = accepted[i];
+    const size_t base = r.tokens_.size() - size_t(staged);       // tokens before the drafts (the last one was pending)
+    int surfaced = 0;
+    bool ended = false;
+    for (int j = 0; j < keep && !ended; ++j) {                   // accepted drafts are output; one that ends the sequence stops it
+      const int32_t t = r.tokens_[base + size_t(j)];
+      r.unseen_.push_back(t);
+      ++metrics_.tokens_generated;
+      ++surfaced;
+      ended = std::find(r.eos_ids_.begin(), r.eos_ids_.end(), t) != r.eos_ids_.end();
+    }
+    r.tokens_.resize(base + size_t(surfaced));
+    r.draft_ = 0;
+    e.num_tokens = 1 + surfaced;                                  // slots the cache keeps: the pending token and the kept drafts
+    if (ended) {
+      // the turn ends on an accepted draft: nothing is sampled after it; the token itself is fed when the turn continues
+      e.num_tokens = surfaced;
+      e.samples = false;
+      ended_on_draft[i] = 1;
+    }
+  }
+  // the ordinary commit appends tokens[i] where the entry samples; entries that ended on a draft complete their turn here
+  const StepOutcome out = Commit(tokens, n);
+  for (size_t i = 0; i < n; ++i) {
+    if (!ended_on_draft[i]) continue;
+    Request& r = *plan_.entries[i].request;
+    if (r.status_ != RequestStatus::kTurnComplete) {
+      r.status_ = RequestStatus::kTurnComplete;
+      ++metrics_.requests_completed;
+      if (std::find(ready_.begin(), ready_.end(), plan_.entries[i].request) == ready_.end()) ready_.push_back(plan_.entries[i].request);
+    }
+  }
+  return out;
 }
 
 StepOutcome EngineCore::Abort(FailureKind kind, const std::string&) {

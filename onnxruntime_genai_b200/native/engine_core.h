@@ -93,6 +93,12 @@ class Request {
 
   void AddTokens(const int32_t* ids, size_t n);      // only while Unassigned
   void ContinueWith(const int32_t* ids, size_t n);   // only while TurnComplete
+  // Speculative decoding: stages up to n proposed continuation tokens behind the pending token of a decoding request.  The
+  // next step then feeds [pending token, drafts...] (1 + n rows whose logits verify the proposal) and is closed with
+  // EngineCore::CommitSpeculative.  Returns how many were staged (clipped so that the accepted tokens plus the correction or
+  // bonus token stay below max_length; 0 for a request that is not decoding with exactly one pending token).
+  int SetDraft(const int32_t* ids, size_t n);
+  int DraftCount() const { return draft_; }
   const std::vector<int>& Blocks() const { return blocks_; }
   const std::vector<int>& WindowBlocks() const { return window_blocks_; }
 
@@ -117,6 +123,7 @@ class Request {
   std::vector<int> blocks_;         // committed blocks of the full-attention layers
   std::vector<int> window_blocks_;  // ring blocks of the sliding-window layers
   uint64_t seed_;
+  int draft_{0};                    // trailing tokens of tokens_ that are an unverified proposal
   bool resident_{false};
   std::optional<Saved> saved_;
 };
@@ -167,6 +174,7 @@ struct EngineOptions {
   bool static_batching{false};  // fixed batches: up to 4 waiting requests (then 2, then 1) are admitted together with all the
                                 // blocks their max_length needs, and only once the batch before them has finished
   int lookahead{0};           // decode entries also reserve the block of their next `lookahead` positions
+  bool lookahead_execution{true};  // false: the reservation above serves speculative drafts; plans never report lookahead_ok
   int window_size{0};         // > 0 enables the sliding-window ring pool
   int num_window_blocks{0};   // blocks in the windowed pool
   int vocab_size{0};
@@ -216,6 +224,11 @@ class EngineCore {
   void Pack(const PackBuffers& buf) const;
   // P5 + P6: tokens[i] is the sampled token of entry i (ignored where !entry.samples).
   StepOutcome Commit(const int32_t* tokens, size_t n);
+  // The same for a step with staged drafts: accepted[i] of entry i's drafts were verified (0 for entries without drafts) and
+  // tokens[i] is the token that follows them (the target's correction at the first rejection, its bonus token when every draft
+  // was accepted, the ordinary sampled token without drafts).  The cache keeps the accepted drafts' slots; rejected drafts
+  // leave the sequence.  A draft that is an end-of-sequence token ends the turn there.
+  StepOutcome CommitSpeculative(const int32_t* accepted, const int32_t* tokens, size_t n);
   StepOutcome Abort(FailureKind kind, const std::string& what);
   bool TransactionOpen() const { return open_; }
 

@@ -93,6 +93,51 @@ def test_draft_model_speculation_on_gpu(spec_dir):
     ops.check_kernel_status()
 
 
+def test_engine_speculation_on_gpu(spec_dir, tmp_path):
+    """Speculative decoding inside the continuous-batching engine on the GPU: several requests, a draft equal to the target.
+    One packed verify forward per step serves the whole batch; most proposals are accepted (bf16 launches of different shapes
+    may flip a near-tie) and every emitted token is a greedy choice of the plain model."""
+    with_draft, plain = spec_dir
+    cfg = json.load(open(os.path.join(with_draft, "genai_config.json")))
+    cfg["engine"] = {"dynamic_batching": {"block_size": 16, "num_blocks": 256, "max_batch_size": 8, "max_scheduled_tokens": 256}}
+    cfg["speculative"] = {"max_draft_tokens": 4}
+    d = str(tmp_path)
+    for f in os.listdir(with_draft):
+        if f != "genai_config.json":
+            os.symlink(os.path.join(with_draft, f), os.path.join(d, f))
+    json.dump(cfg, open(os.path.join(d, "genai_config.json"), "w"))
+    model = og.Model(d)
+    engine = og.Engine(model)
+    assert engine.spec is not None
+    prompts = [PROMPT, PROMPT[3:] + [7, 7, 7], [100, 200, 300, 400, 500, 600], list(range(30, 75))]
+    reqs, outs = [], {}
+    for pr in prompts:
+        gp = og.GeneratorParams(model)
+        gp.set_search_options(max_length=len(pr) + 24)
+        r = og.Request(gp)
+        r.add_tokens(np.asarray(pr, dtype=np.int32))
+        engine.add_request(r)
+        reqs.append(r)
+        outs[id(r)] = []
+    while engine.has_pending_requests():
+        r = engine.step()
+        if r is None:
+            continue
+        while r.has_unseen_tokens():
+            outs[id(r)].append(r.get_unseen_token())
+        if r.is_turn_complete():
+            engine.remove_request(r)
+    ops.check_kernel_status()
+    engine.core.check_invariants()
+    st = engine.spec.stats
+    assert st["rounds"] > 0 and st["accepted"] >= 0.8 * st["proposed"], st
+    assert engine.step_count < sum(len(o) for o in outs.values()) / 2, "several tokens per request and step"
+    ref_model = og.Model(plain)
+    for pr, r in zip(prompts, reqs):
+        assert len(outs[id(r)]) == 24 or 1023 in outs[id(r)]
+        assert_near_greedy(ref_model, pr, pr + outs[id(r)])
+
+
 def test_ngram_speculation_on_gpu(spec_dir):
     model = og.Model(spec_dir[1])
     p = og.GeneratorParams(model)

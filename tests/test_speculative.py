@@ -173,3 +173,86 @@ def test_adaptive_k_and_cooldown():
         c.record(4, 0)
     assert c.should_skip_round() and not c.should_skip_round() and c.skips == 1
     assert not native.ZeroAcceptCooldown(False).should_skip_round()
+
+
+# ------------------------------------------------------------------------------------------------ inside the engine
+def _paged(spec_dir, tmp_path, extra):
+    """The target checkpoint with a paged-engine section and `extra` merged into its genai_config.json."""
+    cfg = json.load(open(os.path.join(spec_dir, "genai_config.json")))
+    cfg["engine"] = {"dynamic_batching": {"block_size": 4, "num_blocks": 256, "max_batch_size": 8, "max_scheduled_tokens": 64}}
+    for k, v in extra.items():
+        if k == "draft":
+            dec = copy.deepcopy(cfg["model"]["decoder"])
+            dec["filename"], dec["num_hidden_layers"] = v
+            cfg["model"]["draft"] = dec
+        else:
+            cfg[k] = v
+    out = str(tmp_path)
+    os.makedirs(out, exist_ok=True)
+    for f in os.listdir(spec_dir):
+        if f != "genai_config.json" and not os.path.exists(os.path.join(out, f)):
+            os.symlink(os.path.join(spec_dir, f), os.path.join(out, f))
+    json.dump(cfg, open(os.path.join(out, "genai_config.json"), "w"))
+    return out
+
+
+def _engine_run(model, prompts, new_tokens, **search):
+    engine = og.Engine(model)
+    reqs, outs = [], {}
+    for i, p in enumerate(prompts):
+        gp = og.GeneratorParams(model)
+        gp.set_search_options(max_length=len(p) + new_tokens, random_seed=7 + i, **search)
+        r = og.Request(gp)
+        r.add_tokens(np.asarray(p, dtype=np.int32))
+        engine.add_request(r)
+        reqs.append(r)
+        outs[id(r)] = []
+    guard = 0
+    while engine.has_pending_requests():
+        guard += 1
+        assert guard < 4000
+        r = engine.step()
+        engine.core.check_invariants()
+        if r is None:
+            continue
+        while r.has_unseen_tokens():
+            outs[id(r)].append(r.get_unseen_token())
+        if r.is_turn_complete():
+            engine.remove_request(r)
+    assert engine.core.free_blocks == engine.options.num_blocks, "every block returns to the pool"
+    return [outs[id(r)] for r in reqs], engine
+
+
+ENGINE_PROMPTS = [PROMPT, [9, 61, 5, 17, 40, 3, 22, 9, 61, 5], [33, 33, 33, 33, 33, 33, 33], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13],
+                  [40, 3, 22, 9, 61, 5, 17, 40, 3, 22, 9, 61, 5, 17, 40, 3, 22]]
+
+
+def test_engine_self_speculation_equals_plain_greedy(spec_dir, tmp_path):
+    """A draft equal to the target inside the engine: every request of the batch accepts every proposal, and the token streams
+    are those of the plain engine (reference semantics: src/speculative_decoding_strategy.cpp:460-792, batched here)."""
+    plain, _ = _engine_run(og.Model(_paged(spec_dir, tmp_path / "plain", {})), ENGINE_PROMPTS, 24)
+    model = og.Model(_paged(spec_dir, tmp_path / "self", {"draft": ("draft.onnx", 2), "speculative": {"max_draft_tokens": 4}}))
+    spec, engine = _engine_run(model, ENGINE_PROMPTS, 24)
+    assert spec == plain
+    st = engine.spec.stats
+    assert st["rounds"] > 0 and st["accepted"] == st["proposed"], st
+    assert engine.step_count < sum(len(o) for o in plain) / 2, "several tokens per request and step"
+
+
+def test_engine_weak_draft_and_ngram_still_equal_plain_greedy(spec_dir, tmp_path):
+    plain, _ = _engine_run(og.Model(_paged(spec_dir, tmp_path / "plain", {})), ENGINE_PROMPTS, 24)
+    weak = og.Model(_paged(spec_dir, tmp_path / "weak", {"draft": ("weak_draft.onnx", 1), "speculative": {"max_draft_tokens": 3}}))
+    out, engine = _engine_run(weak, ENGINE_PROMPTS, 24)
+    assert out == plain and engine.spec.stats["accepted"] < engine.spec.stats["proposed"]
+    ngram = og.Model(_paged(spec_dir, tmp_path / "ngram", {"speculative": {"ngram_size": 3, "max_draft_tokens": 4}}))
+    out, engine = _engine_run(ngram, ENGINE_PROMPTS, 24)
+    assert out == plain and engine.spec is not None and engine.spec.stats["rounds"] > 0
+
+
+def test_engine_speculation_with_sampling_is_reproducible_and_valid(spec_dir, tmp_path):
+    """Sampled requests verify deterministic proposals by rejection sampling (accept d with probability p(d), else draw from p
+    without d): same seeds give the same streams, every token lies in the top-k set of its step, lengths are respected."""
+    model = og.Model(_paged(spec_dir, tmp_path / "s", {"draft": ("draft.onnx", 2), "speculative": {"max_draft_tokens": 3}}))
+    a, _ = _engine_run(model, ENGINE_PROMPTS[:3], 16, do_sample=True, top_k=5, temperature=0.9)
+    b, _ = _engine_run(model, ENGINE_PROMPTS[:3], 16, do_sample=True, top_k=5, temperature=0.9)
+    assert a == b and all(len(o) == 16 or 96 in o for o in a)
