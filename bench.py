@@ -134,7 +134,7 @@ def ours(args):
         torch.cuda.synchronize()
 
     # ---- checkpoint (synthetic weights: the ONNX file only describes the tensors) + model + engine
-    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{os.getuid()}" + ("_spec" if args.spec else ""))
+    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{os.getuid()}" + (f"_spec_{args.draft_model}_{args.draft_seed}" if args.spec else ""))
     if rank == 0 and not os.path.exists(os.path.join(ckpt, "genai_config.json")):
         create_model(MODEL, ckpt, "bf16", "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
                                                   "max_batch_size": N_REQ, "context_length": 4096})
@@ -143,7 +143,7 @@ def ours(args):
             tmp = ckpt + "_draft"
             create_model(args.draft_model, tmp, "bf16", "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
                                                                   "max_batch_size": N_REQ, "context_length": 4096, "filename": "draft.onnx",
-                                                                  "seed": 1})
+                                                                  "seed": args.draft_seed})
             for fn in os.listdir(tmp):
                 if fn.startswith("draft.onnx"):
                     os.replace(os.path.join(tmp, fn), os.path.join(ckpt, fn))
@@ -155,11 +155,24 @@ def ours(args):
             full["speculative"] = {"max_draft_tokens": args.draft_tokens}
             with open(os.path.join(ckpt, "genai_config.json"), "w") as f:
                 json.dump(full, f, indent=1)
+    if rank == 0 and args.json_schema and not os.path.exists(os.path.join(ckpt, "tokenizer.json")):
+        # a byte-level BPE tokenizer trained on a few lines (the grammar needs token -> bytes; ids beyond its vocabulary are never allowed)
+        from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+        tok = Tokenizer(models.BPE())
+        tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+        tok.decoder = decoders.ByteLevel()
+        corpus = ['{"name": "Alice", "score": 30, "notes": "The quick brown fox jumps over the lazy dog."}', "hello world, hello tokens, hello grammar 0123456789",
+                  "abcdefghijklmnopqrstuvwxyz ABCDEFGHIJKLMNOPQRSTUVWXYZ : , [] {} true false null"] * 8
+        tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=2048, special_tokens=["<s>", "</s>"], show_progress=False,
+                                                            initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+        tok.save(os.path.join(ckpt, "tokenizer.json"))
     barrier()
     cfg = og.Config(ckpt)
     blocks = N_REQ * ((PROMPT_HI + NEW_TOKENS + BLOCK - 1) // BLOCK + 1)
     # eos_token_id -1 never matches a sampled id: every request produces exactly NEW_TOKENS tokens (fixed workload).
-    cfg.overlay(json.dumps({"model": {"eos_token_id": -1},
+    # (under a grammar the end-of-sequence id must exist for the matcher: id 1 of the synthetic tokenizer, which the never-ending
+    # schema below never allows)
+    cfg.overlay(json.dumps({"model": {"eos_token_id": 1 if args.json_schema else -1},
                             "engine": {"dynamic_batching": {"block_size": BLOCK, "num_blocks": blocks, "max_batch_size": N_REQ,
                                                              "max_scheduled_tokens": 4096}}}))
     t0 = time.perf_counter()
@@ -169,12 +182,12 @@ def ours(args):
 
     schema = None
     if args.json_schema:
-        # constrained decoding: every request generates under a JSON schema (llguidance masks on the host, applied on the device)
-        schema = json.dumps({"type": "object", "properties": {"name": {"type": "string"}, "tags": {"type": "array", "items": {"type": "string"}},
-                                                               "score": {"type": "number"}, "notes": {"type": "string"}},
-                             "required": ["name", "tags", "score", "notes"]})
-        if not os.path.exists(os.path.join(ckpt, "tokenizer.json")):
-            raise SystemExit("--json-schema needs a tokenizer.json in the checkpoint directory (the grammar walks token bytes)")
+        # Constrained decoding: every request generates under a JSON schema (llguidance computes a token mask per request and
+        # step on the host while the forward runs; the mask is applied on the device before sampling).  The schema's last
+        # field is a string too long to finish within the run, so that every request decodes all its tokens under the grammar.
+        schema = json.dumps({"type": "object", "properties": {"name": {"type": "string", "maxLength": 12}, "score": {"type": "integer"},
+                                                               "notes": {"type": "string", "minLength": 8192}},
+                             "required": ["name", "score", "notes"], "additionalProperties": False})
 
     rng = np.random.RandomState(2)
     lens = rng.randint(PROMPT_LO, PROMPT_HI + 1, size=N_REQ)
@@ -359,6 +372,7 @@ def ours(args):
                        "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": cfg_w["sampling_label"],
                        "engine": "paged-attention continuous batching; warmed with one 2048-token request before the TTFT phase", "l2": "inputs larger than L2 (weights + KV of tens of GB), no flush",
                        "tp_backend": getattr(tp, "backend", None),
+                       "constrained": "every request under a JSON schema (llguidance masks; the e2e figure includes them)" if schema else None,
                        "device_loop": "inputs advanced on the device between steps" if advance else "frozen inputs (sliding-window ring tables advance on the host)"},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes, "d2h_bytes_per_step": 4 * B,
                     "ms_per_step": round(e2e_wall / K * 1e3, 4), "device_ms_per_step": round(e2e_ms / K, 4),
@@ -398,6 +412,8 @@ def main():
     ap.add_argument("--spec", action="store_true", help="speculative decoding inside the engine with a draft model (config llama70b: Llama-3.2-1B shape)")
     ap.add_argument("--draft_model", default="llama-3.2-1b")
     ap.add_argument("--draft_tokens", type=int, default=4)
+    ap.add_argument("--draft_seed", type=int, default=1, help="seed of the draft's random weights (0 with --draft_model equal to the target: "
+                                                              "identical networks, the acceptance ceiling)")
     ap.add_argument("--json-schema", dest="json_schema", action="store_true", help="every request decodes under a JSON schema (needs tokenizer.json)")
     ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS), help="workload; the default is the headline configuration")
     args = ap.parse_args()

@@ -1,4 +1,4 @@
-"""In-tree builders for the two native artefacts.
+"""In-tree builders for the native artefacts.
 
 * `_og_native.*.so` — C++17 runtime core (config, search, engine scheduler ...) with pybind11 bindings,
   compiled by g++.
@@ -6,7 +6,9 @@
   nvcc (`-gencode arch=compute_100a,code=sm_100a`) and loaded through ctypes.  The launchers take raw
   device pointers and a stream, so no torch headers are needed and a full rebuild takes seconds.
 
-Both are rebuilt only when a source is newer than the artefact.  Usage: `python -m
+* `native/c_api/libogb200_genai.so` — the C API over the package (g++, links libpython).
+
+Each is rebuilt only when a source is newer than the artefact.  Usage: `python -m
 onnxruntime_genai_b200.build_native [--force] [--verbose]`.
 """
 from __future__ import annotations
@@ -25,6 +27,8 @@ BUILD_DIR = os.path.join(PKG_DIR, "build")
 
 NATIVE_SO = os.path.join(PKG_DIR, "_og_native" + sysconfig.get_config_var("EXT_SUFFIX"))
 KERNELS_SO = os.path.join(PKG_DIR, "libogb200_kernels.so")
+C_API_DIR = os.path.join(NATIVE_DIR, "c_api")
+C_API_SO = os.path.join(C_API_DIR, "libogb200_genai.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
@@ -94,6 +98,22 @@ def build_kernels(force=False, verbose=False) -> str:
     return KERNELS_SO
 
 
+def build_c_api(force=False, verbose=False) -> str:
+    """libogb200_genai.so: the C API (native/c_api/ogb_genai_c.h), linked against libpython so that a program without an
+    interpreter of its own can host the runtime."""
+    import pybind11
+    src = os.path.join(C_API_DIR, "ogb_genai_c.cpp")
+    hdr = os.path.join(C_API_DIR, "ogb_genai_c.h")
+    if not force and not _newer([src, hdr], C_API_SO):
+        return C_API_SO
+    libdir = sysconfig.get_config_var("LIBDIR") or "/usr/lib"
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    _run(["g++", "-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-I" + pybind11.get_include(),
+          "-I" + sysconfig.get_paths()["include"], "-I" + C_API_DIR, "-shared", "-o", C_API_SO, src,
+          "-L" + libdir, "-lpython" + ver, "-ldl", "-Wl,-rpath," + libdir], verbose)
+    return C_API_SO
+
+
 def build_all(force=False, verbose=False):
     return build_native(force, verbose), build_kernels(force, verbose)
 
@@ -101,5 +121,5 @@ def build_all(force=False, verbose=False):
 if __name__ == "__main__":
     force = "--force" in sys.argv
     verbose = "--verbose" in sys.argv
-    for p in build_all(force, verbose):
+    for p in build_all(force, verbose) + (build_c_api(force, verbose),):
         print("built", p)

@@ -728,7 +728,7 @@ class Engine:
             gp = self._guidance.get(e.request.id)
             if gp is not None:
                 mask_rows.append(len(mask_list))
-                mask_list.append(gp.compute_mask()[0])
+                mask_list.append(gp)
                 any_mask = True
             else:
                 mask_rows.append(-1)
@@ -741,8 +741,32 @@ class Engine:
                 edits.append((g(rows, torch.int32), g(toks, torch.int32), g(opsl, torch.int32), g(vals, torch.float32)))
         masks = None
         if any_mask:
-            masks = (torch.from_numpy(np.stack(mask_list)).to(dev), torch.tensor(mask_rows, dtype=torch.int32, device=dev))
+            masks = (torch.from_numpy(self._grammar_masks(mask_list)).to(dev), torch.tensor(mask_rows, dtype=torch.int32, device=dev))
         return edits, masks
+
+    def _grammar_masks(self, procs) -> np.ndarray:
+        """One bitmask row per constrained request of the step.  The grammar walks of the requests are independent: llguidance's
+        thread pool fills all rows at once (the step's host time is the slowest request's mask, not their sum), while the
+        device runs the forward pass of the same step."""
+        words = procs[0].words
+        out = np.empty((len(procs), words), dtype=np.int32)
+        live = [(gp.matchers[0], i) for i, gp in enumerate(procs) if not gp.matchers[0].is_stopped()]
+        if len(live) > 1:
+            import llguidance
+            import llguidance.numpy as llnp
+            if getattr(self, "_ll_exec", None) is None:
+                self._ll_exec = llguidance.LLExecutor(num_threads=min(16, max(2, (os.cpu_count() or 4) // 2)))
+            llnp.fill_next_token_bitmask_par(self._ll_exec, live, out)
+            done = {i for _, i in live}
+            for m, i in live:
+                if m.is_error():
+                    raise RuntimeError("grammar matcher error: " + m.get_error())
+        else:
+            done = set()
+        for i, gp in enumerate(procs):
+            if i not in done:
+                out[i] = gp.compute_mask()[0]      # a single live request, or a finished grammar (only end-of-sequence may follow)
+        return out
 
     @property
     def metrics(self) -> Dict[str, int]:
