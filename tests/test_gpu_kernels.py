@@ -647,6 +647,24 @@ def test_topk_and_beam_candidates():
     _close(s, rs, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("rows,n", [(1, 201088), (3, 50000), (20, 32064), (40, 128256), (100, 16384)])
+def test_topk_long_rows_cluster_kernel(rows, n):
+    """Long rows take the candidate-list kernel: 8 / 4 / 2 / 1 CTAs per row depending on the row count, ties at the cut."""
+    x = _rand(rows, n, dtype=torch.float32, seed=46)
+    x[:, ::7] = x[:, 3:4]            # many equal values, some of them inside the top-k set
+    for k in (1, 50, 128):
+        v, i = ops.topk(x, k)
+        rv, ri = ref.topk(x.cpu(), k)
+        assert torch.equal(i.cpu(), ri)
+        _close(v, rv, 0, 0)
+    add = _rand(rows, dtype=torch.float32, seed=47)
+    v, i = ops.topk(x, 8, log_softmax=True, add=add)
+    rv, ri = ref.topk(x.cpu(), 8, log_softmax=True, add=add.cpu())
+    assert torch.equal(i.cpu(), ri)
+    _close(v, rv, rtol=1e-4, atol=1e-4)
+    ops.check_kernel_status()
+
+
 def test_logits_mask_and_edit():
     V = 1003
     x = _rand(3, V, dtype=torch.float32, seed=45)
