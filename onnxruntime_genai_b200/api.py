@@ -357,6 +357,7 @@ class SequenceState:
                        block_table=self.block_table[rows_used].contiguous() if len(rows_used) != self.rows else self.block_table,
                        logits_rows=None if want_all_logits else i32(last),
                        max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds,
+                       min_q_len=min(len(t) for t in row_tokens if t),
                        **self._cross_fields(rows_used))
         if mrope:
             s.positions3 = torch.from_numpy(np.ascontiguousarray(np.concatenate(p3, axis=1))).to(dev)

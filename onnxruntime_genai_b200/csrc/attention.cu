@@ -55,6 +55,8 @@ struct AttnParams {
   // 8-bit cache: a (slot, head) row is head_dim int8 values followed by their fp32 scale and 12 bytes of padding
   // (row pitch head_dim + 16); k_cache / v_cache then point at bytes.
   int kv8;
+  // > 0: requests with at least this many query rows are left to the tensor-core prefill kernel (attention_tc.cu)
+  int skip_rows;
 };
 
 template <int SROW>
@@ -101,6 +103,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   const int rows = q_len * G;
   const int row0 = blockIdx.x * BM;
   if (row0 >= rows) return;
+  if (p.skip_rows > 0 && rows >= p.skip_rows) return;
   const int past = p.past_lens[b];
   // window < 0: bidirectional attention over exactly the `past` keys already in the cache (encoder self-attention after
   // its keys were appended, and cross-attention over an encoder's keys); the step's own tokens add no keys.
@@ -614,7 +617,8 @@ static int PagedAttention(const void* q, int q_stride, const void* k_cache, cons
                           const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                           int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
                           int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
-                          long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_, int kv_bits) {
+                          long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_, int kv_bits,
+                          int skip_rows = 0) {
   if (B <= 0 || total_tokens <= 0) return 0;
   if (kv_bits != 16 && kv_bits != 8) return -1;
   if (Hkv <= 0 || Hq % Hkv || (q_stride % 8) || (out_stride % 2)) return -1;
@@ -626,6 +630,7 @@ static int PagedAttention(const void* q, int q_stride, const void* k_cache, cons
   p.status = status;
   p.order = order;
   p.kv8 = kv_bits == 8;
+  p.skip_rows = skip_rows;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.block_table = block_table; p.table_cols = table_cols;
@@ -652,6 +657,18 @@ OGB_API int ogb_paged_attention(const void* q, int q_stride, const void* k_cache
   return PagedAttention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out, out_stride, sinks,
                         scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, kv_chunk, scratch, scratch_bytes,
                         cache_slots, order, status, stream_, 16);
+}
+
+// Same, leaving the requests with at least `skip_rows` query rows to ogb_attention_tc (their output rows are not written here;
+// with splits > 1 the combine pass writes unspecified values there, so the tensor-core launch must come afterwards).
+OGB_API int ogb_paged_attention_skip(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                                     const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                                     int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                                     int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
+                                     long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream_, int skip_rows) {
+  return PagedAttention(q, q_stride, k_cache, v_cache, cu_seqlens, past_lens, block_table, table_cols, block_size, out, out_stride, sinks,
+                        scale, softcap, window, B, total_tokens, max_q_len, Hq, Hkv, D, splits, kv_chunk, scratch, scratch_bytes,
+                        cache_slots, order, status, stream_, 16, skip_rows);
 }
 
 // Same over an 8-bit cache: rows of head_dim int8 values + fp32 scale + 12 bytes of padding (see AttnParams::kv8).

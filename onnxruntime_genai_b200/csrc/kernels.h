@@ -113,6 +113,18 @@ int ogb_paged_attention(const void* q, int q_stride, const void* k_cache, const 
                         int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
                         int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch, long long scratch_bytes,
                         int cache_slots, const int32_t* order, int* status, void* stream);
+// attention_tc.cu: tcgen05 prefill attention for the requests of a launch with at least `min_rows` query rows (bf16 cache,
+// head_dim 64 / 128, cache blocks of a multiple of 16 tokens); ogb_paged_attention_skip serves the others.
+int ogb_attention_tc_supported(int D, int block_size, int kv_bits, int cache_slots);
+int ogb_attention_tc(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                     const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out, int out_stride,
+                     const float* sinks, float scale, float softcap, int window, int B, int max_q_len, int Hq, int Hkv, int D,
+                     int min_rows, int cache_slots, int* status, void* stream);
+int ogb_paged_attention_skip(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
+                             const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
+                             int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,
+                             int max_q_len, int Hq, int Hkv, int D, int splits, int kv_chunk, void* scratch,
+                             long long scratch_bytes, int cache_slots, const int32_t* order, int* status, void* stream, int skip_rows);
 int ogb_paged_attention_kv8(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int32_t* cu_seqlens,
                         const int32_t* past_lens, const int32_t* block_table, int table_cols, int block_size, void* out,
                         int out_stride, const float* sinks, float scale, float softcap, int window, int B, int total_tokens,

@@ -35,6 +35,7 @@ class StepInputs:
     block_table_w: Optional[torch.Tensor] = None
     max_q_len: int = 1
     max_kv_len: int = 1
+    min_q_len: int = 0                            # shortest request of the step when the caller knows it (0: unknown)
     inputs_embeds: Optional[torch.Tensor] = None  # overrides the embedding lookup (multimodal / MTP)
     num_decode: int = 0                           # leading requests of the batch that feed exactly one token (mixed steps)
     positions3: Optional[torch.Tensor] = None     # [3, T] int32 position components of multimodal RoPE (None: `positions`)
@@ -259,7 +260,7 @@ class DecoderModel:
         nd, B = s.num_decode, s.past_lens.shape[0]
         if not (qkv.is_cuda and 0 < nd < B and s.max_q_len > 1):
             return ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, *args, max_q_len=s.max_q_len,
-                                       max_kv_len=s.max_kv_len, order=s.attn_order)
+                                       max_kv_len=s.max_kv_len, order=s.attn_order, min_q_len=s.min_q_len or None)
         out = torch.empty(qkv.shape[0], self.heads_local * a.head_dim, dtype=qkv.dtype, device=qkv.device)
         ops.paged_attention(qkv, kc, vc, s.cu_seqlens[:nd + 1], s.past_lens[:nd], table[:nd], *args, max_q_len=1,
                             max_kv_len=s.max_kv_len, out=out, total_tokens=nd)

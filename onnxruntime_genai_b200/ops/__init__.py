@@ -7,6 +7,7 @@ kernel library on a GPU machine is an error.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import numpy as np
@@ -485,10 +486,16 @@ def choose_kv_splits(batch: int, Hkv: int, max_q_len: int, max_kv_len: int, sm_c
     return int(splits), int(chunk)
 
 
+TC_ATTENTION_MIN_ROWS = 128      # query rows (tokens x heads of a GQA group) from which a request takes the tcgen05 prefill kernel
+_TC_ATTENTION = os.environ.get("OGB_ATTN_TC", "1") != "0"
+
+
 def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale, window=0,
-                    sinks=None, softcap=0.0, max_q_len=None, max_kv_len=None, splits=None, out=None, total_tokens=None, order=None):
+                    sinks=None, softcap=0.0, max_q_len=None, max_kv_len=None, splits=None, out=None, total_tokens=None, order=None,
+                    min_q_len=None):
     """q: [T, stride] with the Hq*D query columns first.  Returns [T, Hq*D].  total_tokens: the requests of this call only cover
-    the first `total_tokens` rows of q (sizes the split-KV scratch)."""
+    the first `total_tokens` rows of q (sizes the split-KV scratch).  min_q_len: shortest request of the call when the caller
+    knows it (a call whose every request is long runs on the tensor-core prefill kernel alone)."""
     if not q.is_cuda:
         return ref.paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
                                    window, sinks, softcap)
@@ -498,12 +505,36 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
         out = torch.empty(q.shape[0], Hq * D, dtype=q.dtype, device=q.device)
     if max_q_len is None:
         max_q_len = T
+    G = Hq // Hkv
+    ws = workspace(q.device)
+    use_tc = (_TC_ATTENTION and max_q_len * G >= TC_ATTENTION_MIN_ROWS and k_cache.dtype == torch.bfloat16 and q.dtype == torch.bfloat16
+              and out.stride(0) % 8 == 0 and _lib.lib().ogb_attention_tc_supported(D, block_size, 16, int(k_cache.shape[0])))
+    if use_tc:
+        all_long = min_q_len is not None and min_q_len * G >= TC_ATTENTION_MIN_ROWS
+        if not all_long:
+            # the short requests first (its split-KV combine pass may scribble on the rows of the long ones)
+            paged_attention_small = _lib.lib().ogb_paged_attention_skip
+            sp, ch = splits if isinstance(splits, tuple) else ((splits, 0) if splits else choose_kv_splits(
+                B, Hkv, max_q_len, max_kv_len or 1024, group=G, ordered=order is not None))
+            need = _lib.lib().ogb_attention_scratch_bytes(T, Hq, D, sp)
+            scratch = ws.attn_scratch(need) if sp > 1 else None
+            _lib.check(paged_attention_small(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
+                                             _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0), _ptr(sinks),
+                                             float(scale), float(softcap), int(window), B, T, int(max_q_len), Hq, Hkv, D, int(sp), int(ch),
+                                             _ptr(scratch), scratch.numel() if scratch is not None else 0, int(k_cache.shape[0]),
+                                             _ptr(order), ws.status, _stream(), TC_ATTENTION_MIN_ROWS), "paged_attention")
+            if sp > 1:
+                _lib.LAUNCH_COUNT += 1
+        _lib.check(_lib.lib().ogb_attention_tc(_ptr(q), q.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(cu_seqlens), _ptr(past_lens),
+                                               _ptr(block_table), block_table.stride(0), block_size, _ptr(out), out.stride(0), _ptr(sinks),
+                                               float(scale), float(softcap), int(window), B, int(max_q_len), Hq, Hkv, D,
+                                               TC_ATTENTION_MIN_ROWS, int(k_cache.shape[0]), ws.status, _stream()), "attention_tc")
+        return out
     kv_chunk = 0
     if splits is None:
         splits, kv_chunk = choose_kv_splits(B, Hkv, max_q_len, max_kv_len or 1024, group=Hq // Hkv, ordered=order is not None)
     elif isinstance(splits, tuple):
         splits, kv_chunk = splits
-    ws = workspace(q.device)
     need = _lib.lib().ogb_attention_scratch_bytes(T, Hq, D, splits)
     scratch = ws.attn_scratch(need) if splits > 1 else None
     fn = _lib.lib().ogb_paged_attention_kv8 if k_cache.dtype == torch.int8 else _lib.lib().ogb_paged_attention

@@ -70,6 +70,11 @@ _SIGS = {
     "ogb_attention_scratch_bytes": (c_longlong, [c_int, c_int, c_int, c_int]),
     "ogb_paged_attention": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
+    "ogb_paged_attention_skip": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
+                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P, c_int]),
+    "ogb_attention_tc_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "ogb_attention_tc": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "ogb_paged_attention_kv8": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
     "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),

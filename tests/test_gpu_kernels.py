@@ -413,6 +413,25 @@ def _attention_case(B, q_lens, past, Hq, Hkv, D, bs, window=0, sinks=False, soft
     _close(out, want, rtol=3e-2, atol=3e-2)
 
 
+def test_attention_tcgen05_prefill_kernel():
+    """Requests with at least 128 query rows run on the tcgen05 kernel (S, P and O in tensor memory, P V with its A operand read
+    from tensor memory, V as an MN-major operand); the short requests of the same call stay on the other kernel."""
+    assert ops.TC_ATTENTION_MIN_ROWS == 128
+    n0 = ops._lib.LAUNCH_COUNT
+    _attention_case(B=1, q_lens=[256], past=[0], Hq=8, Hkv=2, D=128, bs=16)                       # causal, 8 row tiles, diagonal masks
+    assert ops._lib.LAUNCH_COUNT - n0 == 2      # the launch for short requests (all of its CTAs leave at once) + the tensor-core launch
+    _attention_case(B=2, q_lens=[300, 50], past=[100, 700], Hq=8, Hkv=2, D=128, bs=16)            # cached prefixes, a partial row tile
+    _attention_case(B=3, q_lens=[20, 200, 1], past=[64, 0, 333], Hq=8, Hkv=2, D=128, bs=16)       # short requests beside a long one
+    _attention_case(B=1, q_lens=[200], past=[37], Hq=8, Hkv=8, D=64, bs=16)                       # head_dim 64, no grouping
+    _attention_case(B=1, q_lens=[400], past=[300], Hq=8, Hkv=2, D=128, bs=16, window=128, sinks=True)
+    _attention_case(B=1, q_lens=[130], past=[0], Hq=8, Hkv=2, D=128, bs=16, softcap=30.0)
+    _attention_case(B=2, q_lens=[70, 200], past=[70, 200], Hq=8, Hkv=8, D=64, bs=16, window=-1)   # bidirectional over cached keys
+    _attention_case(B=1, q_lens=[256], past=[31], Hq=8, Hkv=2, D=128, bs=32)                      # 32-token cache blocks
+    _attention_case(B=1, q_lens=[1100], past=[0], Hq=4, Hkv=1, D=128, bs=16)                      # more tiles than S buffers and K/V stages
+    _attention_case(B=2, q_lens=[150, 160], past=[2000, 5], Hq=32, Hkv=8, D=128, bs=16, splits=3, order=True)
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("splits", [None, 3])
 def test_attention_bidirectional_over_cached_keys(splits):
     """window < 0: every query sees exactly the `past` cached keys (encoder self-attention after its keys were appended,
