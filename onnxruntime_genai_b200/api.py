@@ -57,16 +57,24 @@ def set_log_callback(fn) -> None:
 
 
 class _Trace:
-    """RAII-style scope that writes a Chrome trace event when tracing is enabled."""
+    """RAII-style scope that writes a Chrome trace event when tracing is enabled and, with OGB_NVTX=1, an NVTX range of the
+    same name (so the scopes line up with the kernels in a CUDA profiler's timeline)."""
+    nvtx = os.environ.get("OGB_NVTX", "0") == "1"
 
     def __init__(self, cat: str, name: str):
         self.cat, self.name = cat, name
+        self._pushed = False
 
     def __enter__(self):
         self.t0 = native.trace_now_us() if native.trace_enabled() else -1
+        if _Trace.nvtx and torch.cuda.is_available():
+            torch.cuda.nvtx.range_push(f"{self.cat}:{self.name}")
+            self._pushed = True
         return self
 
     def __exit__(self, *exc):
+        if self._pushed:
+            torch.cuda.nvtx.range_pop()
         if self.t0 >= 0:
             native.trace_complete(self.cat, self.name, self.t0, native.trace_now_us() - self.t0)
         return False

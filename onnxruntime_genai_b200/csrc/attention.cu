@@ -15,11 +15,10 @@
 // Work decomposition: one CTA = (request, kv head, tile of 64 (or, in decode, 16) query rows, kv split) where a
 // "row" is one (query token, query head of the group) pair, so a decode step of a 4:1 GQA model
 // keeps its 4 heads in one MMA tile and reads each K/V row once.  K/V tiles of 64 keys are
-// gathered through the block table into swizzled shared memory, three tiles in flight per CTA:
-// with cache blocks of a multiple of 16 tokens and head_dim 64 or 128, by TMA — one elected thread issues a
-// [16 keys x 64 dims] box per cache block and half row (tensor map over the cache as [slots, kv_heads * head_dim],
-// 128-byte swizzle, completion on an mbarrier), so the warps spend no instructions on the copies; otherwise with
-// 16-byte cp.async copies.  QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
+// gathered through the block table into swizzled shared memory with 16-byte cp.async copies, three tiles in flight per CTA
+// (K/V tiles fed by TMA boxes of 16 keys were measured slower for this kernel: 0.52 against 0.68 of the copy bandwidth at 64
+// requests x 8 kv heads; the tensor-core prefill kernel in attention_tc.cu is the TMA consumer).
+// QK^T and PV run on mma.sync m16n8k16 bf16 with fp32 online softmax.  (The
 // tile's M is at most a few rows in decode, far below the 64-row minimum of tcgen05.mma, and
 // the kernel is bound by the KV stream, not by tensor throughput.)
 #include <cstdlib>
@@ -68,12 +67,11 @@ __device__ __forceinline__ int swz(int row, int chunk) {  // element offset of a
 // All four warps then share those rows and split the 64 keys of every K/V tile between them
 // (16 keys each), keeping private online-softmax state that is merged through shared memory at the
 // end.  DECODE = false: each warp owns 16 of the 64 query rows and walks the whole tile.
-// TMA = true: K/V tiles arrive as [half row of 64 dims][64 keys][128 bytes] boxes with the 128-byte swizzle.
 // KV8 = true: the cache holds int8 rows with an inline scale; raw tiles are staged by cp.async (three in flight) and
 // expanded to one bf16 K tile and one bf16 V tile per iteration, so the tensor-core part is the same code.
-template <int D, bool DECODE, bool TMA, bool KV8 = false>
+template <int D, bool DECODE, bool KV8 = false>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
-paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, AttnParams p) {
+paged_attention_kernel(AttnParams p) {
   constexpr int SROW = ((D + 63) / 64) * 64;
   constexpr int CHUNKS = D / 8;     // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;    // k-steps of QK^T
@@ -81,9 +79,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   constexpr int BM = DECODE ? 16 : ATT_BM;
   constexpr int NT = DECODE ? 2 : ATT_BN / 8;  // score n-tiles (8 keys each) per warp and K/V tile
   extern __shared__ __align__(128) uint8_t smem_dyn[];
-  // TMA boxes with the 128-byte swizzle need 1 KiB-aligned destinations (the launcher adds the slack)
-  uint8_t* smem_raw = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023)) : smem_dyn;
-  __shared__ uint64_t kv_full[ATT_STAGES];
+  uint8_t* smem_raw = smem_dyn;
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   constexpr int BF_STAGES = KV8 ? 1 : ATT_STAGES;
   constexpr int RP = D + 16;                                 // bytes of an int8 cache row (KV8)
@@ -140,36 +136,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   }
 
   // element offset of 16-byte chunk `ch` of key row `key` inside a K/V stage
-  auto kvoff = [&](int key, int ch) -> int {
-    if (TMA) return (ch >> 3) * (ATT_BN * 64) + key * 64 + (((ch ^ key) & 7) << 3);
-    return swz<SROW>(key, ch);
-  };
-  if (TMA) {
-    if (tid == 0) {
-      for (int sgi = 0; sgi < ATT_STAGES; ++sgi) mbar_init(&kv_full[sgi], 1);
-      mbar_fence_init();
-    }
-    __syncthreads();
-  }
-  // TMA: one thread, per 16 keys and half row one box for K and one for V.  Key groups past the end of the range re-read
-  // the last valid group (finite data; their scores are masked), so every stage always receives the same byte count.
-  auto load_kv_tma = [&](int tile, int buf) {
-    constexpr int HALVES = D / 64;
-    mbar_expect_tx(&kv_full[buf], 2 * ATT_BN * D * 2);
-    __nv_bfloat16* dk = sK + buf * ATT_BN * SROW;
-    __nv_bfloat16* dv = sV + buf * ATT_BN * SROW;
-    const int last_group = max(0, (kv_hi - 1) / 16 * 16);
-#pragma unroll
-    for (int gq = 0; gq < ATT_BN / 16; ++gq) {
-      const int j0 = min(tile * ATT_BN + gq * 16, last_group);
-      const int slot0 = table[j0 / p.block_size] * p.block_size + j0 % p.block_size;
-#pragma unroll
-      for (int h = 0; h < HALVES; ++h) {
-        tma_load_2d(dk + h * (ATT_BN * 64) + gq * 16 * 64, &tmap_k, &kv_full[buf], kvh * D + h * 64, slot0);
-        tma_load_2d(dv + h * (ATT_BN * 64) + gq * 16 * 64, &tmap_v, &kv_full[buf], kvh * D + h * 64, slot0);
-      }
-    }
-  };
+  auto kvoff = [&](int key, int ch) -> int { return swz<SROW>(key, ch); };
   // Each warp copies 16 key rows of the tile.  Lanes 0..15 look up the cache slot of one row each; the
   // copies then walk the warp's rows chunk by chunk with consecutive lanes on consecutive 16-byte
   // chunks, so every warp instruction covers whole 32-byte sectors (full rows for head_dim 128).
@@ -253,13 +220,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     if (ok) src = p.q + size_t(tok0 + gr / G) * p.q_stride + size_t(kvh * G + gr % G) * D + ch * 8;
     cp_async16(sQ + swz<SROW>(r, ch), src, ok);
   }
-  if (TMA) {
-    if (tid == 0) {
-      if (n_tiles > 0) load_kv_tma(tile_begin, 0);
-      if (n_tiles > 1) load_kv_tma(tile_begin + 1, 1);
-    }
-    cp_async_commit();   // the Q tile
-  } else if (KV8) {
+  if (KV8) {
     if (n_tiles > 0) load_kv8(tile_begin, 0);
     cp_async_commit();
     if (n_tiles > 1) load_kv8(tile_begin + 1, 1);
@@ -270,9 +231,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     if (n_tiles > 1) load_kv(tile_begin + 1, 1);
     cp_async_commit();
   }
-  bool kv_dead = false;
-  volatile int kv_dead_flag = 0;   // never set: the wait gives up on its time limit only
-
   const int row_base = DECODE ? 0 : warp * 16;       // first tile row of this warp
   const int key_base = DECODE ? warp * 16 : 0;       // first key (within a K/V tile) of this warp
   const bool warp_active = row0 + row_base < rows;
@@ -290,14 +248,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
 
   for (int it = 0; it < n_tiles; ++it) {
     const int buf = it % ATT_STAGES;
-    if (TMA) {
-      if (tid == 0 && it + 2 < n_tiles) load_kv_tma(tile_begin + it + 2, (it + 2) % ATT_STAGES);
-      if (it == 0) { cp_async_wait<0>(); __syncthreads(); }   // the Q tile
-      if (!kv_dead && !mbar_wait_bounded(&kv_full[buf], (it / ATT_STAGES) & 1, &kv_dead_flag)) {
-        atomicMax(p.status, OGB_ERR_WAIT_TMA);
-        kv_dead = true;
-      }
-    } else if (KV8) {
+    if (KV8) {
       if (it + 2 < n_tiles) load_kv8(tile_begin + it + 2, (it + 2) % ATT_STAGES);
       cp_async_commit();
       cp_async_wait<2>();
@@ -398,7 +349,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         }
       }
     }
-    if (DECODE && !TMA) __syncwarp(); else __syncthreads();
+    if (DECODE) __syncwarp(); else __syncthreads();
   }
   cp_async_wait<0>();
 
@@ -545,31 +496,21 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
-bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
-
-template <int D, bool DECODE, bool TMA, bool KV8 = false>
+template <int D, bool DECODE, bool KV8 = false>
 static int LaunchAttentionMode(const AttnParams& p, int max_q_len, int cache_slots, cudaStream_t stream) {
   constexpr int SROW = ((D + 63) / 64) * 64;
   constexpr int BM = DECODE ? 16 : ATT_BM;
   constexpr int KV_BYTES = KV8 ? 2 * ATT_BN * SROW * 2 + ATT_STAGES * 2 * ATT_BN * (D + 16) : 2 * ATT_STAGES * ATT_BN * SROW * 2;
-  constexpr int SMEM = BM * SROW * 2 + KV_BYTES + (TMA ? 1024 : 0);
+  constexpr int SMEM = BM * SROW * 2 + KV_BYTES;
   // decode mode parks the four warps' partial states in the (idle) K/V area, which starts at the K tile and is contiguous
   static_assert(!DECODE || (4 * 16 * D + 4 * 16 * 2) * 4 <= (KV8 ? KV_BYTES : ATT_STAGES * ATT_BN * SROW * 2), "merge buffers must fit in the K/V area");
-  auto kern = paged_attention_kernel<D, DECODE, TMA, KV8>;
+  auto kern = paged_attention_kernel<D, DECODE, KV8>;
   static bool configured[OGB_MAX_DEVICES] = {};
   if (!set_max_dyn_smem(kern, SMEM, configured)) return -3;
-  CUtensorMap mk, mv;
-  memset(&mk, 0, sizeof(mk));
-  memset(&mv, 0, sizeof(mv));
-  if (TMA) {
-    // the cache as a 2-D tensor [slots, kv_heads * head_dim]; a box is 16 consecutive slots x 64 dims of one head
-    if (!MakeMapBf16(&mk, p.k_cache, cache_slots, p.Hkv * D, p.Hkv * D, 16)) return -2;
-    if (!MakeMapBf16(&mv, p.v_cache, cache_slots, p.Hkv * D, p.Hkv * D, 16)) return -2;
-  }
   const int G = p.Hq / p.Hkv;
   const int q_tiles = (max_q_len * G + BM - 1) / BM;
   dim3 grid(q_tiles, p.Hkv, p.B * p.splits);
-  launch_pdl(kern, grid, dim3(ATT_THREADS), SMEM, stream, mk, mv, p);
+  launch_pdl(kern, grid, dim3(ATT_THREADS), SMEM, stream, p);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (p.splits > 1) {
     const int warps = 4;
@@ -583,24 +524,12 @@ static int LaunchAttentionMode(const AttnParams& p, int max_q_len, int cache_slo
 template <int D>
 static int LaunchAttention(const AttnParams& p, int max_q_len, int cache_slots, cudaStream_t stream) {
   const int G = p.Hq / p.Hkv;
-  // Opt-in (OGB_ATTN_TMA=1): measured on B200 at 64 requests x 8 kv heads the TMA-fed tiles (16-row boxes of 128 bytes, one
-  // issuing thread, two tiles ahead) run at 0.52 of the copy bandwidth against 0.68 for the cp.async gather below.
-  static const int tma_enabled = [] { const char* e = getenv("OGB_ATTN_TMA"); return (e && e[0] == '1') ? 1 : 0; }();
-  // TMA path: whole 16-key groups inside one cache block, 128-byte half rows, aligned cache, a status word for the waits
-  const bool tma = tma_enabled && !p.kv8 && (D == 64 || D == 128) && p.block_size % 16 == 0 && cache_slots >= 16 && p.status != nullptr &&
-                   ((reinterpret_cast<uintptr_t>(p.k_cache) | reinterpret_cast<uintptr_t>(p.v_cache)) & 15) == 0;
-  if constexpr (D == 64 || D == 128) {
-    if (tma) {
-      if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, true>(p, max_q_len, cache_slots, stream);
-      return LaunchAttentionMode<D, false, true>(p, max_q_len, cache_slots, stream);
-    }
-  }
   if (p.kv8) {
-    if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, false, true>(p, max_q_len, cache_slots, stream);
-    return LaunchAttentionMode<D, false, false, true>(p, max_q_len, cache_slots, stream);
+    if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, true>(p, max_q_len, cache_slots, stream);
+    return LaunchAttentionMode<D, false, true>(p, max_q_len, cache_slots, stream);
   }
-  if (max_q_len * G <= 16) return LaunchAttentionMode<D, true, false>(p, max_q_len, cache_slots, stream);
-  return LaunchAttentionMode<D, false, false>(p, max_q_len, cache_slots, stream);
+  if (max_q_len * G <= 16) return LaunchAttentionMode<D, true>(p, max_q_len, cache_slots, stream);
+  return LaunchAttentionMode<D, false>(p, max_q_len, cache_slots, stream);
 }
 
 }  // namespace ogb

@@ -51,7 +51,7 @@ __global__ void embedding_q4_kernel(const int32_t* __restrict__ ids, const uint3
   for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
     const uint32_t w = __ldg(row + i);
     const int blk = i / 4;
-    const float sc = bf2f(f2bf(__half2float(scales[size_t(id) * nb + blk])));
+    const float sc = __half2float(scales[size_t(id) * nb + blk]);     // the checkpoint's fp16 scale, exactly
     int zp = 8;
     if (zps) { const uint8_t z = zps[size_t(id) * zp_pitch + blk / 2]; zp = (blk & 1) ? (z >> 4) : (z & 0xF); }
     uint4 o;
@@ -59,8 +59,7 @@ __global__ void embedding_q4_kernel(const int32_t* __restrict__ ids, const uint3
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int nib = (w >> (4 * j)) & 0xF;
-      const float v = bf2f(f2bf(float(nib - zp) * sc));
-      oe[j] = f2bf(mult == 1.f ? v : v * mult);
+      oe[j] = f2bf(float(nib - zp) * sc * mult);
     }
     out[size_t(t) * (K / 8) + i] = o;
   }

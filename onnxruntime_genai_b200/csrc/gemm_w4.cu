@@ -6,7 +6,10 @@
 // and one scale / zero point per block of 32 along K.  The ONNX layout ([N, K/32, 16] bytes + separate
 // scale and packed zero-point arrays) is repacked once at load time into tiles that one bulk copy can
 // stream: for every (k-block of 64, tile of 128 output rows) a contiguous 5 KiB record
-//     [128 rows][32 bytes of nibbles]  +  [128 rows][scale0, 128+zp0, scale1, 128+zp1 as bf16]
+//     [128 rows][32 bytes of nibbles]  +  [128 rows][hi0, lo0|zp0, hi1, lo1|zp1 as 16-bit fields]
+// where hi is the block scale rounded to bf16, lo the remainder (scale - hi) as a bf16 whose mantissa needs at most three bits
+// for an fp16 scale, and the zero point sits in the four mantissa bits of lo that are always zero: hi + lo is the checkpoint's
+// fp16 scale exactly (storing the scale as one bf16 would drop three of its mantissa bits).
 // with the nibbles of each 32-bit word ordered so that `(word >> 4j) & 0x000F000F` yields two
 // consecutive k values in the two halves of a register (no byte permutes in the inner loop).
 //
@@ -14,8 +17,8 @@
 // up to 12-16 records = 60-80 KiB in flight per CTA, the part that has to cover HBM latency) and
 // the activation tiles through a 2-deep ring; warps 2..5 (one thread per weight row) turn a record
 // into a bf16 K-major tile with the 128-byte swizzle that tcgen05.mma expects
-// ((0x4300 | q) is the bf16 number 128 + q, so (q - zp) * scale is one exact bf16x2 subtract and one
-// multiply); warp 1 issues the MMAs into tensor memory.  HBM traffic is 5 bits per weight.
+// ((0x4300 | q) is the bf16 number 128 + q, so q - zp is one exact bf16x2 subtract; (q - zp) * lo is exact too (4 + 3 bits),
+// and one fused multiply-add with hi rounds (q - zp) * scale to bf16 once); warp 1 issues the MMAs into tensor memory.  HBM traffic is 5 bits per weight.
 // Split-K clusters, the SiLU*mul pairing, bias / residual and programmatic dependent launch come
 // from the shared epilogue / launch path.  Every wait is bounded.
 #include <cstdlib>
@@ -51,10 +54,11 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, 
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t deq_pair(uint32_t word, int shift, __nv_bfloat162 z2, __nv_bfloat162 s2) {
+__device__ __forceinline__ uint32_t deq_pair(uint32_t word, int shift, __nv_bfloat162 z2, __nv_bfloat162 hi2, __nv_bfloat162 lo2) {
   uint32_t t = ((word >> shift) & 0x000F000Fu) | 0x43004300u;  // two bf16 numbers 128 + q
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&t);
-  v = __hmul2(__hsub2(v, z2), s2);
+  v = __hsub2(v, z2);
+  v = __hfma2(v, hi2, __hmul2(v, lo2));                          // round((q - zp) * (hi + lo)) in one rounding
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
@@ -172,14 +176,15 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t* __rest
       uint8_t* dst = w_ring + ws * W_TILE_BYTES + row * 128;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint32_t packed = j < 4 ? sz.x : sz.y;  // (scale, 128 + zp) of the 32-block this word belongs to
-        const __nv_bfloat16 sc = __ushort_as_bfloat16(uint16_t(packed & 0xFFFF)), zp = __ushort_as_bfloat16(uint16_t(packed >> 16));
-        const __nv_bfloat162 s2 = __halves2bfloat162(sc, sc), z2 = __halves2bfloat162(zp, zp);
+        const uint32_t packed = j < 4 ? sz.x : sz.y;  // (hi, lo | zp) of the 32-block this word belongs to
+        const __nv_bfloat16 hi = __ushort_as_bfloat16(uint16_t(packed & 0xFFFF)), lo = __ushort_as_bfloat16(uint16_t((packed >> 16) & 0xFFF0));
+        const __nv_bfloat16 zp = __ushort_as_bfloat16(uint16_t(0x4300u | ((packed >> 16) & 0xF)));
+        const __nv_bfloat162 hi2 = __halves2bfloat162(hi, hi), lo2 = __halves2bfloat162(lo, lo), z2 = __halves2bfloat162(zp, zp);
         uint4 o;
-        o.x = deq_pair(words[j], 0, z2, s2);
-        o.y = deq_pair(words[j], 4, z2, s2);
-        o.z = deq_pair(words[j], 8, z2, s2);
-        o.w = deq_pair(words[j], 12, z2, s2);
+        o.x = deq_pair(words[j], 0, z2, hi2, lo2);
+        o.y = deq_pair(words[j], 4, z2, hi2, lo2);
+        o.z = deq_pair(words[j], 8, z2, hi2, lo2);
+        o.w = deq_pair(words[j], 12, z2, hi2, lo2);
         *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = o;
       }
       fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
@@ -301,7 +306,12 @@ gemv_w4_kernel(const __nv_bfloat16* __restrict__ A, int lda, const uint8_t* __re
       uint4 nib[HB];
       float2 sc[HB];
 #pragma unroll
-      for (int h = 0; h < HB; ++h) { nib[h] = nb[a][h]; sc[h] = unpack_bf16x2(szq[a][h]); }   // (scale, 128 + zero point)
+      for (int h = 0; h < HB; ++h) {     // (scale = hi + lo, 128 + zero point)
+        nib[h] = nb[a][h];
+        const uint32_t pk = szq[a][h];
+        sc[h].x = __uint_as_float(pk << 16) + __uint_as_float(pk & 0xFFF00000u);
+        sc[h].y = __uint_as_float(0x43000000u | ((pk & 0x000F0000u)));
+      }
       if (kb + GEMV_AHEAD < num_kb) fetch(kb + GEMV_AHEAD, a);     // refill the slot just consumed
 #pragma unroll
       for (int h = 0; h < HB; ++h) {

@@ -72,8 +72,26 @@ def check_kernel_status(device=None) -> None:
     _lib.check_status(idx)
 
 
+# ------------------------------------------------------------------------------------------ debug bounds checks
+# OGB_DEBUG_BOUNDS=1: every index tensor an op is about to hand to a kernel (token ids, cache slots, block-table entries,
+# gathered rows, rotary positions) is range-checked first and a bad one raises IndexError naming the op, instead of the kernel
+# reading or writing out of bounds.  The checks synchronise the stream, so this is a debugging mode (and CUDA graphs that
+# were captured with it on replay without checks).
+DEBUG_BOUNDS = os.environ.get("OGB_DEBUG_BOUNDS", "0") == "1"
+
+
+def _check_index(op: str, name: str, t, hi: int, lo: int = 0) -> None:
+    if not DEBUG_BOUNDS or t is None or t.numel() == 0 or (t.is_cuda and torch.cuda.is_current_stream_capturing()):
+        return
+    bad = (t < lo) | (t >= hi)
+    if bool(bad.any()):
+        v = t[bad].flatten()[0].item()
+        raise IndexError(f"{op}: {name} holds {v}, outside [{lo}, {hi})")
+
+
 # ------------------------------------------------------------------------------------------ embedding
 def embedding(ids: torch.Tensor, table, scale: float = 1.0) -> torch.Tensor:
+    _check_index("embedding", "ids", ids, table.V if isinstance(table, QuantizedEmbedding) else table.shape[0])
     if isinstance(table, QuantizedEmbedding):
         if table.device.type != "cuda":
             return ref.embedding(ids, table.dequantize(), scale)
@@ -205,6 +223,8 @@ def qkv_rope_append(x, w, bias, positions, slots, cos_cache, sin_cache, k_cache,
     the rotary dimension must be a multiple of 16 and the caches bf16 - `qkv_fusable` tells; other cases (and prefill-sized
     steps) take the separate kernels."""
     T = x.shape[0]
+    _check_index("qkv_rope_append", "slots", slots[:T], k_cache.shape[0], -1)
+    _check_index("qkv_rope_append", "positions", positions[:T], cos_cache.shape[0])
     if x.is_cuda and T <= FUSED_MAX_TOKENS and not isinstance(w, W4Weight) and qkv_fusable(D, rot, k_cache):
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] == (Hq + 2 * Hkv) * D
         q = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=x.device)
@@ -311,6 +331,7 @@ def decode_advance(sampled, input_ids, positions, past_lens, slot_mapping, sampl
     """In place: the packed inputs of a one-token-per-request step become those of the next step (see
     csrc/elementwise.cu::decode_advance_kernel).  block_table [B, cols] int32, everything else [B] int32."""
     B = sampled.shape[0]
+    _check_index("decode_advance", "positions + 1 (block-table column)", positions[:B] + 1, block_table.shape[1] * block_size)
     if not sampled.is_cuda:
         pos = positions[:B] + 1
         input_ids[:B] = sampled
@@ -440,6 +461,9 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
                    q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None):
     """positions3 [3, T] int32 + mrope_section (rotary pairs per component: temporal, height, width): multimodal RoPE, the
     pairs of each section rotate by their own position component."""
+    _check_index("rope_kv_append", "slots", None if slots is None else slots[:qkv.shape[0]], k_cache.shape[0] if k_cache is not None else 0, -1)
+    if cos_cache is not None:
+        _check_index("rope_kv_append", "positions", positions[:qkv.shape[0]] if positions3 is None else positions3, cos_cache.shape[0])
     if not qkv.is_cuda:
         return ref.rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved,
                                   q_norm_w, k_norm_w, norm_eps, positions3, mrope_section)
@@ -496,6 +520,8 @@ def paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, blo
     """q: [T, stride] with the Hq*D query columns first.  Returns [T, Hq*D].  total_tokens: the requests of this call only cover
     the first `total_tokens` rows of q (sizes the split-KV scratch).  min_q_len: shortest request of the call when the caller
     knows it (a call whose every request is long runs on the tensor-core prefill kernel alone)."""
+    _check_index("paged_attention", "block_table", block_table, k_cache.shape[0] // block_size, -1)
+    _check_index("paged_attention", "cu_seqlens", cu_seqlens[:past_lens.shape[0] + 1], q.shape[0] + 1)
     if not q.is_cuda:
         return ref.paged_attention(q, k_cache, v_cache, cu_seqlens, past_lens, block_table, block_size, Hq, Hkv, D, scale,
                                    window, sinks, softcap)
@@ -560,6 +586,8 @@ def logits_bitmask(logits, mask_words, mask_rows=None):
 
 
 def logits_edit(logits, rows, tokens, ops, values):
+    _check_index("logits_edit", "rows", rows, logits.shape[0])
+    _check_index("logits_edit", "tokens", tokens, logits.shape[1])
     if not logits.is_cuda:
         return ref.logits_edit(logits, rows, tokens, ops, values)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
@@ -580,6 +608,7 @@ def to_float32(x):
 
 def gather_rows(x, rows, f16: bool = False):
     """out[i] = x[rows[i]]; f16: bf16 rows come out as fp16 (input of the fp16 form of the packed FP4 expert GEMM)."""
+    _check_index("gather_rows", "rows", rows, x.shape[0])
     if not x.is_cuda:
         return x[rows.long()].to(torch.float16) if f16 else x[rows.long()]
     out = torch.empty(rows.numel(), x.shape[1], dtype=torch.float16 if f16 else x.dtype, device=x.device)

@@ -2,8 +2,9 @@
 
 `W4Weight.from_quantized(q, scales, zero_points)` repacks once at load time; `ops.linear` and
 `ops.gate_up_act` accept a W4Weight wherever they accept a dense bf16 weight.  `dequantize()` restates
-exactly what the kernel computes (bf16 (q - zp) times bf16 scale, rounded to bf16) for the CPU path
-and for the tests.
+exactly what the kernel computes ((q - zp) times the checkpoint's scale, rounded to bf16 once) for the CPU
+path and for the tests.  The scale travels as two bf16 numbers hi + lo (lo = scale - hi needs three mantissa bits for an fp16
+scale, so the pair is exact; the zero point rides in lo's four spare mantissa bits).
 """
 from __future__ import annotations
 
@@ -47,8 +48,10 @@ class W4Weight:
         words = (qp.view(Np, K // 8, 8) << shifts).sum(-1)                       # [Np, K/8] values < 2^32
         b = torch.stack([(words >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.uint8)  # little endian bytes
         nib = b.view(Np // 128, 128, K // 64, 32).permute(2, 0, 1, 3)             # [K/64, tiles, 128, 32]
-        sz = torch.stack([sp, zpp + 128.0], dim=-1).to(torch.bfloat16)            # [Np, nb, 2]
-        szb = sz.view(torch.int16).view(Np, K // 64, 4).contiguous().view(torch.uint8).view(Np, K // 64, 8)
+        hi, lo_bits = split_scale(sp)
+        second = (lo_bits | zpp.to(torch.int32)).to(torch.int16)                   # lo with the zero point in its low mantissa bits
+        sz = torch.stack([hi.view(torch.int16), second], dim=-1)                   # [Np, nb, 2]
+        szb = sz.view(Np, K // 64, 4).contiguous().view(torch.uint8).view(Np, K // 64, 8)
         szt = szb.view(Np // 128, 128, K // 64, 8).permute(2, 0, 1, 3)
         packed = torch.cat([nib.reshape(K // 64, Np // 128, 128 * 32), szt.reshape(K // 64, Np // 128, 128 * 8)], dim=-1).contiguous()
         return W4Weight(packed.to(device), N, K, q if keep_host else None, scales.float() if keep_host else None,
@@ -59,9 +62,19 @@ class W4Weight:
         if self._q is None:
             raise RuntimeError("host copy of the quantised weight was dropped")
         nb = self.K // 32
-        d = (self._q.float().view(self.N, nb, 32) - self._zp.float().view(self.N, nb, 1)).to(torch.bfloat16)
-        s = self._s.view(self.N, nb, 1).to(torch.bfloat16)
-        return (d * s).float().view(self.N, self.K)
+        d = self._q.float().view(self.N, nb, 32) - self._zp.float().view(self.N, nb, 1)
+        hi, lo_bits = split_scale(self._s.view(self.N, nb).float())
+        s = hi.float() + (lo_bits.to(torch.int32) << 16).view(torch.float32)
+        return (d * s.view(self.N, nb, 1)).to(torch.bfloat16).float().view(self.N, self.K)
+
+
+def split_scale(s: torch.Tensor):
+    """fp32 scales -> (hi bf16, bits of lo as int32 in 0..0xFFF0): hi = bf16(s), lo = bf16(s - hi) with the low four mantissa
+    bits cleared.  hi + lo == s for every fp16 value (11 significant bits = 8 + 3)."""
+    hi = s.to(torch.bfloat16)
+    lo = (s - hi.float()).to(torch.bfloat16)
+    lo_bits = lo.view(torch.int16).to(torch.int32) & 0xFFF0
+    return hi, lo_bits
 
 
 def unpack_ort_q4(qweight: torch.Tensor, zero_points: Optional[torch.Tensor], N: int, K: int):
@@ -101,5 +114,5 @@ class QuantizedEmbedding:
             zp = torch.stack([z & 0xF, z >> 4], dim=-1).view(V, -1)[:, :nb].float()
         else:
             zp = torch.full((V, nb), 8.0, device=self.q.device)
-        sc = self.scales.view(V, nb).float().to(torch.bfloat16).float()
+        sc = self.scales.view(V, nb).float()
         return ((qv - zp[:, :, None]) * sc[:, :, None]).to(torch.bfloat16).to(dtype).view(V, K)

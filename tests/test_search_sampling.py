@@ -193,19 +193,18 @@ def test_append_validation():
         s.append_tokens(np.zeros((2, 9), dtype=np.int32))
 
 
-def test_dense_position_and_mask_updates_follow_the_reference_rules():
-    """position_ids / attention_mask updates of the classic decoder graph (reference: src/cpu/interface.cpp:108-167)."""
+def test_debug_bounds_mode_names_the_bad_index(monkeypatch):
+    """OGB_DEBUG_BOUNDS: an out-of-range id / slot / row raises before any kernel (or reference op) touches memory."""
     import torch
-    from onnxruntime_genai_b200.ops import position_inputs as pi
-    ids = torch.tensor([[0, 0, 5, 6], [7, 8, 9, 0]], dtype=torch.int32)
-    pos, mask = pi.initial_position_ids_and_mask(ids, pad_token_id=0)
-    assert pos.tolist() == [[0, 0, 0, 1], [0, 1, 2, 0]] and mask.tolist() == [[0, 0, 1, 1], [1, 1, 1, 0]]
-    # one row: continuous decoding, 3 new tokens after 5 cached ones
-    assert pi.update_position_ids(torch.zeros(1, 1, dtype=torch.int64), 1, 8, 3).tolist() == [[5, 6, 7]]
-    assert pi.update_attention_mask(torch.zeros(1, 4, dtype=torch.int32), 1, 5).tolist() == [[1, 1, 1, 1, 1]]
-    # several rows: one step
-    assert pi.update_position_ids(torch.tensor([[1], [2]]), 2, 5, 1).tolist() == [[2], [3]]
-    assert pi.update_attention_mask(mask, 2, 5).tolist() == [[0, 0, 1, 1, 1], [1, 1, 1, 0, 1]]
-    static = torch.zeros(2, 8, dtype=torch.int32)
-    static[:, :4] = mask
-    assert pi.update_attention_mask_static(static, 2, 6).tolist() == [[0, 0, 1, 1, 1, 1, 0, 0], [1, 1, 1, 0, 1, 1, 0, 0]]
+    from onnxruntime_genai_b200 import ops
+    monkeypatch.setattr(ops, "DEBUG_BOUNDS", True)
+    table = torch.zeros(10, 8)
+    ops.embedding(torch.tensor([0, 9], dtype=torch.int32), table)
+    with pytest.raises(IndexError, match="embedding: ids holds 10"):
+        ops.embedding(torch.tensor([0, 10], dtype=torch.int32), table)
+    with pytest.raises(IndexError, match="gather_rows: rows holds -1"):
+        ops.gather_rows(torch.zeros(4, 8), torch.tensor([-1], dtype=torch.int32))
+    logits = torch.zeros(2, 16)
+    with pytest.raises(IndexError, match="logits_edit: tokens holds 16"):
+        ops.logits_edit(logits, torch.tensor([0], dtype=torch.int32), torch.tensor([16], dtype=torch.int32),
+                        torch.tensor([0], dtype=torch.int32), torch.tensor([0.0]))

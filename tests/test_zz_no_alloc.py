@@ -57,8 +57,34 @@ def test_noalloc_attention_matches_regular_entry_point_twice():
                 Hq, Hkv, D, splits, stream)
         assert rc == 0
         torch.cuda.synchronize()
-        err = (out.float() - want.float()).abs().max().item()
-        assert err <= 3e-2, f"no-alloc entry point differs from the regular one by {err}"
+        # same kernel, same split plan: the two entry points agree bit for bit
+        assert torch.equal(out, want), f"no-alloc entry point differs from the regular one by {(out.float() - want.float()).abs().max().item()}"
+        _against_oracle(c, out, Hq, Hkv, D, bs)
+
+
+def _against_oracle(c, out, Hq, Hkv, D, bs):
+    from onnxruntime_genai_b200.ops import reference as ref
+    want = ref.paged_attention(c["q"].cpu(), c["kc"].cpu(), c["vc"].cpu(), c["cu"].cpu(), c["pl"].cpu(), c["table"].cpu(), bs, Hq, Hkv, D,
+                               1 / math.sqrt(D))
+    err = (out.float().cpu() - want.float()).abs().max().item()
+    assert err <= 3e-2, f"no-alloc entry point differs from the fp32 reference by {err}"
+
+
+@pytest.mark.parametrize("D,splits", [(64, 3), (96, 1), (128, 1)])
+def test_noalloc_attention_other_head_dims_and_single_split(D, splits):
+    """head_dim 64 / 96 and a call that needs no scratch at all (splits = 1), against the fp32 reference."""
+    fn, need = _symbol()
+    Hq, Hkv, bs = 8, 2, 16
+    past = [300, 17, 1023]
+    c = _case(7 + D, 3, past, Hq, Hkv, D, bs)
+    out = torch.empty(3, Hq * D, dtype=torch.bfloat16, device="cuda")
+    assert need(3, Hq, D, splits) == (0 if splits == 1 else splits * 3 * Hq * (D + 2) * 4)
+    rc = fn(c["q"].data_ptr(), c["q"].stride(0), c["kc"].data_ptr(), c["vc"].data_ptr(), c["cu"].data_ptr(), c["pl"].data_ptr(),
+            c["table"].data_ptr(), c["table"].stride(0), bs, out.data_ptr(), out.stride(0), None, 1 / math.sqrt(D), 0.0, 0, 3, 3, 1,
+            Hq, Hkv, D, splits, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    _against_oracle(c, out, Hq, Hkv, D, bs)
 
 
 def test_noalloc_attention_refuses_oversized_requests():
