@@ -52,6 +52,7 @@ class Request:
         self._native = None
         self._engine = None
         self._opaque = None
+        self._adapter: Optional[str] = None
         self.t_added = self.t_first = None
 
     # tokens ------------------------------------------------------------------------------------
@@ -81,6 +82,15 @@ class Request:
 
     def is_done(self) -> bool:
         return self.is_turn_complete()
+
+    def set_active_adapter(self, adapters, name: Optional[str]):
+        """This request's tokens run with the named LoRA adapter (None: the base model).  Requests with different adapters, and
+        with none, share engine steps: the low-rank products are grouped by adapter inside each step."""
+        if name is not None and name not in adapters._loaded:
+            raise RuntimeError(f"adapter '{name}' is not loaded")
+        self._adapter = name
+        if self._engine is not None:
+            self._engine._adapter_requests = sum(1 for r in self._engine._by_native.values() if r._adapter is not None)
 
     def set_opaque_data(self, obj):
         self._opaque = obj
@@ -196,6 +206,7 @@ class ModelExecutor:
         self._unsplit: Dict[int, bool] = {}
         # decode steps issue the attention CTAs of long requests first (OGB_ATTN_ORDER=0: in batch order)
         self.order_attention = self.use_graphs and os.environ.get("OGB_ATTN_ORDER", "1") != "0"
+        self.lora_of = None          # set by the engine: plan -> (per-token adapter ids on the device, adapter names) or None
 
     def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int, ordered: bool = False) -> StepInputs:
         st = self.staging
@@ -220,7 +231,8 @@ class ModelExecutor:
     def forward(self, plan) -> torch.Tensor:
         B, T = len(plan.entries), plan.token_count
         st = self.staging
-        if self.use_graphs and plan.graph_eligible:
+        lora = self.lora_of(plan) if self.lora_of is not None else None
+        if self.use_graphs and plan.graph_eligible and lora is None:
             key = self.upload_graph_inputs(plan)
             g = self.graphs.get(key)
             if g is None:
@@ -240,6 +252,8 @@ class ModelExecutor:
                     break
                 nd += 1
             s.num_decode = nd
+        if lora is not None:
+            s.lora_ids, s.lora_names = lora
         return self.decoder.forward(s, self.kv)
 
     def upload_graph_inputs(self, plan):
@@ -483,6 +497,9 @@ class Engine:
             from .speculative import EngineSpeculator
             self.spec = EngineSpeculator(self, spec_cfg)
         self._by_native: Dict[int, Request] = {}
+        self._adapter_requests = 0       # requests with a LoRA adapter: their steps run eagerly (no graphs, no look-ahead)
+        if hasattr(self.executor, "lora_of"):
+            self.executor.lora_of = self._lora_of
         self._guidance: Dict[int, Any] = {}
         self.last_outcome = StepOutcome.NoWork
         self.step_count = 0
@@ -517,6 +534,7 @@ class Engine:
         request._native, request._engine = nat, self
         request.t_added = time.perf_counter()
         self._by_native[nat.id] = request
+        self._adapter_requests = sum(1 for r in self._by_native.values() if r._adapter is not None)
         self._need_first.add(nat.id)
         so = request.params.search
         if so.get("min_length", 0) > 0 or so.get("repetition_penalty", 1.0) != 1.0 or so.get("no_repeat_ngram_size", 0) > 0:
@@ -526,6 +544,26 @@ class Engine:
             self._guidance[nat.id] = GuidanceProcessor(self.model, request.params.guidance_type, request.params.guidance_data, 1, False)
             self._guidance[nat.id].commit_prompt(np.asarray(request._pending_tokens, dtype=np.int32).reshape(1, -1))
 
+    def _lora_of(self, plan):
+        """(per-token adapter index on the device, names of the adapters present) for a step that holds at least one request with
+        an adapter, else None.  Tokens of requests without an adapter carry the index len(names)."""
+        if not self._adapter_requests:
+            return None
+        names: List[str] = []
+        per_entry = []
+        for e in plan.entries:
+            rq = self._by_native.get(e.request.id)
+            name = rq._adapter if rq is not None else None
+            if name is not None and name not in names:
+                names.append(name)
+            per_entry.append(name)
+        if not names:
+            return None
+        ids = np.empty(plan.token_count, dtype=np.int32)
+        for e, name in zip(plan.entries, per_entry):
+            ids[e.packed_offset:e.packed_offset + e.num_tokens] = names.index(name) if name is not None else len(names)
+        return torch.from_numpy(ids).to(self.model.device), tuple(names)
+
     def remove_request(self, request: Request):
         if request._native is None:
             return
@@ -533,6 +571,7 @@ class Engine:
             self._drain()     # the request is part of the step in flight: let that step commit first
         self.core.remove_request(request._native)
         self._by_native.pop(request._native.id, None)
+        self._adapter_requests = sum(1 for r in self._by_native.values() if r._adapter is not None)
         self._guidance.pop(request._native.id, None)
         self._with_processors.discard(request._native.id)
         self._need_first.discard(request._native.id)
@@ -620,7 +659,7 @@ class Engine:
                 return
             st = self.staging
             ahead, self._ahead = self._ahead, None
-            plain = not self._with_processors and not self._guidance
+            plain = not self._with_processors and not self._guidance and not self._adapter_requests
             try:
                 st.flip()
                 if ahead is not None and plain and ahead[0] == plan.signature:

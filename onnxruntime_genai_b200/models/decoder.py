@@ -47,6 +47,8 @@ class StepInputs:
     cross_qk_heads: Optional[list] = None         # [(layer, head)]: alignment heads whose cross-attention scores are wanted
     cross_qk_out: Optional[list] = None           # filled by forward: one [tokens, max_cross_len] fp32 tensor per listed head
     return_hidden: bool = False
+    lora_ids: Optional[torch.Tensor] = None      # [T] int32: index of each token's adapter in `lora_names` (len(lora_names) = none)
+    lora_names: Optional[tuple] = None           # adapters present in this step (a batch may mix several and none)
 
 
 class PagedKVCache:
@@ -213,6 +215,7 @@ class DecoderModel:
         self.conv_channels_local = arch.hidden_size // self.tp.size      # channels of a hybrid model's convolution layers
         self.inter_local = arch.intermediate_size // self.tp.size
         self.active_adapter = None  # name -> used by the LoRA hooks
+        self._lora_batch = None     # per-token adapters of the step in flight (models/lora.py::LoraBatch)
         self.norms_folded = False
         self.fuse_steps = True      # decode-sized steps of a folded model take the five-kernel layer (tests compare both forms)
 
@@ -269,6 +272,9 @@ class DecoderModel:
         return out
 
     def _lora(self, lw: LayerWeights, proj: str):
+        if self._lora_batch is not None:
+            from .lora import grouped_lora
+            return grouped_lora(lw, proj, self._lora_batch)
         if self.active_adapter is None:
             return None
         return lw.lora.get(self.active_adapter, {}).get(proj)
@@ -308,7 +314,8 @@ class DecoderModel:
         o_proj (+ residual, + all-reduce), gate/up (+ norm, SiLU * mul), down_proj (+ residual, + all-reduce)."""
         a = self.arch
         lw = self.layers[0]
-        return (self.norms_folded and self.fuse_steps and self.active_adapter is None and s.input_ids.shape[0] <= ops.FUSED_MAX_TOKENS and
+        return (self.norms_folded and self.fuse_steps and self.active_adapter is None and s.lora_ids is None and
+                s.input_ids.shape[0] <= ops.FUSED_MAX_TOKENS and
                 (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and
                 lw.post_attn_norm_w is None and lw.post_ffn_norm_w is None and not s.cross_qk_heads)
 
@@ -434,6 +441,13 @@ class DecoderModel:
 
     def forward(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
         """Returns fp32 logits for `s.logits_rows` (or for every token when it is None)."""
+        if s.lora_ids is not None and self._lora_batch is None:
+            from .lora import LoraBatch
+            self._lora_batch = LoraBatch(s.lora_ids, s.lora_names)
+            try:
+                return self.forward(s, kv)
+            finally:
+                self._lora_batch = None
         a = self.arch
         if self._sp_ok(s):
             return self._forward_sp(s, kv)

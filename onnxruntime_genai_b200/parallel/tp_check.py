@@ -20,6 +20,8 @@ def main():
     ap.add_argument("--backend", default=None)
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--engine", action="store_true", help="also run the continuous-batching engine (CUDA graphs on GPU)")
+    ap.add_argument("--lora", nargs="*", default=[], help="adapter files: the first is active on the generator, the engine's requests "
+                                                          "alternate between them and no adapter")
     a = ap.parse_args()
     import faulthandler
     faulthandler.dump_traceback_later(240, exit=True)   # a stuck rank reports where and ends instead of hanging the job
@@ -33,6 +35,12 @@ def main():
     p = og.GeneratorParams(model)
     p.set_search_options(max_length=64, batch_size=2)
     g = og.Generator(model, p)
+    adapters = None
+    if a.lora:
+        adapters = og.Adapters(model)
+        for i, path in enumerate(a.lora):
+            adapters.load(path, f"adapter{i}")
+        g.set_active_adapter(adapters, "adapter0")
     g.append_tokens(prompt)
     logits = g.get_logits()[:, 0, :]
     for _ in range(a.tokens):
@@ -47,6 +55,8 @@ def main():
             gp.set_search_options(max_length=40 + i, do_sample=True, top_k=20, temperature=0.8, random_seed=3 + i)
             r = og.Request(gp)
             r.add_tokens(rng.randint(0, model.arch.vocab_size, size=(9 + 5 * i,)).astype(np.int32))
+            if adapters is not None and i % (len(a.lora) + 1) < len(a.lora):
+                r.set_active_adapter(adapters, f"adapter{i % (len(a.lora) + 1)}")
             engine.add_request(r)
             reqs.append(r)
         outs = {id(r): [] for r in reqs}

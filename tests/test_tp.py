@@ -49,6 +49,39 @@ def test_tp2_on_cpu_matches_single_rank(ckpt):
     assert two["engine"].tolist() == one["engine"].tolist()
 
 
+def _tp_adapters(base, arch):
+    """Two LoRA adapter files over every projection of the tiny model (q / k / v / o / gate / up / down)."""
+    paths = []
+    for seed in (1, 2):
+        g = torch.Generator().manual_seed(seed)
+        t = {}
+        h, q, kv, inter = arch.hidden_size, arch.q_size, arch.kv_size, arch.intermediate_size
+        for layer in range(arch.num_layers):
+            for proj, (k, n) in {"q_proj": (h, q), "k_proj": (h, kv), "v_proj": (h, kv), "o_proj": (q, h), "gate_proj": (h, inter),
+                                 "up_proj": (h, inter), "down_proj": (inter, h)}.items():
+                t[f"model.layers.{layer}.x.{proj}.lora_A.weight"] = (torch.randn(k, 4, generator=g) * 0.2).numpy()
+                t[f"model.layers.{layer}.x.{proj}.lora_B.weight"] = (torch.randn(4, n, generator=g) * 0.2).numpy()
+        path = os.path.join(base, f"lora{seed}.npz")
+        np.savez(path, **t)
+        paths.append(path)
+    return paths
+
+
+def test_lora_under_tp2_on_cpu_matches_single_rank(ckpt):
+    """Adapters are sharded like the projections they adapt (B by rows for column-parallel layers, A by columns for row-parallel
+    ones); a generator with one adapter and an engine batch that mixes two adapters and none agree with the single-rank run."""
+    from onnxruntime_genai_b200.models.arch import PRESETS
+    cpu, _, base = ckpt
+    paths = _tp_adapters(base, PRESETS["tiny-llama"])
+    plain = _run(cpu, os.path.join(base, "plain1.npz"), 1, 0, ["--engine"])
+    one = _run(cpu, os.path.join(base, "out_lora1.npz"), 1, 0, ["--engine", "--lora", *paths])
+    two = _run(cpu, os.path.join(base, "out_lora2.npz"), 2, 29641, ["--engine", "--lora", *paths])
+    assert np.abs(one["logits"] - plain["logits"]).max() > 1e-3              # the adapter is in effect
+    np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
+    assert two["seqs"].tolist() == one["seqs"].tolist()
+    assert two["engine"].tolist() == one["engine"].tolist()
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 @pytest.mark.parametrize("backend", ["nccl", "fused", "fused-sp", "fused-2hop"])
