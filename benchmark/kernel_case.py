@@ -57,7 +57,7 @@ def _time_graph(fn, iters, reps=3):
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
+    with ops.graph_capture(g):
         for i in range(iters):
             fn(i)
     g.replay()

@@ -133,7 +133,7 @@ def main():
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
+            with ops.graph_capture(graph, stream=side):
                 for _ in range(a.iters):
                     fn()
         torch.cuda.current_stream().wait_stream(side)

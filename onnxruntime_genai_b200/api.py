@@ -438,7 +438,7 @@ class SequenceState:
                 self.decoder.forward(s, self.kv)   # warm-up: allocator, tensor maps, scratch
                 torch.cuda.synchronize(dev)
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, pool=self._g_pool):   # graphs are replayed one at a time: they may share memory
+                with ops.graph_capture(g, pool=self._g_pool):   # graphs are replayed one at a time: they may share memory
                     out = self.decoder.forward(s, self.kv)
             self._graphs[key] = (g, out)
         g, out = self._graphs[key]

@@ -14,6 +14,7 @@ int ogb_runtime_init(int device);                 // allocates the per-device st
 int* ogb_status_device_ptr(int device);           // device address of the status word
 int ogb_status_read_and_clear(int device);        // synchronises the device; returns the OgbStatus code seen since last call
 int ogb_sm_count(int device);
+const char* ogb_last_cuda_error();
 
 // ---- gemm_tcgen05.cu
 int ogb_gemm_token_tile(int M, int dual);

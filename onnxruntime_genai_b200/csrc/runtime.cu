@@ -41,4 +41,8 @@ OGB_API int ogb_status_read_and_clear(int device) {
   return e == cudaSuccess ? v : -4;
 }
 
+// Name of the CUDA runtime's last error in this thread (launchers return -4 without the reason; the Python layer appends this).
+// Reading does not clear it.
+OGB_API const char* ogb_last_cuda_error() { return cudaGetErrorString(cudaPeekAtLastError()); }
+
 OGB_API int ogb_sm_count(int device) { return device >= 0 && device < kMaxDevices ? g_sm_count[device] : 0; }

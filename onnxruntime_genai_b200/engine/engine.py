@@ -313,7 +313,7 @@ class ModelExecutor:
         from ..ops import _lib
         before = _lib.LAUNCH_COUNT
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with ops.graph_capture(graph):
             logits = self.decoder.forward(s, self.kv)
         self.graph_launches[(bb, cb)] = _lib.LAUNCH_COUNT - before
         return graph, logits

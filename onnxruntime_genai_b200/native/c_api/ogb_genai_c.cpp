@@ -215,7 +215,7 @@ T Value(T fallback, F&& fn) {
 template <class H>
 void Destroy(H* h) {
   if (!h) return;
-  if (!g_ready || !Py_IsInitialized()) {  // after a shutdown of a hosted interpreter only the C++ part can be released
+  if (!Py_IsInitialized()) {  // no interpreter (never started, or the host program finalised its own): only the C++ part can go
     h->obj.release();
     delete h;
     return;
@@ -950,6 +950,9 @@ OgaResult* OgaRequestHasUnseenTokens(const OgaRequest* r, bool* out) {
 }
 OgaResult* OgaRequestGetUnseenToken(OgaRequest* r, int32_t* out) {
   return Guard([&] { *out = r->obj.attr("get_unseen_token")().cast<int32_t>(); });
+}
+OgaResult* OgaRequestSetActiveAdapter(OgaRequest* r, OgaAdapters* a, const char* name) {
+  return Guard([&] { r->obj.attr("set_active_adapter")(a->obj, name ? py::object(py::str(name)) : py::object(py::none())); });
 }
 OgaResult* OgaRequestIsTurnComplete(const OgaRequest* r, bool* out) {
   return Guard([&] { *out = r->obj.attr("is_turn_complete")().cast<bool>(); });

@@ -229,6 +229,8 @@ OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestGetOpaqueData(OgaRequest* request, 
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestHasUnseenTokens(const OgaRequest* request, bool* out);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestGetUnseenToken(OgaRequest* request, int32_t* out);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestIsTurnComplete(const OgaRequest* request, bool* out);
+/* not in the reference: the adapter of ONE request (adapter_name NULL = base model); requests with different adapters share engine steps */
+OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestSetActiveAdapter(OgaRequest* request, OgaAdapters* adapters, const char* adapter_name);
 
 #ifdef __cplusplus
 }

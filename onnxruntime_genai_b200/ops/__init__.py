@@ -72,6 +72,26 @@ def check_kernel_status(device=None) -> None:
     _lib.check_status(idx)
 
 
+# ------------------------------------------------------------------------------------------ graph capture
+import contextlib
+import gc
+
+
+@contextlib.contextmanager
+def graph_capture(graph, **kw):
+    """torch.cuda.graph with the cyclic garbage collector off for the duration of the capture: a collected object that owns CUDA
+    resources (an older graph, a pinned buffer) frees them from inside the capture and invalidates it
+    ("operation failed due to a previous error during capture" at the next launch)."""
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, **kw):
+            yield
+    finally:
+        if was_on:
+            gc.enable()
+
+
 # ------------------------------------------------------------------------------------------ debug bounds checks
 # OGB_DEBUG_BOUNDS=1: every index tensor an op is about to hand to a kernel (token ids, cache slots, block-table entries,
 # gathered rows, rotary positions) is range-checked first and a bad one raises IndexError naming the op, instead of the kernel
@@ -224,7 +244,8 @@ def qkv_rope_append(x, w, bias, positions, slots, cos_cache, sin_cache, k_cache,
     steps) take the separate kernels."""
     T = x.shape[0]
     _check_index("qkv_rope_append", "slots", slots[:T], k_cache.shape[0], -1)
-    _check_index("qkv_rope_append", "positions", positions[:T], cos_cache.shape[0])
+    if cos_cache is not None:
+        _check_index("qkv_rope_append", "positions", positions[:T], cos_cache.shape[0])
     if x.is_cuda and T <= FUSED_MAX_TOKENS and not isinstance(w, W4Weight) and qkv_fusable(D, rot, k_cache):
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[0] == (Hq + 2 * Hkv) * D
         q = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=x.device)
@@ -331,7 +352,8 @@ def decode_advance(sampled, input_ids, positions, past_lens, slot_mapping, sampl
     """In place: the packed inputs of a one-token-per-request step become those of the next step (see
     csrc/elementwise.cu::decode_advance_kernel).  block_table [B, cols] int32, everything else [B] int32."""
     B = sampled.shape[0]
-    _check_index("decode_advance", "positions + 1 (block-table column)", positions[:B] + 1, block_table.shape[1] * block_size)
+    if DEBUG_BOUNDS:
+        _check_index("decode_advance", "positions + 1 (block-table column)", positions[:B] + 1, block_table.shape[1] * block_size)
     if not sampled.is_cuda:
         pos = positions[:B] + 1
         input_ids[:B] = sampled

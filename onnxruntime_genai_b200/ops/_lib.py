@@ -29,6 +29,7 @@ _SIGS = {
     "ogb_status_device_ptr": (_P, [c_int]),
     "ogb_status_read_and_clear": (c_int, [c_int]),
     "ogb_sm_count": (c_int, [c_int]),
+    "ogb_last_cuda_error": (ctypes.c_char_p, []),
     "ogb_gemm_token_tile": (c_int, [c_int, c_int]),
     "ogb_gemm_auto_splits": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "ogb_gemm_max_active_clusters": (c_int, [c_int, c_int]),
@@ -144,4 +145,10 @@ def check(rc: int, what: str) -> None:
     global LAUNCH_COUNT
     LAUNCH_COUNT += 1
     if rc != 0:
-        raise RuntimeError(f"{what} failed with code {rc}")
+        why = ""
+        if rc == -4:     # a launch (or the configuration call before it) was refused by the CUDA runtime
+            try:
+                why = ": " + lib().ogb_last_cuda_error().decode()
+            except Exception:
+                pass
+        raise RuntimeError(f"{what} failed with code {rc}{why}")
