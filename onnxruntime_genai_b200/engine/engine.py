@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import os
 import time
+import weakref
 from typing import Any, Dict, List, Optional
 
 import numpy as np
@@ -64,10 +65,17 @@ class Request:
             raise RuntimeError("add_tokens: empty token list")
         self._pending_tokens.extend(arr.tolist())
 
-    def continue_with(self, ids):
+    def continue_with(self, ids, max_length: Optional[int] = None):
+        """Queues another turn on the request's resident state.  max_length: a new (larger) cumulative limit for the turns to
+        come - a turn that ended by reaching max_length can only be continued with one; bounded by the model's context."""
         if self._native is None:
             raise RuntimeError("continue_with: the request has not been added to an engine")
-        self._native.continue_with(np.asarray(ids, dtype=np.int32).reshape(-1))
+        if max_length is not None:
+            limit = int(self._engine.model.config.context_length)
+            if max_length > limit:
+                raise RuntimeError(f"continue_with: max_length {max_length} exceeds the model's context length {limit}")
+            self.params.search["max_length"] = int(max_length)
+        self._native.continue_with(np.asarray(ids, dtype=np.int32).reshape(-1), int(max_length or 0))
 
     def has_unseen_tokens(self) -> bool:
         return self._native is not None and self._native.has_unseen_tokens()
@@ -496,7 +504,12 @@ class Engine:
         if want_spec:
             from .speculative import EngineSpeculator
             self.spec = EngineSpeculator(self, spec_cfg)
-        self._by_native: Dict[int, Request] = {}
+        # Requests are held weakly: when the caller drops its last reference to a submitted request, the request is abandoned and
+        # reclaimed at the next add_request / step boundary (reference: src/engine/engine.cpp:107-136)
+        self._by_native: "weakref.WeakValueDictionary[int, Request]" = weakref.WeakValueDictionary()
+        self._natives: Dict[int, Any] = {}
+        self._abandoned: List[int] = []
+        self.reclaimed = 0               # abandoned requests reclaimed so far
         self._adapter_requests = 0       # requests with a LoRA adapter: their steps run eagerly (no graphs, no look-ahead)
         if hasattr(self.executor, "lora_of"):
             self.executor.lora_of = self._lora_of
@@ -525,7 +538,26 @@ class Engine:
         return max(16, budget // per_block)
 
     # ------------------------------------------------------------------ API
+    def _reclaim_abandoned(self):
+        """Requests whose last external reference is gone: removed from the scheduler, their blocks freed."""
+        while self._abandoned:
+            rid = self._abandoned.pop()
+            nat = self._natives.pop(rid, None)
+            if nat is None:
+                continue            # removed explicitly before it was dropped
+            if self._inflight is not None and any(e.request.id == rid for e in self._inflight[0].entries):
+                self._drain()
+            self.core.remove_request(nat)
+            self._guidance.pop(rid, None)
+            self._with_processors.discard(rid)
+            self._need_first.discard(rid)
+            if self.spec is not None:
+                self.spec.forget(rid)
+            self.reclaimed += 1
+        self._adapter_requests = sum(1 for r in self._by_native.values() if r._adapter is not None)
+
     def add_request(self, request: Request):
+        self._reclaim_abandoned()
         if request._native is not None:
             raise RuntimeError("add_request: request was already added to an engine")
         nat = self.core.create_request(request._options())
@@ -534,6 +566,8 @@ class Engine:
         request._native, request._engine = nat, self
         request.t_added = time.perf_counter()
         self._by_native[nat.id] = request
+        self._natives[nat.id] = nat
+        weakref.finalize(request, self._abandoned.append, nat.id)
         self._adapter_requests = sum(1 for r in self._by_native.values() if r._adapter is not None)
         self._need_first.add(nat.id)
         so = request.params.search
@@ -571,6 +605,7 @@ class Engine:
             self._drain()     # the request is part of the step in flight: let that step commit first
         self.core.remove_request(request._native)
         self._by_native.pop(request._native.id, None)
+        self._natives.pop(request._native.id, None)
         self._adapter_requests = sum(1 for r in self._by_native.values() if r._adapter is not None)
         self._guidance.pop(request._native.id, None)
         self._with_processors.discard(request._native.id)
@@ -588,6 +623,8 @@ class Engine:
         On CUDA the engine runs one step ahead: as soon as the ids of a step are committed the next step is planned,
         packed and enqueued, and only then are the ready requests handed out, so the GPU computes step n + 1 while the
         caller consumes the tokens of step n."""
+        if self._abandoned:
+            self._reclaim_abandoned()
         nat = self.core.next_ready()
         if nat is None:
             self._advance()
@@ -653,6 +690,7 @@ class Engine:
             if plan.unserviceable:
                 for nat in plan.unserviceable:
                     self._by_native.pop(nat.id, None)
+                    self._natives.pop(nat.id, None)
                 if plan.outcome != StepOutcome.Planned:
                     raise EngineStepError(StepOutcome.UnserviceableRequest, "a request needs more KV-cache blocks than the engine owns")
             if plan.outcome != StepOutcome.Planned:

@@ -335,7 +335,8 @@ PYBIND11_MODULE(_og_native, m) {
       .def("tokens", [](const Request& r) { return IntArray(r.Tokens().size(), r.Tokens().data()); })
       .def_property_readonly("num_tokens", [](const Request& r) { return r.Tokens().size(); })
       .def("add_tokens", [](Request& r, IntArray ids) { r.AddTokens(ids.data(), size_t(ids.size())); })
-      .def("continue_with", [](Request& r, IntArray ids) { r.ContinueWith(ids.data(), size_t(ids.size())); })
+      .def("continue_with", [](Request& r, IntArray ids, int new_max_length) { r.ContinueWith(ids.data(), size_t(ids.size()), new_max_length); },
+           py::arg("ids"), py::arg("new_max_length") = 0)
       .def("has_unseen_tokens", &Request::HasUnseen)
       .def("get_unseen_token", &Request::PopUnseen)
       .def("is_turn_complete", &Request::TurnComplete)

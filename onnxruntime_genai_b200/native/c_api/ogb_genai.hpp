@@ -235,6 +235,8 @@ class Request : public Owner<OgaRequest, OgaDestroyRequest> {
   explicit Request(GeneratorParams& p) { Check(OgaCreateRequest(p.get(), &p_)); }
   void AddTokens(const std::vector<int32_t>& t) { Check(OgaRequestAddTokens(p_, Sequences(t).get())); }
   void Continue(const std::vector<int32_t>& t) { Check(OgaRequestContinue(p_, Sequences(t).get())); }
+  void Continue(const std::vector<int32_t>& t, size_t max_length) { Check(OgaRequestContinueWithMaxLength(p_, Sequences(t).get(), max_length)); }
+  void SetActiveAdapter(OgaAdapters* adapters, const char* name) { Check(OgaRequestSetActiveAdapter(p_, adapters, name)); }
   void SetOpaqueData(void* d) { Check(OgaRequestSetOpaqueData(p_, d)); }
   void* GetOpaqueData() const {
     void* d;

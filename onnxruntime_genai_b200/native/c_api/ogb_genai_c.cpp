@@ -936,6 +936,9 @@ OgaResult* OgaRequestAddTokens(OgaRequest* r, const OgaSequences* s) {
 OgaResult* OgaRequestContinue(OgaRequest* r, const OgaSequences* s) {
   return Guard([&] { r->obj.attr("continue_with")(OneSequence(s)); });
 }
+OgaResult* OgaRequestContinueWithMaxLength(OgaRequest* r, const OgaSequences* s, size_t max_length) {
+  return Guard([&] { r->obj.attr("continue_with")(OneSequence(s), max_length); });
+}
 OgaResult* OgaRequestSetOpaqueData(OgaRequest* r, void* data) {
   return Guard([&] { r->obj.attr("set_opaque_data")(py::int_(reinterpret_cast<uintptr_t>(data))); });
 }

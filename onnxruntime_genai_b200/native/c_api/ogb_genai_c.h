@@ -224,6 +224,8 @@ OGA_EXPORT OgaResult* OGA_API_CALL OgaCreateRequest(OgaGeneratorParams* params, 
 OGA_EXPORT void OGA_API_CALL OgaDestroyRequest(OgaRequest* request);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestAddTokens(OgaRequest* request, const OgaSequences* tokens);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestContinue(OgaRequest* request, const OgaSequences* tokens);
+/* not in the reference: continue with a new, larger cumulative max_length (a turn that ended at max_length cannot go on otherwise) */
+OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestContinueWithMaxLength(OgaRequest* request, const OgaSequences* tokens, size_t max_length);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestSetOpaqueData(OgaRequest* request, void* opaque_data);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestGetOpaqueData(OgaRequest* request, void** opaque_data);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaRequestHasUnseenTokens(const OgaRequest* request, bool* out);

@@ -103,10 +103,15 @@ void Request::AddTokens(const int32_t* ids, size_t n) {
   tokens_.insert(tokens_.end(), ids, ids + n);
 }
 
-void Request::ContinueWith(const int32_t* ids, size_t n) {
+void Request::ContinueWith(const int32_t* ids, size_t n, int new_max_length) {
   if (status_ != RequestStatus::kTurnComplete)
     throw std::runtime_error("continue_with: the current turn is not complete");
   if (n == 0) throw std::runtime_error("continue_with: empty token list");
+  if (new_max_length > 0) {
+    // a new budget for the next turn (a turn that ended at max_length can only go on with a larger one)
+    if (new_max_length < opt_.max_length) throw std::runtime_error("continue_with: max_length cannot shrink");
+    opt_.max_length = new_max_length;
+  }
   if (int(tokens_.size() + n) >= opt_.max_length)
     throw std::runtime_error("continue_with: max_length (cumulative across turns) would be exceeded");
   tokens_.insert(tokens_.end(), ids, ids + n);

@@ -92,7 +92,7 @@ class Request {
   uint64_t Seed() const { return seed_; }
 
   void AddTokens(const int32_t* ids, size_t n);      // only while Unassigned
-  void ContinueWith(const int32_t* ids, size_t n);   // only while TurnComplete
+  void ContinueWith(const int32_t* ids, size_t n, int new_max_length = 0);   // only while TurnComplete; > 0: the limit from now on
   // Speculative decoding: stages up to n proposed continuation tokens behind the pending token of a decoding request.  The
   // next step then feeds [pending token, drafts...] (1 + n rows whose logits verify the proposal) and is closed with
   // EngineCore::CommitSpeculative.  Returns how many were staged (clipped so that the accepted tokens plus the correction or

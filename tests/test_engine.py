@@ -584,3 +584,49 @@ def test_attention_split_choice():
     assert s > 1 and chunk % 64 == 0 and s * chunk >= 8192
     assert ops.choose_kv_splits(64, 8, 1, 4096, group=4) == (1, 0)
     assert ops.choose_kv_splits(4, 8, 512, 4096, group=4) == (1, 0)
+
+
+def test_abandoned_request_is_reclaimed_at_the_next_boundary(tmp_path):
+    """Dropping the last reference to a submitted request (no remove_request) frees its blocks before the next step
+    (reference: src/engine/engine.cpp:107-136, abandoned-handle reclamation)."""
+    import gc
+    import onnxruntime_genai_b200 as og
+    from helpers import tiny_model_dir
+    d, _ = tiny_model_dir(str(tmp_path / "m"), std=0.3)
+    model = og.Model(d)
+    eng = og.Engine(model)
+    free0 = eng.core.free_blocks
+
+    def submit(n):
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=n + 40, do_sample=False)
+        r = og.Request(p)
+        r.add_tokens(np.arange(3, 3 + n, dtype=np.int32))
+        eng.add_request(r)
+        return r
+
+    def drain(r):
+        while r.has_unseen_tokens():
+            r.get_unseen_token()
+
+    keep, drop = submit(20), submit(33)
+    for _ in range(3):
+        eng.step()
+        drain(keep)
+        drain(drop)
+    assert eng.core.free_blocks < free0
+    used_both = free0 - eng.core.free_blocks
+    del drop
+    gc.collect()
+    eng.step()                                   # the boundary: the abandoned request goes
+    drain(keep)
+    assert eng.reclaimed == 1
+    assert free0 - eng.core.free_blocks < used_both
+    for _ in range(200):
+        if not eng.has_pending_requests():
+            break
+        eng.step()
+        drain(keep)
+    assert keep.is_turn_complete()
+    eng.remove_request(keep)
+    assert eng.core.free_blocks == free0 and eng.reclaimed == 1
