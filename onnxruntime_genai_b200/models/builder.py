@@ -23,6 +23,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import shutil
 import sys
 import zlib
@@ -181,6 +182,160 @@ def quantize_int4_block32(w: torch.Tensor, symmetric: bool = False, block: int =
     return packed, scale, zp_packed
 
 
+QUANT_METHODS = ("default", "rtn", "k_quant")
+# legacy compound names -> (base method, mixed-precision placement) (reference: builders/quant_config.py:285-290)
+ALGO_ALIASES = {
+    "default": ("default", {}), "rtn": ("rtn", {}), "k_quant": ("k_quant", {}),
+    "rtn_last": ("rtn", {"last_matmul": "int8"}), "k_quant_last": ("k_quant", {"last_matmul": "int8"}),
+    "k_quant_mixed": ("k_quant", {"last_matmul": "int8", "mixed_layers": "int8"}),
+    "k_quant_linear": ("k_quant", {"last_matmul": "int8", "linear_attn": "int8"}),
+}
+
+
+def mixed_precision_layers(num_layers: int):
+    """Layers whose qkv / v and down projections are promoted by `mixed_layers` (the selection llama.cpp uses for its mixed
+    k-quants; reference: builders/base.py:1224-1239)."""
+    return [i for i in range(num_layers) if i < num_layers / 8 or i >= 7 * num_layers / 8 or (i - round(num_layers / 8)) % 3 == 2]
+
+
+def _k_quant_params(wb: torch.Tensor, nmax: int, symmetric: bool):
+    """Scale (and minimum) of every block by a weighted least-squares search over candidate grids, the idea of llama.cpp's
+    k-quants that the reference reaches through onnxruntime's `k_quant` algorithm: for a set of candidate scales the values are
+    rounded to the grid, the (scale, minimum) that best reproduces the block under the weights |x| + rms(x) is solved in closed
+    form, and the candidate with the smallest weighted error wins.  wb: [N, blocks, block] fp32."""
+    if symmetric:
+        half = (nmax + 1) // 2                                   # 8 for 4 bits, 128 for 8 bits
+        amax_idx = wb.abs().argmax(-1, keepdim=True)
+        amax = torch.gather(wb, -1, amax_idx).squeeze(-1)
+        w2 = wb * wb
+        best_err = torch.full_like(amax, float("inf"))
+        best_scale = torch.ones_like(amax)
+        for step in range(-9, 10):
+            iscale = -(half + 0.1 * step) / torch.where(amax == 0, torch.ones_like(amax), amax)
+            L = torch.clamp(torch.round(wb * iscale[..., None]), -half, half - 1)
+            sumlx, suml2 = (w2 * wb * L).sum(-1), (w2 * L * L).sum(-1)
+            sc = torch.where(suml2 > 0, sumlx / suml2.clamp(min=1e-30), torch.zeros_like(suml2))
+            err = (w2 * (wb - sc[..., None] * L) ** 2).sum(-1)
+            take = err < best_err
+            best_err = torch.where(take, err, best_err)
+            best_scale = torch.where(take, sc, best_scale)
+        best_scale = torch.where(best_scale == 0, torch.ones_like(best_scale), best_scale)
+        return best_scale, None
+    mn = wb.amin(-1).clamp(max=0.0)
+    mx = wb.amax(-1).clamp(min=0.0)
+    span = (mx - mn)
+    flat = span == 0
+    span = torch.where(flat, torch.ones_like(span), span)
+    weights = wb.abs() + wb.pow(2).mean(-1, keepdim=True).sqrt()
+    sum_w, sum_x = weights.sum(-1), (weights * wb).sum(-1)
+    best_scale, best_min = span / nmax, mn.clone()
+    L = torch.clamp(torch.round((wb - mn[..., None]) / best_scale[..., None]), 0, nmax)
+    best_err = (weights * (best_scale[..., None] * L + mn[..., None] - wb) ** 2).sum(-1)
+    for step in range(21):
+        iscale = (-1.0 + 0.1 * step + nmax) / span
+        L = torch.clamp(torch.round(iscale[..., None] * (wb - mn[..., None])), 0, nmax)
+        sum_l, sum_l2, sum_xl = (weights * L).sum(-1), (weights * L * L).sum(-1), (weights * L * wb).sum(-1)
+        D = sum_w * sum_l2 - sum_l * sum_l
+        ok = D > 0
+        Ds = torch.where(ok, D, torch.ones_like(D))
+        sc = (sum_w * sum_xl - sum_x * sum_l) / Ds
+        m = (sum_l2 * sum_x - sum_l * sum_xl) / Ds
+        pos = m > 0                                          # the minimum may not be positive: zero is always representable
+        sc = torch.where(pos, sum_xl / sum_l2.clamp(min=1e-30), sc)
+        m = torch.where(pos, torch.zeros_like(m), m)
+        err = (weights * (sc[..., None] * L + m[..., None] - wb) ** 2).sum(-1)
+        take = ok & (err < best_err) & (sc > 0)
+        best_err = torch.where(take, err, best_err)
+        best_scale = torch.where(take, sc, best_scale)
+        best_min = torch.where(take, m, best_min)
+    best_scale = torch.where(flat | (best_scale <= 0), torch.ones_like(best_scale), best_scale)
+    return best_scale, best_min
+
+
+def quantize_block(w: torch.Tensor, bits: int = 4, symmetric: bool = False, method: str = "default", block: int = 32):
+    """Block quantisation in the MatMulNBits layout with the reference's three methods (builders/quant_config.py:168-173):
+    `default` and `rtn` round to the grid spanned by each block's minimum and maximum (absolute maximum when symmetric),
+    `k_quant` searches the grid (see _k_quant_params).  bits 4: qweight uint8 [N, K/block, block/2] (low nibble = even k), zero
+    points packed two per byte; bits 8: qweight uint8 [N, K/block, block], one zero point per byte.  Scales fp32 [N, K/block];
+    zero points are None when symmetric (the op's default, 8 or 128, applies)."""
+    if method not in QUANT_METHODS:
+        raise ValueError(f"quantisation method must be one of {list(QUANT_METHODS)}, got '{method}'")
+    if bits not in (4, 8):
+        raise ValueError("bits must be 4 or 8")
+    if bits == 4 and method != "k_quant":
+        return quantize_int4_block32(w, symmetric, block)
+    N, K = w.shape
+    assert K % block == 0
+    nmax = (1 << bits) - 1
+    half = (nmax + 1) // 2
+    wb = w.float().view(N, K // block, block)
+    if method == "k_quant" and not symmetric:
+        # the searched (scale, minimum), then the integer zero point the op needs and one more closed-form fit of the scale for
+        # the codes that zero point gives; blocks that the plain min / max grid reproduces better (under the same weights) keep it
+        scale, mn = _k_quant_params(wb, nmax, False)
+        weights = wb.abs() + wb.pow(2).mean(-1, keepdim=True).sqrt()
+
+        def fit(sc, lo):
+            zpf = torch.clamp(torch.round(-lo / sc), 0, nmax)
+            c = torch.clamp(torch.round(wb / sc[..., None]) + zpf[..., None], 0, nmax) - zpf[..., None]
+            den = (weights * c * c).sum(-1)
+            sc2 = torch.where(den > 0, (weights * c * wb).sum(-1) / den.clamp(min=1e-30), sc)
+            sc2 = torch.where(sc2 > 0, sc2, sc)
+            c2 = torch.clamp(torch.round(wb / sc2[..., None]) + zpf[..., None], 0, nmax) - zpf[..., None]
+            return sc2, zpf, (weights * (sc2[..., None] * c2 - wb) ** 2).sum(-1)
+
+        lo0, hi0 = wb.amin(-1).clamp(max=0.0), wb.amax(-1).clamp(min=0.0)
+        s0 = (hi0 - lo0) / nmax
+        s0 = torch.where(s0 == 0, torch.ones_like(s0), s0)
+        zp0 = torch.clamp(torch.round(-lo0 / s0), 0, nmax)
+        c0 = torch.clamp(torch.round(wb / s0[..., None]) + zp0[..., None], 0, nmax) - zp0[..., None]
+        e0 = (weights * (s0[..., None] * c0 - wb) ** 2).sum(-1)
+        s1, zp1, e1 = fit(scale, mn)
+        better = e1 < e0
+        scale = torch.where(better, s1, s0)
+        zpf = torch.where(better, zp1, zp0)
+        mn = -zpf * scale
+    elif method == "k_quant":
+        scale, mn = _k_quant_params(wb, nmax, True)
+    elif symmetric:
+        amax_idx = wb.abs().argmax(-1, keepdim=True)
+        scale = (torch.gather(wb, -1, amax_idx) / -float(half)).squeeze(-1)
+        scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+        mn = None
+    else:
+        lo, hi = wb.amin(-1).clamp(max=0.0), wb.amax(-1).clamp(min=0.0)
+        scale = (hi - lo) / nmax
+        scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+        mn = lo
+    if symmetric:
+        q = torch.clamp(torch.round(wb / scale[..., None]) + half, 0, nmax)
+        zp = None
+    else:
+        zpf = torch.clamp(torch.round(-mn / scale), 0, nmax)
+        q = torch.clamp(torch.round(wb / scale[..., None]) + zpf[..., None], 0, nmax)
+        zp = zpf.to(torch.uint8)
+    q = q.to(torch.uint8)
+    if bits == 8:
+        return q.contiguous(), scale, zp
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).contiguous()
+    zp_packed = None
+    if zp is not None:
+        if (K // block) % 2:
+            zp = torch.cat([zp, torch.full((N, 1), 8, dtype=torch.uint8, device=zp.device)], dim=1)
+        zp_packed = (zp[:, 0::2] | (zp[:, 1::2] << 4)).contiguous()
+    return packed, scale, zp_packed
+
+
+def dequantize_block(qweight, scales, zero_points, N: int, K: int, block: int = 32, bits: int = 4) -> torch.Tensor:
+    """fp32 [N, K] from MatMulNBits tensors of 4 or 8 bits: w = (q - zp) * scale."""
+    if bits == 4:
+        return dequantize_int4_block32(qweight, scales, zero_points, N, K, block)
+    nb = K // block
+    q = torch.as_tensor(qweight).view(N, nb, block).float()
+    zz = torch.as_tensor(zero_points).view(N, -1)[:, :nb].float() if zero_points is not None else torch.full((N, nb), 128.0, device=q.device)
+    return ((q - zz[..., None]) * torch.as_tensor(scales).float().view(N, nb)[..., None]).view(N, K)
+
+
 def dequantize_int4_block32(qweight, scales, zero_points, N: int, K: int, block: int = 32) -> torch.Tensor:
     """Inverse of quantize_int4_block32: returns fp32 [N, K] with w = (q - zp) * scale."""
     q = torch.as_tensor(qweight).view(N, K // block, block // 2)
@@ -309,9 +464,27 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                  filename: str = "model.onnx", write_config: bool = True, speculative: Optional[dict] = None,
                  draft_dir_entry: Optional[dict] = None, num_blocks: Optional[int] = None,
                  max_scheduled_tokens: Optional[int] = None, context_length: Optional[int] = None,
-                 int4_tied_embeddings: bool = False, linear_format: str = "") -> str:
-    """Writes a checkpoint directory.  With state_dict=None the weights are random N(0, std) from `seed`."""
+                 int4_tied_embeddings: bool = False, linear_format: str = "", int4_algo_config: str = "default",
+                 mixed_precision: Optional[dict] = None) -> str:
+    """Writes a checkpoint directory.  With state_dict=None the weights are random N(0, std) from `seed`.
+    int4_algo_config: quantisation method `default` | `rtn` | `k_quant`, or one of the reference's compound names (`rtn_last`,
+    `k_quant_last`, `k_quant_mixed`, `k_quant_linear`); mixed_precision: selector -> type, e.g. {"last_matmul": "int8",
+    "mixed_layers": "int8"} (the LM head; the qkv and down projections of the layers llama.cpp's mixed k-quants promote)."""
     os.makedirs(out_dir, exist_ok=True)
+    if int4_algo_config not in ALGO_ALIASES:
+        raise ValueError(f"int4_algo_config must be one of {sorted(ALGO_ALIASES)}, got '{int4_algo_config}'")
+    quant_method, placement = ALGO_ALIASES[int4_algo_config]
+    placement = {**placement, **(mixed_precision or {})}
+    for sel, typ in placement.items():
+        if sel not in ("last_matmul", "mixed_layers", "linear_attn") or typ not in ("int4", "int8"):
+            raise ValueError(f"mixed_precision: unknown selector or type {sel}={typ}")
+    promoted = set(mixed_precision_layers(arch.num_layers)) if placement.get("mixed_layers") == "int8" else set()
+
+    def bits_of(node_name: str) -> int:
+        if node_name == "/lm_head/MatMul":
+            return 8 if placement.get("last_matmul") == "int8" else 4
+        m = re.match(r"/model/layers\.(\d+)/(attn/qkv_proj|mlp/down_proj)/MatMul$", node_name)
+        return 8 if (m and int(m.group(1)) in promoted) else 4
     if precision not in ("fp32", "fp16", "bf16", "int4"):
         raise ValueError(f"unsupported precision {precision}")
     if context_length:
@@ -378,7 +551,18 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                 from .quantized_checkpoint import QuantizedLinear
                 q, s, zp = QuantizedLinear.cat(srcs).matmulnbits()
             else:
-                q, s, zp = quantize_int4_block32(torch.cat([t.float() for t in srcs], dim=0), symmetric=int4_symmetric)
+                nbits = bits_of(node_name)
+                q, s, zp = quantize_block(torch.cat([t.float() for t in srcs], dim=0), nbits, int4_symmetric, quant_method)
+                if nbits == 8:
+                    # promoted node (mixed precision): 8-bit MatMulNBits, one byte per weight, zero points unpacked
+                    W.add_array(base + ".MatMul.weight_Q8", q.numpy(), op.UINT8)
+                    W.add_array(base + ".MatMul.weight_scales", s.reshape(-1).to(torch.float16).numpy(), op.FLOAT16)
+                    ins = [inp, base + ".MatMul.weight_Q8", base + ".MatMul.weight_scales"]
+                    if zp is not None:
+                        W.add_array(base + ".MatMul.weight_zp", zp.reshape(-1).numpy(), op.UINT8)
+                        ins.append(base + ".MatMul.weight_zp")
+                    W.node("MatMulNBits", node_name + "_Q8", ins, [out], domain="com.microsoft", K=K, N=N, bits=8, block_size=32, accuracy_level=4)
+                    return
             W.add_array(base + ".MatMul.weight_Q4", q.numpy(), op.UINT8)
             W.add_array(base + ".MatMul.weight_scales", s.reshape(-1).to(torch.float16).numpy(), op.FLOAT16)
             ins = [inp, base + ".MatMul.weight_Q4", base + ".MatMul.weight_scales"]
@@ -994,7 +1178,9 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         block_size=int(extra.get("paged_block_size", 16)), max_batch_size=int(extra.get("max_batch_size", 64)),
         int4_symmetric=bool(int(extra.get("int4_is_symmetric", 0))), synthetic_weights=bool(int(extra.get("synthetic_weights", 0))),
         filename=extra.get("filename", "model.onnx"), context_length=int(extra["context_length"]) if "context_length" in extra else None,
-        int4_tied_embeddings=bool(int(extra.get("int4_tied_embeddings", 0))), linear_format=str(extra.get("linear_format", "")))
+        int4_tied_embeddings=bool(int(extra.get("int4_tied_embeddings", 0))), linear_format=str(extra.get("linear_format", "")),
+        int4_algo_config=str(extra.get("int4_algo_config", "default")),
+        mixed_precision={k: str(extra[k]) for k in ("last_matmul", "mixed_layers", "linear_attn") if k in extra} or None)
 
 
 def main(argv=None):

@@ -5,7 +5,8 @@ Reference: src/python/py/models/gguf_model.py (tensor-name map :74-214, `undo_pe
 (GGUF version 2 / 3, little endian): magic "GGUF", version u32, tensor count u64, metadata count u64, metadata
 key / value pairs, tensor infos (name, n_dims, dims with the fastest dimension first, type, offset), padding to
 `general.alignment` (32), tensor data.  Tensor types read: F32, F16, BF16, Q8_0 (32 int8 + fp16 scale), Q4_0
-(32 nibbles + fp16 scale, w = (q - 8) d) and Q4_1 (w = q d + m); the k-quants are not.
+(32 nibbles + fp16 scale, w = (q - 8) d), Q4_1 (w = q d + m) and the k-quants Q2_K .. Q6_K (super-blocks of 256 weights with
+6-bit or 8-bit sub-block scales; layouts in the comments of `_dequant_k`).
 
 llama.cpp's converter permutes the rows of q_proj / k_proj of the llama family (interleaved -> half-split rotary
 layout); `undo_permute` restores the Hugging Face order.
@@ -20,7 +21,9 @@ import torch
 
 MAGIC = b"GGUF"
 F32, F16, Q4_0, Q4_1, Q8_0, BF16 = 0, 1, 2, 3, 8, 30
-_BLOCK = {Q4_0: (32, 18), Q4_1: (32, 20), Q8_0: (32, 34)}         # type -> (weights per block, bytes per block)
+Q2_K, Q3_K, Q4_K, Q5_K, Q6_K = 10, 11, 12, 13, 14
+_BLOCK = {Q4_0: (32, 18), Q4_1: (32, 20), Q8_0: (32, 34),         # type -> (weights per block, bytes per block)
+          Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 _SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 PERMUTED_ARCHS = ("llama", "mistral", "granite", "olmo")
 
@@ -60,9 +63,11 @@ def dequantize(raw: np.ndarray, ttype: int, n: int) -> np.ndarray:
     if ttype == BF16:
         return (raw.view("<u2")[:n].astype(np.uint32) << 16).view(np.float32)
     if ttype not in _BLOCK:
-        raise NotImplementedError(f"GGUF tensor type {ttype} is not supported (F32, F16, BF16, Q8_0, Q4_0, Q4_1)")
+        raise NotImplementedError(f"GGUF tensor type {ttype} is not supported (F32, F16, BF16, Q8_0, Q4_0, Q4_1, Q2_K .. Q6_K)")
     per, nbytes = _BLOCK[ttype]
     blocks = raw[: n // per * nbytes].reshape(n // per, nbytes)
+    if per == 256:
+        return _dequant_k(blocks, ttype).reshape(-1)
     d = blocks[:, 0:2].copy().view("<f2").astype(np.float32)                       # [blocks, 1]
     if ttype == Q8_0:
         return (blocks[:, 2:].copy().view(np.int8).astype(np.float32) * d).reshape(-1)
@@ -74,6 +79,85 @@ def dequantize(raw: np.ndarray, ttype: int, n: int) -> np.ndarray:
     q = blocks[:, 4:]
     vals = np.concatenate([q & 0xF, q >> 4], axis=1).astype(np.float32)
     return (vals * d + m).reshape(-1)
+
+
+def _f16(b: np.ndarray) -> np.ndarray:
+    return b.copy().view("<f2").astype(np.float32)
+
+
+def _scale_min_k4(sc: np.ndarray):
+    """The eight 6-bit (scale, minimum) pairs packed in the 12 `scales` bytes of a Q4_K / Q5_K super-block: pairs 0-3 are the
+    low six bits of bytes 0-3 / 4-7, pairs 4-7 take four bits from bytes 8-11 and their top two bits from bytes 0-7."""
+    sc = sc.astype(np.uint8)
+    d = np.empty(sc.shape[:-1] + (8,), dtype=np.float32)
+    m = np.empty_like(d)
+    d[..., :4] = sc[..., 0:4] & 63
+    m[..., :4] = sc[..., 4:8] & 63
+    d[..., 4:] = (sc[..., 8:12] & 0xF) | ((sc[..., 0:4] >> 6) << 4)
+    m[..., 4:] = (sc[..., 8:12] >> 4) | ((sc[..., 4:8] >> 6) << 4)
+    return d, m
+
+
+def _dequant_k(b: np.ndarray, ttype: int) -> np.ndarray:
+    """Super-blocks [blocks, bytes] -> fp32 [blocks, 256] (llama.cpp's k-quant layouts)."""
+    nb = b.shape[0]
+    if ttype == Q4_K:
+        # d f16, dmin f16, scales[12], qs[128]: four groups of 64 weights; a group's 32 bytes hold sub-block 2j in the low
+        # nibbles and sub-block 2j + 1 in the high nibbles; w = d * sc * q - dmin * m
+        d, dmin = _f16(b[:, 0:2]), _f16(b[:, 2:4])
+        sc, mn = _scale_min_k4(b[:, 4:16])
+        qs = b[:, 16:144].reshape(nb, 4, 32)
+        q = np.stack([qs & 0xF, qs >> 4], axis=2).reshape(nb, 8, 32).astype(np.float32)
+        return (q * (d * sc)[:, :, None] - (dmin * mn)[:, :, None]).reshape(nb, 256)
+    if ttype == Q5_K:
+        # d, dmin, scales[12], qh[32], qs[128]: as Q4_K with a fifth bit per weight: bit (2j) / (2j + 1) of qh[l]
+        d, dmin = _f16(b[:, 0:2]), _f16(b[:, 2:4])
+        sc, mn = _scale_min_k4(b[:, 4:16])
+        qh = b[:, 16:48]
+        qs = b[:, 48:176].reshape(nb, 4, 32)
+        q = np.stack([qs & 0xF, qs >> 4], axis=2).reshape(nb, 8, 32).astype(np.float32)
+        hi = np.stack([(qh >> k) & 1 for k in range(8)], axis=1).astype(np.float32)      # [blocks, 8 sub-blocks, 32]
+        return ((q + 16.0 * hi) * (d * sc)[:, :, None] - (dmin * mn)[:, :, None]).reshape(nb, 256)
+    if ttype == Q6_K:
+        # ql[128], qh[64], scales int8[16], d f16: two halves of 128 weights; within a half weight l, l + 32, l + 64, l + 96
+        # take their low four bits from ql[l] / ql[l + 32] (low, high nibble) and two bits from qh[l]; 16 weights share a scale
+        ql = b[:, 0:128].reshape(nb, 2, 64)
+        qh = b[:, 128:192].reshape(nb, 2, 32)
+        scales = b[:, 192:208].copy().view(np.int8).astype(np.float32).reshape(nb, 2, 8)
+        d = _f16(b[:, 208:210])
+        l0, l1 = ql[:, :, :32], ql[:, :, 32:]
+        q = np.stack([(l0 & 0xF) | (((qh >> 0) & 3) << 4), (l1 & 0xF) | (((qh >> 2) & 3) << 4),
+                      (l0 >> 4) | (((qh >> 4) & 3) << 4), (l1 >> 4) | (((qh >> 6) & 3) << 4)], axis=2).astype(np.float32) - 32.0   # [nb, 2, 4, 32]
+        # scale index of weight (quarter k, position l) within a half: l // 16 + 2 k
+        idx = (np.arange(32) // 16)[None, :] + 2 * np.arange(4)[:, None]                                                        # [4, 32]
+        sc = scales[:, :, idx]                                                                                                  # [nb, 2, 4, 32]
+        return (q * sc * d[:, :, None, None]).reshape(nb, 256)
+    if ttype == Q2_K:
+        # scales[16] (low nibble scale, high nibble minimum), qs[64], d f16, dmin f16: two halves of 128; within a half the
+        # four 2-bit fields of byte l give weights l, l + 32, l + 64, l + 96; 16 weights share a (scale, minimum)
+        scales = b[:, 0:16]
+        qs = b[:, 16:80].reshape(nb, 2, 32)
+        d, dmin = _f16(b[:, 80:82]), _f16(b[:, 82:84])
+        q = np.stack([(qs >> s) & 3 for s in (0, 2, 4, 6)], axis=2).astype(np.float32)                                          # [nb, 2, 4, 32]
+        idx = (np.arange(32) // 16)[None, :] + 2 * np.arange(4)[:, None]
+        scl = (scales & 0xF).astype(np.float32).reshape(nb, 2, 8)[:, :, idx]
+        mnl = (scales >> 4).astype(np.float32).reshape(nb, 2, 8)[:, :, idx]
+        return (d[:, :, None, None] * scl * q - dmin[:, :, None, None] * mnl).reshape(nb, 256)
+    if ttype == Q3_K:
+        # hmask[32], qs[64], scales[12] (sixteen 6-bit scales, offset 32), d f16: 2-bit fields as in Q2_K plus a high bit from
+        # hmask (bit k of hmask[l] for field k of half 0, bit 4 + k for half 1); a clear high bit subtracts 4
+        hm = b[:, 0:32]
+        qs = b[:, 32:96].reshape(nb, 2, 32)
+        sb = b[:, 96:108].astype(np.uint32)
+        d = _f16(b[:, 108:110])
+        low = np.concatenate([sb[:, 0:8] & 0xF, sb[:, 0:8] >> 4], axis=1)                 # scales 0..15: low four bits
+        high = np.concatenate([(sb[:, 8:12] >> s) & 3 for s in (0, 2, 4, 6)], axis=1)     # their top two bits
+        sc = ((low | (high << 4)).astype(np.float32) - 32.0).reshape(nb, 2, 8)
+        q = np.stack([(qs >> s) & 3 for s in (0, 2, 4, 6)], axis=2).astype(np.float32)    # [nb, 2, 4, 32]
+        bit = np.stack([np.stack([(hm >> (4 * h + k)) & 1 for k in range(4)], axis=1) for h in range(2)], axis=1).astype(np.float32)
+        idx = (np.arange(32) // 16)[None, :] + 2 * np.arange(4)[:, None]
+        return (d[:, :, None, None] * sc[:, :, idx] * (q - 4.0 * (1.0 - bit))).reshape(nb, 256)
+    raise NotImplementedError(f"k-quant type {ttype}")
 
 
 def read_gguf(path: str) -> Tuple[Dict[str, object], Dict[str, torch.Tensor]]:
@@ -190,8 +274,51 @@ def quantize_q8_0(w: np.ndarray) -> bytes:
     return out.tobytes()
 
 
+def quantize_q4_k(w: np.ndarray) -> bytes:
+    """A plain (min / max per sub-block, no search) Q4_K encoder: enough to write test and tooling files."""
+    b = w.reshape(-1, 8, 32).astype(np.float32)
+    mn = np.minimum(b.min(-1), 0.0)
+    sub_scale = (b.max(-1) - mn) / 15.0                                   # per sub-block
+    d = (sub_scale.max(-1) / 63.0).astype(np.float16)
+    dmin = ((-mn).max(-1) / 63.0).astype(np.float16)
+    df, dmf = d.astype(np.float32), dmin.astype(np.float32)
+    sc = np.clip(np.round(np.divide(sub_scale, df[:, None], out=np.zeros_like(sub_scale), where=df[:, None] != 0)), 0, 63).astype(np.uint8)
+    m = np.clip(np.round(np.divide(-mn, dmf[:, None], out=np.zeros_like(mn), where=dmf[:, None] != 0)), 0, 63).astype(np.uint8)
+    eff = df[:, None] * sc
+    q = np.clip(np.round(np.divide(b + (dmf[:, None] * m)[..., None], eff[..., None], out=np.zeros_like(b), where=eff[..., None] != 0)), 0, 15).astype(np.uint8)
+    out = np.zeros((len(b), 144), dtype=np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
+    out[:, 4:8] = (sc[:, :4] & 63) | ((sc[:, 4:] >> 4) << 6)
+    out[:, 8:12] = (m[:, :4] & 63) | ((m[:, 4:] >> 4) << 6)
+    out[:, 12:16] = (sc[:, 4:] & 0xF) | ((m[:, 4:] & 0xF) << 4)
+    qq = q.reshape(-1, 4, 2, 32)
+    out[:, 16:144] = (qq[:, :, 0] | (qq[:, :, 1] << 4)).reshape(-1, 128)
+    return out.tobytes()
+
+
+def quantize_q6_k(w: np.ndarray) -> bytes:
+    """A plain Q6_K encoder (absolute maximum per 16 weights)."""
+    b = w.reshape(-1, 16, 16).astype(np.float32)
+    amax = np.abs(b).max(-1)
+    d = (amax.max(-1) / (127.0 * 31.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    sc = np.clip(np.round(np.divide(amax / 31.0, df[:, None], out=np.zeros_like(amax), where=df[:, None] != 0)), -128, 127).astype(np.int8)
+    eff = df[:, None] * sc.astype(np.float32)
+    q = (np.clip(np.round(np.divide(b, eff[..., None], out=np.zeros_like(b), where=eff[..., None] != 0)), -32, 31) + 32).astype(np.uint8)
+    q = q.reshape(-1, 2, 4, 32)                                           # [blocks, half, quarter, l]
+    out = np.zeros((len(b), 210), dtype=np.uint8)
+    ql = np.concatenate([(q[:, :, 0] & 0xF) | ((q[:, :, 2] & 0xF) << 4), (q[:, :, 1] & 0xF) | ((q[:, :, 3] & 0xF) << 4)], axis=2)   # [blocks, 2, 64]
+    qh = (q[:, :, 0] >> 4) | ((q[:, :, 1] >> 4) << 2) | ((q[:, :, 2] >> 4) << 4) | ((q[:, :, 3] >> 4) << 6)
+    out[:, 0:128] = ql.reshape(-1, 128)
+    out[:, 128:192] = qh.reshape(-1, 64)
+    out[:, 192:208] = sc.view(np.uint8)
+    out[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    return out.tobytes()
+
+
 def write_gguf(path: str, meta: Dict[str, object], tensors: Dict[str, Tuple[np.ndarray, int]]) -> None:
-    """tensors: name -> (fp32 array, GGUF type among F32, F16, Q8_0, Q4_0)."""
+    """tensors: name -> (fp32 array, GGUF type among F32, F16, Q8_0, Q4_0, Q4_K, Q6_K)."""
     def s(x: str) -> bytes:
         b = x.encode()
         return struct.pack("<Q", len(b)) + b
@@ -209,7 +336,7 @@ def write_gguf(path: str, meta: Dict[str, object], tensors: Dict[str, Tuple[np.n
     for name, (arr, ttype) in tensors.items():
         a = np.ascontiguousarray(arr, dtype=np.float32)
         blob = {F32: lambda: a.tobytes(), F16: lambda: a.astype(np.float16).tobytes(), Q8_0: lambda: quantize_q8_0(a),
-                Q4_0: lambda: quantize_q4_0(a)}[ttype]()
+                Q4_0: lambda: quantize_q4_0(a), Q4_K: lambda: quantize_q4_k(a), Q6_K: lambda: quantize_q6_k(a)}[ttype]()
         head += s(name) + struct.pack("<I", a.ndim) + b"".join(struct.pack("<Q", d) for d in reversed(a.shape)) + struct.pack("<IQ", ttype, off)
         blobs.append(blob)
         off += (len(blob) + 31) // 32 * 32

@@ -21,7 +21,7 @@ import torch
 
 from ..utils import onnx_proto as op
 from .arch import ArchConfig
-from .builder import dequantize_int4_block32, dequantize_mxfp4, quantize_int4_block32, random_tensor, tensor_seed, weight_shapes
+from .builder import dequantize_block, dequantize_int4_block32, dequantize_mxfp4, quantize_int4_block32, random_tensor, tensor_seed, weight_shapes
 from .decoder import DecoderModel, LayerWeights
 
 
@@ -216,14 +216,16 @@ def _linear_weight(g: GraphView, node, dtype, device, rows: Optional[slice] = No
     if node.op_type == "MatMulNBits":
         N, K = int(node.attrs["N"]), int(node.attrs["K"])
         bs = int(node.attrs.get("block_size", 32))
-        if int(node.attrs.get("bits", 4)) != 4:
-            raise NotImplementedError("MatMulNBits: only 4-bit weights are supported")
+        bits = int(node.attrs.get("bits", 4))
+        if bits not in (4, 8):
+            raise NotImplementedError("MatMulNBits: only 4- and 8-bit weights are supported")
         loc = g.lm.info(node.inputs[1]).ext_location or ""
         src_dev = device if loc.startswith("synthetic:") else "cpu"
         q = g.tensor(node.inputs[1], device=src_dev)
         s = g.tensor(node.inputs[2], device=src_dev)
         zp = g.tensor(node.inputs[3], device=src_dev) if len(node.inputs) > 3 and node.inputs[3] else None
-        w = dequantize_int4_block32(q, s, zp, N, K, bs)
+        # 8-bit nodes (the promoted ones of a mixed-precision export) are expanded to the compute type at load
+        w = dequantize_int4_block32(q, s, zp, N, K, bs) if bits == 4 else dequantize_block(q, s, zp, N, K, bs, 8)
     elif node.op_type == "MatMulBlockQuantizedFp8Weight":
         # FP8 e4m3 weight [N, K] with one fp32 scale per output row (or one for the matrix), expanded at load: the GEMMs run
         # in bf16 on the dequantised weight; the optional activation scale (input 3) is not used

@@ -75,3 +75,103 @@ def test_gguf_file_exports_and_matches_the_dense_model(tmp_path):
     g.append_tokens(ids)
     want = dense_logits(model.arch, sd, ids[0].tolist())[-1].numpy()
     np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
+
+
+# ---------------------------------------------------------------------------------------------- k-quants
+def _scalar_k(block: bytes, ttype: int):
+    """One super-block decoded element by element, as a plain transcription of the k-quant definitions (the vectorised reader is
+    checked against this on random bytes)."""
+    import struct
+    from onnxruntime_genai_b200.models import gguf_reader as G
+    b = list(block)
+    f16 = lambda lo: struct.unpack("<e", bytes(b[lo:lo + 2]))[0]
+
+    def scale_min(j, sc):
+        if j < 4:
+            return sc[j] & 63, sc[j + 4] & 63
+        return (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4), (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4)
+
+    y = []
+    if ttype == G.Q4_K:
+        d, dmin, sc, q = f16(0), f16(2), b[4:16], b[16:144]
+        for j in range(4):
+            s1, m1 = scale_min(2 * j, sc)
+            s2, m2 = scale_min(2 * j + 1, sc)
+            y += [d * s1 * (q[32 * j + l] & 0xF) - dmin * m1 for l in range(32)]
+            y += [d * s2 * (q[32 * j + l] >> 4) - dmin * m2 for l in range(32)]
+    elif ttype == G.Q5_K:
+        d, dmin, sc, qh, q = f16(0), f16(2), b[4:16], b[16:48], b[48:176]
+        for j in range(4):
+            s1, m1 = scale_min(2 * j, sc)
+            s2, m2 = scale_min(2 * j + 1, sc)
+            y += [d * s1 * ((q[32 * j + l] & 0xF) + (16 if qh[l] & (1 << (2 * j)) else 0)) - dmin * m1 for l in range(32)]
+            y += [d * s2 * ((q[32 * j + l] >> 4) + (16 if qh[l] & (2 << (2 * j)) else 0)) - dmin * m2 for l in range(32)]
+    elif ttype == G.Q6_K:
+        ql, qh, d = b[0:128], b[128:192], f16(208)
+        sc = [v - 256 if v > 127 else v for v in b[192:208]]
+        for n in range(2):
+            out = [0.0] * 128
+            for l in range(32):
+                i = l // 16
+                q1 = ((ql[64 * n + l] & 0xF) | (((qh[32 * n + l] >> 0) & 3) << 4)) - 32
+                q2 = ((ql[64 * n + l + 32] & 0xF) | (((qh[32 * n + l] >> 2) & 3) << 4)) - 32
+                q3 = ((ql[64 * n + l] >> 4) | (((qh[32 * n + l] >> 4) & 3) << 4)) - 32
+                q4 = ((ql[64 * n + l + 32] >> 4) | (((qh[32 * n + l] >> 6) & 3) << 4)) - 32
+                out[l], out[l + 32] = d * sc[8 * n + i] * q1, d * sc[8 * n + i + 2] * q2
+                out[l + 64], out[l + 96] = d * sc[8 * n + i + 4] * q3, d * sc[8 * n + i + 6] * q4
+            y += out
+    elif ttype == G.Q2_K:
+        scales, q, d, dmin = b[0:16], b[16:80], f16(80), f16(82)
+        i = 0
+        for n in range(2):
+            for j in range(4):
+                for part in range(2):
+                    s = scales[i]; i += 1
+                    y += [d * (s & 0xF) * ((q[32 * n + 16 * part + l] >> (2 * j)) & 3) - dmin * (s >> 4) for l in range(16)]
+    elif ttype == G.Q3_K:
+        hm, q, sb, d = b[0:32], b[32:96], b[96:108], f16(108)
+        sc = [0] * 16
+        for k in range(4):
+            sc[k] = (sb[k] & 0xF) | (((sb[8 + k] >> 0) & 3) << 4)
+            sc[4 + k] = (sb[4 + k] & 0xF) | (((sb[8 + k] >> 2) & 3) << 4)
+            sc[8 + k] = (sb[k] >> 4) | (((sb[8 + k] >> 4) & 3) << 4)
+            sc[12 + k] = (sb[4 + k] >> 4) | (((sb[8 + k] >> 6) & 3) << 4)
+        i, m = 0, 1
+        for n in range(2):
+            for j in range(4):
+                for part in range(2):
+                    dl = d * (sc[i] - 32); i += 1
+                    y += [dl * (((q[32 * n + 16 * part + l] >> (2 * j)) & 3) - (0 if hm[16 * part + l] & m else 4)) for l in range(16)]
+                m <<= 1
+    return np.asarray(y, dtype=np.float32)
+
+
+@pytest.mark.parametrize("name", ["Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K"])
+def test_k_quant_blocks_decode_like_their_definition(name):
+    from onnxruntime_genai_b200.models import gguf_reader as G
+    ttype = getattr(G, name)
+    per, nbytes = G._BLOCK[ttype]
+    rng = np.random.RandomState(ttype)
+    raw = rng.randint(0, 256, size=(5, nbytes)).astype(np.uint8)
+    # the fp16 fields must be finite: overwrite them with small numbers
+    for off in {G.Q4_K: (0, 2), G.Q5_K: (0, 2), G.Q6_K: (208,), G.Q2_K: (80, 82), G.Q3_K: (108,)}[ttype]:
+        raw[:, off:off + 2] = np.asarray(rng.uniform(0.001, 0.02, size=5), dtype=np.float16).view(np.uint8).reshape(5, 2)
+    got = G.dequantize(raw.reshape(-1), ttype, 5 * per).reshape(5, per)
+    for i in range(5):
+        np.testing.assert_allclose(got[i], _scalar_k(raw[i].tobytes(), ttype), rtol=1e-6, atol=1e-6)
+
+
+def test_k_quant_file_loads(tmp_path):
+    """A GGUF file whose projections are Q4_K and whose output matrix is Q6_K (the usual Q4_K_M mix) exports and runs close to
+    the float weights it was written from."""
+    from onnxruntime_genai_b200.models import gguf_reader as G
+    w = (np.random.RandomState(2).randn(8, 512) * 0.05).astype(np.float32)
+    for ttype, fn, tol in ((G.Q4_K, G.quantize_q4_k, 0.02), (G.Q6_K, G.quantize_q6_k, 0.005)):
+        back = G.dequantize(np.frombuffer(fn(w), dtype=np.uint8), ttype, w.size).reshape(w.shape)
+        assert np.abs(back - w).max() < tol
+    path = str(tmp_path / "k.gguf")
+    G.write_gguf(path, {"general.architecture": "llama"}, {"a": (w, G.Q4_K), "b": (w[:2], G.Q6_K), "c": (w[:1, :32], G.F32)})
+    meta, tensors = G.read_gguf(path)
+    assert meta["general.architecture"] == "llama" and tuple(tensors["a"].shape) == (8, 512)
+    assert float((tensors["a"] - torch.from_numpy(w)).abs().max()) < 0.02 and float((tensors["b"] - torch.from_numpy(w[:2])).abs().max()) < 0.005
+    assert torch.equal(tensors["c"], torch.from_numpy(w[:1, :32]))

@@ -162,3 +162,61 @@ def test_modelopt_checkpoint_is_carried_into_the_block_quantised_ops(fmt, tmp_pa
     g.append_tokens(ids)
     want = dense_logits(model.arch, dense, ids[0].tolist())[-1].numpy()
     np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=2e-3, atol=3e-4)
+
+
+def test_int4_methods_and_mixed_precision_placement(tmp_path):
+    """`default` / `rtn` / `k_quant` and the int8 placements of the reference's builder (builders/quant_config.py:168-173,
+    285-290; builders/base.py:1211-1254): k_quant lowers the weighted block error, `k_quant_mixed` writes 8-bit MatMulNBits
+    nodes for the LM head and the promoted layers' qkv / down projections, and the promoted export tracks the float model
+    more closely than the plain int4 one."""
+    import copy
+    import numpy as np
+    import onnxruntime_genai_b200 as og
+    from dense_reference import logits as dense_logits
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import (dequantize_block, export_model, mixed_precision_layers, quantize_block,
+                                                      random_state_dict)
+    from onnxruntime_genai_b200.utils.onnx_proto import decode_model
+
+    torch.manual_seed(0)
+    w = torch.randn(96, 256) * 0.05
+    w[:, ::29] *= 5
+    wt = (w.view(96, 8, 32).abs() + w.view(96, 8, 32).pow(2).mean(-1, keepdim=True).sqrt()).view(96, 256)
+    for bits in (4, 8):
+        err = {}
+        for method in ("default", "rtn", "k_quant"):
+            q, s, zp = quantize_block(w, bits, False, method)
+            assert q.shape == (96, 8, 16 if bits == 4 else 32)
+            err[method] = float((wt * (dequantize_block(q, s, zp, 96, 256, 32, bits) - w) ** 2).sum())
+        assert err["rtn"] == err["default"] and err["k_quant"] < err["default"]
+    with pytest.raises(ValueError):
+        quantize_block(w, 4, False, "gptq")
+    assert mixed_precision_layers(8) == [0, 3, 6, 7] and mixed_precision_layers(32)[:5] == [0, 1, 2, 3, 6]
+
+    arch = ArchConfig(model_type="llama", vocab_size=160, hidden_size=64, num_layers=8, num_heads=4, num_kv_heads=2, head_dim=16,
+                      intermediate_size=128, context_length=64, bos_token_id=0, eos_token_id=1, pad_token_id=1)
+    sd = random_state_dict(arch, seed=3, std=0.08)
+    prompt = np.random.RandomState(1).randint(2, 160, size=12).tolist()
+    want = dense_logits(arch, sd, prompt)[-1].numpy()
+    errs = {}
+    for algo in ("default", "k_quant_mixed"):
+        d = str(tmp_path / algo)
+        export_model(copy.deepcopy(arch), d, "int4", "cpu", state_dict=sd, int4_algo_config=algo)
+        nodes = {n.name: n for n in decode_model(open(os.path.join(d, "model.onnx"), "rb").read()).nodes if n.op_type == "MatMulNBits"}
+        eight = sorted(name for name, n in nodes.items() if int(n.attrs["bits"]) == 8)
+        if algo == "default":
+            assert not eight
+        else:
+            assert "/lm_head/MatMul_Q8" in eight
+            assert {f"/model/layers.{i}/attn/qkv_proj/MatMul_Q8" for i in (0, 3, 6, 7)} <= set(eight)
+            assert {f"/model/layers.{i}/mlp/down_proj/MatMul_Q8" for i in (0, 3, 6, 7)} <= set(eight)
+            assert "/model/layers.1/attn/qkv_proj/MatMul_Q8" not in eight and "/model/layers.0/mlp/gate_up_proj/MatMul_Q8" not in eight
+        model = og.Model(d)
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=32)
+        g = og.Generator(model, p)
+        g.append_tokens(np.asarray([prompt], dtype=np.int32))
+        errs[algo] = float(np.abs(g.get_logits().reshape(-1) - want).mean())
+    assert errs["k_quant_mixed"] < errs["default"]
+    with pytest.raises(ValueError):
+        export_model(copy.deepcopy(arch), str(tmp_path / "bad"), "int4", "cpu", state_dict=sd, int4_algo_config="awq_last")
