@@ -9,6 +9,8 @@ repeats each scale / zero point r times and loses nothing.
 
     AWQ  (quant_method "awq"):  qweight int32 [K, N/8], qzeros int32 [K/g, N/8], scales fp16 [K/g, N];
                                 the eight nibbles of a word hold output features in the order 0 2 4 6 1 3 5 7
+    Quark (quant_method "quark"): dense layers packed like AWQ.
+    Olive (quant_method "olive"): qweight uint8 [N, K/2], scales [N, K/g], qzeros uint8 [N, K/g/2], unsigned, per-layer overrides.
     GPTQ (quant_method "gptq"): qweight int32 [K/8, N] (eight consecutive input features per word),
                                 qzeros int32 [K/g, N/8] (sequential nibbles; stored minus one by the v1 format),
                                 scales fp16 [K/g, N], g_idx int32 [K] (group of each input feature)
@@ -166,10 +168,37 @@ def unpack_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
     K = q.shape[0]
     if group <= 0:
         group = K
-    if g_idx is not None and not torch.equal(g_idx.to(torch.int64), torch.arange(K) // group):
-        raise NotImplementedError("GPTQ act-order checkpoints (a permuted g_idx) are not supported")
     z = (_nibbles(qzeros).reshape(qzeros.shape[0], -1).to(torch.int16) + zero_offset) & 0xF    # v1 stores zero - 1
+    if g_idx is not None and not torch.equal(g_idx.to(torch.int64), torch.arange(K) // group):
+        # act-order (desc_act): input feature k belongs to group g_idx[k], groups are no longer runs of consecutive features, so
+        # the codes cannot be carried into block-32 tensors.  The weight is reconstructed exactly as the checkpoint defines it
+        # and handed on as a float tensor (an int4 export quantises it again with the exporter's own method).
+        g = g_idx.to(torch.int64)
+        w_kn = (q.float() - z[:, :N].float()[g]) * scales.float()[g]
+        return w_kn.t().contiguous()
     return _to_block32(q, scales, z[:, :N], group)
+
+
+def unpack_olive(qweight: torch.Tensor, qzeros: Optional[torch.Tensor], scales: torch.Tensor, group: int) -> QuantizedLinear:
+    """Olive's layout is the MatMulNBits one before blocking: qweight uint8 [N, K/2] (low nibble = even input feature), scales
+    [N, K/group], qzeros uint8 [N, K/group/2] packed the same way, unsigned codes (reference: quantized_model.py:1598-1648)."""
+    N = qweight.shape[0]
+    qb = qweight.to(torch.uint8)
+    q = torch.stack([qb & 0xF, qb >> 4], dim=-1).reshape(N, -1)                    # [N, K]
+    K = q.shape[1]
+    if group <= 0:
+        group = K
+    if group % 32 or K % group:
+        raise NotImplementedError(f"group size {group} is not a multiple of 32 dividing K = {K}")
+    G = K // group
+    if qzeros is not None and qzeros.numel():
+        zb = qzeros.to(torch.uint8).reshape(N, -1)
+        z = torch.stack([zb & 0xF, zb >> 4], dim=-1).reshape(N, -1)[:, :G]
+    else:
+        z = torch.full((N, G), 8, dtype=torch.uint8)
+    r = group // 32
+    return QuantizedLinear(q.contiguous(), scales.float().reshape(N, G).repeat_interleave(r, dim=1).contiguous(),
+                           z.repeat_interleave(r, dim=1).contiguous())
 
 
 def convert_state_dict(sd: Dict[str, torch.Tensor], quant_config: dict) -> Dict[str, object]:
@@ -179,18 +208,22 @@ def convert_state_dict(sd: Dict[str, torch.Tensor], quant_config: dict) -> Dict[
         return convert_modelopt(sd)
     bits = int(quant_config.get("bits", quant_config.get("w_bit", 4)))
     group = int(quant_config.get("group_size", quant_config.get("q_group_size", 128)))
-    if method not in ("awq", "gptq") or bits != 4:
-        raise NotImplementedError(f"quantised checkpoint of method {method!r} with {bits} bits is not supported (awq / gptq, 4 bits)")
-    if method == "gptq" and quant_config.get("desc_act"):
-        raise NotImplementedError("GPTQ act-order checkpoints (desc_act) are not supported")
+    if method not in ("awq", "gptq", "quark", "olive") or bits != 4:
+        raise NotImplementedError(f"quantised checkpoint of method {method!r} with {bits} bits is not supported (awq / gptq / quark / olive, 4 bits)")
+    overrides = (quant_config.get("overrides") or {}) if method == "olive" else {}
     # GPTQ v1 stores zero points minus one; the v2 format (checkpoint_format "gptq_v2") stores them as they are
     zero_offset = 0 if str(quant_config.get("checkpoint_format", "gptq")).lower() == "gptq_v2" else 1
     out: Dict[str, object] = {}
     for k, v in sd.items():
         if k.endswith(".qweight"):
             base = k[: -len(".qweight")]
-            if method == "awq":
+            if method in ("awq", "quark"):       # Quark's dense layers use AWQ's packing (reference: quantized_model.py:802-868)
                 out[base + ".weight"] = unpack_awq(v, sd[base + ".qzeros"], sd[base + ".scales"], group)
+            elif method == "olive":
+                ov = overrides.get(base, {})
+                if int(ov.get("bits", 4)) != 4:
+                    raise NotImplementedError(f"{base}: Olive override to {ov['bits']} bits is not supported")
+                out[base + ".weight"] = unpack_olive(v, sd.get(base + ".qzeros"), sd[base + ".scales"], int(ov.get("group_size", group)))
             else:
                 out[base + ".weight"] = unpack_gptq(v, sd[base + ".qzeros"], sd[base + ".scales"], group, sd.get(base + ".g_idx"), zero_offset)
         elif k.endswith((".qzeros", ".scales", ".g_idx")) and k.rsplit(".", 1)[0] + ".qweight" in sd:

@@ -41,8 +41,7 @@ def test_awq_and_gptq_words_round_trip(group):
     one = QuantizedLinear(torch.zeros(8, 32, dtype=torch.uint8), torch.ones(8, 1), torch.zeros(8, 1, dtype=torch.uint8))
     one.q[2, 0] = 5
     assert int(pack_awq(one, 32)[0][0, 0]) == 5 << 4
-    with pytest.raises(NotImplementedError):
-        unpack_gptq(qw, qz, sc, group, torch.flip(g_idx, [0]), 1)
+    assert isinstance(unpack_gptq(qw, qz, sc, group, torch.flip(g_idx, [0]), 1), torch.Tensor)    # act-order: a float weight
     with pytest.raises(NotImplementedError):
         convert_state_dict({}, {"quant_method": "awq", "bits": 8})
 
@@ -220,3 +219,40 @@ def test_int4_methods_and_mixed_precision_placement(tmp_path):
     assert errs["k_quant_mixed"] < errs["default"]
     with pytest.raises(ValueError):
         export_model(copy.deepcopy(arch), str(tmp_path / "bad"), "int4", "cpu", state_dict=sd, int4_algo_config="awq_last")
+
+
+def test_gptq_act_order_quark_and_olive_layouts():
+    """GPTQ with a permuted g_idx (desc_act) is reconstructed exactly as a float weight; a Quark checkpoint's dense layers read
+    like AWQ; Olive's [N, K/2] bytes carry over unchanged (reference: quantized_model.py GPTQModel / QuarkModel / OliveModel)."""
+    from onnxruntime_genai_b200.models.quantized_checkpoint import unpack_olive
+    g = torch.Generator().manual_seed(4)
+    K, N, group = 128, 16, 32
+    q = torch.randint(0, 16, (N, K), generator=g, dtype=torch.uint8)
+    scales = torch.rand(N, K // 32, generator=g) * 0.02 + 0.001
+    zp = torch.randint(0, 16, (N, K // 32), generator=g, dtype=torch.uint8)
+    ql = QuantizedLinear(q, scales, zp)
+    # ---- GPTQ act-order: the same tensors, but feature k is stored at position perm[k] with its group recorded in g_idx
+    qweight, qzeros, sc, _ = pack_gptq(ql, group)
+    perm = torch.randperm(K, generator=g)
+    g_idx = (perm // group).to(torch.int32)                       # position p holds feature perm[p], whose group is perm[p] // group
+    q_perm = q[:, perm]                                           # columns reordered the way an act-order file stores them
+    qw_perm = pack_gptq(QuantizedLinear(q_perm.contiguous(), scales, zp), group)[0]
+    sd = {"l.qweight": qw_perm, "l.qzeros": qzeros, "l.scales": sc, "l.g_idx": g_idx, "other": torch.ones(2)}
+    out = convert_state_dict(sd, {"quant_method": "gptq", "bits": 4, "group_size": group, "desc_act": True})
+    w = out["l.weight"]
+    assert isinstance(w, torch.Tensor) and tuple(w.shape) == (N, K)
+    torch.testing.assert_close(w, ql.float()[:, perm], rtol=1e-3, atol=1e-5)       # exact up to the fp16 scales of the file
+    # ---- Quark: AWQ packing under another method name
+    aw, az, asc = pack_awq(ql, group)
+    got = convert_state_dict({"l.qweight": aw, "l.qzeros": az, "l.scales": asc}, {"quant_method": "quark", "bits": 4, "group_size": group})["l.weight"]
+    assert torch.equal(got.q, q) and torch.equal(got.zp, zp)
+    # ---- Olive: [N, K/2] bytes, low nibble first, zero points packed likewise, a per-layer group size override
+    ob = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+    oz = (zp[:, 0::2] | (zp[:, 1::2] << 4)).contiguous()
+    ol = unpack_olive(ob, oz, scales, 32)
+    assert torch.equal(ol.q, q) and torch.equal(ol.zp, zp) and torch.equal(ol.scales, scales)
+    got = convert_state_dict({"m.qweight": ob, "m.qzeros": oz, "m.scales": scales},
+                             {"quant_method": "olive", "bits": 4, "group_size": 128, "overrides": {"m": {"group_size": 32}}})["m.weight"]
+    torch.testing.assert_close(got.float(), ql.float())
+    with pytest.raises(NotImplementedError):
+        convert_state_dict({"m.qweight": ob, "m.scales": scales}, {"quant_method": "olive", "bits": 4, "group_size": 32, "overrides": {"m": {"bits": 8}}})
