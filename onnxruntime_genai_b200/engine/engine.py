@@ -767,7 +767,14 @@ class Engine:
                             rq.t_first = now
                     gp = self._guidance.get(rid)
                     if gp is not None:
-                        gp.commit_tokens(np.asarray([toks[i]], dtype=np.int32))
+                        committed = [int(toks[i])]
+                        if accepted is not None and int(accepted[i]) > 0:
+                            # the accepted drafts still sit at the tail of the request's tokens (the commit below trims the rest)
+                            k = e.request.draft_count
+                            all_toks = e.request.tokens()
+                            committed = [int(t) for t in all_toks[len(all_toks) - k: len(all_toks) - k + int(accepted[i])]] + committed
+                        for t in committed:           # (commit_tokens takes one token per batch row)
+                            gp.commit_tokens(np.asarray([t], dtype=np.int32))
             self.t_last_step = now
             if accepted is not None:
                 self.last_outcome = self.core.commit_speculative(np.ascontiguousarray(accepted, dtype=np.int32),

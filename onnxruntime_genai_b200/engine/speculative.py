@@ -63,7 +63,7 @@ class EngineSpeculator:
         if nat.is_prefill or nat.pending != 1 or nat.draft_count or nat.status not in (native.RequestStatus.Active, native.RequestStatus.Assigned):
             return False
         eng = self.engine
-        if nat.id in eng._with_processors or nat.id in eng._guidance:
+        if nat.id in eng._with_processors:
             return False
         need = nat.num_tokens + self.max_k
         return len(nat.blocks()) * eng.block_size >= need and nat.num_tokens + 1 < nat.options.max_length
@@ -150,6 +150,32 @@ class EngineSpeculator:
         nxt = np.zeros(n, dtype=np.int32)
         def is_greedy(o):
             return (not o.do_sample) or o.top_k == 1 or o.temperature == 0
+        # Constrained requests: row 0 of an entry was masked by the engine with the grammar's current state; rows 1..k take the
+        # masks of a cloned cursor that walks the drafts (a draft the grammar forbids is masked in its own row, hence rejected
+        # there, and the rows after it are never consulted)
+        guided = self.engine._guidance
+        if guided:
+            for i, e in enumerate(plan.entries):
+                gp = guided.get(e.request.id) if e.samples else None
+                k = e.request.draft_count if (gp is not None and not e.is_prefill) else 0
+                if k == 0:
+                    continue
+                toks = e.request.tokens()
+                drafts = [int(x) for x in toks[len(toks) - k:]]
+                cursor = gp.clone()
+                for j in range(1, k + 1):
+                    prev = cursor.compute_mask()
+                    d = drafts[j - 1]
+                    if not (int(prev[0, d >> 5]) >> (d & 31)) & 1:
+                        break
+                    cursor.commit_tokens(np.asarray([d], dtype=np.int32))
+                    mask = cursor.compute_mask()
+                    row = logits[row_of[i] + j: row_of[i] + j + 1]
+                    if row.is_cuda:
+                        ops.logits_bitmask(row, torch.from_numpy(mask.copy()).to(row.device))
+                    else:
+                        bits = np.unpackbits(mask.view(np.uint8), bitorder="little")[:row.shape[1]].astype(bool)
+                        row[0, torch.from_numpy(~bits)] = float("-inf")
         greedy = [i for i, e in enumerate(plan.entries) if e.samples and is_greedy(e.request.options)]
         sampled = [i for i, e in enumerate(plan.entries) if e.samples and not is_greedy(e.request.options)]
         am = None

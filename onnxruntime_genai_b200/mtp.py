@@ -135,15 +135,15 @@ class _MtpStrategy(_SpecBase):
 
 
 class MtpGenerator(Generator):
-    """Generator whose proposals come from an MTP head (greedy verification)."""
+    """Generator whose proposals come from an MTP head.  The head proposes its argmax; verification is greedy, or with
+    do_sample the deterministic-proposal form of rejection sampling (accept d with probability p_target(d), otherwise draw the
+    correction from p_target without d; reference: src/mtp_generator.cpp:638, 891)."""
 
     def __init__(self, model: Model, head_dir: str, params: GeneratorParams):
         super().__init__(model, params)
         so = self.search_opts
         if so["batch_size"] != 1 or so["num_beams"] != 1:
             raise RuntimeError("MtpGenerator requires batch_size 1 and num_beams 1")
-        if self.method != "greedy":
-            raise RuntimeError("MtpGenerator verifies greedily: do_sample must be False")
         self.head = MtpHead(model, head_dir)
         spec = dict(params.speculative)
         self._strategy = _MtpStrategy(self, self.head, spec)

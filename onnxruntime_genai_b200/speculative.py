@@ -35,13 +35,14 @@ class _SpecBase:
             raise RuntimeError("speculative decoding requires batch_size 1")
         if so["num_beams"] != 1:
             raise RuntimeError("speculative decoding does not support beam search")
-        if gen._guidance is not None:
-            raise RuntimeError("speculative decoding cannot be combined with guidance in this build")
+        if gen._guidance is not None and gen._guidance.ff:
+            raise RuntimeError("speculative decoding cannot be combined with guidance fast-forward tokens")
         self.gen = gen
         self.max_k = int(spec.get("max_draft_tokens", 4))
         self.adaptive = native.AdaptiveK(self.max_k, int(spec.get("min_adaptive_k", 0)))
         self.cooldown = native.ZeroAcceptCooldown(bool(spec.get("cooldown", False)))
         self.pending: deque = deque()
+        self._grammar_synced = False     # True while a plain step commits its token to the grammar itself
         self.s = dict(rounds=0, proposed=0, evaluated=0, accepted=0, committed=0, bonus=0, corrections=0, standard_steps=0,
                       cooldown_skips=0, empty_proposals=0, propose_ms=0.0, verify_ms=0.0)
 
@@ -74,6 +75,8 @@ class _SpecBase:
     def _surface(self, token: int):
         g = self.gen
         g.search.commit_tokens(np.asarray([token], dtype=np.int32))
+        if g._guidance is not None and not self._grammar_synced:
+            g._guidance.commit_tokens(np.asarray([token], dtype=np.int32))
         if g.search.is_done:
             self.pending.clear()
 
@@ -120,7 +123,7 @@ class _SpecBase:
 
     def _plain_step(self):
         g = self.gen
-        g._standard_step()
+        g._standard_step()                # (applies the grammar mask and advances the grammar itself)
         self.s["standard_steps"] += 1
         self.after_round([int(g.search.next_tokens()[0])], 0, 0)
 
@@ -135,6 +138,33 @@ class _SpecBase:
             logits, _ = st.run([[int(seq[-1])] + list(draft)], want_all_logits=True)
         so = g.search_opts
         penalties = so["min_length"] > 0 or so["repetition_penalty"] != 1.0 or so["no_repeat_ngram_size"] > 0
+        if g._guidance is not None:
+            # Constrained decoding inside the round (reference: src/speculative_decoding_strategy.cpp:532, 944-1270): a CLONE of
+            # the grammar cursor walks the draft; row i is masked with what the grammar allows after the prefix + draft[:i].  A draft
+            # token the grammar forbids ends the walk: its row's mask rejects it, the rows after it are never consulted.  The
+            # real cursor only advances when the committed tokens are surfaced.
+            cursor = g._guidance.clone()
+            logits = logits.float().clone()
+            for i in range(k + 1):
+                mask = cursor.compute_mask()                      # [1, words]
+                row = logits[i:i + 1]
+                if row.is_cuda:
+                    ops.logits_bitmask(row, torch.from_numpy(mask).to(row.device))
+                else:
+                    bits = np.unpackbits(mask.view(np.uint8), bitorder="little")[:row.shape[1]].astype(bool)
+                    row[0, torch.from_numpy(~bits)] = float("-inf")
+                if i == k:
+                    break
+                allowed = bool((int(mask[0, draft[i] >> 5]) >> (draft[i] & 31)) & 1)
+                if not allowed:
+                    k = i                                          # rows beyond i belong to a continuation the grammar excludes
+                    draft, dists = draft[:i + 1], dists[:i + 1]
+                    logits = logits[:i + 1]
+                    # verification sees k = i + 1 drafts with i + 1 rows: give it a last row (never reached: draft i is rejected)
+                    logits = torch.cat([logits, logits[-1:]], dim=0)
+                    k = i + 1
+                    break
+                cursor.commit_tokens(np.asarray([draft[i]], dtype=np.int32))
         if g.method == "greedy" and not penalties:
             if logits.is_cuda:
                 am = ops.argmax(logits)

@@ -256,3 +256,53 @@ def test_engine_speculation_with_sampling_is_reproducible_and_valid(spec_dir, tm
     a, _ = _engine_run(model, ENGINE_PROMPTS[:3], 16, do_sample=True, top_k=5, temperature=0.9)
     b, _ = _engine_run(model, ENGINE_PROMPTS[:3], 16, do_sample=True, top_k=5, temperature=0.9)
     assert a == b and all(len(o) == 16 or 96 in o for o in a)
+
+
+def test_engine_speculation_with_grammar_equals_plain_constrained_decoding(tmp_path):
+    """Requests under a JSON schema are given n-gram proposals too: rows after the first are masked from a cloned grammar cursor
+    and the grammar advances over the accepted drafts; greedy output equals the engine's plain constrained output."""
+    import json
+    import onnxruntime_genai_b200 as og
+    from helpers import tiny_model_dir
+    d, _ = tiny_model_dir(str(tmp_path / "m"), std=0.3)
+    schema = json.dumps({"type": "object", "properties": {"tags": {"type": "array", "items": {"enum": ["a", "b"]}, "maxItems": 8}},
+                         "required": ["tags"], "additionalProperties": False})
+
+    def run(spec):
+        cfg = og.Config(d)
+        if spec:
+            cfg.overlay(json.dumps({"speculative": {"ngram_size": 2, "max_draft_tokens": 3}}))
+        model = og.Model(cfg)
+        tok = og.Tokenizer(model)
+        eng = og.Engine(model)
+        reqs = []
+        for text in ('{"tags": ["a", "b", "a", "b", "a"]} {"tags": ["a", "b", "a", "b", "a"]} ', '{"tags": ["b", "b"]} '):
+            p = og.GeneratorParams(model)
+            ids = tok.encode(text)
+            p.set_search_options(max_length=len(ids) + 60, do_sample=False)
+            p.set_guidance("json_schema", schema)
+            r = og.Request(p)
+            r.add_tokens(ids)
+            eng.add_request(r)
+            reqs.append(r)
+        outs = [[] for _ in reqs]
+        for _ in range(400):
+            if not eng.has_pending_requests():
+                break
+            eng.step()
+            for i, r in enumerate(reqs):
+                while r.has_unseen_tokens():
+                    outs[i].append(r.get_unseen_token())
+        texts = []
+        for o in outs:
+            while o and o[-1] in (0, 1):
+                o.pop()
+            texts.append(tok.decode(np.asarray(o, dtype=np.int32)))
+        return texts, (eng.spec.stats if eng.spec is not None else None)
+
+    plain, _ = run(False)
+    spec, stats = run(True)
+    assert spec == plain
+    for t in spec:
+        assert set(json.loads(t)) == {"tags"}
+    assert stats["rounds"] > 0 and stats["proposed"] > 0

@@ -116,3 +116,37 @@ def test_guidance_errors(model):
     p.set_guidance("json_schema", "{ not json")
     with pytest.raises(Exception):
         og.Generator(model, p)
+
+
+def test_guidance_inside_speculative_rounds(model):
+    """n-gram speculation with a grammar: every verify row is masked with what the grammar allows after the drafts before it
+    (a cloned cursor walks the draft), so greedy speculative decoding gives exactly the constrained greedy text, and sampled
+    verification still only emits text the grammar accepts (reference: src/speculative_decoding_strategy.cpp:944-1270)."""
+    tok = og.Tokenizer(model)
+    schema = json.dumps({"type": "object", "properties": {"name": {"type": "string", "maxLength": 8}, "tags": {"type": "array", "items": {"enum": ["a", "b"]}, "maxItems": 6}},
+                         "required": ["name", "tags"], "additionalProperties": False})
+    prompt = tok.encode('{"name": "ab", "tags": ["a", "b", "a", "b"]} {"name": "ab", "tags": ["a", "b", "a", "b"]} ')
+
+    def run(spec, **search):
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=len(prompt) + 90, **search)
+        p.set_guidance("json_schema", schema)
+        if spec:
+            p.set_speculative_options(ngram_size=2, max_draft_tokens=4)
+        g = og.Generator(model, p)
+        g.append_tokens(np.asarray(prompt, dtype=np.int32))
+        while not g.is_done():
+            g.generate_next_token()
+        out = g.get_sequence(0)[len(prompt):].tolist()
+        while out and out[-1] in (0, 1):
+            out.pop()
+        return out, (g.get_speculative_stats() if spec else {})
+
+    plain, _ = run(False, do_sample=False)
+    spec, stats = run(True, do_sample=False)
+    assert spec == plain
+    assert stats["rounds"] > 0 and stats["proposed"] > 0
+    json.loads(tok.decode(spec))
+    sampled, stats = run(True, do_sample=True, top_k=20, temperature=1.0, random_seed=5)
+    obj = json.loads(tok.decode(sampled))
+    assert set(obj) == {"name", "tags"} and stats["rounds"] > 0
