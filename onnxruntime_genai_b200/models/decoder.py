@@ -19,6 +19,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
+from ..native_loader import native
 from .arch import ArchConfig
 
 
@@ -216,6 +217,7 @@ class DecoderModel:
         self.inter_local = arch.intermediate_size // self.tp.size
         self.active_adapter = None  # name -> used by the LoRA hooks
         self._lora_batch = None     # per-token adapters of the step in flight (models/lora.py::LoraBatch)
+        self._dumping = False
         self.norms_folded = False
         self.fuse_steps = True      # decode-sized steps of a folded model take the five-kernel layer (tests compare both forms)
 
@@ -448,6 +450,18 @@ class DecoderModel:
                 return self.forward(s, kv)
             finally:
                 self._lora_batch = None
+        if native.log_flag("enabled") and not (s.input_ids.is_cuda and torch.cuda.is_current_stream_capturing()):
+            # tensor dumps (flags model_input_values / model_output_shapes / model_output_values / model_logits)
+            from ..utils import debugging
+            if not self._dumping:
+                self._dumping = True
+                try:
+                    debugging.dump_inputs(s)
+                    out = self.forward(s, kv)
+                    debugging.dump_outputs(out, self.last_hidden if isinstance(getattr(self, "last_hidden", None), torch.Tensor) else None)
+                    return out
+                finally:
+                    self._dumping = False
         a = self.arch
         if self._sp_ok(s):
             return self._forward_sp(s, kv)

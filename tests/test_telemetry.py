@@ -45,3 +45,32 @@ def test_model_load_and_generation_events(tmp_path):
     assert last["event"] == "X" and "tokens" not in last and last["n"] == 3
     og.Model(d)
     assert len(open(sink).read().splitlines()) == 3          # disabled again
+
+
+def test_tensor_dumps_follow_the_log_flags(tmp_path):
+    """model_input_values / model_output_shapes / model_output_values: shapes, first and last values and statistics of the step's
+    tensors go to the log callback (reference: src/models/debugging.cpp, src/models/model.cpp:115-130)."""
+    import numpy as np
+    import torch
+    import onnxruntime_genai_b200 as og
+    from helpers import tiny_model_dir
+    from onnxruntime_genai_b200.utils.debugging import describe
+    text = describe("x", torch.tensor([1.0, float("nan"), -3.0, 2.0]))
+    assert "float32[4]" in text and "NON-FINITE: first at [1]" in text and "min -3 at [2]" in text and "max 2 at [3]" in text
+    d, _ = tiny_model_dir(str(tmp_path / "m"), std=0.3)
+    model = og.Model(d)
+    lines = []
+    og.set_log_callback(lines.append)
+    og.set_log_options(enabled=True, model_input_values=True, model_output_shapes=True, model_output_values=True)
+    try:
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=12, do_sample=False)
+        g = og.Generator(model, p)
+        g.append_tokens(np.asarray([[5, 6, 7]], dtype=np.int32))
+        g.generate_next_token()
+    finally:
+        og.set_log_options(enabled=False, model_input_values=False, model_output_shapes=False, model_output_values=False)
+        og.set_log_callback(None)
+    joined = "\n".join(lines)
+    assert "input_ids: int32[3]" in joined and "values: 5, 6, 7" in joined
+    assert "logits: float32[1, 384] on cpu" in joined and "stddev" in joined
