@@ -73,4 +73,5 @@ def test_tensor_dumps_follow_the_log_flags(tmp_path):
         og.set_log_callback(None)
     joined = "\n".join(lines)
     assert "input_ids: int32[3]" in joined and "values: 5, 6, 7" in joined
-    assert "logits: float32[1, 384] on cpu" in joined and "stddev" in joined
+    import re
+    assert re.search(r"logits: float32\[1, \d+\] on cpu", joined) and "stddev" in joined
