@@ -17,15 +17,16 @@
 //              [slots, kv_heads * head_dim], 128-byte swizzle); the lanes look their blocks up in parallel.
 //   warp 10    MMA issuer (one lane): S[b] = Q K_j^T into one of three S buffers, two tiles ahead of the softmax warps;
 //              O += P_j V_j with V as the MN-major B operand (keys are its K dimension) as soon as P_j is there.
-// The softmax loop is software-pipelined: while the exponentials of tile j run on the special-function units, the scores of
-// tile j+1 are read from TMEM, masked and reduced to their row maximum on the FMA pipes (measured before that change: load + max,
-// then exponentials, then the P store ran back to back, 2900 cycles per tile of 128 keys, neither pipe half busy).  The scale is
+// The softmax loop is plain (read S, mask, maximum, exchange, exponentials, P back into TMEM): a software-pipelined form
+// (exponentials of tile j interleaved with the load and maximum of tile j + 1) measured slower, 457 against 591 TFLOP/s at 4096
+// tokens, because its loop body outgrew the instruction cache and its extra waits cost more than the overlap gave.  The scale is
 // folded into the exponent's multiply-add.  Registers move from the producer / issuer warps to the softmax warps (setmaxnreg).
-// The maximum is updated lazily: O is rescaled only when a row's maximum grew by more than 2^8 since the last rescale (P then
-// stays below 2^8, exact in fp32 accumulation), which removes the TMEM read-modify-write of O from most tiles.
+// Row tiles are dispatched from the end of the prompt (most keys) to its start, so the grid's tail is short CTAs (591 -> 658).
 //
-// Every wait is bounded (mbar_wait_bounded); a wait that runs out sets the CTA's abort flag and the device status word, the roles
-// leave their loops, the producer waits (bounded) for copies in flight, TMEM is freed and the kernel returns.
+// Every wait on an mbarrier is bounded (mbar_wait_bounded); a wait that runs out sets the CTA's abort flag and the device status
+// word; the producers and the issuer leave their loops, the softmax warps keep walking theirs without waiting (they share a
+// named barrier per warp pair, which has no time limit, so none of them may leave early), the producer waits (bounded) for
+// copies in flight, TMEM is freed and the kernel returns.
 // The cache must hold finite values in every slot of a block that is in use (PagedKVCache allocates zeros): keys past the end
 // of a request inside its last 16-key group are masked (P = 0) but still multiplied.
 #include <cstdlib>
@@ -116,7 +117,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   uint8_t* sQ = smem;                                  // [HALVES][128 rows][128 B]
   uint8_t* sK = sQ + Cfg::Q_BYTES;                     // [KS][HALVES][BN keys][128 B]
   uint8_t* sV = sK + KS * Cfg::KV_TILE;                // [VS][HALVES][BN keys][128 B]
-  __shared__ uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[Cfg::S_BUFS], p_full[Cfg::S_BUFS], o_done[Cfg::S_BUFS], q_full, pair_bar[4];
+  __shared__ uint64_t k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[Cfg::S_BUFS], p_full[Cfg::S_BUFS], o_done[Cfg::S_BUFS], q_full;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   // Row maxima of the two column halves, [tile parity][half][row] as bf16 (rounded up: a reference maximum only has to be
@@ -130,7 +131,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int tok0 = p.cu_seqlens[b];
   const int q_len = p.cu_seqlens[b + 1] - tok0;
   const int rows = q_len * G;
-  const int row0 = blockIdx.x * TCA_BM;
+  // CTAs are dispatched in block-index order: the last row tiles of a causal prompt see the most keys, so they go first and
+  // the tail of the grid is made of short CTAs
+  const int row0 = int(gridDim.x - 1 - blockIdx.x) * TCA_BM;
   if (rows < p.min_rows || row0 >= rows) return;      // before anything is allocated
   const int past = p.past_lens[b];
   const bool full = p.window < 0;
@@ -146,7 +149,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     for (int i = 0; i < KS; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < VS; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
     for (int i = 0; i < Cfg::S_BUFS; ++i) mbar_init(&s_full[i], 1);
-    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
     for (int i = 0; i < Cfg::S_BUFS; ++i) { mbar_init(&p_full[i], TCA_SOFTMAX_THREADS); mbar_init(&o_done[i], 1); }
     mbar_init(&q_full, TCA_SOFTMAX_THREADS);
     abort_flag = 0;
@@ -266,14 +268,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int tq = valid ? gr / G : q_len - 1;
     const int hq = kvh * G + (valid ? gr % G : 0);
     const int qpos = past + tq;
-    // the two warps of a lane quarter meet on an mbarrier (a bounded wait, unlike bar.sync: a warp that gave up cannot strand its partner)
-    uint32_t pair_phase = 0;
-    auto pair_sync = [&]() -> bool {
-      mbar_arrive(&pair_bar[quarter]);
-      const bool done = mbar_wait_bounded(&pair_bar[quarter], pair_phase & 1, abort_p);
-      ++pair_phase;
-      return done;
-    };
+    // The two warps of a lane quarter meet on a named barrier.  It has no time limit, so no softmax warp ever leaves the tile loop
+    // early: after a bounded wait gave up (abort flag set) a warp keeps walking the loop - its waits then return at once - and
+    // still arrives at every barrier its partner arrives at.
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory"); };
     {
       const __nv_bfloat16* src = p.q + size_t(tok0 + tq) * p.q_stride + size_t(hq) * D;
 #pragma unroll
@@ -334,22 +332,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     auto exchange_max = [&](int it, float mx_raw) -> float {
       const __nv_bfloat16 mxb = __float2bfloat16_ru(mx_raw * kmul);
       xchg[it & 1][half][r] = mxb;
-      if (!pair_sync()) fail(OGB_ERR_WAIT_MMA);
+      pair_sync();
       return fmaxf(__bfloat162float(mxb), __bfloat162float(xchg[it & 1][half ^ 1][r]));
     };
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    float mx_cur = -INFINITY;
-    // One tile: exponentials of `cur` (already masked, maximum known) interleaved with load + mask + maximum of `nxt`.
-    auto body = [&](int it, float (&cur)[HC], float (&nxt)[HC]) -> bool {
-      const bool has_next = it + 1 < n_tiles;
-      bool next_interior = true;
-      if (has_next) {
-        if (!mbar_wait_bounded(&s_full[(it + 1) % Cfg::S_BUFS], ((it + 1) / Cfg::S_BUFS) & 1, abort_p)) { fail(OGB_ERR_WAIT_MMA); return false; }
-        tc_fence_after();
-        issue_loads(it + 1, nxt);
-        next_interior = tile_interior(it + 1);
-      }
+    for (int it = 0; it < n_tiles; ++it) {
+      if (ok && !mbar_wait_bounded(&s_full[it % Cfg::S_BUFS], (it / Cfg::S_BUFS) & 1, abort_p)) { fail(OGB_ERR_WAIT_MMA); ok = false; }
+      tc_fence_after();
+      float sc[HC];
+      issue_loads(it, sc);
+      tmem_ld_wait();
+      const bool interior = tile_interior(it);
+      float mx_raw = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < HC / 16; ++c) mx_raw = fmaxf(mx_raw, prep16(it, sc, c, interior));
+      const float mx_cur = exchange_max(it, mx_raw);
       // lazy maximum: move the reference only when the row maximum outgrew it by more than the gap (both halves decide alike)
       float alpha = 1.f;
       bool moved = false;
@@ -361,25 +359,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       const float nms = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[HC / 2];
-      float nmx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < HC / 16; ++c) {
-#pragma unroll
-        for (int e = c * 16; e < c * 16 + 16; e += 4) {
-          const float p0 = exp2f(fmaf(cur[e], kmul, nms)), p1 = exp2f(fmaf(cur[e + 1], kmul, nms));
-          const float p2 = exp2f(fmaf(cur[e + 2], kmul, nms)), p3 = exp2f(fmaf(cur[e + 3], kmul, nms));
-          sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
-          pk[e / 2] = pack_bf16x2(p0, p1);
-          pk[e / 2 + 1] = pack_bf16x2(p2, p3);
-        }
-        if (has_next) {
-          if (c == 0) tmem_ld_wait();
-          nmx = fmaxf(nmx, prep16(it + 1, nxt, c, next_interior));
-        }
+      for (int e = 0; e < HC; e += 4) {
+        const float p0 = exp2f(fmaf(sc[e], kmul, nms)), p1 = exp2f(fmaf(sc[e + 1], kmul, nms));
+        const float p2 = exp2f(fmaf(sc[e + 2], kmul, nms)), p3 = exp2f(fmaf(sc[e + 3], kmul, nms));
+        sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+        pk[e / 2] = pack_bf16x2(p0, p1);
+        pk[e / 2 + 1] = pack_bf16x2(p2, p3);
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       if (it > 0 && __any_sync(0xffffffffu, moved)) {
-        if (!mbar_wait_bounded(&o_done[(it - 1) % Cfg::S_BUFS], ((it - 1) / Cfg::S_BUFS) & 1, abort_p)) { fail(OGB_ERR_WAIT_MMA); return false; }
+        if (ok && !mbar_wait_bounded(&o_done[(it - 1) % Cfg::S_BUFS], ((it - 1) / Cfg::S_BUFS) & 1, abort_p)) { fail(OGB_ERR_WAIT_MMA); ok = false; }
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < OC / 16; ++c) {
@@ -402,35 +392,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[it % Cfg::S_BUFS]);
-      if (has_next) mx_cur = exchange_max(it + 1, nmx);
-      return !*abort_p;
-    };
-    float sa[HC], sb[HC];
-    if (n_tiles > 0) {
-      if (!mbar_wait_bounded(&s_full[0], 0, abort_p)) { fail(OGB_ERR_WAIT_MMA); ok = false; }
-      if (ok) {
-        tc_fence_after();
-        issue_loads(0, sa);
-        tmem_ld_wait();
-        const bool interior0 = tile_interior(0);
-        float mx0 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < HC / 16; ++c) mx0 = fmaxf(mx0, prep16(0, sa, c, interior0));
-        mx_cur = exchange_max(0, mx0);
-      }
     }
-    for (int it = 0; ok && it < n_tiles; ++it) {
-      ok = body(it, sa, sb);
-#pragma unroll
-      for (int e = 0; e < HC; ++e) sa[e] = sb[e];     // one copy of the loop body in the instruction cache instead of two
-    }
+    ok = ok && !*abort_p;
     if (ok && n_tiles > 0 && !mbar_wait_bounded(&o_done[(n_tiles - 1) % Cfg::S_BUFS], ((n_tiles - 1) / Cfg::S_BUFS) & 1, abort_p)) { fail(OGB_ERR_WAIT_MMA); ok = false; }
     tc_fence_after();
     // the row's sum is the two halves' sums (same reference maximum on both sides)
-    if (!pair_sync()) fail(OGB_ERR_WAIT_MMA);                   // the partner is done reading the last tile's maxima
+    pair_sync();                                                // the partner is done reading the last tile's maxima
     float* lsum = reinterpret_cast<float*>(&xchg[0][0][0]);     // [half][row]
     lsum[half * TCA_BM + r] = l;
-    if (!pair_sync()) fail(OGB_ERR_WAIT_MMA);
+    pair_sync();
     l += lsum[(half ^ 1) * TCA_BM + r];
     if (ok && !*abort_p) {
       float scale_o = 1.f;
