@@ -284,6 +284,7 @@ class SequenceState:
         self.kv = PagedKVCache(decoder.arch, rows * self.blocks_per_row, block_size, dev, decoder.dtype,
                                kv_heads=decoder.kv_heads_local, conv_channels=decoder.conv_channels_local, kv_bits=kv_bits)
         self.block_table = (torch.arange(rows * self.blocks_per_row, dtype=torch.int32).view(rows, self.blocks_per_row)).to(dev)
+        self.kv.ensure_state_slots(rows)             # linear-attention layers: row r keeps its recurrent state in slot r
         self.kv_len = [0] * rows
         # Beam search shares cache blocks between rows (copy-on-write at block granularity).  Until the first reorder every
         # row owns one contiguous run of blocks and none of this is active (`_tbl` is None).
@@ -366,6 +367,7 @@ class SequenceState:
                        logits_rows=None if want_all_logits else i32(last),
                        max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds,
                        min_q_len=min(len(t) for t in row_tokens if t),
+                       state_slots=i32(rows_used) if self.decoder.arch.has_linear_layers else None,
                        **self._cross_fields(rows_used))
         if mrope:
             s.positions3 = torch.from_numpy(np.ascontiguousarray(np.concatenate(p3, axis=1))).to(dev)
@@ -396,6 +398,8 @@ class SequenceState:
             return False   # rotary positions differ from the cache positions (multimodal RoPE after an image)
         if getattr(self, "alignment_heads", None):
             return False   # the recorded cross-attention scores are gathered with host-side shapes
+        if dec.arch.has_linear_layers:
+            return False   # the gate / norm arithmetic around the recurrence runs as tensor ops
         return dec.tp.size == 1
 
     def run_decode_graph(self, last_tokens: List[int]) -> torch.Tensor:
@@ -448,6 +452,10 @@ class SequenceState:
         return out
 
     def rewind(self, row: int, length: int):
+        if self.decoder.arch.has_linear_layers and 0 < length < self.kv_len[row]:
+            # a recurrent state cannot be cropped to an earlier position (the reference keeps a window of snapshot slots for its
+            # speculative paths, src/models/recurrent_state.h:12-66; here only a restart from the empty state is offered)
+            raise RuntimeError("models with linear-attention layers can only be rewound to length 0")
         self.kv_len[row] = min(self.kv_len[row], length)
         if length == 0:
             self.rope_delta[row] = 0
@@ -517,6 +525,8 @@ class SequenceState:
                 return
             self._tbl = self.block_table.cpu().numpy().copy()
         self._tbl = self._tbl[np.asarray(src_rows, dtype=np.int64)].copy()
+        if self.kv.state is not None:       # recurrent states follow their hypotheses
+            self.kv.state = self.kv.state[:, torch.as_tensor(src_rows, dtype=torch.long, device=self.kv.state.device)].contiguous()
         self.kv_len = [self.kv_len[s] for s in src_rows]
         self._recount()
         self._tbl_dirty = True

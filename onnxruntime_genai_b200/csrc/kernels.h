@@ -104,6 +104,10 @@ int ogb_bf16_to_f32(const void* in, float* out, long long n, void* stream);
 int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream);
 int ogb_gather_rows_f16(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream);  // bf16 -> fp16
 
+// ---- linear_attention.cu: gated delta rule over packed sequences; state [slots, Hv, dk, dv] fp32 updated in place
+int ogb_gated_delta(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, const int32_t* slots,
+                    const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream);
+
 // ---- attention.cu
 long long ogb_attention_scratch_bytes(int total_tokens, int Hq, int D, int splits);
 // cache_slots (rows of the key / value cache) and status (device status word) enable the TMA-fed K/V path; 0 / null keep

@@ -215,6 +215,7 @@ class ModelExecutor:
         # decode steps issue the attention CTAs of long requests first (OGB_ATTN_ORDER=0: in batch order)
         self.order_attention = self.use_graphs and os.environ.get("OGB_ATTN_ORDER", "1") != "0"
         self.lora_of = None          # set by the engine: plan -> (per-token adapter ids on the device, adapter names) or None
+        self.state_slots_of = None   # set by the engine for models with linear-attention layers: plan -> [B] int32 state slots
 
     def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int, ordered: bool = False) -> StepInputs:
         st = self.staging
@@ -262,6 +263,8 @@ class ModelExecutor:
             s.num_decode = nd
         if lora is not None:
             s.lora_ids, s.lora_names = lora
+        if self.state_slots_of is not None:
+            s.state_slots = self.state_slots_of(plan)
         return self.decoder.forward(s, self.kv)
 
     def upload_graph_inputs(self, plan):
@@ -478,11 +481,14 @@ class Engine:
                           os.environ.get("OGB_ENGINE_LOOKAHEAD", "1") != "0" and os.environ.get("OGB_ENGINE_RUN_AHEAD", "1") != "0")
         if lookahead is not None:
             self.lookahead = bool(lookahead) and not windowed
+        recurrent = model.arch.has_linear_layers
+        if recurrent:
+            self.lookahead = False        # steps of recurrent models run eagerly, one at a time
         # Speculative decoding (a draft model in the checkpoint, or speculative.ngram_size > 0 in genai_config.json): decoding
         # requests carry proposed tokens that one packed forward of the target verifies for the whole batch (engine/speculative.py).
         # The block look-ahead then reserves room for the proposals instead of serving the enqueue-ahead of plain decode steps.
         spec_cfg = dict(getattr(cfg, "speculative", None) or {})
-        want_spec = (executor is None and not windowed and not static and
+        want_spec = (executor is None and not windowed and not static and not recurrent and      # (a rejected draft cannot be taken out of a recurrent state)
                      (getattr(model, "draft", None) is not None or int(spec_cfg.get("ngram_size", 0) or 0) > 0) and
                      os.environ.get("OGB_ENGINE_SPECULATIVE", "1") != "0")
         if want_spec:
@@ -513,6 +519,13 @@ class Engine:
         self._adapter_requests = 0       # requests with a LoRA adapter: their steps run eagerly (no graphs, no look-ahead)
         if hasattr(self.executor, "lora_of"):
             self.executor.lora_of = self._lora_of
+        self._state_slot: Dict[int, int] = {}      # request id -> slot of the recurrent-state pool (linear-attention models)
+        self._free_slots: List[int] = []
+        if model.arch.has_linear_layers and hasattr(self.executor, "state_slots_of"):
+            self.kv.ensure_state_slots(o.max_batch_size)
+            self._free_slots = list(range(o.max_batch_size - 1, -1, -1))
+            self.executor.state_slots_of = self._state_slots_of
+            self.executor.use_graphs = False       # the gate / norm arithmetic around the recurrence runs as tensor ops
         self._guidance: Dict[int, Any] = {}
         self.last_outcome = StepOutcome.NoWork
         self.step_count = 0
@@ -548,6 +561,7 @@ class Engine:
             if self._inflight is not None and any(e.request.id == rid for e in self._inflight[0].entries):
                 self._drain()
             self.core.remove_request(nat)
+            self._release_state_slot(rid)
             self._guidance.pop(rid, None)
             self._with_processors.discard(rid)
             self._need_first.discard(rid)
@@ -578,6 +592,28 @@ class Engine:
             self._guidance[nat.id] = GuidanceProcessor(self.model, request.params.guidance_type, request.params.guidance_data, 1, False)
             self._guidance[nat.id].commit_prompt(np.asarray(request._pending_tokens, dtype=np.int32).reshape(1, -1))
 
+    def _state_slots_of(self, plan):
+        """Slot of every request of the step in the recurrent-state pool; a request gets one when it first runs (its state starts
+        from zero because its past length is 0 then) and gives it back when it leaves the engine."""
+        out = np.empty(len(plan.entries), dtype=np.int32)
+        for i, e in enumerate(plan.entries):
+            rid = e.request.id
+            slot = self._state_slot.get(rid)
+            if slot is None:
+                if not self._free_slots:
+                    n = self.kv.state_slots
+                    self.kv.ensure_state_slots(2 * n)
+                    self._free_slots = list(range(2 * n - 1, n - 1, -1))
+                slot = self._free_slots.pop()
+                self._state_slot[rid] = slot
+            out[i] = slot
+        return torch.from_numpy(out).to(self.model.device)
+
+    def _release_state_slot(self, rid: int) -> None:
+        slot = self._state_slot.pop(rid, None)
+        if slot is not None:
+            self._free_slots.append(slot)
+
     def _lora_of(self, plan):
         """(per-token adapter index on the device, names of the adapters present) for a step that holds at least one request with
         an adapter, else None.  Tokens of requests without an adapter carry the index len(names)."""
@@ -606,6 +642,7 @@ class Engine:
         self.core.remove_request(request._native)
         self._by_native.pop(request._native.id, None)
         self._natives.pop(request._native.id, None)
+        self._release_state_slot(request._native.id)
         self._adapter_requests = sum(1 for r in self._by_native.values() if r._adapter is not None)
         self._guidance.pop(request._native.id, None)
         self._with_processors.discard(request._native.id)

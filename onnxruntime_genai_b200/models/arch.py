@@ -17,6 +17,7 @@ LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
     "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl",
+    "qwen3_next", "qwen3_5", "qwen3_5_text",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
 
 
@@ -64,6 +65,14 @@ class ArchConfig:
     layer_types: Optional[List[str]] = None
     conv_L_cache: int = 3
     conv_bias: bool = False
+    # Layers of type "linear_attention" are gated-delta-net layers (Qwen3-Next / Qwen3.5 style): a causal depthwise convolution
+    # + SiLU over the packed q / k / v channels, then a recurrent state S [value heads, key dim, value dim] per request updated
+    # by the gated delta rule (reference ops: CausalConvWithState, LinearAttention with update_rule "gated_delta").
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
     # Multimodal RoPE (Qwen2-VL): rotary pairs per position component (temporal, height, width); None: ordinary RoPE
     mrope_section: Optional[List[int]] = None
     cross_attention: bool = False    # encoder-decoder (whisper): every layer also attends to the encoder's output
@@ -115,6 +124,33 @@ class ArchConfig:
 
     def is_conv_layer(self, layer: int) -> bool:
         return self.layer_types is not None and self.layer_types[layer] == "conv"
+
+    def is_linear_layer(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
+
+    @property
+    def has_linear_layers(self) -> bool:
+        return self.layer_types is not None and "linear_attention" in self.layer_types
+
+    @property
+    def linear_key_dim(self) -> int:
+        return self.linear_num_key_heads * self.linear_key_head_dim
+
+    @property
+    def linear_value_dim(self) -> int:
+        return self.linear_num_value_heads * self.linear_value_head_dim
+
+    @property
+    def linear_conv_dim(self) -> int:
+        return 2 * self.linear_key_dim + self.linear_value_dim
+
+    def conv_state_channels(self, layer: int) -> int:
+        """Channels of the paged convolution-input cache of a layer (0: the layer keeps none)."""
+        if self.is_conv_layer(layer):
+            return self.hidden_size
+        if self.is_linear_layer(layer):
+            return self.linear_conv_dim
+        return 0
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window <= 0:
@@ -230,6 +266,15 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.mrope_section = list((cfg.get("rope_scaling") or {}).get("mrope_section") or [16, 24, 24])
         a.rope_scaling = None
         a.attn_bias = True
+    if cfg.get("linear_num_value_heads"):
+        # hybrid gated-delta-net stacks: every `full_attention_interval`-th layer attends, the others are linear-attention layers
+        a.linear_num_key_heads = int(cfg.get("linear_num_key_heads", 0))
+        a.linear_num_value_heads = int(cfg["linear_num_value_heads"])
+        a.linear_key_head_dim = int(cfg.get("linear_key_head_dim", 128))
+        a.linear_value_head_dim = int(cfg.get("linear_value_head_dim", 128))
+        a.linear_conv_kernel_dim = int(cfg.get("linear_conv_kernel_dim", 4))
+        iv = int(cfg.get("full_attention_interval", 4))
+        a.layer_types = list(cfg.get("layer_types") or ["full_attention" if (i + 1) % iv == 0 else "linear_attention" for i in range(a.num_layers)])
     if mt == "lfm2":
         a.layer_types = list(cfg.get("layer_types") or ["full_attention"] * a.num_layers)
         a.conv_L_cache = int(cfg.get("conv_L_cache", 3))

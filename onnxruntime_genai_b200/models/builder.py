@@ -64,6 +64,17 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             if arch.conv_bias:
                 s[p + "conv.conv.bias"] = (H,)
             s[p + "conv.out_proj.weight"] = (H, H)
+        elif arch.is_linear_layer(i):
+            nv, hv = arch.linear_num_value_heads, arch.linear_value_head_dim
+            s[p + "linear_attn.in_proj_qkv.weight"] = (arch.linear_conv_dim, H)
+            s[p + "linear_attn.in_proj_z.weight"] = (arch.linear_value_dim, H)
+            s[p + "linear_attn.in_proj_b.weight"] = (nv, H)
+            s[p + "linear_attn.in_proj_a.weight"] = (nv, H)
+            s[p + "linear_attn.conv1d.weight"] = (arch.linear_conv_dim, arch.linear_conv_kernel_dim)
+            s[p + "linear_attn.dt_bias"] = (nv,)
+            s[p + "linear_attn.A_log"] = (nv,)
+            s[p + "linear_attn.norm.weight"] = (hv,)
+            s[p + "linear_attn.out_proj.weight"] = (H, arch.linear_value_dim)
         else:
             s[p + "self_attn.q_proj.weight"] = (arch.q_size, H)
             s[p + "self_attn.k_proj.weight"] = (arch.kv_size, H)
@@ -83,7 +94,7 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
                             ("v", (arch.q_size, arch.encoder_hidden_size or H)), ("o", (H, arch.q_size))):
                 s[p + f"cross_attn.{nm}_proj.weight"] = shp
                 s[p + f"cross_attn.{nm}_proj.bias"] = (shp[0],)
-        if arch.qk_norm and not arch.is_conv_layer(i):
+        if arch.qk_norm and not arch.is_conv_layer(i) and not arch.is_linear_layer(i):
             s[p + "self_attn.q_norm.weight"] = (arch.head_dim,)
             s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
         if arch.attn_sinks:
@@ -677,6 +688,40 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             W.node("Identity", f"{n}/conv/present", [f"{n}/conv/Conv_1/output_0"], [f"present_conv.{i}"])
             o_out = f"{n}/conv/out_proj/MatMul/output_0"
             put_linear(p + "conv.out_proj", f"{n}/conv/out_proj/MatMul", [p + "conv.out_proj.weight"], f"{n}/conv/Mul_2/output_0", o_out, H, H)
+        elif arch.is_linear_layer(i):
+            # gated-delta-net layer (reference graph: builders/qwen.py:1776-1867): projections, causal depthwise convolution + SiLU
+            # with a carried state, per-head L2 norm of q / k, decay / beta gates, LinearAttention (gated delta rule) with a
+            # recurrent state, gated RMS norm, output projection
+            la = f"{n}/linear_attn"
+            lp = p + "linear_attn."
+            nk, nv, hk, hv, Kc = arch.linear_num_key_heads, arch.linear_num_value_heads, arch.linear_key_head_dim, arch.linear_value_head_dim, arch.linear_conv_kernel_dim
+            cd, vd = arch.linear_conv_dim, arch.linear_value_dim
+            put_linear(lp + "in_proj_qkv", f"{la}/in_proj_qkv/MatMul", [lp + "in_proj_qkv.weight"], x, f"{la}/in_proj_qkv/MatMul/output_0", cd, H)
+            put_linear(lp + "in_proj_z", f"{la}/in_proj_z/MatMul", [lp + "in_proj_z.weight"], x, f"{la}/in_proj_z/MatMul/output_0", vd, H)
+            put_linear(lp + "in_proj_b", f"{la}/in_proj_b/MatMul", [lp + "in_proj_b.weight"], x, f"{la}/in_proj_b/MatMul/output_0", nv, H)
+            put_linear(lp + "in_proj_a", f"{la}/in_proj_a/MatMul", [lp + "in_proj_a.weight"], x, f"{la}/in_proj_a/MatMul/output_0", nv, H)
+            put_plain(lp + "conv1d.weight", [lp + "conv1d.weight"], {"shape": (cd, 1, Kc), "op": "id", "fn": lambda ts: ts[0].float().reshape(cd, 1, Kc)})
+            W.node("Transpose", f"{la}/qkv/Transpose", [f"{la}/in_proj_qkv/MatMul/output_0"], [f"{la}/qkv/Transpose/output_0"], perm=[0, 2, 1])
+            W.node("CausalConvWithState", f"{la}/CausalConvWithState", [f"{la}/qkv/Transpose/output_0", lp + "conv1d.weight", "", f"past_key_values.{i}.conv_state"],
+                   [f"{la}/CausalConvWithState/output_0", f"present.{i}.conv_state"], domain="com.microsoft", ndim=1, activation="silu")
+            W.node("Transpose", f"{la}/conv_out/Transpose", [f"{la}/CausalConvWithState/output_0"], [f"{la}/conv_out/Transpose/output_0"], perm=[0, 2, 1])
+            put_plain(lp + "dt_bias", [lp + "dt_bias"], {"shape": (nv,), "op": "id", "fn": lambda ts: ts[0].float()}, force_fp32=True)
+            put_plain(lp + "neg_exp_A", [lp + "A_log"], {"shape": (nv,), "op": "neg_exp", "fn": lambda ts: -torch.exp(ts[0].float())}, force_fp32=True)
+            W.node("LinearAttentionGate", f"{la}/gate/LinearAttentionGate", [f"{la}/in_proj_a/MatMul/output_0", lp + "dt_bias", lp + "neg_exp_A", f"{la}/in_proj_b/MatMul/output_0"],
+                   [f"{la}/gate/LinearAttentionGate/output_0", f"{la}/gate/LinearAttentionGate/output_1"], domain="com.microsoft")
+            W.node("LinearAttention", f"{la}/LinearAttention",
+                   [f"{la}/conv_out/Transpose/output_0", "", "", f"past_key_values.{i}.recurrent_state", f"{la}/gate/LinearAttentionGate/output_0",
+                    f"{la}/gate/LinearAttentionGate/output_1"],
+                   [f"{la}/LinearAttention/output_0", f"present.{i}.recurrent_state"], domain="com.microsoft", q_num_heads=nk, kv_num_heads=nv,
+                   update_rule="gated_delta", scale=float(1.0 / (hk ** 0.5)), key_head_dim=hk, value_head_dim=hv, packed_qkv=1, l2_normalize_qk=1)
+            put_plain(lp + "norm.weight", [lp + "norm.weight"], {"shape": (hv,), "op": "id", "fn": lambda ts: ts[0].float()})
+            W.node("SimplifiedLayerNormalization", f"{la}/gated_norm/LayerNorm", [f"{la}/LinearAttention/output_0", lp + "norm.weight"],
+                   [f"{la}/gated_norm/LayerNorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1, per_head=hv)
+            W.node("Sigmoid", f"{la}/gated_norm/Sigmoid", [f"{la}/in_proj_z/MatMul/output_0"], [f"{la}/gated_norm/Sigmoid/output_0"])
+            W.node("Mul", f"{la}/gated_norm/Mul_1", [f"{la}/in_proj_z/MatMul/output_0", f"{la}/gated_norm/Sigmoid/output_0"], [f"{la}/gated_norm/Mul_1/output_0"])
+            W.node("Mul", f"{la}/gated_norm/Mul_2", [f"{la}/gated_norm/LayerNorm/output_0", f"{la}/gated_norm/Mul_1/output_0"], [f"{la}/gated_norm/Mul_2/output_0"])
+            o_out = f"{la}/out_proj/MatMul/output_0"
+            put_linear(lp + "out_proj", f"{la}/out_proj/MatMul", [lp + "out_proj.weight"], f"{la}/gated_norm/Mul_2/output_0", o_out, H, vd)
         else:
             # attention
             qkv_out = f"{n}/attn/qkv_proj/MatMul/output_0"
@@ -941,6 +986,12 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             m.inputs.append(op.ValueInfo(f"past_conv.{i}", io_dt, ("batch_size", H, arch.conv_L_cache)))
             m.outputs.append(op.ValueInfo(f"present_conv.{i}", io_dt, ("batch_size", H, arch.conv_L_cache)))
             continue
+        if arch.is_linear_layer(i):
+            cs = ("batch_size", arch.linear_conv_dim, arch.linear_conv_kernel_dim - 1)
+            rs = ("batch_size", arch.linear_num_value_heads, arch.linear_key_head_dim, arch.linear_value_head_dim)
+            m.inputs += [op.ValueInfo(f"past_key_values.{i}.conv_state", io_dt, cs), op.ValueInfo(f"past_key_values.{i}.recurrent_state", io_dt, rs)]
+            m.outputs += [op.ValueInfo(f"present.{i}.conv_state", io_dt, cs), op.ValueInfo(f"present.{i}.recurrent_state", io_dt, rs)]
+            continue
         m.inputs += [op.ValueInfo(f"past_key_values.{i}.key", io_dt, kv_shape), op.ValueInfo(f"past_key_values.{i}.value", io_dt, kv_shape)]
         m.outputs += [op.ValueInfo(f"present.{i}.key", io_dt, kv_shape), op.ValueInfo(f"present.{i}.value", io_dt, kv_shape)]
 
@@ -999,6 +1050,8 @@ def make_genai_config(arch: ArchConfig, precision: str, ep: str, paged: bool, bl
         if arch.sliding_layers is not None:
             sw["layers"] = list(arch.sliding_layers)
         decoder["sliding_window"] = sw
+    if arch.has_linear_layers:
+        decoder["layer_types"] = list(arch.layer_types)
     if arch.layer_types is not None and "conv" in arch.layer_types:
         decoder["layer_types"] = list(arch.layer_types)
         decoder["conv_cache_size"] = int(arch.conv_L_cache)

@@ -50,6 +50,7 @@ class StepInputs:
     return_hidden: bool = False
     lora_ids: Optional[torch.Tensor] = None      # [T] int32: index of each token's adapter in `lora_names` (len(lora_names) = none)
     lora_names: Optional[tuple] = None           # adapters present in this step (a batch may mix several and none)
+    state_slots: Optional[torch.Tensor] = None   # [B] int32 slot of each request in the recurrent-state pool (linear-attention layers)
 
 
 class PagedKVCache:
@@ -59,6 +60,7 @@ class PagedKVCache:
     def __init__(self, arch: ArchConfig, num_blocks: int, block_size: int, device, dtype, kv_heads: Optional[int] = None,
                  num_window_blocks: int = 0, conv_channels: Optional[int] = None, kv_bits: int = 16):
         self.block_size = block_size
+        self.arch, self.device = arch, torch.device(device)
         # kv_bits 8: keys and values are stored as int8 rows with an inline fp32 scale (head_dim + 16 bytes per row and head)
         if kv_bits not in (16, 8):
             raise RuntimeError(f"KV cache quantization: {kv_bits}-bit caches are not supported (8 or none)")
@@ -68,7 +70,7 @@ class PagedKVCache:
         self.num_blocks = num_blocks
         self.num_window_blocks = num_window_blocks
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
-        conv = [arch.is_conv_layer(i) for i in range(arch.num_layers)]
+        conv = [arch.conv_state_channels(i) > 0 for i in range(arch.num_layers)]
         self.windowed = [num_window_blocks > 0 and arch.layer_window(i) > 0 and not conv[i] for i in range(arch.num_layers)]
         n_full = sum(1 for w, c in zip(self.windowed, conv) if not w and not c)
         n_win = sum(1 for w in self.windowed if w)
@@ -76,8 +78,15 @@ class PagedKVCache:
         # the keys and values - rewinding, beam reordering and block sharing need nothing layer-specific.
         self.conv_index = {i: j for j, i in enumerate(i for i, c in enumerate(conv) if c)}
         cc = conv_channels if conv_channels is not None else arch.hidden_size
+        if arch.has_linear_layers:
+            cc = arch.linear_conv_dim
         self.conv = (torch.zeros(len(self.conv_index), num_blocks * block_size, cc, dtype=dtype, device=device)
                      if self.conv_index else None)
+        # Recurrent states of linear-attention layers: [layer, request slot, value heads, key dim, value dim] fp32.  Slots are
+        # handed out by the owner of the cache (a generator's rows; the engine's requests) and travel in StepInputs.state_slots.
+        self.lin_index = {i: j for j, i in enumerate(i for i in range(arch.num_layers) if arch.is_linear_layer(i))}
+        self.state = None
+        self.state_slots = 0
         row, kdt = (arch.head_dim + 16, torch.int8) if kv_bits == 8 else (arch.head_dim, dtype)
         self.full = torch.zeros(max(n_full, 1), 2, num_blocks * block_size, hk, row, dtype=kdt, device=device)
         self.win = (torch.zeros(n_win, 2, num_window_blocks * block_size, hk, row, dtype=kdt, device=device)
@@ -100,12 +109,26 @@ class PagedKVCache:
     def conv_layer(self, i: int) -> torch.Tensor:
         return self.conv[self.conv_index[i]]
 
+    def ensure_state_slots(self, n: int) -> None:
+        """At least n request slots in the recurrent-state pool (grown by copying; states of live slots are kept)."""
+        if not self.lin_index or n <= self.state_slots:
+            return
+        a = self.arch
+        new = torch.zeros(len(self.lin_index), n, a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim,
+                          dtype=torch.float32, device=self.device)
+        if self.state is not None:
+            new[:, :self.state_slots] = self.state
+        self.state, self.state_slots = new, n
+
+    def state_layer(self, i: int) -> torch.Tensor:
+        return self.state[self.lin_index[i]]
+
     @staticmethod
     def bytes_per_block(arch: ArchConfig, block_size: int, dtype, kv_heads: Optional[int] = None, conv_channels: Optional[int] = None,
                         kv_bits: int = 16) -> int:
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
-        n_conv = sum(1 for i in range(arch.num_layers) if arch.is_conv_layer(i))
-        cc = conv_channels if conv_channels is not None else arch.hidden_size
+        n_conv = sum(1 for i in range(arch.num_layers) if arch.conv_state_channels(i) > 0)
+        cc = arch.linear_conv_dim if arch.has_linear_layers else (conv_channels if conv_channels is not None else arch.hidden_size)
         es = torch.empty((), dtype=dtype).element_size()
         kv_row = arch.head_dim + 16 if kv_bits == 8 else arch.head_dim * es
         return ((arch.num_layers - n_conv) * 2 * hk * kv_row + n_conv * cc * es) * block_size
@@ -163,6 +186,12 @@ class LayerWeights:
     conv_w: Optional[torch.Tensor] = None
     conv_b: Optional[torch.Tensor] = None
     conv_out_w: Optional[torch.Tensor] = None
+    lin_in_w: Optional[torch.Tensor] = None    # gated-delta-net layer: stacked [qkv | z | b | a] input projection
+    lin_conv_w: Optional[torch.Tensor] = None  # depthwise taps [conv_dim, K]
+    lin_dt_bias: Optional[torch.Tensor] = None
+    lin_neg_exp_a: Optional[torch.Tensor] = None
+    lin_norm_w: Optional[torch.Tensor] = None
+    lin_out_w: Optional[torch.Tensor] = None
     cross_ln_w: Optional[torch.Tensor] = None  # encoder-decoder cross-attention (whisper)
     cross_ln_b: Optional[torch.Tensor] = None
     cross_q_w: Optional[torch.Tensor] = None
@@ -273,6 +302,33 @@ class DecoderModel:
                             max_kv_len=s.max_kv_len, out=out)
         return out
 
+    def _linear_attention(self, s: StepInputs, kv: PagedKVCache, li: int, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        """A gated-delta-net layer (reference graph: builders/qwen.py:1776-1867).  The causal convolution reads the projected
+        q / k / v rows of the last K - 1 positions from the paged cache (the short-convolution kernel of the hybrid models with
+        unit gates), so rewinding and block copies need no convolution state; the recurrent state lives in the request's slot."""
+        a = self.arch
+        if s.state_slots is None:
+            raise RuntimeError("this model has linear-attention layers: the caller must provide StepInputs.state_slots")
+        T = x.shape[0]
+        cd, vd, nk, nv, hk, hv = a.linear_conv_dim, a.linear_value_dim, a.linear_num_key_heads, a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim
+        proj = self._linear(x, lw.lin_in_w)
+        qkv, z, b_, a_ = proj[:, :cd], proj[:, cd:cd + vd], proj[:, cd + vd:cd + vd + nv], proj[:, cd + vd + nv:]
+        ones = torch.ones(T, cd, dtype=x.dtype, device=x.device)
+        conv = ops.short_conv(torch.cat([ones, ones, qkv], dim=1).contiguous(), lw.lin_conv_w, None, kv.conv_layer(li), s.slot_mapping, s.positions,
+                              s.cu_seqlens, s.past_lens, s.block_table, kv.block_size)
+        conv = torch.nn.functional.silu(conv.float())
+        kd = nk * hk
+        q = torch.nn.functional.normalize(conv[:, :kd].view(T, nk, hk), dim=-1, eps=1e-6) * (hk ** -0.5)
+        k = torch.nn.functional.normalize(conv[:, kd:2 * kd].view(T, nk, hk), dim=-1, eps=1e-6)
+        v = conv[:, 2 * kd:].view(T, nv, hv)
+        beta = torch.sigmoid(b_.float())
+        g = lw.lin_neg_exp_a * torch.nn.functional.softplus(a_.float() + lw.lin_dt_bias)
+        o = ops.gated_delta(q.to(x.dtype).contiguous(), k.to(x.dtype).contiguous(), v.to(x.dtype).contiguous(), g, beta, kv.state_layer(li),
+                            s.state_slots, s.cu_seqlens, s.past_lens).float()
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + a.norm_eps) * lw.lin_norm_w          # RMS norm per value head
+        o = (o.view(T, vd) * torch.nn.functional.silu(z.float())).to(x.dtype)
+        return self._row_parallel(o, lw.lin_out_w, None, None)
+
     def _lora(self, lw: LayerWeights, proj: str):
         if self._lora_batch is not None:
             from .lora import grouped_lora
@@ -318,7 +374,7 @@ class DecoderModel:
         lw = self.layers[0]
         return (self.norms_folded and self.fuse_steps and self.active_adapter is None and s.lora_ids is None and
                 s.input_ids.shape[0] <= ops.FUSED_MAX_TOKENS and
-                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and
+                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and not a.has_linear_layers and
                 lw.post_attn_norm_w is None and lw.post_ffn_norm_w is None and not s.cross_qk_heads)
 
     def _forward_fused(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
@@ -487,6 +543,11 @@ class DecoderModel:
                 y = ops.short_conv(bcx, lw.conv_w, lw.conv_b, kv.conv_layer(li), s.slot_mapping, s.positions, s.cu_seqlens, s.past_lens,
                                    s.block_table, kv.block_size)
                 h = self._row_parallel(y, lw.conv_out_w, None, self._lora(lw, "out_proj"))
+                x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
+                h = self._mlp(lw, x)
+                continue
+            if lw.lin_in_w is not None:
+                h = self._linear_attention(s, kv, li, lw, x)
                 x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
                 h = self._mlp(lw, x)
                 continue

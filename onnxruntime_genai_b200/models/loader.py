@@ -131,8 +131,15 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         any(n.name.endswith(("qkv_proj/Add", "q_proj/Add")) for n in g.find_all(f"{fa}/attn/"))
     a.o_bias = g.by_name.get(f"{fa}/attn/o_proj/Add") is not None
     a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
-    types = ["conv" if g.find(f"/model/layers.{i}/conv/in_proj/", ops=LINEAR_OPS) is not None else "full_attention"
+    types = ["conv" if g.find(f"/model/layers.{i}/conv/in_proj/", ops=LINEAR_OPS) is not None else
+             ("linear_attention" if g.by_name.get(f"/model/layers.{i}/linear_attn/LinearAttention") is not None else "full_attention")
              for i in range(a.num_layers)]
+    if "linear_attention" in types:
+        a.layer_types = types
+        la = g.by_name[f"/model/layers.{types.index('linear_attention')}/linear_attn/LinearAttention"]
+        a.linear_num_key_heads, a.linear_num_value_heads = int(la.attrs["q_num_heads"]), int(la.attrs["kv_num_heads"])
+        a.linear_key_head_dim, a.linear_value_head_dim = int(la.attrs["key_head_dim"]), int(la.attrs["value_head_dim"])
+        a.linear_conv_kernel_dim = int(g.lm.info(f"model.layers.{types.index('linear_attention')}.linear_attn.conv1d.weight").dims[-1])
     if "conv" in types:
         a.layer_types = types
         first = types.index("conv")
@@ -369,6 +376,18 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
             if g.has_init(f"model.layers.{i}.conv.conv.bias"):
                 lw.conv_b = _vec(g, f"model.layers.{i}.conv.conv.bias", dtype, device, ch if tpn > 1 else None)
             lw.conv_out_w = _linear_weight(g, linear_node(f"{n}/conv/", "out_proj"), dtype, device, cols=ch if tpn > 1 else None)
+        elif arch.is_linear_layer(i):
+            # gated-delta-net layer: four input projections stacked into one GEMM [qkv | z | b | a], the depthwise taps, the gate
+            # constants, the per-head norm weight, the output projection
+            if tpn > 1:
+                raise NotImplementedError("linear-attention (gated delta net) layers are not sharded: run these models on one GPU")
+            la = f"{n}/linear_attn/"
+            lw.lin_in_w = torch.cat([_linear_weight(g, linear_node(la, nm), dtype, device) for nm in ("in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a")], 0).contiguous()
+            lw.lin_conv_w = g.tensor(f"model.layers.{i}.linear_attn.conv1d.weight").reshape(arch.linear_conv_dim, -1).to(device=device, dtype=dtype).contiguous()
+            lw.lin_dt_bias = g.tensor(f"model.layers.{i}.linear_attn.dt_bias").float().to(device)
+            lw.lin_neg_exp_a = g.tensor(f"model.layers.{i}.linear_attn.neg_exp_A").float().to(device)
+            lw.lin_norm_w = g.tensor(f"model.layers.{i}.linear_attn.norm.weight").float().to(device)
+            lw.lin_out_w = _linear_weight(g, linear_node(la, "out_proj"), dtype, device)
         else:
             # attention projections: packed or separate
             qkv = linear_node(f"{n}/attn/", "qkv_proj")

@@ -348,6 +348,23 @@ def short_conv(bcx, weight, bias, cache, slots, positions, cu_seqlens, past_lens
     return out
 
 
+def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
+    """Gated-delta-rule recurrence of a linear-attention layer over packed sequences (see ops/reference.py::gated_delta).
+    state [slots, Hv, dk, dv] fp32 is updated in place."""
+    if not q.is_cuda:
+        return ref.gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens)
+    T, Hk, dk = q.shape
+    Hv, dv = v.shape[1], v.shape[2]
+    assert q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and state.dtype == torch.float32
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and state.is_contiguous()
+    gf, bf = g.float().contiguous(), beta.float().contiguous()
+    out = torch.empty(T, Hv, dv, dtype=torch.bfloat16, device=q.device)
+    B = past_lens.shape[0]
+    _lib.check(_lib.lib().ogb_gated_delta(_ptr(q), _ptr(k), _ptr(v), _ptr(gf), _ptr(bf), _ptr(state), _ptr(slots), _ptr(cu_seqlens), _ptr(past_lens),
+                                          _ptr(out), B, Hk, Hv, dk, dv, _stream()), "gated_delta")
+    return out
+
+
 def decode_advance(sampled, input_ids, positions, past_lens, slot_mapping, sample_pos, block_table, block_size: int):
     """In place: the packed inputs of a one-token-per-request step become those of the next step (see
     csrc/elementwise.cu::decode_advance_kernel).  block_table [B, cols] int32, everything else [B] int32."""

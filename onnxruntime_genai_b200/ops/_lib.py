@@ -78,6 +78,7 @@ _SIGS = {
                                  c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "ogb_paged_attention_kv8": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
+    "ogb_gated_delta": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),
     "ogb_topk": (c_int, [_P, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P]),

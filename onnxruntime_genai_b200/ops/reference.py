@@ -292,3 +292,31 @@ def short_conv(bcx, weight, bias, cache, slots, positions, cu_seqlens, past_lens
                 acc = acc + bias.float()
             out[t] = c[t] * acc
     return out.to(bcx.dtype)
+
+
+def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
+    """Gated delta rule over packed sequences (the LinearAttention op with update_rule "gated_delta", reference:
+    src/python/py/models/builders/base.py:3419-3452, qwen.py:1842-1860).  q, k [T, Hk, dk] (already L2-normalised, q scaled),
+    v [T, Hv, dv], g [T, Hv] log decay (<= 0), beta [T, Hv]; state [slots, Hv, dk, dv] fp32, updated in place for the request
+    slots named by `slots` [B] (a request whose past length is 0 starts from a zero state).  Value head h reads key head
+    h // (Hv / Hk).  Per token:  S *= exp(g);  delta = (v - S^T k) * beta;  S += k (x) delta;  out = S^T q."""
+    T, Hk, dk = q.shape
+    Hv, dv = v.shape[1], v.shape[2]
+    rep = Hv // Hk
+    out = torch.zeros(T, Hv, dv, dtype=torch.float32, device=q.device)
+    cu = cu_seqlens.tolist()
+    qf, kf = q.float().repeat_interleave(rep, dim=1), k.float().repeat_interleave(rep, dim=1)      # [T, Hv, dk]
+    vf, gf, bf = v.float(), g.float(), beta.float()
+    for r in range(len(cu) - 1):
+        slot = int(slots[r])
+        S = state[slot].float()
+        if int(past_lens[r]) == 0:
+            S = torch.zeros_like(S)
+        for t in range(cu[r], cu[r + 1]):
+            S = S * torch.exp(gf[t])[:, None, None]
+            mem = torch.einsum("hkv,hk->hv", S, kf[t])
+            delta = (vf[t] - mem) * bf[t][:, None]
+            S = S + kf[t][:, :, None] * delta[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+        state[slot] = S.to(state.dtype)
+    return out.to(v.dtype)

@@ -35,6 +35,8 @@ class _SpecBase:
             raise RuntimeError("speculative decoding requires batch_size 1")
         if so["num_beams"] != 1:
             raise RuntimeError("speculative decoding does not support beam search")
+        if gen.model.arch.has_linear_layers:
+            raise RuntimeError("speculative decoding needs a cache that can drop rejected tokens; models with linear-attention layers keep a recurrent state")
         if gen._guidance is not None and gen._guidance.ff:
             raise RuntimeError("speculative decoding cannot be combined with guidance fast-forward tokens")
         self.gen = gen

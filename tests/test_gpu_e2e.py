@@ -445,3 +445,55 @@ def test_int8_kv_cache_on_gpu(dirs):
             engine.remove_request(r)
     ops.check_kernel_status()
     assert n >= 3 * 10
+
+
+def test_gated_delta_hybrid_model_on_gpu(tmp_path):
+    """A hybrid of gated-delta-net and attention layers in bf16 on the GPU (paged convolution window + recurrent-state slots,
+    recurrence kernel) against the fp32 CPU run of the same checkpoint; engine requests share steps and keep their own states."""
+    import copy
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+    arch = ArchConfig(model_type="qwen3_next", vocab_size=512, hidden_size=256, num_layers=4, num_heads=4, num_kv_heads=2, head_dim=64,
+                      intermediate_size=512, context_length=256, bos_token_id=0, eos_token_id=511, pad_token_id=0,
+                      layer_types=["linear_attention", "linear_attention", "full_attention", "linear_attention"],
+                      linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4)
+    sd = random_state_dict(arch, seed=11, std=0.06)
+    cpu_dir, gpu_dir = str(tmp_path / "cpu"), str(tmp_path / "gpu")
+    export_model(copy.deepcopy(arch), cpu_dir, "fp32", "cpu", state_dict=sd, paged=True, block_size=16, num_blocks=64, max_batch_size=4)
+    export_model(copy.deepcopy(arch), gpu_dir, "bf16", "cuda", state_dict=sd, paged=True, block_size=16, num_blocks=64, max_batch_size=4)
+    prompt = np.random.RandomState(2).randint(1, 500, size=(1, 37)).astype(np.int32)
+    outs = {}
+    for name, d in (("cpu", cpu_dir), ("gpu", gpu_dir)):
+        cfg = og.Config(d)
+        model = og.Model(cfg)
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=64, do_sample=False)
+        g = og.Generator(model, p)
+        g.append_tokens(prompt)
+        first = g.get_logits().reshape(-1).copy()
+        for _ in range(4):
+            g.generate_next_token()
+        outs[name] = (first, g.get_logits().reshape(-1).copy())
+        if name == "gpu":
+            eng = og.Engine(model)
+            reqs = []
+            for n in (37, 9):
+                gp = og.GeneratorParams(model)
+                gp.set_search_options(max_length=n + 6, do_sample=False)
+                r = og.Request(gp)
+                r.add_tokens(prompt[0, :n])
+                eng.add_request(r)
+                reqs.append(r)
+            toks = [[] for _ in reqs]
+            for _ in range(100):
+                if not eng.has_pending_requests():
+                    break
+                eng.step()
+                for j, r in enumerate(reqs):
+                    while r.has_unseen_tokens():
+                        toks[j].append(r.get_unseen_token())
+            assert all(len(t) == 6 for t in toks)
+            assert toks[0][0] == int(np.argmax(first))          # the engine's first token of the long request = the generator's
+    for a_, b_ in zip(outs["cpu"], outs["gpu"]):
+        assert np.abs(a_ - b_).max() < 0.08 * a_.std() + 0.05
+    ops.check_kernel_status()

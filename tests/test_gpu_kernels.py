@@ -984,3 +984,28 @@ def test_verify_sampled_multi_token_and_bonus():
     # twice in a row: the kernel's completion counter resets itself
     b = ops.verify_sampled(x, [worst, draft[1], draft[2], draft[3]], [None] * 4, k, 0.95, 0.7, seed=12, first_position=30)
     assert b[0] == a and b[1] == commit
+
+
+@pytest.mark.parametrize("Hk,Hv,dk,dv", [(2, 4, 16, 16), (4, 4, 64, 64), (2, 8, 128, 128), (1, 2, 32, 96)])
+def test_gated_delta_rule_kernel(Hk, Hv, dk, dv):
+    """The recurrence of a linear-attention layer: prompt chunks, single tokens, a fresh request (state reset) and requests that
+    continue from their slot's state, against the fp32 restatement."""
+    torch.manual_seed(3)
+    q_lens, past = [7, 1, 19, 1], [0, 5, 12, 0]
+    T, B = sum(q_lens), len(q_lens)
+    q = torch.nn.functional.normalize(torch.randn(T, Hk, dk), dim=-1).to(torch.bfloat16).to(DEV)
+    k = torch.nn.functional.normalize(torch.randn(T, Hk, dk), dim=-1).to(torch.bfloat16).to(DEV)
+    v = torch.randn(T, Hv, dv).to(torch.bfloat16).to(DEV)
+    g = (-torch.rand(T, Hv) * 0.5).to(DEV)
+    beta = torch.rand(T, Hv).to(DEV)
+    state = torch.randn(6, Hv, dk, dv, device=DEV) * 0.1
+    slots = torch.tensor([4, 0, 2, 5], dtype=torch.int32, device=DEV)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=DEV)
+    pl = torch.tensor(past, dtype=torch.int32, device=DEV)
+    want_state = state.cpu().clone()
+    want = ref.gated_delta(q.cpu(), k.cpu(), v.cpu(), g.cpu(), beta.cpu(), want_state, slots.cpu(), cu.cpu(), pl.cpu())
+    got = ops.gated_delta(q, k, v, g, beta, state, slots, cu, pl)
+    _close(got, want, rtol=2e-2, atol=2e-2)
+    _close(state, want_state, rtol=1e-3, atol=1e-3)
+    assert torch.equal(state[1].cpu(), want_state[1]) and torch.equal(state[3].cpu(), want_state[3])     # untouched slots
+    ops.check_kernel_status()
