@@ -16,11 +16,10 @@
 // (PTX `mul.bf16x2` keeps subnormal inputs).  The multiplier byte stored in the record is that power's bf16
 // exponent field, scale + 126; scale codes above 128 cannot be represented and are refused by the packer.
 //
-// fp16 form (the default when every block scale lies in 2^-14 .. 2^13): the tensor cores run fp16 x fp16 with the
-// activations converted to fp16 by the row gather (and by the gate/up epilogue for the down projection), the
-// nibbles stay in their natural order and `cvt.rn.f16x2.e2m1x2` expands two codes per instruction; the multiplier
-// byte is then the fp16 exponent field of 2^(scale - 127), scale - 112.  One conversion and one multiply per pair
-// of weights instead of six integer / bf16 operations: the expansion stops being the limit of the weight stream.
+// fp16 form (the default when every block scale lies in 2^-14 .. 2^1): the tensor cores run fp16 x fp16 with the
+// activations converted to fp16 by the row gather (and by the gate/up epilogue for the down projection); the same nibble
+// order, the magnitude bits placed at bits 11..9 of an fp16 (e2m1 * 2^-14) and the multiplier byte the fp16 exponent
+// field of 2^14 * 2^(scale - 127), scale - 98.
 //
 // Pipeline and epilogue are those of the int4 kernel (gemm_w4.cu): warp 0 streams records through a deep ring and the
 // activation tiles through a ring of their own (4 or 8 deep), warps 2..9 expand a record into the swizzled K-major tile,
@@ -85,21 +84,30 @@ __device__ __forceinline__ uint32_t deq_fp4_pair(uint32_t u, __nv_bfloat162 s2) 
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// four bytes of e2m1 pairs (low nibble = first element) -> four fp16x2 registers times the block's multiplier
+// fp16 form.  A record word holds eight consecutive k values: element i < 4 in nibble 2i (the low nibbles of its four
+// bytes), element 4 + i in nibble 2i + 1.  For the kernel below the bytes are regrouped (two byte permutes) so that the
+// codes (2j, 2j + 1) sit in the same nibble of the low and of the high half of a register; the three magnitude bits of a
+// code placed at bits 11..9 of an fp16 are the number e2m1 * 2^-14 (code 1 lands on the subnormal 2^-15 exactly as e2m1's
+// own subnormal 0.5), the sign bit goes to bit 15: two shifts and two logic operations per pair on the integer pipes,
+// then one `mul.f16x2` by 2^14 * 2^(scale - 127) (fp16 multiplies keep subnormal inputs).  `cvt.rn.f16x2.e2m1x2` does the
+// same in one step but runs on the conversion unit at a quarter of the rate.
+template <int J>
+__device__ __forceinline__ uint32_t e2m1_pair_f16_bits(uint32_t w) {
+  const uint32_t mag = (J < 3 ? (w << (9 - 4 * (J < 3 ? J : 0))) : (w >> 3)) & 0x0E000E00u;
+  const uint32_t sgn = (w << (12 - 4 * J)) & 0x80008000u;
+  return mag | sgn;
+}
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+  __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// eight codes of a record word -> four fp16x2 registers (consecutive k) times the block's multiplier
 __device__ __forceinline__ uint4 deq_fp4_word_f16(uint32_t word, __half2 s2) {
-  uint32_t h0, h1, h2, h3;
-  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
-      : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(word));
-  auto mul = [&](uint32_t h) {
-    __half2 v = __hmul2(*reinterpret_cast<__half2*>(&h), s2);
-    return *reinterpret_cast<uint32_t*>(&v);
-  };
-  return make_uint4(mul(h0), mul(h1), mul(h2), mul(h3));
+  const uint32_t s = *reinterpret_cast<uint32_t*>(&s2);
+  const uint32_t x01 = __byte_perm(word, 0u, 0x4140);   // bytes 0, 1 -> the two halves: nibble 0 = k 0, 1; nibble 1 = k 4, 5
+  const uint32_t x23 = __byte_perm(word, 0u, 0x4342);   // bytes 2, 3: nibble 0 = k 2, 3; nibble 1 = k 6, 7
+  return make_uint4(hmul2_bits(e2m1_pair_f16_bits<0>(x01), s), hmul2_bits(e2m1_pair_f16_bits<0>(x23), s),
+                    hmul2_bits(e2m1_pair_f16_bits<1>(x01), s), hmul2_bits(e2m1_pair_f16_bits<1>(x23), s));
 }
 
 // FP4_WBUF: expanded weight tiles in flight; GROUPS: 1 = all eight expander warps share every k-block (two threads per
@@ -107,7 +115,8 @@ __device__ __forceinline__ uint4 deq_fp4_word_f16(uint32_t word, __half2 s2) {
 template <int BT, bool HALF, int FP4_WBUF, int GROUPS, int NACC>
 __global__ void __launch_bounds__(FP4_THREADS, Fp4Cfg<BT, FP4_WBUF>::TWO_PER_SM ? 2 : 1)
 gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                        const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, int w_by_tma, const GemmParams p) {
+                        const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, int w_by_tma, int skip_rows_le,
+                        const GemmParams p) {
   using Cfg = Fp4Cfg<BT, FP4_WBUF>;
   constexpr int RAW = Cfg::RAW;
   constexpr int ARRIVALS = FP4_DEQ_WARPS / GROUPS;
@@ -139,6 +148,7 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const int row0 = p.grp.tile_row0[m_tile];
   const int rows = p.grp.tile_rows[m_tile];
   const int expert = p.grp.tile_expert[m_tile];
+  if (rows <= skip_rows_le) return;         // this tile belongs to the streaming kernel below (uniform over the CTA)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RAW; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], ARRIVALS); }
@@ -243,8 +253,10 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       if constexpr (HALF) {
 #pragma unroll
         for (int jj = 0; jj < WORDS; ++jj) {
-          const int j = part * 4 + jj;
-          const uint32_t m8 = j < 4 ? (mul & 0xFFu) : (mul >> 8);
+          const int rw = part * 4 + jj;                       // word of the record: (q, b) = (rw / 2, rw % 2)
+          const int j = 4 * (rw & 1) + (rw >> 1);             // the 16-byte chunk (8 k values) of the tile row it expands to
+          // the byte is the fp32 exponent field of 2^6 * scale (code + 6); fp16 exponent field of 2^14 * scale = code - 98
+          const uint32_t m8 = ((rw & 1) ? (mul >> 8) : (mul & 0xFFu)) - 104u;
           const uint32_t sb = (m8 << 10) | (m8 << 26);
           *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = deq_fp4_word_f16(words[jj], *reinterpret_cast<const __half2*>(&sb));
         }
@@ -279,12 +291,263 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   if (warp == 2) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Streaming form for 16-token tiles (decode steps: with 4 of 32 experts per token an expert sees one to a handful of
+// tokens).  The kernel above pays the expansion of a whole 128 x 64 tile through shared memory (32 bits of shared-memory
+// traffic per 4.25-bit weight, and a chain of four barriers per k-block between its roles) whatever the number of tokens.
+// Here the expanded weights never touch shared memory:
+//   * One thread streams the packed records, two per stage, through a ring of FP4_STREAM_STAGES bulk copies
+//     (asynchronous, tracked by mbarriers: the copies in flight do not depend on what a warp can keep outstanding
+//     through its registers).
+//   * Each of the eight consumer warps owns 16 weight rows of the record and feeds warp-level `mma.m16n8k16` (fp16 in,
+//     fp32 accumulate) straight from registers: a byte of a record word holds the codes of k values i and 4 + i, one
+//     `cvt.rn.f16x2.e2m1x2` turns it into an A register, one `mul.f16x2` applies the block's power of two.
+//   * The contraction does not care which k value sits in which slot of the instruction as long as both operands agree:
+//     lane q = lane % 4 takes the 8 consecutive k values [8 q, 8 q + 8) of each block of 32 (one word of the record), and
+//     the activations (up to 8 token rows per pass) are staged in shared memory in the matching order (x0 x4 x1 x5 x2 x6
+//     x3 x7 of each group of eight), so a lane's B registers for a block are one 16-byte read.
+// The 5th-generation tensor-core instruction cannot take this shape economically: its A operand would have to be written
+// to tensor or shared memory first, which is the cost this form exists to avoid.  Tiles of 9..16 rows take a second pass,
+// which finds the records in L2.  Every wait is bounded; after a failed wait the warps skip their work but still meet at
+// the pass barriers, and the producer waits for its copies in flight before the CTA leaves.
+constexpr int FP4_STREAM_CONSUMERS = 8;      // warps 0..7, 16 weight rows each; warp 8 is the producer
+constexpr int FP4_STREAM_THREADS = (FP4_STREAM_CONSUMERS + 1) * 32;
+constexpr int FP4_STREAM_TOKENS = 8;         // token rows per pass (the N of the instruction)
+constexpr int FP4_STREAM_STAGES = 6;         // stages of two records in flight per CTA
+constexpr int FP4_STREAM_STAGE_BYTES = 2 * FP4_RECORD_BYTES;
+constexpr int FP4_STREAM_MAX_K = 8192;
+constexpr int FP4_STREAM_XPAD = 64;          // bytes added to a staged row: the rows of a quarter warp fall on different banks
+constexpr int FP4_STREAM_RING_BYTES = FP4_STREAM_STAGES * FP4_STREAM_STAGE_BYTES;
+constexpr int FP4_STREAM_RES_BYTES = FP4_STREAM_TOKENS * GEMM_BLOCK_N * 4;
+constexpr int FP4_STREAM_FIXED_BYTES = FP4_STREAM_RING_BYTES + FP4_STREAM_RES_BYTES + 256;   // + barriers, abort flag
+constexpr int FP4_STREAM_SMEM_MAX = FP4_STREAM_FIXED_BYTES + FP4_STREAM_TOKENS * (FP4_STREAM_MAX_K * 2 + FP4_STREAM_XPAD);
+
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// the four bytes of a record word -> four fp16x2 registers: byte i = (k value i, k value 4 + i)
+__device__ __forceinline__ void cvt_e2m1x8_f16(uint32_t word, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(word));
+}
+
+__global__ void __launch_bounds__(FP4_STREAM_THREADS, 2)
+fp4_stream_grouped_kernel(const __half* __restrict__ A, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, int stage_rows,
+                          const GemmParams p) {
+  extern __shared__ __align__(128) uint8_t stream_smem[];
+  const int K = p.K, num_kb = p.total_kb;
+  const int xld = K * 2 + FP4_STREAM_XPAD;                                                  // bytes of a staged row
+  uint8_t* ring = stream_smem;                                                               // [STAGES][2][4352]
+  float* res = reinterpret_cast<float*>(stream_smem + FP4_STREAM_RING_BYTES);               // [TOKENS][128]
+  uint64_t* full = reinterpret_cast<uint64_t*>(stream_smem + FP4_STREAM_RING_BYTES + FP4_STREAM_RES_BYTES);
+  uint64_t* empty = full + FP4_STREAM_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + FP4_STREAM_STAGES);
+  uint8_t* xs = stream_smem + FP4_STREAM_FIXED_BYTES;                                        // [stage_rows][K / 8 groups][x0 x4 x1 x5 x2 x6 x3 x7]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  if (p.pdl) pdl_wait();                     // the tile list is written by the kernel before this one
+  if (m_tile >= *p.grp.num_tiles) return;
+  const int rows = p.grp.tile_rows[m_tile];
+  if (rows <= 0) return;
+  const int row0 = p.grp.tile_row0[m_tile];
+  const int expert = p.grp.tile_expert[m_tile];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < FP4_STREAM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], FP4_STREAM_CONSUMERS); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (p.pdl) pdl_launch_dependents();
+  auto fail = [&](int code) { atomicMax(p.status, code); *abort_flag = 1; };
+
+  const int pass_rows = min(FP4_STREAM_TOKENS, stage_rows);
+  const int passes = (rows + pass_rows - 1) / pass_rows;
+  const int pairs = (num_kb + 1) >> 1;        // stages per pass: two k-blocks each (the last one may hold a single record)
+  const uint8_t* rec0 = wpacked + (size_t(expert) * num_kb * n_tiles_per_expert + n_tile) * FP4_RECORD_BYTES;
+  const size_t rec_stride = size_t(n_tiles_per_expert) * FP4_RECORD_BYTES;
+
+  if (warp == FP4_STREAM_CONSUMERS) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer
+      int issued = 0, s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int pass = 0; pass < passes && ok; ++pass) {
+        for (int pr = 0; pr < pairs; ++pr) {
+          if (issued >= FP4_STREAM_STAGES) ok = mbar_wait_bounded(&empty[s], phase ^ 1, abort_flag);
+          if (!ok) { fail(OGB_ERR_WAIT_TMA); break; }
+          const int nk = min(2, num_kb - 2 * pr);
+          mbar_expect_tx(&full[s], uint32_t(nk) * FP4_RECORD_BYTES);
+          for (int r = 0; r < nk; ++r)
+            fp4_bulk_copy_g2s(ring + s * FP4_STREAM_STAGE_BYTES + r * FP4_RECORD_BYTES, rec0 + size_t(2 * pr + r) * rec_stride, FP4_RECORD_BYTES,
+                              &full[s]);
+          ++issued;
+          if (++s == FP4_STREAM_STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {   // nothing of this CTA's shared memory may be handed on while a copy is still landing
+        volatile int never = 0;
+        for (int i = max(0, issued - FP4_STREAM_STAGES); i < issued; ++i)
+          mbar_wait_bounded(&full[i % FP4_STREAM_STAGES], (i / FP4_STREAM_STAGES) & 1, &never, 200000000ull);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers (256 threads, named barrier 1)
+  const int ct = threadIdx.x;                // 0..255
+  const int slab = warp * 16;                // rows g and g + 8 of this slab
+  const int pair = p.act_pair != 0;
+  const int woff = (slab + g) * 32 + q * 8;                  // row g: words (q, 0) and (q, 1); row g + 8 is 256 bytes further
+  const int soff = GEMM_BLOCK_N * 32 + (slab + g) * 2;       // the two multiplier bytes of row g; row g + 8 is 16 bytes further
+  auto consumer_sync = [] { asm volatile("bar.sync 1, 256;" ::: "memory"); };
+  bool ok = true;
+  int s = 0;
+  uint32_t phase = 0;
+  for (int c = 0; c < rows; c += pass_rows) {
+    const int nrows = min(pass_rows, rows - c);
+    {
+      const int groups = K >> 3;             // groups of 8 k values per row
+      for (int i = ct; i < pass_rows * groups; i += FP4_STREAM_CONSUMERS * 32) {
+        const int t = i / groups, v = i - t * groups;
+        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+        if (t < nrows) x = *reinterpret_cast<const uint4*>(A + size_t(row0 + c + t) * lda + v * 8);
+        // (x0 x1)(x2 x3)(x4 x5)(x6 x7) -> (x0 x4)(x1 x5)(x2 x6)(x3 x7)
+        const uint4 y = make_uint4(__byte_perm(x.x, x.z, 0x5410), __byte_perm(x.x, x.z, 0x7632), __byte_perm(x.y, x.w, 0x5410), __byte_perm(x.y, x.w, 0x7632));
+        *reinterpret_cast<uint4*>(xs + size_t(t) * xld + v * 16) = y;
+      }
+    }
+    consumer_sync();
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // token g of the pass (rows past the staged ones read row 0: their columns of the product are never stored)
+    const uint8_t* xrow = xs + size_t(g < pass_rows ? g : 0) * xld + q * 16;
+    for (int pr = 0; pr < pairs; ++pr) {
+      ok = ok && mbar_wait_bounded(&full[s], phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int nk = min(2, num_kb - 2 * pr);
+      uint2 ca[2], cb[2];
+      uint32_t ma[2], mb[2];
+      uint4 x0[2], x1[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (r < nk) {
+          const uint8_t* rec = ring + s * FP4_STREAM_STAGE_BYTES + r * FP4_RECORD_BYTES;
+          ca[r] = *reinterpret_cast<const uint2*>(rec + woff);          // .x: block 0, .y: block 1 of row g
+          cb[r] = *reinterpret_cast<const uint2*>(rec + woff + 256);    // row g + 8
+          ma[r] = *reinterpret_cast<const uint16_t*>(rec + soff);
+          mb[r] = *reinterpret_cast<const uint16_t*>(rec + soff + 16);
+          x0[r] = *reinterpret_cast<const uint4*>(xrow + (2 * pr + r) * 128);        // block 0
+          x1[r] = *reinterpret_cast<const uint4*>(xrow + (2 * pr + r) * 128 + 64);   // block 1
+        }
+      }
+      // the records' bytes are in registers: hand the stage back before the arithmetic
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      if (++s == FP4_STREAM_STAGES) { s = 0; phase ^= 1; }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (r < nk) {
+          // the stored byte is code + 6; the fp16 exponent field of 2^(code - 127) is code - 112
+          const uint32_t sa0 = ((ma[r] & 0xFFu) - 118u) * 0x04000400u, sa1 = ((ma[r] >> 8) - 118u) * 0x04000400u;
+          const uint32_t sb0 = ((mb[r] & 0xFFu) - 118u) * 0x04000400u, sb1 = ((mb[r] >> 8) - 118u) * 0x04000400u;
+          uint32_t wa[4], wb[4];
+          cvt_e2m1x8_f16(ca[r].x, wa); cvt_e2m1x8_f16(cb[r].x, wb);
+          mma_m16n8k16_f16(acc, hmul2_bits(wa[0], sa0), hmul2_bits(wb[0], sb0), hmul2_bits(wa[1], sa0), hmul2_bits(wb[1], sb0), x0[r].x, x0[r].y);
+          mma_m16n8k16_f16(acc, hmul2_bits(wa[2], sa0), hmul2_bits(wb[2], sb0), hmul2_bits(wa[3], sa0), hmul2_bits(wb[3], sb0), x0[r].z, x0[r].w);
+          cvt_e2m1x8_f16(ca[r].y, wa); cvt_e2m1x8_f16(cb[r].y, wb);
+          mma_m16n8k16_f16(acc, hmul2_bits(wa[0], sa1), hmul2_bits(wb[0], sb1), hmul2_bits(wa[1], sa1), hmul2_bits(wb[1], sb1), x1[r].x, x1[r].y);
+          mma_m16n8k16_f16(acc, hmul2_bits(wa[2], sa1), hmul2_bits(wb[2], sb1), hmul2_bits(wa[3], sa1), hmul2_bits(wb[3], sb1), x1[r].z, x1[r].w);
+        }
+      }
+    }
+    if (!ok && lane == 0) fail(OGB_ERR_WAIT_TMA);
+    // accumulator fragment: rows g and g + 8 of the slab, tokens 2 q and 2 q + 1 of the pass
+    res[(2 * q) * GEMM_BLOCK_N + slab + g] = acc[0];
+    res[(2 * q + 1) * GEMM_BLOCK_N + slab + g] = acc[1];
+    res[(2 * q) * GEMM_BLOCK_N + slab + g + 8] = acc[2];
+    res[(2 * q + 1) * GEMM_BLOCK_N + slab + g + 8] = acc[3];
+    consumer_sync();
+
+    if (*abort_flag == 0) {
+      auto store = [&](int m, int col, float v) {
+        if (p.out_fp32 == 1) reinterpret_cast<float*>(p.C)[size_t(m) * p.ldc + col] = v;
+        else if (p.out_fp32 == 2) reinterpret_cast<__half*>(p.C)[size_t(m) * p.ldc + col] = __float2half_rn(v);
+        else reinterpret_cast<__nv_bfloat16*>(p.C)[size_t(m) * p.ldc + col] = __float2bfloat16_rn(v);
+      };
+      const int bias_off = expert * p.N + n_tile * GEMM_BLOCK_N;
+      if (pair) {
+        // res[t][0..63] = gate rows, res[t][64..127] = up rows of the same 64 features
+        for (int item = ct; item < FP4_STREAM_TOKENS * 64; item += FP4_STREAM_CONSUMERS * 32) {
+          const int t = item >> 6, i = item & 63;
+          const int col = n_tile * 64 + i;
+          if (t < nrows && col < p.N / 2) {
+            float gt = res[t * GEMM_BLOCK_N + i], up = res[t * GEMM_BLOCK_N + 64 + i];
+            if (p.bias) { gt += bf2f(p.bias[bias_off + i]); up += bf2f(p.bias[bias_off + 64 + i]); }
+            float v;
+            if (p.act_pair == 1) {
+              v = silu(gt) * up;
+            } else {
+              const float gc = p.act_limit > 0.f ? fminf(gt, p.act_limit) : gt;
+              const float uc = p.act_limit > 0.f ? fminf(fmaxf(up, -p.act_limit), p.act_limit) : up;
+              v = gc / (1.f + __expf(-p.act_alpha * gc)) * (uc + 1.f);
+            }
+            store(row0 + c + t, col, v);
+          }
+        }
+      } else {
+        for (int item = ct; item < FP4_STREAM_TOKENS * GEMM_BLOCK_N; item += FP4_STREAM_CONSUMERS * 32) {
+          const int t = item >> 7, i = item & 127;
+          const int col = n_tile * GEMM_BLOCK_N + i;
+          if (t < nrows && col < p.N) {
+            float v = res[t * GEMM_BLOCK_N + i];
+            if (p.bias) v += bf2f(p.bias[bias_off + i]);
+            store(row0 + c + t, col, v);
+          }
+        }
+      }
+    }
+    consumer_sync();   // res and xs are rewritten by the next pass
+  }
+}
+
+// stage_rows: token rows staged per pass (1..8): an upper bound on the rows of any tile when the host knows one, else 8
+static int LaunchFp4Stream(const void* A, int lda, const uint8_t* wp, int n_tiles, const GemmParams& p, int max_tiles, int stage_rows,
+                           cudaStream_t stream) {
+  static bool configured[OGB_MAX_DEVICES] = {};
+  if (!set_max_dyn_smem(fp4_stream_grouped_kernel, FP4_STREAM_SMEM_MAX, configured)) return -3;
+  const size_t smem = size_t(FP4_STREAM_FIXED_BYTES) + size_t(stage_rows) * (size_t(p.K) * 2 + FP4_STREAM_XPAD);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles, max_tiles, 1);
+  cfg.blockDim = dim3(FP4_STREAM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  int na = 0;
+  if (p.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = unsigned(na);
+  return cudaLaunchKernelEx(&cfg, fp4_stream_grouped_kernel, static_cast<const __half*>(A), lda, wp, n_tiles, stage_rows, p) == cudaSuccess ? 0 : -4;
+}
+
 bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
 bool MakeMapBytes128(CUtensorMap* out, const void* ptr, long long rows, int box_rows);          // gemm_tcgen05.cu
 
 template <int BT, bool HALF, int WBUF, int GROUPS, int NACC>
-static int LaunchFp4V(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid,
-                      cudaStream_t stream) {
+static int LaunchFp4V(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, int skip, const GemmParams& p,
+                      dim3 grid, cudaStream_t stream) {
   using Cfg = Fp4Cfg<BT, WBUF>;
   static_assert(NACC <= Fp4Cfg<BT, WBUF>::NACC_MAX, "not enough tensor memory for the accumulators");
   auto kern = gemm_fp4_grouped_kernel<BT, HALF, WBUF, GROUPS, NACC>;
@@ -304,18 +567,18 @@ static int LaunchFp4V(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma
   }
   cfg.attrs = attrs;
   cfg.numAttrs = unsigned(na);
-  return cudaLaunchKernelEx(&cfg, kern, ta, tw, wp, n_tiles, w_by_tma, p) == cudaSuccess ? 0 : -4;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tw, wp, n_tiles, w_by_tma, skip, p) == cudaSuccess ? 0 : -4;
 }
 
 template <int BT, bool HALF>
-static int LaunchFp4(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, const GemmParams& p, dim3 grid,
-                     cudaStream_t stream) {
+static int LaunchFp4(const CUtensorMap& ta, const CUtensorMap& tw, int w_by_tma, const uint8_t* wp, int n_tiles, int skip, const GemmParams& p,
+                     dim3 grid, cudaStream_t stream) {
   // 16-token tiles: four expanded tiles in flight, the expander warps in two groups that alternate k-blocks, four
   // accumulators; larger tiles: two expanded tiles, one group, one accumulator.  Measured on B200 (gate/up of gpt-oss-20b,
   // 32 tokens): 131 us against 142 us for the single-group forms - the kernel is bound by the rate at which the tensor
   // core retires 128 x 16 x 16 instructions, not by the expansion, the copies or the accumulator chain.
-  if constexpr (BT <= 16) return LaunchFp4V<BT, HALF, 4, 2, 4>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-  return LaunchFp4V<BT, HALF, 2, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+  if constexpr (BT <= 16) return LaunchFp4V<BT, HALF, 4, 2, 4>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
+  return LaunchFp4V<BT, HALF, 2, 1, 1>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
 }
 
 }  // namespace ogb
@@ -362,12 +625,20 @@ OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* 
   const int w_by_tma = 0;
   dim3 grid(n_tiles, max_tiles, 1);
   const uint8_t* wp = static_cast<const uint8_t*>(Wpacked);
+  // 16-token tiles of the fp16 form (decode steps) go to the streaming kernel; OGB_FP4_STREAM=0 keeps them on the kernel
+  // that expands through shared memory.
+  static const int stream_enabled = [] { const char* e = getenv("OGB_FP4_STREAM"); return (e && e[0] == '0') ? 0 : 1; }();
+  const int skip = 0;
+  if (stream_enabled && half && bt == 16 && K <= FP4_STREAM_MAX_K && max_tiles <= 65535) {
+    const int stage_rows = max_rows_per_tile > 0 && max_rows_per_tile < FP4_STREAM_TOKENS ? max_rows_per_tile : FP4_STREAM_TOKENS;
+    return LaunchFp4Stream(A, lda, wp, n_tiles, p, max_tiles, stage_rows, stream);
+  }
   switch (bt) {
-    case 16: return half ? LaunchFp4<16, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<16, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    case 32: return half ? LaunchFp4<32, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<32, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    case 64: return half ? LaunchFp4<64, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<64, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    case 128: return half ? LaunchFp4<128, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<128, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
-    case 256: return half ? LaunchFp4<256, true>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream) : LaunchFp4<256, false>(ta, tw, w_by_tma, wp, n_tiles, p, grid, stream);
+    case 16: return half ? LaunchFp4<16, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<16, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
+    case 32: return half ? LaunchFp4<32, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<32, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
+    case 64: return half ? LaunchFp4<64, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<64, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
+    case 128: return half ? LaunchFp4<128, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<128, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
+    case 256: return half ? LaunchFp4<256, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<256, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
   }
   return -5;
 }

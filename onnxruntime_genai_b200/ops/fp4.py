@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 RECORD = 128 * 32 + 128 * 2
-F16_SCALE_CODES = (113, 140)   # fp16 form: 2^(code - 127) must be a normal fp16 and 6 * scale finite
+F16_SCALE_CODES = (113, 128)   # fp16 form: 0.5 * 2^(code - 127) an exact fp16 and the multiplier 2^(code - 113) a finite one
 E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 MAX_SCALE_CODE = 128   # 2^(code - 1) must be a finite bf16: the kernel multiplies by 2^126 * 2^(code - 127)
 
@@ -33,7 +33,7 @@ class Fp4Experts:
 
     def __init__(self, packed: torch.Tensor, E: int, N: int, K: int, codes, scale_codes, half: bool = False):
         self.packed, self.E, self.N, self.K = packed, E, N, K
-        self.half = half       # fp16 form: natural nibble order, fp16 multipliers, fp16 activations
+        self.half = half       # fp16 form: fp16 multipliers, fp16 activations
         self._codes, self._scales = codes, scale_codes
         self.shape = (E, N, K)
         self.dtype = torch.bfloat16
@@ -67,26 +67,32 @@ class Fp4Experts:
         if half is None:
             half = Fp4Experts.fits_fp16(codes, scale_codes)
         if half:
-            assert Fp4Experts.fits_fp16(codes, scale_codes), "block scale outside 2^-14 .. 2^13"
+            assert Fp4Experts.fits_fp16(codes, scale_codes), "block scale outside 2^-14 .. 2^1"
         else:
             assert int(scale_codes.max()) <= MAX_SCALE_CODE, "block scale above 2^1 cannot be folded into a bf16 multiplier"
         dev = codes.device
         nb = K // 32
         Np = (N + 127) // 128 * 128
         parts = []
-        order = [0, 4, 8, 12, 16, 20, 24, 28] if half else [0, 16, 4, 20, 8, 24, 12, 28]
+        # bf16 form: element m of a word at pair p = m // 2, bit 4p, second element of the pair 16 bits higher.
+        # fp16 form: element i < 4 at nibble 2i, element 4 + i at nibble 2i + 1 (the even nibbles of a word are four
+        # consecutive k values, the odd nibbles the next four), and the eight words of a row's 64 k values are stored in
+        # the order (q, b) -> word 2q + b holds k = 32b + 8q .. + 8: the 16 codes that one lane of the streaming kernel
+        # needs (8 of each block of 32) are 8 contiguous bytes.
+        order = [0, 8, 16, 24, 4, 12, 20, 28] if half else [0, 16, 4, 20, 8, 24, 12, 28]
         shifts = torch.tensor(order, dtype=torch.int64, device=dev)
+        word_src = torch.tensor([4 * (w & 1) + (w >> 1) for w in range(8)], dtype=torch.int64, device=dev)   # record word -> k chunk
         for e in range(E):   # one expert at a time bounds the int64 temporaries
             qp = torch.zeros(Np, K, dtype=torch.int64, device=dev)
             qp[:N] = codes[e].to(torch.int64)
-            # bf16 form: nibble m of a word: pair p = m // 2 at bit 4p, second element of the pair 16 bits higher;
-            # fp16 form: natural order (element m at bit 4m)
             words = (qp.view(Np, K // 8, 8) << shifts).sum(-1)
+            if half:
+                words = words.view(Np, K // 64, 8)[:, :, word_src].reshape(Np, K // 8)
             b = torch.stack([(words >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.uint8)
             nib = b.view(Np // 128, 128, K // 64, 32).permute(2, 0, 1, 3)                 # [K/64, tiles, 128, 32]
             mul = torch.zeros(Np, nb, dtype=torch.uint8, device=dev)
-            if half:    # fp16 exponent field of 2^(code - 127); blocks of zeros may carry any scale
-                mul[:N] = (scale_codes[e].to(torch.int16) - 112).clamp(1, 28).to(torch.uint8)
+            if half:    # code + 6 (the kernels subtract to the fp16 exponent field they need); blocks of zeros may carry any scale
+                mul[:N] = (scale_codes[e].to(torch.int16).clamp(*F16_SCALE_CODES) + 6).to(torch.uint8)
             else:       # bf16 exponent field of 2^(code - 1)
                 mul[:N] = (scale_codes[e].to(torch.int16) + 126).to(torch.uint8)
             mt = mul.view(Np // 128, 128, K // 64, 2).permute(2, 0, 1, 3)

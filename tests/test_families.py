@@ -215,9 +215,10 @@ def test_mxfp4_expert_round_trip_and_model(tmp_path):
 
 def _read_fp4_records(packed: torch.Tensor, N: int, K: int, half: bool) -> torch.Tensor:
     """Restates on the host what csrc/gemm_fp4.cu does with a packed expert: thread = weight row reads 8 words and
-    2 multiplier bytes of a 4352-byte record.  bf16 form: pair p of word j is `(word >> 4p)` (low nibbles of the two
-    16-bit halves) and the e2m1 value * 2^-126 is multiplied by the bf16 whose exponent field is the multiplier byte.
-    fp16 form: byte p of word j holds the pair (low nibble first), multiplied by the fp16 whose exponent field is the byte."""
+    2 multiplier bytes of a 4352-byte record.  bf16 form: pair p of word j is `(word >> 4p)` (low nibbles of the two 16-bit
+    halves), words in k order, the e2m1 value * 2^-126 multiplied by the bf16 whose exponent field is the multiplier byte.
+    fp16 form: record word 2q + b holds k = 32b + 8q .. + 8, element i < 4 in nibble 2i and element 4 + i in nibble 2i + 1;
+    the e2m1 value times 2^(byte - 6 - 127)."""
     KB, tiles = packed.shape[0], packed.shape[1]
     rec = packed.view(KB, tiles, 128 * 34)
     nib = rec[:, :, :128 * 32].reshape(KB, tiles, 128, 8, 4).to(torch.int64)
@@ -226,11 +227,20 @@ def _read_fp4_records(packed: torch.Tensor, N: int, K: int, half: bool) -> torch
     grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=torch.float64)
     out = torch.zeros(tiles * 128, KB * 64, dtype=torch.float64)
     for j in range(8):
+        if half:
+            q, blk = j >> 1, j & 1
+            m = mul[..., blk]
+            s = torch.pow(2.0, m.double() - 127.0 - 6.0)
+            for i in range(8):
+                c = (words[..., j] >> (8 * i if i < 4 else 8 * (i - 4) + 4)) & 0xF
+                val = grid[c & 7] * torch.where(c >= 8, -1.0, 1.0) * s
+                out.view(tiles, 128, KB, 64)[:, :, :, 32 * blk + 8 * q + i] = val.permute(1, 2, 0)
+            continue
         m = mul[..., 0 if j < 4 else 1]
-        s = torch.where(m > 0, torch.pow(2.0, m.double() - (15.0 if half else 127.0 + 126.0)), torch.zeros((), dtype=torch.float64))
+        s = torch.where(m > 0, torch.pow(2.0, m.double() - (127.0 + 126.0)), torch.zeros((), dtype=torch.float64))
         for pr in range(4):
-            u = words[..., j] >> ((8 if half else 4) * pr)
-            for second, sh in ((0, 0), (1, 4 if half else 16)):
+            u = words[..., j] >> (4 * pr)
+            for second, sh in ((0, 0), (1, 16)):
                 c = (u >> sh) & 0xF
                 val = grid[c & 7] * torch.where(c >= 8, -1.0, 1.0) * s                               # [KB, tiles, 128]
                 k = j * 8 + pr * 2 + second
