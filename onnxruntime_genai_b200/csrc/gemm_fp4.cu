@@ -16,10 +16,12 @@
 // (PTX `mul.bf16x2` keeps subnormal inputs).  The multiplier byte stored in the record is that power's bf16
 // exponent field, scale + 126; scale codes above 128 cannot be represented and are refused by the packer.
 //
-// fp16 form (the default when every block scale lies in 2^-14 .. 2^1): the tensor cores run fp16 x fp16 with the
-// activations converted to fp16 by the row gather (and by the gate/up epilogue for the down projection); the same nibble
-// order, the magnitude bits placed at bits 11..9 of an fp16 (e2m1 * 2^-14) and the multiplier byte the fp16 exponent
-// field of 2^14 * 2^(scale - 127), scale - 98.
+// fp16 form (the default when every block scale lies in 2^-14 .. 2^13): the tensor cores run fp16 x fp16 with the
+// activations converted to fp16 by the row gather (and by the gate/up epilogue for the down projection).  A record word
+// holds eight consecutive k values, byte i = (element i, element 4 + i); the eight words of a row's 64 k values are stored
+// in the order (q, b) -> word 2q + b = k values 32b + 8q .. + 8, so that the 16 codes one lane of the streaming kernel
+// below needs are 8 contiguous bytes.  `cvt.rn.f16x2.e2m1x2` expands a byte, `mul.f16x2` applies the block scale; the
+// multiplier byte is scale code + 6 (the kernels subtract 118 to reach the fp16 exponent field of 2^(scale - 127)).
 //
 // Pipeline and epilogue are those of the int4 kernel (gemm_w4.cu): warp 0 streams records through a deep ring and the
 // activation tiles through a ring of their own (4 or 8 deep), warps 2..9 expand a record into the swizzled K-major tile,
@@ -32,8 +34,8 @@
 // have to be consumed every 190 cycles to keep up with HBM.  More expander warps, more expanded tiles in flight, a deeper
 // activation ring, tensor-map loads and four independent accumulators each left the time within 8 %.  The kernel
 // therefore streams its weights at about 0.33 of the HBM rate (1.25x faster than the bf16 experts, which move 3.8x the
-// bytes at the full rate).  The way past this limit is to put the weights on the instruction's N side (256 rows per
-// instruction, tokens padded to M = 64), which changes the accumulator layout and the epilogue; not done here.
+// bytes at the full rate).  It serves the larger token tiles (prompts); the 16-token tiles of decode steps go to the
+// streaming kernel further down, which keeps the expanded weights in registers.
 #include <cstdlib>
 
 #include <cuda_fp16.h>
@@ -84,18 +86,18 @@ __device__ __forceinline__ uint32_t deq_fp4_pair(uint32_t u, __nv_bfloat162 s2) 
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// fp16 form.  A record word holds eight consecutive k values: element i < 4 in nibble 2i (the low nibbles of its four
-// bytes), element 4 + i in nibble 2i + 1.  For the kernel below the bytes are regrouped (two byte permutes) so that the
-// codes (2j, 2j + 1) sit in the same nibble of the low and of the high half of a register; the three magnitude bits of a
-// code placed at bits 11..9 of an fp16 are the number e2m1 * 2^-14 (code 1 lands on the subnormal 2^-15 exactly as e2m1's
-// own subnormal 0.5), the sign bit goes to bit 15: two shifts and two logic operations per pair on the integer pipes,
-// then one `mul.f16x2` by 2^14 * 2^(scale - 127) (fp16 multiplies keep subnormal inputs).  `cvt.rn.f16x2.e2m1x2` does the
-// same in one step but runs on the conversion unit at a quarter of the rate.
-template <int J>
-__device__ __forceinline__ uint32_t e2m1_pair_f16_bits(uint32_t w) {
-  const uint32_t mag = (J < 3 ? (w << (9 - 4 * (J < 3 ? J : 0))) : (w >> 3)) & 0x0E000E00u;
-  const uint32_t sgn = (w << (12 - 4 * J)) & 0x80008000u;
-  return mag | sgn;
+// fp16 form.  A record word holds eight consecutive k values: byte i = (element i in the low nibble, element 4 + i in the
+// high nibble).  `cvt.rn.f16x2.e2m1x2` turns a byte into the fp16 pair (element i, element 4 + i); two byte permutes put
+// consecutive elements side by side for the K-major tile; one `mul.f16x2` applies the block's power of two.
+// the four bytes of a record word -> four fp16x2 registers: byte i = (k value i, k value 4 + i)
+__device__ __forceinline__ void cvt_e2m1x8_f16(uint32_t word, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(word));
 }
 __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
   __half2 v = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
@@ -104,10 +106,10 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
 // eight codes of a record word -> four fp16x2 registers (consecutive k) times the block's multiplier
 __device__ __forceinline__ uint4 deq_fp4_word_f16(uint32_t word, __half2 s2) {
   const uint32_t s = *reinterpret_cast<uint32_t*>(&s2);
-  const uint32_t x01 = __byte_perm(word, 0u, 0x4140);   // bytes 0, 1 -> the two halves: nibble 0 = k 0, 1; nibble 1 = k 4, 5
-  const uint32_t x23 = __byte_perm(word, 0u, 0x4342);   // bytes 2, 3: nibble 0 = k 2, 3; nibble 1 = k 6, 7
-  return make_uint4(hmul2_bits(e2m1_pair_f16_bits<0>(x01), s), hmul2_bits(e2m1_pair_f16_bits<0>(x23), s),
-                    hmul2_bits(e2m1_pair_f16_bits<1>(x01), s), hmul2_bits(e2m1_pair_f16_bits<1>(x23), s));
+  uint32_t h[4];
+  cvt_e2m1x8_f16(word, h);       // (k0 k4) (k1 k5) (k2 k6) (k3 k7)
+  return make_uint4(hmul2_bits(__byte_perm(h[0], h[1], 0x5410), s), hmul2_bits(__byte_perm(h[2], h[3], 0x5410), s),
+                    hmul2_bits(__byte_perm(h[0], h[1], 0x7632), s), hmul2_bits(__byte_perm(h[2], h[3], 0x7632), s));
 }
 
 // FP4_WBUF: expanded weight tiles in flight; GROUPS: 1 = all eight expander warps share every k-block (two threads per
@@ -255,8 +257,8 @@ gemm_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int jj = 0; jj < WORDS; ++jj) {
           const int rw = part * 4 + jj;                       // word of the record: (q, b) = (rw / 2, rw % 2)
           const int j = 4 * (rw & 1) + (rw >> 1);             // the 16-byte chunk (8 k values) of the tile row it expands to
-          // the byte is the fp32 exponent field of 2^6 * scale (code + 6); fp16 exponent field of 2^14 * scale = code - 98
-          const uint32_t m8 = ((rw & 1) ? (mul >> 8) : (mul & 0xFFu)) - 104u;
+          // the stored byte is code + 6; the fp16 exponent field of 2^(code - 127) is code - 112
+          const uint32_t m8 = ((rw & 1) ? (mul >> 8) : (mul & 0xFFu)) - 118u;
           const uint32_t sb = (m8 << 10) | (m8 << 26);
           *reinterpret_cast<uint4*>(dst + ((j ^ (row & 7)) << 4)) = deq_fp4_word_f16(words[jj], *reinterpret_cast<const __half2*>(&sb));
         }
@@ -326,17 +328,6 @@ __device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], uint32_t a0, uin
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// the four bytes of a record word -> four fp16x2 registers: byte i = (k value i, k value 4 + i)
-__device__ __forceinline__ void cvt_e2m1x8_f16(uint32_t word, uint32_t (&h)[4]) {
-  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
-      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
-      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
-      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(word));
-}
-
 __global__ void __launch_bounds__(FP4_STREAM_THREADS, 2)
 fp4_stream_grouped_kernel(const __half* __restrict__ A, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, int stage_rows,
                           const GemmParams p) {

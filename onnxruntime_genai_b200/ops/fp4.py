@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 RECORD = 128 * 32 + 128 * 2
-F16_SCALE_CODES = (113, 128)   # fp16 form: 0.5 * 2^(code - 127) an exact fp16 and the multiplier 2^(code - 113) a finite one
+F16_SCALE_CODES = (113, 140)   # fp16 form: 2^(code - 127) must be a normal fp16 and 6 * scale finite
 E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 MAX_SCALE_CODE = 128   # 2^(code - 1) must be a finite bf16: the kernel multiplies by 2^126 * 2^(code - 127)
 
@@ -67,7 +67,7 @@ class Fp4Experts:
         if half is None:
             half = Fp4Experts.fits_fp16(codes, scale_codes)
         if half:
-            assert Fp4Experts.fits_fp16(codes, scale_codes), "block scale outside 2^-14 .. 2^1"
+            assert Fp4Experts.fits_fp16(codes, scale_codes), "block scale outside 2^-14 .. 2^13"
         else:
             assert int(scale_codes.max()) <= MAX_SCALE_CODE, "block scale above 2^1 cannot be folded into a bf16 multiplier"
         dev = codes.device
