@@ -68,10 +68,20 @@ __global__ void embedding_q4_kernel(const int32_t* __restrict__ ids, const uint3
 // ------------------------------------------------------------------------------------ norm
 // One CTA per row. h = x (+ residual_in); residual_out = h (optional); out = norm(h) * w (+ b).
 // The row is kept in registers (up to 2 vectors of 8 bf16 per thread, hidden size <= 16384).
+// comb.y != nullptr: x is not read; the row is the weighted sum of the experts' output rows (the combine step of a
+// mixture-of-experts layer: row t = sum_j topk_w[t, j] * y[inv_pos[t, j]], rows of experts that are not local skipped),
+// summed in fp32 in j order and rounded to bf16 exactly as the stand-alone combine kernel stores it.
+struct NormCombine {
+  const __nv_bfloat16* y;
+  const int* inv_pos;
+  const float* topk_w;
+  int ldy, k;
+};
 template <bool LAYERNORM>
 __global__ void __launch_bounds__(1024) norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in,
                                                     uint4* __restrict__ res_out, const uint4* __restrict__ weight,
-                                                    const uint4* __restrict__ bias, uint4* __restrict__ out, int H, float eps) {
+                                                    const uint4* __restrict__ bias, uint4* __restrict__ out, int H, float eps,
+                                                    const NormCombine comb) {
   constexpr int MAXV = 2;
   pdl_launch_dependents();
   pdl_wait();
@@ -81,7 +91,22 @@ __global__ void __launch_bounds__(1024) norm_kernel(const uint4* __restrict__ x,
   float sum = 0.f, sumsq = 0.f;
   int cnt = 0;
   for (int i = threadIdx.x; i < nvec && cnt < MAXV; i += blockDim.x, ++cnt) {
-    uint4 a = xr[i];
+    uint4 a;
+    if (comb.y) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < comb.k; ++j) {
+        const int pos = comb.inv_pos[size_t(row) * comb.k + j];
+        if (pos < 0) continue;
+        const float w = comb.topk_w[size_t(row) * comb.k + j];
+        const uint4 q = *reinterpret_cast<const uint4*>(comb.y + size_t(pos) * comb.ldy + i * 8);
+        const float2 q0 = unpack_bf16x2(q.x), q1 = unpack_bf16x2(q.y), q2 = unpack_bf16x2(q.z), q3 = unpack_bf16x2(q.w);
+        acc[0] += w * q0.x; acc[1] += w * q0.y; acc[2] += w * q1.x; acc[3] += w * q1.y;
+        acc[4] += w * q2.x; acc[5] += w * q2.y; acc[6] += w * q3.x; acc[7] += w * q3.y;
+      }
+      a = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    } else {
+      a = xr[i];
+    }
     const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
     uint4 r = make_uint4(0, 0, 0, 0);
     if (res_in) r = res_in[size_t(row) * nvec + i];
@@ -439,8 +464,8 @@ OGB_API int ogb_embedding_q4(const int32_t* ids, const void* q, const void* scal
                     static_cast<uint4*>(out), K, vocab, mult) ? 0 : -4;
 }
 
-OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias,
-                     void* out, int rows, int H, float eps, int layernorm, void* stream) {
+static int LaunchNorm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias, void* out, int rows,
+                      int H, float eps, int layernorm, const NormCombine& comb, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8 || H / 8 > 8 * 1024) return -1;
   const int nvec = H / 8;
@@ -450,13 +475,28 @@ OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out,
   auto s = static_cast<cudaStream_t>(stream);
   if (layernorm)
     launch_pdl(norm_kernel<true>, dim3(rows), dim3(threads), 0, s, static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
-                                               static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight),
-                                               static_cast<const uint4*>(bias), static_cast<uint4*>(out), H, eps);
+               static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight), static_cast<const uint4*>(bias), static_cast<uint4*>(out),
+               H, eps, comb);
   else
     launch_pdl(norm_kernel<false>, dim3(rows), dim3(threads), 0, s, static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
-                                                static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight),
-                                                static_cast<const uint4*>(bias), static_cast<uint4*>(out), H, eps);
+               static_cast<uint4*>(residual_out), static_cast<const uint4*>(weight), static_cast<const uint4*>(bias), static_cast<uint4*>(out),
+               H, eps, comb);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+OGB_API int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias,
+                     void* out, int rows, int H, float eps, int layernorm, void* stream) {
+  return LaunchNorm(x, residual_in, residual_out, weight, bias, out, rows, H, eps, layernorm, NormCombine{nullptr, nullptr, nullptr, 0, 0}, stream);
+}
+
+// ogb_norm over rows that are still spread over the experts' outputs: row t = sum_j topk_w[t, j] * y[inv_pos[t, j]]
+// (what ogb_moe_combine would have written), then the residual add and the norm in the same launch.
+OGB_API int ogb_norm_moe_combine(const void* y, int ldy, const int32_t* inv_pos, const float* topk_w, int k, const void* residual_in,
+                                 void* residual_out, const void* weight, const void* bias, void* out, int rows, int H, float eps,
+                                 int layernorm, void* stream) {
+  if ((ldy % 8) || k <= 0 || (reinterpret_cast<uintptr_t>(y) & 15)) return -1;
+  return LaunchNorm(nullptr, residual_in, residual_out, weight, bias, out, rows, H, eps, layernorm,
+                    NormCombine{static_cast<const __nv_bfloat16*>(y), inv_pos, topk_w, ldy, k}, stream);
 }
 
 OGB_API int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,

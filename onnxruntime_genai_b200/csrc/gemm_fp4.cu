@@ -329,8 +329,8 @@ __device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], uint32_t a0, uin
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __global__ void __launch_bounds__(FP4_STREAM_THREADS, 2)
-fp4_stream_grouped_kernel(const __half* __restrict__ A, int lda, const uint8_t* __restrict__ wpacked, int n_tiles_per_expert, int stage_rows,
-                          const GemmParams p) {
+fp4_stream_grouped_kernel(const void* __restrict__ A_, int lda, const int* __restrict__ row_map, const uint8_t* __restrict__ wpacked,
+                          int n_tiles_per_expert, int stage_rows, const GemmParams p) {
   extern __shared__ __align__(128) uint8_t stream_smem[];
   const int K = p.K, num_kb = p.total_kb;
   const int xld = K * 2 + FP4_STREAM_XPAD;                                                  // bytes of a staged row
@@ -409,7 +409,16 @@ fp4_stream_grouped_kernel(const __half* __restrict__ A, int lda, const uint8_t* 
       for (int i = ct; i < pass_rows * groups; i += FP4_STREAM_CONSUMERS * 32) {
         const int t = i / groups, v = i - t * groups;
         uint4 x = make_uint4(0u, 0u, 0u, 0u);
-        if (t < nrows) x = *reinterpret_cast<const uint4*>(A + size_t(row0 + c + t) * lda + v * 8);
+        if (t < nrows) {
+          if (row_map) {
+            // the rows were not gathered: sorted row r is row row_map[r] of the bf16 activations, converted here
+            const uint4 b = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(A_) + size_t(row_map[row0 + c + t]) * lda + v * 8);
+            const float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+            x = make_uint4(pack_f16x2(f0.x, f0.y), pack_f16x2(f1.x, f1.y), pack_f16x2(f2.x, f2.y), pack_f16x2(f3.x, f3.y));
+          } else {
+            x = *reinterpret_cast<const uint4*>(static_cast<const __half*>(A_) + size_t(row0 + c + t) * lda + v * 8);
+          }
+        }
         // (x0 x1)(x2 x3)(x4 x5)(x6 x7) -> (x0 x4)(x1 x5)(x2 x6)(x3 x7)
         const uint4 y = make_uint4(__byte_perm(x.x, x.z, 0x5410), __byte_perm(x.x, x.z, 0x7632), __byte_perm(x.y, x.w, 0x5410), __byte_perm(x.y, x.w, 0x7632));
         *reinterpret_cast<uint4*>(xs + size_t(t) * xld + v * 16) = y;
@@ -511,8 +520,8 @@ fp4_stream_grouped_kernel(const __half* __restrict__ A, int lda, const uint8_t* 
 }
 
 // stage_rows: token rows staged per pass (1..8): an upper bound on the rows of any tile when the host knows one, else 8
-static int LaunchFp4Stream(const void* A, int lda, const uint8_t* wp, int n_tiles, const GemmParams& p, int max_tiles, int stage_rows,
-                           cudaStream_t stream) {
+static int LaunchFp4Stream(const void* A, int lda, const int* row_map, const uint8_t* wp, int n_tiles, const GemmParams& p, int max_tiles,
+                           int stage_rows, cudaStream_t stream) {
   static bool configured[OGB_MAX_DEVICES] = {};
   if (!set_max_dyn_smem(fp4_stream_grouped_kernel, FP4_STREAM_SMEM_MAX, configured)) return -3;
   const size_t smem = size_t(FP4_STREAM_FIXED_BYTES) + size_t(stage_rows) * (size_t(p.K) * 2 + FP4_STREAM_XPAD);
@@ -530,7 +539,7 @@ static int LaunchFp4Stream(const void* A, int lda, const uint8_t* wp, int n_tile
   }
   cfg.attrs = attrs;
   cfg.numAttrs = unsigned(na);
-  return cudaLaunchKernelEx(&cfg, fp4_stream_grouped_kernel, static_cast<const __half*>(A), lda, wp, n_tiles, stage_rows, p) == cudaSuccess ? 0 : -4;
+  return cudaLaunchKernelEx(&cfg, fp4_stream_grouped_kernel, A, lda, row_map, wp, n_tiles, stage_rows, p) == cudaSuccess ? 0 : -4;
 }
 
 bool MakeMapBf16(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);  // gemm_tcgen05.cu
@@ -584,11 +593,19 @@ OGB_API long long ogb_fp4_packed_bytes(int experts, int N, int K) {
 // Grouped expert GEMM over packed MXFP4 experts; arguments as ogb_moe_gemm with `Wpacked` in the record layout above.
 // flags: bit 0 fp32 output, bit 1 paired activation, bit 4 fp16 form (A holds fp16 rows, records in the fp16 layout),
 // bit 5 fp16 output.  max_rows_per_tile: an upper bound on the rows of any tile known on the host (the number of tokens
-// of the step: an expert receives a token at most once), 0 if unknown (not used by the kernel selection).
+// of the step: an expert receives a token at most once), 0 if unknown.  row_map (or null): A holds the bf16 activations
+// [tokens, K] that were NOT gathered, sorted row r is A[row_map[r]] (16-token tiles of the fp16 form only, see
+// ogb_moe_fp4_reads_row_map).
+// 1 when ogb_moe_gemm_fp4 would take the streaming kernel for this token tile and K (the caller may then skip the row gather)
+OGB_API int ogb_moe_fp4_reads_row_map(int token_tile, int K, int half) {
+  const char* e = getenv("OGB_FP4_STREAM");
+  return (!(e && e[0] == '0') && half && token_tile == 16 && K <= FP4_STREAM_MAX_K && (K % 64) == 0) ? 1 : 0;
+}
+
 OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
                              const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
                              const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
-                             int max_rows_per_tile, int* status, void* stream_) {
+                             int max_rows_per_tile, const int32_t* row_map, int* status, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (rows_total <= 0 || N <= 0 || K <= 0 || experts <= 0 || max_tiles <= 0) return 0;
   if ((K % 64) || (lda % 8)) return -1;
@@ -598,8 +615,8 @@ OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* 
   if (max_tiles > 65535) return -1;
   static const int pdl_enabled = [] { const char* e = getenv("OGB_PDL"); return (e && e[0] == '0') ? 0 : 1; }();
   const int bt = token_tile;
-  CUtensorMap ta;
-  if (!MakeMapBf16(&ta, A, rows_total, K, lda, bt)) return -2;
+  CUtensorMap ta = {};
+  if (!row_map && !MakeMapBf16(&ta, A, rows_total, K, lda, bt)) return -2;
   GemmParams p = {};
   p.M = rows_total; p.N = N; p.K = K;
   p.total_kb = K / GEMM_BLOCK_K;
@@ -622,8 +639,9 @@ OGB_API int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* 
   const int skip = 0;
   if (stream_enabled && half && bt == 16 && K <= FP4_STREAM_MAX_K && max_tiles <= 65535) {
     const int stage_rows = max_rows_per_tile > 0 && max_rows_per_tile < FP4_STREAM_TOKENS ? max_rows_per_tile : FP4_STREAM_TOKENS;
-    return LaunchFp4Stream(A, lda, wp, n_tiles, p, max_tiles, stage_rows, stream);
+    return LaunchFp4Stream(A, lda, row_map, wp, n_tiles, p, max_tiles, stage_rows, stream);
   }
+  if (row_map) return -6;   // only the streaming kernel reads its rows through a map
   switch (bt) {
     case 16: return half ? LaunchFp4<16, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<16, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);
     case 32: return half ? LaunchFp4<32, true>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream) : LaunchFp4<32, false>(ta, tw, w_by_tma, wp, n_tiles, skip, p, grid, stream);

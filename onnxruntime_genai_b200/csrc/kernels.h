@@ -60,6 +60,7 @@ int ogb_collective(int mode, const void* in, void* out, const void* residual, lo
 // ---- moe.cu
 int ogb_moe_topk(const float* logits, int ld, int T, int E, int k, int mode, int32_t* topk_idx, float* topk_w, void* stream);
 int ogb_moe_max_tiles(int n, int experts, int bt);
+int ogb_moe_fp4_reads_row_map(int token_tile, int K, int half);
 int ogb_moe_sort(const int32_t* topk_idx, int T, int k, int E, int e_lo, int e_hi, int bt, int32_t* expert_offsets,
                  int32_t* sorted_token, int32_t* inv_pos, int32_t* tile_expert, int32_t* tile_row0, int32_t* tile_rows,
                  int32_t* num_tiles, int max_tiles, void* stream);
@@ -76,12 +77,14 @@ long long ogb_fp4_packed_bytes(int experts, int N, int K);
 int ogb_moe_gemm_fp4(const void* A, int lda, const void* Wpacked, void* C, int ldc, int rows_total, int N, int K, int experts,
                      const void* bias, int flags, int act_kind, float act_alpha, float act_limit, const int* tile_expert,
                      const int* tile_row0, const int* tile_rows, const int* num_tiles, int max_tiles, int token_tile,
-                     int max_rows_per_tile, int* status, void* stream);
+                     int max_rows_per_tile, const int32_t* row_map, int* status, void* stream);
 
 // ---- elementwise.cu
 int ogb_embedding(const int32_t* ids, const void* table, void* out, int T, int H, int vocab, float scale, void* stream);
 int ogb_norm(const void* x, const void* residual_in, void* residual_out, const void* weight, const void* bias, void* out,
              int rows, int H, float eps, int layernorm, void* stream);
+int ogb_norm_moe_combine(const void* y, int ldy, const int32_t* inv_pos, const float* topk_w, int k, const void* residual_in, void* residual_out,
+                         const void* weight, const void* bias, void* out, int rows, int H, float eps, int layernorm, void* stream);
 int ogb_rope_kv_append(void* qkv, int qkv_stride, const int32_t* positions, const int32_t* slots, const float* cos_cache,
                        const float* sin_cache, void* k_cache, void* v_cache, const void* q_norm_w, const void* k_norm_w,
                        float norm_eps, int T, int Hq, int Hkv, int D, int rot, int interleaved, int max_pos, void* stream);

@@ -258,11 +258,18 @@ class DecoderModel:
             y = apply_lora(y, x, lora)
         return y
 
-    def _mlp(self, lw: LayerWeights, x):
+    def _add_norm(self, h, w, b, residual):
+        """(norm(h + residual), h + residual); `h` may be the pending output of a mixture-of-experts layer."""
+        a = self.arch
+        if isinstance(h, ops.PendingCombine):
+            return ops.norm_moe_combine(h, w, a.norm_eps, residual, b, a.layernorm)
+        return ops.norm(h, w, a.norm_eps, residual, b, a.layernorm)
+
+    def _mlp(self, lw: LayerWeights, x, defer: bool = False):
         a = self.arch
         if a.num_experts > 0:
             from .moe import moe_forward
-            return moe_forward(self, lw, x)
+            return moe_forward(self, lw, x, defer)
         if not a.mlp_gated:
             y = ops.activation(self._linear(x, lw.fc1_w, lw.fc1_b, lora=self._lora(lw, "fc1")), a.activation)
             return self._row_parallel(y, lw.fc2_w, lw.fc2_b, self._lora(lw, "fc2"))
@@ -536,7 +543,7 @@ class DecoderModel:
                 x, _ = ops.norm(h, lw.ln1_w, a.norm_eps, None, lw.ln1_b, a.layernorm)
                 residual = h
             else:
-                x, residual = ops.norm(h, lw.ln1_w, a.norm_eps, residual, lw.ln1_b, a.layernorm)
+                x, residual = self._add_norm(h, lw.ln1_w, lw.ln1_b, residual)
             if lw.conv_in_w is not None:
                 # ---- gated short convolution instead of attention (hybrid models)
                 bcx = self._linear(x, lw.conv_in_w, None, lora=self._lora(lw, "in_proj"))
@@ -581,13 +588,13 @@ class DecoderModel:
             if a.residual_multiplier != 1.0:
                 h = (h.float() * a.residual_multiplier).to(h.dtype)
             x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
-            # ---- MLP
-            h = self._mlp(lw, x)
+            # ---- MLP (a mixture-of-experts layer may leave its combine step to the residual add + norm that follows)
+            h = self._mlp(lw, x, defer=lw.post_ffn_norm_w is None and a.residual_multiplier == 1.0)
             if lw.post_ffn_norm_w is not None:
                 h, _ = ops.norm(h, lw.post_ffn_norm_w, a.norm_eps)
             if a.residual_multiplier != 1.0:
                 h = (h.float() * a.residual_multiplier).to(h.dtype)
-        x, residual = ops.norm(h, self.final_norm_w, a.norm_eps, residual, self.final_norm_b, a.layernorm)
+        x, residual = self._add_norm(h, self.final_norm_w, self.final_norm_b, residual)
         return self._logits(s, x)
 
     def _cross_qk(self, s: StepInputs, li: int, q: torch.Tensor, ck: torch.Tensor) -> None:

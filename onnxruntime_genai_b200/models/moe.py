@@ -19,9 +19,15 @@ MLP uses.  The combine of the all-to-all formulation is that all-reduce.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
+
+
+# OGB_MOE_ROW_MAP=0: the token rows of packed experts are gathered into a copy instead of being read through the row map
+_ROW_MAP = os.environ.get("OGB_MOE_ROW_MAP", "1") != "0"
 
 
 def swiglu_interleaved(gu: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
@@ -111,35 +117,42 @@ def _forward_loop(model, lw, x):
     return out.to(x.dtype)
 
 
-def _forward_device(model, lw, x):
+def _forward_device(model, lw, x, defer=False):
     a = model.arch
     lo, hi = lw.exp_lo, lw.exp_hi or a.num_experts
-    logits = ops.linear(x, lw.router_w, lw.router_b, out_fp32=True)
     standard = a.moe_style == "standard"
+    mode = 1 if standard and not a.moe_norm_topk else 0
+    logits = ops.linear(x, lw.router_w, lw.router_b, out_fp32=True)
     if a.moe_sparse_mixer:
         tw, ti = sparse_mixer(logits, a.moe_jitter_eps)
         plan = ops.moe_route(logits, 2, 0, (lo, hi), topk=(ti.to(torch.int32).contiguous(), tw.contiguous()))
     else:
-        plan = ops.moe_route(logits, a.experts_per_token, 1 if standard and not a.moe_norm_topk else 0, (lo, hi))
+        plan = ops.moe_route(logits, a.experts_per_token, mode, (lo, hi))
     half = isinstance(lw.exp_gate_up_w, ops.Fp4Experts) and lw.exp_gate_up_w.half and lw.exp_down_w.half
     if half:
-        # packed MXFP4 experts in their fp16 form: fp16 rows in, fp16 between the two grouped GEMMs, bf16 out
-        xs = ops.gather_rows(x, plan.sorted_token, f16=True)
+        # packed MXFP4 experts in their fp16 form: fp16 rows in, fp16 between the two grouped GEMMs, bf16 out; the streaming
+        # kernel of decode-sized steps reads the token rows through the plan's row map instead of a gathered copy
+        mapped = _ROW_MAP and ops.moe_fp4_reads_rows(lw.exp_gate_up_w, plan) and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0
+        xs = x if mapped else ops.gather_rows(x, plan.sorted_token, f16=True)
         h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, lw.exp_gate_up_b, act_kind=2, alpha=a.moe_swiglu_alpha, limit=a.moe_swiglu_limit,
-                         out_dtype=torch.float16)
+                         out_dtype=torch.float16, row_map=mapped)
         y = ops.moe_gemm(h, lw.exp_down_w, plan, lw.exp_down_b)
-        return ops.moe_combine(y, plan)
+        return ops.PendingCombine(y, plan) if defer else ops.moe_combine(y, plan)
     xs = ops.gather_rows(x, plan.sorted_token)
     if standard:
         h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, None, act_kind=1)
     else:
         h = ops.moe_gemm(xs, lw.exp_gate_up_w, plan, lw.exp_gate_up_b, act_kind=2, alpha=a.moe_swiglu_alpha, limit=a.moe_swiglu_limit)
     y = ops.moe_gemm(h, lw.exp_down_w, plan, lw.exp_down_b)
-    return ops.moe_combine(y, plan)
+    return ops.PendingCombine(y, plan) if defer else ops.moe_combine(y, plan)
 
 
-def moe_forward(model, lw, x: torch.Tensor) -> torch.Tensor:
+def moe_forward(model, lw, x: torch.Tensor, defer: bool = False):
+    """defer: the caller folds the combine step into the residual add + norm that follows (`ops.norm_moe_combine`); the
+    result is then an `ops.PendingCombine` when the layer ran on the device path of a single rank."""
     a = model.arch
     fast = x.is_cuda and lw.exp_blocked and a.hidden_size % 8 == 0 and a.num_experts <= 1024 and a.experts_per_token <= 32
-    out = _forward_device(model, lw, x) if fast else _forward_loop(model, lw, x)
+    if fast:
+        return _forward_device(model, lw, x, defer and model.tp.size == 1) if model.tp.size == 1 else model.tp.reduce(_forward_device(model, lw, x))
+    out = _forward_loop(model, lw, x)
     return model.tp.reduce(out) if model.tp.size > 1 else out

@@ -148,6 +148,27 @@ def norm(x, weight, eps, residual=None, bias=None, layernorm=False, out=None) ->
     return out, residual
 
 
+class PendingCombine:
+    """The output of a mixture-of-experts layer before its combine step: the experts' rows `y` and the routing plan.
+    `norm_moe_combine` folds the weighted sum into the residual add + norm that consumes it."""
+    __slots__ = ("y", "plan")
+
+    def __init__(self, y, plan):
+        self.y, self.plan = y, plan
+
+
+def norm_moe_combine(pending: PendingCombine, weight, eps, residual, bias=None, layernorm=False):
+    """norm(moe_combine(pending.y, pending.plan), weight, eps, residual, ...) in one launch; same results bit for bit."""
+    y, plan = pending.y, pending.plan
+    assert y.is_cuda and y.dtype == torch.bfloat16 and y.stride(-1) == 1 and residual is not None
+    H = y.shape[1]
+    out = torch.empty(plan.T, H, dtype=torch.bfloat16, device=y.device)
+    _lib.check(_lib.lib().ogb_norm_moe_combine(_ptr(y), y.stride(0), _ptr(plan.inv_pos), _ptr(plan.topk_w), plan.k, _ptr(residual),
+                                               _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out), plan.T, H, float(eps), int(layernorm),
+                                               _stream()), "norm_moe_combine")
+    return out, residual
+
+
 # ------------------------------------------------------------------------------------------ GEMM
 GEMM_FP32_OUT, GEMM_ACT_PAIR, GEMM_ALLREDUCE, GEMM_REDUCE_SCATTER, GEMM_GATHERED_A = 1, 2, 4, 8, 16
 
@@ -456,8 +477,13 @@ def moe_route(router_logits: torch.Tensor, k: int, mode: int = 0, expert_range=N
     return pl
 
 
+def moe_fp4_reads_rows(w, plan: MoePlan) -> bool:
+    """True when moe_gemm over these packed experts takes the un-gathered bf16 rows plus the plan's row map (row_map=True)."""
+    return isinstance(w, Fp4Experts) and w.half and bool(_lib.lib().ogb_moe_fp4_reads_row_map(plan.bt, w.K, 1))
+
+
 def moe_gemm(xs: torch.Tensor, w: torch.Tensor, plan: MoePlan, bias=None, act_kind: int = 0, alpha: float = 1.0, limit: float = 0.0,
-             out_dtype=torch.bfloat16):
+             out_dtype=torch.bfloat16, row_map: bool = False):
     """Grouped expert GEMM over rows sorted by expert.  xs [T*k, K] bf16; w [E, N, K] bf16; bias [E, N].
     act_kind 0: plain; 1: silu(gate)*up; 2: clamped SwiGLU(alpha, limit) — both need the 64-row gate/up blocks
     of interleave_experts_gate_up and return N/2 columns."""
@@ -467,13 +493,17 @@ def moe_gemm(xs: torch.Tensor, w: torch.Tensor, plan: MoePlan, bias=None, act_ki
     if isinstance(w, Fp4Experts):
         # MXFP4 experts stay packed in HBM; the kernel expands each tile in shared memory (csrc/gemm_fp4.cu).  The fp16 form
         # takes fp16 rows (ops.gather_rows(..., f16=True) or the previous grouped GEMM with out_dtype=torch.float16).
-        assert xs.dtype == (torch.float16 if w.half else torch.bfloat16) and out_dtype in (torch.bfloat16, torch.float16)
-        out = torch.empty(xs.shape[0], N // 2 if act_kind else N, dtype=out_dtype, device=xs.device)
+        # row_map: xs holds the bf16 token rows [T, K] as they are; the kernel reads sorted row r from xs[plan.sorted_token[r]]
+        assert out_dtype in (torch.bfloat16, torch.float16)
+        assert xs.dtype == (torch.bfloat16 if row_map else (torch.float16 if w.half else torch.bfloat16))
+        rows = plan.T * plan.k if row_map else xs.shape[0]
+        out = torch.empty(rows, N // 2 if act_kind else N, dtype=out_dtype, device=xs.device)
         flags = (GEMM_ACT_PAIR if act_kind else 0) | (16 if w.half else 0) | (32 if out_dtype == torch.float16 else 0)
-        rc = _lib.lib().ogb_moe_gemm_fp4(_ptr(xs), xs.stride(0), _ptr(w.packed), _ptr(out), out.stride(0), xs.shape[0], N, K, E, _ptr(bias),
+        rc = _lib.lib().ogb_moe_gemm_fp4(_ptr(xs), xs.stride(0), _ptr(w.packed), _ptr(out), out.stride(0), rows, N, K, E, _ptr(bias),
                                          flags, int(act_kind), float(alpha), float(limit),
                                          _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.tile_rows), _ptr(plan.num_tiles),
-                                         plan.max_tiles, plan.bt, plan.T, ws.status, _stream())   # an expert sees a token at most once
+                                         plan.max_tiles, plan.bt, plan.T, _ptr(plan.sorted_token) if row_map else None, ws.status,
+                                         _stream())   # plan.T: an expert sees a token at most once
         _lib.check(rc, "moe_gemm_fp4")
         return out
     assert xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()

@@ -46,7 +46,8 @@ _SIGS = {
                              _P, c_int, c_int, _P, _P]),
     "ogb_fp4_packed_bytes": (c_longlong, [c_int, c_int, c_int]),
     "ogb_moe_gemm_fp4": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int, c_float, c_float, _P, _P, _P,
-                                 _P, c_int, c_int, c_int, _P, _P]),
+                                 _P, c_int, c_int, c_int, _P, _P, _P]),
+    "ogb_moe_fp4_reads_row_map": (c_int, [c_int, c_int, c_int]),
     "ogb_collective": (c_int, [c_int, _P, _P, _P, c_longlong, c_int, _P, c_int, _P]),
     "ogb_moe_topk": (c_int, [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P]),
     "ogb_moe_max_tiles": (c_int, [c_int, c_int, c_int]),
@@ -54,6 +55,7 @@ _SIGS = {
     "ogb_moe_combine": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, _P, c_int, _P, c_int, _P]),
     "ogb_embedding": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
+    "ogb_norm_moe_combine": (c_int, [_P, c_int, _P, _P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, _P]),
     "ogb_rope_kv_append": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, _P]),
     "ogb_rope_kv_append_bits": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,

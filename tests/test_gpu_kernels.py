@@ -909,15 +909,37 @@ def test_moe_fp4_grouped_gemm_matches_expert_loop(T, E, k, H, I, half):
         gw = Fp4Experts.from_codes(ops.interleave_experts_gate_up(gu_c[lo:hi]), ops.interleave_experts_gate_up(gu_s[lo:hi]), DEV, half=half)
         dw = Fp4Experts.from_codes(dn_c[lo:hi].contiguous(), dn_s[lo:hi].contiguous(), DEV, half=half)
         plan = ops.moe_route(logits, k, 0, (lo, hi))
-        xs = ops.gather_rows(x, plan.sorted_token, f16=half)
+        mapped = ops.moe_fp4_reads_rows(gw, plan)      # decode-sized steps of the fp16 form read the rows through the plan's map
+        xs = x if mapped else ops.gather_rows(x, plan.sorted_token, f16=half)
         h = ops.moe_gemm(xs, gw, plan, gb[lo:hi].contiguous(), act_kind=2, alpha=alpha, limit=limit,
-                         out_dtype=torch.float16 if half else torch.bfloat16)
+                         out_dtype=torch.float16 if half else torch.bfloat16, row_map=mapped)
+        if mapped:   # the same through a gathered fp16 copy
+            h2 = ops.moe_gemm(ops.gather_rows(x, plan.sorted_token, f16=True), gw, plan, gb[lo:hi].contiguous(), act_kind=2, alpha=alpha,
+                              limit=limit, out_dtype=torch.float16)
+            n_rows = int(plan.expert_offsets[-1].item())
+            assert torch.equal(h[:n_rows], h2[:n_rows])
         y = ops.moe_gemm(h, dw, plan, dn_b[lo:hi].contiguous())
         got = ops.moe_combine(y, plan)
         ops.check_kernel_status()
         ref_out = want if (lo, hi) == (0, E) else _moe_reference(x, router_w, router_b, gu_w, gu_b, dn_w, dn_b, k, alpha, limit, lo, hi)[0]
         bad = ((got.float() - ref_out.to(got.device)).abs() > 0.03 + 0.03 * ref_out.abs().to(got.device)).float().mean().item()
         assert bad < (0.002 if T <= 100 else 0.02), f"{bad:.4f} of the outputs differ (experts {lo}..{hi})"
+
+
+@pytest.mark.parametrize("T,E,k,H", [(1, 32, 4, 2880), (7, 8, 2, 320), (40, 16, 4, 4096)])
+def test_norm_moe_combine_equals_combine_then_norm(T, E, k, H):
+    """The combine step folded into the residual add + norm: same bits as moe_combine followed by norm, also with experts
+    that are not local (rows skipped)."""
+    logits = torch.randn(T, E, device=DEV, generator=torch.Generator(device=DEV).manual_seed(5))
+    w = _rand(H, std=1.0, seed=71)
+    for rng in ((0, E), (E // 2, E)):
+        plan = ops.moe_route(logits, k, 0, rng)
+        y = _rand(T * k, H, std=1.0, seed=72)
+        r1, r2 = _rand(T, H, std=1.0, seed=73), _rand(T, H, std=1.0, seed=73)
+        a, ra = ops.norm(ops.moe_combine(y, plan), w, 1e-5, r1)
+        b, rb = ops.norm_moe_combine(ops.PendingCombine(y, plan), w, 1e-5, r2)
+        ops.check_kernel_status()
+        assert torch.equal(a, b) and torch.equal(ra, rb)
 
 
 # ------------------------------------------------------------------------------------------- sampled speculative verify
