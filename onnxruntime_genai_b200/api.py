@@ -556,6 +556,8 @@ class Generator:
         sp.length_penalty, sp.early_stopping, sp.random_seed = s["length_penalty"], s["early_stopping"], s["random_seed"]
         self._sp = sp
         self.search = native.Search(sp)
+        self._beam_dev = None                                                   # device-side beam scorer, made at the first beam step
+        self._beam_dev_ok = os.environ.get("OGB_DEVICE_BEAM_SCORER", "1") != "0"   # 0: candidates cross to the host scorer
         self.rows = s["batch_size"] * s["num_beams"]
         self.state = SequenceState(model.decoder, self.rows, s["max_length"], kv_bits=model.kv_bits)
         self._logits: Optional[torch.Tensor] = None
@@ -712,6 +714,18 @@ class Generator:
             logits = logits.clone() if logits is self._logits else logits
             self._apply_penalties_device(logits)
         if so["num_beams"] > 1:
+            from . import beam_device
+            if self._beam_dev is None and self._beam_dev_ok and beam_device.supported(so["num_beams"], self._sp.eos_token_ids):
+                seqs = np.stack([self.search.sequence(r) for r in range(self.rows)]).astype(np.int32)
+                self._beam_dev = beam_device.DeviceBeamScorer(seqs, so["batch_size"], so["num_beams"], so["max_length"], self._sp.pad_token_id,
+                                                              list(self._sp.eos_token_ids), so["length_penalty"], so["early_stopping"], dev)
+            if self._beam_dev is not None:
+                # scorer, hypotheses and sequences on the device: one small copy back (tokens, source rows, open entries)
+                cs, ct, cb = ops.beam_candidates(logits, self._beam_dev.beam_scores(), so["batch_size"], so["num_beams"])
+                toks, rows, all_done = self._beam_dev.step(cs, ct, cb)
+                self.search.commit_beam_result(toks, rows, all_done)
+                self.state.reorder_rows(rows.tolist())
+                return
             scores = torch.from_numpy(self.search.beam_scores()).to(dev)
             cs, ct, cb = ops.beam_candidates(logits, scores, so["batch_size"], so["num_beams"])
             self.search.commit_beam_step(cs.cpu().numpy(), ct.cpu().numpy(), cb.cpu().numpy())
@@ -771,6 +785,10 @@ class Generator:
     def get_sequence(self, index: int) -> np.ndarray:
         so = self.search_opts
         if so["num_beams"] > 1 and self.search.is_done:
+            if self._beam_dev is not None and not self._beam_dev.finalized:
+                for b, ranked in enumerate(self._beam_dev.finalize()):
+                    for rank, (toks, score) in enumerate(ranked):
+                        self.search.set_hypothesis(b, rank, toks.astype(np.int32), score)
             self.search.finalize()
             b, rank = divmod(index, so["num_return_sequences"])
             return self.search.hypothesis(b, rank)[0]
@@ -796,6 +814,10 @@ class Generator:
         if length > self.search.length:
             raise RuntimeError("rewind_to: length exceeds the current sequence length")
         self.search.rewind_to(int(length))
+        if self._beam_dev is not None:
+            # the host scorer cannot take over a search the device scorer began: later steps stay on the device, from the
+            # rewound sequences with fresh beam scores
+            self._beam_dev = None
         for r in range(self.rows):
             self.state.rewind(r, int(length))
         self._fresh = False

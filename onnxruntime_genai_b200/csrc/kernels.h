@@ -147,6 +147,14 @@ int ogb_topk(const float* x, long long row_stride, int rows, int n, int k, int m
              int32_t* out_idx, void* stream);
 int ogb_beam_merge(const float* in_vals, const int32_t* in_idx, int batch, int beams, int cand, float* out_scores,
                    int32_t* out_tokens, int32_t* out_beams, void* stream);
+// Beam scorer + sequence append on the device (beam_scorer.cu)
+int ogb_beam_scorer_step(const float* cand_scores, const int32_t* cand_tokens, const int32_t* cand_beams, void* seq0, void* seq1, int cur, int len,
+                         void* scores, void* hyp_tokens, void* hyp_len, void* hyp_score, void* hyp_order, void* hyp_count, void* done, void* out,
+                         int batch, int num_beams, int max_length, int pad_token, int early_stopping, float length_penalty, const int32_t* eos,
+                         int n_eos, void* stream);
+int ogb_beam_scorer_finalize(void* seq0, void* seq1, int cur, int len, void* scores, void* hyp_tokens, void* hyp_len, void* hyp_score,
+                             void* hyp_order, void* hyp_count, void* done, void* out, int batch, int num_beams, int max_length, int pad_token,
+                             int early_stopping, float length_penalty, const int32_t* eos, int n_eos, void* stream);
 int ogb_verify_sampled(const float* logits, long long row_stride, int vocab, int K, const int32_t* top_k, const float* top_p,
                        const float* temperature, const unsigned long long* seeds, const int32_t* positions, const int32_t* draft,
                        const int32_t* q_idx, const float* q_prob, const int32_t* q_n, int q_stride, int32_t* scratch,

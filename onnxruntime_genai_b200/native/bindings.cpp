@@ -191,6 +191,18 @@ PYBIND11_MODULE(_og_native, m) {
         if (cs.size() != want || ct.size() != want || cb.size() != want) throw std::runtime_error("beam candidates must be [batch, 2*num_beams]");
         b->CommitBeamStep(cs.data(), ct.data(), cb.data());
       })
+      .def("commit_beam_result", [](Search& s, IntArray toks, IntArray rows, bool all_done) {
+        auto* b = dynamic_cast<BeamSearch*>(&s);
+        if (!b) throw std::runtime_error("not a beam search");
+        if (toks.size() != s.Params().BatchBeam() || rows.size() != s.Params().BatchBeam())
+          throw std::runtime_error("commit_beam_result: one token and one source row per row required");
+        b->CommitBeamResult(toks.data(), rows.data(), all_done);
+      })
+      .def("set_hypothesis", [](Search& s, int batch, int rank, IntArray toks, float score) {
+        auto* b = dynamic_cast<BeamSearch*>(&s);
+        if (!b) throw std::runtime_error("not a beam search");
+        b->SetHypothesis(batch, rank, toks.data(), int(toks.size()), score);
+      })
       .def("beam_rows", [](Search& s) {
         auto* b = dynamic_cast<BeamSearch*>(&s);
         if (!b) throw std::runtime_error("not a beam search");

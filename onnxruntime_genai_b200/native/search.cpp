@@ -251,10 +251,37 @@ void BeamSearch::SelectTop() {
   CommitBeamStep(cs.data(), ct.data(), cb.data());
 }
 
+void BeamSearch::CommitBeamResult(const int32_t* tokens, const int32_t* rows, bool all_done) {
+  device_scored_ = true;
+  next_tokens_.assign(tokens, tokens + p_.BatchBeam());
+  device_rows_.assign(rows, rows + p_.BatchBeam());
+  for (int r = 0; r < p_.BatchBeam(); ++r)
+    if (device_rows_[size_t(r)] < 0 || device_rows_[size_t(r)] >= p_.BatchBeam()) throw std::runtime_error("beam source row out of range");
+  seq_.AppendBeamColumn(device_rows_.data(), next_tokens_.data());
+  if (all_done || seq_.Length() >= p_.max_length) done_ = true;
+}
+
+void BeamSearch::SetHypothesis(int batch, int rank, const int32_t* tokens, int len, float score) {
+  if (batch < 0 || batch >= p_.batch_size || rank < 0 || rank >= p_.num_beams || len < 0 || len > p_.max_length)
+    throw std::out_of_range("beam hypothesis index out of range");
+  device_scored_ = true;
+  if (device_hyps_.empty()) device_hyps_.resize(size_t(p_.batch_size));
+  auto& list = device_hyps_[size_t(batch)];
+  if (int(list.size()) <= rank) list.resize(size_t(rank) + 1);
+  list[size_t(rank)] = BeamHypothesis{std::vector<int32_t>(tokens, tokens + len), score};
+}
+
+const BeamHypothesis& BeamSearch::Hypothesis(int batch, int rank) const {
+  if (!device_scored_) return scorer_.Hypothesis(batch, rank);
+  if (batch < 0 || batch >= int(device_hyps_.size()) || rank < 0 || rank >= int(device_hyps_[size_t(batch)].size()))
+    throw std::out_of_range("beam hypothesis rank out of range");
+  return device_hyps_[size_t(batch)][size_t(rank)];
+}
+
 void BeamSearch::Finalize() {
   if (finalized_) return;
   finalized_ = true;
-  scorer_.Finalize(seq_);
+  if (!device_scored_) scorer_.Finalize(seq_);   // the device scorer ranks its own hypotheses (SetHypothesis)
 }
 
 std::unique_ptr<Search> MakeSearch(const SearchParams& p) {

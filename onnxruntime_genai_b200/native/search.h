@@ -155,15 +155,22 @@ class BeamSearch : public Search {
   void CommitTokens(const int32_t*) override { throw std::runtime_error("use CommitBeamStep with beam search"); }
   // Device path: 2*num_beams candidates per batch entry (scores already include the running beam score).
   void CommitBeamStep(const float* cand_scores, const int32_t* cand_tokens, const int32_t* cand_beams);
-  const std::vector<int32_t>& NextRows() const { return scorer_.NextRows(); }  // source row per new row
+  // Device scorer path: the step was scored on the device; append the column (new row r continues old row rows[r]) and take
+  // over its verdict.  The host scorer is not consulted; SetHypothesis supplies the ranked results at the end.
+  void CommitBeamResult(const int32_t* tokens, const int32_t* rows, bool all_done);
+  void SetHypothesis(int batch, int rank, const int32_t* tokens, int len, float score);
+  const std::vector<int32_t>& NextRows() const { return device_scored_ ? device_rows_ : scorer_.NextRows(); }  // source row per new row
   const std::vector<float>& BeamScores() const { return scorer_.NextScores(); }
   void Finalize();
-  const BeamHypothesis& Hypothesis(int batch, int rank) const { return scorer_.Hypothesis(batch, rank); }
+  const BeamHypothesis& Hypothesis(int batch, int rank) const;
 
  private:
   BeamScorer scorer_;
   bool finalized_{false};
   std::vector<int32_t> order_;
+  bool device_scored_{false};
+  std::vector<int32_t> device_rows_;
+  std::vector<std::vector<BeamHypothesis>> device_hyps_;   // [batch][rank], filled by SetHypothesis
 };
 
 std::unique_ptr<Search> MakeSearch(const SearchParams& p);

@@ -85,6 +85,10 @@ _SIGS = {
     "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),
     "ogb_topk": (c_int, [_P, c_longlong, c_int, c_int, c_int, c_int, _P, _P, _P, _P]),
     "ogb_beam_merge": (c_int, [_P, _P, c_int, c_int, c_int, _P, _P, _P, _P]),
+    "ogb_beam_scorer_step": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float,
+                                     _P, c_int, _P]),
+    "ogb_beam_scorer_finalize": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P,
+                                         c_int, _P]),
     "ogb_verify_sampled": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, _P, _P]),
     "ogb_verify_greedy": (c_int, [_P, _P, c_int, _P, _P, _P]),
 }

@@ -195,6 +195,28 @@ def test_beam_search_on_gpu_matches_cpu(dirs):
         assert same >= 17 + 6, f"prompt {b}: GPU and CPU beams diverge after {same - 17} generated tokens"
 
 
+def test_beam_search_device_scorer_equals_host_scorer(dirs):
+    """Beam search with the scorer, the hypotheses and the sequences on the device against the same search with the candidates
+    handed to the host scorer: same sequences, for several beam widths and length penalties."""
+    model = og.Model(dirs[0])
+    prompt = np.random.RandomState(21).randint(0, 32000, size=(2, 9)).astype(np.int32)
+    for opts in (dict(num_beams=4, num_return_sequences=4, length_penalty=1.0, early_stopping=True),
+                 dict(num_beams=3, num_return_sequences=2, length_penalty=0.7, early_stopping=False),
+                 dict(num_beams=6, num_return_sequences=1, length_penalty=1.4, early_stopping=False)):
+        outs = []
+        for on_device in (True, False):
+            p = og.GeneratorParams(model)
+            p.set_search_options(max_length=30, batch_size=2, **opts)
+            g = og.Generator(model, p)
+            g._beam_dev_ok = on_device
+            g.append_tokens(prompt)
+            while not g.is_done():
+                g.generate_next_token()
+            assert (g._beam_dev is not None) == on_device
+            outs.append([g.get_sequence(i).tolist() for i in range(2 * opts["num_return_sequences"])])
+        assert outs[0] == outs[1], opts
+
+
 def test_engine_run_ahead_equals_synchronous_and_survives_cancellation(dirs, monkeypatch):
     """The engine computes step n + 1 while the caller consumes step n: same tokens as the synchronous engine, requests
     added and cancelled while a step is in flight, every block back in the pool at the end."""

@@ -942,6 +942,63 @@ def test_norm_moe_combine_equals_combine_then_norm(T, E, k, H):
         assert torch.equal(a, b) and torch.equal(ra, rb)
 
 
+# ------------------------------------------------------------------------------------------- beam scorer on the device
+@pytest.mark.parametrize("batch,beams,lp,early,p_eos", [(1, 2, 1.0, False, 0.2), (3, 4, 1.0, True, 0.25), (2, 8, 0.6, False, 0.15),
+                                                          (4, 3, 1.7, False, 0.3), (2, 5, 1.0, False, 0.0)])
+def test_device_beam_scorer_follows_the_host_scorer(batch, beams, lp, early, p_eos):
+    """The same stream of candidates (random scores, tokens with end-of-sequence ids mixed in, random source beams) through the
+    device scorer and through the host scorer: same tokens, source rows and verdict every step, same sequences, same ranked
+    hypotheses at the end."""
+    from onnxruntime_genai_b200.beam_device import DeviceBeamScorer
+    from onnxruntime_genai_b200.native_loader import native
+    vocab, L, prompt_len, eos = 60, 24, 5, [1, 7]
+    sp = native.SearchParams()
+    sp.batch_size, sp.num_beams, sp.num_return_sequences, sp.vocab_size, sp.max_length = batch, beams, beams, vocab, L
+    sp.eos_token_ids, sp.pad_token_id, sp.length_penalty, sp.early_stopping, sp.random_seed = eos, 0, lp, early, 1
+    host = native.Search(sp)
+    rng = np.random.RandomState(100 * batch + beams)
+    prompt = rng.randint(8, vocab, size=(batch, prompt_len)).astype(np.int32)
+    host.append_tokens(prompt)
+    rows = batch * beams
+    seqs = np.stack([host.sequence(r) for r in range(rows)]).astype(np.int32)
+    dev = DeviceBeamScorer(seqs, batch, beams, L, 0, eos, lp, early, torch.device(DEV))
+    cand = 2 * beams
+    running = np.zeros((batch, beams), dtype=np.float32)
+    steps = 0
+    while not host.is_done:
+        cs = np.zeros((batch, cand), dtype=np.float32)
+        ct = np.zeros((batch, cand), dtype=np.int32)
+        cb = rng.randint(0, beams, size=(batch, cand)).astype(np.int32)
+        for b in range(batch):
+            cs[b] = np.sort(running[b].max() - rng.rand(cand).astype(np.float32) * 3.0 - 0.1)[::-1]
+            toks = rng.randint(8, vocab, size=cand)
+            is_eos = rng.rand(cand) < p_eos
+            is_eos[np.flatnonzero(is_eos)[beams:]] = False          # at least num_beams candidates continue
+            toks[is_eos] = rng.choice(eos, size=int(is_eos.sum()))
+            ct[b] = toks
+        host.commit_beam_step(cs.copy(), ct.copy(), cb.copy())
+        t_d, r_d, done_d = dev.step(torch.from_numpy(cs).to(DEV), torch.from_numpy(ct).to(DEV), torch.from_numpy(cb).to(DEV))
+        assert t_d.tolist() == host.next_tokens().tolist(), f"step {steps}"
+        assert r_d.tolist() == host.beam_rows().tolist(), f"step {steps}"
+        np.testing.assert_allclose(dev.beam_scores().cpu().numpy(), host.beam_scores(), rtol=0, atol=0)
+        dseq = dev.sequences().cpu().numpy()
+        for r in range(rows):
+            assert dseq[r].tolist() == host.sequence(r).tolist()
+        if host.length < L:
+            assert done_d == bool(host.is_done), f"step {steps}"
+        running = host.beam_scores().reshape(batch, beams)
+        steps += 1
+    host.finalize()
+    ranked = dev.finalize()
+    for b in range(batch):
+        assert len(ranked[b]) >= 1
+        for rank, (toks, score) in enumerate(ranked[b]):
+            h_toks, h_score = host.hypothesis(b, rank)
+            assert toks.tolist() == h_toks.tolist(), f"entry {b} rank {rank}"
+            assert abs(score - h_score) <= 1e-5 * max(1.0, abs(h_score))
+    assert steps >= 3
+
+
 # ------------------------------------------------------------------------------------------- sampled speculative verify
 def test_verify_sampled_preserves_the_target_distribution():
     """Rejection sampling theorem: whatever the proposal, the first committed token follows the target's sampled
