@@ -162,14 +162,21 @@ class Model:
         self.device = torch.device("cuda", torch.cuda.current_device()) if want_cuda else torch.device("cpu")
         self.type = c.model_type
         from .models.arch import ALM_TYPES, LLM_TYPES, VLM_TYPES
-        if self.type not in LLM_TYPES + VLM_TYPES + ALM_TYPES:
+        from .models import marian
+        if self.type not in LLM_TYPES + VLM_TYPES + ALM_TYPES + [marian.MODEL_TYPE]:
             raise RuntimeError(f"Unsupported model type: {self.type}")
         self.dtype = torch.bfloat16 if want_cuda else torch.float32
         from .models.loader import load_decoder
         t_load = time.perf_counter()
         with _Trace("model", "load"):
-            self.decoder = load_decoder(c.config_path, c, self.device, self.dtype, tp)
-            self.draft = load_decoder(c.config_path, c, self.device, self.dtype, tp, decoder=c.draft) if c.draft else None
+            if self.type == marian.MODEL_TYPE:
+                # encoder-decoder translation model with a recurrent (SSRU) decoder: its own weights, forward passes and state
+                if tp is not None and getattr(tp, "size", 1) > 1:
+                    raise RuntimeError("marian-ssru models run on one GPU")
+                self.decoder, self.draft = marian.MarianModel.load(c.config_path, c, self.device, self.dtype), None
+            else:
+                self.decoder = load_decoder(c.config_path, c, self.device, self.dtype, tp)
+                self.draft = load_decoder(c.config_path, c, self.device, self.dtype, tp, decoder=c.draft) if c.draft else None
         if telemetry.enabled():
             a = self.decoder.arch
             telemetry.log_event("ModelLoad", {"model_type": self.type, "device": self.device_type, "layers": a.num_layers,
@@ -559,7 +566,11 @@ class Generator:
         self._beam_dev = None                                                   # device-side beam scorer, made at the first beam step
         self._beam_dev_ok = os.environ.get("OGB_DEVICE_BEAM_SCORER", "1") != "0"   # 0: candidates cross to the host scorer
         self.rows = s["batch_size"] * s["num_beams"]
-        self.state = SequenceState(model.decoder, self.rows, s["max_length"], kv_bits=model.kv_bits)
+        if model.type == "marian-ssru":
+            from .models.marian import MarianState
+            self.state = MarianState(model.decoder, self.rows, s["max_length"])
+        else:
+            self.state = SequenceState(model.decoder, self.rows, s["max_length"], kv_bits=model.kv_bits)
         self._logits: Optional[torch.Tensor] = None
         self._fresh = False
         self._started = False

@@ -195,6 +195,40 @@ def test_beam_search_on_gpu_matches_cpu(dirs):
         assert same >= 17 + 6, f"prompt {b}: GPU and CPU beams diverge after {same - 17} generated tokens"
 
 
+def test_marian_ssru_on_gpu_follows_the_cpu_model(tmp_path):
+    """The encoder-decoder translation model with the recurrent (SSRU) decoder: bf16 on the GPU (linear layers and layer norms
+    through the framework's kernels) against the fp32 CPU model on the first decoder steps; beam search runs through the device
+    scorer with the recurrent states reordered."""
+    from onnxruntime_genai_b200.models.marian import MarianConfig, export_marian, random_state_dict
+    cfg = MarianConfig(vocab_size=96, hidden_size=64, encoder_layers=2, decoder_layers=2, num_heads=4, ffn_size=128, max_positions=48)
+    sd = random_state_dict(cfg, seed=5, std=0.2)
+    sd["decoder.output.bias"][cfg.eos_token_id] = -6.0
+    export_marian(cfg, str(tmp_path / "gpu"), "bf16", "cuda", state_dict=sd)
+    export_marian(cfg, str(tmp_path / "cpu"), "fp32", "cpu", state_dict={k: v.to(torch.bfloat16).float() for k, v in sd.items()})
+    gpu, cpu = og.Model(str(tmp_path / "gpu")), og.Model(str(tmp_path / "cpu"))
+    src = np.random.RandomState(3).randint(2, 96, size=(2, 11)).astype(np.int32)
+    gens = []
+    for m in (gpu, cpu):
+        p = og.GeneratorParams(m)
+        p.set_search_options(max_length=11 + 6, batch_size=2)
+        g = og.Generator(m, p)
+        g.append_tokens(src)
+        gens.append(g)
+    a, b = gens[0].get_logits()[:, 0], gens[1].get_logits()[:, 0]
+    cos = (a * b).sum(-1) / np.sqrt((a * a).sum(-1) * (b * b).sum(-1))
+    assert cos.min() > 0.995, cos
+    p = og.GeneratorParams(gpu)
+    p.set_search_options(max_length=11 + 8, batch_size=2, num_beams=3, num_return_sequences=2)
+    g = og.Generator(gpu, p)
+    g.append_tokens(src)
+    while not g.is_done():
+        g.generate_next_token()
+    assert g._beam_dev is not None
+    outs = [g.get_sequence(i).tolist() for i in range(4)]
+    assert all(o[:11] == src[i // 2].tolist() and len(o) > 11 for i, o in enumerate(outs))
+    ops.check_kernel_status()
+
+
 def test_beam_search_device_scorer_equals_host_scorer(dirs):
     """Beam search with the scorer, the hypotheses and the sequences on the device against the same search with the candidates
     handed to the host scorer: same sequences, for several beam widths and length penalties."""
