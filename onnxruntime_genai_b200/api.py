@@ -200,6 +200,13 @@ class Model:
                 self.vision = TransformerEncoder.load(os.path.join(c.config_path, sec["filename"]), self.device, self.dtype)
                 self.multimodal["vision"] = sec
                 self.image_token_id = int(tree.get("image_token_id", -1))
+        from .models import qwen_vl
+        if self.type in qwen_vl.QWEN_VL_TYPES and tree.get("vision"):
+            # Qwen2-VL: patches + (t, h, w) grids in, merged image features out; the decoder takes three position components per token
+            sec = tree["vision"]
+            self.vision = qwen_vl.QwenVisionTower.load(os.path.join(c.config_path, sec["filename"]), self.device, self.dtype)
+            self.multimodal["vision"] = sec
+            self.image_token_id = int(tree.get("image_token_id", -1))
         self.arch = self.decoder.arch
         # KV-cache quantisation is a provider option of the decoder session (reference: src/config_utils.cpp:13-45)
         self.kv_bits = 16
@@ -334,10 +341,13 @@ class SequenceState:
         return dict(cross=self.cross, cross_table=self.cross_table[rows_used].contiguous() if sel else self.cross_table,
                     cross_lens=self.cross_lens[rows_used].contiguous() if sel else self.cross_lens, max_cross_len=self.max_cross_len)
 
-    def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None, positions3=None) -> torch.Tensor:
+    def run(self, row_tokens: List[List[int]], want_all_logits: bool = False, inputs_embeds=None, positions3=None,
+            device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Feeds row_tokens[r] (possibly empty) after the cached prefix of row r; returns fp32 logits of the last
         fed token of every non-empty row (or of every token).  positions3[r]: [3, len(row_tokens[r])] rotary position
-        components of the fed tokens (multimodal RoPE); later tokens continue one past the largest component."""
+        components of the fed tokens (multimodal RoPE); later tokens continue one past the largest component.
+        device_ids: int32 device tensor with the ids of all fed tokens in row order - the values in row_tokens are then only
+        counted, so a token chosen on the device (a draft model's argmax) is fed without a round trip through the host."""
         dev = self.decoder.device
         mrope = self.decoder.arch.mrope_section is not None and (positions3 is not None or any(self.rope_delta))
         p3: List[np.ndarray] = []
@@ -369,7 +379,10 @@ class SequenceState:
             self.kv_len[r] = base + len(toks)
         self._flush_block_moves()
         i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
-        s = StepInputs(input_ids=i32(ids), positions=i32(pos), slot_mapping=i32(slots), cu_seqlens=i32(cu), past_lens=i32(past),
+        if device_ids is not None and (device_ids.dtype != torch.int32 or device_ids.numel() != len(ids) or device_ids.device != dev):
+            raise RuntimeError("device_ids must be an int32 tensor on the model's device with one id per fed token")
+        s = StepInputs(input_ids=device_ids.reshape(-1) if device_ids is not None else i32(ids), positions=i32(pos), slot_mapping=i32(slots),
+                       cu_seqlens=i32(cu), past_lens=i32(past),
                        block_table=self.block_table[rows_used].contiguous() if len(rows_used) != self.rows else self.block_table,
                        logits_rows=None if want_all_logits else i32(last),
                        max_q_len=max(len(t) for t in row_tokens if t), max_kv_len=max(self.kv_len), inputs_embeds=inputs_embeds,
@@ -888,18 +901,42 @@ class Generator:
             if m.vision is None:
                 raise RuntimeError("this model has no vision encoder")
             with _Trace("model", "vision"):
-                feats, lens = m.vision.encode_images(torch.as_tensor(np.asarray(arr(named["pixel_values"]))))
+                if hasattr(m.vision, "encode_patches"):
+                    # Qwen2-VL: pixel_values are flattened patches, image_grid_thw says how they tile every image
+                    if "image_grid_thw" not in named:
+                        raise RuntimeError("this vision encoder needs image_grid_thw beside pixel_values")
+                    grids = [tuple(int(v) for v in g) for g in np.asarray(arr(named["image_grid_thw"])).reshape(-1, 3)]
+                    feats, lens = m.vision.encode_patches(np.asarray(arr(named["pixel_values"]), dtype=np.float32), grids)
+                    self._image_grids = grids
+                else:
+                    feats, lens = m.vision.encode_images(torch.as_tensor(np.asarray(arr(named["pixel_values"]))))
             self._image_features = feats
         if "input_ids" in named:
             self.append_tokens(arr(named["input_ids"]))
 
     _image_features: Optional[torch.Tensor] = None
+    _image_grids = None      # (t, h, w) of the images whose features are pending (Qwen2-VL)
 
     def _take_position_ids(self, row_tokens: List[List[int]]):
         """A staged `position_ids` input of shape [3, batch, sequence] (multimodal RoPE, reference:
         src/models/position_inputs.cpp, the Qwen2-VL branch) applies to the next tokens fed: per row the three components of
         its tokens."""
         extra = getattr(self, "_extra_inputs", {})
+        if self.model.arch.mrope_section is not None and "position_ids" not in extra and self._image_grids:
+            # positions derived here from the image grids (reference: src/models/qwen_vl_model.cpp computes them the same way
+            # when the caller supplies none): every batch entry consumes its images in order, its beams share them
+            from .models.qwen_vl import mrope_positions
+            nb = self.search_opts["num_beams"]
+            merge = self.model.vision.cfg.spatial_merge_size
+            out, grids = [], list(self._image_grids)
+            for r, toks in enumerate(row_tokens):
+                if r % nb == 0:
+                    start = self.state.kv_len[r] + self.state.rope_delta[r]
+                    comp, used, _ = mrope_positions(toks, self.model.image_token_id, grids, merge, start) if toks else (None, 0, 0)
+                    grids = grids[used:]
+                out.append(comp)
+            self._image_grids = grids or None
+            return out
         if self.model.arch.mrope_section is None or "position_ids" not in extra:
             return None
         v = extra.pop("position_ids")

@@ -1152,6 +1152,35 @@ def export_vision_language(arch: ArchConfig, vis, out_dir: str, image_token_id: 
     return out_dir
 
 
+def export_qwen_vl(arch: ArchConfig, vis, out_dir: str, image_token_id: int, precision: str = "bf16", execution_provider: str = "cuda",
+                   decoder_state_dict=None, vision_state_dict=None, seed: int = 0, std: float = 0.02, image_token: str = "<|image_pad|>",
+                   **export_kw) -> str:
+    """Qwen2-VL checkpoint: model.onnx (the text decoder with multimodal RoPE), vision.onnx (`models/qwen_vl.py`: patch embedding,
+    2-D rotary attention blocks, patch merger), genai_config.json with the `vision` section, processor_config.json with the
+    pixel budget of the image front end."""
+    from . import qwen_vl
+    if arch.mrope_section is None:
+        raise ValueError("a Qwen2-VL decoder needs mrope_section")
+    if vis.hidden_size != arch.hidden_size:
+        raise ValueError("the patch merger must map to the decoder's hidden size")
+    export_model(arch, out_dir, precision, execution_provider, state_dict=decoder_state_dict, seed=seed, std=std, **export_kw)
+    qwen_vl.export_qwen_vision(vis, out_dir, vision_state_dict or qwen_vl.random_state_dict(vis, seed, std), "vision.onnx", precision)
+
+    def edit(cfg):
+        cfg["model"]["image_token_id"] = int(image_token_id)
+        cfg["model"]["vision"] = {"filename": "vision.onnx", "config_filename": "processor_config.json", "patch_size": vis.patch_size,
+                                  "spatial_merge_size": vis.spatial_merge_size,
+                                  "inputs": {"pixel_values": "pixel_values", "image_grid_thw": "image_grid_thw"},
+                                  "outputs": {"image_features": "image_features"}}
+    _patch_config(out_dir, edit)
+    with open(os.path.join(out_dir, "processor_config.json"), "w") as f:
+        json.dump({"processor": {"name": "qwen2_vl_image_processing", "patch_size": vis.patch_size, "merge_size": vis.spatial_merge_size,
+                                 "temporal_patch_size": vis.temporal_patch_size, "min_pixels": vis.min_pixels, "max_pixels": vis.max_pixels,
+                                 "image_mean": list(qwen_vl.IMAGE_MEAN), "image_std": list(qwen_vl.IMAGE_STD), "image_token": image_token,
+                                 "image_token_id": int(image_token_id)}}, f, indent=2)
+    return out_dir
+
+
 def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
     """Reads *.safetensors (preferred) or pytorch_model*.bin from a Hugging Face model directory."""
     sd: Dict[str, torch.Tensor] = {}

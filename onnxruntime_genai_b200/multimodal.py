@@ -199,6 +199,42 @@ class MultiModalProcessor:
             raise RuntimeError(f"the prompt has {seen} image placeholders but {n_images} images were given")
         return np.asarray(ids, dtype=np.int32)
 
+    def _qwen_vl_inputs(self, prompt: str, images: "Images") -> "NamedTensors":
+        """Qwen2-VL front end (reference: src/models/qwen2_5_vl_image_processor.cpp): every image is resized to its own smart
+        size, cut into patches in merge-window order, and its placeholder in the prompt becomes t * h * w / merge^2 image tokens."""
+        from .models import qwen_vl
+        c = self.image_cfg
+        vc = qwen_vl.QwenVisionConfig(patch_size=int(c["patch_size"]), spatial_merge_size=int(c["merge_size"]),
+                                      temporal_patch_size=int(c["temporal_patch_size"]), min_pixels=int(c["min_pixels"]),
+                                      max_pixels=int(c["max_pixels"]))
+        pieces, grids = [], []
+        for a in images.arrays:
+            p, g = qwen_vl.preprocess_image(a, vc)
+            pieces.append(p.numpy())
+            grids.append(g)
+        tag = c.get("image_token", "<|image_pad|>")
+        parts = re.split("(" + _IMAGE_TAG.pattern + "|" + re.escape(tag) + ")", prompt)
+        ids: List[int] = []
+        seen = 0
+        for part in parts:
+            if not part:
+                continue
+            if _IMAGE_TAG.fullmatch(part) or part == tag:
+                if seen >= len(grids):
+                    raise RuntimeError(f"the prompt has more image placeholders than the {len(grids)} images given")
+                t, h, w = grids[seen]
+                ids += [int(c["image_token_id"])] * (t * h * w // vc.spatial_merge_size ** 2)
+                seen += 1
+            else:
+                ids += self.tokenizer.encode(part).tolist()
+        if seen != len(grids):
+            raise RuntimeError(f"the prompt has {seen} image placeholders but {len(grids)} images were given")
+        out = NamedTensors()
+        out["pixel_values"] = np.concatenate(pieces, axis=0)
+        out["image_grid_thw"] = np.asarray(grids, dtype=np.int64)
+        out["input_ids"] = np.asarray(ids, dtype=np.int32)[None]
+        return out
+
     def __call__(self, prompt: Union[str, Sequence[str], None] = None, images: Optional[Images] = None,
                  audios: Optional[Audios] = None) -> NamedTensors:
         out = NamedTensors()
@@ -209,6 +245,8 @@ class MultiModalProcessor:
             if len(prompts) != 1:
                 raise RuntimeError("image inputs take one prompt")
             c = self.image_cfg
+            if c.get("name") == "qwen2_vl_image_processing":
+                return self._qwen_vl_inputs(prompts[0] or "", images)
             out["pixel_values"] = np.stack([preprocess_image(a, int(c["image_size"]), c["image_mean"], c["image_std"]) for a in images.arrays])
             out["image_sizes"] = np.asarray([[a.shape[0], a.shape[1]] for a in images.arrays], dtype=np.int64)
             out["input_ids"] = self._encode_with_images(prompts[0] or "", len(images))[None]

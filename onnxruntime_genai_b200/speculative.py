@@ -258,6 +258,18 @@ class DraftModelStrategy(_SpecBase):
         dists = []
         feed = seq[ds.kv_len[0]:]                 # catch up with the committed sequence (includes the unfed last token)
         sample = g.method != "greedy"
+        if not sample and k > 0 and ds.decoder.device.type == "cuda":
+            # greedy proposals never leave the device between draft steps: each step's argmax is the next step's input id,
+            # and the k tokens come back in one copy
+            picked = []
+            with torch.no_grad():
+                logits, _ = ds.run([feed])
+                for i in range(k):
+                    tok = ops.argmax(logits).to(torch.int32).reshape(1)
+                    picked.append(tok)
+                    if i + 1 < k:
+                        logits, _ = ds.run([[0]], device_ids=tok)
+            return torch.cat(picked).cpu().tolist(), [None] * k
         for _ in range(k):
             with torch.no_grad():
                 logits, _ = ds.run([feed])

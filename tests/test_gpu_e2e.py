@@ -229,6 +229,46 @@ def test_marian_ssru_on_gpu_follows_the_cpu_model(tmp_path):
     ops.check_kernel_status()
 
 
+def test_qwen2_vl_image_prompt_on_gpu_follows_the_cpu_model(tmp_path):
+    """Qwen2-VL: vision tower (bf16, linear layers and norms through the framework's kernels) + multimodal-RoPE decoder on the GPU
+    against the same checkpoint in fp32 on the CPU: image features and first-step logits agree, generation runs."""
+    import copy
+    from onnxruntime_genai_b200.models import qwen_vl
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_qwen_vl, random_state_dict
+    IMG = 300
+    arch = ArchConfig(model_type="qwen2_vl", vocab_size=320, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      intermediate_size=256, context_length=256, bos_token_id=0, eos_token_id=319, pad_token_id=0, attn_bias=True,
+                      mrope_section=[16, 8, 8])
+    vis = qwen_vl.QwenVisionConfig(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2.0, min_pixels=28 * 28, max_pixels=28 * 28 * 16)
+    sd = {k: v.to(torch.bfloat16).float() for k, v in random_state_dict(arch, seed=3, std=0.08).items()}
+    vsd = {k: v.to(torch.bfloat16).float() for k, v in qwen_vl.random_state_dict(vis, seed=4, std=0.08).items()}
+    export_qwen_vl(copy.deepcopy(arch), vis, str(tmp_path / "gpu"), IMG, "bf16", "cuda", decoder_state_dict=sd, vision_state_dict=vsd)
+    export_qwen_vl(copy.deepcopy(arch), vis, str(tmp_path / "cpu"), IMG, "fp32", "cpu", decoder_state_dict=sd, vision_state_dict=vsd)
+    gpu, cpu = og.Model(str(tmp_path / "gpu")), og.Model(str(tmp_path / "cpu"))
+    img = np.random.RandomState(5).randint(0, 256, size=(84, 112, 3), dtype=np.uint8)
+    patches, grid = qwen_vl.preprocess_image(img, vis)
+    fa = gpu.vision.forward(patches, [grid]).float().cpu()
+    fb = cpu.vision.forward(patches, [grid])
+    cos = torch.nn.functional.cosine_similarity(fa, fb, dim=-1)
+    assert cos.min() > 0.99, cos
+    n_img = grid[0] * grid[1] * grid[2] // 4
+    ids = np.asarray([[7, 8] + [IMG] * n_img + [9, 10]], dtype=np.int32)
+    logits = []
+    for m in (gpu, cpu):
+        p = og.GeneratorParams(m)
+        p.set_search_options(max_length=ids.shape[1] + 8)
+        g = og.Generator(m, p)
+        g.set_inputs({"pixel_values": patches.numpy(), "image_grid_thw": np.asarray([grid], dtype=np.int64), "input_ids": ids})
+        logits.append(g.get_logits().reshape(-1))
+        while not g.is_done():
+            g.generate_next_token()
+        assert g.token_count() == ids.shape[1] + 8 or g.is_done()
+    c = float((logits[0] * logits[1]).sum() / np.sqrt((logits[0] ** 2).sum() * (logits[1] ** 2).sum()))
+    assert c > 0.99, c
+    ops.check_kernel_status()
+
+
 def test_beam_search_device_scorer_equals_host_scorer(dirs):
     """Beam search with the scorer, the hypotheses and the sequences on the device against the same search with the candidates
     handed to the host scorer: same sequences, for several beam widths and length penalties."""
