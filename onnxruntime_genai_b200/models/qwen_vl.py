@@ -52,6 +52,12 @@ class QwenVisionConfig:
     norm_eps: float = 1e-6
     min_pixels: int = 56 * 56
     max_pixels: int = 28 * 28 * 1280
+    # Qwen2.5-VL: RMS norms, a gated SiLU MLP of `intermediate_size`, and attention inside windows of `window_size` pixels
+    # except in the blocks listed (as a comma-separated string) in `fullatt_blocks`
+    variant: str = "qwen2_vl"        # qwen2_vl | qwen2_5_vl
+    intermediate_size: int = 0
+    window_size: int = 112
+    fullatt_blocks: str = ""
 
     @property
     def head_dim(self) -> int:
@@ -59,7 +65,15 @@ class QwenVisionConfig:
 
     @property
     def mlp_dim(self) -> int:
-        return int(self.embed_dim * self.mlp_ratio)
+        return self.intermediate_size if self.windowed else int(self.embed_dim * self.mlp_ratio)
+
+    @property
+    def windowed(self) -> bool:
+        return self.variant == "qwen2_5_vl"
+
+    @property
+    def full_blocks(self) -> List[int]:
+        return [int(v) for v in self.fullatt_blocks.split(",") if v.strip()]
 
     @property
     def patch_dim(self) -> int:
@@ -71,13 +85,22 @@ def weight_shapes(c: QwenVisionConfig) -> Dict[str, tuple]:
     s: Dict[str, tuple] = {"patch_embed.proj.weight": (E, c.in_channels, T, P, P)}
     for i in range(c.depth):
         p = f"blocks.{i}."
-        s[p + "norm1.weight"], s[p + "norm1.bias"], s[p + "norm2.weight"], s[p + "norm2.bias"] = (E,), (E,), (E,), (E,)
+        s[p + "norm1.weight"], s[p + "norm2.weight"] = (E,), (E,)
+        if not c.windowed:
+            s[p + "norm1.bias"], s[p + "norm2.bias"] = (E,), (E,)
         s[p + "attn.qkv.weight"], s[p + "attn.qkv.bias"] = (3 * E, E), (3 * E,)
         s[p + "attn.proj.weight"], s[p + "attn.proj.bias"] = (E, E), (E,)
-        s[p + "mlp.fc1.weight"], s[p + "mlp.fc1.bias"] = (M, E), (M,)
-        s[p + "mlp.fc2.weight"], s[p + "mlp.fc2.bias"] = (E, M), (E,)
+        if c.windowed:
+            for n in ("gate_proj", "up_proj"):
+                s[p + f"mlp.{n}.weight"], s[p + f"mlp.{n}.bias"] = (M, E), (M,)
+            s[p + "mlp.down_proj.weight"], s[p + "mlp.down_proj.bias"] = (E, M), (E,)
+        else:
+            s[p + "mlp.fc1.weight"], s[p + "mlp.fc1.bias"] = (M, E), (M,)
+            s[p + "mlp.fc2.weight"], s[p + "mlp.fc2.bias"] = (E, M), (E,)
     G = E * c.spatial_merge_size ** 2
-    s["merger.ln_q.weight"], s["merger.ln_q.bias"] = (E,), (E,)
+    s["merger.ln_q.weight"] = (E,)
+    if not c.windowed:
+        s["merger.ln_q.bias"] = (E,)
     s["merger.mlp.0.weight"], s["merger.mlp.0.bias"] = (G, G), (G,)
     s["merger.mlp.2.weight"], s["merger.mlp.2.bias"] = (c.hidden_size, G), (c.hidden_size,)
     return s
@@ -253,11 +276,36 @@ class QwenVisionTower:
         return F.linear(x, w, b)
 
     def _ln(self, x, name):
-        w, b = self.w[name + ".weight"], self.w[name + ".bias"]
+        """LayerNorm (Qwen2-VL) or RMS norm (Qwen2.5-VL)."""
+        w, b = self.w[name + ".weight"], self.w.get(name + ".bias")
+        rms = self.cfg.windowed
         if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
             from .. import ops
-            return ops.norm(x.contiguous(), w, self.cfg.norm_eps, None, b, True)[0]
+            return ops.norm(x.contiguous(), w, self.cfg.norm_eps, None, b, not rms)[0]
+        if rms:
+            xf = x.float()
+            return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.norm_eps) * w.float()).to(x.dtype)
         return F.layer_norm(x.float(), (x.shape[-1],), w.float(), b.float(), self.cfg.norm_eps).to(x.dtype)
+
+    def _window_order(self, grids) -> Tuple[torch.Tensor, List[int]]:
+        """Qwen2.5-VL: the merged patches (groups of merge^2 patches) regrouped so that every attention window - a square of
+        window_size / (patch * merge) merged patches per side, clipped at the image border - is contiguous.  Returns the
+        permutation of the groups and the patch counts of the windows in the new order."""
+        c = self.cfg
+        m2 = c.spatial_merge_size ** 2
+        side = c.window_size // c.spatial_merge_size // c.patch_size
+        order, sizes, base = [], [], 0
+        for t, h, w in grids:
+            gh, gw = h // c.spatial_merge_size, w // c.spatial_merge_size
+            idx = torch.arange(t * gh * gw).reshape(t, gh, gw)
+            for f in range(t):
+                for r0 in range(0, gh, side):
+                    for c0 in range(0, gw, side):
+                        win = idx[f, r0:r0 + side, c0:c0 + side].reshape(-1)
+                        order.append(win + base)
+                        sizes.append(int(win.numel()) * m2)
+            base += t * gh * gw
+        return torch.cat(order), sizes
 
     def _rotary(self, grids) -> Tuple[torch.Tensor, torch.Tensor]:
         """cos / sin [patches, head_dim]: the first half of the rotary pairs turns with the patch's row, the second half with
@@ -294,25 +342,40 @@ class QwenVisionTower:
             x = self._linear(patches.to(self.device, self.dtype), "patch_embed.proj")
             cos, sin = self._rotary(grids)
             frames = [h * w for t, h, w in grids for _ in range(t)]            # attention stays inside one frame of one image
-            H, D = c.num_heads, c.head_dim
+            H, D, m2 = c.num_heads, c.head_dim, c.spatial_merge_size ** 2
+            windows, perm = frames, None
+            if c.windowed:
+                perm, windows = self._window_order(grids)
+                expand = (perm[:, None] * m2 + torch.arange(m2)[None, :]).reshape(-1).to(self.device)     # groups -> their patches
+                x, cos, sin = x[expand], cos[expand], sin[expand]
+                # a full-attention block still sees whole frames: in window order a frame's patches stay contiguous
+            full = set(c.full_blocks)
             for i in range(c.depth):
                 p = f"blocks.{i}."
                 qkv = self._linear(self._ln(x, p + "norm1"), p + "attn.qkv").float().view(N, 3, H, D)
                 q, k, v = self._rotate(qkv[:, 0], cos, sin), self._rotate(qkv[:, 1], cos, sin), qkv[:, 2]
                 out = torch.empty(N, H, D, dtype=torch.float32, device=self.device)
                 s = 0
-                for n in frames:
+                for n in (frames if (not c.windowed or i in full) else windows):
                     qs, ks, vs = (z[s:s + n].transpose(0, 1) for z in (q, k, v))            # [H, n, D]
                     att = torch.softmax(qs @ ks.transpose(-1, -2) / math.sqrt(D), dim=-1) @ vs
                     out[s:s + n] = att.transpose(0, 1)
                     s += n
                 x = x + self._linear(out.reshape(N, H * D).to(self.dtype), p + "attn.proj")
-                hdn = self._linear(self._ln(x, p + "norm2"), p + "mlp.fc1").float()
-                hdn = (hdn * torch.sigmoid(1.702 * hdn)).to(self.dtype)                        # quick GELU
-                x = x + self._linear(hdn, p + "mlp.fc2")
-            g = self._ln(x, "merger.ln_q").reshape(N // c.spatial_merge_size ** 2, c.embed_dim * c.spatial_merge_size ** 2)
+                y = self._ln(x, p + "norm2")
+                if c.windowed:
+                    hdn = (F.silu(self._linear(y, p + "mlp.gate_proj").float()) * self._linear(y, p + "mlp.up_proj").float()).to(self.dtype)
+                    x = x + self._linear(hdn, p + "mlp.down_proj")
+                else:
+                    hdn = self._linear(y, p + "mlp.fc1").float()
+                    hdn = (hdn * torch.sigmoid(1.702 * hdn)).to(self.dtype)                    # quick GELU
+                    x = x + self._linear(hdn, p + "mlp.fc2")
+            g = self._ln(x, "merger.ln_q").reshape(N // m2, c.embed_dim * m2)
             g = F.gelu(self._linear(g, "merger.mlp.0").float()).to(self.dtype)
-            return self._linear(g, "merger.mlp.2")
+            out = self._linear(g, "merger.mlp.2")
+            if perm is not None:
+                out = out[torch.argsort(perm).to(self.device)]                                 # back to the order of the image tokens
+            return out
 
     # the name `Generator.set_inputs` calls on every vision encoder
     def encode_patches(self, patches, grids) -> Tuple[torch.Tensor, List[int]]:

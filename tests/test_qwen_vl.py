@@ -48,10 +48,37 @@ def test_vision_tower_matches_the_checkpoint_familys_implementation(tmp_path):
     torch.testing.assert_close(again.forward(patches, grids), got, rtol=1e-5, atol=1e-5)
 
 
+def test_windowed_vision_tower_matches_the_qwen2_5_vl_implementation():
+    """Qwen2.5-VL: RMS norms, gated SiLU MLP, attention inside windows except in the listed blocks; grids whose sides are and are
+    not multiples of the window."""
+    m25 = pytest.importorskip("transformers.models.qwen2_5_vl.modeling_qwen2_5_vl")
+    c25 = pytest.importorskip("transformers.models.qwen2_5_vl.configuration_qwen2_5_vl")
+    hc = c25.Qwen2_5_VLVisionConfig(depth=3, hidden_size=32, intermediate_size=48, num_heads=4, in_channels=3, out_hidden_size=40,
+                                    patch_size=14, spatial_merge_size=2, temporal_patch_size=2, window_size=56, fullatt_block_indexes=[1],
+                                    hidden_act="silu")
+    torch.manual_seed(2)
+    hf = m25.Qwen2_5_VisionTransformerPretrainedModel(hc).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.copy_(torch.randn_like(p) * 0.1)
+    cfg = QwenVisionConfig(depth=3, embed_dim=32, hidden_size=40, num_heads=4, variant="qwen2_5_vl", intermediate_size=48, window_size=56,
+                           fullatt_blocks="1")
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    assert set(sd) == set(qwen_vl.weight_shapes(cfg))
+    tower = QwenVisionTower(cfg, sd, "cpu", torch.float32)
+    for grids in ([(1, 4, 6), (1, 2, 4)], [(1, 8, 8)], [(2, 6, 10), (1, 2, 2)]):
+        n = sum(t * h * w for t, h, w in grids)
+        patches = torch.randn(n, cfg.patch_dim, generator=torch.Generator().manual_seed(n))
+        with torch.no_grad():
+            want = hf(patches, torch.tensor(grids)).pooler_output
+        torch.testing.assert_close(tower.forward(patches, grids), want, rtol=3e-4, atol=3e-4)
+
+
 def asdict_equal(a, b):
     from dataclasses import asdict
     da, db = asdict(a), asdict(b)
-    return set(da) == set(db) and all(abs(da[k] - db[k]) <= 1e-6 * max(1.0, abs(db[k])) for k in da)   # attributes are stored as fp32
+    return set(da) == set(db) and all(da[k] == db[k] if isinstance(da[k], str) else abs(da[k] - db[k]) <= 1e-6 * max(1.0, abs(db[k]))
+                                      for k in da)   # numeric attributes are stored as fp32
 
 
 def test_smart_resize_and_patch_layout_match_the_checkpoint_familys_processor():
