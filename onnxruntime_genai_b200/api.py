@@ -162,8 +162,8 @@ class Model:
         self.device = torch.device("cuda", torch.cuda.current_device()) if want_cuda else torch.device("cpu")
         self.type = c.model_type
         from .models.arch import ALM_TYPES, LLM_TYPES, VLM_TYPES
-        from .models import marian
-        if self.type not in LLM_TYPES + VLM_TYPES + ALM_TYPES + [marian.MODEL_TYPE]:
+        from .models import marian, transducer
+        if self.type not in LLM_TYPES + VLM_TYPES + ALM_TYPES + [marian.MODEL_TYPE] + list(transducer.MODEL_TYPES):
             raise RuntimeError(f"Unsupported model type: {self.type}")
         self.dtype = torch.bfloat16 if want_cuda else torch.float32
         from .models.loader import load_decoder
@@ -174,6 +174,9 @@ class Model:
                 if tp is not None and getattr(tp, "size", 1) > 1:
                     raise RuntimeError("marian-ssru models run on one GPU")
                 self.decoder, self.draft = marian.MarianModel.load(c.config_path, c, self.device, self.dtype), None
+            elif self.type in transducer.MODEL_TYPES:
+                # speech transducer (RNN-T / TDT): acoustic encoder + prediction network + joiner and their frame-synchronous search
+                self.decoder, self.draft = transducer.TransducerModel.load(c.config_path, c, self.device, self.dtype), None
             else:
                 self.decoder = load_decoder(c.config_path, c, self.device, self.dtype, tp)
                 self.draft = load_decoder(c.config_path, c, self.device, self.dtype, tp, decoder=c.draft) if c.draft else None
@@ -227,7 +230,18 @@ class Model:
         return MultiModalProcessor(self)
 
     def create_streaming_processor(self):
-        raise RuntimeError("this model has no streaming audio component")
+        """Streaming front end of a speech transducer: samples in, log-mel frames out, long silences dropped when the model has a
+        `vad` section (reference: src/models/streaming_processor.cpp, nemotron_streaming_processor.cpp)."""
+        from .models.transducer import TransducerModel
+        if not isinstance(self.decoder, TransducerModel):
+            raise RuntimeError("this model has no streaming audio component")
+        from .streaming import StreamingProcessor
+        return StreamingProcessor(self)
+
+    def create_streaming_session(self):
+        """`feed(samples)` -> tokens emitted so far, `finish()` -> the rest (speech transducers)."""
+        from .streaming import StreamingSession
+        return StreamingSession(self)
 
 
 # ------------------------------------------------------------------------------------------------ params
@@ -582,6 +596,9 @@ class Generator:
         if model.type == "marian-ssru":
             from .models.marian import MarianState
             self.state = MarianState(model.decoder, self.rows, s["max_length"])
+        elif model.type in ("parakeet_tdt", "nemotron_speech"):
+            from .models.transducer import TransducerState
+            self.state = TransducerState(model.decoder, self.rows, s["max_length"])
         else:
             self.state = SequenceState(model.decoder, self.rows, s["max_length"], kv_bits=model.kv_bits)
         self._logits: Optional[torch.Tensor] = None
@@ -888,6 +905,17 @@ class Generator:
         self._extra_inputs = named
         m = self.model
         arr = lambda v: v.as_numpy() if isinstance(v, Tensor) else v
+        if "audio_features" in named and hasattr(self.state, "set_audio"):
+            # speech transducer: the log-mel features of one utterance; decoding starts from the blank token
+            feats = torch.as_tensor(np.asarray(arr(named["audio_features"]), dtype=np.float32))
+            if feats.dim() == 3:
+                if feats.shape[0] != 1:
+                    raise RuntimeError("speech transducers take one utterance at a time")
+                feats = feats[0]
+            self.state.set_audio(feats)
+            if not self._started:
+                self.append_tokens(np.asarray([[m.decoder.cfg.blank_id]], dtype=np.int32))
+            return
         if "audio_features" in named:
             if m.encoder is None:
                 raise RuntimeError("this model has no audio encoder")

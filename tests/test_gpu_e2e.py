@@ -269,6 +269,39 @@ def test_qwen2_vl_image_prompt_on_gpu_follows_the_cpu_model(tmp_path):
     ops.check_kernel_status()
 
 
+def test_speech_transducer_on_gpu(tmp_path):
+    """TDT transducer with the acoustic encoder on the GPU kernels: encoder frames agree with the fp32 CPU model, the greedy search
+    runs to the blank / end-of-sequence id, the streaming session emits the same tokens as the generator over the same frames."""
+    from onnxruntime_genai_b200 import streaming
+    from onnxruntime_genai_b200.models.encoder import EncoderConfig, random_encoder_state_dict
+    from onnxruntime_genai_b200.models.transducer import TransducerConfig, export_transducer, random_state_dict
+    enc = EncoderConfig(kind="audio", hidden_size=64, num_layers=2, num_heads=4, intermediate_size=128, num_mel_bins=16, max_source_positions=400)
+    cfg = TransducerConfig(vocab_size=33, blank_id=32, encoder_hidden=64, pred_hidden=32, pred_layers=1, joint_hidden=48,
+                           tdt_durations="0,1,2,3,4", max_symbols_per_step=4)
+    sd = random_state_dict(cfg, seed=2, std=0.5)
+    esd = {k: v.to(torch.bfloat16).float() for k, v in random_encoder_state_dict(enc, seed=2, std=0.15).items()}
+    for name, prec, ep in (("gpu", "bf16", "cuda"), ("cpu", "fp32", "cpu")):
+        export_transducer(cfg, enc, str(tmp_path / name), "parakeet_tdt", prec, ep, state_dict=sd, encoder_state_dict=esd, num_mels=16,
+                          chunk_samples=3200)
+    gpu, cpu = og.Model(str(tmp_path / "gpu")), og.Model(str(tmp_path / "cpu"))
+    audio = (np.random.RandomState(4).randn(3200 * 5) * 0.1).astype(np.float32)
+    feats = streaming.log_mel_frames(audio, 16)
+    fa = gpu.decoder.encode(torch.from_numpy(feats).cuda()).cpu()
+    fb = cpu.decoder.encode(torch.from_numpy(feats))
+    assert torch.nn.functional.cosine_similarity(fa, fb, dim=-1).min() > 0.99
+    p = og.GeneratorParams(gpu)
+    p.set_search_options(max_length=300)
+    g = og.Generator(gpu, p)
+    g.set_inputs({"audio_features": feats[None]})
+    while not g.is_done():
+        g.generate_next_token()
+    seq = g.get_sequence(0).tolist()
+    assert seq[0] == 32 and seq[-1] == 32 and len(seq) > 3
+    sess = gpu.create_streaming_session()
+    assert sess.feed(audio) + sess.finish() == seq[1:-1]
+    ops.check_kernel_status()
+
+
 def test_beam_search_device_scorer_equals_host_scorer(dirs):
     """Beam search with the scorer, the hypotheses and the sequences on the device against the same search with the candidates
     handed to the host scorer: same sequences, for several beam widths and length penalties."""
