@@ -17,6 +17,7 @@ __version__ = "0.1.0"
 from .api import (Config, Generator, GeneratorParams, Model, NamedTensors, Tensor, get_current_gpu_device_id,  # noqa: F401
                   is_cuda_available, set_current_gpu_device_id, set_log_callback, set_log_options)
 from .tokenizer import Tokenizer, TokenizerStream  # noqa: F401
+from . import streaming  # noqa: F401  (StreamingProcessor, StreamingSession, VoiceActivityDetector)
 
 
 def __getattr__(name):

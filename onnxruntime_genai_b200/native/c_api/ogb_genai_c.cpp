@@ -80,6 +80,9 @@ OGB_HANDLE(OgaNamedTensors) OGB_END  // obj: the package's NamedTensors (a dict 
 OGB_HANDLE(OgaImages) OGB_END
 OGB_HANDLE(OgaAudios) OGB_END
 OGB_HANDLE(OgaMultiModalProcessor) OGB_END
+OGB_HANDLE(OgaStreamingProcessor)
+  std::string option;   // the string the last GetOption returned
+OGB_END
 OGB_HANDLE(OgaAdapters) OGB_END
 OGB_HANDLE(OgaEngine) OGB_END
 OGB_HANDLE(OgaRequest) OGB_END
@@ -847,6 +850,43 @@ OgaResult* OgaCreateMultiModalProcessor(const OgaModel* m, OgaMultiModalProcesso
   });
 }
 void OgaDestroyMultiModalProcessor(OgaMultiModalProcessor* p) { Destroy(p); }
+
+// ---- streaming audio front end
+OgaResult* OgaCreateStreamingProcessor(OgaModel* m, OgaStreamingProcessor** out) {
+  return Guard([&] {
+    auto p = std::make_unique<OgaStreamingProcessor>();
+    p->obj = m->obj.attr("create_streaming_processor")();
+    *out = p.release();
+  });
+}
+void OgaDestroyStreamingProcessor(OgaStreamingProcessor* p) { Destroy(p); }
+static void FramesToNamedTensors(const py::object& frames, OgaNamedTensors** out) {
+  *out = nullptr;
+  if (frames.is_none()) return;
+  auto n = std::make_unique<OgaNamedTensors>();
+  n->obj = Og().attr("streaming").attr("frames_as_inputs")(frames);
+  *out = n.release();
+}
+OgaResult* OgaStreamingProcessorProcess(OgaStreamingProcessor* p, const float* audio, size_t num_samples, OgaNamedTensors** out) {
+  return Guard([&] {
+    py::array_t<float> samples(static_cast<py::ssize_t>(num_samples));
+    if (num_samples) std::memcpy(samples.mutable_data(), audio, num_samples * sizeof(float));
+    FramesToNamedTensors(p->obj.attr("process")(samples), out);
+  });
+}
+OgaResult* OgaStreamingProcessorFlush(OgaStreamingProcessor* p, OgaNamedTensors** out) {
+  return Guard([&] { FramesToNamedTensors(p->obj.attr("flush")(), out); });
+}
+OgaResult* OgaStreamingProcessorSetOption(OgaStreamingProcessor* p, const char* key, const char* value) {
+  return Guard([&] { p->obj.attr("set_option")(key, value); });
+}
+OgaResult* OgaStreamingProcessorGetOption(const OgaStreamingProcessor* p, const char* key, const char** value) {
+  return Guard([&] {
+    auto* self = const_cast<OgaStreamingProcessor*>(p);
+    self->option = p->obj.attr("get_option")(key).cast<std::string>();
+    *value = self->option.c_str();
+  });
+}
 static OgaResult* Process(const OgaMultiModalProcessor* p, const char* prompt, const OgaImages* images, const OgaAudios* audios, OgaNamedTensors** out) {
   return Guard([&] {
     py::dict kw;

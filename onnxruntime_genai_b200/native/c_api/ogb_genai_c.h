@@ -53,6 +53,7 @@ typedef struct OgaStringArray OgaStringArray;
 typedef struct OgaImages OgaImages;
 typedef struct OgaAudios OgaAudios;
 typedef struct OgaMultiModalProcessor OgaMultiModalProcessor;
+typedef struct OgaStreamingProcessor OgaStreamingProcessor;
 typedef struct OgaAdapters OgaAdapters;
 typedef struct OgaEngine OgaEngine;
 typedef struct OgaRequest OgaRequest;
@@ -198,6 +199,19 @@ OGA_EXPORT OgaResult* OGA_API_CALL OgaLoadAudios(const OgaStringArray* audio_pat
 OGA_EXPORT void OGA_API_CALL OgaDestroyAudios(OgaAudios* audios);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaCreateMultiModalProcessor(const OgaModel* model, OgaMultiModalProcessor** out);
 OGA_EXPORT void OGA_API_CALL OgaDestroyMultiModalProcessor(OgaMultiModalProcessor* processor);
+
+/* Streaming audio front end of a speech transducer (reference: src/ort_genai_c.h:1397-1441).  Process takes mono float samples at
+ * the model's sample rate and returns the named tensor "audio_features" [1, mel bins, frames] with the log-mel frames those samples
+ * completed, or NULL in *out when no frame is complete yet (or the voice-activity gate dropped the chunk); Flush returns the frames
+ * of the samples that did not fill a chunk.  Options: "threshold", "silence_duration_ms", "prefix_padding_ms" of the voice-activity
+ * gate (models with a `vad` section). */
+OGA_EXPORT OgaResult* OGA_API_CALL OgaCreateStreamingProcessor(OgaModel* model, OgaStreamingProcessor** out);
+OGA_EXPORT OgaResult* OGA_API_CALL OgaStreamingProcessorProcess(OgaStreamingProcessor* processor, const float* audio_data, size_t num_samples,
+                                                                OgaNamedTensors** out);
+OGA_EXPORT OgaResult* OGA_API_CALL OgaStreamingProcessorFlush(OgaStreamingProcessor* processor, OgaNamedTensors** out);
+OGA_EXPORT void OGA_API_CALL OgaDestroyStreamingProcessor(OgaStreamingProcessor* processor);
+OGA_EXPORT OgaResult* OGA_API_CALL OgaStreamingProcessorSetOption(OgaStreamingProcessor* processor, const char* key, const char* value);
+OGA_EXPORT OgaResult* OGA_API_CALL OgaStreamingProcessorGetOption(const OgaStreamingProcessor* processor, const char* key, const char** value);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaProcessorProcessImages(const OgaMultiModalProcessor* processor, const char* prompt, const OgaImages* images,
                                                              OgaNamedTensors** input_tensors);
 OGA_EXPORT OgaResult* OGA_API_CALL OgaProcessorProcessAudios(const OgaMultiModalProcessor* processor, const char* prompt, const OgaAudios* audios,

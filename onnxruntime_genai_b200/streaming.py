@@ -170,12 +170,50 @@ class StreamingProcessor:
                 outs.append(f)
         return np.concatenate(outs, axis=1) if outs else None
 
+    _OPTIONS = ("threshold", "silence_duration_ms", "prefix_padding_ms")
+
+    def set_option(self, key: str, value: str):
+        """Options of the voice-activity gate (reference: OgaStreamingProcessorSetOption): threshold, silence_duration_ms,
+        prefix_padding_ms."""
+        if key not in self._OPTIONS:
+            raise RuntimeError(f"unknown streaming option {key!r} (known: {', '.join(self._OPTIONS)})")
+        if self.vad is None:
+            raise RuntimeError("this model has no voice-activity detector")
+        v = float(value)
+        chunk_ms = self.chunk_samples / self.sample_rate * 1000.0
+        if key == "threshold":
+            if not 0.0 <= v <= 1.0:
+                raise RuntimeError("threshold must lie in [0, 1]")
+            self.vad.threshold = v
+        elif key == "silence_duration_ms":
+            self.silence_chunks = max(1, int(v / chunk_ms))
+        else:
+            self.prefix_chunks = max(1, int(v / chunk_ms))
+
+    def get_option(self, key: str) -> str:
+        if key not in self._OPTIONS:
+            raise RuntimeError(f"unknown streaming option {key!r} (known: {', '.join(self._OPTIONS)})")
+        if self.vad is None:
+            raise RuntimeError("this model has no voice-activity detector")
+        chunk_ms = self.chunk_samples / self.sample_rate * 1000.0
+        if key == "threshold":
+            return repr(float(self.vad.threshold))
+        return repr(float((self.silence_chunks if key == "silence_duration_ms" else self.prefix_chunks) * chunk_ms))
+
     def flush(self) -> Optional[np.ndarray]:
         """The frames of the samples that did not fill a chunk (the end of the recording)."""
         if len(self.pending):
             self.audio = np.concatenate([self.audio, self.pending])
             self.pending = np.zeros(0, dtype=np.float32)
         return self._frames()
+
+
+def frames_as_inputs(frames: np.ndarray):
+    """Log-mel frames [n_mels, n] as the generator input {"audio_features": [1, n_mels, n]}."""
+    from .api import NamedTensors
+    out = NamedTensors()
+    out["audio_features"] = np.ascontiguousarray(frames, dtype=np.float32)[None]
+    return out
 
 
 class StreamingSession:

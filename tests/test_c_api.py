@@ -109,3 +109,89 @@ def test_library_joins_a_running_interpreter(model_dir):
     assert lib.OgaLiveHandleCount() == 1
     lib.OgaDestroyModel(m)
     assert lib.OgaLiveHandleCount() == 0
+
+
+def test_streaming_processor_through_the_c_api(tmp_path):
+    """OgaCreateStreamingProcessor / Process / Flush / SetOption / GetOption over a speech-transducer model: the frames that come
+    back through the C entry points equal the Python front end's, a chunk that completes no frame returns a null tensor set."""
+    import ctypes
+    import numpy as np
+    import torch
+    import onnxruntime_genai_b200 as og
+    from onnxruntime_genai_b200 import streaming
+    from onnxruntime_genai_b200.models.encoder import EncoderConfig
+    from onnxruntime_genai_b200.models.transducer import TransducerConfig, export_transducer
+    enc = EncoderConfig(kind="audio", hidden_size=32, num_layers=1, num_heads=4, intermediate_size=64, num_mel_bins=16, max_source_positions=200)
+    cfg = TransducerConfig(vocab_size=11, blank_id=10, encoder_hidden=32, pred_hidden=16, pred_layers=1, joint_hidden=16, tdt_durations="0,1,2")
+    g = torch.Generator().manual_seed(0)
+    vsd = {n: torch.randn(s, generator=g) * 0.3 for n, s in streaming.vad_weight_shapes(16000, 8).items()}
+    d = str(tmp_path)
+    streaming.export_vad(d, vsd)
+    export_transducer(cfg, enc, d, "parakeet_tdt", "fp32", "cpu", num_mels=16, chunk_samples=1600,
+                      vad={"filename": "vad.onnx", "threshold": 0.0, "silence_duration_ms": 300, "prefix_padding_ms": 100})
+    lib = ctypes.CDLL(build_c_api())
+    P = ctypes.c_void_p
+    lib.OgaResultGetError.restype = ctypes.c_char_p
+    lib.OgaResultGetError.argtypes = [P]
+    for name, args in (("OgaCreateModel", [ctypes.c_char_p, ctypes.POINTER(P)]), ("OgaCreateStreamingProcessor", [P, ctypes.POINTER(P)]),
+                       ("OgaStreamingProcessorProcess", [P, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t, ctypes.POINTER(P)]),
+                       ("OgaStreamingProcessorFlush", [P, ctypes.POINTER(P)]),
+                       ("OgaStreamingProcessorSetOption", [P, ctypes.c_char_p, ctypes.c_char_p]),
+                       ("OgaStreamingProcessorGetOption", [P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_char_p)]),
+                       ("OgaNamedTensorsGet", [P, ctypes.c_char_p, ctypes.POINTER(P)]), ("OgaTensorGetShapeRank", [P, ctypes.POINTER(ctypes.c_size_t)]),
+                       ("OgaTensorGetShape", [P, ctypes.POINTER(ctypes.c_int64), ctypes.c_size_t]), ("OgaTensorGetData", [P, ctypes.POINTER(P)])):
+        getattr(lib, name).restype = P
+        getattr(lib, name).argtypes = args
+    for name in ("OgaDestroyModel", "OgaDestroyStreamingProcessor", "OgaDestroyNamedTensors", "OgaDestroyTensor", "OgaDestroyResult"):
+        getattr(lib, name).argtypes = [P]
+    ok = lambda r: (not r) or pytest.fail(lib.OgaResultGetError(r).decode())
+    m, sp = P(), P()
+    ok(lib.OgaCreateModel(d.encode(), ctypes.byref(m)))
+    ok(lib.OgaCreateStreamingProcessor(m, ctypes.byref(sp)))
+    val = ctypes.c_char_p()
+    ok(lib.OgaStreamingProcessorGetOption(sp, b"silence_duration_ms", ctypes.byref(val)))
+    assert float(val.value) == 300.0
+    ok(lib.OgaStreamingProcessorSetOption(sp, b"threshold", b"0.0"))
+    r = lib.OgaStreamingProcessorSetOption(sp, b"no_such_option", b"1")
+    assert r and b"unknown streaming option" in lib.OgaResultGetError(r)
+    lib.OgaDestroyResult(r)
+
+    audio = (np.random.RandomState(0).randn(1600 * 3 + 700) * 0.1).astype(np.float32)
+    ref = og.Model(d).create_streaming_processor()
+    ref.set_option("threshold", "0.0")
+
+    def frames_of(nt):
+        t = P()
+        ok(lib.OgaNamedTensorsGet(nt, b"audio_features", ctypes.byref(t)))
+        rank = ctypes.c_size_t()
+        ok(lib.OgaTensorGetShapeRank(t, ctypes.byref(rank)))
+        shape = (ctypes.c_int64 * rank.value)()
+        ok(lib.OgaTensorGetShape(t, shape, rank.value))
+        data = P()
+        ok(lib.OgaTensorGetData(t, ctypes.byref(data)))
+        n = int(np.prod(list(shape)))
+        arr = np.ctypeslib.as_array(ctypes.cast(data, ctypes.POINTER(ctypes.c_float)), shape=(n,)).reshape(list(shape)).copy()
+        lib.OgaDestroyTensor(t)
+        return arr
+
+    for s0, n in ((0, 300), (300, 1600 * 3 - 300), (1600 * 3, 700)):
+        piece = audio[s0:s0 + n]
+        nt = P()
+        ok(lib.OgaStreamingProcessorProcess(sp, piece.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), len(piece), ctypes.byref(nt)))
+        want = ref.process(piece)
+        if want is None:
+            assert not nt
+        else:
+            got = frames_of(nt)
+            assert got.shape == (1,) + want.shape
+            np.testing.assert_allclose(got[0], want, rtol=1e-6, atol=1e-6)
+            lib.OgaDestroyNamedTensors(nt)
+    nt = P()
+    ok(lib.OgaStreamingProcessorFlush(sp, ctypes.byref(nt)))
+    want = ref.flush()
+    assert (want is None) == (not nt)
+    if nt:
+        np.testing.assert_allclose(frames_of(nt)[0], want, rtol=1e-6, atol=1e-6)
+        lib.OgaDestroyNamedTensors(nt)
+    lib.OgaDestroyStreamingProcessor(sp)
+    lib.OgaDestroyModel(m)
