@@ -485,10 +485,30 @@ class SequenceState:
             self.kv_len[r] += 1
         return out
 
+    def snapshot_recurrent(self) -> None:
+        """Saves the recurrent states of every row (linear-attention layers) so that `restore_recurrent` can put them back
+        after tokens were fed that are not kept (reference: the snapshot slots of src/models/recurrent_state.h:12-66)."""
+        if self.kv.state is None:
+            return
+        if self._state_snapshot is None or self._state_snapshot.shape != self.kv.state.shape:
+            self._state_snapshot = torch.empty_like(self.kv.state)
+        rows = list(range(self.rows))
+        ops.copy_state_slots(self.kv.state, self._state_snapshot, rows, rows)
+
+    def restore_recurrent(self) -> None:
+        if self.kv.state is None:
+            return
+        if self._state_snapshot is None or self._state_snapshot.shape != self.kv.state.shape:
+            raise RuntimeError("restore_recurrent without a snapshot")
+        rows = list(range(self.rows))
+        ops.copy_state_slots(self._state_snapshot, self.kv.state, rows, rows)
+
+    _state_snapshot = None
+
     def rewind(self, row: int, length: int):
         if self.decoder.arch.has_linear_layers and 0 < length < self.kv_len[row]:
-            # a recurrent state cannot be cropped to an earlier position (the reference keeps a window of snapshot slots for its
-            # speculative paths, src/models/recurrent_state.h:12-66; here only a restart from the empty state is offered)
+            # a recurrent state cannot be cropped to an earlier position: callers restart from the empty state and feed the kept
+            # tokens again (`Generator.rewind_to`), or restore a snapshot taken before the tokens were fed (speculative rounds)
             raise RuntimeError("models with linear-attention layers can only be rewound to length 0")
         self.kv_len[row] = min(self.kv_len[row], length)
         if length == 0:
@@ -854,7 +874,20 @@ class Generator:
             raise RuntimeError("rewind_to a non-zero length requires batch_size 1")
         if length > self.search.length:
             raise RuntimeError("rewind_to: length exceeds the current sequence length")
+        recurrent = getattr(getattr(self.model, "arch", None), "has_linear_layers", False) and 0 < length < self.search.length
         self.search.rewind_to(int(length))
+        if recurrent:
+            # a recurrent state cannot be cropped: restart from the empty state and feed the kept tokens again
+            for r in range(self.rows):
+                self.state.rewind(r, 0)
+            self._fresh = False
+            self._unfed_last = False
+            self._compute_logits([self.search.sequence(r).tolist() for r in range(self.rows)])
+            if self._guidance is not None:
+                self._guidance.reset()
+            if self._strategy is not None:
+                self._strategy.on_rewind(int(length))
+            return
         if self._beam_dev is not None:
             # the host scorer cannot take over a search the device scorer began: later steps stay on the device, from the
             # rewound sequences with fresh beam scores

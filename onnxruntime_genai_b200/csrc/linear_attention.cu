@@ -87,3 +87,33 @@ OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const f
   }
   return ok ? 0 : -4;
 }
+
+// ---------------------------------------------------------------------------------------------- state snapshots
+// Copies the recurrent states of `count` slots between two pools of the same shape [layers][slots][slot_elems] (or inside
+// one): dst[l][dst_slots[i]] = src[l][src_slots[i]].  Speculative decoding saves a request's state before the verification
+// pass feeds draft tokens into it and puts it back when some of them are rejected (reference: CopyStateSlotsKernel,
+// src/cuda/model_kernels.cu:488-520, used by src/models/recurrent_state.cpp for its snapshot slots).  16 bytes per thread.
+namespace ogb {
+__global__ void copy_state_slots_kernel(const float4* __restrict__ src, float4* __restrict__ dst, long long layer_vecs, long long slot_vecs,
+                                        const int* __restrict__ src_slots, const int* __restrict__ dst_slots, int count) {
+  const int pair = blockIdx.y % count, layer = blockIdx.y / count;
+  const float4* s = src + size_t(layer) * layer_vecs + size_t(src_slots[pair]) * slot_vecs;
+  float4* d = dst + size_t(layer) * layer_vecs + size_t(dst_slots[pair]) * slot_vecs;
+  for (long long i = blockIdx.x * blockDim.x + threadIdx.x; i < slot_vecs; i += (long long)gridDim.x * blockDim.x) d[i] = s[i];
+}
+}  // namespace ogb
+
+OGB_API int ogb_copy_state_slots(const float* src, float* dst, int layers, int slots, long long slot_elems, const int32_t* src_slots,
+                                 const int32_t* dst_slots, int count, void* stream) {
+  if (count <= 0 || layers <= 0) return 0;
+  if (slot_elems <= 0 || (slot_elems % 4) || slots <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) return -1;
+  if (static_cast<long long>(layers) * count > 65535) return -1;
+  const long long slot_vecs = slot_elems / 4;
+  const int threads = 256;
+  int bx = int((slot_vecs + threads - 1) / threads);
+  if (bx > 128) bx = 128;
+  ogb::copy_state_slots_kernel<<<dim3(bx, layers * count), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst), static_cast<long long>(slots) * slot_vecs, slot_vecs, src_slots, dst_slots, count);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -386,6 +386,23 @@ def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
     return out
 
 
+def copy_state_slots(src: torch.Tensor, dst: torch.Tensor, src_slots, dst_slots) -> None:
+    """dst[:, dst_slots[i]] = src[:, src_slots[i]] for recurrent-state pools [layers, slots, ...] fp32 of the same shape (snapshots
+    of linear-attention states around a speculative round)."""
+    assert src.shape == dst.shape and src.dtype == dst.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous()
+    ss = torch.as_tensor(src_slots, dtype=torch.int32, device=src.device).reshape(-1)
+    ds = torch.as_tensor(dst_slots, dtype=torch.int32, device=src.device).reshape(-1)
+    assert ss.numel() == ds.numel()
+    if ss.numel() == 0:
+        return
+    if not src.is_cuda:
+        dst[:, ds.long()] = src[:, ss.long()]
+        return
+    L, S = src.shape[0], src.shape[1]
+    elems = src[0, 0].numel()
+    _lib.check(_lib.lib().ogb_copy_state_slots(_ptr(src), _ptr(dst), L, S, elems, _ptr(ss), _ptr(ds), ss.numel(), _stream()), "copy_state_slots")
+
+
 def decode_advance(sampled, input_ids, positions, past_lens, slot_mapping, sample_pos, block_table, block_size: int):
     """In place: the packed inputs of a one-token-per-request step become those of the next step (see
     csrc/elementwise.cu::decode_advance_kernel).  block_table [B, cols] int32, everything else [B] int32."""

@@ -35,8 +35,6 @@ class _SpecBase:
             raise RuntimeError("speculative decoding requires batch_size 1")
         if so["num_beams"] != 1:
             raise RuntimeError("speculative decoding does not support beam search")
-        if gen.model.arch.has_linear_layers:
-            raise RuntimeError("speculative decoding needs a cache that can drop rejected tokens; models with linear-attention layers keep a recurrent state")
         if gen._guidance is not None and gen._guidance.ff:
             raise RuntimeError("speculative decoding cannot be combined with guidance fast-forward tokens")
         self.gen = gen
@@ -136,8 +134,12 @@ class _SpecBase:
         n = len(seq)
         k = len(draft)
         base = st.kv_len[0]                       # == n - 1: the last committed token has not been fed
+        recurrent = st.decoder.arch.has_linear_layers
+        if recurrent:
+            st.snapshot_recurrent()               # the verification pass feeds the drafts into the recurrent states as well
         with torch.no_grad():
             logits, _ = st.run([[int(seq[-1])] + list(draft)], want_all_logits=True)
+        fed = list(draft)
         so = g.search_opts
         penalties = so["min_length"] > 0 or so["repetition_penalty"] != 1.0 or so["no_repeat_ngram_size"] > 0
         if g._guidance is not None:
@@ -200,6 +202,13 @@ class _SpecBase:
                 accepted, commit, _ = native.verify_sampled(np.asarray(draft, dtype=np.int32), list(dists), rows,
                                                             g.k if g.k > 1 else 0, g.p if 0 < g.p < 1 else 0.0, g.t, g.search)
         # keep the accepted prefix in the cache: [.., last, d1..d_accepted]; the correction / bonus token is unfed
+        if recurrent and accepted < len(fed):
+            # rejected drafts went through the recurrent states: put the saved states back and feed the kept tokens again (their
+            # keys / values are rewritten with the same values)
+            st.restore_recurrent()
+            st.kv_len[0] = base
+            with torch.no_grad():
+                st.run([[int(seq[-1])] + fed[:accepted]])
         st.kv_len[0] = base + 1 + accepted
         g._fresh = False
         g._unfed_last = True
@@ -245,6 +254,8 @@ class DraftModelStrategy(_SpecBase):
         if gen.search_opts["no_repeat_ngram_size"] > 0:
             raise RuntimeError("draft-model speculative decoding cannot be combined with no_repeat_ngram_size")
         from .api import SequenceState
+        if gen.model.draft.arch.has_linear_layers:
+            raise RuntimeError("the draft model's cache is cropped every round: a draft model with linear-attention layers is not supported")
         self.draft_state = SequenceState(gen.model.draft, 1, gen.search_opts["max_length"])
 
     def on_rewind(self, length):

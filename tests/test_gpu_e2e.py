@@ -625,4 +625,23 @@ def test_gated_delta_hybrid_model_on_gpu(tmp_path):
             assert toks[0][0] == int(np.argmax(first))          # the engine's first token of the long request = the generator's
     for a_, b_ in zip(outs["cpu"], outs["gpu"]):
         assert np.abs(a_ - b_).max() < 0.08 * a_.std() + 0.05
+    # speculation over recurrent states on the GPU (state snapshots + replay of the kept tokens) equals plain greedy decoding
+    model = og.Model(gpu_dir)
+    rep = np.asarray([[7, 8, 9, 10, 7, 8, 9, 10, 7, 8, 9, 11, 7, 8]], dtype=np.int32)
+    seqs = []
+    for spec in (False, True):
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=40, do_sample=False)
+        if spec:
+            p.set_speculative_options(ngram_size=2, max_draft_tokens=4)
+        g = og.Generator(model, p)
+        g.append_tokens(rep)
+        while not g.is_done():
+            g.generate_next_token()
+        seqs.append(g.get_sequence(0).tolist())
+        if spec:
+            assert g.get_speculative_stats()["rounds"] > 0
+    # bf16 batched verification rows against bf16 single-token steps: allow the sequences to part ways late, not early
+    same = next((i for i, (x, y) in enumerate(zip(*seqs)) if x != y), len(seqs[0]))
+    assert same >= 14 + 8, f"speculative and plain decoding diverge after {same - 14} generated tokens"
     ops.check_kernel_status()

@@ -942,6 +942,20 @@ def test_norm_moe_combine_equals_combine_then_norm(T, E, k, H):
         assert torch.equal(a, b) and torch.equal(ra, rb)
 
 
+def test_copy_state_slots_between_pools():
+    """Recurrent-state snapshots: dst[:, dst_slots] = src[:, src_slots] over all layers, other slots untouched."""
+    g = torch.Generator(device=DEV).manual_seed(3)
+    src = torch.randn(3, 6, 4, 16, 8, device=DEV, generator=g)
+    dst = torch.randn(3, 6, 4, 16, 8, device=DEV, generator=g)
+    want = dst.clone()
+    want[:, [5, 0, 2]] = src[:, [1, 4, 2]]
+    ops.copy_state_slots(src, dst, [1, 4, 2], [5, 0, 2])
+    assert torch.equal(dst, want)
+    same = src.clone()
+    ops.copy_state_slots(same, same, [0], [3])               # inside one pool
+    assert torch.equal(same[:, 3], src[:, 0]) and torch.equal(same[:, :3], src[:, :3])
+
+
 # ------------------------------------------------------------------------------------------- beam scorer on the device
 @pytest.mark.parametrize("batch,beams,lp,early,p_eos", [(1, 2, 1.0, False, 0.2), (3, 4, 1.0, True, 0.25), (2, 8, 0.6, False, 0.15),
                                                           (4, 3, 1.7, False, 0.3), (2, 5, 1.0, False, 0.0)])

@@ -117,12 +117,39 @@ def test_hybrid_stack_matches_the_per_token_restatement(built):
         g.generate_next_token()
         toks.append(int(g.get_next_tokens()[0]))
         assert toks[-1] == int(oracle_logits(arch, sd, toks[:-1])[-1].argmax())
-    # a recurrent state cannot be cropped: only a restart is offered
-    with pytest.raises(RuntimeError):
-        g.rewind_to(10)
+    # a recurrent state cannot be cropped: rewinding to an earlier length restarts from the empty state and feeds the kept tokens
+    g.rewind_to(15)
+    assert g.token_count() == 15
+    np.testing.assert_allclose(g.get_logits().reshape(-1), oracle_logits(arch, sd, toks[:15])[-1].numpy(), rtol=2e-3, atol=2e-4)
+    g.generate_next_token()
+    assert int(g.get_next_tokens()[0]) == toks[15]
     g.rewind_to(0)
     g.append_tokens(prompt.reshape(1, -1))
     np.testing.assert_allclose(g.get_logits().reshape(-1), want[-1].numpy(), rtol=2e-3, atol=2e-4)
+
+
+def test_speculative_decoding_over_recurrent_states(built):
+    """N-gram speculation on the hybrid model: the verification pass feeds the drafts into the recurrent states; when drafts are
+    rejected the saved states come back and the kept tokens are fed again, so the output equals plain greedy decoding."""
+    arch, sd, d = built
+    model = og.Model(d)
+    prompt = np.asarray([[7, 8, 9, 10, 7, 8, 9, 10, 7, 8, 9, 11, 7, 8]], dtype=np.int32)
+
+    def run(spec):
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=44, do_sample=False)
+        if spec:
+            p.set_speculative_options(ngram_size=2, max_draft_tokens=4)
+        g = og.Generator(model, p)
+        g.append_tokens(prompt)
+        while not g.is_done():
+            g.generate_next_token()
+        return g.get_sequence(0).tolist(), (g.get_speculative_stats() if spec else None)
+
+    plain, _ = run(False)
+    spec, st = run(True)
+    assert spec == plain
+    assert st["rounds"] > 0 and st["proposed"] > st["accepted"]          # some drafts were rejected: the restore path ran
 
 
 def test_engine_batches_recurrent_requests(built):
