@@ -134,9 +134,9 @@ def ours(args):
         torch.cuda.synchronize()
 
     # ---- checkpoint (synthetic weights: the ONNX file only describes the tensors) + model + engine
-    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{os.getuid()}" + (f"_spec_{args.draft_model}_{args.draft_seed}" if args.spec else ""))
+    ckpt = os.path.join(tempfile.gettempdir(), f"ogb_bench_{MODEL}_{args.precision}_{os.getuid()}" + (f"_spec_{args.draft_model}_{args.draft_seed}" if args.spec else ""))
     if rank == 0 and not os.path.exists(os.path.join(ckpt, "genai_config.json")):
-        create_model(MODEL, ckpt, "bf16", "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
+        create_model(MODEL, ckpt, args.precision, "cuda", {"synthetic_weights": 1, "paged_attention": 1, "paged_block_size": BLOCK,
                                                   "max_batch_size": N_REQ, "context_length": 4096})
         if args.spec:
             # speculative decoding: a Llama-3.2-1B-shaped draft next to the target (its own ONNX file, `model.draft` in the config)
@@ -367,7 +367,8 @@ def ours(args):
             "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (random token ids, random-init N(0,0.02) weights generated on device)",
-            "config": {"model": cfg_w["label"], "global_batch": B,
+            "config": {"model": cfg_w["label"].replace("bf16 experts", "packed MXFP4 experts, int4 attention projections") if args.precision == "int4"
+                       else cfg_w["label"], "weights": args.precision, "global_batch": B,
                        "seq_len": f"prompts U[{PROMPT_LO},{PROMPT_HI}] + {NEW_TOKENS} new tokens",
                        "parallelism": f"tp{world}", "kv_block_size": BLOCK, "sampling": cfg_w["sampling_label"],
                        "engine": "paged-attention continuous batching; warmed with one 2048-token request before the TTFT phase", "l2": "inputs larger than L2 (weights + KV of tens of GB), no flush",
@@ -416,6 +417,9 @@ def main():
                                                               "identical networks, the acceptance ceiling)")
     ap.add_argument("--json-schema", dest="json_schema", action="store_true", help="every request decodes under a JSON schema (needs tokenizer.json)")
     ap.add_argument("--config", default="llama8b", choices=sorted(CONFIGS), help="workload; the default is the headline configuration")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "int4"],
+                    help="weights of the checkpoint: bf16 (headline) or 4-bit (int4 block-32 linears; gpt-oss experts as packed MXFP4, the form "
+                         "the reference publishes its gpt-oss numbers for); activations and the KV cache stay bf16")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
