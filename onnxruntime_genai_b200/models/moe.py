@@ -152,6 +152,10 @@ def moe_forward(model, lw, x: torch.Tensor, defer: bool = False):
     result is then an `ops.PendingCombine` when the layer ran on the device path of a single rank."""
     a = model.arch
     fast = x.is_cuda and lw.exp_blocked and a.hidden_size % 8 == 0 and a.num_experts <= 1024 and a.experts_per_token <= 32
+    if model.tp.size > 1 and getattr(model.tp, "ep_mode", "replicated") == "all_to_all":
+        # token-sharded expert parallelism: dispatch / combine all-to-all, the output is complete on every rank
+        from ..parallel.ep import moe_all_to_all
+        return moe_all_to_all(model, lw, x)
     if fast:
         return _forward_device(model, lw, x, defer and model.tp.size == 1) if model.tp.size == 1 else model.tp.reduce(_forward_device(model, lw, x))
     out = _forward_loop(model, lw, x)

@@ -31,6 +31,11 @@ class TensorParallel:
         # steps with at least this many tokens (and a multiple of the world size) take the sequence-parallel form;
         # 0 (the default) keeps every step in the all-reduce form
         self.sp_min_tokens = int(os.environ.get("OGB_TP_SP_MIN_TOKENS", "0"))
+        # mixture-of-experts layers: "replicated" (every rank routes all tokens, runs its experts, the all-reduce combines) or
+        # "all_to_all" (tokens sharded, dispatch / combine exchange: parallel/ep.py)
+        self.ep_mode = os.environ.get("OGB_EP_MODE", "replicated")
+        if self.ep_mode not in ("replicated", "all_to_all"):
+            raise RuntimeError("OGB_EP_MODE must be replicated or all_to_all")
         if backend == "fused":
             try:
                 from .symm import SymmetricComm

@@ -168,6 +168,29 @@ def test_fused_and_multicast_collectives_match_nccl(tmp_path, world):
         assert "gemm_allreduce_decode_nvls1" in names and "allreduce_large_nvls" in names
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_expert_parallel_all_to_all_on_2_gpus(tmp_path):
+    """Mixture of experts on 2 GPUs in both forms - experts over replicated tokens + all-reduce, and tokens sharded with the
+    dispatch / combine all-to-all (NCCL) around the grouped expert GEMMs - against one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+    arch = ArchConfig(model_type="gptoss", vocab_size=256, hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      intermediate_size=128, context_length=128, attn_bias=True, o_bias=True, mlp_bias=True, attn_sinks=True,
+                      num_experts=8, experts_per_token=2, eos_token_id=255, pad_token_id=255, bos_token_id=0)
+    sd = random_state_dict(arch, seed=3, std=0.05)
+    d = str(tmp_path / "moe")
+    export_model(copy.deepcopy(arch), d, "bf16", "cuda", state_dict=sd, paged=True, block_size=16, num_blocks=128, max_batch_size=4)
+    one = _run(d, str(tmp_path / "g1.npz"), 1, 0)
+    spread = one["logits"].std()
+    for mode, port in (("replicated", 29811), ("all_to_all", 29813)):
+        two = _run(d, str(tmp_path / f"g2_{mode}.npz"), 2, port, ["--backend", "nccl"], {"NCCL_NVLS_ENABLE": "0", "OGB_EP_MODE": mode})
+        err = np.abs(two["logits"] - one["logits"]).max()
+        assert err < 0.08 * spread + 0.02, f"{mode}: max |2 gpus - one gpu| = {err:.4f}, logits std {spread:.4f}"
+
+
 def test_expert_parallel_on_cpu_matches_single_rank(tmp_path):
     """Mixture of experts under tensor parallelism: attention heads are sharded, experts are split between the
     ranks (each rank routes every token and runs only its own experts), the partial outputs are all-reduced."""
@@ -183,6 +206,29 @@ def test_expert_parallel_on_cpu_matches_single_rank(tmp_path):
     two = _run(d, str(tmp_path / "m2.npz"), 2, 29641)
     np.testing.assert_allclose(two["logits"], one["logits"], rtol=2e-4, atol=2e-5)
     assert two["seqs"].tolist() == one["seqs"].tolist()
+
+
+def test_expert_parallel_all_to_all_on_cpu_matches_single_rank(tmp_path):
+    """The all-to-all form of expert parallelism (tokens sharded over the ranks, rows dispatched to the owners of their experts,
+    results sent back and summed with the routing weights, outputs all-gathered) gives the single-rank logits and tokens; an odd
+    token count and three ranks exercise uneven token slices and splits."""
+    from onnxruntime_genai_b200.models.arch import ArchConfig
+    from onnxruntime_genai_b200.models.builder import export_model, random_state_dict
+    from onnxruntime_genai_b200.parallel.ep import owner_of, token_slice
+    import torch
+    assert [token_slice(7, r, 3) for r in range(3)] == [(0, 3), (3, 5), (5, 7)] and token_slice(2, 2, 3) == (2, 2)
+    assert owner_of(torch.tensor([0, 1, 2, 5]), 2).tolist() == [0, 0, 1, 2]
+    arch = ArchConfig(model_type="gptoss", vocab_size=96, hidden_size=32, num_layers=2, num_heads=6, num_kv_heads=6, head_dim=8,
+                      intermediate_size=64, context_length=128, attn_bias=True, o_bias=True, mlp_bias=True, attn_sinks=True,
+                      num_experts=6, experts_per_token=2, eos_token_id=95, pad_token_id=95, bos_token_id=0)
+    sd = random_state_dict(arch, seed=3, std=0.1)
+    d = str(tmp_path / "moe")
+    export_model(copy.deepcopy(arch), d, "fp32", "cpu", state_dict=sd)
+    one = _run(d, str(tmp_path / "m1.npz"), 1, 0)
+    for n, port in ((2, 29651), (3, 29653)):
+        got = _run(d, str(tmp_path / f"m{n}.npz"), n, port, env_extra={"OGB_EP_MODE": "all_to_all"})
+        np.testing.assert_allclose(got["logits"], one["logits"], rtol=2e-4, atol=2e-5)
+        assert got["seqs"].tolist() == one["seqs"].tolist()
 
 
 def test_non_gated_parallel_block_under_tp_on_cpu(tmp_path):
