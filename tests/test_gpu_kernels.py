@@ -743,9 +743,9 @@ def test_gemm_w4_gate_up_pair():
 _GEMV_CASES = {}
 
 
-@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 11, 16])
 def test_gemv_w4_few_tokens(M):
-    """One to four tokens take the weight-streaming GEMV: all epilogues, uneven k splits, rows past N, many k-blocks per
+    """One to four tokens take the weight-streaming GEMV, more the tensor-core kernel with its smallest token tile: all epilogues, uneven k splits, rows past N, many k-blocks per
     CTA, against the dequantised fp32 product."""
     for N, K, splits in ((1152, 768, 0), (1000, 512, 3), (128, 64, 1), (256, 4096, 2)):
         if (N, K) not in _GEMV_CASES:      # quantising on the host is the slow part: once per shape
