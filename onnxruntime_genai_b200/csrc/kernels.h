@@ -110,6 +110,9 @@ int ogb_gather_rows_f16(const void* in, const int32_t* rows, void* out, int n_ro
 // ---- linear_attention.cu: gated delta rule over packed sequences; state [slots, Hv, dk, dv] fp32 updated in place
 int ogb_gated_delta(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, const int32_t* slots,
                     const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream);
+int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,
+                    const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int heads, int groups, int P, int N,
+                    void* stream);
 int ogb_copy_state_slots(const float* src, float* dst, int layers, int slots, long long slot_elems, const int32_t* src_slots,
                          const int32_t* dst_slots, int count, void* stream);
 

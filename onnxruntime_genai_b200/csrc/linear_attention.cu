@@ -88,6 +88,84 @@ OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const f
   return ok ? 0 : -4;
 }
 
+// ---------------------------------------------------------------------------------------------- Mamba-2 selective scan
+// The state-space recurrence of a Mamba-2 layer over packed sequences (GraniteMoeHybrid; reference: the Mamba2 branch of
+// src/models/recurrent_state.cpp keeps its conv / ssm states, the layer itself is an opaque graph there).  Per head h with
+// group gr = h / (heads / groups), per token t, with dt already softplus'ed:
+//     S *= exp(dt[t, h] * A[h]);   S[n][p] += dt[t, h] * x[t, h, p] * B[t, gr, n];   y[t, h, p] = sum_n S[n][p] * C[t, gr, n] + D[h] * x[t, h, p]
+// state [slots][heads][N][P] fp32, updated in place for the request slots (a request whose past length is 0 starts from a
+// zero state).  One CTA per (request, head); thread p keeps column S[.][p] in registers, the token's B and C rows sit in
+// shared memory; the tokens of a chunk are walked in order.
+namespace ogb {
+template <int N>
+__global__ void __launch_bounds__(128) mamba2_scan_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dt,
+                                                         const float* __restrict__ neg_a, const __nv_bfloat16* __restrict__ Bm,
+                                                         const __nv_bfloat16* __restrict__ Cm, const float* __restrict__ Dv,
+                                                         float* __restrict__ state, const int32_t* __restrict__ slots,
+                                                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ past_lens,
+                                                         __nv_bfloat16* __restrict__ out, int heads, int groups, int P) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  const int gr = h / (heads / groups);
+  const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+  if (t0 >= t1) return;
+  __shared__ float sB[N], sC[N];
+  float* S = state + ((size_t(slots[b]) * heads + h) * N) * P;
+  float col[N];
+  const bool live = j < P;
+  const bool fresh = past_lens[b] == 0;
+#pragma unroll
+  for (int i = 0; i < N; ++i) col[i] = (live && !fresh) ? S[size_t(i) * P + j] : 0.f;
+  const float a = neg_a[h], d = Dv[h];
+  for (int t = t0; t < t1; ++t) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+      sB[i] = bf2f(Bm[(size_t(t) * groups + gr) * N + i]);
+      sC[i] = bf2f(Cm[(size_t(t) * groups + gr) * N + i]);
+    }
+    __syncthreads();
+    const float step = dt[size_t(t) * heads + h];
+    const float decay = __expf(step * a);
+    const float xj = live ? bf2f(x[(size_t(t) * heads + h) * P + j]) : 0.f;
+    const float dx = step * xj;
+    float y = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      col[i] = fmaf(col[i], decay, dx * sB[i]);
+      y = fmaf(col[i], sC[i], y);
+    }
+    if (live) out[(size_t(t) * heads + h) * P + j] = f2bf(y + d * xj);
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) S[size_t(i) * P + j] = col[i];
+  }
+}
+}  // namespace ogb
+
+OGB_API int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,
+                            const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int heads, int groups,
+                            int P, int N, void* stream) {
+  if (B <= 0) return 0;
+  if (heads <= 0 || groups <= 0 || heads % groups || P <= 0 || P > 128) return -1;
+  dim3 grid(B, heads);
+  auto s = static_cast<cudaStream_t>(stream);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto Bp = static_cast<const __nv_bfloat16*>(Bm);
+  auto Cp = static_cast<const __nv_bfloat16*>(Cm);
+  auto O = static_cast<__nv_bfloat16*>(out);
+  bool ok;
+  switch (N) {
+    case 16: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<16>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
+    case 32: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<32>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
+    case 64: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<64>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
+    case 128: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<128>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
+    default: return -5;
+  }
+  return ok ? 0 : -4;
+}
+
 // ---------------------------------------------------------------------------------------------- state snapshots
 // Copies the recurrent states of `count` slots between two pools of the same shape [layers][slots][slot_elems] (or inside
 // one): dst[l][dst_slots[i]] = src[l][src_slots[i]].  Speculative decoding saves a request's state before the verification

@@ -17,7 +17,7 @@ LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
     "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl",
-    "qwen3_next", "qwen3_5", "qwen3_5_text",      # hybrids of gated-delta-net (linear attention) and full-attention layers
+    "qwen3_next", "qwen3_5", "qwen3_5_text", "granitemoehybrid",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
 
 
@@ -73,12 +73,21 @@ class ArchConfig:
     linear_key_head_dim: int = 0
     linear_value_head_dim: int = 0
     linear_conv_kernel_dim: int = 4
+    # Layers of type "mamba" are Mamba-2 state-space layers (GraniteMoeHybrid): in_proj -> [gate | x, B, C | dt], a causal
+    # depthwise convolution + SiLU over (x, B, C), the selective scan with one state [state_size, head_dim] per head, a gated
+    # RMS norm, out_proj.  The model's other layers are attention layers.
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 0
+    mamba_state_size: int = 0
+    mamba_n_groups: int = 1
+    mamba_conv_kernel: int = 4
     # Multimodal RoPE (Qwen2-VL): rotary pairs per position component (temporal, height, width); None: ordinary RoPE
     mrope_section: Optional[List[int]] = None
     cross_attention: bool = False    # encoder-decoder (whisper): every layer also attends to the encoder's output
     encoder_hidden_size: int = 0     # width of the encoder output the cross-attention keys / values are projected from (0 = hidden_size)
     mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
     parallel_block: bool = False     # phi: attention and MLP both read the input norm; their outputs are summed
+    no_rope: bool = False            # attention without any position encoding (hybrids whose recurrent layers carry the order)
     learned_positions: bool = False  # gpt2: a learned position table added to the token embedding, no rotary embedding
     # mixture of experts (gpt-oss style)
     num_experts: int = 0
@@ -111,6 +120,11 @@ class ArchConfig:
         return r - (r % 2)
 
     @property
+    def applied_rotary_dim(self) -> int:
+        """Rotary width the attention kernels apply: none under a learned position table or without position encoding."""
+        return 0 if (self.learned_positions or self.no_rope) else self.rotary_dim
+
+    @property
     def q_size(self) -> int:
         return self.num_heads * self.head_dim
 
@@ -128,9 +142,39 @@ class ArchConfig:
     def is_linear_layer(self, layer: int) -> bool:
         return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
 
+    def is_mamba_layer(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] == "mamba"
+
+    def is_recurrent_layer(self, layer: int) -> bool:
+        return self.is_linear_layer(layer) or self.is_mamba_layer(layer)
+
     @property
     def has_linear_layers(self) -> bool:
-        return self.layer_types is not None and "linear_attention" in self.layer_types
+        """True for models with layers that carry a recurrent state per request (gated-delta-net or Mamba-2 layers)."""
+        return self.layer_types is not None and ("linear_attention" in self.layer_types or "mamba" in self.layer_types)
+
+    @property
+    def has_mamba_layers(self) -> bool:
+        return self.layer_types is not None and "mamba" in self.layer_types
+
+    @property
+    def mamba_intermediate(self) -> int:
+        return self.mamba_num_heads * self.mamba_head_dim
+
+    @property
+    def mamba_conv_dim(self) -> int:
+        return self.mamba_intermediate + 2 * self.mamba_n_groups * self.mamba_state_size
+
+    @property
+    def recurrent_state_shape(self):
+        """Per request and layer: gated delta net [value heads, key dim, value dim]; Mamba-2 [heads, state size, head dim]."""
+        if self.has_mamba_layers:
+            return (self.mamba_num_heads, self.mamba_state_size, self.mamba_head_dim)
+        return (self.linear_num_value_heads, self.linear_key_head_dim, self.linear_value_head_dim)
+
+    @property
+    def recurrent_conv_dim(self) -> int:
+        return self.mamba_conv_dim if self.has_mamba_layers else self.linear_conv_dim
 
     @property
     def linear_key_dim(self) -> int:
@@ -150,6 +194,8 @@ class ArchConfig:
             return self.hidden_size
         if self.is_linear_layer(layer):
             return self.linear_conv_dim
+        if self.is_mamba_layer(layer):
+            return self.mamba_conv_dim
         return 0
 
     def layer_window(self, layer: int) -> int:
@@ -251,7 +297,20 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
             a.layernorm = True
             a.attn_bias = a.o_bias = True
             a.lm_head_bias = bool(cfg.get("lm_head_bias", True))
-    if mt == "granite":
+    if mt == "granitemoehybrid":
+        # hybrid of Mamba-2 and attention layers; the feed-forward of the dense members is the "shared" gated MLP
+        if int(cfg.get("num_local_experts") or 0) > 0:
+            raise NotImplementedError("granitemoehybrid with routed experts beside the shared MLP is not supported: dense members only")
+        a.layer_types = ["full_attention" if t == "attention" else t for t in (cfg.get("layer_types") or ["mamba"] * a.num_layers)]
+        a.mamba_num_heads = int(cfg.get("mamba_n_heads", 128))
+        dh = cfg.get("mamba_d_head", 64)
+        a.mamba_head_dim = (int(cfg.get("mamba_expand", 2)) * a.hidden_size // a.mamba_num_heads) if dh in (None, 0, "auto") else int(dh)
+        a.mamba_state_size = int(cfg.get("mamba_d_state", 256))
+        a.mamba_n_groups = int(cfg.get("mamba_n_groups", 1))
+        a.mamba_conv_kernel = int(cfg.get("mamba_d_conv", 4))
+        a.intermediate_size = int(cfg.get("shared_intermediate_size", a.intermediate_size))
+        a.no_rope = cfg.get("position_embedding_type") != "rope"
+    if mt in ("granite", "granitemoehybrid"):
         a.residual_multiplier = cfg.get("residual_multiplier", 1.0)
         a.logits_scale = 1.0 / cfg.get("logits_scaling", 1.0)
         a.embed_scale = cfg.get("embedding_multiplier", 1.0)

@@ -64,6 +64,16 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             if arch.conv_bias:
                 s[p + "conv.conv.bias"] = (H,)
             s[p + "conv.out_proj.weight"] = (H, H)
+        elif arch.is_mamba_layer(i):
+            I, cd, nh = arch.mamba_intermediate, arch.mamba_conv_dim, arch.mamba_num_heads
+            s[p + "mamba.in_proj.weight"] = (I + cd + nh, H)
+            s[p + "mamba.conv1d.weight"] = (cd, 1, arch.mamba_conv_kernel)
+            s[p + "mamba.conv1d.bias"] = (cd,)
+            s[p + "mamba.dt_bias"] = (nh,)
+            s[p + "mamba.A_log"] = (nh,)
+            s[p + "mamba.D"] = (nh,)
+            s[p + "mamba.norm.weight"] = (I,)
+            s[p + "mamba.out_proj.weight"] = (H, I)
         elif arch.is_linear_layer(i):
             nv, hv = arch.linear_num_value_heads, arch.linear_value_head_dim
             s[p + "linear_attn.in_proj_qkv.weight"] = (arch.linear_conv_dim, H)
@@ -94,7 +104,7 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
                             ("v", (arch.q_size, arch.encoder_hidden_size or H)), ("o", (H, arch.q_size))):
                 s[p + f"cross_attn.{nm}_proj.weight"] = shp
                 s[p + f"cross_attn.{nm}_proj.bias"] = (shp[0],)
-        if arch.qk_norm and not arch.is_conv_layer(i) and not arch.is_linear_layer(i):
+        if arch.qk_norm and not arch.is_conv_layer(i) and not arch.is_recurrent_layer(i):
             s[p + "self_attn.q_norm.weight"] = (arch.head_dim,)
             s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
         if arch.attn_sinks:
@@ -688,6 +698,36 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             W.node("Identity", f"{n}/conv/present", [f"{n}/conv/Conv_1/output_0"], [f"present_conv.{i}"])
             o_out = f"{n}/conv/out_proj/MatMul/output_0"
             put_linear(p + "conv.out_proj", f"{n}/conv/out_proj/MatMul", [p + "conv.out_proj.weight"], f"{n}/conv/Mul_2/output_0", o_out, H, H)
+        elif arch.is_mamba_layer(i):
+            # Mamba-2 layer: in_proj -> [gate | x, B, C | dt], causal depthwise convolution + SiLU with a carried window, the selective
+            # scan with a carried state, gated RMS norm, out_proj
+            mb = f"{n}/mamba"
+            mp = p + "mamba."
+            I, cd, nh = arch.mamba_intermediate, arch.mamba_conv_dim, arch.mamba_num_heads
+            Kc = arch.mamba_conv_kernel
+            put_linear(mp + "in_proj", f"{mb}/in_proj/MatMul", [mp + "in_proj.weight"], x, f"{mb}/in_proj/MatMul/output_0", I + cd + nh, H)
+            put_plain(mp + "conv1d.weight", [mp + "conv1d.weight"], {"shape": (cd, 1, Kc), "op": "id", "fn": lambda ts: ts[0].float().reshape(cd, 1, Kc)})
+            put_vec(mp + "conv1d.bias", [mp + "conv1d.bias"])
+            put_plain(mp + "dt_bias", [mp + "dt_bias"], {"shape": (nh,), "op": "id", "fn": lambda ts: ts[0].float()}, force_fp32=True)
+            put_plain(mp + "neg_exp_A", [mp + "A_log"], {"shape": (nh,), "op": "neg_exp", "fn": lambda ts: -torch.exp(ts[0].float())}, force_fp32=True)
+            put_plain(mp + "D", [mp + "D"], {"shape": (nh,), "op": "id", "fn": lambda ts: ts[0].float()}, force_fp32=True)
+            put_plain(mp + "norm.weight", [mp + "norm.weight"], {"shape": (I,), "op": "id", "fn": lambda ts: ts[0].float()})
+            W.node("Split", f"{mb}/Split", [f"{mb}/in_proj/MatMul/output_0"], [f"{mb}/Split/output_{j}" for j in range(3)], axis=-1, split=[I, cd, nh])
+            W.node("Transpose", f"{mb}/xbc/Transpose", [f"{mb}/Split/output_1"], [f"{mb}/xbc/Transpose/output_0"], perm=[0, 2, 1])
+            W.node("CausalConvWithState", f"{mb}/CausalConvWithState", [f"{mb}/xbc/Transpose/output_0", mp + "conv1d.weight", mp + "conv1d.bias", f"past_key_values.{i}.conv_state"],
+                   [f"{mb}/CausalConvWithState/output_0", f"present.{i}.conv_state"], domain="com.microsoft", ndim=1, activation="silu")
+            W.node("Transpose", f"{mb}/conv_out/Transpose", [f"{mb}/CausalConvWithState/output_0"], [f"{mb}/conv_out/Transpose/output_0"], perm=[0, 2, 1])
+            W.node("Mamba2", f"{mb}/Mamba2", [f"{mb}/conv_out/Transpose/output_0", f"{mb}/Split/output_2", mp + "dt_bias", mp + "neg_exp_A", mp + "D",
+                                              f"past_key_values.{i}.recurrent_state"],
+                   [f"{mb}/Mamba2/output_0", f"present.{i}.recurrent_state"], domain="com.microsoft", num_heads=nh, head_dim=arch.mamba_head_dim,
+                   state_size=arch.mamba_state_size, n_groups=arch.mamba_n_groups)
+            W.node("Sigmoid", f"{mb}/gated_norm/Sigmoid", [f"{mb}/Split/output_0"], [f"{mb}/gated_norm/Sigmoid/output_0"])
+            W.node("Mul", f"{mb}/gated_norm/Mul_1", [f"{mb}/Split/output_0", f"{mb}/gated_norm/Sigmoid/output_0"], [f"{mb}/gated_norm/Mul_1/output_0"])
+            W.node("Mul", f"{mb}/gated_norm/Mul_2", [f"{mb}/Mamba2/output_0", f"{mb}/gated_norm/Mul_1/output_0"], [f"{mb}/gated_norm/Mul_2/output_0"])
+            W.node("SimplifiedLayerNormalization", f"{mb}/gated_norm/LayerNorm", [f"{mb}/gated_norm/Mul_2/output_0", mp + "norm.weight"],
+                   [f"{mb}/gated_norm/LayerNorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1)
+            o_out = f"{mb}/out_proj/MatMul/output_0"
+            put_linear(mp + "out_proj", f"{mb}/out_proj/MatMul", [mp + "out_proj.weight"], f"{mb}/gated_norm/LayerNorm/output_0", o_out, H, I)
         elif arch.is_linear_layer(i):
             # gated-delta-net layer (reference graph: builders/qwen.py:1776-1867): projections, causal depthwise convolution + SiLU
             # with a carried state, per-head L2 norm of q / k, decay / beta gates, LinearAttention (gated delta rule) with a
@@ -752,7 +792,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                 attn_inputs += [p + "attn.q_norm.layernorm.weight", p + "attn.k_norm.layernorm.weight"]
             attrs = dict(num_heads=arch.num_heads, kv_num_heads=arch.num_kv_heads, scale=float(arch.scale),
                          local_window_size=int(arch.layer_window(i)) if arch.layer_window(i) else -1, softcap=float(arch.softcap),
-                         do_rotary=0 if arch.learned_positions else 1, rotary_interleaved=int(arch.rotary_interleaved))
+                         do_rotary=0 if (arch.learned_positions or arch.no_rope) else 1, rotary_interleaved=int(arch.rotary_interleaved))
             if arch.qk_norm:
                 attrs["qk_norm_epsilon"] = float(arch.norm_eps)
             if arch.mrope_section:
@@ -986,9 +1026,13 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             m.inputs.append(op.ValueInfo(f"past_conv.{i}", io_dt, ("batch_size", H, arch.conv_L_cache)))
             m.outputs.append(op.ValueInfo(f"present_conv.{i}", io_dt, ("batch_size", H, arch.conv_L_cache)))
             continue
-        if arch.is_linear_layer(i):
-            cs = ("batch_size", arch.linear_conv_dim, arch.linear_conv_kernel_dim - 1)
-            rs = ("batch_size", arch.linear_num_value_heads, arch.linear_key_head_dim, arch.linear_value_head_dim)
+        if arch.is_recurrent_layer(i):
+            if arch.is_mamba_layer(i):
+                cs = ("batch_size", arch.mamba_conv_dim, arch.mamba_conv_kernel - 1)
+                rs = ("batch_size", arch.mamba_num_heads, arch.mamba_head_dim, arch.mamba_state_size)
+            else:
+                cs = ("batch_size", arch.linear_conv_dim, arch.linear_conv_kernel_dim - 1)
+                rs = ("batch_size", arch.linear_num_value_heads, arch.linear_key_head_dim, arch.linear_value_head_dim)
             m.inputs += [op.ValueInfo(f"past_key_values.{i}.conv_state", io_dt, cs), op.ValueInfo(f"past_key_values.{i}.recurrent_state", io_dt, rs)]
             m.outputs += [op.ValueInfo(f"present.{i}.conv_state", io_dt, cs), op.ValueInfo(f"present.{i}.recurrent_state", io_dt, rs)]
             continue
@@ -1212,6 +1256,12 @@ def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
             base = k[: -len("gate_up_proj.weight")]
             half = v.shape[0] // 2
             out[base + "gate_proj.weight"], out[base + "up_proj.weight"] = (v.rows(0, half), v.rows(half, 2 * half)) if hasattr(v, "rows") else (v[:half], v[half:])
+        elif k.endswith("shared_mlp.input_linear.weight"):   # granitemoehybrid: the dense feed-forward, gate rows then up rows
+            base = k[: -len("shared_mlp.input_linear.weight")] + "mlp."
+            half = v.shape[0] // 2
+            out[base + "gate_proj.weight"], out[base + "up_proj.weight"] = (v.rows(0, half), v.rows(half, 2 * half)) if hasattr(v, "rows") else (v[:half], v[half:])
+        elif k.endswith("shared_mlp.output_linear.weight"):
+            out[k[: -len("shared_mlp.output_linear.weight")] + "mlp.down_proj.weight"] = v
         else:
             out[k] = v
     return out

@@ -79,12 +79,12 @@ class PagedKVCache:
         self.conv_index = {i: j for j, i in enumerate(i for i, c in enumerate(conv) if c)}
         cc = conv_channels if conv_channels is not None else arch.hidden_size
         if arch.has_linear_layers:
-            cc = arch.linear_conv_dim
+            cc = arch.recurrent_conv_dim
         self.conv = (torch.zeros(len(self.conv_index), num_blocks * block_size, cc, dtype=dtype, device=device)
                      if self.conv_index else None)
         # Recurrent states of linear-attention layers: [layer, request slot, value heads, key dim, value dim] fp32.  Slots are
         # handed out by the owner of the cache (a generator's rows; the engine's requests) and travel in StepInputs.state_slots.
-        self.lin_index = {i: j for j, i in enumerate(i for i in range(arch.num_layers) if arch.is_linear_layer(i))}
+        self.lin_index = {i: j for j, i in enumerate(i for i in range(arch.num_layers) if arch.is_recurrent_layer(i))}
         self.state = None
         self.state_slots = 0
         row, kdt = (arch.head_dim + 16, torch.int8) if kv_bits == 8 else (arch.head_dim, dtype)
@@ -114,8 +114,7 @@ class PagedKVCache:
         if not self.lin_index or n <= self.state_slots:
             return
         a = self.arch
-        new = torch.zeros(len(self.lin_index), n, a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim,
-                          dtype=torch.float32, device=self.device)
+        new = torch.zeros(len(self.lin_index), n, *a.recurrent_state_shape, dtype=torch.float32, device=self.device)
         if self.state is not None:
             new[:, :self.state_slots] = self.state
         self.state, self.state_slots = new, n
@@ -128,7 +127,7 @@ class PagedKVCache:
                         kv_bits: int = 16) -> int:
         hk = kv_heads if kv_heads is not None else arch.num_kv_heads
         n_conv = sum(1 for i in range(arch.num_layers) if arch.conv_state_channels(i) > 0)
-        cc = arch.linear_conv_dim if arch.has_linear_layers else (conv_channels if conv_channels is not None else arch.hidden_size)
+        cc = arch.recurrent_conv_dim if arch.has_linear_layers else (conv_channels if conv_channels is not None else arch.hidden_size)
         es = torch.empty((), dtype=dtype).element_size()
         kv_row = arch.head_dim + 16 if kv_bits == 8 else arch.head_dim * es
         return ((arch.num_layers - n_conv) * 2 * hk * kv_row + n_conv * cc * es) * block_size
@@ -188,6 +187,14 @@ class LayerWeights:
     conv_out_w: Optional[torch.Tensor] = None
     lin_in_w: Optional[torch.Tensor] = None    # gated-delta-net layer: stacked [qkv | z | b | a] input projection
     lin_conv_w: Optional[torch.Tensor] = None  # depthwise taps [conv_dim, K]
+    mamba_in_w: Optional[torch.Tensor] = None  # Mamba-2 layer: input projection [gate | x, B, C | dt]
+    mamba_conv_w: Optional[torch.Tensor] = None
+    mamba_conv_b: Optional[torch.Tensor] = None
+    mamba_dt_bias: Optional[torch.Tensor] = None
+    mamba_neg_a: Optional[torch.Tensor] = None
+    mamba_d: Optional[torch.Tensor] = None
+    mamba_norm_w: Optional[torch.Tensor] = None
+    mamba_out_w: Optional[torch.Tensor] = None
     lin_dt_bias: Optional[torch.Tensor] = None
     lin_neg_exp_a: Optional[torch.Tensor] = None
     lin_norm_w: Optional[torch.Tensor] = None
@@ -336,6 +343,29 @@ class DecoderModel:
         o = (o.view(T, vd) * torch.nn.functional.silu(z.float())).to(x.dtype)
         return self._row_parallel(o, lw.lin_out_w, None, None)
 
+    def _mamba(self, s: StepInputs, kv: PagedKVCache, li: int, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
+        """A Mamba-2 layer (GraniteMoeHybrid).  Like the gated-delta-net layers, the causal convolution reads the projected
+        (x, B, C) rows of the last K - 1 positions from the paged cache and the state of the scan lives in the request's slot."""
+        a = self.arch
+        if s.state_slots is None:
+            raise RuntimeError("this model has Mamba layers: the caller must provide StepInputs.state_slots")
+        T = x.shape[0]
+        I, cd, nh, P, N, G = a.mamba_intermediate, a.mamba_conv_dim, a.mamba_num_heads, a.mamba_head_dim, a.mamba_state_size, a.mamba_n_groups
+        proj = self._linear(x, lw.mamba_in_w)
+        z, xbc, dt = proj[:, :I], proj[:, I:I + cd], proj[:, I + cd:]
+        ones = torch.ones(T, cd, dtype=x.dtype, device=x.device)
+        conv = ops.short_conv(torch.cat([ones, ones, xbc], dim=1).contiguous(), lw.mamba_conv_w, lw.mamba_conv_b, kv.conv_layer(li), s.slot_mapping,
+                              s.positions, s.cu_seqlens, s.past_lens, s.block_table, kv.block_size)
+        conv = torch.nn.functional.silu(conv.float()).to(x.dtype)
+        xs = conv[:, :I].reshape(T, nh, P).contiguous()
+        Bm = conv[:, I:I + G * N].reshape(T, G, N).contiguous()
+        Cm = conv[:, I + G * N:].reshape(T, G, N).contiguous()
+        step = torch.nn.functional.softplus(dt.float() + lw.mamba_dt_bias)
+        y = ops.mamba2_scan(xs, step, lw.mamba_neg_a, Bm, Cm, lw.mamba_d, kv.state_layer(li), s.state_slots, s.cu_seqlens, s.past_lens).float()
+        y = y.view(T, I) * torch.nn.functional.silu(z.float())                                    # gate, then RMS norm over the whole width
+        y = (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + a.norm_eps) * lw.mamba_norm_w).to(x.dtype)
+        return self._row_parallel(y, lw.mamba_out_w, None, None)
+
     def _lora(self, lw: LayerWeights, proj: str):
         if self._lora_batch is not None:
             from .lora import grouped_lora
@@ -390,7 +420,7 @@ class DecoderModel:
         h = s.inputs_embeds.clone() if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
         if a.learned_positions:
             h = h + ops.embedding(s.positions, self.pos_embed, 1.0)
-        rot = 0 if a.learned_positions else a.rotary_dim
+        rot = a.applied_rotary_dim
         cos, sin = self.cos, self.sin
         if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
             cos, sin = self.cos_small, self.sin_small
@@ -482,7 +512,7 @@ class DecoderModel:
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
             ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
-                               a.head_dim, a.rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+                               a.head_dim, a.applied_rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
                                       max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
@@ -533,7 +563,7 @@ class DecoderModel:
         h = s.inputs_embeds if s.inputs_embeds is not None else ops.embedding(s.input_ids, self.embed, a.embed_scale)
         if a.learned_positions:
             h = h + ops.embedding(s.positions, self.pos_embed, 1.0)
-        rot = 0 if a.learned_positions else a.rotary_dim
+        rot = a.applied_rotary_dim
         residual = None
         cos, sin = self.cos, self.sin
         if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
@@ -553,10 +583,14 @@ class DecoderModel:
                 x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
                 h = self._mlp(lw, x)
                 continue
-            if lw.lin_in_w is not None:
-                h = self._linear_attention(s, kv, li, lw, x)
+            if lw.lin_in_w is not None or lw.mamba_in_w is not None:
+                h = self._linear_attention(s, kv, li, lw, x) if lw.lin_in_w is not None else self._mamba(s, kv, li, lw, x)
+                if a.residual_multiplier != 1.0:
+                    h = (h.float() * a.residual_multiplier).to(h.dtype)
                 x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
                 h = self._mlp(lw, x)
+                if a.residual_multiplier != 1.0:
+                    h = (h.float() * a.residual_multiplier).to(h.dtype)
                 continue
             # ---- attention
             qkv = self._linear(x, lw.qkv_w, lw.qkv_b, lora=self._lora(lw, "qkv_proj"))

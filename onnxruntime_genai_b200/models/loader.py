@@ -132,8 +132,15 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
     a.o_bias = g.by_name.get(f"{fa}/attn/o_proj/Add") is not None
     a.post_sublayer_norms = g.find("/model/layers.0/post_feedforward_layernorm/") is not None
     types = ["conv" if g.find(f"/model/layers.{i}/conv/in_proj/", ops=LINEAR_OPS) is not None else
-             ("linear_attention" if g.by_name.get(f"/model/layers.{i}/linear_attn/LinearAttention") is not None else "full_attention")
+             ("linear_attention" if g.by_name.get(f"/model/layers.{i}/linear_attn/LinearAttention") is not None else
+              ("mamba" if g.by_name.get(f"/model/layers.{i}/mamba/Mamba2") is not None else "full_attention"))
              for i in range(a.num_layers)]
+    if "mamba" in types:
+        a.layer_types = types
+        mb = g.by_name[f"/model/layers.{types.index('mamba')}/mamba/Mamba2"]
+        a.mamba_num_heads, a.mamba_head_dim = int(mb.attrs["num_heads"]), int(mb.attrs["head_dim"])
+        a.mamba_state_size, a.mamba_n_groups = int(mb.attrs["state_size"]), int(mb.attrs["n_groups"])
+        a.mamba_conv_kernel = int(g.lm.info(f"model.layers.{types.index('mamba')}.mamba.conv1d.weight").dims[-1])
     if "linear_attention" in types:
         a.layer_types = types
         la = g.by_name[f"/model/layers.{types.index('linear_attention')}/linear_attn/LinearAttention"]
@@ -151,6 +158,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         a.encoder_hidden_size = _linear_shape(g, g.find("/model/layers.0/cross_attn/kv_proj/", ops=LINEAR_OPS))[1]
     a.parallel_block = g.find("/model/layers.0/parallel_block/") is not None
     a.learned_positions = g.by_name.get("/model/pos_embed/Gather") is not None
+    a.no_rope = (not a.learned_positions and attn is not None and attn.op_type in ("GroupQueryAttention", "PagedAttention")
+                 and int(_attr(attn, "do_rotary", 1)) == 0)
     fc1 = g.find("/model/layers.0/mlp/fc1/", ops=LINEAR_OPS)
     if fc1 is not None:
         a.mlp_gated = False
@@ -376,6 +385,18 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
             if g.has_init(f"model.layers.{i}.conv.conv.bias"):
                 lw.conv_b = _vec(g, f"model.layers.{i}.conv.conv.bias", dtype, device, ch if tpn > 1 else None)
             lw.conv_out_w = _linear_weight(g, linear_node(f"{n}/conv/", "out_proj"), dtype, device, cols=ch if tpn > 1 else None)
+        elif arch.is_mamba_layer(i):
+            if tpn > 1:
+                raise NotImplementedError("Mamba layers are not sharded: run these models on one GPU")
+            mb = f"{n}/mamba/"
+            lw.mamba_in_w = _linear_weight(g, linear_node(mb, "in_proj"), dtype, device)
+            lw.mamba_conv_w = g.tensor(f"model.layers.{i}.mamba.conv1d.weight").reshape(arch.mamba_conv_dim, -1).to(device=device, dtype=dtype).contiguous()
+            lw.mamba_conv_b = _vec(g, f"model.layers.{i}.mamba.conv1d.bias", dtype, device)
+            lw.mamba_dt_bias = g.tensor(f"model.layers.{i}.mamba.dt_bias").float().to(device)
+            lw.mamba_neg_a = g.tensor(f"model.layers.{i}.mamba.neg_exp_A").float().to(device)
+            lw.mamba_d = g.tensor(f"model.layers.{i}.mamba.D").float().to(device)
+            lw.mamba_norm_w = g.tensor(f"model.layers.{i}.mamba.norm.weight").float().to(device)
+            lw.mamba_out_w = _linear_weight(g, linear_node(mb, "out_proj"), dtype, device)
         elif arch.is_linear_layer(i):
             # gated-delta-net layer: four input projections stacked into one GEMM [qkv | z | b | a], the depthwise taps, the gate
             # constants, the per-head norm weight, the output projection

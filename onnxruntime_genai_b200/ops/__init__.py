@@ -386,6 +386,22 @@ def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
     return out
 
 
+def mamba2_scan(x, dt, neg_a, Bm, Cm, Dv, state, slots, cu_seqlens, past_lens):
+    """Mamba-2 selective scan of a state-space layer over packed sequences (see ops/reference.py::mamba2_scan).
+    state [slots, heads, N, P] fp32 is updated in place."""
+    if not x.is_cuda:
+        return ref.mamba2_scan(x, dt, neg_a, Bm, Cm, Dv, state, slots, cu_seqlens, past_lens)
+    T, heads, P = x.shape
+    groups, N = Bm.shape[1], Bm.shape[2]
+    assert x.dtype == torch.bfloat16 and Bm.dtype == torch.bfloat16 and Cm.dtype == torch.bfloat16 and state.dtype == torch.float32
+    assert x.is_contiguous() and Bm.is_contiguous() and Cm.is_contiguous() and state.is_contiguous()
+    dtf, af, df = dt.float().contiguous(), neg_a.float().contiguous(), Dv.float().contiguous()
+    out = torch.empty(T, heads, P, dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.lib().ogb_mamba2_scan(_ptr(x), _ptr(dtf), _ptr(af), _ptr(Bm), _ptr(Cm), _ptr(df), _ptr(state), _ptr(slots), _ptr(cu_seqlens),
+                                          _ptr(past_lens), _ptr(out), past_lens.shape[0], heads, groups, P, N, _stream()), "mamba2_scan")
+    return out
+
+
 def copy_state_slots(src: torch.Tensor, dst: torch.Tensor, src_slots, dst_slots) -> None:
     """dst[:, dst_slots[i]] = src[:, src_slots[i]] for recurrent-state pools [layers, slots, ...] fp32 of the same shape (snapshots
     of linear-attention states around a speculative round)."""

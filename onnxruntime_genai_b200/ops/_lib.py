@@ -81,6 +81,7 @@ _SIGS = {
     "ogb_paged_attention_kv8": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
     "ogb_gated_delta": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "ogb_mamba2_scan": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_copy_state_slots": (c_int, [_P, _P, c_int, c_int, c_longlong, _P, _P, c_int, _P]),
     "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),
     "ogb_argmax": (c_int, [_P, c_longlong, c_int, c_int, _P, _P]),

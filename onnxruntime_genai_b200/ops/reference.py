@@ -320,3 +320,29 @@ def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
             out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
         state[slot] = S.to(state.dtype)
     return out.to(v.dtype)
+
+
+def mamba2_scan(x, dt, neg_a, Bm, Cm, Dv, state, slots, cu_seqlens, past_lens):
+    """Mamba-2 selective scan over packed sequences.  x [T, heads, P], dt [T, heads] (after softplus), neg_a [heads] (= -exp(A_log)),
+    Bm / Cm [T, groups, N], Dv [heads]; state [slots, heads, N, P] fp32, updated in place for the request slots (a request whose
+    past length is 0 starts from a zero state).  Head h reads group h // (heads / groups).  Per token:
+    S *= exp(dt * A);  S[n][p] += dt * x[p] * B[n];  y[p] = sum_n S[n][p] * C[n] + D * x[p]."""
+    T, heads, P = x.shape
+    groups = Bm.shape[1]
+    rep = heads // groups
+    out = torch.zeros(T, heads, P, dtype=torch.float32, device=x.device)
+    cu = cu_seqlens.tolist()
+    xf, dtf = x.float(), dt.float()
+    Bf, Cf = Bm.float().repeat_interleave(rep, dim=1), Cm.float().repeat_interleave(rep, dim=1)      # [T, heads, N]
+    for r in range(len(cu) - 1):
+        slot = int(slots[r])
+        S = state[slot].float()
+        if int(past_lens[r]) == 0:
+            S = torch.zeros_like(S)
+        for t in range(cu[r], cu[r + 1]):
+            S = S * torch.exp(dtf[t] * neg_a.float())[:, None, None]
+            S = S + Bf[t][:, :, None] * (dtf[t][:, None] * xf[t])[:, None, :]
+            out[t] = torch.einsum("hnp,hn->hp", S, Cf[t]) + Dv.float()[:, None] * xf[t]
+        state[slot] = S.to(state.dtype)
+    return out.to(x.dtype)
+
