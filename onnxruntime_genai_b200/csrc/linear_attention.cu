@@ -94,29 +94,33 @@ OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const f
 // group gr = h / (heads / groups), per token t, with dt already softplus'ed:
 //     S *= exp(dt[t, h] * A[h]);   S[n][p] += dt[t, h] * x[t, h, p] * B[t, gr, n];   y[t, h, p] = sum_n S[n][p] * C[t, gr, n] + D[h] * x[t, h, p]
 // state [slots][heads][N][P] fp32, updated in place for the request slots (a request whose past length is 0 starts from a
-// zero state).  One CTA per (request, head); thread p keeps column S[.][p] in registers, the token's B and C rows sit in
+// zero state).  One CTA per (request, head); a thread keeps 16 to 64 rows of one state column in registers (the rows of a column
+// are split over up to 8 threads whose partial sums meet in shared memory), the token's B and C rows sit in
 // shared memory; the tokens of a chunk are walked in order.
 namespace ogb {
-template <int N>
-__global__ void __launch_bounds__(128) mamba2_scan_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dt,
-                                                         const float* __restrict__ neg_a, const __nv_bfloat16* __restrict__ Bm,
-                                                         const __nv_bfloat16* __restrict__ Cm, const float* __restrict__ Dv,
-                                                         float* __restrict__ state, const int32_t* __restrict__ slots,
-                                                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ past_lens,
-                                                         __nv_bfloat16* __restrict__ out, int heads, int groups, int P) {
+template <int NPT>
+__global__ void __launch_bounds__(512) mamba2_scan_kernel(
+    const __nv_bfloat16* __restrict__ x, const float* __restrict__ dt, const float* __restrict__ neg_a, const __nv_bfloat16* __restrict__ Bm,
+    const __nv_bfloat16* __restrict__ Cm, const float* __restrict__ Dv, float* __restrict__ state, const int32_t* __restrict__ slots,
+    const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ past_lens, __nv_bfloat16* __restrict__ out, int heads, int groups, int P,
+    int N) {
+  // thread (j, sp): column j of the state, rows [sp * NPT, (sp + 1) * NPT); the partial dot products of the splits meet in shared memory
   pdl_launch_dependents();
   pdl_wait();
-  const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int splits = N / NPT, Pp = blockDim.x / splits;
+  const int j = threadIdx.x % Pp, sp = threadIdx.x / Pp, n0 = sp * NPT;
   const int gr = h / (heads / groups);
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   if (t0 >= t1) return;
-  __shared__ float sB[N], sC[N];
-  float* S = state + ((size_t(slots[b]) * heads + h) * N) * P;
-  float col[N];
+  __shared__ float sB[256], sC[256];
+  __shared__ float sY[8][128];
+  float* S = state + ((size_t(slots[b]) * heads + h) * N + n0) * P;
+  float col[NPT];
   const bool live = j < P;
   const bool fresh = past_lens[b] == 0;
 #pragma unroll
-  for (int i = 0; i < N; ++i) col[i] = (live && !fresh) ? S[size_t(i) * P + j] : 0.f;
+  for (int i = 0; i < NPT; ++i) col[i] = (live && !fresh) ? S[size_t(i) * P + j] : 0.f;
   const float a = neg_a[h], d = Dv[h];
   for (int t = t0; t < t1; ++t) {
     __syncthreads();
@@ -131,15 +135,21 @@ __global__ void __launch_bounds__(128) mamba2_scan_kernel(const __nv_bfloat16* _
     const float dx = step * xj;
     float y = 0.f;
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-      col[i] = fmaf(col[i], decay, dx * sB[i]);
-      y = fmaf(col[i], sC[i], y);
+    for (int i = 0; i < NPT; ++i) {
+      col[i] = fmaf(col[i], decay, dx * sB[n0 + i]);
+      y = fmaf(col[i], sC[n0 + i], y);
     }
-    if (live) out[(size_t(t) * heads + h) * P + j] = f2bf(y + d * xj);
+    if (splits > 1) {
+      sY[sp][j] = y;
+      __syncthreads();
+      if (sp == 0)
+        for (int q = 1; q < splits; ++q) y += sY[q][j];
+    }
+    if (live && sp == 0) out[(size_t(t) * heads + h) * P + j] = f2bf(y + d * xj);
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < N; ++i) S[size_t(i) * P + j] = col[i];
+    for (int i = 0; i < NPT; ++i) S[size_t(i) * P + j] = col[i];
   }
 }
 }  // namespace ogb
@@ -149,18 +159,23 @@ OGB_API int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, 
                             int P, int N, void* stream) {
   if (B <= 0) return 0;
   if (heads <= 0 || groups <= 0 || heads % groups || P <= 0 || P > 128) return -1;
-  dim3 grid(B, heads);
+  if (N < 16 || N > 256 || (N & (N - 1))) return -5;
+  const int Pp = (P + 31) / 32 * 32;
+  int npt = N < 32 ? N : 32;
+  if (Pp * (N / npt) > 512) npt = 64;
+  const int splits = N / npt;
+  if (splits > 8 || Pp * splits > 512) return -5;
+  dim3 grid(B, heads), block(Pp * splits);
   auto s = static_cast<cudaStream_t>(stream);
   auto X = static_cast<const __nv_bfloat16*>(x);
   auto Bp = static_cast<const __nv_bfloat16*>(Bm);
   auto Cp = static_cast<const __nv_bfloat16*>(Cm);
   auto O = static_cast<__nv_bfloat16*>(out);
   bool ok;
-  switch (N) {
-    case 16: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<16>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
-    case 32: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<32>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
-    case 64: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<64>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
-    case 128: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<128>, grid, dim3(128), 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P); break;
+  switch (npt) {
+    case 16: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<16>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N); break;
+    case 32: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<32>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N); break;
+    case 64: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<64>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N); break;
     default: return -5;
   }
   return ok ? 0 : -4;

@@ -17,7 +17,7 @@ LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
     "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl",
-    "qwen3_next", "qwen3_5", "qwen3_5_text", "granitemoehybrid",      # hybrids of gated-delta-net (linear attention) and full-attention layers
+    "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoehybrid", "granitemoeshared",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
 
 
@@ -87,6 +87,9 @@ class ArchConfig:
     encoder_hidden_size: int = 0     # width of the encoder output the cross-attention keys / values are projected from (0 = hidden_size)
     mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
     parallel_block: bool = False     # phi: attention and MLP both read the input norm; their outputs are summed
+    shared_expert_intermediate: int = 0   # MoE layers with an always-on dense gated MLP beside the routed experts (0 = none)
+    shared_expert_gated: bool = False     # its output is scaled by sigmoid(x . w) of a one-row projection
+    attn_output_gate: bool = False   # q_proj carries a second half per head: sigmoid of it gates the attention output before o_proj
     no_rope: bool = False            # attention without any position encoding (hybrids whose recurrent layers carry the order)
     learned_positions: bool = False  # gpt2: a learned position table added to the token embedding, no rotary embedding
     # mixture of experts (gpt-oss style)
@@ -214,6 +217,18 @@ class ArchConfig:
 
 def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
     """Maps a Hugging Face `config.json` dictionary to an ArchConfig."""
+    if isinstance(cfg.get("text_config"), dict) and "hidden_size" not in cfg:
+        # a multimodal checkpoint's configuration: the decoder is described by its text part
+        cfg = {**{k: v for k, v in cfg.items() if k not in ("text_config", "vision_config", "audio_config")}, **cfg["text_config"],
+               "architectures": cfg.get("architectures"), "model_type": cfg["text_config"].get("model_type", cfg.get("model_type"))}
+    if isinstance(cfg.get("rope_parameters"), dict):
+        # newer configurations keep the rotary settings in one dictionary
+        rp = cfg["rope_parameters"]
+        cfg = dict(cfg)
+        cfg.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
+        cfg.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0))
+        if rp.get("rope_type", "default") not in ("default", None) and not cfg.get("rope_scaling"):
+            cfg["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
     archs = cfg.get("architectures") or [cfg.get("model_type", "llama")]
     name = archs[0]
     mtype = name.split("For")[0].lower() if "For" in name else cfg.get("model_type", name).lower()
@@ -243,6 +258,8 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         pad_token_id=cfg.get("pad_token_id") if cfg.get("pad_token_id") is not None else 0,
     )
     mt = cfg.get("model_type", mtype)
+    if a.model_type not in LLM_TYPES and mt in LLM_TYPES:
+        a.model_type = mt      # class names that do not spell the family the way its configuration does (Qwen2Moe..., GraniteMoeHybrid...)
     if mt == "gpt2":
         a.hidden_size = cfg.get("n_embd", a.hidden_size)
         a.num_heads = a.num_kv_heads = cfg.get("n_head", a.num_heads)
@@ -252,6 +269,8 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.context_length = cfg.get("n_positions", a.context_length)
     if mt == "qwen2":
         a.attn_bias = True
+    if mt == "qwen2_moe":
+        a.attn_bias = bool(cfg.get("qkv_bias", True))
     if mt in ("qwen3", "gemma3_text", "olmo2"):
         a.qk_norm = mt != "olmo2" or True
     if mt in ("mistral", "qwen2", "phi3") and cfg.get("sliding_window") and cfg.get("use_sliding_window", mt != "qwen2"):
@@ -283,7 +302,8 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.sliding_layers = ([i for i, t in enumerate(lt) if t == "sliding_attention"] if lt
                             else [i for i in range(a.num_layers) if i % 2 == 0])
         a.moe_swiglu_limit = cfg.get("swiglu_limit", 7.0)
-    if mt in ("mixtral", "phimoe", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe"):
+    if (mt in ("mixtral", "phimoe", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoeshared") or
+            (mt == "granitemoehybrid" and int(cfg.get("num_local_experts") or 0) > 0)):
         a.moe_style = "standard"
         a.num_experts = cfg.get("num_local_experts", cfg.get("num_experts", 8))
         a.experts_per_token = cfg.get("num_experts_per_tok", 2)
@@ -291,6 +311,14 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.intermediate_size = cfg.get("moe_intermediate_size", a.intermediate_size)
         if mt == "qwen3_moe":
             a.qk_norm = True
+        if mt in ("qwen2_moe", "qwen3_5_moe", "qwen3_5_moe_text"):
+            a.shared_expert_intermediate = int(cfg.get("shared_expert_intermediate_size") or 0)
+            a.shared_expert_gated = a.shared_expert_intermediate > 0
+        if mt in ("granitemoeshared", "granitemoehybrid"):
+            a.shared_expert_intermediate = int(cfg.get("shared_intermediate_size") or 0)
+            a.intermediate_size = int(cfg.get("intermediate_size", a.intermediate_size))
+        if mt in ("granitemoe", "granitemoeshared", "granitemoehybrid"):
+            a.moe_norm_topk = True        # softmax over the selected experts' logits: the softmax over all, renormalised over the selected
         if mt == "phimoe":
             a.moe_sparse_mixer = True
             a.moe_jitter_eps = float(cfg.get("router_jitter_noise", 0.01))
@@ -299,8 +327,6 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
             a.lm_head_bias = bool(cfg.get("lm_head_bias", True))
     if mt == "granitemoehybrid":
         # hybrid of Mamba-2 and attention layers; the feed-forward of the dense members is the "shared" gated MLP
-        if int(cfg.get("num_local_experts") or 0) > 0:
-            raise NotImplementedError("granitemoehybrid with routed experts beside the shared MLP is not supported: dense members only")
         a.layer_types = ["full_attention" if t == "attention" else t for t in (cfg.get("layer_types") or ["mamba"] * a.num_layers)]
         a.mamba_num_heads = int(cfg.get("mamba_n_heads", 128))
         dh = cfg.get("mamba_d_head", 64)
@@ -308,9 +334,10 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.mamba_state_size = int(cfg.get("mamba_d_state", 256))
         a.mamba_n_groups = int(cfg.get("mamba_n_groups", 1))
         a.mamba_conv_kernel = int(cfg.get("mamba_d_conv", 4))
-        a.intermediate_size = int(cfg.get("shared_intermediate_size", a.intermediate_size))
+        if a.num_experts == 0:
+            a.intermediate_size = int(cfg.get("shared_intermediate_size", a.intermediate_size))
         a.no_rope = cfg.get("position_embedding_type") != "rope"
-    if mt in ("granite", "granitemoehybrid"):
+    if mt in ("granite", "granitemoe", "granitemoeshared", "granitemoehybrid"):
         a.residual_multiplier = cfg.get("residual_multiplier", 1.0)
         a.logits_scale = 1.0 / cfg.get("logits_scaling", 1.0)
         a.embed_scale = cfg.get("embedding_multiplier", 1.0)
@@ -325,6 +352,12 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.mrope_section = list((cfg.get("rope_scaling") or {}).get("mrope_section") or [16, 24, 24])
         a.rope_scaling = None
         a.attn_bias = True
+    if mt in ("qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text"):
+        # zero-centred RMS norms (weights stored as offsets from one), per-head q / k norms, attention output gated by the second half of q_proj
+        a.qk_norm = True
+        a.norm_offset = 1.0
+        a.attn_output_gate = True
+        a.mrope_section = None          # text positions: the three rotary components coincide
     if cfg.get("linear_num_value_heads"):
         # hybrid gated-delta-net stacks: every `full_attention_interval`-th layer attends, the others are linear-attention layers
         a.linear_num_key_heads = int(cfg.get("linear_num_key_heads", 0))

@@ -87,6 +87,8 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             s[p + "linear_attn.out_proj.weight"] = (H, arch.linear_value_dim)
         else:
             s[p + "self_attn.q_proj.weight"] = (arch.q_size, H)
+            if arch.attn_output_gate:
+                s[p + "self_attn.gate_proj.weight"] = (arch.q_size, H)
             s[p + "self_attn.k_proj.weight"] = (arch.kv_size, H)
             s[p + "self_attn.v_proj.weight"] = (arch.kv_size, H)
             s[p + "self_attn.o_proj.weight"] = (H, arch.q_size)
@@ -115,6 +117,13 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
             s[p + "mlp.experts.gate_proj"] = (E, I, H)
             s[p + "mlp.experts.up_proj"] = (E, I, H)
             s[p + "mlp.experts.down_proj"] = (E, H, I)
+            if arch.shared_expert_intermediate:
+                Is = arch.shared_expert_intermediate
+                s[p + "mlp.shared_expert.gate_proj.weight"] = (Is, H)
+                s[p + "mlp.shared_expert.up_proj.weight"] = (Is, H)
+                s[p + "mlp.shared_expert.down_proj.weight"] = (H, Is)
+                if arch.shared_expert_gated:
+                    s[p + "mlp.shared_expert_gate.weight"] = (1, H)
         elif arch.num_experts > 0:
             E = arch.num_experts
             s[p + "mlp.router.weight"] = (E, H)
@@ -801,8 +810,16 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                 attrs["rotary_embedding_dim"] = int(arch.rotary_dim)
             W.node(attn_op, f"{n}/attn/{attn_op}", attn_inputs, [f"{n}/attn/{attn_op}/output_0", f"present.{i}.key", f"present.{i}.value"],
                    domain="com.microsoft", **attrs)
+            o_in = f"{n}/attn/{attn_op}/output_0"
+            if arch.attn_output_gate:
+                # the attention output is scaled by sigmoid of a second projection of the layer input (stored as the odd head-halves of q_proj)
+                put_linear(p + "attn.gate_proj", f"{n}/attn/gate_proj/MatMul", [p + "self_attn.gate_proj.weight"], x, f"{n}/attn/gate_proj/MatMul/output_0",
+                           arch.q_size, H)
+                W.node("Sigmoid", f"{n}/attn/gate/Sigmoid", [f"{n}/attn/gate_proj/MatMul/output_0"], [f"{n}/attn/gate/Sigmoid/output_0"])
+                W.node("Mul", f"{n}/attn/gate/Mul", [o_in, f"{n}/attn/gate/Sigmoid/output_0"], [f"{n}/attn/gate/Mul/output_0"])
+                o_in = f"{n}/attn/gate/Mul/output_0"
             o_out = f"{n}/attn/o_proj/MatMul/output_0"
-            put_linear(p + "attn.o_proj", f"{n}/attn/o_proj/MatMul", [p + "self_attn.o_proj.weight"], f"{n}/attn/{attn_op}/output_0", o_out,
+            put_linear(p + "attn.o_proj", f"{n}/attn/o_proj/MatMul", [p + "self_attn.o_proj.weight"], o_in, o_out,
                        H, arch.q_size)
             if arch.o_bias:
                 put_vec(p + "attn.o_proj.Add.bias", [p + "self_attn.o_proj.bias"])
@@ -872,6 +889,27 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                    activation_beta=0.0, swiglu_fusion=0, normalize_routing_weights=int(arch.moe_norm_topk),
                    use_sparse_mixer=int(arch.moe_sparse_mixer), **({"sparse_mixer_jitter_eps": float(arch.moe_jitter_eps)} if arch.moe_sparse_mixer else {}))
             mlp_out = f"{n}/moe/MoE/output_0"
+            if arch.shared_expert_intermediate:
+                # the always-on dense gated MLP beside the routed experts (reference graph: builders/qwen.py make_shared_expert); its output is
+                # scaled by sigmoid of a one-row projection where the family has that gate, then added to the routed output
+                Is, sh = arch.shared_expert_intermediate, f"{n}/moe/shared_expert"
+                put_linear(p + "moe.shared_expert.gate_up_proj", f"{sh}/gate_up_proj/MatMul",
+                           [p + "mlp.shared_expert.gate_proj.weight", p + "mlp.shared_expert.up_proj.weight"], x, f"{sh}/gate_up_proj/MatMul/output_0", 2 * Is, H)
+                W.node("Split", f"{sh}/gate_up_proj/Split", [f"{sh}/gate_up_proj/MatMul/output_0"], [f"{sh}/gate", f"{sh}/up"], axis=-1, num_outputs=2)
+                W.node("Sigmoid", f"{sh}/act_fn/Sigmoid", [f"{sh}/gate"], [f"{sh}/act_fn/Sigmoid/output_0"])
+                W.node("Mul", f"{sh}/act_fn/Mul", [f"{sh}/gate", f"{sh}/act_fn/Sigmoid/output_0"], [f"{sh}/act_fn/output_0"])
+                W.node("Mul", f"{sh}/Mul", [f"{sh}/act_fn/output_0", f"{sh}/up"], [f"{sh}/Mul/output_0"])
+                put_linear(p + "moe.shared_expert.down_proj", f"{sh}/down_proj/MatMul", [p + "mlp.shared_expert.down_proj.weight"], f"{sh}/Mul/output_0",
+                           f"{sh}/down_proj/MatMul/output_0", H, Is)
+                sh_out = f"{sh}/down_proj/MatMul/output_0"
+                if arch.shared_expert_gated:
+                    put_linear(p + "moe.shared_expert_gate", f"{n}/moe/shared_expert_gate/MatMul", [p + "mlp.shared_expert_gate.weight"], x,
+                               f"{n}/moe/shared_expert_gate/MatMul/output_0", 1, H)
+                    W.node("Sigmoid", f"{n}/moe/shared_expert_gate/Sigmoid", [f"{n}/moe/shared_expert_gate/MatMul/output_0"], [f"{n}/moe/shared_expert_gate/Sigmoid/output_0"])
+                    W.node("Mul", f"{n}/moe/shared_expert_gate/Mul", [sh_out, f"{n}/moe/shared_expert_gate/Sigmoid/output_0"], [f"{n}/moe/shared_expert_gate/Mul/output_0"])
+                    sh_out = f"{n}/moe/shared_expert_gate/Mul/output_0"
+                W.node("Add", f"{n}/moe/shared_expert/Add", [mlp_out, sh_out], [f"{n}/moe/shared_expert/Add/output_0"])
+                mlp_out = f"{n}/moe/shared_expert/Add/output_0"
         elif arch.num_experts > 0:
             E = arch.num_experts
             put_linear(p + "moe.router", f"{n}/moe/router/MatMul", [p + "mlp.router.weight"], x, f"{n}/moe/router/MatMul/output_0", E, H)
@@ -1247,6 +1285,9 @@ def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
             from .quantized_checkpoint import convert_state_dict
             sd = convert_state_dict(sd, qc)
     out = {}
+    if any(k.startswith("model.language_model.") for k in sd):
+        # the decoder of a multimodal checkpoint: its weights under the plain decoder names (the towers keep theirs)
+        sd = {("model." + k[len("model.language_model."):] if k.startswith("model.language_model.") else k): v for k, v in sd.items()}
     for k, v in sd.items():
         if k.endswith("qkv_proj.weight"):  # phi3 packs q, k, v
             base = k[: -len("qkv_proj.weight")]
@@ -1265,6 +1306,49 @@ def load_hf_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
         else:
             out[k] = v
     return out
+
+
+def _canonical_moe_names(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
+    """Routed experts of a Hugging Face checkpoint under this exporter's names: `mlp.router.weight` [E, H] and
+    `mlp.experts.{gate,up,down}_proj` stacked over the experts.  Sources: one module per expert (`block_sparse_moe.experts.N.w1/w3/w2`,
+    `mlp.experts.N.gate_proj/up_proj/down_proj`), stacked and fused tensors (`mlp.experts.gate_up_proj` [E, 2I, H] gate rows first,
+    `block_sparse_moe.input_linear / output_linear`); a dense MLP stored beside them becomes the shared expert."""
+    if arch.num_experts == 0 or arch.moe_style != "standard":
+        return
+    E = arch.num_experts
+    for i in range(arch.num_layers):
+        p = f"model.layers.{i}."
+        for src in ("block_sparse_moe.gate.weight", "block_sparse_moe.router.layer.weight", "mlp.gate.weight"):
+            if p + src in sd:
+                sd[p + "mlp.router.weight"] = sd.pop(p + src)
+        for base, names in (("block_sparse_moe.experts.", ("w1", "w3", "w2")), ("mlp.experts.", ("gate_proj", "up_proj", "down_proj"))):
+            if f"{p}{base}0.{names[0]}.weight" in sd:
+                for nm, dst in zip(names, ("gate_proj", "up_proj", "down_proj")):
+                    sd[p + "mlp.experts." + dst] = torch.stack([sd.pop(f"{p}{base}{e}.{nm}.weight").float() for e in range(E)])
+        for fused, down in (("mlp.experts.gate_up_proj", None), ("block_sparse_moe.input_linear.weight", "block_sparse_moe.output_linear.weight")):
+            if p + fused in sd and sd[p + fused].dim() == 3:
+                gu = sd.pop(p + fused)
+                half = gu.shape[1] // 2
+                sd[p + "mlp.experts.gate_proj"], sd[p + "mlp.experts.up_proj"] = gu[:, :half].contiguous(), gu[:, half:].contiguous()
+                if down is not None:
+                    sd[p + "mlp.experts.down_proj"] = sd.pop(p + down)
+        if arch.shared_expert_intermediate and p + "mlp.gate_proj.weight" in sd:      # from `shared_mlp.input_linear / output_linear`
+            for nm in ("gate_proj", "up_proj", "down_proj"):
+                sd[p + f"mlp.shared_expert.{nm}.weight"] = sd.pop(p + f"mlp.{nm}.weight")
+
+
+def _split_gated_q(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
+    """q_proj of a gated-attention checkpoint holds [query | gate] per head: the gate halves become a projection of their own."""
+    if not arch.attn_output_gate:
+        return
+    D = arch.head_dim
+    for k in [k for k in sd if k.endswith("self_attn.q_proj.weight")]:
+        v = sd[k]
+        if v.shape[0] != 2 * arch.q_size:
+            continue
+        w = v.reshape(arch.num_heads, 2, D, v.shape[1])
+        sd[k] = w[:, 0].reshape(arch.q_size, v.shape[1]).contiguous()
+        sd[k[: -len("q_proj.weight")] + "gate_proj.weight"] = w[:, 1].reshape(arch.q_size, v.shape[1]).contiguous()
 
 
 def _split_packed_qkv(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
@@ -1296,6 +1380,8 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         if not int(extra.get("random_weights", 0)) and not int(extra.get("synthetic_weights", 0)):
             state_dict = load_hf_state_dict(model_name_or_dir)
             _split_packed_qkv(state_dict, arch)
+            _split_gated_q(state_dict, arch)
+            _canonical_moe_names(state_dict, arch)
             if precision != "int4":   # an int4 checkpoint exported at a float precision: dequantise
                 state_dict = {k: (v.float() if hasattr(v, "matmulnbits") else v) for k, v in state_dict.items()}
         for fn in ("tokenizer.json", "tokenizer_config.json", "special_tokens_map.json", "tokenizer.model", "chat_template.jinja",

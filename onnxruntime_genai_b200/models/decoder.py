@@ -172,6 +172,8 @@ class LayerWeights:
     ln2_b: Optional[torch.Tensor] = None
     qkv_b: Optional[torch.Tensor] = None
     o_b: Optional[torch.Tensor] = None
+    shared_gate_w: Optional[torch.Tensor] = None # MoE layers with a shared expert (held in gate_up_w / down_w): its output * sigmoid(x @ shared_gate_w^T)
+    attn_gate_w: Optional[torch.Tensor] = None   # gated attention output: att * sigmoid(x @ attn_gate_w^T) before o_proj
     q_norm_w: Optional[torch.Tensor] = None
     k_norm_w: Optional[torch.Tensor] = None
     sinks: Optional[torch.Tensor] = None
@@ -276,7 +278,15 @@ class DecoderModel:
         a = self.arch
         if a.num_experts > 0:
             from .moe import moe_forward
-            return moe_forward(self, lw, x, defer)
+            if lw.gate_up_w is None:
+                return moe_forward(self, lw, x, defer)
+            # routed experts + the always-on shared expert
+            y = moe_forward(self, lw, x, False)
+            act = ops.gate_up_act(x, lw.gate_up_w, lw.gate_up_b, a.activation, interleaved=lw.gate_up_interleaved)
+            sh = self._linear(act, lw.down_w, lw.down_b)
+            if lw.shared_gate_w is not None:
+                sh = (sh.float() * torch.sigmoid(x.float() @ lw.shared_gate_w.float().t())).to(sh.dtype)
+            return y + sh
         if not a.mlp_gated:
             y = ops.activation(self._linear(x, lw.fc1_w, lw.fc1_b, lora=self._lora(lw, "fc1")), a.activation)
             return self._row_parallel(y, lw.fc2_w, lw.fc2_b, self._lora(lw, "fc2"))
@@ -411,7 +421,7 @@ class DecoderModel:
         lw = self.layers[0]
         return (self.norms_folded and self.fuse_steps and self.active_adapter is None and s.lora_ids is None and
                 s.input_ids.shape[0] <= ops.FUSED_MAX_TOKENS and
-                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and not a.has_linear_layers and
+                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and not a.has_linear_layers and not a.attn_output_gate and
                 lw.post_attn_norm_w is None and lw.post_ffn_norm_w is None and not s.cross_qk_heads)
 
     def _forward_fused(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
@@ -601,6 +611,8 @@ class DecoderModel:
                                a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
                                s.positions3 if a.mrope_section else None, a.mrope_section)
             att = self._attention(s, qkv, kc, vc, table, kv.block_size, lw)
+            if lw.attn_gate_w is not None:
+                att = (att.float() * torch.sigmoid(self._linear(x, lw.attn_gate_w, None).float())).to(att.dtype)
             h = self._row_parallel(att, lw.o_w, lw.o_b, self._lora(lw, "o_proj"))
             if lw.cross_q_w is not None:
                 if s.cross is None:

@@ -440,6 +440,12 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                 lw.o_w = _q4_weight(g, [o], device)
             else:
                 lw.o_w = _linear_weight(g, o, dtype, device, cols=slice(tpr * hq_l * D, (tpr + 1) * hq_l * D) if tpn > 1 else None)
+            gate = g.find(f"{n}/attn/gate_proj/", ops=LINEAR_OPS)
+            if gate is not None:
+                if tpn > 1:
+                    raise NotImplementedError("gated attention output is not sharded: run these models on one GPU")
+                lw.attn_gate_w = _linear_weight(g, gate, dtype, device)
+                arch.attn_output_gate = True
             oadd = g.by_name.get(f"{n}/attn/o_proj/Add")
             if oadd is not None:
                 lw.o_b = _vec(g, oadd.inputs[1], dtype, device)
@@ -558,6 +564,18 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
             else:
                 lw.exp_gate_up_w, lw.exp_gate_up_b = experts(moe.inputs[2]), experts(moe.inputs[3])
                 lw.exp_down_w, lw.exp_down_b = experts(moe.inputs[4]), experts(moe.inputs[5])
+            sh = linear_node(f"{n}/moe/shared_expert/", "gate_up_proj")
+            if sh is not None:
+                # the always-on dense MLP beside the routed experts: [gate rows | up rows], not sharded
+                if tpn > 1:
+                    raise NotImplementedError("shared experts are not sharded: run these models on one GPU")
+                lw.gate_up_w = _linear_weight(g, sh, dtype, device)
+                lw.gate_up_interleaved = False
+                lw.down_w = _linear_weight(g, linear_node(f"{n}/moe/shared_expert/", "down_proj"), dtype, device)
+                sg = linear_node(f"{n}/moe/", "shared_expert_gate")
+                lw.shared_gate_w = _linear_weight(g, sg, dtype, device) if sg is not None else None
+                arch.shared_expert_intermediate = lw.down_w.shape[1]
+                arch.shared_expert_gated = sg is not None
             if not packed_experts:
                 lw.exp_blocked = False
             if not packed_experts and torch.device(device).type == "cuda" and (lw.exp_gate_up_w.shape[1] // 2) % 64 == 0:
