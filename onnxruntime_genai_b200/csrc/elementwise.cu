@@ -288,6 +288,7 @@ __global__ void act_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
       if (act == 0) a = g / (1.f + __expf(-g));
       else if (act == 1) a = 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
       else if (act == 2) a = fmaxf(g, 0.f);
+      else if (act == 4) { const float r = fmaxf(g, 0.f); a = r * r; }
       else a = 0.5f * g * (1.f + erff(g * 0.70710678f));
       e[j] = f2bf(a);
     }

@@ -14,8 +14,8 @@ from typing import Any, Dict, List, Optional
 import numpy as np
 
 LLM_TYPES = [
-    "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan",
-    "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
+    "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan", "hunyuandensev1", "hunyuan_v1_dense",
+    "internlm2", "llama", "mistral", "nemotron", "olmo", "phi", "phi3", "phi3small", "phimoe", "qwen2", "qwen3",
     "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl",
     "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoehybrid", "granitemoeshared",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
@@ -89,7 +89,11 @@ class ArchConfig:
     parallel_block: bool = False     # phi: attention and MLP both read the input norm; their outputs are summed
     shared_expert_intermediate: int = 0   # MoE layers with an always-on dense gated MLP beside the routed experts (0 = none)
     shared_expert_gated: bool = False     # its output is scaled by sigmoid(x . w) of a one-row projection
+    qk_norm_full_width: bool = False # olmoe: q and k are normalised over all their heads at once (weights [q_size] / [kv_size]), before the rotary embedding
+    qk_norm_after_rope: bool = False # hunyuan: the per-head q / k norms follow the rotary embedding
     attn_output_gate: bool = False   # q_proj carries a second half per head: sigmoid of it gates the attention output before o_proj
+    rope_local_theta: float = 0.0    # gemma3: sliding-window layers rotate with this base and no rescaling (a second cache pair)
+    no_rope_layers: Optional[List[int]] = None   # layers whose attention applies no rotary embedding (smollm3)
     no_rope: bool = False            # attention without any position encoding (hybrids whose recurrent layers carry the order)
     learned_positions: bool = False  # gpt2: a learned position table added to the token embedding, no rotary embedding
     # mixture of experts (gpt-oss style)
@@ -121,6 +125,12 @@ class ArchConfig:
     def rotary_dim(self) -> int:
         r = int(self.head_dim * self.partial_rotary_factor)
         return r - (r % 2)
+
+    def layer_rope_mode(self, layer: int) -> int:
+        """0: the model's rotary caches, 1: the local caches (`rope_local_theta`), 2: no rotary embedding."""
+        if self.learned_positions or self.no_rope or (self.no_rope_layers is not None and layer in self.no_rope_layers):
+            return 2
+        return 1 if (self.rope_local_theta and self.layer_window(layer)) else 0
 
     @property
     def applied_rotary_dim(self) -> int:
@@ -225,10 +235,28 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         # newer configurations keep the rotary settings in one dictionary
         rp = cfg["rope_parameters"]
         cfg = dict(cfg)
+        if isinstance(rp.get("full_attention"), dict):
+            # one dictionary per layer kind: the sliding-window layers' base becomes the local base
+            if isinstance(rp.get("sliding_attention"), dict) and rp["sliding_attention"].get("rope_theta"):
+                cfg.setdefault("rope_local_base_freq", rp["sliding_attention"]["rope_theta"])
+            rp = rp["full_attention"]
         cfg.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
         cfg.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0))
         if rp.get("rope_type", "default") not in ("default", None) and not cfg.get("rope_scaling"):
             cfg["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
+    if "ffn_hidden_size" in cfg and "multi_query_group_num" in cfg:
+        # ChatGLM's own key names (reference reads the same fallbacks: builders/base.py:80-121)
+        cfg = dict(cfg)
+        cfg.setdefault("vocab_size", cfg.get("padded_vocab_size"))
+        cfg.setdefault("num_hidden_layers", cfg.get("num_layers"))
+        cfg.setdefault("intermediate_size", cfg["ffn_hidden_size"])
+        cfg.setdefault("num_key_value_heads", cfg["multi_query_group_num"] if cfg.get("multi_query_attention", True) else cfg.get("num_attention_heads"))
+        cfg.setdefault("head_dim", cfg.get("kv_channels"))
+        cfg.setdefault("max_position_embeddings", cfg.get("seq_length", 8192))
+        cfg.setdefault("rms_norm_eps", cfg.get("layernorm_epsilon", 1e-5))
+        cfg.setdefault("rope_theta", 10000.0 * float(cfg.get("rope_ratio", 1.0)))
+        cfg.setdefault("attention_bias", bool(cfg.get("add_qkv_bias", False)))
+        cfg["model_type"] = "chatglm"
     archs = cfg.get("architectures") or [cfg.get("model_type", "llama")]
     name = archs[0]
     mtype = name.split("For")[0].lower() if "For" in name else cfg.get("model_type", name).lower()
@@ -267,12 +295,46 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.head_dim = a.hidden_size // a.num_heads
         a.intermediate_size = cfg.get("n_inner") or 4 * a.hidden_size
         a.context_length = cfg.get("n_positions", a.context_length)
+    if cfg.get("attention_bias") and mt not in ("qwen2", "qwen2_moe"):
+        a.o_bias = True               # the families that read this switch put the bias on all four projections
+    if mt == "smollm3" and cfg.get("no_rope_layers"):
+        a.no_rope_layers = [i for i, keep in enumerate(cfg["no_rope_layers"]) if not keep]      # the list marks the layers that DO rotate
+    if mt in ("ernie4_5", "helium"):
+        a.rotary_interleaved = True   # pairs (x[2i], x[2i+1]) rotate together
+        if mt == "ernie4_5":
+            a.attn_bias = a.o_bias = a.mlp_bias = bool(cfg.get("use_bias", False))
+    if mt in ("hunyuan_v1_dense", "hunyuandensev1", "hunyuan"):
+        a.model_type = "hunyuandensev1"
+        a.qk_norm = bool(cfg.get("use_qk_norm", True))
+        a.qk_norm_after_rope = a.qk_norm
+    if mt == "nemotron":
+        # layer norms whose stored weight is the offset from one, a two-matrix MLP with squared ReLU
+        a.layernorm = True
+        a.norm_offset = 1.0
+        a.norm_eps = cfg.get("norm_eps", a.norm_eps)
+        a.mlp_gated = False
+        a.activation = "relu2"
+    if mt == "olmo":
+        a.layernorm = True            # layer norm without parameters: exported with unit weights and zero biases
+        a.norm_eps = 1e-5
+    if mt == "chatglm":
+        a.model_type = "chatglm"
+        a.partial_rotary_factor = 0.5         # half of every head rotates, in interleaved pairs (reference: builders/chatglm.py:12-17)
+        a.rotary_interleaved = True
+        a.o_bias = a.mlp_bias = bool(cfg.get("add_bias_linear", False))
+        a.tie_embeddings = False
+    if mt == "internlm2":
+        a.attn_bias = a.o_bias = bool(cfg.get("bias", False))
     if mt == "qwen2":
         a.attn_bias = True
     if mt == "qwen2_moe":
         a.attn_bias = bool(cfg.get("qkv_bias", True))
-    if mt in ("qwen3", "gemma3_text", "olmo2"):
-        a.qk_norm = mt != "olmo2" or True
+    if mt == "olmo2":
+        raise NotImplementedError("olmo2 (norms after the sub-layers only) is not supported")
+    if mt in ("qwen3", "gemma3_text"):
+        a.qk_norm = True
+    if mt == "olmoe":
+        a.qk_norm = a.qk_norm_full_width = True
     if mt in ("mistral", "qwen2", "phi3") and cfg.get("sliding_window") and cfg.get("use_sliding_window", mt != "qwen2"):
         a.sliding_window = int(cfg["sliding_window"])
     if mt.startswith("gemma"):
@@ -289,8 +351,12 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
             sw = cfg.get("sliding_window") or 0
             if sw:
                 a.sliding_window = sw
-                pattern = cfg.get("sliding_window_pattern", 2 if mt == "gemma2" else 6)
-                a.sliding_layers = [i for i in range(a.num_layers) if (i + 1) % pattern != 0]
+                pattern = cfg.get("sliding_window_pattern", cfg.get("_sliding_window_pattern", 2 if mt == "gemma2" else 6))
+                lt = cfg.get("layer_types")
+                a.sliding_layers = ([i for i, t in enumerate(lt) if t == "sliding_attention"] if lt
+                                    else [i for i in range(a.num_layers) if (i + 1) % pattern != 0])
+            if mt == "gemma3_text":
+                a.rope_local_theta = float(cfg.get("rope_local_base_freq") or 10000.0)
     if mt in ("gpt_oss", "gptoss"):
         a.model_type = "gptoss"
         a.num_experts = cfg.get("num_local_experts", 32)
@@ -323,7 +389,7 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
             a.moe_sparse_mixer = True
             a.moe_jitter_eps = float(cfg.get("router_jitter_noise", 0.01))
             a.layernorm = True
-            a.attn_bias = a.o_bias = True
+            a.attn_bias = a.o_bias = bool(cfg.get("attention_bias", True))
             a.lm_head_bias = bool(cfg.get("lm_head_bias", True))
     if mt == "granitemoehybrid":
         # hybrid of Mamba-2 and attention layers; the feed-forward of the dense members is the "shared" gated MLP
@@ -381,21 +447,25 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.attn_bias = a.o_bias = a.mlp_bias = True
         a.mlp_gated = False
         a.learned_positions = True
-        a.tie_embeddings = True
+        a.tie_embeddings = bool(cfg.get("tie_word_embeddings", True))
         a.norm_eps = cfg.get("layer_norm_epsilon", 1e-5)
+        a.activation = {"gelu_new": "gelu", "gelu": "gelu_erf", "relu": "relu"}.get(cfg.get("activation_function", "gelu_new"), "gelu")
+    if mt == "phi":
+        a.activation = {"gelu_new": "gelu", "gelu": "gelu_erf", "relu": "relu"}.get(cfg.get("hidden_act", "gelu_new"), "gelu")
     return a
 
 
 # --------------------------------------------------------------------------------------------- RoPE caches
-def rope_caches(arch: ArchConfig, max_positions: Optional[int] = None):
+def rope_caches(arch: ArchConfig, max_positions: Optional[int] = None, local: bool = False):
     """cos/sin caches of shape [positions, rotary_dim/2] (fp32), with the frequency rescaling the
     reference's exporter applies (default, linear, llama3, yarn; src/python/py/models/builders/
     base.py:2478-2617, builders/llama.py:15-31)."""
     n = max_positions or arch.context_length
     rot = arch.rotary_dim
-    inv_freq = 1.0 / (arch.rope_theta ** (np.arange(0, rot, 2, dtype=np.float64) / rot))
+    theta = arch.rope_local_theta if local else arch.rope_theta
+    inv_freq = 1.0 / (theta ** (np.arange(0, rot, 2, dtype=np.float64) / rot))
     attn_factor = 1.0
-    sc = arch.rope_scaling or {}
+    sc = {} if local else (arch.rope_scaling or {})
     kind = sc.get("rope_type", sc.get("type", "default"))
     if kind in ("longrope", "su"):
         multi = longrope_caches(arch)

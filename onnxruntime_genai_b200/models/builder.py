@@ -107,8 +107,8 @@ def weight_shapes(arch: ArchConfig) -> Dict[str, tuple]:
                 s[p + f"cross_attn.{nm}_proj.weight"] = shp
                 s[p + f"cross_attn.{nm}_proj.bias"] = (shp[0],)
         if arch.qk_norm and not arch.is_conv_layer(i) and not arch.is_recurrent_layer(i):
-            s[p + "self_attn.q_norm.weight"] = (arch.head_dim,)
-            s[p + "self_attn.k_norm.weight"] = (arch.head_dim,)
+            s[p + "self_attn.q_norm.weight"] = (arch.q_size if arch.qk_norm_full_width else arch.head_dim,)
+            s[p + "self_attn.k_norm.weight"] = (arch.kv_size if arch.qk_norm_full_width else arch.head_dim,)
         if arch.attn_sinks:
             s[p + "self_attn.sinks"] = (arch.num_heads,)
         if arch.num_experts > 0 and arch.moe_style == "standard":
@@ -659,6 +659,11 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
     cos, sin = rope_caches(arch)
     W.add_float("cos_cache", torch.from_numpy(cos), force_fp32=(precision == "fp32"))
     W.add_float("sin_cache", torch.from_numpy(sin), force_fp32=(precision == "fp32"))
+    if arch.rope_local_theta:
+        # sliding-window layers rotate with their own base (reference: builders/gemma.py:144-158, cos_cache_local / sin_cache_local)
+        cos, sin = rope_caches(arch, local=True)
+        W.add_float("cos_cache_local", torch.from_numpy(cos), force_fp32=(precision == "fp32"))
+        W.add_float("sin_cache_local", torch.from_numpy(sin), force_fp32=(precision == "fp32"))
 
     if arch.residual_multiplier != 1.0:
         W.model.initializers["/model/constants/residual_multiplier"] = op.Tensor(
@@ -782,13 +787,15 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                 W.node("Add", f"{n}/attn/qkv_proj/Add", [qkv_out, p + "attn.qkv_proj.Add.bias"], [f"{n}/attn/qkv_proj/Add/output_0"])
                 qkv_out = f"{n}/attn/qkv_proj/Add/output_0"
             attn_inputs = [qkv_out, "", ""]
+            rope_mode = arch.layer_rope_mode(i)
+            cos_name, sin_name = ("cos_cache_local", "sin_cache_local") if rope_mode == 1 else ("cos_cache", "sin_cache")
             if paged:
                 attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "cumulative_sequence_lengths",
                                 "past_sequence_lengths", "block_table_windowed" if arch.layer_window(i) else "block_table",
-                                "cos_cache", "sin_cache", ""]
+                                cos_name, sin_name, ""]
             else:
                 attn_inputs += [f"past_key_values.{i}.key", f"past_key_values.{i}.value", "/model/attn_mask_reformat/seqlens_k",
-                                "/model/attn_mask_reformat/total_seq_len", "cos_cache", "sin_cache", "", ""]
+                                "/model/attn_mask_reformat/total_seq_len", cos_name, sin_name, "", ""]
             if arch.attn_sinks:
                 put_plain(p + "attn.sinks", [p + "self_attn.sinks"], {"shape": (arch.num_heads,), "op": "id", "fn": lambda ts: ts[0].float()})
                 attn_inputs.append(p + "attn.sinks")
@@ -801,9 +808,13 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                 attn_inputs += [p + "attn.q_norm.layernorm.weight", p + "attn.k_norm.layernorm.weight"]
             attrs = dict(num_heads=arch.num_heads, kv_num_heads=arch.num_kv_heads, scale=float(arch.scale),
                          local_window_size=int(arch.layer_window(i)) if arch.layer_window(i) else -1, softcap=float(arch.softcap),
-                         do_rotary=0 if (arch.learned_positions or arch.no_rope) else 1, rotary_interleaved=int(arch.rotary_interleaved))
+                         do_rotary=0 if rope_mode == 2 else 1, rotary_interleaved=int(arch.rotary_interleaved))
             if arch.qk_norm:
                 attrs["qk_norm_epsilon"] = float(arch.norm_eps)
+                if arch.qk_norm_after_rope:
+                    attrs["qk_norm_after_rotary"] = 1
+                if arch.qk_norm_full_width:
+                    attrs["qk_norm_full_width"] = 1
             if arch.mrope_section:
                 attrs["mrope_section"] = [int(v) for v in arch.mrope_section]   # position_ids then carry three components per token
             if arch.rotary_dim != arch.head_dim:
@@ -973,6 +984,9 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                 W.node("Gelu", f"{n}/mlp/act_fn/Gelu", [f1], [f"{n}/mlp/act_fn/output_0"], domain="com.microsoft")
             elif arch.activation == "relu":
                 W.node("Relu", f"{n}/mlp/act_fn/Relu", [f1], [f"{n}/mlp/act_fn/output_0"])
+            elif arch.activation == "relu2":
+                W.node("Relu", f"{n}/mlp/act_fn/Relu", [f1], [f"{n}/mlp/act_fn/Relu/output_0"])
+                W.node("Mul", f"{n}/mlp/act_fn/Square", [f"{n}/mlp/act_fn/Relu/output_0", f"{n}/mlp/act_fn/Relu/output_0"], [f"{n}/mlp/act_fn/output_0"])
             else:
                 W.node("FastGelu", f"{n}/mlp/act_fn/FastGelu", [f1], [f"{n}/mlp/act_fn/output_0"], domain="com.microsoft")
             mlp_out = f"{n}/mlp/fc2/MatMul/output_0"
@@ -1337,6 +1351,90 @@ def _canonical_moe_names(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
                 sd[p + f"mlp.shared_expert.{nm}.weight"] = sd.pop(p + f"mlp.{nm}.weight")
 
 
+def _canonical_family_names(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
+    """Families whose checkpoints name (or lay out) their tensors differently from the llama convention this exporter reads."""
+    mt = arch.model_type
+    def rename(pairs):
+        for k in list(sd):
+            for old, new in pairs:
+                if old in k:
+                    sd[k.replace(old, new)] = sd.pop(k)
+                    break
+    if mt == "gpt2":
+        # Conv1D modules keep [in, out] matrices; q, k, v share one of them
+        H = arch.hidden_size
+        for k in list(sd):
+            v = sd[k]
+            if k.endswith((".attn.bias", ".attn.masked_bias")):
+                sd.pop(k)
+                continue
+            nk = k.replace("transformer.h.", "model.layers.").replace("transformer.wte.", "model.embed_tokens.").replace(
+                "transformer.wpe.", "model.position_embeddings.").replace("transformer.ln_f.", "model.norm.").replace(
+                ".ln_1.", ".input_layernorm.").replace(".ln_2.", ".post_attention_layernorm.")
+            sd.pop(k)
+            if ".attn.c_attn." in nk:
+                parts = (v.t() if v.dim() == 2 else v).split(H, dim=0)
+                for nm, part in zip(("q_proj", "k_proj", "v_proj"), parts):
+                    sd[nk.replace(".attn.c_attn.", f".self_attn.{nm}.")] = part.contiguous()
+            elif ".attn.c_proj." in nk:
+                sd[nk.replace(".attn.c_proj.", ".self_attn.o_proj.")] = v.t().contiguous() if v.dim() == 2 else v
+            elif ".mlp.c_fc." in nk:
+                sd[nk.replace(".mlp.c_fc.", ".mlp.fc1.")] = v.t().contiguous() if v.dim() == 2 else v
+            elif ".mlp.c_proj." in nk:
+                sd[nk.replace(".mlp.c_proj.", ".mlp.fc2.")] = v.t().contiguous() if v.dim() == 2 else v
+            else:
+                sd[nk] = v
+        sd["model.position_embeddings.weight"] = sd["model.position_embeddings.weight"][: arch.context_length]
+    elif mt == "phi":
+        rename([(".self_attn.dense.", ".self_attn.o_proj."), ("model.final_layernorm.", "model.norm.")])
+    elif mt == "lfm2":
+        rename([(".operator_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."), (".feed_forward.w1.", ".mlp.gate_proj."),
+                (".feed_forward.w3.", ".mlp.up_proj."), (".feed_forward.w2.", ".mlp.down_proj."), (".self_attn.out_proj.", ".self_attn.o_proj."),
+                (".self_attn.q_layernorm.", ".self_attn.q_norm."), (".self_attn.k_layernorm.", ".self_attn.k_norm."),
+                ("model.embedding_norm.", "model.norm.")])
+        for k in [k for k in sd if k.endswith("conv.conv.weight") and sd[k].dim() == 3]:
+            sd[k] = sd[k].squeeze(1)
+    elif mt == "nemotron":
+        rename([(".mlp.up_proj.", ".mlp.fc1."), (".mlp.down_proj.", ".mlp.fc2.")])
+    elif mt == "hunyuandensev1":
+        rename([(".self_attn.query_layernorm.", ".self_attn.q_norm."), (".self_attn.key_layernorm.", ".self_attn.k_norm.")])
+    elif mt == "chatglm":
+        # transformer.encoder.layers.N.{self_attention.query_key_value, self_attention.dense, mlp.dense_h_to_4h [gate; up], mlp.dense_4h_to_h}
+        rename([("transformer.embedding.word_embeddings.", "model.embed_tokens."), ("transformer.encoder.final_layernorm.", "model.norm."),
+                ("transformer.output_layer.", "lm_head."), ("transformer.encoder.layers.", "model.layers.")])
+        rename([(".self_attention.dense.", ".self_attn.o_proj."), (".mlp.dense_4h_to_h.", ".mlp.down_proj.")])
+        for k in [k for k in sd if ".self_attention.query_key_value." in k]:
+            v = sd.pop(k)
+            for nm, part in zip(("q_proj", "k_proj", "v_proj"), torch.split(v, [arch.q_size, arch.kv_size, arch.kv_size], dim=0)):
+                sd[k.replace(".self_attention.query_key_value.", f".self_attn.{nm}.")] = part.contiguous()
+        for k in [k for k in sd if ".mlp.dense_h_to_4h." in k]:
+            v = sd.pop(k)
+            half = v.shape[0] // 2
+            sd[k.replace(".mlp.dense_h_to_4h.", ".mlp.gate_proj.")], sd[k.replace(".mlp.dense_h_to_4h.", ".mlp.up_proj.")] = v[:half].contiguous(), v[half:].contiguous()
+        for k in [k for k in sd if "rotary_pos_emb" in k]:
+            sd.pop(k)
+    elif mt == "internlm2":
+        # wqkv rows are grouped by key/value head: the group's query heads, then its key head, then its value head
+        # (reference: builders/internlm.py load_weights)
+        rename([("model.tok_embeddings.", "model.embed_tokens."), (".attention_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."),
+                (".feed_forward.w1.", ".mlp.gate_proj."), (".feed_forward.w3.", ".mlp.up_proj."), (".feed_forward.w2.", ".mlp.down_proj."),
+                (".attention.wo.", ".self_attn.o_proj.")])
+        if "output.weight" in sd:
+            sd["lm_head.weight"] = sd.pop("output.weight")
+        D, r = arch.head_dim, arch.num_heads // arch.num_kv_heads
+        for k in [k for k in sd if ".attention.wqkv." in k]:
+            v = sd.pop(k)
+            g = v.reshape(arch.num_kv_heads, r + 2, D, *v.shape[1:])
+            parts = (g[:, :r].reshape(arch.q_size, *v.shape[1:]), g[:, r].reshape(arch.kv_size, *v.shape[1:]), g[:, r + 1].reshape(arch.kv_size, *v.shape[1:]))
+            for nm, part in zip(("q_proj", "k_proj", "v_proj"), parts):
+                sd[k.replace(".attention.wqkv.", f".self_attn.{nm}.")] = part.contiguous()
+    elif mt == "olmo":
+        H = arch.hidden_size
+        for nm in [f"model.layers.{i}.{w}" for i in range(arch.num_layers) for w in ("input_layernorm", "post_attention_layernorm")] + ["model.norm"]:
+            sd.setdefault(nm + ".weight", torch.ones(H))
+            sd.setdefault(nm + ".bias", torch.zeros(H))
+
+
 def _split_gated_q(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> None:
     """q_proj of a gated-attention checkpoint holds [query | gate] per head: the gate halves become a projection of their own."""
     if not arch.attn_output_gate:
@@ -1379,6 +1477,7 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
             arch = from_hf_config(json.load(f))
         if not int(extra.get("random_weights", 0)) and not int(extra.get("synthetic_weights", 0)):
             state_dict = load_hf_state_dict(model_name_or_dir)
+            _canonical_family_names(state_dict, arch)
             _split_packed_qkv(state_dict, arch)
             _split_gated_q(state_dict, arch)
             _canonical_moe_names(state_dict, arch)

@@ -245,6 +245,8 @@ class DecoderModel:
         self.sin: Optional[torch.Tensor] = None
         # long-context RoPE (Phi-3 longrope): `cos` / `sin` are the long-factor caches; these serve steps whose KV bound
         # stays within the original context length
+        self.cos_local: Optional[torch.Tensor] = None    # sliding-window layers with a rotary base of their own (gemma3)
+        self.sin_local: Optional[torch.Tensor] = None
         self.cos_small: Optional[torch.Tensor] = None
         self.sin_small: Optional[torch.Tensor] = None
         self.rope_original_context = 0
@@ -273,6 +275,15 @@ class DecoderModel:
         if isinstance(h, ops.PendingCombine):
             return ops.norm_moe_combine(h, w, a.norm_eps, residual, b, a.layernorm)
         return ops.norm(h, w, a.norm_eps, residual, b, a.layernorm)
+
+    def _layer_rope(self, li: int, cos, sin, rot: int):
+        """The rotary caches and width of one layer: the model's, the local pair of sliding-window layers, or none."""
+        mode = self.arch.layer_rope_mode(li)
+        if mode == 2:
+            return cos, sin, 0
+        if mode == 1 and self.cos_local is not None:
+            return self.cos_local, self.sin_local, rot
+        return cos, sin, rot
 
     def _mlp(self, lw: LayerWeights, x, defer: bool = False):
         a = self.arch
@@ -421,7 +432,7 @@ class DecoderModel:
         lw = self.layers[0]
         return (self.norms_folded and self.fuse_steps and self.active_adapter is None and s.lora_ids is None and
                 s.input_ids.shape[0] <= ops.FUSED_MAX_TOKENS and
-                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and not a.has_linear_layers and not a.attn_output_gate and
+                (s.inputs_embeds is None or s.inputs_embeds.is_cuda) and a.residual_multiplier == 1.0 and not a.has_linear_layers and not a.attn_output_gate and not a.qk_norm_after_rope and not a.qk_norm_full_width and
                 lw.post_attn_norm_w is None and lw.post_ffn_norm_w is None and not s.cross_qk_heads)
 
     def _forward_fused(self, s: StepInputs, kv: PagedKVCache) -> torch.Tensor:
@@ -438,13 +449,14 @@ class DecoderModel:
             kc, vc, windowed = kv.layer(li)
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
+            lcos, lsin, lrot = self._layer_rope(li, cos, sin, rot)
             if (lw.q_norm_w is None and lw.k_norm_w is None and not a.rotary_interleaved and not a.mrope_section and
-                    ops.qkv_fusable(a.head_dim, rot if cos is not None else 0, kc)):
-                q = ops.qkv_rope_append(h, lw.qkv_w, lw.qkv_b, s.positions, slots, cos, sin, kc, vc, self.heads_local,
-                                        self.kv_heads_local, a.head_dim, rot, norm_eps=a.norm_eps)
+                    ops.qkv_fusable(a.head_dim, lrot if lcos is not None else 0, kc)):
+                q = ops.qkv_rope_append(h, lw.qkv_w, lw.qkv_b, s.positions, slots, lcos, lsin, kc, vc, self.heads_local,
+                                        self.kv_heads_local, a.head_dim, lrot, norm_eps=a.norm_eps)
             else:
                 q = ops.linear(h, lw.qkv_w, lw.qkv_b, norm_eps=a.norm_eps)
-                ops.rope_kv_append(q, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local, a.head_dim, rot,
+                ops.rope_kv_append(q, s.positions, slots, lcos, lsin, kc, vc, self.heads_local, self.kv_heads_local, a.head_dim, lrot,
                                    a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
                                    s.positions3 if a.mrope_section else None, a.mrope_section)
             att = self._attention(s, q, kc, vc, table, kv.block_size, lw)
@@ -485,7 +497,7 @@ class DecoderModel:
         reduce-scatter and the column-parallel ones start from a fused all-gather."""
         tp, a = self.tp, self.arch
         comm = getattr(tp, "comm", None)
-        if tp.size <= 1 or comm is None or s.inputs_embeds is not None or self.active_adapter is not None:
+        if tp.size <= 1 or comm is None or s.inputs_embeds is not None or self.active_adapter is not None or a.qk_norm_after_rope:
             return False
         T = s.input_ids.shape[0]
         lw = self.layers[0]
@@ -521,8 +533,9 @@ class DecoderModel:
             kc, vc, windowed = kv.layer(li)
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
-            ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
-                               a.head_dim, a.applied_rotary_dim, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+            lcos, lsin, lrot = self._layer_rope(li, cos, sin, a.applied_rotary_dim)
+            ops.rope_kv_append(qkv, s.positions, slots, lcos, lsin, kc, vc, self.heads_local, self.kv_heads_local,
+                               a.head_dim, lrot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
             att = ops.paged_attention(qkv, kc, vc, s.cu_seqlens, s.past_lens, table, kv.block_size, self.heads_local,
                                       self.kv_heads_local, a.head_dim, a.scale, lw.window, lw.sinks, a.softcap,
                                       max_q_len=s.max_q_len, max_kv_len=s.max_kv_len)
@@ -607,9 +620,21 @@ class DecoderModel:
             kc, vc, windowed = kv.layer(li)
             slots = s.slot_mapping_w if windowed else s.slot_mapping
             table = s.block_table_w if windowed else s.block_table
-            ops.rope_kv_append(qkv, s.positions, slots, cos, sin, kc, vc, self.heads_local, self.kv_heads_local,
-                               a.head_dim, rot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
-                               s.positions3 if a.mrope_section else None, a.mrope_section)
+            lcos, lsin, lrot = self._layer_rope(li, cos, sin, rot)
+            if a.qk_norm_full_width and lw.q_norm_w is not None:
+                from ..ops import reference as _ref
+                qkv = _ref.full_width_qk_norm(qkv, self.heads_local * a.head_dim, self.kv_heads_local * a.head_dim, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+                ops.rope_kv_append(qkv, s.positions, slots, lcos, lsin, kc, vc, self.heads_local, self.kv_heads_local, a.head_dim, lrot,
+                                   a.rotary_interleaved)
+            elif a.qk_norm_after_rope and lw.q_norm_w is not None:
+                from ..ops import reference as _ref
+                qkv = _ref.rope_then_head_norm(qkv, s.positions, lcos, lsin, self.heads_local, self.kv_heads_local, a.head_dim, lrot,
+                                               a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps)
+                ops.rope_kv_append(qkv, s.positions, slots, None, None, kc, vc, self.heads_local, self.kv_heads_local, a.head_dim, 0)
+            else:
+                ops.rope_kv_append(qkv, s.positions, slots, lcos, lsin, kc, vc, self.heads_local, self.kv_heads_local,
+                                   a.head_dim, lrot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
+                                   s.positions3 if a.mrope_section else None, a.mrope_section)
             att = self._attention(s, qkv, kc, vc, table, kv.block_size, lw)
             if lw.attn_gate_w is not None:
                 att = (att.float() * torch.sigmoid(self._linear(x, lw.attn_gate_w, None).float())).to(att.dtype)

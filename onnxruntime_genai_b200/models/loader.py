@@ -116,14 +116,23 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         if rd:
             a.partial_rotary_factor = rd / a.head_dim
         a.qk_norm = "qk_norm_epsilon" in attn.attrs
+        a.qk_norm_after_rope = bool(int(_attr(attn, "qk_norm_after_rotary", 0) or 0))
+        a.qk_norm_full_width = bool(int(_attr(attn, "qk_norm_full_width", 0) or 0))
         ms = _attr(attn, "mrope_section")
         a.mrope_section = [int(v) for v in ms] if ms else None
         a.attn_sinks = any(".sinks" in i for i in attn.inputs)
-    windows = []
+    windows, unrotated = [], []
     for i in range(L):
         n = g.find(f"/model/layers.{i}/attn/", ops=["GroupQueryAttention", "PagedAttention"])
         w = int(_attr(n, "local_window_size", -1) or -1)
         windows.append(w if w > 0 else 0)
+        if n is not None and int(_attr(n, "do_rotary", 1)) == 0:
+            unrotated.append(i)
+    attending = [i for i in range(L) if g.find(f"/model/layers.{i}/attn/", ops=["GroupQueryAttention", "PagedAttention"]) is not None]
+    if unrotated and len(unrotated) < len(attending):
+        a.no_rope_layers = unrotated
+    if g.has_init("cos_cache_local"):
+        a.rope_local_theta = 1.0       # the local caches are read from the model; only the switch matters here
     if any(windows):
         a.sliding_window = max(windows)
         a.sliding_layers = None if all(windows) else [i for i, w in enumerate(windows) if w > 0]
@@ -159,7 +168,7 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
     a.parallel_block = g.find("/model/layers.0/parallel_block/") is not None
     a.learned_positions = g.by_name.get("/model/pos_embed/Gather") is not None
     a.no_rope = (not a.learned_positions and attn is not None and attn.op_type in ("GroupQueryAttention", "PagedAttention")
-                 and int(_attr(attn, "do_rotary", 1)) == 0)
+                 and int(_attr(attn, "do_rotary", 1)) == 0 and a.no_rope_layers is None)
     fc1 = g.find("/model/layers.0/mlp/fc1/", ops=LINEAR_OPS)
     if fc1 is not None:
         a.mlp_gated = False
@@ -197,6 +206,8 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
             a.mlp_bias = g.find("/model/layers.0/mlp/down_proj/Add") is not None
         act = g.find("/model/layers.0/mlp/act_fn/", ops=["FastGelu", "Gelu", "BiasGelu", "Relu"])
         a.activation = "silu" if act is None else {"Gelu": "gelu_erf", "Relu": "relu"}.get(act.op_type, "gelu") if fc1 is not None else "gelu"
+        if a.activation == "relu" and g.by_name.get("/model/layers.0/mlp/act_fn/Square") is not None:
+            a.activation = "relu2"
     if g.by_name.get("/model/embed_tokens/Mul") is not None:
         a.embed_scale = float(g.tensor("/model/constants/embed_scale").float().item())
     if g.has_init("/model/constants/residual_multiplier"):
@@ -347,6 +358,9 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
         model.embed = emb.to(device=device, dtype=dtype).contiguous()
     cos, sin = g.tensor("cos_cache").float(), g.tensor("sin_cache").float()
     model.cos, model.sin = cos.to(device).contiguous(), sin.to(device).contiguous()
+    if g.has_init("cos_cache_local"):
+        model.cos_local = g.tensor("cos_cache_local").float().to(device).contiguous()
+        model.sin_local = g.tensor("sin_cache_local").float().to(device).contiguous()
     if arch.learned_positions:
         model.pos_embed = g.tensor("model.position_embeddings.weight", device=device).to(device=device, dtype=dtype).contiguous()
     if g.has_init("cos_cache_small") and g.has_init("cos_cache_large"):
@@ -474,6 +488,8 @@ def load_decoder(model_dir: str, cfg, device, dtype, tp=None, decoder: Optional[
                     s = g.tensor(inp).float()
                     lw.sinks = (s[tpr * hq_l:(tpr + 1) * hq_l] if tpn > 1 else s).to(device).contiguous()
                 elif "q_norm" in inp:
+                    if arch.qk_norm_full_width and tpn > 1:
+                        raise NotImplementedError("q / k norms over all heads are not sharded: run these models on one GPU")
                     lw.q_norm_w = _vec(g, inp, dtype, device)
                 elif "k_norm" in inp:
                     lw.k_norm_w = _vec(g, inp, dtype, device)

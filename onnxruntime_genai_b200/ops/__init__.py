@@ -18,7 +18,7 @@ from . import _lib
 from .fp4 import Fp4Experts
 from .w4 import QuantizedEmbedding, W4Weight, unpack_ort_q4
 
-_ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "gelu_erf": 3}
+_ACT = {"silu": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "gelu_erf": 3, "relu2": 4}
 
 
 def _ptr(t: Optional[torch.Tensor]):

@@ -82,11 +82,36 @@ def activation(x, act="gelu"):
         y = torch.nn.functional.silu(f)
     elif act == "relu":
         y = torch.relu(f)
+    elif act == "relu2":
+        y = torch.relu(f) ** 2
     elif act == "gelu_erf":
         y = torch.nn.functional.gelu(f)
     else:
         y = torch.nn.functional.gelu(f, approximate="tanh")
     return y.to(x.dtype)
+
+
+def full_width_qk_norm(qkv, q_size, kv_size, q_norm_w, k_norm_w, norm_eps):
+    """Families that normalise q and k over all their heads at once (olmoe): returns qkv with those two parts normalised."""
+    x = qkv.float().clone()
+    for a, b, w in ((0, q_size, q_norm_w), (q_size, q_size + kv_size, k_norm_w)):
+        t = x[:, a:b]
+        x[:, a:b] = t * torch.rsqrt((t * t).mean(-1, keepdim=True) + norm_eps) * w.float()
+    return x.to(qkv.dtype)
+
+
+def rope_then_head_norm(qkv, positions, cos_cache, sin_cache, Hq, Hkv, D, rot, interleaved, q_norm_w, k_norm_w, norm_eps):
+    """Families whose per-head q / k norms follow the rotary embedding (hunyuan): returns qkv with q and k rotated, then normalised; plain
+    tensor operations on the tensor's own device."""
+    T = qkv.shape[0]
+    x = qkv.float().view(T, Hq + 2 * Hkv, D).clone()
+    qk = x[:, :Hq + Hkv]
+    if rot > 0:
+        pos = positions.long().clamp(0, cos_cache.shape[0] - 1)
+        qk = _rotate(qk, cos_cache[pos].float(), sin_cache[pos].float(), rot, interleaved)
+    w = torch.cat([q_norm_w.float().expand(Hq, D), k_norm_w.float().expand(Hkv, D)], 0)
+    x[:, :Hq + Hkv] = qk * torch.rsqrt((qk * qk).mean(-1, keepdim=True) + norm_eps) * w
+    return x.view(T, -1).to(qkv.dtype)
 
 
 def _rotate(v, cos, sin, rot, interleaved):
