@@ -229,8 +229,11 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
     """Maps a Hugging Face `config.json` dictionary to an ArchConfig."""
     if isinstance(cfg.get("text_config"), dict) and "hidden_size" not in cfg:
         # a multimodal checkpoint's configuration: the decoder is described by its text part
+        tmt = cfg["text_config"].get("model_type", cfg.get("model_type"))
+        if tmt in ("qwen2_vl_text", "qwen2_5_vl_text"):
+            tmt = tmt[: -len("_text")]
         cfg = {**{k: v for k, v in cfg.items() if k not in ("text_config", "vision_config", "audio_config")}, **cfg["text_config"],
-               "architectures": cfg.get("architectures"), "model_type": cfg["text_config"].get("model_type", cfg.get("model_type"))}
+               "architectures": cfg.get("architectures"), "model_type": tmt}
     if isinstance(cfg.get("rope_parameters"), dict):
         # newer configurations keep the rotary settings in one dictionary
         rp = cfg["rope_parameters"]
@@ -242,7 +245,7 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
             rp = rp["full_attention"]
         cfg.setdefault("rope_theta", rp.get("rope_theta", 10000.0))
         cfg.setdefault("partial_rotary_factor", rp.get("partial_rotary_factor", 1.0))
-        if rp.get("rope_type", "default") not in ("default", None) and not cfg.get("rope_scaling"):
+        if (rp.get("rope_type", "default") not in ("default", None) or rp.get("mrope_section")) and not cfg.get("rope_scaling"):
             cfg["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
     if "ffn_hidden_size" in cfg and "multi_query_group_num" in cfg:
         # ChatGLM's own key names (reference reads the same fallbacks: builders/base.py:80-121)

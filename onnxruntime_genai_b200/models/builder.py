@@ -1489,6 +1489,33 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
             if os.path.exists(src):
                 os.makedirs(output_dir, exist_ok=True)
                 shutil.copy(src, os.path.join(output_dir, fn))
+    qwen_vision = None
+    if state_dict is not None and os.path.isdir(model_name_or_dir):
+        with open(os.path.join(model_name_or_dir, "config.json")) as f:
+            raw = json.load(f)
+        if isinstance(raw.get("vision_config"), dict) and arch.model_type in ("qwen2_vl", "qwen2_5_vl") and not int(extra.get("text_only", 0)):
+            # a Qwen2-VL / Qwen2.5-VL checkpoint: the vision tower is exported beside the decoder
+            from . import qwen_vl
+            vc = raw["vision_config"]
+            v25 = arch.model_type == "qwen2_5_vl"
+            vis = qwen_vl.QwenVisionConfig(
+                depth=int(vc["depth"]), embed_dim=int(vc["hidden_size"] if v25 else vc["embed_dim"]), hidden_size=arch.hidden_size,
+                num_heads=int(vc["num_heads"]), mlp_ratio=float(vc.get("mlp_ratio", 4.0)), in_channels=int(vc.get("in_channels", vc.get("in_chans", 3))),
+                patch_size=int(vc.get("patch_size", 14)), spatial_merge_size=int(vc.get("spatial_merge_size", 2)),
+                temporal_patch_size=int(vc.get("temporal_patch_size", 2)), variant="qwen2_5_vl" if v25 else "qwen2_vl",
+                intermediate_size=int(vc.get("intermediate_size", 0)) if v25 else 0, window_size=int(vc.get("window_size", 112)),
+                fullatt_blocks=",".join(str(int(b)) for b in vc.get("fullatt_block_indexes", [])) if v25 else "")
+            qwen_vision = (vis, qwen_vl.strip_prefix(state_dict), int(raw.get("image_token_id", 151655)))
+            state_dict = {k: v for k, v in state_dict.items() if not k.startswith(("model.visual.", "visual."))}
+    if qwen_vision is not None:
+        vis, vsd, image_token_id = qwen_vision
+        return export_qwen_vl(
+            arch, vis, output_dir, image_token_id, precision, execution_provider, decoder_state_dict=state_dict, vision_state_dict=vsd,
+            seed=int(extra.get("seed", 0)), paged=bool(int(extra.get("paged_attention", extra.get("use_paged_attention", 0)))),
+            block_size=int(extra.get("paged_block_size", 16)), max_batch_size=int(extra.get("max_batch_size", 64)),
+            int4_symmetric=bool(int(extra.get("int4_is_symmetric", 0))), filename=extra.get("filename", "model.onnx"),
+            context_length=int(extra["context_length"]) if "context_length" in extra else None, linear_format=str(extra.get("linear_format", "")),
+            int4_algo_config=str(extra.get("int4_algo_config", "default")))
     return export_model(
         arch, output_dir, precision, execution_provider, state_dict=state_dict, seed=int(extra.get("seed", 0)),
         paged=bool(int(extra.get("paged_attention", extra.get("use_paged_attention", 0)))),

@@ -188,3 +188,58 @@ def test_generator_with_an_image_follows_the_dense_reference(tmp_path):
     with pytest.raises(RuntimeError):
         g2.set_inputs({"pixel_values": pa.numpy(), "image_grid_thw": np.asarray([ga], dtype=np.int64),
                        "input_ids": np.asarray([[5] + [IMG] * 4 + [7]], dtype=np.int32)})
+
+
+def test_hf_checkpoint_directory_exports_decoder_and_tower(tmp_path):
+    """A Qwen2.5-VL checkpoint directory (config.json with text_config / vision_config, `model.language_model.*` and `model.visual.*`
+    tensors) through create_model: the decoder and the vision tower are exported together, and a prompt with an image gives the logits
+    of the family's own implementation (patch features spliced into the prompt, three-component rotary positions)."""
+    import json
+    from safetensors.torch import save_file
+    transformers = pytest.importorskip("transformers")
+    if not hasattr(transformers, "Qwen2_5_VLForConditionalGeneration"):
+        pytest.skip("transformers has no Qwen2_5_VLForConditionalGeneration")
+    import onnxruntime_genai_b200 as og
+    from onnxruntime_genai_b200.models.builder import create_model
+    IMG = 110
+    cfg = transformers.Qwen2_5_VLConfig(
+        text_config=dict(vocab_size=120, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=256, rope_parameters={"rope_type": "default", "mrope_section": [2, 3, 3], "rope_theta": 10000.0},
+                         tie_word_embeddings=False, bos_token_id=0, eos_token_id=119, pad_token_id=0),
+        vision_config=dict(depth=2, hidden_size=32, out_hidden_size=64, num_heads=2, intermediate_size=48, patch_size=14, spatial_merge_size=2,
+                           temporal_patch_size=2, window_size=56, fullatt_block_indexes=[1], in_channels=3, tokens_per_second=1),
+        image_token_id=IMG, video_token_id=111, vision_start_token_id=108, vision_end_token_id=109, tie_word_embeddings=False)
+    # (tokens_per_second = 1: a still image's temporal position is the position where the image starts, as in the family's published
+    # position rule and the reference's src/models/position_inputs.cpp; some transformers versions scale that start by the rate)
+    torch.manual_seed(0)
+    m = transformers.Qwen2_5_VLForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(1 + 0.1 * torch.randn_like(p) if ("norm" in n and n.endswith("weight")) else torch.randn_like(p) * 0.1)
+    src = tmp_path / "hf"
+    src.mkdir()
+    save_file({k: v.detach().clone().contiguous() for k, v in m.state_dict().items()}, str(src / "model.safetensors"))
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen2_5_VLForConditionalGeneration"]
+    (src / "config.json").write_text(json.dumps(d))
+    out = str(tmp_path / "out")
+    create_model(str(src), out, "fp32", "cpu")
+    model = og.Model(out)
+    assert model.type == "qwen2_5_vl" and model.vision is not None and model.image_token_id == IMG and model.arch.mrope_section == [2, 3, 3]
+
+    vis = model.vision.cfg
+    rng = np.random.RandomState(4)
+    patches, grid = qwen_vl.preprocess_image(rng.randint(0, 256, size=(56, 84, 3), dtype=np.uint8), vis)
+    assert grid == (1, 4, 6)
+    ids = [5, 108] + [IMG] * 6 + [109, 7, 8, 9]
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=32)
+    g = og.Generator(model, p)
+    g.set_inputs({"pixel_values": patches.numpy(), "image_grid_thw": np.asarray([grid], dtype=np.int64), "input_ids": np.asarray([ids], dtype=np.int32)})
+    with torch.no_grad():
+        kw = dict(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([grid]))
+        try:
+            want = m(**kw, mm_token_type_ids=torch.tensor([[1 if t == IMG else 0 for t in ids]])).logits[0, -1].float().numpy()
+        except TypeError:
+            want = m(**kw).logits[0, -1].float().numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=5e-4)
