@@ -289,6 +289,10 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         pad_token_id=cfg.get("pad_token_id") if cfg.get("pad_token_id") is not None else 0,
     )
     mt = cfg.get("model_type", mtype)
+    act = cfg.get("hidden_activation") or cfg.get("hidden_act")
+    if act:
+        a.activation = {"silu": "silu", "swish": "silu", "gelu": "gelu_erf", "gelu_new": "gelu", "gelu_fast": "gelu", "gelu_pytorch_tanh": "gelu",
+                        "relu": "relu", "relu2": "relu2"}.get(act, a.activation)
     if a.model_type not in LLM_TYPES and mt in LLM_TYPES:
         a.model_type = mt      # class names that do not spell the family the way its configuration does (Qwen2Moe..., GraniteMoeHybrid...)
     if mt == "gpt2":
@@ -316,7 +320,7 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.norm_offset = 1.0
         a.norm_eps = cfg.get("norm_eps", a.norm_eps)
         a.mlp_gated = False
-        a.activation = "relu2"
+        a.activation = {"relu2": "relu2", "relu": "relu", "gelu": "gelu_erf", "gelu_new": "gelu", "gelu_pytorch_tanh": "gelu"}.get(cfg.get("hidden_act", "relu2"), "relu2")
     if mt == "olmo":
         a.layernorm = True            # layer norm without parameters: exported with unit weights and zero biases
         a.norm_eps = 1e-5

@@ -47,7 +47,7 @@ FAMILIES = {
 }
 
 
-def _randomise(m):
+def _randomise(m, std=0.08):
     with torch.no_grad():
         for n, p in m.named_parameters():
             if "norm" in n.lower() or n.endswith((".ln_1.weight", ".ln_2.weight", "ln_f.weight")):
@@ -56,7 +56,7 @@ def _randomise(m):
             elif n.endswith("mlp.gate.weight") or "router" in n:
                 p.copy_(torch.randn_like(p) * 0.5)
             else:
-                p.copy_(torch.randn_like(p) * 0.08)
+                p.copy_(torch.randn_like(p) * std)
     return m.float().eval()
 
 
@@ -97,6 +97,8 @@ def test_checkpoint_matches_the_family_implementation(family, tmp_path):
         np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=3e-4)
         g.generate_next_token()
         seq.append(int(g.get_next_tokens()[0]))
+        if g.is_done():      # the end-of-sequence token: no further logits
+            break
 
 
 def _generate_and_compare(tmp_path, cfg_dict, sd, m):
@@ -120,6 +122,8 @@ def _generate_and_compare(tmp_path, cfg_dict, sd, m):
         np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=3e-4)
         g.generate_next_token()
         seq.append(int(g.get_next_tokens()[0]))
+        if g.is_done():      # the end-of-sequence token: no further logits
+            break
     return model
 
 
@@ -178,3 +182,56 @@ def test_chatglm_layout(tmp_path):
              add_qkv_bias=True, add_bias_linear=False, rope_ratio=1.0, rmsnorm=True, eos_token_id=VOCAB - 1, pad_token_id=0)
     model = _generate_and_compare(tmp_path, d, sd, m)
     assert model.type == "chatglm" and model.arch.rotary_interleaved and model.arch.rotary_dim == 8
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("family", ["gemma3_text", "smollm3", "nemotron", "hunyuan_v1_dense", "olmoe", "ernie4_5", "lfm2", "gpt2"])
+def test_checkpoint_on_the_gpu(family, tmp_path):
+    """The same checkpoints in bf16 on the CUDA path (per-layer rotary caches in the fused decode step, the squared-ReLU kernel, the
+    q / k norm variants), against the fp32 logits of the family's implementation."""
+    from safetensors.torch import save_file
+    cfg_cls, model_cls, extra = FAMILIES[family]
+    if not hasattr(transformers, cfg_cls) or not hasattr(transformers, model_cls):
+        pytest.skip(f"transformers has no {model_cls}")
+    torch.manual_seed(0)
+    kw = {**COMMON, **extra, "hidden_size": 256, "intermediate_size": 384}      # 4 heads of 64: the head size the attention kernels take
+    for key, val in (("head_dim", 64), ("n_embd", 256), ("block_ff_dim", 384)):
+        if key in kw:
+            kw[key] = val
+    if family == "olmoe":
+        kw["intermediate_size"] = 64
+    cfg = getattr(transformers, cfg_cls)(**kw)
+    if hasattr(cfg, "_attn_implementation"):
+        cfg._attn_implementation = "eager"
+    m = _randomise(getattr(transformers, model_cls)(cfg), std=0.04)     # four times the width of the CPU cases: keep the attention scores in the same range
+    sd = {k: v.detach().clone().contiguous() for k, v in m.state_dict().items()
+          if not (getattr(cfg, "tie_word_embeddings", False) and k == "lm_head.weight")}
+    src = tmp_path / "hf"
+    os.makedirs(src)
+    save_file(sd, str(src / "model.safetensors"))
+    d = cfg.to_dict()
+    d["architectures"] = [model_cls]
+    (src / "config.json").write_text(json.dumps(d))
+    import copy
+    m16 = copy.deepcopy(m).to(torch.bfloat16)
+    out = str(tmp_path / "out")
+    create_model(str(src), out, "bf16", "cuda")
+    model = og.Model(out)
+    ids = np.random.RandomState(0).randint(1, VOCAB - 1, size=(1, 14)).astype(np.int32)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=32)
+    g = og.Generator(model, p)
+    g.append_tokens(ids)
+    seq = ids[0].tolist()
+    for _ in range(4):
+        with torch.no_grad():
+            want = m(torch.tensor([seq])).logits[0, -1].float().numpy()
+        got = np.asarray(g.get_logits(), dtype=np.float32).reshape(-1)
+        # the yardstick for bf16 rounding: the family's own implementation run in bf16 against itself in fp32
+        with torch.no_grad():
+            own = np.abs(m16(torch.tensor([seq])).logits[0, -1].float().numpy() - want).max()
+        assert np.abs(got - want).max() < max(0.04 * max(1.0, np.abs(want).max()), 2.5 * own), (family, np.abs(got - want).max(), own)
+        g.generate_next_token()
+        seq.append(int(g.get_next_tokens()[0]))
+        if g.is_done():      # the end-of-sequence token: no further logits
+            break

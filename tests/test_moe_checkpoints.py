@@ -120,3 +120,5 @@ def test_moe_checkpoint_matches_the_family_implementation(family, tmp_path):
         np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=3e-4)
         g.generate_next_token()
         seq.append(int(g.get_next_tokens()[0]))
+        if g.is_done():      # the end-of-sequence token: no further logits
+            break

@@ -69,6 +69,8 @@ def _check(model, m, seed):
         np.testing.assert_allclose(g.get_logits().reshape(-1), _hf_logits(m, seq)[-1].numpy(), rtol=3e-3, atol=3e-4)
         g.generate_next_token()
         seq.append(int(g.get_next_tokens()[0]))
+        if g.is_done():      # the end-of-sequence token: no further logits
+            break
 
 
 def test_text_checkpoint_matches_the_family_implementation(tmp_path):
