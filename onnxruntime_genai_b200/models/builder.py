@@ -1219,6 +1219,46 @@ def export_whisper(arch: ArchConfig, enc, out_dir: str, precision: str = "bf16",
     return out_dir
 
 
+def whisper_from_hf(cfg: dict, sd: Dict[str, torch.Tensor]):
+    """A Hugging Face Whisper checkpoint (`WhisperForConditionalGeneration`) as this exporter's inputs: the decoder's family flags
+    and the encoder's configuration, and both state dictionaries under the names `export_whisper` reads (reference:
+    src/python/py/models/builders/whisper.py).  The key projections of Whisper carry no bias: zero biases are written."""
+    from .encoder import EncoderConfig
+    D = int(cfg["d_model"])
+    arch = whisper_decoder_arch(int(cfg["vocab_size"]), D, int(cfg["decoder_layers"]), int(cfg["decoder_attention_heads"]), int(cfg["decoder_ffn_dim"]),
+                                encoder_hidden_size=D, context_length=int(cfg.get("max_target_positions", 448)),
+                                bos_token_id=int(cfg.get("decoder_start_token_id") or cfg.get("bos_token_id") or 0),
+                                eos_token_id=cfg.get("eos_token_id") if cfg.get("eos_token_id") is not None else 0,
+                                pad_token_id=int(cfg.get("pad_token_id") if cfg.get("pad_token_id") is not None else 0))
+    act = {"gelu": "gelu_erf", "gelu_new": "gelu", "relu": "relu"}.get(cfg.get("activation_function", "gelu"), "gelu_erf")
+    arch.activation = act
+    enc = EncoderConfig(kind="audio", hidden_size=D, num_layers=int(cfg["encoder_layers"]), num_heads=int(cfg["encoder_attention_heads"]),
+                        intermediate_size=int(cfg["encoder_ffn_dim"]), num_mel_bins=int(cfg.get("num_mel_bins", 80)),
+                        max_source_positions=int(cfg.get("max_source_positions", 1500)), activation=act)
+    dec_sd, enc_sd = {}, {}
+    renames = ((".self_attn_layer_norm.", ".input_layernorm."), (".encoder_attn_layer_norm.", ".cross_attn_layernorm."),
+               (".final_layer_norm.", ".post_attention_layernorm."), (".self_attn.out_proj.", ".self_attn.o_proj."),
+               (".encoder_attn.out_proj.", ".cross_attn.o_proj."), (".encoder_attn.", ".cross_attn."), (".fc1.", ".mlp.fc1."), (".fc2.", ".mlp.fc2."))
+    for k, v in sd.items():
+        if k.startswith("model.encoder."):
+            enc_sd[k[len("model."):]] = v
+        elif k.startswith("model.decoder."):
+            k2 = "model." + k[len("model.decoder."):]
+            k2 = k2.replace("model.embed_positions.", "model.position_embeddings.").replace("model.layer_norm.", "model.norm.")
+            for old, new in renames:
+                if old in k2:
+                    k2 = k2.replace(old, new)
+                    break
+            dec_sd[k2] = v
+    for i in range(enc.num_layers):
+        enc_sd.setdefault(f"encoder.layers.{i}.self_attn.k_proj.bias", torch.zeros(D))
+    for i in range(arch.num_layers):
+        dec_sd.setdefault(f"model.layers.{i}.self_attn.k_proj.bias", torch.zeros(D))
+        dec_sd.setdefault(f"model.layers.{i}.cross_attn.k_proj.bias", torch.zeros(D))
+    dec_sd["model.position_embeddings.weight"] = dec_sd["model.position_embeddings.weight"][: arch.context_length]
+    return arch, enc, dec_sd, enc_sd
+
+
 def export_vision_language(arch: ArchConfig, vis, out_dir: str, image_token_id: int, precision: str = "bf16",
                            execution_provider: str = "cuda", decoder_state_dict=None, vision_state_dict=None, seed: int = 0,
                            std: float = 0.02, model_type: str = "phi3v", image_token: str = "<|image|>", **export_kw) -> str:
@@ -1474,7 +1514,18 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
         arch = from_hf_config(cfg)
     else:
         with open(os.path.join(model_name_or_dir, "config.json")) as f:
-            arch = from_hf_config(json.load(f))
+            raw_cfg = json.load(f)
+        if (raw_cfg.get("architectures") or [""])[0] == "WhisperForConditionalGeneration" or raw_cfg.get("model_type") == "whisper":
+            # encoder-decoder speech checkpoint: decoder.onnx + encoder.onnx + the log-mel front end's configuration
+            arch, enc, dsd, esd = whisper_from_hf(raw_cfg, load_hf_state_dict(model_name_or_dir))
+            for fn in ("tokenizer.json", "tokenizer_config.json", "special_tokens_map.json", "generation_config.json", "preprocessor_config.json",
+                       "vocab.json", "merges.txt", "added_tokens.json", "normalizer.json"):
+                if os.path.exists(os.path.join(model_name_or_dir, fn)):
+                    os.makedirs(output_dir, exist_ok=True)
+                    shutil.copy(os.path.join(model_name_or_dir, fn), os.path.join(output_dir, fn))
+            return export_whisper(arch, enc, output_dir, precision, execution_provider, decoder_state_dict=dsd, encoder_state_dict=esd,
+                                  num_frames=2 * enc.max_source_positions)
+        arch = from_hf_config(raw_cfg)
         if not int(extra.get("random_weights", 0)) and not int(extra.get("synthetic_weights", 0)):
             state_dict = load_hf_state_dict(model_name_or_dir)
             _canonical_family_names(state_dict, arch)

@@ -226,3 +226,48 @@ def test_whisper_alignment_heads_record_cross_attention_scores(tmp_path):
     g3 = og.Generator(model, p)
     with pytest.raises(RuntimeError, match="alignment_heads"):
         g3.get_output("cross_qk")
+
+
+def test_hf_whisper_checkpoint_directory(tmp_path):
+    """A `WhisperForConditionalGeneration` directory through create_model: encoder.onnx + decoder.onnx, and the decoder's logits over
+    log-mel features against the family's implementation in `transformers` (reference: src/python/py/models/builders/whisper.py)."""
+    import json
+    transformers = pytest.importorskip("transformers")
+    from safetensors.torch import save_file
+    from onnxruntime_genai_b200.models.builder import create_model
+    cfg = transformers.WhisperConfig(vocab_size=120, d_model=64, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4, decoder_attention_heads=4,
+                                     encoder_ffn_dim=128, decoder_ffn_dim=96, num_mel_bins=16, max_source_positions=50, max_target_positions=40,
+                                     decoder_start_token_id=3, bos_token_id=1, eos_token_id=2, pad_token_id=2, suppress_tokens=None, begin_suppress_tokens=None)
+    torch.manual_seed(0)
+    m = transformers.WhisperForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "embed_positions" in n and "encoder" in n:
+                continue                       # the fixed sinusoid table
+            p.copy_(1 + 0.1 * torch.randn_like(p) if ("layer_norm" in n and n.endswith("weight")) else torch.randn_like(p) * 0.1)
+    src = tmp_path / "hf"
+    src.mkdir()
+    sd = {k: v.detach().clone().contiguous() for k, v in m.state_dict().items() if k != "proj_out.weight"}
+    save_file(sd, str(src / "model.safetensors"))
+    d = cfg.to_dict()
+    d["architectures"] = ["WhisperForConditionalGeneration"]
+    (src / "config.json").write_text(json.dumps(d))
+    out = str(tmp_path / "out")
+    create_model(str(src), out, "fp32", "cpu")
+    model = og.Model(out)
+    assert model.type == "whisper" and model.arch.num_layers == 2 and model.arch.intermediate_size == 96
+    feats = np.random.RandomState(0).randn(1, 16, 100).astype(np.float32)
+    ids = [3, 7, 9, 11]
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=20, batch_size=1)
+    g = og.Generator(model, p)
+    g.set_inputs(og.NamedTensors(audio_features=feats, input_ids=np.array([ids], dtype=np.int32)))
+    seq = list(ids)
+    for _ in range(4):
+        with torch.no_grad():
+            want = m(input_features=torch.from_numpy(feats), decoder_input_ids=torch.tensor([seq])).logits[0, -1].numpy()
+        np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=4e-4)
+        g.generate_next_token()
+        seq.append(int(g.get_next_tokens()[0]))
+        if g.is_done():
+            break
