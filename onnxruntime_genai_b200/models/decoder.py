@@ -245,6 +245,7 @@ class DecoderModel:
         self.sin: Optional[torch.Tensor] = None
         # long-context RoPE (Phi-3 longrope): `cos` / `sin` are the long-factor caches; these serve steps whose KV bound
         # stays within the original context length
+        self._rope_modes: Optional[List[int]] = None     # per layer: 0 the model's rotary caches, 1 the local pair, 2 none
         self.cos_local: Optional[torch.Tensor] = None    # sliding-window layers with a rotary base of their own (gemma3)
         self.sin_local: Optional[torch.Tensor] = None
         self.cos_small: Optional[torch.Tensor] = None
@@ -278,7 +279,10 @@ class DecoderModel:
 
     def _layer_rope(self, li: int, cos, sin, rot: int):
         """The rotary caches and width of one layer: the model's, the local pair of sliding-window layers, or none."""
-        mode = self.arch.layer_rope_mode(li)
+        modes = self._rope_modes
+        if modes is None or len(modes) != len(self.layers):
+            modes = self._rope_modes = [self.arch.layer_rope_mode(i) for i in range(len(self.layers))]
+        mode = modes[li]
         if mode == 2:
             return cos, sin, 0
         if mode == 1 and self.cos_local is not None:

@@ -235,3 +235,31 @@ def test_checkpoint_on_the_gpu(family, tmp_path):
         seq.append(int(g.get_next_tokens()[0]))
         if g.is_done():      # the end-of-sequence token: no further logits
             break
+
+
+@pytest.mark.parametrize("wrapper", ["gemma3", "mistral3", "llava"])
+def test_text_decoder_of_a_multimodal_wrapper(wrapper, tmp_path):
+    """`...ForConditionalGeneration` checkpoints: the decoder's settings sit under `text_config`, its weights under `model.language_model.`;
+    create_model exports the text decoder (as the reference's builder does for these architectures) and text prompts match the wrapper."""
+    text = dict(vocab_size=VOCAB, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=3, intermediate_size=96,
+                max_position_embeddings=128, head_dim=16)
+    vision = dict(hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2, image_size=28, patch_size=14)
+    if wrapper == "gemma3":
+        cfg = transformers.Gemma3Config(text_config=dict(**text, sliding_window=6, query_pre_attn_scalar=24), vision_config=vision, mm_tokens_per_image=1,
+                                        image_token_index=VOCAB - 1)
+        cls, kind = transformers.Gemma3ForConditionalGeneration, "gemma3_text"
+    elif wrapper == "mistral3":
+        cfg = transformers.Mistral3Config(text_config=dict(**text, model_type="mistral", sliding_window=None), vision_config=dict(**vision, head_dim=16),
+                                          image_token_index=VOCAB - 1)
+        cls, kind = transformers.Mistral3ForConditionalGeneration, "mistral"
+    else:
+        cfg = transformers.LlavaConfig(text_config=dict(**text, model_type="llama"), vision_config=dict(**vision, model_type="clip_vision_model"),
+                                       image_token_index=VOCAB - 1)
+        cls, kind = transformers.LlavaForConditionalGeneration, "llama"
+    torch.manual_seed(0)
+    m = _randomise(cls(cfg))
+    sd = {k: v for k, v in m.state_dict().items() if not (k == "lm_head.weight" and getattr(cfg.get_text_config(), "tie_word_embeddings", False))}
+    d = cfg.to_dict()
+    d["architectures"] = [cls.__name__]
+    model = _generate_and_compare(tmp_path, d, sd, m)
+    assert model.type == kind
