@@ -180,12 +180,20 @@ struct RopeParams {
   int kv8;   // 8-bit cache: rows of D int8 values + fp32 scale (absmax / 127 of the row) + 12 bytes of padding
   // Multimodal RoPE (Qwen2-VL): three position components per token ([3, T]: temporal, height, width); rotary pair i takes
   // component 0 below sec0, component 1 below sec1, component 2 above.  Null: the single `positions` array.
+  // Interleaved layout (Qwen3-VL), passed as sec0 < 0: pair i takes the height component when i % 3 == 1 and i < -sec0, the width
+  // component when i % 3 == 2 and i < sec1, the temporal component otherwise (-sec0 = 3 * height pairs, sec1 = 3 * width pairs).
   const int32_t* positions3;
   int sec0, sec1;
 };
 
+__device__ __forceinline__ int rope_component(const RopeParams& p, int i) {
+  if (p.sec0 >= 0) return i < p.sec0 ? 0 : (i < p.sec1 ? 1 : 2);
+  const int m = i % 3;
+  return (m == 1 && i < -p.sec0) ? 1 : ((m == 2 && i < p.sec1) ? 2 : 0);
+}
+
 __device__ __forceinline__ int rope_pos(const RopeParams& p, int t, int i) {
-  int pos = p.positions3 ? p.positions3[size_t(i < p.sec0 ? 0 : (i < p.sec1 ? 1 : 2)) * p.T + t] : p.positions[t];
+  int pos = p.positions3 ? p.positions3[size_t(rope_component(p, i)) * p.T + t] : p.positions[t];
   return pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
 }
 

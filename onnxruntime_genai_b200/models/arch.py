@@ -16,7 +16,7 @@ import numpy as np
 LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan", "hunyuandensev1", "hunyuan_v1_dense",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "phi", "phi3", "phimoe", "qwen2", "qwen3",
-    "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl",
+    "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl", "qwen3_vl",
     "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoehybrid", "granitemoeshared",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
 
@@ -83,6 +83,7 @@ class ArchConfig:
     mamba_conv_kernel: int = 4
     # Multimodal RoPE (Qwen2-VL): rotary pairs per position component (temporal, height, width); None: ordinary RoPE
     mrope_section: Optional[List[int]] = None
+    mrope_interleaved: bool = False  # qwen3_vl: the three position components alternate over the rotary pairs
     cross_attention: bool = False    # encoder-decoder (whisper): every layer also attends to the encoder's output
     encoder_hidden_size: int = 0     # width of the encoder output the cross-attention keys / values are projected from (0 = hidden_size)
     mlp_gated: bool = True           # False: fc1 -> activation -> fc2 (phi, gpt2) instead of act(gate) * up -> down
@@ -425,8 +426,13 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.parallel_block = True
     if mt in ("qwen2_vl", "qwen2_5_vl") or (cfg.get("rope_scaling") or {}).get("mrope_section"):
         a.mrope_section = list((cfg.get("rope_scaling") or {}).get("mrope_section") or [16, 24, 24])
+        a.mrope_interleaved = bool((cfg.get("rope_scaling") or {}).get("mrope_interleaved", False))
         a.rope_scaling = None
-        a.attn_bias = True
+        a.attn_bias = mt not in ("qwen3_vl", "qwen3_vl_text")
+    if mt in ("qwen3_vl", "qwen3_vl_text"):
+        # the text decoder of Qwen3-VL: qwen3 with three-component rotary positions in the interleaved layout
+        a.model_type = "qwen3_vl"
+        a.qk_norm = True
     if mt in ("qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text"):
         # zero-centred RMS norms (weights stored as offsets from one), per-head q / k norms, attention output gated by the second half of q_proj
         a.qk_norm = True

@@ -817,6 +817,8 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
                     attrs["qk_norm_full_width"] = 1
             if arch.mrope_section:
                 attrs["mrope_section"] = [int(v) for v in arch.mrope_section]   # position_ids then carry three components per token
+                if arch.mrope_interleaved:
+                    attrs["mrope_interleaved"] = 1
             if arch.rotary_dim != arch.head_dim:
                 attrs["rotary_embedding_dim"] = int(arch.rotary_dim)
             W.node(attn_op, f"{n}/attn/{attn_op}", attn_inputs, [f"{n}/attn/{attn_op}/output_0", f"present.{i}.key", f"present.{i}.value"],

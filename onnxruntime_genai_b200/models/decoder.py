@@ -462,7 +462,7 @@ class DecoderModel:
                 q = ops.linear(h, lw.qkv_w, lw.qkv_b, norm_eps=a.norm_eps)
                 ops.rope_kv_append(q, s.positions, slots, lcos, lsin, kc, vc, self.heads_local, self.kv_heads_local, a.head_dim, lrot,
                                    a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
-                                   s.positions3 if a.mrope_section else None, a.mrope_section)
+                                   s.positions3 if a.mrope_section else None, a.mrope_section, a.mrope_interleaved)
             att = self._attention(s, q, kc, vc, table, kv.block_size, lw)
             h = self._row_parallel_residual(att, lw.o_w, lw.o_b, h)
             act = ops.gate_up_act(h, lw.gate_up_w, lw.gate_up_b, a.activation, interleaved=lw.gate_up_interleaved, norm_eps=a.norm_eps)
@@ -638,7 +638,7 @@ class DecoderModel:
             else:
                 ops.rope_kv_append(qkv, s.positions, slots, lcos, lsin, kc, vc, self.heads_local, self.kv_heads_local,
                                    a.head_dim, lrot, a.rotary_interleaved, lw.q_norm_w, lw.k_norm_w, a.norm_eps,
-                                   s.positions3 if a.mrope_section else None, a.mrope_section)
+                                   s.positions3 if a.mrope_section else None, a.mrope_section, a.mrope_interleaved)
             att = self._attention(s, qkv, kc, vc, table, kv.block_size, lw)
             if lw.attn_gate_w is not None:
                 att = (att.float() * torch.sigmoid(self._linear(x, lw.attn_gate_w, None).float())).to(att.dtype)

@@ -120,6 +120,7 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
         a.qk_norm_full_width = bool(int(_attr(attn, "qk_norm_full_width", 0) or 0))
         ms = _attr(attn, "mrope_section")
         a.mrope_section = [int(v) for v in ms] if ms else None
+        a.mrope_interleaved = bool(int(_attr(attn, "mrope_interleaved", 0) or 0))
         a.attn_sinks = any(".sinks" in i for i in attn.inputs)
     windows, unrotated = [], []
     for i in range(L):

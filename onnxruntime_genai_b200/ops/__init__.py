@@ -560,15 +560,16 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, residual=None) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------ RoPE + KV append
 def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
-                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None):
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None, mrope_interleaved=False):
     """positions3 [3, T] int32 + mrope_section (rotary pairs per component: temporal, height, width): multimodal RoPE, the
-    pairs of each section rotate by their own position component."""
+    pairs of each section rotate by their own position component.  mrope_interleaved: the components alternate pair by pair
+    (t h w t h w ... while a component has pairs left) instead of occupying three contiguous ranges."""
     _check_index("rope_kv_append", "slots", None if slots is None else slots[:qkv.shape[0]], k_cache.shape[0] if k_cache is not None else 0, -1)
     if cos_cache is not None:
         _check_index("rope_kv_append", "positions", positions[:qkv.shape[0]] if positions3 is None else positions3, cos_cache.shape[0])
     if not qkv.is_cuda:
         return ref.rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved,
-                                  q_norm_w, k_norm_w, norm_eps, positions3, mrope_section)
+                                  q_norm_w, k_norm_w, norm_eps, positions3, mrope_section, mrope_interleaved)
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
     assert cos_cache is None or cos_cache.dtype == torch.float32
     T = qkv.shape[0]
@@ -578,8 +579,9 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
                                             _ptr(k_cache), _ptr(v_cache), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), T, Hq, Hkv,
                                             D, int(rot if cos_cache is not None else 0), int(interleaved), max_pos, kv_bits,
                                             _ptr(positions3.contiguous()) if positions3 is not None else None,
-                                            int(mrope_section[0]) if positions3 is not None else 0,
-                                            int(mrope_section[0] + mrope_section[1]) if positions3 is not None else 0, _stream())
+                                            (0 if positions3 is None else -3 * int(mrope_section[1]) if mrope_interleaved else int(mrope_section[0])),
+                                            (0 if positions3 is None else 3 * int(mrope_section[2]) if mrope_interleaved
+                                             else int(mrope_section[0] + mrope_section[1])), _stream())
     _lib.check(rc, "rope_kv_append")
     return qkv
 

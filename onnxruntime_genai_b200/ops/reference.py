@@ -131,7 +131,7 @@ def _rotate(v, cos, sin, rot, interleaved):
 
 
 def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache, Hq, Hkv, D, rot, interleaved=False,
-                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None):
+                   q_norm_w=None, k_norm_w=None, norm_eps=1e-6, positions3=None, mrope_section=None, mrope_interleaved=False):
     """In place: rotates q inside `qkv`, writes rotated k and v into the caches at `slots`."""
     T = qkv.shape[0]
     dt = qkv.dtype
@@ -153,6 +153,9 @@ def rope_kv_append(qkv, positions, slots, cos_cache, sin_cache, k_cache, v_cache
             # multimodal RoPE: rotary pair i takes the angle of its section's position component
             p3 = positions3.long().clamp(0, cos_cache.shape[0] - 1)
             comp = torch.repeat_interleave(torch.arange(3), torch.tensor([mrope_section[0], mrope_section[1], rot // 2 - mrope_section[0] - mrope_section[1]]))
+            if mrope_interleaved:
+                pair = torch.arange(rot // 2)
+                comp = torch.where((pair % 3 == 1) & (pair < 3 * mrope_section[1]), 1, torch.where((pair % 3 == 2) & (pair < 3 * mrope_section[2]), 2, 0))
             idx = torch.arange(rot // 2)
             cos = cos_cache[p3[comp], idx[:, None]].t().float()      # [T, rot/2]
             sin = sin_cache[p3[comp], idx[:, None]].t().float()

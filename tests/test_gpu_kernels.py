@@ -275,9 +275,10 @@ def test_rope_kv_append(D, rot, inter, qk_norm):
     _close(vc, vc2, rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("interleaved_sections", [False, True])
 @pytest.mark.parametrize("kv8", [False, True])
-def test_rope_multimodal_positions(kv8):
-    """Three position components per token, rotary pairs split into sections (Qwen2-VL); bf16 and int8 caches."""
+def test_rope_multimodal_positions(kv8, interleaved_sections):
+    """Three position components per token, rotary pairs split into sections (Qwen2-VL) or alternating t h w (Qwen3-VL); bf16 and int8 caches."""
     T, Hq, Hkv, D, slots_n = 9, 4, 2, 128, 32
     qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=29)
     rng = np.random.RandomState(1)
@@ -291,8 +292,13 @@ def test_rope_multimodal_positions(kv8):
     kc, vc = torch.zeros(slots_n, Hkv, row, dtype=dt, device=DEV), torch.zeros(slots_n, Hkv, row, dtype=dt, device=DEV)
     q2, kc2, vc2 = qkv.cpu().clone(), kc.cpu().clone(), vc.cpu().clone()
     sec = [16, 24, 24]
-    ops.rope_kv_append(qkv, pos.to(DEV), slots.to(DEV), cos.to(DEV), sin.to(DEV), kc, vc, Hq, Hkv, D, D, False, None, None, 1e-6, p3.to(DEV), sec)
-    ref.rope_kv_append(q2, pos, slots, cos, sin, kc2, vc2, Hq, Hkv, D, D, False, None, None, 1e-6, p3, sec)
+    il = interleaved_sections
+    ops.rope_kv_append(qkv, pos.to(DEV), slots.to(DEV), cos.to(DEV), sin.to(DEV), kc, vc, Hq, Hkv, D, D, False, None, None, 1e-6, p3.to(DEV), sec, il)
+    ref.rope_kv_append(q2, pos, slots, cos, sin, kc2, vc2, Hq, Hkv, D, D, False, None, None, 1e-6, p3, sec, il)
+    if il:
+        other = qkv.cpu().clone().copy_(_rand(T, (Hq + 2 * Hkv) * D, seed=29).cpu())
+        ref.rope_kv_append(other, pos, None, cos, sin, None, None, Hq, Hkv, D, D, False, None, None, 1e-6, p3, sec, False)
+        assert (other[:, :Hq * D].float() - q2[:, :Hq * D].float()).abs().max() > 0.05   # the two layouts really differ
     _close(qkv[:, :Hq * D], q2[:, :Hq * D], rtol=2e-2, atol=3e-2)
     if kv8:
         _close(ref.kv8_load(kc.cpu(), Hkv, D), ref.kv8_load(kc2, Hkv, D), rtol=3e-2, atol=3e-2)

@@ -263,3 +263,33 @@ def test_text_decoder_of_a_multimodal_wrapper(wrapper, tmp_path):
     d["architectures"] = [cls.__name__]
     model = _generate_and_compare(tmp_path, d, sd, m)
     assert model.type == kind
+
+
+def test_qwen3_vl_text_decoder_and_interleaved_positions(tmp_path):
+    """Qwen3-VL's decoder: qwen3 with three position components per token whose rotary pairs alternate t h w t h w ... (reference:
+    builders/qwen.py Qwen3VLTextModel).  A text prompt, then a prompt with explicit [3, batch, sequence] positions whose components
+    differ, against `transformers`."""
+    if not hasattr(transformers, "Qwen3VLForConditionalGeneration"):
+        pytest.skip("transformers has no Qwen3VLForConditionalGeneration")
+    cfg = transformers.Qwen3VLConfig(
+        text_config=dict(vocab_size=VOCAB, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=3, intermediate_size=96,
+                         max_position_embeddings=128, head_dim=16, bos_token_id=0, eos_token_id=VOCAB - 1, pad_token_id=0,
+                         rope_parameters={"rope_type": "default", "mrope_section": [2, 3, 3], "mrope_interleaved": True, "rope_theta": 10000.0}),
+        vision_config=dict(depth=1, hidden_size=32, out_hidden_size=64, num_heads=2, intermediate_size=48, patch_size=14, spatial_merge_size=2,
+                           temporal_patch_size=2, deepstack_visual_indexes=[0], num_position_embeddings=16),
+        image_token_id=80, video_token_id=81, vision_start_token_id=78, vision_end_token_id=79, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    m = _randomise(transformers.Qwen3VLForConditionalGeneration(cfg))
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen3VLForConditionalGeneration"]
+    model = _generate_and_compare(tmp_path, d, dict(m.state_dict()), m)
+    assert model.type == "qwen3_vl" and model.arch.mrope_interleaved and model.arch.mrope_section == [2, 3, 3] and model.arch.qk_norm
+    ids = np.random.RandomState(2).randint(1, 70, size=(1, 10)).astype(np.int32)
+    pos = np.stack([np.arange(10), np.array([0, 1, 2, 2, 2, 3, 3, 3, 5, 6]), np.array([0, 1, 2, 3, 4, 2, 3, 4, 5, 6])])[:, None, :].astype(np.int64)
+    p = og.GeneratorParams(model)
+    p.set_search_options(max_length=24)
+    g = og.Generator(model, p)
+    g.set_inputs({"input_ids": ids, "position_ids": pos})
+    with torch.no_grad():
+        want = m(input_ids=torch.tensor(ids.astype(np.int64)), position_ids=torch.from_numpy(pos)).logits[0, -1].float().numpy()
+    np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=3e-4)
