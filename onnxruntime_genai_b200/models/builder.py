@@ -1542,6 +1542,17 @@ def create_model(model_name_or_dir: str, output_dir: str, precision: str, execut
             if os.path.exists(src):
                 os.makedirs(output_dir, exist_ok=True)
                 shutil.copy(src, os.path.join(output_dir, fn))
+    if state_dict is not None and int(extra.get("mtp_head", 0)):
+        # the checkpoint's multi-token-prediction head as a model directory of its own under <output>/mtp (for MtpGenerator)
+        from ..mtp import export_mtp_head, mtp_state_dict_from_hf
+        head_sd = mtp_state_dict_from_hf(arch, state_dict)
+        if head_sd is None:
+            raise ValueError("mtp_head=1: the checkpoint has no mtp.* tensors")
+        _split_gated_q(head_sd, arch)
+        _canonical_moe_names(head_sd, arch)
+        export_mtp_head(arch, os.path.join(output_dir, "mtp"), precision, execution_provider, state_dict=head_sd)
+    if state_dict is not None:
+        state_dict = {k: v for k, v in state_dict.items() if not k.startswith("mtp.")}
     qwen_vision = None
     if state_dict is not None and os.path.isdir(model_name_or_dir):
         with open(os.path.join(model_name_or_dir, "config.json")) as f:

@@ -39,6 +39,10 @@ def export_mtp_head(arch: ArchConfig, out_dir: str, precision: str = "bf16", exe
     head = copy.deepcopy(arch)
     head.num_layers = 1
     head.tie_embeddings = False
+    if head.layer_types is not None:
+        head.layer_types = ["full_attention"]      # the head's one layer attends, whatever mix the main stack has
+    head.sliding_layers = None if head.sliding_layers is None else []
+    head.no_rope_layers = None
     export_model(head, out_dir, precision, execution_provider, state_dict=state_dict, seed=seed, std=std, filename="mtp.onnx")
     H = arch.hidden_size
     extra = {"mtp.enorm.weight": (H,), "mtp.hnorm.weight": (H,), "mtp.fc.weight": (H, 2 * H)}
@@ -49,6 +53,31 @@ def export_mtp_head(arch: ArchConfig, out_dir: str, precision: str = "bf16", exe
         tensors[name] = t.float()
     np.savez(os.path.join(out_dir, "mtp_extra.npz"), **{k: v.numpy() for k, v in tensors.items()})
     return out_dir
+
+
+def mtp_state_dict_from_hf(arch: ArchConfig, sd: Dict[str, torch.Tensor]) -> Optional[Dict[str, torch.Tensor]]:
+    """The multi-token-prediction tensors of a Hugging Face checkpoint (`mtp.fc`, `mtp.pre_fc_norm_embedding`, `mtp.pre_fc_norm_hidden`,
+    `mtp.layers.0.*`, `mtp.norm`; reference: src/python/py/models/builders/qwen_mtp.py) under the names `export_mtp_head` reads.  The
+    embedding table and the LM head are the main model's.  None when the checkpoint has no such tensors."""
+    if not any(k.startswith("mtp.") for k in sd):
+        return None
+    out = {}
+    for k, v in sd.items():
+        if k.startswith("mtp.layers.0."):
+            out["model.layers.0." + k[len("mtp.layers.0."):]] = v
+        elif k == "mtp.norm.weight":
+            out["model.norm.weight"] = v
+        elif k == "mtp.fc.weight":
+            out[k] = v
+        elif k == "mtp.pre_fc_norm_embedding.weight":
+            out["mtp.enorm.weight"] = v.float() + arch.norm_offset      # zero-centred norms store the offset from one
+        elif k == "mtp.pre_fc_norm_hidden.weight":
+            out["mtp.hnorm.weight"] = v.float() + arch.norm_offset
+        elif k in ("model.embed_tokens.weight", "lm_head.weight"):
+            out[k] = v
+    if "lm_head.weight" not in out and "model.embed_tokens.weight" in out:
+        out["lm_head.weight"] = out["model.embed_tokens.weight"]
+    return out
 
 
 class MtpHead:

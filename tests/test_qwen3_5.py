@@ -96,3 +96,54 @@ def test_decoder_of_the_multimodal_wrapper(tmp_path):
          "vision_config": {"depth": 1, "hidden_size": 8}, "tie_word_embeddings": False}
     out = _export(tmp_path, d, sd, "w")
     _check(og.Model(out), m, 1)
+
+
+def test_mtp_head_of_the_checkpoint(tmp_path):
+    """`mtp.*` tensors of a Qwen3.5 checkpoint (reference: src/python/py/models/builders/qwen_mtp.py) exported with `mtp_head=1` as a
+    head directory for MtpGenerator: zero-centred pre-projection norms are stored with their offset applied, the head's layer is an
+    attention layer, and self-speculation with it reproduces plain greedy decoding of the hybrid main model."""
+    cfg, m = _hf_model(seed=2)
+    sd = dict(m.state_dict())
+    g = torch.Generator().manual_seed(5)
+    H = cfg.hidden_size
+    ref_layer = "model.layers.1."                 # an attention layer of the main stack lends the head its shapes
+    for k, v in list(sd.items()):
+        if k.startswith(ref_layer):
+            sd["mtp.layers.0." + k[len(ref_layer):]] = (0.1 * torch.randn(v.shape, generator=g)) if "norm" in k else 0.08 * torch.randn(v.shape, generator=g)
+    sd["mtp.fc.weight"] = 0.08 * torch.randn(H, 2 * H, generator=g)
+    sd["mtp.norm.weight"] = 0.1 * torch.randn(H, generator=g)
+    sd["mtp.pre_fc_norm_embedding.weight"] = 0.1 * torch.randn(H, generator=g)
+    sd["mtp.pre_fc_norm_hidden.weight"] = 0.1 * torch.randn(H, generator=g)
+    d = cfg.to_dict()
+    d["architectures"] = ["Qwen3_5ForCausalLM"]
+    from safetensors.torch import save_file
+    src = tmp_path / "hf"
+    os.makedirs(src)
+    save_file({k: v.detach().contiguous() for k, v in sd.items()}, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps(d))
+    out = str(tmp_path / "out")
+    create_model(str(src), out, "fp32", "cpu", {"mtp_head": 1})
+    head_dir = os.path.join(out, "mtp")
+    z = np.load(os.path.join(head_dir, "mtp_extra.npz"))
+    np.testing.assert_allclose(z["mtp.enorm.weight"], 1 + sd["mtp.pre_fc_norm_embedding.weight"].numpy(), rtol=1e-6)
+    np.testing.assert_allclose(z["mtp.fc.weight"], sd["mtp.fc.weight"].numpy(), rtol=1e-6)
+    model = og.Model(out)
+    _check(model, m, 3)                           # the main model ignores the extra tensors
+    head = og.Model(head_dir)
+    assert head.arch.num_layers == 1 and head.arch.attn_output_gate and not head.arch.has_linear_layers
+    prompt = np.random.RandomState(5).randint(1, VOCAB - 1, size=(1, 9)).astype(np.int32)
+
+    def run(make):
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=30)
+        gen = make(p)
+        gen.append_tokens(prompt)
+        while not gen.is_done():
+            gen.generate_next_token()
+        return gen.get_sequence(0).tolist()
+
+    def spec(p):
+        p.set_speculative_options(max_draft_tokens=3)
+        return og.MtpGenerator(model, head_dir, p)
+
+    assert run(spec) == run(lambda p: og.Generator(model, p))
