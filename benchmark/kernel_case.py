@@ -205,6 +205,21 @@ def build_case(name, T, L, tp=1):
         cos, sin = torch.randn(4096, D // 2, device="cuda"), torch.randn(4096, D // 2, device="cuda")
         kc, vc = _bf(T + 16, HKV, D), _bf(T + 16, HKV, D)
         return (lambda i: ops.rope_kv_append(qkv, pos, slots, cos, sin, kc, vc, HQ, HKV, D, D)), T * (HQ + 2 * HKV) * D * 2 * 2, 0.0
+    if name == "mamba2_scan":
+        # one decode step of a Mamba-2 layer for T requests (heads 128, head size 64, state size 128, one B / C group): every request's
+        # fp32 state [heads, N, P] is read and written once; L state pools are rotated so that the states come from HBM
+        heads, P, N, groups = 128, 64, 128, 1
+        x = _bf(T, heads, P, std=1.0)
+        dt = torch.rand(T, heads, device="cuda") * 0.5 + 0.01
+        neg_a = -(torch.rand(heads, device="cuda") + 0.1)
+        Bm, Cm = _bf(T, groups, N, std=0.5), _bf(T, groups, N, std=0.5)
+        Dv = torch.randn(heads, device="cuda")
+        pools = [torch.randn(T, heads, N, P, device="cuda") * 0.1 for _ in range(max(2, min(L, 4)))]
+        slots = torch.arange(T, dtype=torch.int32, device="cuda")
+        cu = torch.arange(T + 1, dtype=torch.int32, device="cuda")
+        past = torch.full((T,), 7, dtype=torch.int32, device="cuda")
+        return (lambda i: ops.mamba2_scan(x, dt, neg_a, Bm, Cm, Dv, pools[i % len(pools)], slots, cu, past)), \
+            T * heads * N * P * 4 * 2 + T * heads * P * 2 * 2, 4.0 * T * heads * N * P
     if name in ("sample", "argmax"):
         logits = torch.randn(T, V, device="cuda") * 3
         k = torch.full((T,), 50, dtype=torch.int32, device="cuda")
