@@ -205,6 +205,19 @@ def build_case(name, T, L, tp=1):
         cos, sin = torch.randn(4096, D // 2, device="cuda"), torch.randn(4096, D // 2, device="cuda")
         kc, vc = _bf(T + 16, HKV, D), _bf(T + 16, HKV, D)
         return (lambda i: ops.rope_kv_append(qkv, pos, slots, cos, sin, kc, vc, HQ, HKV, D, D)), T * (HQ + 2 * HKV) * D * 2 * 2, 0.0
+    if name == "gated_delta":
+        # one decode step of a gated-delta-net layer for T requests (Qwen3.5 shapes: 16 key heads, 32 value heads, head sizes 128): every
+        # request's fp32 state [32, 128, 128] (2 MiB) is read and written once
+        Hk, Hv, dk, dv = 16, 32, 128, 128
+        q, k, v = _bf(T, Hk, dk, std=0.1), _bf(T, Hk, dk, std=0.1), _bf(T, Hv, dv, std=1.0)
+        g = -torch.rand(T, Hv, device="cuda") * 0.2
+        beta = torch.rand(T, Hv, device="cuda")
+        pools = [torch.randn(T, Hv, dk, dv, device="cuda") * 0.1 for _ in range(max(2, min(L, 4)))]
+        slots = torch.arange(T, dtype=torch.int32, device="cuda")
+        cu = torch.arange(T + 1, dtype=torch.int32, device="cuda")
+        past = torch.full((T,), 7, dtype=torch.int32, device="cuda")
+        return (lambda i: ops.gated_delta(q, k, v, g, beta, pools[i % len(pools)], slots, cu, past)), \
+            T * Hv * dk * dv * 4 * 2 + T * (2 * Hk * dk + 2 * Hv * dv) * 2, 6.0 * T * Hv * dk * dv
     if name == "mamba2_scan":
         # one decode step of a Mamba-2 layer for T requests (heads 128, head size 64, state size 128, one B / C group): every request's
         # fp32 state [heads, N, P] is read and written once; L state pools are rotated so that the states come from HBM

@@ -2,7 +2,9 @@
 // with update_rule "gated_delta" that the reference's builder emits for Qwen3-Next / Qwen3.5 style hybrids
 // (src/python/py/models/builders/base.py:3419-3452, qwen.py:1842-1860; state handling src/models/recurrent_state.h:12-66).
 //
-// One CTA = (request, value head).  Thread j owns column j of the head's state S [dk, dv] in registers (dk <= 128 floats), so the
+// One CTA = (request, value head, 32 columns of the head's state S [dk, dv]).  The tile lives in registers: a thread keeps 16 to 64
+// rows of one column (the rows of a column are split over up to 8 threads); CTAs are small so that several share an SM and their
+// load / update / store phases overlap.  The
 // per-token update needs no shared-memory traffic for S: with k_t, q_t broadcast from shared memory,
 //     S[:, j] *= exp(g);   mem = sum_i S[i, j] k[i];   delta = (v[j] - mem) * beta;   S[i, j] += k[i] * delta;   o[j] = sum_i S[i, j] q[i]
 // Tokens of a request are walked in order inside the kernel (a decode step is one token, a prompt chunk many); the state is read
@@ -12,54 +14,71 @@
 
 namespace ogb {
 
-template <int DK>
-__global__ void __launch_bounds__(128) gated_delta_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+template <int NPT>
+__global__ void __launch_bounds__(512) gated_delta_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                                                          const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                                                          const float* __restrict__ beta, float* __restrict__ state,
                                                          const int32_t* __restrict__ slots, const int32_t* __restrict__ cu_seqlens,
                                                          const int32_t* __restrict__ past_lens, __nv_bfloat16* __restrict__ out,
-                                                         int Hk, int Hv, int dv) {
+                                                         int Hk, int Hv, int dv, int dk) {
+  // thread (j, sp): column j of the state, rows [sp * NPT, (sp + 1) * NPT); the two dot products of a token (with k, then with q)
+  // are summed over the splits through shared memory
   pdl_launch_dependents();
   pdl_wait();
-  const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int splits = dk / NPT, CT = blockDim.x / splits;      // CT columns per CTA (blockIdx.z walks the column tiles)
+  const int jj = threadIdx.x % CT, j = blockIdx.z * CT + jj, sp = threadIdx.x / CT, n0 = sp * NPT;
   const int hk = h / (Hv / Hk);
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   if (t0 >= t1) return;
-  __shared__ float sk[DK], sq[DK];
-  float* S = state + ((size_t(slots[b]) * Hv + h) * DK) * dv;
-  float col[DK];
+  __shared__ float sk[256], sq[256];
+  __shared__ float sM[8][128], sO[8][128];
+  float* S = state + ((size_t(slots[b]) * Hv + h) * dk + n0) * dv;
+  float col[NPT];
   const bool live = j < dv;
   const bool fresh = past_lens[b] == 0;
 #pragma unroll
-  for (int i = 0; i < DK; ++i) col[i] = (live && !fresh) ? S[size_t(i) * dv + j] : 0.f;
+  for (int i = 0; i < NPT; ++i) col[i] = (live && !fresh) ? S[size_t(i) * dv + j] : 0.f;
   for (int t = t0; t < t1; ++t) {
     __syncthreads();
-    for (int i = threadIdx.x; i < DK; i += blockDim.x) {
-      sk[i] = bf2f(k[(size_t(t) * Hk + hk) * DK + i]);
-      sq[i] = bf2f(q[(size_t(t) * Hk + hk) * DK + i]);
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+      sk[i] = bf2f(k[(size_t(t) * Hk + hk) * dk + i]);
+      sq[i] = bf2f(q[(size_t(t) * Hk + hk) * dk + i]);
     }
     __syncthreads();
     const float decay = __expf(g[size_t(t) * Hv + h]);
     const float bt = beta[size_t(t) * Hv + h];
     float mem = 0.f;
 #pragma unroll
-    for (int i = 0; i < DK; ++i) {
+    for (int i = 0; i < NPT; ++i) {
       col[i] *= decay;
-      mem = fmaf(col[i], sk[i], mem);
+      mem = fmaf(col[i], sk[n0 + i], mem);
+    }
+    if (splits > 1) {
+      sM[sp][jj] = mem;
+      __syncthreads();
+      mem = 0.f;
+      for (int s2 = 0; s2 < splits; ++s2) mem += sM[s2][jj];
     }
     const float vj = live ? bf2f(v[(size_t(t) * Hv + h) * dv + j]) : 0.f;
     const float delta = (vj - mem) * bt;
     float o = 0.f;
 #pragma unroll
-    for (int i = 0; i < DK; ++i) {
-      col[i] = fmaf(sk[i], delta, col[i]);
-      o = fmaf(col[i], sq[i], o);
+    for (int i = 0; i < NPT; ++i) {
+      col[i] = fmaf(sk[n0 + i], delta, col[i]);
+      o = fmaf(col[i], sq[n0 + i], o);
     }
-    if (live) out[(size_t(t) * Hv + h) * dv + j] = f2bf(o);
+    if (splits > 1) {
+      sO[sp][jj] = o;
+      __syncthreads();
+      if (sp == 0)
+        for (int s2 = 1; s2 < splits; ++s2) o += sO[s2][jj];
+    }
+    if (live && sp == 0) out[(size_t(t) * Hv + h) * dv + j] = f2bf(o);
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i) S[size_t(i) * dv + j] = col[i];
+    for (int i = 0; i < NPT; ++i) S[size_t(i) * dv + j] = col[i];
   }
 }
 
@@ -71,18 +90,26 @@ OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const f
                             const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream) {
   if (B <= 0) return 0;
   if (Hk <= 0 || Hv % Hk || dv > 128 || dv <= 0) return -1;
-  dim3 grid(B, Hv);
+  if (dk < 16 || dk > 256 || (dk & (dk - 1))) return -5;
+  // a CTA takes 32 columns of the head's state (all of them when dv is not a multiple of 32): small CTAs, several per SM, so that
+  // the load, update and store phases of different CTAs overlap
+  const int Pp = (dv % 32 == 0) ? 32 : (dv + 31) / 32 * 32;
+  const int ztiles = (dv % 32 == 0) ? dv / 32 : 1;
+  int npt = dk < 32 ? dk : 32;
+  if (Pp * (dk / npt) > 512) npt = 64;
+  const int splits = dk / npt;
+  if (splits > 8 || Pp * splits > 512) return -5;
+  dim3 grid(B, Hv, ztiles), block(Pp * splits);
   auto s = static_cast<cudaStream_t>(stream);
   auto Q = static_cast<const __nv_bfloat16*>(q);
   auto K = static_cast<const __nv_bfloat16*>(k);
   auto V = static_cast<const __nv_bfloat16*>(v);
   auto O = static_cast<__nv_bfloat16*>(out);
   bool ok;
-  switch (dk) {
-    case 16: ok = launch_pdl(gated_delta_kernel<16>, grid, dim3(128), 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv); break;
-    case 32: ok = launch_pdl(gated_delta_kernel<32>, grid, dim3(128), 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv); break;
-    case 64: ok = launch_pdl(gated_delta_kernel<64>, grid, dim3(128), 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv); break;
-    case 128: ok = launch_pdl(gated_delta_kernel<128>, grid, dim3(128), 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv); break;
+  switch (npt) {
+    case 16: ok = launch_pdl(gated_delta_kernel<16>, grid, block, 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv, dk); break;
+    case 32: ok = launch_pdl(gated_delta_kernel<32>, grid, block, 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv, dk); break;
+    case 64: ok = launch_pdl(gated_delta_kernel<64>, grid, block, 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv, dk); break;
     default: return -5;
   }
   return ok ? 0 : -4;
