@@ -432,8 +432,6 @@ class SequenceState:
             return False   # rotary positions differ from the cache positions (multimodal RoPE after an image)
         if getattr(self, "alignment_heads", None):
             return False   # the recorded cross-attention scores are gathered with host-side shapes
-        if dec.arch.has_linear_layers:
-            return False   # the gate / norm arithmetic around the recurrence runs as tensor ops
         return dec.tp.size == 1
 
     def run_decode_graph(self, last_tokens: List[int]) -> torch.Tensor:
@@ -469,11 +467,18 @@ class SequenceState:
         key = (bound, self.decoder.active_adapter)
         d = self._g_dev
         if key not in self._graphs:
+            recurrent = self.decoder.arch.has_linear_layers
             s = StepInputs(input_ids=d[:R], positions=d[R:2 * R], slot_mapping=d[2 * R:3 * R], cu_seqlens=self._g_cu, past_lens=d[3 * R:],
                            block_table=self.block_table, logits_rows=self._g_rows, max_q_len=1, max_kv_len=bound,
-                           **self._cross_fields())
+                           state_slots=self._g_rows if recurrent else None, **self._cross_fields())
             with torch.no_grad():
+                # the warm-up run really executes the step: appending keys and values twice is harmless, advancing a recurrent
+                # state twice is not, so those states are put back before the replay
+                saved = self.kv.state.clone() if recurrent and self.kv.state is not None else None
                 self.decoder.forward(s, self.kv)   # warm-up: allocator, tensor maps, scratch
+                if saved is not None:
+                    self.kv.state.copy_(saved)
+                    del saved
                 torch.cuda.synchronize(dev)
                 g = torch.cuda.CUDAGraph()
                 with ops.graph_capture(g, pool=self._g_pool):   # graphs are replayed one at a time: they may share memory
