@@ -319,6 +319,8 @@ struct ShortConvParams {
   const int32_t* block_table; int table_cols, block_size;
   uint4* out;                             // [T, C]
   int T, B, C, L;
+  int plain;                              // no gates: bcx holds x alone ([T, C], the causal convolutions of the recurrent layer kinds)
+  int silu;                               // SiLU on the output
 };
 
 __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvParams p) {
@@ -347,12 +349,16 @@ __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvParams p) {
       if (q >= past) {
         // produced in this step by token t0 + (q - past): recompute b * x from the packed input
         const uint4* row = p.bcx + size_t(t0 + (q - past)) * (p.bcx_stride / 8);
-        const uint4 bb = row[v], xx = row[2 * nvec + v];
-        const __nv_bfloat16* be = reinterpret_cast<const __nv_bfloat16*>(&bb);
-        const __nv_bfloat16* xe = reinterpret_cast<const __nv_bfloat16*>(&xx);
-        __nv_bfloat16* ee = reinterpret_cast<__nv_bfloat16*>(&e);
+        if (p.plain) {
+          e = row[v];
+        } else {
+          const uint4 bb = row[v], xx = row[2 * nvec + v];
+          const __nv_bfloat16* be = reinterpret_cast<const __nv_bfloat16*>(&bb);
+          const __nv_bfloat16* xe = reinterpret_cast<const __nv_bfloat16*>(&xx);
+          __nv_bfloat16* ee = reinterpret_cast<__nv_bfloat16*>(&e);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ee[j] = f2bf(bf2f(be[j]) * bf2f(xe[j]));
+          for (int j = 0; j < 8; ++j) ee[j] = f2bf(bf2f(be[j]) * bf2f(xe[j]));
+        }
         if (k == 0) mine = e;
       } else {
         const int blk = table[q / p.block_size];
@@ -363,12 +369,16 @@ __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvParams p) {
       for (int j = 0; j < 8; ++j) acc[j] += bf2f(p.weight[size_t(v * 8 + j) * p.L + (p.L - 1 - k)]) * bf2f(ee[j]);
     }
     if (slot >= 0) p.cache[size_t(slot) * nvec + v] = mine;
-    const uint4 cc = (p.bcx + size_t(t) * (p.bcx_stride / 8))[nvec + v];
-    const __nv_bfloat16* ce = reinterpret_cast<const __nv_bfloat16*>(&cc);
     uint4 o;
     __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
+    if (!p.plain) {
+      const uint4 cc = (p.bcx + size_t(t) * (p.bcx_stride / 8))[nvec + v];
+      const __nv_bfloat16* ce = reinterpret_cast<const __nv_bfloat16*>(&cc);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) oe[j] = f2bf(bf2f(ce[j]) * acc[j]);
+      for (int j = 0; j < 8; ++j) acc[j] *= bf2f(ce[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = f2bf(p.silu ? acc[j] / (1.f + __expf(-acc[j])) : acc[j]);
     p.out[size_t(t) * nvec + v] = o;
   }
 }
@@ -554,9 +564,30 @@ OGB_API int ogb_act(const void* x, void* out, long long n, int act, void* stream
                     static_cast<const uint4*>(x), static_cast<uint4*>(out), nv, act) ? 0 : -4;
 }
 
+static int LaunchShortConv(const void* bcx, int bcx_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
+                           const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                           int table_cols, int block_size, void* out, int T, int B, int C, int L, int plain, int silu, void* stream);
+
 OGB_API int ogb_short_conv(const void* bcx, int bcx_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
                            const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
                            int table_cols, int block_size, void* out, int T, int B, int C, int L, void* stream) {
+  return LaunchShortConv(bcx, bcx_stride, weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, table_cols, block_size, out,
+                         T, B, C, L, 0, 0, stream);
+}
+
+// The causal depthwise convolution without gates (x [T, C] with a row stride, e.g. a slice of a wider projection), optional SiLU:
+// the CausalConvWithState op of the gated-delta-net and Mamba-2 layers over the same paged window.
+OGB_API int ogb_causal_conv(const void* x, int x_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
+                            const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                            int table_cols, int block_size, void* out, int T, int B, int C, int L, int silu, void* stream) {
+  if (reinterpret_cast<uintptr_t>(x) & 15) return -1;
+  return LaunchShortConv(x, x_stride, weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, table_cols, block_size, out,
+                         T, B, C, L, 1, silu, stream);
+}
+
+static int LaunchShortConv(const void* bcx, int bcx_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
+                           const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                           int table_cols, int block_size, void* out, int T, int B, int C, int L, int plain, int silu, void* stream) {
   if (T <= 0) return 0;
   if (B <= 0 || (C % 8) || (bcx_stride % 8) || L < 1 || L > 16 || block_size <= 0) return -1;
   ShortConvParams p;
@@ -564,7 +595,7 @@ OGB_API int ogb_short_conv(const void* bcx, int bcx_stride, const void* weight, 
   p.weight = static_cast<const __nv_bfloat16*>(weight); p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.cache = static_cast<uint4*>(cache); p.slots = slots; p.positions = positions; p.cu_seqlens = cu_seqlens; p.past_lens = past_lens;
   p.block_table = block_table; p.table_cols = table_cols; p.block_size = block_size; p.out = static_cast<uint4*>(out);
-  p.T = T; p.B = B; p.C = C; p.L = L;
+  p.T = T; p.B = B; p.C = C; p.L = L; p.plain = plain; p.silu = silu;
   const int threads = min(256, max(32, (C / 8 + 31) / 32 * 32));
   return launch_pdl(short_conv_kernel, dim3(T), dim3(threads), 0, static_cast<cudaStream_t>(stream), p) ? 0 : -4;
 }

@@ -95,6 +95,9 @@ int ogb_embedding_q4(const int32_t* ids, const void* q, const void* scales, cons
                      float mult, void* stream);
 int ogb_act_mul(const void* x, void* out, int T, int I, int act, void* stream);
 int ogb_act(const void* x, void* out, long long n, int act, void* stream);
+int ogb_causal_conv(const void* x, int x_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
+                    const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
+                    int table_cols, int block_size, void* out, int T, int B, int C, int L, int silu, void* stream);
 int ogb_short_conv(const void* bcx, int bcx_stride, const void* weight, const void* bias, void* cache, const int32_t* slots,
                    const int32_t* positions, const int32_t* cu_seqlens, const int32_t* past_lens, const int32_t* block_table,
                    int table_cols, int block_size, void* out, int T, int B, int C, int L, void* stream);
@@ -108,6 +111,11 @@ int ogb_gather_rows(const void* in, const int32_t* rows, void* out, int n_rows, 
 int ogb_gather_rows_f16(const void* in, const int32_t* rows, void* out, int n_rows, int row_bytes, void* stream);  // bf16 -> fp16
 
 // ---- linear_attention.cu: gated delta rule over packed sequences; state [slots, Hv, dk, dv] fp32 updated in place
+int ogb_gated_delta_fused(const void* conv, long long conv_stride, long long q_off, long long k_off, long long v_off, const void* ba,
+                          long long ba_stride, long long b_off, long long a_off, const float* neg_exp_a, const float* dt_bias, float q_scale,
+                          float* state, const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk,
+                          int Hv, int dk, int dv, void* stream);
+int ogb_gdn_gate_norm(const void* o, const void* z, long long z_stride, const float* w, float eps, void* out, int T, int Hv, int dv, void* stream);
 int ogb_gated_delta(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, const int32_t* slots,
                     const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream);
 int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,

@@ -14,40 +14,74 @@
 
 namespace ogb {
 
+struct GdnParams {
+  const __nv_bfloat16 *q, *k, *v;     // rows of token t at q + t * tok_stride (+ head offsets): separate tensors or slices of one projection
+  long long tok_stride_qk, tok_stride_v;
+  const float *g, *beta;              // [T, Hv] log-decay and write strength ...
+  const __nv_bfloat16 *b_raw, *a_raw; // ... or (g == null) their raw projections [T, Hv] with a row stride: beta = sigmoid(b),
+  long long ba_stride;                //     g = neg_exp_a[h] * softplus(a + dt_bias[h])
+  const float *neg_exp_a, *dt_bias;
+  int l2norm;                         // q and k are L2-normalised per head here (q then scaled by q_scale)
+  float q_scale;
+  float* state;
+  const int32_t *slots, *cu_seqlens, *past_lens;
+  __nv_bfloat16* out;
+  int Hk, Hv, dv, dk;
+};
+
 template <int NPT>
-__global__ void __launch_bounds__(512) gated_delta_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
-                                                         const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
-                                                         const float* __restrict__ beta, float* __restrict__ state,
-                                                         const int32_t* __restrict__ slots, const int32_t* __restrict__ cu_seqlens,
-                                                         const int32_t* __restrict__ past_lens, __nv_bfloat16* __restrict__ out,
-                                                         int Hk, int Hv, int dv, int dk) {
+__global__ void __launch_bounds__(512) gated_delta_kernel(GdnParams p) {
   // thread (j, sp): column j of the state, rows [sp * NPT, (sp + 1) * NPT); the two dot products of a token (with k, then with q)
   // are summed over the splits through shared memory
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
+  const int Hk = p.Hk, Hv = p.Hv, dv = p.dv, dk = p.dk;
   const int splits = dk / NPT, CT = blockDim.x / splits;      // CT columns per CTA (blockIdx.z walks the column tiles)
   const int jj = threadIdx.x % CT, j = blockIdx.z * CT + jj, sp = threadIdx.x / CT, n0 = sp * NPT;
   const int hk = h / (Hv / Hk);
-  const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+  const int t0 = p.cu_seqlens[b], t1 = p.cu_seqlens[b + 1];
   if (t0 >= t1) return;
   __shared__ float sk[256], sq[256];
   __shared__ float sM[8][128], sO[8][128];
-  float* S = state + ((size_t(slots[b]) * Hv + h) * dk + n0) * dv;
+  __shared__ float sNorm[2][16];
+  float* S = p.state + ((size_t(p.slots[b]) * Hv + h) * dk + n0) * dv;
   float col[NPT];
   const bool live = j < dv;
-  const bool fresh = past_lens[b] == 0;
+  const bool fresh = p.past_lens[b] == 0;
 #pragma unroll
   for (int i = 0; i < NPT; ++i) col[i] = (live && !fresh) ? S[size_t(i) * dv + j] : 0.f;
   for (int t = t0; t < t1; ++t) {
     __syncthreads();
+    float ssk = 0.f, ssq = 0.f;
     for (int i = threadIdx.x; i < dk; i += blockDim.x) {
-      sk[i] = bf2f(k[(size_t(t) * Hk + hk) * dk + i]);
-      sq[i] = bf2f(q[(size_t(t) * Hk + hk) * dk + i]);
+      const float kv_ = bf2f(p.k[size_t(t) * p.tok_stride_qk + size_t(hk) * dk + i]);
+      const float qv_ = bf2f(p.q[size_t(t) * p.tok_stride_qk + size_t(hk) * dk + i]);
+      sk[i] = kv_; sq[i] = qv_;
+      ssk += kv_ * kv_; ssq += qv_ * qv_;
+    }
+    float rk = 1.f, rq = 1.f;
+    if (p.l2norm) {
+      ssk = warp_sum(ssk); ssq = warp_sum(ssq);
+      if ((threadIdx.x & 31) == 0) { sNorm[0][threadIdx.x >> 5] = ssk; sNorm[1][threadIdx.x >> 5] = ssq; }
     }
     __syncthreads();
-    const float decay = __expf(g[size_t(t) * Hv + h]);
-    const float bt = beta[size_t(t) * Hv + h];
+    if (p.l2norm) {
+      float tk = 0.f, tq = 0.f;
+      for (int w = 0; w < int(blockDim.x >> 5); ++w) { tk += sNorm[0][w]; tq += sNorm[1][w]; }
+      rk = 1.f / fmaxf(sqrtf(tk), 1e-6f);
+      rq = p.q_scale / fmaxf(sqrtf(tq), 1e-6f);
+    }
+    float decay, bt;
+    if (p.g) {
+      decay = __expf(p.g[size_t(t) * Hv + h]);
+      bt = p.beta[size_t(t) * Hv + h];
+    } else {
+      const float ar = bf2f(p.a_raw[size_t(t) * p.ba_stride + h]) + p.dt_bias[h];
+      const float soft = ar > 20.f ? ar : log1pf(__expf(ar));
+      decay = __expf(p.neg_exp_a[h] * soft);
+      bt = 1.f / (1.f + __expf(-bf2f(p.b_raw[size_t(t) * p.ba_stride + h])));
+    }
     float mem = 0.f;
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
@@ -60,8 +94,8 @@ __global__ void __launch_bounds__(512) gated_delta_kernel(const __nv_bfloat16* _
       mem = 0.f;
       for (int s2 = 0; s2 < splits; ++s2) mem += sM[s2][jj];
     }
-    const float vj = live ? bf2f(v[(size_t(t) * Hv + h) * dv + j]) : 0.f;
-    const float delta = (vj - mem) * bt;
+    const float vj = live ? bf2f(p.v[size_t(t) * p.tok_stride_v + size_t(h) * dv + j]) : 0.f;
+    const float delta = (vj - mem * rk) * bt * rk;       // the normalised key is rk * sk: once in the read, once in the write
     float o = 0.f;
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
@@ -74,7 +108,7 @@ __global__ void __launch_bounds__(512) gated_delta_kernel(const __nv_bfloat16* _
       if (sp == 0)
         for (int s2 = 1; s2 < splits; ++s2) o += sO[s2][jj];
     }
-    if (live && sp == 0) out[(size_t(t) * Hv + h) * dv + j] = f2bf(o);
+    if (live && sp == 0) p.out[(size_t(t) * Hv + h) * dv + j] = f2bf(o * rq);
   }
   if (live) {
 #pragma unroll
@@ -82,14 +116,37 @@ __global__ void __launch_bounds__(512) gated_delta_kernel(const __nv_bfloat16* _
   }
 }
 
+// Output gate of a gated-delta-net layer: per value head, RMS norm of the recurrence output times its weight, times silu of the gate
+// projection z (a column slice of the layer's input projection).  One warp per (token, head).
+__global__ void gdn_gate_norm_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, long long z_stride,
+                                     const float* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out, int rows, int Hv, int dv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int t = row / Hv, h = row % Hv;
+  const __nv_bfloat16* src = o + size_t(row) * dv;
+  float x[8];
+  float ss = 0.f;
+  int n = 0;
+  for (int e = lane; e < dv; e += 32, ++n) { x[n] = bf2f(src[e]); ss += x[n] * x[n]; }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / dv + eps);
+  n = 0;
+  for (int e = lane; e < dv; e += 32, ++n) {
+    const float zz = bf2f(z[size_t(t) * z_stride + size_t(h) * dv + e]);
+    out[size_t(row) * dv + e] = f2bf(x[n] * inv * w[e] * (zz / (1.f + __expf(-zz))));
+  }
+}
+
 }  // namespace ogb
 
 using namespace ogb;
 
-OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, const int32_t* slots,
-                            const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream) {
+static int LaunchGatedDelta(GdnParams p, int B, void* stream) {
   if (B <= 0) return 0;
-  if (Hk <= 0 || Hv % Hk || dv > 128 || dv <= 0) return -1;
+  const int dk = p.dk, dv = p.dv;
+  if (p.Hk <= 0 || p.Hv % p.Hk || dv > 128 || dv <= 0) return -1;
   if (dk < 16 || dk > 256 || (dk & (dk - 1))) return -5;
   // a CTA takes 32 columns of the head's state (all of them when dv is not a multiple of 32): small CTAs, several per SM, so that
   // the load, update and store phases of different CTAs overlap
@@ -99,20 +156,55 @@ OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const f
   if (Pp * (dk / npt) > 512) npt = 64;
   const int splits = dk / npt;
   if (splits > 8 || Pp * splits > 512) return -5;
-  dim3 grid(B, Hv, ztiles), block(Pp * splits);
+  dim3 grid(B, p.Hv, ztiles), block(Pp * splits);
   auto s = static_cast<cudaStream_t>(stream);
-  auto Q = static_cast<const __nv_bfloat16*>(q);
-  auto K = static_cast<const __nv_bfloat16*>(k);
-  auto V = static_cast<const __nv_bfloat16*>(v);
-  auto O = static_cast<__nv_bfloat16*>(out);
   bool ok;
   switch (npt) {
-    case 16: ok = launch_pdl(gated_delta_kernel<16>, grid, block, 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv, dk); break;
-    case 32: ok = launch_pdl(gated_delta_kernel<32>, grid, block, 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv, dk); break;
-    case 64: ok = launch_pdl(gated_delta_kernel<64>, grid, block, 0, s, Q, K, V, g, beta, state, slots, cu_seqlens, past_lens, O, Hk, Hv, dv, dk); break;
+    case 16: ok = launch_pdl(gated_delta_kernel<16>, grid, block, 0, s, p); break;
+    case 32: ok = launch_pdl(gated_delta_kernel<32>, grid, block, 0, s, p); break;
+    case 64: ok = launch_pdl(gated_delta_kernel<64>, grid, block, 0, s, p); break;
     default: return -5;
   }
   return ok ? 0 : -4;
+}
+
+OGB_API int ogb_gated_delta(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, const int32_t* slots,
+                            const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream) {
+  GdnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q); p.k = static_cast<const __nv_bfloat16*>(k); p.v = static_cast<const __nv_bfloat16*>(v);
+  p.tok_stride_qk = static_cast<long long>(Hk) * dk; p.tok_stride_v = static_cast<long long>(Hv) * dv;
+  p.g = g; p.beta = beta; p.l2norm = 0; p.q_scale = 1.f;
+  p.state = state; p.slots = slots; p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.out = static_cast<__nv_bfloat16*>(out);
+  p.Hk = Hk; p.Hv = Hv; p.dv = dv; p.dk = dk;
+  return LaunchGatedDelta(p, B, stream);
+}
+
+// The recurrence fed straight from the layer's tensors: q / k / v are column ranges of the convolved projection `conv` [T, row
+// stride] (q at q_off, k at k_off, v at v_off), normalised here; the decay and the write strength come from the raw b / a
+// projections (column ranges of `ba`, row stride ba_stride) with the layer's -exp(A_log) and dt_bias.
+OGB_API int ogb_gated_delta_fused(const void* conv, long long conv_stride, long long q_off, long long k_off, long long v_off, const void* ba,
+                                  long long ba_stride, long long b_off, long long a_off, const float* neg_exp_a, const float* dt_bias,
+                                  float q_scale, float* state, const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens,
+                                  void* out, int B, int Hk, int Hv, int dk, int dv, void* stream) {
+  GdnParams p{};
+  auto c = static_cast<const __nv_bfloat16*>(conv);
+  auto r = static_cast<const __nv_bfloat16*>(ba);
+  p.q = c + q_off; p.k = c + k_off; p.v = c + v_off; p.tok_stride_qk = conv_stride; p.tok_stride_v = conv_stride;
+  p.g = nullptr; p.beta = nullptr; p.b_raw = r + b_off; p.a_raw = r + a_off; p.ba_stride = ba_stride;
+  p.neg_exp_a = neg_exp_a; p.dt_bias = dt_bias; p.l2norm = 1; p.q_scale = q_scale;
+  p.state = state; p.slots = slots; p.cu_seqlens = cu_seqlens; p.past_lens = past_lens; p.out = static_cast<__nv_bfloat16*>(out);
+  p.Hk = Hk; p.Hv = Hv; p.dv = dv; p.dk = dk;
+  return LaunchGatedDelta(p, B, stream);
+}
+
+OGB_API int ogb_gdn_gate_norm(const void* o, const void* z, long long z_stride, const float* w, float eps, void* out, int T, int Hv, int dv,
+                              void* stream) {
+  if (T <= 0) return 0;
+  if (dv <= 0 || dv > 256) return -1;
+  const int rows = T * Hv;
+  return launch_pdl(gdn_gate_norm_kernel, dim3((rows + 7) / 8), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(z), z_stride, w, eps,
+                    static_cast<__nv_bfloat16*>(out), rows, Hv, dv) ? 0 : -4;
 }
 
 // ---------------------------------------------------------------------------------------------- Mamba-2 selective scan

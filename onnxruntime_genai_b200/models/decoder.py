@@ -352,10 +352,15 @@ class DecoderModel:
         cd, vd, nk, nv, hk, hv = a.linear_conv_dim, a.linear_value_dim, a.linear_num_key_heads, a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim
         proj = self._linear(x, lw.lin_in_w)
         qkv, z, b_, a_ = proj[:, :cd], proj[:, cd:cd + vd], proj[:, cd + vd:cd + vd + nv], proj[:, cd + vd + nv:]
-        ones = torch.ones(T, cd, dtype=x.dtype, device=x.device)
-        conv = ops.short_conv(torch.cat([ones, ones, qkv], dim=1).contiguous(), lw.lin_conv_w, None, kv.conv_layer(li), s.slot_mapping, s.positions,
-                              s.cu_seqlens, s.past_lens, s.block_table, kv.block_size)
-        conv = torch.nn.functional.silu(conv.float())
+        conv = ops.causal_conv(qkv, lw.lin_conv_w, None, kv.conv_layer(li), s.slot_mapping, s.positions, s.cu_seqlens, s.past_lens,
+                               s.block_table, kv.block_size, silu=True)
+        if (conv.is_cuda and conv.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16 and hv <= 128 and hk in (16, 32, 64, 128, 256) and
+                lw.lin_norm_w.dtype == torch.float32):
+            # normalisation, gates, recurrence and the gated output norm in two kernels
+            o = ops.gated_delta_layer(conv, proj, cd, vd, nk, nv, hk, hv, lw.lin_neg_exp_a, lw.lin_dt_bias, lw.lin_norm_w, a.norm_eps,
+                                      kv.state_layer(li), s.state_slots, s.cu_seqlens, s.past_lens)
+            return self._row_parallel(o, lw.lin_out_w, None, None)
+        conv = conv.float()
         kd = nk * hk
         q = torch.nn.functional.normalize(conv[:, :kd].view(T, nk, hk), dim=-1, eps=1e-6) * (hk ** -0.5)
         k = torch.nn.functional.normalize(conv[:, kd:2 * kd].view(T, nk, hk), dim=-1, eps=1e-6)
@@ -378,10 +383,8 @@ class DecoderModel:
         I, cd, nh, P, N, G = a.mamba_intermediate, a.mamba_conv_dim, a.mamba_num_heads, a.mamba_head_dim, a.mamba_state_size, a.mamba_n_groups
         proj = self._linear(x, lw.mamba_in_w)
         z, xbc, dt = proj[:, :I], proj[:, I:I + cd], proj[:, I + cd:]
-        ones = torch.ones(T, cd, dtype=x.dtype, device=x.device)
-        conv = ops.short_conv(torch.cat([ones, ones, xbc], dim=1).contiguous(), lw.mamba_conv_w, lw.mamba_conv_b, kv.conv_layer(li), s.slot_mapping,
-                              s.positions, s.cu_seqlens, s.past_lens, s.block_table, kv.block_size)
-        conv = torch.nn.functional.silu(conv.float()).to(x.dtype)
+        conv = ops.causal_conv(xbc, lw.mamba_conv_w, lw.mamba_conv_b, kv.conv_layer(li), s.slot_mapping, s.positions, s.cu_seqlens, s.past_lens,
+                               s.block_table, kv.block_size, silu=True)
         xs = conv[:, :I].reshape(T, nh, P).contiguous()
         Bm = conv[:, I:I + G * N].reshape(T, G, N).contiguous()
         Cm = conv[:, I + G * N:].reshape(T, G, N).contiguous()

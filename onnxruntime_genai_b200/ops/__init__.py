@@ -369,6 +369,23 @@ def short_conv(bcx, weight, bias, cache, slots, positions, cu_seqlens, past_lens
     return out
 
 
+def causal_conv(x, weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, block_size: int, silu: bool = True):
+    """Causal depthwise convolution (no gates) of the recurrent layer kinds over packed sequences, with the window of earlier
+    positions read from the paged `cache` [slots, C] that this step's rows are appended to; optional SiLU.  x [T, C] may be a
+    column slice of a wider tensor.  Returns [T, C] in x's dtype."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.stride(1) != 1 or (x.stride(0) % 8) or (x.data_ptr() % 16):
+        ones = torch.ones_like(x)
+        y = short_conv(torch.cat([ones, ones, x], dim=1).contiguous(), weight, bias, cache, slots, positions, cu_seqlens, past_lens, block_table, block_size)
+        return torch.nn.functional.silu(y.float()).to(x.dtype) if silu else y
+    T, C = x.shape[0], weight.shape[0]
+    assert weight.is_contiguous() and cache.is_contiguous() and block_table.stride(1) == 1
+    out = torch.empty(T, C, dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().ogb_causal_conv(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(cache), _ptr(slots), _ptr(positions),
+                                         _ptr(cu_seqlens), _ptr(past_lens), _ptr(block_table), block_table.stride(0), int(block_size),
+                                         _ptr(out), T, past_lens.shape[0], C, weight.shape[1], int(silu), _stream()), "causal_conv")
+    return out
+
+
 def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
     """Gated-delta-rule recurrence of a linear-attention layer over packed sequences (see ops/reference.py::gated_delta).
     state [slots, Hv, dk, dv] fp32 is updated in place."""
@@ -383,6 +400,27 @@ def gated_delta(q, k, v, g, beta, state, slots, cu_seqlens, past_lens):
     B = past_lens.shape[0]
     _lib.check(_lib.lib().ogb_gated_delta(_ptr(q), _ptr(k), _ptr(v), _ptr(gf), _ptr(bf), _ptr(state), _ptr(slots), _ptr(cu_seqlens), _ptr(past_lens),
                                           _ptr(out), B, Hk, Hv, dk, dv, _stream()), "gated_delta")
+    return out
+
+
+def gated_delta_layer(conv, proj, cd, vd, Hk, Hv, dk, dv, neg_exp_a, dt_bias, norm_w, norm_eps, state, slots, cu_seqlens, past_lens):
+    """The part of a gated-delta-net layer between its convolution and its output projection, as two kernels on bf16 CUDA tensors:
+    conv [T, cd] = silu(conv1d([q | k | v])), proj [T, cd + vd + 2 Hv] = the input projection [qkv | z | b | a].  q and k are
+    L2-normalised per head (q also scaled by dk^-0.5), beta = sigmoid(b), log-decay = neg_exp_a * softplus(a + dt_bias), the
+    recurrence updates `state` in place, and the result is RMS-normalised per value head, weighted and gated by silu(z).
+    Returns [T, Hv * dv]."""
+    T = conv.shape[0]
+    assert conv.is_cuda and conv.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16 and conv.stride(1) == 1 and proj.stride(1) == 1
+    kd = Hk * dk
+    o = torch.empty(T, Hv, dv, dtype=torch.bfloat16, device=conv.device)
+    B = past_lens.shape[0]
+    _lib.check(_lib.lib().ogb_gated_delta_fused(_ptr(conv), conv.stride(0), 0, kd, 2 * kd, _ptr(proj), proj.stride(0), cd + vd, cd + vd + Hv,
+                                                _ptr(neg_exp_a), _ptr(dt_bias), float(dk) ** -0.5, _ptr(state), _ptr(slots), _ptr(cu_seqlens),
+                                                _ptr(past_lens), _ptr(o), B, Hk, Hv, dk, dv, _stream()), "gated_delta_fused")
+    out = torch.empty(T, Hv * dv, dtype=torch.bfloat16, device=conv.device)
+    z = proj[:, cd:cd + vd]
+    _lib.check(_lib.lib().ogb_gdn_gate_norm(_ptr(o), _ptr(z), proj.stride(0), _ptr(norm_w), float(norm_eps), _ptr(out), T, Hv, dv, _stream()),
+               "gdn_gate_norm")
     return out
 
 

@@ -63,6 +63,7 @@ _SIGS = {
     "ogb_embedding_q4": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_float, _P]),
     "ogb_act_mul": (c_int, [_P, _P, c_int, c_int, c_int, _P]),
     "ogb_act": (c_int, [_P, _P, c_longlong, c_int, _P]),
+    "ogb_causal_conv": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_short_conv": (c_int, [_P, c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, _P]),
     "ogb_decode_advance": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, _P]),
     "ogb_logits_edit": (c_int, [_P, c_int, _P, _P, _P, _P, c_int, _P]),
@@ -80,6 +81,9 @@ _SIGS = {
                                  c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "ogb_paged_attention_kv8": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, _P, c_float, c_float, c_int, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_longlong, c_int, _P, _P, _P]),
+    "ogb_gated_delta_fused": (c_int, [_P, c_longlong, c_longlong, c_longlong, c_longlong, _P, c_longlong, c_longlong, c_longlong, _P, _P, c_float,
+                                      _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "ogb_gdn_gate_norm": (c_int, [_P, _P, c_longlong, _P, c_float, _P, c_int, c_int, c_int, _P]),
     "ogb_gated_delta": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_mamba2_scan": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_copy_state_slots": (c_int, [_P, _P, c_int, c_int, c_longlong, _P, _P, c_int, _P]),

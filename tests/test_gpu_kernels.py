@@ -374,6 +374,79 @@ def test_short_conv_matches_reference(L, bias):
     assert torch.equal(cache.cpu(), c_cpu)
 
 
+@pytest.mark.parametrize("bias", [False, True])
+def test_causal_conv_plain_mode_matches_the_gated_form_with_unit_gates(bias):
+    """The convolution of the recurrent layer kinds: x is a column slice of a wider projection, no gates, SiLU on the output; the same
+    packed launch shapes as the gated test, against the CPU restatement fed with unit gates."""
+    rng = np.random.RandomState(6)
+    C, bs, L = 192, 16, 4
+    q_lens, past = [19, 1, 5, 1], [0, 37, 14, 2]
+    B, T = len(q_lens), sum(q_lens)
+    cols = max((p_ + q_ + bs - 1) // bs for p_, q_ in zip(past, q_lens))
+    perm = rng.permutation(B * cols + 2)
+    table = torch.full((B, cols), -1, dtype=torch.int32)
+    used = 0
+    for b in range(B):
+        need = (past[b] + q_lens[b] + bs - 1) // bs
+        table[b, :need] = torch.from_numpy(perm[used:used + need].astype(np.int32))
+        used += need
+    cache = _rand((B * cols + 2) * bs, C, std=1.0, seed=50)
+    wide = _rand(T, 64 + C + 40, std=1.0, seed=51)
+    x = wide[:, 64:64 + C]                       # 128-byte offset, row stride of the wider tensor
+    w = _rand(C, L, std=0.5, seed=52)
+    bvec = _rand(C, std=0.5, seed=53) if bias else None
+    pos, slots = [], []
+    for b in range(B):
+        for j in range(q_lens[b]):
+            p_ = past[b] + j
+            pos.append(p_)
+            slots.append(int(table[b, p_ // bs]) * bs + p_ % bs)
+    pos, slots = torch.tensor(pos, dtype=torch.int32), torch.tensor(slots, dtype=torch.int32)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    pl = torch.tensor(past, dtype=torch.int32)
+    c_cpu = cache.cpu().clone()
+    xc = x.cpu().contiguous()
+    ones = torch.ones_like(xc)
+    want = ref.short_conv(torch.cat([ones, ones, xc], 1), w.cpu(), bvec.cpu() if bias else None, c_cpu, slots, pos, cu, pl, table, bs)
+    want = torch.nn.functional.silu(want.float())
+    got = ops.causal_conv(x, w, bvec, cache, slots.to(DEV), pos.to(DEV), cu.to(DEV), pl.to(DEV), table.to(DEV), bs, silu=True)
+    _close(got, want.to(torch.bfloat16), rtol=3e-2, atol=3e-2)
+    assert torch.equal(cache.cpu(), c_cpu)
+
+
+def test_gated_delta_layer_matches_the_tensor_form():
+    """ops.gated_delta_layer (normalisation, gates, recurrence, gated output norm in two kernels) against the same arithmetic written
+    with tensor operations around the plain recurrence restatement."""
+    torch.manual_seed(3)
+    Hk, Hv, dk, dv = 2, 4, 64, 64
+    kd, vd = Hk * dk, Hv * dv
+    cd = 2 * kd + vd
+    lens, past = [9, 1, 1, 21], [0, 5, 1, 16]
+    T = sum(lens)
+    conv = torch.nn.functional.silu(torch.randn(T, cd, device=DEV)).to(torch.bfloat16)
+    proj = torch.randn(T, cd + vd + 2 * Hv, device=DEV).to(torch.bfloat16)
+    neg_exp_a = -(torch.rand(Hv, device=DEV) * 2 + 0.1)
+    dt_bias = torch.randn(Hv, device=DEV) * 0.5
+    norm_w = 1 + 0.1 * torch.randn(dv, device=DEV)
+    state = torch.randn(6, Hv, dk, dv, device=DEV) * 0.1
+    slots = torch.tensor([4, 1, 5, 0], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+    pl = torch.tensor(past, dtype=torch.int32, device=DEV)
+    st_ref = state.clone().cpu()
+    c, pr = conv.float().cpu(), proj.float().cpu()
+    q = torch.nn.functional.normalize(c[:, :kd].view(T, Hk, dk), dim=-1, eps=1e-6) * dk ** -0.5
+    k = torch.nn.functional.normalize(c[:, kd:2 * kd].view(T, Hk, dk), dim=-1, eps=1e-6)
+    v = c[:, 2 * kd:].view(T, Hv, dv)
+    z, b_, a_ = pr[:, cd:cd + vd], pr[:, cd + vd:cd + vd + Hv], pr[:, cd + vd + Hv:]
+    g = neg_exp_a.cpu() * torch.nn.functional.softplus(a_ + dt_bias.cpu())
+    o = ref.gated_delta(q, k, v, g, torch.sigmoid(b_), st_ref, slots.cpu(), cu.cpu(), pl.cpu()).float()
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.cpu()
+    want = o.view(T, vd) * torch.nn.functional.silu(z)
+    got = ops.gated_delta_layer(conv, proj, cd, vd, Hk, Hv, dk, dv, neg_exp_a, dt_bias, norm_w, 1e-6, state, slots, cu, pl)
+    _close(got, want.to(torch.bfloat16), rtol=4e-2, atol=4e-2)
+    torch.testing.assert_close(state.cpu(), st_ref, rtol=2e-3, atol=2e-3)
+
+
 def test_decode_advance_matches_reference():
     rng = np.random.RandomState(3)
     B, cols, bs = 37, 9, 16
