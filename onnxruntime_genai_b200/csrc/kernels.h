@@ -118,6 +118,10 @@ int ogb_gated_delta_fused(const void* conv, long long conv_stride, long long q_o
 int ogb_gdn_gate_norm(const void* o, const void* z, long long z_stride, const float* w, float eps, void* out, int T, int Hv, int dv, void* stream);
 int ogb_gated_delta(const void* q, const void* k, const void* v, const float* g, const float* beta, float* state, const int32_t* slots,
                     const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int Hk, int Hv, int dk, int dv, void* stream);
+int ogb_mamba2_scan_fused(const void* conv, long long conv_stride, const void* dt_raw, long long dt_stride, const float* dt_bias, const float* neg_a,
+                          const float* Dv, float* state, const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B,
+                          int heads, int groups, int P, int N, void* stream);
+int ogb_mamba_gate_norm(const void* y, const void* z, long long z_stride, const float* w, float eps, void* out, int T, int I, void* stream);
 int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,
                     const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int heads, int groups, int P, int N,
                     void* stream);

@@ -222,7 +222,11 @@ __global__ void __launch_bounds__(512) mamba2_scan_kernel(
     const __nv_bfloat16* __restrict__ x, const float* __restrict__ dt, const float* __restrict__ neg_a, const __nv_bfloat16* __restrict__ Bm,
     const __nv_bfloat16* __restrict__ Cm, const float* __restrict__ Dv, float* __restrict__ state, const int32_t* __restrict__ slots,
     const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ past_lens, __nv_bfloat16* __restrict__ out, int heads, int groups, int P,
-    int N) {
+    int N, long long x_stride, long long bc_stride, const __nv_bfloat16* __restrict__ dt_raw, long long dt_stride,
+    const float* __restrict__ dt_bias) {
+  // x_stride / bc_stride: elements between the rows of consecutive tokens in x and in Bm / Cm (tensors of their own, or column
+  // ranges of one convolved projection);
+  // dt_raw (dt == null): the raw step projection [T, heads] with a row stride, step = softplus(dt_raw + dt_bias[h]) computed here
   // thread (j, sp): column j of the state, rows [sp * NPT, (sp + 1) * NPT); the partial dot products of the splits meet in shared memory
   pdl_launch_dependents();
   pdl_wait();
@@ -244,13 +248,18 @@ __global__ void __launch_bounds__(512) mamba2_scan_kernel(
   for (int t = t0; t < t1; ++t) {
     __syncthreads();
     for (int i = threadIdx.x; i < N; i += blockDim.x) {
-      sB[i] = bf2f(Bm[(size_t(t) * groups + gr) * N + i]);
-      sC[i] = bf2f(Cm[(size_t(t) * groups + gr) * N + i]);
+      sB[i] = bf2f(Bm[size_t(t) * bc_stride + size_t(gr) * N + i]);
+      sC[i] = bf2f(Cm[size_t(t) * bc_stride + size_t(gr) * N + i]);
     }
     __syncthreads();
-    const float step = dt[size_t(t) * heads + h];
+    float step;
+    if (dt) step = dt[size_t(t) * heads + h];
+    else {
+      const float r = bf2f(dt_raw[size_t(t) * dt_stride + h]) + dt_bias[h];
+      step = r > 20.f ? r : log1pf(__expf(r));
+    }
     const float decay = __expf(step * a);
-    const float xj = live ? bf2f(x[(size_t(t) * heads + h) * P + j]) : 0.f;
+    const float xj = live ? bf2f(x[size_t(t) * x_stride + size_t(h) * P + j]) : 0.f;
     const float dx = step * xj;
     float y = 0.f;
 #pragma unroll
@@ -273,9 +282,9 @@ __global__ void __launch_bounds__(512) mamba2_scan_kernel(
 }
 }  // namespace ogb
 
-OGB_API int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,
-                            const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int heads, int groups,
-                            int P, int N, void* stream) {
+static int LaunchMamba2(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,
+                        const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int heads, int groups, int P,
+                        int N, long long x_stride, long long bc_stride, const void* dt_raw, long long dt_stride, const float* dt_bias, void* stream) {
   if (B <= 0) return 0;
   if (heads <= 0 || groups <= 0 || heads % groups || P <= 0 || P > 128) return -1;
   if (N < 16 || N > 256 || (N & (N - 1))) return -5;
@@ -290,14 +299,70 @@ OGB_API int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, 
   auto Bp = static_cast<const __nv_bfloat16*>(Bm);
   auto Cp = static_cast<const __nv_bfloat16*>(Cm);
   auto O = static_cast<__nv_bfloat16*>(out);
+  auto R = static_cast<const __nv_bfloat16*>(dt_raw);
   bool ok;
   switch (npt) {
-    case 16: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<16>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N); break;
-    case 32: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<32>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N); break;
-    case 64: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<64>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N); break;
+    case 16: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<16>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N, x_stride, bc_stride, R, dt_stride, dt_bias); break;
+    case 32: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<32>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N, x_stride, bc_stride, R, dt_stride, dt_bias); break;
+    case 64: ok = ogb::launch_pdl(ogb::mamba2_scan_kernel<64>, grid, block, 0, s, X, dt, neg_a, Bp, Cp, Dv, state, slots, cu_seqlens, past_lens, O, heads, groups, P, N, x_stride, bc_stride, R, dt_stride, dt_bias); break;
     default: return -5;
   }
   return ok ? 0 : -4;
+}
+
+OGB_API int ogb_mamba2_scan(const void* x, const float* dt, const float* neg_a, const void* Bm, const void* Cm, const float* Dv, float* state,
+                            const int32_t* slots, const int32_t* cu_seqlens, const int32_t* past_lens, void* out, int B, int heads, int groups,
+                            int P, int N, void* stream) {
+  return LaunchMamba2(x, dt, neg_a, Bm, Cm, Dv, state, slots, cu_seqlens, past_lens, out, B, heads, groups, P, N,
+                      static_cast<long long>(heads) * P, static_cast<long long>(groups) * N, nullptr, 0, nullptr, stream);
+}
+
+// The scan fed straight from the layer's tensors: x / B / C are column ranges of the convolved projection `conv` (row stride
+// conv_stride; x at 0, B at heads * P, C after B), the step comes from the raw dt projection (a column range of `proj`) with dt_bias.
+OGB_API int ogb_mamba2_scan_fused(const void* conv, long long conv_stride, const void* dt_raw, long long dt_stride, const float* dt_bias,
+                                  const float* neg_a, const float* Dv, float* state, const int32_t* slots, const int32_t* cu_seqlens,
+                                  const int32_t* past_lens, void* out, int B, int heads, int groups, int P, int N, void* stream) {
+  auto c = static_cast<const __nv_bfloat16*>(conv);
+  const long long I = static_cast<long long>(heads) * P, GN = static_cast<long long>(groups) * N;
+  return LaunchMamba2(c, nullptr, neg_a, c + I, c + I + GN, Dv, state, slots, cu_seqlens, past_lens, out, B, heads, groups, P, N, conv_stride,
+                      conv_stride, dt_raw, dt_stride, dt_bias, stream);
+}
+
+// Output gate of a Mamba-2 layer: y * silu(z) (z a column range of the input projection), then an RMS norm over the whole width with
+// the layer's weight.  One CTA per token.
+namespace ogb {
+__global__ void __launch_bounds__(256) mamba_gate_norm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
+                                                             long long z_stride, const float* __restrict__ w, float eps,
+                                                             __nv_bfloat16* __restrict__ out, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  __shared__ float part[8];
+  float v[16];
+  float ss = 0.f;
+  int n = 0;
+  for (int e = threadIdx.x; e < I; e += blockDim.x, ++n) {
+    const float zz = bf2f(z[size_t(t) * z_stride + e]);
+    v[n] = bf2f(y[size_t(t) * I + e]) * (zz / (1.f + __expf(-zz)));
+    ss += v[n] * v[n];
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < int(blockDim.x >> 5); ++i) tot += part[i];
+  const float inv = rsqrtf(tot / I + eps);
+  n = 0;
+  for (int e = threadIdx.x; e < I; e += blockDim.x, ++n) out[size_t(t) * I + e] = f2bf(v[n] * inv * w[e]);
+}
+}  // namespace ogb
+
+OGB_API int ogb_mamba_gate_norm(const void* y, const void* z, long long z_stride, const float* w, float eps, void* out, int T, int I, void* stream) {
+  if (T <= 0) return 0;
+  if (I <= 0 || I > 16 * 256) return -1;
+  return ogb::launch_pdl(ogb::mamba_gate_norm_kernel, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                         static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), z_stride, w, eps,
+                         static_cast<__nv_bfloat16*>(out), I) ? 0 : -4;
 }
 
 // ---------------------------------------------------------------------------------------------- state snapshots

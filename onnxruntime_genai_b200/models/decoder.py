@@ -385,6 +385,12 @@ class DecoderModel:
         z, xbc, dt = proj[:, :I], proj[:, I:I + cd], proj[:, I + cd:]
         conv = ops.causal_conv(xbc, lw.mamba_conv_w, lw.mamba_conv_b, kv.conv_layer(li), s.slot_mapping, s.positions, s.cu_seqlens, s.past_lens,
                                s.block_table, kv.block_size, silu=True)
+        if (conv.is_cuda and conv.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16 and P <= 128 and N in (16, 32, 64, 128, 256) and
+                I <= 4096 and lw.mamba_norm_w.dtype == torch.float32):
+            # step sizes, scan and the gated output norm in two kernels
+            y = ops.mamba2_layer(conv, proj, nh, G, P, N, lw.mamba_dt_bias, lw.mamba_neg_a, lw.mamba_d, lw.mamba_norm_w, a.norm_eps,
+                                 kv.state_layer(li), s.state_slots, s.cu_seqlens, s.past_lens)
+            return self._row_parallel(y, lw.mamba_out_w, None, None)
         xs = conv[:, :I].reshape(T, nh, P).contiguous()
         Bm = conv[:, I:I + G * N].reshape(T, G, N).contiguous()
         Cm = conv[:, I + G * N:].reshape(T, G, N).contiguous()

@@ -424,6 +424,25 @@ def gated_delta_layer(conv, proj, cd, vd, Hk, Hv, dk, dv, neg_exp_a, dt_bias, no
     return out
 
 
+def mamba2_layer(conv, proj, heads, groups, P, N, dt_bias, neg_a, Dv, norm_w, norm_eps, state, slots, cu_seqlens, past_lens):
+    """The part of a Mamba-2 layer between its convolution and its output projection, as two kernels on bf16 CUDA tensors:
+    conv [T, I + 2 G N] = silu(conv1d([x | B | C])), proj [T, I + conv width + heads] = the input projection [z | xBC | dt].
+    step = softplus(dt + dt_bias), the scan updates `state` in place, y * silu(z) is RMS-normalised over the whole width I = heads * P
+    and weighted.  Returns [T, I]."""
+    T = conv.shape[0]
+    I = heads * P
+    assert conv.is_cuda and conv.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16 and conv.stride(1) == 1 and proj.stride(1) == 1
+    y = torch.empty(T, I, dtype=torch.bfloat16, device=conv.device)
+    dt_raw = proj[:, I + conv.shape[1]:]
+    _lib.check(_lib.lib().ogb_mamba2_scan_fused(_ptr(conv), conv.stride(0), _ptr(dt_raw), proj.stride(0), _ptr(dt_bias), _ptr(neg_a), _ptr(Dv),
+                                                _ptr(state), _ptr(slots), _ptr(cu_seqlens), _ptr(past_lens), _ptr(y), past_lens.shape[0], heads,
+                                                groups, P, N, _stream()), "mamba2_scan_fused")
+    out = torch.empty(T, I, dtype=torch.bfloat16, device=conv.device)
+    _lib.check(_lib.lib().ogb_mamba_gate_norm(_ptr(y), _ptr(proj), proj.stride(0), _ptr(norm_w), float(norm_eps), _ptr(out), T, I, _stream()),
+               "mamba_gate_norm")
+    return out
+
+
 def mamba2_scan(x, dt, neg_a, Bm, Cm, Dv, state, slots, cu_seqlens, past_lens):
     """Mamba-2 selective scan of a state-space layer over packed sequences (see ops/reference.py::mamba2_scan).
     state [slots, heads, N, P] fp32 is updated in place."""

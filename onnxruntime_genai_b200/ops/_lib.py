@@ -85,6 +85,8 @@ _SIGS = {
                                       _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_gdn_gate_norm": (c_int, [_P, _P, c_longlong, _P, c_float, _P, c_int, c_int, c_int, _P]),
     "ogb_gated_delta": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "ogb_mamba2_scan_fused": (c_int, [_P, c_longlong, _P, c_longlong, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "ogb_mamba_gate_norm": (c_int, [_P, _P, c_longlong, _P, c_float, _P, c_int, c_int, _P]),
     "ogb_mamba2_scan": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "ogb_copy_state_slots": (c_int, [_P, _P, c_int, c_int, c_longlong, _P, _P, c_int, _P]),
     "ogb_sample": (c_int, [_P, c_longlong, c_int, c_int, _P, _P, _P, _P, _P, _P, _P]),

@@ -447,6 +447,37 @@ def test_gated_delta_layer_matches_the_tensor_form():
     torch.testing.assert_close(state.cpu(), st_ref, rtol=2e-3, atol=2e-3)
 
 
+def test_mamba2_layer_matches_the_tensor_form():
+    """ops.mamba2_layer (step sizes, scan over column ranges of the convolved projection, gated norm over the whole width) against the
+    same arithmetic written with tensor operations around the plain scan restatement."""
+    torch.manual_seed(4)
+    heads, groups, P, N = 8, 2, 32, 64
+    I, GN = heads * P, groups * N
+    cd = I + 2 * GN
+    lens, past = [9, 1, 1, 21], [0, 5, 1, 16]
+    T = sum(lens)
+    conv = torch.nn.functional.silu(torch.randn(T, cd, device=DEV)).to(torch.bfloat16)
+    proj = torch.randn(T, I + cd + heads, device=DEV).to(torch.bfloat16)
+    dt_bias = torch.randn(heads, device=DEV) * 0.5
+    neg_a = -(torch.rand(heads, device=DEV) * 2 + 0.1)
+    Dv = torch.randn(heads, device=DEV)
+    norm_w = 1 + 0.1 * torch.randn(I, device=DEV)
+    state = torch.randn(6, heads, N, P, device=DEV) * 0.1
+    slots = torch.tensor([4, 1, 5, 0], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+    pl = torch.tensor(past, dtype=torch.int32, device=DEV)
+    st_ref = state.clone().cpu()
+    c, pr = conv.float().cpu(), proj.float().cpu()
+    step = torch.nn.functional.softplus(pr[:, I + cd:] + dt_bias.cpu())
+    y = ref.mamba2_scan(c[:, :I].reshape(T, heads, P), step, neg_a.cpu(), c[:, I:I + GN].reshape(T, groups, N), c[:, I + GN:].reshape(T, groups, N),
+                        Dv.cpu(), st_ref, slots.cpu(), cu.cpu(), pl.cpu()).float().view(T, I)
+    y = y * torch.nn.functional.silu(pr[:, :I])
+    want = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + 1e-5) * norm_w.cpu()
+    got = ops.mamba2_layer(conv, proj, heads, groups, P, N, dt_bias, neg_a, Dv, norm_w, 1e-5, state, slots, cu, pl)
+    _close(got, want.to(torch.bfloat16), rtol=4e-2, atol=4e-2)
+    torch.testing.assert_close(state.cpu(), st_ref, rtol=2e-3, atol=2e-3)
+
+
 def test_decode_advance_matches_reference():
     rng = np.random.RandomState(3)
     B, cols, bs = 37, 9, 16
