@@ -146,6 +146,7 @@ class _Staging:
         add("cu_seqlens", max_batch + 1)
         for f in self.FIELDS_ROW:
             add(f, max_batch)
+        add("state_slots", max_batch)     # recurrent models: slot of every request in the state pool (filled by the executor, not the core)
         add("top_p", max_batch)
         add("temperature", max_batch)
         add("seeds", 2 * max_batch)
@@ -165,7 +166,7 @@ class _Staging:
         self.tokens_ring = [torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
         self.ring_next = 0
         for h in self._hosts:
-            a = {k: h.data_ptr() + 4 * o for k, (o, _) in lay.items()}
+            a = {k: h.data_ptr() + 4 * o for k, (o, _) in lay.items() if k != "state_slots"}
             if not windowed:
                 a.pop("slot_mapping_w", None)
             self._addrs.append(a)
@@ -216,6 +217,7 @@ class ModelExecutor:
         self.order_attention = self.use_graphs and os.environ.get("OGB_ATTN_ORDER", "1") != "0"
         self.lora_of = None          # set by the engine: plan -> (per-token adapter ids on the device, adapter names) or None
         self.state_slots_of = None   # set by the engine for models with linear-attention layers: plan -> [B] int32 state slots
+        self._graph_state_slots = False   # building the inputs of a graph step: the state slots are read from the staging buffer
 
     def _step_inputs(self, T: int, B: int, cols: int, max_q: int, max_kv: int, ordered: bool = False) -> StepInputs:
         st = self.staging
@@ -223,6 +225,8 @@ class ModelExecutor:
         s = StepInputs(input_ids=st.view("input_ids", T), positions=st.view("positions", T), slot_mapping=st.view("slot_mapping", T),
                        cu_seqlens=st.view("cu_seqlens", B + 1), past_lens=st.view("past_lens", B), block_table=table,
                        logits_rows=st.view("logits_rows", B), max_q_len=max_q, max_kv_len=max_kv)
+        if self.state_slots_of is not None and self._graph_state_slots:
+            s.state_slots = st.view("state_slots", B)
         if self.windowed:
             s.slot_mapping_w = st.view("slot_mapping_w", T)
             s.block_table_w = st.view("block_table_w").view(st.max_batch, st.table_cols)[:B, :cols]
@@ -299,6 +303,12 @@ class ModelExecutor:
             if self.windowed:
                 o, _ = st.layout["slot_mapping_w"]
                 h[o + T:o + bb] = -1
+        if self.state_slots_of is not None:
+            # recurrent models: the requests' state slots travel with the other inputs (padded rows feed no token and touch no state)
+            o, _ = st.layout["state_slots"]
+            hn = st.host_np()
+            hn[o:o + B] = self.state_slots_of(plan, host=True)
+            hn[o + B:o + bb] = 0
         if self.order_attention:
             # requests by cached length, longest first: the order in which the attention kernel issues its CTAs
             hn = st.host_np()
@@ -310,7 +320,12 @@ class ModelExecutor:
 
     def _capture(self, bb: int, cb: int):
         st = self.staging
+        self._graph_state_slots = True
         s = self._step_inputs(bb, bb, st.table_cols, 1, cb * self.kv.block_size, ordered=self.order_attention)
+        self._graph_state_slots = False
+        # the warm-up runs really execute the step: appending keys and values again is harmless, advancing a recurrent state is
+        # not, so the states are copied aside and put back before the first replay
+        saved = self.kv.state.clone() if (self.state_slots_of is not None and self.kv.state is not None) else None
         tp = self.decoder.tp
         if tp.size > 1:
             tp.barrier()   # ranks enter warm-up and capture together (peer waits in the fused kernels are bounded)
@@ -320,6 +335,9 @@ class ModelExecutor:
             for _ in range(2):  # warm-up: tensor maps, attribute set-up, allocator
                 self.decoder.forward(s, self.kv)
         torch.cuda.current_stream().wait_stream(stream)
+        if saved is not None:
+            self.kv.state.copy_(saved)
+            del saved
         torch.cuda.synchronize()
         from ..ops import _lib
         before = _lib.LAUNCH_COUNT
@@ -525,7 +543,6 @@ class Engine:
             self.kv.ensure_state_slots(o.max_batch_size)
             self._free_slots = list(range(o.max_batch_size - 1, -1, -1))
             self.executor.state_slots_of = self._state_slots_of
-            self.executor.use_graphs = False       # the gate / norm arithmetic around the recurrence runs as tensor ops
         self._guidance: Dict[int, Any] = {}
         self.last_outcome = StepOutcome.NoWork
         self.step_count = 0
@@ -592,7 +609,7 @@ class Engine:
             self._guidance[nat.id] = GuidanceProcessor(self.model, request.params.guidance_type, request.params.guidance_data, 1, False)
             self._guidance[nat.id].commit_prompt(np.asarray(request._pending_tokens, dtype=np.int32).reshape(1, -1))
 
-    def _state_slots_of(self, plan):
+    def _state_slots_of(self, plan, host: bool = False):
         """Slot of every request of the step in the recurrent-state pool; a request gets one when it first runs (its state starts
         from zero because its past length is 0 then) and gives it back when it leaves the engine."""
         out = np.empty(len(plan.entries), dtype=np.int32)
@@ -604,10 +621,12 @@ class Engine:
                     n = self.kv.state_slots
                     self.kv.ensure_state_slots(2 * n)
                     self._free_slots = list(range(2 * n - 1, n - 1, -1))
+                    if hasattr(self.executor, "graphs"):
+                        self.executor.graphs.clear()      # captured steps hold the address of the old pool
                 slot = self._free_slots.pop()
                 self._state_slot[rid] = slot
             out[i] = slot
-        return torch.from_numpy(out).to(self.model.device)
+        return out if host else torch.from_numpy(out).to(self.model.device)
 
     def _release_state_slot(self, rid: int) -> None:
         slot = self._state_slot.pop(rid, None)

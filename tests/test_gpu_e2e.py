@@ -604,25 +604,32 @@ def test_gated_delta_hybrid_model_on_gpu(tmp_path):
             g.generate_next_token()
         outs[name] = (first, g.get_logits().reshape(-1).copy())
         if name == "gpu":
-            eng = og.Engine(model)
-            reqs = []
-            for n in (37, 9):
-                gp = og.GeneratorParams(model)
-                gp.set_search_options(max_length=n + 6, do_sample=False)
-                r = og.Request(gp)
-                r.add_tokens(prompt[0, :n])
-                eng.add_request(r)
-                reqs.append(r)
-            toks = [[] for _ in reqs]
-            for _ in range(100):
-                if not eng.has_pending_requests():
-                    break
-                eng.step()
-                for j, r in enumerate(reqs):
-                    while r.has_unseen_tokens():
-                        toks[j].append(r.get_unseen_token())
-            assert all(len(t) == 6 for t in toks)
-            assert toks[0][0] == int(np.argmax(first))          # the engine's first token of the long request = the generator's
+            runs = []
+            for graphs in (True, False):      # decode steps replayed from CUDA graphs, then the same requests step by step
+                eng = og.Engine(model)
+                eng.executor.use_graphs = graphs
+                reqs = []
+                for n in (37, 9):
+                    gp = og.GeneratorParams(model)
+                    gp.set_search_options(max_length=n + 6, do_sample=False)
+                    r = og.Request(gp)
+                    r.add_tokens(prompt[0, :n])
+                    eng.add_request(r)
+                    reqs.append(r)
+                toks = [[] for _ in reqs]
+                for _ in range(100):
+                    if not eng.has_pending_requests():
+                        break
+                    eng.step()
+                    for j, r in enumerate(reqs):
+                        while r.has_unseen_tokens():
+                            toks[j].append(r.get_unseen_token())
+                assert all(len(t) == 6 for t in toks)
+                assert toks[0][0] == int(np.argmax(first))          # the engine's first token of the long request = the generator's
+                if graphs:
+                    assert eng.executor.graphs, "the decode steps of a recurrent model must run from captured graphs"
+                runs.append(toks)
+            assert runs[0] == runs[1]
     for a_, b_ in zip(outs["cpu"], outs["gpu"]):
         assert np.abs(a_ - b_).max() < 0.08 * a_.std() + 0.05
     # speculation over recurrent states on the GPU (state snapshots + replay of the kept tokens) equals plain greedy decoding

@@ -228,3 +228,36 @@ def test_gpu_generation_matches_the_family_implementation(tmp_path):
         seq.append(int(g.get_next_tokens()[0]))
         if g.is_done():      # the end-of-sequence token: no further logits
             break
+
+
+@pytest.mark.gpu
+def test_gpu_engine_graph_steps_equal_eager_steps(tmp_path):
+    """Three requests of a Mamba-2 hybrid through the engine in bf16: decode steps replayed from CUDA graphs (state slots in the staging
+    buffer, states put back after the capture warm-up) give the tokens of the same run without graphs."""
+    cfg, m = _hf_model(seed=6, hidden=256)
+    out = _export(tmp_path, cfg, m, "eng", "bf16", "cuda")
+    model = og.Model(out)
+    prompts = [list(range(3, 3 + n)) for n in (21, 5, 12)]
+    runs = []
+    for graphs in (True, False):
+        eng = og.Engine(model)
+        eng.executor.use_graphs = graphs
+        reqs = []
+        for pr in prompts:
+            p = og.GeneratorParams(model)
+            p.set_search_options(max_length=len(pr) + 8, min_length=len(pr) + 8)
+            r = og.Request(p)
+            r.add_tokens(np.array(pr, dtype=np.int32))
+            eng.add_request(r)
+            reqs.append(r)
+        got = [[] for _ in prompts]
+        while eng.has_pending_requests():
+            eng.step()
+            for i, r in enumerate(reqs):
+                while r.has_unseen_tokens():
+                    got[i].append(int(r.get_unseen_token()))
+        assert all(len(g_) == 8 for g_ in got)
+        if graphs:
+            assert eng.executor.graphs
+        runs.append(got)
+    assert runs[0] == runs[1]
