@@ -717,16 +717,16 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             # scan with a carried state, gated RMS norm, out_proj
             mb = f"{n}/mamba"
             mp = p + "mamba."
-            I, cd, nh = arch.mamba_intermediate, arch.mamba_conv_dim, arch.mamba_num_heads
+            Im, cd, nh = arch.mamba_intermediate, arch.mamba_conv_dim, arch.mamba_num_heads
             Kc = arch.mamba_conv_kernel
-            put_linear(mp + "in_proj", f"{mb}/in_proj/MatMul", [mp + "in_proj.weight"], x, f"{mb}/in_proj/MatMul/output_0", I + cd + nh, H)
+            put_linear(mp + "in_proj", f"{mb}/in_proj/MatMul", [mp + "in_proj.weight"], x, f"{mb}/in_proj/MatMul/output_0", Im + cd + nh, H)
             put_plain(mp + "conv1d.weight", [mp + "conv1d.weight"], {"shape": (cd, 1, Kc), "op": "id", "fn": lambda ts: ts[0].float().reshape(cd, 1, Kc)})
             put_vec(mp + "conv1d.bias", [mp + "conv1d.bias"])
             put_plain(mp + "dt_bias", [mp + "dt_bias"], {"shape": (nh,), "op": "id", "fn": lambda ts: ts[0].float()}, force_fp32=True)
             put_plain(mp + "neg_exp_A", [mp + "A_log"], {"shape": (nh,), "op": "neg_exp", "fn": lambda ts: -torch.exp(ts[0].float())}, force_fp32=True)
             put_plain(mp + "D", [mp + "D"], {"shape": (nh,), "op": "id", "fn": lambda ts: ts[0].float()}, force_fp32=True)
-            put_plain(mp + "norm.weight", [mp + "norm.weight"], {"shape": (I,), "op": "id", "fn": lambda ts: ts[0].float()})
-            W.node("Split", f"{mb}/Split", [f"{mb}/in_proj/MatMul/output_0"], [f"{mb}/Split/output_{j}" for j in range(3)], axis=-1, split=[I, cd, nh])
+            put_plain(mp + "norm.weight", [mp + "norm.weight"], {"shape": (Im,), "op": "id", "fn": lambda ts: ts[0].float()})
+            W.node("Split", f"{mb}/Split", [f"{mb}/in_proj/MatMul/output_0"], [f"{mb}/Split/output_{j}" for j in range(3)], axis=-1, split=[Im, cd, nh])
             W.node("Transpose", f"{mb}/xbc/Transpose", [f"{mb}/Split/output_1"], [f"{mb}/xbc/Transpose/output_0"], perm=[0, 2, 1])
             W.node("CausalConvWithState", f"{mb}/CausalConvWithState", [f"{mb}/xbc/Transpose/output_0", mp + "conv1d.weight", mp + "conv1d.bias", f"past_key_values.{i}.conv_state"],
                    [f"{mb}/CausalConvWithState/output_0", f"present.{i}.conv_state"], domain="com.microsoft", ndim=1, activation="silu")
@@ -741,7 +741,7 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
             W.node("SimplifiedLayerNormalization", f"{mb}/gated_norm/LayerNorm", [f"{mb}/gated_norm/Mul_2/output_0", mp + "norm.weight"],
                    [f"{mb}/gated_norm/LayerNorm/output_0"], epsilon=float(arch.norm_eps), axis=-1, stash_type=1)
             o_out = f"{mb}/out_proj/MatMul/output_0"
-            put_linear(mp + "out_proj", f"{mb}/out_proj/MatMul", [mp + "out_proj.weight"], f"{mb}/gated_norm/LayerNorm/output_0", o_out, H, I)
+            put_linear(mp + "out_proj", f"{mb}/out_proj/MatMul", [mp + "out_proj.weight"], f"{mb}/gated_norm/LayerNorm/output_0", o_out, H, Im)
         elif arch.is_linear_layer(i):
             # gated-delta-net layer (reference graph: builders/qwen.py:1776-1867): projections, causal depthwise convolution + SiLU
             # with a carried state, per-head L2 norm of q / k, decay / beta gates, LinearAttention (gated delta rule) with a

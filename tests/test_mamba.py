@@ -184,6 +184,24 @@ def test_engine_serves_a_mamba_hybrid(exported):
     assert got == want
 
 
+def test_int4_export_of_the_hybrid(exported, tmp_path):
+    """The int4 exporter quantises every projection of the hybrid (Mamba in / out projections, attention, MLP): the checkpoint loads
+    and follows the fp32 export (a tiny random model: 4-bit rounding is coarse, so the check is the correlation of the logits)."""
+    cfg, m, out32 = exported
+    out4 = _export(tmp_path, cfg, m, "q4", "int4", "cpu")
+    ids = np.random.RandomState(0).randint(1, VOCAB - 1, size=(1, 12)).astype(np.int32)
+    logits = []
+    for d in (out32, out4):
+        model = og.Model(d)
+        p = og.GeneratorParams(model)
+        p.set_search_options(max_length=32)
+        g = og.Generator(model, p)
+        g.append_tokens(ids)
+        logits.append(g.get_logits().reshape(-1).astype(np.float64))
+    assert np.isfinite(logits[1]).all()
+    assert np.corrcoef(logits[0], logits[1])[0, 1] > 0.8
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("heads,groups,P,N", [(8, 2, 16, 16), (24, 1, 64, 128), (4, 4, 64, 256)])
 def test_scan_kernel_matches_reference(heads, groups, P, N):
