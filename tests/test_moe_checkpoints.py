@@ -97,7 +97,17 @@ def _granite_hybrid_moe():
     return cfg, _randomise(transformers.GraniteMoeHybridForCausalLM(cfg)), {}
 
 
-@pytest.mark.parametrize("family", [_mixtral, _mixtral_per_expert, _qwen2_moe, _qwen3_5_moe, _granite_hybrid_moe], ids=lambda f: f.__name__.strip("_"))
+def _granite_moe_shared():
+    if not hasattr(transformers, "GraniteMoeSharedForCausalLM"):
+        pytest.skip("transformers has no GraniteMoeSharedForCausalLM")
+    cfg = transformers.GraniteMoeSharedConfig(**_common(), intermediate_size=32, shared_intermediate_size=40, num_hidden_layers=2, num_local_experts=4,
+                                              num_experts_per_tok=2, embedding_multiplier=2.0, logits_scaling=3.0, residual_multiplier=0.5,
+                                              attention_multiplier=0.25)
+    return cfg, _randomise(transformers.GraniteMoeSharedForCausalLM(cfg)), {}
+
+
+@pytest.mark.parametrize("family", [_mixtral, _mixtral_per_expert, _qwen2_moe, _qwen3_5_moe, _granite_hybrid_moe, _granite_moe_shared],
+                         ids=lambda f: f.__name__.strip("_"))
 def test_moe_checkpoint_matches_the_family_implementation(family, tmp_path):
     from safetensors.torch import save_file
     torch.manual_seed(0)
