@@ -9,8 +9,6 @@
 //     S[:, j] *= exp(g);   mem = sum_i S[i, j] k[i];   delta = (v[j] - mem) * beta;   S[i, j] += k[i] * delta;   o[j] = sum_i S[i, j] q[i]
 // Tokens of a request are walked in order inside the kernel (a decode step is one token, a prompt chunk many); the state is read
 // from / written to the request's slot of the fp32 pool once per launch.  A request whose past length is 0 starts from zero.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.h"
 
@@ -154,11 +152,7 @@ static int LaunchGatedDelta(GdnParams p, int B, void* stream) {
   // the load, update and store phases of different CTAs overlap
   const int Pp = (dv % 32 == 0) ? 32 : (dv + 31) / 32 * 32;
   const int ztiles = (dv % 32 == 0) ? dv / 32 : 1;
-  int npt = dk < 32 ? dk : 32;
-  if (const char* e = getenv("OGB_GDN_ROWS_PER_THREAD")) {      // 16 / 32 / 64 rows of a state column per thread (tuning switch)
-    const int v = atoi(e);
-    if ((v == 16 || v == 32 || v == 64) && v <= dk && dk / v <= 8) npt = v;
-  }
+  int npt = dk < 32 ? dk : 32;      // measured at Qwen3.5 shapes: 32 rows per thread 51 us, 16 rows 63 us, 64 rows 54 us (64 requests)
   if (Pp * (dk / npt) > 512) npt = 64;
   const int splits = dk / npt;
   if (splits > 8 || Pp * splits > 512) return -5;
