@@ -16,7 +16,7 @@ import numpy as np
 LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan", "hunyuandensev1", "hunyuan_v1_dense",
     "internlm2", "llama", "mistral", "nemotron", "olmo", "phi", "phi3", "phimoe", "qwen2", "qwen3",
-    "smollm3", "lfm2", "gpt2", "helium", "exaone", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl", "qwen3_vl",
+    "smollm3", "lfm2", "gpt2", "helium", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl", "qwen3_vl",
     "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoehybrid", "granitemoeshared",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
 
@@ -339,8 +339,10 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.attn_bias = bool(cfg.get("qkv_bias", True))
     if mt in ("phi3small", "phi3_small") or name.startswith("Phi3Small"):
         raise NotImplementedError("phi3small (block-sparse attention, gegelu) is not supported")
-    if mt == "olmo2":
-        raise NotImplementedError("olmo2 (norms after the sub-layers only) is not supported")
+    if mt in ("olmo2", "exaone4"):
+        raise NotImplementedError(f"{mt} (norms after the sub-layers only) is not supported")
+    if mt == "exaone":
+        raise NotImplementedError("exaone (its own tensor names, not mapped here) is not supported")
     if mt in ("qwen3", "gemma3_text"):
         a.qk_norm = True
     if mt == "olmoe":
