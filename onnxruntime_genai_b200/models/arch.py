@@ -15,7 +15,7 @@ import numpy as np
 
 LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan", "hunyuandensev1", "hunyuan_v1_dense",
-    "internlm2", "llama", "mistral", "nemotron", "olmo", "phi", "phi3", "phimoe", "qwen2", "qwen3",
+    "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phimoe", "qwen2", "qwen3",
     "smollm3", "lfm2", "gpt2", "helium", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl", "qwen3_vl",
     "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoehybrid", "granitemoeshared",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
@@ -90,6 +90,7 @@ class ArchConfig:
     parallel_block: bool = False     # phi: attention and MLP both read the input norm; their outputs are summed
     shared_expert_intermediate: int = 0   # MoE layers with an always-on dense gated MLP beside the routed experts (0 = none)
     shared_expert_gated: bool = False     # its output is scaled by sigmoid(x . w) of a one-row projection
+    pre_norm: bool = True            # False (olmo2): the sub-layers read the residual stream itself, their norms follow them (post_sublayer_norms)
     qk_norm_full_width: bool = False # olmoe: q and k are normalised over all their heads at once (weights [q_size] / [kv_size]), before the rotary embedding
     qk_norm_after_rope: bool = False # hunyuan: the per-head q / k norms follow the rotary embedding
     attn_output_gate: bool = False   # q_proj carries a second half per head: sigmoid of it gates the attention output before o_proj
@@ -339,8 +340,12 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.attn_bias = bool(cfg.get("qkv_bias", True))
     if mt in ("phi3small", "phi3_small") or name.startswith("Phi3Small"):
         raise NotImplementedError("phi3small (block-sparse attention, gegelu) is not supported")
-    if mt in ("olmo2", "exaone4"):
-        raise NotImplementedError(f"{mt} (norms after the sub-layers only) is not supported")
+    if mt == "exaone4":
+        raise NotImplementedError("exaone4 is not supported")
+    if mt == "olmo2":
+        a.pre_norm = False
+        a.post_sublayer_norms = True
+        a.qk_norm = a.qk_norm_full_width = True
     if mt == "exaone":
         raise NotImplementedError("exaone (its own tensor names, not mapped here) is not supported")
     if mt in ("qwen3", "gemma3_text"):

@@ -691,7 +691,8 @@ def export_model(arch: ArchConfig, out_dir: str, precision: str = "bf16", execut
         outs = [f"{n}/input_layernorm/output_0"] + ([] if residual is None else ["", "", f"{n}/input_layernorm/output_3"])
         W.node(norm_op if residual is None else skip_op, f"{n}/input_layernorm/{'LayerNorm' if residual is None else 'SkipLayerNorm'}",
                ins, outs, domain="" if residual is None else "com.microsoft", epsilon=float(arch.norm_eps),
-               **({"axis": -1, "stash_type": 1} if residual is None else {}))
+               **({"axis": -1, "stash_type": 1} if residual is None else {}),
+               **({} if arch.pre_norm else {"bypass": 1}))     # bypass: the node only adds (its unit weights are placeholders)
         residual = hidden if residual is None else f"{n}/input_layernorm/output_3"
         x = f"{n}/input_layernorm/output_0"
         if arch.is_conv_layer(i):
@@ -1470,6 +1471,11 @@ def _canonical_family_names(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> No
             parts = (g[:, :r].reshape(arch.q_size, *v.shape[1:]), g[:, r].reshape(arch.kv_size, *v.shape[1:]), g[:, r + 1].reshape(arch.kv_size, *v.shape[1:]))
             for nm, part in zip(("q_proj", "k_proj", "v_proj"), parts):
                 sd[k.replace(".attention.wqkv.", f".self_attn.{nm}.")] = part.contiguous()
+    elif mt == "olmo2":
+        # no norms before the sub-layers: placeholders for the exporter's node chain (the runtime adds without normalising)
+        for i in range(arch.num_layers):
+            sd.setdefault(f"model.layers.{i}.input_layernorm.weight", torch.ones(arch.hidden_size))
+            sd.setdefault(f"model.layers.{i}.pre_feedforward_layernorm.weight", torch.ones(arch.hidden_size))
     elif mt == "olmo":
         H = arch.hidden_size
         for nm in [f"model.layers.{i}.{w}" for i in range(arch.num_layers) for w in ("input_layernorm", "post_attention_layernorm")] + ["model.norm"]:

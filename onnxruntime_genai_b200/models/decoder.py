@@ -270,6 +270,13 @@ class DecoderModel:
             y = apply_lora(y, x, lora)
         return y
 
+    @staticmethod
+    def _plain(h):
+        """A layer output as a tensor (blocks without norms before their sub-layers never defer a mixture-of-experts combine)."""
+        if isinstance(h, ops.PendingCombine):
+            raise RuntimeError("a deferred mixture-of-experts combine needs the residual add + norm that folds it")
+        return h
+
     def _add_norm(self, h, w, b, residual):
         """(norm(h + residual), h + residual); `h` may be the pending output of a mixture-of-experts layer."""
         a = self.arch
@@ -422,7 +429,7 @@ class DecoderModel:
         a = self.arch
         if self.norms_folded:
             return True
-        if (self.device.type != "cuda" or self.dtype != torch.bfloat16 or a.layernorm or a.parallel_block or a.num_experts > 0 or
+        if (self.device.type != "cuda" or self.dtype != torch.bfloat16 or a.layernorm or a.parallel_block or a.num_experts > 0 or not a.pre_norm or
                 not a.mlp_gated or os.environ.get("OGB_FOLD_NORMS", "1") == "0"):
             return False
         for lw in self.layers:
@@ -605,7 +612,10 @@ class DecoderModel:
         if self.cos_small is not None and s.max_kv_len <= self.rope_original_context:
             cos, sin = self.cos_small, self.sin_small      # the whole step lies within the original context length
         for li, lw in enumerate(self.layers):
-            if residual is None:
+            if not a.pre_norm:
+                # blocks whose sub-layers read the residual stream itself (their norms follow the sub-layers)
+                x = residual = h if residual is None else self._plain(h) + residual
+            elif residual is None:
                 x, _ = ops.norm(h, lw.ln1_w, a.norm_eps, None, lw.ln1_b, a.layernorm)
                 residual = h
             else:
@@ -671,9 +681,12 @@ class DecoderModel:
                 h, _ = ops.norm(h, lw.post_attn_norm_w, a.norm_eps)
             if a.residual_multiplier != 1.0:
                 h = (h.float() * a.residual_multiplier).to(h.dtype)
-            x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
+            if a.pre_norm:
+                x, residual = ops.norm(h, lw.ln2_w, a.norm_eps, residual, lw.ln2_b, a.layernorm)
+            else:
+                x = residual = h + residual
             # ---- MLP (a mixture-of-experts layer may leave its combine step to the residual add + norm that follows)
-            h = self._mlp(lw, x, defer=lw.post_ffn_norm_w is None and a.residual_multiplier == 1.0)
+            h = self._mlp(lw, x, defer=lw.post_ffn_norm_w is None and a.residual_multiplier == 1.0 and a.pre_norm)
             if lw.post_ffn_norm_w is not None:
                 h, _ = ops.norm(h, lw.post_ffn_norm_w, a.norm_eps)
             if a.residual_multiplier != 1.0:

@@ -104,6 +104,7 @@ def arch_from_checkpoint(cfg, g: GraphView, decoder: Optional[dict] = None) -> A
     if first_norm is not None:
         a.norm_eps = float(_attr(first_norm, "epsilon", 1e-5))
         a.layernorm = "Simplified" not in first_norm.op_type
+        a.pre_norm = not bool(int(_attr(first_norm, "bypass", 0) or 0))
     # the first layer that attends (hybrid models may start with convolution layers)
     fa = next((i for i in range(L) if g.find(f"/model/layers.{i}/attn/", ops=["GroupQueryAttention", "PagedAttention"]) is not None), 0)
     fa = f"/model/layers.{fa}"
