@@ -15,7 +15,7 @@ import numpy as np
 
 LLM_TYPES = [
     "chatglm", "decoder", "ernie4_5", "gemma", "gemma2", "gemma3_text", "gptoss", "gpt_oss", "granite", "hunyuan", "hunyuandensev1", "hunyuan_v1_dense",
-    "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "phi", "phi3", "phimoe", "qwen2", "qwen3",
+    "internlm2", "llama", "mistral", "nemotron", "olmo", "olmo2", "exaone4", "phi", "phi3", "phimoe", "qwen2", "qwen3",
     "smollm3", "lfm2", "gpt2", "helium", "mixtral", "qwen2_moe", "qwen3_moe", "granitemoe", "olmoe", "qwen2_vl", "qwen2_5_vl", "qwen3_vl",
     "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "granitemoehybrid", "granitemoeshared",      # hybrids of gated-delta-net (linear attention) and full-attention layers
 ]
@@ -341,7 +341,15 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
     if mt in ("phi3small", "phi3_small") or name.startswith("Phi3Small"):
         raise NotImplementedError("phi3small (block-sparse attention, gegelu) is not supported")
     if mt == "exaone4":
-        raise NotImplementedError("exaone4 is not supported")
+        # norms after the sub-layers, per-head q / k norms; with a sliding window the layers alternate and the global ones do not rotate
+        a.pre_norm = False
+        a.post_sublayer_norms = True
+        a.qk_norm = True
+        if cfg.get("sliding_window"):
+            lt = cfg.get("layer_types") or []
+            a.sliding_window = int(cfg["sliding_window"])
+            a.sliding_layers = [i for i, t in enumerate(lt) if t == "sliding_attention"]
+            a.no_rope_layers = [i for i, t in enumerate(lt) if t != "sliding_attention"]
     if mt == "olmo2":
         a.pre_norm = False
         a.post_sublayer_norms = True

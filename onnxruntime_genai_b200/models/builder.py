@@ -1471,7 +1471,7 @@ def _canonical_family_names(sd: Dict[str, torch.Tensor], arch: ArchConfig) -> No
             parts = (g[:, :r].reshape(arch.q_size, *v.shape[1:]), g[:, r].reshape(arch.kv_size, *v.shape[1:]), g[:, r + 1].reshape(arch.kv_size, *v.shape[1:]))
             for nm, part in zip(("q_proj", "k_proj", "v_proj"), parts):
                 sd[k.replace(".attention.wqkv.", f".self_attn.{nm}.")] = part.contiguous()
-    elif mt == "olmo2":
+    elif mt in ("olmo2", "exaone4"):
         # no norms before the sub-layers: placeholders for the exporter's node chain (the runtime adds without normalising)
         for i in range(arch.num_layers):
             sd.setdefault(f"model.layers.{i}.input_layernorm.weight", torch.ones(arch.hidden_size))

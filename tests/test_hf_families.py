@@ -31,6 +31,8 @@ FAMILIES = {
     "granite": ("GraniteConfig", "GraniteForCausalLM", dict(embedding_multiplier=3.0, logits_scaling=2.0, residual_multiplier=0.4, attention_multiplier=0.2)),
     "olmo": ("OlmoConfig", "OlmoForCausalLM", dict(clip_qkv=None)),
     "olmo2": ("Olmo2Config", "Olmo2ForCausalLM", dict()),
+    "exaone4": ("Exaone4Config", "Exaone4ForCausalLM", dict(num_hidden_layers=4, sliding_window=6, sliding_window_pattern=2, head_dim=16)),
+    "exaone4_global": ("Exaone4Config", "Exaone4ForCausalLM", dict(sliding_window=None, sliding_window_pattern=4, layer_types=["full_attention"] * 3, head_dim=16)),
     "smollm3": ("SmolLM3Config", "SmolLM3ForCausalLM", dict(no_rope_layers=[1, 0, 1], use_sliding_window=False)),
     "nemotron": ("NemotronConfig", "NemotronForCausalLM", dict(partial_rotary_factor=0.5, head_dim=16)),
     "ernie4_5": ("Ernie4_5Config", "Ernie4_5ForCausalLM", dict(head_dim=16, use_bias=False)),
@@ -186,7 +188,7 @@ def test_chatglm_layout(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("family", ["gemma3_text", "smollm3", "nemotron", "hunyuan_v1_dense", "olmoe", "olmo2", "ernie4_5", "lfm2", "gpt2"])
+@pytest.mark.parametrize("family", ["gemma3_text", "smollm3", "nemotron", "hunyuan_v1_dense", "olmoe", "olmo2", "exaone4", "ernie4_5", "lfm2", "gpt2"])
 def test_checkpoint_on_the_gpu(family, tmp_path):
     """The same checkpoints in bf16 on the CUDA path (per-layer rotary caches in the fused decode step, the squared-ReLU kernel, the
     q / k norm variants), against the fp32 logits of the family's implementation."""
