@@ -340,6 +340,8 @@ def from_hf_config(cfg: Dict[str, Any]) -> ArchConfig:
         a.attn_bias = bool(cfg.get("qkv_bias", True))
     if mt in ("phi3small", "phi3_small") or name.startswith("Phi3Small"):
         raise NotImplementedError("phi3small (block-sparse attention, gegelu) is not supported")
+    if mt in ("phi4_multimodal", "phi4mm"):
+        a.model_type = "phi3"         # the text decoder of Phi-4-multimodal is a phi3 decoder with a partial rotary embedding
     if mt == "exaone4":
         # norms after the sub-layers, per-head q / k norms; with a sliding window the layers alternate and the global ones do not rotate
         a.pre_norm = False

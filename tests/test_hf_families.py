@@ -296,3 +296,20 @@ def test_qwen3_vl_text_decoder_and_interleaved_positions(tmp_path):
     with torch.no_grad():
         want = m(input_ids=torch.tensor(ids.astype(np.int64)), position_ids=torch.from_numpy(pos)).logits[0, -1].float().numpy()
     np.testing.assert_allclose(g.get_logits().reshape(-1), want, rtol=3e-3, atol=3e-4)
+
+
+def test_phi4_multimodal_text_decoder(tmp_path):
+    """Phi-4-multimodal: create_model exports the text decoder (packed qkv / gate-up projections, three quarters of each head rotated);
+    the image and audio towers' tensors in the checkpoint are ignored.  Text prompts match the family's implementation."""
+    if not hasattr(transformers, "Phi4MultimodalForCausalLM"):
+        pytest.skip("transformers has no Phi4MultimodalForCausalLM")
+    cfg = transformers.Phi4MultimodalConfig(vocab_size=VOCAB, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                            num_key_value_heads=2, max_position_embeddings=128, original_max_position_embeddings=128,
+                                            partial_rotary_factor=0.75, pad_token_id=0, bos_token_id=1, eos_token_id=VOCAB - 1,
+                                            tie_word_embeddings=False)
+    torch.manual_seed(0)
+    m = _randomise(transformers.Phi4MultimodalForCausalLM(cfg))
+    d = cfg.to_dict()
+    d["architectures"] = ["Phi4MultimodalForCausalLM"]
+    model = _generate_and_compare(tmp_path, d, dict(m.state_dict()), m)
+    assert model.type == "phi3" and model.arch.rotary_dim == 12
