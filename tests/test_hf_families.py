@@ -306,7 +306,11 @@ def test_phi4_multimodal_text_decoder(tmp_path):
     cfg = transformers.Phi4MultimodalConfig(vocab_size=VOCAB, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
                                             num_key_value_heads=2, max_position_embeddings=128, original_max_position_embeddings=128,
                                             partial_rotary_factor=0.75, pad_token_id=0, bos_token_id=1, eos_token_id=VOCAB - 1,
-                                            tie_word_embeddings=False)
+                                            tie_word_embeddings=False,
+                                            vision_config=dict(hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=2,
+                                                               image_size=28, patch_size=14, crop_size=28),
+                                            audio_config=dict(hidden_size=32, intermediate_size=48, num_blocks=1, num_attention_heads=2, input_size=16,
+                                                              nemo_conv_channels=32, depthwise_separable_out_channel=16))
     torch.manual_seed(0)
     m = _randomise(transformers.Phi4MultimodalForCausalLM(cfg))
     d = cfg.to_dict()
